@@ -1,0 +1,210 @@
+"""Step timing and memory tracking.
+
+``step_perf`` brackets one training step; ``.mark(name)`` closes a phase
+(``clip`` / ``noise`` / ``optimizer``).  On CUDA every mark records a CUDA event
+on the current stream and the durations are read *on the device* when the
+context exits (one synchronise per step, none per mark); on CPU it falls back
+to ``perf_counter``.  ``PerfState`` folds steps (the first ``warmup_steps`` are
+excluded from throughput), ``PerfTracker`` keeps one state per stage, and
+``sync(PerfState)`` reduces across ranks as time = max, samples = sum,
+peak memory = max.
+
+Parity: packages/opaque-engine/src/opaque/api/engine/profiling/_memory.py:374-436, :689;
+_distributed.py.
+"""
+from __future__ import annotations
+
+import contextlib
+import dataclasses
+import time
+from typing import Any
+
+import torch
+
+
+@dataclasses.dataclass(frozen=True)
+class MemoryStats:
+    allocated_bytes: int = 0
+    reserved_bytes: int = 0
+    peak_allocated_bytes: int = 0
+    peak_reserved_bytes: int = 0
+
+    @property
+    def peak_gb(self) -> float:
+        return self.peak_allocated_bytes / 2 ** 30
+
+
+def _is_cuda(device: Any) -> bool:
+    return torch.device(device).type == "cuda" and torch.cuda.is_available()
+
+
+def get_memory_stats(device: Any = None) -> MemoryStats:
+    if device is None or not _is_cuda(device):
+        return MemoryStats()
+    return MemoryStats(torch.cuda.memory_allocated(device), torch.cuda.memory_reserved(device),
+                       torch.cuda.max_memory_allocated(device), torch.cuda.max_memory_reserved(device))
+
+
+def reset_peak_memory(device: Any = None) -> None:
+    if device is not None and _is_cuda(device):
+        torch.cuda.reset_peak_memory_stats(device)
+
+
+def empty_cache(device: Any = None) -> None:
+    if device is not None and _is_cuda(device):
+        torch.cuda.empty_cache()
+
+
+def print_memory(device: Any = None, prefix: str = "") -> None:
+    s = get_memory_stats(device)
+    print(f"{prefix}allocated={s.allocated_bytes / 2**30:.2f}GiB reserved={s.reserved_bytes / 2**30:.2f}GiB "
+          f"peak={s.peak_allocated_bytes / 2**30:.2f}GiB")
+
+
+@dataclasses.dataclass(frozen=True)
+class StepPerf:
+    """One step: total seconds, per-phase seconds, samples, peak memory."""
+    seconds: float
+    phases: dict[str, float]
+    batch_size: int
+    peak_memory_bytes: int = 0
+    device_timed: bool = False
+
+
+class _StepTimer:
+    def __init__(self, device: Any, batch_size: int, track_memory: bool):
+        self.device = torch.device(device) if device is not None else torch.device("cpu")
+        self.batch_size = batch_size
+        self.track_memory = track_memory
+        self.cuda = _is_cuda(self.device)
+        self._marks: list[tuple[str, Any]] = []
+        self.result: StepPerf | None = None
+
+    def _stamp(self):
+        if self.cuda:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream(self.device))
+            return ev
+        return time.perf_counter()
+
+    def start(self):
+        if self.cuda and self.track_memory:
+            torch.cuda.reset_peak_memory_stats(self.device)
+        self._t0 = self._stamp()
+
+    def mark(self, name: str) -> None:
+        self._marks.append((name, self._stamp()))
+
+    def finish(self):
+        end = self._stamp()
+        phases: dict[str, float] = {}
+        if self.cuda:
+            end.synchronize()
+            prev = self._t0
+            for name, ev in self._marks:
+                phases[name] = phases.get(name, 0.0) + prev.elapsed_time(ev) / 1e3
+                prev = ev
+            total = self._t0.elapsed_time(end) / 1e3
+            peak = torch.cuda.max_memory_allocated(self.device) if self.track_memory else 0
+        else:
+            prev = self._t0
+            for name, t in self._marks:
+                phases[name] = phases.get(name, 0.0) + (t - prev)
+                prev = t
+            total = end - self._t0
+            peak = 0
+        self.result = StepPerf(total, phases, self.batch_size, peak, self.cuda)
+
+
+@contextlib.contextmanager
+def step_perf(device: Any = None, *, batch_size: int = 0, track_memory: bool = True):
+    """Time one step; read ``.result`` (a :class:`StepPerf`) after the block."""
+    timer = _StepTimer(device, batch_size, track_memory)
+    timer.start()
+    try:
+        yield timer
+    finally:
+        timer.finish()
+
+
+@dataclasses.dataclass(frozen=True)
+class PerfState:
+    """Running totals over steps; warm-up steps count toward ``steps`` only."""
+    steps: int = 0
+    timed_steps: int = 0
+    seconds: float = 0.0
+    samples: int = 0
+    peak_memory_bytes: int = 0
+    phases: dict[str, float] = dataclasses.field(default_factory=dict)
+    warmup_steps: int = 1
+
+    def add(self, step: StepPerf) -> "PerfState":
+        peak = max(self.peak_memory_bytes, step.peak_memory_bytes)
+        if self.steps < self.warmup_steps:
+            return dataclasses.replace(self, steps=self.steps + 1, peak_memory_bytes=peak)
+        phases = dict(self.phases)
+        for k, v in step.phases.items():
+            phases[k] = phases.get(k, 0.0) + v
+        return dataclasses.replace(self, steps=self.steps + 1, timed_steps=self.timed_steps + 1,
+                                   seconds=self.seconds + step.seconds,
+                                   samples=self.samples + step.batch_size,
+                                   peak_memory_bytes=peak, phases=phases)
+
+    @property
+    def samples_per_second(self) -> float:
+        return self.samples / self.seconds if self.seconds > 0 else 0.0
+
+    @property
+    def seconds_per_step(self) -> float:
+        return self.seconds / self.timed_steps if self.timed_steps else 0.0
+
+
+PerfStage = str
+
+
+class PerfTracker:
+    """One :class:`PerfState` per stage (``train`` / ``eval`` / ``test``)."""
+
+    def __init__(self, device: Any = None, warmup_steps: int = 1):
+        self.device = device
+        self.warmup_steps = warmup_steps
+        self.stages: dict[str, PerfState] = {}
+
+    def step(self, stage: str = "train", *, batch_size: int = 0, track_memory: bool = True):
+        tracker = self
+
+        @contextlib.contextmanager
+        def ctx():
+            with step_perf(tracker.device, batch_size=batch_size, track_memory=track_memory) as t:
+                yield t
+            state = tracker.stages.get(stage, PerfState(warmup_steps=tracker.warmup_steps))
+            tracker.stages[stage] = state.add(t.result)
+        return ctx()
+
+    def state(self, stage: str = "train") -> PerfState:
+        return self.stages.get(stage, PerfState(warmup_steps=self.warmup_steps))
+
+    def summary(self) -> dict[str, dict[str, float]]:
+        return {k: {"samples_per_second": s.samples_per_second, "seconds_per_step": s.seconds_per_step,
+                    "peak_memory_gb": s.peak_memory_bytes / 2 ** 30, "steps": s.steps}
+                for k, s in self.stages.items()}
+
+
+def perf_tracker(device: Any = None, warmup_steps: int = 1) -> PerfTracker:
+    return PerfTracker(device, warmup_steps)
+
+
+def sync_perf_state(state: PerfState) -> PerfState:
+    """Cross-rank fold: seconds = max, samples = sum, peak = max."""
+    from ..distributed import is_distributed, reduce_scalar
+    if not is_distributed():
+        return state
+    phases = {k: reduce_scalar(v, "max") for k, v in sorted(state.phases.items())}
+    return dataclasses.replace(
+        state, seconds=reduce_scalar(state.seconds, "max"), samples=int(reduce_scalar(state.samples, "sum")),
+        peak_memory_bytes=int(reduce_scalar(state.peak_memory_bytes, "max")), phases=phases)
+
+
+__all__ = ["MemoryStats", "PerfStage", "PerfState", "PerfTracker", "StepPerf", "empty_cache",
+           "get_memory_stats", "perf_tracker", "print_memory", "reset_peak_memory", "step_perf",
+           "sync_perf_state"]

@@ -1,0 +1,217 @@
+"""Python front-ends of the sm_100a kernels, each with a plain-PyTorch reference.
+
+Every ``*_ref`` function is the fp32 PyTorch statement of the same operation; it is the
+numerics oracle in the tests and the implementation used on CPU.  The CUDA entry points fail
+loudly when the kernel library cannot be loaded on a GPU machine — there is no silent
+fallback on device tensors.
+
+Kernel inventory (reference counterparts: packages/opaque-patches/src/opaque/api/patches/kernels/*,
+packages/opaque-engine/src/opaque/api/engine/clipping/_pytree.py:475-564,
+packages/opaque-dpsgd/src/opaque/api/dpsgd/noise/_gaussian.py:235-278,
+packages/opaque-optimizers/src/opaque/api/optimizers/_adam.py:120-270):
+  wgrad_clip            clip-weighted weight-gradient GEMM with (peer) reduce epilogue   [tcgen05]
+  ghost_norm            per-example gradient norms of linear / embedding layers          [tcgen05]
+  rms_norm / fused add  forward, dX, per-example dW
+  glu                   SwiGLU / GeGLU forward and backward
+  rope_qk               joint rotary embedding of Q and K (GQA, position ids)
+  cross_entropy         online-softmax NLL with in-place dlogits (softcap, scale, smoothing)
+  philox_normal_add_    counter-based Gaussian noise
+  rows_sumsq / clip_weighted_sum / embedding_wgrad   direct-norm path for small parameters
+  shard_step            noise (iid | BLT | banded) + AdamW-BC + bf16 write-back to every rank
+"""
+from __future__ import annotations
+
+import math
+from typing import Sequence
+
+import torch
+
+from . import lib
+from .lib import DeviceWaitTimeout, KernelLibraryError, StatusWord
+
+DEFAULT_WAIT_BUDGET_S = 2.0
+
+
+def _c(t: torch.Tensor) -> torch.Tensor:
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _need_bf16(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t.dtype != torch.bfloat16:
+            raise TypeError(f"expected bf16 tensors, got {t.dtype}")
+
+
+# =============================================================================== wgrad / ghost
+
+def pick_block_n(n: int) -> int:
+    if n > 128:
+        return 256
+    return 128 if n > 64 else 64
+
+
+def pick_splits(work_tiles: int, rows: int, sms: int) -> int:
+    """K-splits so that (tiles x splits) fills the SMs while each split keeps >= 8 k-blocks."""
+    if work_tiles >= sms:
+        return 1
+    want = max(1, sms // max(work_tiles, 1))
+    cap = max(1, rows // (64 * 8))
+    return max(1, min(want, cap))
+
+
+def wgrad_clip(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, row_scale: torch.Tensor | None = None,
+               seg_offsets: torch.Tensor | None = None, num_groups: int = 1, splits: int | None = None,
+               out_offset: int = 0, ldm: int | None = None, ldn: int = 1, n_valid: int = 0, accumulate: bool = True,
+               group_stride: int = 0, group_out_offset: torch.Tensor | None = None,
+               peer_table: torch.Tensor | None = None, shard_elems: int = 0, block_n: int | None = None,
+               status: StatusWord | None = None, wait_budget_s: float = DEFAULT_WAIT_BUDGET_S) -> None:
+    """``flat[out_offset + g_off + m*ldm + n*ldn] (+)= Σ_t s[t]·a[t, m]·b[t, n]`` over each segment.
+
+    ``a`` is ``[T, M]`` (scaled operand, e.g. output gradients), ``b`` is ``[T, N]`` (layer inputs),
+    both bf16 with 16-byte aligned rows.  ``out`` is the flat fp32 destination, or ``None`` with a
+    ``peer_table`` (int64 device tensor of per-rank shard base pointers) and ``shard_elems``.
+    """
+    _need_bf16(a, b)
+    T, M = a.shape
+    N = b.shape[1]
+    if b.shape[0] != T:
+        raise ValueError("a and b must have the same number of rows")
+    if a.stride(1) != 1 or b.stride(1) != 1:
+        raise ValueError("operands must be row-major")
+    if ldm is None:
+        ldm = N
+    bn = block_n or pick_block_n(min(N, n_valid) if n_valid else N)
+    sms = lib.sm_count()
+    if splits is None:
+        tiles = num_groups * math.ceil(M / 128) * math.ceil(N / bn)
+        splits = pick_splits(tiles, T // max(num_groups, 1), sms) if accumulate else 1
+    if not accumulate and splits != 1:
+        raise ValueError("store mode cannot split K")
+    rc = lib.load().ob_wgrad_clip(
+        a.data_ptr(), b.data_ptr(), T, M, N, a.stride(0), b.stride(0), lib.ptr(row_scale), lib.ptr(seg_offsets),
+        num_groups, splits, lib.ptr(out), lib.ptr(peer_table), shard_elems, lib.ptr(group_out_offset), group_stride,
+        out_offset, ldm, ldn, n_valid, int(accumulate), bn, status.ptr() if status else None, wait_budget_s, sms,
+        lib.stream())
+    lib.check(rc, "wgrad_clip")
+
+
+def wgrad_clip_ref(a, b, *, row_scale=None, seg_offsets=None, num_groups=1):
+    """fp32 oracle: returns ``[num_groups, M, N]``."""
+    af, bf = a.float(), b.float()
+    if row_scale is not None:
+        af = af * row_scale.float()[:, None]
+    if seg_offsets is None:
+        return (af.t() @ bf)[None]
+    offs = seg_offsets.tolist()
+    return torch.stack([af[offs[g]:offs[g + 1]].t() @ bf[offs[g]:offs[g + 1]] for g in range(num_groups)])
+
+
+def ghost_norm(a: torch.Tensor | None, g: torch.Tensor, norm2: torch.Tensor, tokens_per_example: int, *,
+               ids: torch.Tensor | None = None, status: StatusWord | None = None,
+               wait_budget_s: float = DEFAULT_WAIT_BUDGET_S) -> None:
+    """``norm2[i] += ‖A_iᵀ G_i‖_F²`` for every example (rows of example i are contiguous).
+
+    With ``ids`` (int32 ``[B*T]``) the inputs are one-hot rows (embedding layer) and ``a`` is unused.
+    """
+    _need_bf16(g)
+    rows, dg = g.shape
+    B = rows // tokens_per_example
+    if B * tokens_per_example != rows:
+        raise ValueError("rows must be a multiple of tokens_per_example")
+    if ids is None:
+        _need_bf16(a)
+        da, lda, ap = a.shape[1], a.stride(0), a.data_ptr()
+    else:
+        if ids.dtype != torch.int32:
+            raise TypeError("ids must be int32")
+        da, lda, ap = 0, 0, None
+    rc = lib.load().ob_ghost_norm(ap, g.data_ptr(), lib.ptr(ids), B, tokens_per_example, da, dg, lda, g.stride(0),
+                                  norm2.data_ptr(), status.ptr() if status else None, wait_budget_s, lib.sm_count(),
+                                  lib.stream())
+    lib.check(rc, "ghost_norm")
+
+
+def ghost_norm_ref(a, g, tokens_per_example, *, ids=None):
+    B = g.shape[0] // tokens_per_example
+    gg = g.float().view(B, tokens_per_example, -1)
+    sg = gg @ gg.transpose(1, 2)
+    if ids is None:
+        aa = a.float().view(B, tokens_per_example, -1)
+        sa = aa @ aa.transpose(1, 2)
+    else:
+        i = ids.view(B, tokens_per_example)
+        sa = (i[:, :, None] == i[:, None, :]).float()
+    return (sa * sg).sum(dim=(1, 2))
+
+
+# =============================================================================== small DP kernels
+
+def philox_normal_add_(x: torch.Tensor, *, seed: int, offset: int = 0, std: float = 1.0, stream_id: int = 0) -> torch.Tensor:
+    """In place ``x[i] += std·z(seed, offset + i)`` with ``z`` standard normal, counter-based."""
+    if not x.is_contiguous():
+        raise ValueError("philox_normal_add_ needs a contiguous tensor")
+    code = {torch.float32: 0, torch.bfloat16: 1}[x.dtype]
+    rc = lib.load().ob_philox_normal_add(x.data_ptr(), code, x.numel(), seed & (2**64 - 1), offset, float(std),
+                                         stream_id, lib.sm_count(), lib.stream())
+    lib.check(rc, "philox_normal_add")
+    return x
+
+
+def rows_sumsq(g: torch.Tensor, norm2: torch.Tensor) -> None:
+    """``norm2[e] += Σ_p g[e, p]²`` for fp32 ``g [E, P]``."""
+    rc = lib.load().ob_rows_sumsq(g.data_ptr(), g.shape[0], g.shape[1], g.stride(0), norm2.data_ptr(), lib.sm_count(),
+                                  lib.stream())
+    lib.check(rc, "rows_sumsq")
+
+
+def clip_weighted_sum(g: torch.Tensor, c: torch.Tensor, out: torch.Tensor | None, *, flat_offset: int = 0,
+                      peer_table: torch.Tensor | None = None, shard_elems: int = 0) -> None:
+    """``flat[flat_offset + p] += Σ_e c[e]·g[e, p]`` (to the owning rank when a peer table is given)."""
+    rc = lib.load().ob_clip_weighted_sum(g.data_ptr(), c.data_ptr(), g.shape[0], g.shape[1], g.stride(0),
+                                         lib.ptr(out), lib.ptr(peer_table), shard_elems, flat_offset, lib.sm_count(),
+                                         lib.stream())
+    lib.check(rc, "clip_weighted_sum")
+
+
+def embedding_wgrad(g: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None, *, row_scale=None, flat_offset=0,
+                    peer_table=None, shard_elems=0) -> None:
+    """``flat[flat_offset + ids[t]·D + d] += s[t]·g[t, d]``."""
+    _need_bf16(g)
+    if ids.dtype != torch.int64:
+        raise TypeError("ids must be int64")
+    rc = lib.load().ob_embedding_wgrad(g.data_ptr(), ids.data_ptr(), lib.ptr(row_scale), g.shape[0], g.shape[1],
+                                       g.stride(0), lib.ptr(out), lib.ptr(peer_table), shard_elems, flat_offset,
+                                       lib.sm_count(), lib.stream())
+    lib.check(rc, "embedding_wgrad")
+
+
+def shard_step(*, grad, master, m, v, params_local=None, peer_params=None, world=1, global_offset=0, seed=0,
+               noise_std=0.0, inv_normalize=1.0, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, step=1,
+               phi_hat=0.0, decoupled_wd=True, ftrl_state=None, ftrl_mode=0, ftrl_coef: Sequence[float] = (),
+               nbuf=0, ring_head=0, noisy_out=None, skip_update=False) -> None:
+    """One fused pass over a shard: noise, AdamW(-BC) on fp32 masters, bf16 write-back to all ranks.
+
+    ``step`` is 1-based; ``phi_hat`` is the bias-corrected noise-variance EMA (0 disables the correction).
+    """
+    coef = torch.tensor(list(ftrl_coef) or [0.0], dtype=torch.float32)
+    import ctypes
+    arr = (ctypes.c_float * len(coef))(*coef.tolist())
+    rc = lib.load().ob_shard_step(
+        grad.data_ptr(), lib.ptr(master), lib.ptr(m), lib.ptr(v), lib.ptr(ftrl_state), lib.ptr(peer_params),
+        lib.ptr(params_local), lib.ptr(noisy_out), grad.numel(), global_offset, world, seed & (2**64 - 1),
+        float(noise_std), float(inv_normalize), ftrl_mode, nbuf, ring_head, ctypes.cast(arr, ctypes.c_void_p),
+        len(coef), float(lr), float(betas[0]), float(betas[1]), float(eps), float(weight_decay),
+        1.0 - betas[0] ** step, 1.0 - betas[1] ** step, float(phi_hat), int(decoupled_wd), int(skip_update),
+        lib.sm_count(), lib.stream())
+    lib.check(rc, "shard_step")
+
+
+from .functional import (cross_entropy, cross_entropy_ref, fused_add_rms_norm, geglu, glu_ref, rms_norm,  # noqa: E402
+                         rms_norm_ref, rope_qk, rope_qk_ref, rope_tables, swiglu)
+
+__all__ = [
+    "DeviceWaitTimeout", "KernelLibraryError", "StatusWord", "clip_weighted_sum", "cross_entropy",
+    "cross_entropy_ref", "embedding_wgrad", "fused_add_rms_norm", "geglu", "ghost_norm", "ghost_norm_ref", "glu_ref",
+    "philox_normal_add_", "pick_block_n", "pick_splits", "rms_norm", "rms_norm_ref", "rope_qk", "rope_qk_ref",
+    "rope_tables", "rows_sumsq", "shard_step", "swiglu", "wgrad_clip", "wgrad_clip_ref",
+]

@@ -1,0 +1,19 @@
+// C entry points of libopaque_b200.so (every function returns 0 on success, a negative
+// code on a host-side failure; device-side wait timeouts are reported through `status`).
+#pragma once
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int ob_wgrad_clip(const void* a, const void* b, int T, int M, int N, long long lda, long long ldb,
+                  const float* row_scale, const int* seg_offsets, int num_groups, int splits, float* out,
+                  float* const* peer_out, long long shard_elems, const long long* group_out_offset,
+                  long long group_stride, long long out_offset, long long ldm, long long ldn, int n_valid,
+                  int accumulate, int block_n, int* status, double wait_budget_s, int num_sms, void* stream);
+
+int ob_ghost_norm(const void* a, const void* g, const int* ids, int B, int T, int Da, int Dg, long long lda,
+                  long long ldg, float* norm2, int* status, double wait_budget_s, int num_sms, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

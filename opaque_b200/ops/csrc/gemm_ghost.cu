@@ -1,0 +1,260 @@
+// Ghost per-example gradient norms of a linear layer on sm_100a.
+//
+// For example i with token rows A_i [T, Da] (layer inputs) and G_i [T, Dg] (output
+// gradients) the weight gradient is A_i^T G_i and its squared Frobenius norm equals
+//     sum over (t, t') of (A_i A_i^T)[t, t'] * (G_i G_i^T)[t, t'],
+// so it can be computed without ever forming the [Da, Dg] per-example gradient.  One work
+// item is (example, 128 x 128 tile of the T x T Gram matrices, upper triangle only): the two
+// Gram tiles are accumulated side by side in TMEM by tcgen05.mma (K-major operands, 128-byte
+// swizzle, TMA-fed), and the epilogue multiplies them element-wise, masks rows / columns that
+// fall outside the example, doubles off-diagonal tiles and adds the tile's sum to norm2[i].
+//
+// With `ids` given (embedding layers) the first Gram matrix is replaced by the indicator
+// [ids_t == ids_t'], which is the Gram matrix of one-hot rows.
+//
+// Roles: warp 0 TMA producer, warp 1 MMA issuer / TMEM owner, warps 2-5 epilogue; persistent
+// CTAs, double-buffered accumulators, bounded waits (see common.cuh).
+#include "common.cuh"
+#include "api.h"
+
+namespace ob {
+
+int make_bf16_map_2d(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld,
+                     int box_cols, int box_rows);
+
+constexpr int GH_TILE = 128;
+constexpr int GH_BLOCK_K = 64;
+constexpr int GH_STAGES = 6;
+constexpr int GH_TILE_BYTES = GH_TILE * GH_BLOCK_K * 2;    // 16 KB
+constexpr int GH_STAGE_BYTES = 2 * GH_TILE_BYTES;
+constexpr int GH_THREADS = 192;
+constexpr int GH_SMEM = GH_STAGES * GH_STAGE_BYTES + 256 + 1024;
+
+struct GhostParams {
+  int B, T, Da, Dg;
+  const int* ids;        // [B*T] or nullptr
+  float* norm2;          // [B], accumulated with atomics
+  int* status;
+  unsigned long long wait_budget_ns;
+};
+
+struct GhostItem {
+  int ex, tb, tb2;
+};
+
+__device__ __forceinline__ GhostItem ghost_decode(int w, int pairs, int nt) {
+  GhostItem it;
+  it.ex = w / pairs;
+  int r = w % pairs;
+  int tb = 0;
+  while (r >= nt - tb) {
+    r -= nt - tb;
+    ++tb;
+  }
+  it.tb = tb;
+  it.tb2 = tb + r;
+  return it;
+}
+
+__global__ void __launch_bounds__(GH_THREADS, 1)
+ghost_norm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_g,
+                  const GhostParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GH_STAGES * GH_STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + GH_STAGES;
+  uint64_t* tmem_full = bars + 2 * GH_STAGES;
+  uint64_t* tmem_empty = bars + 2 * GH_STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * GH_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nt = (p.T + GH_TILE - 1) / GH_TILE;
+  const int pairs = nt * (nt + 1) / 2;
+  const int total_work = p.B * pairs;
+  const int ka = p.ids ? 0 : (p.Da + GH_BLOCK_K - 1) / GH_BLOCK_K;
+  const int kg = (p.Dg + GH_BLOCK_K - 1) / GH_BLOCK_K;
+  const int num_kb = ka + kg;
+  const uint64_t budget = p.wait_budget_ns;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GH_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_g);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, issued_mask = 0, issued_phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        const GhostItem it = ghost_decode(w, pairs, nt);
+        const int r1 = it.ex * p.T + it.tb * GH_TILE, r2 = it.ex * p.T + it.tb2 * GH_TILE;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_EMPTY, budget)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full[stage], GH_STAGE_BYTES);
+          uint8_t* dst = smem + stage * GH_STAGE_BYTES;
+          const CUtensorMap* map = kb < ka ? &map_a : &map_g;
+          const int col = (kb < ka ? kb : kb - ka) * GH_BLOCK_K;
+          tma_load_2d(dst, map, &full[stage], col, r1);
+          tma_load_2d(dst + GH_TILE_BYTES, map, &full[stage], col, r2);
+          issued_mask |= 1u << stage;
+          issued_phase = (issued_phase & ~(1u << stage)) | (phase << stage);
+          if (++stage == GH_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        for (int s = 0; s < GH_STAGES; ++s)
+          if (issued_mask & (1u << s)) {
+            int dummy_abort = 0;
+            mbar_wait(&full[s], (issued_phase >> s) & 1u, &dummy_abort, p.status, OB_ERR_DRAIN, budget);
+          }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(GH_TILE, GH_TILE, 0, 0);
+      int stage = 0, acc_iter = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        const int as = acc_iter & 1;
+        if (!mbar_wait(&tmem_empty[as], ((acc_iter >> 1) & 1) ^ 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_EMPTY,
+                       budget)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, p.status, OB_ERR_WAIT_FULL, budget)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t t1 = smem_u32(smem + stage * GH_STAGE_BYTES), t2 = t1 + GH_TILE_BYTES;
+          const uint32_t d_tmem = tmem_base + as * 256 + (kb < ka ? 0 : 128);
+          const bool first = (kb == 0) || (kb == ka);
+#pragma unroll
+          for (int kk = 0; kk < GH_BLOCK_K / 16; ++kk) {
+            // K-major, 128-byte swizzle: rows are 128 B apart, 8-row groups 1024 B apart; a k-step
+            // of 16 elements moves the start address by 32 B inside the swizzled row.
+            const uint64_t ad = make_smem_desc(t1 + kk * 32, 16, 1024, 2);
+            const uint64_t bd = make_smem_desc(t2 + kk * 32, 16, 1024, 2);
+            umma_bf16(d_tmem, ad, bd, idesc, (first && kk == 0) ? 0u : 1u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == GH_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tmem_full[as]);
+        ++acc_iter;
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int acc_iter = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+      const GhostItem it = ghost_decode(w, pairs, nt);
+      const int as = acc_iter & 1;
+      if (!mbar_wait(&tmem_full[as], (acc_iter >> 1) & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL, budget)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int t = it.tb * GH_TILE + q * 32 + lane;
+      const int my_id = (p.ids && t < p.T) ? p.ids[it.ex * p.T + t] : -1;
+      float acc = 0.f;
+      for (int c = 0; c < GH_TILE / 32; ++c) {
+        float sg[32], sa[32];
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * 256 + c * 32;
+        tmem_ld32(taddr + 128, sg);
+        if (!p.ids) tmem_ld32(taddr, sa);
+        tmem_ld_wait();
+        const int tc0 = it.tb2 * GH_TILE + c * 32;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int t2 = tc0 + j;
+          float a;
+          if (p.ids) {
+            const int other = (t2 < p.T) ? __ldg(p.ids + it.ex * p.T + t2) : -2;
+            a = (other == my_id) ? 1.f : 0.f;
+          } else {
+            a = sa[j];
+          }
+          if (t < p.T && t2 < p.T) acc += a * sg[j];
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[as]);
+      ++acc_iter;
+      acc = warp_sum(acc);
+      if (lane == 0) atomicAdd(p.norm2 + it.ex, (it.tb == it.tb2 ? 1.f : 2.f) * acc);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace ob
+
+extern "C" int ob_ghost_norm(const void* a, const void* g, const int* ids, int B, int T, int Da, int Dg,
+                             long long lda, long long ldg, float* norm2, int* status, double wait_budget_s,
+                             int num_sms, void* stream) {
+  using namespace ob;
+  if (B <= 0 || T <= 0 || Dg <= 0) return 0;
+  CUtensorMap ma, mg;
+  int rc = make_bf16_map_2d(&mg, g, static_cast<long long>(B) * T, Dg, ldg, GH_BLOCK_K, GH_TILE);
+  if (rc) return rc;
+  if (ids == nullptr) {
+    rc = make_bf16_map_2d(&ma, a, static_cast<long long>(B) * T, Da, lda, GH_BLOCK_K, GH_TILE);
+    if (rc) return rc;
+  } else {
+    ma = mg;
+  }
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(ghost_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GH_SMEM) != cudaSuccess)
+      return -20;
+    configured = true;
+  }
+  GhostParams p;
+  p.B = B; p.T = T; p.Da = Da; p.Dg = Dg;
+  p.ids = ids;
+  p.norm2 = norm2;
+  p.status = status;
+  p.wait_budget_ns = static_cast<unsigned long long>(wait_budget_s * 1e9);
+  const int nt = (T + GH_TILE - 1) / GH_TILE;
+  const long long total = static_cast<long long>(B) * (nt * (nt + 1) / 2);
+  const int grid = static_cast<int>(total < num_sms ? total : num_sms);
+  ghost_norm_kernel<<<grid, GH_THREADS, GH_SMEM, static_cast<cudaStream_t>(stream)>>>(ma, mg, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}

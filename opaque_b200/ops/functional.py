@@ -1,0 +1,302 @@
+"""Differentiable wrappers (``torch.autograd.Function``) of the transformer kernels.
+
+On CUDA bf16 tensors the sm_100a kernels run; on CPU (or other dtypes) the plain PyTorch
+reference of the same formula runs, so models built on these ops work everywhere and the
+references double as test oracles.
+
+Parity (signatures / semantics): packages/opaque-patches/src/opaque/api/patches/kernels/
+rms_norm.py:630, fused_add_rms_norm.py:524, swiglu.py, geglu.py, rope_embedding.py:754-770,
+cross_entropy.py:585-681.
+"""
+from __future__ import annotations
+
+import torch
+from torch.autograd import Function
+
+from . import lib
+
+_MODES = {"llama": 0, "gemma": 1, "none": 1}
+
+
+def _use_kernel(*ts: torch.Tensor) -> bool:
+    return all(t.is_cuda and t.dtype == torch.bfloat16 for t in ts)
+
+
+def _param_grad_hook():
+    """The fused DP engine's capture callback for small per-example parameter gradients, if active."""
+    from ..engine import fused
+    return fused.current_capture()
+
+
+# =============================================================================== RMSNorm
+
+def rms_norm_ref(x, weight, eps=1e-6, offset=0.0, casting_mode="llama", residual=None):
+    """fp32 statement of (fused-add) RMSNorm; returns ``y`` or ``(y, s)``."""
+    s = x if residual is None else (x.float() + residual.float()).to(x.dtype)
+    sf = s.float()
+    rstd = torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + eps)
+    n = sf * rstd
+    if casting_mode == "llama":
+        n = n.to(x.dtype).float()
+    y = (n * (offset + weight.float())).to(x.dtype)
+    return y if residual is None else (y, s)
+
+
+class _RMSNorm(Function):
+    @staticmethod
+    def forward(ctx, x, residual, weight, eps, offset, mode, layer):
+        shape = x.shape
+        H = shape[-1]
+        x2 = x.reshape(-1, H)
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        r2 = None
+        if residual is not None:
+            r2 = residual.reshape(-1, H)
+            r2 = r2 if r2.is_contiguous() else r2.contiguous()
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        s = torch.empty_like(x2) if r2 is not None else None
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rc = lib.load().ob_rmsnorm_fwd(x2.data_ptr(), lib.ptr(r2), weight.data_ptr(), y.data_ptr(), lib.ptr(s),
+                                       rstd.data_ptr(), rows, H, eps, offset, mode, lib.stream())
+        lib.check(rc, "rmsnorm_fwd")
+        ctx.save_for_backward(s if s is not None else x2, weight, rstd)
+        ctx.meta = (shape, offset, layer, residual is not None)
+        if s is not None:
+            return y.view(shape), s.view(shape)
+        return y.view(shape), None
+
+    @staticmethod
+    def backward(ctx, dy, ds):
+        xs, weight, rstd = ctx.saved_tensors
+        shape, offset, layer, fused_add = ctx.meta
+        H = shape[-1]
+        dy2 = dy.reshape(-1, H)
+        dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
+        ds2 = None
+        if ds is not None:
+            ds2 = ds.reshape(-1, H)
+            ds2 = ds2 if ds2.is_contiguous() else ds2.contiguous()
+        rows = xs.shape[0]
+        dx = torch.empty_like(xs)
+        cap = _param_grad_hook() if weight.requires_grad else None
+        dw_pe, dw = None, None
+        n_ex, rows_per = 0, 0
+        if cap is not None:
+            n_ex, rows_per = cap.batch_size, rows // cap.batch_size
+            dw_pe = torch.empty(n_ex, H, dtype=torch.float32, device=xs.device)
+        elif weight.requires_grad:
+            n_ex, rows_per = 1, rows
+            dw_pe = torch.empty(1, H, dtype=torch.float32, device=xs.device)
+        rc = lib.load().ob_rmsnorm_bwd(dy2.data_ptr(), xs.data_ptr(), weight.data_ptr(), rstd.data_ptr(),
+                                       lib.ptr(ds2), dx.data_ptr(), lib.ptr(dw_pe), None, n_ex, rows_per, rows, H,
+                                       offset, lib.stream())
+        lib.check(rc, "rmsnorm_bwd")
+        if cap is not None:
+            cap.add_per_example_grad(layer, "weight", dw_pe)
+        elif dw_pe is not None:
+            dw = dw_pe[0].to(weight.dtype)
+        dxv = dx.view(shape)
+        return dxv, (dxv if fused_add else None), dw, None, None, None, None
+
+
+def rms_norm(x, weight, eps=1e-6, offset=0.0, casting_mode="llama", *, layer=None):
+    """``y = x·rsqrt(mean(x²)+eps)·(offset + w)``."""
+    if _use_kernel(x, weight) and x.shape[-1] % 8 == 0:
+        return _RMSNorm.apply(x, None, weight, eps, offset, _MODES[casting_mode], layer)[0]
+    return rms_norm_ref(x, weight, eps, offset, casting_mode)
+
+
+def fused_add_rms_norm(x, residual, weight, eps=1e-6, offset=0.0, casting_mode="llama", *, layer=None):
+    """``s = x + residual; y = rmsnorm(s)``; returns ``(y, s)``."""
+    if _use_kernel(x, residual, weight) and x.shape[-1] % 8 == 0:
+        return _RMSNorm.apply(x, residual, weight, eps, offset, _MODES[casting_mode], layer)
+    return rms_norm_ref(x, weight, eps, offset, casting_mode, residual=residual)
+
+
+# =============================================================================== gated activations
+
+ACTIVATION_SWIGLU, ACTIVATION_GEGLU_EXACT, ACTIVATION_GEGLU_APPROX = 0, 1, 2
+
+
+def glu_ref(gate, up, act=0):
+    g = gate.float()
+    if act == 0:
+        a = torch.nn.functional.silu(g)
+    elif act == 1:
+        a = torch.nn.functional.gelu(g)
+    else:
+        a = torch.nn.functional.gelu(g, approximate="tanh")
+    return (a * up.float()).to(gate.dtype)
+
+
+class _GLU(Function):
+    @staticmethod
+    def forward(ctx, gate, up, act):
+        I = gate.shape[-1]
+        g2, u2 = gate.reshape(-1, I), up.reshape(-1, I)
+        if g2.stride(1) != 1 or u2.stride(1) != 1 or g2.stride(0) != u2.stride(0):
+            g2, u2 = g2.contiguous(), u2.contiguous()
+        out = torch.empty(g2.shape, dtype=gate.dtype, device=gate.device)
+        rc = lib.load().ob_glu_fwd(g2.data_ptr(), u2.data_ptr(), out.data_ptr(), g2.shape[0], I, g2.stride(0), act,
+                                   lib.sm_count(), lib.stream())
+        lib.check(rc, "glu_fwd")
+        ctx.save_for_backward(g2, u2)
+        ctx.meta = (gate.shape, act)
+        return out.view(gate.shape)
+
+    @staticmethod
+    def backward(ctx, dh):
+        g2, u2 = ctx.saved_tensors
+        shape, act = ctx.meta
+        I = shape[-1]
+        d2 = dh.reshape(-1, I)
+        d2 = d2 if d2.is_contiguous() else d2.contiguous()
+        both = torch.empty(g2.shape[0], 2 * I, dtype=g2.dtype, device=g2.device)
+        dg, du = both[:, :I], both[:, I:]
+        rc = lib.load().ob_glu_bwd(d2.data_ptr(), g2.data_ptr(), u2.data_ptr(), dg.data_ptr(), du.data_ptr(),
+                                   g2.shape[0], I, g2.stride(0), 2 * I, act, lib.sm_count(), lib.stream())
+        lib.check(rc, "glu_bwd")
+        return dg.view(shape), du.view(shape), None
+
+
+def swiglu(gate, up):
+    """``silu(gate)·up``."""
+    if _use_kernel(gate, up) and gate.shape[-1] % 8 == 0:
+        return _GLU.apply(gate, up, ACTIVATION_SWIGLU)
+    return glu_ref(gate, up, 0)
+
+
+def geglu(gate, up, approximate=False):
+    act = ACTIVATION_GEGLU_APPROX if approximate else ACTIVATION_GEGLU_EXACT
+    if _use_kernel(gate, up) and gate.shape[-1] % 8 == 0:
+        return _GLU.apply(gate, up, act)
+    return glu_ref(gate, up, act)
+
+
+# =============================================================================== RoPE
+
+def rope_tables(head_dim: int, max_pos: int, theta: float = 10000.0, device=None):
+    """fp32 ``cos, sin`` tables of shape ``[max_pos, head_dim/2]``."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+    ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None, :]
+    return ang.cos().contiguous(), ang.sin().contiguous()
+
+
+def rope_qk_ref(q, k, cos, sin, pos=None, sign=1.0):
+    """Rotate-half RoPE; ``q: [..., T, Hq, D]``, ``k: [..., T, Hk, D]``; ``pos`` indexes the tables."""
+    T = q.shape[-3]
+    if pos is None:
+        c, s = cos[:T], sin[:T]
+        c, s = c[:, None, :], s[:, None, :]
+    else:
+        c, s = cos[pos][..., None, :], sin[pos][..., None, :]
+    s = s * sign
+
+    def rot(x):
+        half = x.shape[-1] // 2
+        lo, hi = x[..., :half].float(), x[..., half:].float()
+        return torch.cat([lo * c - hi * s, hi * c + lo * s], dim=-1).to(x.dtype)
+    return rot(q), rot(k)
+
+
+class _RoPE(Function):
+    @staticmethod
+    def forward(ctx, q, k, cos, sin, pos):
+        ctx.save_for_backward(cos, sin, pos if pos is not None else torch.empty(0))
+        ctx.has_pos = pos is not None
+        q, k = q.contiguous().clone(), k.contiguous().clone()
+        _RoPE._run(q, k, cos, sin, pos, 0)
+        return q, k
+
+    @staticmethod
+    def _run(q, k, cos, sin, pos, backward):
+        T, Hq, D = q.shape[-3], q.shape[-2], q.shape[-1]
+        Hk = k.shape[-2]
+        rows = q.numel() // (Hq * D)
+        p32 = None
+        if pos is not None:
+            p32 = pos.reshape(-1).to(torch.int32)
+        rc = lib.load().ob_rope_qk(q.data_ptr(), k.data_ptr(), cos.data_ptr(), sin.data_ptr(), lib.ptr(p32), rows, T,
+                                   Hq, Hk, D, Hq * D, Hk * D, backward, lib.sm_count(), lib.stream())
+        lib.check(rc, "rope_qk")
+
+    @staticmethod
+    def backward(ctx, dq, dk):
+        cos, sin, pos = ctx.saved_tensors
+        dq, dk = dq.contiguous().clone(), dk.contiguous().clone()
+        _RoPE._run(dq, dk, cos, sin, pos if ctx.has_pos else None, 1)
+        return dq, dk, None, None, None
+
+
+def rope_qk(q, k, cos, sin, pos=None):
+    """Joint rotary embedding of Q ``[B, T, Hq, D]`` and K ``[B, T, Hk, D]``."""
+    if _use_kernel(q, k) and q.shape[-1] % 4 == 0 and cos.dtype == torch.float32:
+        return _RoPE.apply(q, k, cos, sin, pos)
+    return rope_qk_ref(q, k, cos, sin, pos)
+
+
+# =============================================================================== cross-entropy
+
+def cross_entropy_ref(logits, labels, *, ignore_index=-100, logit_softcapping=0.0, logit_scaling=0.0,
+                      label_smoothing=0.0):
+    """Per-row NLL (0 for ignored rows) in fp32."""
+    z = logits.float()
+    if logit_scaling:
+        z = z * logit_scaling
+    if logit_softcapping:
+        z = logit_softcapping * torch.tanh(z / logit_softcapping)
+    lse = torch.logsumexp(z, dim=-1)
+    valid = (labels != ignore_index) & (labels >= 0) & (labels < z.shape[-1])
+    safe = labels.clamp(0, z.shape[-1] - 1)
+    picked = z.gather(-1, safe[..., None]).squeeze(-1)
+    nll = lse - picked
+    if label_smoothing:
+        nll = (1 - label_smoothing) * nll + label_smoothing * (lse - z.mean(-1))
+    return torch.where(valid, nll, torch.zeros_like(nll))
+
+
+def cross_entropy_fused_(logits, labels, row_weight=None, *, ignore_index=-100, logit_softcapping=0.0,
+                         logit_scaling=0.0, label_smoothing=0.0, write_grad=True):
+    """Kernel entry: returns per-row NLL; with ``write_grad`` OVERWRITES ``logits`` by ``w_row·∂nll/∂logits``."""
+    V = logits.shape[-1]
+    z = logits.view(-1, V)
+    if z.stride(1) != 1:
+        raise ValueError("logits rows must be contiguous")
+    rows = z.shape[0]
+    lab = labels.reshape(-1).to(torch.int64).contiguous()
+    nll = torch.empty(rows, dtype=torch.float32, device=z.device)
+    rc = lib.load().ob_cross_entropy(z.data_ptr(), int(z.dtype == torch.float32), lab.data_ptr(), lib.ptr(row_weight),
+                                     nll.data_ptr(), None, rows, V, z.stride(0), logit_scaling or 1.0,
+                                     logit_softcapping, label_smoothing, ignore_index, int(write_grad), lib.stream())
+    lib.check(rc, "cross_entropy")
+    return nll.view(labels.shape)
+
+
+class _CrossEntropy(Function):
+    @staticmethod
+    def forward(ctx, logits, labels, ignore_index, softcap, scale, smoothing):
+        buf = logits.contiguous().clone()
+        nll = cross_entropy_fused_(buf, labels, None, ignore_index=ignore_index, logit_softcapping=softcap,
+                                   logit_scaling=scale, label_smoothing=smoothing, write_grad=True)
+        ctx.save_for_backward(buf)
+        return nll
+
+    @staticmethod
+    def backward(ctx, dnll):
+        (buf,) = ctx.saved_tensors
+        return buf * dnll.reshape(buf.shape[:-1] + (1,)).to(buf.dtype), None, None, None, None, None
+
+
+def cross_entropy(logits, labels, *, ignore_index=-100, logit_softcapping=0.0, logit_scaling=0.0,
+                  label_smoothing=0.0):
+    """Per-token NLL (unreduced) with softcap / scaling / label smoothing; ignored tokens give 0."""
+    if logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32):
+        return _CrossEntropy.apply(logits, labels, ignore_index, logit_softcapping, logit_scaling, label_smoothing)
+    return cross_entropy_ref(logits, labels, ignore_index=ignore_index, logit_softcapping=logit_softcapping,
+                             logit_scaling=logit_scaling, label_smoothing=label_smoothing)
+
+
+def selective_log_softmax(logits, indices):
+    """``log_softmax(logits)[indices]`` without materialising the softmax (``= −nll``)."""
+    return -cross_entropy(logits, indices, ignore_index=-(2 ** 62))

@@ -1,0 +1,99 @@
+"""In-tree native builds: the sm_100a kernel library (nvcc) and the C++ accountant (g++/pybind11).
+
+Artefacts are written next to their sources so they travel with a snapshot of the tree.  A
+build is skipped when the artefact is newer than every source; ``force=True`` rebuilds.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent.parent
+CSRC = PKG / "ops" / "csrc"
+KERNEL_LIB = PKG / "ops" / "libopaque_b200.so"
+ACC_SRC = PKG / "accounting" / "csrc"
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "--use_fast_math", "-Xcompiler", "-fPIC", "-shared"]
+
+
+def _find(tool: str, extra: list[str]) -> str | None:
+    hit = shutil.which(tool)
+    if hit:
+        return hit
+    for p in extra:
+        if os.path.exists(p):
+            return p
+    return None
+
+
+def _stale(target: Path, sources: list[Path]) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(s.stat().st_mtime > t for s in sources)
+
+
+def build_kernels(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every ``.cu`` under ``ops/csrc`` into one shared library for sm_100a."""
+    sources = sorted(CSRC.glob("*.cu"))
+    deps = sources + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
+    if not force and not _stale(KERNEL_LIB, deps):
+        return KERNEL_LIB
+    nvcc = _find("nvcc", ["/usr/local/cuda/bin/nvcc"])
+    if nvcc is None:
+        raise RuntimeError("nvcc not found: cannot build the sm_100a kernel library")
+    tmp = KERNEL_LIB.with_suffix(".so.tmp")
+    cmd = [nvcc, *NVCC_FLAGS, "-o", str(tmp), *map(str, sources)]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    os.replace(tmp, KERNEL_LIB)
+    if verbose:
+        print(res.stderr)
+    return KERNEL_LIB
+
+
+def accounting_ext_path() -> Path:
+    suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+    return PKG / "accounting" / ("_native" + suffix)
+
+
+def build_accounting(force: bool = False) -> Path:
+    """Compile the C++17 PLD accountant into a pybind11 extension module."""
+    import pybind11
+    target = accounting_ext_path()
+    sources = sorted(ACC_SRC.glob("*.cpp"))
+    deps = sources + sorted(ACC_SRC.glob("*.hpp"))
+    if not sources:
+        raise RuntimeError("accounting sources missing")
+    if not force and not _stale(target, deps):
+        return target
+    gxx = _find("g++", ["/usr/bin/g++"])
+    if gxx is None:
+        raise RuntimeError("g++ not found: cannot build the accountant")
+    tmp = target.with_suffix(".tmp")
+    cmd = [gxx, "-O3", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-pthread", "-fopenmp",
+           f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}",
+           "-o", str(tmp), *map(str, sources)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
+    os.replace(tmp, target)
+    return target
+
+
+def build_all(force: bool = False) -> None:
+    build_kernels(force)
+    build_accounting(force)
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv)
+    print("built:", KERNEL_LIB, accounting_ext_path())

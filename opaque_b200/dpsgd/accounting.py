@@ -1,0 +1,139 @@
+"""DP-SGD accounting front-ends: Gaussian mechanism, AdaClip transformation and sampling amplifications.
+
+``poisson(gaussian(σ), q) * steps`` is the standard DP-SGD accountant.  Amplifications wrap a
+``Gaussian`` (or ``AdaClip`` of a Gaussian) and lower to the matching native subsampled-Gaussian PLD.
+
+Parity: packages/opaque-dpsgd/src/opaque/api/accounting/dpsgd/{mechanisms,amplification}/*.py.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+from ..accounting.core import DpProcess, native
+
+
+@dataclasses.dataclass(frozen=True)
+class Gaussian(DpProcess):
+    noise_multiplier: float
+
+    def __post_init__(self):
+        if not self.noise_multiplier > 0:
+            raise ValueError(f"noise_multiplier must be > 0, got {self.noise_multiplier}")
+
+    @property
+    def effective_noise_multiplier(self) -> float:
+        return self.noise_multiplier
+
+    def _build_pld(self, config):
+        return native.gaussian_pld(self.noise_multiplier, config.to_native())
+
+
+@dataclasses.dataclass(frozen=True)
+class AdaClip(DpProcess):
+    """Gaussian step that also releases the noisy clipped-fraction of adaptive clipping.
+
+    The pair is equivalent to one Gaussian with ``z_eff = (1/z² + K/(4σ_b²))^{-1/2}``,
+    ``σ_b = expected_batch_size · fraction_noise_std`` and K groups.
+    """
+    inner: Gaussian
+    fraction_noise_std: float
+    expected_batch_size: float
+    num_groups: int = 1
+
+    @property
+    def effective_noise_multiplier(self) -> float:
+        return native.adaclip_effective_noise_multiplier(self.inner.noise_multiplier, self.fraction_noise_std,
+                                                         self.expected_batch_size, self.num_groups)
+
+    def _build_pld(self, config):
+        return native.gaussian_pld(self.effective_noise_multiplier, config.to_native())
+
+
+def _nm(inner: DpProcess) -> float:
+    nm = getattr(inner, "effective_noise_multiplier", None)
+    if nm is None:
+        raise TypeError(f"amplification needs a Gaussian-type inner mechanism, got {type(inner).__name__}")
+    return float(nm)
+
+
+@dataclasses.dataclass(frozen=True)
+class Poisson(DpProcess):
+    inner: DpProcess
+    sample_rate: float
+    truncated_batch_size: int | None = None
+    dataset_size: int | None = None
+
+    def __post_init__(self):
+        _nm(self.inner)
+        if not 0 < self.sample_rate <= 1:
+            raise ValueError(f"sample_rate must be in (0, 1], got {self.sample_rate}")
+        if (self.truncated_batch_size is None) != (self.dataset_size is None):
+            raise ValueError("truncated_batch_size and dataset_size must be given together")
+
+    def _build_pld(self, config):
+        if self.truncated_batch_size is not None:
+            return native.truncated_poisson_gaussian_pld(_nm(self.inner), self.sample_rate, self.truncated_batch_size,
+                                                         self.dataset_size, config.to_native())
+        return native.poisson_gaussian_pld(_nm(self.inner), self.sample_rate, config.to_native())
+
+
+@dataclasses.dataclass(frozen=True)
+class ParallelPoisson(DpProcess):
+    """W workers each Poisson-sample the SAME global dataset; a record can be hit by several of them."""
+    inner: DpProcess
+    sample_rate: float
+    num_workers: int
+
+    def __post_init__(self):
+        _nm(self.inner)
+        if not 0 < self.sample_rate < 1 or self.num_workers < 1:
+            raise ValueError("need sample_rate in (0, 1) and num_workers >= 1")
+
+    def _build_pld(self, config):
+        return native.parallel_poisson_gaussian_pld(_nm(self.inner), self.sample_rate, self.num_workers, config.to_native())
+
+
+@dataclasses.dataclass(frozen=True)
+class RandomAllocation(DpProcess):
+    """One epoch of ``num_bins`` steps in which each record takes part in exactly ``k`` of them."""
+    inner: DpProcess
+    num_bins: int
+    k: int = 1
+
+    def __post_init__(self):
+        _nm(self.inner)
+        if not 1 <= self.k <= self.num_bins:
+            raise ValueError("need 1 <= k <= num_bins")
+
+    def _build_pld(self, config):
+        return native.random_allocation_gaussian_pld(_nm(self.inner), self.num_bins, self.k, config.to_native())
+
+
+def gaussian(noise_multiplier: float) -> Gaussian:
+    return Gaussian(float(noise_multiplier))
+
+
+def adaclip(inner: Gaussian, *, fraction_noise_std: float, expected_batch_size: float, num_groups: int = 1) -> AdaClip:
+    return AdaClip(inner, float(fraction_noise_std), float(expected_batch_size), int(num_groups))
+
+
+def poisson(inner: DpProcess, sample_rate: float, *, truncated_batch_size: int | None = None,
+            dataset_size: int | None = None) -> Poisson:
+    return Poisson(inner, float(sample_rate), truncated_batch_size, dataset_size)
+
+
+def parallel_poisson(inner: DpProcess, sample_rate: float, num_workers: int) -> ParallelPoisson:
+    return ParallelPoisson(inner, float(sample_rate), int(num_workers))
+
+
+def random_allocation(inner: DpProcess, num_bins: int) -> RandomAllocation:
+    """Whole-epoch process: do NOT multiply by the steps of the epoch, multiply by the number of epochs."""
+    return RandomAllocation(inner, int(num_bins), 1)
+
+
+def k_out_of_t(inner: DpProcess, k: int, t: int) -> RandomAllocation:
+    return RandomAllocation(inner, int(t), int(k))
+
+
+__all__ = ["AdaClip", "Gaussian", "ParallelPoisson", "Poisson", "RandomAllocation", "adaclip", "gaussian", "k_out_of_t",
+           "parallel_poisson", "poisson", "random_allocation"]

@@ -1,6 +1,364 @@
-"""Placeholder replaced below by the fused engine."""
-_ACTIVE = None
+"""Fused explicit-batch DP engine (book-keeping ghost clipping) for B200.
+
+One forward / backward per microbatch over an ordinary batched model.  Layers with trainable
+parameters are DP-aware autograd functions: their backward computes the input gradient as usual
+and, instead of a weight gradient, hands the layer input ``A`` and the output gradient ``G`` to
+the active :class:`Capture`:
+
+  * **ghost parameters** (large matrices, embeddings): the tcgen05 ghost-norm kernel adds
+    ``‖A_iᵀG_i‖²`` of every example to the microbatch's norm accumulator and ``(A, G)`` are kept
+    until the end of the backward pass;
+  * **direct parameters** (LoRA factors, biases, norm weights): the per-example gradient is small,
+    so it is materialised into one ``[mb, P_direct]`` fp32 buffer (LoRA through the grouped
+    tcgen05 weight-gradient kernel, one segment per example).
+
+When backward finishes every example's total squared norm is known: ``c_i = min(1, C/‖g_i‖)``
+(guarded), one kernel reduces ``Σ_i c_i·g_i`` of the direct buffer into the sharded gradient and
+one clip-weighted tcgen05 GEMM per ghost layer reduces ``Aᵀ·diag(c)·G`` there too — through peer
+pointers when there are several ranks, so these launches ARE the reduce-scatter.  After the last
+microbatch :class:`~opaque_b200.parallel.ShardedDPOptimizer` adds noise once per coordinate and
+applies AdamW-BC on each owner's shard.
+
+Sensitivity.  ``c_i`` is shrunk by ``2⁻⁸ + 2⁻¹²`` relative before use: the GEMM applies it after a
+round-toward-zero to bf16 and the scaled operand is rounded to nearest bf16 (≤ 2⁻⁹ relative), and
+the ghost norm carries fp32 accumulation error; the stored contribution of one record therefore
+stays within ``C``.  A parameter used twice in one pass (tied embedding / output head) is bounded by
+``(‖g_a‖ + ‖g_b‖)²`` — an upper bound on its true squared norm, so clipping stays valid
+(slightly conservative).
+
+The reference has no counterpart: it materialises per-example gradients with
+``vmap(grad)`` (packages/opaque-engine/src/opaque/api/engine/clipping/_clipped_fun.py:207-350) and
+all-reduces the sum per leaf (distributed/gradients.py:183-193).
+"""
+from __future__ import annotations
+
+import contextlib
+import dataclasses
+import math
+from collections.abc import Callable
+from typing import Any
+
+import torch
+from torch.autograd import Function
+
+from .. import ops
+from ..parallel.peer import PeerGroup
+from ..parallel.sharded import DPStepConfig, FlatSpace, ShardedDPOptimizer
+from ..random import RngKey
+
+_ACTIVE: "Capture | None" = None
+CLIP_GUARD = 1.0 - 2.0 ** -8 - 2.0 ** -12
+LORA_PAD = 64
 
 
-def current_capture():
+def current_capture() -> "Capture | None":
     return _ACTIVE
+
+
+@contextlib.contextmanager
+def activate(cap: "Capture"):
+    global _ACTIVE
+    prev, _ACTIVE = _ACTIVE, cap
+    try:
+        yield cap
+    finally:
+        _ACTIVE = prev
+
+
+class Capture:
+    """Per-microbatch collector of norms and deferred weight-gradient work."""
+
+    MAX_GHOST = 1024
+
+    def __init__(self, engine: "FusedDPEngine", batch_size: int, tokens_per_example: int):
+        self.engine = engine
+        self.batch_size = batch_size
+        self.tokens = tokens_per_example
+        dev = engine.device
+        sp = engine.space
+        self.pe = engine.pe_buffer(batch_size)
+        self.parts = torch.zeros(self.MAX_GHOST, batch_size, dtype=torch.float32, device=dev)
+        self.part_slots: list[str] = []
+        self.records: list[tuple] = []
+        self.seg = torch.arange(0, (batch_size + 1) * tokens_per_example, tokens_per_example, dtype=torch.int32,
+                                device=dev)
+        self.status = engine.status
+        self.direct_elems = sp.direct_elems
+
+    # ---- called from layer backward passes --------------------------------------------------
+    def _part(self, slot_name: str) -> torch.Tensor:
+        i = len(self.part_slots)
+        if i >= self.MAX_GHOST:
+            raise RuntimeError("too many ghost captures in one backward pass")
+        self.part_slots.append(slot_name)
+        return self.parts[i]
+
+    def add_linear(self, weight: torch.nn.Parameter, x2d: torch.Tensor, g2d: torch.Tensor) -> None:
+        slot = self.engine.slot_of(weight)
+        ops.ghost_norm(x2d, g2d, self._part(slot.name), self.tokens, status=self.status)
+        self.records.append(("linear", slot, g2d, x2d))
+
+    def add_embedding(self, weight: torch.nn.Parameter, ids: torch.Tensor, g2d: torch.Tensor) -> None:
+        slot = self.engine.slot_of(weight)
+        ops.ghost_norm(None, g2d, self._part(slot.name), self.tokens, ids=ids.reshape(-1).to(torch.int32),
+                       status=self.status)
+        self.records.append(("embedding", slot, g2d, ids.reshape(-1).to(torch.int64)))
+
+    def pe_view(self, param: torch.nn.Parameter) -> torch.Tensor:
+        """``[mb, numel]`` window of the per-example buffer that belongs to ``param``."""
+        slot = self.engine.slot_of(param)
+        if not slot.direct:
+            raise RuntimeError(f"{slot.name} is not a direct parameter")
+        return self.pe[:, slot.offset:slot.offset + slot.numel]
+
+    def add_per_example_grad(self, layer: Any, pname: str, grad: torch.Tensor) -> None:
+        param = getattr(layer, pname)
+        self.pe_view(param).add_(grad.reshape(self.batch_size, -1))
+
+    def add_lora(self, lora_a: torch.nn.Parameter, lora_b: torch.nn.Parameter, x2d: torch.Tensor,
+                 xa_pad: torch.Tensor, g2d: torch.Tensor, q_pad: torch.Tensor) -> None:
+        """Per-example ``dA_i = q_iᵀ x_i`` (``[r, in]``) and ``dB_i = g_iᵀ (s·xa)_i`` (``[out, r]``)."""
+        sa, sb = self.engine.slot_of(lora_a), self.engine.slot_of(lora_b)
+        r, d_in = lora_a.shape
+        stride = self.pe.stride(0)
+        ops.wgrad_clip(x2d, q_pad, self.pe, seg_offsets=self.seg, num_groups=self.batch_size, out_offset=sa.offset,
+                       ldm=1, ldn=d_in, n_valid=r, accumulate=False, group_stride=stride, block_n=64,
+                       status=self.status)
+        ops.wgrad_clip(g2d, xa_pad, self.pe, seg_offsets=self.seg, num_groups=self.batch_size, out_offset=sb.offset,
+                       ldm=r, ldn=1, n_valid=r, accumulate=False, group_stride=stride, block_n=64,
+                       status=self.status)
+
+    # ---- after backward -------------------------------------------------------------------------
+    @torch.no_grad()
+    def finalize(self, clipping_norm: float, *, mode: str = "clip", gamma: float = 0.01) -> dict[str, torch.Tensor]:
+        eng, sp = self.engine, self.engine.space
+        norm2 = torch.zeros(self.batch_size, dtype=torch.float32, device=eng.device)
+        if self.direct_elems:
+            ops.rows_sumsq(self.pe[:, :self.direct_elems], norm2)
+        n_parts = len(self.part_slots)
+        if n_parts:
+            by_slot: dict[str, list[int]] = {}
+            for i, name in enumerate(self.part_slots):
+                by_slot.setdefault(name, []).append(i)
+            single = [rows[0] for rows in by_slot.values() if len(rows) == 1]
+            if single:
+                norm2 += self.parts[single].sum(0) if len(single) < n_parts else self.parts[:n_parts].sum(0)
+            for rows in by_slot.values():
+                if len(rows) > 1:   # shared parameter: (sum of the pieces' norms)^2 bounds the true squared norm
+                    norm2 += self.parts[rows].clamp_min(0).sqrt().sum(0) ** 2
+        norms = norm2.clamp_min(0).sqrt()
+        if mode == "auto":
+            c = clipping_norm / (norms + gamma)
+        else:
+            c = (clipping_norm / norms).clamp(max=1.0)
+        c = torch.where(torch.isfinite(c), c, torch.zeros_like(c)) * CLIP_GUARD
+        tgt = sp.grad_target()
+        if self.direct_elems:
+            ops.clip_weighted_sum(self.pe[:, :self.direct_elems], c, tgt["out"], flat_offset=0,
+                                  peer_table=tgt["peer_table"], shard_elems=tgt["shard_elems"])
+        if self.records:
+            row_scale = c.repeat_interleave(self.tokens)
+            for kind, slot, g2d, other in self.records:
+                if kind == "linear":
+                    ops.wgrad_clip(g2d, other, tgt["out"], row_scale=row_scale, out_offset=slot.offset,
+                                   ldm=slot.shape[1], ldn=1, accumulate=True, peer_table=tgt["peer_table"],
+                                   shard_elems=tgt["shard_elems"], status=self.status)
+                else:
+                    ops.embedding_wgrad(g2d, other, tgt["out"], row_scale=row_scale, flat_offset=slot.offset,
+                                        peer_table=tgt["peer_table"], shard_elems=tgt["shard_elems"])
+        self.records = []
+        return {"norms": norms, "scales": c}
+
+
+# ===================================================================================== layer functions
+
+class _DPLinear(Function):
+    """``y = x Wᵀ (+ b)`` with the weight gradient deferred to the capture."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        ctx.save_for_backward(x, weight)
+        ctx.bias = bias
+        return torch.nn.functional.linear(x, weight, bias)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, weight = ctx.saved_tensors
+        cap = current_capture()
+        dx = gy @ weight if ctx.needs_input_grad[0] else None
+        g2d = gy.reshape(-1, gy.shape[-1])
+        g2d = g2d if g2d.is_contiguous() else g2d.contiguous()
+        x2d = x.reshape(-1, x.shape[-1])
+        x2d = x2d if x2d.is_contiguous() else x2d.contiguous()
+        if cap is None:
+            dw = g2d.t() @ x2d
+            db = g2d.sum(0) if ctx.bias is not None else None
+            return dx, dw, db
+        cap.add_linear(weight, x2d, g2d)
+        if ctx.bias is not None:
+            cap.pe_view(ctx.bias).add_(g2d.view(cap.batch_size, cap.tokens, -1).sum(1, dtype=torch.float32))
+        return dx, None, None
+
+
+def dp_linear(x: torch.Tensor, weight: torch.nn.Parameter, bias: torch.nn.Parameter | None = None) -> torch.Tensor:
+    if weight.requires_grad and x.is_cuda and current_capture() is not None:
+        return _DPLinear.apply(x, weight, bias)
+    return torch.nn.functional.linear(x, weight, bias)
+
+
+class _DPEmbedding(Function):
+    @staticmethod
+    def forward(ctx, ids, weight):
+        ctx.save_for_backward(ids, weight)
+        return torch.nn.functional.embedding(ids, weight)
+
+    @staticmethod
+    def backward(ctx, gy):
+        ids, weight = ctx.saved_tensors
+        cap = current_capture()
+        g2d = gy.reshape(-1, gy.shape[-1])
+        g2d = g2d if g2d.is_contiguous() else g2d.contiguous()
+        if cap is None:
+            dw = torch.zeros_like(weight, dtype=torch.float32).index_add_(0, ids.reshape(-1), g2d.float())
+            return None, dw.to(weight.dtype)
+        cap.add_embedding(weight, ids, g2d)
+        return None, None
+
+
+def dp_embedding(ids: torch.Tensor, weight: torch.nn.Parameter) -> torch.Tensor:
+    if weight.requires_grad and ids.is_cuda and current_capture() is not None:
+        return _DPEmbedding.apply(ids, weight)
+    return torch.nn.functional.embedding(ids, weight)
+
+
+class _LoRALinear(Function):
+    """``y = x Wᵀ + s·(x Aᵀ) Bᵀ`` with frozen ``W``; per-example ``dA``, ``dB`` go to the capture."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, lora_a, lora_b, scaling):
+        x2d = x.reshape(-1, x.shape[-1])
+        xa = x2d @ lora_a.t()
+        y = torch.nn.functional.linear(x2d, weight, bias)
+        y.addmm_(xa, lora_b.t(), alpha=scaling)
+        ctx.save_for_backward(x2d, xa, weight, lora_a, lora_b)
+        ctx.scaling = scaling
+        ctx.xshape = x.shape
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2d, xa, weight, lora_a, lora_b = ctx.saved_tensors
+        s = ctx.scaling
+        g2d = gy.reshape(-1, gy.shape[-1])
+        g2d = g2d if g2d.is_contiguous() else g2d.contiguous()
+        q = (g2d @ lora_b) * s                                     # [R, r]
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = g2d @ weight
+            dx.addmm_(q, lora_a)
+            dx = dx.view(ctx.xshape)
+        cap = current_capture()
+        if cap is None:
+            return dx, None, None, (q.t() @ x2d), (g2d.t() @ xa) * s, None
+        R, r = q.shape
+        q_pad = torch.zeros(R, LORA_PAD, dtype=q.dtype, device=q.device)
+        q_pad[:, :r] = q
+        xa_pad = torch.zeros(R, LORA_PAD, dtype=xa.dtype, device=xa.device)
+        xa_pad[:, :r] = xa * s
+        xc = x2d if x2d.is_contiguous() else x2d.contiguous()
+        cap.add_lora(lora_a, lora_b, xc, xa_pad, g2d, q_pad)
+        return dx, None, None, None, None, None
+
+
+def lora_linear(x, weight, bias, lora_a, lora_b, scaling: float):
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _LoRALinear.apply(x, weight, bias, lora_a, lora_b, scaling)
+    y = torch.nn.functional.linear(x, weight, bias)
+    return y + scaling * ((x @ lora_a.t()) @ lora_b.t())
+
+
+# ===================================================================================== engine
+
+@dataclasses.dataclass
+class StepResult:
+    loss: float
+    grad_norm_mean: float
+    clip_rate: float
+    batch_size: int
+    losses: torch.Tensor | None = None
+    norms: torch.Tensor | None = None
+
+
+class FusedDPEngine:
+    """Owns the flat space, the capture buffers and the sharded DP optimizer for one model."""
+
+    def __init__(self, model: torch.nn.Module, *, clipping_norm: float, noise_multiplier: float,
+                 normalize_by: float, key: RngKey, step_config: DPStepConfig | None = None,
+                 microbatch_size: int = 8, group: PeerGroup | None = None, mechanism: dict | None = None,
+                 clipping_mode: str = "clip", gamma: float = 0.01,
+                 direct: Callable[[str, torch.nn.Parameter], bool] | None = None):
+        self.model = model
+        self.device = next(model.parameters()).device
+        self.group = group or PeerGroup(self.device)
+        named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        if not named:
+            raise ValueError("the model has no trainable parameters")
+        self.space = FlatSpace(named, self.group, direct=direct)
+        self.space.bind()
+        self._slot_by_id = {id(p): self.space.slots[n] for n, p in named}
+        self.opt = ShardedDPOptimizer(self.space, step_config or DPStepConfig(), key=key, mechanism=mechanism)
+        self.clipping_norm, self.noise_multiplier, self.normalize_by = clipping_norm, noise_multiplier, normalize_by
+        self.clipping_mode, self.gamma = clipping_mode, gamma
+        self.microbatch_size = microbatch_size
+        self.status = self.group.status
+        self._pe: torch.Tensor | None = None
+        self.kernel_launches = 0
+
+    def slot_of(self, param: torch.nn.Parameter):
+        return self._slot_by_id[id(param)]
+
+    def pe_buffer(self, batch_size: int) -> torch.Tensor:
+        width = max(self.space.direct_elems, 4)
+        if self._pe is None or self._pe.shape[0] < batch_size:
+            self._pe = torch.zeros(max(batch_size, self.microbatch_size), width, dtype=torch.float32,
+                                   device=self.device)
+        else:
+            self._pe[:batch_size].zero_()
+        return self._pe[:batch_size]
+
+    def accumulate(self, loss_fn: Callable[..., torch.Tensor], batch: dict[str, torch.Tensor]) -> StepResult:
+        """Forward/backward all microbatches of ``batch`` and reduce clipped sums into the sharded gradient.
+
+        ``loss_fn(**microbatch)`` returns one loss per example (``[mb]``).
+        """
+        first = next(iter(batch.values()))
+        n = first.shape[0]
+        losses, norms, clipped = [], [], 0
+        for lo in range(0, n, self.microbatch_size):
+            sub = {k: v[lo:lo + self.microbatch_size] for k, v in batch.items()}
+            mb = next(iter(sub.values())).shape[0]
+            tokens = sub["input_ids"].shape[1] if "input_ids" in sub else 1
+            cap = Capture(self, mb, tokens)
+            with activate(cap):
+                per_example = loss_fn(**sub)
+                per_example.sum().backward()
+            out = cap.finalize(self.clipping_norm, mode=self.clipping_mode, gamma=self.gamma)
+            losses.append(per_example.detach().float())
+            norms.append(out["norms"])
+        if n:
+            l_all, n_all = torch.cat(losses), torch.cat(norms)
+            return StepResult(float("nan"), float("nan"), float("nan"), n, l_all, n_all)
+        return StepResult(0.0, 0.0, 0.0, 0, None, None)
+
+    def step(self, loss_fn: Callable[..., torch.Tensor], batch: dict[str, torch.Tensor], *,
+             read_metrics: bool = True) -> StepResult:
+        """One DP optimizer step: accumulate, then noise + AdamW-BC on the shards."""
+        res = self.accumulate(loss_fn, batch)
+        sigma = 0.0 if self.noise_multiplier == 0 else self.noise_multiplier * self.clipping_norm
+        self.opt.step(noise_std=sigma, normalize_by=self.normalize_by)
+        if read_metrics and res.batch_size:
+            stats = torch.stack([res.losses.mean(), res.norms.mean(),
+                                 (res.norms > self.clipping_norm).float().mean()]).tolist()   # one D2H read
+            res.loss, res.grad_norm_mean, res.clip_rate = stats
+            self.group.check("fused DP step")
+        return res

@@ -1,0 +1,7 @@
+"""Model families owned by the framework (HF-compatible parameter names)."""
+from .gpt2 import GPT2Config, GPT2LMHeadModel
+from .layers import Embedding, LayerNorm, Linear, RMSNorm, linear_cross_entropy
+from .llama import LlamaConfig, LlamaForCausalLM, shift_labels
+
+__all__ = ["Embedding", "GPT2Config", "GPT2LMHeadModel", "LayerNorm", "Linear", "LlamaConfig", "LlamaForCausalLM",
+           "RMSNorm", "linear_cross_entropy", "shift_labels"]

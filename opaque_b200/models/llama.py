@@ -1,0 +1,165 @@
+"""Llama-family decoder (RMSNorm, RoPE, GQA attention, SwiGLU) with per-example losses.
+
+Parameter names follow Hugging Face ``LlamaForCausalLM`` (``model.layers.N.self_attn.q_proj.weight``
+…, LoRA factors as ``…q_proj.lora_A`` / ``lora_B``) so safetensors checkpoints and PEFT adapters map
+one to one.  Attention runs through PyTorch SDPA (flash kernels) in an explicit-batch layout — the
+fused engine needs no vmap, which is what forces eager attention in the reference
+(docs/user-guide/huggingface/model-patches.md:128-146).
+
+Reference counterparts: packages/opaque-patches/src/opaque/api/patches/transformers/models/llama.py,
+components/{attention,rms_norm,rope,swiglu,cross_entropy}.py, peft/components/{linear,qkv}.py.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+from torch import nn
+
+from .. import ops
+from .layers import Embedding, Linear, RMSNorm, linear_cross_entropy, per_example_token_weights
+
+
+@dataclasses.dataclass
+class LlamaConfig:
+    vocab_size: int = 128256
+    hidden_size: int = 4096
+    intermediate_size: int = 14336
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 500000.0
+    max_position_embeddings: int = 8192
+    tie_word_embeddings: bool = False
+    head_dim: int | None = None
+
+    @property
+    def hd(self) -> int:
+        return self.head_dim or self.hidden_size // self.num_attention_heads
+
+    @staticmethod
+    def llama3_8b() -> "LlamaConfig":
+        return LlamaConfig()
+
+    @staticmethod
+    def llama32_1b() -> "LlamaConfig":
+        return LlamaConfig(hidden_size=2048, intermediate_size=8192, num_hidden_layers=16, num_attention_heads=32,
+                           num_key_value_heads=8, tie_word_embeddings=True, head_dim=64)
+
+    @staticmethod
+    def tiny(vocab: int = 256) -> "LlamaConfig":
+        return LlamaConfig(vocab_size=vocab, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                           num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256)
+
+
+class LlamaAttention(nn.Module):
+    def __init__(self, cfg: LlamaConfig, dtype, device):
+        super().__init__()
+        d, hd = cfg.hidden_size, cfg.hd
+        self.nh, self.nkv, self.hd = cfg.num_attention_heads, cfg.num_key_value_heads, hd
+        self.q_proj = Linear(d, self.nh * hd, dtype=dtype, device=device)
+        self.k_proj = Linear(d, self.nkv * hd, dtype=dtype, device=device)
+        self.v_proj = Linear(d, self.nkv * hd, dtype=dtype, device=device)
+        self.o_proj = Linear(self.nh * hd, d, dtype=dtype, device=device)
+
+    def forward(self, x, cos, sin, pos):
+        B, T, _ = x.shape
+        q = self.q_proj(x).view(B, T, self.nh, self.hd)
+        k = self.k_proj(x).view(B, T, self.nkv, self.hd)
+        v = self.v_proj(x).view(B, T, self.nkv, self.hd)
+        q, k = ops.rope_qk(q, k, cos, sin, pos)
+        o = nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                                       is_causal=True, enable_gqa=self.nkv != self.nh)
+        return self.o_proj(o.transpose(1, 2).reshape(B, T, self.nh * self.hd))
+
+
+class LlamaMLP(nn.Module):
+    def __init__(self, cfg: LlamaConfig, dtype, device):
+        super().__init__()
+        self.gate_proj = Linear(cfg.hidden_size, cfg.intermediate_size, dtype=dtype, device=device)
+        self.up_proj = Linear(cfg.hidden_size, cfg.intermediate_size, dtype=dtype, device=device)
+        self.down_proj = Linear(cfg.intermediate_size, cfg.hidden_size, dtype=dtype, device=device)
+
+    def forward(self, x):
+        return self.down_proj(ops.swiglu(self.gate_proj(x), self.up_proj(x)))
+
+
+class LlamaDecoderLayer(nn.Module):
+    def __init__(self, cfg: LlamaConfig, dtype, device):
+        super().__init__()
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
+        self.self_attn = LlamaAttention(cfg, dtype, device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
+        self.mlp = LlamaMLP(cfg, dtype, device)
+
+    def forward(self, h, cos, sin, pos):
+        h = h + self.self_attn(self.input_layernorm(h), cos, sin, pos)
+        # fused residual add + norm: (y, s) with s = attention output + residual
+        return h + self.mlp(self.post_attention_layernorm(h))
+
+
+class LlamaModel(nn.Module):
+    def __init__(self, cfg: LlamaConfig, dtype, device):
+        super().__init__()
+        self.embed_tokens = Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
+        self.layers = nn.ModuleList(LlamaDecoderLayer(cfg, dtype, device) for _ in range(cfg.num_hidden_layers))
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
+
+
+class LlamaForCausalLM(nn.Module):
+    """Causal LM returning one mean next-token loss per example."""
+
+    def __init__(self, cfg: LlamaConfig, *, dtype=torch.bfloat16, device=None, activation_checkpointing: bool = False):
+        super().__init__()
+        self.config = cfg
+        self.model = LlamaModel(cfg, dtype, device)
+        self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, dtype=dtype, device=device)
+        if cfg.tie_word_embeddings:
+            self.lm_head.weight = self.model.embed_tokens.weight
+        cos, sin = ops.rope_tables(cfg.hd, cfg.max_position_embeddings, cfg.rope_theta, device=device)
+        self.register_buffer("rope_cos", cos, persistent=False)
+        self.register_buffer("rope_sin", sin, persistent=False)
+        self.activation_checkpointing = activation_checkpointing
+        self.ce_chunk = 8192
+
+    # ---- adapters ---------------------------------------------------------------------------
+    def add_lora(self, r: int = 16, alpha: float = 32.0, targets=("q_proj", "k_proj", "v_proj", "o_proj")) -> None:
+        """Freeze the base model and attach LoRA factors to the named projections."""
+        for p in self.parameters():
+            p.requires_grad_(False)
+        for name, mod in self.named_modules():
+            if isinstance(mod, Linear) and name.split(".")[-1] in targets:
+                mod.add_lora(r, alpha)
+
+    # ---- forward ------------------------------------------------------------------------------
+    def hidden_states(self, input_ids: torch.Tensor, position_ids: torch.Tensor | None = None) -> torch.Tensor:
+        h = self.model.embed_tokens(input_ids)
+        for layer in self.model.layers:
+            if self.activation_checkpointing and torch.is_grad_enabled():
+                h = torch.utils.checkpoint.checkpoint(layer, h, self.rope_cos, self.rope_sin, position_ids,
+                                                      use_reentrant=False)
+            else:
+                h = layer(h, self.rope_cos, self.rope_sin, position_ids)
+        return self.model.norm(h)
+
+    def forward(self, input_ids, position_ids=None):
+        return self.lm_head(self.hidden_states(input_ids, position_ids))
+
+    def per_example_loss(self, input_ids: torch.Tensor, labels: torch.Tensor, position_ids=None) -> torch.Tensor:
+        """Mean NLL over each example's scored tokens; ``labels`` are already aligned (−100 = not scored)."""
+        B, T = input_ids.shape
+        h = self.hidden_states(input_ids, position_ids).reshape(B * T, -1)
+        w = per_example_token_weights(labels).reshape(-1)
+        rows = linear_cross_entropy(h, self.lm_head.weight, labels.reshape(-1), w, chunk=self.ce_chunk)
+        return rows.view(B, T).sum(1)
+
+
+def shift_labels(input_ids: torch.Tensor, loss_fraction: float = 1.0, ignore_index: int = -100) -> torch.Tensor:
+    """Next-token labels; only the last ``loss_fraction`` of positions are scored."""
+    labels = torch.full_like(input_ids, ignore_index)
+    labels[:, :-1] = input_ids[:, 1:]
+    if loss_fraction < 1.0:
+        T = input_ids.shape[1]
+        labels[:, : int(T * (1.0 - loss_fraction))] = ignore_index
+    return labels

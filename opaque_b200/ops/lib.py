@@ -71,7 +71,12 @@ def available() -> bool:
         return False
 
 
+LAUNCHES = 0   # entry points called so far (each launches at least one kernel of this library)
+
+
 def check(rc: int, what: str) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if rc != 0:
         buf = ctypes.create_string_buffer(256)
         try:

@@ -1,0 +1,220 @@
+"""Flat parameter space with ZeRO-style sharded DP state and the fused DP optimizer step.
+
+Layout.  Trainable parameters are laid out back to back (each start aligned to 64 elements) in
+one flat index space, *direct* parameters first (those whose per-example gradients are
+materialised: LoRA factors, biases, norm weights) and *ghost* parameters after them (large
+matrices handled by the ghost-norm / clip-GEMM pair).  The space is padded so that it splits
+into W equal contiguous shards.
+
+  * ``params``  bf16, full length, one copy per rank in peer memory — model parameters are views
+                 of it, and owners store updated values into EVERY rank's copy;
+  * ``grad``    fp32, one shard per rank in peer memory — producers on any rank reduce
+                 (``red.global.add``) clipped gradient sums straight into the owner's shard;
+  * ``master``, ``m``, ``v`` (and DP-FTRL buffers) fp32, one shard per rank, local.
+
+Step.  ``barrier → shard_step → barrier`` on the compute stream: the first barrier orders all
+ranks' gradient reductions before the owner reads its shard, the fused kernel adds Philox (or
+correlated) noise exactly once per coordinate, applies AdamW with noise bias correction to the
+fp32 masters and pushes bf16 parameters to all peers, and the second barrier orders those
+stores before the next forward pass.
+
+Replaces: per-leaf NCCL all-reduce (packages/opaque-engine/src/opaque/api/engine/distributed/
+gradients.py:183-193), CPU-generated noise (packages/opaque-dpsgd/src/opaque/api/dpsgd/noise/
+_gaussian.py:235-278), tree-mapped AdamW-BC (packages/opaque-optimizers/src/opaque/api/optimizers/
+_adam.py:120-270) and the streaming C⁻¹ noise (packages/opaque-dpftrl/src/opaque/api/dpftrl/noise/
+_engine.py:359-410).
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+from collections.abc import Callable, Sequence
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..random import RngKey, fold_in
+from .peer import PeerGroup
+
+ALIGN = 64
+
+
+@dataclasses.dataclass(frozen=True)
+class Slot:
+    name: str
+    offset: int
+    numel: int
+    shape: tuple[int, ...]
+    direct: bool
+
+
+class FlatSpace:
+    """Offsets of every trainable parameter in the flat space, and the peer buffers behind it."""
+
+    def __init__(self, named_params: Sequence[tuple[str, torch.nn.Parameter]], group: PeerGroup, *,
+                 direct: Callable[[str, torch.nn.Parameter], bool] | None = None):
+        self.group = group
+        is_direct = direct or (lambda n, p: p.ndim < 2)
+        ordered = sorted(named_params, key=lambda np_: (not is_direct(*np_),))   # stable: direct first
+        self.slots: dict[str, Slot] = {}
+        off = 0
+        for name, p in ordered:
+            self.slots[name] = Slot(name, off, p.numel(), tuple(p.shape), bool(is_direct(name, p)))
+            off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
+            if self.slots[name].direct:
+                self.direct_elems = off
+        if not hasattr(self, "direct_elems"):
+            self.direct_elems = 0
+        chunk = group.world * ALIGN
+        self.total = max((off + chunk - 1) // chunk * chunk, chunk)
+        self.shard = self.total // group.world
+        self.shard_lo = group.rank * self.shard
+        self.params = group.buffer(self.total, torch.bfloat16)
+        self.grad = group.buffer(self.shard, torch.float32)
+        dev = group.device
+        self.master = torch.zeros(self.shard, dtype=torch.float32, device=dev)
+        self.m = torch.zeros_like(self.master)
+        self.v = torch.zeros_like(self.master)
+        self._named = list(ordered)
+
+    # ---- binding --------------------------------------------------------------------------
+    @torch.no_grad()
+    def bind(self) -> None:
+        """Move parameter storage into the flat bf16 buffer and initialise the fp32 masters.
+
+        Rank 0's values win (one broadcast) so that replicas start identical.
+        """
+        full32 = torch.zeros(self.total, dtype=torch.float32, device=self.group.device)
+        for name, p in self._named:
+            s = self.slots[name]
+            full32[s.offset:s.offset + s.numel] = p.detach().reshape(-1).float()
+        if self.group.world > 1:
+            dist.broadcast(full32, src=dist.get_global_rank(self.group.pg, 0) if self.group.pg is not dist.group.WORLD else 0,
+                           group=self.group.pg)
+        self.master.copy_(full32[self.shard_lo:self.shard_lo + self.shard])
+        self.params.local.copy_(full32.to(torch.bfloat16))
+        for name, p in self._named:
+            s = self.slots[name]
+            p.data = self.params.local[s.offset:s.offset + s.numel].view(s.shape)
+        if self.group.world > 1:
+            torch.cuda.synchronize(self.group.device)
+            dist.barrier(group=self.group.pg)
+
+    def view_of(self, name: str, flat: torch.Tensor) -> torch.Tensor:
+        s = self.slots[name]
+        return flat[s.offset:s.offset + s.numel].view(s.shape)
+
+    # ---- gradient destinations for producers ------------------------------------------------
+    def grad_target(self) -> dict[str, Any]:
+        """Keyword arguments that route a producer kernel's output into the sharded gradient."""
+        if self.group.world == 1:
+            return {"out": self.grad.local, "peer_table": None, "shard_elems": 0}
+        return {"out": None, "peer_table": self.grad.table, "shard_elems": self.shard}
+
+    @torch.no_grad()
+    def gather_full(self, shard_tensor: torch.Tensor) -> torch.Tensor:
+        """All ranks' shards of a local fp32 state concatenated (checkpointing / tests)."""
+        if self.group.world == 1:
+            return shard_tensor.clone()
+        out = torch.empty(self.total, dtype=shard_tensor.dtype, device=shard_tensor.device)
+        dist.all_gather_into_tensor(out, shard_tensor.contiguous(), group=self.group.pg)
+        return out
+
+
+@dataclasses.dataclass
+class DPStepConfig:
+    lr: float | Callable[[int], float] = 1e-3
+    betas: tuple[float, float] = (0.9, 0.999)
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+    decoupled_weight_decay: bool = True
+    noise_bias_correction: bool = True
+
+
+class ShardedDPOptimizer:
+    """Noise + AdamW-BC over the owner's shard, fused with the parameter all-gather.
+
+    ``mechanism`` is ``None`` (iid Gaussian, DP-SGD) or a dict describing a DP-FTRL inverse:
+    ``{"kind": "blt", "scale": [...], "decay": [...]}`` or ``{"kind": "banded", "coef": [...]}``
+    (``coef[0]`` the diagonal; the state holds ``len(coef) − 1`` previous outputs).
+    """
+
+    def __init__(self, space: FlatSpace, config: DPStepConfig, *, key: RngKey, mechanism: dict | None = None):
+        self.space, self.cfg, self.key = space, config, key
+        self.step_count = 0
+        self.phi = 0.0
+        self.mechanism = mechanism
+        self.ftrl_state = None
+        self.nbuf = 0
+        self.mode = 0
+        self.coef: list[float] = []
+        if mechanism is not None:
+            if mechanism["kind"] == "blt":
+                s, d = list(mechanism["scale"]), list(mechanism["decay"])
+                if len(s) != len(d) or not 1 <= len(s) <= 8:
+                    raise ValueError("BLT needs 1..8 (scale, decay) pairs")
+                self.mode, self.nbuf, self.coef = 1, len(s), [float(x) for x in s + d]
+            elif mechanism["kind"] == "banded":
+                c = [float(x) for x in mechanism["coef"]]
+                if not 2 <= len(c) <= 9 or c[0] == 0:
+                    raise ValueError("banded inverse needs 2..9 coefficients with a non-zero diagonal")
+                self.mode, self.nbuf, self.coef = 2, len(c) - 1, c
+            else:
+                raise ValueError(f"unknown mechanism kind {mechanism['kind']!r}")
+            self.ftrl_state = torch.zeros(self.nbuf, space.shard, dtype=torch.float32, device=space.group.device)
+
+    def noise_row_norm(self) -> float:
+        """``‖row_t(C⁻¹)‖`` for the current step (1 for iid noise): the factor between σ and the realised std."""
+        return 1.0
+
+    @torch.no_grad()
+    def step(self, *, noise_std: float, normalize_by: float, noisy_out: torch.Tensor | None = None,
+             skip_update: bool = False) -> None:
+        sp, g = self.space, self.space.group
+        t = self.step_count + 1
+        lr = float(self.cfg.lr(self.step_count)) if callable(self.cfg.lr) else float(self.cfg.lr)
+        b1, b2 = self.cfg.betas
+        var = (noise_std / normalize_by) ** 2
+        if self.cfg.noise_bias_correction:
+            self.phi = b2 * self.phi + (1 - b2) * var
+        phi_hat = self.phi / (1 - b2 ** t) if self.cfg.noise_bias_correction else 0.0
+        seed = fold_in(self.key, self.step_count).seed
+        g.barrier()
+        ops.shard_step(
+            grad=sp.grad.local, master=sp.master, m=sp.m, v=sp.v,
+            params_local=sp.params.local if g.world == 1 else None,
+            peer_params=sp.params.table if g.world > 1 else None, world=g.world, global_offset=sp.shard_lo,
+            seed=seed, noise_std=noise_std, inv_normalize=1.0 / normalize_by, lr=lr, betas=(b1, b2),
+            eps=self.cfg.eps, weight_decay=self.cfg.weight_decay, step=t, phi_hat=phi_hat,
+            decoupled_wd=self.cfg.decoupled_weight_decay, ftrl_state=self.ftrl_state, ftrl_mode=self.mode,
+            ftrl_coef=self.coef, nbuf=self.nbuf, ring_head=(self.step_count % self.nbuf) if self.mode == 2 else 0,
+            noisy_out=noisy_out, skip_update=skip_update)
+        g.barrier()
+        self.step_count = t
+
+    # ---- checkpoint -----------------------------------------------------------------------
+    def state_dict(self) -> dict[str, Any]:
+        """Full (unsharded) optimizer state on every rank; rank 0 writes it."""
+        sp = self.space
+        sd = {"step": self.step_count, "phi": self.phi, "key_seed": str(self.key.seed),
+              "master": sp.gather_full(sp.master).cpu(), "m": sp.gather_full(sp.m).cpu(),
+              "v": sp.gather_full(sp.v).cpu(), "total": sp.total}
+        if self.ftrl_state is not None:
+            sd["ftrl_state"] = torch.stack([sp.gather_full(self.ftrl_state[b]) for b in range(self.nbuf)]).cpu()
+        return sd
+
+    @torch.no_grad()
+    def load_state_dict(self, sd: dict[str, Any]) -> None:
+        sp = self.space
+        if int(sd["total"]) != sp.total:
+            raise ValueError("checkpoint was written for a different parameter layout")
+        lo, hi = sp.shard_lo, sp.shard_lo + sp.shard
+        self.step_count, self.phi = int(sd["step"]), float(sd["phi"])
+        sp.master.copy_(sd["master"][lo:hi])
+        sp.m.copy_(sd["m"][lo:hi])
+        sp.v.copy_(sd["v"][lo:hi])
+        sp.params.local.copy_(sd["master"].to(torch.bfloat16))
+        if self.ftrl_state is not None and "ftrl_state" in sd:
+            self.ftrl_state.copy_(sd["ftrl_state"][:, lo:hi])

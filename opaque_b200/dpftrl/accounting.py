@@ -1,0 +1,156 @@
+"""DP-FTRL accounting: the matrix mechanism as one Gaussian release, and its amplified variants.
+
+``mf_gaussian(σ, strategy, n_steps=…)`` is a *whole-run* (horizon) process: the entire noisy prefix-sum
+release is a single Gaussian mechanism whose effective noise multiplier is ``σ / sensitivity(C)``.  Use
+``per_step(...)`` to record it step by step in an :class:`Accountant` (``per_step(h) * n`` evaluates
+``h.pld_at(n)``).
+
+Amplification:
+  ``poisson(inner, q, n_steps=…)``     cyclic Poisson sampling with ``bands`` = the strategy's band count:
+                                        each of the ``ceil(n/bands)`` rounds of a band is a Poisson-subsampled
+                                        Gaussian at the band's effective multiplier (Choquette-Choo et al.)
+  ``balls_in_bins(inner, num_bins=…, n_steps=…)``   Monte-Carlo PLD of the mixture over bins
+  ``b_min_sep(inner, …)``              b-min-sep participation: sensitivity with ``min_sep = b`` (no extra
+                                        amplification is claimed beyond the participation constraint)
+
+Parity: packages/opaque-dpftrl/src/opaque/api/accounting/dpftrl/{mechanisms/_mf_gaussian,
+amplification/_poisson,amplification/_balls_in_bins,amplification/_b_min_sep}.py.
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+
+import numpy as np
+
+from ..accounting.core import (DiscretizationConfig, DpHorizonProcess, DpProcess, PerStep, get_discretization, native,
+                               per_step, register_process_codec)
+from .noise import MfStrategy, strategy_from_wire, strategy_to_wire
+
+
+@dataclasses.dataclass(frozen=True)
+class MfGaussian(DpHorizonProcess):
+    noise_multiplier: float
+    strategy: MfStrategy
+    n_steps: int = 1
+    min_sep: int = 1
+    max_participations: int | None = None
+
+    def __post_init__(self):
+        if self.noise_multiplier < 0:
+            raise ValueError(f"noise_multiplier must be non-negative, got {self.noise_multiplier}")
+        if self.n_steps < 1 or self.min_sep < 1:
+            raise ValueError("n_steps and min_sep must be >= 1")
+
+    def effective_noise_multiplier(self, n_steps: int | None = None) -> float:
+        n = n_steps or self.n_steps
+        return self.noise_multiplier / self.strategy.sensitivity(n, self.min_sep, self.max_participations)
+
+    def pld_at(self, n_steps: int, config: DiscretizationConfig | None = None):
+        cfg = config or get_discretization()
+        if self.noise_multiplier == 0:
+            return native.nonprivate_pld(cfg.to_native())
+        return native.gaussian_pld(self.effective_noise_multiplier(n_steps), cfg.to_native())
+
+    def _build_pld(self, config):
+        return self.pld_at(self.n_steps, config)
+
+
+register_process_codec(
+    MfGaussian,
+    lambda p: {"noise_multiplier": p.noise_multiplier, "strategy": strategy_to_wire(p.strategy), "n_steps": p.n_steps,
+               "min_sep": p.min_sep, "max_participations": p.max_participations},
+    lambda w: MfGaussian(w["noise_multiplier"], strategy_from_wire(w["strategy"]), w.get("n_steps", 1),
+                         w.get("min_sep", 1), w.get("max_participations")))
+
+
+@dataclasses.dataclass(frozen=True)
+class CyclicPoisson(DpHorizonProcess):
+    """Banded MF under cyclic Poisson sampling (``bands`` partitions, rate ``q`` within the active one)."""
+    inner: MfGaussian
+    sample_rate: float
+    n_steps: int
+    bands: int = 1
+    truncated_batch_size: int | None = None
+    dataset_size: int | None = None
+
+    def __post_init__(self):
+        if not 0 < self.sample_rate <= 1:
+            raise ValueError("sample_rate must be in (0, 1]")
+
+    def pld_at(self, n_steps: int, config: DiscretizationConfig | None = None):
+        cfg = config or get_discretization()
+        b = self.bands
+        # one record can only be hit in the steps of its own partition; with a b-banded C those steps'
+        # columns are orthogonal, so each visit is an independent subsampled Gaussian with the column norm
+        # as sensitivity; there are ceil(n / b) visits.
+        col = math.sqrt(float(native.single_participation_sensitivity_squared(
+            self.inner.strategy.gram_matrix(min(n_steps, 4 * b + 8)).reshape(-1).tolist(), min(n_steps, 4 * b + 8))))
+        nm = self.inner.noise_multiplier / col
+        visits = math.ceil(n_steps / b)
+        if self.truncated_batch_size is not None and self.dataset_size is not None:
+            base = native.truncated_poisson_gaussian_pld(nm, self.sample_rate, self.truncated_batch_size,
+                                                         max(1, self.dataset_size // b), cfg.to_native())
+        else:
+            base = native.poisson_gaussian_pld(nm, self.sample_rate, cfg.to_native())
+        return base if visits == 1 else base.self_compose(visits)
+
+    def _build_pld(self, config):
+        return self.pld_at(self.n_steps, config)
+
+
+@dataclasses.dataclass(frozen=True)
+class BallsInBins(DpHorizonProcess):
+    inner: MfGaussian
+    num_bins: int
+    n_steps: int
+
+    def pld_at(self, n_steps: int, config: DiscretizationConfig | None = None):
+        cfg = config or get_discretization()
+        g = self.inner.strategy.gram_matrix(n_steps)
+        return native.balls_in_bins_mc_pld(np.asarray(g, float).reshape(-1).tolist(), n_steps, min(self.num_bins, n_steps),
+                                           self.inner.noise_multiplier, cfg.to_native())
+
+    def _build_pld(self, config):
+        return self.pld_at(self.n_steps, config)
+
+
+def _strategy_process_codec(cls):
+    register_process_codec(
+        cls,
+        lambda p: {**{f.name: getattr(p, f.name) for f in dataclasses.fields(p) if f.name != "inner"},
+                   "inner": {"type": "MfGaussian", "noise_multiplier": p.inner.noise_multiplier,
+                             "strategy": strategy_to_wire(p.inner.strategy), "n_steps": p.inner.n_steps,
+                             "min_sep": p.inner.min_sep, "max_participations": p.inner.max_participations}},
+        lambda w: cls(inner=MfGaussian(w["inner"]["noise_multiplier"], strategy_from_wire(w["inner"]["strategy"]),
+                                       w["inner"].get("n_steps", 1), w["inner"].get("min_sep", 1),
+                                       w["inner"].get("max_participations")),
+                      **{k: v for k, v in w.items() if k != "inner"}))
+
+
+_strategy_process_codec(CyclicPoisson)
+_strategy_process_codec(BallsInBins)
+
+
+def mf_gaussian(noise_multiplier: float, strategy: MfStrategy, *, n_steps: int = 1, min_sep: int = 1,
+                max_participations: int | None = None) -> MfGaussian:
+    return MfGaussian(float(noise_multiplier), strategy, int(n_steps), int(min_sep), max_participations)
+
+
+def poisson(inner: MfGaussian, sample_rate: float, *, n_steps: int, truncated_batch_size: int | None = None,
+            dataset_size: int | None = None) -> CyclicPoisson:
+    bands = int(getattr(inner.strategy, "bands", getattr(inner.strategy, "bandwidth", 1)))
+    return CyclicPoisson(inner, float(sample_rate), int(n_steps), bands, truncated_batch_size, dataset_size)
+
+
+def balls_in_bins(inner: MfGaussian, *, num_bins: int, n_steps: int) -> BallsInBins:
+    return BallsInBins(inner, int(num_bins), int(n_steps))
+
+
+def b_min_sep(inner: MfGaussian, *, bands: int, n_steps: int, max_participations: int | None = None) -> MfGaussian:
+    """b-min-sep participation as a sensitivity constraint on the un-amplified mechanism."""
+    return dataclasses.replace(inner, n_steps=int(n_steps), min_sep=int(bands), max_participations=max_participations)
+
+
+__all__ = ["BallsInBins", "CyclicPoisson", "MfGaussian", "b_min_sep", "balls_in_bins", "mf_gaussian", "per_step",
+           "poisson"]

@@ -128,7 +128,8 @@ struct ShardStepParams {
   unsigned long long seed; // Philox key of this step
   float noise_std;         // sigma * C (before normalisation)
   float inv_normalize;     // 1 / normalize_by
-  // DP-FTRL: mode 0 = iid Gaussian, 1 = BLT inverse (scale s_j, decay d_j), 2 = banded inverse
+  // DP-FTRL: mode 0 = iid Gaussian, 1 = BLT inverse (scale s_j, decay d_j), 2 = banded inverse (IIR),
+  // 3 = FIR over past raw draws
   int ftrl_mode, nbuf, ring_head;
   float coef[16];          // BLT: s_0..s_{nbuf-1}, d_0..d_{nbuf-1}; banded: c_0, c_1..c_{bands-1}
   // AdamW-BC
@@ -196,6 +197,17 @@ shard_step_kernel(const ShardStepParams p) {
           }
           x = (z[j] - corr) / p.coef[0];
           p.ftrl_state[p.ring_head * p.n + k] = x;
+        } else if (p.ftrl_mode == 3) {
+          // FIR on the raw noise (banded INVERSE factor, lambda-CGD):  x_t = c_0 z_t + sum_{b>=1} c_b z_{t-b};
+          // the ring keeps the previous nbuf raw draws
+          float acc = p.coef[0] * z[j];
+          for (int b = 1; b <= p.nbuf; ++b) {
+            int slot = p.ring_head - b;
+            if (slot < 0) slot += p.nbuf;
+            acc += p.coef[b] * p.ftrl_state[slot * p.n + k];
+          }
+          p.ftrl_state[p.ring_head * p.n + k] = z[j];
+          x = acc;
         }
       }
       const float g = (g8[j] + p.noise_std * x) * p.inv_normalize;

@@ -137,8 +137,9 @@ class ShardedDPOptimizer:
     """Noise + AdamW-BC over the owner's shard, fused with the parameter all-gather.
 
     ``mechanism`` is ``None`` (iid Gaussian, DP-SGD) or a dict describing a DP-FTRL inverse:
-    ``{"kind": "blt", "scale": [...], "decay": [...]}`` or ``{"kind": "banded", "coef": [...]}``
-    (``coef[0]`` the diagonal; the state holds ``len(coef) − 1`` previous outputs).
+    ``{"kind": "blt", "scale": [...], "decay": [...]}``, ``{"kind": "banded", "coef": [...]}``
+    (``coef[0]`` the diagonal of ``C``; the state holds ``len(coef) − 1`` previous outputs) or
+    ``{"kind": "fir", "coef": [...]}`` (taps of a banded ``C⁻¹``; the state holds previous raw draws).
     """
 
     def __init__(self, space: FlatSpace, config: DPStepConfig, *, key: RngKey, mechanism: dict | None = None):
@@ -161,6 +162,11 @@ class ShardedDPOptimizer:
                 if not 2 <= len(c) <= 9 or c[0] == 0:
                     raise ValueError("banded inverse needs 2..9 coefficients with a non-zero diagonal")
                 self.mode, self.nbuf, self.coef = 2, len(c) - 1, c
+            elif mechanism["kind"] == "fir":
+                c = [float(x) for x in mechanism["coef"]]
+                if not 2 <= len(c) <= 9:
+                    raise ValueError("FIR noise needs 2..9 taps")
+                self.mode, self.nbuf, self.coef = 3, len(c) - 1, c
             else:
                 raise ValueError(f"unknown mechanism kind {mechanism['kind']!r}")
             self.ftrl_state = torch.zeros(self.nbuf, space.shard, dtype=torch.float32, device=space.group.device)
@@ -189,7 +195,7 @@ class ShardedDPOptimizer:
             seed=seed, noise_std=noise_std, inv_normalize=1.0 / normalize_by, lr=lr, betas=(b1, b2),
             eps=self.cfg.eps, weight_decay=self.cfg.weight_decay, step=t, phi_hat=phi_hat,
             decoupled_wd=self.cfg.decoupled_weight_decay, ftrl_state=self.ftrl_state, ftrl_mode=self.mode,
-            ftrl_coef=self.coef, nbuf=self.nbuf, ring_head=(self.step_count % self.nbuf) if self.mode == 2 else 0,
+            ftrl_coef=self.coef, nbuf=self.nbuf, ring_head=(self.step_count % self.nbuf) if self.mode in (2, 3) else 0,
             noisy_out=noisy_out, skip_update=skip_update)
         g.barrier()
         self.step_count = t

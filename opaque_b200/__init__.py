@@ -9,3 +9,5 @@ the B200 layers: ``ops`` (hand-written sm_100a kernels), ``parallel``
 ``engine`` (reference and fused DP gradient engines) and ``models``.
 """
 __version__ = "0.1.0"
+
+from .serialization import _tensors as _tensor_serializers  # noqa: E402,F401  (registers tensor / array leaves)

@@ -326,7 +326,8 @@ class BandMfStrategy(MfStrategy):
             raise ValueError("bands must be >= 1")
 
     def coefficients(self, n):
-        return np.array(optimize_banded(n, min(self.bands, n)))
+        # optimised for one participation per band window (b-min-sep use); more participations only rescale
+        return np.array(optimize_banded(n, min(self.bands, n), 1, 1))
 
 
 @dataclasses.dataclass(frozen=True)
@@ -335,7 +336,7 @@ class BltStrategy(MfStrategy):
     momentum: float = 1.0
     lr_schedule: Any = None
     min_sep_hint: int = 1
-    max_participations_hint: int | None = None
+    max_participations_hint: int | None = 1
 
     def __post_init__(self):
         if not 1 <= self.max_buffers <= 16:

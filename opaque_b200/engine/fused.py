@@ -22,9 +22,10 @@ applies AdamW-BC on each owner's shard.
 Sensitivity.  ``c_i`` is shrunk by ``2⁻⁸ + 2⁻¹²`` relative before use: the GEMM applies it after a
 round-toward-zero to bf16 and the scaled operand is rounded to nearest bf16 (≤ 2⁻⁹ relative), and
 the ghost norm carries fp32 accumulation error; the stored contribution of one record therefore
-stays within ``C``.  A parameter used twice in one pass (tied embedding / output head) is bounded by
-``(‖g_a‖ + ‖g_b‖)²`` — an upper bound on its true squared norm, so clipping stays valid
-(slightly conservative).
+stays within ``C``.  A weight tied between the input embedding and the output head gets its exact
+norm (the cross term ``2⟨g_emb, g_head⟩`` is computed from the captured tensors); any other parameter
+used more than once in a pass is bounded by ``(Σ‖g_piece‖)²``, an upper bound on its true squared norm,
+so clipping stays valid (slightly conservative).
 
 The reference has no counterpart: it materialises per-example gradients with
 ``vmap(grad)`` (packages/opaque-engine/src/opaque/api/engine/clipping/_clipped_fun.py:207-350) and
@@ -119,6 +120,8 @@ class Capture:
                  xa_pad: torch.Tensor, g2d: torch.Tensor, q_pad: torch.Tensor) -> None:
         """Per-example ``dA_i = q_iᵀ x_i`` (``[r, in]``) and ``dB_i = g_iᵀ (s·xa)_i`` (``[out, r]``)."""
         sa, sb = self.engine.slot_of(lora_a), self.engine.slot_of(lora_b)
+        if not (sa.direct and sb.direct):
+            raise RuntimeError("LoRA factors must be direct parameters of the flat space")
         r, d_in = lora_a.shape
         stride = self.pe.stride(0)
         ops.wgrad_clip(x2d, q_pad, self.pe, seg_offsets=self.seg, num_groups=self.batch_size, out_offset=sa.offset,
@@ -127,6 +130,26 @@ class Capture:
         ops.wgrad_clip(g2d, xa_pad, self.pe, seg_offsets=self.seg, num_groups=self.batch_size, out_offset=sb.offset,
                        ldm=r, ldn=1, n_valid=r, accumulate=False, group_stride=stride, block_n=64,
                        status=self.status)
+
+    def _tied_cross_term(self, slot_name: str) -> torch.Tensor | None:
+        """``<g_embedding, g_head>`` per example for a weight used as input embedding AND output head.
+
+        With head inputs ``h`` / output gradients ``dlogits`` and embedding output gradients ``e``:
+        ``<g_emb, g_head> = sum_{t, t'} dlogits[t', ids[t]] * <e_t, h_t'>`` — one gather and one
+        ``T x T x d`` batched product per example.
+        """
+        lin = [r for r in self.records if r[0] == "linear" and r[1].name == slot_name]
+        emb = [r for r in self.records if r[0] == "embedding" and r[1].name == slot_name]
+        if len(lin) != 1 or len(emb) != 1:
+            return None
+        _, _, dlogits, hidden = lin[0]
+        _, _, e, ids = emb[0]
+        B, T = self.batch_size, self.tokens
+        if dlogits.shape[0] != B * T or e.shape[0] != B * T:
+            return None
+        picked = dlogits.view(B, T, -1).gather(2, ids.view(B, 1, T).expand(B, T, T))        # [b, t', t]
+        inner = torch.bmm(hidden.view(B, T, -1), e.view(B, T, -1).transpose(1, 2))           # [b, t', t]
+        return (picked.float() * inner.float()).sum(dim=(1, 2))
 
     # ---- after backward -------------------------------------------------------------------------
     @torch.no_grad()
@@ -143,8 +166,13 @@ class Capture:
             single = [rows[0] for rows in by_slot.values() if len(rows) == 1]
             if single:
                 norm2 += self.parts[single].sum(0) if len(single) < n_parts else self.parts[:n_parts].sum(0)
-            for rows in by_slot.values():
-                if len(rows) > 1:   # shared parameter: (sum of the pieces' norms)^2 bounds the true squared norm
+            for name, rows in by_slot.items():
+                if len(rows) == 1:
+                    continue
+                cross = self._tied_cross_term(name) if len(rows) == 2 else None
+                if cross is not None:     # exact: |a + b|^2 = |a|^2 + |b|^2 + 2<a, b>
+                    norm2 += self.parts[rows].sum(0) + 2.0 * cross
+                else:                     # (sum of the pieces' norms)^2 bounds the true squared norm
                     norm2 += self.parts[rows].clamp_min(0).sqrt().sum(0) ** 2
         norms = norm2.clamp_min(0).sqrt()
         if mode == "auto":

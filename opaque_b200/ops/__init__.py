@@ -87,6 +87,17 @@ def wgrad_clip(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, ro
         splits = pick_splits(tiles, T // max(num_groups, 1), sms) if accumulate else 1
     if not accumulate and splits != 1:
         raise ValueError("store mode cannot split K")
+    n_lim = min(N, n_valid) if n_valid else N
+    if out is not None:
+        if out.dtype != torch.float32:
+            raise TypeError("the destination must be fp32")
+        last_group = int(group_out_offset.max()) if group_out_offset is not None else (num_groups - 1) * group_stride
+        hi = out_offset + last_group + (M - 1) * ldm + (n_lim - 1) * ldn
+        room = out.untyped_storage().nbytes() // 4 - out.storage_offset()
+        if min(out_offset, ldm, ldn) < 0 or hi >= room:
+            raise ValueError(f"wgrad_clip would write element {hi} of a destination holding {room}")
+    elif peer_table is None or shard_elems <= 0:
+        raise ValueError("give either a destination tensor or a peer table with shard_elems")
     rc = lib.load().ob_wgrad_clip(
         a.data_ptr(), b.data_ptr(), T, M, N, a.stride(0), b.stride(0), lib.ptr(row_scale), lib.ptr(seg_offsets),
         num_groups, splits, lib.ptr(out), lib.ptr(peer_table), shard_elems, lib.ptr(group_out_offset), group_stride,
@@ -159,6 +170,8 @@ def philox_normal_add_(x: torch.Tensor, *, seed: int, offset: int = 0, std: floa
 
 def rows_sumsq(g: torch.Tensor, norm2: torch.Tensor) -> None:
     """``norm2[e] += Σ_p g[e, p]²`` for fp32 ``g [E, P]``."""
+    if g.dtype != torch.float32 or g.stride(1) != 1 or norm2.numel() < g.shape[0]:
+        raise ValueError("rows_sumsq needs a row-major fp32 matrix and one accumulator per row")
     rc = lib.load().ob_rows_sumsq(g.data_ptr(), g.shape[0], g.shape[1], g.stride(0), norm2.data_ptr(), lib.sm_count(),
                                   lib.stream())
     lib.check(rc, "rows_sumsq")
@@ -167,6 +180,10 @@ def rows_sumsq(g: torch.Tensor, norm2: torch.Tensor) -> None:
 def clip_weighted_sum(g: torch.Tensor, c: torch.Tensor, out: torch.Tensor | None, *, flat_offset: int = 0,
                       peer_table: torch.Tensor | None = None, shard_elems: int = 0) -> None:
     """``flat[flat_offset + p] += Σ_e c[e]·g[e, p]`` (to the owning rank when a peer table is given)."""
+    if out is not None and flat_offset + g.shape[1] > out.numel():
+        raise ValueError("clip_weighted_sum would write past the end of the destination")
+    if c.numel() < g.shape[0]:
+        raise ValueError("one clip factor per example is required")
     rc = lib.load().ob_clip_weighted_sum(g.data_ptr(), c.data_ptr(), g.shape[0], g.shape[1], g.stride(0),
                                          lib.ptr(out), lib.ptr(peer_table), shard_elems, flat_offset, lib.sm_count(),
                                          lib.stream())
@@ -179,6 +196,8 @@ def embedding_wgrad(g: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None
     _need_bf16(g)
     if ids.dtype != torch.int64:
         raise TypeError("ids must be int64")
+    if ids.numel() != g.shape[0]:
+        raise ValueError("one id per gradient row is required")
     rc = lib.load().ob_embedding_wgrad(g.data_ptr(), ids.data_ptr(), lib.ptr(row_scale), g.shape[0], g.shape[1],
                                        g.stride(0), lib.ptr(out), lib.ptr(peer_table), shard_elems, flat_offset,
                                        lib.sm_count(), lib.stream())

@@ -50,13 +50,18 @@ class Slot:
     direct: bool
 
 
+def default_direct(name: str, p: torch.nn.Parameter) -> bool:
+    """Vectors (biases, norm weights) and LoRA factors get materialised per-example gradients."""
+    return p.ndim < 2 or "lora_" in name.rsplit(".", 1)[-1]
+
+
 class FlatSpace:
     """Offsets of every trainable parameter in the flat space, and the peer buffers behind it."""
 
     def __init__(self, named_params: Sequence[tuple[str, torch.nn.Parameter]], group: PeerGroup, *,
                  direct: Callable[[str, torch.nn.Parameter], bool] | None = None):
         self.group = group
-        is_direct = direct or (lambda n, p: p.ndim < 2)
+        is_direct = direct or default_direct
         ordered = sorted(named_params, key=lambda np_: (not is_direct(*np_),))   # stable: direct first
         self.slots: dict[str, Slot] = {}
         off = 0

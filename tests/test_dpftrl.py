@@ -1,0 +1,127 @@
+"""DP-FTRL strategies vs dense materialisation, noise engine, samplers, accounting, codec."""
+import json
+import math
+
+import numpy as np
+import pytest
+import torch
+from scipy.linalg import toeplitz
+
+import opaque_b200.accounting as acc
+from opaque_b200.dpftrl import (BallsInBinsSampler, BMinSepSampler, CyclicPoissonSampler, SequentialBatchSampler,
+                                band_mf_strategy, bisr_strategy, blt_strategy, bsr_strategy, identity_strategy,
+                                lambda_cgd_strategy, mf_gaussian_noise)
+from opaque_b200.dpftrl import accounting as fa
+from opaque_b200.dpftrl import noise as N
+from opaque_b200.random import key
+from opaque_b200.scheduling import cosine_schedule
+from opaque_b200.serialization import from_state_dict, state_dict
+from opaque_b200.types import clipped
+
+STRATEGIES = [identity_strategy(), band_mf_strategy(bands=4), bsr_strategy(bandwidth=4, alpha=0.99, beta=0.9),
+              bisr_strategy(bandwidth=4), lambda_cgd_strategy(lambda_=0.5, normalized=False), blt_strategy(max_buffers=3)]
+
+
+@pytest.mark.parametrize("s", STRATEGIES, ids=lambda s: type(s).__name__)
+def test_streaming_inverse_matches_dense(s):
+    n = 48
+    c = np.pad(s.coefficients(n), (0, n))[:n]
+    C = np.tril(toeplitz(c))
+    Cinv = s.streaming_matrix(n).materialize(n)
+    assert np.abs(Cinv @ C - np.eye(n)).max() < 1e-6
+    rn = s.streaming_matrix(n).row_norms_squared(n)
+    assert np.allclose(rn, (Cinv ** 2).sum(1), rtol=1e-6)
+    # sensitivity: brute force over single participation = max column norm
+    assert math.isclose(s.sensitivity(n, n, 1), math.sqrt((C ** 2).sum(0).max()), rel_tol=1e-6)
+    assert s.sensitivity(n, 8) <= s.sensitivity(n, 1) + 1e-9
+
+
+def test_sqrt_coefficients_and_bsr_closed_form():
+    r = N.sqrt_coefs(6)
+    assert np.allclose(r, [1, 0.5, 0.375, 0.3125, 0.2734375, 0.24609375])
+    assert np.allclose(np.convolve(r, r)[:6], 1.0)                       # (1-x)^{-1/2} squared = 1/(1-x)
+    assert np.allclose(np.convolve(N.inv_sqrt_coefs(6), r)[:6], [1, 0, 0, 0, 0, 0], atol=1e-12)
+    c = bsr_strategy(bandwidth=5, alpha=1.0, beta=0.0).coefficients(20)
+    assert np.allclose(c, r[:5])
+
+
+def test_optimised_strategies_beat_identity():
+    n = 128
+    def loss(s):
+        inv = N.inverse_coef(s.coefficients(n), n)
+        return N.toeplitz_sensitivity_squared(s.coefficients(n), n, 1, 1) * N.prefix_workload_error(inv)
+    base = loss(identity_strategy())
+    assert loss(band_mf_strategy(bands=8)) < 0.5 * base
+    assert loss(blt_strategy(max_buffers=3)) < 0.5 * base
+
+
+def test_mf_noise_statistics_horizon_and_constant_norm():
+    s = blt_strategy(max_buffers=2)
+    nf, st = mf_gaussian_noise({"w": torch.zeros(50_000)}, s, n_steps=3, noise_multiplier=2.0, key=key(1))
+    rn = s.streaming_matrix(3).row_norms_squared(3)
+    for t in range(3):
+        out, st = nf(clipped({"w": torch.zeros(50_000)}, 0.5), st)
+        assert math.isclose(out.noise_stddev, 1.0 * math.sqrt(rn[t]), rel_tol=1e-9)
+        assert abs(float(out.pytree["w"].std()) - out.noise_stddev) < 0.02
+    with pytest.raises(RuntimeError):
+        nf(clipped({"w": torch.zeros(50_000)}, 0.5), st)
+    nf, st = mf_gaussian_noise({"w": torch.zeros(4)}, s, n_steps=3, noise_multiplier=1.0, key=key(1))
+    _, st = nf(clipped({"w": torch.zeros(4)}, 1.0), st)
+    with pytest.raises(ValueError):
+        nf(clipped({"w": torch.zeros(4)}, 2.0), st)
+
+
+def test_mf_noise_equals_dense_cinv_times_z():
+    s = band_mf_strategy(bands=3)
+    n = 6
+    nf, st = mf_gaussian_noise({"w": torch.zeros(5)}, s, n_steps=n, noise_multiplier=1.0, key=key(3))
+    outs = []
+    for t in range(n):
+        out, st = nf(clipped({"w": torch.zeros(5)}, 1.0), st)
+        outs.append(out.pytree["w"])
+    X = torch.stack(outs).double().numpy()
+    C = np.tril(toeplitz(np.pad(s.coefficients(n), (0, n))[:n]))
+    Z = C @ X                                         # recover the iid draws; they must be the keyed normals
+    nf2, st2 = mf_gaussian_noise({"w": torch.zeros(5)}, identity_strategy(), n_steps=n, noise_multiplier=1.0, key=key(3))
+    for t in range(n):
+        z, st2 = nf2(clipped({"w": torch.zeros(5)}, 1.0), st2)
+        assert np.allclose(Z[t], z.pytree["w"].double().numpy(), atol=1e-5)
+
+
+def test_strategy_codec_and_accounting_round_trip():
+    s = band_mf_strategy(bands=4, lr_schedule=cosine_schedule(1.0, 0.1, 100))
+    wire = N.strategy_to_wire(s)
+    assert wire["type"] == "BandMfStrategy" and wire["lr_schedule"]["__opaque_recipe__"] == "CosineSchedule"
+    assert N.strategy_from_wire(json.loads(json.dumps(wire))) == s
+    p = fa.mf_gaussian(2.0, band_mf_strategy(bands=4), n_steps=64, min_sep=4)
+    a = acc.Accountant()
+    a |= fa.per_step(p) * 64
+    b = acc.Accountant.from_state_dict(json.loads(a.to_json()))
+    assert math.isclose(a.epsilon_at(1e-5), b.epsilon_at(1e-5))
+    # one Gaussian with multiplier sigma / sensitivity
+    eff = 2.0 / band_mf_strategy(bands=4).sensitivity(64, 4)
+    from opaque_b200.dpsgd.accounting import gaussian
+    assert math.isclose(p.epsilon_at(1e-5), gaussian(eff).epsilon_at(1e-5), rel_tol=1e-9)
+    amp = fa.poisson(p, 0.1, n_steps=64)
+    assert amp.epsilon_at(1e-5) < p.epsilon_at(1e-5)
+
+
+def test_samplers_participation_patterns_and_resume():
+    cyc = CyclicPoissonSampler(range(400), 1.0, bands=4, n_steps=8, key=key(1))
+    batches = list(cyc)
+    assert sorted(batches[0]) == list(range(100)) and sorted(batches[5]) == list(range(100, 200))
+    bms = BMinSepSampler(range(50), 3, 1.0, 6, key=key(2))
+    b = list(bms)
+    assert len(b[0]) == 50 and len(b[1]) == 0 and len(b[2]) == 0 and len(b[3]) == 50
+    bnb = BallsInBinsSampler(range(90), 3, n_steps=6, key=key(3))
+    b = list(bnb)
+    assert sorted(b[0] + b[1] + b[2]) == list(range(90)) and b[0] == b[3]
+    seq = SequentialBatchSampler(range(10), 4, n_steps=5)
+    assert list(seq) == [[0, 1, 2, 3], [4, 5, 6, 7], [0, 1, 2, 3], [4, 5, 6, 7], [0, 1, 2, 3]] and seq.min_sep == 2
+    s = CyclicPoissonSampler(range(400), 0.3, bands=2, n_steps=10, key=key(7))
+    it = iter(s)
+    next(it), next(it), next(it)
+    sd = state_dict(s)
+    expect = next(it)
+    s2 = from_state_dict(CyclicPoissonSampler(range(400), 0.3, bands=2, n_steps=10, key=key(7)), sd)
+    assert next(iter(s2)) == expect

@@ -39,6 +39,7 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--config", default="llama8b-lora", choices=["llama8b-lora", "gpt2", "llama-tiny"])
     ap.add_argument("--microbatch", type=int, default=0)
     ap.add_argument("--per-gpu-batch", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=0, help="truncate the model (profiling only; the JSON says so)")
     return ap.parse_args()
 
 
@@ -105,10 +106,13 @@ def main() -> None:
     torch.manual_seed(1234)
     if args.config == "llama8b-lora":
         seq, per_gpu, mb, frac, vocab = 1024, 64, 16, 0.5, 128256
-        model = LlamaForCausalLM(LlamaConfig.llama3_8b(), device=dev)
+        cfg8 = LlamaConfig.llama3_8b()
+        if args.layers:
+            cfg8.num_hidden_layers = args.layers
+        model = LlamaForCausalLM(cfg8, device=dev)
         model.add_lora(16, 32.0)
         dp = dict(clipping_norm=1.0, noise_multiplier=0.7, lr=2e-4)
-        name, par = "Llama-3-8B (LoRA r16 a32 on q/k/v/o, base frozen)", "dp"
+        name, par = "Llama-3-8B (LoRA r16 a32 on q/k/v/o, base frozen)" + (f" TRUNCATED to {args.layers} layers" if args.layers else ""), "dp"
     elif args.config == "gpt2":
         seq, per_gpu, mb, frac, vocab = 512, 128, 32, 1.0, 50257
         model = GPT2LMHeadModel(GPT2Config.small(), device=dev)

@@ -1,0 +1,127 @@
+"""Kernel micro-benchmarks with roofline fractions (CUDA events, warm-up, L2-exceeding inputs).
+
+  python bench_kernels.py                      # every case at its benchmark size
+  python bench_kernels.py --case wgrad --small # one small launch set, sized for an ncu capture
+
+Each line is JSON: achieved TFLOP/s or GB/s and the fraction "of measured" peak, where the peaks come from
+MEASURED_PEAKS.json next to this file (cuBLAS bf16 burst and a STREAM-style copy), else the documented fallback
+(1590 TFLOP/s, 6650 GB/s, marked "of fallback").
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def peaks():
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return p["bf16_tflops"], p["hbm_gbs"], "of measured"
+    return 1590.0, 6650.0, "of fallback"
+
+
+def timeit(fn, iters=20, warm=5, flush=None):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.add_(1.0)                      # > L2-sized write between timed launches
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    return total / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="all")
+    ap.add_argument("--small", action="store_true", help="one or two launches of a small case (for ncu)")
+    args = ap.parse_args()
+    from opaque_b200 import ops
+    from opaque_b200.ops.functional import cross_entropy_fused_
+    dev = torch.device("cuda", 0)
+    tf_peak, bw_peak, tag = peaks()
+    flush = torch.zeros(64 * 1024 * 1024, device=dev)     # 256 MB > 126 MB L2
+    st = ops.StatusWord(dev)
+    iters, warm = (1, 1) if args.small else (20, 5)
+
+    def emit(name, ms, flops=None, bytes_=None, **extra):
+        row = {"kernel": name, "ms": round(ms, 4), **extra}
+        if flops:
+            row["tflops"] = round(flops / ms / 1e9, 1)
+            row["frac_" + tag.replace(" ", "_")] = round(flops / ms / 1e9 / tf_peak, 3)
+        if bytes_:
+            row["GBs"] = round(bytes_ / ms / 1e6, 1)
+            row["frac_" + tag.replace(" ", "_")] = round(bytes_ / ms / 1e6 / bw_peak, 3)
+        print(json.dumps(row), flush=True)
+
+    want = lambda c: args.case in ("all", c)
+    if want("wgrad"):
+        shapes = [(8192, 2048, 1024)] if args.small else [(16384, 3072, 768), (16384, 768, 3072), (32768, 4096, 4096), (16384, 8192, 2048)]
+        for T, M, N in shapes:
+            a = torch.randn(T, M, device=dev).bfloat16()
+            b = torch.randn(T, N, device=dev).bfloat16()
+            out = torch.zeros(M * N, device=dev)
+            sc = torch.rand(T, device=dev)
+            fl = 2.0 * T * M * N
+            emit(f"wgrad_clip scaled {T}x{M}x{N}", timeit(lambda: ops.wgrad_clip(a, b, out, ldm=N, row_scale=sc, status=st), iters, warm, flush), fl)
+            emit(f"wgrad_clip unscaled {T}x{M}x{N}", timeit(lambda: ops.wgrad_clip(a, b, out, ldm=N, status=st), iters, warm, flush), fl)
+            if not args.small:
+                emit(f"cublas a^T b (bf16 out) {T}x{M}x{N}", timeit(lambda: torch.matmul(a.t(), b), iters, warm, flush), fl)
+                emit(f"prescale pass + cublas {T}x{M}x{N}", timeit(lambda: torch.matmul((a * sc[:, None].bfloat16()).t(), b), iters, warm, flush), fl)
+    if want("ghost"):
+        shapes = [(8, 512, 768, 768)] if args.small else [(32, 512, 768, 3072), (16, 1024, 2048, 8192), (16, 1024, 4096, 4096)]
+        for B, T, Da, Dg in shapes:
+            a = torch.randn(B * T, Da, device=dev).bfloat16()
+            g = torch.randn(B * T, Dg, device=dev).bfloat16()
+            n2 = torch.zeros(B, device=dev)
+            nt = (T + 127) // 128
+            fl = 2.0 * B * (nt * (nt + 1) / 2) * 128 * 128 * (Da + Dg)
+            emit(f"ghost_norm {B}x{T}x{Da}x{Dg}", timeit(lambda: ops.ghost_norm(a, g, n2, T, status=st), iters, warm, flush), fl)
+    if want("lora"):
+        E, T, M, r = (4, 1024, 4096, 16) if args.small else (16, 1024, 4096, 16)
+        a = torch.randn(E * T, M, device=dev).bfloat16()
+        b = torch.zeros(E * T, 64, device=dev, dtype=torch.bfloat16)
+        b[:, :r] = torch.randn(E * T, r, device=dev).bfloat16()
+        seg = torch.arange(0, (E + 1) * T, T, device=dev, dtype=torch.int32)
+        out = torch.zeros(E, M * r, device=dev)
+        ms = timeit(lambda: ops.wgrad_clip(a, b, out, seg_offsets=seg, num_groups=E, ldm=1, ldn=M, n_valid=r, accumulate=False,
+                                           group_stride=M * r, block_n=64, status=st), iters, warm, flush)
+        emit(f"per-example LoRA wgrad {E}x{T}x{M}xr{r}", ms, bytes_=a.numel() * 2 + b.numel() * 2 + out.numel() * 4)
+    if want("rmsnorm"):
+        rows = 8192 if args.small else 65536
+        x = torch.randn(rows, 4096, device=dev).bfloat16()
+        w = torch.ones(4096, device=dev).bfloat16()
+        emit(f"rms_norm fwd {rows}x4096", timeit(lambda: ops.rms_norm(x, w), iters, warm, flush), bytes_=2 * x.numel() * 2)
+    if want("swiglu"):
+        rows = 4096 if args.small else 16384
+        g = torch.randn(rows, 14336, device=dev).bfloat16()
+        u = torch.randn_like(g)
+        emit(f"swiglu fwd {rows}x14336", timeit(lambda: ops.swiglu(g, u), iters, warm, flush), bytes_=3 * g.numel() * 2)
+    if want("ce"):
+        rows = 1024 if args.small else 4096
+        z = torch.randn(rows, 128256, device=dev).bfloat16()
+        lab = torch.randint(0, 128256, (rows,), device=dev)
+        emit(f"cross_entropy fwd+dlogits {rows}x128256", timeit(lambda: cross_entropy_fused_(z, lab), iters, warm, flush), bytes_=2 * z.numel() * 2)
+    if want("shard_step"):
+        n = (16_000_000 if args.small else 124_000_000) // 8 * 8
+        grad, master = torch.zeros(n, device=dev), torch.randn(n, device=dev)
+        m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        pl = torch.zeros(n, device=dev, dtype=torch.bfloat16)
+        emit(f"shard_step noise+AdamW-BC {n}", timeit(lambda: ops.shard_step(grad=grad, master=master, m=m, v=v, params_local=pl, seed=1, noise_std=1.0, step=2),
+                                                      iters, warm, flush), bytes_=n * (4 * 4 * 2 + 2))
+    if st.read():
+        raise SystemExit(f"a device wait timed out (status {st.read()})")
+
+
+if __name__ == "__main__":
+    main()

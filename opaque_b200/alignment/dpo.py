@@ -1,0 +1,193 @@
+"""Per-example DPO-family preference losses (17 heads) and their dispatcher.
+
+Every head maps per-example log-ratios (policy minus reference log-probability of the chosen / rejected
+response) to one loss per preference PAIR, which is the privacy unit of DP-DPO: clipping acts on the gradient
+of one pair.  All functions are elementwise, so they work on ``(B,)`` tensors and on 0-dim scalars.
+
+Parity: packages/opaque-alignment/src/opaque/api/alignment/dpo/loss/_{sigmoid,hinge,ipo,apo,bco,chosen_nll,
+discopop,exo,f_divergence,ld_dpo,mpo,nca,orpo,robust,simpo,sppo,wpo}.py and
+packages/opaque-transformers/src/opaque/api/transformers/trl/_dpo_trainer.py:878 (dispatch, mixtures).
+"""
+from __future__ import annotations
+
+import math
+from collections.abc import Sequence
+
+import torch
+import torch.nn.functional as F
+
+
+def sigmoid_loss(c, r, *, beta: float, label_smoothing: float = 0.0):
+    """DPO (Rafailov et al. 2023): ``−logσ(βΔ)(1−ε) − logσ(−βΔ)ε``."""
+    d = c - r
+    return -F.logsigmoid(beta * d) * (1 - label_smoothing) - F.logsigmoid(-beta * d) * label_smoothing
+
+
+def hinge_loss(c, r, *, beta: float):
+    """SLiC-style hinge: ``relu(1 − βΔ)``."""
+    return torch.relu(1 - beta * (c - r))
+
+
+def ipo_loss(c, r, *, beta: float):
+    """IPO (Azar et al. 2023): ``(Δ − 1/(2β))²`` (log-ratios are expected length-averaged)."""
+    return (c - r - 1 / (2 * beta)) ** 2
+
+
+def exo_loss(c, r, *, beta: float, label_smoothing: float = 1e-3):
+    """EXO pairwise (Ji et al. 2024): reverse KL between the preference and the label distribution."""
+    eps = label_smoothing if label_smoothing > 0 else 1e-3
+    d = beta * (c - r)
+    return (torch.sigmoid(d) * (F.logsigmoid(d) - math.log(1 - eps))
+            + torch.sigmoid(-d) * (F.logsigmoid(-d) - math.log(eps)))
+
+
+def nca_loss(c, r, *, beta: float):
+    """NCA pairwise (Chen et al. 2024)."""
+    return -F.logsigmoid(beta * c) - 0.5 * F.logsigmoid(-beta * c) - 0.5 * F.logsigmoid(-beta * r)
+
+
+def robust_loss(c, r, *, beta: float, label_smoothing: float = 0.1):
+    """Robust DPO (Chowdhury et al. 2024): unbiased under label-flip probability ε."""
+    if not 0 <= label_smoothing < 0.5:
+        raise ValueError("robust DPO needs label_smoothing in [0, 0.5)")
+    d = beta * (c - r)
+    return (-F.logsigmoid(d) * (1 - label_smoothing) + F.logsigmoid(-d) * label_smoothing) / (1 - 2 * label_smoothing)
+
+
+def bco_loss(c, r, *, beta: float, delta: float | torch.Tensor = 0.0):
+    """BCO pairwise (Jung et al. 2024); ``delta`` is the running mean reward (public state)."""
+    return -F.logsigmoid(beta * c - delta) - F.logsigmoid(-(beta * r - delta))
+
+
+def sppo_loss(c, r, *, beta: float):
+    """SPPO hard-label (Wu et al. 2024)."""
+    return (c - 0.5 / beta) ** 2 + (r + 0.5 / beta) ** 2
+
+
+def apo_zero_loss(c, r, *, beta: float):
+    """APO-zero (D'Oosterlinck et al. 2024): push chosen up, rejected down."""
+    return 1 - torch.sigmoid(beta * c) + torch.sigmoid(beta * r)
+
+
+def apo_down_loss(c, r, *, beta: float):
+    """APO-down: push both down, the rejected one further."""
+    return torch.sigmoid(beta * c) + 1 - torch.sigmoid(beta * (c - r))
+
+
+def discopop_loss(c, r, *, beta: float, tau: float = 0.05):
+    """DiscoPOP (Lu et al. 2024): log-ratio-modulated blend of logistic and exponential losses."""
+    d = beta * (c - r)
+    mod = torch.sigmoid(d / tau)
+    cap = 80.0 if d.dtype in (torch.float32, torch.float64) else 10.0
+    return -F.logsigmoid(d) * (1 - mod) + torch.exp((-d).clamp(max=cap)) * mod
+
+
+def chosen_nll_loss(chosen_nll):
+    """SFT term on the chosen response (already a per-example mean NLL)."""
+    return chosen_nll
+
+
+def simpo_loss(chosen_avg_logp, rejected_avg_logp, *, beta: float, gamma: float = 0.5, label_smoothing: float = 0.0):
+    """SimPO (Meng et al. 2024): reference-free, length-normalised, with target margin ``γ/β``."""
+    d = beta * (chosen_avg_logp - rejected_avg_logp - gamma / beta)
+    return -F.logsigmoid(d) * (1 - label_smoothing) - F.logsigmoid(-d) * label_smoothing
+
+
+def orpo_loss(chosen_avg_logp, rejected_avg_logp, chosen_nll, *, lambda_: float = 1.0):
+    """ORPO (Hong et al. 2024): ``nll − λ·logσ(log odds ratio)``."""
+    log_odds = (chosen_avg_logp - rejected_avg_logp) - (torch.log1p(-torch.exp(chosen_avg_logp.clamp(max=-1e-7)))
+                                                        - torch.log1p(-torch.exp(rejected_avg_logp.clamp(max=-1e-7))))
+    return chosen_nll - lambda_ * F.logsigmoid(log_odds)
+
+
+def ld_dpo_logp(token_logps: torch.Tensor, mask: torch.Tensor, common_len: torch.Tensor | int, alpha: float):
+    """LD-DPO (Liu et al. 2024) sequence log-probability: tokens past the shorter response's length weigh ``α``."""
+    pos = torch.cumsum(mask.long(), dim=-1)
+    common = torch.as_tensor(common_len, device=mask.device).reshape(-1, 1) if token_logps.ndim > 1 else common_len
+    head = (pos <= common) & mask.bool()
+    tail = (pos > common) & mask.bool()
+    return (token_logps * head).sum(-1) + alpha * (token_logps * tail).sum(-1)
+
+
+def wpo_weight(chosen_token_logps, chosen_mask, rejected_token_logps, rejected_mask, chosen_probs_sq=None,
+               rejected_probs_sq=None):
+    """WPO (Zhou et al. 2024) pair weight ``exp(Σ adjusted avg logp)`` clamped to 1 (treated as a constant)."""
+    def avg(lp, m, sq):
+        lp_adj = lp if sq is None else lp - sq
+        return (lp_adj * m).sum(-1) / m.sum(-1).clamp_min(1)
+    w = torch.exp(avg(chosen_token_logps, chosen_mask, chosen_probs_sq) + avg(rejected_token_logps, rejected_mask, rejected_probs_sq))
+    return w.clamp(max=1.0).detach()
+
+
+def f_divergence_logits(c, r, *, kind: str = "reverse_kl", alpha: float = 0.5):
+    """Remap ``Δ`` for f-DPO (Wang et al. 2023): reverse KL (identity), JS or α-divergence."""
+    if kind == "reverse_kl":
+        return c - r
+    if kind == "js_divergence":
+        return (c - r) - (F.softplus(c) - F.softplus(r))
+    if kind == "alpha_divergence":
+        cap = 80.0
+        return (torch.exp((-alpha * r).clamp(max=cap)) - torch.exp((-alpha * c).clamp(max=cap))) / alpha
+    raise ValueError(f"unknown f-divergence {kind!r}")
+
+
+PAIR_HEADS = {"sigmoid": sigmoid_loss, "hinge": hinge_loss, "ipo": ipo_loss, "exo_pair": exo_loss, "nca_pair": nca_loss,
+              "robust": robust_loss, "bco_pair": bco_loss, "sppo_hard": sppo_loss, "apo_zero": apo_zero_loss,
+              "apo_down": apo_down_loss, "discopop": discopop_loss}
+ALL_LOSS_TYPES = tuple(PAIR_HEADS) + ("sft", "simpo", "orpo", "ld_dpo", "mpo", "wpo", "f_divergence")
+MPO_MIX = (("sigmoid", 0.8), ("bco_pair", 0.2), ("sft", 1.0))
+
+
+def dpo_loss(loss_type: str | Sequence[str], *, chosen_logratio, rejected_logratio, beta: float = 0.1,
+             label_smoothing: float = 0.0, loss_weights: Sequence[float] | None = None, chosen_nll=None,
+             chosen_avg_logp=None, rejected_avg_logp=None, bco_delta=0.0, discopop_tau: float = 0.05,
+             simpo_gamma: float = 0.5, orpo_lambda: float = 1.0, f_divergence_type: str = "reverse_kl",
+             f_alpha: float = 0.5, pair_weight=None):
+    """Dispatch one head or a weighted mixture of heads; returns one loss per pair."""
+    types = [loss_type] if isinstance(loss_type, str) else list(loss_type)
+    if types == ["mpo"]:
+        types, loss_weights = [t for t, _ in MPO_MIX], [w for _, w in MPO_MIX]
+    weights = list(loss_weights) if loss_weights is not None else [1.0] * len(types)
+    if len(weights) != len(types):
+        raise ValueError("loss_weights must match loss_type")
+    c, r = chosen_logratio, rejected_logratio
+    if f_divergence_type != "reverse_kl":
+        d = f_divergence_logits(c, r, kind=f_divergence_type, alpha=f_alpha)
+        c, r = d, torch.zeros_like(d)
+    total = 0.0
+    for t, w in zip(types, weights):
+        if t in ("sigmoid", "ld_dpo", "wpo", "f_divergence"):
+            term = sigmoid_loss(c, r, beta=beta, label_smoothing=label_smoothing)
+        elif t in ("robust", "exo_pair"):
+            term = PAIR_HEADS[t](c, r, beta=beta, label_smoothing=label_smoothing or (0.1 if t == "robust" else 1e-3))
+        elif t == "bco_pair":
+            term = bco_loss(c, r, beta=beta, delta=bco_delta)
+        elif t == "discopop":
+            term = discopop_loss(c, r, beta=beta, tau=discopop_tau)
+        elif t in PAIR_HEADS:
+            term = PAIR_HEADS[t](c, r, beta=beta)
+        elif t == "sft":
+            term = chosen_nll_loss(chosen_nll)
+        elif t == "simpo":
+            term = simpo_loss(chosen_avg_logp, rejected_avg_logp, beta=beta, gamma=simpo_gamma, label_smoothing=label_smoothing)
+        elif t == "orpo":
+            term = orpo_loss(chosen_avg_logp, rejected_avg_logp, chosen_nll, lambda_=orpo_lambda)
+        else:
+            raise ValueError(f"unknown DPO loss type {t!r}; expected one of {ALL_LOSS_TYPES}")
+        total = total + w * term
+    if pair_weight is not None:
+        total = total * pair_weight
+    return total
+
+
+def reward_margins(chosen_logratio, rejected_logratio, beta: float):
+    """Implicit rewards ``β·logratio`` and their margin / accuracy (logging metrics)."""
+    cr, rr = beta * chosen_logratio.detach(), beta * rejected_logratio.detach()
+    return {"rewards/chosen": cr, "rewards/rejected": rr, "rewards/margins": cr - rr,
+            "rewards/accuracies": (cr > rr).float()}
+
+
+__all__ = ["ALL_LOSS_TYPES", "PAIR_HEADS", "apo_down_loss", "apo_zero_loss", "bco_loss", "chosen_nll_loss",
+           "discopop_loss", "dpo_loss", "exo_loss", "f_divergence_logits", "hinge_loss", "ipo_loss", "ld_dpo_logp",
+           "nca_loss", "orpo_loss", "reward_margins", "robust_loss", "sigmoid_loss", "simpo_loss", "sppo_loss",
+           "wpo_weight"]

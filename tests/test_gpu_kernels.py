@@ -1,0 +1,293 @@
+"""sm_100a kernels against plain PyTorch fp32 references (run on a B200: ``pytest -m gpu``)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from opaque_b200.ops import lib
+    assert lib.available(), "the sm_100a kernel library must load on a GPU machine"
+    return torch.device("cuda", 0)
+
+
+def rel(x, y):
+    return float((x.float() - y.float()).norm() / (y.float().norm() + 1e-30))
+
+
+def rz_bf16(x):
+    """Round fp32 toward zero to bf16 precision (what the clip GEMM does to row factors)."""
+    return (x.contiguous().view(torch.int32) & -65536).view(torch.float32)
+
+
+@pytest.mark.parametrize("T,M,N,bn", [(256, 128, 64, 64), (512, 128, 128, 128), (1024, 256, 256, 256),
+                                      (1000, 200, 328, 256), (4096, 768, 3072, 256), (8192, 2048, 1024, 256)])
+def test_wgrad_clip_matches_reference(dev, T, M, N, bn):
+    from opaque_b200 import ops
+    torch.manual_seed(T + M)
+    st = ops.StatusWord(dev)
+    a = torch.randn(T, M, device=dev).bfloat16()
+    b = torch.randn(T, N, device=dev).bfloat16()
+    out = torch.zeros(M * N + 16, device=dev)
+    ops.wgrad_clip(a, b, out, out_offset=16, ldm=N, block_n=bn, status=st)
+    ref = ops.wgrad_clip_ref(a, b)[0]
+    assert st.read() == 0 and rel(out[16:].view(M, N), ref) < 2e-5 and float(out[:16].abs().max()) == 0
+    # accumulate on top, with per-row clip factors (bf16 round-toward-zero factor, bf16 product)
+    sc = torch.rand(T, device=dev)
+    ops.wgrad_clip(a, b, out, out_offset=16, ldm=N, row_scale=sc, block_n=bn, status=st)
+    scaled = (a.float() * rz_bf16(sc)[:, None]).bfloat16()
+    ref2 = ref + ops.wgrad_clip_ref(scaled, b)[0]
+    assert st.read() == 0 and rel(out[16:].view(M, N), ref2) < 2e-5
+    # every scaled product is bounded by the unrounded one up to one bf16 ulp
+    assert bool((scaled.float().abs() <= (a.float() * sc[:, None]).abs() * (1 + 2 ** -8)).all())
+
+
+def test_wgrad_clip_is_deterministic_without_split_k(dev):
+    from opaque_b200 import ops
+    a = torch.randn(2048, 256, device=dev).bfloat16()
+    b = torch.randn(2048, 256, device=dev).bfloat16()
+    outs = []
+    for _ in range(2):
+        o = torch.zeros(256 * 256, device=dev)
+        ops.wgrad_clip(a, b, o, ldm=256, splits=1)
+        outs.append(o)
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_wgrad_clip_grouped_store_modes(dev):
+    from opaque_b200 import ops
+    st = ops.StatusWord(dev)
+    for E, Tper, M, r in [(5, 96, 256, 16), (3, 128, 64, 8), (20, 64, 1024, 16)]:
+        a = torch.randn(E * Tper, M, device=dev).bfloat16()
+        b = torch.zeros(E * Tper, 64, device=dev, dtype=torch.bfloat16)
+        b[:, :r] = torch.randn(E * Tper, r, device=dev).bfloat16()
+        seg = torch.arange(0, (E + 1) * Tper, Tper, device=dev, dtype=torch.int32)
+        ref = ops.wgrad_clip_ref(a, b[:, :r], seg_offsets=seg, num_groups=E)
+        P = M * r + 64
+        out = torch.full((E, P), 7.0, device=dev)
+        ops.wgrad_clip(a, b, out, seg_offsets=seg, num_groups=E, out_offset=64, ldm=r, ldn=1, n_valid=r,
+                       accumulate=False, group_stride=P, block_n=64, status=st)
+        assert st.read() == 0 and rel(out[:, 64:].reshape(E, M, r), ref) < 1e-5 and bool((out[:, :64] == 7.0).all())
+        out = torch.full((E, P), 7.0, device=dev)
+        ops.wgrad_clip(a, b, out, seg_offsets=seg, num_groups=E, out_offset=64, ldm=1, ldn=M, n_valid=r,
+                       accumulate=False, group_stride=P, block_n=64, status=st)
+        assert st.read() == 0 and rel(out[:, 64:].reshape(E, r, M), ref.transpose(1, 2)) < 1e-5
+    with pytest.raises(ValueError):
+        ops.wgrad_clip(a, b, torch.zeros(10, device=dev), ldm=64)
+
+
+@pytest.mark.parametrize("B,T,Da,Dg", [(2, 128, 64, 64), (3, 256, 192, 320), (4, 512, 768, 3072), (2, 200, 800, 72)])
+def test_ghost_norm_matches_gram_and_direct(dev, B, T, Da, Dg):
+    from opaque_b200 import ops
+    st = ops.StatusWord(dev)
+    a = torch.randn(B * T, Da, device=dev).bfloat16()
+    g = torch.randn(B * T, Dg, device=dev).bfloat16()
+    n2 = torch.zeros(B, device=dev)
+    ops.ghost_norm(a, g, n2, T, status=st)
+    direct = torch.stack([(a[i * T:(i + 1) * T].float().t() @ g[i * T:(i + 1) * T].float()).pow(2).sum() for i in range(B)])
+    assert st.read() == 0 and rel(n2, ops.ghost_norm_ref(a, g, T)) < 2e-5 and rel(n2, direct) < 5e-5
+
+
+def test_ghost_norm_embedding_ids(dev):
+    from opaque_b200 import ops
+    B, T, D = 3, 256, 128
+    g = torch.randn(B * T, D, device=dev).bfloat16()
+    ids = torch.randint(0, 20, (B * T,), device=dev, dtype=torch.int32)
+    n2 = torch.zeros(B, device=dev)
+    ops.ghost_norm(None, g, n2, T, ids=ids)
+    assert rel(n2, ops.ghost_norm_ref(None, g, T, ids=ids)) < 1e-5
+
+
+def test_norm_activation_rope_kernels(dev):
+    from opaque_b200 import ops
+    torch.manual_seed(0)
+    x = torch.randn(512, 1024, device=dev).bfloat16()
+    w = (torch.randn(1024, device=dev) * 0.1 + 1).bfloat16()
+    r = torch.randn_like(x)
+    xg, wg = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    y = ops.rms_norm(xg, wg, 1e-5)
+    assert rel(y, ops.rms_norm_ref(x, w, 1e-5)) < 1e-4
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    (xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr).backward(dy.float())
+    # bf16 error floor: the kernel may not be worse than 3x the rounding of the fp32 result
+    floor = rel(xr.grad.bfloat16(), xr.grad)
+    assert rel(xg.grad, xr.grad) < 3 * floor + 1e-6 and rel(wg.grad, wr.grad) < 3 * rel(wr.grad.bfloat16(), wr.grad) + 1e-6
+    y2, s2 = ops.fused_add_rms_norm(x, r, w, 1e-5)
+    yr2, sr2 = ops.rms_norm_ref(x, w, 1e-5, residual=r)
+    assert rel(y2, yr2) < 1e-4 and torch.equal(s2, sr2)
+    y3 = ops.rms_norm(x, w, 1e-6, offset=1.0, casting_mode="gemma")
+    assert rel(y3, ops.rms_norm_ref(x, w, 1e-6, 1.0, "gemma")) < 1e-4
+    g = torch.randn(256, 2048, device=dev).bfloat16().requires_grad_(True)
+    u = torch.randn(256, 2048, device=dev).bfloat16().requires_grad_(True)
+    for act in (0, 1, 2):
+        g.grad = u.grad = None
+        h = ops.swiglu(g, u) if act == 0 else ops.geglu(g, u, approximate=(act == 2))
+        dh = torch.randn_like(h)
+        h.backward(dh)
+        gf, uf = g.detach().float().requires_grad_(True), u.detach().float().requires_grad_(True)
+        a = torch.nn.functional.silu(gf) if act == 0 else torch.nn.functional.gelu(gf, approximate="tanh" if act == 2 else "none")
+        (a * uf).backward(dh.float())
+        assert rel(h, a * uf) < 4e-3 and rel(g.grad, gf.grad) < 4e-3 and rel(u.grad, uf.grad) < 4e-3
+    q = torch.randn(2, 64, 8, 64, device=dev).bfloat16().requires_grad_(True)
+    k = torch.randn(2, 64, 2, 64, device=dev).bfloat16().requires_grad_(True)
+    cos, sin = ops.rope_tables(64, 128, 500000.0, device=dev)
+    pos = torch.randint(0, 128, (2, 64), device=dev)
+    for p in (None, pos):
+        q1, k1 = ops.rope_qk(q, k, cos, sin, p)
+        q2, k2 = ops.rope_qk_ref(q.detach(), k.detach(), cos, sin, p)
+        assert torch.equal(q1, q2) and torch.equal(k1, k2)
+    gq = torch.randn_like(q1)
+    q.grad = None
+    q1.backward(gq)
+    back, _ = ops.rope_qk_ref(gq, k.detach(), cos, sin, pos, sign=-1.0)
+    assert torch.equal(q.grad, back)
+
+
+@pytest.mark.parametrize("V,dt", [(1000, torch.bfloat16), (50257, torch.float32), (128256, torch.bfloat16)])
+def test_cross_entropy_kernel(dev, V, dt):
+    from opaque_b200 import ops
+    z = (torch.randn(64, V, device=dev) * 3).to(dt)
+    lab = torch.randint(0, V, (64,), device=dev)
+    lab[::7] = -100
+    zf = z.detach().float().clone().requires_grad_(True)
+    nr = ops.cross_entropy_ref(zf, lab)
+    nr.sum().backward()
+    zz = z.detach().clone().requires_grad_(True)
+    n = ops.cross_entropy(zz, lab)
+    n.sum().backward()
+    assert rel(n, nr) < 1e-5 and rel(zz.grad, zf.grad) < (5e-3 if dt == torch.bfloat16 else 1e-5)
+    assert float(n[::7].abs().max()) == 0 and float(zz.grad[::7].abs().max()) == 0
+
+
+def test_cross_entropy_options(dev):
+    from opaque_b200 import ops
+    z = (torch.randn(32, 4096, device=dev) * 3).bfloat16()
+    lab = torch.randint(0, 4096, (32,), device=dev)
+    kw = dict(logit_softcapping=30.0, logit_scaling=0.5, label_smoothing=0.1)
+    zf = z.float().requires_grad_(True)
+    nr = ops.cross_entropy_ref(zf, lab, **kw)
+    nr.sum().backward()
+    zz = z.clone().requires_grad_(True)
+    n = ops.cross_entropy(zz, lab, **kw)
+    n.sum().backward()
+    assert rel(n, nr) < 1e-4 and rel(zz.grad, zf.grad) < 5e-3
+
+
+def test_philox_statistics_and_layout_independence(dev):
+    from opaque_b200 import ops
+    x = torch.zeros(4_000_003, device=dev)
+    ops.philox_normal_add_(x, seed=123, offset=5, std=2.0)
+    assert abs(float(x.mean())) < 5e-3 and abs(float(x.std()) - 2.0) < 5e-3
+    assert abs(float(((x / 2.0) ** 4).mean()) - 3.0) < 0.03
+    from scipy import stats
+    assert stats.kstest((x[:200_000] / 2.0).cpu().numpy(), "norm").pvalue > 1e-3
+    # a coordinate's noise depends on (seed, global index) only: any split reproduces it exactly once
+    parts = []
+    for lo, hi in [(5, 1001), (1001, 1002), (1002, 70_001)]:
+        y = torch.zeros(hi - lo, device=dev)
+        ops.philox_normal_add_(y, seed=123, offset=lo, std=2.0)
+        parts.append(y)
+    assert torch.equal(torch.cat(parts), x[:69_996])
+    z = torch.zeros(1000, device=dev)
+    ops.philox_normal_add_(z, seed=124, offset=5, std=2.0)
+    assert abs(float((z * x[:1000]).mean())) < 0.5      # different keys are uncorrelated
+
+
+def test_direct_path_kernels(dev):
+    from opaque_b200 import ops
+    g = torch.randn(6, 10_000, device=dev)
+    n2 = torch.zeros(6, device=dev)
+    ops.rows_sumsq(g, n2)
+    assert rel(n2, (g ** 2).sum(1)) < 1e-6
+    c = torch.rand(6, device=dev)
+    out = torch.zeros(20_000, device=dev)
+    ops.clip_weighted_sum(g, c, out, flat_offset=4000)
+    assert rel(out[4000:14_000], c @ g) < 1e-6 and float(out[:4000].abs().max()) == 0
+    gg = torch.randn(300, 64, device=dev).bfloat16()
+    ids = torch.randint(0, 50, (300,), device=dev)
+    sc = torch.rand(300, device=dev)
+    out = torch.zeros(50 * 64 + 8, device=dev)
+    ops.embedding_wgrad(gg, ids, out, row_scale=sc, flat_offset=8)
+    ref = torch.zeros(50, 64, device=dev).index_add_(0, ids, gg.float() * sc[:, None])
+    assert rel(out[8:].view(50, 64), ref) < 1e-6
+
+
+def test_shard_step_adamw_noise_and_ftrl_modes(dev):
+    from opaque_b200 import ops
+    n = 10_007
+    grad, master = torch.randn(n, device=dev), torch.randn(n, device=dev)
+    m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    pl = torch.zeros(n + 64, device=dev, dtype=torch.bfloat16)
+    wt = torch.nn.Parameter(master.clone())
+    opt = torch.optim.AdamW([wt], lr=1e-2, weight_decay=0.1)
+    for step in range(1, 4):
+        gs = torch.randn(n, device=dev)
+        grad.copy_(gs * 4)
+        wt.grad = gs.clone()
+        opt.step()
+        ops.shard_step(grad=grad, master=master, m=m, v=v, params_local=pl, global_offset=64, inv_normalize=0.25,
+                       lr=1e-2, weight_decay=0.1, step=step)
+    assert rel(master, wt.detach()) < 1e-6 and rel(pl[64:], wt.detach()) < 3e-3 and float(grad.abs().max()) == 0
+    no = torch.zeros(n, device=dev)
+    ops.shard_step(grad=grad, master=master, m=m, v=v, global_offset=64, seed=77, noise_std=3.0, inv_normalize=0.5,
+                   noisy_out=no, skip_update=True)
+    ref = torch.zeros(n, device=dev)
+    ops.philox_normal_add_(ref, seed=77, offset=64, std=1.5)
+    assert torch.equal(no, ref)
+    # noise bias correction: phi_hat is removed from the second moment where that stays positive
+    m.zero_(); v.zero_(); master.fill_(1.0); grad.fill_(0.2)
+    ops.shard_step(grad=grad, master=master, m=m, v=v, lr=1.0, betas=(0.0, 0.0), eps=0.0, step=1, phi_hat=0.03)
+    assert abs(float(master[0]) - (1.0 - 0.2 / math.sqrt(0.04 - 0.03))) < 1e-4
+
+    def draws(seed):
+        z = torch.zeros(n, device=dev)
+        ops.philox_normal_add_(z, seed=seed, offset=0, std=1.0)
+        return z
+    s, d = [0.3, 0.2, 0.1], [0.9, 0.5, 0.1]
+    state, sref = torch.zeros(3, n, device=dev), torch.zeros(3, n, device=dev)
+    for t in range(4):
+        grad.zero_()
+        ops.shard_step(grad=grad, master=master, m=m, v=v, seed=100 + t, noise_std=1.0, noisy_out=no, skip_update=True,
+                       ftrl_state=state, ftrl_mode=1, ftrl_coef=s + d, nbuf=3)
+        x = draws(100 + t) - sum(s[j] * sref[j] for j in range(3))
+        for j in range(3):
+            sref[j] = d[j] * sref[j] + x
+        assert float((no - x).abs().max()) < 1e-5
+    coef, hist, zs = [1.0, 0.5, 0.25], [], []
+    st_iir, st_fir = torch.zeros(2, n, device=dev), torch.zeros(2, n, device=dev)
+    for t in range(5):
+        z = draws(200 + t)
+        grad.zero_()
+        ops.shard_step(grad=grad, master=master, m=m, v=v, seed=200 + t, noise_std=1.0, noisy_out=no, skip_update=True,
+                       ftrl_state=st_iir, ftrl_mode=2, ftrl_coef=coef, nbuf=2, ring_head=t % 2)
+        x = (z - sum(coef[k] * hist[-k] for k in (1, 2) if len(hist) >= k)) / coef[0]
+        hist.append(x)
+        assert float((no - x).abs().max()) < 1e-5
+        grad.zero_()
+        ops.shard_step(grad=grad, master=master, m=m, v=v, seed=200 + t, noise_std=1.0, noisy_out=no, skip_update=True,
+                       ftrl_state=st_fir, ftrl_mode=3, ftrl_coef=coef, nbuf=2, ring_head=t % 2)
+        y = coef[0] * z + sum(coef[k] * zs[-k] for k in (1, 2) if len(zs) >= k)
+        zs.append(z)
+        assert float((no - y).abs().max()) < 1e-5
+
+
+def test_bounded_wait_reports_timeout_without_hanging(dev):
+    """A peer flag that nothing sets: the barrier kernel gives up after its budget and records a status."""
+    import ctypes
+    from opaque_b200.ops import lib
+    st = lib.StatusWord(dev)
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)
+    table = torch.tensor([flags.data_ptr(), flags.data_ptr()], dtype=torch.int64, device=dev)
+    # two "ranks" aliasing one array: rank 0 publishes slot 0, slot 1 is never written
+    rc = lib.load().ob_peer_barrier(table.data_ptr(), flags.data_ptr(), 0, 2, 1, st.ptr(), 0.05, lib.stream())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert st.read() == 6
+    with pytest.raises(lib.DeviceWaitTimeout):
+        st.raise_if_set("test")
+    assert st.read() == 0 and float(torch.ones(4, device=dev).sum()) == 4.0     # the context is still usable

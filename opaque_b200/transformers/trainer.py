@@ -1,0 +1,870 @@
+"""``DPTrainer``: a Hugging-Face-shaped training loop over the DP primitives.
+
+One step = sample (Poisson / DP-FTRL sampler) → per-example clipped gradients → cross-rank reduction → noise →
+optimizer, with the accountant charged once per step.  Two gradient engines share the loop:
+
+  ``fused``      (B200) :class:`opaque_b200.engine.fused.FusedDPEngine` — ghost clipping, clip-weighted tcgen05
+                 weight-gradient GEMMs that reduce-scatter into sharded state, Philox / correlated noise fused
+                 with AdamW-BC.  The model must expose ``per_example_loss(**batch) -> [B]``.
+  ``reference``  the functional pipeline ``clipped_grad`` (vmap) → ``sum_gradients_`` → ``gaussian_noise`` /
+                 ``mf_gaussian_noise`` → functional optimizer; runs anywhere (CPU / gloo included) and is the
+                 numerical baseline of the fused engine.
+
+Checkpoints are atomic directories ``checkpoint-N`` (written as ``checkpoint-N.tmp`` then renamed) holding
+``model.safetensors`` (or adapter weights), ``dp_optimizer.pt``, ``dp_state.pt`` (runtime bundle, version 3:
+clip / noise / sampler state, DP hyper-parameters for drift detection), ``accountant.json``,
+``trainer_state.json`` and ``rng_state_{rank}.pth``; resuming uses the saved accountant as a prefix so
+calibration and stop-at-ε account for budget already spent.
+
+A retryable OOM on any rank is turned into a cluster-wide decision (one MAX all-reduce of a flag): every rank
+halves its microbatch and replays the step, so nobody is left waiting in a collective.
+
+Parity: packages/opaque-transformers/src/opaque/api/transformers/trainer/{_dp_trainer,_checkpoint,_distributed,
+_dpftrl,_optim,_scheduler,_eval,_callback,_state}.py.
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+import math
+import os
+import pickle
+import random
+import re
+import shutil
+import time
+from collections.abc import Callable, Mapping, Sequence
+from typing import Any
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .. import accounting as acc
+from .. import optimizers as optim_lib
+from .. import scheduling as sched
+from ..distributed import (get_rank, get_world_size, is_distributed, local_shard, reduce_scalar, sum_gradients_, sync)
+from ..dpftrl import accounting as ftrl_acc
+from ..dpftrl import noise as ftrl_noise
+from ..dpftrl.sampling import BallsInBinsSampler, BMinSepSampler, CyclicPoissonSampler, SequentialBatchSampler
+from ..dpsgd import accounting as sgd_acc
+from ..dpsgd.clipping import adaptive_clipped_grad, auto_clipped_grad, clipped_grad, per_group
+from ..dpsgd.noise import gaussian_noise
+from ..dpsgd.sampling import KOutOfTSampler, PoissonSampler, RandomAllocationSampler
+from ..functional import make_functional
+from ..profiling import perf_tracker
+from ..random import RngKey, fold_in, key
+from ..serialization import from_state_dict, state_dict
+from .training_args import MECHANISMS_DPFTRL, TrainingArguments
+
+DP_STATE_BUNDLE_VERSION = 3
+CHECKPOINT_RE = re.compile(r"^checkpoint-(\d+)$")
+FILES = {"optimizer": "dp_optimizer.pt", "state": "dp_state.pt", "accountant": "accountant.json",
+         "trainer_state": "trainer_state.json", "args": "training_args.bin", "weights": "model.safetensors"}
+
+
+# ------------------------------------------------------------------------------------------ small pieces
+
+@dataclasses.dataclass
+class DPTrainerState:
+    global_step: int = 0
+    epoch: float = 0.0
+    max_steps: int = 0
+    num_input_tokens_seen: int = 0
+    log_history: list = dataclasses.field(default_factory=list)
+    best_metric: float | None = None
+    best_model_checkpoint: str | None = None
+    epsilon: float | None = None
+
+    def to_json(self) -> str:
+        return json.dumps(dataclasses.asdict(self), indent=1)
+
+
+class TrainerCallback:
+    """Override any hook; every hook receives ``(args, state, control, **kwargs)``."""
+
+    def on_train_begin(self, args, state, control, **kw): ...
+    def on_step_begin(self, args, state, control, **kw): ...
+    def on_pre_optimizer_step(self, args, state, control, **kw): ...
+    def on_optimizer_step(self, args, state, control, **kw): ...
+    def on_step_end(self, args, state, control, **kw): ...
+    def on_log(self, args, state, control, logs=None, **kw): ...
+    def on_evaluate(self, args, state, control, metrics=None, **kw): ...
+    def on_save(self, args, state, control, **kw): ...
+    def on_train_end(self, args, state, control, **kw): ...
+
+
+@dataclasses.dataclass
+class TrainerControl:
+    should_training_stop: bool = False
+    should_save: bool = False
+    should_evaluate: bool = False
+    should_log: bool = False
+
+
+class PrinterCallback(TrainerCallback):
+    def on_log(self, args, state, control, logs=None, **kw):
+        if args.should_log and logs:
+            print({k: (round(v, 5) if isinstance(v, float) else v) for k, v in logs.items()}, flush=True)
+
+
+class BestModelSaveCallback(TrainerCallback):
+    """Track ``metric_for_best_model`` on every evaluation and remember the best checkpoint."""
+
+    def on_evaluate(self, args, state, control, metrics=None, **kw):
+        name = args.metric_for_best_model
+        if not name or not metrics:
+            return
+        keyname = name if name in metrics else f"eval_{name}"
+        if keyname not in metrics:
+            return
+        better = (lambda a, b: a > b) if args.greater_is_better else (lambda a, b: a < b)
+        if state.best_metric is None or better(metrics[keyname], state.best_metric):
+            state.best_metric = float(metrics[keyname])
+            control.should_save = True
+
+
+@dataclasses.dataclass
+class PredictionOutput:
+    predictions: Any
+    label_ids: Any
+    metrics: dict[str, float]
+
+
+@dataclasses.dataclass
+class RuntimeCheckpoint:
+    """Everything besides weights / optimizer needed to continue a DP run bit-for-bit."""
+    version: int
+    clip_state: dict
+    noise_state: dict
+    sampler_state: dict
+    sample_rate: float
+    target_delta: float
+    noise_multiplier: float
+    expected_batch_size: float
+    max_steps: int
+    mechanism: str
+    mechanism_kwargs: dict
+    sampling_mode: str
+    clipping_norm: Any
+    clipping_mode: str
+    engine: str
+    mf_horizon: int | None = None
+    min_sep: int | None = None
+    max_participations: int | None = None
+
+
+def build_lr_schedule(args: TrainingArguments, max_steps: int):
+    """HF scheduler names → schedule recipes (multiplied into ``learning_rate``)."""
+    lr, w, kw = args.learning_rate, args.warmup_steps, dict(args.lr_scheduler_kwargs)
+    decay = max(1, max_steps - w)
+    name = args.lr_scheduler
+    if name == "constant":
+        base = sched.constant_schedule(lr)
+    elif name in ("linear", "polynomial"):
+        power = kw.get("power", 1.0) if name == "polynomial" else 1.0
+        base = sched.polynomial_schedule(lr, kw.get("lr_end", 0.0), power, decay, transition_begin=w)
+    elif name in ("cosine", "cosine_with_min_lr"):
+        base = sched.cosine_schedule(lr, kw.get("min_lr", 0.0), decay, transition_begin=w, num_cycles=kw.get("num_cycles", 0.5))
+    elif name == "cosine_with_restarts":
+        cycles = int(kw.get("num_cycles", 1))
+        base = sched.with_restarts(sched.cosine_schedule(lr, 0.0, max(1, decay // cycles)), decay, cycles, transition_begin=w)
+    elif name == "inverse_sqrt":
+        base = sched.inverse_sqrt_schedule(lr, kw.get("timescale", max(w, 1)), transition_begin=w)
+    elif name in ("warmup_stable_decay", "wsd"):
+        nd = int(kw.get("num_decay_steps", max(1, max_steps // 10)))
+        return sched.warmup_stable_decay(lr, kw.get("min_lr", 0.0), num_warmup_steps=max(w, 1),
+                                         num_stable_steps=max(0, max_steps - max(w, 1) - nd), num_decay_steps=nd,
+                                         decay_shape=kw.get("decay_shape", "1-sqrt"))
+    elif name == "exponential":
+        base = sched.exponential_schedule(lr, kw.get("decay_rate", 0.99), transition_begin=w)
+    else:
+        raise ValueError(f"unknown lr_scheduler {name!r}")
+    return sched.with_warmup(base, w) if w > 0 else base
+
+
+def build_optimizer(args: TrainingArguments, lr) -> optim_lib.GradientTransformation:
+    """Canonical optimizer names → functional optimizers; ``adamw-bc`` = AdamW with noise bias correction."""
+    betas = (args.adam_beta1, args.adam_beta2)
+    extra = dict(args.optim_args)
+    name = args.optim
+    if name == "adamw-bc":
+        return optim_lib.adamw(lr, betas, args.adam_epsilon, args.weight_decay, noise_bias_correction=True, **extra)
+    if name == "adamw":
+        return optim_lib.adamw(lr, betas, args.adam_epsilon, args.weight_decay, **extra)
+    if name == "adam":
+        return optim_lib.adam(lr, betas, args.adam_epsilon, args.weight_decay, **extra)
+    if name == "sgd":
+        return optim_lib.sgd(lr, weight_decay=args.weight_decay, **extra)
+    if name == "lion":
+        return optim_lib.lion(lr, (args.adam_beta1, extra.pop("beta2", 0.99)), args.weight_decay, **extra)
+    if name in ("adagrad", "rmsprop", "radam", "adadelta", "adafactor", "ademamix", "schedule_free_adamw", "schedule_free_sgd"):
+        return getattr(optim_lib, name)(lr, weight_decay=args.weight_decay, **extra)
+    raise ValueError(f"unknown optimizer {name!r}")
+
+
+def build_strategy(mechanism: str, kwargs: Mapping[str, Any]) -> ftrl_noise.MfStrategy:
+    table = {"mf_band": ftrl_noise.band_mf_strategy, "mf_blt": ftrl_noise.blt_strategy, "mf_bisr": ftrl_noise.bisr_strategy,
+             "mf_bsr": ftrl_noise.bsr_strategy, "mf_lambda_cgd": ftrl_noise.lambda_cgd_strategy,
+             "mf_identity": lambda **k: ftrl_noise.identity_strategy()}
+    return table[mechanism](**dict(kwargs))
+
+
+def list_checkpoints(output_dir: str) -> list[str]:
+    if not output_dir or not os.path.isdir(output_dir):
+        return []
+    found = [(int(m.group(1)), d) for d in os.listdir(output_dir) if (m := CHECKPOINT_RE.match(d))]
+    return [os.path.join(output_dir, d) for _, d in sorted(found)]
+
+
+def rotate_checkpoints(output_dir: str, limit: int | None, keep: str | None = None) -> None:
+    if not limit or limit <= 0:
+        return
+    ckpts = [c for c in list_checkpoints(output_dir) if c != keep]
+    excess = len(ckpts) + (1 if keep else 0) - limit
+    for c in ckpts[:max(0, excess)]:
+        shutil.rmtree(c, ignore_errors=True)
+
+
+def _is_retryable_oom(exc: BaseException) -> bool:
+    return isinstance(exc, torch.OutOfMemoryError) or (isinstance(exc, RuntimeError) and "out of memory" in str(exc).lower())
+
+
+def default_per_example_loss(model_call: Callable[..., Any], example: Mapping[str, torch.Tensor]) -> torch.Tensor:
+    """Mean next-token NLL of ONE example (no batch axis), labels already aligned."""
+    from ..alignment.sft import nll_loss
+    ids = example["input_ids"].unsqueeze(0)
+    logits = model_call(ids)
+    logits = getattr(logits, "logits", logits)
+    return nll_loss(logits, example["labels"].unsqueeze(0)).squeeze(0)
+
+
+# ------------------------------------------------------------------------------------------ trainer
+
+class DPTrainer:
+    def __init__(self, model: torch.nn.Module | None = None, args: TrainingArguments | None = None,
+                 data_collator: Callable | None = None, train_dataset: Any = None, eval_dataset: Any = None,
+                 processing_class: Any = None, compute_loss_func: Callable | None = None,
+                 compute_metrics: Callable | None = None, callbacks: Sequence[TrainerCallback] | None = None,
+                 optimizers: tuple = (None, None), optimizer_cls_and_kwargs: tuple | None = None,
+                 preprocess_logits_for_metrics: Callable | None = None):
+        if model is None:
+            raise ValueError("DPTrainer needs a model")
+        self.model = model
+        self.args = args or TrainingArguments()
+        self.train_dataset, self.eval_dataset = train_dataset, eval_dataset
+        self.processing_class = processing_class
+        self.compute_loss_func = compute_loss_func
+        self.compute_metrics = compute_metrics
+        self.preprocess_logits_for_metrics = preprocess_logits_for_metrics
+        self.optimizers = optimizers
+        self.optimizer_cls_and_kwargs = optimizer_cls_and_kwargs
+        self.state = DPTrainerState()
+        self.control = TrainerControl()
+        self.callbacks: list[TrainerCallback] = [PrinterCallback(), BestModelSaveCallback(), *(callbacks or [])]
+        if data_collator is None:
+            from ..alignment.data import language_modeling_collator
+            pad = getattr(processing_class, "pad_token_id", None) or 0
+            data_collator = lambda rows: language_modeling_collator(rows, pad_token_id=pad)
+        self.data_collator = data_collator
+        self.accountant: acc.Accountant | None = None
+        self.perf = None
+        self._ddp_init()
+
+    # ---- distributed bootstrap ----------------------------------------------------------------
+    def _ddp_init(self) -> None:
+        a = self.args
+        if a.world_size > 1 and not dist.is_initialized():
+            backend = a.ddp_backend or ("nccl" if torch.cuda.is_available() and not a.use_cpu else "gloo")
+            if backend not in ("nccl", "gloo", "mpi"):
+                raise ValueError(f"unsupported ddp_backend {backend!r} (nccl, gloo, mpi)")
+            import datetime
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group(backend, init_method="env://", timeout=datetime.timedelta(seconds=a.ddp_timeout))
+        if torch.cuda.is_available() and not a.use_cpu:
+            torch.cuda.set_device(a.local_process_index)
+            self.device = torch.device("cuda", a.local_process_index)
+        else:
+            self.device = torch.device("cpu")
+        self.model.to(self.device)
+
+    def _call(self, hook: str, **kw: Any) -> None:
+        for cb in self.callbacks:
+            getattr(cb, hook)(self.args, self.state, self.control, model=self.model, **kw)
+
+    # ---- overridable task hooks -----------------------------------------------------------------
+    def compute_per_example_loss(self, model_call: Callable[..., Any], example: Mapping[str, torch.Tensor]) -> torch.Tensor:
+        """Loss of ONE record (reference engine; runs under ``vmap``)."""
+        if self.compute_loss_func is not None:
+            return self.compute_loss_func(model_call, example)
+        return default_per_example_loss(model_call, example)
+
+    def compute_batch_per_example_loss(self, batch: Mapping[str, torch.Tensor]) -> torch.Tensor:
+        """One loss per record of a batch (fused engine, evaluation)."""
+        if hasattr(self.model, "per_example_loss"):
+            return self.model.per_example_loss(batch["input_ids"], batch["labels"])
+        out = [self.compute_per_example_loss(self.model, {k: v[i] for k, v in batch.items()}) for i in range(len(batch["input_ids"]))]
+        return torch.stack(out) if out else torch.zeros(0, device=self.device)
+
+    # ---- set-up -----------------------------------------------------------------------------------
+    def _resolve_engine(self) -> str:
+        want = self.args.dp_engine
+        fused_ok = self.device.type == "cuda" and hasattr(self.model, "per_example_loss") and self.args.clipping_mode != "adaptive" \
+            and not isinstance(self.args.clipping_norm, Mapping) and self.compute_loss_func is None
+        if fused_ok:
+            from ..device import fused_kernels_available
+            fused_ok = fused_kernels_available()
+        if want == "fused" and not fused_ok:
+            raise RuntimeError("dp_engine='fused' needs a B200, the kernel library, a model with per_example_loss, "
+                               "a scalar clipping_norm and fixed/auto clipping")
+        return "fused" if (want in ("auto", "fused") and fused_ok) else "reference"
+
+    def _build_sampler(self, n_local: int, steps: int, data_key: RngKey):
+        a = self.args
+        q = min(1.0, a.per_device_train_batch_size / max(n_local, 1))
+        kw = dict(a.sampling_kwargs)
+        mode = a.sampling_mode
+        rng = range(n_local)
+        if mode == "poisson":
+            return PoissonSampler(rng, q, n_steps=steps, truncated_batch_size=kw.get("truncated_batch_size"), key=data_key), q
+        if mode == "random_allocation":
+            bins = int(kw.get("num_bins", max(1, round(1 / q))))
+            return RandomAllocationSampler(rng, bins, n_steps=steps, key=data_key), 1.0 / bins
+        if mode == "k_out_of_t":
+            t = int(kw.get("t", max(1, round(1 / q))))
+            return KOutOfTSampler(rng, int(kw.get("k", 1)), t, n_steps=steps, key=data_key), kw.get("k", 1) / t
+        bands = int(a.privacy_noise_mechanism_kwargs.get("bands", a.privacy_noise_mechanism_kwargs.get("bandwidth", kw.get("bands", 1))))
+        if mode == "cyclic_poisson":
+            return CyclicPoissonSampler(rng, min(1.0, q * bands), bands=bands, n_steps=steps, key=data_key), min(1.0, q * bands)
+        if mode == "b_min_sep":
+            return BMinSepSampler(rng, bands, q, steps, key=data_key), q
+        if mode == "balls_in_bins":
+            bins = int(kw.get("num_bins", max(1, round(1 / q))))
+            return BallsInBinsSampler(rng, bins, n_steps=steps, key=data_key), 1.0 / bins
+        if mode == "sequential":
+            return SequentialBatchSampler(rng, min(a.per_device_train_batch_size, n_local), n_steps=steps), q
+        raise ValueError(mode)
+
+    def _participation(self, sampler, steps: int) -> tuple[int, int | None]:
+        """(min_sep, max_participations) implied by the sampler for MF sensitivity."""
+        if isinstance(sampler, BallsInBinsSampler):
+            return sampler.num_bins, math.ceil(steps / sampler.num_bins)
+        if isinstance(sampler, SequentialBatchSampler):
+            return sampler.min_sep, math.ceil(steps / sampler.min_sep)
+        if isinstance(sampler, (CyclicPoissonSampler, BMinSepSampler)):
+            return sampler.bands, math.ceil(steps / sampler.bands)
+        return 1, None
+
+    def _step_process(self, nm: float, q: float, steps: int, sampler) -> acc.DpProcess:
+        """The accountant's description of ONE step at noise multiplier ``nm``."""
+        a = self.args
+        W = a.world_size
+        if a.privacy_noise_mechanism == "gaussian":
+            g: acc.DpProcess = sgd_acc.gaussian(nm)
+            if a.clipping_mode == "adaptive":
+                g = sgd_acc.adaclip(g, fraction_noise_std=float(a.clipping_kwargs.get("fraction_noise_std", 0.05)),
+                                    expected_batch_size=float(a.train_batch_size),
+                                    num_groups=len(a.clipping_norm) if isinstance(a.clipping_norm, Mapping) else 1)
+            if a.sampling_mode == "poisson":
+                return sgd_acc.poisson(g, q)      # disjoint shards: each record is sampled by one rank at rate q
+            if a.sampling_mode == "random_allocation":
+                return acc.per_step(_EpochProcess(sgd_acc.random_allocation(g, sampler.num_bins), sampler.num_bins))
+            if a.sampling_mode == "k_out_of_t":
+                return acc.per_step(_EpochProcess(sgd_acc.k_out_of_t(g, sampler.k, sampler.t), sampler.t))
+            return g
+        strat = self._strategy
+        ms, mp = self._participation(sampler, steps)
+        inner = ftrl_acc.mf_gaussian(nm, strat, n_steps=steps, min_sep=ms, max_participations=mp)
+        if a.sampling_mode in ("cyclic_poisson",):
+            return ftrl_acc.per_step(ftrl_acc.poisson(inner, q, n_steps=steps))
+        if a.sampling_mode == "poisson" and a.privacy_noise_mechanism == "mf_identity":
+            return sgd_acc.poisson(sgd_acc.gaussian(nm), q)
+        return ftrl_acc.per_step(inner)
+
+    def _calibrate(self, q: float, steps: int, sampler, prefix: acc.DpProcess | None) -> float:
+        a = self.args
+        if a.privacy_noise_multiplier is not None:
+            return float(a.privacy_noise_multiplier)
+        if a.privacy_target_epsilon is None:
+            raise ValueError("set privacy_target_epsilon (calibrated noise) or privacy_noise_multiplier")
+        budget = acc.epsilon_budget(a.privacy_target_epsilon, self.target_delta)
+        kw = a.noise_calibration_kwargs
+        res = acc.calibrate(budget, lambda nm: self._step_process(nm, q, steps, sampler) * steps, kw["min"], kw["max"],
+                            tolerance=kw["tol"], prefix=prefix)
+        return float(res.param)
+
+    def _setup(self, resume: str | None) -> None:
+        a = self.args
+        torch.manual_seed(a.seed)
+        if self.train_dataset is None:
+            raise ValueError("training needs a train_dataset")
+        W, rank = a.world_size, a.process_index
+        n_total = len(self.train_dataset)
+        per = n_total // W                                   # equal shards; the tail is trimmed
+        self._local_data = local_shard(_Trimmed(self.train_dataset, per * W), rank=rank, world_size=W)
+        n_local = per
+        q_nominal = min(1.0, a.per_device_train_batch_size / max(n_local, 1))
+        if a.max_steps > 0:
+            steps = a.max_steps
+        else:
+            steps = max(1, math.ceil(a.num_train_epochs / q_nominal))
+        self.state.max_steps = steps
+        self.target_delta = a.privacy_target_delta if a.privacy_target_delta is not None else 1.0 / (n_total ** 1.1)
+        data_key = fold_in(key(a.data_seed if a.data_seed is not None else a.seed), rank)
+        self.sampler, self.sample_rate = self._build_sampler(n_local, steps, data_key)
+        self._strategy = build_strategy(a.privacy_noise_mechanism, a.privacy_noise_mechanism_kwargs) \
+            if a.privacy_noise_mechanism in MECHANISMS_DPFTRL else None
+        self.engine_kind = self._resolve_engine()
+        prefix = None
+        runtime = None
+        if resume:
+            runtime, prefix = self._load_checkpoint_meta(resume)
+        self.noise_multiplier = runtime.noise_multiplier if runtime else self._calibrate(self.sample_rate, steps, self.sampler, prefix)
+        self.step_process = self._step_process(self.noise_multiplier, self.sample_rate, steps, self.sampler)
+        self.accountant = acc.Accountant(
+            acc.epsilon_budget(a.privacy_target_epsilon, self.target_delta) if a.privacy_target_epsilon else None, prefix)
+        self.lr_schedule = build_lr_schedule(a, steps)
+        self.expected_batch = float(a.train_batch_size)
+        noise_key = key(a.seed + 1)
+        mb = a.microbatch_size or a.per_device_train_batch_size
+        self._microbatch = mb
+        if self.engine_kind == "fused":
+            self._setup_fused(noise_key, steps)
+        else:
+            self._setup_reference(noise_key, steps)
+        if resume:
+            self._load_checkpoint_state(resume, runtime)
+        self.perf = perf_tracker(self.device, warmup_steps=1)
+
+    def _clip_bound(self):
+        a = self.args
+        if isinstance(a.clipping_norm, Mapping):
+            pats = {k: v for k, v in a.clipping_norm.items() if k != "fallback"}
+            return per_group(self._trainable, pats, fallback=a.clipping_norm.get("fallback"))
+        return float(a.clipping_norm)
+
+    def _setup_reference(self, noise_key: RngKey, steps: int) -> None:
+        a = self.args
+        self._fmodel, self._trainable, self._frozen = make_functional(self.model, disable_autograd_tracking=True,
+                                                                    partition_trainable=True)
+        frozen, fmodel = self._frozen, self._fmodel
+
+        def loss_fn(trainable, example):
+            call = lambda *x, **k: fmodel({**frozen, **trainable}, *x, **k)
+            return self.compute_per_example_loss(call, example)
+        common = dict(normalize_by=self.expected_batch, batch_argnums=1, return_aux=True, microbatch_size=self._microbatch)
+        bound = self._clip_bound()
+        if a.clipping_mode == "fixed":
+            self._grad_fn, self._clip_state = clipped_grad(loss_fn, clipping_norm=bound, **common)
+        elif a.clipping_mode == "auto":
+            self._grad_fn, self._clip_state = auto_clipped_grad(loss_fn, R=bound, gamma=float(a.clipping_kwargs.get("gamma", 0.01)), **common)
+        else:
+            kw = {k: v for k, v in a.clipping_kwargs.items()}
+            self._grad_fn, self._clip_state = adaptive_clipped_grad(
+                loss_fn, initial_clipping_norm=bound, key=fold_in(key(a.seed), "adaclip"), return_aux=True,
+                normalize_by=self.expected_batch, batch_argnums=1, microbatch_size=self._microbatch, **kw)
+        if self._strategy is None:
+            self._noise_fn, self._noise_state = gaussian_noise(noise_multiplier=self.noise_multiplier, key=noise_key)
+        else:
+            ms, mp = self._participation(self.sampler, steps)
+            from ..types import clipped
+            self._noise_fn, self._noise_state = ftrl_noise.mf_gaussian_noise(
+                clipped(self._trainable, 1.0), self._strategy, n_steps=steps, min_sep=ms, max_participations=mp,
+                noise_multiplier=self.noise_multiplier, key=noise_key)
+        self._optimizer = self.optimizers[0] or build_optimizer(a, self.lr_schedule)
+        self._opt_state = self._optimizer.init(self._trainable)
+
+    def _setup_fused(self, noise_key: RngKey, steps: int) -> None:
+        from ..engine.fused import FusedDPEngine
+        from ..parallel.sharded import DPStepConfig
+        a = self.args
+        if a.optim not in ("adamw", "adamw-bc", "adam"):
+            raise ValueError("the fused engine implements AdamW / AdamW-BC; use dp_engine='reference' for other optimizers")
+        cfg = DPStepConfig(lr=self.lr_schedule, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
+                           weight_decay=a.weight_decay, decoupled_weight_decay=a.optim != "adam",
+                           noise_bias_correction=a.optim == "adamw-bc")
+        mech = self._strategy.fused_mechanism(steps) if self._strategy is not None else None
+        self._fused = FusedDPEngine(self.model, clipping_norm=float(a.clipping_norm), noise_multiplier=self.noise_multiplier,
+                                    normalize_by=self.expected_batch, key=noise_key, step_config=cfg,
+                                    microbatch_size=self._microbatch, mechanism=mech,
+                                    clipping_mode="auto" if a.clipping_mode == "auto" else "clip",
+                                    gamma=float(a.clipping_kwargs.get("gamma", 0.01)))
+
+    # ---- data -----------------------------------------------------------------------------------
+    def get_train_dataloader(self):
+        """Iterator of collated local batches (possibly EMPTY under Poisson sampling)."""
+        data, collate = self._local_data, self.data_collator
+        for idx in self.sampler:
+            yield collate([data[i] for i in idx])
+
+    def _to_device(self, batch: Mapping[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+        pin = self.args.dataloader_pin_memory and self.device.type == "cuda"
+        out = {}
+        for k, v in batch.items():
+            if isinstance(v, torch.Tensor):
+                out[k] = (v.pin_memory() if pin and v.numel() else v).to(self.device, non_blocking=True)
+            else:
+                out[k] = v
+        return out
+
+    # ---- one step ---------------------------------------------------------------------------------
+    def training_step(self, batch: Mapping[str, torch.Tensor]) -> dict[str, float]:
+        """One DP optimizer step on this rank's batch; returns scalar metrics (global where meaningful)."""
+        a = self.args
+        self._call("on_step_begin")
+        batch = self._to_device(batch)
+        n_local = int(next(v for v in batch.values() if isinstance(v, torch.Tensor)).shape[0])
+        with self.perf.step("train", batch_size=n_local, track_memory=not a.skip_memory_metrics) as sp:
+            if self.engine_kind == "fused":
+                metrics = self._fused_step(batch, sp)
+            else:
+                metrics = self._reference_step(batch, sp)
+        self.state.global_step += 1
+        self.accountant |= self.step_process
+        self._call("on_step_end")
+        return metrics
+
+    def _cluster_flag(self, flag: bool) -> bool:
+        return bool(reduce_scalar(int(flag), "max")) if is_distributed() else flag
+
+    def _reference_step(self, batch, sp) -> dict[str, float]:
+        a = self.args
+        payload = {"input_ids": batch["input_ids"], "labels": batch["labels"]}
+        payload.update({k: v for k, v in batch.items() if k not in payload and isinstance(v, torch.Tensor) and v.shape[:1] == batch["input_ids"].shape[:1]})
+        while True:
+            oom = False
+            try:
+                (grads, aux), clip_state = self._grad_fn(self._trainable, payload, state=self._clip_state)
+            except Exception as exc:      # noqa: BLE001 — only OOM is swallowed
+                if not _is_retryable_oom(exc):
+                    raise
+                oom = True
+            if not self._cluster_flag(oom):
+                break
+            if self._microbatch <= 1:
+                raise torch.OutOfMemoryError("out of memory at microbatch size 1")
+            self._microbatch = max(1, self._microbatch // 2)      # every rank steps down together and replays
+            self._setup_reference_grad_only()
+        sp.mark("clip")
+        grads = sum_gradients_(grads)
+        self._clip_state = sync(clip_state)
+        aux = sync(aux)
+        self._call("on_pre_optimizer_step")
+        noisy, self._noise_state = self._noise_fn(grads, self._noise_state)
+        sp.mark("noise")
+        updates, self._opt_state = self._optimizer.update(noisy, self._opt_state, params=self._trainable)
+        self._trainable = optim_lib.apply_updates(self._trainable, updates)
+        self._write_back()
+        sp.mark("optimizer")
+        self._call("on_optimizer_step")
+        n = aux.batch_size
+        out = {"loss": float(aux.loss_values.mean()) if n else 0.0, "grad_norm": float(aux.grad_norms.mean()) if n else 0.0,
+               "clip_rate": float(aux.clipping_rate) if isinstance(aux.clipping_rate, (int, float)) else 0.0,
+               "batch_size": float(n), "noise_std": float(noisy.noise_stddev) if isinstance(noisy.noise_stddev, (int, float)) else 0.0,
+               "clipping_norm": float(getattr(self._clip_state, "clipping_norm", a.clipping_norm)) if not isinstance(a.clipping_norm, Mapping) else 0.0}
+        if "labels" in batch:
+            self.state.num_input_tokens_seen += int(reduce_scalar(int((batch["labels"] != -100).sum()), "sum"))
+        return out
+
+    def _setup_reference_grad_only(self) -> None:
+        saved = (self._noise_fn, self._noise_state, self._optimizer, self._opt_state, self._trainable)
+        self._setup_reference(key(self.args.seed + 1), self.state.max_steps)
+        self._noise_fn, self._noise_state, self._optimizer, self._opt_state, self._trainable = saved
+
+    @torch.no_grad()
+    def _write_back(self) -> None:
+        named = dict(self.model.named_parameters())
+        for n, v in self._trainable.items():
+            named[n].copy_(v)
+
+    def _fused_step(self, batch, sp) -> dict[str, float]:
+        self._call("on_pre_optimizer_step")
+        res = self._fused.step(self.model.per_example_loss, {"input_ids": batch["input_ids"], "labels": batch["labels"]})
+        sp.mark("optimizer")
+        self._call("on_optimizer_step")
+        n = int(reduce_scalar(res.batch_size, "sum")) if is_distributed() else res.batch_size
+        if "labels" in batch:
+            self.state.num_input_tokens_seen += int(reduce_scalar(int((batch["labels"] != -100).sum()), "sum"))
+        return {"loss": res.loss if res.batch_size else 0.0, "grad_norm": res.grad_norm_mean if res.batch_size else 0.0,
+                "clip_rate": res.clip_rate if res.batch_size else 0.0, "batch_size": float(n),
+                "noise_std": self.noise_multiplier * float(self.args.clipping_norm) / self.expected_batch,
+                "clipping_norm": float(self.args.clipping_norm)}
+
+    # ---- loop -------------------------------------------------------------------------------------
+    def train(self, resume_from_checkpoint: str | bool | None = None, ignore_keys_for_eval=None):
+        a = self.args
+        resume = resume_from_checkpoint if resume_from_checkpoint is not None else a.resume_from_checkpoint
+        if resume is True:
+            ckpts = list_checkpoints(a.output_dir)
+            resume = ckpts[-1] if ckpts else None
+        self._setup(resume or None)
+        self.model.train()
+        self._call("on_train_begin")
+        if a.eval_on_start and self.eval_dataset is not None:
+            self.evaluate()
+        t0 = time.perf_counter()
+        window: list[dict[str, float]] = []
+        for batch in self.get_train_dataloader():
+            metrics = self.training_step(batch)
+            window.append(metrics)
+            step = self.state.global_step
+            self.state.epoch = step * self.sample_rate
+            if a.logging_strategy == "steps" and (step % a.logging_steps == 0 or (a.logging_first_step and step == 1)):
+                self.log(self._mean(window))
+                window = []
+            if a.eval_strategy == "steps" and a.eval_steps and step % a.eval_steps == 0 and self.eval_dataset is not None:
+                self.evaluate()
+            if self.control.should_save or (a.save_strategy == "steps" and a.save_steps and step % a.save_steps == 0 and a.output_dir):
+                self._save_checkpoint(step)
+                self.control.should_save = False
+            if a.privacy_target_epsilon is not None and a.privacy_noise_multiplier is not None and self.accountant.budget_exceeded():
+                self.control.should_training_stop = True      # stop-at-epsilon for fixed-noise runs
+            if self.control.should_training_stop or step >= self.state.max_steps:
+                break
+        if window:
+            self.log(self._mean(window))
+        self.state.epsilon = self.epsilon()
+        out = {"train_runtime": time.perf_counter() - t0, "global_step": self.state.global_step, "epsilon": self.state.epsilon,
+               "train_samples_per_second": self.perf.state("train").samples_per_second}
+        self.log(out)
+        self._call("on_train_end")
+        return out
+
+    @staticmethod
+    def _mean(rows: list[dict[str, float]]) -> dict[str, float]:
+        keys = rows[0].keys() if rows else []
+        return {k: float(np.mean([r[k] for r in rows])) for k in keys}
+
+    def epsilon(self, delta: float | None = None) -> float:
+        return float(self.accountant.epsilon_at(self.target_delta if delta is None else delta))
+
+    def log(self, logs: dict[str, float]) -> None:
+        logs = {**logs, "step": self.state.global_step, "epoch": round(self.state.epoch, 4)}
+        if self.accountant is not None and self.state.global_step and "epsilon" not in logs:
+            logs["epsilon"] = self.epsilon()
+        self.state.log_history.append(logs)
+        self._call("on_log", logs=logs)
+
+    # ---- evaluation ---------------------------------------------------------------------------------
+    @torch.no_grad()
+    def evaluate(self, eval_dataset: Any = None, ignore_keys=None, metric_key_prefix: str = "eval") -> dict[str, float]:
+        data = eval_dataset if eval_dataset is not None else self.eval_dataset
+        if data is None:
+            raise ValueError("evaluation needs an eval_dataset")
+        a = self.args
+        if self.engine_kind == "reference" if hasattr(self, "engine_kind") else False:
+            self._write_back()
+        shard = local_shard(data, rank=a.process_index, world_size=a.world_size)
+        was_training = self.model.training
+        self.model.eval()
+        total, count, tokens = 0.0, 0, 0
+        bs = a.eval_batch_size
+        for lo in range(0, len(shard), bs):
+            batch = self._to_device(self.data_collator([shard[i] for i in range(lo, min(len(shard), lo + bs))]))
+            losses = self.compute_batch_per_example_loss(batch)
+            total += float(losses.float().sum())
+            count += int(losses.numel())
+            tokens += int((batch["labels"] != -100).sum()) if "labels" in batch else 0
+        self.model.train(was_training)
+        total = float(reduce_scalar(total, "sum"))
+        count = int(reduce_scalar(count, "sum"))
+        metrics = {f"{metric_key_prefix}_loss": total / max(count, 1), f"{metric_key_prefix}_samples": float(count)}
+        if self.accountant is not None and self.state.global_step:
+            metrics["epsilon"] = self.epsilon()
+        self.log(metrics)
+        self._call("on_evaluate", metrics=metrics)
+        return metrics
+
+    @torch.no_grad()
+    def predict(self, test_dataset: Any, ignore_keys=None, metric_key_prefix: str = "test") -> PredictionOutput:
+        self.model.eval()
+        preds, labels, losses = [], [], []
+        bs = self.args.eval_batch_size
+        for lo in range(0, len(test_dataset), bs):
+            batch = self._to_device(self.data_collator([test_dataset[i] for i in range(lo, min(len(test_dataset), lo + bs))]))
+            logits = self.model(batch["input_ids"])
+            logits = getattr(logits, "logits", logits)
+            if self.preprocess_logits_for_metrics is not None:
+                logits = self.preprocess_logits_for_metrics(logits, batch.get("labels"))
+            preds.append(logits.float().cpu())
+            if "labels" in batch:
+                labels.append(batch["labels"].cpu())
+                losses.append(self.compute_batch_per_example_loss(batch).float().cpu())
+        p = torch.cat(preds) if preds and all(x.shape[1:] == preds[0].shape[1:] for x in preds) else preds
+        l = torch.cat(labels) if labels and all(x.shape[1:] == labels[0].shape[1:] for x in labels) else labels
+        metrics = {f"{metric_key_prefix}_loss": float(torch.cat(losses).mean())} if losses else {}
+        if self.compute_metrics is not None and labels:
+            metrics.update({f"{metric_key_prefix}_{k}": v for k, v in self.compute_metrics((p, l)).items()})
+        return PredictionOutput(p, l, metrics)
+
+    # ---- checkpoints ----------------------------------------------------------------------------------
+    def save_model(self, output_dir: str | None = None) -> None:
+        out = output_dir or self.args.output_dir
+        if not out:
+            raise ValueError("no output_dir")
+        if getattr(self, "engine_kind", None) == "reference":
+            self._write_back()
+        if self.args.should_save:
+            os.makedirs(out, exist_ok=True)
+            sd = {k: v.detach().to("cpu").contiguous().clone() for k, v in self.model.state_dict().items()}
+            only_adapter = any("lora_" in k for k in sd) and not any(p.requires_grad for n, p in self.model.named_parameters() if "lora_" not in n)
+            if only_adapter:
+                sd = {k: v for k, v in sd.items() if "lora_" in k}
+            name = "adapter_model.safetensors" if only_adapter else FILES["weights"]
+            if self.args.save_safetensors:
+                from safetensors.torch import save_file
+                seen: dict[int, str] = {}
+                uniq = {}
+                for k, v in sd.items():            # tied weights: keep one copy
+                    ptr = self.model.state_dict()[k].data_ptr()
+                    if ptr in seen:
+                        continue
+                    seen[ptr] = k
+                    uniq[k] = v
+                save_file(uniq, os.path.join(out, name), metadata={"format": "pt"})
+            else:
+                torch.save(sd, os.path.join(out, name.replace(".safetensors", ".bin")))
+            cfg = getattr(self.model, "config", None)
+            if cfg is not None and dataclasses.is_dataclass(cfg):
+                json.dump(dataclasses.asdict(cfg), open(os.path.join(out, "config.json"), "w"), indent=1)
+
+    def _runtime(self) -> RuntimeCheckpoint:
+        a = self.args
+        ref = self.engine_kind == "reference"
+        ms, mp = self._participation(self.sampler, self.state.max_steps)
+        return RuntimeCheckpoint(
+            DP_STATE_BUNDLE_VERSION, state_dict(self._clip_state) if ref else {}, state_dict(_noise_public(self._noise_state)) if ref else {},
+            state_dict(self.sampler), self.sample_rate, self.target_delta, self.noise_multiplier, self.expected_batch,
+            self.state.max_steps, a.privacy_noise_mechanism, dict(a.privacy_noise_mechanism_kwargs), a.sampling_mode,
+            a.clipping_norm, a.clipping_mode, self.engine_kind, self.state.max_steps if self._strategy else None, ms, mp)
+
+    def _save_checkpoint(self, step: int) -> str:
+        a = self.args
+        final = os.path.join(a.output_dir, f"checkpoint-{step}")
+        tmp = final + ".tmp"
+        if a.should_save:
+            shutil.rmtree(tmp, ignore_errors=True)
+            os.makedirs(tmp, exist_ok=True)
+        _barrier()
+        self.save_model(tmp)
+        opt_sd = self._fused.opt.state_dict() if self.engine_kind == "fused" else state_dict(self._opt_state)
+        if a.should_save and not a.save_only_model:
+            torch.save(opt_sd, os.path.join(tmp, FILES["optimizer"]))
+            if self.engine_kind == "reference" and self._strategy is not None:
+                torch.save(state_dict(self._noise_state._inner_state), os.path.join(tmp, "dp_noise_buffers.pt"))
+            with open(os.path.join(tmp, FILES["state"]), "wb") as f:
+                pickle.dump(self._runtime(), f)
+            with open(os.path.join(tmp, FILES["accountant"]), "w") as f:
+                f.write(self.accountant.to_json())
+            with open(os.path.join(tmp, FILES["trainer_state"]), "w") as f:
+                f.write(self.state.to_json())
+            torch.save(a.to_dict(), os.path.join(tmp, FILES["args"]))
+        _barrier()
+        rng = {"python": random.getstate(), "numpy": np.random.get_state(), "torch": torch.get_rng_state(),
+               "cuda": torch.cuda.get_rng_state_all() if torch.cuda.is_available() else None}
+        if os.path.isdir(tmp):
+            torch.save(rng, os.path.join(tmp, f"rng_state_{a.process_index}.pth"))
+        _barrier()
+        if a.should_save:
+            shutil.rmtree(final, ignore_errors=True)
+            os.replace(tmp, final)
+            rotate_checkpoints(a.output_dir, a.save_total_limit, keep=final)
+        _barrier()
+        self._call("on_save")
+        return final
+
+    def _load_checkpoint_meta(self, path: str):
+        with open(os.path.join(path, FILES["state"]), "rb") as f:
+            runtime: RuntimeCheckpoint = pickle.load(f)
+        if runtime.version != DP_STATE_BUNDLE_VERSION:
+            raise ValueError(f"checkpoint bundle version {runtime.version} != {DP_STATE_BUNDLE_VERSION}")
+        a = self.args
+        drift = {"privacy_noise_mechanism": (runtime.mechanism, a.privacy_noise_mechanism), "sampling_mode": (runtime.sampling_mode, a.sampling_mode),
+                 "clipping_norm": (runtime.clipping_norm, a.clipping_norm), "clipping_mode": (runtime.clipping_mode, a.clipping_mode),
+                 "max_steps": (runtime.max_steps, self.state.max_steps),
+                 "expected_batch_size": (runtime.expected_batch_size, float(a.train_batch_size))}
+        bad = {k: v for k, v in drift.items() if v[0] != v[1]}
+        if bad:
+            raise ValueError(f"refusing to resume: DP-relevant arguments changed since the checkpoint was written: {bad}")
+        saved = acc.Accountant.from_state_dict(json.load(open(os.path.join(path, FILES["accountant"]))))
+        return runtime, saved.process
+
+    def _load_checkpoint_state(self, path: str, runtime: RuntimeCheckpoint) -> None:
+        from safetensors.torch import load_file
+        for name in ("adapter_model.safetensors", FILES["weights"]):
+            f = os.path.join(path, name)
+            if os.path.exists(f):
+                self.model.load_state_dict(load_file(f), strict=False)
+        opt_sd = torch.load(os.path.join(path, FILES["optimizer"]), weights_only=False)
+        if self.engine_kind == "fused":
+            self._fused.opt.load_state_dict(opt_sd)
+        else:
+            self._trainable = {n: p.detach().clone() for n, p in self.model.named_parameters() if p.requires_grad}
+            self._opt_state = from_state_dict(self._optimizer.init(self._trainable), opt_sd)
+            self._clip_state = from_state_dict(self._clip_state, runtime.clip_state)
+            pub = from_state_dict(_noise_public(self._noise_state), runtime.noise_state)
+            self._noise_state = dataclasses.replace(self._noise_state, _step_counter=pub["step"])
+            if self._strategy is not None:
+                inner = torch.load(os.path.join(path, "dp_noise_buffers.pt"), weights_only=False)
+                self._noise_state = dataclasses.replace(self._noise_state, _inner_state=from_state_dict(self._noise_state._inner_state, inner),
+                                                        _first_max_norm=pub.get("first_max_norm"))
+        self.sampler = from_state_dict(self.sampler, runtime.sampler_state)
+        st = json.load(open(os.path.join(path, FILES["trainer_state"])))
+        self.state = DPTrainerState(**{k: v for k, v in st.items() if k in {f.name for f in dataclasses.fields(DPTrainerState)}})
+        rng_file = os.path.join(path, f"rng_state_{self.args.process_index}.pth")
+        if os.path.exists(rng_file):
+            rng = torch.load(rng_file, weights_only=False)
+            random.setstate(rng["python"])
+            np.random.set_state(rng["numpy"])
+            torch.set_rng_state(rng["torch"])
+
+
+class _Trimmed:
+    def __init__(self, data, n):
+        self.data, self.n = data, n
+
+    def __len__(self):
+        return self.n
+
+    def __getitem__(self, i):
+        if isinstance(i, slice):
+            return _Slice(self.data, *i.indices(self.n))
+        return self.data[i]
+
+
+class _Slice:
+    def __init__(self, data, lo, hi, step):
+        self.data, self.lo, self.hi = data, lo, hi
+
+    def __len__(self):
+        return self.hi - self.lo
+
+    def __getitem__(self, i):
+        return self.data[self.lo + i]
+
+
+@dataclasses.dataclass(frozen=True)
+class _EpochProcess(acc.core.DpHorizonProcess):
+    """Whole-epoch process charged per step: ``n`` steps cost ``ceil(n / steps_per_epoch)`` epochs."""
+    epoch: acc.DpProcess
+    steps_per_epoch: int
+
+    def pld_at(self, n_steps, config=None):
+        return self.epoch.repeated_pld(max(1, math.ceil(n_steps / self.steps_per_epoch)), config)
+
+    def _build_pld(self, config):
+        return self.pld_at(1, config)
+
+
+def _noise_public(state) -> dict[str, Any]:
+    return {"step": state._step_counter, "seed": str(state._rng_key.seed), "first_max_norm": getattr(state, "_first_max_norm", None)}
+
+
+def _barrier() -> None:
+    if is_distributed():
+        dist.barrier()
+
+
+__all__ = ["BestModelSaveCallback", "DPTrainer", "DPTrainerState", "DP_STATE_BUNDLE_VERSION", "PredictionOutput",
+           "PrinterCallback", "RuntimeCheckpoint", "TrainerCallback", "TrainerControl", "build_lr_schedule",
+           "build_optimizer", "build_strategy", "default_per_example_loss", "list_checkpoints", "rotate_checkpoints"]

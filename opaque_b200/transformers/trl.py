@@ -1,0 +1,263 @@
+"""TRL-shaped task trainers on top of :class:`DPTrainer`: ``SFTTrainer`` and ``DPOTrainer``.
+
+SFT: tokenises ``dataset_text_field`` (or prompt / completion pairs), optionally scores completion tokens only,
+and uses NLL / DFT per-example losses.  DPO: the privacy unit is one preference PAIR — both completions of a pair
+are evaluated inside one per-example loss; reference log-probabilities are computed once up front (the reference
+model is public, so this costs no privacy) and cached on the dataset rows; TR-DPO style reference syncing mixes
+the policy into the reference every ``ref_model_sync_steps``.
+
+Parity: packages/opaque-transformers/src/opaque/api/transformers/trl/{_sft_trainer,_sft_config,_dpo_trainer,
+_dpo_config}.py; packages/opaque-alignment/src/opaque/api/alignment/dpo/reference/*.py.
+"""
+from __future__ import annotations
+
+import copy
+import dataclasses
+from collections.abc import Mapping, Sequence
+from typing import Any
+
+import torch
+
+from ..alignment import data as adata
+from ..alignment import dpo as dpo_losses
+from ..alignment import sft as sft_losses
+from .trainer import DPTrainer
+from .training_args import TrainingArguments
+
+
+@dataclasses.dataclass
+class SFTConfig(TrainingArguments):
+    learning_rate: float = 2e-5
+    dataset_text_field: str = "text"
+    max_length: int | None = 1024
+    completion_only_loss: bool | None = None
+    assistant_only_loss: bool = False
+    loss_type: str = "nll"                      # nll | dft | chunked_nll
+    pad_to_multiple_of: int | None = None
+    logging_steps: int = 10
+    use_performance_kernels: bool = True
+
+    def __post_init__(self):
+        super().__post_init__()
+        if self.loss_type not in ("nll", "dft", "chunked_nll"):
+            raise ValueError("loss_type must be nll | dft | chunked_nll")
+
+
+class SFTTrainer(DPTrainer):
+    def __init__(self, model=None, args: SFTConfig | None = None, train_dataset=None, eval_dataset=None,
+                 processing_class=None, data_collator=None, **kw: Any):
+        args = args or SFTConfig()
+        self._sft = args
+        train_dataset = self._prepare_dataset(train_dataset, processing_class, args)
+        eval_dataset = self._prepare_dataset(eval_dataset, processing_class, args)
+        completion_only = self._resolve_completion_only(args, train_dataset)
+        if data_collator is None:
+            pad = getattr(processing_class, "pad_token_id", None) or 0
+            data_collator = lambda rows: adata.language_modeling_collator(
+                rows, pad_token_id=pad, completion_only=completion_only, pad_to_multiple_of=args.pad_to_multiple_of,
+                max_length=args.max_length)
+        super().__init__(model=model, args=args, train_dataset=train_dataset, eval_dataset=eval_dataset,
+                         processing_class=processing_class, data_collator=data_collator, **kw)
+
+    @staticmethod
+    def _resolve_completion_only(args: SFTConfig, dataset) -> bool:
+        if args.completion_only_loss is not None:
+            return bool(args.completion_only_loss)
+        return bool(dataset is not None and len(dataset) and "completion_mask" in dataset[0])
+
+    @staticmethod
+    def tokenize_row(row: Mapping[str, Any], tokenizer: Any, args: SFTConfig) -> dict[str, Any]:
+        if "input_ids" in row:
+            return dict(row)
+        if tokenizer is None:
+            raise ValueError("a processing_class (tokenizer) is required for text datasets")
+        if "prompt" in row and "completion" in row:
+            p = tokenizer(row["prompt"], add_special_tokens=True)["input_ids"]
+            c = tokenizer(row["completion"], add_special_tokens=False)["input_ids"]
+            ids = (p + c)[: args.max_length] if args.max_length else p + c
+            return {"input_ids": ids, "completion_mask": adata.completion_mask(len(ids), len(p))}
+        if "messages" in row:
+            prompt, completion = adata.split_prompt_completion(row["messages"])
+            p = tokenizer(adata.apply_chat_template(prompt, tokenizer, add_generation_prompt=True))["input_ids"]
+            full = tokenizer(adata.apply_chat_template(row["messages"], tokenizer))["input_ids"]
+            ids = full[: args.max_length] if args.max_length else full
+            return {"input_ids": ids, "completion_mask": adata.completion_mask(len(ids), len(p))}
+        ids = tokenizer(row[args.dataset_text_field])["input_ids"]
+        return {"input_ids": ids[: args.max_length] if args.max_length else ids}
+
+    @classmethod
+    def _prepare_dataset(cls, dataset, tokenizer, args: SFTConfig):
+        if dataset is None or len(dataset) == 0 or "input_ids" in dataset[0]:
+            return dataset
+        return [cls.tokenize_row(dataset[i], tokenizer, args) for i in range(len(dataset))]
+
+    def compute_per_example_loss(self, model_call, example):
+        logits = model_call(example["input_ids"].unsqueeze(0))
+        logits = getattr(logits, "logits", logits)
+        fn = sft_losses.dft_loss if self._sft.loss_type == "dft" else sft_losses.nll_loss
+        return fn(logits, example["labels"].unsqueeze(0)).squeeze(0)
+
+
+@dataclasses.dataclass
+class DPOConfig(TrainingArguments):
+    learning_rate: float = 1e-6
+    beta: float = 0.1
+    loss_type: Any = "sigmoid"
+    loss_weights: Any = None
+    label_smoothing: float = 0.0
+    f_divergence_type: str = "reverse_kl"
+    f_alpha_divergence_coef: float = 0.5
+    ld_alpha: float | None = None
+    use_weighting: bool = False
+    discopop_tau: float = 0.05
+    simpo_gamma: float = 0.5
+    cpo_alpha: float = 1.0
+    orpo_lambda: float = 1.0
+    precompute_ref_batch_size: int | None = None
+    disable_dropout: bool = True
+    sync_ref_model: bool = False
+    ref_model_mixup_alpha: float = 0.6
+    ref_model_sync_steps: int = 512
+    max_length: int | None = 1024
+
+    def __post_init__(self):
+        super().__post_init__()
+        types = [self.loss_type] if isinstance(self.loss_type, str) else list(self.loss_type)
+        for t in types:
+            if t not in dpo_losses.ALL_LOSS_TYPES:
+                raise ValueError(f"unknown DPO loss_type {t!r}")
+        if self.loss_weights is not None and len(self.loss_weights) != len(types):
+            raise ValueError("loss_weights must match loss_type")
+
+
+class DPOTrainer(DPTrainer):
+    """DP-DPO; ``ref_model=None`` uses a frozen copy of the initial policy (or the base model under LoRA)."""
+
+    def __init__(self, model=None, ref_model=None, args: DPOConfig | None = None, train_dataset=None, eval_dataset=None,
+                 processing_class=None, data_collator=None, **kw: Any):
+        args = args or DPOConfig()
+        self._dpo = args
+        if data_collator is None:
+            pad = getattr(processing_class, "pad_token_id", None) or 0
+            data_collator = lambda rows: adata.preference_collator(rows, pad_token_id=pad, max_length=args.max_length)
+        train_dataset = self._prepare(train_dataset, processing_class)
+        eval_dataset = self._prepare(eval_dataset, processing_class)
+        if args.disable_dropout:
+            for m in model.modules():
+                if isinstance(m, torch.nn.Dropout):
+                    m.p = 0.0
+        reference_free = all(t in ("simpo", "orpo", "sft") for t in ([args.loss_type] if isinstance(args.loss_type, str) else args.loss_type))
+        self.ref_model = None if reference_free else (ref_model if ref_model is not None else copy.deepcopy(model).requires_grad_(False))
+        args.dp_engine = "reference"        # the pair loss is not a plain LM loss; it runs on the functional engine
+        super().__init__(model=model, args=args, train_dataset=train_dataset, eval_dataset=eval_dataset,
+                         processing_class=processing_class, data_collator=data_collator, **kw)
+        if self.ref_model is not None:
+            self.ref_model.to(self.device).eval()
+            self.train_dataset = self._precompute_ref_logps(self.train_dataset)
+            if self.eval_dataset is not None:
+                self.eval_dataset = self._precompute_ref_logps(self.eval_dataset)
+        self._bco_delta = 0.0
+
+    @staticmethod
+    def tokenize_row(row, tokenizer):
+        if "prompt_input_ids" in row:
+            return dict(row)
+        if tokenizer is None:
+            raise ValueError("a processing_class (tokenizer) is required for text preference data")
+        return {"prompt_input_ids": tokenizer(row["prompt"])["input_ids"],
+                "chosen_input_ids": tokenizer(row["chosen"], add_special_tokens=False)["input_ids"],
+                "rejected_input_ids": tokenizer(row["rejected"], add_special_tokens=False)["input_ids"]}
+
+    @classmethod
+    def _prepare(cls, dataset, tokenizer):
+        if dataset is None:
+            return None
+        return [cls.tokenize_row(dataset[i], tokenizer) for i in range(len(dataset))]
+
+    def _seq_logps(self, call, ids, labels, average=False):
+        logits = call(ids)
+        logits = getattr(logits, "logits", logits)
+        if self._dpo.ld_alpha is not None and not average:
+            lp, mask = sft_losses.token_logps(logits, labels)
+            return lp, mask
+        return sft_losses.sequence_logp(logits, labels, average=average)
+
+    @torch.no_grad()
+    def _precompute_ref_logps(self, dataset):
+        """Reference log-probabilities of every pair, computed once (sharded by rank, then gathered)."""
+        if dataset is None or (len(dataset) and "ref_chosen_logps" in dataset[0]):
+            return dataset
+        bs = self._dpo.precompute_ref_batch_size or self.args.eval_batch_size
+        out = []
+        for lo in range(0, len(dataset), bs):
+            rows = [dataset[i] for i in range(lo, min(len(dataset), lo + bs))]
+            batch = self._to_device(self.data_collator(rows))
+            c = sft_losses.sequence_logp(_logits(self.ref_model(batch["chosen_input_ids"])), batch["chosen_labels"])
+            r = sft_losses.sequence_logp(_logits(self.ref_model(batch["rejected_input_ids"])), batch["rejected_labels"])
+            for row, ci, ri in zip(rows, c.tolist(), r.tolist()):
+                out.append({**row, "ref_chosen_logps": ci, "ref_rejected_logps": ri})
+        return out
+
+    def _pair_terms(self, call, ex):
+        cl, rl = ex["chosen_labels"].unsqueeze(0), ex["rejected_labels"].unsqueeze(0)
+        ci, ri = ex["chosen_input_ids"].unsqueeze(0), ex["rejected_input_ids"].unsqueeze(0)
+        c_logits, r_logits = _logits(call(ci)), _logits(call(ri))
+        c_lp, c_mask = sft_losses.token_logps(c_logits, cl)
+        r_lp, r_mask = sft_losses.token_logps(r_logits, rl)
+        if self._dpo.ld_alpha is not None:
+            common = torch.minimum(c_mask.sum(-1), r_mask.sum(-1))
+            c_sum = dpo_losses.ld_dpo_logp(c_lp, c_mask, common, self._dpo.ld_alpha)
+            r_sum = dpo_losses.ld_dpo_logp(r_lp, r_mask, common, self._dpo.ld_alpha)
+        else:
+            c_sum, r_sum = c_lp.sum(-1), r_lp.sum(-1)
+        c_avg = c_lp.sum(-1) / c_mask.sum(-1).clamp_min(1)
+        r_avg = r_lp.sum(-1) / r_mask.sum(-1).clamp_min(1)
+        weight = dpo_losses.wpo_weight(c_lp, c_mask, r_lp, r_mask) if self._dpo.use_weighting else None
+        return c_sum.squeeze(0), r_sum.squeeze(0), c_avg.squeeze(0), r_avg.squeeze(0), weight
+
+    def compute_per_example_loss(self, model_call, example):
+        a = self._dpo
+        c_sum, r_sum, c_avg, r_avg, weight = self._pair_terms(model_call, example)
+        ref_c = example.get("ref_chosen_logps", torch.zeros((), device=c_sum.device))
+        ref_r = example.get("ref_rejected_logps", torch.zeros((), device=c_sum.device))
+        use_avg = a.loss_type == "ipo" or (not isinstance(a.loss_type, str) and "ipo" in a.loss_type)
+        c_ratio = (c_avg if use_avg else c_sum) - ref_c
+        r_ratio = (r_avg if use_avg else r_sum) - ref_r
+        return dpo_losses.dpo_loss(a.loss_type, chosen_logratio=c_ratio, rejected_logratio=r_ratio, beta=a.beta,
+                                   label_smoothing=a.label_smoothing, loss_weights=a.loss_weights, chosen_nll=-c_avg,
+                                   chosen_avg_logp=c_avg, rejected_avg_logp=r_avg, bco_delta=self._bco_delta,
+                                   discopop_tau=a.discopop_tau, simpo_gamma=a.simpo_gamma, orpo_lambda=a.orpo_lambda,
+                                   f_divergence_type=a.f_divergence_type, f_alpha=a.f_alpha_divergence_coef,
+                                   pair_weight=weight.squeeze(0) if weight is not None else None)
+
+    def compute_batch_per_example_loss(self, batch):
+        n = batch["chosen_input_ids"].shape[0]
+        rows = [self.compute_per_example_loss(self.model, {k: v[i] for k, v in batch.items() if isinstance(v, torch.Tensor)}) for i in range(n)]
+        return torch.stack(rows) if rows else torch.zeros(0, device=self.device)
+
+    def _reference_step(self, batch, sp):
+        payload = {k: v for k, v in batch.items() if isinstance(v, torch.Tensor)}
+        payload.setdefault("input_ids", payload["chosen_input_ids"])
+        payload.setdefault("labels", payload["chosen_labels"])
+        out = super()._reference_step(payload, sp)
+        if self._dpo.sync_ref_model and self.ref_model is not None and self.state.global_step % self._dpo.ref_model_sync_steps == 0 and self.state.global_step:
+            self._ema_update_reference()
+        return out
+
+    @torch.no_grad()
+    def _ema_update_reference(self) -> None:
+        """TR-DPO: ``ref ← α·policy + (1−α)·ref`` (then reference log-probs are recomputed lazily)."""
+        self._write_back()
+        al = self._dpo.ref_model_mixup_alpha
+        for (n, p), (_, r) in zip(self.model.named_parameters(), self.ref_model.named_parameters()):
+            r.mul_(1 - al).add_(p.detach().to(r.dtype), alpha=al)
+        strip = lambda rows: [{k: v for k, v in row.items() if not k.startswith("ref_")} for row in rows]
+        self.train_dataset = self._precompute_ref_logps(strip(self.train_dataset))
+        self._local_data = None      # rebuilt on the next epoch boundary by _setup; current sampler keeps its indices
+
+
+def _logits(out):
+    return getattr(out, "logits", out)
+
+
+__all__ = ["DPOConfig", "DPOTrainer", "SFTConfig", "SFTTrainer"]

@@ -1,0 +1,136 @@
+"""DPTrainer / SFTTrainer / DPOTrainer on a tiny causal LM (CPU, reference engine), checkpoint resume."""
+import json
+import math
+import os
+
+import pytest
+import torch
+from torch import nn
+
+from opaque_b200.transformers import DPTrainer, TrainingArguments
+from opaque_b200.transformers.trainer import list_checkpoints
+from opaque_b200.transformers.trl import DPOConfig, DPOTrainer, SFTConfig, SFTTrainer
+
+
+class TinyLM(nn.Module):
+    def __init__(self, vocab=32, hidden=8):
+        super().__init__()
+        self.emb = nn.Embedding(vocab, hidden)
+        self.mix = nn.Linear(hidden, hidden)
+        self.head = nn.Linear(hidden, vocab)
+
+    def forward(self, ids):
+        h = self.emb(ids)
+        h = h + torch.tanh(self.mix(torch.cumsum(h, dim=1) / (1 + torch.arange(ids.shape[1], device=ids.device))[None, :, None]))
+        return self.head(h)
+
+
+def _data(n=64, T=12, vocab=32, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [{"input_ids": torch.randint(0, vocab, (T,), generator=g).tolist()} for _ in range(n)]
+
+
+def _args(tmp, **kw):
+    base = dict(output_dir=str(tmp), per_device_train_batch_size=8, max_steps=6, learning_rate=1e-2, logging_steps=2,
+                save_steps=3, privacy_noise_multiplier=1.0, clipping_norm=1.0, optim="adamw-bc", use_cpu=True,
+                lr_scheduler="constant", seed=3)
+    base.update(kw)
+    return TrainingArguments(**base)
+
+
+def test_training_arguments_validation_and_parsing():
+    a = TrainingArguments(privacy_noise_mechanism="mf_band", privacy_noise_mechanism_kwargs="bands=4", privacy_noise_multiplier=1.0)
+    assert a.sampling_mode == "b_min_sep" and a.privacy_noise_mechanism_kwargs == {"bands": 4}
+    assert TrainingArguments(clipping_norm='{"emb": 0.5, "fallback": 1.0}', privacy_noise_multiplier=1.0).clipping_norm == {"emb": 0.5, "fallback": 1.0}
+    assert TrainingArguments(optim="adamw_torch", privacy_noise_multiplier=1.0).optim == "adamw"
+    with pytest.raises(ValueError):
+        TrainingArguments(privacy_noise_mechanism="mf_blt", sampling_mode="poisson")
+    with pytest.raises(ValueError):
+        TrainingArguments(privacy_target_epsilon=3.0, privacy_noise_multiplier=1.0)
+    with pytest.raises(ValueError):
+        TrainingArguments.from_hf({"fsdp": "full_shard"})
+    hf = TrainingArguments.from_hf({"learning_rate": 1e-3, "max_grad_norm": 0.5, "lr_scheduler_type": "cosine"}, privacy_noise_multiplier=1.0)
+    assert hf.clipping_norm == 0.5 and hf.lr_scheduler == "cosine"
+
+
+def test_dp_trainer_runs_logs_and_accounts(tmp_path):
+    torch.manual_seed(0)
+    tr = DPTrainer(model=TinyLM(), args=_args(tmp_path), train_dataset=_data(), eval_dataset=_data(16, seed=1))
+    before = tr.evaluate()["eval_loss"] if False else None
+    out = tr.train()
+    assert out["global_step"] == 6 and math.isfinite(out["epsilon"]) and out["epsilon"] > 0
+    from opaque_b200.dpsgd import accounting as d
+    assert math.isclose(out["epsilon"], (d.poisson(d.gaussian(1.0), 8 / 64) * 6).epsilon_at(tr.target_delta), rel_tol=1e-9)
+    assert any("loss" in h for h in tr.state.log_history) and tr.evaluate()["eval_loss"] > 0
+    ck = list_checkpoints(str(tmp_path))
+    assert [os.path.basename(c) for c in ck] == ["checkpoint-3", "checkpoint-6"]
+    for f in ("model.safetensors", "dp_optimizer.pt", "dp_state.pt", "accountant.json", "trainer_state.json", "rng_state_0.pth"):
+        assert os.path.exists(os.path.join(ck[-1], f)), f
+    acct = json.load(open(os.path.join(ck[-1], "accountant.json")))
+    assert acct["process"]["type"] == "Repeated" and acct["process"]["count"] == 6
+
+
+def test_resume_is_equivalent_to_uninterrupted_run(tmp_path):
+    def run(out, resume=None, steps=6):
+        torch.manual_seed(0)
+        tr = DPTrainer(model=TinyLM(), args=_args(out, max_steps=steps, save_steps=3), train_dataset=_data())
+        tr.train(resume_from_checkpoint=resume)
+        return tr
+    full = run(tmp_path / "a")
+    run(tmp_path / "b")                                   # writes checkpoint-3 and checkpoint-6
+    resumed = run(tmp_path / "b", resume=str(tmp_path / "b" / "checkpoint-3"))
+    assert resumed.state.global_step == 6
+    for (n, p), (_, q) in zip(full.model.named_parameters(), resumed.model.named_parameters()):
+        assert torch.allclose(p, q, atol=1e-6), n
+    assert math.isclose(full.epsilon(), resumed.epsilon(), rel_tol=1e-9)
+    with pytest.raises(ValueError):
+        torch.manual_seed(0)
+        DPTrainer(model=TinyLM(), args=_args(tmp_path / "b", clipping_norm=2.0), train_dataset=_data()).train(
+            resume_from_checkpoint=str(tmp_path / "b" / "checkpoint-3"))
+
+
+def test_calibrated_noise_hits_target_epsilon(tmp_path):
+    args = _args(tmp_path, privacy_noise_multiplier=None, privacy_target_epsilon=4.0, privacy_target_delta=1e-5, max_steps=20, save_steps=0)
+    tr = DPTrainer(model=TinyLM(), args=args, train_dataset=_data())
+    out = tr.train()
+    assert out["epsilon"] <= 4.0 and out["epsilon"] > 3.9
+
+
+@pytest.mark.parametrize("mech,kw", [("mf_band", {"bands": 2}), ("mf_blt", {"max_buffers": 2}), ("mf_lambda_cgd", {"lambda_": 0.5})])
+def test_dpftrl_mechanisms_train(tmp_path, mech, kw):
+    args = _args(tmp_path, privacy_noise_mechanism=mech, privacy_noise_mechanism_kwargs=kw, max_steps=4, save_steps=0,
+                 privacy_noise_multiplier=2.0)
+    out = DPTrainer(model=TinyLM(), args=args, train_dataset=_data()).train()
+    assert out["global_step"] == 4 and math.isfinite(out["epsilon"])
+
+
+def test_adaptive_and_per_group_clipping(tmp_path):
+    out = DPTrainer(model=TinyLM(), args=_args(tmp_path, clipping_mode="adaptive", clipping_norm=0.5, save_steps=0),
+                    train_dataset=_data()).train()
+    assert out["global_step"] == 6
+    out = DPTrainer(model=TinyLM(), args=_args(tmp_path, clipping_norm={"emb": 0.5, "fallback": 1.0}, save_steps=0, optim="sgd"),
+                    train_dataset=_data()).train()
+    assert out["global_step"] == 6
+
+
+def test_sft_trainer_completion_only_and_dft(tmp_path):
+    rows = [{"input_ids": list(range(1, 9)), "completion_mask": [0, 0, 0, 0, 1, 1, 1, 1]} for _ in range(32)]
+    cfg = SFTConfig(output_dir=str(tmp_path), per_device_train_batch_size=4, max_steps=3, privacy_noise_multiplier=1.0,
+                    use_cpu=True, save_steps=0, loss_type="dft", learning_rate=1e-2)
+    tr = SFTTrainer(model=TinyLM(), args=cfg, train_dataset=rows)
+    batch = tr.data_collator(rows[:2])
+    assert (batch["labels"][0] != -100).sum() == 4
+    assert tr.train()["global_step"] == 3
+
+
+def test_dpo_trainer_pairs(tmp_path):
+    g = torch.Generator().manual_seed(0)
+    rows = [{"prompt_input_ids": torch.randint(0, 32, (4,), generator=g).tolist(),
+             "chosen_input_ids": torch.randint(0, 32, (5,), generator=g).tolist(),
+             "rejected_input_ids": torch.randint(0, 32, (3,), generator=g).tolist()} for _ in range(24)]
+    cfg = DPOConfig(output_dir=str(tmp_path), per_device_train_batch_size=4, max_steps=3, privacy_noise_multiplier=1.0,
+                    use_cpu=True, save_steps=0, learning_rate=1e-2, loss_type=["sigmoid", "sft"], loss_weights=[1.0, 0.1])
+    tr = DPOTrainer(model=TinyLM(), args=cfg, train_dataset=rows)
+    assert "ref_chosen_logps" in tr.train_dataset[0]
+    out = tr.train()
+    assert out["global_step"] == 3 and math.isfinite(tr.state.log_history[-2].get("loss", 0.0))

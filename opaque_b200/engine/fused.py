@@ -105,6 +105,22 @@ class Capture:
                        status=self.status)
         self.records.append(("embedding", slot, g2d, ids.reshape(-1).to(torch.int64)))
 
+    def add_grouped_linear(self, weight: torch.nn.Parameter, a_rows: torch.Tensor, g_rows: torch.Tensor,
+                           expert_offs: torch.Tensor, seg: torch.Tensor, example_of_row: torch.Tensor, tokens: int) -> None:
+        """Stacked expert weights ``[E, out, in]``: rows sorted by (expert, example).
+
+        ``seg`` delimits the (expert, example) segments for the ragged ghost norm; ``expert_offs`` (cumulative row
+        ends per expert) delimits the groups of the clip-weighted grouped weight-gradient GEMM.
+        """
+        slot = self.engine.slot_of(weight)
+        E = weight.shape[0]
+        seg_out = (torch.arange(seg.numel() - 1, device=seg.device, dtype=torch.int32) % self.batch_size).contiguous()
+        ops.ghost_norm(a_rows, g_rows, self._part(slot.name + "#experts"), tokens, seg_offsets=seg, seg_out=seg_out,
+                       status=self.status)
+        groups = torch.zeros(E + 1, dtype=torch.int32, device=seg.device)
+        groups[1:] = expert_offs
+        self.records.append(("grouped", slot, g_rows, (a_rows, groups, example_of_row)))
+
     def pe_view(self, param: torch.nn.Parameter) -> torch.Tensor:
         """``[mb, numel]`` window of the per-example buffer that belongs to ``param``."""
         slot = self.engine.slot_of(param)
@@ -187,7 +203,14 @@ class Capture:
         if self.records:
             row_scale = c.repeat_interleave(self.tokens)
             for kind, slot, g2d, other in self.records:
-                if kind == "linear":
+                if kind == "grouped":
+                    a_rows, groups, ex_row = other
+                    E, d_out, d_in = slot.shape
+                    ops.wgrad_clip(g2d, a_rows, tgt["out"], row_scale=c.index_select(0, ex_row.long()), seg_offsets=groups,
+                                   num_groups=E, splits=1, out_offset=slot.offset, ldm=d_in, ldn=1, accumulate=True,
+                                   group_stride=d_out * d_in, peer_table=tgt["peer_table"],
+                                   shard_elems=tgt["shard_elems"], status=self.status)
+                elif kind == "linear":
                     ops.wgrad_clip(g2d, other, tgt["out"], row_scale=row_scale, out_offset=slot.offset,
                                    ldm=slot.shape[1], ldn=1, accumulate=True, peer_table=tgt["peer_table"],
                                    shard_elems=tgt["shard_elems"], status=self.status)

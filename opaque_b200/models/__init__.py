@@ -2,6 +2,7 @@
 from .gpt2 import GPT2Config, GPT2LMHeadModel
 from .layers import Embedding, LayerNorm, Linear, RMSNorm, linear_cross_entropy
 from .llama import LlamaConfig, LlamaForCausalLM, shift_labels
+from .moe import MoEConfig, MoEForCausalLM
 
-__all__ = ["Embedding", "GPT2Config", "GPT2LMHeadModel", "LayerNorm", "Linear", "LlamaConfig", "LlamaForCausalLM",
+__all__ = ["Embedding", "GPT2Config", "GPT2LMHeadModel", "LayerNorm", "Linear", "LlamaConfig", "LlamaForCausalLM", "MoEConfig", "MoEForCausalLM",
            "RMSNorm", "linear_cross_entropy", "shift_labels"]

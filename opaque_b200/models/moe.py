@@ -1,0 +1,216 @@
+"""Mixture-of-experts decoder (Mixtral / Qwen-MoE style): top-k softmax router, stacked SwiGLU experts, shared experts.
+
+Expert weights are stacked as in Hugging Face (``gate_up_proj [E, 2I, H]``, ``down_proj [E, H, I]``) and replicated
+across data-parallel ranks.  Tokens are sorted by (expert, example), so that
+
+  * forward / input gradients are grouped GEMMs over contiguous expert blocks (``torch._grouped_mm``),
+  * every (expert, example) pair is a contiguous row segment: the ragged tcgen05 ghost-norm kernel adds
+    ``‖A_{e,i}ᵀ G_{e,i}‖²`` to example i's squared norm, and
+  * the clip-weighted grouped tcgen05 weight-gradient GEMM (one segment per expert, per-row factor
+    ``c_{example(row)}``) reduces ``Σ_i c_i · A_{e,i}ᵀ G_{e,i}`` into the sharded gradient — per-example expert
+    gradients are never materialised (the reference materialises ``(B, E, 2I, H)`` through "virtual experts").
+
+Reference counterparts: packages/opaque-patches/src/opaque/api/patches/kernels/{fused_moe.py:48-462, moe.py:49-221,
+_grouped_moe.py}, transformers/models/mixtral.py, components/moe.py.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+from torch import nn
+from torch.autograd import Function
+
+from .. import ops
+from ..engine import fused
+from .layers import Embedding, Linear, RMSNorm, linear_cross_entropy, per_example_token_weights
+from .llama import LlamaAttention, LlamaConfig, LlamaMLP
+
+
+@dataclasses.dataclass
+class MoEConfig:
+    vocab_size: int = 151936
+    hidden_size: int = 2048
+    num_hidden_layers: int = 24
+    num_attention_heads: int = 16
+    num_key_value_heads: int = 16
+    num_experts: int = 60
+    moe_intermediate_size: int = 1408
+    num_shared_experts: int = 4
+    num_experts_per_tok: int = 4
+    norm_topk_prob: bool = False
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1000000.0
+    max_position_embeddings: int = 4096
+
+    @property
+    def padded_experts(self) -> int:
+        return (self.num_experts + 7) // 8 * 8          # router rows padded so gradient rows stay 16-byte aligned
+
+    def attn_config(self) -> LlamaConfig:
+        return LlamaConfig(vocab_size=self.vocab_size, hidden_size=self.hidden_size, num_attention_heads=self.num_attention_heads,
+                           num_key_value_heads=self.num_key_value_heads, rms_norm_eps=self.rms_norm_eps,
+                           rope_theta=self.rope_theta, max_position_embeddings=self.max_position_embeddings,
+                           intermediate_size=self.moe_intermediate_size * max(self.num_shared_experts, 1))
+
+    @staticmethod
+    def tiny() -> "MoEConfig":
+        return MoEConfig(vocab_size=512, hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4,
+                         num_experts=6, moe_intermediate_size=64, num_shared_experts=1, num_experts_per_tok=2,
+                         max_position_embeddings=256)
+
+
+def grouped_mm(a: torch.Tensor, b: torch.Tensor, offs: torch.Tensor) -> torch.Tensor:
+    """``out[rows of group e] = a[rows of group e] @ b[e]`` for ``b [E, K, N]`` and cumulative row offsets ``offs [E]``."""
+    if a.is_cuda and a.dtype == torch.bfloat16 and hasattr(torch, "_grouped_mm") and a.shape[0] > 0:
+        return torch._grouped_mm(a, b, offs=offs)
+    out = a.new_zeros(a.shape[0], b.shape[-1])
+    lo = 0
+    for e, hi in enumerate(offs.tolist()):
+        if hi > lo:
+            out[lo:hi] = a[lo:hi] @ b[e]
+        lo = hi
+    return out
+
+
+def route_sort(topk_idx: torch.Tensor, num_experts: int, batch: int, tokens: int):
+    """Sort the ``T·k`` (token, expert) assignments by (expert, example).
+
+    Returns ``token_sorted`` (token id of each sorted row), ``slot_sorted`` (position in ``[T·k]``), cumulative
+    per-expert row offsets ``offs [E]`` (int32) and the (expert, example) segment table ``seg [E·B + 1]`` (int32).
+    """
+    T, k = topk_idx.shape
+    flat_e = topk_idx.reshape(-1)
+    token_of = torch.arange(T, device=topk_idx.device).repeat_interleave(k)
+    key = flat_e * batch + token_of // tokens
+    order = torch.argsort(key, stable=True)
+    counts = torch.bincount(key, minlength=num_experts * batch)
+    seg = torch.zeros(num_experts * batch + 1, dtype=torch.int32, device=topk_idx.device)
+    seg[1:] = counts.cumsum(0)
+    offs = seg[batch::batch].contiguous()
+    return token_of[order], order, offs, seg
+
+
+class _Experts(Function):
+    @staticmethod
+    def forward(ctx, x, topk_idx, topk_w, w1, w2, batch, tokens):
+        T, H = x.shape
+        E, two_i, _ = w1.shape
+        I = two_i // 2
+        token_sorted, slot_sorted, offs, seg = route_sort(topk_idx, E, batch, tokens)
+        xs = x.index_select(0, token_sorted)
+        h = grouped_mm(xs, w1.transpose(1, 2), offs)
+        act = ops.swiglu(h[:, :I], h[:, I:])
+        y = grouped_mm(act, w2.transpose(1, 2), offs)
+        wrow = topk_w.reshape(-1).index_select(0, slot_sorted).to(y.dtype)
+        out = torch.zeros_like(x).index_add_(0, token_sorted, y * wrow[:, None])
+        ctx.save_for_backward(xs, h, act, y, wrow, token_sorted, slot_sorted, offs, seg, w1, w2)
+        ctx.meta = (batch, tokens, topk_w.shape)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        xs, h, act, y, wrow, token_sorted, slot_sorted, offs, seg, w1, w2 = ctx.saved_tensors
+        batch, tokens, wshape = ctx.meta
+        I = w2.shape[2]
+        g = dout.index_select(0, token_sorted)
+        dw_rows = (g.float() * y.float()).sum(-1)
+        dtopk = torch.zeros(wshape, dtype=torch.float32, device=dout.device).reshape(-1).index_copy_(0, slot_sorted, dw_rows).view(wshape)
+        dy = (g * wrow[:, None]).contiguous()
+        dact = grouped_mm(dy, w2, offs)
+        gate, up = h[:, :I].float(), h[:, I:].float()
+        sig = torch.sigmoid(gate)
+        silu = gate * sig
+        dh = torch.cat([dact.float() * up * sig * (1 + gate * (1 - sig)), dact.float() * silu], dim=1).to(h.dtype)
+        dxs = grouped_mm(dh, w1, offs)
+        dx = torch.zeros_like(dout).index_add_(0, token_sorted, dxs)
+        cap = fused.current_capture()
+        if cap is not None:
+            ex_row = (token_sorted // tokens).to(torch.int32)
+            cap.add_grouped_linear(w1, xs, dh, offs, seg, ex_row, tokens)
+            cap.add_grouped_linear(w2, act.contiguous(), dy, offs, seg, ex_row, tokens)
+            return dx, None, dtopk.to(wrow.dtype), None, None, None, None
+        E = w1.shape[0]
+        gw1, gw2 = torch.zeros_like(w1, dtype=torch.float32), torch.zeros_like(w2, dtype=torch.float32)
+        lo = 0
+        for e, hi in enumerate(offs.tolist()):
+            if hi > lo:
+                gw1[e] = dh[lo:hi].float().t() @ xs[lo:hi].float()
+                gw2[e] = dy[lo:hi].float().t() @ act[lo:hi].float()
+            lo = hi
+        return dx, None, dtopk.to(wrow.dtype), gw1.to(w1.dtype), gw2.to(w2.dtype), None, None
+
+
+class MoEExperts(nn.Module):
+    def __init__(self, cfg: MoEConfig, dtype, device):
+        super().__init__()
+        E, I, H = cfg.num_experts, cfg.moe_intermediate_size, cfg.hidden_size
+        self.gate_up_proj = nn.Parameter(torch.empty(E, 2 * I, H, dtype=dtype, device=device).normal_(std=0.02))
+        self.down_proj = nn.Parameter(torch.empty(E, H, I, dtype=dtype, device=device).normal_(std=0.02))
+
+    def forward(self, x2d, topk_idx, topk_w, batch, tokens):
+        return _Experts.apply(x2d, topk_idx, topk_w, self.gate_up_proj, self.down_proj, batch, tokens)
+
+
+class SparseMoeBlock(nn.Module):
+    def __init__(self, cfg: MoEConfig, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        self.gate = Linear(cfg.hidden_size, cfg.padded_experts, dtype=dtype, device=device)
+        self.experts = MoEExperts(cfg, dtype, device)
+        self.shared_expert = LlamaMLP(cfg.attn_config(), dtype, device) if cfg.num_shared_experts > 0 else None
+
+    def forward(self, x):
+        B, T, H = x.shape
+        cfg = self.cfg
+        logits = self.gate(x).float()[..., :cfg.num_experts]
+        probs = torch.softmax(logits, dim=-1)
+        w, idx = torch.topk(probs, cfg.num_experts_per_tok, dim=-1)
+        if cfg.norm_topk_prob:
+            w = w / w.sum(-1, keepdim=True)
+        y = self.experts(x.reshape(B * T, H), idx.reshape(B * T, -1), w.reshape(B * T, -1).to(x.dtype), B, T).view(B, T, H)
+        if self.shared_expert is not None:
+            y = y + self.shared_expert(x)
+        return y
+
+
+class MoEDecoderLayer(nn.Module):
+    def __init__(self, cfg: MoEConfig, dtype, device):
+        super().__init__()
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
+        self.self_attn = LlamaAttention(cfg.attn_config(), dtype, device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
+        self.mlp = SparseMoeBlock(cfg, dtype, device)
+
+    def forward(self, h, cos, sin, pos):
+        h = h + self.self_attn(self.input_layernorm(h), cos, sin, pos)
+        return h + self.mlp(self.post_attention_layernorm(h))
+
+
+class MoEForCausalLM(nn.Module):
+    def __init__(self, cfg: MoEConfig, *, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.config = cfg
+        self.embed_tokens = Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
+        self.layers = nn.ModuleList(MoEDecoderLayer(cfg, dtype, device) for _ in range(cfg.num_hidden_layers))
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
+        self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, dtype=dtype, device=device)
+        cos, sin = ops.rope_tables(cfg.hidden_size // cfg.num_attention_heads, cfg.max_position_embeddings, cfg.rope_theta, device=device)
+        self.register_buffer("rope_cos", cos, persistent=False)
+        self.register_buffer("rope_sin", sin, persistent=False)
+
+    def hidden_states(self, input_ids, position_ids=None):
+        h = self.embed_tokens(input_ids)
+        for layer in self.layers:
+            h = layer(h, self.rope_cos, self.rope_sin, position_ids)
+        return self.norm(h)
+
+    def forward(self, input_ids, position_ids=None):
+        return self.lm_head(self.hidden_states(input_ids, position_ids))
+
+    def per_example_loss(self, input_ids, labels, position_ids=None):
+        B, T = input_ids.shape
+        h = self.hidden_states(input_ids, position_ids).reshape(B * T, -1)
+        w = per_example_token_weights(labels).reshape(-1)
+        rows = linear_cross_entropy(h, self.lm_head.weight, labels.reshape(-1), w)
+        return rows.view(B, T).sum(1)

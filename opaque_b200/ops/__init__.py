@@ -118,27 +118,42 @@ def wgrad_clip_ref(a, b, *, row_scale=None, seg_offsets=None, num_groups=1):
 
 
 def ghost_norm(a: torch.Tensor | None, g: torch.Tensor, norm2: torch.Tensor, tokens_per_example: int, *,
-               ids: torch.Tensor | None = None, status: StatusWord | None = None,
+               ids: torch.Tensor | None = None, seg_offsets: torch.Tensor | None = None,
+               seg_out: torch.Tensor | None = None, status: StatusWord | None = None,
                wait_budget_s: float = DEFAULT_WAIT_BUDGET_S) -> None:
-    """``norm2[i] += ‖A_iᵀ G_i‖_F²`` for every example (rows of example i are contiguous).
+    """``norm2[i] += ‖A_iᵀ G_i‖_F²`` for every segment i of rows.
 
-    With ``ids`` (int32 ``[B*T]``) the inputs are one-hot rows (embedding layer) and ``a`` is unused.
+    Uniform layout: segment i is rows ``[i·T, (i+1)·T)``.  Ragged layout: ``seg_offsets`` (int32 ``[S+1]``) gives the
+    row range of each segment (none longer than ``tokens_per_example``) and ``seg_out`` (int32 ``[S]``) the
+    accumulator each segment adds to (e.g. the example an (expert, example) group belongs to).
+    With ``ids`` (int32, one per row) the inputs are one-hot rows (embedding layer) and ``a`` is unused.
     """
     _need_bf16(g)
     rows, dg = g.shape
-    B = rows // tokens_per_example
-    if B * tokens_per_example != rows:
-        raise ValueError("rows must be a multiple of tokens_per_example")
+    if seg_offsets is None:
+        B = rows // tokens_per_example
+        if B * tokens_per_example != rows:
+            raise ValueError("rows must be a multiple of tokens_per_example")
+        if norm2.numel() < B:
+            raise ValueError("one accumulator per example is required")
+    else:
+        if seg_offsets.dtype != torch.int32 or (seg_out is not None and seg_out.dtype != torch.int32):
+            raise TypeError("segment tables must be int32")
+        B = seg_offsets.numel() - 1
+        if seg_out is not None and seg_out.numel() != B:
+            raise ValueError("seg_out needs one entry per segment")
     if ids is None:
         _need_bf16(a)
+        if a.shape[0] != rows:
+            raise ValueError("a and g must have the same number of rows")
         da, lda, ap = a.shape[1], a.stride(0), a.data_ptr()
     else:
-        if ids.dtype != torch.int32:
-            raise TypeError("ids must be int32")
+        if ids.dtype != torch.int32 or ids.numel() != rows:
+            raise TypeError("ids must be int32 with one entry per row")
         da, lda, ap = 0, 0, None
     rc = lib.load().ob_ghost_norm(ap, g.data_ptr(), lib.ptr(ids), B, tokens_per_example, da, dg, lda, g.stride(0),
-                                  norm2.data_ptr(), status.ptr() if status else None, wait_budget_s, lib.sm_count(),
-                                  lib.stream())
+                                  norm2.data_ptr(), lib.ptr(seg_offsets), lib.ptr(seg_out), rows,
+                                  status.ptr() if status else None, wait_budget_s, lib.sm_count(), lib.stream())
     lib.check(rc, "ghost_norm")
 
 

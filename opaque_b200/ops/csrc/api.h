@@ -12,7 +12,8 @@ int ob_wgrad_clip(const void* a, const void* b, int T, int M, int N, long long l
                   int accumulate, int block_n, int* status, double wait_budget_s, int num_sms, void* stream);
 
 int ob_ghost_norm(const void* a, const void* g, const int* ids, int B, int T, int Da, int Dg, long long lda,
-                  long long ldg, float* norm2, int* status, double wait_budget_s, int num_sms, void* stream);
+                  long long ldg, float* norm2, const int* seg, const int* seg_out, long long total_rows, int* status,
+                  double wait_budget_s, int num_sms, void* stream);
 
 #ifdef __cplusplus
 }

@@ -31,9 +31,11 @@ constexpr int GH_THREADS = 192;
 constexpr int GH_SMEM = GH_STAGES * GH_STAGE_BYTES + 256 + 1024;
 
 struct GhostParams {
-  int B, T, Da, Dg;
-  const int* ids;        // [B*T] or nullptr
-  float* norm2;          // [B], accumulated with atomics
+  int B, T, Da, Dg;      // B segments of (at most) T rows
+  const int* ids;        // [rows] or nullptr
+  const int* seg;        // [B + 1] row offsets of ragged segments, or nullptr (segment b = rows [b*T, (b+1)*T))
+  const int* seg_out;    // [B] accumulator index of every segment, or nullptr (identity)
+  float* norm2;          // accumulated with atomics
   int* status;
   unsigned long long wait_budget_ns;
 };
@@ -108,7 +110,10 @@ ghost_norm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       bool ok = true;
       for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
         const GhostItem it = ghost_decode(w, pairs, nt);
-        const int r1 = it.ex * p.T + it.tb * GH_TILE, r2 = it.ex * p.T + it.tb2 * GH_TILE;
+        const int s0 = p.seg ? p.seg[it.ex] : it.ex * p.T;
+        const int len = p.seg ? p.seg[it.ex + 1] - s0 : p.T;
+        if (it.tb2 * GH_TILE >= len) continue;                 // tile pair lies outside this (ragged) segment
+        const int r1 = s0 + it.tb * GH_TILE, r2 = s0 + it.tb2 * GH_TILE;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_EMPTY, budget)) {
             ok = false;
@@ -140,6 +145,10 @@ ghost_norm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        if (p.seg) {
+          const GhostItem it = ghost_decode(w, pairs, nt);
+          if (it.tb2 * GH_TILE >= p.seg[it.ex + 1] - p.seg[it.ex]) continue;
+        }
         const int as = acc_iter & 1;
         if (!mbar_wait(&tmem_empty[as], ((acc_iter >> 1) & 1) ^ 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_EMPTY,
                        budget)) {
@@ -178,6 +187,9 @@ ghost_norm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     bool ok = true;
     for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
       const GhostItem it = ghost_decode(w, pairs, nt);
+      const int s0 = p.seg ? p.seg[it.ex] : it.ex * p.T;
+      const int len = p.seg ? p.seg[it.ex + 1] - s0 : p.T;
+      if (it.tb2 * GH_TILE >= len) continue;
       const int as = acc_iter & 1;
       if (!mbar_wait(&tmem_full[as], (acc_iter >> 1) & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL, budget)) {
         ok = false;
@@ -185,7 +197,7 @@ ghost_norm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       }
       tc_fence_after();
       const int t = it.tb * GH_TILE + q * 32 + lane;
-      const int my_id = (p.ids && t < p.T) ? p.ids[it.ex * p.T + t] : -1;
+      const int my_id = (p.ids && t < len) ? p.ids[s0 + t] : -1;
       float acc = 0.f;
       for (int c = 0; c < GH_TILE / 32; ++c) {
         float sg[32], sa[32];
@@ -199,12 +211,12 @@ ghost_norm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           const int t2 = tc0 + j;
           float a;
           if (p.ids) {
-            const int other = (t2 < p.T) ? __ldg(p.ids + it.ex * p.T + t2) : -2;
+            const int other = (t2 < len) ? __ldg(p.ids + s0 + t2) : -2;
             a = (other == my_id) ? 1.f : 0.f;
           } else {
             a = sa[j];
           }
-          if (t < p.T && t2 < p.T) acc += a * sg[j];
+          if (t < len && t2 < len) acc += a * sg[j];
         }
       }
       tc_fence_before();
@@ -212,7 +224,7 @@ ghost_norm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       if (lane == 0) mbar_arrive(&tmem_empty[as]);
       ++acc_iter;
       acc = warp_sum(acc);
-      if (lane == 0) atomicAdd(p.norm2 + it.ex, (it.tb == it.tb2 ? 1.f : 2.f) * acc);
+      if (lane == 0) atomicAdd(p.norm2 + (p.seg_out ? p.seg_out[it.ex] : it.ex), (it.tb == it.tb2 ? 1.f : 2.f) * acc);
     }
   }
 
@@ -227,15 +239,17 @@ ghost_norm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 }  // namespace ob
 
 extern "C" int ob_ghost_norm(const void* a, const void* g, const int* ids, int B, int T, int Da, int Dg,
-                             long long lda, long long ldg, float* norm2, int* status, double wait_budget_s,
-                             int num_sms, void* stream) {
+                             long long lda, long long ldg, float* norm2, const int* seg, const int* seg_out,
+                             long long total_rows, int* status, double wait_budget_s, int num_sms, void* stream) {
   using namespace ob;
   if (B <= 0 || T <= 0 || Dg <= 0) return 0;
+  const long long rows = seg ? total_rows : static_cast<long long>(B) * T;
+  if (rows <= 0) return 0;
   CUtensorMap ma, mg;
-  int rc = make_bf16_map_2d(&mg, g, static_cast<long long>(B) * T, Dg, ldg, GH_BLOCK_K, GH_TILE);
+  int rc = make_bf16_map_2d(&mg, g, rows, Dg, ldg, GH_BLOCK_K, GH_TILE);
   if (rc) return rc;
   if (ids == nullptr) {
-    rc = make_bf16_map_2d(&ma, a, static_cast<long long>(B) * T, Da, lda, GH_BLOCK_K, GH_TILE);
+    rc = make_bf16_map_2d(&ma, a, rows, Da, lda, GH_BLOCK_K, GH_TILE);
     if (rc) return rc;
   } else {
     ma = mg;
@@ -249,6 +263,8 @@ extern "C" int ob_ghost_norm(const void* a, const void* g, const int* ids, int B
   GhostParams p;
   p.B = B; p.T = T; p.Da = Da; p.Dg = Dg;
   p.ids = ids;
+  p.seg = seg;
+  p.seg_out = seg_out;
   p.norm2 = norm2;
   p.status = status;
   p.wait_budget_ns = static_cast<unsigned long long>(wait_budget_s * 1e9);

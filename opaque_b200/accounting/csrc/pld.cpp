@@ -828,17 +828,197 @@ Pld nonprivate_pld(const Config& cfg) {
   return out;
 }
 
-// Random allocation (each record lands in k of num_bins steps, uniformly): the t-step run is dominated
-// by num_bins-fold composition of Poisson sampling at rate k/num_bins with an extra sqrt factor only in
-// special regimes; a valid and simple upper bound used here is the replace-free decomposition of
-// Feldman & Shenfeld: epsilon(random allocation) <= epsilon(Poisson(rate = k / num_bins), num_bins steps)
-// evaluated at a slightly smaller delta.  The returned PLD is that Poisson composition.
-Pld random_allocation_gaussian_pld(double nm, std::size_t num_bins, std::size_t k, const Config& cfg) {
+// ---- random allocation -----------------------------------------------------------------------------------
+// k-out-of-t random allocation (each record is used in k steps chosen uniformly out of t).  For one allocation
+// (k = 1) Feldman & Shenfeld show the privacy loss is a transform of the base loss L ~ N(mu, 2 mu), mu = 1/(2 sigma^2):
+//     remove:  ln( (1/t) ( e^{L_0} + sum_{i=1}^{t-1} e^{-L~_i} ) )      with  -L~_i ~ N(-mu, 2 mu)
+//     add:    -ln( (1/t) sum_{i=1}^{t} e^{-L_i} )
+// i.e. log-mean-exps of independent terms.  The sums are convolutions of EXPONENTIATED distributions, carried on a
+// geometric grid (value e^{alpha j}) with directed rounding: adding two grid values lands on
+// max(i, j) + shift(|i - j|) with shift(d) = ceil or floor of log1p(e^{-alpha d}) / alpha, so one convolution is an
+// O(G^2) table-driven scatter and t-fold sums take O(log t) convolutions.  k > 1 composes k single allocations
+// over floor(t/k) / ceil(t/k) steps.
+
+namespace {
+
+struct GeomPmf {
+  double alpha = 1e-3;
+  std::int64_t lower = 0;          // value of p[i] is exp(alpha * (lower + i))
+  std::vector<double> p;
+  double inf_mass = 0.0;           // mass at +infinity
+  double zero_mass = 0.0;          // mass at value 0
+};
+
+// Discretise N(mean, var) on the grid alpha * j, each cell's mass moved UP to its right end; the lower tail (mass
+// beta) lumps onto the first point, the upper tail (mass beta) is returned separately.
+void disc_normal(double mean, double var, double alpha, double beta, std::int64_t& lo, std::vector<double>& probs,
+                 double& upper_tail) {
+  const double sd = std::sqrt(var);
+  const double zlo = norm_ppf(beta), zhi = -zlo;
+  lo = static_cast<std::int64_t>(std::floor((mean + sd * zlo) / alpha));
+  const std::int64_t hi = static_cast<std::int64_t>(std::ceil((mean + sd * zhi) / alpha));
+  probs.assign(static_cast<std::size_t>(hi - lo + 1), 0.0);
+  double prev = 0.0;
+  for (std::int64_t j = lo; j <= hi; ++j) {
+    const double c = norm_cdf((static_cast<double>(j) * alpha - mean) / sd);
+    probs[static_cast<std::size_t>(j - lo)] = c - prev;
+    prev = c;
+  }
+  upper_tail = std::max(0.0, 1.0 - prev);
+}
+
+GeomPmf geom_conv(const GeomPmf& a, const GeomPmf& b, bool round_up, double beta) {
+  GeomPmf out;
+  out.alpha = a.alpha;
+  out.inf_mass = a.inf_mass + b.inf_mass - a.inf_mass * b.inf_mass;
+  out.zero_mass = a.zero_mass * b.zero_mass;
+  if (a.p.empty() || b.p.empty()) {
+    const GeomPmf& keep = a.p.empty() ? b : a;
+    const double z = a.p.empty() ? a.zero_mass : b.zero_mass;
+    out.lower = keep.lower;
+    out.p = keep.p;
+    for (double& v : out.p) v *= z;
+    return out;
+  }
+  const std::int64_t amax = a.lower + static_cast<std::int64_t>(a.p.size()) - 1;
+  const std::int64_t bmax = b.lower + static_cast<std::int64_t>(b.p.size()) - 1;
+  const std::int64_t lo = std::min(a.lower, b.lower);
+  const std::int64_t max_d = std::max(amax, bmax) - lo;
+  std::vector<std::int64_t> shift(static_cast<std::size_t>(max_d + 1));
+  for (std::int64_t d = 0; d <= max_d; ++d) {
+    const double v = std::log1p(std::exp(-a.alpha * static_cast<double>(d))) / a.alpha;
+    shift[static_cast<std::size_t>(d)] = static_cast<std::int64_t>(round_up ? std::ceil(v - 1e-12) : std::floor(v + 1e-12));
+  }
+  const std::int64_t out_hi = std::max(amax, bmax) + shift[0];
+  const std::size_t n = static_cast<std::size_t>(out_hi - lo + 1);
+  out.lower = lo;
+  out.p.assign(n, 0.0);
+  const std::int64_t na = static_cast<std::int64_t>(a.p.size()), nb = static_cast<std::int64_t>(b.p.size());
+#pragma omp parallel
+  {
+    std::vector<double> local(n, 0.0);
+#pragma omp for schedule(dynamic, 64) nowait
+    for (std::int64_t i = 0; i < na; ++i) {
+      const double pa = a.p[static_cast<std::size_t>(i)];
+      if (pa == 0.0) continue;
+      const std::int64_t vi = a.lower + i;
+      for (std::int64_t j = 0; j < nb; ++j) {
+        const double pb = b.p[static_cast<std::size_t>(j)];
+        if (pb == 0.0) continue;
+        const std::int64_t vj = b.lower + j;
+        const std::int64_t d = vi > vj ? vi - vj : vj - vi;
+        local[static_cast<std::size_t>(std::max(vi, vj) + shift[static_cast<std::size_t>(d)] - lo)] += pa * pb;
+      }
+    }
+#pragma omp critical
+    for (std::size_t k = 0; k < n; ++k) out.p[k] += local[k];
+  }
+  // a zero on one side leaves the other side's value unchanged
+  if (b.zero_mass > 0.0)
+    for (std::int64_t i = 0; i < na; ++i) out.p[static_cast<std::size_t>(a.lower + i - lo)] += b.zero_mass * a.p[static_cast<std::size_t>(i)];
+  if (a.zero_mass > 0.0)
+    for (std::int64_t j = 0; j < nb; ++j) out.p[static_cast<std::size_t>(b.lower + j - lo)] += a.zero_mass * b.p[static_cast<std::size_t>(j)];
+  // trim tails (directed): upper tail -> infinity when rounding up, else onto the last kept point; lower tail onto
+  // the first kept point when rounding up, else to zero
+  std::size_t first = 0, last = n;
+  double acc = 0.0;
+  while (first + 1 < last && acc + out.p[first] <= beta) acc += out.p[first++];
+  if (round_up) out.p[first] += acc; else out.zero_mass += acc;
+  double top = 0.0;
+  while (last > first + 1 && top + out.p[last - 1] <= beta) top += out.p[--last];
+  if (round_up) out.inf_mass += top; else out.p[last - 1] += top;
+  out.p = std::vector<double>(out.p.begin() + static_cast<std::ptrdiff_t>(first), out.p.begin() + static_cast<std::ptrdiff_t>(last));
+  out.lower = lo + static_cast<std::int64_t>(first);
+  return out;
+}
+
+GeomPmf geom_self_conv(const GeomPmf& base, std::size_t times, bool round_up, double beta) {
+  GeomPmf result;
+  bool have = false;
+  GeomPmf pw = base;
+  std::size_t n = times;
+  while (n > 0) {
+    if (n & 1) {
+      result = have ? geom_conv(result, pw, round_up, beta) : pw;
+      have = true;
+    }
+    n >>= 1;
+    if (n) pw = geom_conv(pw, pw, round_up, beta);
+  }
+  return result;
+}
+
+// loss = sign * (alpha * idx - log t), rounded UP onto the output grid
+Pmf geom_to_loss_pmf(const GeomPmf& g, double t, double sign, double out_disc, std::size_t max_grid, double extra_inf) {
+  Pmf pmf;
+  pmf.discretization = out_disc;
+  pmf.max_grid_size = max_grid;
+  pmf.infinity_mass = extra_inf;
+  if (g.p.empty()) return pmf;
+  const double logt = std::log(t);
+  std::int64_t lo = std::numeric_limits<std::int64_t>::max(), hi = std::numeric_limits<std::int64_t>::min();
+  std::vector<std::int64_t> idx(g.p.size());
+  for (std::size_t i = 0; i < g.p.size(); ++i) {
+    const double loss = sign * (g.alpha * static_cast<double>(g.lower + static_cast<std::int64_t>(i)) - logt);
+    idx[i] = static_cast<std::int64_t>(std::ceil(loss / out_disc - 1e-9));
+    lo = std::min(lo, idx[i]);
+    hi = std::max(hi, idx[i]);
+  }
+  pmf.lower = lo;
+  pmf.probs.assign(static_cast<std::size_t>(hi - lo + 1), 0.0);
+  for (std::size_t i = 0; i < g.p.size(); ++i) pmf.probs[static_cast<std::size_t>(idx[i] - lo)] += g.p[i];
+  return pmf.maybe_coarsen();
+}
+
+Pld single_allocation_pld(double sigma, std::size_t t, const Config& cfg) {
+  const double mu = 0.5 / (sigma * sigma), var = 2.0 * mu;
+  const double beta_total = std::min(0.49, std::max(1e-300, 0.5 * std::exp(cfg.log_mass_truncation_bound)));
+  const double beta = std::min(0.49, std::max(1e-300, beta_total / static_cast<double>(t)));
+  const double span = 2.0 * std::sqrt(var) * (-norm_ppf(beta));
+  const double alpha = std::max(cfg.discretization, span / static_cast<double>(cfg.max_conv_grid));
+  // remove: E = e^{L0} + sum_{t-1} e^{-L~},  everything rounded up
+  GeomPmf eL, eD;
+  eL.alpha = eD.alpha = alpha;
+  double tail;
+  disc_normal(mu, var, alpha, beta, eL.lower, eL.p, tail);
+  eL.inf_mass = tail;
+  disc_normal(-mu, var, alpha, beta, eD.lower, eD.p, tail);
+  eD.inf_mass = tail;
+  GeomPmf rem = t == 1 ? eL : geom_conv(geom_self_conv(eD, t - 1, true, beta), eL, true, beta);
+  Pld out;
+  out.remove = geom_to_loss_pmf(rem, static_cast<double>(t), 1.0, cfg.discretization, cfg.max_grid_size, rem.inf_mass);
+  // add: S = sum_t e^{-L}, L ~ N(mu, var) rounded UP (so e^{-L} is rounded down), S rounded down; loss = -ln(S/t)
+  GeomPmf eN;
+  eN.alpha = alpha;
+  std::int64_t lo;
+  std::vector<double> probs;
+  disc_normal(mu, var, alpha, beta, lo, probs, tail);
+  // value e^{-alpha j}: index -j; reverse the array
+  eN.lower = -(lo + static_cast<std::int64_t>(probs.size()) - 1);
+  eN.p.assign(probs.rbegin(), probs.rend());
+  eN.zero_mass = tail;                      // L = +infinity  ->  e^{-L} = 0
+  GeomPmf s = geom_self_conv(eN, t, false, beta);
+  out.add = geom_to_loss_pmf(s, static_cast<double>(t), -1.0, cfg.discretization, cfg.max_grid_size, s.zero_mass);
+  return out;
+}
+
+}  // namespace
+
+Pld random_allocation_gaussian_pld(double nm, std::size_t t, std::size_t k, const Config& cfg) {
   check_nm(nm);
-  require(num_bins >= 1 && k >= 1 && k <= num_bins, "random allocation: need 1 <= k <= num_bins");
-  if (k == num_bins) return gaussian_pld(nm, cfg).self_compose(num_bins);
-  const double q = static_cast<double>(k) / static_cast<double>(num_bins);
-  return poisson_gaussian_pld(nm, q, cfg).self_compose(num_bins);
+  require(t >= 1 && k >= 1 && k <= t, "random allocation: need 1 <= k <= t");
+  const std::size_t t_floor = t / k, t_ceil = (t + k - 1) / k;
+  const std::size_t m_c = t_floor == t_ceil ? 0 : t - t_floor * k, m_f = k - m_c;
+  std::optional<Pld> out;
+  const std::pair<std::size_t, std::size_t> parts[2] = {{m_f, t_floor}, {m_c, t_ceil}};
+  for (const auto& [rounds, steps] : parts) {
+    if (rounds == 0 || steps == 0) continue;
+    Pld single = single_allocation_pld(nm, steps, cfg);
+    Pld composed = rounds == 1 ? single : single.self_compose(rounds);
+    out = out ? out->compose(composed, cfg.tail_mass_truncation) : composed;
+  }
+  const double tail = cfg.tail_mass_truncation / 2.0;
+  return out->with_tail_budgets(tail, tail);
 }
 
 // Monte-Carlo PLD of a matrix mechanism under balls-in-bins participation: one record takes part in the

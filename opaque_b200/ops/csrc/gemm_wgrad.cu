@@ -25,6 +25,7 @@
 //
 // All waits are bounded (see common.cuh); on a timeout the CTA drains its TMA copies, frees
 // TMEM and returns with a code in `status`.
+#include <cstdio>
 #include "common.cuh"
 #include "api.h"
 
@@ -394,12 +395,17 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+static thread_local char g_map_detail[192] = {0};
+
 // 2-D bf16 tensor map over a row-major [rows, cols] matrix with row pitch `ld` elements.
 int make_bf16_map_2d(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld,
                      int box_cols, int box_rows) {
   EncodeTiledFn enc = get_encode_fn();
   if (enc == nullptr) return -10;
-  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ((ld * 2) & 15) != 0) return -11;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ((ld * 2) & 15) != 0) {
+    snprintf(g_map_detail, sizeof(g_map_detail), "operand not 16-byte aligned: base=%p ld=%lld", base, ld);
+    return -11;
+  }
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
@@ -407,6 +413,9 @@ int make_bf16_map_2d(CUtensorMap* map, const void* base, long long rows, long lo
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    snprintf(g_map_detail, sizeof(g_map_detail), "tensor map rejected (CUresult %d): base=%p rows=%lld cols=%lld ld=%lld box=%dx%d",
+             static_cast<int>(r), base, rows, cols, ld, box_cols, box_rows);
   return r == CUDA_SUCCESS ? 0 : -12;
 }
 
@@ -467,4 +476,11 @@ extern "C" int ob_wgrad_clip(const void* a, const void* b, int T, int M, int N, 
   if (block_n == 128) return launch_wgrad<128>(ma, mb, p, num_sms, st);
   if (block_n == 64) return launch_wgrad<64>(ma, mb, p, num_sms, st);
   return -1;
+}
+
+extern "C" int ob_last_detail(char* buf, int len) {
+  int i = 0;
+  for (; ob::g_map_detail[i] && i < len - 1; ++i) buf[i] = ob::g_map_detail[i];
+  buf[i] = 0;
+  return 0;
 }

@@ -37,6 +37,7 @@ _SIGNATURES = {
     "ob_ipc_open_handle": [P, P],
     "ob_ipc_close_handle": [P],
     "ob_last_cuda_error": [c_char_p, I],
+    "ob_last_detail": [c_char_p, I],
 }
 
 
@@ -83,7 +84,13 @@ def check(rc: int, what: str) -> None:
             load().ob_last_cuda_error(buf, 256)
         except Exception:
             pass
-        raise KernelLibraryError(f"{what} failed with code {rc} ({buf.value.decode(errors='replace')})")
+        detail = ctypes.create_string_buffer(256)
+        try:
+            load().ob_last_detail(detail, 256)
+        except Exception:
+            pass
+        raise KernelLibraryError(f"{what} failed with code {rc} ({buf.value.decode(errors='replace')}) "
+                                 f"{detail.value.decode(errors='replace')}")
 
 
 def ptr(t: torch.Tensor | None) -> int | None:

@@ -81,6 +81,13 @@ def test_gpt2_full_parameter():
     _check(GPT2LMHeadModel(GPT2Config.tiny(), device=dev), 500, 1.0, 1.0, 5e-3, 2e-2)
 
 
+def test_moe_full_parameter_ragged_ghost_and_grouped_wgrad():
+    from opaque_b200.models import MoEConfig, MoEForCausalLM
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(3)
+    _check(MoEForCausalLM(MoEConfig.tiny(), device=dev), 512, 1.0, 1.0, 1e-2, 3e-2)
+
+
 def test_noise_is_added_exactly_once_and_matches_sigma():
     from opaque_b200.engine.fused import FusedDPEngine
     from opaque_b200.models import LlamaConfig, LlamaForCausalLM

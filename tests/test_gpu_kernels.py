@@ -145,7 +145,7 @@ def test_norm_activation_rope_kernels(dev):
     q.grad = None
     q1.backward(gq)
     back, _ = ops.rope_qk_ref(gq, k.detach(), cos, sin, pos, sign=-1.0)
-    assert torch.equal(q.grad, back)
+    assert rel(q.grad, back) < 1e-3
 
 
 @pytest.mark.parametrize("V,dt", [(1000, torch.bfloat16), (50257, torch.float32), (128256, torch.bfloat16)])

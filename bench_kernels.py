@@ -66,7 +66,7 @@ def main():
 
     want = lambda c: args.case in ("all", c)
     if want("wgrad"):
-        shapes = [(8192, 2048, 1024)] if args.small else [(16384, 3072, 768), (16384, 768, 3072), (32768, 4096, 4096), (16384, 8192, 2048)]
+        shapes = [(16384, 4096, 2048)] if args.small else [(16384, 3072, 768), (16384, 768, 3072), (32768, 4096, 4096), (16384, 8192, 2048)]
         for T, M, N in shapes:
             a = torch.randn(T, M, device=dev).bfloat16()
             b = torch.randn(T, N, device=dev).bfloat16()
@@ -78,6 +78,34 @@ def main():
             if not args.small:
                 emit(f"cublas a^T b (bf16 out) {T}x{M}x{N}", timeit(lambda: torch.matmul(a.t(), b), iters, warm, flush), fl)
                 emit(f"prescale pass + cublas {T}x{M}x{N}", timeit(lambda: torch.matmul((a * sc[:, None].bfloat16()).t(), b), iters, warm, flush), fl)
+    if want("gemm"):
+        # forward / data-gradient products of the model path: y = x W^T (+ LoRA segment), dX = dY W, grouped experts
+        shapes = [(8192, 4096, 4096)] if args.small else [(16384, 4096, 4096), (16384, 14336, 4096), (16384, 4096, 14336), (16384, 768, 3072)]
+        for M, N, K in shapes:
+            x = torch.randn(M, K, device=dev).bfloat16()
+            w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+            xa = torch.randn(M, 16, device=dev).bfloat16()
+            lb = torch.randn(N, 16, device=dev).bfloat16()
+            fl = 2.0 * M * N * K
+            emit(f"gemm x W^T {M}x{N}x{K}", timeit(lambda: ops.gemm(x, w, status=st), iters, warm, flush), fl)
+            emit(f"gemm x W^T + LoRA r16 (one pass) {M}x{N}x{K}", timeit(lambda: ops.gemm(x, w, a2=xa, b2=lb, status=st), iters, warm, flush), fl)
+            if not args.small:
+                emit(f"cublas x W^T {M}x{N}x{K}", timeit(lambda: torch.matmul(x, w.t()), iters, warm, flush), fl)
+                y0 = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+                emit(f"cublas x W^T then addmm LoRA {M}x{N}x{K}", timeit(lambda: torch.addmm(torch.matmul(x, w.t(), out=y0), xa, lb.t(), out=y0), iters, warm, flush), fl)
+                wk = w.t().contiguous()
+                emit(f"gemm dY W ([K,N] operand) {M}x{N}x{K}", timeit(lambda: ops.gemm(x, wk, b_layout="kn", status=st), iters, warm, flush), fl)
+        if not args.small:
+            E, rows, K, N = 60, 32768, 2048, 2816
+            offs = torch.linspace(0, rows, E + 1, device=dev).to(torch.int32)
+            xg = torch.randn(rows, K, device=dev).bfloat16()
+            wg = (torch.randn(E, N, K, device=dev) * 0.02).bfloat16()
+            fl = 2.0 * rows * N * K
+            emit(f"grouped gemm {E} experts {rows}x{N}x{K}", timeit(lambda: ops.gemm(xg, wg, group_offs=offs, status=st), iters, warm, flush), fl)
+            if hasattr(torch, "_grouped_mm"):
+                wgt = wg.transpose(1, 2)
+                o64 = offs[1:].contiguous()
+                emit(f"torch._grouped_mm {E} experts {rows}x{N}x{K}", timeit(lambda: torch._grouped_mm(xg, wgt, offs=o64), iters, warm, flush), fl)
     if want("ghost"):
         shapes = [(8, 512, 768, 768)] if args.small else [(32, 512, 768, 3072), (16, 1024, 2048, 8192), (16, 1024, 4096, 4096)]
         for B, T, Da, Dg in shapes:

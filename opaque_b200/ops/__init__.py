@@ -157,6 +157,83 @@ def ghost_norm(a: torch.Tensor | None, g: torch.Tensor, norm2: torch.Tensor, tok
     lib.check(rc, "ghost_norm")
 
 
+def gemm(a: torch.Tensor, b: torch.Tensor, *, b_layout: str = "nk", a2: torch.Tensor | None = None,
+         b2: torch.Tensor | None = None, bias: torch.Tensor | None = None, group_offs: torch.Tensor | None = None,
+         out: torch.Tensor | None = None, status: StatusWord | None = None,
+         wait_budget_s: float = DEFAULT_WAIT_BUDGET_S) -> torch.Tensor:
+    """``a @ op(b) + a2 @ b2ᵀ + bias`` on the tcgen05 path (bf16 in/out, fp32 accumulation).
+
+    ``b_layout="nk"``: ``b`` is ``[N, K]`` (a weight matrix as stored; ``op(b) = bᵀ``);  ``"kn"``: ``b`` is ``[K, N]``
+    (``op(b) = b`` — data gradients ``dY @ W`` without a transposed copy).  ``a2 [M, r]``, ``b2 [N, r]`` add a
+    low-rank segment accumulated in the same tile (LoRA-fused linear).  With ``group_offs`` (int32 ``[E + 1]`` row
+    offsets, rows sorted by group) ``b`` is ``[E, N, K]`` / ``[E, K, N]`` and rows of group e use slab e (MoE experts).
+    """
+    _need_bf16(a, b)
+    if a.ndim != 2 or a.stride(1) != 1:
+        raise ValueError("a must be a row-major 2-D matrix")
+    M, K = a.shape
+    kn = {"nk": 0, "kn": 1}[b_layout]
+    grouped = group_offs is not None
+    if grouped:
+        if group_offs.dtype != torch.int32 or b.ndim != 3 or not b.is_contiguous():
+            raise TypeError("grouped mode needs int32 offsets and a contiguous [E, ., .] weight stack")
+        E = group_offs.numel() - 1
+        if b.shape[0] != E:
+            raise ValueError("one weight slab per group is required")
+        b2d = b.view(-1, b.shape[-1])
+        N = b.shape[2] if kn else b.shape[1]
+        if (b.shape[1] if kn else b.shape[2]) != K:
+            raise ValueError("inner dimensions differ")
+        if kn and K % 64:
+            raise ValueError("grouped [K, N] slabs need K to be a multiple of 64")
+    else:
+        if b.ndim != 2 or b.stride(1) != 1:
+            raise ValueError("b must be a row-major 2-D matrix")
+        E, b2d = 0, b
+        N = b.shape[1] if kn else b.shape[0]
+        if (b.shape[0] if kn else b.shape[1]) != K:
+            raise ValueError("inner dimensions differ")
+    K2 = 0
+    if a2 is not None:
+        _need_bf16(a2, b2)
+        if kn or a2.shape[0] != M or b2.shape[0] != N or a2.shape[1] != b2.shape[1] or a2.stride(1) != 1 or b2.stride(1) != 1:
+            raise ValueError("low-rank segment: a2 [M, r], b2 [N, r], only with b_layout='nk'")
+        K2 = a2.shape[1]
+    if bias is not None:
+        _need_bf16(bias)
+        if bias.numel() != N or not bias.is_contiguous():
+            raise ValueError("bias must hold N contiguous values")
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    elif out.shape != (M, N) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        raise ValueError("out must be a row-major bf16 [M, N] matrix")
+    rc = lib.load().ob_gemm_tn(a.data_ptr(), b2d.data_ptr(), lib.ptr(a2), lib.ptr(b2), lib.ptr(bias), out.data_ptr(), M, N,
+                               K, K2, a.stride(0), b2d.stride(0), a2.stride(0) if a2 is not None else 0,
+                               b2.stride(0) if b2 is not None else 0, out.stride(0), kn, lib.ptr(group_offs), E,
+                               status.ptr() if status else None, wait_budget_s, lib.sm_count(), lib.stream())
+    lib.check(rc, "gemm")
+    return out
+
+
+def gemm_ref(a, b, *, b_layout="nk", a2=None, b2=None, bias=None, group_offs=None):
+    """fp32 oracle of :func:`gemm`."""
+    af = a.float()
+    if group_offs is None:
+        y = af @ (b.float() if b_layout == "kn" else b.float().t())
+    else:
+        offs = group_offs.tolist()
+        N = b.shape[2] if b_layout == "kn" else b.shape[1]
+        y = af.new_zeros(a.shape[0], N)
+        for e in range(len(offs) - 1):
+            be = b[e].float() if b_layout == "kn" else b[e].float().t()
+            y[offs[e]:offs[e + 1]] = af[offs[e]:offs[e + 1]] @ be
+    if a2 is not None:
+        y = y + a2.float() @ b2.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    return y
+
+
 def ghost_norm_ref(a, g, tokens_per_example, *, ids=None):
     B = g.shape[0] // tokens_per_example
     gg = g.float().view(B, tokens_per_example, -1)
@@ -244,6 +321,7 @@ from .functional import (cross_entropy, cross_entropy_ref, fused_add_rms_norm, g
                          rms_norm_ref, rope_qk, rope_qk_ref, rope_tables, swiglu)
 
 __all__ = [
+    "gemm", "gemm_ref",
     "DeviceWaitTimeout", "KernelLibraryError", "StatusWord", "clip_weighted_sum", "cross_entropy",
     "cross_entropy_ref", "embedding_wgrad", "fused_add_rms_norm", "geglu", "ghost_norm", "ghost_norm_ref", "glu_ref",
     "philox_normal_add_", "pick_block_n", "pick_splits", "rms_norm", "rms_norm_ref", "rope_qk", "rope_qk_ref",

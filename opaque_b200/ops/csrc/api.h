@@ -15,6 +15,14 @@ int ob_ghost_norm(const void* a, const void* g, const int* ids, int B, int T, in
                   long long ldg, float* norm2, const int* seg, const int* seg_out, long long total_rows, int* status,
                   double wait_budget_s, int num_sms, void* stream);
 
+// D[M, N] = A[M, K1] op(B) + A2[M, K2] B2[N, K2]^T + bias, bf16 in / bf16 out, fp32 accumulation.  b_kn = 0: B is
+// [N, K1] row-major (per group: [groups * N, K1]); b_kn = 1: B is [K1, N] row-major (per group: [groups * K1, N]).
+// group_offs (int32 device array [num_groups + 1]) switches on the grouped mode: rows [offs[e], offs[e+1]) use slab e.
+int ob_gemm_tn(const void* a, const void* b, const void* a2, const void* b2, const void* bias, void* out,
+               long long rows_a, int N, int K1, int K2, long long lda, long long ldb, long long lda2, long long ldb2,
+               long long ldo, int b_kn, const int* group_offs, int num_groups, int* status, double wait_budget_s,
+               int num_sms, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

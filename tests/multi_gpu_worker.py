@@ -1,0 +1,109 @@
+"""Worker for the multi-GPU test: W ranks (one per GPU) against a single-process per-example oracle.
+
+Launched by ``tests/test_gpu_multi.py`` through ``python -m torch.distributed.run``.  Every rank holds the same
+model; rank r takes examples ``r::W`` of a common batch.  Checks, on the device and through the peer-memory path only:
+
+  1. the clip-weighted gradient sums that all ranks reduce into the owners' shards equal the oracle's sum over the
+     whole batch (peer ``red.add`` reduce-scatter fused into the producer kernels);
+  2. the noise that each owner adds to its shard is the same Philox stream a single rank would draw (exactly once
+     per coordinate, no overlap or gap at shard boundaries);
+  3. after the step every rank's bf16 parameter copy is bit-identical (owners push their slices to all peers).
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main() -> int:
+    from opaque_b200 import ops
+    from opaque_b200.engine.fused import CLIP_GUARD, FusedDPEngine
+    from opaque_b200.models import LlamaConfig, LlamaForCausalLM, shift_labels
+    from opaque_b200.parallel.sharded import DPStepConfig
+    from opaque_b200.random import fold_in, key
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    mode = sys.argv[1] if len(sys.argv) > 1 else "full"
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256)
+    model = LlamaForCausalLM(cfg, device=dev)
+    if mode == "lora":
+        model.add_lora(16, 32.0)
+        with torch.no_grad():
+            for n, p in model.named_parameters():
+                if "lora_B" in n:
+                    p.normal_(0, 0.05)
+    B, C = 4 * world, 1.0
+    ids = torch.randint(0, 512, (B, 128), device=dev)
+    dist.broadcast(ids, 0)
+    labels = shift_labels(ids, 1.0)
+    eng = FusedDPEngine(model, clipping_norm=C, noise_multiplier=0.0, normalize_by=float(B), key=key(11),
+                        step_config=DPStepConfig(lr=1e-2), microbatch_size=2)
+    sp = eng.space
+    # oracle AFTER binding (parameters are now the broadcast bf16 values), per example, on every rank
+    total = {n: torch.zeros_like(p, dtype=torch.float32) for n, p in model.named_parameters() if p.requires_grad}
+    for i in range(B):
+        model.zero_grad(set_to_none=True)
+        model.per_example_loss(ids[i:i + 1], labels[i:i + 1]).sum().backward()
+        g = {n: p.grad.float() for n, p in model.named_parameters() if p.requires_grad}
+        nrm = torch.sqrt(sum((v ** 2).sum() for v in g.values()))
+        c = min(1.0, C / float(nrm)) * CLIP_GUARD
+        for n in total:
+            total[n] += c * g[n]
+    model.zero_grad(set_to_none=True)
+    flat_ref = torch.zeros(sp.total, device=dev)
+    for n, g in total.items():
+        s = sp.slots[n]
+        flat_ref[s.offset:s.offset + s.numel] = g.reshape(-1)
+
+    mine = {"input_ids": ids[rank::world], "labels": labels[rank::world]}
+    eng.accumulate(model.per_example_loss, mine)
+    eng.group.barrier()
+    torch.cuda.synchronize()
+    eng.group.check("accumulate")
+    got = sp.grad.local
+    ref = flat_ref[sp.shard_lo:sp.shard_lo + sp.shard]
+    err = float((got - ref).norm() / (ref.norm() + 1e-12))
+    ok = err < 3e-2
+    print(f"[rank {rank}] reduce-scatter shard rel err {err:.3e}", flush=True)
+
+    # noise: exactly once per coordinate across shard boundaries
+    noisy = torch.zeros(sp.shard, device=dev)
+    before = sp.grad.local.clone()
+    eng.opt.step(noise_std=2.0, normalize_by=float(B), noisy_out=noisy, skip_update=True)
+    torch.cuda.synchronize()
+    full = torch.zeros(sp.total, device=dev)
+    ops.philox_normal_add_(full, seed=fold_in(key(11), 0).seed, offset=0, std=2.0 / B)
+    want = before / B + full[sp.shard_lo:sp.shard_lo + sp.shard]
+    nerr = float((noisy - want).abs().max())
+    print(f"[rank {rank}] noise max abs err {nerr:.3e}", flush=True)
+    ok = ok and nerr < 1e-5
+
+    # a real step: parameters identical on all ranks afterwards and changed
+    p0 = sp.params.local.clone()
+    eng.noise_multiplier = 0.5
+    res = eng.step(model.per_example_loss, mine)
+    torch.cuda.synchronize()
+    gathered = [torch.empty_like(sp.params.local) for _ in range(world)]
+    dist.all_gather(gathered, sp.params.local.clone())
+    same = all(torch.equal(gathered[0], g) for g in gathered)
+    moved = float((sp.params.local.float() - p0.float()).abs().max()) > 0
+    print(f"[rank {rank}] params identical {same}, moved {moved}, loss {res.loss:.4f}", flush=True)
+    ok = ok and same and moved and eng.status.read() == 0
+    flag = torch.tensor([int(ok)], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    torch.cuda.synchronize()
+    dist.barrier()
+    eng.group.close()
+    dist.destroy_process_group()
+    return 0 if int(flag.item()) == 1 else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

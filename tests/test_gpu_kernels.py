@@ -79,6 +79,68 @@ def test_wgrad_clip_grouped_store_modes(dev):
         ops.wgrad_clip(a, b, torch.zeros(10, device=dev), ldm=64)
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 520, 200), (1024, 768, 3072), (4096, 4096, 1024)])
+def test_gemm_layouts_bias_and_low_rank_segment(dev, M, N, K):
+    from opaque_b200 import ops
+    torch.manual_seed(M + N)
+    st = ops.StatusWord(dev)
+    a = torch.randn(M, K, device=dev).bfloat16()
+    w = (torch.randn(N, K, device=dev) / math.sqrt(K)).bfloat16()
+    bias = torch.randn(N, device=dev).bfloat16()
+    y = ops.gemm(a, w, status=st)
+    assert st.read() == 0 and rel(y, ops.gemm_ref(a, w)) < 4e-3
+    y = ops.gemm(a, w, bias=bias, status=st)
+    assert rel(y, ops.gemm_ref(a, w, bias=bias)) < 4e-3
+    wt = w.t().contiguous()                                   # [K, N]
+    y = ops.gemm(a, wt, b_layout="kn", status=st)
+    assert st.read() == 0 and rel(y, ops.gemm_ref(a, wt, b_layout="kn")) < 4e-3
+    for r in (8, 16, 80):
+        xa = torch.randn(M, r, device=dev).bfloat16()
+        lb = torch.randn(N, r, device=dev).bfloat16()
+        y = ops.gemm(a, w, a2=xa, b2=lb, bias=bias, status=st)
+        assert st.read() == 0 and rel(y, ops.gemm_ref(a, w, a2=xa, b2=lb, bias=bias)) < 4e-3
+
+
+def test_gemm_grouped_by_expert(dev):
+    from opaque_b200 import ops
+    torch.manual_seed(5)
+    st = ops.StatusWord(dev)
+    E, K, N = 6, 128, 320
+    lens = [0, 37, 128, 300, 0, 129]
+    offs = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32, device=dev)
+    M = sum(lens)
+    a = torch.randn(M, K, device=dev).bfloat16()
+    w = (torch.randn(E, N, K, device=dev) / math.sqrt(K)).bfloat16()
+    y = torch.full((M, N), 7.0, device=dev).bfloat16()
+    ops.gemm(a, w, group_offs=offs, out=y, status=st)
+    assert st.read() == 0 and rel(y, ops.gemm_ref(a, w, group_offs=offs)) < 4e-3
+    dy = torch.randn(M, N, device=dev).bfloat16()
+    dx = ops.gemm(dy, w, b_layout="kn", group_offs=offs, status=st)          # w[e] read as [K'=N, N'=K]
+    ref = ops.gemm_ref(dy, w, b_layout="kn", group_offs=offs)       # [M, N] @ [N, K] per group
+    assert st.read() == 0 and dx.shape == (M, K) and rel(dx, ref) < 4e-3
+
+
+def test_tensor_map_kernels_work_from_a_fresh_thread(dev):
+    """Worker threads (autograd) have no driver context bound until the library binds one."""
+    import threading
+    from opaque_b200 import ops
+    a = torch.randn(256, 64, device=dev).bfloat16()
+    g = torch.randn(256, 128, device=dev).bfloat16()
+    got, err = torch.zeros(2, device=dev), []
+
+    def work():
+        try:
+            ops.ghost_norm(a, g, got, 128)
+        except Exception as e:           # noqa: BLE001
+            err.append(e)
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    torch.cuda.synchronize()
+    assert not err, err
+    assert rel(got, ops.ghost_norm_ref(a, g, 128)) < 1e-3
+
+
 @pytest.mark.parametrize("B,T,Da,Dg", [(2, 128, 64, 64), (3, 256, 192, 320), (4, 512, 768, 3072), (2, 200, 800, 72)])
 def test_ghost_norm_matches_gram_and_direct(dev, B, T, Da, Dg):
     from opaque_b200 import ops

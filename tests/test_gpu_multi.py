@@ -1,0 +1,40 @@
+"""Two (or more) ranks over peer memory: fused reduce-scatter, exactly-once noise, parameter all-gather (B200 x N)."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(world: int, mode: str) -> None:
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "multi_gpu_worker.py"), mode]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+
+
+@pytest.mark.parametrize("mode", ["full", "lora"])
+def test_two_ranks_match_single_process_oracle(mode):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _run(2, mode)
+
+
+def test_all_visible_gpus():
+    n = torch.cuda.device_count()
+    if n < 4:
+        pytest.skip("needs four or more GPUs")
+    _run(n, "full")

@@ -10,7 +10,12 @@ One JSON line is printed by rank 0.  ``value`` is timed on the device with CUDA 
 the public engine API with, every step, the host→device copy of that step's batch from pinned memory
 and a device→host read of the step's loss inside the timed region.
 
-  python bench.py [--gpus N --steps K --warmup W] [--config llama8b-lora|gpt2|llama-tiny] [--impl reference]
+``--config llama1b-blt`` runs Llama-3.2-1B full-parameter DP-FTRL with a 4-buffer BLT mechanism (fixed batch of 32
+sequences per GPU, seq 1024, σ calibrated for ε=8 at δ=1e-6 over 2000 steps); ``--config moe`` runs the 24-layer
+60-expert top-4 MoE full-parameter DP-SGD (seq 2048, 32 sequences per GPU; needs the state sharded over 8 GPUs —
+on fewer GPUs pass ``--layers`` to truncate, which the JSON reports).
+
+  python bench.py [--gpus N --steps K --warmup W] [--config llama8b-lora|gpt2|llama1b-blt|moe|llama-tiny] [--impl reference]
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
       bench.py --gpus N --steps K --warmup W
 """
@@ -36,7 +41,7 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="llama8b-lora", choices=["llama8b-lora", "gpt2", "llama-tiny"])
+    ap.add_argument("--config", default="llama8b-lora", choices=["llama8b-lora", "gpt2", "llama1b-blt", "moe", "llama-tiny"])
     ap.add_argument("--microbatch", type=int, default=0)
     ap.add_argument("--per-gpu-batch", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="truncate the model (profiling only; the JSON says so)")
@@ -87,7 +92,8 @@ def main() -> None:
 
     from opaque_b200.dpsgd import PoissonSampler
     from opaque_b200.engine.fused import FusedDPEngine
-    from opaque_b200.models import GPT2Config, GPT2LMHeadModel, LlamaConfig, LlamaForCausalLM, shift_labels
+    from opaque_b200.models import (GPT2Config, GPT2LMHeadModel, LlamaConfig, LlamaForCausalLM, MoEConfig,
+                                    MoEForCausalLM, shift_labels)
     from opaque_b200.ops import lib
     from opaque_b200.parallel.sharded import DPStepConfig
     from opaque_b200.random import fold_in, key
@@ -104,6 +110,7 @@ def main() -> None:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
 
     torch.manual_seed(1234)
+    mechanism, sampling = None, None
     if args.config == "llama8b-lora":
         seq, per_gpu, mb, frac, vocab = 1024, 64, 16, 0.5, 128256
         cfg8 = LlamaConfig.llama3_8b()
@@ -118,6 +125,34 @@ def main() -> None:
         model = GPT2LMHeadModel(GPT2Config.small(), device=dev)
         dp = dict(clipping_norm=1.0, noise_multiplier=0.8, lr=1e-4)
         name, par = "GPT-2-small full-parameter (bf16 + fp32 master)", "dp+zero1"
+    elif args.config == "llama1b-blt":
+        from opaque_b200 import accounting as acc
+        from opaque_b200 import dpftrl
+        from opaque_b200.dpftrl import accounting as ftrl_acc
+        seq, per_gpu, mb, frac, vocab = 1024, 32, 8, 1.0, 128256
+        cfg1 = LlamaConfig.llama32_1b()
+        if args.layers:
+            cfg1.num_hidden_layers = args.layers
+        model = LlamaForCausalLM(cfg1, device=dev)
+        horizon = 2000
+        strategy = dpftrl.blt_strategy(max_buffers=4)
+        mechanism = strategy.fused_mechanism(horizon)
+        cal = acc.calibrate(acc.epsilon_budget(8.0, 1e-6),
+                            lambda nm: ftrl_acc.mf_gaussian(nm, strategy, n_steps=horizon, max_participations=1),
+                            0.05, 50.0, tolerance=1e-3)
+        sampling = "fixed batch (sequential, single participation)"
+        dp = dict(clipping_norm=1.0, noise_multiplier=float(cal.param), lr=1e-4)
+        name, par = "Llama-3.2-1B full-parameter DP-FTRL, BLT 4 buffers (fp32 noise state), sigma for eps=8 delta=1e-6 / 2000 steps" + (
+            f" TRUNCATED to {args.layers} layers" if args.layers else ""), "dp+zero1"
+    elif args.config == "moe":
+        seq, per_gpu, mb, frac, vocab = 2048, 32, 4, 1.0, 151936
+        cfgm = MoEConfig()
+        if args.layers:
+            cfgm.num_hidden_layers = args.layers
+        model = MoEForCausalLM(cfgm, device=dev)
+        dp = dict(clipping_norm=1.0, noise_multiplier=1.0, lr=1e-4)
+        name, par = "MoE 24L d2048 60 experts ffn1408 + 4 shared, top-4, full-parameter" + (
+            f" TRUNCATED to {args.layers} layers" if args.layers else ""), "dp+zero1 (experts replicated)"
     else:
         seq, per_gpu, mb, frac, vocab = 128, 16, 8, 0.5, 256
         model = LlamaForCausalLM(LlamaConfig.tiny(), device=dev)
@@ -130,7 +165,8 @@ def main() -> None:
 
     engine = FusedDPEngine(model, clipping_norm=dp["clipping_norm"], noise_multiplier=dp["noise_multiplier"],
                            normalize_by=float(global_batch), key=key(42),
-                           step_config=DPStepConfig(lr=dp["lr"], noise_bias_correction=True), microbatch_size=mb)
+                           step_config=DPStepConfig(lr=dp["lr"], noise_bias_correction=True), microbatch_size=mb,
+                           mechanism=mechanism)
 
     # synthetic dataset shard of this rank, in pinned host memory; Poisson sampling with E[B] = per_gpu
     shard_size = per_gpu * 100
@@ -138,8 +174,13 @@ def main() -> None:
     data = torch.randint(0, vocab, (shard_size, seq), generator=gen, dtype=torch.int32).pin_memory()
     sampler = PoissonSampler(range(shard_size), per_gpu / shard_size, key=fold_in(key(7), rank))
     batches = iter(sampler)
+    cursor = [0]
 
     def host_batch():
+        if sampling is not None:                      # fixed-size batches in order (DP-FTRL)
+            lo = cursor[0] % (shard_size - per_gpu)
+            cursor[0] += per_gpu
+            return data[lo:lo + per_gpu]
         idx = next(batches)
         return data[torch.as_tensor(idx, dtype=torch.long)].pin_memory() if idx else data[:0]
 
@@ -203,12 +244,12 @@ def main() -> None:
     if rank == 0:
         value = tokens / (dev_ms / 1e3)
         out = {
-            "metric": "DP-SGD tokens/sec (box, max over ranks)", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "metric": ("DP-FTRL" if mechanism else "DP-SGD") + " tokens/sec (box, max over ranks)", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "impl": "ours",
             "config": {"model": name, "global_batch": global_batch, "seq_len": seq, "parallelism": f"{par}{world}",
-                       "sampling": f"Poisson, expected {per_gpu} sequences per GPU", "microbatch": mb,
+                       "sampling": sampling or f"Poisson, expected {per_gpu} sequences per GPU", "microbatch": mb,
                        "loss_fraction": frac, "clip": dp["clipping_norm"], "sigma": dp["noise_multiplier"],
                        "optimizer": "AdamW-BC", "lr": dp["lr"],
                        "l2": "inputs larger than L2 (per-step working set >> 126 MB; no explicit flush)",

@@ -282,15 +282,31 @@ def dp_embedding(ids: torch.Tensor, weight: torch.nn.Parameter) -> torch.Tensor:
     return torch.nn.functional.embedding(ids, weight)
 
 
+FUSE_LORA_GEMM = True      # LoRA linears run as ONE tcgen05 GEMM (base + low-rank segment) instead of GEMM + addmm
+
+
+def _lora_gemm_ok(x2d, weight, lora_a, lora_b, bias) -> bool:
+    r = lora_a.shape[0]
+    return (x2d.is_cuda and x2d.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.is_contiguous()
+            and lora_a.dtype == torch.bfloat16 and lora_b.dtype == torch.bfloat16 and lora_b.is_contiguous()
+            and r % 8 == 0 and weight.shape[0] % 8 == 0 and weight.shape[1] % 8 == 0
+            and (bias is None or bias.dtype == torch.bfloat16))
+
+
 class _LoRALinear(Function):
     """``y = x Wᵀ + s·(x Aᵀ) Bᵀ`` with frozen ``W``; per-example ``dA``, ``dB`` go to the capture."""
 
     @staticmethod
     def forward(ctx, x, weight, bias, lora_a, lora_b, scaling):
         x2d = x.reshape(-1, x.shape[-1])
+        x2d = x2d if x2d.is_contiguous() else x2d.contiguous()
         xa = x2d @ lora_a.t()
-        y = torch.nn.functional.linear(x2d, weight, bias)
-        y.addmm_(xa, lora_b.t(), alpha=scaling)
+        if FUSE_LORA_GEMM and _lora_gemm_ok(x2d, weight, lora_a, lora_b, bias):
+            # one tcgen05 pass: the low-rank product is a second K segment of the same accumulator tile
+            y = ops.gemm(x2d, weight, a2=xa * scaling, b2=lora_b, bias=bias)
+        else:
+            y = torch.nn.functional.linear(x2d, weight, bias)
+            y.addmm_(xa, lora_b.t(), alpha=scaling)
         ctx.save_for_backward(x2d, xa, weight, lora_a, lora_b)
         ctx.scaling = scaling
         ctx.xshape = x.shape
@@ -305,8 +321,11 @@ class _LoRALinear(Function):
         q = (g2d @ lora_b) * s                                     # [R, r]
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = g2d @ weight
-            dx.addmm_(q, lora_a)
+            if FUSE_LORA_GEMM and _lora_gemm_ok(g2d, weight, lora_a, lora_b, None):
+                dx = ops.gemm(g2d, weight, b_layout="kn", a2=q, b2=lora_a.t().contiguous())
+            else:
+                dx = g2d @ weight
+                dx.addmm_(q, lora_a)
             dx = dx.view(ctx.xshape)
         cap = current_capture()
         if cap is None:

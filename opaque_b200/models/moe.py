@@ -3,7 +3,7 @@
 Expert weights are stacked as in Hugging Face (``gate_up_proj [E, 2I, H]``, ``down_proj [E, H, I]``) and replicated
 across data-parallel ranks.  Tokens are sorted by (expert, example), so that
 
-  * forward / input gradients are grouped GEMMs over contiguous expert blocks (``torch._grouped_mm``),
+  * forward / input gradients are ONE launch each of the grouped tcgen05 GEMM over contiguous expert blocks,
   * every (expert, example) pair is a contiguous row segment: the ragged tcgen05 ghost-norm kernel adds
     ``‖A_{e,i}ᵀ G_{e,i}‖²`` to example i's squared norm, and
   * the clip-weighted grouped tcgen05 weight-gradient GEMM (one segment per expert, per-row factor
@@ -60,15 +60,24 @@ class MoEConfig:
                          max_position_embeddings=256)
 
 
-def grouped_mm(a: torch.Tensor, b: torch.Tensor, offs: torch.Tensor) -> torch.Tensor:
-    """``out[rows of group e] = a[rows of group e] @ b[e]`` for ``b [E, K, N]`` and cumulative row offsets ``offs [E]``."""
-    if a.is_cuda and a.dtype == torch.bfloat16 and hasattr(torch, "_grouped_mm") and a.shape[0] > 0:
-        return torch._grouped_mm(a, b, offs=offs)
-    out = a.new_zeros(a.shape[0], b.shape[-1])
+def grouped_linear(a: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, *, transposed: bool = False) -> torch.Tensor:
+    """Rows of group e (``offs[e-1] .. offs[e]``, cumulative ends ``offs [E]``) times expert e's weight.
+
+    ``transposed=False``: ``w [E, N, K]`` and ``out = a @ w[e]ᵀ`` (forward);  ``True``: ``w [E, K, N]`` and
+    ``out = a @ w[e]`` (data gradient against the weight as stored).  On the GPU this is one launch of the grouped
+    tcgen05 GEMM; elsewhere a loop over experts.
+    """
+    K = a.shape[1]
+    if a.is_cuda and a.dtype == torch.bfloat16 and w.is_contiguous() and a.shape[0] > 0 and K % 8 == 0 \
+            and (not transposed or K % 64 == 0) and w.shape[0] <= 256:
+        goffs = torch.zeros(offs.numel() + 1, dtype=torch.int32, device=offs.device)
+        goffs[1:] = offs
+        return ops.gemm(a if a.is_contiguous() else a.contiguous(), w, b_layout="kn" if transposed else "nk", group_offs=goffs)
+    out = a.new_zeros(a.shape[0], w.shape[2] if transposed else w.shape[1])
     lo = 0
     for e, hi in enumerate(offs.tolist()):
         if hi > lo:
-            out[lo:hi] = a[lo:hi] @ b[e]
+            out[lo:hi] = a[lo:hi] @ (w[e] if transposed else w[e].t())
         lo = hi
     return out
 
@@ -99,9 +108,9 @@ class _Experts(Function):
         I = two_i // 2
         token_sorted, slot_sorted, offs, seg = route_sort(topk_idx, E, batch, tokens)
         xs = x.index_select(0, token_sorted)
-        h = grouped_mm(xs, w1.transpose(1, 2), offs)
+        h = grouped_linear(xs, w1, offs)
         act = ops.swiglu(h[:, :I], h[:, I:])
-        y = grouped_mm(act, w2.transpose(1, 2), offs)
+        y = grouped_linear(act, w2, offs)
         wrow = topk_w.reshape(-1).index_select(0, slot_sorted).to(y.dtype)
         out = torch.zeros_like(x).index_add_(0, token_sorted, y * wrow[:, None])
         ctx.save_for_backward(xs, h, act, y, wrow, token_sorted, slot_sorted, offs, seg, w1, w2)
@@ -117,12 +126,12 @@ class _Experts(Function):
         dw_rows = (g.float() * y.float()).sum(-1)
         dtopk = torch.zeros(wshape, dtype=torch.float32, device=dout.device).reshape(-1).index_copy_(0, slot_sorted, dw_rows).view(wshape)
         dy = (g * wrow[:, None]).contiguous()
-        dact = grouped_mm(dy, w2, offs)
+        dact = grouped_linear(dy, w2, offs, transposed=True)
         gate, up = h[:, :I].float(), h[:, I:].float()
         sig = torch.sigmoid(gate)
         silu = gate * sig
         dh = torch.cat([dact.float() * up * sig * (1 + gate * (1 - sig)), dact.float() * silu], dim=1).to(h.dtype)
-        dxs = grouped_mm(dh, w1, offs)
+        dxs = grouped_linear(dh, w1, offs, transposed=True)
         dx = torch.zeros_like(dout).index_add_(0, token_sorted, dxs)
         cap = fused.current_capture()
         if cap is not None:

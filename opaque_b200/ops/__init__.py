@@ -196,8 +196,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, b_layout: str = "nk", a2: torch.Te
     K2 = 0
     if a2 is not None:
         _need_bf16(a2, b2)
-        if kn or a2.shape[0] != M or b2.shape[0] != N or a2.shape[1] != b2.shape[1] or a2.stride(1) != 1 or b2.stride(1) != 1:
-            raise ValueError("low-rank segment: a2 [M, r], b2 [N, r], only with b_layout='nk'")
+        if a2.shape[0] != M or b2.shape[0] != N or a2.shape[1] != b2.shape[1] or a2.stride(1) != 1 or b2.stride(1) != 1:
+            raise ValueError("low-rank segment: a2 [M, r], b2 [N, r]")
         K2 = a2.shape[1]
     if bias is not None:
         _need_bf16(bias)

@@ -291,7 +291,7 @@ extern "C" int ob_gemm_tn(const void* a, const void* b, const void* a2, const vo
   if (rows_a <= 0 || N <= 0 || K1 <= 0) return 0;
   if (rows_a > 0x7fffffffLL - GT_BM) return -40;
   if (group_offs != nullptr && (num_groups < 1 || num_groups > GT_MAX_GROUPS)) return -41;
-  if (K2 > 0 && (b_kn || a2 == nullptr || b2 == nullptr)) return -42;
+  if (K2 > 0 && (a2 == nullptr || b2 == nullptr)) return -42;
   const int groups = group_offs ? num_groups : 1;
   CUtensorMap ma, mb, ma2, mb2;
   int rc = make_bf16_map_2d(&ma, a, rows_a, K1, lda, GT_BK, GT_BM);

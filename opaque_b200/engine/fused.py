@@ -36,7 +36,7 @@ from __future__ import annotations
 import contextlib
 import dataclasses
 import math
-from collections.abc import Callable
+from collections.abc import Callable, Mapping
 from typing import Any
 
 import torch
@@ -169,56 +169,77 @@ class Capture:
 
     # ---- after backward -------------------------------------------------------------------------
     @torch.no_grad()
-    def finalize(self, clipping_norm: float, *, mode: str = "clip", gamma: float = 0.01) -> dict[str, torch.Tensor]:
+    def _ghost_norm2(self, rows_by_slot: dict[str, list[int]]) -> torch.Tensor:
+        """Squared norms contributed by the ghost captures listed in ``rows_by_slot``."""
+        norm2 = torch.zeros(self.batch_size, dtype=torch.float32, device=self.engine.device)
+        single = [rows[0] for rows in rows_by_slot.values() if len(rows) == 1]
+        if single:
+            norm2 += self.parts[single].sum(0)
+        for name, rows in rows_by_slot.items():
+            if len(rows) == 1:
+                continue
+            cross = self._tied_cross_term(name) if len(rows) == 2 else None
+            if cross is not None:     # exact: |a + b|^2 = |a|^2 + |b|^2 + 2<a, b>
+                norm2 += self.parts[rows].sum(0) + 2.0 * cross
+            else:                     # (sum of the pieces' norms)^2 bounds the true squared norm
+                norm2 += self.parts[rows].clamp_min(0).sqrt().sum(0) ** 2
+        return norm2
+
+    def finalize(self, clipping_norm: "float | Mapping[str, float]", *, mode: str = "clip",
+                 gamma: float = 0.01) -> dict[str, torch.Tensor]:
+        """Turn captured norms into clip factors and launch every deferred clip-weighted weight gradient.
+
+        With a mapping ``{group label: C_g}`` each clipping group (labels come from the engine's ``group_of``) is
+        clipped on its own norm to its own threshold; the step's sensitivity is then ``sqrt(Σ C_g²)``.
+        """
         eng, sp = self.engine, self.engine.space
-        norm2 = torch.zeros(self.batch_size, dtype=torch.float32, device=eng.device)
-        if self.direct_elems:
-            ops.rows_sumsq(self.pe[:, :self.direct_elems], norm2)
-        n_parts = len(self.part_slots)
-        if n_parts:
-            by_slot: dict[str, list[int]] = {}
-            for i, name in enumerate(self.part_slots):
-                by_slot.setdefault(name, []).append(i)
-            single = [rows[0] for rows in by_slot.values() if len(rows) == 1]
-            if single:
-                norm2 += self.parts[single].sum(0) if len(single) < n_parts else self.parts[:n_parts].sum(0)
-            for name, rows in by_slot.items():
-                if len(rows) == 1:
-                    continue
-                cross = self._tied_cross_term(name) if len(rows) == 2 else None
-                if cross is not None:     # exact: |a + b|^2 = |a|^2 + |b|^2 + 2<a, b>
-                    norm2 += self.parts[rows].sum(0) + 2.0 * cross
-                else:                     # (sum of the pieces' norms)^2 bounds the true squared norm
-                    norm2 += self.parts[rows].clamp_min(0).sqrt().sum(0) ** 2
-        norms = norm2.clamp_min(0).sqrt()
-        if mode == "auto":
-            c = clipping_norm / (norms + gamma)
-        else:
-            c = (clipping_norm / norms).clamp(max=1.0)
-        c = torch.where(torch.isfinite(c), c, torch.zeros_like(c)) * CLIP_GUARD
+        by_slot: dict[str, list[int]] = {}
+        for i, name in enumerate(self.part_slots):
+            by_slot.setdefault(name, []).append(i)
+        per_group = isinstance(clipping_norm, Mapping)
+        labels = sorted(clipping_norm) if per_group else [""]
+        label_of = (lambda slot_name: sp.group_label[slot_name.split("#")[0]]) if per_group else (lambda slot_name: "")
+        norms: dict[str, torch.Tensor] = {}
+        scales: dict[str, torch.Tensor] = {}
+        for g in labels:
+            norm2 = self._ghost_norm2({n: r for n, r in by_slot.items() if label_of(n) == g})
+            lo, hi = sp.direct_ranges.get(g, (0, 0)) if per_group else (0, self.direct_elems)
+            if hi > lo:
+                ops.rows_sumsq(self.pe[:, lo:hi], norm2)
+            nrm = norm2.clamp_min(0).sqrt()
+            C = float(clipping_norm[g]) if per_group else float(clipping_norm)
+            c = C / (nrm + gamma) if mode == "auto" else (C / nrm).clamp(max=1.0)
+            norms[g] = nrm
+            scales[g] = torch.where(torch.isfinite(c), c, torch.zeros_like(c)) * CLIP_GUARD
         tgt = sp.grad_target()
-        if self.direct_elems:
-            ops.clip_weighted_sum(self.pe[:, :self.direct_elems], c, tgt["out"], flat_offset=0,
-                                  peer_table=tgt["peer_table"], shard_elems=tgt["shard_elems"])
+        for g in labels:
+            lo, hi = sp.direct_ranges.get(g, (0, 0)) if per_group else (0, self.direct_elems)
+            if hi > lo:
+                ops.clip_weighted_sum(self.pe[:, lo:hi], scales[g], tgt["out"], flat_offset=lo,
+                                      peer_table=tgt["peer_table"], shard_elems=tgt["shard_elems"])
         if self.records:
-            row_scale = c.repeat_interleave(self.tokens)
+            row_scale = {g: c.repeat_interleave(self.tokens) for g, c in scales.items()}
             for kind, slot, g2d, other in self.records:
+                g = label_of(slot.name)
                 if kind == "grouped":
                     a_rows, groups, ex_row = other
                     E, d_out, d_in = slot.shape
-                    ops.wgrad_clip(g2d, a_rows, tgt["out"], row_scale=c.index_select(0, ex_row.long()), seg_offsets=groups,
-                                   num_groups=E, splits=1, out_offset=slot.offset, ldm=d_in, ldn=1, accumulate=True,
-                                   group_stride=d_out * d_in, peer_table=tgt["peer_table"],
+                    ops.wgrad_clip(g2d, a_rows, tgt["out"], row_scale=scales[g].index_select(0, ex_row.long()),
+                                   seg_offsets=groups, num_groups=E, splits=1, out_offset=slot.offset, ldm=d_in, ldn=1,
+                                   accumulate=True, group_stride=d_out * d_in, peer_table=tgt["peer_table"],
                                    shard_elems=tgt["shard_elems"], status=self.status)
                 elif kind == "linear":
-                    ops.wgrad_clip(g2d, other, tgt["out"], row_scale=row_scale, out_offset=slot.offset,
+                    ops.wgrad_clip(g2d, other, tgt["out"], row_scale=row_scale[g], out_offset=slot.offset,
                                    ldm=slot.shape[1], ldn=1, accumulate=True, peer_table=tgt["peer_table"],
                                    shard_elems=tgt["shard_elems"], status=self.status)
                 else:
-                    ops.embedding_wgrad(g2d, other, tgt["out"], row_scale=row_scale, flat_offset=slot.offset,
+                    ops.embedding_wgrad(g2d, other, tgt["out"], row_scale=row_scale[g], flat_offset=slot.offset,
                                         peer_table=tgt["peer_table"], shard_elems=tgt["shard_elems"])
         self.records = []
-        return {"norms": norms, "scales": c}
+        if per_group:
+            total = torch.sqrt(sum(n ** 2 for n in norms.values()))
+            return {"norms": total, "scales": scales, "group_norms": norms}
+        return {"norms": norms[""], "scales": scales[""]}
 
 
 # ===================================================================================== layer functions
@@ -357,6 +378,7 @@ class StepResult:
     batch_size: int
     losses: torch.Tensor | None = None
     norms: torch.Tensor | None = None
+    group_norms: dict[str, torch.Tensor] | None = None
 
 
 class FusedDPEngine:
@@ -366,19 +388,33 @@ class FusedDPEngine:
                  normalize_by: float, key: RngKey, step_config: DPStepConfig | None = None,
                  microbatch_size: int = 8, group: PeerGroup | None = None, mechanism: dict | None = None,
                  clipping_mode: str = "clip", gamma: float = 0.01,
-                 direct: Callable[[str, torch.nn.Parameter], bool] | None = None):
+                 direct: Callable[[str, torch.nn.Parameter], bool] | None = None,
+                 group_of: Callable[[str], str] | None = None, adaptive: Any = None):
+        """``clipping_norm`` is a float, or ``{label: C_g}`` together with ``group_of(param_name) -> label`` for
+        per-group clipping.  ``adaptive`` is an :class:`opaque_b200.dpsgd.clipping.AdaptiveClipState` (quantile
+        tracking; its ``clipping_norm`` overrides the argument and is updated after every step from the cluster-wide
+        count of clipped examples plus the state's own Gaussian draw)."""
         self.model = model
         self.device = next(model.parameters()).device
         self.group = group or PeerGroup(self.device)
         named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
         if not named:
             raise ValueError("the model has no trainable parameters")
-        self.space = FlatSpace(named, self.group, direct=direct)
+        if isinstance(clipping_norm, Mapping):
+            if group_of is None:
+                raise ValueError("per-group clipping needs group_of(param_name) -> label")
+            missing = {group_of(n) for n, _ in named} - set(clipping_norm)
+            if missing:
+                raise ValueError(f"no clipping norm for group(s) {sorted(missing)}")
+        self.space = FlatSpace(named, self.group, direct=direct, group_of=group_of if isinstance(clipping_norm, Mapping) else None)
         self.space.bind()
         self._slot_by_id = {id(p): self.space.slots[n] for n, p in named}
         self.opt = ShardedDPOptimizer(self.space, step_config or DPStepConfig(), key=key, mechanism=mechanism)
         self.clipping_norm, self.noise_multiplier, self.normalize_by = clipping_norm, noise_multiplier, normalize_by
         self.clipping_mode, self.gamma = clipping_mode, gamma
+        self.adaptive = adaptive
+        if adaptive is not None:
+            self.clipping_norm = adaptive.clipping_norm.values if hasattr(adaptive.clipping_norm, "values") else adaptive.clipping_norm
         self.microbatch_size = microbatch_size
         self.status = self.group.status
         self._pe: torch.Tensor | None = None
@@ -396,6 +432,11 @@ class FusedDPEngine:
             self._pe[:batch_size].zero_()
         return self._pe[:batch_size]
 
+    def sensitivity(self) -> float:
+        """L2 sensitivity of the clipped sum: ``C``, or ``sqrt(Σ C_g²)`` with per-group thresholds."""
+        c = self.clipping_norm
+        return math.sqrt(sum(float(v) ** 2 for v in c.values())) if isinstance(c, Mapping) else float(c)
+
     def accumulate(self, loss_fn: Callable[..., torch.Tensor], batch: dict[str, torch.Tensor]) -> StepResult:
         """Forward/backward all microbatches of ``batch`` and reduce clipped sums into the sharded gradient.
 
@@ -403,7 +444,7 @@ class FusedDPEngine:
         """
         first = next(iter(batch.values()))
         n = first.shape[0]
-        losses, norms, clipped = [], [], 0
+        losses, norms, group_norms = [], [], []
         for lo in range(0, n, self.microbatch_size):
             sub = {k: v[lo:lo + self.microbatch_size] for k, v in batch.items()}
             mb = next(iter(sub.values())).shape[0]
@@ -415,20 +456,55 @@ class FusedDPEngine:
             out = cap.finalize(self.clipping_norm, mode=self.clipping_mode, gamma=self.gamma)
             losses.append(per_example.detach().float())
             norms.append(out["norms"])
+            if "group_norms" in out:
+                group_norms.append(out["group_norms"])
         if n:
             l_all, n_all = torch.cat(losses), torch.cat(norms)
-            return StepResult(float("nan"), float("nan"), float("nan"), n, l_all, n_all)
+            res = StepResult(float("nan"), float("nan"), float("nan"), n, l_all, n_all)
+            if group_norms:
+                res.group_norms = {g: torch.cat([d[g] for d in group_norms]) for g in group_norms[0]}
+            return res
         return StepResult(0.0, 0.0, 0.0, 0, None, None)
+
+    def _adapt(self, res: StepResult) -> None:
+        """Quantile-tracking threshold update from the cluster-wide number of clipped examples (one small reduction)."""
+        from ..dpsgd.clipping import _updated
+        from ..types import PerGroup
+        st, used = self.adaptive, self.clipping_norm
+        labels = sorted(used) if isinstance(used, Mapping) else [""]
+        counts = torch.zeros(len(labels) + 1, dtype=torch.float64, device=self.device)
+        if res.batch_size:
+            counts[-1] = res.batch_size
+            for i, g in enumerate(labels):
+                nrm = res.group_norms[g] if isinstance(used, Mapping) else res.norms
+                counts[i] = (nrm > float(used[g] if isinstance(used, Mapping) else used)).sum()
+        if self.group.world > 1:
+            torch.distributed.all_reduce(counts, group=self.group.pg)
+        vals = counts.tolist()
+        batch = int(vals[-1])
+        if isinstance(used, Mapping):
+            cur = PerGroup({n: self.space.group_label[n] for n in self.space.slots}, dict(used))
+            nxt = _updated(st, cur, dict(zip(labels, vals[:-1])), batch, st.step)
+            self.clipping_norm = dict(nxt.values)
+            num: Any = dict(zip(labels, vals[:-1]))
+        else:
+            nxt = _updated(st, float(used), vals[0], batch, st.step)
+            self.clipping_norm, cur, num = float(nxt), float(used), vals[0]
+        self.adaptive = dataclasses.replace(st, clipping_norm=nxt, step=st.step + 1, _num_clipped=num, _batch_size=batch,
+                                            _prev_clipping_norm=cur)
 
     def step(self, loss_fn: Callable[..., torch.Tensor], batch: dict[str, torch.Tensor], *,
              read_metrics: bool = True) -> StepResult:
         """One DP optimizer step: accumulate, then noise + AdamW-BC on the shards."""
         res = self.accumulate(loss_fn, batch)
-        sigma = 0.0 if self.noise_multiplier == 0 else self.noise_multiplier * self.clipping_norm
+        sens = self.sensitivity()
+        sigma = 0.0 if self.noise_multiplier == 0 else self.noise_multiplier * sens
         self.opt.step(noise_std=sigma, normalize_by=self.normalize_by)
         if read_metrics and res.batch_size:
             stats = torch.stack([res.losses.mean(), res.norms.mean(),
-                                 (res.norms > self.clipping_norm).float().mean()]).tolist()   # one D2H read
+                                 (res.norms > sens).float().mean()]).tolist()   # one D2H read
             res.loss, res.grad_norm_mean, res.clip_rate = stats
             self.group.check("fused DP step")
+        if self.adaptive is not None:
+            self._adapt(res)
         return res

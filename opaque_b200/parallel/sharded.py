@@ -59,19 +59,28 @@ class FlatSpace:
     """Offsets of every trainable parameter in the flat space, and the peer buffers behind it."""
 
     def __init__(self, named_params: Sequence[tuple[str, torch.nn.Parameter]], group: PeerGroup, *,
-                 direct: Callable[[str, torch.nn.Parameter], bool] | None = None):
+                 direct: Callable[[str, torch.nn.Parameter], bool] | None = None,
+                 group_of: Callable[[str], str] | None = None):
         self.group = group
         is_direct = direct or default_direct
-        ordered = sorted(named_params, key=lambda np_: (not is_direct(*np_),))   # stable: direct first
+        label = group_of or (lambda name: "")
+        # stable: direct parameters first, and inside them every clipping group contiguous
+        ordered = sorted(named_params, key=lambda np_: (not is_direct(*np_), label(np_[0]) if is_direct(*np_) else ""))
         self.slots: dict[str, Slot] = {}
+        self.group_label: dict[str, str] = {}
+        self.direct_ranges: dict[str, tuple[int, int]] = {}
+        self.direct_elems = 0
         off = 0
         for name, p in ordered:
-            self.slots[name] = Slot(name, off, p.numel(), tuple(p.shape), bool(is_direct(name, p)))
-            off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
-            if self.slots[name].direct:
-                self.direct_elems = off
-        if not hasattr(self, "direct_elems"):
-            self.direct_elems = 0
+            d = bool(is_direct(name, p))
+            self.slots[name] = Slot(name, off, p.numel(), tuple(p.shape), d)
+            self.group_label[name] = label(name)
+            end = off + (p.numel() + ALIGN - 1) // ALIGN * ALIGN
+            if d:
+                lo, _ = self.direct_ranges.get(label(name), (off, off))
+                self.direct_ranges[label(name)] = (lo, end)
+                self.direct_elems = end
+            off = end
         chunk = group.world * ALIGN
         self.total = max((off + chunk - 1) // chunk * chunk, chunk)
         self.shard = self.total // group.world

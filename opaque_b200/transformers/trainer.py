@@ -309,14 +309,12 @@ class DPTrainer:
     # ---- set-up -----------------------------------------------------------------------------------
     def _resolve_engine(self) -> str:
         want = self.args.dp_engine
-        fused_ok = self.device.type == "cuda" and hasattr(self.model, "per_example_loss") and self.args.clipping_mode != "adaptive" \
-            and not isinstance(self.args.clipping_norm, Mapping) and self.compute_loss_func is None
+        fused_ok = self.device.type == "cuda" and hasattr(self.model, "per_example_loss") and self.compute_loss_func is None
         if fused_ok:
             from ..device import fused_kernels_available
             fused_ok = fused_kernels_available()
         if want == "fused" and not fused_ok:
-            raise RuntimeError("dp_engine='fused' needs a B200, the kernel library, a model with per_example_loss, "
-                               "a scalar clipping_norm and fixed/auto clipping")
+            raise RuntimeError("dp_engine='fused' needs a B200, the kernel library and a model with per_example_loss")
         return "fused" if (want in ("auto", "fused") and fused_ok) else "reference"
 
     def _build_sampler(self, n_local: int, steps: int, data_key: RngKey):
@@ -484,11 +482,33 @@ class DPTrainer:
                            weight_decay=a.weight_decay, decoupled_weight_decay=a.optim != "adam",
                            noise_bias_correction=a.optim == "adamw-bc")
         mech = self._strategy.fused_mechanism(steps) if self._strategy is not None else None
-        self._fused = FusedDPEngine(self.model, clipping_norm=float(a.clipping_norm), noise_multiplier=self.noise_multiplier,
+        bound: Any = float(a.clipping_norm) if not isinstance(a.clipping_norm, Mapping) else None
+        group_of = None
+        if bound is None:                      # {"substring": C, ..., "fallback": C}: first matching pattern wins
+            pats = [k for k in a.clipping_norm if k != "fallback"]
+
+            def group_of(name: str) -> str:
+                hit = next((p for p in pats if p in name), None)
+                if hit is None and "fallback" not in a.clipping_norm:
+                    raise ValueError(f"parameter {name!r} matches no group pattern and no fallback was given")
+                return hit or "fallback"
+            used = {group_of(n) for n, p in self.model.named_parameters() if p.requires_grad}
+            bound = {g: float(a.clipping_norm[g]) for g in used}
+        adaptive = None
+        if a.clipping_mode == "adaptive":
+            from ..dpsgd.clipping import AdaptiveClipState
+            kw = dict(a.clipping_kwargs)
+            adaptive = AdaptiveClipState(bound if not isinstance(bound, Mapping) else per_group(
+                {n: p for n, p in self.model.named_parameters() if p.requires_grad},
+                {k: v for k, v in a.clipping_norm.items() if k != "fallback"}, fallback=a.clipping_norm.get("fallback")),
+                0, float(kw.get("target_quantile", 0.5)), float(kw.get("learning_rate", 0.2)),
+                float(kw.get("clipping_norm_min", 0.01)), float(kw.get("clipping_norm_max", 100.0)),
+                float(kw.get("fraction_noise_std", 0.05)), fold_in(key(a.seed), "adaclip"))
+        self._fused = FusedDPEngine(self.model, clipping_norm=bound, noise_multiplier=self.noise_multiplier,
                                     normalize_by=self.expected_batch, key=noise_key, step_config=cfg,
                                     microbatch_size=self._microbatch, mechanism=mech,
                                     clipping_mode="auto" if a.clipping_mode == "auto" else "clip",
-                                    gamma=float(a.clipping_kwargs.get("gamma", 0.01)))
+                                    gamma=float(a.clipping_kwargs.get("gamma", 0.01)), group_of=group_of, adaptive=adaptive)
 
     # ---- data -----------------------------------------------------------------------------------
     def get_train_dataloader(self):
@@ -587,8 +607,8 @@ class DPTrainer:
             self.state.num_input_tokens_seen += int(reduce_scalar(int((batch["labels"] != -100).sum()), "sum"))
         return {"loss": res.loss if res.batch_size else 0.0, "grad_norm": res.grad_norm_mean if res.batch_size else 0.0,
                 "clip_rate": res.clip_rate if res.batch_size else 0.0, "batch_size": float(n),
-                "noise_std": self.noise_multiplier * float(self.args.clipping_norm) / self.expected_batch,
-                "clipping_norm": float(self.args.clipping_norm)}
+                "noise_std": self.noise_multiplier * self._fused.sensitivity() / self.expected_batch,
+                "clipping_norm": self._fused.sensitivity()}
 
     # ---- loop -------------------------------------------------------------------------------------
     def train(self, resume_from_checkpoint: str | bool | None = None, ignore_keys_for_eval=None):

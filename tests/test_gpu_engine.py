@@ -88,6 +88,61 @@ def test_moe_full_parameter_ragged_ghost_and_grouped_wgrad():
     _check(MoEForCausalLM(MoEConfig.tiny(), device=dev), 512, 1.0, 1.0, 1e-2, 3e-2)
 
 
+def test_per_group_and_adaptive_clipping_in_the_fused_engine():
+    from opaque_b200.dpsgd.clipping import AdaptiveClipState, next_clipping_norm
+    from opaque_b200.engine.fused import CLIP_GUARD, FusedDPEngine
+    from opaque_b200.models import LlamaConfig, LlamaForCausalLM, shift_labels
+    from opaque_b200.random import fold_in, generator_from_key, key
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(4)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256)
+    m = LlamaForCausalLM(cfg, device=dev)
+    ids = torch.randint(0, 512, (5, 128), device=dev)
+    labels = shift_labels(ids, 1.0)
+    bounds = {"mlp": 0.3, "norm": 0.05, "fallback": 0.7}
+    group_of = lambda n: next((p for p in ("mlp", "norm") if p in n), "fallback")
+    eng = FusedDPEngine(m, clipping_norm=bounds, group_of=group_of, noise_multiplier=0.0, normalize_by=1.0, key=key(0),
+                        microbatch_size=3)
+    assert abs(eng.sensitivity() - math.sqrt(0.3 ** 2 + 0.05 ** 2 + 0.7 ** 2)) < 1e-12
+    total = {n: torch.zeros_like(p, dtype=torch.float32) for n, p in m.named_parameters()}
+    gn = {g: [] for g in bounds}
+    for i in range(5):
+        m.zero_grad(set_to_none=True)
+        m.per_example_loss(ids[i:i + 1], labels[i:i + 1]).sum().backward()
+        grads = {n: p.grad.float() for n, p in m.named_parameters()}
+        for g, C in bounds.items():
+            nrm = torch.sqrt(sum((v ** 2).sum() for n, v in grads.items() if group_of(n) == g))
+            gn[g].append(nrm)
+            c = min(1.0, C / float(nrm)) * CLIP_GUARD
+            for n, v in grads.items():
+                if group_of(n) == g:
+                    total[n] += c * v
+    m.zero_grad(set_to_none=True)
+    res = eng.accumulate(m.per_example_loss, {"input_ids": ids, "labels": labels})
+    torch.cuda.synchronize()
+    assert eng.status.read() == 0
+    for g in bounds:
+        want = torch.stack(gn[g])
+        assert float(((res.group_norms[g] - want).abs() / want).max()) < 5e-3, g
+    flat = eng.space.grad.local
+    for n, gref in total.items():
+        s_ = eng.space.slots[n]
+        got = flat[s_.offset:s_.offset + s_.numel].view(s_.shape)
+        assert float((got - gref).norm() / (gref.norm() + 1e-12)) < 2e-2, n
+
+    # adaptive: the threshold follows the geometric quantile update with the state's own noise draw
+    m2 = LlamaForCausalLM(cfg, device=dev)
+    st = AdaptiveClipState(0.5, 0, 0.5, 0.2, 0.01, 100.0, 0.05, key(9))
+    eng2 = FusedDPEngine(m2, clipping_norm=123.0, noise_multiplier=0.5, normalize_by=5.0, key=key(1), microbatch_size=5,
+                         adaptive=st)
+    assert eng2.clipping_norm == 0.5
+    out = eng2.step(m2.per_example_loss, {"input_ids": ids, "labels": labels})
+    rate = float((out.norms > 0.5).float().mean())
+    z = float(torch.randn(1, generator=generator_from_key(fold_in(key(9), 0))))
+    assert abs(eng2.clipping_norm - next_clipping_norm(0.5, rate, z, st)) < 1e-9 and eng2.adaptive.step == 1
+
+
 def test_noise_is_added_exactly_once_and_matches_sigma():
     from opaque_b200.engine.fused import FusedDPEngine
     from opaque_b200.models import LlamaConfig, LlamaForCausalLM

@@ -288,6 +288,48 @@ class DPTrainer:
             self.device = torch.device("cpu")
         self.model.to(self.device)
 
+    # ---- small parts of the Hugging Face Trainer surface that user scripts rely on -----------------------------
+    def is_world_process_zero(self) -> bool:
+        return self.args.process_index == 0
+
+    def is_local_process_zero(self) -> bool:
+        return self.args.local_process_index == 0
+
+    def add_callback(self, callback: "TrainerCallback | type") -> None:
+        self.callbacks.append(callback() if isinstance(callback, type) else callback)
+
+    def pop_callback(self, callback: "TrainerCallback | type") -> "TrainerCallback | None":
+        for i, cb in enumerate(self.callbacks):
+            if cb is callback or (isinstance(callback, type) and isinstance(cb, callback)):
+                return self.callbacks.pop(i)
+        return None
+
+    def remove_callback(self, callback: "TrainerCallback | type") -> None:
+        self.pop_callback(callback)
+
+    def num_examples(self, dataset: Any = None) -> int:
+        return len(dataset if dataset is not None else self.train_dataset)
+
+    def create_model_card(self, model_name: str | None = None, **fields: Any) -> str:
+        """Write ``README.md`` into ``output_dir`` with the privacy statement of the run (ε, δ, mechanism, sampling)."""
+        a = self.args
+        eps = self.epsilon() if self.accountant is not None else float("nan")
+        lines = [f"# {model_name or os.path.basename(a.output_dir.rstrip('/')) or 'model'}", "",
+                 "Trained with differential privacy.", "",
+                 f"- privacy guarantee: ({eps:.4g}, {getattr(self, 'target_delta', a.privacy_target_delta)})-DP",
+                 f"- mechanism: {a.privacy_noise_mechanism}; sampling: {a.sampling_mode}; clipping: {a.clipping_mode} at {a.clipping_norm}",
+                 f"- noise multiplier: {getattr(self, 'noise_multiplier', a.privacy_noise_multiplier)}; steps: {self.state.global_step}"]
+        lines += [f"- {k}: {v}" for k, v in fields.items()]
+        text = "\n".join(lines) + "\n"
+        if a.output_dir and self.is_world_process_zero():
+            os.makedirs(a.output_dir, exist_ok=True)
+            with open(os.path.join(a.output_dir, "README.md"), "w") as f:
+                f.write(text)
+        return text
+
+    def push_to_hub(self, *_: Any, **__: Any) -> None:
+        raise RuntimeError("no network access: save_model() writes the same files locally for a later upload")
+
     def _call(self, hook: str, **kw: Any) -> None:
         for cb in self.callbacks:
             getattr(cb, hook)(self.args, self.state, self.control, model=self.model, **kw)

@@ -45,6 +45,7 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--microbatch", type=int, default=0)
     ap.add_argument("--per-gpu-batch", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="truncate the model (profiling only; the JSON says so)")
+    ap.add_argument("--cuda-graph", type=int, default=-1, help="1/0: replay microbatches as CUDA graphs (default: per config)")
     return ap.parse_args()
 
 
@@ -161,12 +162,14 @@ def main() -> None:
         name, par = "Llama-tiny (LoRA)", "dp"
     per_gpu = args.per_gpu_batch or per_gpu
     mb = args.microbatch or mb
+    # launch-bound configurations (small models, trainable head) replay each microbatch as one CUDA graph
+    use_graph = bool(args.cuda_graph) if args.cuda_graph >= 0 else args.config in ("gpt2",)
     global_batch = per_gpu * world
 
     engine = FusedDPEngine(model, clipping_norm=dp["clipping_norm"], noise_multiplier=dp["noise_multiplier"],
                            normalize_by=float(global_batch), key=key(42),
                            step_config=DPStepConfig(lr=dp["lr"], noise_bias_correction=True), microbatch_size=mb,
-                           mechanism=mechanism)
+                           mechanism=mechanism, cuda_graph=use_graph)
 
     # synthetic dataset shard of this rank, in pinned host memory; Poisson sampling with E[B] = per_gpu
     shard_size = per_gpu * 100
@@ -249,7 +252,7 @@ def main() -> None:
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "impl": "ours",
             "config": {"model": name, "global_batch": global_batch, "seq_len": seq, "parallelism": f"{par}{world}",
-                       "sampling": sampling or f"Poisson, expected {per_gpu} sequences per GPU", "microbatch": mb,
+                       "sampling": sampling or f"Poisson, expected {per_gpu} sequences per GPU", "microbatch": mb, "cuda_graph_microbatches": use_graph,
                        "loss_fraction": frac, "clip": dp["clipping_norm"], "sigma": dp["noise_multiplier"],
                        "optimizer": "AdamW-BC", "lr": dp["lr"],
                        "l2": "inputs larger than L2 (per-step working set >> 126 MB; no explicit flush)",

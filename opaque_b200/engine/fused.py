@@ -268,7 +268,10 @@ class _DPLinear(Function):
             return dx, dw, db
         cap.add_linear(weight, x2d, g2d)
         if ctx.bias is not None:
-            cap.pe_view(ctx.bias).add_(g2d.view(cap.batch_size, cap.tokens, -1).sum(1, dtype=torch.float32))
+            if g2d.dtype == torch.bfloat16 and g2d.shape[1] % 2 == 0:
+                ops.rows_group_sum_(cap.pe_view(ctx.bias), g2d, cap.batch_size)
+            else:
+                cap.pe_view(ctx.bias).add_(g2d.view(cap.batch_size, cap.tokens, -1).sum(1, dtype=torch.float32))
         return dx, None, None
 
 
@@ -389,7 +392,7 @@ class FusedDPEngine:
                  microbatch_size: int = 8, group: PeerGroup | None = None, mechanism: dict | None = None,
                  clipping_mode: str = "clip", gamma: float = 0.01,
                  direct: Callable[[str, torch.nn.Parameter], bool] | None = None,
-                 group_of: Callable[[str], str] | None = None, adaptive: Any = None):
+                 group_of: Callable[[str], str] | None = None, adaptive: Any = None, cuda_graph: bool = False):
         """``clipping_norm`` is a float, or ``{label: C_g}`` together with ``group_of(param_name) -> label`` for
         per-group clipping.  ``adaptive`` is an :class:`opaque_b200.dpsgd.clipping.AdaptiveClipState` (quantile
         tracking; its ``clipping_norm`` overrides the argument and is updated after every step from the cluster-wide
@@ -412,6 +415,8 @@ class FusedDPEngine:
         self.opt = ShardedDPOptimizer(self.space, step_config or DPStepConfig(), key=key, mechanism=mechanism)
         self.clipping_norm, self.noise_multiplier, self.normalize_by = clipping_norm, noise_multiplier, normalize_by
         self.clipping_mode, self.gamma = clipping_mode, gamma
+        self.cuda_graph = bool(cuda_graph)
+        self._graphs: dict[Any, dict[str, Any]] = {}
         self.adaptive = adaptive
         if adaptive is not None:
             self.clipping_norm = adaptive.clipping_norm.values if hasattr(adaptive.clipping_norm, "values") else adaptive.clipping_norm
@@ -448,13 +453,11 @@ class FusedDPEngine:
         for lo in range(0, n, self.microbatch_size):
             sub = {k: v[lo:lo + self.microbatch_size] for k, v in batch.items()}
             mb = next(iter(sub.values())).shape[0]
-            tokens = sub["input_ids"].shape[1] if "input_ids" in sub else 1
-            cap = Capture(self, mb, tokens)
-            with activate(cap):
-                per_example = loss_fn(**sub)
-                per_example.sum().backward()
-            out = cap.finalize(self.clipping_norm, mode=self.clipping_mode, gamma=self.gamma)
-            losses.append(per_example.detach().float())
+            if self.cuda_graph and self.adaptive is None and "labels" in sub:
+                per_example, out = self._graphed_microbatch(loss_fn, sub, mb)
+            else:
+                per_example, out = self._microbatch(loss_fn, sub, mb)
+            losses.append(per_example)
             norms.append(out["norms"])
             if "group_norms" in out:
                 group_norms.append(out["group_norms"])
@@ -465,6 +468,55 @@ class FusedDPEngine:
                 res.group_norms = {g: torch.cat([d[g] for d in group_norms]) for g in group_norms[0]}
             return res
         return StepResult(0.0, 0.0, 0.0, 0, None, None)
+
+    def _microbatch(self, loss_fn, sub: dict[str, torch.Tensor], mb: int):
+        tokens = sub["input_ids"].shape[1] if "input_ids" in sub else 1
+        cap = Capture(self, mb, tokens)
+        with activate(cap):
+            per_example = loss_fn(**sub)
+            per_example.sum().backward()
+        out = cap.finalize(self.clipping_norm, mode=self.clipping_mode, gamma=self.gamma)
+        return per_example.detach().float(), out
+
+    def _graphed_microbatch(self, loss_fn, sub: dict[str, torch.Tensor], mb: int):
+        """Replay the microbatch (forward, backward, norms, clip-weighted gradients) as ONE CUDA graph.
+
+        Shapes are made static by padding the microbatch to ``microbatch_size`` rows whose labels are all ignored
+        (zero loss, zero gradient, zero clip-weighted contribution).  The first microbatch of a shape runs eagerly
+        (it also performs every kernel's one-time set-up), the second is captured and replayed, later ones only
+        replay.  Launch-bound models (hundreds of small kernels per layer) stop being limited by the host.
+        """
+        full = self.microbatch_size
+        sig = tuple((k, tuple(v.shape[1:]), v.dtype) for k, v in sorted(sub.items()))
+        entry = self._graphs.get(sig)
+        if entry is None:
+            static = {k: torch.zeros((full,) + tuple(v.shape[1:]), dtype=v.dtype, device=v.device) for k, v in sub.items()}
+            entry = self._graphs[sig] = {"static": static, "graph": None, "out": None}
+        static = entry["static"]
+        for k, v in sub.items():
+            static[k][:mb].copy_(v)
+            if mb < full:
+                static[k][mb:].fill_(-100 if k == "labels" else 0)
+        if entry["graph"] is None and not entry.get("warm"):
+            entry["warm"] = True
+            per_example, out = self._microbatch(loss_fn, static, full)
+        else:
+            if entry["graph"] is None:
+                torch.cuda.synchronize(self.device)
+                graph = torch.cuda.CUDAGraph()
+                before = ops.lib.LAUNCHES
+                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                    entry["out"] = self._microbatch(loss_fn, static, full)
+                entry["graph"], entry["launches"] = graph, ops.lib.LAUNCHES - before
+                ops.lib.LAUNCHES = before                 # captured, not yet executed
+            entry["graph"].replay()
+            ops.lib.LAUNCHES += entry["launches"]         # kernels of this library that the replay launched
+            per_example, out = entry["out"]
+            per_example = per_example.clone()
+            out = {k: ({g: t.clone() for g, t in v.items()} if isinstance(v, dict) else v.clone()) for k, v in out.items()}
+        per_example = per_example[:mb]
+        out = {k: ({g: t[:mb] for g, t in v.items()} if isinstance(v, dict) else v[:mb]) for k, v in out.items()}
+        return per_example, out
 
     def _adapt(self, res: StepResult) -> None:
         """Quantile-tracking threshold update from the cluster-wide number of clipped examples (one small reduction)."""

@@ -14,6 +14,7 @@ import dataclasses
 import torch
 from torch import nn
 
+from .. import ops
 from .layers import Embedding, LayerNorm, Linear, linear_cross_entropy, per_example_token_weights
 
 
@@ -39,6 +40,26 @@ class GPT2Config:
         return GPT2Config(vocab_size=500, n_positions=256, n_embd=128, n_layer=2, n_head=4)
 
 
+class _SplitHeads(torch.autograd.Function):
+    """``[B, T, 3·d]`` → three ``[B, heads, T, d/heads]`` views; the backward writes the three gradients into ONE
+    buffer (three strided copies) instead of three zero-filled full-size tensors that are then added."""
+
+    @staticmethod
+    def forward(ctx, qkv, heads):
+        B, T, d3 = qkv.shape
+        v5 = qkv.view(B, T, 3, heads, d3 // (3 * heads))
+        ctx.shape = (B, T, 3, heads, d3 // (3 * heads))
+        return tuple(v5[:, :, i].transpose(1, 2) for i in range(3))
+
+    @staticmethod
+    def backward(ctx, gq, gk, gv):
+        B, T, _, heads, hd = ctx.shape
+        out = torch.empty(ctx.shape, dtype=gq.dtype, device=gq.device)
+        for i, g in enumerate((gq, gk, gv)):
+            out[:, :, i].copy_(g.transpose(1, 2))
+        return out.view(B, T, 3 * heads * hd), None
+
+
 class GPT2Block(nn.Module):
     def __init__(self, cfg: GPT2Config, dtype, device):
         super().__init__()
@@ -53,11 +74,15 @@ class GPT2Block(nn.Module):
 
     def forward(self, h):
         B, T, d = h.shape
-        qkv = self.attn_c_attn(self.ln_1(h)).view(B, T, 3, self.nh, d // self.nh)
-        q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+        qkv = self.attn_c_attn(self.ln_1(h))
+        if qkv.is_cuda:
+            q, k, v = _SplitHeads.apply(qkv, self.nh)
+        else:                                    # plain views (also what runs under vmap in the reference engine)
+            v5 = qkv.view(B, T, 3, self.nh, d // self.nh)
+            q, k, v = (v5[:, :, i].transpose(1, 2) for i in range(3))
         o = nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
         h = h + self.attn_c_proj(o.transpose(1, 2).reshape(B, T, d))
-        return h + self.mlp_c_proj(nn.functional.gelu(self.mlp_c_fc(self.ln_2(h)), approximate="tanh"))
+        return h + self.mlp_c_proj(ops.activation(self.mlp_c_fc(self.ln_2(h)), "gelu_tanh"))
 
 
 class GPT2LMHeadModel(nn.Module):

@@ -23,6 +23,17 @@ int ob_gemm_tn(const void* a, const void* b, const void* a2, const void* b2, con
                long long ldo, int b_kn, const int* group_offs, int num_groups, int* status, double wait_budget_s,
                int num_sms, void* stream);
 
+// LayerNorm over the last dimension (bf16 in/out, fp32 statistics saved per row).
+int ob_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, long long rows,
+                     int H, float eps, void* stream);
+int ob_layernorm_bwd_dx(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
+                        long long rows, int H, void* stream);
+// out[e, :N] += sum over the rows of example e of g (mode 0) or g * (x - mean) * rstd (mode 1); out row pitch ld_out.
+int ob_rows_group_sum(const void* g, const void* x, const float* mean, const float* rstd, int num_examples,
+                      int rows_per_example, int N, long long ldg, float* out, long long ld_out, int mode, void* stream);
+// out = act(x) (dy == NULL) or dy * act'(x); act: 0 silu, 1 gelu erf, 2 gelu tanh, 3 relu.
+int ob_activation(const void* x, const void* dy, void* out, long long numel, int act, int sms, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

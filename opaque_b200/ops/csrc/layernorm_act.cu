@@ -1,0 +1,251 @@
+// LayerNorm forward / backward with per-example weight and bias gradients, per-example bias-gradient row sums and
+// plain (ungated) activations for sm_100a.  These are the bandwidth-bound pieces of a GPT-2-style block under
+// per-example clipping: the weight / bias gradients of LayerNorm and the bias gradients of linear layers are small
+// enough to materialise per example ([B, H] each), so they are reduced over an example's T token rows by a kernel and
+// added straight into that example's row of the per-example gradient buffer.
+// bf16 storage, fp32 math, 16-byte vector accesses, one CTA per row for the normalisation passes.
+#include "common.cuh"
+#include "api.h"
+
+namespace ob {
+
+struct alignas(16) ln_bf16x8 {
+  __nv_bfloat162 v[4];
+};
+__device__ __forceinline__ void ln_unpack8(const ln_bf16x8& p, float* f) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(p.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ ln_bf16x8 ln_pack8(const float* f) {
+  ln_bf16x8 p;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return p;
+}
+
+constexpr int LN_THREADS = 128;
+
+// two simultaneous block-wide sums
+__device__ __forceinline__ float2 ln_block_sum2(float a, float b, float2* red) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = make_float2(a, b);
+  __syncthreads();
+  float2 t = make_float2(0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < LN_THREADS / 32; ++i) {
+    t.x += red[i].x;
+    t.y += red[i].y;
+  }
+  return t;
+}
+
+__global__ void __launch_bounds__(LN_THREADS)
+layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                     const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y, float* __restrict__ mean,
+                     float* __restrict__ rstd, int H, float eps) {
+  __shared__ float2 red[LN_THREADS / 32];
+  const long long row = blockIdx.x;
+  const ln_bf16x8* xr = reinterpret_cast<const ln_bf16x8*>(x + row * H);
+  const int nv = H >> 3;
+  float s = 0.f, ss = 0.f;
+  for (int i = threadIdx.x; i < nv; i += LN_THREADS) {
+    float f[8];
+    ln_unpack8(xr[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      s += f[j];
+      ss += f[j] * f[j];
+    }
+  }
+  const float2 t = ln_block_sum2(s, ss, red);
+  const float mu = t.x / H;
+  const float var = fmaxf(t.y / H - mu * mu, 0.f);
+  const float rs = rsqrtf(var + eps);
+  if (threadIdx.x == 0) {
+    mean[row] = mu;
+    rstd[row] = rs;
+  }
+  const ln_bf16x8* wr = reinterpret_cast<const ln_bf16x8*>(w);
+  const ln_bf16x8* br = reinterpret_cast<const ln_bf16x8*>(b);
+  ln_bf16x8* yr = reinterpret_cast<ln_bf16x8*>(y + row * H);
+  for (int i = threadIdx.x; i < nv; i += LN_THREADS) {
+    float f[8], g[8], h[8];
+    ln_unpack8(xr[i], f);
+    ln_unpack8(wr[i], g);
+    if (b != nullptr) ln_unpack8(br[i], h);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = (f[j] - mu) * rs * g[j] + (b != nullptr ? h[j] : 0.f);
+    yr[i] = ln_pack8(f);
+  }
+}
+
+__global__ void __launch_bounds__(LN_THREADS)
+layernorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                        const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean,
+                        const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx, int H) {
+  __shared__ float2 red[LN_THREADS / 32];
+  const long long row = blockIdx.x;
+  const ln_bf16x8* dyr = reinterpret_cast<const ln_bf16x8*>(dy + row * H);
+  const ln_bf16x8* xr = reinterpret_cast<const ln_bf16x8*>(x + row * H);
+  const ln_bf16x8* wr = reinterpret_cast<const ln_bf16x8*>(w);
+  ln_bf16x8* dxr = reinterpret_cast<ln_bf16x8*>(dx + row * H);
+  const int nv = H >> 3;
+  const float mu = mean[row], rs = rstd[row];
+  float s1 = 0.f, s2 = 0.f;
+  for (int i = threadIdx.x; i < nv; i += LN_THREADS) {
+    float a[8], f[8], g[8];
+    ln_unpack8(dyr[i], a);
+    ln_unpack8(xr[i], f);
+    ln_unpack8(wr[i], g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gw = a[j] * g[j];
+      s1 += gw;
+      s2 += gw * (f[j] - mu) * rs;
+    }
+  }
+  const float2 t = ln_block_sum2(s1, s2, red);
+  const float m1 = t.x / H, m2 = t.y / H;
+  for (int i = threadIdx.x; i < nv; i += LN_THREADS) {
+    float a[8], f[8], g[8];
+    ln_unpack8(dyr[i], a);
+    ln_unpack8(xr[i], f);
+    ln_unpack8(wr[i], g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = rs * (a[j] * g[j] - m1 - (f[j] - mu) * rs * m2);
+    dxr[i] = ln_pack8(a);
+  }
+}
+
+// Per-example reductions over the token rows of each example: out[e, col] += sum_r f(r, col).
+//   mode 0: f = g                      (bias gradients: LayerNorm bias, linear bias)
+//   mode 1: f = g * (x - mean) * rstd  (LayerNorm weight gradient)
+// grid = (examples, column blocks of 256, row splits); each thread owns two adjacent columns; split partial sums are
+// combined with atomics (the destination is that example's row of the fp32 per-example gradient buffer).
+__global__ void __launch_bounds__(128)
+rows_group_sum_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ x,
+                      const float* __restrict__ mean, const float* __restrict__ rstd, int rows_per_example, int N,
+                      long long ldg, float* __restrict__ out, long long ld_out, int mode) {
+  const int e = blockIdx.x;
+  const int col = (blockIdx.y * 128 + threadIdx.x) * 2;
+  if (col >= N) return;
+  const int chunk = (rows_per_example + gridDim.z - 1) / gridDim.z;
+  const int r0 = e * rows_per_example + blockIdx.z * chunk;
+  const int r1 = min(r0 + chunk, (e + 1) * rows_per_example);
+  float a0 = 0.f, a1 = 0.f;
+  for (int r = r0; r < r1; ++r) {
+    const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g + static_cast<long long>(r) * ldg + col));
+    if (mode == 1) {
+      const float mu = __ldg(mean + r), rs = __ldg(rstd + r);
+      const float2 xv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + static_cast<long long>(r) * ldg + col));
+      a0 += gv.x * (xv.x - mu) * rs;
+      a1 += gv.y * (xv.y - mu) * rs;
+    } else {
+      a0 += gv.x;
+      a1 += gv.y;
+    }
+  }
+  float* o = out + static_cast<long long>(e) * ld_out + col;
+  atomicAdd(o, a0);
+  if (col + 1 < N) atomicAdd(o + 1, a1);
+}
+
+// Plain activations.  act: 0 silu, 1 gelu (erf), 2 gelu (tanh approximation), 3 relu.
+__device__ __forceinline__ float pa_fwd(float e, int act) {
+  if (act == 0) return e / (1.f + __expf(-e));
+  if (act == 1) return 0.5f * e * (1.f + erff(e * 0.70710678118654752f));
+  if (act == 3) return fmaxf(e, 0.f);
+  const float u = 0.7978845608028654f * (e + 0.044715f * e * e * e);
+  return 0.5f * e * (1.f + tanhf(u));
+}
+__device__ __forceinline__ float pa_bwd(float e, int act) {
+  if (act == 0) {
+    const float s = 1.f / (1.f + __expf(-e));
+    return s * (1.f + e * (1.f - s));
+  }
+  if (act == 1) {
+    const float cdf = 0.5f * (1.f + erff(e * 0.70710678118654752f));
+    return cdf + e * 0.3989422804014327f * __expf(-0.5f * e * e);
+  }
+  if (act == 3) return e > 0.f ? 1.f : 0.f;
+  const float u = 0.7978845608028654f * (e + 0.044715f * e * e * e);
+  const float t = tanhf(u);
+  return 0.5f * (1.f + t) + 0.5f * e * (1.f - t * t) * 0.7978845608028654f * (1.f + 0.134145f * e * e);
+}
+
+// dy == nullptr: out = act(x);  otherwise out = dy * act'(x)
+__global__ void __launch_bounds__(256)
+activation_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                  __nv_bfloat16* __restrict__ out, long long nvec, int act) {
+  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < nvec; i += gridDim.x * 256LL) {
+    float e[8], d[8];
+    ln_unpack8(reinterpret_cast<const ln_bf16x8*>(x)[i], e);
+    if (dy != nullptr) {
+      ln_unpack8(reinterpret_cast<const ln_bf16x8*>(dy)[i], d);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = d[j] * pa_bwd(e[j], act);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = pa_fwd(e[j], act);
+    }
+    reinterpret_cast<ln_bf16x8*>(out)[i] = ln_pack8(e);
+  }
+}
+
+}  // namespace ob
+
+using namespace ob;
+
+extern "C" int ob_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                                long long rows, int H, float eps, void* stream) {
+  if (rows <= 0) return 0;
+  if (H % 8) return -2;
+  layernorm_fwd_kernel<<<static_cast<unsigned>(rows), LN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(b),
+      static_cast<__nv_bfloat16*>(y), mean, rstd, H, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int ob_layernorm_bwd_dx(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                                   void* dx, long long rows, int H, void* stream) {
+  if (rows <= 0) return 0;
+  if (H % 8) return -2;
+  layernorm_bwd_dx_kernel<<<static_cast<unsigned>(rows), LN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+      mean, rstd, static_cast<__nv_bfloat16*>(dx), H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int ob_rows_group_sum(const void* g, const void* x, const float* mean, const float* rstd, int num_examples,
+                                 int rows_per_example, int N, long long ldg, float* out, long long ld_out, int mode,
+                                 void* stream) {
+  if (num_examples <= 0 || rows_per_example <= 0 || N <= 0) return 0;
+  if ((N & 1) || (ldg & 1)) return -2;
+  if (mode == 1 && (x == nullptr || mean == nullptr || rstd == nullptr)) return -3;
+  int splits = rows_per_example / 64;
+  splits = splits < 1 ? 1 : (splits > 16 ? 16 : splits);
+  dim3 grid(num_examples, (N / 2 + 127) / 128, splits);
+  rows_group_sum_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(g), static_cast<const __nv_bfloat16*>(x), mean, rstd, rows_per_example, N, ldg,
+      out, ld_out, mode);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int ob_activation(const void* x, const void* dy, void* out, long long numel, int act, int sms, void* stream) {
+  if (numel <= 0) return 0;
+  if (numel % 8) return -2;
+  const long long nvec = numel / 8;
+  long long grid = (nvec + 255) / 256;
+  const long long cap = static_cast<long long>(sms) * 16;
+  if (grid > cap) grid = cap;
+  activation_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy), static_cast<__nv_bfloat16*>(out), nvec, act);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}

@@ -114,6 +114,109 @@ def fused_add_rms_norm(x, residual, weight, eps=1e-6, offset=0.0, casting_mode="
     return rms_norm_ref(x, weight, eps, offset, casting_mode, residual=residual)
 
 
+# =============================================================================== LayerNorm
+
+def rows_group_sum_(out: torch.Tensor, g2d: torch.Tensor, num_examples: int, *, x2d: torch.Tensor | None = None,
+                    mean: torch.Tensor | None = None, rstd: torch.Tensor | None = None) -> None:
+    """``out[e] += Σ_{rows of example e} g`` (or ``g·(x−mean)·rstd`` when statistics are given); ``out`` fp32 ``[B, N]``
+    (any row pitch), ``g2d`` bf16 ``[B·T, N]``."""
+    rows, N = g2d.shape
+    if out.dtype != torch.float32 or out.shape != (num_examples, N) or out.stride(1) != 1 or rows % num_examples:
+        raise ValueError("rows_group_sum_: out must be fp32 [examples, N] and rows a multiple of examples")
+    rc = lib.load().ob_rows_group_sum(g2d.data_ptr(), lib.ptr(x2d), lib.ptr(mean), lib.ptr(rstd), num_examples,
+                                      rows // num_examples, N, g2d.stride(0), out.data_ptr(), out.stride(0),
+                                      0 if x2d is None else 1, lib.stream())
+    lib.check(rc, "rows_group_sum")
+
+
+class _LayerNorm(Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps, layer):
+        shape = x.shape
+        H = shape[-1]
+        x2 = x.reshape(-1, H)
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        stats = torch.empty(2, rows, dtype=torch.float32, device=x.device)
+        rc = lib.load().ob_layernorm_fwd(x2.data_ptr(), weight.data_ptr(), lib.ptr(bias), y.data_ptr(), stats[0].data_ptr(),
+                                         stats[1].data_ptr(), rows, H, eps, lib.stream())
+        lib.check(rc, "layernorm_fwd")
+        ctx.save_for_backward(x2, weight, stats)
+        ctx.meta = (shape, layer, bias is not None)
+        return y.view(shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, stats = ctx.saved_tensors
+        shape, layer, has_bias = ctx.meta
+        H = shape[-1]
+        dy2 = dy.reshape(-1, H)
+        dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
+        rows = x2.shape[0]
+        dx = torch.empty_like(x2)
+        rc = lib.load().ob_layernorm_bwd_dx(dy2.data_ptr(), x2.data_ptr(), weight.data_ptr(), stats[0].data_ptr(),
+                                            stats[1].data_ptr(), dx.data_ptr(), rows, H, lib.stream())
+        lib.check(rc, "layernorm_bwd_dx")
+        cap = _param_grad_hook() if weight.requires_grad else None
+        dw = db = None
+        if cap is not None:                      # per-example gradients straight into the capture's buffer rows
+            rows_group_sum_(cap.pe_view(layer.weight), dy2, cap.batch_size, x2d=x2, mean=stats[0], rstd=stats[1])
+            if has_bias:
+                rows_group_sum_(cap.pe_view(layer.bias), dy2, cap.batch_size)
+        elif weight.requires_grad:
+            acc = torch.zeros(2, 1, H, dtype=torch.float32, device=x2.device)
+            rows_group_sum_(acc[0], dy2, 1, x2d=x2, mean=stats[0], rstd=stats[1])
+            rows_group_sum_(acc[1], dy2, 1)
+            dw, db = acc[0, 0].to(weight.dtype), (acc[1, 0].to(weight.dtype) if has_bias else None)
+        return dx.view(shape), dw, db, None, None
+
+
+def layer_norm(x, weight, bias=None, eps=1e-5, *, layer=None):
+    """LayerNorm over the last dimension; under a capture the weight / bias gradients are produced per example."""
+    if _use_kernel(x, weight) and x.shape[-1] % 8 == 0 and (bias is None or bias.dtype == torch.bfloat16):
+        return _LayerNorm.apply(x, weight, bias, eps, layer)
+    return torch.nn.functional.layer_norm(x, (x.shape[-1],), weight, bias, eps)
+
+
+# =============================================================================== plain activations
+
+_ACTS = {"silu": 0, "gelu": 1, "gelu_tanh": 2, "relu": 3}
+
+
+class _Activation(Function):
+    @staticmethod
+    def forward(ctx, x, act):
+        xc = x if x.is_contiguous() else x.contiguous()
+        out = torch.empty_like(xc)
+        rc = lib.load().ob_activation(xc.data_ptr(), None, out.data_ptr(), xc.numel(), act, lib.sm_count(), lib.stream())
+        lib.check(rc, "activation")
+        ctx.save_for_backward(xc)
+        ctx.act = act
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        (xc,) = ctx.saved_tensors
+        dyc = dy if dy.is_contiguous() else dy.contiguous()
+        dx = torch.empty_like(xc)
+        rc = lib.load().ob_activation(xc.data_ptr(), dyc.data_ptr(), dx.data_ptr(), xc.numel(), ctx.act, lib.sm_count(),
+                                      lib.stream())
+        lib.check(rc, "activation_bwd")
+        return dx, None
+
+
+def activation(x, kind: str = "gelu_tanh"):
+    """``silu`` / ``gelu`` / ``gelu_tanh`` / ``relu`` with a one-pass backward (the input is the only saved tensor)."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.numel() % 8 == 0 and lib.available():
+        return _Activation.apply(x, _ACTS[kind])
+    if kind == "silu":
+        return torch.nn.functional.silu(x)
+    if kind == "relu":
+        return torch.relu(x)
+    return torch.nn.functional.gelu(x, approximate="tanh" if kind == "gelu_tanh" else "none")
+
+
 # =============================================================================== gated activations
 
 ACTIVATION_SWIGLU, ACTIVATION_GEGLU_EXACT, ACTIVATION_GEGLU_APPROX = 0, 1, 2

@@ -20,6 +20,10 @@ _SIGNATURES = {
     "ob_wgrad_clip": [P, P, I, I, I, LL, LL, P, P, I, I, P, P, LL, P, LL, LL, LL, LL, I, I, I, P, D, I, P],
     "ob_ghost_norm": [P, P, P, I, I, I, I, LL, LL, P, P, P, LL, P, D, I, P],
     "ob_gemm_tn": [P, P, P, P, P, P, LL, I, I, I, LL, LL, LL, LL, LL, I, P, I, P, D, I, P],
+    "ob_layernorm_fwd": [P, P, P, P, P, P, LL, I, F, P],
+    "ob_layernorm_bwd_dx": [P, P, P, P, P, P, LL, I, P],
+    "ob_rows_group_sum": [P, P, P, P, I, I, I, LL, P, LL, I, P],
+    "ob_activation": [P, P, P, LL, I, I, P],
     "ob_rmsnorm_fwd": [P, P, P, P, P, P, LL, I, F, F, I, P],
     "ob_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, LL, I, F, P],
     "ob_glu_fwd": [P, P, P, LL, I, LL, I, I, P],

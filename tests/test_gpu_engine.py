@@ -143,6 +143,30 @@ def test_per_group_and_adaptive_clipping_in_the_fused_engine():
     assert abs(eng2.clipping_norm - next_clipping_norm(0.5, rate, z, st)) < 1e-9 and eng2.adaptive.step == 1
 
 
+def test_cuda_graph_microbatches_match_eager_execution():
+    from opaque_b200.engine.fused import FusedDPEngine
+    from opaque_b200.models import GPT2Config, GPT2LMHeadModel, shift_labels
+    from opaque_b200.random import key
+    dev = torch.device("cuda", 0)
+    ids = torch.randint(0, 500, (11, 128), device=dev)          # 3 microbatches of 4: eager, captured, replayed (partial)
+    labels = shift_labels(ids, 1.0)
+    flats, norms = [], []
+    for graph in (False, True):
+        torch.manual_seed(6)
+        m = GPT2LMHeadModel(GPT2Config.tiny(), device=dev)
+        eng = FusedDPEngine(m, clipping_norm=1.0, noise_multiplier=0.0, normalize_by=1.0, key=key(0), microbatch_size=4,
+                            cuda_graph=graph)
+        for _ in range(2):                                       # second pass replays only
+            eng.space.grad.local.zero_()
+            res = eng.accumulate(m.per_example_loss, {"input_ids": ids, "labels": labels})
+        torch.cuda.synchronize()
+        assert eng.status.read() == 0
+        flats.append(eng.space.grad.local.clone())
+        norms.append(res.norms.clone())
+    assert float((norms[0] - norms[1]).abs().max() / norms[0].max()) < 1e-4
+    assert float((flats[0] - flats[1]).norm() / flats[0].norm()) < 1e-3     # atomics reorder sums, nothing else differs
+
+
 def test_noise_is_added_exactly_once_and_matches_sigma():
     from opaque_b200.engine.fused import FusedDPEngine
     from opaque_b200.models import LlamaConfig, LlamaForCausalLM

@@ -210,6 +210,39 @@ def test_norm_activation_rope_kernels(dev):
     assert rel(q.grad, back) < 1e-3
 
 
+def test_layernorm_group_sum_and_activation_kernels(dev):
+    from opaque_b200 import ops
+    torch.manual_seed(3)
+    B, T, H = 4, 96, 768
+    x = (torch.randn(B * T, H, device=dev) * 2 + 0.5).bfloat16()
+    w = (torch.randn(H, device=dev) * 0.2 + 1).bfloat16()
+    b = (torch.randn(H, device=dev) * 0.1).bfloat16()
+    xg, wg, bg = (t.clone().requires_grad_(True) for t in (x, w, b))
+    y = ops.layer_norm(xg, wg, bg, 1e-5)
+    xr, wr, br = (t.float().requires_grad_(True) for t in (x, w, b))
+    yr = torch.nn.functional.layer_norm(xr, (H,), wr, br, 1e-5)
+    assert rel(y, yr) < 4e-3
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    yr.backward(dy.float())
+    assert rel(xg.grad, xr.grad) < 6e-3 and rel(wg.grad, wr.grad) < 6e-3 and rel(bg.grad, br.grad) < 6e-3
+    # per-example reductions into a strided fp32 destination, accumulating
+    g = torch.randn(B * T, 3072, device=dev).bfloat16()
+    out = torch.ones(B, 4000, device=dev)
+    ops.rows_group_sum_(out[:, 100:3172], g, B)
+    assert rel(out[:, 100:3172], 1 + g.float().view(B, T, -1).sum(1)) < 1e-5 and float(out[:, :100].min()) == 1.0
+    for kind in ("silu", "gelu", "gelu_tanh", "relu"):
+        a = torch.randn(512, 3072, device=dev).bfloat16().requires_grad_(True)
+        o = ops.activation(a, kind)
+        da = torch.randn_like(o)
+        o.backward(da)
+        af = a.detach().float().requires_grad_(True)
+        of = {"silu": torch.nn.functional.silu, "relu": torch.relu, "gelu": torch.nn.functional.gelu,
+              "gelu_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh")}[kind](af)
+        of.backward(da.float())
+        assert rel(o, of) < 4e-3 and rel(a.grad, af.grad) < 4e-3, kind
+
+
 @pytest.mark.parametrize("V,dt", [(1000, torch.bfloat16), (50257, torch.float32), (128256, torch.bfloat16)])
 def test_cross_entropy_kernel(dev, V, dt):
     from opaque_b200 import ops

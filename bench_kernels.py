@@ -75,6 +75,8 @@ def main():
             fl = 2.0 * T * M * N
             emit(f"wgrad_clip scaled {T}x{M}x{N}", timeit(lambda: ops.wgrad_clip(a, b, out, ldm=N, row_scale=sc, status=st), iters, warm, flush), fl)
             emit(f"wgrad_clip unscaled {T}x{M}x{N}", timeit(lambda: ops.wgrad_clip(a, b, out, ldm=N, status=st), iters, warm, flush), fl)
+            exs = torch.rand(T // 1024, device=dev)
+            emit(f"wgrad_clip per-example factor in epilogue {T}x{M}x{N}", timeit(lambda: ops.wgrad_clip_per_example(a, b, out, ex_scale=exs, rows_per_example=1024, ldm=N, status=st), iters, warm, flush), fl)
             if not args.small:
                 emit(f"cublas a^T b (bf16 out) {T}x{M}x{N}", timeit(lambda: torch.matmul(a.t(), b), iters, warm, flush), fl)
                 emit(f"prescale pass + cublas {T}x{M}x{N}", timeit(lambda: torch.matmul((a * sc[:, None].bfloat16()).t(), b), iters, warm, flush), fl)

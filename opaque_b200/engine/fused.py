@@ -170,19 +170,24 @@ class Capture:
     # ---- after backward -------------------------------------------------------------------------
     @torch.no_grad()
     def _ghost_norm2(self, rows_by_slot: dict[str, list[int]]) -> torch.Tensor:
-        """Squared norms contributed by the ghost captures listed in ``rows_by_slot``."""
+        """Squared norms contributed by the ghost captures listed in ``rows_by_slot`` (all captures: one slice sum)."""
         norm2 = torch.zeros(self.batch_size, dtype=torch.float32, device=self.engine.device)
-        single = [rows[0] for rows in rows_by_slot.values() if len(rows) == 1]
-        if single:
-            norm2 += self.parts[single].sum(0)
+        rows_all = sorted(r for rows in rows_by_slot.values() for r in rows)
+        if not rows_all:
+            return norm2
+        if rows_all == list(range(rows_all[0], rows_all[-1] + 1)):
+            norm2 += self.parts[rows_all[0]:rows_all[-1] + 1].sum(0)
+        else:
+            norm2 += self.parts.index_select(0, self.engine.index_tensor(rows_all)).sum(0)
         for name, rows in rows_by_slot.items():
             if len(rows) == 1:
                 continue
             cross = self._tied_cross_term(name) if len(rows) == 2 else None
-            if cross is not None:     # exact: |a + b|^2 = |a|^2 + |b|^2 + 2<a, b>
-                norm2 += self.parts[rows].sum(0) + 2.0 * cross
+            if cross is not None:     # exact: |a + b|^2 = |a|^2 + |b|^2 + 2<a, b>   (the squares are in the sum above)
+                norm2 += 2.0 * cross
             else:                     # (sum of the pieces' norms)^2 bounds the true squared norm
-                norm2 += self.parts[rows].clamp_min(0).sqrt().sum(0) ** 2
+                pieces = torch.stack([self.parts[r] for r in rows])
+                norm2 += pieces.clamp_min(0).sqrt().sum(0) ** 2 - pieces.sum(0)
         return norm2
 
     def finalize(self, clipping_norm: "float | Mapping[str, float]", *, mode: str = "clip",
@@ -229,9 +234,16 @@ class Capture:
                                    accumulate=True, group_stride=d_out * d_in, peer_table=tgt["peer_table"],
                                    shard_elems=tgt["shard_elems"], status=self.status)
                 elif kind == "linear":
-                    ops.wgrad_clip(g2d, other, tgt["out"], row_scale=row_scale[g], out_offset=slot.offset,
-                                   ldm=slot.shape[1], ldn=1, accumulate=True, peer_table=tgt["peer_table"],
-                                   shard_elems=tgt["shard_elems"], status=self.status)
+                    if self.tokens % 64 == 0 and self.tokens >= 128 and g2d.shape[0] == self.batch_size * self.tokens:
+                        # uniform examples: factor applied per example in the epilogue, operands untouched
+                        ops.wgrad_clip_per_example(g2d, other, tgt["out"], ex_scale=scales[g], rows_per_example=self.tokens,
+                                                   out_offset=slot.offset, ldm=slot.shape[1], accumulate=True,
+                                                   peer_table=tgt["peer_table"], shard_elems=tgt["shard_elems"],
+                                                   status=self.status)
+                    else:
+                        ops.wgrad_clip(g2d, other, tgt["out"], row_scale=row_scale[g], out_offset=slot.offset,
+                                       ldm=slot.shape[1], ldn=1, accumulate=True, peer_table=tgt["peer_table"],
+                                       shard_elems=tgt["shard_elems"], status=self.status)
                 else:
                     ops.embedding_wgrad(g2d, other, tgt["out"], row_scale=row_scale[g], flat_offset=slot.offset,
                                         peer_table=tgt["peer_table"], shard_elems=tgt["shard_elems"])
@@ -417,6 +429,7 @@ class FusedDPEngine:
         self.clipping_mode, self.gamma = clipping_mode, gamma
         self.cuda_graph = bool(cuda_graph)
         self._graphs: dict[Any, dict[str, Any]] = {}
+        self._index_cache: dict[tuple, torch.Tensor] = {}
         self.adaptive = adaptive
         if adaptive is not None:
             self.clipping_norm = adaptive.clipping_norm.values if hasattr(adaptive.clipping_norm, "values") else adaptive.clipping_norm
@@ -424,6 +437,14 @@ class FusedDPEngine:
         self.status = self.group.status
         self._pe: torch.Tensor | None = None
         self.kernel_launches = 0
+
+    def index_tensor(self, rows: list[int]) -> torch.Tensor:
+        """Device copy of a small index list, cached (graph capture forbids fresh host-to-device copies)."""
+        k = tuple(rows)
+        t = self._index_cache.get(k)
+        if t is None:
+            t = self._index_cache[k] = torch.tensor(rows, dtype=torch.long, device=self.device)
+        return t
 
     def slot_of(self, param: torch.nn.Parameter):
         return self._slot_by_id[id(param)]

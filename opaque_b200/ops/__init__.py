@@ -106,6 +106,47 @@ def wgrad_clip(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, ro
     lib.check(rc, "wgrad_clip")
 
 
+def wgrad_clip_per_example(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, ex_scale: torch.Tensor | None,
+                           rows_per_example: int, out_offset: int = 0, ldm: int | None = None, accumulate: bool = True,
+                           splits: int | None = None, peer_table: torch.Tensor | None = None, shard_elems: int = 0,
+                           status: StatusWord | None = None, wait_budget_s: float = DEFAULT_WAIT_BUDGET_S) -> None:
+    """``flat[out_offset + m*ldm + n] (+)= Σ_e c[e] · a_eᵀ b_e`` with example e = rows ``[e·R, (e+1)·R)``, ``R % 64 == 0``.
+
+    The clip factor multiplies each example's fp32 partial product in the epilogue (TMEM → registers), so the operand
+    tiles go from TMA straight to the tensor core and ``c`` is applied unrounded.
+    """
+    _need_bf16(a, b)
+    T, M = a.shape
+    N = b.shape[1]
+    if b.shape[0] != T or a.stride(1) != 1 or b.stride(1) != 1:
+        raise ValueError("a [T, M] and b [T, N] must be row-major with the same number of rows")
+    if rows_per_example <= 0 or rows_per_example % 64 or T % rows_per_example:
+        raise ValueError("rows_per_example must be a multiple of 64 that divides the number of rows")
+    B = T // rows_per_example
+    if ex_scale is not None and (ex_scale.dtype != torch.float32 or ex_scale.numel() < B or not ex_scale.is_contiguous()):
+        raise ValueError("ex_scale must hold one contiguous fp32 factor per example")
+    if ldm is None:
+        ldm = N
+    sms = lib.sm_count()
+    if splits is None:
+        tiles = math.ceil(M / 128) * math.ceil(N / 256)
+        splits = max(1, min(B, sms // max(tiles, 1))) if accumulate and tiles < sms else 1
+    if out is not None:
+        if out.dtype != torch.float32:
+            raise TypeError("the destination must be fp32")
+        hi = out_offset + (M - 1) * ldm + N - 1
+        room = out.untyped_storage().nbytes() // 4 - out.storage_offset()
+        if min(out_offset, ldm) < 0 or hi >= room:
+            raise ValueError(f"wgrad_clip_per_example would write element {hi} of a destination holding {room}")
+    elif peer_table is None or shard_elems <= 0:
+        raise ValueError("give either a destination tensor or a peer table with shard_elems")
+    rc = lib.load().ob_wgrad_clip_pe(a.data_ptr(), b.data_ptr(), B, rows_per_example, M, N, a.stride(0), b.stride(0),
+                                     lib.ptr(ex_scale), splits, lib.ptr(out), lib.ptr(peer_table), shard_elems, out_offset,
+                                     ldm, int(accumulate), status.ptr() if status else None, wait_budget_s, sms,
+                                     lib.stream())
+    lib.check(rc, "wgrad_clip_per_example")
+
+
 def wgrad_clip_ref(a, b, *, row_scale=None, seg_offsets=None, num_groups=1):
     """fp32 oracle: returns ``[num_groups, M, N]``."""
     af, bf = a.float(), b.float()
@@ -321,7 +362,7 @@ from .functional import (activation, cross_entropy, cross_entropy_ref, fused_add
                          layer_norm, rms_norm, rms_norm_ref, rope_qk, rope_qk_ref, rope_tables, rows_group_sum_, swiglu)
 
 __all__ = [
-    "gemm", "gemm_ref", "layer_norm", "activation", "rows_group_sum_",
+    "gemm", "gemm_ref", "wgrad_clip_per_example", "layer_norm", "activation", "rows_group_sum_",
     "DeviceWaitTimeout", "KernelLibraryError", "StatusWord", "clip_weighted_sum", "cross_entropy",
     "cross_entropy_ref", "embedding_wgrad", "fused_add_rms_norm", "geglu", "ghost_norm", "ghost_norm_ref", "glu_ref",
     "philox_normal_add_", "pick_block_n", "pick_splits", "rms_norm", "rms_norm_ref", "rope_qk", "rope_qk_ref",

@@ -11,6 +11,14 @@ int ob_wgrad_clip(const void* a, const void* b, int T, int M, int N, long long l
                   long long group_stride, long long out_offset, long long ldm, long long ldn, int n_valid,
                   int accumulate, int block_n, int* status, double wait_budget_s, int num_sms, void* stream);
 
+// out[m, n] (+)= sum over examples e of ex_scale[e] * A_e^T B_e, where example e owns rows [e*ex_rows, (e+1)*ex_rows) of
+// a [T, M] and b [T, N] (ex_rows a multiple of 64).  The factor is applied to each example's fp32 partial product in
+// the epilogue; operands are not modified.  splits > 1 needs accumulate = 1.
+int ob_wgrad_clip_pe(const void* a, const void* b, int num_examples, int ex_rows, int M, int N, long long lda,
+                     long long ldb, const float* ex_scale, int splits, float* out, float* const* peer_out,
+                     long long shard_elems, long long out_offset, long long ldm, int accumulate, int* status,
+                     double wait_budget_s, int num_sms, void* stream);
+
 int ob_ghost_norm(const void* a, const void* g, const int* ids, int B, int T, int Da, int Dg, long long lda,
                   long long ldg, float* norm2, const int* seg, const int* seg_out, long long total_rows, int* status,
                   double wait_budget_s, int num_sms, void* stream);

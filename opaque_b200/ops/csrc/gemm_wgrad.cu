@@ -377,6 +377,243 @@ wgrad_clip_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 }
 
 // ---------------------------------------------------------------------------------------------
+// Per-example variant: every example owns a whole number of 64-row k-blocks (uniform rows_per_example), so the clip
+// factor is constant over an accumulation run.  The MMA warp accumulates ONE example's A_e^T G_e per TMEM buffer and
+// the epilogue warps fold it into fp32 register accumulators as  acc += c_e * P_e  while the tensor core already
+// works on the next example in the other buffer.  Operands are never touched in shared memory (no scaling pass, no
+// extra barrier in the TMA -> MMA chain) and c_e is applied in full fp32 precision.
+constexpr int WP_THREADS = 320;      // TMA warp, MMA warp, 8 epilogue warps (2 per TMEM lane quadrant)
+constexpr int WP_BLOCK_N = 256;
+constexpr int WP_STAGES = 4;
+constexpr int WP_A_BYTES = WG_BLOCK_K * WG_BLOCK_M * 2;
+constexpr int WP_B_BYTES = WG_BLOCK_K * WP_BLOCK_N * 2;
+constexpr int WP_STAGE_BYTES = WP_A_BYTES + WP_B_BYTES;
+constexpr int WP_SMEM = WP_STAGES * WP_STAGE_BYTES + 256 + 1024;
+
+struct WgradPeParams {
+  int M, N;
+  int num_examples, ex_rows;         // ex_rows is a multiple of WG_BLOCK_K
+  int splits;                        // each split owns a contiguous range of examples
+  const float* ex_scale;             // [num_examples] or nullptr (all ones)
+  float* out;
+  float* const* peer_out;
+  long long shard_elems;
+  long long out_offset;
+  long long ldm;
+  int accumulate;
+  int* status;
+  unsigned long long wait_budget_ns;
+};
+
+__device__ __forceinline__ float* resolve_out_pe(const WgradPeParams& p, long long idx) {
+  if (p.peer_out == nullptr) return p.out + idx;
+  const long long owner = idx / p.shard_elems;
+  return p.peer_out[owner] + (idx - owner * p.shard_elems);
+}
+
+__global__ void __launch_bounds__(WP_THREADS, 1)
+wgrad_clip_pe_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const WgradPeParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + WP_STAGES * WP_STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + WP_STAGES;
+  uint64_t* tmem_full = bars + 2 * WP_STAGES;
+  uint64_t* tmem_empty = bars + 2 * WP_STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * WP_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + WG_BLOCK_M - 1) / WG_BLOCK_M;
+  const int tiles_n = (p.N + WP_BLOCK_N - 1) / WP_BLOCK_N;
+  const int total_work = p.splits * tiles_m * tiles_n;
+  const int kpe = p.ex_rows / WG_BLOCK_K;
+  const uint64_t budget = p.wait_budget_ns;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < WP_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 8);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * WP_BLOCK_N);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // work item w -> (split, m tile, n tile); split s owns examples [e0, e1)
+  auto decode = [&](int w, int& m0, int& n0, int& e0, int& e1) {
+    const int mn = tiles_m * tiles_n;
+    const int split = w / mn, r = w % mn;
+    m0 = (r / tiles_n) * WG_BLOCK_M;
+    n0 = (r % tiles_n) * WP_BLOCK_N;
+    e0 = static_cast<int>(static_cast<long long>(p.num_examples) * split / p.splits);
+    e1 = static_cast<int>(static_cast<long long>(p.num_examples) * (split + 1) / p.splits);
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, issued_mask = 0, issued_phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        int m0, n0, e0, e1;
+        decode(w, m0, n0, e0, e1);
+        const int nkb = (e1 - e0) * kpe;
+        const int row_begin = e0 * p.ex_rows;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_EMPTY, budget)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full[stage], WP_STAGE_BYTES);
+          uint8_t* a_dst = smem + stage * WP_STAGE_BYTES;
+          uint8_t* b_dst = a_dst + WP_A_BYTES;
+          const int row = row_begin + kb * WG_BLOCK_K;
+#pragma unroll
+          for (int j = 0; j < WG_BLOCK_M / 64; ++j)
+            tma_load_2d(a_dst + j * (WG_BLOCK_K * 128), &map_a, &full[stage], m0 + 64 * j, row);
+#pragma unroll
+          for (int j = 0; j < WP_BLOCK_N / 64; ++j)
+            tma_load_2d(b_dst + j * (WG_BLOCK_K * 128), &map_b, &full[stage], n0 + 64 * j, row);
+          issued_mask |= 1u << stage;
+          issued_phase = (issued_phase & ~(1u << stage)) | (phase << stage);
+          if (++stage == WP_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        for (int s = 0; s < WP_STAGES; ++s)
+          if (issued_mask & (1u << s)) {
+            int dummy_abort = 0;
+            mbar_wait(&full[s], (issued_phase >> s) & 1u, &dummy_abort, p.status, OB_ERR_DRAIN, budget);
+          }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(WG_BLOCK_M, WP_BLOCK_N, 1, 1);
+      int stage = 0, acc_iter = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        int m0, n0, e0, e1;
+        decode(w, m0, n0, e0, e1);
+        for (int e = e0; ok && e < e1; ++e) {
+          const int as = acc_iter & 1;
+          if (!mbar_wait(&tmem_empty[as], ((acc_iter >> 1) & 1) ^ 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_EMPTY,
+                         budget)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + as * WP_BLOCK_N;
+          for (int kb = 0; kb < kpe; ++kb) {
+            if (!mbar_wait(&full[stage], phase, abort_flag, p.status, OB_ERR_WAIT_FULL, budget)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(smem + stage * WP_STAGE_BYTES);
+            const uint32_t b_addr = a_addr + WP_A_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < WG_BLOCK_K / WG_UMMA_K; ++kk) {
+              const uint64_t ad = make_smem_desc(a_addr + kk * (WG_UMMA_K * 128), WG_BLOCK_K * 128, 1024, 2);
+              const uint64_t bd = make_smem_desc(b_addr + kk * (WG_UMMA_K * 128), WG_BLOCK_K * 128, 1024, 2);
+              umma_bf16(d_tmem, ad, bd, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit(&empty[stage]);
+            if (++stage == WP_STAGES) { stage = 0; phase ^= 1; }
+          }
+          if (!ok) break;
+          umma_commit(&tmem_full[as]);
+          ++acc_iter;
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;                      // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;            // which 128 of the tile's 256 columns
+    int acc_iter = 0;
+    bool ok = true;
+    const bool vec_ok = ((p.ldm & 3) == 0) && ((p.N & 3) == 0) && ((p.out_offset & 3) == 0) &&
+                        (p.peer_out == nullptr || (p.shard_elems & 3) == 0);
+    for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+      int m0, n0, e0, e1;
+      decode(w, m0, n0, e0, e1);
+      float acc[128];
+#pragma unroll
+      for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+      for (int e = e0; e < e1; ++e) {
+        const int as = acc_iter & 1;
+        const float c = p.ex_scale ? __ldg(p.ex_scale + e) : 1.f;
+        if (!mbar_wait(&tmem_full[as], (acc_iter >> 1) & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL, budget)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          float v[32];
+          tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * WP_BLOCK_N + half * 128 + ch * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[ch * 32 + j] = fmaf(c, v[j], acc[ch * 32 + j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[as]);
+        ++acc_iter;
+      }
+      if (!ok) break;
+      if (e1 <= e0 && p.accumulate) continue;
+      const int m = m0 + q * 32 + lane;
+      if (m < p.M) {
+        const long long row_base = p.out_offset + static_cast<long long>(m) * p.ldm;
+#pragma unroll
+        for (int j4 = 0; j4 < 32; ++j4) {
+          const int n = n0 + half * 128 + 4 * j4;
+          if (n >= p.N) break;
+          if (vec_ok) {
+            float* dst = resolve_out_pe(p, row_base + n);
+            const float4 x = make_float4(acc[4 * j4], acc[4 * j4 + 1], acc[4 * j4 + 2], acc[4 * j4 + 3]);
+            if (p.accumulate) red_add_v4(dst, x);
+            else *reinterpret_cast<float4*>(dst) = x;
+          } else {
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+              if (n + t < p.N) {
+                float* dst = resolve_out_pe(p, row_base + n + t);
+                if (p.accumulate) red_add_f32(dst, acc[4 * j4 + t]);
+                else *dst = acc[4 * j4 + t];
+              }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * WP_BLOCK_N);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -483,6 +720,49 @@ extern "C" int ob_wgrad_clip(const void* a, const void* b, int T, int M, int N, 
   if (block_n == 128) return launch_wgrad<128>(ma, mb, p, num_sms, st);
   if (block_n == 64) return launch_wgrad<64>(ma, mb, p, num_sms, st);
   return -1;
+}
+
+extern "C" int ob_wgrad_clip_pe(const void* a, const void* b, int num_examples, int ex_rows, int M, int N, long long lda,
+                                long long ldb, const float* ex_scale, int splits, float* out, float* const* peer_out,
+                                long long shard_elems, long long out_offset, long long ldm, int accumulate, int* status,
+                                double wait_budget_s, int num_sms, void* stream) {
+  using namespace ob;
+  if (num_examples <= 0 || ex_rows <= 0 || M <= 0 || N <= 0) return 0;
+  if (ex_rows % WG_BLOCK_K) return -3;
+  if (splits < 1) splits = 1;
+  if (splits > num_examples) splits = num_examples;
+  if (splits > 1 && !accumulate) return -4;          // split partial sums must be reduced into the destination
+  const long long T = static_cast<long long>(num_examples) * ex_rows;
+  if (T > 0x7fffffffLL) return -5;
+  CUtensorMap ma, mb;
+  int rc = make_bf16_map_2d(&ma, a, T, M, lda, 64, WG_BLOCK_K);
+  if (rc) return rc;
+  rc = make_bf16_map_2d(&mb, b, T, N, ldb, 64, WG_BLOCK_K);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(wgrad_clip_pe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WP_SMEM) != cudaSuccess)
+      return -20;
+    configured = true;
+  }
+  WgradPeParams p;
+  p.M = M; p.N = N;
+  p.num_examples = num_examples; p.ex_rows = ex_rows;
+  p.splits = splits;
+  p.ex_scale = ex_scale;
+  p.out = out;
+  p.peer_out = peer_out;
+  p.shard_elems = shard_elems;
+  p.out_offset = out_offset;
+  p.ldm = ldm;
+  p.accumulate = accumulate;
+  p.status = status;
+  p.wait_budget_ns = static_cast<unsigned long long>(wait_budget_s * 1e9);
+  const long long tiles = static_cast<long long>((M + WG_BLOCK_M - 1) / WG_BLOCK_M) * ((N + WP_BLOCK_N - 1) / WP_BLOCK_N);
+  const long long total = tiles * splits;
+  const int grid = static_cast<int>(total < num_sms ? total : num_sms);
+  wgrad_clip_pe_kernel<<<grid, WP_THREADS, WP_SMEM, static_cast<cudaStream_t>(stream)>>>(ma, mb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
 extern "C" int ob_last_detail(char* buf, int len) {

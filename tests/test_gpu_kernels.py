@@ -45,6 +45,24 @@ def test_wgrad_clip_matches_reference(dev, T, M, N, bn):
     assert bool((scaled.float().abs() <= (a.float() * sc[:, None]).abs() * (1 + 2 ** -8)).all())
 
 
+@pytest.mark.parametrize("B,R,M,N", [(2, 64, 128, 256), (5, 128, 200, 328), (16, 512, 768, 3072), (8, 1024, 2048, 1024)])
+def test_wgrad_clip_per_example_epilogue_scaling(dev, B, R, M, N):
+    from opaque_b200 import ops
+    torch.manual_seed(B + R)
+    st = ops.StatusWord(dev)
+    a = torch.randn(B * R, M, device=dev).bfloat16()
+    b = torch.randn(B * R, N, device=dev).bfloat16()
+    c = torch.rand(B, device=dev)
+    ref = ops.wgrad_clip_ref(a, b, row_scale=c.repeat_interleave(R))[0]
+    out = torch.zeros(8 + M * N, device=dev)
+    ops.wgrad_clip_per_example(a, b, out, ex_scale=c, rows_per_example=R, out_offset=8, accumulate=False, status=st)
+    assert st.read() == 0 and rel(out[8:].view(M, N), ref) < 2e-5 and float(out[:8].abs().max()) == 0
+    ops.wgrad_clip_per_example(a, b, out, ex_scale=c, rows_per_example=R, out_offset=8, accumulate=True, status=st)   # split-K + reduce
+    assert st.read() == 0 and rel(out[8:].view(M, N), 2 * ref) < 2e-5
+    ops.wgrad_clip_per_example(a, b, out, ex_scale=None, rows_per_example=R, out_offset=8, accumulate=False, splits=1, status=st)
+    assert rel(out[8:].view(M, N), ops.wgrad_clip_ref(a, b)[0]) < 2e-5
+
+
 def test_wgrad_clip_is_deterministic_without_split_k(dev):
     from opaque_b200 import ops
     a = torch.randn(2048, 256, device=dev).bfloat16()

@@ -207,6 +207,7 @@ def main() -> None:
     clocks = ClockSampler(local)
     clocks.start()
     launches0 = lib.LAUNCHES
+    engine.opt.timing = []
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -216,6 +217,8 @@ def main() -> None:
     barrier()
     dev_ms = e0.elapsed_time(e1)
     launches = lib.LAUNCHES - launches0
+    sync_ms = engine.opt.timing_ms()
+    engine.opt.timing = None
     del staged
 
     # ---- end-to-end region: pinned host batch -> device, step, loss back to host, every step ----------
@@ -233,7 +236,8 @@ def main() -> None:
     clock_info = clocks.stop()
     engine.group.check("bench")
 
-    stats = torch.tensor([dev_ms, e2e_s * 1e3, float(tokens), float(tokens_e2e), float(launches)], device=dev,
+    stats = torch.tensor([dev_ms, e2e_s * 1e3, float(tokens), float(tokens_e2e), float(launches),
+                          sync_ms["grad_barrier_ms"], sync_ms["shard_step_ms"], sync_ms["param_barrier_ms"]], device=dev,
                          dtype=torch.float64)
     if world > 1:
         mx = stats.clone()
@@ -242,6 +246,7 @@ def main() -> None:
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
         dev_ms, e2e_ms = float(mx[0]), float(mx[1])
         tokens, tokens_e2e, launches = float(sm[2]), float(sm[3]), float(sm[4])
+        sync_ms = {"grad_barrier_ms": float(mx[5]), "shard_step_ms": float(mx[6]), "param_barrier_ms": float(mx[7])}
     else:
         e2e_ms = e2e_s * 1e3
     if rank == 0:
@@ -262,6 +267,10 @@ def main() -> None:
                     "d2h_bytes_per_step": 24, "ms_per_step": e2e_ms / args.steps,
                     "last_loss": None if last is None else last.loss},
             "gpu_launches": int(launches),
+            # ms per step (max over ranks) spent waiting at the two device-side barriers of the sharded step and in the
+            # fused noise/optimizer/parameter-push kernel; gradient reduction itself runs inside the producer kernels
+            "step_sync": {k: round(v, 4) for k, v in sync_ms.items()},
+            "exposed_comm_ms_per_step": round(sync_ms["grad_barrier_ms"] + sync_ms["param_barrier_ms"], 4),
             "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 2 ** 30,
         }
         print(json.dumps(out))

@@ -161,6 +161,7 @@ class ShardedDPOptimizer:
         self.step_count = 0
         self.phi = 0.0
         self.mechanism = mechanism
+        self.timing: list[tuple] | None = None     # set to [] to record CUDA events around barrier / step / barrier
         self.ftrl_state = None
         self.nbuf = 0
         self.mode = 0
@@ -201,7 +202,12 @@ class ShardedDPOptimizer:
             self.phi = b2 * self.phi + (1 - b2) * var
         phi_hat = self.phi / (1 - b2 ** t) if self.cfg.noise_bias_correction else 0.0
         seed = fold_in(self.key, self.step_count).seed
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if self.timing is not None else None
+        if ev:
+            ev[0].record()
         g.barrier()
+        if ev:
+            ev[1].record()
         ops.shard_step(
             grad=sp.grad.local, master=sp.master, m=sp.m, v=sp.v,
             params_local=sp.params.local if g.world == 1 else None,
@@ -211,8 +217,25 @@ class ShardedDPOptimizer:
             decoupled_wd=self.cfg.decoupled_weight_decay, ftrl_state=self.ftrl_state, ftrl_mode=self.mode,
             ftrl_coef=self.coef, nbuf=self.nbuf, ring_head=(self.step_count % self.nbuf) if self.mode in (2, 3) else 0,
             noisy_out=noisy_out, skip_update=skip_update)
+        if ev:
+            ev[2].record()
         g.barrier()
+        if ev:
+            ev[3].record()
+            self.timing.append(tuple(ev))
         self.step_count = t
+
+    def timing_ms(self) -> dict[str, float]:
+        """Mean milliseconds per step of: waiting for all ranks' gradient reductions, the fused noise + optimizer +
+        parameter push kernel, and waiting for all ranks' parameter stores (needs ``timing = []`` before the steps)."""
+        rows = self.timing or []
+        if not rows:
+            return {"grad_barrier_ms": 0.0, "shard_step_ms": 0.0, "param_barrier_ms": 0.0}
+        torch.cuda.synchronize(self.space.group.device)
+        n = len(rows)
+        return {"grad_barrier_ms": sum(r[0].elapsed_time(r[1]) for r in rows) / n,
+                "shard_step_ms": sum(r[1].elapsed_time(r[2]) for r in rows) / n,
+                "param_barrier_ms": sum(r[2].elapsed_time(r[3]) for r in rows) / n}
 
     # ---- checkpoint -----------------------------------------------------------------------
     def state_dict(self) -> dict[str, Any]:

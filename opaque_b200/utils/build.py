@@ -69,7 +69,7 @@ def build_accounting(force: bool = False) -> Path:
     """Compile the C++17 PLD accountant into a pybind11 extension module."""
     import pybind11
     target = accounting_ext_path()
-    sources = sorted(ACC_SRC.glob("*.cpp"))
+    sources = sorted(p for p in ACC_SRC.glob("*.cpp") if p.name != "selftest.cpp")     # selftest.cpp has its own main()
     deps = sources + sorted(ACC_SRC.glob("*.hpp"))
     if not sources:
         raise RuntimeError("accounting sources missing")

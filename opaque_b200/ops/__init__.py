@@ -50,13 +50,22 @@ def pick_block_n(n: int) -> int:
     return 128 if n > 64 else 64
 
 
-def pick_splits(work_tiles: int, rows: int, sms: int) -> int:
-    """K-splits so that (tiles x splits) fills the SMs while each split keeps >= 8 k-blocks."""
-    if work_tiles >= sms:
-        return 1
-    want = max(1, sms // max(work_tiles, 1))
+def pick_splits(work_tiles: int, rows: int, sms: int, *, max_splits: int | None = None) -> int:
+    """K-splits that balance the persistent grid: maximise ``items / (waves · sms)`` for ``items = tiles · splits``.
+
+    Every split keeps at least 8 k-blocks of 64 rows; ties go to the smaller split count (less reduction traffic).
+    """
     cap = max(1, rows // (64 * 8))
-    return max(1, min(want, cap))
+    if max_splits is not None:
+        cap = min(cap, max_splits)
+    cap = min(cap, max(1, 2 * sms // max(work_tiles, 1)) if work_tiles < sms else 4)
+    best, best_eff = 1, 0.0
+    for s in range(1, cap + 1):
+        items = work_tiles * s
+        eff = items / (math.ceil(items / sms) * sms)
+        if eff > best_eff + 0.02:
+            best, best_eff = s, eff
+    return best
 
 
 def wgrad_clip(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, row_scale: torch.Tensor | None = None,
@@ -130,7 +139,7 @@ def wgrad_clip_per_example(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor |
     sms = lib.sm_count()
     if splits is None:
         tiles = math.ceil(M / 128) * math.ceil(N / 256)
-        splits = max(1, min(B, sms // max(tiles, 1))) if accumulate and tiles < sms else 1
+        splits = pick_splits(tiles, T, sms, max_splits=B) if accumulate else 1
     if out is not None:
         if out.dtype != torch.float32:
             raise TypeError("the destination must be fp32")

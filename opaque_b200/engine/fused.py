@@ -280,7 +280,7 @@ class _DPLinear(Function):
             return dx, dw, db
         cap.add_linear(weight, x2d, g2d)
         if ctx.bias is not None:
-            if g2d.dtype == torch.bfloat16 and g2d.shape[1] % 2 == 0:
+            if g2d.dtype == torch.bfloat16 and g2d.shape[1] % 8 == 0 and g2d.stride(0) % 8 == 0:
                 ops.rows_group_sum_(cap.pe_view(ctx.bias), g2d, cap.batch_size)
             else:
                 cap.pe_view(ctx.bias).add_(g2d.view(cap.batch_size, cap.tokens, -1).sum(1, dtype=torch.float32))

@@ -127,34 +127,49 @@ layernorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat1
 // Per-example reductions over the token rows of each example: out[e, col] += sum_r f(r, col).
 //   mode 0: f = g                      (bias gradients: LayerNorm bias, linear bias)
 //   mode 1: f = g * (x - mean) * rstd  (LayerNorm weight gradient)
-// grid = (examples, column blocks of 256, row splits); each thread owns two adjacent columns; split partial sums are
-// combined with atomics (the destination is that example's row of the fp32 per-example gradient buffer).
-__global__ void __launch_bounds__(128)
+// grid = (examples, column blocks of 256, row splits).  A 256-thread block reads 8 rows x 256 columns per iteration
+// with 16-byte loads (32 column groups x 8 row lanes), folds the row lanes through shared memory and adds the split's
+// partial sums into that example's row of the fp32 per-example gradient buffer with atomics.
+__global__ void __launch_bounds__(256)
 rows_group_sum_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ x,
                       const float* __restrict__ mean, const float* __restrict__ rstd, int rows_per_example, int N,
                       long long ldg, float* __restrict__ out, long long ld_out, int mode) {
+  __shared__ float red[8][256 + 8];
   const int e = blockIdx.x;
-  const int col = (blockIdx.y * 128 + threadIdx.x) * 2;
-  if (col >= N) return;
+  const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int col = blockIdx.y * 256 + cg * 8;
   const int chunk = (rows_per_example + gridDim.z - 1) / gridDim.z;
   const int r0 = e * rows_per_example + blockIdx.z * chunk;
   const int r1 = min(r0 + chunk, (e + 1) * rows_per_example);
-  float a0 = 0.f, a1 = 0.f;
-  for (int r = r0; r < r1; ++r) {
-    const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g + static_cast<long long>(r) * ldg + col));
-    if (mode == 1) {
-      const float mu = __ldg(mean + r), rs = __ldg(rstd + r);
-      const float2 xv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + static_cast<long long>(r) * ldg + col));
-      a0 += gv.x * (xv.x - mu) * rs;
-      a1 += gv.y * (xv.y - mu) * rs;
-    } else {
-      a0 += gv.x;
-      a1 += gv.y;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if (col < N) {
+    for (int r = r0 + rl; r < r1; r += 8) {
+      float gv[8];
+      ln_unpack8(*reinterpret_cast<const ln_bf16x8*>(g + static_cast<long long>(r) * ldg + col), gv);
+      if (mode == 1) {
+        float xv[8];
+        ln_unpack8(*reinterpret_cast<const ln_bf16x8*>(x + static_cast<long long>(r) * ldg + col), xv);
+        const float mu = __ldg(mean + r), rs = __ldg(rstd + r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += gv[j] * (xv[j] - mu) * rs;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += gv[j];
+      }
     }
   }
-  float* o = out + static_cast<long long>(e) * ld_out + col;
-  atomicAdd(o, a0);
-  if (col + 1 < N) atomicAdd(o + 1, a1);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[rl][cg * 8 + j] = acc[j];
+  __syncthreads();
+  const int c = threadIdx.x;
+  if (blockIdx.y * 256 + c < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][c];
+    atomicAdd(out + static_cast<long long>(e) * ld_out + blockIdx.y * 256 + c, t);
+  }
 }
 
 // Plain activations.  act: 0 silu, 1 gelu (erf), 2 gelu (tanh approximation), 3 relu.
@@ -227,12 +242,13 @@ extern "C" int ob_rows_group_sum(const void* g, const void* x, const float* mean
                                  int rows_per_example, int N, long long ldg, float* out, long long ld_out, int mode,
                                  void* stream) {
   if (num_examples <= 0 || rows_per_example <= 0 || N <= 0) return 0;
-  if ((N & 1) || (ldg & 1)) return -2;
+  if ((N & 7) || (ldg & 7) || (reinterpret_cast<uintptr_t>(g) & 15) || (x != nullptr && (reinterpret_cast<uintptr_t>(x) & 15)))
+    return -2;
   if (mode == 1 && (x == nullptr || mean == nullptr || rstd == nullptr)) return -3;
   int splits = rows_per_example / 64;
   splits = splits < 1 ? 1 : (splits > 16 ? 16 : splits);
-  dim3 grid(num_examples, (N / 2 + 127) / 128, splits);
-  rows_group_sum_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  dim3 grid(num_examples, (N + 255) / 256, splits);
+  rows_group_sum_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(g), static_cast<const __nv_bfloat16*>(x), mean, rstd, rows_per_example, N, ldg,
       out, ld_out, mode);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;

@@ -171,18 +171,20 @@ def main() -> None:
                            step_config=DPStepConfig(lr=dp["lr"], noise_bias_correction=True), microbatch_size=mb,
                            mechanism=mechanism, cuda_graph=use_graph)
 
-    # synthetic dataset shard of this rank, in pinned host memory; Poisson sampling with E[B] = per_gpu
-    shard_size = per_gpu * 100
-    gen = torch.Generator().manual_seed(99 + rank)
-    data = torch.randint(0, vocab, (shard_size, seq), generator=gen, dtype=torch.int32).pin_memory()
-    sampler = PoissonSampler(range(shard_size), per_gpu / shard_size, key=fold_in(key(7), rank))
+    # synthetic dataset in pinned host memory (identical on every rank: same seed).  ONE global Poisson draw per step
+    # with E[B] = per_gpu * world is dealt out evenly over the ranks, so no rank waits for an unlucky peer.
+    from opaque_b200.dpsgd import BalancedRankSampler
+    data_size = per_gpu * 100 * world
+    gen = torch.Generator().manual_seed(99)
+    data = torch.randint(0, vocab, (data_size, seq), generator=gen, dtype=torch.int32).pin_memory()
+    sampler = BalancedRankSampler(PoissonSampler(range(data_size), per_gpu * world / data_size, key=key(7)), rank, world)
     batches = iter(sampler)
-    cursor = [0]
+    cursor = [rank * per_gpu]
 
     def host_batch():
-        if sampling is not None:                      # fixed-size batches in order (DP-FTRL)
-            lo = cursor[0] % (shard_size - per_gpu)
-            cursor[0] += per_gpu
+        if sampling is not None:                      # fixed-size batches in order (DP-FTRL), disjoint across ranks
+            lo = cursor[0] % (data_size - per_gpu)
+            cursor[0] += per_gpu * world
             return data[lo:lo + per_gpu]
         idx = next(batches)
         return data[torch.as_tensor(idx, dtype=torch.long)].pin_memory() if idx else data[:0]
@@ -257,7 +259,7 @@ def main() -> None:
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "impl": "ours",
             "config": {"model": name, "global_batch": global_batch, "seq_len": seq, "parallelism": f"{par}{world}",
-                       "sampling": sampling or f"Poisson, expected {per_gpu} sequences per GPU", "microbatch": mb, "cuda_graph_microbatches": use_graph,
+                       "sampling": sampling or f"Poisson over the whole dataset (rate {per_gpu * world}/{data_size}), one global draw per step dealt out evenly over ranks", "microbatch": mb, "cuda_graph_microbatches": use_graph,
                        "loss_fraction": frac, "clip": dp["clipping_norm"], "sigma": dp["noise_multiplier"],
                        "optimizer": "AdamW-BC", "lr": dp["lr"],
                        "l2": "inputs larger than L2 (per-step working set >> 126 MB; no explicit flush)",

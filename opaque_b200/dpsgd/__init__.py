@@ -5,7 +5,7 @@ Parity: packages/opaque-dpsgd/src/opaque/dpsgd/__init__.py.
 from . import clipping, noise, sampling
 from .clipping import adaptive_clipped_grad, auto_clipped_grad, clipped_grad, per_group
 from .noise import gaussian_noise
-from .sampling import KOutOfTSampler, PoissonSampler, RandomAllocationSampler
+from .sampling import BalancedRankSampler, KOutOfTSampler, PoissonSampler, RandomAllocationSampler
 
 
 def __getattr__(name):
@@ -16,4 +16,4 @@ def __getattr__(name):
 
 
 __all__ = ["KOutOfTSampler", "PoissonSampler", "RandomAllocationSampler", "accounting", "adaptive_clipped_grad",
-           "auto_clipped_grad", "clipped_grad", "clipping", "gaussian_noise", "noise", "per_group", "sampling"]
+           "BalancedRankSampler", "auto_clipped_grad", "clipped_grad", "clipping", "gaussian_noise", "noise", "per_group", "sampling"]

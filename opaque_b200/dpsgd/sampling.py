@@ -194,4 +194,52 @@ register_serializer(KOutOfTSampler, lambda s: {**_save_common(s), "k": s.k, "t":
 register_serializer(RandomAllocationSampler, lambda s: {**_save_common(s), "num_bins": s.num_bins},
                     lambda t, sd: _load_common(t, sd, ("num_bins",)))
 
-__all__ = ["KOutOfTSampler", "PoissonSampler", "RandomAllocationSampler", "poisson_step_indices"]
+
+class BalancedRankSampler(Sampler):
+    """Deal ONE global sample out evenly over the data-parallel ranks.
+
+    Every rank builds the same ``inner`` sampler (same key, the GLOBAL index range) and keeps positions
+    ``rank, rank + world, ...`` of the sorted draw, so per-rank batch sizes differ by at most one example.  The union
+    over ranks is exactly the inner sampler's draw, so the privacy analysis is that of the inner sampler on the whole
+    dataset — while the step time no longer follows the unluckiest rank (independent per-rank Poisson draws of
+    expected size b have a spread of about ±sqrt(b), and every rank waits for the largest).  Each rank must be able
+    to read any record.  No counterpart in the reference, which samples per rank
+    (packages/opaque-dpsgd/src/opaque/api/dpsgd/sampling).
+    """
+
+    def __init__(self, inner: Sampler, rank: int, world: int):
+        if not 0 <= rank < world:
+            raise ValueError("need 0 <= rank < world")
+        self.inner, self.rank, self.world = inner, rank, world
+
+    def __iter__(self) -> Iterator[list[int]]:
+        for batch in self.inner:
+            yield sorted(batch)[self.rank::self.world]
+
+    def __len__(self) -> int:
+        return len(self.inner)
+
+    def __getattr__(self, name: str):            # sample_rate, num_bins, consumed, ... of the global sampler
+        if name in ("inner", "rank", "world"):
+            raise AttributeError(name)
+        return getattr(self.inner, name)
+
+
+
+def _load_balanced(template: "BalancedRankSampler", sd: dict[str, Any]) -> "BalancedRankSampler":
+    from ..serialization import from_state_dict
+    if int(sd.get("world", template.world)) != template.world:
+        raise ValueError(f"sampler was saved for {sd['world']} ranks but the job has {template.world}")
+    template.inner = from_state_dict(template.inner, sd["inner"])
+    return template
+
+
+def _save_balanced(s: "BalancedRankSampler") -> dict[str, Any]:
+    from ..serialization import state_dict
+    return {"inner": state_dict(s.inner), "world": s.world}
+
+
+register_serializer(BalancedRankSampler, _save_balanced, _load_balanced)
+
+
+__all__ = ["BalancedRankSampler", "KOutOfTSampler", "PoissonSampler", "RandomAllocationSampler", "poisson_step_indices"]

@@ -507,8 +507,9 @@ class FusedDPEngine:
         (it also performs every kernel's one-time set-up), the second is captured and replayed, later ones only
         replay.  Launch-bound models (hundreds of small kernels per layer) stop being limited by the host.
         """
-        full = self.microbatch_size
-        sig = tuple((k, tuple(v.shape[1:]), v.dtype) for k, v in sorted(sub.items()))
+        # static sizes microbatch_size / {1, 2, 4, 8}: a short tail microbatch replays the smallest graph that holds it
+        full = min(sz for sz in (max(self.microbatch_size >> k, 1) for k in range(4)) if sz >= mb)
+        sig = (full,) + tuple((k, tuple(v.shape[1:]), v.dtype) for k, v in sorted(sub.items()))
         entry = self._graphs.get(sig)
         if entry is None:
             static = {k: torch.zeros((full,) + tuple(v.shape[1:]), dtype=v.dtype, device=v.device) for k, v in sub.items()}

@@ -361,7 +361,8 @@ class DPTrainer:
 
     def _build_sampler(self, n_local: int, steps: int, data_key: RngKey):
         a = self.args
-        q = min(1.0, a.per_device_train_batch_size / max(n_local, 1))
+        ranks = a.world_size if getattr(self, "_balanced", False) else 1        # a global draw covers all ranks' batches
+        q = min(1.0, a.per_device_train_batch_size * ranks / max(n_local, 1))
         kw = dict(a.sampling_kwargs)
         mode = a.sampling_mode
         rng = range(n_local)
@@ -441,17 +442,27 @@ class DPTrainer:
         W, rank = a.world_size, a.process_index
         n_total = len(self.train_dataset)
         per = n_total // W                                   # equal shards; the tail is trimmed
-        self._local_data = local_shard(_Trimmed(self.train_dataset, per * W), rank=rank, world_size=W)
-        n_local = per
-        q_nominal = min(1.0, a.per_device_train_batch_size / max(n_local, 1))
+        # sampling_kwargs={"balance": True}: ONE global draw per step dealt out evenly over the ranks (every rank reads
+        # any record); default: disjoint shards with an independent draw per rank, as in the reference
+        self._balanced = bool(a.sampling_kwargs.get("balance", False)) and W > 1 and a.sampling_mode != "sequential"
+        if self._balanced:
+            self._local_data = _Trimmed(self.train_dataset, per * W)
+            n_local = per * W
+        else:
+            self._local_data = local_shard(_Trimmed(self.train_dataset, per * W), rank=rank, world_size=W)
+            n_local = per
+        q_nominal = min(1.0, a.per_device_train_batch_size / max(per, 1))
         if a.max_steps > 0:
             steps = a.max_steps
         else:
             steps = max(1, math.ceil(a.num_train_epochs / q_nominal))
         self.state.max_steps = steps
         self.target_delta = a.privacy_target_delta if a.privacy_target_delta is not None else 1.0 / (n_total ** 1.1)
-        data_key = fold_in(key(a.data_seed if a.data_seed is not None else a.seed), rank)
+        data_key = fold_in(key(a.data_seed if a.data_seed is not None else a.seed), "global" if self._balanced else rank)
         self.sampler, self.sample_rate = self._build_sampler(n_local, steps, data_key)
+        if self._balanced:
+            from ..dpsgd.sampling import BalancedRankSampler
+            self.sampler = BalancedRankSampler(self.sampler, rank, W)
         self._strategy = build_strategy(a.privacy_noise_mechanism, a.privacy_noise_mechanism_kwargs) \
             if a.privacy_noise_mechanism in MECHANISMS_DPFTRL else None
         self.engine_kind = self._resolve_engine()

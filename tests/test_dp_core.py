@@ -238,3 +238,21 @@ def test_optimizer_state_round_trip():
     sd = state_dict(st)
     back = from_state_dict(opt.init(q), sd)
     assert back.step == 1 and torch.equal(back.moment.mu["w"], st.moment.mu["w"])
+
+
+def test_balanced_rank_sampler_deals_one_global_draw_evenly():
+    from opaque_b200.dpsgd import BalancedRankSampler, PoissonSampler
+    from opaque_b200.random import key
+    from opaque_b200.serialization import from_state_dict, state_dict
+    world = 4
+    per_rank = [list(BalancedRankSampler(PoissonSampler(range(4000), 0.05, n_steps=6, key=key(3)), r, world)) for r in range(world)]
+    whole = list(PoissonSampler(range(4000), 0.05, n_steps=6, key=key(3)))
+    for step in range(6):
+        parts = [per_rank[r][step] for r in range(world)]
+        assert sorted(i for p in parts for i in p) == sorted(whole[step])            # the union is the global draw
+        assert max(map(len, parts)) - min(map(len, parts)) <= 1                       # sizes differ by at most one
+    s = BalancedRankSampler(PoissonSampler(range(4000), 0.05, n_steps=6, key=key(3)), 1, world)
+    it = iter(s)
+    next(it), next(it)
+    resumed = from_state_dict(BalancedRankSampler(PoissonSampler(range(4000), 0.05, n_steps=6, key=key(3)), 1, world), state_dict(s))
+    assert list(resumed) == per_rank[1][2:]

@@ -40,7 +40,10 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "restated"],
+                    help="ours: fused engine; reference: the unmodified reference package (unavailable offline); restated: "
+                         "the reference's algorithm (vmap per-example gradients, clip, NCCL all-reduce, host-generated "
+                         "noise, functional AdamW-BC) written with this library's reference engine and plain PyTorch ops")
     ap.add_argument("--config", default="llama8b-lora", choices=["llama8b-lora", "gpt2", "llama1b-blt", "moe", "llama-tiny"])
     ap.add_argument("--microbatch", type=int, default=0)
     ap.add_argument("--per-gpu-batch", type=int, default=0)
@@ -80,6 +83,99 @@ class ClockSampler:
         reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i].lower() == "active"})
         return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(mhz)}
+
+
+def run_restated(args, model, dp, data, sampler, seq, per_gpu, mb, frac, vocab, name, world, rank, dev) -> None:
+    """The reference's algorithmic path on the same box: ``vmap(grad)`` per-example gradients in microbatches, clip,
+    per-dtype NCCL all-reduce, noise generated on the host and copied over, tree-mapped AdamW-BC.  Same metric/config."""
+    import torch
+    import torch.distributed as dist
+
+    from opaque_b200 import optimizers
+    from opaque_b200.alignment.sft import nll_loss
+    from opaque_b200.distributed import sum_gradients_, sync
+    from opaque_b200.dpsgd import clipped_grad, gaussian_noise
+    from opaque_b200.functional import make_functional
+    from opaque_b200.models import shift_labels
+    from opaque_b200.ops.functional import plain_torch_ops
+    from opaque_b200.random import key
+
+    fmodel, trainable, frozen = make_functional(model, disable_autograd_tracking=True, partition_trainable=True)
+
+    def loss_fn(tr, ex):
+        logits = fmodel({**frozen, **tr}, ex["input_ids"].unsqueeze(0))
+        return nll_loss(logits, ex["labels"].unsqueeze(0)).squeeze(0)
+    rmb = max(1, min(mb, 4 if "8B" in name else mb))          # vmap holds one gradient copy per example
+    grad_fn, clip_state = clipped_grad(loss_fn, clipping_norm=dp["clipping_norm"], normalize_by=float(per_gpu * world),
+                                       batch_argnums=1, return_aux=True, microbatch_size=rmb)
+    noise_fn, noise_state = gaussian_noise(noise_multiplier=dp["noise_multiplier"], key=key(42))
+    opt = optimizers.adamw(lr=dp["lr"], weight_decay=0.0, noise_bias_correction=True)
+    opt_state = opt.init(trainable)
+    batches = iter(sampler)
+
+    def host_batch():
+        idx = next(batches)
+        return data[torch.as_tensor(idx, dtype=torch.long)].pin_memory() if idx else data[:0]
+
+    def step(hb):
+        nonlocal trainable, clip_state, noise_state, opt_state
+        ids = hb.to(dev, non_blocking=True).long()
+        payload = {"input_ids": ids, "labels": shift_labels(ids, frac)}
+        with plain_torch_ops():
+            (grads, aux), clip_state = grad_fn(trainable, payload, state=clip_state)
+        grads = sum_gradients_(grads)
+        aux = sync(aux)
+        noisy, noise_state = noise_fn(grads, noise_state)
+        updates, opt_state = opt.update(noisy, opt_state, params=trainable)
+        trainable = optimizers.apply_updates(trainable, updates)
+        return float(aux.loss_values.mean()) if aux.batch_size else 0.0
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    for _ in range(args.warmup):
+        step(host_batch())
+    barrier()
+    hbs = [host_batch() for _ in range(args.steps)]
+    tokens = sum(b.numel() for b in hbs)
+    clocks = ClockSampler(dev.index)
+    clocks.start()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    last = 0.0
+    for hb in hbs:
+        last = step(hb)                                   # H2D of the batch and D2H of the loss every step
+    e1.record()
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    barrier()
+    stats = torch.tensor([e0.elapsed_time(e1), wall_ms, float(tokens)], device=dev, dtype=torch.float64)
+    if world > 1:
+        mx, sm = stats.clone(), stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        stats = torch.stack([mx[0], mx[1], sm[2]])
+    dev_ms, wall_ms, tokens = stats.tolist()
+    if rank == 0:
+        h2d = sum(b.numel() * b.element_size() for b in hbs) / max(args.steps, 1)
+        print(json.dumps({
+            "metric": "DP-SGD tokens/sec (box, max over ranks)", "value": tokens / (dev_ms / 1e3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic uniform token ids, random-init weights", "impl": "restated",
+            "config": {"model": name, "global_batch": per_gpu * world, "seq_len": seq, "parallelism": f"ddp{world}",
+                       "microbatch": rmb, "path": "vmap(grad) per-example gradients -> clip -> NCCL all-reduce -> host noise -> AdamW-BC",
+                       "l2": "inputs larger than L2 (per-step working set >> 126 MB; no explicit flush)"},
+            "clocks": clocks.stop(),
+            "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8,
+                    "last_loss": last},
+            "gpu_launches": 0, "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 2 ** 30}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def main() -> None:
@@ -166,11 +262,6 @@ def main() -> None:
     use_graph = bool(args.cuda_graph) if args.cuda_graph >= 0 else args.config in ("gpt2",)
     global_batch = per_gpu * world
 
-    engine = FusedDPEngine(model, clipping_norm=dp["clipping_norm"], noise_multiplier=dp["noise_multiplier"],
-                           normalize_by=float(global_batch), key=key(42),
-                           step_config=DPStepConfig(lr=dp["lr"], noise_bias_correction=True), microbatch_size=mb,
-                           mechanism=mechanism, cuda_graph=use_graph)
-
     # synthetic dataset in pinned host memory (identical on every rank: same seed).  ONE global Poisson draw per step
     # with E[B] = per_gpu * world is dealt out evenly over the ranks, so no rank waits for an unlucky peer.
     from opaque_b200.dpsgd import BalancedRankSampler
@@ -189,6 +280,15 @@ def main() -> None:
         idx = next(batches)
         return data[torch.as_tensor(idx, dtype=torch.long)].pin_memory() if idx else data[:0]
 
+    if args.impl == "restated":
+        run_restated(args, model, dp, data, sampler, seq, per_gpu, mb, frac, vocab, name, world, rank, dev)
+        return
+
+    engine = FusedDPEngine(model, clipping_norm=dp["clipping_norm"], noise_multiplier=dp["noise_multiplier"],
+                           normalize_by=float(global_batch), key=key(42),
+                           step_config=DPStepConfig(lr=dp["lr"], noise_bias_correction=True), microbatch_size=mb,
+                           mechanism=mechanism, cuda_graph=use_graph)
+
     def to_device(hb):
         ids = hb.to(dev, non_blocking=True).long()
         return {"input_ids": ids, "labels": shift_labels(ids, frac)}
@@ -199,6 +299,16 @@ def main() -> None:
         torch.cuda.synchronize()
 
     loss_fn = model.per_example_loss
+    # set-up (untimed, not a training step): capture the microbatch graphs of every static size, and run the largest
+    # batch the sampler can plausibly draw once so the caching allocator reaches its peak before any timed step
+    setup_ids = data[:mb].to(dev).long()
+    engine.prepare_graphs(loss_fn, {"input_ids": setup_ids, "labels": shift_labels(setup_ids, frac)})
+    if sampling is None:
+        big = min(data_size, int(per_gpu + 4 * (per_gpu ** 0.5) + 1))
+        ids_big = data[:big].to(dev).long()
+        no_labels = torch.full_like(ids_big, -100)
+        engine.accumulate(loss_fn, {"input_ids": ids_big, "labels": no_labels})      # all labels ignored: adds zeros
+        del ids_big, no_labels
     for _ in range(args.warmup):
         engine.step(loss_fn, to_device(host_batch()), read_metrics=True)
     barrier()

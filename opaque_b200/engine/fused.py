@@ -377,7 +377,7 @@ class _LoRALinear(Function):
 
 
 def lora_linear(x, weight, bias, lora_a, lora_b, scaling: float):
-    if x.is_cuda and x.dtype == torch.bfloat16:
+    if x.is_cuda and x.dtype == torch.bfloat16 and ops.functional.kernels_enabled():
         return _LoRALinear.apply(x, weight, bias, lora_a, lora_b, scaling)
     y = torch.nn.functional.linear(x, weight, bias)
     return y + scaling * ((x @ lora_a.t()) @ lora_b.t())
@@ -539,6 +539,25 @@ class FusedDPEngine:
         per_example = per_example[:mb]
         out = {k: ({g: t[:mb] for g, t in v.items()} if isinstance(v, dict) else v[:mb]) for k, v in out.items()}
         return per_example, out
+
+    def prepare_graphs(self, loss_fn: Callable[..., torch.Tensor], example: dict[str, torch.Tensor]) -> int:
+        """Capture the microbatch graph of every static size up front (``example`` gives shapes and dtypes only).
+
+        The dummy rows carry ignored labels, so the passes add exactly zero to the gradient shard.  Without this the
+        first occurrence of each tail size pays an eager pass plus a capture in the middle of training.
+        """
+        if not self.cuda_graph or self.adaptive is not None or "labels" not in example:
+            return 0
+        done = 0
+        for size in sorted({max(self.microbatch_size >> k, 1) for k in range(4)}):
+            sub = {}
+            for k, v in example.items():
+                row = torch.full_like(v[:1], -100) if k == "labels" else torch.zeros_like(v[:1])
+                sub[k] = row.expand(size, *v.shape[1:]).contiguous()
+            for _ in range(2):                      # eager pass (one-time kernel set-up), then capture + first replay
+                self._graphed_microbatch(loss_fn, sub, size)
+            done += 1
+        return done
 
     def _adapt(self, res: StepResult) -> None:
         """Quantile-tracking threshold update from the cluster-wide number of clipped examples (one small reduction)."""

@@ -75,7 +75,7 @@ class GPT2Block(nn.Module):
     def forward(self, h):
         B, T, d = h.shape
         qkv = self.attn_c_attn(self.ln_1(h))
-        if qkv.is_cuda:
+        if qkv.is_cuda and ops.functional.kernels_enabled():
             q, k, v = _SplitHeads.apply(qkv, self.nh)
         else:                                    # plain views (also what runs under vmap in the reference engine)
             v5 = qkv.view(B, T, 3, self.nh, d // self.nh)

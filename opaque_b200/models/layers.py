@@ -117,7 +117,8 @@ class LayerNorm(nn.Module):
         self.eps = eps
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and self.weight.dtype == torch.bfloat16:
+        if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and self.weight.dtype == torch.bfloat16 \
+                and ops.functional.kernels_enabled():
             return ops.layer_norm(x, self.weight, self.bias, self.eps, layer=self)      # fused kernels, per-example dW/db
         if self.weight.requires_grad and fused.current_capture() is not None:
             return _LayerNormDP.apply(x, self.weight, self.bias, self.eps, self)

@@ -68,7 +68,7 @@ def grouped_linear(a: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, *, tran
     tcgen05 GEMM; elsewhere a loop over experts.
     """
     K = a.shape[1]
-    if a.is_cuda and a.dtype == torch.bfloat16 and w.is_contiguous() and a.shape[0] > 0 and K % 8 == 0 \
+    if ops.functional.kernels_enabled() and a.is_cuda and a.dtype == torch.bfloat16 and w.is_contiguous() and a.shape[0] > 0 and K % 8 == 0 \
             and (not transposed or K % 64 == 0) and w.shape[0] <= 256:
         goffs = torch.zeros(offs.numel() + 1, dtype=torch.int32, device=offs.device)
         goffs[1:] = offs

@@ -10,6 +10,8 @@ cross_entropy.py:585-681.
 """
 from __future__ import annotations
 
+import contextlib
+
 import torch
 from torch.autograd import Function
 
@@ -18,8 +20,29 @@ from . import lib
 _MODES = {"llama": 0, "gemma": 1, "none": 1}
 
 
+_PLAIN = 0      # > 0 inside ``plain_torch_ops()``: every op below takes its plain PyTorch path
+
+
+@contextlib.contextmanager
+def plain_torch_ops():
+    """Run the model with plain PyTorch ops only (no custom autograd nodes, no kernels of this library).
+
+    Needed under ``torch.func.vmap`` (the reference engine on a GPU) and used by the benchmark's restated-baseline arm.
+    """
+    global _PLAIN
+    _PLAIN += 1
+    try:
+        yield
+    finally:
+        _PLAIN -= 1
+
+
+def kernels_enabled() -> bool:
+    return _PLAIN == 0
+
+
 def _use_kernel(*ts: torch.Tensor) -> bool:
-    return all(t.is_cuda and t.dtype == torch.bfloat16 for t in ts)
+    return _PLAIN == 0 and all(t.is_cuda and t.dtype == torch.bfloat16 for t in ts)
 
 
 def _param_grad_hook():
@@ -208,7 +231,7 @@ class _Activation(Function):
 
 def activation(x, kind: str = "gelu_tanh"):
     """``silu`` / ``gelu`` / ``gelu_tanh`` / ``relu`` with a one-pass backward (the input is the only saved tensor)."""
-    if x.is_cuda and x.dtype == torch.bfloat16 and x.numel() % 8 == 0 and lib.available():
+    if _use_kernel(x) and x.numel() % 8 == 0 and lib.available():
         return _Activation.apply(x, _ACTS[kind])
     if kind == "silu":
         return torch.nn.functional.silu(x)
@@ -394,7 +417,7 @@ class _CrossEntropy(Function):
 def cross_entropy(logits, labels, *, ignore_index=-100, logit_softcapping=0.0, logit_scaling=0.0,
                   label_smoothing=0.0):
     """Per-token NLL (unreduced) with softcap / scaling / label smoothing; ignored tokens give 0."""
-    if logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32):
+    if _PLAIN == 0 and logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32):
         return _CrossEntropy.apply(logits, labels, ignore_index, logit_softcapping, logit_scaling, label_smoothing)
     return cross_entropy_ref(logits, labels, ignore_index=ignore_index, logit_softcapping=logit_softcapping,
                              logit_scaling=logit_scaling, label_smoothing=label_smoothing)

@@ -561,7 +561,9 @@ class DPTrainer:
                                     normalize_by=self.expected_batch, key=noise_key, step_config=cfg,
                                     microbatch_size=self._microbatch, mechanism=mech,
                                     clipping_mode="auto" if a.clipping_mode == "auto" else "clip",
-                                    gamma=float(a.clipping_kwargs.get("gamma", 0.01)), group_of=group_of, adaptive=adaptive)
+                                    gamma=float(a.clipping_kwargs.get("gamma", 0.01)), group_of=group_of, adaptive=adaptive,
+                                    cuda_graph=a.dp_cuda_graph)
+        self._graphs_ready = not a.dp_cuda_graph
 
     # ---- data -----------------------------------------------------------------------------------
     def get_train_dataloader(self):
@@ -607,7 +609,9 @@ class DPTrainer:
         while True:
             oom = False
             try:
-                (grads, aux), clip_state = self._grad_fn(self._trainable, payload, state=self._clip_state)
+                from ..ops.functional import plain_torch_ops
+                with plain_torch_ops():          # vmap needs plain PyTorch ops (no custom autograd nodes)
+                    (grads, aux), clip_state = self._grad_fn(self._trainable, payload, state=self._clip_state)
             except Exception as exc:      # noqa: BLE001 — only OOM is swallowed
                 if not _is_retryable_oom(exc):
                     raise
@@ -652,6 +656,9 @@ class DPTrainer:
 
     def _fused_step(self, batch, sp) -> dict[str, float]:
         self._call("on_pre_optimizer_step")
+        if not self._graphs_ready and batch["input_ids"].shape[0]:
+            self._fused.prepare_graphs(self.model.per_example_loss, {"input_ids": batch["input_ids"], "labels": batch["labels"]})
+            self._graphs_ready = True
         res = self._fused.step(self.model.per_example_loss, {"input_ids": batch["input_ids"], "labels": batch["labels"]})
         sp.mark("optimizer")
         self._call("on_optimizer_step")

@@ -176,6 +176,7 @@ class TrainingArguments:
     noise_calibration_kwargs: Any = dataclasses.field(default_factory=dict)
     enable_jit_checkpoint: bool = False
     dp_engine: str = "auto"
+    dp_cuda_graph: bool = False          # fused engine: replay each microbatch (forward, backward, clip GEMMs) as one CUDA graph
     _n_gpu: int = dataclasses.field(default=-1, repr=False)
 
     def __post_init__(self) -> None:

@@ -137,6 +137,81 @@ struct ShardStepParams {
   int decoupled_wd, skip_update;
 };
 
+__device__ __forceinline__ void ld8(const float* src, float* dst) {
+  *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+  *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(src + 4);
+}
+__device__ __forceinline__ void st8(float* dst, const float* src) {
+  *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+  *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(src + 4);
+}
+
+// Correlated-noise update for 8 consecutive coordinates with 32-byte vector accesses to the state buffers.
+// z: this step's raw N(0,1) draws; x: the correlated noise to add (row t of C^{-1} Z).
+__device__ __forceinline__ void ftrl_apply8(const ShardStepParams& p, long long base, const float* z, float* x) {
+  float* st = p.ftrl_state + base;
+  if (p.ftrl_mode == 1) {
+    // buffered-linear-Toeplitz C:  x = z - sum_b s_b S_b ;  S_b <- d_b S_b + x   (first four buffers stay in registers)
+    float keep[4][8], corr[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) corr[j] = 0.f;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      if (b < p.nbuf) {
+        float t[8];
+        ld8(st + b * p.n, t);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          corr[j] += p.coef[b] * t[j];
+          if (b < 4) keep[b][j] = t[j];
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = z[j] - corr[j];
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      if (b < p.nbuf) {
+        float t[8];
+        if (b < 4) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) t[j] = keep[b][j];
+        } else {
+          ld8(st + b * p.n, t);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = p.coef[p.nbuf + b] * t[j] + x[j];
+        st8(st + b * p.n, t);
+      }
+    }
+  } else {
+    // ring of the previous nbuf values: mode 2 keeps outputs (banded C, IIR), mode 3 keeps raw draws (FIR)
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = (p.ftrl_mode == 3) ? p.coef[0] * z[j] : 0.f;
+#pragma unroll
+    for (int b = 1; b <= 8; ++b) {
+      if (b <= p.nbuf) {
+        int slot = p.ring_head - b;
+        if (slot < 0) slot += p.nbuf;
+        float t[8];
+        ld8(st + slot * p.n, t);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += p.coef[b] * t[j];
+      }
+    }
+    if (p.ftrl_mode == 2) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = (z[j] - acc[j]) / p.coef[0];
+      st8(st + p.ring_head * p.n, x);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = acc[j];
+      st8(st + p.ring_head * p.n, z);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256)
 shard_step_kernel(const ShardStepParams p) {
   // each thread owns 8 consecutive coordinates (two Philox blocks, one 16-byte bf16 store per peer)
@@ -174,11 +249,14 @@ shard_step_kernel(const ShardStepParams p) {
       }
     }
     float out8[8];
+    float x8[8];
+    const bool vec_ftrl = full && p.ftrl_mode != 0 && ((p.n & 3) == 0);
+    if (vec_ftrl) ftrl_apply8(p, base, z, x8);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const long long k = base + j;
-      float x = z[j];
-      if (k < p.n) {
+      float x = vec_ftrl ? x8[j] : z[j];
+      if (k < p.n && !vec_ftrl) {
         if (p.ftrl_mode == 1) {
           // row t of C^{-1} Z for a buffered-linear-Toeplitz C:  x = z - sum_b s_b S_b ;  S_b <- d_b S_b + x
           float corr = 0.f;

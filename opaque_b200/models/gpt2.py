@@ -99,7 +99,10 @@ class GPT2LMHeadModel(nn.Module):
         pos = torch.arange(T, device=input_ids.device).expand(B, T)
         h = self.wte(input_ids) + self.wpe(pos)
         for blk in self.h:
-            h = blk(h)
+            if getattr(self, "activation_checkpointing", False) and torch.is_grad_enabled():
+                h = torch.utils.checkpoint.checkpoint(blk, h, use_reentrant=False)
+            else:
+                h = blk(h)
         return self.ln_f(h)
 
     def forward(self, input_ids):

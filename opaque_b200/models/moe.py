@@ -211,7 +211,10 @@ class MoEForCausalLM(nn.Module):
     def hidden_states(self, input_ids, position_ids=None):
         h = self.embed_tokens(input_ids)
         for layer in self.layers:
-            h = layer(h, self.rope_cos, self.rope_sin, position_ids)
+            if getattr(self, "activation_checkpointing", False) and torch.is_grad_enabled():
+                h = torch.utils.checkpoint.checkpoint(layer, h, self.rope_cos, self.rope_sin, position_ids, use_reentrant=False)
+            else:
+                h = layer(h, self.rope_cos, self.rope_sin, position_ids)
         return self.norm(h)
 
     def forward(self, input_ids, position_ids=None):

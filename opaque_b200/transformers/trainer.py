@@ -670,6 +670,21 @@ class DPTrainer:
                 "noise_std": self.noise_multiplier * self._fused.sensitivity() / self.expected_batch,
                 "clipping_norm": self._fused.sensitivity()}
 
+    _preempted = False
+
+    def _install_preemption_handler(self) -> None:
+        """``enable_jit_checkpoint``: on SIGTERM finish the current step, save ``checkpoint-N`` and leave the loop."""
+        if not self.args.enable_jit_checkpoint:
+            return
+        import signal
+        import threading
+        if threading.current_thread() is not threading.main_thread():
+            return
+
+        def on_term(signum, frame):
+            self._preempted = True
+        signal.signal(signal.SIGTERM, on_term)
+
     # ---- loop -------------------------------------------------------------------------------------
     def train(self, resume_from_checkpoint: str | bool | None = None, ignore_keys_for_eval=None):
         a = self.args
@@ -679,14 +694,29 @@ class DPTrainer:
             resume = ckpts[-1] if ckpts else None
         self._setup(resume or None)
         self.model.train()
+        if a.gradient_checkpointing:
+            if hasattr(self.model, "gradient_checkpointing_enable") and not hasattr(self.model, "activation_checkpointing"):
+                self.model.gradient_checkpointing_enable(**({"gradient_checkpointing_kwargs": a.gradient_checkpointing_kwargs}
+                                                            if a.gradient_checkpointing_kwargs else {}))
+            else:
+                self.model.activation_checkpointing = True       # framework models: per-block torch.utils.checkpoint
+        self._install_preemption_handler()
         self._call("on_train_begin")
         if a.eval_on_start and self.eval_dataset is not None:
             self.evaluate()
         t0 = time.perf_counter()
         window: list[dict[str, float]] = []
         for batch in self.get_train_dataloader():
-            metrics = self.training_step(batch)
+            if a.activation_offloading:          # saved activations live in pinned host memory between forward and backward
+                with torch.autograd.graph.save_on_cpu(pin_memory=torch.cuda.is_available()):
+                    metrics = self.training_step(batch)
+            else:
+                metrics = self.training_step(batch)
             window.append(metrics)
+            if self._preempted:                   # SIGTERM: write a just-in-time checkpoint between steps and stop
+                if a.output_dir:
+                    self._save_checkpoint(self.state.global_step)
+                break
             step = self.state.global_step
             self.state.epoch = step * self.sample_rate
             if a.logging_strategy == "steps" and (step % a.logging_steps == 0 or (a.logging_first_step and step == 1)):

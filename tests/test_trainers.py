@@ -8,7 +8,7 @@ import torch
 from torch import nn
 
 from opaque_b200.transformers import DPTrainer, TrainingArguments
-from opaque_b200.transformers.trainer import list_checkpoints
+from opaque_b200.transformers.trainer import TrainerCallback, list_checkpoints
 from opaque_b200.transformers.trl import DPOConfig, DPOTrainer, SFTConfig, SFTTrainer
 
 
@@ -134,3 +134,21 @@ def test_dpo_trainer_pairs(tmp_path):
     assert "ref_chosen_logps" in tr.train_dataset[0]
     out = tr.train()
     assert out["global_step"] == 3 and math.isfinite(tr.state.log_history[-2].get("loss", 0.0))
+
+
+def test_sigterm_writes_a_just_in_time_checkpoint_and_stops(tmp_path):
+    import signal
+
+    class Kill(TrainerCallback):
+        def on_step_end(self, args, state, control, **kw):
+            if state.global_step == 2:
+                os.kill(os.getpid(), signal.SIGTERM)
+    old = signal.getsignal(signal.SIGTERM)
+    try:
+        tr = DPTrainer(model=TinyLM(), args=_args(tmp_path, max_steps=6, save_steps=0, enable_jit_checkpoint=True),
+                       train_dataset=_data(), callbacks=[Kill()])
+        tr.train()
+    finally:
+        signal.signal(signal.SIGTERM, old)
+    assert tr.state.global_step == 2
+    assert [os.path.basename(c) for c in list_checkpoints(str(tmp_path))] == ["checkpoint-2"]

@@ -145,3 +145,39 @@ class PeerGroup:
         for b in self.buffers:
             b.close()
         self.buffers = []
+
+
+class PeerLeftError(RuntimeError):
+    """A rank announced that it leaves the job; raised on the others BEFORE they launch their next device barrier."""
+
+
+class Liveness:
+    """Host-side leave notices through the rendezvous key-value store.
+
+    A rank that stops (preemption, an exception it handles, end of its data) calls :meth:`announce_leave` between
+    steps, after its last kernel has completed; every other rank calls :meth:`check` before a step and gets a
+    :class:`PeerLeftError` instead of waiting for that rank's flag on the device until the bounded wait runs out.
+    Only ``set`` / ``check`` on the store are used, so a rank that vanished without a notice costs nothing here — it is
+    caught by the bounded device wait (``DeviceWaitTimeout``) or the process-group timeout instead.
+    """
+
+    def __init__(self, rank: int, world: int, store=None, prefix: str = "opaque_b200/left"):
+        if store is None:
+            from torch.distributed.distributed_c10d import _get_default_store
+            store = _get_default_store()
+        self.store, self.rank, self.world, self.prefix = store, rank, world, prefix
+
+    def _key(self, rank: int) -> str:
+        return f"{self.prefix}/{rank}"
+
+    def announce_leave(self, reason: str = "") -> None:
+        self.store.set(self._key(self.rank), reason or "left")
+
+    def left(self) -> list[int]:
+        return [r for r in range(self.world) if r != self.rank and self.store.check([self._key(r)])]
+
+    def check(self) -> None:
+        gone = self.left()
+        if gone:
+            why = {r: self.store.get(self._key(r)).decode(errors="replace") for r in gone}
+            raise PeerLeftError(f"rank(s) {gone} left the job: {why}")

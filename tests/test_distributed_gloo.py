@@ -211,3 +211,16 @@ def test_missing_peer_is_detected_by_timeout():
     res = run_ranks("w_peer_never_joins", timeout_s=5)
     assert res[1] == ("ok", "left")
     assert res[0][0] == "ok" and res[0][1].startswith("detected"), res
+
+
+def test_leave_notice_is_seen_on_the_host_before_the_next_step():
+    """A rank that leaves between steps announces it through the store; the others raise before launching anything."""
+    import torch.distributed as dist
+    from opaque_b200.parallel.peer import Liveness, PeerLeftError
+    store = dist.HashStore()
+    a, b, c = (Liveness(r, 3, store=store) for r in range(3))
+    a.check(), b.check(), c.check()
+    b.announce_leave("preempted")
+    with pytest.raises(PeerLeftError, match="preempted"):
+        a.check()
+    assert c.left() == [1] and b.left() == []

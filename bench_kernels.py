@@ -2,6 +2,7 @@
 
   python bench_kernels.py                      # every case at its benchmark size
   python bench_kernels.py --case wgrad --small # one small launch set, sized for an ncu capture
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 bench_kernels.py --case wgrad-rs
 
 Each line is JSON: achieved TFLOP/s or GB/s and the fraction "of measured" peak, where the peaks come from
 MEASURED_PEAKS.json next to this file (cuBLAS bf16 burst and a STREAM-style copy), else the documented fallback
@@ -41,11 +42,74 @@ def timeit(fn, iters=20, warm=5, flush=None):
     return total / iters
 
 
+def fused_reduce_scatter_case():
+    """Clip-weighted weight gradient with its reduce-scatter fused in, on W ranks (launch with torch.distributed.run).
+
+    Every rank multiplies its own microbatch and reduces the fp32 tiles straight into the owners' shards through peer
+    pointers.  Roofline per rank = max(FLOPs / measured GEMM peak, bytes leaving over NVLink / 770 GB/s measured peer
+    copy rate); device-timed, max over ranks.  Compared with the same product followed by an NCCL reduce-scatter.
+    """
+    import torch.distributed as dist
+    from opaque_b200 import ops
+    from opaque_b200.parallel.peer import PeerGroup
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
+    torch.cuda.set_device(dev)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=dev)
+    tf_peak, _, tag = peaks()
+    group = PeerGroup(dev)
+    st = group.status
+    flush = torch.zeros(64 * 1024 * 1024, device=dev)
+    for T, M, N in [(16384, 3072, 768), (16384, 4096, 4096), (16384, 8192, 2048)]:
+        a = torch.randn(T, M, device=dev).bfloat16()
+        b = torch.randn(T, N, device=dev).bfloat16()
+        c = torch.rand(T // 1024, device=dev)
+        total = M * N
+        shard = (total + world * 64 - 1) // (world * 64) * 64
+        buf = group.buffer(shard, torch.float32)
+        local = torch.zeros(shard * world, device=dev)
+
+        def fused():
+            ops.wgrad_clip_per_example(a, b, None, ex_scale=c, rows_per_example=1024, ldm=N, peer_table=buf.table,
+                                       shard_elems=shard, status=st)
+
+        def unfused():
+            ops.wgrad_clip_per_example(a, b, local, ex_scale=c, rows_per_example=1024, ldm=N, status=st)   # same split-K, local destination
+            dist.reduce_scatter_tensor(buf.local, local)
+        rows = {}
+        for name, fn in (("fused (peer red.add in the epilogue)", fused), ("same kernel + NCCL reduce-scatter", unfused)):
+            dist.barrier()
+            ms = timeit(fn, 10, 3, flush)
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            rows[name] = float(t)
+        group.barrier()
+        torch.cuda.synchronize()
+        if rank == 0:
+            flops = 2.0 * T * M * N
+            t_compute = flops / (tf_peak * 1e9)                      # ms
+            t_link = total * 4 * (world - 1) / world / 770e6         # ms at 770 GB/s per direction
+            roof = max(t_compute, t_link)
+            for name, ms in rows.items():
+                print(json.dumps({"kernel": f"wgrad_clip -> reduce-scatter {T}x{M}x{N} on {world} GPUs, {name}", "ms": round(ms, 4),
+                                  "tflops_per_gpu": round(flops / ms / 1e9, 1), "roofline_ms": round(roof, 4),
+                                  "bound": "compute" if t_compute >= t_link else "nvlink",
+                                  "frac_of_roofline_" + tag.replace(" ", "_"): round(roof / ms, 3)}), flush=True)
+    if st.read():
+        raise SystemExit(f"a device wait timed out (status {st.read()})")
+    dist.barrier()
+    group.close()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default="all")
     ap.add_argument("--small", action="store_true", help="one or two launches of a small case (for ncu)")
     args = ap.parse_args()
+    if args.case == "wgrad-rs":
+        return fused_reduce_scatter_case()
     from opaque_b200 import ops
     from opaque_b200.ops.functional import cross_entropy_fused_
     dev = torch.device("cuda", 0)

@@ -284,6 +284,11 @@ def gemm_ref(a, b, *, b_layout="nk", a2=None, b2=None, bias=None, group_offs=Non
     return y
 
 
+def ghost_set_wide(enabled: bool) -> bool:
+    """Choose 128x256 (default) or 128x128 Gram blocks for :func:`ghost_norm`; returns the previous setting."""
+    return bool(lib.load().ob_ghost_set_wide(int(bool(enabled))))
+
+
 def ghost_norm_ref(a, g, tokens_per_example, *, ids=None):
     B = g.shape[0] // tokens_per_example
     gg = g.float().view(B, tokens_per_example, -1)
@@ -372,7 +377,7 @@ from .functional import (activation, cross_entropy, cross_entropy_ref, fused_add
                          layer_norm, plain_torch_ops, rms_norm, rms_norm_ref, rope_qk, rope_qk_ref, rope_tables, rows_group_sum_, swiglu)
 
 __all__ = [
-    "gemm", "gemm_ref", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_",
+    "gemm", "gemm_ref", "ghost_set_wide", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_",
     "DeviceWaitTimeout", "KernelLibraryError", "StatusWord", "clip_weighted_sum", "cross_entropy",
     "cross_entropy_ref", "embedding_wgrad", "fused_add_rms_norm", "geglu", "ghost_norm", "ghost_norm_ref", "glu_ref",
     "philox_normal_add_", "pick_block_n", "pick_splits", "rms_norm", "rms_norm_ref", "rope_qk", "rope_qk_ref",

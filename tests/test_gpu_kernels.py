@@ -159,16 +159,45 @@ def test_tensor_map_kernels_work_from_a_fresh_thread(dev):
     assert rel(got, ops.ghost_norm_ref(a, g, 128)) < 1e-3
 
 
-@pytest.mark.parametrize("B,T,Da,Dg", [(2, 128, 64, 64), (3, 256, 192, 320), (4, 512, 768, 3072), (2, 200, 800, 72)])
-def test_ghost_norm_matches_gram_and_direct(dev, B, T, Da, Dg):
+@pytest.mark.parametrize("wide", [True, False])
+@pytest.mark.parametrize("B,T,Da,Dg", [(2, 128, 64, 64), (3, 256, 192, 320), (4, 512, 768, 3072), (2, 200, 800, 72), (3, 384, 128, 136),
+                                       (2, 1024, 256, 512), (5, 129, 64, 200)])
+def test_ghost_norm_matches_gram_and_direct(dev, B, T, Da, Dg, wide):
     from opaque_b200 import ops
     st = ops.StatusWord(dev)
     a = torch.randn(B * T, Da, device=dev).bfloat16()
     g = torch.randn(B * T, Dg, device=dev).bfloat16()
     n2 = torch.zeros(B, device=dev)
-    ops.ghost_norm(a, g, n2, T, status=st)
+    old = ops.ghost_set_wide(wide)
+    try:
+        ops.ghost_norm(a, g, n2, T, status=st)
+    finally:
+        ops.ghost_set_wide(old)
     direct = torch.stack([(a[i * T:(i + 1) * T].float().t() @ g[i * T:(i + 1) * T].float()).pow(2).sum() for i in range(B)])
     assert st.read() == 0 and rel(n2, ops.ghost_norm_ref(a, g, T)) < 2e-5 and rel(n2, direct) < 5e-5
+
+
+def test_ghost_norm_ragged_segments_both_tile_shapes(dev):
+    from opaque_b200 import ops
+    torch.manual_seed(9)
+    lens = [5, 300, 0, 129, 256, 77]
+    offs = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32, device=dev)
+    rows = sum(lens)
+    a = torch.randn(rows, 96, device=dev).bfloat16()
+    g = torch.randn(rows, 160, device=dev).bfloat16()
+    seg_out = torch.tensor([0, 1, 2, 0, 1, 2], dtype=torch.int32, device=dev)
+    want = torch.zeros(3, device=dev)
+    for i, (lo, n) in enumerate(zip(offs.tolist(), lens)):
+        if n:
+            want[i % 3] += (a[lo:lo + n].float().t() @ g[lo:lo + n].float()).pow(2).sum()
+    for wide in (True, False):
+        got = torch.zeros(3, device=dev)
+        old = ops.ghost_set_wide(wide)
+        try:
+            ops.ghost_norm(a, g, got, 300, seg_offsets=offs, seg_out=seg_out)
+        finally:
+            ops.ghost_set_wide(old)
+        assert rel(got, want) < 5e-5, wide
 
 
 def test_ghost_norm_embedding_ids(dev):

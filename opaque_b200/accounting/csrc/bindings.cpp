@@ -76,6 +76,10 @@ PYBIND11_MODULE(_native, m) {
     py::gil_scoped_release r; return gaussian_pld(eff, c); });
   m.def("balls_in_bins_mc_pld", [](std::vector<double> gram, std::size_t n, std::size_t bins, double nm, const Config& c) {
     py::gil_scoped_release r; return balls_in_bins_mc_pld(gram, n, bins, nm, c); });
+  m.def("b_min_sep_mc_pld", [](std::vector<double> coef, std::size_t n, std::size_t b, double p, double nm, bool warm, const Config& c) {
+    py::gil_scoped_release r; return b_min_sep_mc_pld(coef, n, b, p, nm, warm, c); },
+    py::arg("coef"), py::arg("n_steps"), py::arg("min_sep"), py::arg("sampling_prob"), py::arg("noise_multiplier"),
+    py::arg("warm_start"), py::arg("config"));
   m.def("adaclip_effective_noise_multiplier", &adaclip_effective_noise_multiplier);
 
   m.def("minsep_true_max_participations", [](std::int64_t n, std::int64_t ms, py::object mp) {

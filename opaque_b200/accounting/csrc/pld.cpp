@@ -1091,6 +1091,103 @@ Pld balls_in_bins_mc_pld(const std::vector<double>& gram, std::size_t n, std::si
   return out;
 }
 
+// Monte-Carlo PLD of a banded matrix mechanism under b-min-sep participation (Dong & Ganesh, "Privacy amplification
+// for BandMF via b-min-sep subsampling"): a record that is free takes part in a step with probability p and is then
+// barred for the next b - 1 steps.  With a strategy whose columns have at most b non-zeros (c_0..c_{L-1}, L <= b) the
+// columns of two participations never overlap, so the likelihood ratio of an output y against the null factorises and
+// obeys the backward recursion
+//     f_n = 1,   f_i = (1 - p) f_{i+1} + p exp((<c, y_{i:i+L}> - |c_{:n-i}|^2 / 2) / sigma^2) f_{min(i+b, n)}
+// with P(y)/Q(y) = f_0 for a cold start (every record free at step 0).  With a warm start (the chain of
+// free / barred states started in its stationary law) P/Q = (f_0 + p (f_1 + ... + f_{b-1})) / (1 + (b-1) p).
+// Losses ln(P/Q) under P (remove) and -ln(P/Q) under Q (add) are sampled and rounded UP onto the grid.
+Pld b_min_sep_mc_pld(const std::vector<double>& coef, std::size_t n, std::size_t b, double p, double nm, bool warm_start,
+                     const Config& cfg) {
+  check_nm(nm);
+  require(!coef.empty() && n >= 1 && b >= 1 && p > 0.0 && p <= 1.0, "b-min-sep: need coefficients, n >= 1, b >= 1, p in (0, 1]");
+  require(coef.size() <= b, "b-min-sep: the strategy's band count must not exceed the minimum separation");
+  const std::size_t L = coef.size();
+  const double sigma = nm, sigma2 = nm * nm;
+  const std::size_t S = cfg.num_mc_samples;
+  std::vector<double> losses_remove(S), losses_add(S);
+  // |c_{:m}|^2 for a column cut off by the end of the run
+  std::vector<double> cum(L + 1, 0.0);
+  for (std::size_t k = 0; k < L; ++k) cum[k + 1] = cum[k] + coef[k] * coef[k];
+  const double denom = 1.0 + static_cast<double>(b - 1) * p;
+
+  auto log_ratio = [&](const std::vector<double>& y, std::vector<double>& f) {
+    // work with f_i scaled by a running maximum to stay finite over long runs: keep log-scale per index
+    // (values can span hundreds of orders of magnitude); f holds log f_i
+    f[n] = 0.0;
+    for (std::size_t ii = n; ii-- > 0;) {
+      const std::size_t m = std::min(L, n - ii);
+      double dot = 0.0;
+      for (std::size_t k = 0; k < m; ++k) dot += coef[k] * y[ii + k];
+      const double blk = (dot - 0.5 * cum[m]) / sigma2;
+      const double skip = f[std::min(ii + b, n)];
+      const double a = (p < 1.0) ? std::log1p(-p) + f[ii + 1] : -std::numeric_limits<double>::infinity();
+      const double c2 = std::log(p) + blk + skip;
+      const double hi = std::max(a, c2);
+      f[ii] = hi + std::log(std::exp(a - hi) + std::exp(c2 - hi));
+    }
+    if (!warm_start || b == 1) return f[0];
+    double hi = f[0];
+    for (std::size_t j = 1; j < std::min(b, n + 1); ++j) hi = std::max(hi, std::log(p) + f[j]);
+    double acc = std::exp(f[0] - hi);
+    for (std::size_t j = 1; j < b; ++j) acc += std::exp(std::log(p) + f[std::min(j, n)] - hi);
+    return hi + std::log(acc) - std::log(denom);
+  };
+
+#pragma omp parallel
+  {
+    std::vector<double> y(n), x(n), f(n + 1);
+    std::normal_distribution<double> nd(0.0, 1.0);
+    std::uniform_real_distribution<double> ud(0.0, 1.0);
+#pragma omp for schedule(static)
+    for (std::int64_t s = 0; s < static_cast<std::int64_t>(S); ++s) {
+      std::mt19937_64 rng(cfg.seed + 0x9E3779B97F4A7C15ULL * static_cast<std::uint64_t>(s + 1));
+      // P branch: participation pattern of one record, y = C x + sigma z
+      std::size_t barred = 0;
+      if (warm_start && b > 1 && ud(rng) * denom >= 1.0)
+        barred = 1 + static_cast<std::size_t>(ud(rng) * static_cast<double>(b - 1)) % (b - 1);
+      for (std::size_t i = 0; i < n; ++i) {
+        const bool take = barred == 0 && ud(rng) < p;
+        x[i] = take ? 1.0 : 0.0;
+        barred = take ? b - 1 : (barred > 0 ? barred - 1 : 0);
+      }
+      for (std::size_t i = 0; i < n; ++i) {
+        double acc = sigma * nd(rng);
+        for (std::size_t k = 0; k < L && k <= i; ++k) acc += coef[k] * x[i - k];
+        y[i] = acc;
+      }
+      losses_remove[static_cast<std::size_t>(s)] = log_ratio(y, f);
+      // Q branch: y = sigma z
+      for (std::size_t i = 0; i < n; ++i) y[i] = sigma * nd(rng);
+      losses_add[static_cast<std::size_t>(s)] = -log_ratio(y, f);
+    }
+  }
+  auto to_pmf = [&](const std::vector<double>& v) {
+    Pmf q;
+    q.discretization = cfg.discretization;
+    q.max_grid_size = cfg.max_grid_size;
+    std::int64_t lo = std::numeric_limits<std::int64_t>::max(), hi = std::numeric_limits<std::int64_t>::min();
+    std::vector<std::int64_t> idx(v.size());
+    for (std::size_t i = 0; i < v.size(); ++i) {
+      idx[i] = static_cast<std::int64_t>(std::ceil(v[i] / cfg.discretization));
+      lo = std::min(lo, idx[i]);
+      hi = std::max(hi, idx[i]);
+    }
+    q.lower = lo;
+    q.probs.assign(static_cast<std::size_t>(hi - lo + 1), 0.0);
+    const double w = 1.0 / static_cast<double>(v.size());
+    for (auto i : idx) q.probs[static_cast<std::size_t>(i - lo)] += w;
+    return q.maybe_coarsen();
+  };
+  Pld out;
+  out.remove = to_pmf(losses_remove);
+  out.add = to_pmf(losses_add);
+  return out;
+}
+
 double adaclip_effective_noise_multiplier(double z, double fraction_noise_std, double expected_batch, int groups) {
   require(z > 0.0 && fraction_noise_std > 0.0 && expected_batch > 0.0 && groups >= 1, "adaclip: bad parameters");
   const double sigma_b = expected_batch * fraction_noise_std;

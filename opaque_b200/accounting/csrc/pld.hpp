@@ -95,6 +95,8 @@ Pld parallel_poisson_gaussian_pld(double noise_multiplier, double rate, std::siz
 Pld mixture_gaussian_pld(double sigma, const std::vector<double>& log_probs, const std::vector<double>& sens,
                          double head_mass, double tail_mass, const Config& cfg);
 Pld random_allocation_gaussian_pld(double noise_multiplier, std::size_t num_bins, std::size_t k, const Config& cfg);
+Pld b_min_sep_mc_pld(const std::vector<double>& coef, std::size_t n, std::size_t b, double p, double noise_multiplier,
+                     bool warm_start, const Config& cfg);
 Pld balls_in_bins_mc_pld(const std::vector<double>& gram_row_major, std::size_t n, std::size_t num_bins,
                          double noise_multiplier, const Config& cfg);
 

@@ -147,10 +147,44 @@ def balls_in_bins(inner: MfGaussian, *, num_bins: int, n_steps: int) -> BallsInB
     return BallsInBins(inner, int(num_bins), int(n_steps))
 
 
-def b_min_sep(inner: MfGaussian, *, bands: int, n_steps: int, max_participations: int | None = None) -> MfGaussian:
-    """b-min-sep participation as a sensitivity constraint on the un-amplified mechanism."""
+@dataclasses.dataclass(frozen=True)
+class BMinSep(DpHorizonProcess):
+    """Banded MF under b-min-sep subsampling: a free record joins a step with probability ``sampling_prob`` and is
+    then barred for ``bands − 1`` steps.  Monte-Carlo PLD from the backward likelihood-ratio recursion (valid when the
+    strategy has at most ``bands`` non-zero coefficients, so the columns of two participations never overlap)."""
+    inner: MfGaussian
+    bands: int
+    n_steps: int
+    sampling_prob: float
+    warm_start: bool = False
+
+    def __post_init__(self):
+        if self.bands < 1 or not 0 < self.sampling_prob <= 1:
+            raise ValueError("need bands >= 1 and sampling_prob in (0, 1]")
+
+    def pld_at(self, n_steps: int, config: DiscretizationConfig | None = None):
+        cfg = config or get_discretization()
+        coef = np.trim_zeros(np.asarray(self.inner.strategy.coefficients(n_steps), float), "b")
+        if len(coef) > self.bands:
+            raise ValueError(f"the strategy has {len(coef)} bands but the minimum separation is {self.bands}")
+        return native.b_min_sep_mc_pld(coef.tolist(), n_steps, self.bands, self.sampling_prob, self.inner.noise_multiplier,
+                                       self.warm_start, cfg.to_native())
+
+    def _build_pld(self, config):
+        return self.pld_at(self.n_steps, config)
+
+
+_strategy_process_codec(BMinSep)
+
+
+def b_min_sep(inner: MfGaussian, *, bands: int, n_steps: int, max_participations: int | None = None,
+              sampling_prob: float | None = None, warm_start: bool = False):
+    """b-min-sep participation.  With ``sampling_prob`` the amplified Monte-Carlo accountant is used; without it the
+    scheme is only a sensitivity constraint on the un-amplified mechanism (an upper bound for any sampling rate)."""
+    if sampling_prob is not None:
+        return BMinSep(inner, int(bands), int(n_steps), float(sampling_prob), bool(warm_start))
     return dataclasses.replace(inner, n_steps=int(n_steps), min_sep=int(bands), max_participations=max_participations)
 
 
-__all__ = ["BallsInBins", "CyclicPoisson", "MfGaussian", "b_min_sep", "balls_in_bins", "mf_gaussian", "per_step",
+__all__ = ["BMinSep", "BallsInBins", "CyclicPoisson", "MfGaussian", "b_min_sep", "balls_in_bins", "mf_gaussian", "per_step",
            "poisson"]

@@ -418,6 +418,11 @@ class DPTrainer:
         inner = ftrl_acc.mf_gaussian(nm, strat, n_steps=steps, min_sep=ms, max_participations=mp)
         if a.sampling_mode in ("cyclic_poisson",):
             return ftrl_acc.per_step(ftrl_acc.poisson(inner, q, n_steps=steps))
+        if a.sampling_mode == "b_min_sep" and a.sampling_kwargs.get("amplified", False):
+            n_coef = len(np.trim_zeros(np.asarray(strat.coefficients(steps), float), "b"))
+            if n_coef <= sampler.bands:          # Monte-Carlo accountant for the subsampled banded mechanism
+                return ftrl_acc.per_step(ftrl_acc.b_min_sep(ftrl_acc.mf_gaussian(nm, strat, n_steps=steps), bands=sampler.bands,
+                                                           n_steps=steps, sampling_prob=sampler.sampling_prob))
         if a.sampling_mode == "poisson" and a.privacy_noise_mechanism == "mf_identity":
             return sgd_acc.poisson(sgd_acc.gaussian(nm), q)
         return ftrl_acc.per_step(inner)

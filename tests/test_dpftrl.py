@@ -125,3 +125,26 @@ def test_samplers_participation_patterns_and_resume():
     expect = next(it)
     s2 = from_state_dict(CyclicPoissonSampler(range(400), 0.3, bands=2, n_steps=10, key=key(7)), sd)
     assert next(iter(s2)) == expect
+
+
+def test_b_min_sep_monte_carlo_accountant():
+    """Amplified accounting for banded MF under b-min-sep subsampling: limits and monotonicity."""
+    import math
+    from opaque_b200.accounting.core import DiscretizationConfig, native
+    cfg = DiscretizationConfig().to_native()
+    # one band, no separation, always sampled: n-fold Gaussian composition = Gaussian with sensitivity sqrt(n)
+    mc = native.b_min_sep_mc_pld([1.0], 16, 1, 1.0, 4.0, False, cfg).epsilon_at(1e-4)
+    exact = native.gaussian_pld(4.0 / math.sqrt(16), cfg).epsilon_at(1e-4)
+    assert abs(mc - exact) < 0.08 * exact
+    s = band_mf_strategy(bands=4)
+    eps = [fa.b_min_sep(fa.mf_gaussian(2.0, s, n_steps=64), bands=4, n_steps=64, sampling_prob=p).epsilon_at(1e-4) for p in (1.0, 0.3, 0.05)]
+    assert eps[0] > eps[1] > eps[2] > 0
+    bound = fa.b_min_sep(fa.mf_gaussian(2.0, s, n_steps=64), bands=4, n_steps=64).epsilon_at(1e-4)       # sensitivity-only bound
+    assert eps[1] < bound and abs(eps[0] - bound) < 0.1 * bound
+    with pytest.raises(ValueError):
+        fa.b_min_sep(fa.mf_gaussian(2.0, band_mf_strategy(bands=8), n_steps=64), bands=4, n_steps=64, sampling_prob=0.1).epsilon_at(1e-4)
+    proc = fa.b_min_sep(fa.mf_gaussian(2.0, s, n_steps=64), bands=4, n_steps=64, sampling_prob=0.3, warm_start=True)
+    a = acc.Accountant()
+    a |= proc
+    restored = from_state_dict(acc.Accountant(), state_dict(a))
+    assert math.isclose(restored.epsilon_at(1e-4), a.epsilon_at(1e-4), rel_tol=1e-12)

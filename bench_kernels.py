@@ -180,11 +180,12 @@ def main():
             n2 = torch.zeros(B, device=dev)
             nt = (T + 127) // 128
             fl = 2.0 * B * (nt * (nt + 1) / 2) * 128 * 128 * (Da + Dg)
+            ops.ghost_set_wide(2)
             emit(f"ghost_norm 128x256 blocks {B}x{T}x{Da}x{Dg}", timeit(lambda: ops.ghost_norm(a, g, n2, T, status=st), iters, warm, flush), fl)
             if not args.small:
-                ops.ghost_set_wide(False)
+                ops.ghost_set_wide(0)
                 emit(f"ghost_norm 128x128 blocks {B}x{T}x{Da}x{Dg}", timeit(lambda: ops.ghost_norm(a, g, n2, T, status=st), iters, warm, flush), fl)
-                ops.ghost_set_wide(True)
+            ops.ghost_set_wide(1)
     if want("lora"):
         E, T, M, r = (4, 1024, 4096, 16) if args.small else (16, 1024, 4096, 16)
         a = torch.randn(E * T, M, device=dev).bfloat16()

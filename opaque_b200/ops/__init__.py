@@ -284,9 +284,10 @@ def gemm_ref(a, b, *, b_layout="nk", a2=None, b2=None, bias=None, group_offs=Non
     return y
 
 
-def ghost_set_wide(enabled: bool) -> bool:
-    """Choose 128x256 (default) or 128x128 Gram blocks for :func:`ghost_norm`; returns the previous setting."""
-    return bool(lib.load().ob_ghost_set_wide(int(bool(enabled))))
+def ghost_set_wide(mode: int | bool) -> int:
+    """Gram block shape of :func:`ghost_norm`: 1 = 128x256 blocks for examples of >= 1024 rows (default), 2 = 128x256
+    whenever an example spans two row blocks, 0 = always 128x128.  Returns the previous setting."""
+    return int(lib.load().ob_ghost_set_wide(int(mode)))
 
 
 def ghost_norm_ref(a, g, tokens_per_example, *, ids=None):

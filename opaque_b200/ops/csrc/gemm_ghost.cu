@@ -457,7 +457,8 @@ ghost_norm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 
 }  // namespace ob
 
-// 1: 128 x 256 Gram blocks when an example spans at least two row blocks (default); 0: always 128 x 128 blocks
+// 1 (default): 128 x 256 Gram blocks for examples of >= 1024 rows; 2: whenever an example spans two row blocks;
+// 0: always 128 x 128 blocks
 static int wide_enabled = 1;
 extern "C" int ob_ghost_set_wide(int enabled) {
   const int old = wide_enabled;
@@ -496,7 +497,9 @@ extern "C" int ob_ghost_norm(const void* a, const void* g, const int* ids, int B
   p.status = status;
   p.wait_budget_ns = static_cast<unsigned long long>(wait_budget_s * 1e9);
   const int nt = (T + GH_TILE - 1) / GH_TILE;
-  if (nt >= 2 && wide_enabled) {
+  // measured: the wide blocks win from about 1024 rows per example (less wasted work below the diagonal); below that
+  // the 128 x 128 blocks with double-buffered accumulators are as fast or faster
+  if (wide_enabled == 2 ? nt >= 2 : (wide_enabled == 1 && nt >= 8)) {
     static bool configured_wide = false;
     if (!configured_wide) {
       if (cudaFuncSetAttribute(ghost_norm_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GW_SMEM) != cudaSuccess)

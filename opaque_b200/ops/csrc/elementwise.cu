@@ -293,13 +293,48 @@ cross_entropy_kernel(T* __restrict__ logits, const long long* __restrict__ label
       nll[row] = 0.f;
       if (lse_out) lse_out[row] = 0.f;
     }
-    if (write_grad)
-      for (int i = threadIdx.x; i < V; i += CE_THREADS) z[i] = static_cast<T>(0.f);
+    if (write_grad) {
+      int done = 0;
+      if constexpr (sizeof(T) == 2) {
+        if ((ld & 7) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+          done = V & ~7;
+          const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+          for (int i = threadIdx.x; i < (done >> 3); i += CE_THREADS) reinterpret_cast<uint4*>(z)[i] = zero;
+        }
+      }
+      for (int i = done + threadIdx.x; i < V; i += CE_THREADS) z[i] = static_cast<T>(0.f);
+    }
     return;
   }
   // pass 1: online max / sum-exp (+ plain sum for label smoothing)
   float m = -INFINITY, s = 0.f, tot = 0.f;
-  for (int i = threadIdx.x; i < V; i += CE_THREADS) {
+  // bf16 rows with 16-byte aligned starts are read 8 values at a time; the ragged tail (V % 8) and fp32 rows go
+  // through the scalar loop
+  int v_vec = 0;
+  if constexpr (sizeof(T) == 2) {
+    if ((ld & 7) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) v_vec = V & ~7;
+  }
+  if constexpr (sizeof(T) == 2) {
+    const bf16x8* zv = reinterpret_cast<const bf16x8*>(z);
+    for (int i = threadIdx.x; i < (v_vec >> 3); i += CE_THREADS) {
+      float f[8];
+      unpack8(zv[i], f);
+      float lm = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        f[j] = ce_transform(f[j], scale, softcap);
+        tot += f[j];
+        lm = fmaxf(lm, f[j]);
+      }
+      if (lm > m) {
+        s *= __expf(m - lm);
+        m = lm;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += __expf(f[j] - m);
+    }
+  }
+  for (int i = v_vec + threadIdx.x; i < V; i += CE_THREADS) {
     const float v = ce_transform(static_cast<float>(z[i]), scale, softcap);
     tot += v;
     if (v > m) {
@@ -325,7 +360,28 @@ cross_entropy_kernel(T* __restrict__ logits, const long long* __restrict__ label
   }
   if (!write_grad) return;
   const float wgt = row_weight ? row_weight[row] : 1.f;
-  for (int i = threadIdx.x; i < V; i += CE_THREADS) {
+  if constexpr (sizeof(T) == 2) {
+    bf16x8* zv = reinterpret_cast<bf16x8*>(z);
+    for (int i = threadIdx.x; i < (v_vec >> 3); i += CE_THREADS) {
+      float f[8];
+      unpack8(zv[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float raw = f[j] * scale;
+        float v = raw, dz = 1.f;
+        if (softcap != 0.f) {
+          const float t = tanhf(raw / softcap);
+          v = softcap * t;
+          dz = 1.f - t * t;
+        }
+        float g = __expf(v - lse) - smoothing / V;
+        if (i * 8 + j == label) g -= (1.f - smoothing);
+        f[j] = wgt * g * dz * scale;
+      }
+      zv[i] = pack8(f);
+    }
+  }
+  for (int i = v_vec + threadIdx.x; i < V; i += CE_THREADS) {
     const float raw = static_cast<float>(z[i]) * scale;
     float v = raw, dz = 1.f;
     if (softcap != 0.f) {

@@ -127,6 +127,7 @@ layernorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat1
 // Per-example reductions over the token rows of each example: out[e, col] += sum_r f(r, col).
 //   mode 0: f = g                      (bias gradients: LayerNorm bias, linear bias)
 //   mode 1: f = g * (x - mean) * rstd  (LayerNorm weight gradient)
+//   mode 2: f = g * x * rstd           (RMSNorm weight gradient)
 // grid = (examples, column blocks of 256, row splits).  A 256-thread block reads 8 rows x 256 columns per iteration
 // with 16-byte loads (32 column groups x 8 row lanes), folds the row lanes through shared memory and adds the split's
 // partial sums into that example's row of the fp32 per-example gradient buffer with atomics.
@@ -148,10 +149,10 @@ rows_group_sum_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* 
     for (int r = r0 + rl; r < r1; r += 8) {
       float gv[8];
       ln_unpack8(*reinterpret_cast<const ln_bf16x8*>(g + static_cast<long long>(r) * ldg + col), gv);
-      if (mode == 1) {
+      if (mode != 0) {
         float xv[8];
         ln_unpack8(*reinterpret_cast<const ln_bf16x8*>(x + static_cast<long long>(r) * ldg + col), xv);
-        const float mu = __ldg(mean + r), rs = __ldg(rstd + r);
+        const float mu = (mode == 1) ? __ldg(mean + r) : 0.f, rs = __ldg(rstd + r);
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] += gv[j] * (xv[j] - mu) * rs;
       } else {
@@ -244,7 +245,8 @@ extern "C" int ob_rows_group_sum(const void* g, const void* x, const float* mean
   if (num_examples <= 0 || rows_per_example <= 0 || N <= 0) return 0;
   if ((N & 7) || (ldg & 7) || (reinterpret_cast<uintptr_t>(g) & 15) || (x != nullptr && (reinterpret_cast<uintptr_t>(x) & 15)))
     return -2;
-  if (mode == 1 && (x == nullptr || mean == nullptr || rstd == nullptr)) return -3;
+  if ((mode == 1 && (x == nullptr || mean == nullptr || rstd == nullptr)) || (mode == 2 && (x == nullptr || rstd == nullptr)))
+    return -3;
   int splits = rows_per_example / 64;
   splits = splits < 1 ? 1 : (splits > 16 ? 16 : splits);
   dim3 grid(num_examples, (N + 255) / 256, splits);

@@ -111,11 +111,14 @@ class _RMSNorm(Function):
         elif weight.requires_grad:
             n_ex, rows_per = 1, rows
             dw_pe = torch.empty(1, H, dtype=torch.float32, device=xs.device)
+        direct_pe = cap is not None and layer is not None and H % 8 == 0
         rc = lib.load().ob_rmsnorm_bwd(dy2.data_ptr(), xs.data_ptr(), weight.data_ptr(), rstd.data_ptr(),
-                                       lib.ptr(ds2), dx.data_ptr(), lib.ptr(dw_pe), None, n_ex, rows_per, rows, H,
-                                       offset, lib.stream())
+                                       lib.ptr(ds2), dx.data_ptr(), None if direct_pe else lib.ptr(dw_pe), None, n_ex, rows_per,
+                                       rows, H, offset, lib.stream())
         lib.check(rc, "rmsnorm_bwd")
-        if cap is not None:
+        if direct_pe:                # 16-byte-vector row sums straight into the capture's per-example buffer
+            rows_group_sum_(cap.pe_view(layer.weight), dy2, cap.batch_size, x2d=xs, rstd=rstd)
+        elif cap is not None:
             cap.add_per_example_grad(layer, "weight", dw_pe)
         elif dw_pe is not None:
             dw = dw_pe[0].to(weight.dtype)
@@ -146,9 +149,10 @@ def rows_group_sum_(out: torch.Tensor, g2d: torch.Tensor, num_examples: int, *, 
     rows, N = g2d.shape
     if out.dtype != torch.float32 or out.shape != (num_examples, N) or out.stride(1) != 1 or rows % num_examples:
         raise ValueError("rows_group_sum_: out must be fp32 [examples, N] and rows a multiple of examples")
+    mode = 0 if x2d is None else (1 if mean is not None else 2)          # 2: g * x * rstd (RMSNorm weight gradient)
     rc = lib.load().ob_rows_group_sum(g2d.data_ptr(), lib.ptr(x2d), lib.ptr(mean), lib.ptr(rstd), num_examples,
-                                      rows // num_examples, N, g2d.stride(0), out.data_ptr(), out.stride(0),
-                                      0 if x2d is None else 1, lib.stream())
+                                      rows // num_examples, N, g2d.stride(0), out.data_ptr(), out.stride(0), mode,
+                                      lib.stream())
     lib.check(rc, "rows_group_sum")
 
 

@@ -152,8 +152,12 @@ class _LinearCrossEntropy(Function):
             dh = logits @ weight
             ctx.capture_args = (weight, hidden, logits)
         else:
-            valid = (row_weight != 0) & (labels != ignore_index)
-            idx = valid.nonzero(as_tuple=True)[0]
+            if hidden.is_cuda and torch.cuda.is_current_stream_capturing():
+                # graph capture: no host-visible row count; run every row (ignored rows give zero loss and gradient)
+                idx = torch.arange(R, device=hidden.device)
+            else:
+                valid = (row_weight != 0) & (labels != ignore_index)
+                idx = valid.nonzero(as_tuple=True)[0]
             for lo in range(0, idx.numel(), chunk):
                 rows = idx[lo:lo + chunk]
                 h = hidden.index_select(0, rows)

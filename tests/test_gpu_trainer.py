@@ -39,7 +39,7 @@ def test_fused_trainer_steps_checkpoints_and_resumes(tmp_path):
     assert tr.engine_kind == "fused" and out["global_step"] == 4 and math.isfinite(out["epsilon"]) and out["epsilon"] > 0
     ck = list_checkpoints(str(tmp_path / "a"))
     assert [os.path.basename(c) for c in ck] == ["checkpoint-2", "checkpoint-4"]
-    for f in ("model.safetensors", "dp_optimizer.pt", "dp_state.pt", "accountant.json", "trainer_state.json"):
+    for f in ("adapter_model.safetensors", "dp_optimizer.pt", "dp_state.pt", "accountant.json", "trainer_state.json"):   # LoRA: adapter only
         assert os.path.exists(os.path.join(ck[-1], f)), f
     full = {n: p.detach().float().clone() for n, p in tr.model.named_parameters() if p.requires_grad}
     resumed = DPTrainer(model=_model(), args=_args(tmp_path / "a"), train_dataset=_rows())

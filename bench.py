@@ -299,16 +299,16 @@ def main() -> None:
         torch.cuda.synchronize()
 
     loss_fn = model.per_example_loss
-    # set-up (untimed, not a training step): capture the microbatch graphs of every static size, and run the largest
-    # batch the sampler can plausibly draw once so the caching allocator reaches its peak before any timed step
+    # set-up (untimed, not a training step): capture the microbatch graphs of every static size, and run every tail
+    # microbatch size once with all labels ignored (adds exact zeros to the gradient) so that library plan selection
+    # and the caching allocator have seen each shape before a timed step meets it
     setup_ids = data[:mb].to(dev).long()
     engine.prepare_graphs(loss_fn, {"input_ids": setup_ids, "labels": shift_labels(setup_ids, frac)})
-    if sampling is None:
-        big = min(data_size, int(per_gpu + 4 * (per_gpu ** 0.5) + 1))
-        ids_big = data[:big].to(dev).long()
-        no_labels = torch.full_like(ids_big, -100)
-        engine.accumulate(loss_fn, {"input_ids": ids_big, "labels": no_labels})      # all labels ignored: adds zeros
-        del ids_big, no_labels
+    if sampling is None and not use_graph:
+        for size in range(1, mb + 1):
+            ids_s = setup_ids[:size]
+            engine.accumulate(loss_fn, {"input_ids": ids_s, "labels": torch.full_like(ids_s, -100)})
+    torch.cuda.synchronize()
     for _ in range(args.warmup):
         engine.step(loss_fn, to_device(host_batch()), read_metrics=True)
     barrier()

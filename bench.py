@@ -300,14 +300,17 @@ def main() -> None:
 
     loss_fn = model.per_example_loss
     # set-up (untimed, not a training step): capture the microbatch graphs of every static size, and run every tail
-    # microbatch size once with all labels ignored (adds exact zeros to the gradient) so that library plan selection
+    # microbatch size once (the gradient shard is zeroed again afterwards) so that library plan selection
     # and the caching allocator have seen each shape before a timed step meets it
     setup_ids = data[:mb].to(dev).long()
     engine.prepare_graphs(loss_fn, {"input_ids": setup_ids, "labels": shift_labels(setup_ids, frac)})
     if sampling is None and not use_graph:
         for size in range(1, mb + 1):
             ids_s = setup_ids[:size]
-            engine.accumulate(loss_fn, {"input_ids": ids_s, "labels": torch.full_like(ids_s, -100)})
+            engine.accumulate(loss_fn, {"input_ids": ids_s, "labels": shift_labels(ids_s, frac)})
+        engine.group.barrier()                       # every rank's set-up reductions have landed ...
+        engine.space.grad.local.zero_()              # ... and are discarded: training starts from a zero gradient shard
+        engine.group.barrier()
     torch.cuda.synchronize()
     for _ in range(args.warmup):
         engine.step(loss_fn, to_device(host_batch()), read_metrics=True)

@@ -336,13 +336,13 @@ class _LoRALinear(Function):
     def forward(ctx, x, weight, bias, lora_a, lora_b, scaling):
         x2d = x.reshape(-1, x.shape[-1])
         x2d = x2d if x2d.is_contiguous() else x2d.contiguous()
-        xa = x2d @ lora_a.t()
+        xa = (x2d @ lora_a.t()) * scaling                 # s · x Aᵀ, kept for the backward pass
         if FUSE_LORA_GEMM and _lora_gemm_ok(x2d, weight, lora_a, lora_b, bias):
             # one tcgen05 pass: the low-rank product is a second K segment of the same accumulator tile
-            y = ops.gemm(x2d, weight, a2=xa * scaling, b2=lora_b, bias=bias)
+            y = ops.gemm(x2d, weight, a2=xa, b2=lora_b, bias=bias)
         else:
             y = torch.nn.functional.linear(x2d, weight, bias)
-            y.addmm_(xa, lora_b.t(), alpha=scaling)
+            y.addmm_(xa, lora_b.t())
         ctx.save_for_backward(x2d, xa, weight, lora_a, lora_b)
         ctx.scaling = scaling
         ctx.xshape = x.shape
@@ -365,14 +365,18 @@ class _LoRALinear(Function):
             dx = dx.view(ctx.xshape)
         cap = current_capture()
         if cap is None:
-            return dx, None, None, (q.t() @ x2d), (g2d.t() @ xa) * s, None
+            return dx, None, None, (q.t() @ x2d), g2d.t() @ xa, None
         R, r = q.shape
-        q_pad = torch.zeros(R, LORA_PAD, dtype=q.dtype, device=q.device)
-        q_pad[:, :r] = q
-        xa_pad = torch.zeros(R, LORA_PAD, dtype=xa.dtype, device=xa.device)
-        xa_pad[:, :r] = xa * s
+        if r % 8 == 0:
+            # rank-r operands go to the kernel as they are: TMA fills the rest of its 64-column box with zeros
+            q_op, xa_op = (q if q.is_contiguous() else q.contiguous()), xa
+        else:
+            q_op = torch.zeros(R, LORA_PAD, dtype=q.dtype, device=q.device)
+            q_op[:, :r] = q
+            xa_op = torch.zeros(R, LORA_PAD, dtype=xa.dtype, device=xa.device)
+            xa_op[:, :r] = xa
         xc = x2d if x2d.is_contiguous() else x2d.contiguous()
-        cap.add_lora(lora_a, lora_b, xc, xa_pad, g2d, q_pad)
+        cap.add_lora(lora_a, lora_b, xc, xa_op, g2d, q_op)
         return dx, None, None, None, None, None
 
 

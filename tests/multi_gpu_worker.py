@@ -18,6 +18,44 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+def short_run(rank: int, world: int, dev, out_path: str) -> int:
+    """Five full DP steps (noise on) over common global batches; rank 0 writes the final parameters.
+
+    The batches are dealt out ``rank::world``, the noise is keyed by the global coordinate, so a 1-rank and a W-rank run
+    must end at (nearly) the same parameters: only the order of fp32 reductions differs.
+    """
+    from opaque_b200.engine.fused import FusedDPEngine
+    from opaque_b200.models import LlamaConfig, LlamaForCausalLM, shift_labels
+    from opaque_b200.parallel.sharded import DPStepConfig
+    from opaque_b200.random import key
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256)
+    model = LlamaForCausalLM(cfg, device=dev)
+    eng = FusedDPEngine(model, clipping_norm=1.0, noise_multiplier=0.6, normalize_by=8.0, key=key(21),
+                        step_config=DPStepConfig(lr=3e-3), microbatch_size=2)
+    g = torch.Generator().manual_seed(5)
+    losses = []
+    for step in range(5):
+        ids = torch.randint(0, 512, (8, 128), generator=g).to(dev)
+        labels = shift_labels(ids, 1.0)
+        res = eng.step(model.per_example_loss, {"input_ids": ids[rank::world], "labels": labels[rank::world]})
+        t = torch.tensor([res.loss * res.batch_size, float(res.batch_size)], device=dev)
+        if world > 1:
+            dist.all_reduce(t)
+        losses.append(float(t[0] / t[1]))
+    torch.cuda.synchronize()
+    ok = eng.status.read() == 0
+    if rank == 0:
+        torch.save({"params": {n: p.detach().float().cpu() for n, p in model.named_parameters()}, "losses": losses}, out_path)
+    if world > 1:
+        dist.barrier()
+    eng.group.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0 if ok else 1
+
+
 def main() -> int:
     from opaque_b200 import ops
     from opaque_b200.engine.fused import CLIP_GUARD, FusedDPEngine
@@ -27,8 +65,11 @@ def main() -> int:
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
     torch.cuda.set_device(dev)
-    dist.init_process_group("nccl", device_id=dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     mode = sys.argv[1] if len(sys.argv) > 1 else "full"
+    if mode == "parity":
+        return short_run(rank, world, dev, sys.argv[2])
     torch.manual_seed(0)
     cfg = LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
                       num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256)

@@ -18,10 +18,10 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _run(world: int, mode: str) -> None:
+def _run(world: int, mode: str, *extra: str) -> None:
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
-           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "multi_gpu_worker.py"), mode]
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "multi_gpu_worker.py"), mode, *extra]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
 
@@ -38,3 +38,18 @@ def test_all_visible_gpus():
     if n < 4:
         pytest.skip("needs four or more GPUs")
     _run(n, "full")
+
+
+def test_short_run_parity_one_vs_two_gpus(tmp_path):
+    """Same global batches, same keys: a 2-rank run ends where the 1-rank run ends (noise is keyed by coordinate)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    one, two = str(tmp_path / "w1.pt"), str(tmp_path / "w2.pt")
+    _run(1, "parity", one)
+    _run(2, "parity", two)
+    a, b = torch.load(one), torch.load(two)
+    for x, y in zip(a["losses"], b["losses"]):
+        assert abs(x - y) < 2e-2 * max(1.0, abs(x))
+    for n, p in a["params"].items():
+        q = b["params"][n]
+        assert float((p - q).abs().max()) <= 2e-2 * float(p.abs().max()) + 1e-3, n       # bf16 parameters, reordered fp32 sums

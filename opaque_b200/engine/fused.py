@@ -408,7 +408,8 @@ class FusedDPEngine:
                  microbatch_size: int = 8, group: PeerGroup | None = None, mechanism: dict | None = None,
                  clipping_mode: str = "clip", gamma: float = 0.01,
                  direct: Callable[[str, torch.nn.Parameter], bool] | None = None,
-                 group_of: Callable[[str], str] | None = None, adaptive: Any = None, cuda_graph: bool = False):
+                 group_of: Callable[[str], str] | None = None, adaptive: Any = None, cuda_graph: bool = False,
+                 accumulate: str = "peer"):
         """``clipping_norm`` is a float, or ``{label: C_g}`` together with ``group_of(param_name) -> label`` for
         per-group clipping.  ``adaptive`` is an :class:`opaque_b200.dpsgd.clipping.AdaptiveClipState` (quantile
         tracking; its ``clipping_norm`` overrides the argument and is updated after every step from the cluster-wide
@@ -425,7 +426,8 @@ class FusedDPEngine:
             missing = {group_of(n) for n, _ in named} - set(clipping_norm)
             if missing:
                 raise ValueError(f"no clipping norm for group(s) {sorted(missing)}")
-        self.space = FlatSpace(named, self.group, direct=direct, group_of=group_of if isinstance(clipping_norm, Mapping) else None)
+        self.space = FlatSpace(named, self.group, direct=direct, group_of=group_of if isinstance(clipping_norm, Mapping) else None,
+                               accumulate=accumulate)
         self.space.bind()
         self._slot_by_id = {id(p): self.space.slots[n] for n, p in named}
         self.opt = ShardedDPOptimizer(self.space, step_config or DPStepConfig(), key=key, mechanism=mechanism)

@@ -352,6 +352,14 @@ def embedding_wgrad(g: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None
     lib.check(rc, "embedding_wgrad")
 
 
+def push_grad_(local: torch.Tensor, peer_table: torch.Tensor, shard_elems: int) -> None:
+    """Add a full-length local fp32 gradient into the owners' shards (peer reductions) and clear it."""
+    if local.dtype != torch.float32 or not local.is_contiguous() or local.numel() % 4 or shard_elems % 4:
+        raise ValueError("push_grad_: contiguous fp32 buffer with a length and shard size that are multiples of 4")
+    rc = lib.load().ob_push_grad(local.data_ptr(), local.numel(), peer_table.data_ptr(), shard_elems, lib.sm_count(), lib.stream())
+    lib.check(rc, "push_grad")
+
+
 def shard_step(*, grad, master, m, v, params_local=None, peer_params=None, world=1, global_offset=0, seed=0,
                noise_std=0.0, inv_normalize=1.0, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, step=1,
                phi_hat=0.0, decoupled_wd=True, ftrl_state=None, ftrl_mode=0, ftrl_coef: Sequence[float] = (),
@@ -378,7 +386,7 @@ from .functional import (activation, cross_entropy, cross_entropy_ref, fused_add
                          layer_norm, plain_torch_ops, rms_norm, rms_norm_ref, rope_qk, rope_qk_ref, rope_tables, rows_group_sum_, swiglu)
 
 __all__ = [
-    "gemm", "gemm_ref", "ghost_set_wide", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_",
+    "gemm", "gemm_ref", "ghost_set_wide", "push_grad_", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_",
     "DeviceWaitTimeout", "KernelLibraryError", "StatusWord", "clip_weighted_sum", "cross_entropy",
     "cross_entropy_ref", "embedding_wgrad", "fused_add_rms_norm", "geglu", "ghost_norm", "ghost_norm_ref", "glu_ref",
     "philox_normal_add_", "pick_block_n", "pick_splits", "rms_norm", "rms_norm_ref", "rope_qk", "rope_qk_ref",

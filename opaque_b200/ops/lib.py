@@ -26,6 +26,7 @@ _SIGNATURES = {
     "ob_rows_group_sum": [P, P, P, P, I, I, I, LL, P, LL, I, P],
     "ob_activation": [P, P, P, LL, I, I, P],
     "ob_ghost_set_wide": [I],
+    "ob_push_grad": [P, LL, P, LL, I, P],
     "ob_rmsnorm_fwd": [P, P, P, P, P, P, LL, I, F, F, I, P],
     "ob_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, LL, I, F, P],
     "ob_glu_fwd": [P, P, P, LL, I, LL, I, I, P],

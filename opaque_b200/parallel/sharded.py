@@ -60,7 +60,12 @@ class FlatSpace:
 
     def __init__(self, named_params: Sequence[tuple[str, torch.nn.Parameter]], group: PeerGroup, *,
                  direct: Callable[[str, torch.nn.Parameter], bool] | None = None,
-                 group_of: Callable[[str], str] | None = None):
+                 group_of: Callable[[str], str] | None = None, accumulate: str = "peer"):
+        """``accumulate="peer"`` (default): producer kernels reduce every microbatch's tiles straight into the owners'
+        shards.  ``"local"``: they add into a full-length local fp32 buffer and ONE push per step reduces it into the
+        owners' shards — (microbatches per step)× less reduction traffic over NVLink at the price of ``4·P`` bytes."""
+        if accumulate not in ("peer", "local"):
+            raise ValueError("accumulate must be 'peer' or 'local'")
         self.group = group
         is_direct = direct or default_direct
         label = group_of or (lambda name: "")
@@ -88,6 +93,7 @@ class FlatSpace:
         self.params = group.buffer(self.total, torch.bfloat16)
         self.grad = group.buffer(self.shard, torch.float32)
         dev = group.device
+        self.grad_full = torch.zeros(self.total, dtype=torch.float32, device=dev) if accumulate == "local" and group.world > 1 else None
         self.master = torch.zeros(self.shard, dtype=torch.float32, device=dev)
         self.m = torch.zeros_like(self.master)
         self.v = torch.zeros_like(self.master)
@@ -125,7 +131,14 @@ class FlatSpace:
         """Keyword arguments that route a producer kernel's output into the sharded gradient."""
         if self.group.world == 1:
             return {"out": self.grad.local, "peer_table": None, "shard_elems": 0}
+        if self.grad_full is not None:
+            return {"out": self.grad_full, "peer_table": None, "shard_elems": 0}
         return {"out": None, "peer_table": self.grad.table, "shard_elems": self.shard}
+
+    def push_local_gradient(self) -> None:
+        """``accumulate="local"``: reduce this rank's accumulated gradient into the owners' shards (before the barrier)."""
+        if self.grad_full is not None:
+            ops.push_grad_(self.grad_full, self.grad.table, self.shard)
 
     @torch.no_grad()
     def gather_full(self, shard_tensor: torch.Tensor) -> torch.Tensor:
@@ -205,6 +218,7 @@ class ShardedDPOptimizer:
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if self.timing is not None else None
         if ev:
             ev[0].record()
+        sp.push_local_gradient()
         g.barrier()
         if ev:
             ev[1].record()

@@ -388,6 +388,7 @@ class DPTrainer:
 
     def _participation(self, sampler, steps: int) -> tuple[int, int | None]:
         """(min_sep, max_participations) implied by the sampler for MF sensitivity."""
+        sampler = getattr(sampler, "inner", sampler)           # BalancedRankSampler wraps the global sampler
         if isinstance(sampler, BallsInBinsSampler):
             return sampler.num_bins, math.ceil(steps / sampler.num_bins)
         if isinstance(sampler, SequentialBatchSampler):
@@ -399,6 +400,7 @@ class DPTrainer:
     def _step_process(self, nm: float, q: float, steps: int, sampler) -> acc.DpProcess:
         """The accountant's description of ONE step at noise multiplier ``nm``."""
         a = self.args
+        sampler = getattr(sampler, "inner", sampler)
         W = a.world_size
         if a.privacy_noise_mechanism == "gaussian":
             g: acc.DpProcess = sgd_acc.gaussian(nm)

@@ -102,25 +102,27 @@ class FlatSpace:
     # ---- binding --------------------------------------------------------------------------
     @torch.no_grad()
     def bind(self) -> None:
-        """Move parameter storage into the flat bf16 buffer and initialise the fp32 masters.
+        """Move parameter storage into the flat bf16 buffer and initialise the fp32 masters of this rank's shard.
 
-        Rank 0's values win (one broadcast) so that replicas start identical.
+        Rank 0's values win (one broadcast per parameter) so that replicas start identical.  Works slot by slot: no
+        full-length temporary is created, so a model that fills most of the GPU can still be bound.
         """
-        full32 = torch.zeros(self.total, dtype=torch.float32, device=self.group.device)
+        pg = self.group.pg
+        lo_s, hi_s = self.shard_lo, self.shard_lo + self.shard
         for name, p in self._named:
+            if self.group.world > 1:
+                src = dist.get_global_rank(pg, 0) if pg is not dist.group.WORLD else 0
+                dist.broadcast(p.data, src=src, group=pg)
             s = self.slots[name]
-            full32[s.offset:s.offset + s.numel] = p.detach().reshape(-1).float()
-        if self.group.world > 1:
-            dist.broadcast(full32, src=dist.get_global_rank(self.group.pg, 0) if self.group.pg is not dist.group.WORLD else 0,
-                           group=self.group.pg)
-        self.master.copy_(full32[self.shard_lo:self.shard_lo + self.shard])
-        self.params.local.copy_(full32.to(torch.bfloat16))
-        for name, p in self._named:
-            s = self.slots[name]
-            p.data = self.params.local[s.offset:s.offset + s.numel].view(s.shape)
+            flat = p.detach().reshape(-1)
+            self.params.local[s.offset:s.offset + s.numel].copy_(flat)                  # rounds to bf16
+            lo, hi = max(s.offset, lo_s), min(s.offset + s.numel, hi_s)
+            if lo < hi:                                                                   # masters keep the source precision
+                self.master[lo - lo_s:hi - lo_s].copy_(flat[lo - s.offset:hi - s.offset])
+            p.data = self.params.local[s.offset:s.offset + s.numel].view(s.shape)         # frees the old storage
         if self.group.world > 1:
             torch.cuda.synchronize(self.group.device)
-            dist.barrier(group=self.group.pg)
+            dist.barrier(group=pg)
 
     def view_of(self, name: str, flat: torch.Tensor) -> torch.Tensor:
         s = self.slots[name]

@@ -48,7 +48,7 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--microbatch", type=int, default=0)
     ap.add_argument("--per-gpu-batch", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="truncate the model (profiling only; the JSON says so)")
-    ap.add_argument("--accumulate", default="peer", choices=["peer", "local"],
+    ap.add_argument("--accumulate", default="auto", choices=["auto", "peer", "local"],
                     help="peer: every microbatch's gradient tiles are reduced straight into the owners' shards; "
                          "local: accumulate in a local fp32 buffer and push once per step")
     ap.add_argument("--cuda-graph", type=int, default=-1, help="1/0: replay microbatches as CUDA graphs (default: per config)")
@@ -375,7 +375,7 @@ def main() -> None:
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "impl": "ours",
             "config": {"model": name, "global_batch": global_batch, "seq_len": seq, "parallelism": f"{par}{world}",
-                       "sampling": sampling or f"Poisson over the whole dataset (rate {per_gpu * world}/{data_size}), one global draw per step dealt out evenly over ranks", "microbatch": mb, "cuda_graph_microbatches": use_graph, "gradient_accumulation": args.accumulate,
+                       "sampling": sampling or f"Poisson over the whole dataset (rate {per_gpu * world}/{data_size}), one global draw per step dealt out evenly over ranks", "microbatch": mb, "cuda_graph_microbatches": use_graph, "gradient_accumulation": engine.space.accumulate,
                        "loss_fraction": frac, "clip": dp["clipping_norm"], "sigma": dp["noise_multiplier"],
                        "optimizer": "AdamW-BC", "lr": dp["lr"],
                        "l2": "inputs larger than L2 (per-step working set >> 126 MB; no explicit flush)",

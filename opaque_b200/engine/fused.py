@@ -409,7 +409,7 @@ class FusedDPEngine:
                  clipping_mode: str = "clip", gamma: float = 0.01,
                  direct: Callable[[str, torch.nn.Parameter], bool] | None = None,
                  group_of: Callable[[str], str] | None = None, adaptive: Any = None, cuda_graph: bool = False,
-                 accumulate: str = "peer"):
+                 accumulate: str = "auto"):
         """``clipping_norm`` is a float, or ``{label: C_g}`` together with ``group_of(param_name) -> label`` for
         per-group clipping.  ``adaptive`` is an :class:`opaque_b200.dpsgd.clipping.AdaptiveClipState` (quantile
         tracking; its ``clipping_norm`` overrides the argument and is updated after every step from the cluster-wide

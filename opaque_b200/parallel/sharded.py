@@ -39,6 +39,7 @@ from ..random import RngKey, fold_in
 from .peer import PeerGroup
 
 ALIGN = 64
+LOCAL_ACCUMULATE_LIMIT_BYTES = 16 << 30      # "auto": accumulate locally when the full fp32 gradient fits in 16 GiB
 
 
 @dataclasses.dataclass(frozen=True)
@@ -63,9 +64,10 @@ class FlatSpace:
                  group_of: Callable[[str], str] | None = None, accumulate: str = "peer"):
         """``accumulate="peer"`` (default): producer kernels reduce every microbatch's tiles straight into the owners'
         shards.  ``"local"``: they add into a full-length local fp32 buffer and ONE push per step reduces it into the
-        owners' shards — (microbatches per step)× less reduction traffic over NVLink at the price of ``4·P`` bytes."""
-        if accumulate not in ("peer", "local"):
-            raise ValueError("accumulate must be 'peer' or 'local'")
+        owners' shards — (microbatches per step)× less reduction traffic over NVLink at the price of ``4·P`` bytes.
+        ``"auto"``: local while that buffer stays under ``LOCAL_ACCUMULATE_LIMIT_BYTES``."""
+        if accumulate not in ("peer", "local", "auto"):
+            raise ValueError("accumulate must be 'peer', 'local' or 'auto'")
         self.group = group
         is_direct = direct or default_direct
         label = group_of or (lambda name: "")
@@ -93,7 +95,10 @@ class FlatSpace:
         self.params = group.buffer(self.total, torch.bfloat16)
         self.grad = group.buffer(self.shard, torch.float32)
         dev = group.device
-        self.grad_full = torch.zeros(self.total, dtype=torch.float32, device=dev) if accumulate == "local" and group.world > 1 else None
+        if accumulate == "auto":     # measured on 4 GPUs: per-microbatch peer reductions cost 15-35 % for 0.1-1 B parameter
+            accumulate = "local" if 4 * self.total <= LOCAL_ACCUMULATE_LIMIT_BYTES else "peer"      # models; huge models keep memory
+        self.accumulate = accumulate if group.world > 1 else "peer"
+        self.grad_full = torch.zeros(self.total, dtype=torch.float32, device=dev) if self.accumulate == "local" else None
         self.master = torch.zeros(self.shard, dtype=torch.float32, device=dev)
         self.m = torch.zeros_like(self.master)
         self.v = torch.zeros_like(self.master)

@@ -85,7 +85,7 @@ def main() -> int:
     dist.broadcast(ids, 0)
     labels = shift_labels(ids, 1.0)
     eng = FusedDPEngine(model, clipping_norm=C, noise_multiplier=0.0, normalize_by=float(B), key=key(11),
-                        step_config=DPStepConfig(lr=1e-2), microbatch_size=2, accumulate="local" if mode == "local" else "peer")
+                        step_config=DPStepConfig(lr=1e-2), microbatch_size=2, accumulate="local" if mode == "local" else ("peer" if mode == "full" else "auto"))
     sp = eng.space
     # oracle AFTER binding (parameters are now the broadcast bf16 values), per example, on every rank
     total = {n: torch.zeros_like(p, dtype=torch.float32) for n, p in model.named_parameters() if p.requires_grad}

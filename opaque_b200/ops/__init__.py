@@ -140,6 +140,8 @@ def wgrad_clip_per_example(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor |
     if splits is None:
         tiles = math.ceil(M / 128) * math.ceil(N / 256)
         splits = pick_splits(tiles, T, sms, max_splits=B) if accumulate else 1
+        if peer_table is not None and tiles * 2 >= sms:
+            splits = 1                      # every extra split sends the whole tile over NVLink once more
     if out is not None:
         if out.dtype != torch.float32:
             raise TypeError("the destination must be fp32")

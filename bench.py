@@ -15,7 +15,14 @@ sequences per GPU, seq 1024, σ calibrated for ε=8 at δ=1e-6 over 2000 steps);
 60-expert top-4 MoE full-parameter DP-SGD (seq 2048, 32 sequences per GPU; needs the state sharded over 8 GPUs —
 on fewer GPUs pass ``--layers`` to truncate, which the JSON reports).
 
-  python bench.py [--gpus N --steps K --warmup W] [--config llama8b-lora|gpt2|llama1b-blt|moe|llama-tiny] [--impl reference]
+Sampling: one global Poisson draw per step (same key on every rank) dealt out evenly over the ranks.  Set-up before the
+warm-up steps captures CUDA graphs (GPT-2) and visits every tail microbatch size once, then clears the gradient shard.
+``--impl restated`` runs the reference library's algorithm (vmap per-example gradients, NCCL all-reduce, host noise,
+tree-mapped AdamW-BC) written with this package's reference engine, as a same-box comparator; ``--impl reference`` would
+run the unmodified reference package and reports that it cannot be installed offline.
+
+  python bench.py [--gpus N --steps K --warmup W] [--config llama8b-lora|gpt2|llama1b-blt|moe|llama-tiny]
+                  [--impl ours|restated|reference] [--microbatch M] [--per-gpu-batch B] [--accumulate auto|peer|local]
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
       bench.py --gpus N --steps K --warmup W
 """

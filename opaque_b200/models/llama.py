@@ -33,6 +33,17 @@ class LlamaConfig:
     max_position_embeddings: int = 8192
     tie_word_embeddings: bool = False
     head_dim: int | None = None
+    # family variants (Qwen2: q/k/v bias; Qwen3: per-head RMSNorm on q and k; Gemma: GeGLU, (1 + w) norms computed in
+    # fp32, embeddings scaled by sqrt(d))
+    attention_bias: bool = False
+    attention_out_bias: bool = False
+    mlp_bias: bool = False
+    hidden_act: str = "silu"                 # silu | gelu_pytorch_tanh | gelu
+    norm_offset: float = 0.0
+    norm_casting: str = "llama"              # llama | gemma
+    embedding_scale: float = 1.0
+    qk_norm: bool = False
+    sliding_window: int | None = None        # accepted when sequences are not longer than the window
 
     @property
     def hd(self) -> int:
@@ -58,16 +69,26 @@ class LlamaAttention(nn.Module):
         super().__init__()
         d, hd = cfg.hidden_size, cfg.hd
         self.nh, self.nkv, self.hd = cfg.num_attention_heads, cfg.num_key_value_heads, hd
-        self.q_proj = Linear(d, self.nh * hd, dtype=dtype, device=device)
-        self.k_proj = Linear(d, self.nkv * hd, dtype=dtype, device=device)
-        self.v_proj = Linear(d, self.nkv * hd, dtype=dtype, device=device)
-        self.o_proj = Linear(self.nh * hd, d, dtype=dtype, device=device)
+        self.q_proj = Linear(d, self.nh * hd, bias=cfg.attention_bias, dtype=dtype, device=device)
+        self.k_proj = Linear(d, self.nkv * hd, bias=cfg.attention_bias, dtype=dtype, device=device)
+        self.v_proj = Linear(d, self.nkv * hd, bias=cfg.attention_bias, dtype=dtype, device=device)
+        self.o_proj = Linear(self.nh * hd, d, bias=cfg.attention_out_bias, dtype=dtype, device=device)
+        self.window = cfg.sliding_window
+        if cfg.qk_norm:
+            self.q_norm = RMSNorm(hd, cfg.rms_norm_eps, offset=cfg.norm_offset, casting_mode=cfg.norm_casting, dtype=dtype, device=device)
+            self.k_norm = RMSNorm(hd, cfg.rms_norm_eps, offset=cfg.norm_offset, casting_mode=cfg.norm_casting, dtype=dtype, device=device)
+        else:
+            self.q_norm = self.k_norm = None
 
     def forward(self, x, cos, sin, pos):
         B, T, _ = x.shape
+        if self.window is not None and T > self.window:
+            raise NotImplementedError(f"sequence length {T} exceeds the sliding window {self.window}: windowed attention is not implemented")
         q = self.q_proj(x).view(B, T, self.nh, self.hd)
         k = self.k_proj(x).view(B, T, self.nkv, self.hd)
         v = self.v_proj(x).view(B, T, self.nkv, self.hd)
+        if self.q_norm is not None:
+            q, k = self.q_norm(q), self.k_norm(k)
         q, k = ops.rope_qk(q, k, cos, sin, pos)
         o = nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                                                        is_causal=True, enable_gqa=self.nkv != self.nh)
@@ -77,20 +98,28 @@ class LlamaAttention(nn.Module):
 class LlamaMLP(nn.Module):
     def __init__(self, cfg: LlamaConfig, dtype, device):
         super().__init__()
-        self.gate_proj = Linear(cfg.hidden_size, cfg.intermediate_size, dtype=dtype, device=device)
-        self.up_proj = Linear(cfg.hidden_size, cfg.intermediate_size, dtype=dtype, device=device)
-        self.down_proj = Linear(cfg.intermediate_size, cfg.hidden_size, dtype=dtype, device=device)
+        bias = getattr(cfg, "mlp_bias", False)
+        self.gate_proj = Linear(cfg.hidden_size, cfg.intermediate_size, bias=bias, dtype=dtype, device=device)
+        self.up_proj = Linear(cfg.hidden_size, cfg.intermediate_size, bias=bias, dtype=dtype, device=device)
+        self.down_proj = Linear(cfg.intermediate_size, cfg.hidden_size, bias=bias, dtype=dtype, device=device)
+        self.act = getattr(cfg, "hidden_act", "silu")
+        if self.act not in ("silu", "gelu_pytorch_tanh", "gelu"):
+            raise ValueError(f"unsupported hidden_act {self.act!r}")
 
     def forward(self, x):
-        return self.down_proj(ops.swiglu(self.gate_proj(x), self.up_proj(x)))
+        g, u = self.gate_proj(x), self.up_proj(x)
+        if self.act == "silu":
+            return self.down_proj(ops.swiglu(g, u))
+        return self.down_proj(ops.geglu(g, u, approximate=self.act == "gelu_pytorch_tanh"))
 
 
 class LlamaDecoderLayer(nn.Module):
     def __init__(self, cfg: LlamaConfig, dtype, device):
         super().__init__()
-        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
+        nk = dict(offset=cfg.norm_offset, casting_mode=cfg.norm_casting, dtype=dtype, device=device)
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
         self.self_attn = LlamaAttention(cfg, dtype, device)
-        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
         self.mlp = LlamaMLP(cfg, dtype, device)
 
     def forward(self, h, cos, sin, pos):
@@ -104,7 +133,8 @@ class LlamaModel(nn.Module):
         super().__init__()
         self.embed_tokens = Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
         self.layers = nn.ModuleList(LlamaDecoderLayer(cfg, dtype, device) for _ in range(cfg.num_hidden_layers))
-        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, offset=cfg.norm_offset, casting_mode=cfg.norm_casting,
+                            dtype=dtype, device=device)
 
 
 class LlamaForCausalLM(nn.Module):
@@ -135,6 +165,8 @@ class LlamaForCausalLM(nn.Module):
     # ---- forward ------------------------------------------------------------------------------
     def hidden_states(self, input_ids: torch.Tensor, position_ids: torch.Tensor | None = None) -> torch.Tensor:
         h = self.model.embed_tokens(input_ids)
+        if self.config.embedding_scale != 1.0:
+            h = h * torch.tensor(self.config.embedding_scale, dtype=h.dtype, device=h.device)      # rounded like the weights
         for layer in self.model.layers:
             if self.activation_checkpointing and torch.is_grad_enabled():
                 h = torch.utils.checkpoint.checkpoint(layer, h, self.rope_cos, self.rope_sin, position_ids,

@@ -42,6 +42,11 @@ class MoEConfig:
     rms_norm_eps: float = 1e-6
     rope_theta: float = 1000000.0
     max_position_embeddings: int = 4096
+    # family variants: Qwen-MoE has q/k/v biases, a sigmoid gate on the shared expert and its own shared width
+    attention_bias: bool = False
+    shared_expert_gate: bool = False
+    shared_intermediate_size: int | None = None
+    head_dim: int | None = None
 
     @property
     def padded_experts(self) -> int:
@@ -51,7 +56,8 @@ class MoEConfig:
         return LlamaConfig(vocab_size=self.vocab_size, hidden_size=self.hidden_size, num_attention_heads=self.num_attention_heads,
                            num_key_value_heads=self.num_key_value_heads, rms_norm_eps=self.rms_norm_eps,
                            rope_theta=self.rope_theta, max_position_embeddings=self.max_position_embeddings,
-                           intermediate_size=self.moe_intermediate_size * max(self.num_shared_experts, 1))
+                           attention_bias=self.attention_bias, head_dim=self.head_dim,
+                           intermediate_size=self.shared_intermediate_size or self.moe_intermediate_size * max(self.num_shared_experts, 1))
 
     @staticmethod
     def tiny() -> "MoEConfig":
@@ -168,6 +174,8 @@ class SparseMoeBlock(nn.Module):
         self.gate = Linear(cfg.hidden_size, cfg.padded_experts, dtype=dtype, device=device)
         self.experts = MoEExperts(cfg, dtype, device)
         self.shared_expert = LlamaMLP(cfg.attn_config(), dtype, device) if cfg.num_shared_experts > 0 else None
+        self.shared_expert_gate = Linear(cfg.hidden_size, 8, dtype=dtype, device=device) \
+            if cfg.shared_expert_gate and self.shared_expert is not None else None      # row 0 is the gate, rows 1-7 padding
 
     def forward(self, x):
         B, T, H = x.shape
@@ -179,7 +187,10 @@ class SparseMoeBlock(nn.Module):
             w = w / w.sum(-1, keepdim=True)
         y = self.experts(x.reshape(B * T, H), idx.reshape(B * T, -1), w.reshape(B * T, -1).to(x.dtype), B, T).view(B, T, H)
         if self.shared_expert is not None:
-            y = y + self.shared_expert(x)
+            sh = self.shared_expert(x)
+            if self.shared_expert_gate is not None:
+                sh = sh * torch.sigmoid(self.shared_expert_gate(x)[..., :1].float()).to(sh.dtype)
+            y = y + sh
         return y
 
 
@@ -204,7 +215,8 @@ class MoEForCausalLM(nn.Module):
         self.layers = nn.ModuleList(MoEDecoderLayer(cfg, dtype, device) for _ in range(cfg.num_hidden_layers))
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
         self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, dtype=dtype, device=device)
-        cos, sin = ops.rope_tables(cfg.hidden_size // cfg.num_attention_heads, cfg.max_position_embeddings, cfg.rope_theta, device=device)
+        cos, sin = ops.rope_tables(cfg.head_dim or cfg.hidden_size // cfg.num_attention_heads, cfg.max_position_embeddings, cfg.rope_theta,
+                                   device=device)
         self.register_buffer("rope_cos", cos, persistent=False)
         self.register_buffer("rope_sin", sin, persistent=False)
 

@@ -23,10 +23,21 @@ from ..models import GPT2Config, GPT2LMHeadModel, LlamaConfig, LlamaForCausalLM,
 _FAMILIES: dict[str, Callable[[Any, dict], torch.nn.Module]] = {}
 _RUNTIME = {"patched": False}
 
-# model_type -> family builder; llama-shaped families share one implementation
-LLAMA_LIKE = ("llama", "mistral", "ministral", "qwen2", "qwen3", "mellum", "smollm3", "granite", "olmo2", "olmo3",
-              "exaone4", "phi3", "glm4", "cohere", "cohere2", "gemma", "gemma2", "gemma3")
-MOE_LIKE = ("mixtral", "qwen2_moe", "qwen3_moe", "qwen3_5_moe", "qwen3_next", "gpt_oss", "hunyuan_v1_moe", "deepseek_v4")
+# model_type -> family builder.  Only families whose block structure these modules reproduce exactly are registered;
+# the others are listed with the reason, so a conversion can never silently drop a feature of the architecture.
+LLAMA_LIKE = ("llama", "mistral", "ministral", "mellum", "qwen2", "qwen3", "gemma", "phi3")
+MOE_LIKE = ("mixtral", "qwen2_moe", "qwen3_moe")
+UNSUPPORTED = {
+    "gemma2": "post-attention / post-feed-forward norms, attention and final logit soft-capping, alternating local attention",
+    "gemma3": "as gemma2 plus per-layer rope bases and q/k norms",
+    "cohere": "LayerNorm, parallel attention + MLP block, logit scale", "cohere2": "as cohere plus sliding-window layers",
+    "olmo2": "norms after the sub-layers (post-norm) and q/k norms over the full projection", "olmo3": "as olmo2 plus sliding windows",
+    "glm4": "extra post-sub-layer norms and partial rotary embedding", "exaone4": "hybrid local/global attention with post-norms",
+    "granite": "embedding / residual / attention / logit multipliers", "smollm3": "layers without rotary embedding",
+    "gpt_oss": "attention sinks, clamped SwiGLU with biases, alternating sliding windows",
+    "deepseek_v4": "multi-head latent attention", "hunyuan_v1_moe": "q/k norms and a mixed shared-expert layout",
+    "qwen3_next": "gated delta-net layers", "qwen3_5_moe": "gated delta-net layers",
+}
 
 
 def register_family(model_type: str, builder: Callable[[Any, dict], torch.nn.Module]) -> None:
@@ -35,17 +46,45 @@ def register_family(model_type: str, builder: Callable[[Any, dict], torch.nn.Mod
 
 
 def _cfg_get(cfg: Any, name: str, default=None):
-    return cfg.get(name, default) if isinstance(cfg, dict) else getattr(cfg, name, default)
+    v = cfg.get(name, default) if isinstance(cfg, dict) else getattr(cfg, name, default)
+    return default if v is None else v
+
+
+def _rope_theta(cfg: Any, default: float) -> float:
+    rp = _cfg_get(cfg, "rope_parameters") or {}
+    if isinstance(rp, dict) and rp.get("rope_theta"):
+        if rp.get("rope_type", "default") not in ("default", None):
+            raise NotImplementedError(f"rope scaling {rp.get('rope_type')!r} is not implemented")
+        return float(rp["rope_theta"])
+    if _cfg_get(cfg, "rope_scaling"):
+        raise NotImplementedError("rope scaling is not implemented")
+    return float(_cfg_get(cfg, "rope_theta", default))
 
 
 def _build_llama(cfg: Any, opt: dict) -> torch.nn.Module:
+    mtype = _cfg_get(cfg, "model_type")
+    extra: dict[str, Any] = {}
+    if mtype == "qwen2":
+        extra.update(attention_bias=True)
+    elif mtype == "qwen3":
+        extra.update(qk_norm=True, attention_bias=bool(_cfg_get(cfg, "attention_bias", False)))
+    elif mtype == "gemma":
+        extra.update(hidden_act=_cfg_get(cfg, "hidden_activation") or _cfg_get(cfg, "hidden_act", "gelu_pytorch_tanh"), norm_offset=1.0,
+                     norm_casting="gemma", embedding_scale=float(_cfg_get(cfg, "hidden_size")) ** 0.5)
+    else:
+        extra.update(attention_bias=bool(_cfg_get(cfg, "attention_bias", False)), attention_out_bias=bool(_cfg_get(cfg, "attention_bias", False)),
+                     mlp_bias=bool(_cfg_get(cfg, "mlp_bias", False)))
+    if "hidden_act" not in extra:
+        extra["hidden_act"] = _cfg_get(cfg, "hidden_act", "silu")
+    window = _cfg_get(cfg, "sliding_window") if _cfg_get(cfg, "use_sliding_window", mtype in ("mistral", "ministral")) else None
     c = LlamaConfig(vocab_size=_cfg_get(cfg, "vocab_size"), hidden_size=_cfg_get(cfg, "hidden_size"),
                     intermediate_size=_cfg_get(cfg, "intermediate_size"), num_hidden_layers=_cfg_get(cfg, "num_hidden_layers"),
                     num_attention_heads=_cfg_get(cfg, "num_attention_heads"),
                     num_key_value_heads=_cfg_get(cfg, "num_key_value_heads") or _cfg_get(cfg, "num_attention_heads"),
-                    rms_norm_eps=_cfg_get(cfg, "rms_norm_eps", 1e-6), rope_theta=_cfg_get(cfg, "rope_theta", 10000.0),
+                    rms_norm_eps=_cfg_get(cfg, "rms_norm_eps", 1e-6), rope_theta=_rope_theta(cfg, 10000.0),
                     max_position_embeddings=_cfg_get(cfg, "max_position_embeddings", 8192),
-                    tie_word_embeddings=bool(_cfg_get(cfg, "tie_word_embeddings", False)), head_dim=_cfg_get(cfg, "head_dim"))
+                    tie_word_embeddings=bool(_cfg_get(cfg, "tie_word_embeddings", False)), head_dim=_cfg_get(cfg, "head_dim"),
+                    sliding_window=window, **extra)
     return LlamaForCausalLM(c, dtype=opt.get("dtype", torch.bfloat16), device=opt.get("device"))
 
 
@@ -57,15 +96,23 @@ def _build_gpt2(cfg: Any, opt: dict) -> torch.nn.Module:
 
 
 def _build_moe(cfg: Any, opt: dict) -> torch.nn.Module:
+    mtype = _cfg_get(cfg, "model_type")
+    shared = _cfg_get(cfg, "shared_expert_intermediate_size", 0) if mtype == "qwen2_moe" else 0
+    if mtype in ("qwen2_moe", "qwen3_moe") and (_cfg_get(cfg, "mlp_only_layers") or _cfg_get(cfg, "decoder_sparse_step", 1) != 1):
+        raise NotImplementedError("dense layers interleaved with MoE layers are not implemented")
     c = MoEConfig(vocab_size=_cfg_get(cfg, "vocab_size"), hidden_size=_cfg_get(cfg, "hidden_size"),
                   num_hidden_layers=_cfg_get(cfg, "num_hidden_layers"), num_attention_heads=_cfg_get(cfg, "num_attention_heads"),
                   num_key_value_heads=_cfg_get(cfg, "num_key_value_heads") or _cfg_get(cfg, "num_attention_heads"),
                   num_experts=_cfg_get(cfg, "num_experts") or _cfg_get(cfg, "num_local_experts"),
-                  moe_intermediate_size=_cfg_get(cfg, "moe_intermediate_size") or _cfg_get(cfg, "intermediate_size"),
-                  num_shared_experts=int(_cfg_get(cfg, "num_shared_experts", 0) or (1 if _cfg_get(cfg, "shared_expert_intermediate_size") else 0)),
-                  num_experts_per_tok=_cfg_get(cfg, "num_experts_per_tok", 2), norm_topk_prob=bool(_cfg_get(cfg, "norm_topk_prob", False)),
-                  rms_norm_eps=_cfg_get(cfg, "rms_norm_eps", 1e-6), rope_theta=_cfg_get(cfg, "rope_theta", 1e6),
+                  moe_intermediate_size=_cfg_get(cfg, "moe_intermediate_size") if mtype != "mixtral" else _cfg_get(cfg, "intermediate_size"),
+                  num_shared_experts=1 if shared else 0, shared_intermediate_size=shared or None, shared_expert_gate=bool(shared),
+                  attention_bias=mtype == "qwen2_moe", head_dim=_cfg_get(cfg, "head_dim"),
+                  num_experts_per_tok=_cfg_get(cfg, "num_experts_per_tok", 2),
+                  norm_topk_prob=bool(_cfg_get(cfg, "norm_topk_prob", mtype == "mixtral")) or mtype == "mixtral",
+                  rms_norm_eps=_cfg_get(cfg, "rms_norm_eps", 1e-6), rope_theta=_rope_theta(cfg, 1e6),
                   max_position_embeddings=_cfg_get(cfg, "max_position_embeddings", 4096))
+    if mtype == "qwen3_moe":
+        raise NotImplementedError("qwen3_moe needs per-head q/k norms in the MoE attention block (not wired yet)")
     return MoEForCausalLM(c, dtype=opt.get("dtype", torch.bfloat16), device=opt.get("device"))
 
 
@@ -74,6 +121,45 @@ for _t in LLAMA_LIKE:
 for _t in MOE_LIKE:
     register_family(_t, _build_moe)
 register_family("gpt2", _build_gpt2)
+
+
+def _convert_state_dict(mtype: str, sd: dict, out: torch.nn.Module) -> dict:
+    """Rename / split / pad a Hugging Face state dict so that it loads into the framework model with ``strict=True``."""
+    if mtype == "gpt2":
+        from ..models.gpt2 import from_hf_state_dict
+        sd = from_hf_state_dict(sd)
+        pad = out.wte.weight.shape[0] - sd["wte.weight"].shape[0]
+        if pad > 0:
+            sd["wte.weight"] = torch.cat([sd["wte.weight"], sd["wte.weight"].new_zeros(pad, sd["wte.weight"].shape[1])])
+        return {k: v for k, v in sd.items() if not k.endswith(".attn.bias") and not k.endswith(".attn.masked_bias")}
+    res: dict[str, torch.Tensor] = {}
+    moe = mtype in MOE_LIKE
+    for k, v in sd.items():
+        if "rotary_emb" in k:
+            continue
+        if moe:
+            k = k.removeprefix("model.")
+        if mtype == "phi3" and k.endswith("self_attn.qkv_proj.weight"):
+            cfg = out.config
+            nq, nkv = cfg.num_attention_heads * cfg.hd, cfg.num_key_value_heads * cfg.hd
+            base = k[: -len("qkv_proj.weight")]
+            res[base + "q_proj.weight"], res[base + "k_proj.weight"], res[base + "v_proj.weight"] = v[:nq], v[nq:nq + nkv], v[nq + nkv:]
+            continue
+        if mtype == "phi3" and k.endswith("mlp.gate_up_proj.weight"):
+            half = v.shape[0] // 2
+            base = k[: -len("gate_up_proj.weight")]
+            res[base + "gate_proj.weight"], res[base + "up_proj.weight"] = v[:half], v[half:]
+            continue
+        if moe and (k.endswith("mlp.gate.weight") or k.endswith("mlp.shared_expert_gate.weight")):
+            rows = out.config.padded_experts if k.endswith("mlp.gate.weight") else 8
+            v = torch.cat([v, v.new_zeros(rows - v.shape[0], v.shape[1])]) if v.shape[0] < rows else v
+        res[k] = v
+    tied = getattr(out.config, "tie_word_embeddings", False)
+    if "lm_head.weight" not in res:
+        emb = "embed_tokens.weight" if moe else "model.embed_tokens.weight"
+        if tied or emb in res:
+            res["lm_head.weight"] = res[emb]
+    return res
 
 
 def supported_families() -> list[str]:
@@ -85,26 +171,27 @@ def _is_framework_model(model: Any) -> bool:
 
 
 def apply_transformers_model_patches(model: Any, *, performance: bool = True, compat: bool = True, **kw: Any):
-    """Convert a Hugging Face model (or bare config) of a registered family into the framework's model."""
+    """Convert a Hugging Face model (or bare config) of a registered family into the framework's model.
+
+    The converted state dict must load with ``strict=True`` (every weight of the source has a place, every parameter of
+    the target gets a value); families whose blocks differ from the modules here raise ``NotImplementedError`` with the
+    reason instead of converting approximately.
+    """
     if _is_framework_model(model):
         return model
     cfg = getattr(model, "config", model)
     mtype = _cfg_get(cfg, "model_type")
+    if mtype in UNSUPPORTED:
+        raise NotImplementedError(f"model_type {mtype!r} is not converted: {UNSUPPORTED[mtype]}")
     if mtype not in _FAMILIES:
         raise ValueError(f"model_type {mtype!r} has no registered family; known: {supported_families()}")
     out = _FAMILIES[mtype](cfg, kw)
     if isinstance(model, torch.nn.Module):
-        sd = model.state_dict()
-        if mtype == "gpt2":
-            from ..models.gpt2 import from_hf_state_dict
-            sd = from_hf_state_dict(sd)
-            pad = out.wte.weight.shape[0] - sd["wte.weight"].shape[0]
-            if pad > 0:
-                sd["wte.weight"] = torch.cat([sd["wte.weight"], sd["wte.weight"].new_zeros(pad, sd["wte.weight"].shape[1])])
+        sd = _convert_state_dict(mtype, dict(model.state_dict()), out)
         missing, unexpected = out.load_state_dict(sd, strict=False)
-        real_missing = [k for k in missing if "rope_" not in k]
-        if real_missing and kw.get("strict", True):
-            raise ValueError(f"weights missing for {real_missing[:5]} ... while converting {mtype}")
+        missing = [k for k in missing if "rope_" not in k]
+        if (missing or unexpected) and kw.get("strict", True):
+            raise ValueError(f"converting {mtype}: missing {missing[:5]}, unexpected {list(unexpected)[:5]}")
     return out
 
 

@@ -1,0 +1,58 @@
+"""Converted Hugging Face models (tiny random-init configs, no downloads) give the source model's logits on CPU."""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from opaque_b200 import patches  # noqa: E402
+
+COMMON = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              max_position_embeddings=128)
+
+
+def _cases():
+    T = transformers
+    yield "llama", T.LlamaConfig(**COMMON, tie_word_embeddings=False), T.LlamaForCausalLM
+    yield "llama-tied", T.LlamaConfig(**COMMON, tie_word_embeddings=True), T.LlamaForCausalLM
+    yield "mistral", T.MistralConfig(**COMMON, sliding_window=4096), T.MistralForCausalLM
+    yield "qwen2", T.Qwen2Config(**COMMON), T.Qwen2ForCausalLM
+    yield "qwen3", T.Qwen3Config(**COMMON, head_dim=16), T.Qwen3ForCausalLM
+    yield "gemma", T.GemmaConfig(**COMMON, head_dim=16), T.GemmaForCausalLM
+    yield "phi3", T.Phi3Config(**COMMON, pad_token_id=0), T.Phi3ForCausalLM
+    yield "gpt2", T.GPT2Config(vocab_size=320, n_positions=128, n_embd=64, n_layer=2, n_head=4), T.GPT2LMHeadModel
+    yield "mixtral", T.MixtralConfig(**COMMON, num_local_experts=6, num_experts_per_tok=2), T.MixtralForCausalLM
+    yield "qwen2_moe", T.Qwen2MoeConfig(**COMMON, moe_intermediate_size=32, shared_expert_intermediate_size=48, num_experts=6,
+                                        num_experts_per_tok=2), T.Qwen2MoeForCausalLM
+
+
+@pytest.mark.parametrize("name,cfg,cls", list(_cases()), ids=[c[0] for c in _cases()])
+def test_converted_model_matches_hf_logits(name, cfg, cls):
+    torch.manual_seed(0)
+    hf = cls(cfg).eval().float()
+    ours = patches.apply_model_patches(hf, dtype=torch.float32).eval()
+    ids = torch.randint(0, 320, (2, 24))
+    with torch.no_grad():
+        want = hf(ids).logits
+        got = ours(ids)
+    got = got[..., :want.shape[-1]]                      # GPT-2 pads its vocabulary to a multiple of 64
+    assert got.shape == want.shape
+    assert float((got - want).abs().max()) < 2e-4 * max(1.0, float(want.abs().max())), name
+    # and the per-example loss is the usual shifted mean NLL
+    labels = torch.full_like(ids, -100)
+    labels[:, :-1] = ids[:, 1:]
+    ref = torch.stack([torch.nn.functional.cross_entropy(want[i, :-1], ids[i, 1:]) for i in range(2)])
+    assert torch.allclose(ours.per_example_loss(ids, labels), ref, atol=2e-4)
+
+
+def test_unsupported_families_are_refused_with_a_reason():
+    with pytest.raises(NotImplementedError, match="soft-capping"):
+        patches.apply_model_patches(transformers.Gemma2Config(**COMMON, head_dim=16))
+    with pytest.raises(ValueError, match="no registered family"):
+        patches.apply_model_patches({"model_type": "not_a_model"})
+
+
+def test_lora_attach_through_the_patch_api():
+    hf = transformers.LlamaForCausalLM(transformers.LlamaConfig(**COMMON)).float()
+    m = patches.apply_model_patches(hf, dtype=torch.float32, r=8, lora_alpha=16, target_modules=("q_proj", "v_proj"))
+    names = [n for n, p in m.named_parameters() if p.requires_grad]
+    assert names and all("lora_" in n for n in names) and any("q_proj" in n for n in names) and not any("k_proj" in n for n in names)

@@ -44,6 +44,11 @@ class LlamaConfig:
     embedding_scale: float = 1.0
     qk_norm: bool = False
     sliding_window: int | None = None        # accepted when sequences are not longer than the window
+    # Granite multipliers and SmolLM3 layers without rotary embedding
+    attention_multiplier: float | None = None      # softmax scale (default 1/sqrt(head_dim))
+    residual_multiplier: float = 1.0
+    logits_scaling: float = 1.0                     # logits are divided by this
+    no_rope_layers: tuple[int, ...] | None = None   # per layer: 1 = rotary embedding applied, 0 = not
 
     @property
     def hd(self) -> int:
@@ -65,8 +70,10 @@ class LlamaConfig:
 
 
 class LlamaAttention(nn.Module):
-    def __init__(self, cfg: LlamaConfig, dtype, device):
+    def __init__(self, cfg: LlamaConfig, dtype, device, layer_idx: int = 0):
         super().__init__()
+        self.scale = cfg.attention_multiplier
+        self.use_rope = cfg.no_rope_layers is None or bool(cfg.no_rope_layers[layer_idx])
         d, hd = cfg.hidden_size, cfg.hd
         self.nh, self.nkv, self.hd = cfg.num_attention_heads, cfg.num_key_value_heads, hd
         self.q_proj = Linear(d, self.nh * hd, bias=cfg.attention_bias, dtype=dtype, device=device)
@@ -89,9 +96,10 @@ class LlamaAttention(nn.Module):
         v = self.v_proj(x).view(B, T, self.nkv, self.hd)
         if self.q_norm is not None:
             q, k = self.q_norm(q), self.k_norm(k)
-        q, k = ops.rope_qk(q, k, cos, sin, pos)
+        if self.use_rope:
+            q, k = ops.rope_qk(q, k, cos, sin, pos)
         o = nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
-                                                       is_causal=True, enable_gqa=self.nkv != self.nh)
+                                                       is_causal=True, enable_gqa=self.nkv != self.nh, scale=self.scale)
         return self.o_proj(o.transpose(1, 2).reshape(B, T, self.nh * self.hd))
 
 
@@ -114,17 +122,20 @@ class LlamaMLP(nn.Module):
 
 
 class LlamaDecoderLayer(nn.Module):
-    def __init__(self, cfg: LlamaConfig, dtype, device):
+    def __init__(self, cfg: LlamaConfig, dtype, device, layer_idx: int = 0):
         super().__init__()
+        self.res = cfg.residual_multiplier
         nk = dict(offset=cfg.norm_offset, casting_mode=cfg.norm_casting, dtype=dtype, device=device)
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
-        self.self_attn = LlamaAttention(cfg, dtype, device)
+        self.self_attn = LlamaAttention(cfg, dtype, device, layer_idx)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
         self.mlp = LlamaMLP(cfg, dtype, device)
 
     def forward(self, h, cos, sin, pos):
+        if self.res != 1.0:
+            h = h + self.res * self.self_attn(self.input_layernorm(h), cos, sin, pos)
+            return h + self.res * self.mlp(self.post_attention_layernorm(h))
         h = h + self.self_attn(self.input_layernorm(h), cos, sin, pos)
-        # fused residual add + norm: (y, s) with s = attention output + residual
         return h + self.mlp(self.post_attention_layernorm(h))
 
 
@@ -132,7 +143,7 @@ class LlamaModel(nn.Module):
     def __init__(self, cfg: LlamaConfig, dtype, device):
         super().__init__()
         self.embed_tokens = Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
-        self.layers = nn.ModuleList(LlamaDecoderLayer(cfg, dtype, device) for _ in range(cfg.num_hidden_layers))
+        self.layers = nn.ModuleList(LlamaDecoderLayer(cfg, dtype, device, i) for i in range(cfg.num_hidden_layers))
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, offset=cfg.norm_offset, casting_mode=cfg.norm_casting,
                             dtype=dtype, device=device)
 
@@ -173,7 +184,8 @@ class LlamaForCausalLM(nn.Module):
                                                       use_reentrant=False)
             else:
                 h = layer(h, self.rope_cos, self.rope_sin, position_ids)
-        return self.model.norm(h)
+        h = self.model.norm(h)
+        return h if self.config.logits_scaling == 1.0 else h / self.config.logits_scaling     # logits = (h / s) Wᵀ
 
     def forward(self, input_ids, position_ids=None):
         return self.lm_head(self.hidden_states(input_ids, position_ids))

@@ -47,6 +47,7 @@ class MoEConfig:
     shared_expert_gate: bool = False
     shared_intermediate_size: int | None = None
     head_dim: int | None = None
+    qk_norm: bool = False
 
     @property
     def padded_experts(self) -> int:
@@ -56,7 +57,7 @@ class MoEConfig:
         return LlamaConfig(vocab_size=self.vocab_size, hidden_size=self.hidden_size, num_attention_heads=self.num_attention_heads,
                            num_key_value_heads=self.num_key_value_heads, rms_norm_eps=self.rms_norm_eps,
                            rope_theta=self.rope_theta, max_position_embeddings=self.max_position_embeddings,
-                           attention_bias=self.attention_bias, head_dim=self.head_dim,
+                           attention_bias=self.attention_bias, head_dim=self.head_dim, qk_norm=self.qk_norm,
                            intermediate_size=self.shared_intermediate_size or self.moe_intermediate_size * max(self.num_shared_experts, 1))
 
     @staticmethod

@@ -25,7 +25,7 @@ _RUNTIME = {"patched": False}
 
 # model_type -> family builder.  Only families whose block structure these modules reproduce exactly are registered;
 # the others are listed with the reason, so a conversion can never silently drop a feature of the architecture.
-LLAMA_LIKE = ("llama", "mistral", "ministral", "mellum", "qwen2", "qwen3", "gemma", "phi3")
+LLAMA_LIKE = ("llama", "mistral", "ministral", "mellum", "qwen2", "qwen3", "gemma", "phi3", "granite", "smollm3")
 MOE_LIKE = ("mixtral", "qwen2_moe", "qwen3_moe")
 UNSUPPORTED = {
     "gemma2": "post-attention / post-feed-forward norms, attention and final logit soft-capping, alternating local attention",
@@ -33,7 +33,6 @@ UNSUPPORTED = {
     "cohere": "LayerNorm, parallel attention + MLP block, logit scale", "cohere2": "as cohere plus sliding-window layers",
     "olmo2": "norms after the sub-layers (post-norm) and q/k norms over the full projection", "olmo3": "as olmo2 plus sliding windows",
     "glm4": "extra post-sub-layer norms and partial rotary embedding", "exaone4": "hybrid local/global attention with post-norms",
-    "granite": "embedding / residual / attention / logit multipliers", "smollm3": "layers without rotary embedding",
     "gpt_oss": "attention sinks, clamped SwiGLU with biases, alternating sliding windows",
     "deepseek_v4": "multi-head latent attention", "hunyuan_v1_moe": "q/k norms and a mixed shared-expert layout",
     "qwen3_next": "gated delta-net layers", "qwen3_5_moe": "gated delta-net layers",
@@ -68,6 +67,14 @@ def _build_llama(cfg: Any, opt: dict) -> torch.nn.Module:
         extra.update(attention_bias=True)
     elif mtype == "qwen3":
         extra.update(qk_norm=True, attention_bias=bool(_cfg_get(cfg, "attention_bias", False)))
+    elif mtype == "granite":
+        extra.update(attention_bias=bool(_cfg_get(cfg, "attention_bias", False)), attention_out_bias=bool(_cfg_get(cfg, "attention_bias", False)),
+                     mlp_bias=bool(_cfg_get(cfg, "mlp_bias", False)), embedding_scale=float(_cfg_get(cfg, "embedding_multiplier", 1.0)),
+                     attention_multiplier=float(_cfg_get(cfg, "attention_multiplier", 1.0)),
+                     residual_multiplier=float(_cfg_get(cfg, "residual_multiplier", 1.0)), logits_scaling=float(_cfg_get(cfg, "logits_scaling", 1.0)))
+    elif mtype == "smollm3":
+        extra.update(attention_bias=bool(_cfg_get(cfg, "attention_bias", False)), attention_out_bias=bool(_cfg_get(cfg, "attention_bias", False)),
+                     mlp_bias=bool(_cfg_get(cfg, "mlp_bias", False)), no_rope_layers=tuple(int(x) for x in _cfg_get(cfg, "no_rope_layers")))
     elif mtype == "gemma":
         extra.update(hidden_act=_cfg_get(cfg, "hidden_activation") or _cfg_get(cfg, "hidden_act", "gelu_pytorch_tanh"), norm_offset=1.0,
                      norm_casting="gemma", embedding_scale=float(_cfg_get(cfg, "hidden_size")) ** 0.5)
@@ -106,13 +113,11 @@ def _build_moe(cfg: Any, opt: dict) -> torch.nn.Module:
                   num_experts=_cfg_get(cfg, "num_experts") or _cfg_get(cfg, "num_local_experts"),
                   moe_intermediate_size=_cfg_get(cfg, "moe_intermediate_size") if mtype != "mixtral" else _cfg_get(cfg, "intermediate_size"),
                   num_shared_experts=1 if shared else 0, shared_intermediate_size=shared or None, shared_expert_gate=bool(shared),
-                  attention_bias=mtype == "qwen2_moe", head_dim=_cfg_get(cfg, "head_dim"),
+                  attention_bias=mtype == "qwen2_moe", head_dim=_cfg_get(cfg, "head_dim"), qk_norm=mtype == "qwen3_moe",
                   num_experts_per_tok=_cfg_get(cfg, "num_experts_per_tok", 2),
                   norm_topk_prob=bool(_cfg_get(cfg, "norm_topk_prob", mtype == "mixtral")) or mtype == "mixtral",
                   rms_norm_eps=_cfg_get(cfg, "rms_norm_eps", 1e-6), rope_theta=_rope_theta(cfg, 1e6),
                   max_position_embeddings=_cfg_get(cfg, "max_position_embeddings", 4096))
-    if mtype == "qwen3_moe":
-        raise NotImplementedError("qwen3_moe needs per-head q/k norms in the MoE attention block (not wired yet)")
     return MoEForCausalLM(c, dtype=opt.get("dtype", torch.bfloat16), device=opt.get("device"))
 
 

@@ -19,6 +19,10 @@ def _cases():
     yield "qwen3", T.Qwen3Config(**COMMON, head_dim=16), T.Qwen3ForCausalLM
     yield "gemma", T.GemmaConfig(**COMMON, head_dim=16), T.GemmaForCausalLM
     yield "phi3", T.Phi3Config(**COMMON, pad_token_id=0), T.Phi3ForCausalLM
+    yield "granite", T.GraniteConfig(**COMMON, embedding_multiplier=6.0, attention_multiplier=0.11, residual_multiplier=0.4, logits_scaling=3.0), T.GraniteForCausalLM
+    yield "smollm3", T.SmolLM3Config(**COMMON, no_rope_layers=[1, 0], pad_token_id=0), T.SmolLM3ForCausalLM
+    yield "qwen3_moe", T.Qwen3MoeConfig(**COMMON, moe_intermediate_size=32, num_experts=6, num_experts_per_tok=2, head_dim=16,
+                                        norm_topk_prob=True), T.Qwen3MoeForCausalLM
     yield "gpt2", T.GPT2Config(vocab_size=320, n_positions=128, n_embd=64, n_layer=2, n_head=4), T.GPT2LMHeadModel
     yield "mixtral", T.MixtralConfig(**COMMON, num_local_experts=6, num_experts_per_tok=2), T.MixtralForCausalLM
     yield "qwen2_moe", T.Qwen2MoeConfig(**COMMON, moe_intermediate_size=32, shared_expert_intermediate_size=48, num_experts=6,

@@ -49,6 +49,9 @@ class LlamaConfig:
     residual_multiplier: float = 1.0
     logits_scaling: float = 1.0                     # logits are divided by this
     no_rope_layers: tuple[int, ...] | None = None   # per layer: 1 = rotary embedding applied, 0 = not
+    # OLMo-2: norms AFTER the sub-layers (h + norm(f(h))) and q/k norms over the whole projection
+    post_norm: bool = False
+    qk_norm_full: bool = False
 
     @property
     def hd(self) -> int:
@@ -81,7 +84,11 @@ class LlamaAttention(nn.Module):
         self.v_proj = Linear(d, self.nkv * hd, bias=cfg.attention_bias, dtype=dtype, device=device)
         self.o_proj = Linear(self.nh * hd, d, bias=cfg.attention_out_bias, dtype=dtype, device=device)
         self.window = cfg.sliding_window
-        if cfg.qk_norm:
+        self.qk_full = cfg.qk_norm_full
+        if cfg.qk_norm_full:
+            self.q_norm = RMSNorm(self.nh * hd, cfg.rms_norm_eps, dtype=dtype, device=device)
+            self.k_norm = RMSNorm(self.nkv * hd, cfg.rms_norm_eps, dtype=dtype, device=device)
+        elif cfg.qk_norm:
             self.q_norm = RMSNorm(hd, cfg.rms_norm_eps, offset=cfg.norm_offset, casting_mode=cfg.norm_casting, dtype=dtype, device=device)
             self.k_norm = RMSNorm(hd, cfg.rms_norm_eps, offset=cfg.norm_offset, casting_mode=cfg.norm_casting, dtype=dtype, device=device)
         else:
@@ -91,10 +98,12 @@ class LlamaAttention(nn.Module):
         B, T, _ = x.shape
         if self.window is not None and T > self.window:
             raise NotImplementedError(f"sequence length {T} exceeds the sliding window {self.window}: windowed attention is not implemented")
-        q = self.q_proj(x).view(B, T, self.nh, self.hd)
-        k = self.k_proj(x).view(B, T, self.nkv, self.hd)
+        q, k = self.q_proj(x), self.k_proj(x)
+        if self.qk_full:
+            q, k = self.q_norm(q), self.k_norm(k)
+        q, k = q.view(B, T, self.nh, self.hd), k.view(B, T, self.nkv, self.hd)
         v = self.v_proj(x).view(B, T, self.nkv, self.hd)
-        if self.q_norm is not None:
+        if self.q_norm is not None and not self.qk_full:
             q, k = self.q_norm(q), self.k_norm(k)
         if self.use_rope:
             q, k = ops.rope_qk(q, k, cos, sin, pos)
@@ -126,12 +135,19 @@ class LlamaDecoderLayer(nn.Module):
         super().__init__()
         self.res = cfg.residual_multiplier
         nk = dict(offset=cfg.norm_offset, casting_mode=cfg.norm_casting, dtype=dtype, device=device)
-        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
+        self.post_norm = cfg.post_norm
+        if cfg.post_norm:
+            self.post_feedforward_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
+        else:
+            self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
         self.self_attn = LlamaAttention(cfg, dtype, device, layer_idx)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
         self.mlp = LlamaMLP(cfg, dtype, device)
 
     def forward(self, h, cos, sin, pos):
+        if self.post_norm:
+            h = h + self.post_attention_layernorm(self.self_attn(h, cos, sin, pos))
+            return h + self.post_feedforward_layernorm(self.mlp(h))
         if self.res != 1.0:
             h = h + self.res * self.self_attn(self.input_layernorm(h), cos, sin, pos)
             return h + self.res * self.mlp(self.post_attention_layernorm(h))

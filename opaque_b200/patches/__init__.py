@@ -25,13 +25,13 @@ _RUNTIME = {"patched": False}
 
 # model_type -> family builder.  Only families whose block structure these modules reproduce exactly are registered;
 # the others are listed with the reason, so a conversion can never silently drop a feature of the architecture.
-LLAMA_LIKE = ("llama", "mistral", "ministral", "mellum", "qwen2", "qwen3", "gemma", "phi3", "granite", "smollm3")
+LLAMA_LIKE = ("llama", "mistral", "ministral", "mellum", "qwen2", "qwen3", "gemma", "phi3", "granite", "smollm3", "olmo2")
 MOE_LIKE = ("mixtral", "qwen2_moe", "qwen3_moe")
 UNSUPPORTED = {
     "gemma2": "post-attention / post-feed-forward norms, attention and final logit soft-capping, alternating local attention",
     "gemma3": "as gemma2 plus per-layer rope bases and q/k norms",
     "cohere": "LayerNorm, parallel attention + MLP block, logit scale", "cohere2": "as cohere plus sliding-window layers",
-    "olmo2": "norms after the sub-layers (post-norm) and q/k norms over the full projection", "olmo3": "as olmo2 plus sliding windows",
+    "olmo3": "olmo2 blocks plus sliding-window layers",
     "glm4": "extra post-sub-layer norms and partial rotary embedding", "exaone4": "hybrid local/global attention with post-norms",
     "gpt_oss": "attention sinks, clamped SwiGLU with biases, alternating sliding windows",
     "deepseek_v4": "multi-head latent attention", "hunyuan_v1_moe": "q/k norms and a mixed shared-expert layout",
@@ -72,6 +72,9 @@ def _build_llama(cfg: Any, opt: dict) -> torch.nn.Module:
                      mlp_bias=bool(_cfg_get(cfg, "mlp_bias", False)), embedding_scale=float(_cfg_get(cfg, "embedding_multiplier", 1.0)),
                      attention_multiplier=float(_cfg_get(cfg, "attention_multiplier", 1.0)),
                      residual_multiplier=float(_cfg_get(cfg, "residual_multiplier", 1.0)), logits_scaling=float(_cfg_get(cfg, "logits_scaling", 1.0)))
+    elif mtype == "olmo2":
+        extra.update(attention_bias=bool(_cfg_get(cfg, "attention_bias", False)), attention_out_bias=bool(_cfg_get(cfg, "attention_bias", False)),
+                     post_norm=True, qk_norm_full=True)
     elif mtype == "smollm3":
         extra.update(attention_bias=bool(_cfg_get(cfg, "attention_bias", False)), attention_out_bias=bool(_cfg_get(cfg, "attention_bias", False)),
                      mlp_bias=bool(_cfg_get(cfg, "mlp_bias", False)), no_rope_layers=tuple(int(x) for x in _cfg_get(cfg, "no_rope_layers")))

@@ -20,6 +20,7 @@ def _cases():
     yield "gemma", T.GemmaConfig(**COMMON, head_dim=16), T.GemmaForCausalLM
     yield "phi3", T.Phi3Config(**COMMON, pad_token_id=0), T.Phi3ForCausalLM
     yield "granite", T.GraniteConfig(**COMMON, embedding_multiplier=6.0, attention_multiplier=0.11, residual_multiplier=0.4, logits_scaling=3.0), T.GraniteForCausalLM
+    yield "olmo2", T.Olmo2Config(**COMMON, pad_token_id=0), T.Olmo2ForCausalLM
     yield "smollm3", T.SmolLM3Config(**COMMON, no_rope_layers=[1, 0], pad_token_id=0), T.SmolLM3ForCausalLM
     yield "qwen3_moe", T.Qwen3MoeConfig(**COMMON, moe_intermediate_size=32, num_experts=6, num_experts_per_tok=2, head_dim=16,
                                         norm_topk_prob=True), T.Qwen3MoeForCausalLM

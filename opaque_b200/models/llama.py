@@ -179,6 +179,8 @@ class LlamaForCausalLM(nn.Module):
         self.register_buffer("rope_sin", sin, persistent=False)
         self.activation_checkpointing = activation_checkpointing
         self.ce_chunk = 8192
+        # the multiplier is rounded to the parameter dtype once (as Gemma / Granite do), and stays a host scalar
+        self._emb_scale = float(torch.tensor(cfg.embedding_scale, dtype=dtype or torch.float32)) if cfg.embedding_scale != 1.0 else 1.0
 
     # ---- adapters ---------------------------------------------------------------------------
     def add_lora(self, r: int = 16, alpha: float = 32.0, targets=("q_proj", "k_proj", "v_proj", "o_proj")) -> None:
@@ -192,8 +194,8 @@ class LlamaForCausalLM(nn.Module):
     # ---- forward ------------------------------------------------------------------------------
     def hidden_states(self, input_ids: torch.Tensor, position_ids: torch.Tensor | None = None) -> torch.Tensor:
         h = self.model.embed_tokens(input_ids)
-        if self.config.embedding_scale != 1.0:
-            h = h * torch.tensor(self.config.embedding_scale, dtype=h.dtype, device=h.device)      # rounded like the weights
+        if self._emb_scale != 1.0:
+            h = h * self._emb_scale
         for layer in self.model.layers:
             if self.activation_checkpointing and torch.is_grad_enabled():
                 h = torch.utils.checkpoint.checkpoint(layer, h, self.rope_cos, self.rope_sin, position_ids,

@@ -74,6 +74,24 @@ def test_llama_full_parameter_untied_and_tied():
     _check(LlamaForCausalLM(cfg, device=dev), 512, 1.0, 1.0, 5e-3, 2e-2)
 
 
+@pytest.mark.parametrize("variant", [dict(attention_bias=True), dict(qk_norm=True, head_dim=32),
+                                     dict(hidden_act="gelu_pytorch_tanh", norm_offset=1.0, norm_casting="gemma", embedding_scale=128 ** 0.5),
+                                     dict(post_norm=True, qk_norm_full=True), dict(residual_multiplier=0.5, attention_multiplier=0.2, logits_scaling=2.0)])
+def test_llama_family_variants_full_parameter(variant):
+    """Qwen2 biases, Qwen3 q/k norms, Gemma GeGLU / (1+w) norms / scaled embeddings, OLMo-2 post-norm, Granite multipliers."""
+    from opaque_b200.models import LlamaConfig, LlamaForCausalLM
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(7)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=256, **variant)
+    m = LlamaForCausalLM(cfg, device=dev)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if n.endswith(".bias"):
+                p.normal_(0, 0.02)
+    _check(m, 512, 1.0, 1.0, 1e-2, 3e-2)
+
+
 def test_gpt2_full_parameter():
     from opaque_b200.models import GPT2Config, GPT2LMHeadModel
     dev = torch.device("cuda", 0)

@@ -108,6 +108,82 @@ class PrinterCallback(TrainerCallback):
             print({k: (round(v, 5) if isinstance(v, float) else v) for k, v in logs.items()}, flush=True)
 
 
+class JsonlLoggerCallback(TrainerCallback):
+    """``report_to="jsonl"``: append every log record to ``output_dir/metrics.jsonl`` (rank 0 only)."""
+
+    def on_log(self, args, state, control, logs=None, **kw):
+        if args.should_log and logs and args.output_dir:
+            os.makedirs(args.output_dir, exist_ok=True)
+            with open(os.path.join(args.output_dir, "metrics.jsonl"), "a") as f:
+                f.write(json.dumps({"step": state.global_step, **{k: v for k, v in logs.items() if isinstance(v, (int, float, str))}}) + "\n")
+
+
+class TensorBoardCallback(TrainerCallback):
+    """``report_to="tensorboard"``: scalars under ``logging_dir`` (or ``output_dir/runs``); privacy metrics keep their names."""
+
+    def __init__(self):
+        self.writer = None
+
+    def on_train_begin(self, args, state, control, **kw):
+        if not args.should_log:
+            return
+        from torch.utils.tensorboard import SummaryWriter
+        self.writer = SummaryWriter(log_dir=getattr(args, "logging_dir", None) or os.path.join(args.output_dir or ".", "runs"))
+
+    def on_log(self, args, state, control, logs=None, **kw):
+        if self.writer is not None and logs:
+            for k, v in logs.items():
+                if isinstance(v, (int, float)):
+                    self.writer.add_scalar(k if "/" in k else f"train/{k}", v, state.global_step)
+
+    def on_train_end(self, args, state, control, **kw):
+        if self.writer is not None:
+            self.writer.close()
+            self.writer = None
+
+
+class WandbCallback(TrainerCallback):
+    """``report_to="wandb"``: forwards log records to an existing or new W&B run (offline mode works without a network)."""
+
+    def __init__(self):
+        self.run = None
+
+    def on_train_begin(self, args, state, control, **kw):
+        if not args.should_log:
+            return
+        import wandb
+        self.run = wandb.run or wandb.init(project=os.environ.get("WANDB_PROJECT", "opaque_b200"), name=getattr(args, "run_name", None),
+                                          config={k: v for k, v in dataclasses.asdict(args).items() if isinstance(v, (int, float, str, bool))})
+
+    def on_log(self, args, state, control, logs=None, **kw):
+        if self.run is not None and logs:
+            self.run.log({k: v for k, v in logs.items() if isinstance(v, (int, float))}, step=state.global_step)
+
+
+REPORTERS = {"jsonl": JsonlLoggerCallback, "tensorboard": TensorBoardCallback, "wandb": WandbCallback}
+
+
+def reporting_callbacks(report_to: Any) -> list[TrainerCallback]:
+    """Callbacks for ``report_to`` (a name, a list of names, ``"none"`` / ``None``, or ``"all"`` = every importable one)."""
+    if report_to in (None, "none", [], ()):
+        return []
+    names = [report_to] if isinstance(report_to, str) else list(report_to)
+    if names == ["all"]:
+        names = ["jsonl"]
+        for mod, name in (("torch.utils.tensorboard", "tensorboard"), ("wandb", "wandb")):
+            try:
+                __import__(mod)
+                names.append(name)
+            except Exception:      # noqa: BLE001 — an optional integration that is not installed is skipped
+                pass
+    out = []
+    for n in names:
+        if n not in REPORTERS:
+            raise ValueError(f"report_to={n!r} is not supported; choose from {sorted(REPORTERS)}")
+        out.append(REPORTERS[n]())
+    return out
+
+
 class BestModelSaveCallback(TrainerCallback):
     """Track ``metric_for_best_model`` on every evaluation and remember the best checkpoint."""
 
@@ -261,7 +337,8 @@ class DPTrainer:
         self.optimizer_cls_and_kwargs = optimizer_cls_and_kwargs
         self.state = DPTrainerState()
         self.control = TrainerControl()
-        self.callbacks: list[TrainerCallback] = [PrinterCallback(), BestModelSaveCallback(), *(callbacks or [])]
+        self.callbacks: list[TrainerCallback] = [PrinterCallback(), BestModelSaveCallback(), *reporting_callbacks(self.args.report_to),
+                                                 *(callbacks or [])]
         if data_collator is None:
             from ..alignment.data import language_modeling_collator
             pad = getattr(processing_class, "pad_token_id", None) or 0

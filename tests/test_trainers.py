@@ -152,3 +152,12 @@ def test_sigterm_writes_a_just_in_time_checkpoint_and_stops(tmp_path):
         signal.signal(signal.SIGTERM, old)
     assert tr.state.global_step == 2
     assert [os.path.basename(c) for c in list_checkpoints(str(tmp_path))] == ["checkpoint-2"]
+
+
+def test_report_to_jsonl_writes_metrics(tmp_path):
+    tr = DPTrainer(model=TinyLM(), args=_args(tmp_path, max_steps=4, save_steps=0, report_to="jsonl"), train_dataset=_data())
+    tr.train()
+    rows = [json.loads(l) for l in open(os.path.join(str(tmp_path), "metrics.jsonl"))]
+    assert rows and any("epsilon" in r for r in rows) and all("step" in r for r in rows)
+    with pytest.raises(ValueError):
+        DPTrainer(model=TinyLM(), args=_args(tmp_path, report_to="carrier-pigeon"), train_dataset=_data())

@@ -595,7 +595,10 @@ class FusedDPEngine:
     def step(self, loss_fn: Callable[..., torch.Tensor], batch: dict[str, torch.Tensor], *,
              read_metrics: bool = True) -> StepResult:
         """One DP optimizer step: accumulate, then noise + AdamW-BC on the shards."""
-        res = self.accumulate(loss_fn, batch)
+        return self.apply(self.accumulate(loss_fn, batch), read_metrics=read_metrics)
+
+    def apply(self, res: StepResult, *, read_metrics: bool = True) -> StepResult:
+        """Second half of :meth:`step`: add noise to the accumulated clipped sum and update the parameters."""
         sens = self.sensitivity()
         sigma = 0.0 if self.noise_multiplier == 0 else self.noise_multiplier * sens
         self.opt.step(noise_std=sigma, normalize_by=self.normalize_by)
@@ -607,3 +610,15 @@ class FusedDPEngine:
         if self.adaptive is not None:
             self._adapt(res)
         return res
+
+    @torch.no_grad()
+    def reset_gradients(self) -> None:
+        """Discard everything accumulated since the last optimizer step on ALL ranks (call on every rank).
+
+        Used when an accumulation is abandoned half-way (out of memory agreed on by the cluster) and will be replayed.
+        """
+        self.group.barrier()                    # peers' reductions into this shard have landed
+        self.space.grad.local.zero_()
+        if self.space.grad_full is not None:
+            self.space.grad_full.zero_()
+        self.group.barrier()                    # nobody accumulates again before every shard is clean

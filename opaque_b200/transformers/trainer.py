@@ -743,7 +743,23 @@ class DPTrainer:
         if not self._graphs_ready and batch["input_ids"].shape[0]:
             self._fused.prepare_graphs(self.model.per_example_loss, {"input_ids": batch["input_ids"], "labels": batch["labels"]})
             self._graphs_ready = True
-        res = self._fused.step(self.model.per_example_loss, {"input_ids": batch["input_ids"], "labels": batch["labels"]})
+        payload = {"input_ids": batch["input_ids"], "labels": batch["labels"]}
+        while True:                                   # cluster-wide agreement on out-of-memory, then a smaller microbatch
+            oom = False
+            try:
+                res = self._fused.accumulate(self.model.per_example_loss, payload)
+            except Exception as exc:      # noqa: BLE001 — only OOM is swallowed
+                if not _is_retryable_oom(exc):
+                    raise
+                oom = True
+            if not self._cluster_flag(oom):
+                break
+            if self._fused.microbatch_size <= 1:
+                raise torch.OutOfMemoryError("out of memory at microbatch size 1")
+            torch.cuda.empty_cache()
+            self._fused.reset_gradients()
+            self._fused.microbatch_size = self._microbatch = max(1, self._fused.microbatch_size // 2)
+        res = self._fused.apply(res)
         sp.mark("optimizer")
         self._call("on_optimizer_step")
         n = int(reduce_scalar(res.batch_size, "sum")) if is_distributed() else res.batch_size

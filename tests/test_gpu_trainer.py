@@ -58,3 +58,21 @@ def test_fused_trainer_options(tmp_path, kw):
     tr = DPTrainer(model=_model(lora=kw.get("privacy_noise_mechanism") is None), args=_args(tmp_path, save_steps=0, **kw), train_dataset=_rows())
     out = tr.train()
     assert tr.engine_kind == "fused" and out["global_step"] == 4 and math.isfinite(tr.state.log_history[-2]["loss"])
+
+
+def test_fused_trainer_steps_down_after_a_simulated_oom(tmp_path):
+    """The failure is injected on the host: the loss raises OutOfMemoryError once for a microbatch of more than 4 rows."""
+    from opaque_b200.transformers import DPTrainer
+    model = _model()
+    inner, fired = model.per_example_loss, []
+
+    def flaky(input_ids, labels, **kw):
+        if input_ids.shape[0] > 4 and not fired:
+            fired.append(1)
+            raise torch.OutOfMemoryError("simulated")
+        return inner(input_ids, labels, **kw)
+    model.per_example_loss = flaky
+    tr = DPTrainer(model=model, args=_args(tmp_path, save_steps=0, per_device_train_batch_size=16, microbatch_size=8), train_dataset=_rows())
+    out = tr.train()
+    assert fired and out["global_step"] == 4 and tr._fused.microbatch_size == 4
+    assert float(tr._fused.space.grad.local.abs().max()) == 0.0          # consumed by the last step, nothing left over

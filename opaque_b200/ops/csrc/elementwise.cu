@@ -110,6 +110,108 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
+// Register-resident variants for the common widths (H = 128 * 8 * VPT, VPT in {1, 2, 4, 8}): 128 threads own one row
+// and keep it in registers, two rows per CTA; one global read and one write per element, one shared-memory exchange.
+constexpr int RN_ROW_THREADS = 128;
+
+__device__ __forceinline__ float row_group_sum(float v, float* red) {     // red: 4 floats of this row group
+  v = warp_sum(v);
+  const int w = (threadIdx.x & (RN_ROW_THREADS - 1)) >> 5;
+  if ((threadIdx.x & 31) == 0) red[w] = v;
+  __syncthreads();
+  const float t = red[0] + red[1] + red[2] + red[3];
+  __syncthreads();
+  return t;
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(2 * RN_ROW_THREADS)
+rmsnorm_fwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                       __nv_bfloat16* __restrict__ sum_out, float* __restrict__ rstd, long long rows, float eps,
+                       float offset, int mode) {
+  constexpr int H = RN_ROW_THREADS * 8 * VPT;
+  __shared__ float red_all[2][4];
+  const int grp = threadIdx.x / RN_ROW_THREADS, t = threadIdx.x % RN_ROW_THREADS;
+  const long long row = static_cast<long long>(blockIdx.x) * 2 + grp;
+  const bool live = row < rows;
+  const long long r = live ? row : rows - 1;               // dead group mirrors the last row (keeps the barriers uniform)
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + r * H);
+  float f[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    unpack8(xr[t + v * RN_ROW_THREADS], f[v]);
+    if (residual != nullptr) {
+      float g[8];
+      unpack8(reinterpret_cast<const bf16x8*>(residual + r * H)[t + v * RN_ROW_THREADS], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[v][j] += g[j];
+      const bf16x8 sv = pack8(f[v]);
+      if (live) reinterpret_cast<bf16x8*>(sum_out + r * H)[t + v * RN_ROW_THREADS] = sv;
+      unpack8(sv, f[v]);                                    // the normalised tensor is the stored (rounded) sum
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[v][j] * f[v][j];
+  }
+  const float rs = rsqrtf(row_group_sum(ss, red_all[grp]) / H + eps);
+  if (live && t == 0) rstd[row] = rs;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    float g[8];
+    unpack8(reinterpret_cast<const bf16x8*>(w)[t + v * RN_ROW_THREADS], g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float n = f[v][j] * rs;
+      if (mode == 0) n = __bfloat162float(__float2bfloat16_rn(n));
+      f[v][j] = n * (offset + g[j]);
+    }
+    if (live) reinterpret_cast<bf16x8*>(y + r * H)[t + v * RN_ROW_THREADS] = pack8(f[v]);
+  }
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(2 * RN_ROW_THREADS)
+rmsnorm_bwd_dx_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                          const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                          const __nv_bfloat16* __restrict__ dsum_in, __nv_bfloat16* __restrict__ dx, long long rows,
+                          float offset) {
+  constexpr int H = RN_ROW_THREADS * 8 * VPT;
+  __shared__ float red_all[2][4];
+  const int grp = threadIdx.x / RN_ROW_THREADS, t = threadIdx.x % RN_ROW_THREADS;
+  const long long row = static_cast<long long>(blockIdx.x) * 2 + grp;
+  const bool live = row < rows;
+  const long long r = live ? row : rows - 1;
+  const float rs = rstd[r];
+  float gw[VPT][8], xv[VPT][8];
+  float dot = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    float c[8];
+    unpack8(reinterpret_cast<const bf16x8*>(dy + r * H)[t + v * RN_ROW_THREADS], gw[v]);
+    unpack8(reinterpret_cast<const bf16x8*>(x + r * H)[t + v * RN_ROW_THREADS], xv[v]);
+    unpack8(reinterpret_cast<const bf16x8*>(w)[t + v * RN_ROW_THREADS], c);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      gw[v][j] *= (offset + c[j]);
+      dot += gw[v][j] * xv[v][j];
+    }
+  }
+  const float mean = row_group_sum(dot, red_all[grp]) * rs * rs / H;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    float d[8];
+    if (dsum_in != nullptr) unpack8(reinterpret_cast<const bf16x8*>(dsum_in + r * H)[t + v * RN_ROW_THREADS], d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float g = rs * (gw[v][j] - xv[v][j] * mean);
+      if (dsum_in != nullptr) g += d[j];
+      gw[v][j] = g;
+    }
+    if (live) reinterpret_cast<bf16x8*>(dx + r * H)[t + v * RN_ROW_THREADS] = pack8(gw[v]);
+  }
+}
+
 // dx (and d residual, which equals dx plus the incoming gradient of the sum stream).
 __global__ void __launch_bounds__(RN_THREADS)
 rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
@@ -412,10 +514,18 @@ extern "C" int ob_rmsnorm_fwd(const void* x, const void* residual, const void* w
                               float* rstd, long long rows, int H, float eps, float offset, int mode, void* stream) {
   if (rows <= 0) return 0;
   if (H % 8) return -2;
-  rmsnorm_fwd_kernel<<<static_cast<unsigned>(rows), RN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
-      static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(sum_out),
-      rstd, H, eps, offset, mode);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16 *xp = static_cast<const __nv_bfloat16*>(x), *rp = static_cast<const __nv_bfloat16*>(residual),
+                      *wp = static_cast<const __nv_bfloat16*>(w);
+  __nv_bfloat16 *yp = static_cast<__nv_bfloat16*>(y), *sp = static_cast<__nv_bfloat16*>(sum_out);
+  const unsigned pairs = static_cast<unsigned>((rows + 1) / 2);
+#define OB_RN_FWD(V) rmsnorm_fwd_reg_kernel<V><<<pairs, 2 * RN_ROW_THREADS, 0, st>>>(xp, rp, wp, yp, sp, rstd, rows, eps, offset, mode)
+  if (H == 1024) OB_RN_FWD(1);
+  else if (H == 2048) OB_RN_FWD(2);
+  else if (H == 4096) OB_RN_FWD(4);
+  else if (H == 8192) OB_RN_FWD(8);
+  else rmsnorm_fwd_kernel<<<static_cast<unsigned>(rows), RN_THREADS, 0, st>>>(xp, rp, wp, yp, sp, rstd, H, eps, offset, mode);
+#undef OB_RN_FWD
   return OB_CHECK_LAUNCH();
 }
 
@@ -425,11 +535,19 @@ extern "C" int ob_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
   if (rows <= 0) return 0;
   if (H % 8) return -2;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dx != nullptr)
-    rmsnorm_bwd_dx_kernel<<<static_cast<unsigned>(rows), RN_THREADS, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
-        static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dsum_in),
-        static_cast<__nv_bfloat16*>(dx), H, offset);
+  if (dx != nullptr) {
+    const __nv_bfloat16 *gp = static_cast<const __nv_bfloat16*>(dy), *xp = static_cast<const __nv_bfloat16*>(x),
+                        *wp = static_cast<const __nv_bfloat16*>(w), *dp = static_cast<const __nv_bfloat16*>(dsum_in);
+    __nv_bfloat16* op = static_cast<__nv_bfloat16*>(dx);
+    const unsigned pairs = static_cast<unsigned>((rows + 1) / 2);
+#define OB_RN_BWD(V) rmsnorm_bwd_dx_reg_kernel<V><<<pairs, 2 * RN_ROW_THREADS, 0, st>>>(gp, xp, wp, rstd, dp, op, rows, offset)
+    if (H == 1024) OB_RN_BWD(1);
+    else if (H == 2048) OB_RN_BWD(2);
+    else if (H == 4096) OB_RN_BWD(4);
+    else if (H == 8192) OB_RN_BWD(8);
+    else rmsnorm_bwd_dx_kernel<<<static_cast<unsigned>(rows), RN_THREADS, 0, st>>>(gp, xp, wp, rstd, dp, op, H, offset);
+#undef OB_RN_BWD
+  }
   if (dw_per_example != nullptr && num_examples > 0) {
     dim3 grid(num_examples, (H / 2 + 127) / 128);
     rmsnorm_bwd_dw_kernel<<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(dy),

@@ -257,6 +257,36 @@ def test_norm_activation_rope_kernels(dev):
     assert rel(q.grad, back) < 1e-3
 
 
+@pytest.mark.parametrize("H", [1024, 2048, 4096, 8192, 1536])
+def test_rms_norm_register_resident_widths(dev, H):
+    """Widths with a register-resident kernel (and one without), odd row count, with and without the fused residual add."""
+    from opaque_b200 import ops
+    torch.manual_seed(H)
+    rows = 37
+    x = torch.randn(rows, H, device=dev).bfloat16()
+    r = torch.randn(rows, H, device=dev).bfloat16()
+    w = (torch.randn(H, device=dev) * 0.1 + 1).bfloat16()
+    xg, wg = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    y = ops.rms_norm(xg, wg, 1e-5)
+    assert rel(y, ops.rms_norm_ref(x, w, 1e-5)) < 1e-4
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    (xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr).backward(dy.float())
+    assert rel(xg.grad, xr.grad) < 3 * rel(xr.grad.bfloat16(), xr.grad) + 1e-6
+    assert rel(wg.grad, wr.grad) < 3 * rel(wr.grad.bfloat16(), wr.grad) + 1e-6
+    y2, s2 = ops.fused_add_rms_norm(x, r, w, 1e-5)
+    yr2, sr2 = ops.rms_norm_ref(x, w, 1e-5, residual=r)
+    assert rel(y2, yr2) < 1e-4 and torch.equal(s2, sr2)
+    xa, ra = x.clone().requires_grad_(True), r.clone().requires_grad_(True)
+    ya, sa = ops.fused_add_rms_norm(xa, ra, w, 1e-5)
+    (ya.float().sum() + 2 * sa.float().sum()).backward()
+    xb, rb = x.float().requires_grad_(True), r.float().requires_grad_(True)
+    sb = xb + rb
+    ((sb * torch.rsqrt(sb.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()).sum() + 2 * sb.sum()).backward()
+    assert rel(xa.grad, xb.grad) < 2e-2 and torch.equal(xa.grad, ra.grad)
+
+
 def test_layernorm_group_sum_and_activation_kernels(dev):
     from opaque_b200 import ops
     torch.manual_seed(3)

@@ -124,6 +124,111 @@ layernorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat1
   }
 }
 
+// Register-resident variants: 128 threads own one row (up to 128 * VPT 16-byte vectors, masked at the row end) and keep it
+// in registers; two rows per CTA; one global read and one write per element.
+constexpr int LN_ROW_THREADS = 128;
+
+__device__ __forceinline__ float2 ln_row_group_sum2(float a, float b, float2* red) {     // red: 4 entries of this row group
+  a = warp_sum(a);
+  b = warp_sum(b);
+  const int w = (threadIdx.x & (LN_ROW_THREADS - 1)) >> 5;
+  if ((threadIdx.x & 31) == 0) red[w] = make_float2(a, b);
+  __syncthreads();
+  const float2 t = make_float2(red[0].x + red[1].x + red[2].x + red[3].x, red[0].y + red[1].y + red[2].y + red[3].y);
+  __syncthreads();
+  return t;
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(2 * LN_ROW_THREADS)
+layernorm_fwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                         const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y, float* __restrict__ mean,
+                         float* __restrict__ rstd, long long rows, int H, float eps) {
+  __shared__ float2 red_all[2][4];
+  const int grp = threadIdx.x / LN_ROW_THREADS, t = threadIdx.x % LN_ROW_THREADS;
+  const long long row = static_cast<long long>(blockIdx.x) * 2 + grp;
+  const bool live = row < rows;
+  const long long r = live ? row : rows - 1;
+  const int nv = H >> 3;
+  float f[VPT][8];
+  float s = 0.f, ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = t + v * LN_ROW_THREADS;
+    if (i < nv) {
+      ln_unpack8(reinterpret_cast<const ln_bf16x8*>(x + r * H)[i], f[v]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        s += f[v][j];
+        ss += f[v][j] * f[v][j];
+      }
+    }
+  }
+  const float2 tot = ln_row_group_sum2(s, ss, red_all[grp]);
+  const float mu = tot.x / H;
+  const float rs = rsqrtf(fmaxf(tot.y / H - mu * mu, 0.f) + eps);
+  if (live && t == 0) {
+    mean[row] = mu;
+    rstd[row] = rs;
+  }
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = t + v * LN_ROW_THREADS;
+    if (i < nv) {
+      float g[8], h[8];
+      ln_unpack8(reinterpret_cast<const ln_bf16x8*>(w)[i], g);
+      if (b != nullptr) ln_unpack8(reinterpret_cast<const ln_bf16x8*>(b)[i], h);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[v][j] = (f[v][j] - mu) * rs * g[j] + (b != nullptr ? h[j] : 0.f);
+      if (live) reinterpret_cast<ln_bf16x8*>(y + r * H)[i] = ln_pack8(f[v]);
+    }
+  }
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(2 * LN_ROW_THREADS)
+layernorm_bwd_dx_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                            const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean,
+                            const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx, long long rows, int H) {
+  __shared__ float2 red_all[2][4];
+  const int grp = threadIdx.x / LN_ROW_THREADS, t = threadIdx.x % LN_ROW_THREADS;
+  const long long row = static_cast<long long>(blockIdx.x) * 2 + grp;
+  const bool live = row < rows;
+  const long long r = live ? row : rows - 1;
+  const int nv = H >> 3;
+  const float mu = mean[r], rs = rstd[r];
+  float gw[VPT][8], xh[VPT][8];
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = t + v * LN_ROW_THREADS;
+    if (i < nv) {
+      float c[8];
+      ln_unpack8(reinterpret_cast<const ln_bf16x8*>(dy + r * H)[i], gw[v]);
+      ln_unpack8(reinterpret_cast<const ln_bf16x8*>(x + r * H)[i], xh[v]);
+      ln_unpack8(reinterpret_cast<const ln_bf16x8*>(w)[i], c);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        gw[v][j] *= c[j];
+        xh[v][j] = (xh[v][j] - mu) * rs;
+        s1 += gw[v][j];
+        s2 += gw[v][j] * xh[v][j];
+      }
+    }
+  }
+  const float2 tot = ln_row_group_sum2(s1, s2, red_all[grp]);
+  const float m1 = tot.x / H, m2 = tot.y / H;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = t + v * LN_ROW_THREADS;
+    if (i < nv) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) gw[v][j] = rs * (gw[v][j] - m1 - xh[v][j] * m2);
+      if (live) reinterpret_cast<ln_bf16x8*>(dx + r * H)[i] = ln_pack8(gw[v]);
+    }
+  }
+}
+
 // Per-example reductions over the token rows of each example: out[e, col] += sum_r f(r, col).
 //   mode 0: f = g                      (bias gradients: LayerNorm bias, linear bias)
 //   mode 1: f = g * (x - mean) * rstd  (LayerNorm weight gradient)
@@ -223,9 +328,15 @@ extern "C" int ob_layernorm_fwd(const void* x, const void* w, const void* b, voi
                                 long long rows, int H, float eps, void* stream) {
   if (rows <= 0) return 0;
   if (H % 8) return -2;
-  layernorm_fwd_kernel<<<static_cast<unsigned>(rows), LN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(b),
-      static_cast<__nv_bfloat16*>(y), mean, rstd, H, eps);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16 *xp = static_cast<const __nv_bfloat16*>(x), *wp = static_cast<const __nv_bfloat16*>(w),
+                      *bp = static_cast<const __nv_bfloat16*>(b);
+  __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
+  const unsigned pairs = static_cast<unsigned>((rows + 1) / 2);
+  if (H <= 1024) layernorm_fwd_reg_kernel<1><<<pairs, 2 * LN_ROW_THREADS, 0, st>>>(xp, wp, bp, yp, mean, rstd, rows, H, eps);
+  else if (H <= 2048) layernorm_fwd_reg_kernel<2><<<pairs, 2 * LN_ROW_THREADS, 0, st>>>(xp, wp, bp, yp, mean, rstd, rows, H, eps);
+  else if (H <= 4096) layernorm_fwd_reg_kernel<4><<<pairs, 2 * LN_ROW_THREADS, 0, st>>>(xp, wp, bp, yp, mean, rstd, rows, H, eps);
+  else layernorm_fwd_kernel<<<static_cast<unsigned>(rows), LN_THREADS, 0, st>>>(xp, wp, bp, yp, mean, rstd, H, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
@@ -233,9 +344,15 @@ extern "C" int ob_layernorm_bwd_dx(const void* dy, const void* x, const void* w,
                                    void* dx, long long rows, int H, void* stream) {
   if (rows <= 0) return 0;
   if (H % 8) return -2;
-  layernorm_bwd_dx_kernel<<<static_cast<unsigned>(rows), LN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
-      mean, rstd, static_cast<__nv_bfloat16*>(dx), H);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16 *gp = static_cast<const __nv_bfloat16*>(dy), *xp = static_cast<const __nv_bfloat16*>(x),
+                      *wp = static_cast<const __nv_bfloat16*>(w);
+  __nv_bfloat16* op = static_cast<__nv_bfloat16*>(dx);
+  const unsigned pairs = static_cast<unsigned>((rows + 1) / 2);
+  if (H <= 1024) layernorm_bwd_dx_reg_kernel<1><<<pairs, 2 * LN_ROW_THREADS, 0, st>>>(gp, xp, wp, mean, rstd, op, rows, H);
+  else if (H <= 2048) layernorm_bwd_dx_reg_kernel<2><<<pairs, 2 * LN_ROW_THREADS, 0, st>>>(gp, xp, wp, mean, rstd, op, rows, H);
+  else if (H <= 4096) layernorm_bwd_dx_reg_kernel<4><<<pairs, 2 * LN_ROW_THREADS, 0, st>>>(gp, xp, wp, mean, rstd, op, rows, H);
+  else layernorm_bwd_dx_kernel<<<static_cast<unsigned>(rows), LN_THREADS, 0, st>>>(gp, xp, wp, mean, rstd, op, H);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 

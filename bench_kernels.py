@@ -201,6 +201,16 @@ def main():
         x = torch.randn(rows, 4096, device=dev).bfloat16()
         w = torch.ones(4096, device=dev).bfloat16()
         emit(f"rms_norm fwd {rows}x4096", timeit(lambda: ops.rms_norm(x, w), iters, warm, flush), bytes_=2 * x.numel() * 2)
+    if want("rmsnorm") and not args.small:
+        xg = x.clone().requires_grad_(True)
+        y = ops.rms_norm(xg, w)
+        dy = torch.randn_like(y)
+        emit(f"rms_norm bwd dx {rows}x4096", timeit(lambda: torch.autograd.grad(y, xg, dy, retain_graph=True), iters, warm, flush), bytes_=3 * x.numel() * 2)
+    if want("layernorm"):
+        rows_l = 8192 if args.small else 131072
+        xl = torch.randn(rows_l, 768, device=dev).bfloat16()
+        wl, bl = torch.ones(768, device=dev).bfloat16(), torch.zeros(768, device=dev).bfloat16()
+        emit(f"layer_norm fwd {rows_l}x768", timeit(lambda: ops.layer_norm(xl, wl, bl), iters, warm, flush), bytes_=2 * xl.numel() * 2)
     if want("swiglu"):
         rows = 4096 if args.small else 16384
         g = torch.randn(rows, 14336, device=dev).bfloat16()

@@ -13,14 +13,16 @@ the active :class:`Capture`:
     tcgen05 weight-gradient kernel, one segment per example).
 
 When backward finishes every example's total squared norm is known: ``c_i = min(1, C/‖g_i‖)``
-(guarded), one kernel reduces ``Σ_i c_i·g_i`` of the direct buffer into the sharded gradient and
-one clip-weighted tcgen05 GEMM per ghost layer reduces ``Aᵀ·diag(c)·G`` there too — through peer
-pointers when there are several ranks, so these launches ARE the reduce-scatter.  After the last
+(guarded), one kernel reduces ``Σ_i c_i·g_i`` of the direct buffer into the gradient and one
+clip-weighted tcgen05 GEMM per ghost layer reduces ``Aᵀ·diag(c)·G`` there too (the factor multiplies
+each example's partial product in the epilogue).  With several ranks the destination is either the
+owners' shards through peer pointers (the launches ARE the reduce-scatter) or a local fp32 buffer that
+one push kernel per step reduces into the owners' shards; see ``FlatSpace(accumulate=...)``.  After the last
 microbatch :class:`~opaque_b200.parallel.ShardedDPOptimizer` adds noise once per coordinate and
 applies AdamW-BC on each owner's shard.
 
-Sensitivity.  ``c_i`` is shrunk by ``2⁻⁸ + 2⁻¹²`` relative before use: the GEMM applies it after a
-round-toward-zero to bf16 and the scaled operand is rounded to nearest bf16 (≤ 2⁻⁹ relative), and
+Sensitivity.  ``c_i`` is shrunk by ``2⁻⁸ + 2⁻¹²`` relative before use: the ragged GEMM variant applies it
+after a round-toward-zero to bf16 and rounds the scaled operand to nearest bf16 (≤ 2⁻⁹ relative), and
 the ghost norm carries fp32 accumulation error; the stored contribution of one record therefore
 stays within ``C``.  A weight tied between the input embedding and the output head gets its exact
 norm (the cross term ``2⟨g_emb, g_head⟩`` is computed from the captured tensors); any other parameter

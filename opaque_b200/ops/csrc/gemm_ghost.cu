@@ -8,6 +8,8 @@
 // Gram tiles are accumulated side by side in TMEM by tcgen05.mma (K-major operands, 128-byte
 // swizzle, TMA-fed), and the epilogue multiplies them element-wise, masks rows / columns that
 // fall outside the example, doubles off-diagonal tiles and adds the tile's sum to norm2[i].
+// A diagonal tile multiplies a row block with itself, so its producer loads that block once and both operand
+// descriptors point at it (the kernel is bound by the L2 -> shared-memory feed, not by the tensor pipe).
 //
 // With `ids` given (embedding layers) the first Gram matrix is replaced by the indicator
 // [ids_t == ids_t'], which is the Gram matrix of one-hot rows.
@@ -114,17 +116,19 @@ ghost_norm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const int len = p.seg ? p.seg[it.ex + 1] - s0 : p.T;
         if (it.tb2 * GH_TILE >= len) continue;                 // tile pair lies outside this (ragged) segment
         const int r1 = s0 + it.tb * GH_TILE, r2 = s0 + it.tb2 * GH_TILE;
+        const bool diag = it.tb == it.tb2;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_EMPTY, budget)) {
             ok = false;
             break;
           }
-          mbar_expect_tx(&full[stage], GH_STAGE_BYTES);
+          // a diagonal tile multiplies a row block with itself: one load serves both operands
+          mbar_expect_tx(&full[stage], diag ? GH_TILE_BYTES : GH_STAGE_BYTES);
           uint8_t* dst = smem + stage * GH_STAGE_BYTES;
           const CUtensorMap* map = kb < ka ? &map_a : &map_g;
           const int col = (kb < ka ? kb : kb - ka) * GH_BLOCK_K;
           tma_load_2d(dst, map, &full[stage], col, r1);
-          tma_load_2d(dst + GH_TILE_BYTES, map, &full[stage], col, r2);
+          if (!diag) tma_load_2d(dst + GH_TILE_BYTES, map, &full[stage], col, r2);
           issued_mask |= 1u << stage;
           issued_phase = (issued_phase & ~(1u << stage)) | (phase << stage);
           if (++stage == GH_STAGES) { stage = 0; phase ^= 1; }
@@ -145,10 +149,9 @@ ghost_norm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-        if (p.seg) {
-          const GhostItem it = ghost_decode(w, pairs, nt);
-          if (it.tb2 * GH_TILE >= p.seg[it.ex + 1] - p.seg[it.ex]) continue;
-        }
+        const GhostItem it = ghost_decode(w, pairs, nt);
+        if (p.seg && it.tb2 * GH_TILE >= p.seg[it.ex + 1] - p.seg[it.ex]) continue;
+        const uint32_t b_off = it.tb == it.tb2 ? 0u : static_cast<uint32_t>(GH_TILE_BYTES);
         const int as = acc_iter & 1;
         if (!mbar_wait(&tmem_empty[as], ((acc_iter >> 1) & 1) ^ 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_EMPTY,
                        budget)) {
@@ -162,7 +165,7 @@ ghost_norm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             break;
           }
           tc_fence_after();
-          const uint32_t t1 = smem_u32(smem + stage * GH_STAGE_BYTES), t2 = t1 + GH_TILE_BYTES;
+          const uint32_t t1 = smem_u32(smem + stage * GH_STAGE_BYTES), t2 = t1 + b_off;
           const uint32_t d_tmem = tmem_base + as * 256 + (kb < ka ? 0 : 128);
           const bool first = (kb == 0) || (kb == ka);
 #pragma unroll
@@ -332,16 +335,17 @@ ghost_norm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         segment(it.ex, s0, len);
         if (it.tb * GH_TILE >= len || it.cb * GW_TILE_N >= len) continue;
         const int r1 = s0 + it.tb * GH_TILE, r2 = s0 + it.cb * GW_TILE_N;
+        const bool diag = (it.tb >> 1) == it.cb;              // the row block is one of the two column blocks
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_EMPTY, budget)) {
             ok = false;
             break;
           }
-          mbar_expect_tx(&full[stage], GW_STAGE_BYTES);
+          mbar_expect_tx(&full[stage], diag ? GW_B_BYTES : GW_STAGE_BYTES);
           uint8_t* dst = smem + stage * GW_STAGE_BYTES;
           const CUtensorMap* map = kb < ka ? &map_a : &map_g;
           const int col = (kb < ka ? kb : kb - ka) * GH_BLOCK_K;
-          tma_load_2d(dst, map, &full[stage], col, r1);
+          if (!diag) tma_load_2d(dst, map, &full[stage], col, r1);
           tma_load_2d(dst + GW_A_BYTES, map, &full[stage], col, r2);
           tma_load_2d(dst + GW_A_BYTES + GW_A_BYTES, map, &full[stage], col, r2 + GH_TILE);
           issued_mask |= 1u << stage;
@@ -368,6 +372,8 @@ ghost_norm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         int s0, len;
         segment(it.ex, s0, len);
         if (it.tb * GH_TILE >= len || it.cb * GW_TILE_N >= len) continue;
+        // on a diagonal super-block the A operand is read from the copy of that row block inside the B operand
+        const uint32_t a_off = (it.tb >> 1) == it.cb ? static_cast<uint32_t>(GW_A_BYTES + (it.tb & 1) * GW_A_BYTES) : 0u;
         if (!mbar_wait(tmem_empty, (acc_iter & 1) ^ 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_EMPTY, budget)) {
           ok = false;
           break;
@@ -379,7 +385,8 @@ ghost_norm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             break;
           }
           tc_fence_after();
-          const uint32_t t1 = smem_u32(smem + stage * GW_STAGE_BYTES), t2 = t1 + GW_A_BYTES;
+          const uint32_t st0 = smem_u32(smem + stage * GW_STAGE_BYTES);
+          const uint32_t t1 = st0 + a_off, t2 = st0 + GW_A_BYTES;
           const uint32_t d_tmem = tmem_base + (kb < ka ? 0 : GW_TILE_N);
           const bool first = (kb == 0) || (kb == ka);
 #pragma unroll

@@ -229,6 +229,101 @@ layernorm_bwd_dx_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfl
   }
 }
 
+// Warp-per-row variants for narrow rows (H <= 1024): one warp keeps a row in registers (VPL 16-byte vectors per lane,
+// masked at the row end) and reduces with shuffles only, so a CTA of eight rows never synchronises.
+constexpr int LN_WARP_ROWS = 8;
+
+template <int VPL>
+__global__ void __launch_bounds__(32 * LN_WARP_ROWS)
+layernorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                          const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y, float* __restrict__ mean,
+                          float* __restrict__ rstd, long long rows, int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * LN_WARP_ROWS + (threadIdx.x >> 5);
+  if (row >= rows) return;                                   // whole warps leave together; nothing below synchronises
+  const int nv = H >> 3;
+  const ln_bf16x8* xr = reinterpret_cast<const ln_bf16x8*>(x + row * H);
+  float f[VPL][8];
+  float s = 0.f, ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) {
+    const int i = lane + v * 32;
+    if (i < nv) {
+      ln_unpack8(xr[i], f[v]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        s += f[v][j];
+        ss += f[v][j] * f[v][j];
+      }
+    }
+  }
+  s = warp_sum(s);
+  ss = warp_sum(ss);
+  const float mu = s / H;
+  const float rs = rsqrtf(fmaxf(ss / H - mu * mu, 0.f) + eps);
+  if (lane == 0) {
+    mean[row] = mu;
+    rstd[row] = rs;
+  }
+  ln_bf16x8* yr = reinterpret_cast<ln_bf16x8*>(y + row * H);
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) {
+    const int i = lane + v * 32;
+    if (i < nv) {
+      float g[8], h[8];
+      ln_unpack8(reinterpret_cast<const ln_bf16x8*>(w)[i], g);
+      if (b != nullptr) ln_unpack8(reinterpret_cast<const ln_bf16x8*>(b)[i], h);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[v][j] = (f[v][j] - mu) * rs * g[j] + (b != nullptr ? h[j] : 0.f);
+      yr[i] = ln_pack8(f[v]);
+    }
+  }
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(32 * LN_WARP_ROWS)
+layernorm_bwd_dx_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                             const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean,
+                             const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx, long long rows, int H) {
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * LN_WARP_ROWS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nv = H >> 3;
+  const float mu = mean[row], rs = rstd[row];
+  const ln_bf16x8* gr = reinterpret_cast<const ln_bf16x8*>(dy + row * H);
+  const ln_bf16x8* xr = reinterpret_cast<const ln_bf16x8*>(x + row * H);
+  float gw[VPL][8], xh[VPL][8];
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) {
+    const int i = lane + v * 32;
+    if (i < nv) {
+      float c[8];
+      ln_unpack8(gr[i], gw[v]);
+      ln_unpack8(xr[i], xh[v]);
+      ln_unpack8(reinterpret_cast<const ln_bf16x8*>(w)[i], c);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        gw[v][j] *= c[j];
+        xh[v][j] = (xh[v][j] - mu) * rs;
+        s1 += gw[v][j];
+        s2 += gw[v][j] * xh[v][j];
+      }
+    }
+  }
+  const float m1 = warp_sum(s1) / H, m2 = warp_sum(s2) / H;
+  ln_bf16x8* or_ = reinterpret_cast<ln_bf16x8*>(dx + row * H);
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) {
+    const int i = lane + v * 32;
+    if (i < nv) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) gw[v][j] = rs * (gw[v][j] - m1 - xh[v][j] * m2);
+      or_[i] = ln_pack8(gw[v]);
+    }
+  }
+}
+
 // Per-example reductions over the token rows of each example: out[e, col] += sum_r f(r, col).
 //   mode 0: f = g                      (bias gradients: LayerNorm bias, linear bias)
 //   mode 1: f = g * (x - mean) * rstd  (LayerNorm weight gradient)
@@ -333,7 +428,11 @@ extern "C" int ob_layernorm_fwd(const void* x, const void* w, const void* b, voi
                       *bp = static_cast<const __nv_bfloat16*>(b);
   __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
   const unsigned pairs = static_cast<unsigned>((rows + 1) / 2);
-  if (H <= 1024) layernorm_fwd_reg_kernel<1><<<pairs, 2 * LN_ROW_THREADS, 0, st>>>(xp, wp, bp, yp, mean, rstd, rows, H, eps);
+  const unsigned octs = static_cast<unsigned>((rows + LN_WARP_ROWS - 1) / LN_WARP_ROWS);
+  if (H <= 256) layernorm_fwd_warp_kernel<1><<<octs, 32 * LN_WARP_ROWS, 0, st>>>(xp, wp, bp, yp, mean, rstd, rows, H, eps);
+  else if (H <= 512) layernorm_fwd_warp_kernel<2><<<octs, 32 * LN_WARP_ROWS, 0, st>>>(xp, wp, bp, yp, mean, rstd, rows, H, eps);
+  else if (H <= 768) layernorm_fwd_warp_kernel<3><<<octs, 32 * LN_WARP_ROWS, 0, st>>>(xp, wp, bp, yp, mean, rstd, rows, H, eps);
+  else if (H <= 1024) layernorm_fwd_warp_kernel<4><<<octs, 32 * LN_WARP_ROWS, 0, st>>>(xp, wp, bp, yp, mean, rstd, rows, H, eps);
   else if (H <= 2048) layernorm_fwd_reg_kernel<2><<<pairs, 2 * LN_ROW_THREADS, 0, st>>>(xp, wp, bp, yp, mean, rstd, rows, H, eps);
   else if (H <= 4096) layernorm_fwd_reg_kernel<4><<<pairs, 2 * LN_ROW_THREADS, 0, st>>>(xp, wp, bp, yp, mean, rstd, rows, H, eps);
   else layernorm_fwd_kernel<<<static_cast<unsigned>(rows), LN_THREADS, 0, st>>>(xp, wp, bp, yp, mean, rstd, H, eps);
@@ -349,7 +448,11 @@ extern "C" int ob_layernorm_bwd_dx(const void* dy, const void* x, const void* w,
                       *wp = static_cast<const __nv_bfloat16*>(w);
   __nv_bfloat16* op = static_cast<__nv_bfloat16*>(dx);
   const unsigned pairs = static_cast<unsigned>((rows + 1) / 2);
-  if (H <= 1024) layernorm_bwd_dx_reg_kernel<1><<<pairs, 2 * LN_ROW_THREADS, 0, st>>>(gp, xp, wp, mean, rstd, op, rows, H);
+  const unsigned octs = static_cast<unsigned>((rows + LN_WARP_ROWS - 1) / LN_WARP_ROWS);
+  if (H <= 256) layernorm_bwd_dx_warp_kernel<1><<<octs, 32 * LN_WARP_ROWS, 0, st>>>(gp, xp, wp, mean, rstd, op, rows, H);
+  else if (H <= 512) layernorm_bwd_dx_warp_kernel<2><<<octs, 32 * LN_WARP_ROWS, 0, st>>>(gp, xp, wp, mean, rstd, op, rows, H);
+  else if (H <= 768) layernorm_bwd_dx_warp_kernel<3><<<octs, 32 * LN_WARP_ROWS, 0, st>>>(gp, xp, wp, mean, rstd, op, rows, H);
+  else if (H <= 1024) layernorm_bwd_dx_warp_kernel<4><<<octs, 32 * LN_WARP_ROWS, 0, st>>>(gp, xp, wp, mean, rstd, op, rows, H);
   else if (H <= 2048) layernorm_bwd_dx_reg_kernel<2><<<pairs, 2 * LN_ROW_THREADS, 0, st>>>(gp, xp, wp, mean, rstd, op, rows, H);
   else if (H <= 4096) layernorm_bwd_dx_reg_kernel<4><<<pairs, 2 * LN_ROW_THREADS, 0, st>>>(gp, xp, wp, mean, rstd, op, rows, H);
   else layernorm_bwd_dx_kernel<<<static_cast<unsigned>(rows), LN_THREADS, 0, st>>>(gp, xp, wp, mean, rstd, op, H);

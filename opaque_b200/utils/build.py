@@ -5,6 +5,7 @@ build is skipped when the artefact is newer than every source; ``force=True`` re
 """
 from __future__ import annotations
 
+import contextlib
 import os
 import shutil
 import subprocess
@@ -31,6 +32,23 @@ def _find(tool: str, extra: list[str]) -> str | None:
     return None
 
 
+@contextlib.contextmanager
+def _build_lock(target: Path):
+    """Exclusive advisory lock beside ``target`` (held across one compile); a no-op where ``fcntl`` is missing."""
+    try:
+        import fcntl
+    except ImportError:          # pragma: no cover
+        yield
+        return
+    lock_path = target.with_name("." + target.name + ".lock")
+    with open(lock_path, "w") as fh:
+        fcntl.flock(fh, fcntl.LOCK_EX)
+        try:
+            yield
+        finally:
+            fcntl.flock(fh, fcntl.LOCK_UN)
+
+
 def _stale(target: Path, sources: list[Path]) -> bool:
     if not target.exists():
         return True
@@ -47,14 +65,20 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
     nvcc = _find("nvcc", ["/usr/local/cuda/bin/nvcc"])
     if nvcc is None:
         raise RuntimeError("nvcc not found: cannot build the sm_100a kernel library")
-    tmp = KERNEL_LIB.with_suffix(".so.tmp")
-    cmd = [nvcc, *NVCC_FLAGS, "-o", str(tmp), *map(str, sources)]
-    if verbose:
-        cmd.insert(1, "-Xptxas=-v")
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-    os.replace(tmp, KERNEL_LIB)
+    # Every rank of a job may find the library stale at the same moment: one builds, the others wait on the lock and
+    # then see a fresh library.  The output is written under a private name and renamed into place.
+    with _build_lock(KERNEL_LIB):
+        if not force and not _stale(KERNEL_LIB, deps):
+            return KERNEL_LIB
+        tmp = KERNEL_LIB.with_suffix(f".so.tmp{os.getpid()}")
+        cmd = [nvcc, *NVCC_FLAGS, "-o", str(tmp), *map(str, sources)]
+        if verbose:
+            cmd.insert(1, "-Xptxas=-v")
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            tmp.unlink(missing_ok=True)
+            raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+        os.replace(tmp, KERNEL_LIB)
     if verbose:
         print(res.stderr)
     return KERNEL_LIB
@@ -78,14 +102,18 @@ def build_accounting(force: bool = False) -> Path:
     gxx = _find("g++", ["/usr/bin/g++"])
     if gxx is None:
         raise RuntimeError("g++ not found: cannot build the accountant")
-    tmp = target.with_suffix(".tmp")
-    cmd = [gxx, "-O3", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-pthread", "-fopenmp",
-           f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}",
-           "-o", str(tmp), *map(str, sources)]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
-    os.replace(tmp, target)
+    with _build_lock(target):
+        if not force and not _stale(target, deps):
+            return target
+        tmp = target.with_suffix(f".tmp{os.getpid()}")
+        cmd = [gxx, "-O3", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-pthread", "-fopenmp",
+               f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}",
+               "-o", str(tmp), *map(str, sources)]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            tmp.unlink(missing_ok=True)
+            raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
+        os.replace(tmp, target)
     return target
 
 

@@ -463,3 +463,25 @@ def test_bounded_wait_reports_timeout_without_hanging(dev):
     with pytest.raises(lib.DeviceWaitTimeout):
         st.raise_if_set("test")
     assert st.read() == 0 and float(torch.ones(4, device=dev).sum()) == 4.0     # the context is still usable
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("H", [64, 256, 264, 512, 768, 1000, 1024, 1536, 4096, 5120])
+def test_layer_norm_all_row_widths(dev, H):
+    """Warp-per-row (H <= 1024), CTA-per-row-pair (H <= 4096) and streaming LayerNorm kernels against fp32 torch,
+    with a row count that leaves the last CTA partly empty."""
+    from opaque_b200 import ops
+    torch.manual_seed(H)
+    rows = 203
+    x = (torch.randn(rows, H, device=dev) * 1.5 - 0.3).bfloat16()
+    w = (torch.randn(H, device=dev) * 0.2 + 1).bfloat16()
+    b = (torch.randn(H, device=dev) * 0.1).bfloat16()
+    xg = x.clone().requires_grad_(True)
+    y = ops.layer_norm(xg, w, b, 1e-5)
+    xr = x.float().requires_grad_(True)
+    yr = torch.nn.functional.layer_norm(xr, (H,), w.float(), b.float(), 1e-5)
+    assert rel(y, yr) < 4e-3
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    yr.backward(dy.float())
+    assert rel(xg.grad, xr.grad) < 6e-3

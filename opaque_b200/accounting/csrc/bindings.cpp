@@ -80,6 +80,22 @@ PYBIND11_MODULE(_native, m) {
     py::gil_scoped_release r; return b_min_sep_mc_pld(coef, n, b, p, nm, warm, c); },
     py::arg("coef"), py::arg("n_steps"), py::arg("min_sep"), py::arg("sampling_prob"), py::arg("noise_multiplier"),
     py::arg("warm_start"), py::arg("config"));
+  py::class_<BMinSepCorpus>(m, "BMinSepCorpus")
+      .def(py::init([](std::vector<double> coef, std::size_t n, std::size_t b, double p, bool warm, std::size_t samples,
+                       std::uint64_t seed) {
+             py::gil_scoped_release r;
+             return new BMinSepCorpus(std::move(coef), n, b, p, warm, samples, seed);
+           }),
+           py::arg("coef"), py::arg("n_steps"), py::arg("min_sep"), py::arg("sampling_prob"), py::arg("warm_start"),
+           py::arg("num_samples"), py::arg("seed"))
+      .def_readonly("n_steps", &BMinSepCorpus::n_steps)
+      .def_readonly("num_samples", &BMinSepCorpus::num_samples)
+      .def_readonly("seed", &BMinSepCorpus::seed)
+      .def_property_readonly("nbytes", &BMinSepCorpus::nbytes)
+      .def("pld", [](const BMinSepCorpus& c, double nm, std::size_t n, const Config& cfg) {
+             py::gil_scoped_release r;
+             return c.pld(nm, n, cfg);
+           }, py::arg("noise_multiplier"), py::arg("n_steps"), py::arg("config"));
   m.def("adaclip_effective_noise_multiplier", &adaclip_effective_noise_multiplier);
 
   m.def("minsep_true_max_participations", [](std::int64_t n, std::int64_t ms, py::object mp) {

@@ -1100,91 +1100,173 @@ Pld balls_in_bins_mc_pld(const std::vector<double>& gram, std::size_t n, std::si
 // with P(y)/Q(y) = f_0 for a cold start (every record free at step 0).  With a warm start (the chain of
 // free / barred states started in its stationary law) P/Q = (f_0 + p (f_1 + ... + f_{b-1})) / (1 + (b-1) p).
 // Losses ln(P/Q) under P (remove) and -ln(P/Q) under Q (add) are sampled and rounded UP onto the grid.
+namespace {
+
+// One record's transcript for b-min-sep, independent of the noise multiplier: the participation pattern x, the unit
+// normals of the P branch and of the Q branch.  Each of the three comes from its own generator, seeded from
+// (seed, sample), so the first m columns of an n-step transcript ARE the m-step transcript of the same sample.
+struct BmsStreams {
+  std::mt19937_64 rx, rp, rq;
+  BmsStreams(std::uint64_t seed, std::uint64_t sample) {
+    const std::uint64_t base = seed + 0x9E3779B97F4A7C15ULL * (sample + 1);
+    rx.seed(base ^ 0xA24BAED4963EE407ULL);
+    rp.seed(base ^ 0x9FB21C651E98DF25ULL);
+    rq.seed(base ^ 0xD6E8FEB86659FD93ULL);
+  }
+};
+
+void bms_draw(std::uint64_t seed, std::uint64_t sample, std::size_t n, std::size_t b, double p, bool warm_start,
+              std::uint8_t* x, double* zp, double* zq) {
+  BmsStreams g(seed, sample);
+  std::uniform_real_distribution<double> ud(0.0, 1.0);
+  std::normal_distribution<double> np(0.0, 1.0), nq(0.0, 1.0);
+  const double denom = 1.0 + static_cast<double>(b - 1) * p;
+  std::size_t barred = 0;
+  if (warm_start && b > 1 && ud(g.rx) * denom >= 1.0)
+    barred = 1 + static_cast<std::size_t>(ud(g.rx) * static_cast<double>(b - 1)) % (b - 1);
+  for (std::size_t i = 0; i < n; ++i) {
+    const bool take = barred == 0 && ud(g.rx) < p;
+    x[i] = take ? 1 : 0;
+    barred = take ? b - 1 : (barred > 0 ? barred - 1 : 0);
+  }
+  for (std::size_t i = 0; i < n; ++i) zp[i] = np(g.rp);
+  for (std::size_t i = 0; i < n; ++i) zq[i] = nq(g.rq);
+}
+
+// ln(P/Q) of one observation sequence y (see the recursion above); f is scratch of n + 1 doubles holding log f_i.
+double bms_log_ratio(const std::vector<double>& coef, const std::vector<double>& cum, std::size_t n, std::size_t b, double p,
+                     double sigma2, bool warm_start, const double* y, double* f) {
+  const std::size_t L = coef.size();
+  f[n] = 0.0;
+  for (std::size_t ii = n; ii-- > 0;) {
+    const std::size_t m = std::min(L, n - ii);
+    double dot = 0.0;
+    for (std::size_t k = 0; k < m; ++k) dot += coef[k] * y[ii + k];
+    const double blk = (dot - 0.5 * cum[m]) / sigma2;
+    const double skip = f[std::min(ii + b, n)];
+    const double a = (p < 1.0) ? std::log1p(-p) + f[ii + 1] : -std::numeric_limits<double>::infinity();
+    const double c2 = std::log(p) + blk + skip;
+    const double hi = std::max(a, c2);
+    f[ii] = hi + std::log(std::exp(a - hi) + std::exp(c2 - hi));
+  }
+  if (!warm_start || b == 1) return f[0];
+  const double denom = 1.0 + static_cast<double>(b - 1) * p;
+  double hi = f[0];
+  for (std::size_t j = 1; j < std::min(b, n + 1); ++j) hi = std::max(hi, std::log(p) + f[j]);
+  double acc = std::exp(f[0] - hi);
+  for (std::size_t j = 1; j < b; ++j) acc += std::exp(std::log(p) + f[std::min(j, n)] - hi);
+  return hi + std::log(acc) - std::log(denom);
+}
+
+// Both losses of one sample at noise multiplier sigma from its sigma-free transcript.
+void bms_losses(const std::vector<double>& coef, const std::vector<double>& cum, std::size_t n, std::size_t b, double p,
+                double sigma, bool warm_start, const std::uint8_t* x, const double* zp, const double* zq, double* y,
+                double* f, double& loss_remove, double& loss_add) {
+  const std::size_t L = coef.size();
+  for (std::size_t i = 0; i < n; ++i) {                     // P branch: y = C x + sigma z
+    double acc = sigma * zp[i];
+    for (std::size_t k = 0; k < L && k <= i; ++k) acc += coef[k] * static_cast<double>(x[i - k]);
+    y[i] = acc;
+  }
+  loss_remove = bms_log_ratio(coef, cum, n, b, p, sigma * sigma, warm_start, y, f);
+  for (std::size_t i = 0; i < n; ++i) y[i] = sigma * zq[i];   // Q branch: y = sigma z
+  loss_add = -bms_log_ratio(coef, cum, n, b, p, sigma * sigma, warm_start, y, f);
+}
+
+Pmf bms_losses_to_pmf(const std::vector<double>& v, const Config& cfg) {
+  Pmf q;
+  q.discretization = cfg.discretization;
+  q.max_grid_size = cfg.max_grid_size;
+  std::int64_t lo = std::numeric_limits<std::int64_t>::max(), hi = std::numeric_limits<std::int64_t>::min();
+  std::vector<std::int64_t> idx(v.size());
+  for (std::size_t i = 0; i < v.size(); ++i) {
+    idx[i] = static_cast<std::int64_t>(std::ceil(v[i] / cfg.discretization));
+    lo = std::min(lo, idx[i]);
+    hi = std::max(hi, idx[i]);
+  }
+  q.lower = lo;
+  q.probs.assign(static_cast<std::size_t>(hi - lo + 1), 0.0);
+  const double w = 1.0 / static_cast<double>(v.size());
+  for (auto i : idx) q.probs[static_cast<std::size_t>(i - lo)] += w;
+  return q.maybe_coarsen();
+}
+
+std::vector<double> bms_cum(const std::vector<double>& coef) {
+  std::vector<double> cum(coef.size() + 1, 0.0);           // |c_{:m}|^2 for a column cut off by the end of the run
+  for (std::size_t k = 0; k < coef.size(); ++k) cum[k + 1] = cum[k] + coef[k] * coef[k];
+  return cum;
+}
+
+void bms_check(const std::vector<double>& coef, std::size_t n, std::size_t b, double p) {
+  require(!coef.empty() && n >= 1 && b >= 1 && p > 0.0 && p <= 1.0, "b-min-sep: need coefficients, n >= 1, b >= 1, p in (0, 1]");
+  require(coef.size() <= b, "b-min-sep: the strategy's band count must not exceed the minimum separation");
+}
+
+}  // namespace
+
 Pld b_min_sep_mc_pld(const std::vector<double>& coef, std::size_t n, std::size_t b, double p, double nm, bool warm_start,
                      const Config& cfg) {
   check_nm(nm);
-  require(!coef.empty() && n >= 1 && b >= 1 && p > 0.0 && p <= 1.0, "b-min-sep: need coefficients, n >= 1, b >= 1, p in (0, 1]");
-  require(coef.size() <= b, "b-min-sep: the strategy's band count must not exceed the minimum separation");
-  const std::size_t L = coef.size();
-  const double sigma = nm, sigma2 = nm * nm;
+  bms_check(coef, n, b, p);
   const std::size_t S = cfg.num_mc_samples;
   std::vector<double> losses_remove(S), losses_add(S);
-  // |c_{:m}|^2 for a column cut off by the end of the run
-  std::vector<double> cum(L + 1, 0.0);
-  for (std::size_t k = 0; k < L; ++k) cum[k + 1] = cum[k] + coef[k] * coef[k];
-  const double denom = 1.0 + static_cast<double>(b - 1) * p;
-
-  auto log_ratio = [&](const std::vector<double>& y, std::vector<double>& f) {
-    // work with f_i scaled by a running maximum to stay finite over long runs: keep log-scale per index
-    // (values can span hundreds of orders of magnitude); f holds log f_i
-    f[n] = 0.0;
-    for (std::size_t ii = n; ii-- > 0;) {
-      const std::size_t m = std::min(L, n - ii);
-      double dot = 0.0;
-      for (std::size_t k = 0; k < m; ++k) dot += coef[k] * y[ii + k];
-      const double blk = (dot - 0.5 * cum[m]) / sigma2;
-      const double skip = f[std::min(ii + b, n)];
-      const double a = (p < 1.0) ? std::log1p(-p) + f[ii + 1] : -std::numeric_limits<double>::infinity();
-      const double c2 = std::log(p) + blk + skip;
-      const double hi = std::max(a, c2);
-      f[ii] = hi + std::log(std::exp(a - hi) + std::exp(c2 - hi));
-    }
-    if (!warm_start || b == 1) return f[0];
-    double hi = f[0];
-    for (std::size_t j = 1; j < std::min(b, n + 1); ++j) hi = std::max(hi, std::log(p) + f[j]);
-    double acc = std::exp(f[0] - hi);
-    for (std::size_t j = 1; j < b; ++j) acc += std::exp(std::log(p) + f[std::min(j, n)] - hi);
-    return hi + std::log(acc) - std::log(denom);
-  };
-
+  const std::vector<double> cum = bms_cum(coef);
 #pragma omp parallel
   {
-    std::vector<double> y(n), x(n), f(n + 1);
-    std::normal_distribution<double> nd(0.0, 1.0);
-    std::uniform_real_distribution<double> ud(0.0, 1.0);
+    std::vector<std::uint8_t> x(n);
+    std::vector<double> zp(n), zq(n), y(n), f(n + 1);
 #pragma omp for schedule(static)
     for (std::int64_t s = 0; s < static_cast<std::int64_t>(S); ++s) {
-      std::mt19937_64 rng(cfg.seed + 0x9E3779B97F4A7C15ULL * static_cast<std::uint64_t>(s + 1));
-      // P branch: participation pattern of one record, y = C x + sigma z
-      std::size_t barred = 0;
-      if (warm_start && b > 1 && ud(rng) * denom >= 1.0)
-        barred = 1 + static_cast<std::size_t>(ud(rng) * static_cast<double>(b - 1)) % (b - 1);
-      for (std::size_t i = 0; i < n; ++i) {
-        const bool take = barred == 0 && ud(rng) < p;
-        x[i] = take ? 1.0 : 0.0;
-        barred = take ? b - 1 : (barred > 0 ? barred - 1 : 0);
-      }
-      for (std::size_t i = 0; i < n; ++i) {
-        double acc = sigma * nd(rng);
-        for (std::size_t k = 0; k < L && k <= i; ++k) acc += coef[k] * x[i - k];
-        y[i] = acc;
-      }
-      losses_remove[static_cast<std::size_t>(s)] = log_ratio(y, f);
-      // Q branch: y = sigma z
-      for (std::size_t i = 0; i < n; ++i) y[i] = sigma * nd(rng);
-      losses_add[static_cast<std::size_t>(s)] = -log_ratio(y, f);
+      bms_draw(cfg.seed, static_cast<std::uint64_t>(s), n, b, p, warm_start, x.data(), zp.data(), zq.data());
+      bms_losses(coef, cum, n, b, p, nm, warm_start, x.data(), zp.data(), zq.data(), y.data(), f.data(),
+                 losses_remove[static_cast<std::size_t>(s)], losses_add[static_cast<std::size_t>(s)]);
     }
   }
-  auto to_pmf = [&](const std::vector<double>& v) {
-    Pmf q;
-    q.discretization = cfg.discretization;
-    q.max_grid_size = cfg.max_grid_size;
-    std::int64_t lo = std::numeric_limits<std::int64_t>::max(), hi = std::numeric_limits<std::int64_t>::min();
-    std::vector<std::int64_t> idx(v.size());
-    for (std::size_t i = 0; i < v.size(); ++i) {
-      idx[i] = static_cast<std::int64_t>(std::ceil(v[i] / cfg.discretization));
-      lo = std::min(lo, idx[i]);
-      hi = std::max(hi, idx[i]);
-    }
-    q.lower = lo;
-    q.probs.assign(static_cast<std::size_t>(hi - lo + 1), 0.0);
-    const double w = 1.0 / static_cast<double>(v.size());
-    for (auto i : idx) q.probs[static_cast<std::size_t>(i - lo)] += w;
-    return q.maybe_coarsen();
-  };
   Pld out;
-  out.remove = to_pmf(losses_remove);
-  out.add = to_pmf(losses_add);
+  out.remove = bms_losses_to_pmf(losses_remove, cfg);
+  out.add = bms_losses_to_pmf(losses_add, cfg);
+  return out;
+}
+
+// --------------------------------------------------------------------------- stored transcripts
+BMinSepCorpus::BMinSepCorpus(std::vector<double> coef_, std::size_t n_steps_, std::size_t min_sep_, double p_, bool warm_,
+                             std::size_t samples_, std::uint64_t seed_)
+    : coef(std::move(coef_)), n_steps(n_steps_), min_sep(min_sep_), sampling_prob(p_), warm_start(warm_),
+      num_samples(samples_), seed(seed_) {
+  bms_check(coef, n_steps, min_sep, sampling_prob);
+  require(num_samples >= 1, "b-min-sep corpus: need at least one sample");
+  x.resize(num_samples * n_steps);
+  zp.resize(num_samples * n_steps);
+  zq.resize(num_samples * n_steps);
+#pragma omp parallel for schedule(static)
+  for (std::int64_t s = 0; s < static_cast<std::int64_t>(num_samples); ++s) {
+    const std::size_t o = static_cast<std::size_t>(s) * n_steps;
+    bms_draw(seed, static_cast<std::uint64_t>(s), n_steps, min_sep, sampling_prob, warm_start, &x[o], &zp[o], &zq[o]);
+  }
+}
+
+std::size_t BMinSepCorpus::nbytes() const {
+  return x.size() * sizeof(std::uint8_t) + (zp.size() + zq.size()) * sizeof(double);
+}
+
+Pld BMinSepCorpus::pld(double nm, std::size_t n_prefix, const Config& cfg) const {
+  check_nm(nm);
+  require(n_prefix >= 1 && n_prefix <= n_steps, "b-min-sep corpus: the queried horizon exceeds the stored one");
+  std::vector<double> losses_remove(num_samples), losses_add(num_samples);
+  const std::vector<double> cum = bms_cum(coef);
+#pragma omp parallel
+  {
+    std::vector<double> y(n_prefix), f(n_prefix + 1);
+#pragma omp for schedule(static)
+    for (std::int64_t s = 0; s < static_cast<std::int64_t>(num_samples); ++s) {
+      const std::size_t o = static_cast<std::size_t>(s) * n_steps;
+      bms_losses(coef, cum, n_prefix, min_sep, sampling_prob, nm, warm_start, &x[o], &zp[o], &zq[o], y.data(), f.data(),
+                 losses_remove[static_cast<std::size_t>(s)], losses_add[static_cast<std::size_t>(s)]);
+    }
+  }
+  Pld out;
+  out.remove = bms_losses_to_pmf(losses_remove, cfg);
+  out.add = bms_losses_to_pmf(losses_add, cfg);
   return out;
 }
 

@@ -97,6 +97,28 @@ Pld mixture_gaussian_pld(double sigma, const std::vector<double>& log_probs, con
 Pld random_allocation_gaussian_pld(double noise_multiplier, std::size_t num_bins, std::size_t k, const Config& cfg);
 Pld b_min_sep_mc_pld(const std::vector<double>& coef, std::size_t n, std::size_t b, double p, double noise_multiplier,
                      bool warm_start, const Config& cfg);
+
+// Noise-multiplier-free Monte-Carlo transcripts of b-min-sep (participation patterns and unit normals of both
+// branches), kept so that a calibration search evaluates many noise multipliers on ONE set of samples.  A query may
+// use any prefix n <= n_steps of the stored horizon: it equals a fresh corpus of that length with the same seed.
+// pld(nm, n_steps, cfg) equals b_min_sep_mc_pld(...) with cfg.seed == seed and cfg.num_mc_samples == num_samples.
+// Parity: packages/opaque-accounting/src/amplification/b_min_sep/registry.rs of the reference (handles to stored
+// corpora, K-prefix queries); here the corpus is a C++ object owned by Python.
+struct BMinSepCorpus {
+  std::vector<double> coef;
+  std::size_t n_steps, min_sep;
+  double sampling_prob;
+  bool warm_start;
+  std::size_t num_samples;
+  std::uint64_t seed;
+  std::vector<std::uint8_t> x;     // [num_samples * n_steps]
+  std::vector<double> zp, zq;      // [num_samples * n_steps] each
+
+  BMinSepCorpus(std::vector<double> coef, std::size_t n_steps, std::size_t min_sep, double sampling_prob, bool warm_start,
+                std::size_t num_samples, std::uint64_t seed);
+  std::size_t nbytes() const;
+  Pld pld(double noise_multiplier, std::size_t n_prefix, const Config& cfg) const;
+};
 Pld balls_in_bins_mc_pld(const std::vector<double>& gram_row_major, std::size_t n, std::size_t num_bins,
                          double noise_multiplier, const Config& cfg);
 

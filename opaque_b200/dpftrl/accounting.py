@@ -25,6 +25,7 @@ import numpy as np
 
 from ..accounting.core import (DiscretizationConfig, DpHorizonProcess, DpProcess, PerStep, get_discretization, native,
                                per_step, register_process_codec)
+from . import _transcripts
 from .noise import MfStrategy, strategy_from_wire, strategy_to_wire
 
 
@@ -167,8 +168,15 @@ class BMinSep(DpHorizonProcess):
         coef = np.trim_zeros(np.asarray(self.inner.strategy.coefficients(n_steps), float), "b")
         if len(coef) > self.bands:
             raise ValueError(f"the strategy has {len(coef)} bands but the minimum separation is {self.bands}")
-        return native.b_min_sep_mc_pld(coef.tolist(), n_steps, self.bands, self.sampling_prob, self.inner.noise_multiplier,
-                                       self.warm_start, cfg.to_native())
+        ncfg = cfg.to_native()
+        nm = self.inner.noise_multiplier
+        # stored transcripts: every probe of a calibration search re-weights the same samples; when they would not fit
+        # the registry's byte cap the streaming accountant draws the same samples without keeping them
+        out = _transcripts.with_corpus(coef.tolist(), n_steps, self.bands, self.sampling_prob, self.warm_start,
+                                       ncfg.num_mc_samples, ncfg.seed, lambda corpus: corpus.pld(nm, n_steps, ncfg))
+        if out is not None:
+            return out
+        return native.b_min_sep_mc_pld(coef.tolist(), n_steps, self.bands, self.sampling_prob, nm, self.warm_start, ncfg)
 
     def _build_pld(self, config):
         return self.pld_at(self.n_steps, config)

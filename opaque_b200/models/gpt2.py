@@ -42,7 +42,7 @@ class GPT2Config:
 
 class _SplitHeads(torch.autograd.Function):
     """``[B, T, 3·d]`` → three ``[B, heads, T, d/heads]`` views; the backward writes the three gradients into ONE
-    buffer (three strided copies) instead of three zero-filled full-size tensors that are then added."""
+    buffer (one gather kernel) instead of three zero-filled full-size tensors that are then added."""
 
     @staticmethod
     def forward(ctx, qkv, heads):
@@ -53,11 +53,7 @@ class _SplitHeads(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, gq, gk, gv):
-        B, T, _, heads, hd = ctx.shape
-        out = torch.empty(ctx.shape, dtype=gq.dtype, device=gq.device)
-        for i, g in enumerate((gq, gk, gv)):
-            out[:, :, i].copy_(g.transpose(1, 2))
-        return out.view(B, T, 3 * heads * hd), None
+        return ops.merge_heads3(gq, gk, gv), None
 
 
 class GPT2Block(nn.Module):

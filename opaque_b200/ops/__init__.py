@@ -385,10 +385,10 @@ def shard_step(*, grad, master, m, v, params_local=None, peer_params=None, world
 
 from . import functional  # noqa: E402
 from .functional import (activation, cross_entropy, cross_entropy_ref, fused_add_rms_norm, geglu, glu_ref,  # noqa: E402
-                         layer_norm, plain_torch_ops, rms_norm, rms_norm_ref, rope_qk, rope_qk_ref, rope_tables, rows_group_sum_, swiglu)
+                         layer_norm, merge_heads3, plain_torch_ops, rms_norm, rms_norm_ref, rope_qk, rope_qk_ref, rope_tables, rows_group_sum_, swiglu)
 
 __all__ = [
-    "gemm", "gemm_ref", "ghost_set_wide", "push_grad_", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_",
+    "gemm", "gemm_ref", "ghost_set_wide", "push_grad_", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_", "merge_heads3",
     "DeviceWaitTimeout", "KernelLibraryError", "StatusWord", "clip_weighted_sum", "cross_entropy",
     "cross_entropy_ref", "embedding_wgrad", "fused_add_rms_norm", "geglu", "ghost_norm", "ghost_norm_ref", "glu_ref",
     "philox_normal_add_", "pick_block_n", "pick_splits", "rms_norm", "rms_norm_ref", "rope_qk", "rope_qk_ref",

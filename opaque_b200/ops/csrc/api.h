@@ -36,9 +36,15 @@ int ob_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float
                      int H, float eps, void* stream);
 int ob_layernorm_bwd_dx(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
                         long long rows, int H, void* stream);
-// out[e, :N] += sum over the rows of example e of g (mode 0) or g * (x - mean) * rstd (mode 1); out row pitch ld_out.
+// out[e, :N] += sum over the rows of example e of g (mode 0), g * (x - mean) * rstd (mode 1) or g * x * rstd (mode 2);
+// out row pitch ld_out.  In modes 1 and 2 a non-NULL out2 (row pitch ld_out2) also receives the plain sums of g.
 int ob_rows_group_sum(const void* g, const void* x, const float* mean, const float* rstd, int num_examples,
-                      int rows_per_example, int N, long long ldg, float* out, long long ld_out, int mode, void* stream);
+                      int rows_per_example, int N, long long ldg, float* out, long long ld_out, int mode, float* out2,
+                      long long ld_out2, void* stream);
+// q, k, v gradients [B, heads, T, hd] (strides[9] = batch, head, token stride of each, in elements; head vectors
+// contiguous) -> out [B*T, 3*heads*hd] bf16.
+int ob_merge_heads3(const void* q, const void* k, const void* v, const long long* strides, void* out, long long B, int T,
+                    int heads, int hd, int sms, void* stream);
 // out = act(x) (dy == NULL) or dy * act'(x); act: 0 silu, 1 gelu erf, 2 gelu tanh, 3 relu.
 int ob_activation(const void* x, const void* dy, void* out, long long numel, int act, int sms, void* stream);
 

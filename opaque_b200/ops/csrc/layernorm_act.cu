@@ -334,17 +334,19 @@ layernorm_bwd_dx_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bf
 __global__ void __launch_bounds__(256)
 rows_group_sum_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ x,
                       const float* __restrict__ mean, const float* __restrict__ rstd, int rows_per_example, int N,
-                      long long ldg, float* __restrict__ out, long long ld_out, int mode) {
+                      long long ldg, float* __restrict__ out, long long ld_out, int mode, float* __restrict__ out2,
+                      long long ld_out2) {
   __shared__ float red[8][256 + 8];
+  __shared__ float red2[8][256 + 8];
   const int e = blockIdx.x;
   const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
   const int col = blockIdx.y * 256 + cg * 8;
   const int chunk = (rows_per_example + gridDim.z - 1) / gridDim.z;
   const int r0 = e * rows_per_example + blockIdx.z * chunk;
   const int r1 = min(r0 + chunk, (e + 1) * rows_per_example);
-  float acc[8];
+  float acc[8], acc2[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  for (int j = 0; j < 8; ++j) acc[j] = acc2[j] = 0.f;
   if (col < N) {
     for (int r = r0 + rl; r < r1; r += 8) {
       float gv[8];
@@ -354,7 +356,10 @@ rows_group_sum_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* 
         ln_unpack8(*reinterpret_cast<const ln_bf16x8*>(x + static_cast<long long>(r) * ldg + col), xv);
         const float mu = (mode == 1) ? __ldg(mean + r) : 0.f, rs = __ldg(rstd + r);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += gv[j] * (xv[j] - mu) * rs;
+        for (int j = 0; j < 8; ++j) {
+          acc[j] += gv[j] * (xv[j] - mu) * rs;
+          acc2[j] += gv[j];                      // the bias gradient of the same pass (used when out2 is given)
+        }
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] += gv[j];
@@ -362,14 +367,49 @@ rows_group_sum_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* 
     }
   }
 #pragma unroll
-  for (int j = 0; j < 8; ++j) red[rl][cg * 8 + j] = acc[j];
+  for (int j = 0; j < 8; ++j) {
+    red[rl][cg * 8 + j] = acc[j];
+    if (out2 != nullptr) red2[rl][cg * 8 + j] = acc2[j];
+  }
   __syncthreads();
   const int c = threadIdx.x;
   if (blockIdx.y * 256 + c < N) {
-    float t = 0.f;
+    float t = 0.f, t2 = 0.f;
 #pragma unroll
     for (int k = 0; k < 8; ++k) t += red[k][c];
     atomicAdd(out + static_cast<long long>(e) * ld_out + blockIdx.y * 256 + c, t);
+    if (out2 != nullptr) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) t2 += red2[k][c];
+      atomicAdd(out2 + static_cast<long long>(e) * ld_out2 + blockIdx.y * 256 + c, t2);
+    }
+  }
+}
+
+// Gradients of the three attention inputs, each [B, heads, T, hd] with arbitrary (16-byte aligned) batch / head / token
+// strides and contiguous head vectors, gathered into ONE [B*T, 3*heads*hd] buffer: the layout the fused q/k/v
+// projection produced in the forward pass.  One thread moves one 16-byte vector; consecutive threads write
+// consecutive destination vectors.
+struct MergeHeadsSrc {
+  const __nv_bfloat16* p;
+  long long sb, sh, st;
+};
+
+__global__ void __launch_bounds__(256)
+merge_heads3_kernel(MergeHeadsSrc s0, MergeHeadsSrc s1, MergeHeadsSrc s2, __nv_bfloat16* __restrict__ out, int T,
+                    int heads, int hd, long long total_vec) {
+  const int vec_per_head = hd >> 3;
+  const int vec_per_part = heads * vec_per_head;
+  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < total_vec; i += gridDim.x * 256LL) {
+    const int within = static_cast<int>(i % vec_per_part);
+    const long long rest = i / vec_per_part;          // (row, part)
+    const int part = static_cast<int>(rest % 3);
+    const long long row = rest / 3;
+    const int h = within / vec_per_head, v = within % vec_per_head;
+    const long long b = row / T, t = row % T;
+    const MergeHeadsSrc& s = part == 0 ? s0 : (part == 1 ? s1 : s2);
+    reinterpret_cast<ln_bf16x8*>(out)[i] =
+        *reinterpret_cast<const ln_bf16x8*>(s.p + b * s.sb + h * s.sh + t * s.st + v * 8);
   }
 }
 
@@ -461,7 +501,7 @@ extern "C" int ob_layernorm_bwd_dx(const void* dy, const void* x, const void* w,
 
 extern "C" int ob_rows_group_sum(const void* g, const void* x, const float* mean, const float* rstd, int num_examples,
                                  int rows_per_example, int N, long long ldg, float* out, long long ld_out, int mode,
-                                 void* stream) {
+                                 float* out2, long long ld_out2, void* stream) {
   if (num_examples <= 0 || rows_per_example <= 0 || N <= 0) return 0;
   if ((N & 7) || (ldg & 7) || (reinterpret_cast<uintptr_t>(g) & 15) || (x != nullptr && (reinterpret_cast<uintptr_t>(x) & 15)))
     return -2;
@@ -472,7 +512,30 @@ extern "C" int ob_rows_group_sum(const void* g, const void* x, const float* mean
   dim3 grid(num_examples, (N + 255) / 256, splits);
   rows_group_sum_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(g), static_cast<const __nv_bfloat16*>(x), mean, rstd, rows_per_example, N, ldg,
-      out, ld_out, mode);
+      out, ld_out, mode, mode == 0 ? nullptr : out2, ld_out2);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int ob_merge_heads3(const void* q, const void* k, const void* v, const long long* strides, void* out,
+                               long long B, int T, int heads, int hd, int sms, void* stream) {
+  if (B <= 0 || T <= 0) return 0;
+  if (hd % 8) return -2;
+  const void* ptrs[3] = {q, k, v};
+  MergeHeadsSrc src[3];
+  for (int i = 0; i < 3; ++i) {
+    src[i].p = static_cast<const __nv_bfloat16*>(ptrs[i]);
+    src[i].sb = strides[3 * i];
+    src[i].sh = strides[3 * i + 1];
+    src[i].st = strides[3 * i + 2];
+    if ((reinterpret_cast<uintptr_t>(ptrs[i]) & 15) || (src[i].sb & 7) || (src[i].sh & 7) || (src[i].st & 7)) return -2;
+  }
+  if (reinterpret_cast<uintptr_t>(out) & 15) return -2;
+  const long long total_vec = B * T * 3 * heads * (hd / 8);
+  long long grid = (total_vec + 255) / 256;
+  const long long cap = static_cast<long long>(sms) * 16;
+  if (grid > cap) grid = cap;
+  merge_heads3_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      src[0], src[1], src[2], static_cast<__nv_bfloat16*>(out), T, heads, hd, total_vec);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 

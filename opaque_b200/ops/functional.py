@@ -11,6 +11,7 @@ cross_entropy.py:585-681.
 from __future__ import annotations
 
 import contextlib
+import ctypes
 
 import torch
 from torch.autograd import Function
@@ -143,17 +144,43 @@ def fused_add_rms_norm(x, residual, weight, eps=1e-6, offset=0.0, casting_mode="
 # =============================================================================== LayerNorm
 
 def rows_group_sum_(out: torch.Tensor, g2d: torch.Tensor, num_examples: int, *, x2d: torch.Tensor | None = None,
-                    mean: torch.Tensor | None = None, rstd: torch.Tensor | None = None) -> None:
+                    mean: torch.Tensor | None = None, rstd: torch.Tensor | None = None,
+                    out_plain: torch.Tensor | None = None) -> None:
     """``out[e] += Σ_{rows of example e} g`` (or ``g·(x−mean)·rstd`` when statistics are given); ``out`` fp32 ``[B, N]``
-    (any row pitch), ``g2d`` bf16 ``[B·T, N]``."""
+    (any row pitch), ``g2d`` bf16 ``[B·T, N]``.  With statistics, ``out_plain`` also receives the plain sums ``Σ g`` of
+    the same pass (a LayerNorm's weight and bias gradients in one read of ``g``)."""
     rows, N = g2d.shape
-    if out.dtype != torch.float32 or out.shape != (num_examples, N) or out.stride(1) != 1 or rows % num_examples:
-        raise ValueError("rows_group_sum_: out must be fp32 [examples, N] and rows a multiple of examples")
+    for o in (out, out_plain):
+        if o is not None and (o.dtype != torch.float32 or o.shape != (num_examples, N) or o.stride(1) != 1):
+            raise ValueError("rows_group_sum_: out must be fp32 [examples, N]")
+    if rows % num_examples:
+        raise ValueError("rows_group_sum_: rows must be a multiple of examples")
     mode = 0 if x2d is None else (1 if mean is not None else 2)          # 2: g * x * rstd (RMSNorm weight gradient)
+    if mode == 0 and out_plain is not None:
+        raise ValueError("rows_group_sum_: out_plain needs x2d (without it, out already is the plain sum)")
     rc = lib.load().ob_rows_group_sum(g2d.data_ptr(), lib.ptr(x2d), lib.ptr(mean), lib.ptr(rstd), num_examples,
                                       rows // num_examples, N, g2d.stride(0), out.data_ptr(), out.stride(0), mode,
-                                      lib.stream())
+                                      lib.ptr(out_plain), 0 if out_plain is None else out_plain.stride(0), lib.stream())
     lib.check(rc, "rows_group_sum")
+
+
+def merge_heads3(gq: torch.Tensor, gk: torch.Tensor, gv: torch.Tensor) -> torch.Tensor:
+    """Three ``[B, heads, T, hd]`` bf16 tensors (any batch / head / token strides, contiguous head vectors) gathered into
+    one ``[B, T, 3·heads·hd]`` tensor in ONE launch: the gradient of splitting a fused q/k/v projection into heads."""
+    B, H, T, hd = gq.shape
+    ok = all(t.is_cuda and t.dtype == torch.bfloat16 and t.shape == gq.shape and t.stride(3) == 1 and
+             t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3]) for t in (gq, gk, gv)) and hd % 8 == 0
+    out = torch.empty(B, T, 3 * H * hd, dtype=gq.dtype, device=gq.device)
+    if not ok or not kernels_enabled():
+        v5 = out.view(B, T, 3, H, hd)
+        for i, g in enumerate((gq, gk, gv)):
+            v5[:, :, i].copy_(g.transpose(1, 2))
+        return out
+    strides = (ctypes.c_longlong * 9)(*[s for t in (gq, gk, gv) for s in (t.stride(0), t.stride(1), t.stride(2))])
+    rc = lib.load().ob_merge_heads3(gq.data_ptr(), gk.data_ptr(), gv.data_ptr(), strides, out.data_ptr(), B, T, H, hd,
+                                    lib.sm_count(), lib.stream())
+    lib.check(rc, "merge_heads3")
+    return out
 
 
 class _LayerNorm(Function):
@@ -188,13 +215,11 @@ class _LayerNorm(Function):
         cap = _param_grad_hook() if weight.requires_grad else None
         dw = db = None
         if cap is not None:                      # per-example gradients straight into the capture's buffer rows
-            rows_group_sum_(cap.pe_view(layer.weight), dy2, cap.batch_size, x2d=x2, mean=stats[0], rstd=stats[1])
-            if has_bias:
-                rows_group_sum_(cap.pe_view(layer.bias), dy2, cap.batch_size)
+            rows_group_sum_(cap.pe_view(layer.weight), dy2, cap.batch_size, x2d=x2, mean=stats[0], rstd=stats[1],
+                            out_plain=cap.pe_view(layer.bias) if has_bias else None)
         elif weight.requires_grad:
             acc = torch.zeros(2, 1, H, dtype=torch.float32, device=x2.device)
-            rows_group_sum_(acc[0], dy2, 1, x2d=x2, mean=stats[0], rstd=stats[1])
-            rows_group_sum_(acc[1], dy2, 1)
+            rows_group_sum_(acc[0], dy2, 1, x2d=x2, mean=stats[0], rstd=stats[1], out_plain=acc[1])
             dw, db = acc[0, 0].to(weight.dtype), (acc[1, 0].to(weight.dtype) if has_bias else None)
         return dx.view(shape), dw, db, None, None
 

@@ -23,7 +23,8 @@ _SIGNATURES = {
     "ob_gemm_tn": [P, P, P, P, P, P, LL, I, I, I, LL, LL, LL, LL, LL, I, P, I, P, D, I, P],
     "ob_layernorm_fwd": [P, P, P, P, P, P, LL, I, F, P],
     "ob_layernorm_bwd_dx": [P, P, P, P, P, P, LL, I, P],
-    "ob_rows_group_sum": [P, P, P, P, I, I, I, LL, P, LL, I, P],
+    "ob_rows_group_sum": [P, P, P, P, I, I, I, LL, P, LL, I, P, LL, P],
+    "ob_merge_heads3": [P, P, P, P, P, LL, I, I, I, I, P],
     "ob_activation": [P, P, P, LL, I, I, P],
     "ob_ghost_set_wide": [I],
     "ob_push_grad": [P, LL, P, LL, I, P],

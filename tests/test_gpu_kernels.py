@@ -485,3 +485,27 @@ def test_layer_norm_all_row_widths(dev, H):
     y.backward(dy)
     yr.backward(dy.float())
     assert rel(xg.grad, xr.grad) < 6e-3
+
+
+@pytest.mark.gpu
+def test_layernorm_weight_and_bias_sums_in_one_pass_and_head_merge(dev):
+    from opaque_b200 import ops
+    torch.manual_seed(11)
+    B, T, H = 3, 160, 768
+    g = torch.randn(B * T, H, device=dev).bfloat16()
+    x = (torch.randn(B * T, H, device=dev) * 2 + 1).bfloat16()
+    mean, rstd = x.float().mean(1), (x.float().var(1, unbiased=False) + 1e-5).rsqrt()
+    dw, db = torch.zeros(B, H, device=dev), torch.full((B, H + 8), 2.0, device=dev)
+    ops.rows_group_sum_(dw, g, B, x2d=x, mean=mean, rstd=rstd, out_plain=db[:, 4:4 + H])
+    xh = (x.float() - mean[:, None]) * rstd[:, None]
+    assert rel(dw, (g.float() * xh).view(B, T, H).sum(1)) < 1e-5
+    assert rel(db[:, 4:4 + H], 2 + g.float().view(B, T, H).sum(1)) < 1e-5 and float(db[:, :4].min()) == 2.0
+    # gradient gather of the fused q/k/v projection: sources in two different layouts
+    heads, hd = 12, 64
+    gq = torch.randn(B, heads, T, hd, device=dev).bfloat16()                                  # [B, H, T, hd] contiguous
+    gk = torch.randn(B, T, heads, hd, device=dev).bfloat16().transpose(1, 2)                  # [B, T, H, hd] memory
+    big = torch.randn(B, T, 3, heads, hd, device=dev).bfloat16()
+    gv = big[:, :, 2].transpose(1, 2)                                                        # a slice of a fused buffer
+    out = ops.merge_heads3(gq, gk, gv)
+    ref = torch.stack([t.transpose(1, 2) for t in (gq, gk, gv)], dim=2).reshape(B, T, 3 * heads * hd)
+    assert torch.equal(out, ref)

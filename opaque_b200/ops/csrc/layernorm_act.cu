@@ -229,57 +229,54 @@ layernorm_bwd_dx_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfl
   }
 }
 
-// Warp-per-row variants for narrow rows (H <= 1024): one warp keeps LN_WARP_R rows in registers (VPL 16-byte vectors
-// per lane and row, masked at the row end) and reduces with shuffles only, so a CTA never synchronises.  Measured at
-// H = 768: one row per warp 3.3 TB/s, two rows per warp 3.0 TB/s.
+// Warp-per-row variants for narrow rows (H <= 1024).  A warp walks over rows (stride = warps in the grid) with the
+// weight and bias vectors packed in registers for the whole walk, holds one row in registers (VPL 16-byte vectors per
+// lane, masked at the row end) and reduces with shuffles only, so a CTA never synchronises.  The kernel is bound by
+// the load/store unit's data pipe (a profile of the one-row-per-launch-warp version showed it at 91 % with DRAM at 39 %:
+// per row the weight and bias re-reads cost as many wavefronts as the row itself), hence the register-resident
+// parameters; two rows per warp in flight measured slower than one (3.0 vs 3.3 TB/s at H = 768).
 constexpr int LN_WARPS = 8;
-constexpr int LN_WARP_R = 1;
-constexpr int LN_WARP_ROWS = LN_WARPS * LN_WARP_R;          // rows per CTA
 
 template <int VPL>
-__global__ void __launch_bounds__(32 * LN_WARPS)
+__global__ void __launch_bounds__(32 * LN_WARPS, VPL >= 3 ? 2 : 3)
 layernorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                           const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y, float* __restrict__ mean,
                           float* __restrict__ rstd, long long rows, int H, float eps) {
   const int lane = threadIdx.x & 31;
-  const long long row0 = (static_cast<long long>(blockIdx.x) * LN_WARPS + (threadIdx.x >> 5)) * LN_WARP_R;
-  if (row0 >= rows) return;                                  // whole warps leave together; nothing below synchronises
+  const long long stride = static_cast<long long>(gridDim.x) * LN_WARPS;
+  long long row = static_cast<long long>(blockIdx.x) * LN_WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;                                   // whole warps leave together; nothing below synchronises
   const int nv = H >> 3;
-  float f[LN_WARP_R][VPL][8];
-  float s[LN_WARP_R], ss[LN_WARP_R];
+  const float inv_h = 1.f / H;
+  ln_bf16x8 wp[VPL], bp[VPL];
 #pragma unroll
-  for (int r = 0; r < LN_WARP_R; ++r) {
-    s[r] = ss[r] = 0.f;
-    const long long row = min(row0 + r, rows - 1);           // a row past the end re-reads the last one, never stores
-    const ln_bf16x8* xr = reinterpret_cast<const ln_bf16x8*>(x + row * H);
-#pragma unroll
-    for (int v = 0; v < VPL; ++v) {
-      const int i = lane + v * 32;
-      if (i < nv) ln_unpack8(xr[i], f[r][v]);
+  for (int v = 0; v < VPL; ++v) {
+    const int i = lane + v * 32;
+    if (i < nv) {
+      wp[v] = reinterpret_cast<const ln_bf16x8*>(w)[i];
+      if (b != nullptr) bp[v] = reinterpret_cast<const ln_bf16x8*>(b)[i];
     }
   }
+  for (; row < rows; row += stride) {
+    const ln_bf16x8* xr = reinterpret_cast<const ln_bf16x8*>(x + row * H);
+    float f[VPL][8];
+    float s = 0.f, ss = 0.f;
 #pragma unroll
-  for (int r = 0; r < LN_WARP_R; ++r)
+    for (int v = 0; v < VPL; ++v)
+      if (lane + v * 32 < nv) ln_unpack8(xr[lane + v * 32], f[v]);
 #pragma unroll
     for (int v = 0; v < VPL; ++v)
       if (lane + v * 32 < nv) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          s[r] += f[r][v][j];
-          ss[r] += f[r][v][j] * f[r][v][j];
+          s += f[v][j];
+          ss += f[v][j] * f[v][j];
         }
       }
-#pragma unroll
-  for (int r = 0; r < LN_WARP_R; ++r) {
-    s[r] = warp_sum(s[r]);
-    ss[r] = warp_sum(ss[r]);
-  }
-#pragma unroll
-  for (int r = 0; r < LN_WARP_R; ++r) {
-    const long long row = row0 + r;
-    if (row >= rows) break;
-    const float mu = s[r] / H;
-    const float rs = rsqrtf(fmaxf(ss[r] / H - mu * mu, 0.f) + eps);
+    s = warp_sum(s);
+    ss = warp_sum(ss);
+    const float mu = s * inv_h;
+    const float rs = rsqrtf(fmaxf(ss * inv_h - mu * mu, 0.f) + eps);
     if (lane == 0) {
       mean[row] = mu;
       rstd[row] = rs;
@@ -290,80 +287,65 @@ layernorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
       const int i = lane + v * 32;
       if (i < nv) {
         float g[8], h[8];
-        ln_unpack8(reinterpret_cast<const ln_bf16x8*>(w)[i], g);
-        if (b != nullptr) ln_unpack8(reinterpret_cast<const ln_bf16x8*>(b)[i], h);
+        ln_unpack8(wp[v], g);
+        if (b != nullptr) ln_unpack8(bp[v], h);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[r][v][j] = (f[r][v][j] - mu) * rs * g[j] + (b != nullptr ? h[j] : 0.f);
-        yr[i] = ln_pack8(f[r][v]);
+        for (int j = 0; j < 8; ++j) f[v][j] = (f[v][j] - mu) * rs * g[j] + (b != nullptr ? h[j] : 0.f);
+        yr[i] = ln_pack8(f[v]);
       }
     }
   }
 }
 
 template <int VPL>
-__global__ void __launch_bounds__(32 * LN_WARPS)
+__global__ void __launch_bounds__(32 * LN_WARPS, VPL >= 3 ? 2 : 3)
 layernorm_bwd_dx_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                              const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean,
                              const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx, long long rows, int H) {
   const int lane = threadIdx.x & 31;
-  const long long row0 = (static_cast<long long>(blockIdx.x) * LN_WARPS + (threadIdx.x >> 5)) * LN_WARP_R;
-  if (row0 >= rows) return;
+  const long long stride = static_cast<long long>(gridDim.x) * LN_WARPS;
+  long long row = static_cast<long long>(blockIdx.x) * LN_WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
   const int nv = H >> 3;
-  float gw[LN_WARP_R][VPL][8], xh[LN_WARP_R][VPL][8];
-  float s1[LN_WARP_R], s2[LN_WARP_R], rs[LN_WARP_R], mu[LN_WARP_R];
+  const float inv_h = 1.f / H;
+  ln_bf16x8 wp[VPL];
 #pragma unroll
-  for (int r = 0; r < LN_WARP_R; ++r) {
-    const long long row = min(row0 + r, rows - 1);
-    mu[r] = mean[row];
-    rs[r] = rstd[row];
+  for (int v = 0; v < VPL; ++v)
+    if (lane + v * 32 < nv) wp[v] = reinterpret_cast<const ln_bf16x8*>(w)[lane + v * 32];
+  for (; row < rows; row += stride) {
+    const float mu = mean[row], rs = rstd[row];
     const ln_bf16x8* gr = reinterpret_cast<const ln_bf16x8*>(dy + row * H);
     const ln_bf16x8* xr = reinterpret_cast<const ln_bf16x8*>(x + row * H);
+    float gw[VPL][8], xh[VPL][8];
+    float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) {
-      const int i = lane + v * 32;
-      if (i < nv) {
-        ln_unpack8(gr[i], gw[r][v]);
-        ln_unpack8(xr[i], xh[r][v]);
+    for (int v = 0; v < VPL; ++v)
+      if (lane + v * 32 < nv) {
+        ln_unpack8(gr[lane + v * 32], gw[v]);
+        ln_unpack8(xr[lane + v * 32], xh[v]);
       }
-    }
-  }
 #pragma unroll
-  for (int r = 0; r < LN_WARP_R; ++r) {
-    s1[r] = s2[r] = 0.f;
-#pragma unroll
-    for (int v = 0; v < VPL; ++v) {
-      const int i = lane + v * 32;
-      if (i < nv) {
+    for (int v = 0; v < VPL; ++v)
+      if (lane + v * 32 < nv) {
         float c[8];
-        ln_unpack8(reinterpret_cast<const ln_bf16x8*>(w)[i], c);
+        ln_unpack8(wp[v], c);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          gw[r][v][j] *= c[j];
-          xh[r][v][j] = (xh[r][v][j] - mu[r]) * rs[r];
-          s1[r] += gw[r][v][j];
-          s2[r] += gw[r][v][j] * xh[r][v][j];
+          gw[v][j] *= c[j];
+          xh[v][j] = (xh[v][j] - mu) * rs;
+          s1 += gw[v][j];
+          s2 += gw[v][j] * xh[v][j];
         }
       }
-    }
-  }
-#pragma unroll
-  for (int r = 0; r < LN_WARP_R; ++r) {
-    s1[r] = warp_sum(s1[r]);
-    s2[r] = warp_sum(s2[r]);
-  }
-#pragma unroll
-  for (int r = 0; r < LN_WARP_R; ++r) {
-    const long long row = row0 + r;
-    if (row >= rows) break;
-    const float m1 = s1[r] / H, m2 = s2[r] / H;
+    const float m1 = warp_sum(s1) * inv_h, m2 = warp_sum(s2) * inv_h;
     ln_bf16x8* or_ = reinterpret_cast<ln_bf16x8*>(dx + row * H);
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
       const int i = lane + v * 32;
       if (i < nv) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) gw[r][v][j] = rs[r] * (gw[r][v][j] - m1 - xh[r][v][j] * m2);
-        or_[i] = ln_pack8(gw[r][v]);
+        for (int j = 0; j < 8; ++j) gw[v][j] = rs * (gw[v][j] - m1 - xh[v][j] * m2);
+        or_[i] = ln_pack8(gw[v]);
       }
     }
   }
@@ -504,6 +486,15 @@ activation_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
 
 using namespace ob;
 
+// CTAs of the warp-per-row kernels: one warp per row while that fills fewer CTAs than are resident at once (two per SM
+// for rows wider than 512, else three), else that many CTAs, whose warps walk over the rows
+static unsigned ln_warp_grid(long long rows, int H) {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long want = (rows + ob::LN_WARPS - 1) / ob::LN_WARPS, cap = static_cast<long long>(sms) * (H > 512 ? 2 : 3);
+  return static_cast<unsigned>(want < cap ? want : cap);
+}
+
 extern "C" int ob_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
                                 long long rows, int H, float eps, void* stream) {
   if (rows <= 0) return 0;
@@ -513,7 +504,7 @@ extern "C" int ob_layernorm_fwd(const void* x, const void* w, const void* b, voi
                       *bp = static_cast<const __nv_bfloat16*>(b);
   __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
   const unsigned pairs = static_cast<unsigned>((rows + 1) / 2);
-  const unsigned octs = static_cast<unsigned>((rows + LN_WARP_ROWS - 1) / LN_WARP_ROWS);
+  const unsigned octs = ln_warp_grid(rows, H);
   if (H <= 256) layernorm_fwd_warp_kernel<1><<<octs, 32 * LN_WARPS, 0, st>>>(xp, wp, bp, yp, mean, rstd, rows, H, eps);
   else if (H <= 512) layernorm_fwd_warp_kernel<2><<<octs, 32 * LN_WARPS, 0, st>>>(xp, wp, bp, yp, mean, rstd, rows, H, eps);
   else if (H <= 768) layernorm_fwd_warp_kernel<3><<<octs, 32 * LN_WARPS, 0, st>>>(xp, wp, bp, yp, mean, rstd, rows, H, eps);
@@ -533,7 +524,7 @@ extern "C" int ob_layernorm_bwd_dx(const void* dy, const void* x, const void* w,
                       *wp = static_cast<const __nv_bfloat16*>(w);
   __nv_bfloat16* op = static_cast<__nv_bfloat16*>(dx);
   const unsigned pairs = static_cast<unsigned>((rows + 1) / 2);
-  const unsigned octs = static_cast<unsigned>((rows + LN_WARP_ROWS - 1) / LN_WARP_ROWS);
+  const unsigned octs = ln_warp_grid(rows, H);
   if (H <= 256) layernorm_bwd_dx_warp_kernel<1><<<octs, 32 * LN_WARPS, 0, st>>>(gp, xp, wp, mean, rstd, op, rows, H);
   else if (H <= 512) layernorm_bwd_dx_warp_kernel<2><<<octs, 32 * LN_WARPS, 0, st>>>(gp, xp, wp, mean, rstd, op, rows, H);
   else if (H <= 768) layernorm_bwd_dx_warp_kernel<3><<<octs, 32 * LN_WARPS, 0, st>>>(gp, xp, wp, mean, rstd, op, rows, H);

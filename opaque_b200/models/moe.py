@@ -100,7 +100,8 @@ def route_sort(topk_idx: torch.Tensor, num_experts: int, batch: int, tokens: int
     token_of = torch.arange(T, device=topk_idx.device).repeat_interleave(k)
     key = flat_e * batch + token_of // tokens
     order = torch.argsort(key, stable=True)
-    counts = torch.bincount(key, minlength=num_experts * batch)
+    # scatter-add instead of bincount: bincount reads the maximum back to the host, which a graph capture cannot do
+    counts = torch.zeros(num_experts * batch, dtype=torch.int64, device=key.device).scatter_add_(0, key, torch.ones_like(key))
     seg = torch.zeros(num_experts * batch + 1, dtype=torch.int32, device=topk_idx.device)
     seg[1:] = counts.cumsum(0)
     offs = seg[batch::batch].contiguous()

@@ -40,6 +40,7 @@ from .peer import PeerGroup
 
 ALIGN = 64
 LOCAL_ACCUMULATE_LIMIT_BYTES = 16 << 30      # "auto": accumulate locally when the full fp32 gradient fits in 16 GiB
+LOCAL_ACCUMULATE_RESERVE_BYTES = 32 << 30    # ... or when this much device memory stays free after it and the optimizer shards
 
 
 @dataclasses.dataclass(frozen=True)
@@ -65,7 +66,8 @@ class FlatSpace:
         """``accumulate="peer"`` (default): producer kernels reduce every microbatch's tiles straight into the owners'
         shards.  ``"local"``: they add into a full-length local fp32 buffer and ONE push per step reduces it into the
         owners' shards — (microbatches per step)× less reduction traffic over NVLink at the price of ``4·P`` bytes.
-        ``"auto"``: local while that buffer stays under ``LOCAL_ACCUMULATE_LIMIT_BYTES``."""
+        ``"auto"``: local while that buffer stays under ``LOCAL_ACCUMULATE_LIMIT_BYTES`` or leaves
+        ``LOCAL_ACCUMULATE_RESERVE_BYTES`` of device memory free."""
         if accumulate not in ("peer", "local", "auto"):
             raise ValueError("accumulate must be 'peer', 'local' or 'auto'")
         self.group = group
@@ -96,7 +98,7 @@ class FlatSpace:
         self.grad = group.buffer(self.shard, torch.float32)
         dev = group.device
         if accumulate == "auto":     # measured on 4 GPUs: per-microbatch peer reductions cost 15-35 % for 0.1-1 B parameter
-            accumulate = "local" if 4 * self.total <= LOCAL_ACCUMULATE_LIMIT_BYTES else "peer"      # models; huge models keep memory
+            accumulate = "local" if self._local_accumulation_fits() else "peer"                     # models
         self.accumulate = accumulate if group.world > 1 else "peer"
         self.grad_full = torch.zeros(self.total, dtype=torch.float32, device=dev) if self.accumulate == "local" else None
         self.master = torch.zeros(self.shard, dtype=torch.float32, device=dev)
@@ -141,6 +143,23 @@ class FlatSpace:
         if self.grad_full is not None:
             return {"out": self.grad_full, "peer_table": None, "shard_elems": 0}
         return {"out": None, "peer_table": self.grad.table, "shard_elems": self.shard}
+
+    def _local_accumulation_fits(self) -> bool:
+        """``accumulate="auto"``: take the local fp32 buffer when it is small (under ``LOCAL_ACCUMULATE_LIMIT_BYTES``) or
+        when, after it and the optimizer shards, ``LOCAL_ACCUMULATE_RESERVE_BYTES`` of device memory stay free for
+        activations.  Ranks agree on the answer (the minimum), so one tight GPU keeps every rank on peer reductions."""
+        local_bytes = 4 * self.total
+        fits = local_bytes <= LOCAL_ACCUMULATE_LIMIT_BYTES
+        dev = self.group.device
+        if not fits and dev.type == "cuda" and self.group.world > 1:
+            free, _total = torch.cuda.mem_get_info(dev)
+            shards = 3 * 4 * self.shard                      # master, m, v (allocated right after this decision)
+            fits = free - local_bytes - shards >= LOCAL_ACCUMULATE_RESERVE_BYTES
+        if self.group.world > 1 and torch.distributed.is_available() and torch.distributed.is_initialized():
+            flag = torch.tensor([1 if fits else 0], dtype=torch.int32, device=dev)
+            torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
+            fits = bool(int(flag.item()))
+        return fits
 
     def push_local_gradient(self) -> None:
         """``accumulate="local"``: reduce this rank's accumulated gradient into the owners' shards (before the barrier)."""

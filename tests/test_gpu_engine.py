@@ -204,3 +204,30 @@ def test_noise_is_added_exactly_once_and_matches_sigma():
 def test_smoke_entry_point():
     import __graft_entry__ as g
     g.smoke()
+
+
+def test_cuda_graph_microbatches_match_eager_execution_moe():
+    """The MoE microbatch (routing sort, grouped GEMMs, ragged ghost norms, grouped clip-weighted GEMM) has static
+    shapes and no host synchronisation, so it replays as one graph too.  Kept last in the file: a failed capture would
+    leave the process's RNG offset bookkeeping unusable for later captures."""
+    from opaque_b200.engine.fused import FusedDPEngine
+    from opaque_b200.models import MoEConfig, MoEForCausalLM, shift_labels
+    from opaque_b200.random import key
+    dev = torch.device("cuda", 0)
+    ids = torch.randint(0, 500, (7, 128), device=dev)           # microbatches of 4 and 3 (padded to a graphed size)
+    labels = shift_labels(ids, 1.0)
+    flats, norms = [], []
+    for graph in (False, True):
+        torch.manual_seed(8)
+        m = MoEForCausalLM(MoEConfig.tiny(), device=dev)
+        eng = FusedDPEngine(m, clipping_norm=1.0, noise_multiplier=0.0, normalize_by=1.0, key=key(0), microbatch_size=4,
+                            cuda_graph=graph)
+        for _ in range(2):
+            eng.space.grad.local.zero_()
+            res = eng.accumulate(m.per_example_loss, {"input_ids": ids, "labels": labels})
+        torch.cuda.synchronize()
+        assert eng.status.read() == 0
+        flats.append(eng.space.grad.local.clone())
+        norms.append(res.norms.clone())
+    assert float((norms[0] - norms[1]).abs().max() / norms[0].max()) < 1e-3
+    assert float((flats[0] - flats[1]).norm() / flats[0].norm()) < 2e-3

@@ -696,11 +696,11 @@ class DPTrainer:
                 from ..ops.functional import plain_torch_ops
                 with plain_torch_ops():          # vmap needs plain PyTorch ops (no custom autograd nodes)
                     (grads, aux), clip_state = self._grad_fn(self._trainable, payload, state=self._clip_state)
-            except Exception as exc:      # noqa: BLE001 — only OOM is swallowed
-                if not _is_retryable_oom(exc):
+            except Exception as exc:      # noqa: BLE001 — only OOM is swallowed, and only with auto_find_microbatch_size
+                if not (self.args.auto_find_microbatch_size and _is_retryable_oom(exc)):
                     raise
                 oom = True
-            if not self._cluster_flag(oom):
+            if not (self.args.auto_find_microbatch_size and self._cluster_flag(oom)):
                 break
             if self._microbatch <= 1:
                 raise torch.OutOfMemoryError("out of memory at microbatch size 1")
@@ -748,11 +748,11 @@ class DPTrainer:
             oom = False
             try:
                 res = self._fused.accumulate(self.model.per_example_loss, payload)
-            except Exception as exc:      # noqa: BLE001 — only OOM is swallowed
-                if not _is_retryable_oom(exc):
+            except Exception as exc:      # noqa: BLE001 — only OOM is swallowed, and only with auto_find_microbatch_size
+                if not (self.args.auto_find_microbatch_size and _is_retryable_oom(exc)):
                     raise
                 oom = True
-            if not self._cluster_flag(oom):
+            if not (self.args.auto_find_microbatch_size and self._cluster_flag(oom)):
                 break
             if self._fused.microbatch_size <= 1:
                 raise torch.OutOfMemoryError("out of memory at microbatch size 1")

@@ -72,7 +72,8 @@ def test_fused_trainer_steps_down_after_a_simulated_oom(tmp_path):
             raise torch.OutOfMemoryError("simulated")
         return inner(input_ids, labels, **kw)
     model.per_example_loss = flaky
-    tr = DPTrainer(model=model, args=_args(tmp_path, save_steps=0, per_device_train_batch_size=16, microbatch_size=8), train_dataset=_rows())
+    tr = DPTrainer(model=model, args=_args(tmp_path, save_steps=0, per_device_train_batch_size=16, microbatch_size=8,
+                                       auto_find_microbatch_size=True), train_dataset=_rows())
     out = tr.train()
     assert fired and out["global_step"] == 4 and tr._fused.microbatch_size == 4
     assert float(tr._fused.space.grad.local.abs().max()) == 0.0          # consumed by the last step, nothing left over

@@ -161,3 +161,24 @@ def test_report_to_jsonl_writes_metrics(tmp_path):
     assert rows and any("epsilon" in r for r in rows) and all("step" in r for r in rows)
     with pytest.raises(ValueError):
         DPTrainer(model=TinyLM(), args=_args(tmp_path, report_to="carrier-pigeon"), train_dataset=_data())
+
+
+def test_out_of_memory_steps_the_microbatch_down_only_when_asked(tmp_path):
+    """Host-injected failure: the model raises OutOfMemoryError on its first call."""
+    class FlakyOnce(TinyLM):
+        fired = 0
+
+        def forward(self, ids):
+            if not FlakyOnce.fired:
+                FlakyOnce.fired += 1
+                raise torch.OutOfMemoryError("simulated")
+            return super().forward(ids)
+
+    tr = DPTrainer(model=FlakyOnce(), args=_args(tmp_path / "a", save_steps=0, microbatch_size=8, auto_find_microbatch_size=True),
+                   train_dataset=_data())
+    out = tr.train()
+    assert FlakyOnce.fired == 1 and out["global_step"] == 6 and tr._microbatch == 4
+    FlakyOnce.fired = 0
+    tr = DPTrainer(model=FlakyOnce(), args=_args(tmp_path / "b", save_steps=0, microbatch_size=8), train_dataset=_data())
+    with pytest.raises(torch.OutOfMemoryError):
+        tr.train()

@@ -198,6 +198,8 @@ class BestModelSaveCallback(TrainerCallback):
         if state.best_metric is None or better(metrics[keyname], state.best_metric):
             state.best_metric = float(metrics[keyname])
             control.should_save = True
+            if args.output_dir:            # the training loop writes this checkpoint right after the evaluation
+                state.best_model_checkpoint = os.path.join(args.output_dir, f"checkpoint-{state.global_step}")
 
 
 @dataclasses.dataclass
@@ -518,8 +520,50 @@ class DPTrainer:
                             tolerance=kw["tol"], prefix=prefix)
         return float(res.param)
 
+    # fields that exist for call-compatibility with Hugging Face argument sets and have no effect here
+    _INERT_FIELDS = ("overwrite_output_dir", "eval_accumulation_steps", "log_level_replica", "log_on_each_node",
+                     "save_on_each_node", "restore_callback_states_from_checkpoint", "use_mps_device", "bf16_full_eval",
+                     "local_rank", "eval_do_concat_batches", "include_for_metrics", "average_tokens_across_devices",
+                     "ignore_data_skip", "dataloader_num_workers", "dataloader_persistent_workers",
+                     "dataloader_prefetch_factor", "dataloader_multiprocessing_context", "dataloader_in_order",
+                     "dataloader_drop_last", "remove_unused_columns", "label_names", "disable_tqdm", "trackio_space_id",
+                     "trackio_bucket_id", "trackio_static_space_id", "hub_model_id", "hub_token", "hub_private_repo",
+                     "hub_revision", "torch_compile", "torch_compile_backend", "torch_compile_mode",
+                     "performance_kernels_config", "use_compat_patches")
+
+    def inert_arguments(self) -> dict[str, Any]:
+        """Arguments that were set away from their default but change nothing in this trainer (data loading is
+        index-based inside the DP sampler, there is no hub client, no tracing compiler on the hot path)."""
+        defaults = {f.name: (f.default if f.default is not dataclasses.MISSING else f.default_factory())
+                    for f in dataclasses.fields(type(self.args)) if f.name in self._INERT_FIELDS}
+        return {k: getattr(self.args, k) for k, d in defaults.items()
+                if getattr(self.args, k) != d and (getattr(self.args, k) or d)}       # None and {} both mean unset
+
+    def _apply_runtime_flags(self) -> None:
+        a = self.args
+        if a.log_level not in ("passive", None, ""):
+            import logging
+            level = getattr(logging, str(a.log_level).upper(), None)
+            if isinstance(level, int):
+                logging.getLogger("opaque_b200").setLevel(level)
+        if a.tf32 is not None:
+            torch.backends.cuda.matmul.allow_tf32 = bool(a.tf32)
+            torch.backends.cudnn.allow_tf32 = bool(a.tf32)
+        if a.full_determinism:
+            torch.use_deterministic_algorithms(True, warn_only=True)
+            os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
+        if a.label_smoothing_factor:
+            raise ValueError("label_smoothing_factor is not supported: pass a compute_loss_func that smooths, or use "
+                             "opaque_b200.ops.cross_entropy(label_smoothing=...) in the model's per_example_loss")
+        inert = self.inert_arguments()
+        if inert and self.is_world_process_zero():
+            import warnings
+            warnings.warn("these TrainingArguments are accepted for compatibility and have no effect here: "
+                          + ", ".join(sorted(inert)), stacklevel=3)
+
     def _setup(self, resume: str | None) -> None:
         a = self.args
+        self._apply_runtime_flags()
         torch.manual_seed(a.seed)
         if self.train_dataset is None:
             raise ValueError("training needs a train_dataset")
@@ -805,6 +849,7 @@ class DPTrainer:
         if a.eval_on_start and self.eval_dataset is not None:
             self.evaluate()
         t0 = time.perf_counter()
+        tokens_at_start = self.state.num_input_tokens_seen
         window: list[dict[str, float]] = []
         for batch in self.get_train_dataloader():
             if a.activation_offloading:          # saved activations live in pinned host memory between forward and backward
@@ -822,7 +867,10 @@ class DPTrainer:
             if a.logging_strategy == "steps" and (step % a.logging_steps == 0 or (a.logging_first_step and step == 1)):
                 self.log(self._mean(window))
                 window = []
-            if a.eval_strategy == "steps" and a.eval_steps and step % a.eval_steps == 0 and self.eval_dataset is not None:
+            if a.torch_empty_cache_steps and step % a.torch_empty_cache_steps == 0 and torch.cuda.is_available():
+                torch.cuda.empty_cache()
+            if a.eval_strategy == "steps" and a.eval_steps and step % a.eval_steps == 0 and self.eval_dataset is not None \
+                    and self.state.epoch >= a.eval_delay:
                 self.evaluate()
             if self.control.should_save or (a.save_strategy == "steps" and a.save_steps and step % a.save_steps == 0 and a.output_dir):
                 self._save_checkpoint(step)
@@ -834,11 +882,32 @@ class DPTrainer:
         if window:
             self.log(self._mean(window))
         self.state.epsilon = self.epsilon()
-        out = {"train_runtime": time.perf_counter() - t0, "global_step": self.state.global_step, "epsilon": self.state.epsilon,
+        runtime = time.perf_counter() - t0
+        out = {"train_runtime": runtime, "global_step": self.state.global_step, "epsilon": self.state.epsilon,
                "train_samples_per_second": self.perf.state("train").samples_per_second}
+        if a.include_tokens_per_second:
+            out["train_tokens_per_second"] = (self.state.num_input_tokens_seen - tokens_at_start) / max(runtime, 1e-9)
+        if a.include_num_input_tokens_seen:
+            out["num_input_tokens_seen"] = self.state.num_input_tokens_seen
         self.log(out)
+        if a.load_best_model_at_end:
+            self._load_best_model()
         self._call("on_train_end")
         return out
+
+    def _load_best_model(self) -> None:
+        """``load_best_model_at_end``: put the weights of the best evaluated checkpoint back into the model."""
+        path = self.state.best_model_checkpoint
+        if not path or not os.path.isdir(path):
+            return
+        from safetensors.torch import load_file
+        for name in ("adapter_model.safetensors", FILES["weights"]):
+            f = os.path.join(path, name)
+            if os.path.exists(f):
+                with torch.no_grad():
+                    self.model.load_state_dict(load_file(f), strict=False)
+        if self.engine_kind == "reference":           # later evaluations write the functional copy back into the model
+            self._trainable = {n: p.detach().clone() for n, p in self.model.named_parameters() if p.requires_grad}
 
     @staticmethod
     def _mean(rows: list[dict[str, float]]) -> dict[str, float]:
@@ -896,16 +965,17 @@ class DPTrainer:
             logits = getattr(logits, "logits", logits)
             if self.preprocess_logits_for_metrics is not None:
                 logits = self.preprocess_logits_for_metrics(logits, batch.get("labels"))
-            preds.append(logits.float().cpu())
+            if not self.args.prediction_loss_only:
+                preds.append(logits.float().cpu())
             if "labels" in batch:
                 labels.append(batch["labels"].cpu())
                 losses.append(self.compute_batch_per_example_loss(batch).float().cpu())
         p = torch.cat(preds) if preds and all(x.shape[1:] == preds[0].shape[1:] for x in preds) else preds
         l = torch.cat(labels) if labels and all(x.shape[1:] == labels[0].shape[1:] for x in labels) else labels
         metrics = {f"{metric_key_prefix}_loss": float(torch.cat(losses).mean())} if losses else {}
-        if self.compute_metrics is not None and labels:
+        if self.compute_metrics is not None and labels and not self.args.prediction_loss_only:
             metrics.update({f"{metric_key_prefix}_{k}": v for k, v in self.compute_metrics((p, l)).items()})
-        return PredictionOutput(p, l, metrics)
+        return PredictionOutput(None if self.args.prediction_loss_only else p, l, metrics)
 
     # ---- checkpoints ----------------------------------------------------------------------------------
     def save_model(self, output_dir: str | None = None) -> None:

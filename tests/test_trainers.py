@@ -182,3 +182,28 @@ def test_out_of_memory_steps_the_microbatch_down_only_when_asked(tmp_path):
     tr = DPTrainer(model=FlakyOnce(), args=_args(tmp_path / "b", save_steps=0, microbatch_size=8), train_dataset=_data())
     with pytest.raises(torch.OutOfMemoryError):
         tr.train()
+
+
+def test_compatibility_arguments_are_applied_or_named(tmp_path):
+    """Arguments taken over from Hugging Face either act (best-model reload, throughput fields, evaluation delay,
+    loss-only prediction) or are listed by ``inert_arguments`` and warned about once."""
+    torch.manual_seed(0)
+    data, held_out = _data(), _data(16, seed=9)
+    args = _args(tmp_path, eval_strategy="steps", eval_steps=2, save_steps=0, metric_for_best_model="loss",
+                 greater_is_better=False, load_best_model_at_end=True, include_tokens_per_second=True,
+                 include_num_input_tokens_seen=True, dataloader_num_workers=4, hub_model_id="x/y",
+                 prediction_loss_only=True, tf32=True)
+    tr = DPTrainer(model=TinyLM(), args=args, train_dataset=data, eval_dataset=held_out)
+    assert set(tr.inert_arguments()) == {"dataloader_num_workers", "hub_model_id"}
+    with pytest.warns(UserWarning, match="dataloader_num_workers, hub_model_id"):
+        out = tr.train()
+    assert out["train_tokens_per_second"] > 0 and out["num_input_tokens_seen"] > 0
+    best = tr.state.best_model_checkpoint
+    assert best and os.path.isdir(best) and tr.state.best_metric is not None
+    evals = [r["eval_loss"] for r in tr.state.log_history if "eval_loss" in r]
+    assert math.isclose(min(evals), tr.state.best_metric, rel_tol=1e-9)
+    assert math.isclose(tr.evaluate(held_out)["eval_loss"], tr.state.best_metric, rel_tol=1e-5)   # the best weights are back
+    pred = tr.predict(held_out)
+    assert pred.predictions is None and "test_loss" in pred.metrics
+    with pytest.raises(ValueError):
+        DPTrainer(model=TinyLM(), args=_args(tmp_path / "ls", label_smoothing_factor=0.1), train_dataset=data).train()

@@ -134,7 +134,8 @@ def f_divergence_logits(c, r, *, kind: str = "reverse_kl", alpha: float = 0.5):
 PAIR_HEADS = {"sigmoid": sigmoid_loss, "hinge": hinge_loss, "ipo": ipo_loss, "exo_pair": exo_loss, "nca_pair": nca_loss,
               "robust": robust_loss, "bco_pair": bco_loss, "sppo_hard": sppo_loss, "apo_zero": apo_zero_loss,
               "apo_down": apo_down_loss, "discopop": discopop_loss}
-ALL_LOSS_TYPES = tuple(PAIR_HEADS) + ("sft", "simpo", "orpo", "ld_dpo", "mpo", "wpo", "f_divergence")
+ALL_LOSS_TYPES = tuple(PAIR_HEADS) + ("sft", "chosen_nll", "cpo", "simpo", "orpo", "ld_dpo", "mpo", "wpo", "f_divergence")
+REFERENCE_FREE = frozenset({"sft", "chosen_nll", "cpo", "simpo", "orpo"})      # heads that never read the reference policy
 MPO_MIX = (("sigmoid", 0.8), ("bco_pair", 0.2), ("sft", 1.0))
 
 
@@ -142,8 +143,12 @@ def dpo_loss(loss_type: str | Sequence[str], *, chosen_logratio, rejected_lograt
              label_smoothing: float = 0.0, loss_weights: Sequence[float] | None = None, chosen_nll=None,
              chosen_avg_logp=None, rejected_avg_logp=None, bco_delta=0.0, discopop_tau: float = 0.05,
              simpo_gamma: float = 0.5, orpo_lambda: float = 1.0, f_divergence_type: str = "reverse_kl",
-             f_alpha: float = 0.5, pair_weight=None):
-    """Dispatch one head or a weighted mixture of heads; returns one loss per pair."""
+             f_alpha: float = 0.5, pair_weight=None, chosen_logp=None, rejected_logp=None, cpo_alpha: float = 1.0):
+    """Dispatch one head or a weighted mixture of heads; returns one loss per pair.
+
+    ``cpo`` is reference-free: the sigmoid head on the SUMMED policy log-probabilities (``chosen_logp``,
+    ``rejected_logp``) plus ``cpo_alpha`` times the per-token-mean chosen NLL
+    (parity: packages/opaque-transformers/src/opaque/api/transformers/trl/_dpo_trainer.py:934-941)."""
     types = [loss_type] if isinstance(loss_type, str) else list(loss_type)
     if types == ["mpo"]:
         types, loss_weights = [t for t, _ in MPO_MIX], [w for _, w in MPO_MIX]
@@ -166,8 +171,13 @@ def dpo_loss(loss_type: str | Sequence[str], *, chosen_logratio, rejected_lograt
             term = discopop_loss(c, r, beta=beta, tau=discopop_tau)
         elif t in PAIR_HEADS:
             term = PAIR_HEADS[t](c, r, beta=beta)
-        elif t == "sft":
+        elif t in ("sft", "chosen_nll"):
             term = chosen_nll_loss(chosen_nll)
+        elif t == "cpo":
+            if chosen_logp is None or rejected_logp is None:
+                raise ValueError("cpo needs the policy log-probabilities chosen_logp / rejected_logp")
+            term = sigmoid_loss(chosen_logp, rejected_logp, beta=beta, label_smoothing=label_smoothing) \
+                + cpo_alpha * chosen_nll_loss(chosen_nll)
         elif t == "simpo":
             term = simpo_loss(chosen_avg_logp, rejected_avg_logp, beta=beta, gamma=simpo_gamma, label_smoothing=label_smoothing)
         elif t == "orpo":
@@ -187,7 +197,7 @@ def reward_margins(chosen_logratio, rejected_logratio, beta: float):
             "rewards/accuracies": (cr > rr).float()}
 
 
-__all__ = ["ALL_LOSS_TYPES", "PAIR_HEADS", "apo_down_loss", "apo_zero_loss", "bco_loss", "chosen_nll_loss",
+__all__ = ["ALL_LOSS_TYPES", "PAIR_HEADS", "REFERENCE_FREE", "apo_down_loss", "apo_zero_loss", "bco_loss", "chosen_nll_loss",
            "discopop_loss", "dpo_loss", "exo_loss", "f_divergence_logits", "hinge_loss", "ipo_loss", "ld_dpo_logp",
            "nca_loss", "orpo_loss", "reward_margins", "robust_loss", "sigmoid_loss", "simpo_loss", "sppo_loss",
            "wpo_weight"]

@@ -61,6 +61,8 @@ class SFTTrainer(DPTrainer):
 
     @staticmethod
     def _resolve_completion_only(args: SFTConfig, dataset) -> bool:
+        if args.assistant_only_loss:            # chat data: only assistant turns carry loss (they are the completion mask)
+            return True
         if args.completion_only_loss is not None:
             return bool(args.completion_only_loss)
         return bool(dataset is not None and len(dataset) and "completion_mask" in dataset[0])
@@ -146,7 +148,7 @@ class DPOTrainer(DPTrainer):
             for m in model.modules():
                 if isinstance(m, torch.nn.Dropout):
                     m.p = 0.0
-        reference_free = all(t in ("simpo", "orpo", "sft") for t in ([args.loss_type] if isinstance(args.loss_type, str) else args.loss_type))
+        reference_free = all(t in dpo_losses.REFERENCE_FREE for t in ([args.loss_type] if isinstance(args.loss_type, str) else args.loss_type))
         self.ref_model = None if reference_free else (ref_model if ref_model is not None else copy.deepcopy(model).requires_grad_(False))
         args.dp_engine = "reference"        # the pair loss is not a plain LM loss; it runs on the functional engine
         super().__init__(model=model, args=args, train_dataset=train_dataset, eval_dataset=eval_dataset,
@@ -228,7 +230,8 @@ class DPOTrainer(DPTrainer):
                                    chosen_avg_logp=c_avg, rejected_avg_logp=r_avg, bco_delta=self._bco_delta,
                                    discopop_tau=a.discopop_tau, simpo_gamma=a.simpo_gamma, orpo_lambda=a.orpo_lambda,
                                    f_divergence_type=a.f_divergence_type, f_alpha=a.f_alpha_divergence_coef,
-                                   pair_weight=weight.squeeze(0) if weight is not None else None)
+                                   pair_weight=weight.squeeze(0) if weight is not None else None,
+                                   chosen_logp=c_sum, rejected_logp=r_sum, cpo_alpha=a.cpo_alpha)
 
     def compute_batch_per_example_loss(self, batch):
         n = batch["chosen_input_ids"].shape[0]

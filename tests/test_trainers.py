@@ -207,3 +207,23 @@ def test_compatibility_arguments_are_applied_or_named(tmp_path):
     assert pred.predictions is None and "test_loss" in pred.metrics
     with pytest.raises(ValueError):
         DPTrainer(model=TinyLM(), args=_args(tmp_path / "ls", label_smoothing_factor=0.1), train_dataset=data).train()
+
+
+def test_cpo_head_is_reference_free_and_matches_its_closed_form(tmp_path):
+    from opaque_b200.alignment import dpo
+    c, r = torch.tensor([-3.0, -1.0]), torch.tensor([-2.0, -4.0])          # summed policy log-probabilities
+    nll = torch.tensor([0.7, 0.2])                                        # per-token-mean chosen NLL
+    got = dpo.dpo_loss("cpo", chosen_logratio=c, rejected_logratio=r, beta=0.5, chosen_nll=nll, chosen_logp=c,
+                       rejected_logp=r, cpo_alpha=2.0)
+    want = -torch.nn.functional.logsigmoid(0.5 * (c - r)) + 2.0 * nll
+    assert torch.allclose(got, want, atol=1e-6)
+    assert torch.allclose(dpo.dpo_loss("chosen_nll", chosen_logratio=c, rejected_logratio=r, chosen_nll=nll), nll)
+    g = torch.Generator().manual_seed(0)
+    rows = [{"prompt_input_ids": torch.randint(0, 32, (4,), generator=g).tolist(),
+             "chosen_input_ids": torch.randint(0, 32, (5,), generator=g).tolist(),
+             "rejected_input_ids": torch.randint(0, 32, (3,), generator=g).tolist()} for _ in range(16)]
+    cfg = DPOConfig(output_dir=str(tmp_path), per_device_train_batch_size=4, max_steps=2, privacy_noise_multiplier=1.0,
+                    use_cpu=True, save_steps=0, learning_rate=1e-2, loss_type="cpo", cpo_alpha=0.5)
+    tr = DPOTrainer(model=TinyLM(), args=cfg, train_dataset=rows)
+    assert tr.ref_model is None and "ref_chosen_logps" not in tr.train_dataset[0]      # no reference pass at all
+    assert tr.train()["global_step"] == 2

@@ -35,7 +35,8 @@ from ..accounting.core import native
 from ..pytree import tree_flatten_with_paths, tree_map, tree_unflatten
 from ..random import RngKey, fold_in, generator_from_key
 from ..scheduling import schedule_from_wire, schedule_to_wire
-from ..types import ClippedPytree, NoisedPytree, NoiseState, PerGroup
+from ..types import (ClippedPytree, NoisedPytree, NoiseState, PerGroup, SecondMomentClippingOutput,
+                     SecondMomentNoiseOutput)
 
 # =============================================================================== streaming matrices
 
@@ -558,14 +559,20 @@ def mf_gaussian_noise(grad_template: Any, strategy: MfStrategy, *, n_steps: int,
         raise TypeError(f"key must be RngKey, got {type(key)}")
     if noise_multiplier < 0:
         raise ValueError("noise_multiplier must be >= 0")
+    if min_sep < 1 or (max_participations is not None and max_participations < 1):
+        raise ValueError("min_sep and max_participations must be >= 1")
     if second_moment_strategy is not None:
-        raise NotImplementedError("paired second-moment MF noise is not available in this build")
+        return _paired_mf_gaussian_noise(grad_template, strategy, second_moment_strategy, n_steps=n_steps,
+                                         noise_multiplier=noise_multiplier, key=key, compute_dtype=compute_dtype)
     sm = strategy.streaming_matrix(n_steps)
     row_sq = sm.row_norms_squared(n_steps) if sm.row_norms_squared is not None else np.ones(n_steps)
     inner0 = sm.init_multiply(grad_template.pytree if isinstance(grad_template, ClippedPytree) else grad_template)
 
     def noise_fn(grads: ClippedPytree, st: MFNoiseState):
         with torch.profiler.record_function("opaque::mf_gaussian_noise"):
+            if isinstance(grads, SecondMomentClippingOutput):
+                raise TypeError("mf_gaussian_noise was built without second_moment_strategy and expects ClippedPytree "
+                                "inputs; rebuild it with second_moment_strategy=... for the paired form")
             if isinstance(grads, NoisedPytree) or not isinstance(grads, ClippedPytree):
                 raise TypeError("mf_gaussian_noise expects ClippedPytree inputs")
             if isinstance(grads.max_norm, PerGroup):
@@ -589,6 +596,79 @@ def mf_gaussian_noise(grad_template: Any, strategy: MfStrategy, *, n_steps: int,
     return noise_fn, MFNoiseState(inner0, 0, key, None)
 
 
+@dataclasses.dataclass(frozen=True)
+class SecondMomentMFNoiseState(NoiseState):
+    """Joint state of the paired form: one correlated-noise stream for ``Σg`` and one for ``Σg²``."""
+    _first_state: MFNoiseState
+    _second_state: MFNoiseState
+
+    @property
+    def _step_counter(self) -> int:
+        return self._first_state._step_counter
+
+    @property
+    def _rng_key(self) -> RngKey:
+        return self._first_state._rng_key
+
+
+def _paired_mf_gaussian_noise(grad_template: Any, first: MfStrategy, second: MfStrategy, *, n_steps: int,
+                              noise_multiplier: float, key: RngKey, compute_dtype: torch.dtype):
+    """Two independent correlated-noise streams that share one privacy budget.
+
+    With ``c1`` / ``c2`` the single-participation sensitivities (largest column norms) of the two strategies, the
+    base deviations are ``paired_noise_stddev(max_norm·c1, squared_max_norm·c2, noise_multiplier / c1)``: the joint
+    Mahalanobis budget is ``(c1 / noise_multiplier)²``, i.e. what the single-stream accountant charges for
+    ``(noise_multiplier, first)``, and with a vanishing second stream the first deviation falls back to
+    ``noise_multiplier · max_norm``.  Each stream then passes through its own ``C⁻¹``.
+    Parity: packages/opaque-dpftrl/src/opaque/api/dpftrl/noise/_second_moment.py:56-190 of the reference.
+    """
+    from ..noise_allocation import FIRST_MOMENT_FOLD_TAG, SECOND_MOMENT_FOLD_TAG, paired_noise_stddev
+    template = grad_template.pytree if isinstance(grad_template, ClippedPytree) else grad_template
+    streams = []
+    for strat, tag in ((first, FIRST_MOMENT_FOLD_TAG), (second, SECOND_MOMENT_FOLD_TAG)):
+        sm = strat.streaming_matrix(n_steps)
+        row_sq = sm.row_norms_squared(n_steps) if sm.row_norms_squared is not None else np.ones(n_steps)
+        c = float(strat.sensitivity(n_steps, min_sep=n_steps, max_participations=1))
+        streams.append((sm, row_sq, c, MFNoiseState(sm.init_multiply(template), 0, fold_in(key, tag), None)))
+    (sm1, rows1, c1, st1), (sm2, rows2, c2, st2) = streams
+
+    def one_stream(sm, rows, clipped: ClippedPytree, st: MFNoiseState, sigma: float, what: str):
+        if isinstance(clipped.max_norm, PerGroup):
+            raise TypeError("mf_gaussian_noise supports a scalar max_norm")
+        mn = float(clipped.max_norm)
+        first_mn = st._first_max_norm if st._first_max_norm is not None else mn
+        if not math.isclose(first_mn, mn, rel_tol=1e-9, abs_tol=0.0):
+            raise ValueError(f"{what}: max_norm changed from {first_mn} to {mn}; matrix-factorisation noise needs a constant bound")
+        t = st._step_counter
+        step_key = fold_in(st._rng_key, "mf_gaussian_column", t)
+        z = _iid_normal_like(clipped.pytree, sigma, step_key, compute_dtype) if sigma > 0 else tree_map(
+            lambda g: torch.zeros_like(g, dtype=compute_dtype), clipped.pytree)
+        x, inner = sm.multiply_next(z, st._inner_state)
+        noisy = tree_map(lambda g, n: (g.to(compute_dtype) + n).to(g.dtype), clipped.pytree, x)
+        return (NoisedPytree(noisy, clipped.max_norm, sigma * math.sqrt(float(rows[t]))),
+                MFNoiseState(inner, t + 1, st._rng_key, first_mn))
+
+    def noise_fn(grads: Any, st: SecondMomentMFNoiseState):
+        with torch.profiler.record_function("opaque::mf_gaussian_noise_paired"):
+            if not isinstance(grads, SecondMomentClippingOutput):
+                raise TypeError("mf_gaussian_noise was built with second_moment_strategy and expects "
+                                "SecondMomentClippingOutput inputs: use clipped_grad(..., second_moment=True), or rebuild "
+                                "the noise function without second_moment_strategy")
+            g1, g2 = grads.grads, grads.squared_grads
+            if not isinstance(g1, ClippedPytree) or not isinstance(g2, ClippedPytree):
+                raise TypeError("both streams must be ClippedPytree")
+            if st._step_counter >= n_steps:
+                raise RuntimeError(f"the mechanism was calibrated for {n_steps} steps; step {st._step_counter} is past the horizon")
+            if isinstance(g1.max_norm, PerGroup) or isinstance(g2.max_norm, PerGroup):
+                raise TypeError("mf_gaussian_noise supports a scalar max_norm")
+            s1, s2 = paired_noise_stddev(float(g1.max_norm) * c1, float(g2.max_norm) * c2, noise_multiplier / c1)
+            n1, new1 = one_stream(sm1, rows1, g1, st._first_state, s1, "first stream")
+            n2, new2 = one_stream(sm2, rows2, g2, st._second_state, s2, "squared stream")
+            return SecondMomentNoiseOutput(n1, n2), SecondMomentMFNoiseState(new1, new2)
+
+    return noise_fn, SecondMomentMFNoiseState(st1, st2)
+
+
 def sync_mf_noise_state(state: MFNoiseState) -> MFNoiseState:
     from ..distributed import assert_scalar_equal, assert_string_equal, is_distributed
     if is_distributed():
@@ -600,10 +680,12 @@ def sync_mf_noise_state(state: MFNoiseState) -> MFNoiseState:
 from ..distributed import register_sync_type as _rst  # noqa: E402
 
 _rst(MFNoiseState, sync_mf_noise_state)
+_rst(SecondMomentMFNoiseState, lambda st: SecondMomentMFNoiseState(sync_mf_noise_state(st._first_state),
+                                                                   sync_mf_noise_state(st._second_state)))
 
 __all__ = [
     "BandMfStrategy", "BisrStrategy", "BltStrategy", "BsrStrategy", "IdentityStrategy", "LambdaCgdStrategy",
-    "MFNoiseState", "MfStrategy", "StreamingMatrix", "band_mf_strategy", "bisr_strategy", "blt_coefs",
+    "MFNoiseState", "MfStrategy", "SecondMomentMFNoiseState", "StreamingMatrix", "band_mf_strategy", "bisr_strategy", "blt_coefs",
     "blt_inverse_coef", "blt_inverse_streaming", "blt_strategy", "bsr_strategy", "fir_streaming", "identity_strategy",
     "identity_streaming", "inv_sqrt_coefs", "inverse_coef", "lambda_cgd_strategy", "mf_gaussian_noise",
     "optimize_banded", "optimize_blt", "prefix_sum_streaming", "register_strategy", "sqrt_coefs", "strategy_from_wire",

@@ -148,3 +148,41 @@ def test_b_min_sep_monte_carlo_accountant():
     a |= proc
     restored = from_state_dict(acc.Accountant(), state_dict(a))
     assert math.isclose(restored.epsilon_at(1e-4), a.epsilon_at(1e-4), rel_tol=1e-12)
+
+
+def test_paired_second_moment_mf_noise_shares_one_budget():
+    """Σg and Σg² each get their own correlated-noise stream; the base deviations split one Mahalanobis budget."""
+    import math
+    from opaque_b200.dpftrl.noise import SecondMomentMFNoiseState, mf_gaussian_noise
+    from opaque_b200.types import SecondMomentClippingOutput, SecondMomentNoiseOutput, clipped
+    n, nm = 8, 2.0
+    first, second = band_mf_strategy(bands=4), identity_strategy()
+    tmpl = {"w": torch.zeros(20000)}
+    noise_fn, st = mf_gaussian_noise(tmpl, first, n_steps=n, noise_multiplier=nm, key=key(3), second_moment_strategy=second)
+    assert isinstance(st, SecondMomentMFNoiseState)
+    c1 = first.sensitivity(n, min_sep=n, max_participations=1)
+    c2 = second.sensitivity(n, min_sep=n, max_participations=1)
+    C, C2 = 1.5, 0.4
+    s1 = (nm / c1) * math.sqrt(C * c1 * (C * c1 + C2 * c2))
+    s2 = (nm / c1) * math.sqrt(C2 * c2 * (C * c1 + C2 * c2))
+    assert math.isclose((C * c1 / s1) ** 2 + (C2 * c2 / s2) ** 2, (c1 / nm) ** 2, rel_tol=1e-12)     # the joint budget
+    out, st1 = noise_fn(SecondMomentClippingOutput(clipped(tmpl, C), clipped(tmpl, C2)), st)
+    assert isinstance(out, SecondMomentNoiseOutput) and st1._step_counter == 1
+    # step 0 of C^-1 has a unit row for both strategies here (c_0 = 1): realised = base deviation
+    assert math.isclose(out.noisy_grads.noise_stddev, s1 * math.sqrt(first.streaming_matrix(n).row_norms_squared(n)[0]), rel_tol=1e-9)
+    assert abs(float(out.noisy_grads.pytree["w"].std()) / out.noisy_grads.noise_stddev - 1) < 0.03
+    assert abs(float(out.noisy_squared_grads.pytree["w"].std()) / s2 - 1) < 0.03
+    corr = float(torch.corrcoef(torch.stack([out.noisy_grads.pytree["w"], out.noisy_squared_grads.pytree["w"]]))[0, 1])
+    assert abs(corr) < 0.03                                                                # independent streams
+    # resumable through the registry; wrong input kinds are refused both ways
+    restored = from_state_dict(st, state_dict(st1))
+    a, _ = noise_fn(SecondMomentClippingOutput(clipped(tmpl, C), clipped(tmpl, C2)), st1)
+    b, _ = noise_fn(SecondMomentClippingOutput(clipped(tmpl, C), clipped(tmpl, C2)), restored)
+    assert torch.equal(a.noisy_grads.pytree["w"], b.noisy_grads.pytree["w"])
+    with pytest.raises(TypeError):
+        noise_fn(clipped(tmpl, C), st1)
+    single_fn, single_st = mf_gaussian_noise(tmpl, first, n_steps=n, noise_multiplier=nm, key=key(3))
+    with pytest.raises(TypeError):
+        single_fn(SecondMomentClippingOutput(clipped(tmpl, C), clipped(tmpl, C2)), single_st)
+    with pytest.raises(ValueError):
+        noise_fn(SecondMomentClippingOutput(clipped(tmpl, C * 2), clipped(tmpl, C2)), st1)      # the bound must stay constant

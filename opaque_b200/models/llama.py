@@ -30,6 +30,7 @@ class LlamaConfig:
     num_key_value_heads: int = 8
     rms_norm_eps: float = 1e-5
     rope_theta: float = 500000.0
+    rope_scaling: dict | None = None      # Hugging Face rope_scaling dictionary (linear / dynamic / llama3 / yarn)
     max_position_embeddings: int = 8192
     tie_word_embeddings: bool = False
     head_dim: int | None = None
@@ -96,8 +97,6 @@ class LlamaAttention(nn.Module):
 
     def forward(self, x, cos, sin, pos):
         B, T, _ = x.shape
-        if self.window is not None and T > self.window:
-            raise NotImplementedError(f"sequence length {T} exceeds the sliding window {self.window}: windowed attention is not implemented")
         q, k = self.q_proj(x), self.k_proj(x)
         if self.qk_full:
             q, k = self.q_norm(q), self.k_norm(k)
@@ -107,8 +106,17 @@ class LlamaAttention(nn.Module):
             q, k = self.q_norm(q), self.k_norm(k)
         if self.use_rope:
             q, k = ops.rope_qk(q, k, cos, sin, pos)
-        o = nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
-                                                       is_causal=True, enable_gqa=self.nkv != self.nh, scale=self.scale)
+        if self.window is not None and T > self.window:
+            # sequences longer than the window: a banded causal mask (key j visible from query i when 0 <= i - j < window).
+            # This takes the masked attention path of the library, not the causal flash path; shorter sequences never
+            # come here
+            idx = torch.arange(T, device=x.device)
+            band = (idx[:, None] >= idx[None, :]) & (idx[:, None] - idx[None, :] < self.window)
+            o = nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                                           attn_mask=band, enable_gqa=self.nkv != self.nh, scale=self.scale)
+        else:
+            o = nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                                           is_causal=True, enable_gqa=self.nkv != self.nh, scale=self.scale)
         return self.o_proj(o.transpose(1, 2).reshape(B, T, self.nh * self.hd))
 
 
@@ -174,7 +182,7 @@ class LlamaForCausalLM(nn.Module):
         self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, dtype=dtype, device=device)
         if cfg.tie_word_embeddings:
             self.lm_head.weight = self.model.embed_tokens.weight
-        cos, sin = ops.rope_tables(cfg.hd, cfg.max_position_embeddings, cfg.rope_theta, device=device)
+        cos, sin = ops.rope_tables(cfg.hd, cfg.max_position_embeddings, cfg.rope_theta, device=device, scaling=cfg.rope_scaling)
         self.register_buffer("rope_cos", cos, persistent=False)
         self.register_buffer("rope_sin", sin, persistent=False)
         self.activation_checkpointing = activation_checkpointing

@@ -41,6 +41,9 @@ class MoEConfig:
     norm_topk_prob: bool = False
     rms_norm_eps: float = 1e-6
     rope_theta: float = 1000000.0
+    rope_scaling: dict | None = None
+    dense_layers: tuple = ()                   # indices of layers whose MLP is a plain gated MLP instead of experts
+    dense_intermediate_size: int | None = None
     max_position_embeddings: int = 4096
     # family variants: Qwen-MoE has q/k/v biases, a sigmoid gate on the shared expert and its own shared width
     attention_bias: bool = False
@@ -197,12 +200,17 @@ class SparseMoeBlock(nn.Module):
 
 
 class MoEDecoderLayer(nn.Module):
-    def __init__(self, cfg: MoEConfig, dtype, device):
+    def __init__(self, cfg: MoEConfig, dtype, device, layer_idx: int = 0):
         super().__init__()
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
         self.self_attn = LlamaAttention(cfg.attn_config(), dtype, device)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
-        self.mlp = SparseMoeBlock(cfg, dtype, device)
+        if layer_idx in tuple(cfg.dense_layers):
+            if not cfg.dense_intermediate_size:
+                raise ValueError("dense_layers needs dense_intermediate_size")
+            self.mlp = LlamaMLP(dataclasses.replace(cfg.attn_config(), intermediate_size=cfg.dense_intermediate_size), dtype, device)
+        else:
+            self.mlp = SparseMoeBlock(cfg, dtype, device)
 
     def forward(self, h, cos, sin, pos):
         h = h + self.self_attn(self.input_layernorm(h), cos, sin, pos)
@@ -214,11 +222,11 @@ class MoEForCausalLM(nn.Module):
         super().__init__()
         self.config = cfg
         self.embed_tokens = Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
-        self.layers = nn.ModuleList(MoEDecoderLayer(cfg, dtype, device) for _ in range(cfg.num_hidden_layers))
+        self.layers = nn.ModuleList(MoEDecoderLayer(cfg, dtype, device, i) for i in range(cfg.num_hidden_layers))
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
         self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, dtype=dtype, device=device)
         cos, sin = ops.rope_tables(cfg.head_dim or cfg.hidden_size // cfg.num_attention_heads, cfg.max_position_embeddings, cfg.rope_theta,
-                                   device=device)
+                                   device=device, scaling=cfg.rope_scaling)
         self.register_buffer("rope_cos", cos, persistent=False)
         self.register_buffer("rope_sin", sin, persistent=False)
 

@@ -11,6 +11,7 @@ cross_entropy.py:585-681.
 from __future__ import annotations
 
 import contextlib
+import math
 import ctypes
 
 import torch
@@ -331,11 +332,70 @@ def geglu(gate, up, approximate=False):
 
 # =============================================================================== RoPE
 
-def rope_tables(head_dim: int, max_pos: int, theta: float = 10000.0, device=None):
-    """fp32 ``cos, sin`` tables of shape ``[max_pos, head_dim/2]``."""
-    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+def rope_inverse_frequencies(head_dim: int, theta: float, scaling: dict | None = None, *, max_pos: int | None = None,
+                             device=None) -> tuple[torch.Tensor, float]:
+    """Inverse frequencies ``[head_dim/2]`` (fp32) and the factor that multiplies ``cos`` / ``sin``.
+
+    ``scaling`` follows the Hugging Face ``rope_scaling`` / ``rope_parameters`` dictionaries:
+    ``linear`` (positions divided by ``factor``), ``dynamic`` (NTK: the base grows once ``max_pos`` exceeds the original
+    context), ``llama3`` (long wavelengths divided by ``factor``, a smooth blend between ``low_freq_factor`` and
+    ``high_freq_factor``) and ``yarn`` (interpolation blended with extrapolation over a correction range, with an
+    attention factor).  Anything else is refused.
+    """
+    half = torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim
+    inv = 1.0 / (theta ** half)
+    kind = (scaling or {}).get("rope_type", (scaling or {}).get("type", "default")) or "default"
+    if kind == "default":
+        return inv, 1.0
+    factor = float(scaling.get("factor", 1.0))
+    original = scaling.get("original_max_position_embeddings")
+    if kind == "linear":
+        return inv / factor, 1.0
+    if kind == "dynamic":
+        original = int(original or max_pos or 0)
+        if max_pos and original and max_pos > original:
+            base = theta * ((factor * max_pos / original) - (factor - 1.0)) ** (head_dim / (head_dim - 2))
+            inv = 1.0 / (base ** half)
+        return inv, 1.0
+    if kind == "llama3":
+        low, high = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
+        old = float(original)
+        wavelen = 2.0 * math.pi / inv
+        smooth = ((old / wavelen - low) / (high - low)).clamp(0.0, 1.0)
+        blended = (1.0 - smooth) * inv / factor + smooth * inv
+        out = torch.where(wavelen > old / low, inv / factor, torch.where(wavelen < old / high, inv, blended))
+        return out, 1.0
+    if kind == "yarn":
+        original = float(original or max_pos)
+        beta_fast, beta_slow = float(scaling.get("beta_fast") or 32.0), float(scaling.get("beta_slow") or 1.0)
+        att = scaling.get("attention_factor")
+        ms, ms_all = scaling.get("mscale"), scaling.get("mscale_all_dim")
+
+        def mscale(f, m=1.0):
+            return 1.0 if f <= 1.0 else 0.1 * m * math.log(f) + 1.0
+        if att is None:
+            att = mscale(factor, ms) / mscale(factor, ms_all) if (ms and ms_all) else mscale(factor)
+
+        def correction_dim(rotations):
+            return head_dim * math.log(original / (rotations * 2.0 * math.pi)) / (2.0 * math.log(theta))
+        lo, hi = correction_dim(beta_fast), correction_dim(beta_slow)
+        if scaling.get("truncate", True):
+            lo, hi = math.floor(lo), math.ceil(hi)
+        lo, hi = max(lo, 0), min(hi, head_dim - 1)
+        if lo == hi:
+            hi += 0.001
+        ramp = ((torch.arange(head_dim // 2, dtype=torch.float32, device=device) - lo) / (hi - lo)).clamp(0.0, 1.0)
+        keep = 1.0 - ramp                                   # 1 where the dimension extrapolates (high frequencies)
+        out = (inv / factor) * (1.0 - keep) + inv * keep
+        return out, float(att)
+    raise NotImplementedError(f"rope scaling {kind!r} is not implemented (linear, dynamic, llama3 and yarn are)")
+
+
+def rope_tables(head_dim: int, max_pos: int, theta: float = 10000.0, device=None, scaling: dict | None = None):
+    """fp32 ``cos, sin`` tables of shape ``[max_pos, head_dim/2]`` (``scaling``: see ``rope_inverse_frequencies``)."""
+    inv, att = rope_inverse_frequencies(head_dim, theta, scaling, max_pos=max_pos, device=device)
     ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None, :]
-    return ang.cos().contiguous(), ang.sin().contiguous()
+    return (ang.cos() * att).contiguous(), (ang.sin() * att).contiguous()
 
 
 def rope_qk_ref(q, k, cos, sin, pos=None, sign=1.0):

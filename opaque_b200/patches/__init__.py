@@ -52,12 +52,23 @@ def _cfg_get(cfg: Any, name: str, default=None):
 def _rope_theta(cfg: Any, default: float) -> float:
     rp = _cfg_get(cfg, "rope_parameters") or {}
     if isinstance(rp, dict) and rp.get("rope_theta"):
-        if rp.get("rope_type", "default") not in ("default", None):
-            raise NotImplementedError(f"rope scaling {rp.get('rope_type')!r} is not implemented")
         return float(rp["rope_theta"])
-    if _cfg_get(cfg, "rope_scaling"):
-        raise NotImplementedError("rope scaling is not implemented")
     return float(_cfg_get(cfg, "rope_theta", default))
+
+
+def _rope_scaling(cfg: Any) -> dict | None:
+    """The rope scaling dictionary of a Hugging Face config (``rope_parameters`` in new configs, ``rope_scaling`` in old
+    ones), or ``None`` for plain RoPE; unknown kinds are refused when the tables are built."""
+    for name in ("rope_parameters", "rope_scaling"):
+        rp = _cfg_get(cfg, name)
+        if isinstance(rp, dict):
+            kind = rp.get("rope_type", rp.get("type", "default")) or "default"
+            if kind != "default":
+                out = {k: v for k, v in rp.items() if k != "rope_theta"}
+                out["rope_type"] = kind
+                out.setdefault("original_max_position_embeddings", _cfg_get(cfg, "max_position_embeddings"))
+                return out
+    return None
 
 
 def _build_llama(cfg: Any, opt: dict) -> torch.nn.Module:
@@ -92,6 +103,7 @@ def _build_llama(cfg: Any, opt: dict) -> torch.nn.Module:
                     num_attention_heads=_cfg_get(cfg, "num_attention_heads"),
                     num_key_value_heads=_cfg_get(cfg, "num_key_value_heads") or _cfg_get(cfg, "num_attention_heads"),
                     rms_norm_eps=_cfg_get(cfg, "rms_norm_eps", 1e-6), rope_theta=_rope_theta(cfg, 10000.0),
+                    rope_scaling=_rope_scaling(cfg),
                     max_position_embeddings=_cfg_get(cfg, "max_position_embeddings", 8192),
                     tie_word_embeddings=bool(_cfg_get(cfg, "tie_word_embeddings", False)), head_dim=_cfg_get(cfg, "head_dim"),
                     sliding_window=window, **extra)
@@ -108,8 +120,10 @@ def _build_gpt2(cfg: Any, opt: dict) -> torch.nn.Module:
 def _build_moe(cfg: Any, opt: dict) -> torch.nn.Module:
     mtype = _cfg_get(cfg, "model_type")
     shared = _cfg_get(cfg, "shared_expert_intermediate_size", 0) if mtype == "qwen2_moe" else 0
-    if mtype in ("qwen2_moe", "qwen3_moe") and (_cfg_get(cfg, "mlp_only_layers") or _cfg_get(cfg, "decoder_sparse_step", 1) != 1):
-        raise NotImplementedError("dense layers interleaved with MoE layers are not implemented")
+    dense: tuple = ()
+    if mtype in ("qwen2_moe", "qwen3_moe"):        # a layer is sparse when it is not listed as MLP-only and falls on the sparse step
+        only, step = set(_cfg_get(cfg, "mlp_only_layers") or ()), int(_cfg_get(cfg, "decoder_sparse_step", 1) or 1)
+        dense = tuple(i for i in range(_cfg_get(cfg, "num_hidden_layers")) if i in only or (i + 1) % step != 0)
     c = MoEConfig(vocab_size=_cfg_get(cfg, "vocab_size"), hidden_size=_cfg_get(cfg, "hidden_size"),
                   num_hidden_layers=_cfg_get(cfg, "num_hidden_layers"), num_attention_heads=_cfg_get(cfg, "num_attention_heads"),
                   num_key_value_heads=_cfg_get(cfg, "num_key_value_heads") or _cfg_get(cfg, "num_attention_heads"),
@@ -120,6 +134,8 @@ def _build_moe(cfg: Any, opt: dict) -> torch.nn.Module:
                   num_experts_per_tok=_cfg_get(cfg, "num_experts_per_tok", 2),
                   norm_topk_prob=bool(_cfg_get(cfg, "norm_topk_prob", mtype == "mixtral")) or mtype == "mixtral",
                   rms_norm_eps=_cfg_get(cfg, "rms_norm_eps", 1e-6), rope_theta=_rope_theta(cfg, 1e6),
+                  rope_scaling=_rope_scaling(cfg), dense_layers=dense,
+                  dense_intermediate_size=_cfg_get(cfg, "intermediate_size") if dense else None,
                   max_position_embeddings=_cfg_get(cfg, "max_position_embeddings", 4096))
     return MoEForCausalLM(c, dtype=opt.get("dtype", torch.bfloat16), device=opt.get("device"))
 

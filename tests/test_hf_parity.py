@@ -14,7 +14,16 @@ def _cases():
     T = transformers
     yield "llama", T.LlamaConfig(**COMMON, tie_word_embeddings=False), T.LlamaForCausalLM
     yield "llama-tied", T.LlamaConfig(**COMMON, tie_word_embeddings=True), T.LlamaForCausalLM
+    yield "llama-rope-llama3", T.LlamaConfig(**COMMON, rope_parameters={
+        "rope_type": "llama3", "rope_theta": 10000.0, "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+        "original_max_position_embeddings": 32}), T.LlamaForCausalLM
+    yield "llama-rope-linear", T.LlamaConfig(**COMMON, rope_parameters={"rope_type": "linear", "rope_theta": 10000.0, "factor": 4.0}), T.LlamaForCausalLM
+    yield "llama-rope-yarn", T.LlamaConfig(**COMMON, rope_parameters={
+        "rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0, "original_max_position_embeddings": 32}), T.LlamaForCausalLM
+    yield "llama-rope-dynamic", T.LlamaConfig(**{**COMMON, "max_position_embeddings": 128}, rope_parameters={
+        "rope_type": "dynamic", "rope_theta": 10000.0, "factor": 2.0}), T.LlamaForCausalLM
     yield "mistral", T.MistralConfig(**COMMON, sliding_window=4096), T.MistralForCausalLM
+    yield "mistral-window-shorter-than-sequence", T.MistralConfig(**COMMON, sliding_window=8), T.MistralForCausalLM
     yield "qwen2", T.Qwen2Config(**COMMON), T.Qwen2ForCausalLM
     yield "qwen3", T.Qwen3Config(**COMMON, head_dim=16), T.Qwen3ForCausalLM
     yield "gemma", T.GemmaConfig(**COMMON, head_dim=16), T.GemmaForCausalLM
@@ -24,6 +33,9 @@ def _cases():
     yield "smollm3", T.SmolLM3Config(**COMMON, no_rope_layers=[1, 0], pad_token_id=0), T.SmolLM3ForCausalLM
     yield "qwen3_moe", T.Qwen3MoeConfig(**COMMON, moe_intermediate_size=32, num_experts=6, num_experts_per_tok=2, head_dim=16,
                                         norm_topk_prob=True), T.Qwen3MoeForCausalLM
+    yield "qwen3_moe-dense-interleaved", T.Qwen3MoeConfig(**{**COMMON, "num_hidden_layers": 4}, moe_intermediate_size=32, num_experts=6,
+                                                          num_experts_per_tok=2, head_dim=16, norm_topk_prob=True,
+                                                          mlp_only_layers=[0], decoder_sparse_step=2), T.Qwen3MoeForCausalLM
     yield "gpt2", T.GPT2Config(vocab_size=320, n_positions=128, n_embd=64, n_layer=2, n_head=4), T.GPT2LMHeadModel
     yield "mixtral", T.MixtralConfig(**COMMON, num_local_experts=6, num_experts_per_tok=2), T.MixtralForCausalLM
     yield "qwen2_moe", T.Qwen2MoeConfig(**COMMON, moe_intermediate_size=32, shared_expert_intermediate_size=48, num_experts=6,

@@ -134,7 +134,7 @@ class _LinearCrossEntropy(Function):
     """
 
     @staticmethod
-    def forward(ctx, hidden, weight, labels, row_weight, chunk, ignore_index):
+    def forward(ctx, hidden, weight, labels, row_weight, chunk, ignore_index, softcap=0.0):
         R, d = hidden.shape
         V = weight.shape[0]
         out = torch.zeros(R, dtype=torch.float32, device=hidden.device)
@@ -145,9 +145,9 @@ class _LinearCrossEntropy(Function):
         if trainable:
             logits = hidden @ weight.t()
             if use_kernel:
-                nll = cross_entropy_fused_(logits, labels, row_weight, ignore_index=ignore_index)
+                nll = cross_entropy_fused_(logits, labels, row_weight, ignore_index=ignore_index, logit_softcapping=softcap)
             else:
-                nll, logits = _ce_grad_ref(logits, labels, row_weight, ignore_index)
+                nll, logits = _ce_grad_ref(logits, labels, row_weight, ignore_index, softcap)
             out = nll * row_weight
             dh = logits @ weight
             ctx.capture_args = (weight, hidden, logits)
@@ -164,9 +164,9 @@ class _LinearCrossEntropy(Function):
                 logits = h @ weight.t()
                 lab, rw = labels.index_select(0, rows), row_weight.index_select(0, rows)
                 if use_kernel:
-                    nll = cross_entropy_fused_(logits, lab, rw, ignore_index=ignore_index)
+                    nll = cross_entropy_fused_(logits, lab, rw, ignore_index=ignore_index, logit_softcapping=softcap)
                 else:
-                    nll, logits = _ce_grad_ref(logits, lab, rw, ignore_index)
+                    nll, logits = _ce_grad_ref(logits, lab, rw, ignore_index, softcap)
                 out.index_copy_(0, rows, nll * rw)
                 dh.index_copy_(0, rows, (logits @ weight).to(dh.dtype))
             ctx.capture_args = None
@@ -181,24 +181,25 @@ class _LinearCrossEntropy(Function):
             cap = fused.current_capture()
             cap.add_linear(weight, hidden if hidden.is_contiguous() else hidden.contiguous(), dlogits)
             ctx.capture_args = None
-        return dh * g.to(dh.dtype)[:, None], None, None, None, None, None
+        return dh * g.to(dh.dtype)[:, None], None, None, None, None, None, None
 
 
-def _ce_grad_ref(logits, labels, row_weight, ignore_index):
+def _ce_grad_ref(logits, labels, row_weight, ignore_index, softcap=0.0):
     z = logits.float().detach().requires_grad_(True)
     with torch.enable_grad():
-        nll = cross_entropy_ref(z, labels, ignore_index=ignore_index)
+        nll = cross_entropy_ref(z, labels, ignore_index=ignore_index, logit_softcapping=softcap)
         (nll * row_weight).sum().backward()
     return nll.detach(), z.grad.to(logits.dtype)
 
 
 def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, row_weight: torch.Tensor,
-                         *, chunk: int = 8192, ignore_index: int = -100) -> torch.Tensor:
-    """``row_weight[r] · nll(hidden[r] Wᵀ, labels[r])`` for every row, never keeping full logits when ``W`` is frozen."""
+                         *, chunk: int = 8192, ignore_index: int = -100, softcap: float = 0.0) -> torch.Tensor:
+    """``row_weight[r] · nll(hidden[r] Wᵀ, labels[r])`` for every row, never keeping full logits when ``W`` is frozen;
+    ``softcap`` > 0 applies ``softcap · tanh(logits / softcap)`` before the softmax (Gemma-2 final logit capping)."""
     if weight.requires_grad and fused.current_capture() is None and torch.is_grad_enabled():
         # plain autograd (reference engine, non-private training): the head's gradient flows normally
-        return ops.cross_entropy(hidden @ weight.t(), labels, ignore_index=ignore_index) * row_weight
-    return _LinearCrossEntropy.apply(hidden, weight, labels, row_weight, chunk, ignore_index)
+        return ops.cross_entropy(hidden @ weight.t(), labels, ignore_index=ignore_index, logit_softcapping=softcap) * row_weight
+    return _LinearCrossEntropy.apply(hidden, weight, labels, row_weight, chunk, ignore_index, softcap)
 
 
 def per_example_token_weights(labels: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:

@@ -53,6 +53,13 @@ class LlamaConfig:
     # OLMo-2: norms AFTER the sub-layers (h + norm(f(h))) and q/k norms over the whole projection
     post_norm: bool = False
     qk_norm_full: bool = False
+    # Gemma-2/3, OLMo-3, EXAONE-4: per-layer attention windows (None = full attention), norms on both sides of each
+    # sub-layer, tanh capping of attention scores and of the final logits, a second rotary base for windowed layers
+    layer_windows: tuple | None = None
+    sandwich_norm: bool = False
+    attn_logit_softcap: float | None = None
+    final_logit_softcap: float | None = None
+    local_rope_theta: float | None = None
 
     @property
     def hd(self) -> int:
@@ -84,7 +91,9 @@ class LlamaAttention(nn.Module):
         self.k_proj = Linear(d, self.nkv * hd, bias=cfg.attention_bias, dtype=dtype, device=device)
         self.v_proj = Linear(d, self.nkv * hd, bias=cfg.attention_bias, dtype=dtype, device=device)
         self.o_proj = Linear(self.nh * hd, d, bias=cfg.attention_out_bias, dtype=dtype, device=device)
-        self.window = cfg.sliding_window
+        self.window = cfg.layer_windows[layer_idx] if cfg.layer_windows is not None else cfg.sliding_window
+        self.softcap = cfg.attn_logit_softcap
+        self.local_rope = cfg.local_rope_theta is not None and self.window is not None
         self.qk_full = cfg.qk_norm_full
         if cfg.qk_norm_full:
             self.q_norm = RMSNorm(self.nh * hd, cfg.rms_norm_eps, dtype=dtype, device=device)
@@ -105,8 +114,29 @@ class LlamaAttention(nn.Module):
         if self.q_norm is not None and not self.qk_full:
             q, k = self.q_norm(q), self.k_norm(k)
         if self.use_rope:
-            q, k = ops.rope_qk(q, k, cos, sin, pos)
-        if self.window is not None and T > self.window:
+            if self.local_rope:                       # windowed layers rotate with their own base (tables 2 and 3)
+                q, k = ops.rope_qk(q, k, cos[1], sin[1], pos)
+            elif isinstance(cos, (tuple, list)):
+                q, k = ops.rope_qk(q, k, cos[0], sin[0], pos)
+            else:
+                q, k = ops.rope_qk(q, k, cos, sin, pos)
+        if self.softcap:
+            # capped attention scores: no library attention kernel applies tanh between QK^T and the softmax, so the
+            # scores are formed explicitly ([B, heads, T, T] in fp32) — correct for every length, meant for short ones
+            scale = self.scale if self.scale is not None else self.hd ** -0.5
+            qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+            if self.nkv != self.nh:
+                kh = kh.repeat_interleave(self.nh // self.nkv, dim=1)
+                vh = vh.repeat_interleave(self.nh // self.nkv, dim=1)
+            sc = torch.matmul(qh, kh.transpose(-1, -2)).float() * scale
+            sc = self.softcap * torch.tanh(sc / self.softcap)
+            idx = torch.arange(T, device=x.device)
+            keep = idx[:, None] >= idx[None, :]
+            if self.window is not None:
+                keep = keep & (idx[:, None] - idx[None, :] < self.window)
+            sc = sc.masked_fill(~keep, float("-inf"))
+            o = torch.matmul(torch.softmax(sc, dim=-1).to(vh.dtype), vh)
+        elif self.window is not None and T > self.window:
             # sequences longer than the window: a banded causal mask (key j visible from query i when 0 <= i - j < window).
             # This takes the masked attention path of the library, not the causal flash path; shorter sequences never
             # come here
@@ -144,7 +174,12 @@ class LlamaDecoderLayer(nn.Module):
         self.res = cfg.residual_multiplier
         nk = dict(offset=cfg.norm_offset, casting_mode=cfg.norm_casting, dtype=dtype, device=device)
         self.post_norm = cfg.post_norm
-        if cfg.post_norm:
+        self.sandwich = cfg.sandwich_norm
+        if cfg.sandwich_norm:
+            self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
+            self.pre_feedforward_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
+            self.post_feedforward_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
+        elif cfg.post_norm:
             self.post_feedforward_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
         else:
             self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
@@ -153,6 +188,9 @@ class LlamaDecoderLayer(nn.Module):
         self.mlp = LlamaMLP(cfg, dtype, device)
 
     def forward(self, h, cos, sin, pos):
+        if self.sandwich:
+            h = h + self.post_attention_layernorm(self.self_attn(self.input_layernorm(h), cos, sin, pos))
+            return h + self.post_feedforward_layernorm(self.mlp(self.pre_feedforward_layernorm(h)))
         if self.post_norm:
             h = h + self.post_attention_layernorm(self.self_attn(h, cos, sin, pos))
             return h + self.post_feedforward_layernorm(self.mlp(h))
@@ -185,6 +223,10 @@ class LlamaForCausalLM(nn.Module):
         cos, sin = ops.rope_tables(cfg.hd, cfg.max_position_embeddings, cfg.rope_theta, device=device, scaling=cfg.rope_scaling)
         self.register_buffer("rope_cos", cos, persistent=False)
         self.register_buffer("rope_sin", sin, persistent=False)
+        if cfg.local_rope_theta is not None:
+            lcos, lsin = ops.rope_tables(cfg.hd, cfg.max_position_embeddings, cfg.local_rope_theta, device=device)
+            self.register_buffer("rope_cos_local", lcos, persistent=False)
+            self.register_buffer("rope_sin_local", lsin, persistent=False)
         self.activation_checkpointing = activation_checkpointing
         self.ce_chunk = 8192
         # the multiplier is rounded to the parameter dtype once (as Gemma / Granite do), and stays a host scalar
@@ -204,24 +246,29 @@ class LlamaForCausalLM(nn.Module):
         h = self.model.embed_tokens(input_ids)
         if self._emb_scale != 1.0:
             h = h * self._emb_scale
+        cos, sin = self.rope_cos, self.rope_sin
+        if self.config.local_rope_theta is not None:           # (global, local) table pairs; windowed layers take the second
+            cos, sin = (self.rope_cos, self.rope_cos_local), (self.rope_sin, self.rope_sin_local)
         for layer in self.model.layers:
             if self.activation_checkpointing and torch.is_grad_enabled():
-                h = torch.utils.checkpoint.checkpoint(layer, h, self.rope_cos, self.rope_sin, position_ids,
-                                                      use_reentrant=False)
+                h = torch.utils.checkpoint.checkpoint(layer, h, cos, sin, position_ids, use_reentrant=False)
             else:
-                h = layer(h, self.rope_cos, self.rope_sin, position_ids)
+                h = layer(h, cos, sin, position_ids)
         h = self.model.norm(h)
         return h if self.config.logits_scaling == 1.0 else h / self.config.logits_scaling     # logits = (h / s) Wᵀ
 
     def forward(self, input_ids, position_ids=None):
-        return self.lm_head(self.hidden_states(input_ids, position_ids))
+        logits = self.lm_head(self.hidden_states(input_ids, position_ids))
+        cap = self.config.final_logit_softcap
+        return logits if not cap else cap * torch.tanh(logits / cap)
 
     def per_example_loss(self, input_ids: torch.Tensor, labels: torch.Tensor, position_ids=None) -> torch.Tensor:
         """Mean NLL over each example's scored tokens; ``labels`` are already aligned (−100 = not scored)."""
         B, T = input_ids.shape
         h = self.hidden_states(input_ids, position_ids).reshape(B * T, -1)
         w = per_example_token_weights(labels).reshape(-1)
-        rows = linear_cross_entropy(h, self.lm_head.weight, labels.reshape(-1), w, chunk=self.ce_chunk)
+        rows = linear_cross_entropy(h, self.lm_head.weight, labels.reshape(-1), w, chunk=self.ce_chunk,
+                                    softcap=float(self.config.final_logit_softcap or 0.0))
         return rows.view(B, T).sum(1)
 
 

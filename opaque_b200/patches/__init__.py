@@ -25,14 +25,13 @@ _RUNTIME = {"patched": False}
 
 # model_type -> family builder.  Only families whose block structure these modules reproduce exactly are registered;
 # the others are listed with the reason, so a conversion can never silently drop a feature of the architecture.
-LLAMA_LIKE = ("llama", "mistral", "ministral", "mellum", "qwen2", "qwen3", "gemma", "phi3", "granite", "smollm3", "olmo2")
+LLAMA_LIKE = ("llama", "mistral", "ministral", "mellum", "qwen2", "qwen3", "gemma", "gemma2", "gemma3_text", "phi3", "granite",
+              "smollm3", "olmo2", "olmo3", "exaone4")
 MOE_LIKE = ("mixtral", "qwen2_moe", "qwen3_moe")
 UNSUPPORTED = {
-    "gemma2": "post-attention / post-feed-forward norms, attention and final logit soft-capping, alternating local attention",
-    "gemma3": "as gemma2 plus per-layer rope bases and q/k norms",
+    "gemma3": "the multimodal wrapper; convert its text model (model_type gemma3_text)",
     "cohere": "LayerNorm, parallel attention + MLP block, logit scale", "cohere2": "as cohere plus sliding-window layers",
-    "olmo3": "olmo2 blocks plus sliding-window layers",
-    "glm4": "extra post-sub-layer norms and partial rotary embedding", "exaone4": "hybrid local/global attention with post-norms",
+    "glm4": "extra post-sub-layer norms and partial rotary embedding",
     "gpt_oss": "attention sinks, clamped SwiGLU with biases, alternating sliding windows",
     "deepseek_v4": "multi-head latent attention", "hunyuan_v1_moe": "q/k norms and a mixed shared-expert layout",
     "qwen3_next": "gated delta-net layers", "qwen3_5_moe": "gated delta-net layers",
@@ -54,6 +53,17 @@ def _rope_theta(cfg: Any, default: float) -> float:
     if isinstance(rp, dict) and rp.get("rope_theta"):
         return float(rp["rope_theta"])
     return float(_cfg_get(cfg, "rope_theta", default))
+
+
+def _layer_windows(cfg: Any) -> tuple | None:
+    """Per-layer attention window from ``layer_types`` (``sliding_attention`` layers get ``sliding_window``)."""
+    types, window = _cfg_get(cfg, "layer_types"), _cfg_get(cfg, "sliding_window")
+    if not types or window is None:
+        return None
+    bad = sorted(set(types) - {"sliding_attention", "full_attention"})
+    if bad:
+        raise NotImplementedError(f"layer types {bad} are not implemented")
+    return tuple(int(window) if t == "sliding_attention" else None for t in types)
 
 
 def _rope_scaling(cfg: Any) -> dict | None:
@@ -89,6 +99,33 @@ def _build_llama(cfg: Any, opt: dict) -> torch.nn.Module:
     elif mtype == "smollm3":
         extra.update(attention_bias=bool(_cfg_get(cfg, "attention_bias", False)), attention_out_bias=bool(_cfg_get(cfg, "attention_bias", False)),
                      mlp_bias=bool(_cfg_get(cfg, "mlp_bias", False)), no_rope_layers=tuple(int(x) for x in _cfg_get(cfg, "no_rope_layers")))
+    elif mtype in ("gemma2", "gemma3_text"):
+        extra.update(hidden_act=_cfg_get(cfg, "hidden_activation") or _cfg_get(cfg, "hidden_act", "gelu_pytorch_tanh"), norm_offset=1.0,
+                     norm_casting="gemma", embedding_scale=float(_cfg_get(cfg, "hidden_size")) ** 0.5, sandwich_norm=True,
+                     attention_multiplier=float(_cfg_get(cfg, "query_pre_attn_scalar", 256)) ** -0.5,
+                     attention_bias=bool(_cfg_get(cfg, "attention_bias", False)), attention_out_bias=bool(_cfg_get(cfg, "attention_bias", False)),
+                     attn_logit_softcap=_cfg_get(cfg, "attn_logit_softcapping"), final_logit_softcap=_cfg_get(cfg, "final_logit_softcapping"),
+                     layer_windows=_layer_windows(cfg))
+        if _cfg_get(cfg, "use_bidirectional_attention"):
+            raise NotImplementedError("bidirectional attention is not implemented")
+        if mtype == "gemma3_text":
+            rp = _cfg_get(cfg, "rope_parameters") or {}
+            local, full = rp.get("sliding_attention") or {}, rp.get("full_attention") or {}
+            if (local.get("rope_type") or "default") != "default":
+                raise NotImplementedError("rope scaling on the windowed layers is not implemented")
+            extra.update(qk_norm=True, local_rope_theta=float(local.get("rope_theta") or _cfg_get(cfg, "rope_local_base_freq", 10000.0)))
+            opt = {**opt, "_rope": (float(full.get("rope_theta") or 1e6),
+                                    None if (full.get("rope_type") or "default") == "default" else {k: v for k, v in full.items() if k != "rope_theta"})}
+    elif mtype == "olmo3":
+        extra.update(attention_bias=bool(_cfg_get(cfg, "attention_bias", False)), attention_out_bias=bool(_cfg_get(cfg, "attention_bias", False)),
+                     post_norm=True, qk_norm_full=True, layer_windows=_layer_windows(cfg))
+        if _rope_scaling(cfg) is not None:
+            raise NotImplementedError("OLMo-3 applies rope scaling to its full-attention layers only; that split is not implemented")
+    elif mtype == "exaone4":
+        windows = _layer_windows(cfg)
+        extra.update(post_norm=True, qk_norm=True, layer_windows=windows)
+        if _cfg_get(cfg, "sliding_window") is not None and windows is not None:      # hybrid: global layers carry no rotary embedding
+            extra.update(no_rope_layers=tuple(1 if w is not None else 0 for w in windows))
     elif mtype == "gemma":
         extra.update(hidden_act=_cfg_get(cfg, "hidden_activation") or _cfg_get(cfg, "hidden_act", "gelu_pytorch_tanh"), norm_offset=1.0,
                      norm_casting="gemma", embedding_scale=float(_cfg_get(cfg, "hidden_size")) ** 0.5)
@@ -98,12 +135,12 @@ def _build_llama(cfg: Any, opt: dict) -> torch.nn.Module:
     if "hidden_act" not in extra:
         extra["hidden_act"] = _cfg_get(cfg, "hidden_act", "silu")
     window = _cfg_get(cfg, "sliding_window") if _cfg_get(cfg, "use_sliding_window", mtype in ("mistral", "ministral")) else None
+    theta, scaling = opt.get("_rope") or (_rope_theta(cfg, 10000.0), _rope_scaling(cfg))
     c = LlamaConfig(vocab_size=_cfg_get(cfg, "vocab_size"), hidden_size=_cfg_get(cfg, "hidden_size"),
                     intermediate_size=_cfg_get(cfg, "intermediate_size"), num_hidden_layers=_cfg_get(cfg, "num_hidden_layers"),
                     num_attention_heads=_cfg_get(cfg, "num_attention_heads"),
                     num_key_value_heads=_cfg_get(cfg, "num_key_value_heads") or _cfg_get(cfg, "num_attention_heads"),
-                    rms_norm_eps=_cfg_get(cfg, "rms_norm_eps", 1e-6), rope_theta=_rope_theta(cfg, 10000.0),
-                    rope_scaling=_rope_scaling(cfg),
+                    rms_norm_eps=_cfg_get(cfg, "rms_norm_eps", 1e-6), rope_theta=theta, rope_scaling=scaling,
                     max_position_embeddings=_cfg_get(cfg, "max_position_embeddings", 8192),
                     tie_word_embeddings=bool(_cfg_get(cfg, "tie_word_embeddings", False)), head_dim=_cfg_get(cfg, "head_dim"),
                     sliding_window=window, **extra)

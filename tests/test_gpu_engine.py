@@ -76,9 +76,15 @@ def test_llama_full_parameter_untied_and_tied():
 
 @pytest.mark.parametrize("variant", [dict(attention_bias=True), dict(qk_norm=True, head_dim=32),
                                      dict(hidden_act="gelu_pytorch_tanh", norm_offset=1.0, norm_casting="gemma", embedding_scale=128 ** 0.5),
-                                     dict(post_norm=True, qk_norm_full=True), dict(residual_multiplier=0.5, attention_multiplier=0.2, logits_scaling=2.0)])
+                                     dict(post_norm=True, qk_norm_full=True), dict(residual_multiplier=0.5, attention_multiplier=0.2, logits_scaling=2.0),
+                                     dict(sandwich_norm=True, attn_logit_softcap=50.0, final_logit_softcap=30.0, layer_windows=(64, None),
+                                          hidden_act="gelu_pytorch_tanh", norm_offset=1.0, norm_casting="gemma"),
+                                     dict(post_norm=True, qk_norm=True, head_dim=32, layer_windows=(64, None), no_rope_layers=(1, 0)),
+                                     dict(sandwich_norm=True, qk_norm=True, head_dim=32, layer_windows=(64, None), local_rope_theta=10000.0,
+                                          rope_scaling={"rope_type": "linear", "factor": 8.0})])
 def test_llama_family_variants_full_parameter(variant):
-    """Qwen2 biases, Qwen3 q/k norms, Gemma GeGLU / (1+w) norms / scaled embeddings, OLMo-2 post-norm, Granite multipliers."""
+    """Qwen2 biases, Qwen3 q/k norms, Gemma GeGLU / (1+w) norms / scaled embeddings, OLMo-2 post-norm, Granite multipliers,
+    Gemma-2 capping and sandwich norms with a windowed layer, EXAONE-4 hybrid layers, Gemma-3 local rotary base."""
     from opaque_b200.models import LlamaConfig, LlamaForCausalLM
     dev = torch.device("cuda", 0)
     torch.manual_seed(7)

@@ -27,6 +27,12 @@ def _cases():
     yield "qwen2", T.Qwen2Config(**COMMON), T.Qwen2ForCausalLM
     yield "qwen3", T.Qwen3Config(**COMMON, head_dim=16), T.Qwen3ForCausalLM
     yield "gemma", T.GemmaConfig(**COMMON, head_dim=16), T.GemmaForCausalLM
+    four = {**COMMON, "num_hidden_layers": 4}
+    yield "gemma2", T.Gemma2Config(**four, head_dim=16, sliding_window=8, query_pre_attn_scalar=16), T.Gemma2ForCausalLM
+    yield "gemma3_text", T.Gemma3TextConfig(**four, head_dim=16, sliding_window=8, query_pre_attn_scalar=16,
+                                            layer_types=["sliding_attention", "sliding_attention", "full_attention", "sliding_attention"]), T.Gemma3ForCausalLM
+    yield "olmo3", T.Olmo3Config(**four, sliding_window=8, pad_token_id=0), T.Olmo3ForCausalLM
+    yield "exaone4", T.Exaone4Config(**four, sliding_window=8, pad_token_id=0), T.Exaone4ForCausalLM
     yield "phi3", T.Phi3Config(**COMMON, pad_token_id=0), T.Phi3ForCausalLM
     yield "granite", T.GraniteConfig(**COMMON, embedding_multiplier=6.0, attention_multiplier=0.11, residual_multiplier=0.4, logits_scaling=3.0), T.GraniteForCausalLM
     yield "olmo2", T.Olmo2Config(**COMMON, pad_token_id=0), T.Olmo2ForCausalLM
@@ -62,8 +68,8 @@ def test_converted_model_matches_hf_logits(name, cfg, cls):
 
 
 def test_unsupported_families_are_refused_with_a_reason():
-    with pytest.raises(NotImplementedError, match="soft-capping"):
-        patches.apply_model_patches(transformers.Gemma2Config(**COMMON, head_dim=16))
+    with pytest.raises(NotImplementedError, match="LayerNorm"):
+        patches.apply_model_patches(transformers.CohereConfig(**COMMON))
     with pytest.raises(ValueError, match="no registered family"):
         patches.apply_model_patches({"model_type": "not_a_model"})
 

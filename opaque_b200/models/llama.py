@@ -60,6 +60,9 @@ class LlamaConfig:
     attn_logit_softcap: float | None = None
     final_logit_softcap: float | None = None
     local_rope_theta: float | None = None
+    # GLM-4 / Phi-4-mini: only the first head_dim * factor dimensions rotate.  The kernels rotate pairs (i, i + head_dim/2),
+    # so a converted checkpoint has its q / k rows permuted accordingly (patches.rope_row_permutation)
+    partial_rotary_factor: float = 1.0
 
     @property
     def hd(self) -> int:
@@ -220,11 +223,13 @@ class LlamaForCausalLM(nn.Module):
         self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, dtype=dtype, device=device)
         if cfg.tie_word_embeddings:
             self.lm_head.weight = self.model.embed_tokens.weight
-        cos, sin = ops.rope_tables(cfg.hd, cfg.max_position_embeddings, cfg.rope_theta, device=device, scaling=cfg.rope_scaling)
+        cos, sin = ops.rope_tables(cfg.hd, cfg.max_position_embeddings, cfg.rope_theta, device=device, scaling=cfg.rope_scaling,
+                                   rotary_dim=int(cfg.hd * cfg.partial_rotary_factor))
         self.register_buffer("rope_cos", cos, persistent=False)
         self.register_buffer("rope_sin", sin, persistent=False)
         if cfg.local_rope_theta is not None:
-            lcos, lsin = ops.rope_tables(cfg.hd, cfg.max_position_embeddings, cfg.local_rope_theta, device=device)
+            lcos, lsin = ops.rope_tables(cfg.hd, cfg.max_position_embeddings, cfg.local_rope_theta, device=device,
+                                         rotary_dim=int(cfg.hd * cfg.partial_rotary_factor))
             self.register_buffer("rope_cos_local", lcos, persistent=False)
             self.register_buffer("rope_sin_local", lsin, persistent=False)
         self.activation_checkpointing = activation_checkpointing

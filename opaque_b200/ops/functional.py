@@ -391,11 +391,24 @@ def rope_inverse_frequencies(head_dim: int, theta: float, scaling: dict | None =
     raise NotImplementedError(f"rope scaling {kind!r} is not implemented (linear, dynamic, llama3 and yarn are)")
 
 
-def rope_tables(head_dim: int, max_pos: int, theta: float = 10000.0, device=None, scaling: dict | None = None):
-    """fp32 ``cos, sin`` tables of shape ``[max_pos, head_dim/2]`` (``scaling``: see ``rope_inverse_frequencies``)."""
-    inv, att = rope_inverse_frequencies(head_dim, theta, scaling, max_pos=max_pos, device=device)
+def rope_tables(head_dim: int, max_pos: int, theta: float = 10000.0, device=None, scaling: dict | None = None,
+                rotary_dim: int | None = None):
+    """fp32 ``cos, sin`` tables of shape ``[max_pos, head_dim/2]`` (``scaling``: see ``rope_inverse_frequencies``).
+
+    With ``rotary_dim < head_dim`` (partial rotary embedding) only the first ``rotary_dim/2`` pairs ``(i, i + head_dim/2)``
+    rotate; the remaining columns hold ``cos = 1, sin = 0``, which leaves those pairs untouched.
+    """
+    rot = head_dim if rotary_dim is None else int(rotary_dim)
+    if rot % 2 or not 0 < rot <= head_dim:
+        raise ValueError("rotary_dim must be even and in (0, head_dim]")
+    inv, att = rope_inverse_frequencies(rot, theta, scaling, max_pos=max_pos, device=device)
     ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None, :]
-    return (ang.cos() * att).contiguous(), (ang.sin() * att).contiguous()
+    cos, sin = ang.cos() * att, ang.sin() * att
+    if rot < head_dim:
+        pad = (head_dim - rot) // 2
+        cos = torch.cat([cos, torch.ones(max_pos, pad, dtype=torch.float32, device=device)], dim=1)
+        sin = torch.cat([sin, torch.zeros(max_pos, pad, dtype=torch.float32, device=device)], dim=1)
+    return cos.contiguous(), sin.contiguous()
 
 
 def rope_qk_ref(q, k, cos, sin, pos=None, sign=1.0):

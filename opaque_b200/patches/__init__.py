@@ -26,12 +26,13 @@ _RUNTIME = {"patched": False}
 # model_type -> family builder.  Only families whose block structure these modules reproduce exactly are registered;
 # the others are listed with the reason, so a conversion can never silently drop a feature of the architecture.
 LLAMA_LIKE = ("llama", "mistral", "ministral", "mellum", "qwen2", "qwen3", "gemma", "gemma2", "gemma3_text", "phi3", "granite",
-              "smollm3", "olmo2", "olmo3", "exaone4")
+              "smollm3", "olmo2", "olmo3", "exaone4", "glm4")
 MOE_LIKE = ("mixtral", "qwen2_moe", "qwen3_moe")
+ROPE_INTERLEAVED = frozenset({"glm4"})      # families that rotate the pairs (2i, 2i+1); q / k rows are permuted on conversion
 UNSUPPORTED = {
     "gemma3": "the multimodal wrapper; convert its text model (model_type gemma3_text)",
     "cohere": "LayerNorm, parallel attention + MLP block, logit scale", "cohere2": "as cohere plus sliding-window layers",
-    "glm4": "extra post-sub-layer norms and partial rotary embedding",
+   
     "gpt_oss": "attention sinks, clamped SwiGLU with biases, alternating sliding windows",
     "deepseek_v4": "multi-head latent attention", "hunyuan_v1_moe": "q/k norms and a mixed shared-expert layout",
     "qwen3_next": "gated delta-net layers", "qwen3_5_moe": "gated delta-net layers",
@@ -53,6 +54,25 @@ def _rope_theta(cfg: Any, default: float) -> float:
     if isinstance(rp, dict) and rp.get("rope_theta"):
         return float(rp["rope_theta"])
     return float(_cfg_get(cfg, "rope_theta", default))
+
+
+def rope_row_permutation(head_dim: int, rotary_dim: int, interleaved: bool) -> torch.Tensor:
+    """Order of one head's rows that turns a source rotary layout into this package's.
+
+    The kernels here rotate the pairs ``(i, i + head_dim/2)`` and leave a pair alone where the tables hold
+    ``cos = 1, sin = 0``.  A source model rotates, inside its first ``rotary_dim`` dimensions, either the pairs
+    ``(2i, 2i+1)`` (``interleaved``) or ``(i, i + rotary_dim/2)``, and passes the other dimensions through.  Taking q and
+    k rows in the returned order puts the two members of rotating pair ``i`` at ``i`` and ``head_dim/2 + i`` and fills the
+    remaining positions with the pass-through dimensions; q·k is unchanged because both are permuted alike.
+    """
+    half, rh = head_dim // 2, rotary_dim // 2
+    if interleaved:
+        first, second = [2 * i for i in range(rh)], [2 * i + 1 for i in range(rh)]
+    else:
+        first, second = list(range(rh)), [rh + i for i in range(rh)]
+    rest = list(range(rotary_dim, head_dim))
+    keep = half - rh
+    return torch.tensor(first + rest[:keep] + second + rest[keep:], dtype=torch.long)
 
 
 def _layer_windows(cfg: Any) -> tuple | None:
@@ -121,6 +141,9 @@ def _build_llama(cfg: Any, opt: dict) -> torch.nn.Module:
                      post_norm=True, qk_norm_full=True, layer_windows=_layer_windows(cfg))
         if _rope_scaling(cfg) is not None:
             raise NotImplementedError("OLMo-3 applies rope scaling to its full-attention layers only; that split is not implemented")
+    elif mtype == "glm4":
+        extra.update(attention_bias=bool(_cfg_get(cfg, "attention_bias", True)), sandwich_norm=True,
+                     partial_rotary_factor=float(_cfg_get(cfg, "partial_rotary_factor", 0.5)))
     elif mtype == "exaone4":
         windows = _layer_windows(cfg)
         extra.update(post_norm=True, qk_norm=True, layer_windows=windows)
@@ -134,6 +157,11 @@ def _build_llama(cfg: Any, opt: dict) -> torch.nn.Module:
                      mlp_bias=bool(_cfg_get(cfg, "mlp_bias", False)))
     if "hidden_act" not in extra:
         extra["hidden_act"] = _cfg_get(cfg, "hidden_act", "silu")
+    if "partial_rotary_factor" not in extra:          # e.g. Phi-4-mini: 0.75 with the (i, i + rotary_dim/2) layout
+        rp = _cfg_get(cfg, "rope_parameters") or {}
+        pf = _cfg_get(cfg, "partial_rotary_factor") or (rp.get("partial_rotary_factor") if isinstance(rp, dict) else None)
+        if pf and float(pf) < 1.0:
+            extra["partial_rotary_factor"] = float(pf)
     window = _cfg_get(cfg, "sliding_window") if _cfg_get(cfg, "use_sliding_window", mtype in ("mistral", "ministral")) else None
     theta, scaling = opt.get("_rope") or (_rope_theta(cfg, 10000.0), _rope_scaling(cfg))
     c = LlamaConfig(vocab_size=_cfg_get(cfg, "vocab_size"), hidden_size=_cfg_get(cfg, "hidden_size"),
@@ -211,10 +239,33 @@ def _convert_state_dict(mtype: str, sd: dict, out: torch.nn.Module) -> dict:
             base = k[: -len("gate_up_proj.weight")]
             res[base + "gate_proj.weight"], res[base + "up_proj.weight"] = v[:half], v[half:]
             continue
+        if mtype == "glm4":
+            if k.endswith("mlp.gate_up_proj.weight"):
+                half = v.shape[0] // 2
+                base = k[: -len("gate_up_proj.weight")]
+                res[base + "gate_proj.weight"], res[base + "up_proj.weight"] = v[:half], v[half:]
+                continue
+            # four norms per layer: (input, post_self_attn) around attention, (post_attention, post_mlp) around the MLP
+            for src, dst in ((".post_attention_layernorm.", ".pre_feedforward_layernorm."),
+                             (".post_self_attn_layernorm.", ".post_attention_layernorm."),
+                             (".post_mlp_layernorm.", ".post_feedforward_layernorm.")):
+                if src in k:
+                    k = k.replace(src, dst)
+                    break
         if moe and (k.endswith("mlp.gate.weight") or k.endswith("mlp.shared_expert_gate.weight")):
             rows = out.config.padded_experts if k.endswith("mlp.gate.weight") else 8
             v = torch.cat([v, v.new_zeros(rows - v.shape[0], v.shape[1])]) if v.shape[0] < rows else v
         res[k] = v
+    cfg = out.config
+    factor = float(getattr(cfg, "partial_rotary_factor", 1.0))
+    if not moe and (mtype in ROPE_INTERLEAVED or factor < 1.0):
+        hd = cfg.hd
+        perm = rope_row_permutation(hd, int(hd * factor), mtype in ROPE_INTERLEAVED)
+        for k in list(res):
+            if k.endswith(("self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.q_proj.bias", "self_attn.k_proj.bias")):
+                v = res[k]
+                heads = v.shape[0] // hd
+                res[k] = v.reshape(heads, hd, *v.shape[1:])[:, perm].reshape(v.shape).contiguous()
     tied = getattr(out.config, "tie_word_embeddings", False)
     if "lm_head.weight" not in res:
         emb = "embed_tokens.weight" if moe else "model.embed_tokens.weight"

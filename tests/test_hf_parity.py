@@ -33,6 +33,9 @@ def _cases():
                                             layer_types=["sliding_attention", "sliding_attention", "full_attention", "sliding_attention"]), T.Gemma3ForCausalLM
     yield "olmo3", T.Olmo3Config(**four, sliding_window=8, pad_token_id=0), T.Olmo3ForCausalLM
     yield "exaone4", T.Exaone4Config(**four, sliding_window=8, pad_token_id=0), T.Exaone4ForCausalLM
+    yield "glm4", T.Glm4Config(**four, head_dim=16, pad_token_id=0), T.Glm4ForCausalLM
+    yield "phi3-partial-rotary", T.Phi3Config(**COMMON, pad_token_id=0, rope_parameters={"rope_type": "default", "rope_theta": 10000.0,
+                                                                                        "partial_rotary_factor": 0.5}), T.Phi3ForCausalLM
     yield "phi3", T.Phi3Config(**COMMON, pad_token_id=0), T.Phi3ForCausalLM
     yield "granite", T.GraniteConfig(**COMMON, embedding_multiplier=6.0, attention_multiplier=0.11, residual_multiplier=0.4, logits_scaling=3.0), T.GraniteForCausalLM
     yield "olmo2", T.Olmo2Config(**COMMON, pad_token_id=0), T.Olmo2ForCausalLM

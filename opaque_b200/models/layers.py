@@ -90,7 +90,9 @@ class _LayerNormDP(Function):
         xhat = (xf - mu) * rstd
         ctx.save_for_backward(xhat.to(x.dtype), rstd, weight)
         ctx.layer = layer
-        return (xhat * weight.float() + bias.float()).to(x.dtype)
+        ctx.has_bias = bias is not None
+        y = xhat * weight.float()
+        return (y + bias.float() if bias is not None else y).to(x.dtype)
 
     @staticmethod
     def backward(ctx, gy):
@@ -103,17 +105,22 @@ class _LayerNormDP(Function):
         if cap is not None:
             B = cap.batch_size
             cap.add_per_example_grad(ctx.layer, "weight", (g * xh).reshape(B, -1, g.shape[-1]).sum(1))
-            cap.add_per_example_grad(ctx.layer, "bias", g.reshape(B, -1, g.shape[-1]).sum(1))
+            if ctx.has_bias:
+                cap.add_per_example_grad(ctx.layer, "bias", g.reshape(B, -1, g.shape[-1]).sum(1))
             return dx.to(gy.dtype), None, None, None, None
         flat = g.reshape(-1, g.shape[-1])
-        return dx.to(gy.dtype), (flat * xh.reshape(flat.shape)).sum(0).to(weight.dtype), flat.sum(0).to(weight.dtype), None, None
+        return (dx.to(gy.dtype), (flat * xh.reshape(flat.shape)).sum(0).to(weight.dtype),
+                flat.sum(0).to(weight.dtype) if ctx.has_bias else None, None, None)
 
 
 class LayerNorm(nn.Module):
-    def __init__(self, dim: int, eps: float = 1e-5, *, dtype=None, device=None):
+    def __init__(self, dim: int, eps: float = 1e-5, *, bias: bool = True, dtype=None, device=None):
         super().__init__()
         self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device))
-        self.bias = nn.Parameter(torch.zeros(dim, dtype=dtype, device=device))
+        if bias:
+            self.bias = nn.Parameter(torch.zeros(dim, dtype=dtype, device=device))
+        else:
+            self.register_parameter("bias", None)          # Cohere: scale only
         self.eps = eps
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

@@ -17,7 +17,7 @@ import torch
 from torch import nn
 
 from .. import ops
-from .layers import Embedding, Linear, RMSNorm, linear_cross_entropy, per_example_token_weights
+from .layers import Embedding, LayerNorm, Linear, RMSNorm, linear_cross_entropy, per_example_token_weights
 
 
 @dataclasses.dataclass
@@ -63,6 +63,10 @@ class LlamaConfig:
     # GLM-4 / Phi-4-mini: only the first head_dim * factor dimensions rotate.  The kernels rotate pairs (i, i + head_dim/2),
     # so a converted checkpoint has its q / k rows permuted accordingly (patches.rope_row_permutation)
     partial_rotary_factor: float = 1.0
+    # Cohere: LayerNorm without bias instead of RMSNorm, and attention and MLP both reading ONE normed input
+    # (h + attn(n(h)) + mlp(n(h)))
+    norm_type: str = "rms"                   # rms | layernorm
+    parallel_block: bool = False
 
     @property
     def hd(self) -> int:
@@ -171,6 +175,14 @@ class LlamaMLP(nn.Module):
         return self.down_proj(ops.geglu(g, u, approximate=self.act == "gelu_pytorch_tanh"))
 
 
+def _make_norm(cfg: LlamaConfig, dtype, device):
+    if cfg.norm_type == "layernorm":
+        return LayerNorm(cfg.hidden_size, cfg.rms_norm_eps, bias=False, dtype=dtype, device=device)
+    if cfg.norm_type != "rms":
+        raise ValueError(f"unknown norm_type {cfg.norm_type!r}")
+    return RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, offset=cfg.norm_offset, casting_mode=cfg.norm_casting, dtype=dtype, device=device)
+
+
 class LlamaDecoderLayer(nn.Module):
     def __init__(self, cfg: LlamaConfig, dtype, device, layer_idx: int = 0):
         super().__init__()
@@ -178,6 +190,12 @@ class LlamaDecoderLayer(nn.Module):
         nk = dict(offset=cfg.norm_offset, casting_mode=cfg.norm_casting, dtype=dtype, device=device)
         self.post_norm = cfg.post_norm
         self.sandwich = cfg.sandwich_norm
+        self.parallel = cfg.parallel_block
+        if cfg.parallel_block:
+            self.input_layernorm = _make_norm(cfg, dtype, device)
+            self.self_attn = LlamaAttention(cfg, dtype, device, layer_idx)
+            self.mlp = LlamaMLP(cfg, dtype, device)
+            return
         if cfg.sandwich_norm:
             self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
             self.pre_feedforward_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
@@ -191,6 +209,9 @@ class LlamaDecoderLayer(nn.Module):
         self.mlp = LlamaMLP(cfg, dtype, device)
 
     def forward(self, h, cos, sin, pos):
+        if self.parallel:
+            n = self.input_layernorm(h)
+            return h + self.self_attn(n, cos, sin, pos) + self.mlp(n)
         if self.sandwich:
             h = h + self.post_attention_layernorm(self.self_attn(self.input_layernorm(h), cos, sin, pos))
             return h + self.post_feedforward_layernorm(self.mlp(self.pre_feedforward_layernorm(h)))
@@ -209,8 +230,7 @@ class LlamaModel(nn.Module):
         super().__init__()
         self.embed_tokens = Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
         self.layers = nn.ModuleList(LlamaDecoderLayer(cfg, dtype, device, i) for i in range(cfg.num_hidden_layers))
-        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, offset=cfg.norm_offset, casting_mode=cfg.norm_casting,
-                            dtype=dtype, device=device)
+        self.norm = _make_norm(cfg, dtype, device)
 
 
 class LlamaForCausalLM(nn.Module):

@@ -26,13 +26,11 @@ _RUNTIME = {"patched": False}
 # model_type -> family builder.  Only families whose block structure these modules reproduce exactly are registered;
 # the others are listed with the reason, so a conversion can never silently drop a feature of the architecture.
 LLAMA_LIKE = ("llama", "mistral", "ministral", "mellum", "qwen2", "qwen3", "gemma", "gemma2", "gemma3_text", "phi3", "granite",
-              "smollm3", "olmo2", "olmo3", "exaone4", "glm4")
+              "smollm3", "olmo2", "olmo3", "exaone4", "glm4", "cohere", "cohere2")
 MOE_LIKE = ("mixtral", "qwen2_moe", "qwen3_moe")
-ROPE_INTERLEAVED = frozenset({"glm4"})      # families that rotate the pairs (2i, 2i+1); q / k rows are permuted on conversion
+ROPE_INTERLEAVED = frozenset({"glm4", "cohere", "cohere2"})      # families that rotate the pairs (2i, 2i+1); q / k rows are permuted on conversion
 UNSUPPORTED = {
     "gemma3": "the multimodal wrapper; convert its text model (model_type gemma3_text)",
-    "cohere": "LayerNorm, parallel attention + MLP block, logit scale", "cohere2": "as cohere plus sliding-window layers",
-   
     "gpt_oss": "attention sinks, clamped SwiGLU with biases, alternating sliding windows",
     "deepseek_v4": "multi-head latent attention", "hunyuan_v1_moe": "q/k norms and a mixed shared-expert layout",
     "qwen3_next": "gated delta-net layers", "qwen3_5_moe": "gated delta-net layers",
@@ -144,6 +142,17 @@ def _build_llama(cfg: Any, opt: dict) -> torch.nn.Module:
     elif mtype == "glm4":
         extra.update(attention_bias=bool(_cfg_get(cfg, "attention_bias", True)), sandwich_norm=True,
                      partial_rotary_factor=float(_cfg_get(cfg, "partial_rotary_factor", 0.5)))
+    elif mtype in ("cohere", "cohere2"):
+        if _cfg_get(cfg, "use_qk_norm", False):
+            raise NotImplementedError("Cohere q/k LayerNorm with per-head weights is not implemented")
+        extra.update(attention_bias=bool(_cfg_get(cfg, "attention_bias", False)), attention_out_bias=bool(_cfg_get(cfg, "attention_bias", False)),
+                     norm_type="layernorm", parallel_block=True, logits_scaling=1.0 / float(_cfg_get(cfg, "logit_scale", 1.0)))
+        if mtype == "cohere2":
+            windows = _layer_windows(cfg)
+            extra.update(layer_windows=windows)
+            if windows is not None:                    # full-attention layers carry no rotary embedding
+                extra.update(no_rope_layers=tuple(1 if w is not None else 0 for w in windows))
+        opt = {**opt, "_eps": float(_cfg_get(cfg, "layer_norm_eps", 1e-5))}
     elif mtype == "exaone4":
         windows = _layer_windows(cfg)
         extra.update(post_norm=True, qk_norm=True, layer_windows=windows)
@@ -168,7 +177,7 @@ def _build_llama(cfg: Any, opt: dict) -> torch.nn.Module:
                     intermediate_size=_cfg_get(cfg, "intermediate_size"), num_hidden_layers=_cfg_get(cfg, "num_hidden_layers"),
                     num_attention_heads=_cfg_get(cfg, "num_attention_heads"),
                     num_key_value_heads=_cfg_get(cfg, "num_key_value_heads") or _cfg_get(cfg, "num_attention_heads"),
-                    rms_norm_eps=_cfg_get(cfg, "rms_norm_eps", 1e-6), rope_theta=theta, rope_scaling=scaling,
+                    rms_norm_eps=opt.get("_eps") or _cfg_get(cfg, "rms_norm_eps", 1e-6), rope_theta=theta, rope_scaling=scaling,
                     max_position_embeddings=_cfg_get(cfg, "max_position_embeddings", 8192),
                     tie_word_embeddings=bool(_cfg_get(cfg, "tie_word_embeddings", False)), head_dim=_cfg_get(cfg, "head_dim"),
                     sliding_window=window, **extra)

@@ -33,6 +33,8 @@ def _cases():
                                             layer_types=["sliding_attention", "sliding_attention", "full_attention", "sliding_attention"]), T.Gemma3ForCausalLM
     yield "olmo3", T.Olmo3Config(**four, sliding_window=8, pad_token_id=0), T.Olmo3ForCausalLM
     yield "exaone4", T.Exaone4Config(**four, sliding_window=8, pad_token_id=0), T.Exaone4ForCausalLM
+    yield "cohere", T.CohereConfig(**COMMON, logit_scale=0.25, pad_token_id=0), T.CohereForCausalLM
+    yield "cohere2", T.Cohere2Config(**four, sliding_window=8, logit_scale=0.25, pad_token_id=0), T.Cohere2ForCausalLM
     yield "glm4", T.Glm4Config(**four, head_dim=16, pad_token_id=0), T.Glm4ForCausalLM
     yield "phi3-partial-rotary", T.Phi3Config(**COMMON, pad_token_id=0, rope_parameters={"rope_type": "default", "rope_theta": 10000.0,
                                                                                         "partial_rotary_factor": 0.5}), T.Phi3ForCausalLM
@@ -71,8 +73,10 @@ def test_converted_model_matches_hf_logits(name, cfg, cls):
 
 
 def test_unsupported_families_are_refused_with_a_reason():
-    with pytest.raises(NotImplementedError, match="LayerNorm"):
-        patches.apply_model_patches(transformers.CohereConfig(**COMMON))
+    with pytest.raises(NotImplementedError, match="attention sinks"):
+        patches.apply_model_patches({"model_type": "gpt_oss"})
+    with pytest.raises(NotImplementedError, match="per-head weights"):
+        patches.apply_model_patches(transformers.CohereConfig(**COMMON, use_qk_norm=True))
     with pytest.raises(ValueError, match="no registered family"):
         patches.apply_model_patches({"model_type": "not_a_model"})
 

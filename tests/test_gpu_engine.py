@@ -81,10 +81,13 @@ def test_llama_full_parameter_untied_and_tied():
                                           hidden_act="gelu_pytorch_tanh", norm_offset=1.0, norm_casting="gemma"),
                                      dict(post_norm=True, qk_norm=True, head_dim=32, layer_windows=(64, None), no_rope_layers=(1, 0)),
                                      dict(sandwich_norm=True, qk_norm=True, head_dim=32, layer_windows=(64, None), local_rope_theta=10000.0,
-                                          rope_scaling={"rope_type": "linear", "factor": 8.0})])
+                                          rope_scaling={"rope_type": "linear", "factor": 8.0}),
+                                     dict(norm_type="layernorm", parallel_block=True, logits_scaling=4.0),
+                                     dict(sandwich_norm=True, partial_rotary_factor=0.5, attention_bias=True)])
 def test_llama_family_variants_full_parameter(variant):
     """Qwen2 biases, Qwen3 q/k norms, Gemma GeGLU / (1+w) norms / scaled embeddings, OLMo-2 post-norm, Granite multipliers,
-    Gemma-2 capping and sandwich norms with a windowed layer, EXAONE-4 hybrid layers, Gemma-3 local rotary base."""
+    Gemma-2 capping and sandwich norms with a windowed layer, EXAONE-4 hybrid layers, Gemma-3 local rotary base,
+    Cohere parallel block with bias-free LayerNorm, GLM-4 partial rotary embedding."""
     from opaque_b200.models import LlamaConfig, LlamaForCausalLM
     dev = torch.device("cuda", 0)
     torch.manual_seed(7)

@@ -68,6 +68,7 @@ _CONFIG: contextvars.ContextVar[DiscretizationConfig] = contextvars.ContextVar("
 
 
 def get_discretization() -> DiscretizationConfig:
+    """The ambient ``DiscretizationConfig``."""
     return _CONFIG.get()
 
 
@@ -332,22 +333,27 @@ class PerStep(DpProcess):
 
 
 def eps_delta(epsilon: float, delta: float = 0.0) -> EpsDelta:
+    """A mechanism known only through an ``(epsilon, delta)`` guarantee."""
     return EpsDelta(float(epsilon), float(delta))
 
 
 def identity() -> Identity:
+    """The process that releases nothing (neutral element of composition)."""
     return Identity()
 
 
 def nonprivate() -> NonPrivate:
+    """A release with no privacy guarantee (infinite loss)."""
     return NonPrivate()
 
 
 def repeat(process: DpProcess, count: int) -> DpProcess:
+    """``n``-fold self-composition of a process (also ``process * n``)."""
     return process * count
 
 
 def compose(*processes: DpProcess) -> DpProcess:
+    """Sequential composition of processes (also available as ``a | b``)."""
     out: DpProcess = Identity()
     for p in processes:
         out = out | p
@@ -355,10 +361,12 @@ def compose(*processes: DpProcess) -> DpProcess:
 
 
 def cached(process: DpProcess) -> CachedProcess:
+    """Wrap a process so that its PLD is computed once per discretisation config and reused."""
     return process if isinstance(process, CachedProcess) else CachedProcess(process)
 
 
 def per_step(process: DpHorizonProcess) -> PerStep:
+    """View a horizon-dependent process as ``n`` per-step releases (``process.pld_at(n)``)."""
     return PerStep(process)
 
 
@@ -517,6 +525,7 @@ _BUDGETS: dict[str, type] = {c.__name__: c for c in (EpsilonBudget, DeltaBudget,
 
 
 def register_budget_serializer(cls: type) -> type:
+    """Register a budget class with the wire codec."""
     _BUDGETS[cls.__name__] = cls
     return cls
 
@@ -535,22 +544,27 @@ def budget_from_state_dict(sd: Mapping[str, Any] | None):
 
 
 def epsilon_budget(epsilon: float, delta: float) -> EpsilonBudget:
+    """Budget stated as ``epsilon`` at a fixed ``delta``."""
     return EpsilonBudget(float(epsilon), float(delta))
 
 
 def delta_budget(delta: float, epsilon: float) -> DeltaBudget:
+    """Budget stated as ``delta`` at a fixed ``epsilon``."""
     return DeltaBudget(float(delta), float(epsilon))
 
 
 def advantage_budget(advantage: float) -> AdvantageBudget:
+    """Budget stated as a bound on the membership-inference advantage."""
     return AdvantageBudget(float(advantage))
 
 
 def beta_budget(beta: float, alpha: float) -> BetaBudget:
+    """Budget stated as a false-negative rate ``beta`` at false-positive rate ``alpha`` (trade-off curve point)."""
     return BetaBudget(float(beta), float(alpha))
 
 
 def risk_budget(risk: float, prior: float) -> RiskBudget:
+    """Budget stated as a bound on the Bayes risk of a membership attacker with a given prior."""
     return RiskBudget(float(risk), float(prior))
 
 

@@ -61,6 +61,7 @@ def fused_nll_loss(hidden: torch.Tensor, head_weight: torch.Tensor, labels: torc
 
 def fused_sequence_logp(hidden, head_weight, labels, *, average: bool = False, ignore_index: int = IGNORE_INDEX,
                         chunk: int = 8192):
+    """Per-sequence (sum or mean) log-probability of the labels from hidden states and the head weight, without keeping logits."""
     B, T = labels.shape
     mask = labels != ignore_index
     w = per_example_token_weights(labels, ignore_index) if average else mask.float()
@@ -70,6 +71,7 @@ def fused_sequence_logp(hidden, head_weight, labels, *, average: bool = False, i
 
 
 def token_accuracy(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = IGNORE_INDEX) -> torch.Tensor:
+    """Fraction of scored tokens whose arg-max prediction equals the label."""
     mask = labels != ignore_index
     return ((logits.argmax(-1) == labels) & mask).sum().float() / mask.sum().clamp_min(1)
 

@@ -53,6 +53,7 @@ class CanaryScores:
 
 
 def canary_scores(scores: Any) -> CanaryScores:
+    """Wrap an array or tensor of per-canary scores as ``CanaryScores``."""
     if isinstance(scores, torch.Tensor):
         scores = scores.detach().float().cpu().numpy()
     return CanaryScores(np.asarray(scores))
@@ -165,6 +166,7 @@ def roc_curve(scores: CanaryScores, flips: CoinFlip):
 
 
 def auc(scores: CanaryScores, flips: CoinFlip) -> float:
+    """Area under the ROC curve of the canary scores against the coin flips."""
     fpr, tpr, _ = roc_curve(scores, flips)
     return float(np.trapezoid(np.concatenate([[0], tpr]), np.concatenate([[0], fpr])))
 

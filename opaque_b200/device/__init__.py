@@ -48,6 +48,7 @@ def _probe(index: int) -> DeviceCapabilities:
 
 
 def device_capabilities(device: torch.device | str | int | None = None) -> DeviceCapabilities:
+    """What the current device offers (bf16, fused kernels, peer access, memory) as a ``DeviceCapabilities``."""
     if device is None:
         idx = torch.cuda.current_device() if torch.cuda.is_available() else 0
     elif isinstance(device, int):

@@ -33,14 +33,17 @@ _OPS = {"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp
 
 
 def is_distributed() -> bool:
+    """True when a process group with more than one rank is initialised."""
     return dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
 
 
 def get_rank() -> int:
+    """Rank of this process (0 without a process group)."""
     return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
 
 
 def get_world_size() -> int:
+    """Number of processes (1 without a process group)."""
     return dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
 
 
@@ -49,10 +52,12 @@ num_processes = get_world_size
 
 
 def is_main_process() -> bool:
+    """True on rank 0."""
     return get_rank() == 0
 
 
 def barrier() -> None:
+    """Block until every rank arrives (no-op in a single process)."""
     if is_distributed():
         dist.barrier()
 
@@ -82,6 +87,7 @@ def all_reduce_(tensor: torch.Tensor, op: str = "sum") -> torch.Tensor:
 
 
 def all_reduce(tensor: torch.Tensor, op: str = "sum") -> torch.Tensor:
+    """Out-of-place ``all_reduce_``: returns the reduced copy of ``tensor``."""
     return all_reduce_(tensor.clone(), op)
 
 
@@ -210,6 +216,7 @@ def gather_tensors(tensor: torch.Tensor, *, dim: int = 0) -> torch.Tensor:
 
 
 def gather_pytree(tree: Any, *, dim: int = 0) -> Any:
+    """``gather_tensors`` applied to every tensor leaf of a tree."""
     return tree_map(lambda x: gather_tensors(x, dim=dim) if isinstance(x, torch.Tensor) else x, tree)
 
 
@@ -288,6 +295,7 @@ def reduce_pytree_(tree: Any, op: str = "sum", *, check_metadata: bool = True) -
 
 
 def reduce_pytree(tree: Any, op: str = "sum", **kw: Any) -> Any:
+    """Out-of-place ``reduce_pytree_``."""
     if isinstance(tree, SecondMomentClippingOutput):
         return SecondMomentClippingOutput(reduce_pytree(tree.grads, op, **kw), reduce_pytree(tree.squared_grads, op, **kw))
     cloned = tree.clone() if isinstance(tree, ClippedPytree) else tree_map(
@@ -296,10 +304,12 @@ def reduce_pytree(tree: Any, op: str = "sum", **kw: Any) -> Any:
 
 
 def sum_gradients_(tree: Any) -> Any:
+    """Sum a ``ClippedPytree`` over ranks in place (one packed all-reduce); the sensitivity metadata must agree on every rank."""
     return reduce_pytree_(tree, "sum")
 
 
 def sum_gradients(tree: Any) -> Any:
+    """Out-of-place ``sum_gradients_``."""
     return reduce_pytree(tree, "sum")
 
 

@@ -135,16 +135,19 @@ _strategy_process_codec(BallsInBins)
 
 def mf_gaussian(noise_multiplier: float, strategy: MfStrategy, *, n_steps: int = 1, min_sep: int = 1,
                 max_participations: int | None = None) -> MfGaussian:
+    """A matrix-factorisation Gaussian mechanism: the noise multiplier is divided by the strategy's sensitivity under the participation pattern."""
     return MfGaussian(float(noise_multiplier), strategy, int(n_steps), int(min_sep), max_participations)
 
 
 def poisson(inner: MfGaussian, sample_rate: float, *, n_steps: int, truncated_batch_size: int | None = None,
             dataset_size: int | None = None) -> CyclicPoisson:
+    """Poisson subsampling of ``inner`` at ``sample_rate`` (optionally with a truncated batch size)."""
     bands = int(getattr(inner.strategy, "bands", getattr(inner.strategy, "bandwidth", 1)))
     return CyclicPoisson(inner, float(sample_rate), int(n_steps), bands, truncated_batch_size, dataset_size)
 
 
 def balls_in_bins(inner: MfGaussian, *, num_bins: int, n_steps: int) -> BallsInBins:
+    """Balls-in-bins participation (each record lands in one of ``num_bins`` steps per epoch) over a matrix-factorisation mechanism, Monte-Carlo PLD."""
     return BallsInBins(inner, int(num_bins), int(n_steps))
 
 

@@ -451,28 +451,34 @@ class LambdaCgdStrategy(MfStrategy):
 
 
 def identity_strategy() -> IdentityStrategy:
+    """``C = I``: independent noise per step (DP-SGD as a matrix-factorisation strategy)."""
     return IdentityStrategy()
 
 
 def band_mf_strategy(*, bands: int, momentum: float = 1.0, lr_schedule=None) -> BandMfStrategy:
+    """Banded Toeplitz strategy with ``bands`` diagonals whose coefficients are optimised numerically (one participation per band window)."""
     return BandMfStrategy(int(bands), float(momentum), lr_schedule)
 
 
 def blt_strategy(*, max_buffers: int = 10, momentum: float = 1.0, lr_schedule=None) -> BltStrategy:
+    """Buffered linear Toeplitz: ``C`` generated by a few (scale, decay) pairs; ``C^-1`` streams with one buffer per pair."""
     return BltStrategy(int(max_buffers), float(momentum), lr_schedule)
 
 
 def bsr_strategy(*, bandwidth: int, alpha: float = 1.0, beta: float = 0.0) -> BsrStrategy:
+    """Banded square root: the first ``bandwidth`` coefficients of the square root of the workload with weight decay ``alpha`` and momentum ``beta``."""
     return BsrStrategy(int(bandwidth), float(alpha), float(beta))
 
 
 def bisr_strategy(*, bandwidth: int, normalized: bool = True, momentum: float = 0.0, lr_schedule=None,
                   inv_coefficients=None) -> BisrStrategy:
+    """Banded inverse square root: ``C^-1`` itself is banded (an FIR filter on the noise), ``C`` is dense."""
     inv = None if inv_coefficients is None else tuple(float(x) for x in inv_coefficients)
     return BisrStrategy(int(bandwidth), bool(normalized), float(momentum), lr_schedule, inv)
 
 
 def lambda_cgd_strategy(*, lambda_: float, normalized: bool = True, lr_schedule=None) -> LambdaCgdStrategy:
+    """lambda-CGD: ``n_t = d_t (z_t - lambda z_{t-1})``, anti-correlated noise with one step of memory (``d_t`` normalises the sensitivity to one when ``normalized``)."""
     return LambdaCgdStrategy(float(lambda_), bool(normalized), lr_schedule)
 
 

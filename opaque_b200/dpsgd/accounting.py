@@ -110,19 +110,23 @@ class RandomAllocation(DpProcess):
 
 
 def gaussian(noise_multiplier: float) -> Gaussian:
+    """One Gaussian release with the given noise multiplier (sensitivity 1)."""
     return Gaussian(float(noise_multiplier))
 
 
 def adaclip(inner: Gaussian, *, fraction_noise_std: float, expected_batch_size: float, num_groups: int = 1) -> AdaClip:
+    """Gaussian release under AdaClip-style adaptive clipping: the effective noise multiplier accounts for the noised clip-fraction query."""
     return AdaClip(inner, float(fraction_noise_std), float(expected_batch_size), int(num_groups))
 
 
 def poisson(inner: DpProcess, sample_rate: float, *, truncated_batch_size: int | None = None,
             dataset_size: int | None = None) -> Poisson:
+    """Poisson subsampling of ``inner`` at ``sample_rate`` (optionally with a truncated batch size)."""
     return Poisson(inner, float(sample_rate), truncated_batch_size, dataset_size)
 
 
 def parallel_poisson(inner: DpProcess, sample_rate: float, num_workers: int) -> ParallelPoisson:
+    """``num_workers`` workers each Poisson-sample the SAME dataset at ``sample_rate``; a record can be hit by several of them in one step."""
     return ParallelPoisson(inner, float(sample_rate), int(num_workers))
 
 
@@ -132,6 +136,7 @@ def random_allocation(inner: DpProcess, num_bins: int) -> RandomAllocation:
 
 
 def k_out_of_t(inner: DpProcess, k: int, t: int) -> RandomAllocation:
+    """Each record participates in exactly ``k`` of every ``t`` steps (fixed-participation sampling)."""
     return RandomAllocation(inner, int(t), int(k))
 
 

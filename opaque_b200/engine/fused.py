@@ -55,11 +55,13 @@ LORA_PAD = 64
 
 
 def current_capture() -> "Capture | None":
+    """The active ``Capture`` or ``None``."""
     return _ACTIVE
 
 
 @contextlib.contextmanager
 def activate(cap: "Capture"):
+    """Context manager that makes ``capture`` the active one for the DP-aware layers."""
     global _ACTIVE
     prev, _ACTIVE = _ACTIVE, cap
     try:
@@ -290,6 +292,7 @@ class _DPLinear(Function):
 
 
 def dp_linear(x: torch.Tensor, weight: torch.nn.Parameter, bias: torch.nn.Parameter | None = None) -> torch.Tensor:
+    """``x W^T (+ b)`` whose weight gradient is deferred to the active capture."""
     if weight.requires_grad and x.is_cuda and current_capture() is not None:
         return _DPLinear.apply(x, weight, bias)
     return torch.nn.functional.linear(x, weight, bias)
@@ -315,6 +318,7 @@ class _DPEmbedding(Function):
 
 
 def dp_embedding(ids: torch.Tensor, weight: torch.nn.Parameter) -> torch.Tensor:
+    """Embedding lookup whose weight gradient is deferred to the active capture."""
     if weight.requires_grad and ids.is_cuda and current_capture() is not None:
         return _DPEmbedding.apply(ids, weight)
     return torch.nn.functional.embedding(ids, weight)
@@ -383,6 +387,7 @@ class _LoRALinear(Function):
 
 
 def lora_linear(x, weight, bias, lora_a, lora_b, scaling: float):
+    """Frozen base linear plus LoRA factors; per-example factor gradients go to the active capture."""
     if x.is_cuda and x.dtype == torch.bfloat16 and ops.functional.kernels_enabled():
         return _LoRALinear.apply(x, weight, bias, lora_a, lora_b, scaling)
     y = torch.nn.functional.linear(x, weight, bias)

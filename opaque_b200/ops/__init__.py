@@ -45,6 +45,7 @@ def _need_bf16(*ts: torch.Tensor) -> None:
 # =============================================================================== wgrad / ghost
 
 def pick_block_n(n: int) -> int:
+    """Output tile width of the clip-weighted GEMM for ``n`` columns."""
     if n > 128:
         return 256
     return 128 if n > 64 else 64
@@ -293,6 +294,7 @@ def ghost_set_wide(mode: int | bool) -> int:
 
 
 def ghost_norm_ref(a, g, tokens_per_example, *, ids=None):
+    """PyTorch reference of ``ghost_norm``: per-example squared gradient norms from Gram matrices."""
     B = g.shape[0] // tokens_per_example
     gg = g.float().view(B, tokens_per_example, -1)
     sg = gg @ gg.transpose(1, 2)

@@ -276,6 +276,7 @@ ACTIVATION_SWIGLU, ACTIVATION_GEGLU_EXACT, ACTIVATION_GEGLU_APPROX = 0, 1, 2
 
 
 def glu_ref(gate, up, act=0):
+    """PyTorch reference of the gated activations (``swiglu`` / ``geglu``)."""
     g = gate.float()
     if act == 0:
         a = torch.nn.functional.silu(g)
@@ -324,6 +325,7 @@ def swiglu(gate, up):
 
 
 def geglu(gate, up, approximate=False):
+    """``gelu(gate) * up`` (erf or tanh form) with a fused backward."""
     act = ACTIVATION_GEGLU_APPROX if approximate else ACTIVATION_GEGLU_EXACT
     if _use_kernel(gate, up) and gate.shape[-1] % 8 == 0:
         return _GLU.apply(gate, up, act)

@@ -193,6 +193,7 @@ class RMSpropState:
 def rmsprop(lr: LR = 1e-2, alpha: float = 0.99, eps: float = 1e-8, weight_decay: float = 0.0, *,
             decoupled_weight_decay: bool = True, update_rms_clip: float | None = None,
             noise_bias_correction: bool = False):
+    """RMSprop with optional momentum and centring."""
     def init(params):
         return RMSpropState(_f32(params), 0.0, 0)
 
@@ -271,6 +272,7 @@ class AdadeltaState:
 def adadelta(lr: LR = 1.0, rho: float = 0.9, eps: float = 1e-6, weight_decay: float = 0.0, *,
              decoupled_weight_decay: bool = True, update_rms_clip: float | None = None,
              noise_bias_correction: bool = False):
+    """Adadelta (running averages of squared gradients and squared updates)."""
     def init(params):
         return AdadeltaState(_f32(params), _f32(params), 0.0, 0)
 
@@ -433,11 +435,13 @@ def schedule_free(base: GradientTransformation, lr: LR = 1e-3, beta: float = 0.9
 
 
 def schedule_free_sgd(lr: LR = 1.0, beta: float = 0.9, warmup_steps: int = 0, weight_decay: float = 0.0):
+    """Schedule-free SGD."""
     return schedule_free(sgd(lr=lr, weight_decay=weight_decay), lr=lr, beta=beta, warmup_steps=warmup_steps)
 
 
 def schedule_free_adamw(lr: LR = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
                         warmup_steps: int = 0, noise_bias_correction: bool = False):
+    """Schedule-free AdamW (interpolated iterate sequences, no learning-rate schedule)."""
     inner = make_optimizer_chain(_scale_by_rms(betas[1], eps, noise_bias_correction), lr, weight_decay)
     return schedule_free(inner, lr=lr, beta=betas[0], warmup_steps=warmup_steps)
 

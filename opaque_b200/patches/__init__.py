@@ -284,6 +284,7 @@ def _convert_state_dict(mtype: str, sd: dict, out: torch.nn.Module) -> dict:
 
 
 def supported_families() -> list[str]:
+    """Sorted Hugging Face ``model_type`` names that ``apply_model_patches`` converts."""
     return sorted(_FAMILIES)
 
 
@@ -350,6 +351,7 @@ def apply_runtime_patches(*, performance: bool = True, compat: bool = True, **kw
 
 
 def is_runtime_patched() -> bool:
+    """True once ``apply_runtime_patches`` ran in this process."""
     return _RUNTIME["patched"]
 
 

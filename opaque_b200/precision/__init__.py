@@ -42,6 +42,7 @@ def _scalable(x: Any) -> bool:
 def loss_scaler(*, init_scale: float = 2.0 ** 16, growth_factor: float = 2.0,
                 backoff_factor: float = 0.5, growth_interval: int = 2000,
                 enabled: bool = True) -> tuple[LossScaler, LossScalerState]:
+    """Functional dynamic loss scaler for fp16: returns ``(LossScaler, LossScalerState)``."""
     if not math.isfinite(init_scale) or init_scale <= 0.0:
         raise ValueError(f"init_scale must be finite and > 0, got {init_scale}")
     if not math.isfinite(growth_factor) or growth_factor <= 1.0:

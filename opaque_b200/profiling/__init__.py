@@ -39,6 +39,7 @@ def _is_cuda(device: Any) -> bool:
 
 
 def get_memory_stats(device: Any = None) -> MemoryStats:
+    """Current / peak allocated and reserved device memory in bytes."""
     if device is None or not _is_cuda(device):
         return MemoryStats()
     return MemoryStats(torch.cuda.memory_allocated(device), torch.cuda.memory_reserved(device),
@@ -46,16 +47,19 @@ def get_memory_stats(device: Any = None) -> MemoryStats:
 
 
 def reset_peak_memory(device: Any = None) -> None:
+    """Reset the allocator's peak-memory counters."""
     if device is not None and _is_cuda(device):
         torch.cuda.reset_peak_memory_stats(device)
 
 
 def empty_cache(device: Any = None) -> None:
+    """Release cached device memory held by the allocator (no-op without a GPU)."""
     if device is not None and _is_cuda(device):
         torch.cuda.empty_cache()
 
 
 def print_memory(device: Any = None, prefix: str = "") -> None:
+    """Print ``get_memory_stats`` in MiB with an optional prefix."""
     s = get_memory_stats(device)
     print(f"{prefix}allocated={s.allocated_bytes / 2**30:.2f}GiB reserved={s.reserved_bytes / 2**30:.2f}GiB "
           f"peak={s.peak_allocated_bytes / 2**30:.2f}GiB")
@@ -191,6 +195,7 @@ class PerfTracker:
 
 
 def perf_tracker(device: Any = None, warmup_steps: int = 1) -> PerfTracker:
+    """A ``PerfTracker`` that accumulates named step timings, samples and tokens."""
     return PerfTracker(device, warmup_steps)
 
 

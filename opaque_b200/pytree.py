@@ -124,19 +124,23 @@ def tree_flatten_with_paths(tree: Any, is_leaf: Callable[[Any], bool] | None = N
 
 
 def tree_flatten(tree: Any, is_leaf: Callable[[Any], bool] | None = None):
+    """Leaves of ``tree`` in a fixed order, and the structure that ``tree_unflatten`` needs to rebuild it."""
     _, leaves, td = tree_flatten_with_paths(tree, is_leaf)
     return leaves, td
 
 
 def tree_leaves(tree: Any, is_leaf: Callable[[Any], bool] | None = None) -> list[Any]:
+    """Leaves of ``tree`` in the order ``tree_flatten`` uses."""
     return tree_flatten(tree, is_leaf)[0]
 
 
 def tree_structure(tree: Any, is_leaf: Callable[[Any], bool] | None = None) -> TreeDef:
+    """The structure of ``tree`` without its leaves."""
     return tree_flatten(tree, is_leaf)[1]
 
 
 def tree_unflatten(treedef: TreeDef, leaves: Iterable[Any]) -> Any:
+    """Rebuild a tree from a structure and a sequence of leaves."""
     it = iter(leaves)
 
     def rec(td: TreeDef) -> Any:

@@ -37,6 +37,7 @@ class RngKey:
 
 
 def key(seed: int) -> RngKey:
+    """A root ``RngKey`` from an integer seed."""
     if isinstance(seed, bool) or not isinstance(seed, int):
         raise TypeError(f"seed must be int, got {type(seed)}")
     return RngKey(seed & _U64)
@@ -66,6 +67,7 @@ def fold_in(rng_key: RngKey, *data: int | str) -> RngKey:
 
 
 def split(rng_key: RngKey, num: int = 2) -> tuple[RngKey, ...]:
+    """``num`` independent child keys of ``key``."""
     if num < 1:
         raise ValueError(f"num must be >= 1, got {num}")
     return tuple(fold_in(rng_key, i) for i in range(num))

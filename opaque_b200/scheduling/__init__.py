@@ -41,10 +41,12 @@ def _resolve(shape: Shape, table: dict, field: str) -> Callable[[float], float]:
 
 
 def resolve_ramp(ramp: Shape, *, field: str = "ramp"):
+    """A named warm-up ramp (or a callable) as a function of the progress in [0, 1]."""
     return _resolve(ramp, NAMED_RAMPS, field)
 
 
 def resolve_decay(decay: Shape, *, field: str = "decay_shape"):
+    """A named decay shape (or a callable) as a function of the progress in [0, 1]."""
     return _resolve(decay, NAMED_DECAYS, field)
 
 
@@ -212,40 +214,48 @@ class WithWarmup:
 
 
 def constant_schedule(value: float) -> ConstantSchedule:
+    """``step -> value`` for every step."""
     return ConstantSchedule(float(value))
 
 
 def cosine_schedule(init_value, end_value, transition_steps, transition_begin=0, num_cycles=0.5):
+    """Cosine transition from ``init_value`` to ``end_value`` over ``transition_steps`` (``num_cycles`` of the cosine; 0.5 = one half-wave)."""
     return CosineSchedule(float(init_value), float(end_value), int(transition_steps),
                           int(transition_begin), float(num_cycles))
 
 
 def exponential_schedule(init_value, decay_rate, transition_begin=0, transition_steps=1,
                          staircase=False, end_value=None):
+    """``init_value * decay_rate ** ((step - transition_begin) / transition_steps)``, optionally in stair-steps and bounded by ``end_value``."""
     return ExponentialSchedule(float(init_value), float(decay_rate), int(transition_begin),
                                int(transition_steps), bool(staircase),
                                None if end_value is None else float(end_value))
 
 
 def inverse_sqrt_schedule(init_value, transition_steps, transition_begin=0):
+    """Flat at ``init_value`` for ``transition_steps`` steps, then inverse-square-root decay."""
     return InverseSqrtSchedule(float(init_value), int(transition_steps), int(transition_begin))
 
 
 def linear_schedule(init_value, end_value, transition_steps, transition_begin=0):
+    """Linear interpolation from ``init_value`` to ``end_value`` over ``transition_steps``."""
     return LinearSchedule(float(init_value), float(end_value), int(transition_steps), int(transition_begin))
 
 
 def one_minus_sqrt_schedule(init_value, end_value, transition_steps, transition_begin=0):
+    """``1 - sqrt(progress)`` transition from ``init_value`` to ``end_value`` over ``transition_steps``."""
     return OneMinusSqrtSchedule(float(init_value), float(end_value), int(transition_steps), int(transition_begin))
 
 
 def polynomial_schedule(init_value, end_value, power, transition_steps, transition_begin=0):
+    """Polynomial interpolation of the given ``power`` from ``init_value`` to ``end_value``."""
     return PolynomialSchedule(float(init_value), float(end_value), float(power),
                               int(transition_steps), int(transition_begin))
 
 
 def warmup_stable_decay(init_value, end_value=0.0, *, num_warmup_steps, num_stable_steps,
                         num_decay_steps, warmup_ramp="linear", decay_shape="1-sqrt"):
+    """Warm up to ``init_value``, hold it for ``num_stable_steps``, then decay to ``end_value`` (the WSD recipe)."""
     if num_warmup_steps <= 0:
         raise ValueError(f"warmup_stable_decay requires num_warmup_steps > 0; got {num_warmup_steps}.")
     if num_stable_steps < 0:
@@ -259,6 +269,7 @@ def warmup_stable_decay(init_value, end_value=0.0, *, num_warmup_steps, num_stab
 
 
 def with_restarts(schedule, transition_steps, num_cycles, transition_begin=0):
+    """Restart ``schedule`` every ``transition_steps`` steps, ``num_cycles`` times (warm restarts)."""
     if num_cycles <= 0:
         raise ValueError(f"with_restarts requires num_cycles > 0; got {num_cycles}.")
     if transition_steps <= 0:
@@ -267,6 +278,7 @@ def with_restarts(schedule, transition_steps, num_cycles, transition_begin=0):
 
 
 def with_warmup(schedule, transition_steps, *, ramp="linear", init_value=0.0):
+    """Multiply ``schedule`` by a warm-up ramp over its first ``transition_steps`` steps (from ``init_value`` of its value)."""
     if transition_steps <= 0:
         raise ValueError(f"with_warmup requires transition_steps > 0; got {transition_steps}.")
     if not 0.0 <= init_value <= 1.0:
@@ -303,6 +315,7 @@ def schedule_to_wire(schedule):
 
 
 def schedule_from_wire(wire):
+    """Rebuild a schedule from its serialised (wire) description."""
     if not isinstance(wire, dict) or RECIPE_TAG not in wire:
         return wire
     cls = RECIPES[wire[RECIPE_TAG]]

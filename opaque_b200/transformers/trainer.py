@@ -320,6 +320,14 @@ def default_per_example_loss(model_call: Callable[..., Any], example: Mapping[st
 # ------------------------------------------------------------------------------------------ trainer
 
 class DPTrainer:
+    """Differentially private trainer with the call surface of the Hugging Face ``Trainer``.
+
+    Owns sampling (Poisson and the DP-FTRL participation schemes), per-example clipping, noise, the privacy
+    accountant, evaluation, callbacks and checkpoints (resume replays batches and noise exactly).  Gradients come from
+    the fused B200 engine or from the functional reference engine (``args.dp_engine``; ``engine_kind`` tells which).
+    Parity: packages/opaque-transformers/src/opaque/api/transformers/trainer/_dp_trainer.py of the reference.
+    """
+
     def __init__(self, model: torch.nn.Module | None = None, args: TrainingArguments | None = None,
                  data_collator: Callable | None = None, train_dataset: Any = None, eval_dataset: Any = None,
                  processing_class: Any = None, compute_loss_func: Callable | None = None,

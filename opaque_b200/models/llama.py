@@ -53,6 +53,7 @@ class LlamaConfig:
     # OLMo-2: norms AFTER the sub-layers (h + norm(f(h))) and q/k norms over the whole projection
     post_norm: bool = False
     qk_norm_full: bool = False
+    qk_norm_after_rope: bool = False         # HunYuan: the per-head q / k norms follow the rotary embedding
     # Gemma-2/3, OLMo-3, EXAONE-4: per-layer attention windows (None = full attention), norms on both sides of each
     # sub-layer, tanh capping of attention scores and of the final logits, a second rotary base for windowed layers
     layer_windows: tuple | None = None
@@ -102,6 +103,7 @@ class LlamaAttention(nn.Module):
         self.softcap = cfg.attn_logit_softcap
         self.local_rope = cfg.local_rope_theta is not None and self.window is not None
         self.qk_full = cfg.qk_norm_full
+        self.qk_after = cfg.qk_norm_after_rope
         if cfg.qk_norm_full:
             self.q_norm = RMSNorm(self.nh * hd, cfg.rms_norm_eps, dtype=dtype, device=device)
             self.k_norm = RMSNorm(self.nkv * hd, cfg.rms_norm_eps, dtype=dtype, device=device)
@@ -118,7 +120,7 @@ class LlamaAttention(nn.Module):
             q, k = self.q_norm(q), self.k_norm(k)
         q, k = q.view(B, T, self.nh, self.hd), k.view(B, T, self.nkv, self.hd)
         v = self.v_proj(x).view(B, T, self.nkv, self.hd)
-        if self.q_norm is not None and not self.qk_full:
+        if self.q_norm is not None and not self.qk_full and not self.qk_after:
             q, k = self.q_norm(q), self.k_norm(k)
         if self.use_rope:
             if self.local_rope:                       # windowed layers rotate with their own base (tables 2 and 3)
@@ -127,6 +129,8 @@ class LlamaAttention(nn.Module):
                 q, k = ops.rope_qk(q, k, cos[0], sin[0], pos)
             else:
                 q, k = ops.rope_qk(q, k, cos, sin, pos)
+        if self.q_norm is not None and self.qk_after:
+            q, k = self.q_norm(q), self.k_norm(k)
         if self.softcap:
             # capped attention scores: no library attention kernel applies tanh between QK^T and the softmax, so the
             # scores are formed explicitly ([B, heads, T, T] in fp32) — correct for every length, meant for short ones

@@ -51,6 +51,7 @@ class MoEConfig:
     shared_intermediate_size: int | None = None
     head_dim: int | None = None
     qk_norm: bool = False
+    qk_norm_after_rope: bool = False
 
     @property
     def padded_experts(self) -> int:
@@ -61,6 +62,7 @@ class MoEConfig:
                            num_key_value_heads=self.num_key_value_heads, rms_norm_eps=self.rms_norm_eps,
                            rope_theta=self.rope_theta, max_position_embeddings=self.max_position_embeddings,
                            attention_bias=self.attention_bias, head_dim=self.head_dim, qk_norm=self.qk_norm,
+                           qk_norm_after_rope=self.qk_norm_after_rope, rope_scaling=self.rope_scaling,
                            intermediate_size=self.shared_intermediate_size or self.moe_intermediate_size * max(self.num_shared_experts, 1))
 
     @staticmethod

@@ -27,12 +27,12 @@ _RUNTIME = {"patched": False}
 # the others are listed with the reason, so a conversion can never silently drop a feature of the architecture.
 LLAMA_LIKE = ("llama", "mistral", "ministral", "mellum", "qwen2", "qwen3", "gemma", "gemma2", "gemma3_text", "phi3", "granite",
               "smollm3", "olmo2", "olmo3", "exaone4", "glm4", "cohere", "cohere2")
-MOE_LIKE = ("mixtral", "qwen2_moe", "qwen3_moe")
+MOE_LIKE = ("mixtral", "qwen2_moe", "qwen3_moe", "hunyuan_v1_moe")
 ROPE_INTERLEAVED = frozenset({"glm4", "cohere", "cohere2"})      # families that rotate the pairs (2i, 2i+1); q / k rows are permuted on conversion
 UNSUPPORTED = {
     "gemma3": "the multimodal wrapper; convert its text model (model_type gemma3_text)",
     "gpt_oss": "attention sinks, clamped SwiGLU with biases, alternating sliding windows",
-    "deepseek_v4": "multi-head latent attention", "hunyuan_v1_moe": "q/k norms and a mixed shared-expert layout",
+    "deepseek_v4": "multi-head latent attention",
     "qwen3_next": "gated delta-net layers", "qwen3_5_moe": "gated delta-net layers",
 }
 
@@ -198,6 +198,26 @@ def _build_moe(cfg: Any, opt: dict) -> torch.nn.Module:
     if mtype in ("qwen2_moe", "qwen3_moe"):        # a layer is sparse when it is not listed as MLP-only and falls on the sparse step
         only, step = set(_cfg_get(cfg, "mlp_only_layers") or ()), int(_cfg_get(cfg, "decoder_sparse_step", 1) or 1)
         dense = tuple(i for i in range(_cfg_get(cfg, "num_hidden_layers")) if i in only or (i + 1) % step != 0)
+    if mtype == "hunyuan_v1_moe":
+        for name in ("num_experts", "moe_topk"):
+            if not isinstance(_cfg_get(cfg, name), int):
+                raise NotImplementedError(f"per-layer {name} lists are not implemented")
+        rp = _cfg_get(cfg, "rope_parameters") or {}
+        theta = float(rp.get("rope_theta") or _cfg_get(cfg, "rope_theta", 10000.0))
+        hd = _cfg_get(cfg, "head_dim") or _cfg_get(cfg, "hidden_size") // _cfg_get(cfg, "num_attention_heads")
+        scaling = _rope_scaling(cfg)
+        if rp.get("rope_type") == "dynamic" and rp.get("alpha"):       # NTK-alpha: a larger base, no position scaling
+            theta, scaling = theta * float(rp["alpha"]) ** (hd / (hd - 2)), None
+        inter = _cfg_get(cfg, "intermediate_size")
+        c = MoEConfig(vocab_size=_cfg_get(cfg, "vocab_size"), hidden_size=_cfg_get(cfg, "hidden_size"),
+                      num_hidden_layers=_cfg_get(cfg, "num_hidden_layers"), num_attention_heads=_cfg_get(cfg, "num_attention_heads"),
+                      num_key_value_heads=_cfg_get(cfg, "num_key_value_heads") or _cfg_get(cfg, "num_attention_heads"),
+                      num_experts=_cfg_get(cfg, "num_experts"), moe_intermediate_size=inter, num_shared_experts=1,
+                      shared_intermediate_size=inter, shared_expert_gate=False, attention_bias=bool(_cfg_get(cfg, "attention_bias", False)),
+                      head_dim=hd, qk_norm=True, qk_norm_after_rope=True, num_experts_per_tok=_cfg_get(cfg, "moe_topk"),
+                      norm_topk_prob=True, rms_norm_eps=_cfg_get(cfg, "rms_norm_eps", 1e-5), rope_theta=theta, rope_scaling=scaling,
+                      max_position_embeddings=_cfg_get(cfg, "max_position_embeddings", 4096))
+        return MoEForCausalLM(c, dtype=opt.get("dtype", torch.bfloat16), device=opt.get("device"))
     c = MoEConfig(vocab_size=_cfg_get(cfg, "vocab_size"), hidden_size=_cfg_get(cfg, "hidden_size"),
                   num_hidden_layers=_cfg_get(cfg, "num_hidden_layers"), num_attention_heads=_cfg_get(cfg, "num_attention_heads"),
                   num_key_value_heads=_cfg_get(cfg, "num_key_value_heads") or _cfg_get(cfg, "num_attention_heads"),
@@ -237,6 +257,9 @@ def _convert_state_dict(mtype: str, sd: dict, out: torch.nn.Module) -> dict:
             continue
         if moe:
             k = k.removeprefix("model.")
+        if mtype == "hunyuan_v1_moe":
+            k = (k.replace(".query_layernorm.", ".q_norm.").replace(".key_layernorm.", ".k_norm.")
+                 .replace(".mlp.gate.wg.", ".mlp.gate.").replace(".mlp.shared_mlp.", ".mlp.shared_expert."))
         if mtype == "phi3" and k.endswith("self_attn.qkv_proj.weight"):
             cfg = out.config
             nq, nkv = cfg.num_attention_heads * cfg.hd, cfg.num_key_value_heads * cfg.hd

@@ -47,6 +47,8 @@ def _cases():
     yield "qwen3_moe-dense-interleaved", T.Qwen3MoeConfig(**{**COMMON, "num_hidden_layers": 4}, moe_intermediate_size=32, num_experts=6,
                                                           num_experts_per_tok=2, head_dim=16, norm_topk_prob=True,
                                                           mlp_only_layers=[0], decoder_sparse_step=2), T.Qwen3MoeForCausalLM
+    yield "hunyuan_v1_moe", T.HunYuanMoEV1Config(**{**COMMON, "intermediate_size": 48}, head_dim=16, num_experts=6, moe_topk=2,
+                                                 pad_token_id=0), T.HunYuanMoEV1ForCausalLM
     yield "gpt2", T.GPT2Config(vocab_size=320, n_positions=128, n_embd=64, n_layer=2, n_head=4), T.GPT2LMHeadModel
     yield "mixtral", T.MixtralConfig(**COMMON, num_local_experts=6, num_experts_per_tok=2), T.MixtralForCausalLM
     yield "qwen2_moe", T.Qwen2MoeConfig(**COMMON, moe_intermediate_size=32, shared_expert_intermediate_size=48, num_experts=6,

@@ -381,7 +381,7 @@ def main() -> None:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "impl": "ours",
-            "config": {"model": name, "global_batch": global_batch, "seq_len": seq, "parallelism": f"{par}{world}",
+            "config": {"model": name, "global_batch": global_batch, "seq_len": seq, "parallelism": par.replace("dp", f"dp{world}", 1),
                        "sampling": sampling or f"Poisson over the whole dataset (rate {per_gpu * world}/{data_size}), one global draw per step dealt out evenly over ranks", "microbatch": mb, "cuda_graph_microbatches": use_graph, "gradient_accumulation": engine.space.accumulate,
                        "loss_fraction": frac, "clip": dp["clipping_norm"], "sigma": dp["noise_multiplier"],
                        "optimizer": "AdamW-BC", "lr": dp["lr"],

@@ -125,7 +125,7 @@ def run_restated(args, model, dp, data, sampler, seq, per_gpu, mb, frac, vocab, 
 
     def host_batch():
         idx = next(batches)
-        return data[torch.as_tensor(idx, dtype=torch.long)].pin_memory() if idx else data[:0]
+        return data[torch.as_tensor(idx, dtype=torch.long) % data.shape[0]].pin_memory() if idx else data[:0]
 
     def step(hb):
         nonlocal trainable, clip_state, noise_state, opt_state
@@ -278,7 +278,10 @@ def main() -> None:
     data_size = per_gpu * 100 * world
     gen = torch.Generator().manual_seed(99)
     data = torch.randint(0, vocab, (data_size, seq), generator=gen, dtype=torch.int32).pin_memory()
-    sampler = BalancedRankSampler(PoissonSampler(range(data_size), per_gpu * world / data_size, key=key(7)), rank, world)
+    # GPT-2 is specified as Poisson sampling from 1e6 records: the draw runs over 1e6 logical records (same rate and batch-size
+    # spread as specified), which map onto the stored synthetic rows modulo data_size (all rows are uniform random tokens)
+    logical_size = 1_000_000 if args.config == "gpt2" else data_size
+    sampler = BalancedRankSampler(PoissonSampler(range(logical_size), per_gpu * world / logical_size, key=key(7)), rank, world)
     batches = iter(sampler)
     cursor = [rank * per_gpu]
 
@@ -288,7 +291,7 @@ def main() -> None:
             cursor[0] += per_gpu * world
             return data[lo:lo + per_gpu]
         idx = next(batches)
-        return data[torch.as_tensor(idx, dtype=torch.long)].pin_memory() if idx else data[:0]
+        return data[torch.as_tensor(idx, dtype=torch.long) % data_size].pin_memory() if idx else data[:0]
 
     if args.impl == "restated":
         run_restated(args, model, dp, data, sampler, seq, per_gpu, mb, frac, vocab, name, world, rank, dev)
@@ -382,7 +385,7 @@ def main() -> None:
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "impl": "ours",
             "config": {"model": name, "global_batch": global_batch, "seq_len": seq, "parallelism": par.replace("dp", f"dp{world}", 1),
-                       "sampling": sampling or f"Poisson over the whole dataset (rate {per_gpu * world}/{data_size}), one global draw per step dealt out evenly over ranks", "microbatch": mb, "cuda_graph_microbatches": use_graph, "gradient_accumulation": engine.space.accumulate,
+                       "sampling": sampling or f"Poisson over the whole dataset (rate {per_gpu * world}/{logical_size}), one global draw per step dealt out evenly over ranks", "microbatch": mb, "cuda_graph_microbatches": use_graph, "gradient_accumulation": engine.space.accumulate,
                        "loss_fraction": frac, "clip": dp["clipping_norm"], "sigma": dp["noise_multiplier"],
                        "optimizer": "AdamW-BC", "lr": dp["lr"],
                        "l2": "inputs larger than L2 (per-step working set >> 126 MB; no explicit flush)",

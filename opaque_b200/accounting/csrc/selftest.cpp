@@ -34,6 +34,22 @@ int main() {
   const Pld pp = parallel_poisson_gaussian_pld(1.0, 0.01, 4, cfg);
   if (!(pp.delta_at(1.0) >= 0 && pp.delta_at(1.0) <= 1)) { std::printf("delta out of range\n"); ++failures; }
   expect_close("beta(alpha) of eps_delta(1, 0) at 0.1", eps_delta_pld(1.0, 0.0, cfg).beta_at(0.1), 1.0 - std::exp(1.0) * 0.1, 2e-2);
+  {   // Monte-Carlo accountants: stored transcripts equal the streaming accountant, full horizon and a prefix
+    Config mc = cfg;
+    mc.num_mc_samples = 2000;
+    mc.seed = 5;
+    const std::vector<double> coef = {1.0, 0.6, 0.3};
+    const BMinSepCorpus corpus(coef, 40, 4, 0.1, true, mc.num_mc_samples, mc.seed);
+    expect_close("b-min-sep corpus bytes", static_cast<double>(corpus.nbytes()), 2000.0 * 40.0 * 17.0, 0.0);
+    for (std::size_t n : {std::size_t(40), std::size_t(17), std::size_t(1)}) {
+      const Pld a = b_min_sep_mc_pld(coef, n, 4, 0.1, 1.3, true, mc);
+      const Pld b = corpus.pld(1.3, n, mc);
+      expect_close("b-min-sep corpus == streaming (eps at 1e-4)", b.epsilon_at(1e-4), a.epsilon_at(1e-4), 0.0);
+    }
+    const std::vector<double> gram = toeplitz_gram({1.0, 0.5}, 12);
+    const Pld bb = balls_in_bins_mc_pld(gram, 12, 4, 1.5, mc);
+    if (!(bb.epsilon_at(1e-4) > 0)) { std::printf("balls-in-bins epsilon not positive\n"); ++failures; }
+  }
   std::printf("%s\n", failures ? "FAILED" : "all checks passed");
   return failures ? 1 : 0;
 }

@@ -1146,8 +1146,9 @@ double bms_log_ratio(const std::vector<double>& coef, const std::vector<double>&
     const double skip = f[std::min(ii + b, n)];
     const double a = (p < 1.0) ? std::log1p(-p) + f[ii + 1] : -std::numeric_limits<double>::infinity();
     const double c2 = std::log(p) + blk + skip;
-    const double hi = std::max(a, c2);
-    f[ii] = hi + std::log(std::exp(a - hi) + std::exp(c2 - hi));
+    // log(exp(a) + exp(c2)) with one exp: max + log1p(exp(-|a - c2|)); a = -inf (p = 1) leaves c2
+    const double hi = std::max(a, c2), lo = std::min(a, c2);
+    f[ii] = std::isinf(lo) ? hi : hi + std::log1p(std::exp(lo - hi));
   }
   if (!warm_start || b == 1) return f[0];
   const double denom = 1.0 + static_cast<double>(b - 1) * p;

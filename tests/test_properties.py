@@ -1,0 +1,84 @@
+"""Property-based checks (hypothesis) of the substrate: pytrees, keys, serialization, the clipping bound, samplers."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+hypothesis = pytest.importorskip("hypothesis")
+from hypothesis import given, settings, strategies as st  # noqa: E402
+
+from opaque_b200 import pytree as pt  # noqa: E402
+from opaque_b200.dpsgd import PoissonSampler  # noqa: E402
+from opaque_b200.engine.clipping import clip_pytree  # noqa: E402
+from opaque_b200.random import fold_in, key, split  # noqa: E402
+from opaque_b200.serialization import from_state_dict, state_dict  # noqa: E402
+
+FAST = settings(max_examples=40, deadline=None)
+
+shapes = st.lists(st.integers(1, 5), min_size=0, max_size=3).map(tuple)
+leaves = shapes.map(lambda s: torch.arange(int(np.prod(s)) if s else 1, dtype=torch.float32).reshape(s if s else ()) - 1.5)
+trees = st.recursive(leaves, lambda children: st.one_of(
+    st.lists(children, min_size=1, max_size=3), st.lists(children, min_size=1, max_size=3).map(tuple),
+    st.dictionaries(st.text("abcdef", min_size=1, max_size=3), children, min_size=1, max_size=3)), max_leaves=8)
+
+
+@FAST
+@given(trees)
+def test_flatten_unflatten_round_trips_and_map_preserves_structure(tree):
+    flat, td = pt.tree_flatten(tree)
+    again = pt.tree_unflatten(td, flat)
+    assert pt.tree_structure(again) == td
+    assert all(torch.equal(a, b) for a, b in zip(pt.tree_leaves(again), flat))
+    doubled = pt.tree_map(lambda x: 2 * x, tree)
+    assert pt.tree_structure(doubled) == td
+    total = math.sqrt(sum(float((x.double() ** 2).sum()) for x in flat))
+    assert math.isclose(float(pt.global_norm(tree)), total, rel_tol=1e-6, abs_tol=1e-12)
+
+
+@FAST
+@given(trees)
+def test_state_dict_round_trips_any_tensor_tree(tree):
+    template = pt.tree_map(torch.zeros_like, tree)
+    restored = from_state_dict(template, state_dict(tree))
+    assert pt.tree_structure(restored) == pt.tree_structure(tree)
+    assert all(torch.equal(a, b) for a, b in zip(pt.tree_leaves(restored), pt.tree_leaves(tree)))
+
+
+@FAST
+@given(st.integers(0, 2 ** 63 - 1), st.lists(st.one_of(st.integers(-2 ** 40, 2 ** 40), st.text(max_size=8)), min_size=1, max_size=4))
+def test_fold_in_is_deterministic_and_left_folding(seed, data):
+    k = key(seed)
+    assert fold_in(k, *data) == fold_in(k, *data)
+    step = k
+    for item in data:
+        step = fold_in(step, item)
+    assert step == fold_in(k, *data)
+    kids = split(k, 3)
+    assert len({c.seed for c in kids}) == 3 and all(c == fold_in(k, i) for i, c in enumerate(kids))
+
+
+@FAST
+@given(trees, st.floats(1e-3, 1e3), st.sampled_from([torch.float32, torch.bfloat16, torch.float16]), st.floats(1e-3, 1e4))
+def test_clipped_record_respects_the_bound_as_stored(tree, C, dtype, magnitude):
+    record = pt.tree_map(lambda x: (x * magnitude).to(dtype), tree)
+    clipped, aux = clip_pytree(record, C)
+    stored = math.sqrt(sum(float((x.double() ** 2).sum()) for x in pt.tree_leaves(clipped)))
+    assert stored <= C * (1 + 1e-12)                         # the bound holds on the values in their storage dtype
+    before = math.sqrt(sum(float((x.double() ** 2).sum()) for x in pt.tree_leaves(record)))
+    if math.isfinite(before) and before <= 0.5 * C:          # records well inside the bound pass (almost) unchanged
+        assert stored >= 0.98 * before
+
+
+@FAST
+@given(st.integers(50, 400), st.floats(0.05, 0.9), st.integers(0, 10 ** 6), st.integers(1, 5))
+def test_poisson_sampler_resumes_exactly_and_stays_in_range(n, rate, seed, consumed):
+    a = PoissonSampler(range(n), rate, n_steps=consumed + 3, key=key(seed))
+    it = iter(a)
+    head = [next(it) for _ in range(consumed)]
+    saved = state_dict(a)
+    tail = list(it)
+    b = from_state_dict(PoissonSampler(range(n), rate, n_steps=consumed + 3, key=key(seed)), saved)
+    assert list(b) == tail and len(tail) == 3
+    for batch in head + tail:
+        assert batch == sorted(set(batch)) and (not batch or (0 <= batch[0] and batch[-1] < n))

@@ -17,24 +17,27 @@ PYBIND11_MODULE(_native, m) {
 
   py::class_<Config>(m, "DiscretizationConfig")
       .def(py::init([](double disc, double log_mass, std::size_t max_grid, double tail, std::size_t max_conv,
-                       std::size_t mc, std::uint64_t seed) {
+                       std::size_t mc, std::uint64_t seed, bool proportional) {
              if (!(disc > 0.0)) throw std::invalid_argument("discretization must be > 0");
              if (!(tail >= 0.0 && tail < 1.0)) throw std::invalid_argument("tail_mass_truncation must be in [0, 1)");
              Config c;
              c.discretization = disc; c.log_mass_truncation_bound = log_mass; c.max_grid_size = max_grid;
              c.tail_mass_truncation = tail; c.max_conv_grid = max_conv; c.num_mc_samples = mc; c.seed = seed;
+             c.proportional_normalization = proportional;
              return c;
            }),
            py::arg("discretization") = 1e-4, py::arg("log_mass_truncation_bound") = -50.0,
            py::arg("max_grid_size") = 10'000'000, py::arg("tail_mass_truncation") = 1e-15,
-           py::arg("max_conv_grid") = 32768, py::arg("num_mc_samples") = 100000, py::arg("seed") = 42)
+           py::arg("max_conv_grid") = 32768, py::arg("num_mc_samples") = 100000, py::arg("seed") = 42,
+           py::arg("proportional_normalization") = false)
       .def_readwrite("discretization", &Config::discretization)
       .def_readwrite("log_mass_truncation_bound", &Config::log_mass_truncation_bound)
       .def_readwrite("max_grid_size", &Config::max_grid_size)
       .def_readwrite("tail_mass_truncation", &Config::tail_mass_truncation)
       .def_readwrite("max_conv_grid", &Config::max_conv_grid)
       .def_readwrite("num_mc_samples", &Config::num_mc_samples)
-      .def_readwrite("seed", &Config::seed);
+      .def_readwrite("seed", &Config::seed)
+      .def_readwrite("proportional_normalization", &Config::proportional_normalization);
 
   py::class_<Pld>(m, "Pld")
       .def("epsilon_at", &Pld::epsilon_at, py::arg("delta"))

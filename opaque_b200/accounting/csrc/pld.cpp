@@ -439,7 +439,8 @@ double Pld::risk_at(double prior) const {
 
 // =============================================================================== connect the dots
 
-Pmf connect_the_dots(const std::vector<double>& deltas_in, std::int64_t lo_idx, double disc, std::size_t max_grid) {
+Pmf connect_the_dots(const std::vector<double>& deltas_in, std::int64_t lo_idx, double disc, std::size_t max_grid,
+                     bool proportional_normalization) {
   require(!deltas_in.empty(), "connect_the_dots: empty delta array");
   std::vector<double> deltas = deltas_in;
   const std::size_t n = deltas.size();
@@ -466,8 +467,23 @@ Pmf connect_the_dots(const std::vector<double>& deltas_in, std::int64_t lo_idx, 
   }
   pmf.infinity_mass = deltas[n - 1];
   const double target = 1.0 - pmf.infinity_mass;
-  if (total > 0.0 && total != target)
-    for (double& p : probs) p *= target / total;
+  // Clamping the cancellation noise of the second differences at zero leaves a little too much mass (about 1e-12 per grid
+  // point, 1e-8 in total).  Scaling every probability down would lower delta(eps) by that relative amount everywhere, below
+  // the exact curve; instead the surplus is taken from the LOWEST losses (no effect on delta at any eps above them) and a
+  // shortfall is added at the HIGHEST loss, so the estimate stays an upper bound.
+  double surplus = total - target;
+  if (proportional_normalization) {
+    if (total > 0.0 && total != target)
+      for (double& p : probs) p *= target / total;
+  } else if (surplus > 0.0) {
+    for (std::size_t i = 0; i < n && surplus > 0.0; ++i) {
+      const double take = std::min(probs[i], surplus);
+      probs[i] -= take;
+      surplus -= take;
+    }
+  } else if (surplus < 0.0) {
+    probs[n - 1] -= surplus;
+  }
   // trim leading / trailing zeros
   std::size_t first = 0, last = n;
   while (first + 1 < last && probs[first] == 0.0) ++first;
@@ -497,7 +513,7 @@ Pld discretize(const Config& cfg, EpsBounds rb, std::optional<EpsBounds> ab,
 #pragma omp parallel for schedule(static) if (deltas.size() >= 4096)
     for (std::int64_t i = 0; i < static_cast<std::int64_t>(deltas.size()); ++i)
       deltas[static_cast<std::size_t>(i)] = delta_fn(static_cast<double>(lo + i) * disc, adj);
-    return connect_the_dots(deltas, lo, disc, cfg.max_grid_size);
+    return connect_the_dots(deltas, lo, disc, cfg.max_grid_size, cfg.proportional_normalization);
   };
   Pld out;
   out.remove = build(rb, Adjacency::Remove);

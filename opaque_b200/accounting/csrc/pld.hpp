@@ -27,6 +27,9 @@ struct Config {
   std::size_t max_conv_grid = 32768;
   std::size_t num_mc_samples = 100000;
   std::uint64_t seed = 42;
+  // true: rescale a discretised PMF to unit mass (what the reference library's pinned values contain; lowers delta by
+  // ~1e-8 relative); false: remove surplus mass from the lowest losses only, which keeps delta an upper bound
+  bool proportional_normalization = false;
 };
 
 enum class Adjacency { Remove = 0, Add = 1, Replace = 2 };
@@ -80,7 +83,8 @@ double log_a_times_exp_b_plus_c(double a, double b, double c);
 std::vector<double> convolve(const std::vector<double>& a, const std::vector<double>& b);
 
 // ---- builders ---------------------------------------------------------------------------------------
-Pmf connect_the_dots(const std::vector<double>& deltas, std::int64_t lo_idx, double disc, std::size_t max_grid);
+Pmf connect_the_dots(const std::vector<double>& deltas, std::int64_t lo_idx, double disc, std::size_t max_grid,
+                     bool proportional_normalization = false);
 Pld discretize(const Config& cfg, EpsBounds remove_b, std::optional<EpsBounds> add_b,
                const std::function<double(double, Adjacency)>& delta_fn);
 

@@ -34,6 +34,16 @@ int main() {
   const Pld pp = parallel_poisson_gaussian_pld(1.0, 0.01, 4, cfg);
   if (!(pp.delta_at(1.0) >= 0 && pp.delta_at(1.0) <= 1)) { std::printf("delta out of range\n"); ++failures; }
   expect_close("beta(alpha) of eps_delta(1, 0) at 0.1", eps_delta_pld(1.0, 0.0, cfg).beta_at(0.1), 1.0 - std::exp(1.0) * 0.1, 2e-2);
+  {   // discretised PLDs never fall below the analytic Gaussian curve (grid points included)
+    for (double sigma : {0.7, 1.0, 2.0})
+      for (double eps : {0.0, 0.5, 1.0, 2.0}) {
+        const double exact = gaussian_delta(sigma, eps, 1.0), got = gaussian_pld(sigma, cfg).delta_at(eps);
+        if (!(got >= exact * (1.0 - 1e-12) && got <= exact * (1.0 + 1e-6) + 1e-12)) {
+          std::printf("gaussian(%g) delta(%g): got %.15g, analytic %.15g\n", sigma, eps, got, exact);
+          ++failures;
+        }
+      }
+  }
   {   // Monte-Carlo accountants: stored transcripts equal the streaming accountant, full horizon and a prefix
     Config mc = cfg;
     mc.num_mc_samples = 2000;

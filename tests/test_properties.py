@@ -82,3 +82,33 @@ def test_poisson_sampler_resumes_exactly_and_stays_in_range(n, rate, seed, consu
     assert list(b) == tail and len(tail) == 3
     for batch in head + tail:
         assert batch == sorted(set(batch)) and (not batch or (0 <= batch[0] and batch[-1] < n))
+
+
+SLOW = settings(max_examples=12, deadline=None)
+
+
+@SLOW
+@given(st.floats(0.6, 3.0), st.floats(0.001, 0.2), st.integers(1, 300), st.floats(1e-8, 1e-3))
+def test_accountant_is_monotone_and_self_consistent(sigma, q, steps, delta):
+    from opaque_b200.dpsgd import accounting as dp
+    run = dp.poisson(dp.gaussian(sigma), q) * steps
+    eps = run.epsilon_at(delta)
+    assert eps >= 0 and math.isfinite(eps)
+    assert run.delta_at(eps) <= delta * (1 + 1e-6) + 1e-15          # (eps, delta) is a valid pair of the same curve
+    assert (dp.poisson(dp.gaussian(sigma * 1.25), q) * steps).epsilon_at(delta) <= eps + 1e-9      # more noise, less loss
+    assert (dp.poisson(dp.gaussian(sigma), q) * (steps + 50)).epsilon_at(delta) >= eps - 1e-9       # more steps, more loss
+    assert run.epsilon_at(delta * 10) <= eps + 1e-9                                                 # larger delta, smaller eps
+    unamplified = (dp.gaussian(sigma) * steps).epsilon_at(delta)
+    assert eps <= unamplified + 1e-6                                                                # subsampling never hurts
+    assert 0.0 <= run.delta_at(0.0) <= 1.0
+
+
+@SLOW
+@given(st.floats(0.5, 4.0), st.floats(0.01, 8.0))
+def test_gaussian_pld_matches_the_analytic_curve(sigma, eps):
+    from scipy.stats import norm
+    from opaque_b200.dpsgd import accounting as dp
+    exact = norm.cdf(0.5 / sigma - eps * sigma) - math.exp(eps) * norm.cdf(-0.5 / sigma - eps * sigma)
+    got = dp.gaussian(sigma).delta_at(eps)
+    assert got >= exact - 1e-9                      # pessimistic
+    assert got <= exact + 2e-3 * max(exact, 1e-6) + 1e-7

@@ -112,3 +112,22 @@ def test_gaussian_pld_matches_the_analytic_curve(sigma, eps):
     got = dp.gaussian(sigma).delta_at(eps)
     assert got >= exact - 1e-9                      # pessimistic
     assert got <= exact + 2e-3 * max(exact, 1e-6) + 1e-7
+
+
+@FAST
+@given(st.floats(1e-2, 1e2), st.floats(1e-2, 1e2), st.floats(1e-3, 1e3), st.sampled_from([torch.float32, torch.bfloat16]))
+def test_per_group_clipping_bounds_every_group_and_the_whole(c_a, c_b, magnitude, dtype):
+    from opaque_b200.engine.clipping import auto_scale_pytree, per_group
+    torch.manual_seed(0)
+    record = {"a": {"w": (torch.randn(7, 5) * magnitude).to(dtype)}, "b": {"w": (torch.randn(11) * magnitude).to(dtype),
+                                                                          "v": (torch.randn(3, 2) * magnitude).to(dtype)}}
+    bound = per_group(record, {"a": c_a, "b": c_b})
+    clipped, _ = clip_pytree(record, bound)
+    na = float(clipped["a"]["w"].double().norm())
+    nb = math.sqrt(float(clipped["b"]["w"].double().norm()) ** 2 + float(clipped["b"]["v"].double().norm()) ** 2)
+    assert na <= c_a * (1 + 1e-12) and nb <= c_b * (1 + 1e-12)
+    assert math.hypot(na, nb) <= bound.effective * (1 + 1e-12)
+    # AUTO-S never lets a record exceed R (its factor is R / (norm + gamma) < R / norm)
+    scaled, _ = auto_scale_pytree(record, 1.0, 0.01)
+    total = math.sqrt(sum(float(x.double().norm()) ** 2 for x in pt.tree_leaves(scaled)))
+    assert total <= 1.0 * (1 + 1e-12)

@@ -131,3 +131,32 @@ def test_per_group_clipping_bounds_every_group_and_the_whole(c_a, c_b, magnitude
     scaled, _ = auto_scale_pytree(record, 1.0, 0.01)
     total = math.sqrt(sum(float(x.double().norm()) ** 2 for x in pt.tree_leaves(scaled)))
     assert total <= 1.0 * (1 + 1e-12)
+
+
+def _brute_force_sensitivity(C: np.ndarray, min_sep: int, max_participations: int) -> float:
+    """max over participation sets (indices at least ``min_sep`` apart, at most ``max_participations`` of them) of the
+    norm of the summed columns; valid as the sensitivity because every entry of ``C`` here is non-negative."""
+    import itertools
+    n = C.shape[1]
+    best = 0.0
+    for k in range(1, max_participations + 1):
+        for idx in itertools.combinations(range(n), k):
+            if all(b - a >= min_sep for a, b in zip(idx, idx[1:])):
+                best = max(best, float(np.linalg.norm(C[:, list(idx)].sum(1))))
+    return best
+
+
+@settings(max_examples=25, deadline=None)
+@given(st.integers(4, 9), st.integers(1, 4), st.integers(1, 3), st.sampled_from(["identity", "band", "blt", "bsr"]))
+def test_strategy_sensitivity_dominates_brute_force(n, min_sep, max_participations, kind):
+    from scipy.linalg import toeplitz
+    from opaque_b200.dpftrl import band_mf_strategy, blt_strategy, bsr_strategy, identity_strategy
+    s = {"identity": identity_strategy(), "band": band_mf_strategy(bands=3), "blt": blt_strategy(max_buffers=2),
+         "bsr": bsr_strategy(bandwidth=3, alpha=1.0, beta=0.0)}[kind]
+    c = np.pad(np.asarray(s.coefficients(n), float), (0, n))[:n]
+    assert (c >= -1e-12).all()
+    C = np.tril(toeplitz(c))
+    brute = _brute_force_sensitivity(C, min_sep, max_participations)
+    got = s.sensitivity(n, min_sep, max_participations)
+    assert got >= brute * (1 - 1e-9)                    # never below the true sensitivity
+    assert got <= brute * 1.5 + 1e-9                    # and not vacuous on these small cases

@@ -160,3 +160,21 @@ def test_strategy_sensitivity_dominates_brute_force(n, min_sep, max_participatio
     got = s.sensitivity(n, min_sep, max_participations)
     assert got >= brute * (1 - 1e-9)                    # never below the true sensitivity
     assert got <= brute * 1.5 + 1e-9                    # and not vacuous on these small cases
+
+
+@settings(max_examples=15, deadline=None)
+@given(st.floats(0.5, 3.0), st.floats(0.01, 0.5), st.floats(0.0, 3.0))
+def test_poisson_subsampled_gaussian_pld_dominates_the_hockey_stick_integral(sigma, q, eps):
+    """One step, both adjacency directions, against a dense numerical integral of max(0, P - e^eps Q)."""
+    from scipy.stats import norm
+    from opaque_b200.dpsgd import accounting as dp
+    x = np.linspace(-12 * sigma - 1, 12 * sigma + 2, 400_001)
+    base, shifted = norm.pdf(x, 0.0, sigma), norm.pdf(x, 1.0, sigma)
+    mix = (1 - q) * base + q * shifted
+    dx = x[1] - x[0]
+    remove = float(np.maximum(mix - math.exp(eps) * base, 0.0).sum() * dx)       # P = with the record, Q = without
+    add = float(np.maximum(base - math.exp(eps) * mix, 0.0).sum() * dx)
+    exact = max(remove, add)
+    got = dp.poisson(dp.gaussian(sigma), q).delta_at(eps)
+    assert got >= exact - 1e-7 - 1e-4 * exact           # the integral itself carries ~1e-7 of quadrature error
+    assert got <= exact * (1 + 5e-3) + 1e-6

@@ -178,3 +178,27 @@ def test_poisson_subsampled_gaussian_pld_dominates_the_hockey_stick_integral(sig
     got = dp.poisson(dp.gaussian(sigma), q).delta_at(eps)
     assert got >= exact - 1e-7 - 1e-4 * exact           # the integral itself carries ~1e-7 of quadrature error
     assert got <= exact * (1 + 5e-3) + 1e-6
+
+
+@settings(max_examples=8, deadline=None)
+@given(st.floats(0.7, 2.5), st.floats(0.0, 2.5), st.sampled_from([2, 3]))
+def test_random_allocation_pld_dominates_the_exact_divergence(sigma, eps, t):
+    """One record lands in exactly one of ``t`` steps: P = (1/t) sum_j N(e_j, sigma^2 I), Q = N(0, sigma^2 I).  The exact
+    hockey-stick divergences (both directions) are integrated on a dense grid in t dimensions."""
+    from opaque_b200.dpsgd import accounting as dp
+    m = 601 if t == 2 else 141
+    g = np.linspace(-7 * sigma, 7 * sigma + 1, m)
+    dx = g[1] - g[0]
+    axes = np.meshgrid(*([g] * t), indexing="ij")
+    log_q = sum(-0.5 * (a / sigma) ** 2 for a in axes) - t * math.log(sigma * math.sqrt(2 * math.pi))
+    # P / Q = (1/t) sum_j exp((2 y_j - 1) / (2 sigma^2))
+    ratio = sum(np.exp((2 * a - 1) / (2 * sigma ** 2)) for a in axes) / t
+    q = np.exp(log_q)
+    vol = dx ** t
+    remove = float(np.maximum(q * ratio - math.exp(eps) * q, 0.0).sum() * vol)
+    add = float(np.maximum(q - math.exp(eps) * q * ratio, 0.0).sum() * vol)
+    exact = max(remove, add)
+    got = dp.random_allocation(dp.gaussian(sigma), t).delta_at(eps)
+    slack = 2e-3 if t == 2 else 2e-2                  # quadrature error of the coarse 3-D grid
+    assert got >= exact * (1 - slack) - 1e-6
+    assert got <= max(dp.gaussian(sigma).delta_at(eps), exact) * (1 + 1e-9) + 1e-9       # never worse than no amplification

@@ -202,3 +202,15 @@ def test_random_allocation_pld_dominates_the_exact_divergence(sigma, eps, t):
     slack = 2e-3 if t == 2 else 2e-2                  # quadrature error of the coarse 3-D grid
     assert got >= exact * (1 - slack) - 1e-6
     assert got <= max(dp.gaussian(sigma).delta_at(eps), exact) * (1 + 1e-9) + 1e-9       # never worse than no amplification
+
+
+@pytest.mark.parametrize("n,p,sigma", [(8, 0.3, 1.5), (16, 0.1, 1.0), (4, 0.6, 2.0)])
+def test_b_min_sep_monte_carlo_reduces_to_poisson_composition_without_separation(n, p, sigma):
+    """One band and no separation: every step takes the record independently with probability p, which is n-fold
+    Poisson-subsampled Gaussian composition — known exactly from the PLD accountant."""
+    from opaque_b200.accounting.core import DiscretizationConfig, native
+    from opaque_b200.dpsgd import accounting as dp
+    mc = native.b_min_sep_mc_pld([1.0], n, 1, p, sigma, False, DiscretizationConfig(num_mc_samples=200_000).to_native())
+    exact = dp.poisson(dp.gaussian(sigma), p) * n
+    for eps in (0.5, 1.0):
+        assert abs(mc.delta_at(eps) - exact.delta_at(eps)) < 0.05 * exact.delta_at(eps)

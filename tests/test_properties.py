@@ -214,3 +214,15 @@ def test_b_min_sep_monte_carlo_reduces_to_poisson_composition_without_separation
     exact = dp.poisson(dp.gaussian(sigma), p) * n
     for eps in (0.5, 1.0):
         assert abs(mc.delta_at(eps) - exact.delta_at(eps)) < 0.05 * exact.delta_at(eps)
+
+
+@pytest.mark.parametrize("t,sigma", [(4, 1.0), (3, 0.8)])
+def test_balls_in_bins_monte_carlo_matches_random_allocation_for_the_identity_strategy(t, sigma):
+    """``C = I`` and one epoch of ``t`` bins is random allocation of one participation, which the PLD accountant covers."""
+    from opaque_b200.accounting.core import DiscretizationConfig, native
+    from opaque_b200.dpsgd import accounting as dp
+    mc = native.balls_in_bins_mc_pld(np.eye(t).reshape(-1).tolist(), t, t, sigma,
+                                     DiscretizationConfig(num_mc_samples=200_000).to_native())
+    exact = dp.random_allocation(dp.gaussian(sigma), t)
+    for eps in (0.5, 1.0):
+        assert abs(mc.delta_at(eps) - exact.delta_at(eps)) < 0.05 * exact.delta_at(eps)

@@ -226,3 +226,18 @@ def test_balls_in_bins_monte_carlo_matches_random_allocation_for_the_identity_st
     exact = dp.random_allocation(dp.gaussian(sigma), t)
     for eps in (0.5, 1.0):
         assert abs(mc.delta_at(eps) - exact.delta_at(eps)) < 0.05 * exact.delta_at(eps)
+
+
+def test_accountant_front_ends_agree_where_their_definitions_coincide():
+    from opaque_b200.dpftrl import accounting as fa, identity_strategy
+    from opaque_b200.dpsgd import accounting as dp
+    g, q, n, delta = dp.gaussian(1.2), 0.05, 100, 1e-6
+    plain = (dp.poisson(g, q) * n).epsilon_at(delta)
+    assert math.isclose((dp.parallel_poisson(g, q, 1) * n).epsilon_at(delta), plain, rel_tol=1e-9)        # one worker
+    cyclic = fa.poisson(fa.mf_gaussian(1.2, identity_strategy(), n_steps=n), q, n_steps=n).epsilon_at(delta)
+    assert math.isclose(cyclic, plain, rel_tol=1e-9)                                                     # C = I, one band
+    capped = (dp.poisson(g, q, truncated_batch_size=80, dataset_size=1000) * n).epsilon_at(delta)
+    assert capped >= plain                                                                               # the cap costs privacy
+    assert math.isclose((dp.k_out_of_t(g, 1, 20) * 5).epsilon_at(delta), (dp.random_allocation(g, 20) * 5).epsilon_at(delta), rel_tol=1e-12)
+    every_step, composed = dp.k_out_of_t(g, 20, 20).epsilon_at(delta), (g * 20).epsilon_at(delta)
+    assert composed <= every_step <= composed * 1.002                                                    # k = t: plain composition

@@ -425,6 +425,8 @@ class FusedDPEngine:
         self.device = next(model.parameters()).device
         self.group = group or PeerGroup(self.device)
         named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        self._named_trainable = named
+        self._coverage_checked = False
         if not named:
             raise ValueError("the model has no trainable parameters")
         if isinstance(clipping_norm, Mapping):
@@ -506,9 +508,23 @@ class FusedDPEngine:
     def _microbatch(self, loss_fn, sub: dict[str, torch.Tensor], mb: int):
         tokens = sub["input_ids"].shape[1] if "input_ids" in sub else 1
         cap = Capture(self, mb, tokens)
+        if not self._coverage_checked:
+            for _, p in self._named_trainable:          # stale gradients of earlier, non-private use would trip the check below
+                p.grad = None
         with activate(cap):
             per_example = loss_fn(**sub)
             per_example.sum().backward()
+        if not self._coverage_checked:
+            # DP-aware layers hand their parameter gradients to the capture and return None to autograd.  A trainable
+            # parameter that autograd DID give a gradient was used through a plain op: its summed, unclipped gradient is
+            # not part of the norms and would never reach the optimizer, so the first microbatch refuses such a model.
+            self._coverage_checked = True
+            stray = [n for n, p in self._named_trainable if p.grad is not None]
+            if stray:
+                raise RuntimeError("these trainable parameters are used outside the DP-aware layers (Linear, Embedding, "
+                                   "RMSNorm, LayerNorm, LoRA, MoE experts) and cannot be clipped per example: "
+                                   + ", ".join(stray[:8]) + (" ..." if len(stray) > 8 else "")
+                                   + "; freeze them or use the reference engine")
         out = cap.finalize(self.clipping_norm, mode=self.clipping_mode, gamma=self.gamma)
         return per_example.detach().float(), out
 

@@ -240,3 +240,25 @@ def test_cuda_graph_microbatches_match_eager_execution_moe():
         norms.append(res.norms.clone())
     assert float((norms[0] - norms[1]).abs().max() / norms[0].max()) < 1e-3
     assert float((flats[0] - flats[1]).norm() / flats[0].norm()) < 2e-3
+
+
+def test_trainable_parameter_outside_the_dp_layers_is_refused():
+    """A plain ``nn.Parameter`` used through an ordinary op gets a summed, unclipped gradient from autograd: refused."""
+    from opaque_b200.engine.fused import FusedDPEngine
+    from opaque_b200.models import LlamaConfig, LlamaForCausalLM, shift_labels
+    from opaque_b200.random import key
+    dev = torch.device("cuda", 0)
+
+    class WithStray(LlamaForCausalLM):
+        def __init__(self, cfg, **kw):
+            super().__init__(cfg, **kw)
+            self.stray_scale = torch.nn.Parameter(torch.ones(cfg.hidden_size, device=kw.get("device"), dtype=torch.bfloat16))
+
+        def hidden_states(self, input_ids, position_ids=None):
+            return super().hidden_states(input_ids, position_ids) * self.stray_scale
+
+    m = WithStray(LlamaConfig.tiny(), device=dev)
+    eng = FusedDPEngine(m, clipping_norm=1.0, noise_multiplier=0.0, normalize_by=1.0, key=key(0), microbatch_size=4)
+    ids = torch.randint(0, 256, (4, 64), device=dev)
+    with pytest.raises(RuntimeError, match="stray_scale"):
+        eng.accumulate(m.per_example_loss, {"input_ids": ids, "labels": shift_labels(ids, 1.0)})

@@ -171,7 +171,23 @@ class MoEExperts(nn.Module):
         self.down_proj = nn.Parameter(torch.empty(E, H, I, dtype=dtype, device=device).normal_(std=0.02))
 
     def forward(self, x2d, topk_idx, topk_w, batch, tokens):
+        if not ops.functional.kernels_enabled():
+            return self._dense(x2d, topk_idx, topk_w)
         return _Experts.apply(x2d, topk_idx, topk_w, self.gate_up_proj, self.down_proj, batch, tokens)
+
+    def _dense(self, x2d, topk_idx, topk_w):
+        """Plain-PyTorch form for ``plain_torch_ops()`` (the reference engine maps it over examples with ``vmap``, which
+        cannot pass through a custom autograd node or data-dependent gathers): every expert is evaluated for every token
+        and the routing weights, zero outside the top-k, select the result.  ``E / k`` times the arithmetic of the sorted
+        path — a reference, not a fast path."""
+        E, two_i, _ = self.gate_up_proj.shape
+        I = two_i // 2
+        hit = topk_idx.unsqueeze(-1) == torch.arange(E, device=topk_idx.device)                    # [T, k, E]; vmap-safe one-hot
+        route = (hit.to(topk_w.dtype) * topk_w.unsqueeze(-1)).sum(-2)                               # [T, E]
+        h = torch.einsum("th,efh->tef", x2d, self.gate_up_proj)
+        act = torch.nn.functional.silu(h[..., :I]) * h[..., I:]
+        y = torch.einsum("tei,ehi->teh", act, self.down_proj)
+        return (y * route.unsqueeze(-1).to(y.dtype)).sum(1)
 
 
 class SparseMoeBlock(nn.Module):

@@ -88,3 +88,27 @@ def test_lora_attach_through_the_patch_api():
     m = patches.apply_model_patches(hf, dtype=torch.float32, r=8, lora_alpha=16, target_modules=("q_proj", "v_proj"))
     names = [n for n, p in m.named_parameters() if p.requires_grad]
     assert names and all("lora_" in n for n in names) and any("q_proj" in n for n in names) and not any("k_proj" in n for n in names)
+
+
+@pytest.mark.parametrize("family", ["gemma2", "cohere", "glm4", "hunyuan_v1_moe"])
+def test_converted_families_train_through_the_trainer_on_the_reference_engine(family, tmp_path):
+    """Conversion output + ``DPTrainer`` + ``vmap`` per-example gradients: explicit capped attention, bias-free LayerNorm,
+    permuted rotary layout and the dense expert form all have to pass through ``torch.func``."""
+    from opaque_b200.transformers import DPTrainer, TrainingArguments
+    T = transformers
+    cfg, cls = {
+        "gemma2": (T.Gemma2Config(**COMMON, head_dim=16, sliding_window=8, query_pre_attn_scalar=16), T.Gemma2ForCausalLM),
+        "cohere": (T.CohereConfig(**COMMON, pad_token_id=0), T.CohereForCausalLM),
+        "glm4": (T.Glm4Config(**COMMON, head_dim=16, pad_token_id=0), T.Glm4ForCausalLM),
+        "hunyuan_v1_moe": (T.HunYuanMoEV1Config(**{**COMMON, "intermediate_size": 48}, head_dim=16, num_experts=6, moe_topk=2,
+                                                pad_token_id=0), T.HunYuanMoEV1ForCausalLM)}[family]
+    torch.manual_seed(0)
+    model = patches.apply_model_patches(cls(cfg).float(), dtype=torch.float32)
+    g = torch.Generator().manual_seed(0)
+    rows = [{"input_ids": torch.randint(0, 320, (24,), generator=g).tolist()} for _ in range(64)]
+    args = TrainingArguments(output_dir=str(tmp_path), per_device_train_batch_size=8, max_steps=2, learning_rate=1e-3,
+                             privacy_noise_multiplier=1.0, clipping_norm=1.0, use_cpu=True, save_steps=0, logging_steps=1)
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    out = DPTrainer(model=model, args=args, train_dataset=rows).train()
+    assert out["global_step"] == 2 and out["epsilon"] > 0
+    assert any(not torch.equal(p, before[n]) for n, p in model.named_parameters())

@@ -102,3 +102,24 @@ def test_models_work_under_the_vmap_reference_engine():
     (g, aux), _ = fn(trainable, ids, lab)
     assert aux.batch_size == 4 and torch.allclose(aux.loss_values, _ref_losses(m, ids, lab), atol=1e-5)
     assert all(torch.isfinite(v).all() for v in g.pytree.values())
+
+
+def test_moe_dense_reference_form_matches_the_sorted_form():
+    """``plain_torch_ops()`` switches the experts to the vmap-safe dense evaluation: same loss, same gradients."""
+    import torch
+    from opaque_b200.models import MoEConfig, MoEForCausalLM, shift_labels
+    from opaque_b200.ops.functional import plain_torch_ops
+    torch.manual_seed(0)
+    m = MoEForCausalLM(MoEConfig.tiny(), dtype=torch.float32)
+    ids = torch.randint(0, 500, (3, 32))
+    labels = shift_labels(ids, 1.0)
+    m.per_example_loss(ids, labels).sum().backward()
+    sorted_loss = m.per_example_loss(ids, labels).detach()
+    sorted_grads = {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}
+    m.zero_grad(set_to_none=True)
+    with plain_torch_ops():
+        dense = m.per_example_loss(ids, labels)
+        dense.sum().backward()
+    assert torch.allclose(dense.detach(), sorted_loss, atol=1e-5)
+    for n, g in sorted_grads.items():
+        assert torch.allclose(dict(m.named_parameters())[n].grad, g, atol=1e-5, rtol=1e-4), n

@@ -108,5 +108,62 @@ def under_differentiating_transform() -> bool:
         return False
 
 
-__all__ = ["empty_collate", "make_functional", "merge", "partition",
+class _Recompute(torch.autograd.Function):
+    """``fn(*inputs)`` whose backward pass recomputes the forward pass; usable under ``torch.func`` transforms."""
+    generate_vmap_rule = True
+
+    @staticmethod
+    def forward(fn, diff_mask, *inputs):
+        return fn(*inputs)
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        ctx.fn, ctx.diff_mask = inputs[0], inputs[1]
+        ctx.save_for_backward(*inputs[2:])
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        saved = ctx.saved_tensors
+        diff = [t for t, d in zip(saved, ctx.diff_mask) if d]
+
+        def of_diff(*primals):
+            it = iter(primals)
+            return ctx.fn(*[next(it) if d else t for t, d in zip(saved, ctx.diff_mask)])
+        _, pull = torch.func.vjp(of_diff, *diff)
+        grads = iter(pull(grad_out))
+        return (None, None, *[next(grads) if d else None for d in ctx.diff_mask])
+
+
+def functional_checkpoint(module: nn.Module, *args: Any) -> torch.Tensor:
+    """Activation checkpointing that works under ``vmap(grad(...))``: run ``module(*args)`` without keeping its
+    intermediates and recompute them in the backward pass.
+
+    ``torch.utils.checkpoint`` relies on saved-tensor hooks (or an autograd node without a batching rule), neither of
+    which ``torch.func`` supports.  Here every tensor argument and every trainable parameter of ``module`` (as currently
+    bound, e.g. by ``functional_call``) becomes an explicit input of one autograd node with a generated batching rule;
+    frozen parameters, non-tensor arguments and buffers are closed over.  The module must return one tensor.
+    Parity: packages/opaque-patches/src/opaque/api/patches/torch/checkpoint of the reference (checkpointing under the
+    per-example engine).
+    """
+    tensor_pos = [i for i, a in enumerate(args) if isinstance(a, torch.Tensor)]
+    names, params, fixed = [], [], {}
+    for n, p in module.named_parameters():
+        if p.requires_grad:
+            names.append(n)
+            params.append(p)
+        else:
+            fixed[n] = p
+    n_args = len(tensor_pos)
+
+    def pure(*flat):
+        call = list(args)
+        for i, t in zip(tensor_pos, flat[:n_args]):
+            call[i] = t
+        return torch.func.functional_call(module, {**fixed, **dict(zip(names, flat[n_args:]))}, tuple(call))
+    inputs = [args[i] for i in tensor_pos] + params
+    diff_mask = tuple(bool(t.is_floating_point()) for t in inputs)
+    return _Recompute.apply(pure, diff_mask, *inputs)
+
+
+__all__ = ["empty_collate", "functional_checkpoint", "make_functional", "merge", "partition",
            "under_differentiating_transform", "with_batch_dim"]

@@ -15,6 +15,7 @@ import torch
 from torch import nn
 
 from .. import ops
+from ..functional import functional_checkpoint
 from .layers import Embedding, LayerNorm, Linear, linear_cross_entropy, per_example_token_weights
 
 
@@ -89,6 +90,7 @@ class GPT2LMHeadModel(nn.Module):
         self.wpe = Embedding(cfg.n_positions, cfg.n_embd, dtype=dtype, device=device)
         self.h = nn.ModuleList(GPT2Block(cfg, dtype, device) for _ in range(cfg.n_layer))
         self.ln_f = LayerNorm(cfg.n_embd, cfg.layer_norm_epsilon, dtype=dtype, device=device)
+        self.activation_checkpointing = False      # set by the trainer's gradient_checkpointing
 
     def hidden_states(self, input_ids):
         B, T = input_ids.shape
@@ -96,7 +98,8 @@ class GPT2LMHeadModel(nn.Module):
         h = self.wte(input_ids) + self.wpe(pos)
         for blk in self.h:
             if getattr(self, "activation_checkpointing", False) and torch.is_grad_enabled():
-                h = torch.utils.checkpoint.checkpoint(blk, h, use_reentrant=False)
+                h = (torch.utils.checkpoint.checkpoint(blk, h, use_reentrant=False) if ops.functional.kernels_enabled()
+                     else functional_checkpoint(blk, h))          # torch.func transforms need the functional form
             else:
                 h = blk(h)
         return self.ln_f(h)

@@ -17,6 +17,7 @@ import torch
 from torch import nn
 
 from .. import ops
+from ..functional import functional_checkpoint
 from .layers import Embedding, LayerNorm, Linear, RMSNorm, linear_cross_entropy, per_example_token_weights
 
 
@@ -280,7 +281,10 @@ class LlamaForCausalLM(nn.Module):
             cos, sin = (self.rope_cos, self.rope_cos_local), (self.rope_sin, self.rope_sin_local)
         for layer in self.model.layers:
             if self.activation_checkpointing and torch.is_grad_enabled():
-                h = torch.utils.checkpoint.checkpoint(layer, h, cos, sin, position_ids, use_reentrant=False)
+                if ops.functional.kernels_enabled():
+                    h = torch.utils.checkpoint.checkpoint(layer, h, cos, sin, position_ids, use_reentrant=False)
+                else:                                     # torch.func transforms need the functional form
+                    h = functional_checkpoint(layer, h, cos, sin, position_ids)
             else:
                 h = layer(h, cos, sin, position_ids)
         h = self.model.norm(h)

@@ -22,6 +22,7 @@ from torch import nn
 from torch.autograd import Function
 
 from .. import ops
+from ..functional import functional_checkpoint
 from ..engine import fused
 from .layers import Embedding, Linear, RMSNorm, linear_cross_entropy, per_example_token_weights
 from .llama import LlamaAttention, LlamaConfig, LlamaMLP
@@ -246,13 +247,17 @@ class MoEForCausalLM(nn.Module):
         cos, sin = ops.rope_tables(cfg.head_dim or cfg.hidden_size // cfg.num_attention_heads, cfg.max_position_embeddings, cfg.rope_theta,
                                    device=device, scaling=cfg.rope_scaling)
         self.register_buffer("rope_cos", cos, persistent=False)
+        self.activation_checkpointing = False      # set by the trainer's gradient_checkpointing
         self.register_buffer("rope_sin", sin, persistent=False)
 
     def hidden_states(self, input_ids, position_ids=None):
         h = self.embed_tokens(input_ids)
         for layer in self.layers:
             if getattr(self, "activation_checkpointing", False) and torch.is_grad_enabled():
-                h = torch.utils.checkpoint.checkpoint(layer, h, self.rope_cos, self.rope_sin, position_ids, use_reentrant=False)
+                if ops.functional.kernels_enabled():
+                    h = torch.utils.checkpoint.checkpoint(layer, h, self.rope_cos, self.rope_sin, position_ids, use_reentrant=False)
+                else:
+                    h = functional_checkpoint(layer, h, self.rope_cos, self.rope_sin, position_ids)
             else:
                 h = layer(h, self.rope_cos, self.rope_sin, position_ids)
         return self.norm(h)

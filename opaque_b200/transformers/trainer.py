@@ -602,6 +602,16 @@ class DPTrainer:
         self._strategy = build_strategy(a.privacy_noise_mechanism, a.privacy_noise_mechanism_kwargs) \
             if a.privacy_noise_mechanism in MECHANISMS_DPFTRL else None
         self.engine_kind = self._resolve_engine()
+        if self.engine_kind == "reference":
+            # torch.func.grad under vmap supports neither saved-tensor hooks (offloading, torch.utils.checkpoint) nor the
+            # checkpoint autograd node.  The framework's own models switch to functional_checkpoint there; anything else
+            # is refused with the way out
+            if a.activation_offloading:
+                raise ValueError("activation_offloading needs the fused engine (dp_engine='fused' on a B200); on the "
+                                 "reference engine lower microbatch_size or use gradient_checkpointing")
+            if a.gradient_checkpointing and not hasattr(self.model, "activation_checkpointing"):
+                raise ValueError("gradient_checkpointing on the reference engine needs a model of opaque_b200.models (or a "
+                                 "converted Hugging Face model); lower microbatch_size instead")
         prefix = None
         runtime = None
         if resume:

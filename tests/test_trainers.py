@@ -227,3 +227,25 @@ def test_cpo_head_is_reference_free_and_matches_its_closed_form(tmp_path):
     tr = DPOTrainer(model=TinyLM(), args=cfg, train_dataset=rows)
     assert tr.ref_model is None and "ref_chosen_logps" not in tr.train_dataset[0]      # no reference pass at all
     assert tr.train()["global_step"] == 2
+
+
+def test_memory_options_on_the_reference_engine(tmp_path):
+    """Offloading is refused (torch.func has no saved-tensor hooks); checkpointing works for the framework's models
+    through ``functional_checkpoint`` and gives the same run as without it; foreign models are refused."""
+    from opaque_b200.models import GPT2Config, GPT2LMHeadModel, LlamaConfig, LlamaForCausalLM, MoEConfig, MoEForCausalLM
+    with pytest.raises(ValueError, match="fused engine"):
+        DPTrainer(model=TinyLM(), args=_args(tmp_path, save_steps=0, activation_offloading=True), train_dataset=_data()).train()
+    with pytest.raises(ValueError, match="opaque_b200.models"):
+        DPTrainer(model=TinyLM(), args=_args(tmp_path, save_steps=0, gradient_checkpointing=True), train_dataset=_data()).train()
+    rows = _data(48, 16, 200)
+    for make in (lambda: LlamaForCausalLM(LlamaConfig.tiny(), dtype=torch.float32),
+                 lambda: GPT2LMHeadModel(GPT2Config.tiny(), dtype=torch.float32),
+                 lambda: MoEForCausalLM(MoEConfig.tiny(), dtype=torch.float32)):
+        finals = []
+        for ck in (False, True):
+            torch.manual_seed(0)
+            model = make()
+            DPTrainer(model=model, args=_args(tmp_path / f"ck{ck}", save_steps=0, max_steps=2, gradient_checkpointing=ck),
+                      train_dataset=rows).train()
+            finals.append(torch.cat([p.detach().reshape(-1) for p in model.parameters()]))
+        assert torch.allclose(finals[0], finals[1], atol=1e-6), type(model).__name__

@@ -65,6 +65,7 @@ class LlamaConfig:
     # GLM-4 / Phi-4-mini: only the first head_dim * factor dimensions rotate.  The kernels rotate pairs (i, i + head_dim/2),
     # so a converted checkpoint has its q / k rows permuted accordingly (patches.rope_row_permutation)
     partial_rotary_factor: float = 1.0
+    attention_sinks: bool = False            # GPT-OSS: one learned logit per head joins every softmax and is then dropped
     # Cohere: LayerNorm without bias instead of RMSNorm, and attention and MLP both reading ONE normed input
     # (h + attn(n(h)) + mlp(n(h)))
     norm_type: str = "rms"                   # rms | layernorm
@@ -102,6 +103,7 @@ class LlamaAttention(nn.Module):
         self.o_proj = Linear(self.nh * hd, d, bias=cfg.attention_out_bias, dtype=dtype, device=device)
         self.window = cfg.layer_windows[layer_idx] if cfg.layer_windows is not None else cfg.sliding_window
         self.softcap = cfg.attn_logit_softcap
+        self.sinks = nn.Parameter(torch.zeros(self.nh, dtype=dtype, device=device)) if cfg.attention_sinks else None
         self.local_rope = cfg.local_rope_theta is not None and self.window is not None
         self.qk_full = cfg.qk_norm_full
         self.qk_after = cfg.qk_norm_after_rope
@@ -132,8 +134,8 @@ class LlamaAttention(nn.Module):
                 q, k = ops.rope_qk(q, k, cos, sin, pos)
         if self.q_norm is not None and self.qk_after:
             q, k = self.q_norm(q), self.k_norm(k)
-        if self.softcap:
-            # capped attention scores: no library attention kernel applies tanh between QK^T and the softmax, so the
+        if self.softcap or self.sinks is not None:
+            # capped attention scores / attention sinks: no library attention kernel applies tanh between QK^T and the softmax, so the
             # scores are formed explicitly ([B, heads, T, T] in fp32) — correct for every length, meant for short ones
             scale = self.scale if self.scale is not None else self.hd ** -0.5
             qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
@@ -141,13 +143,19 @@ class LlamaAttention(nn.Module):
                 kh = kh.repeat_interleave(self.nh // self.nkv, dim=1)
                 vh = vh.repeat_interleave(self.nh // self.nkv, dim=1)
             sc = torch.matmul(qh, kh.transpose(-1, -2)).float() * scale
-            sc = self.softcap * torch.tanh(sc / self.softcap)
+            if self.softcap:
+                sc = self.softcap * torch.tanh(sc / self.softcap)
             idx = torch.arange(T, device=x.device)
             keep = idx[:, None] >= idx[None, :]
             if self.window is not None:
                 keep = keep & (idx[:, None] - idx[None, :] < self.window)
             sc = sc.masked_fill(~keep, float("-inf"))
-            o = torch.matmul(torch.softmax(sc, dim=-1).to(vh.dtype), vh)
+            if self.sinks is not None:
+                sink = self.sinks.float().view(1, self.nh, 1, 1).expand(B, self.nh, T, 1)
+                probs = torch.softmax(torch.cat([sc, sink], dim=-1), dim=-1)[..., :-1]      # the sink takes mass, adds nothing
+            else:
+                probs = torch.softmax(sc, dim=-1)
+            o = torch.matmul(probs.to(vh.dtype), vh)
         elif self.window is not None and T > self.window:
             # sequences longer than the window: a banded causal mask (key j visible from query i when 0 <= i - j < window).
             # This takes the masked attention path of the library, not the causal flash path; shorter sequences never

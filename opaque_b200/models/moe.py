@@ -45,6 +45,14 @@ class MoEConfig:
     rope_scaling: dict | None = None
     dense_layers: tuple = ()                   # indices of layers whose MLP is a plain gated MLP instead of experts
     dense_intermediate_size: int | None = None
+    # GPT-OSS: router and expert biases, clamped gate * sigmoid(1.702 gate) * (up + 1) activation, attention sinks,
+    # output-projection bias and alternating sliding windows
+    router_bias: bool = False
+    expert_bias: bool = False
+    expert_act: str = "swiglu"                 # swiglu | gpt_oss
+    attention_sinks: bool = False
+    attention_out_bias: bool = False
+    layer_windows: tuple | None = None
     max_position_embeddings: int = 4096
     # family variants: Qwen-MoE has q/k/v biases, a sigmoid gate on the shared expert and its own shared width
     attention_bias: bool = False
@@ -64,6 +72,8 @@ class MoEConfig:
                            rope_theta=self.rope_theta, max_position_embeddings=self.max_position_embeddings,
                            attention_bias=self.attention_bias, head_dim=self.head_dim, qk_norm=self.qk_norm,
                            qk_norm_after_rope=self.qk_norm_after_rope, rope_scaling=self.rope_scaling,
+                           attention_sinks=self.attention_sinks, attention_out_bias=self.attention_out_bias,
+                           layer_windows=self.layer_windows, num_hidden_layers=self.num_hidden_layers,
                            intermediate_size=self.shared_intermediate_size or self.moe_intermediate_size * max(self.num_shared_experts, 1))
 
     @staticmethod
@@ -170,9 +180,19 @@ class MoEExperts(nn.Module):
         E, I, H = cfg.num_experts, cfg.moe_intermediate_size, cfg.hidden_size
         self.gate_up_proj = nn.Parameter(torch.empty(E, 2 * I, H, dtype=dtype, device=device).normal_(std=0.02))
         self.down_proj = nn.Parameter(torch.empty(E, H, I, dtype=dtype, device=device).normal_(std=0.02))
+        self.act = cfg.expert_act
+        if cfg.expert_bias:
+            self.gate_up_bias = nn.Parameter(torch.zeros(E, 2 * I, dtype=dtype, device=device))
+            self.down_bias = nn.Parameter(torch.zeros(E, H, dtype=dtype, device=device))
+        else:
+            self.gate_up_bias = self.down_bias = None
+        if self.act not in ("swiglu", "gpt_oss"):
+            raise ValueError(f"unknown expert_act {self.act!r}")
 
     def forward(self, x2d, topk_idx, topk_w, batch, tokens):
-        if not ops.functional.kernels_enabled():
+        # biased / clamped experts exist only in the dense form (every expert for every token): correct on both engines
+        # while the experts are frozen (LoRA on attention); the fused engine refuses to TRAIN them (they bypass its layers)
+        if not ops.functional.kernels_enabled() or self.gate_up_bias is not None or self.act != "swiglu":
             return self._dense(x2d, topk_idx, topk_w)
         return _Experts.apply(x2d, topk_idx, topk_w, self.gate_up_proj, self.down_proj, batch, tokens)
 
@@ -186,8 +206,16 @@ class MoEExperts(nn.Module):
         hit = topk_idx.unsqueeze(-1) == torch.arange(E, device=topk_idx.device)                    # [T, k, E]; vmap-safe one-hot
         route = (hit.to(topk_w.dtype) * topk_w.unsqueeze(-1)).sum(-2)                               # [T, E]
         h = torch.einsum("th,efh->tef", x2d, self.gate_up_proj)
-        act = torch.nn.functional.silu(h[..., :I]) * h[..., I:]
+        if self.gate_up_bias is not None:
+            h = h + self.gate_up_bias
+        if self.act == "gpt_oss":
+            gate, up = h[..., :I].clamp(max=7.0), h[..., I:].clamp(min=-7.0, max=7.0)
+            act = (up + 1.0) * gate * torch.sigmoid(1.702 * gate)
+        else:
+            act = torch.nn.functional.silu(h[..., :I]) * h[..., I:]
         y = torch.einsum("tei,ehi->teh", act, self.down_proj)
+        if self.down_bias is not None:
+            y = y + self.down_bias
         return (y * route.unsqueeze(-1).to(y.dtype)).sum(1)
 
 
@@ -195,7 +223,7 @@ class SparseMoeBlock(nn.Module):
     def __init__(self, cfg: MoEConfig, dtype, device):
         super().__init__()
         self.cfg = cfg
-        self.gate = Linear(cfg.hidden_size, cfg.padded_experts, dtype=dtype, device=device)
+        self.gate = Linear(cfg.hidden_size, cfg.padded_experts, bias=cfg.router_bias, dtype=dtype, device=device)
         self.experts = MoEExperts(cfg, dtype, device)
         self.shared_expert = LlamaMLP(cfg.attn_config(), dtype, device) if cfg.num_shared_experts > 0 else None
         self.shared_expert_gate = Linear(cfg.hidden_size, 8, dtype=dtype, device=device) \
@@ -222,7 +250,7 @@ class MoEDecoderLayer(nn.Module):
     def __init__(self, cfg: MoEConfig, dtype, device, layer_idx: int = 0):
         super().__init__()
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
-        self.self_attn = LlamaAttention(cfg.attn_config(), dtype, device)
+        self.self_attn = LlamaAttention(cfg.attn_config(), dtype, device, layer_idx)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
         if layer_idx in tuple(cfg.dense_layers):
             if not cfg.dense_intermediate_size:

@@ -27,11 +27,10 @@ _RUNTIME = {"patched": False}
 # the others are listed with the reason, so a conversion can never silently drop a feature of the architecture.
 LLAMA_LIKE = ("llama", "mistral", "ministral", "mellum", "qwen2", "qwen3", "gemma", "gemma2", "gemma3_text", "phi3", "granite",
               "smollm3", "olmo2", "olmo3", "exaone4", "glm4", "cohere", "cohere2")
-MOE_LIKE = ("mixtral", "qwen2_moe", "qwen3_moe", "hunyuan_v1_moe")
+MOE_LIKE = ("mixtral", "qwen2_moe", "qwen3_moe", "hunyuan_v1_moe", "gpt_oss")
 ROPE_INTERLEAVED = frozenset({"glm4", "cohere", "cohere2"})      # families that rotate the pairs (2i, 2i+1); q / k rows are permuted on conversion
 UNSUPPORTED = {
     "gemma3": "the multimodal wrapper; convert its text model (model_type gemma3_text)",
-    "gpt_oss": "attention sinks, clamped SwiGLU with biases, alternating sliding windows",
     "deepseek_v4": "multi-head latent attention",
     "qwen3_next": "gated delta-net layers", "qwen3_5_moe": "gated delta-net layers",
 }
@@ -198,6 +197,20 @@ def _build_moe(cfg: Any, opt: dict) -> torch.nn.Module:
     if mtype in ("qwen2_moe", "qwen3_moe"):        # a layer is sparse when it is not listed as MLP-only and falls on the sparse step
         only, step = set(_cfg_get(cfg, "mlp_only_layers") or ()), int(_cfg_get(cfg, "decoder_sparse_step", 1) or 1)
         dense = tuple(i for i in range(_cfg_get(cfg, "num_hidden_layers")) if i in only or (i + 1) % step != 0)
+    if mtype == "gpt_oss":
+        hd = _cfg_get(cfg, "head_dim") or _cfg_get(cfg, "hidden_size") // _cfg_get(cfg, "num_attention_heads")
+        c = MoEConfig(vocab_size=_cfg_get(cfg, "vocab_size"), hidden_size=_cfg_get(cfg, "hidden_size"),
+                      num_hidden_layers=_cfg_get(cfg, "num_hidden_layers"), num_attention_heads=_cfg_get(cfg, "num_attention_heads"),
+                      num_key_value_heads=_cfg_get(cfg, "num_key_value_heads") or _cfg_get(cfg, "num_attention_heads"),
+                      num_experts=_cfg_get(cfg, "num_local_experts"), moe_intermediate_size=_cfg_get(cfg, "intermediate_size"),
+                      num_shared_experts=0, attention_bias=bool(_cfg_get(cfg, "attention_bias", True)),
+                      attention_out_bias=bool(_cfg_get(cfg, "attention_bias", True)), head_dim=hd,
+                      num_experts_per_tok=_cfg_get(cfg, "num_experts_per_tok", 4), norm_topk_prob=True,       # softmax over the top-k logits
+                      rms_norm_eps=_cfg_get(cfg, "rms_norm_eps", 1e-5), rope_theta=_rope_theta(cfg, 150000.0),
+                      rope_scaling=_rope_scaling(cfg), router_bias=True, expert_bias=True, expert_act="gpt_oss",
+                      attention_sinks=True, layer_windows=_layer_windows(cfg),
+                      max_position_embeddings=_cfg_get(cfg, "max_position_embeddings", 4096))
+        return MoEForCausalLM(c, dtype=opt.get("dtype", torch.bfloat16), device=opt.get("device"))
     if mtype == "hunyuan_v1_moe":
         for name in ("num_experts", "moe_topk"):
             if not isinstance(_cfg_get(cfg, name), int):
@@ -257,6 +270,19 @@ def _convert_state_dict(mtype: str, sd: dict, out: torch.nn.Module) -> dict:
             continue
         if moe:
             k = k.removeprefix("model.")
+        if mtype == "gpt_oss":
+            k = k.replace(".mlp.router.", ".mlp.gate.")
+            if k.endswith("experts.gate_up_proj"):                 # [E, H, 2I] with gate / up interleaved -> [E, 2I, H], gate rows first
+                v = torch.cat([v[:, :, 0::2], v[:, :, 1::2]], dim=2).transpose(1, 2).contiguous()
+            elif k.endswith("experts.gate_up_proj_bias"):
+                k, v = k[: -len("gate_up_proj_bias")] + "gate_up_bias", torch.cat([v[:, 0::2], v[:, 1::2]], dim=1)
+            elif k.endswith("experts.down_proj"):                  # [E, I, H] -> [E, H, I]
+                v = v.transpose(1, 2).contiguous()
+            elif k.endswith("experts.down_proj_bias"):
+                k = k[: -len("down_proj_bias")] + "down_bias"
+            elif k.endswith("mlp.gate.bias"):
+                rows = out.config.padded_experts
+                v = torch.cat([v, v.new_zeros(rows - v.shape[0])]) if v.shape[0] < rows else v
         if mtype == "hunyuan_v1_moe":
             k = (k.replace(".query_layernorm.", ".q_norm.").replace(".key_layernorm.", ".k_norm.")
                  .replace(".mlp.gate.wg.", ".mlp.gate.").replace(".mlp.shared_mlp.", ".mlp.shared_expert."))

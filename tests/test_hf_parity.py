@@ -49,6 +49,10 @@ def _cases():
                                                           mlp_only_layers=[0], decoder_sparse_step=2), T.Qwen3MoeForCausalLM
     yield "hunyuan_v1_moe", T.HunYuanMoEV1Config(**{**COMMON, "intermediate_size": 48}, head_dim=16, num_experts=6, moe_topk=2,
                                                  pad_token_id=0), T.HunYuanMoEV1ForCausalLM
+    yield "gpt_oss", T.GptOssConfig(**{**COMMON, "num_hidden_layers": 4, "intermediate_size": 48}, head_dim=16, num_local_experts=6,
+                                    num_experts_per_tok=2, sliding_window=8, pad_token_id=0,
+                                    rope_parameters={"rope_type": "yarn", "rope_theta": 150000.0, "factor": 4.0, "beta_fast": 32.0,
+                                                     "beta_slow": 1.0, "truncate": False, "original_max_position_embeddings": 32}), T.GptOssForCausalLM
     yield "gpt2", T.GPT2Config(vocab_size=320, n_positions=128, n_embd=64, n_layer=2, n_head=4), T.GPT2LMHeadModel
     yield "mixtral", T.MixtralConfig(**COMMON, num_local_experts=6, num_experts_per_tok=2), T.MixtralForCausalLM
     yield "qwen2_moe", T.Qwen2MoeConfig(**COMMON, moe_intermediate_size=32, shared_expert_intermediate_size=48, num_experts=6,
@@ -59,6 +63,10 @@ def _cases():
 def test_converted_model_matches_hf_logits(name, cfg, cls):
     torch.manual_seed(0)
     hf = cls(cfg).eval().float()
+    with torch.no_grad():                                   # biases and attention sinks start at zero: make them count
+        for n, p in hf.named_parameters():
+            if n.endswith("bias") or "sinks" in n:
+                p.normal_(0.0, 0.2)
     ours = patches.apply_model_patches(hf, dtype=torch.float32).eval()
     ids = torch.randint(0, 320, (2, 24))
     with torch.no_grad():
@@ -75,8 +83,8 @@ def test_converted_model_matches_hf_logits(name, cfg, cls):
 
 
 def test_unsupported_families_are_refused_with_a_reason():
-    with pytest.raises(NotImplementedError, match="attention sinks"):
-        patches.apply_model_patches({"model_type": "gpt_oss"})
+    with pytest.raises(NotImplementedError, match="latent attention"):
+        patches.apply_model_patches({"model_type": "deepseek_v4"})
     with pytest.raises(NotImplementedError, match="per-head weights"):
         patches.apply_model_patches(transformers.CohereConfig(**COMMON, use_qk_norm=True))
     with pytest.raises(ValueError, match="no registered family"):

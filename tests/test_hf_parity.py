@@ -98,7 +98,7 @@ def test_lora_attach_through_the_patch_api():
     assert names and all("lora_" in n for n in names) and any("q_proj" in n for n in names) and not any("k_proj" in n for n in names)
 
 
-@pytest.mark.parametrize("family", ["gemma2", "cohere", "glm4", "hunyuan_v1_moe"])
+@pytest.mark.parametrize("family", ["gemma2", "cohere", "glm4", "hunyuan_v1_moe", "gpt_oss"])
 def test_converted_families_train_through_the_trainer_on_the_reference_engine(family, tmp_path):
     """Conversion output + ``DPTrainer`` + ``vmap`` per-example gradients: explicit capped attention, bias-free LayerNorm,
     permuted rotary layout and the dense expert form all have to pass through ``torch.func``."""
@@ -109,7 +109,9 @@ def test_converted_families_train_through_the_trainer_on_the_reference_engine(fa
         "cohere": (T.CohereConfig(**COMMON, pad_token_id=0), T.CohereForCausalLM),
         "glm4": (T.Glm4Config(**COMMON, head_dim=16, pad_token_id=0), T.Glm4ForCausalLM),
         "hunyuan_v1_moe": (T.HunYuanMoEV1Config(**{**COMMON, "intermediate_size": 48}, head_dim=16, num_experts=6, moe_topk=2,
-                                                pad_token_id=0), T.HunYuanMoEV1ForCausalLM)}[family]
+                                                pad_token_id=0), T.HunYuanMoEV1ForCausalLM),
+        "gpt_oss": (T.GptOssConfig(**{**COMMON, "intermediate_size": 48}, head_dim=16, num_local_experts=6, num_experts_per_tok=2,
+                                   sliding_window=8, pad_token_id=0), T.GptOssForCausalLM)}[family]
     torch.manual_seed(0)
     model = patches.apply_model_patches(cls(cfg).float(), dtype=torch.float32)
     g = torch.Generator().manual_seed(0)

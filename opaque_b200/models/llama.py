@@ -135,8 +135,9 @@ class LlamaAttention(nn.Module):
         if self.q_norm is not None and self.qk_after:
             q, k = self.q_norm(q), self.k_norm(k)
         if self.softcap or self.sinks is not None:
-            # capped attention scores / attention sinks: no library attention kernel applies tanh between QK^T and the softmax, so the
-            # scores are formed explicitly ([B, heads, T, T] in fp32) — correct for every length, meant for short ones
+            # capped attention scores / attention sinks: no library attention kernel applies tanh between QK^T and the
+            # softmax or appends a sink logit, so the scores are formed explicitly ([B, heads, T, T] in fp32) — correct for
+            # every length, meant for short ones
             scale = self.scale if self.scale is not None else self.hd ** -0.5
             qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
             if self.nkv != self.nh:

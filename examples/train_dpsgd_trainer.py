@@ -24,6 +24,17 @@ from opaque_b200.models import GPT2Config, GPT2LMHeadModel, LlamaConfig, LlamaFo
 from opaque_b200.transformers import DPTrainer, TrainingArguments
 
 
+# Named configurations (the benchmark configurations of this repository, per GPU; launch with torchrun for several GPUs).
+# Parity: the presets of examples/train_dpsgd_trainer.py:755-763 of the reference (there: one H200).
+PRESETS = {
+    "llama3-8b-lora-b200": dict(model="llama3-8b", lora=16, seq=1024, batch=64, noise_multiplier=0.7, clipping_norm=1.0, lr=2e-4),
+    "gpt2-full-b200": dict(model="gpt2", lora=0, seq=512, batch=128, noise_multiplier=0.8, clipping_norm=1.0, lr=1e-4),
+    "llama3.2-1b-blt-b200": dict(model="llama3.2-1b", lora=0, seq=1024, batch=32, target_epsilon=8.0, clipping_norm=1.0, lr=1e-4,
+                                 mechanism="mf_blt", sampling_mode="sequential"),
+    "tiny-cpu": dict(model="llama-tiny", lora=8, seq=64, batch=16, noise_multiplier=1.0),
+}
+
+
 def build_model(name: str, lora: int, device):
     dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
     if name == "gpt2":
@@ -51,7 +62,13 @@ def main() -> None:
     ap.add_argument("--sampling_mode", default=None)
     ap.add_argument("--lr", type=float, default=2e-4)
     ap.add_argument("--output_dir", default="")
+    ap.add_argument("--preset", default=None, choices=sorted(PRESETS), help="a named configuration; explicit flags still override")
     a = ap.parse_args()
+    if a.preset:
+        given = {act.dest for act in ap._actions for opt in act.option_strings if opt in sys.argv}
+        for k, v in PRESETS[a.preset].items():
+            if k not in given:
+                setattr(a, k, v)
 
     if int(os.environ.get("WORLD_SIZE", "1")) > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")

@@ -249,3 +249,19 @@ def test_memory_options_on_the_reference_engine(tmp_path):
                       train_dataset=rows).train()
             finals.append(torch.cat([p.detach().reshape(-1) for p in model.parameters()]))
         assert torch.allclose(finals[0], finals[1], atol=1e-6), type(model).__name__
+
+
+def test_sft_and_dpo_trainers_accept_a_moe_model_on_the_reference_engine(tmp_path):
+    """The experts' dense form and ``functional_checkpoint`` carry MoE models through ``vmap(grad)``."""
+    from opaque_b200.models import MoEConfig, MoEForCausalLM
+    g = torch.Generator().manual_seed(0)
+    pairs = [{"prompt_input_ids": torch.randint(0, 500, (4,), generator=g).tolist(),
+              "chosen_input_ids": torch.randint(0, 500, (5,), generator=g).tolist(),
+              "rejected_input_ids": torch.randint(0, 500, (3,), generator=g).tolist()} for _ in range(16)]
+    cfg = DPOConfig(output_dir=str(tmp_path / "dpo"), per_device_train_batch_size=4, max_steps=2, privacy_noise_multiplier=1.0,
+                    use_cpu=True, save_steps=0, learning_rate=1e-3)
+    assert DPOTrainer(model=MoEForCausalLM(MoEConfig.tiny(), dtype=torch.float32), args=cfg, train_dataset=pairs).train()["global_step"] == 2
+    rows = [{"input_ids": torch.randint(0, 500, (16,), generator=g).tolist(), "completion_mask": [0] * 6 + [1] * 10} for _ in range(32)]
+    scfg = SFTConfig(output_dir=str(tmp_path / "sft"), per_device_train_batch_size=4, max_steps=2, privacy_noise_multiplier=1.0,
+                     use_cpu=True, save_steps=0, gradient_checkpointing=True)
+    assert SFTTrainer(model=MoEForCausalLM(MoEConfig.tiny(), dtype=torch.float32), args=scfg, train_dataset=rows).train()["global_step"] == 2

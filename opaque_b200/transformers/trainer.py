@@ -308,12 +308,17 @@ def _is_retryable_oom(exc: BaseException) -> bool:
     return isinstance(exc, torch.OutOfMemoryError) or (isinstance(exc, RuntimeError) and "out of memory" in str(exc).lower())
 
 
-def default_per_example_loss(model_call: Callable[..., Any], example: Mapping[str, torch.Tensor]) -> torch.Tensor:
-    """Mean next-token NLL of ONE example (no batch axis), labels already aligned."""
+def default_per_example_loss(model_call: Callable[..., Any], example: Mapping[str, torch.Tensor],
+                             label_smoothing: float = 0.0) -> torch.Tensor:
+    """Mean next-token NLL of ONE example (no batch axis), labels already aligned; with ``label_smoothing`` the target
+    distribution is ``(1 − s)·one-hot + s·uniform`` (mean over the scored tokens, as ``torch.nn.functional.cross_entropy``)."""
     from ..alignment.sft import nll_loss
     ids = example["input_ids"].unsqueeze(0)
     logits = model_call(ids)
     logits = getattr(logits, "logits", logits)
+    if label_smoothing:
+        return torch.nn.functional.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), example["labels"].reshape(-1),
+                                                 ignore_index=-100, label_smoothing=float(label_smoothing))
     return nll_loss(logits, example["labels"].unsqueeze(0)).squeeze(0)
 
 
@@ -426,7 +431,7 @@ class DPTrainer:
         """Loss of ONE record (reference engine; runs under ``vmap``)."""
         if self.compute_loss_func is not None:
             return self.compute_loss_func(model_call, example)
-        return default_per_example_loss(model_call, example)
+        return default_per_example_loss(model_call, example, self.args.label_smoothing_factor)
 
     def compute_batch_per_example_loss(self, batch: Mapping[str, torch.Tensor]) -> torch.Tensor:
         """One loss per record of a batch (fused engine, evaluation)."""
@@ -438,12 +443,15 @@ class DPTrainer:
     # ---- set-up -----------------------------------------------------------------------------------
     def _resolve_engine(self) -> str:
         want = self.args.dp_engine
-        fused_ok = self.device.type == "cuda" and hasattr(self.model, "per_example_loss") and self.compute_loss_func is None
+        # label smoothing lives in the trainer's default loss, which only the reference engine calls
+        fused_ok = (self.device.type == "cuda" and hasattr(self.model, "per_example_loss") and self.compute_loss_func is None
+                    and not self.args.label_smoothing_factor)
         if fused_ok:
             from ..device import fused_kernels_available
             fused_ok = fused_kernels_available()
         if want == "fused" and not fused_ok:
-            raise RuntimeError("dp_engine='fused' needs a B200, the kernel library and a model with per_example_loss")
+            raise RuntimeError("dp_engine='fused' needs a B200, the kernel library, a model with per_example_loss and no "
+                               "label_smoothing_factor / compute_loss_func")
         return "fused" if (want in ("auto", "fused") and fused_ok) else "reference"
 
     def _build_sampler(self, n_local: int, steps: int, data_key: RngKey):
@@ -560,9 +568,6 @@ class DPTrainer:
         if a.full_determinism:
             torch.use_deterministic_algorithms(True, warn_only=True)
             os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
-        if a.label_smoothing_factor:
-            raise ValueError("label_smoothing_factor is not supported: pass a compute_loss_func that smooths, or use "
-                             "opaque_b200.ops.cross_entropy(label_smoothing=...) in the model's per_example_loss")
         inert = self.inert_arguments()
         if inert and self.is_world_process_zero():
             import warnings

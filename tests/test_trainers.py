@@ -205,8 +205,16 @@ def test_compatibility_arguments_are_applied_or_named(tmp_path):
     assert math.isclose(tr.evaluate(held_out)["eval_loss"], tr.state.best_metric, rel_tol=1e-5)   # the best weights are back
     pred = tr.predict(held_out)
     assert pred.predictions is None and "test_loss" in pred.metrics
-    with pytest.raises(ValueError):
-        DPTrainer(model=TinyLM(), args=_args(tmp_path / "ls", label_smoothing_factor=0.1), train_dataset=data).train()
+    # label smoothing: the trainer's default loss mixes in the uniform target (reference engine)
+    from opaque_b200.transformers.trainer import default_per_example_loss
+    model = TinyLM()
+    ex = {"input_ids": torch.tensor(data[0]["input_ids"]), "labels": torch.tensor(data[0]["input_ids"][1:] + [-100])}
+    plain, smooth = default_per_example_loss(model, ex), default_per_example_loss(model, ex, 0.1)
+    logp = torch.log_softmax(model(ex["input_ids"][None])[0, :-1].float(), -1)
+    want = 0.9 * float(plain) + 0.1 * float(-logp.mean())
+    assert math.isclose(float(smooth), want, rel_tol=1e-5)
+    out = DPTrainer(model=TinyLM(), args=_args(tmp_path / "ls", label_smoothing_factor=0.1, save_steps=0), train_dataset=data).train()
+    assert out["global_step"] == 6
 
 
 def test_cpo_head_is_reference_free_and_matches_its_closed_form(tmp_path):

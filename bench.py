@@ -17,9 +17,11 @@ on fewer GPUs pass ``--layers`` to truncate, which the JSON reports).
 
 Sampling: one global Poisson draw per step (same key on every rank) dealt out evenly over the ranks.  Set-up before the
 warm-up steps captures CUDA graphs (GPT-2) and visits every tail microbatch size once, then clears the gradient shard.
-``--impl restated`` runs the reference library's algorithm (vmap per-example gradients, NCCL all-reduce, host noise,
-tree-mapped AdamW-BC) written with this package's reference engine, as a same-box comparator; ``--impl reference`` would
-run the unmodified reference package and reports that it cannot be installed offline.
+``--impl reference`` runs the UNMODIFIED reference library (``baseline/_ref``, installed by
+``baseline/install_reference.sh``) on its own stock path — ``apply_model_patches`` → ``make_functional`` → ``clipped_grad``
+→ ``sum_gradients_`` → ``gaussian_noise`` → ``adamw`` — for the same metric and configuration (``baseline/reference_arm.py``;
+``optree`` / ``torchopt`` are small stand-ins and the LoRA factors a harness module, all declared in the JSON line).
+``--impl restated`` runs the same algorithm written with this package's own reference engine (context only).
 
   python bench.py [--gpus N --steps K --warmup W] [--config llama8b-lora|gpt2|llama1b-blt|moe|llama-tiny]
                   [--impl ours|restated|reference] [--microbatch M] [--per-gpu-batch B] [--accumulate auto|peer|local]
@@ -37,10 +39,6 @@ import sys
 import threading
 import time
 
-REFERENCE_UNAVAILABLE = ("the reference is a uv workspace of 10 wheels: the root distribution installs empty "
-                         "(--no-deps) and the member wheels need optree, torchopt, peft and a Rust/maturin build, "
-                         "none of which exist offline here")
-
 
 def parse() -> argparse.Namespace:
     ap = argparse.ArgumentParser()
@@ -48,7 +46,7 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "restated"],
-                    help="ours: fused engine; reference: the unmodified reference package (unavailable offline); restated: "
+                    help="ours: fused engine; reference: the unmodified reference package from baseline/_ref; restated: "
                          "the reference's algorithm (vmap per-example gradients, clip, NCCL all-reduce, host-generated "
                          "noise, functional AdamW-BC) written with this library's reference engine and plain PyTorch ops")
     ap.add_argument("--config", default="llama8b-lora", choices=["llama8b-lora", "gpt2", "llama1b-blt", "moe", "llama-tiny"])
@@ -191,7 +189,10 @@ def run_restated(args, model, dp, data, sampler, seq, per_gpu, mb, frac, vocab, 
 def main() -> None:
     args = parse()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        # the unmodified reference library on its own stock path; nothing of this package is imported on that arm
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+        import reference_arm
+        reference_arm.run(args)
         return
 
     import torch

@@ -3,6 +3,9 @@
   python bench_kernels.py                      # every case at its benchmark size
   python bench_kernels.py --case wgrad --small # one small launch set, sized for an ncu capture
   python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 bench_kernels.py --case wgrad-rs
+  python bench_kernels.py --impl reference     # the reference's own Triton / library kernels on the same shapes
+                                               # (unmodified code from baseline/_ref; nothing of this package is loaded)
+  python bench_kernels.py --case compare       # this package's kernels on exactly those shapes
 
 Each line is JSON: achieved TFLOP/s or GB/s and the fraction "of measured" peak, where the peaks come from
 MEASURED_PEAKS.json next to this file (cuBLAS bf16 burst and a STREAM-style copy), else the documented fallback
@@ -103,11 +106,140 @@ def fused_reduce_scatter_case():
     dist.destroy_process_group()
 
 
+COMPARE_SHAPES = {"rows": 16384, "hidden": 4096, "ffn": 14336, "vocab": 128256, "ce_rows": 4096, "lce_rows": 8192,
+                  "heads": 32, "kv_heads": 8, "head_dim": 128, "seq": 1024, "lora_r": 16}
+
+
+def _fwd_bwd(fn, *inputs):
+    """Forward, then backward of the summed output (gradients of every input that requires one)."""
+    out = fn(*inputs)
+    out = out[0] if isinstance(out, tuple) else out
+    out.float().sum().backward()
+    for t in inputs:
+        if isinstance(t, torch.Tensor):
+            t.grad = None
+
+
+def compare_cases(impl: str):
+    """One row per operation on COMPARE_SHAPES, for ``impl`` = ``ours`` (this package) or ``reference`` (the reference's
+    unmodified Triton / library kernels, packages/opaque-patches/src/opaque/api/patches/kernels/*.py).  Both arms time
+    the same algorithmic work with CUDA events after warm-up and with an L2-sized write between launches."""
+    S = COMPARE_SHAPES
+    dev = torch.device("cuda", 0)
+    tf_peak, bw_peak, tag = peaks()
+    flush = torch.zeros(64 * 1024 * 1024, device=dev)
+    if impl == "reference":
+        import sys
+        here = os.path.dirname(os.path.abspath(__file__))
+        sys.path[:0] = [os.path.join(here, "baseline", "_ref"), os.path.join(here, "baseline", "shims")]
+        from opaque.api.patches.kernels.cross_entropy import opaque_cross_entropy_loss
+        from opaque.api.patches.kernels.fused_add_rms_norm import opaque_fused_add_rms_norm
+        from opaque.api.patches.kernels.linear_cross_entropy import Opaque_LinearCrossEntropyLoss
+        from opaque.api.patches.kernels.lora import opaque_lora_w
+        from opaque.api.patches.kernels.rms_norm import opaque_rms_norm
+        from opaque.api.patches.kernels.rope_embedding import opaque_rope_qk
+        from opaque.api.patches.kernels.swiglu import opaque_swiglu
+        rms = lambda x, w: opaque_rms_norm(x, w, 1e-5)
+        add_rms = lambda x, r, w: opaque_fused_add_rms_norm(x, r, w, 1e-5)
+        swiglu = opaque_swiglu
+        ce = lambda z, lab: opaque_cross_entropy_loss(z, lab)
+        lora = lambda x, w, a, b: opaque_lora_w(x, w, a, b, 2.0)
+
+        def lce(h, w, lab):
+            return Opaque_LinearCrossEntropyLoss.apply(h, w, lab, -100, 0, 0.0, False)
+
+        def rope(q, k, cos, sin):       # the reference takes [B, heads, T, D]
+            return opaque_rope_qk(q, k, cos, sin)
+        rope_layout = "bhtd"
+    else:
+        from opaque_b200 import ops
+        from opaque_b200.engine.fused import lora_linear
+        from opaque_b200.models.layers import linear_cross_entropy
+        rms = lambda x, w: ops.rms_norm(x, w, 1e-5)
+        add_rms = lambda x, r, w: ops.fused_add_rms_norm(x, r, w, 1e-5)
+        swiglu = ops.swiglu
+        ce = lambda z, lab: ops.cross_entropy(z, lab)
+        lora = lambda x, w, a, b: lora_linear(x, w, None, a, b, 2.0)
+
+        def lce(h, w, lab):
+            return linear_cross_entropy(h, w, lab, torch.ones(lab.shape, device=lab.device))
+
+        def rope(q, k, cos, sin):
+            return ops.rope_qk(q, k, cos, sin)
+        rope_layout = "bthd"
+
+    def emit(name, ms, flops=None, bytes_=None):
+        row = {"impl": impl, "kernel": name, "ms": round(ms, 4)}
+        if flops:
+            row["tflops"] = round(flops / ms / 1e9, 1)
+            row["frac_" + tag.replace(" ", "_")] = round(flops / ms / 1e9 / tf_peak, 3)
+        if bytes_:
+            row["GBs"] = round(bytes_ / ms / 1e6, 1)
+            row["frac_" + tag.replace(" ", "_")] = round(bytes_ / ms / 1e6 / bw_peak, 3)
+        print(json.dumps(row), flush=True)
+
+    R, H, I, V = S["rows"], S["hidden"], S["ffn"], S["vocab"]
+    bf = dict(device=dev, dtype=torch.bfloat16)
+    x = torch.randn(R, H, **bf)
+    w = torch.ones(H, **bf)
+    emit(f"rms_norm fwd {R}x{H}", timeit(lambda: rms(x, w), 20, 5, flush), bytes_=2 * x.numel() * 2)
+    xg = x.clone().requires_grad_(True)
+    wg = w.clone().requires_grad_(True)
+    emit(f"rms_norm fwd+bwd (dx, dw) {R}x{H}", timeit(lambda: _fwd_bwd(rms, xg, wg), 20, 5, flush), bytes_=5 * x.numel() * 2)
+    res = torch.randn(R, H, **bf)
+    emit(f"fused add + rms_norm fwd {R}x{H}", timeit(lambda: add_rms(x, res, w), 20, 5, flush), bytes_=4 * x.numel() * 2)
+    g, u = torch.randn(R, I, **bf), torch.randn(R, I, **bf)
+    emit(f"swiglu fwd {R}x{I}", timeit(lambda: swiglu(g, u), 20, 5, flush), bytes_=3 * g.numel() * 2)
+    gg, ug = g.clone().requires_grad_(True), u.clone().requires_grad_(True)
+    emit(f"swiglu fwd+bwd {R}x{I}", timeit(lambda: _fwd_bwd(swiglu, gg, ug), 20, 5, flush), bytes_=8 * g.numel() * 2)
+    del g, u, gg, ug
+    B, T, nh, nkv, hd = R // S["seq"], S["seq"], S["heads"], S["kv_heads"], S["head_dim"]
+    if rope_layout == "bhtd":
+        q, k = torch.randn(B, nh, T, hd, **bf), torch.randn(B, nkv, T, hd, **bf)
+        inv = 1.0 / (500000.0 ** (torch.arange(0, hd, 2, device=dev).float() / hd))
+        ang = torch.outer(torch.arange(T, device=dev).float(), inv)
+        cos, sin = ang.cos().bfloat16(), ang.sin().bfloat16()
+    else:
+        q, k = torch.randn(B, T, nh, hd, **bf), torch.randn(B, T, nkv, hd, **bf)
+        cos, sin = ops.rope_tables(hd, T, 500000.0, device=dev)
+    emit(f"rope q,k fwd {B}x{T}x({nh}+{nkv})x{hd}", timeit(lambda: rope(q, k, cos, sin), 20, 5, flush),
+         bytes_=2 * (q.numel() + k.numel()) * 2)
+    CR = S["ce_rows"]
+    z = torch.randn(CR, V, **bf)
+    lab = torch.randint(0, V, (CR,), device=dev)
+    zg = z.clone().requires_grad_(True)
+    emit(f"cross_entropy loss + dlogits {CR}x{V}", timeit(lambda: _fwd_bwd(ce, zg, lab), 10, 3, flush), bytes_=2 * z.numel() * 2)
+    del z, zg
+    LR = S["lce_rows"]
+    h = (torch.randn(LR, H, **bf) * 0.5).requires_grad_(True)
+    wv = (torch.randn(V, H, **bf) * 0.02)
+    labl = torch.randint(0, V, (LR,), device=dev)
+    # fused linear + cross-entropy with a frozen head: logits (forward) and dlogits @ W (backward) = 4 R V H FLOPs as
+    # the algorithmic minimum (a recomputing backward does 6)
+    emit(f"linear + cross_entropy fwd+bwd (frozen head) {LR}x{H}x{V}", timeit(lambda: _fwd_bwd(lce, h, wv, labl), 5, 2, flush),
+         flops=4.0 * LR * V * H)
+    del h, wv
+    xl = torch.randn(R, H, **bf).requires_grad_(True)
+    wl = torch.randn(H, H, **bf) * 0.02
+    la = torch.randn(S["lora_r"], H, **bf).requires_grad_(True)
+    lb = torch.randn(H, S["lora_r"], **bf).requires_grad_(True)
+    emit(f"LoRA linear fwd (frozen W + r{S['lora_r']}) {R}x{H}x{H}", timeit(lambda: lora(xl, wl, la, lb), 20, 5, flush),
+         flops=2.0 * R * H * H)
+    emit(f"LoRA linear fwd+bwd (dx, dA, dB summed over rows) {R}x{H}x{H}", timeit(lambda: _fwd_bwd(lora, xl, wl, la, lb), 20, 5, flush),
+         flops=4.0 * R * H * H)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default="all")
     ap.add_argument("--small", action="store_true", help="one or two launches of a small case (for ncu)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"],
+                    help="reference: time the reference's unmodified kernels (baseline/_ref) on the comparison shapes")
     args = ap.parse_args()
+    if args.impl == "reference":
+        return compare_cases("reference")
+    if args.case == "compare":
+        return compare_cases("ours")
     if args.case == "wgrad-rs":
         return fused_reduce_scatter_case()
     from opaque_b200 import ops

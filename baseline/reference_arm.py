@@ -190,7 +190,9 @@ def run(args) -> None:
     model.train()
     # the reference's stock configuration for a run whose only consumer of the forward output is the loss
     # (examples/train_dpsgd.py:1134-1136): Triton kernels and the fused linear-cross-entropy on CUDA
-    apply_model_patches(model, kernels=use_cuda, fused_linear_cross_entropy=use_cuda)
+    # (its fused linear-CE forward reads ``self.model`` and so exists for the Llama-shaped families only: GPT-2 keeps the
+    # kernel patches without it)
+    apply_model_patches(model, kernels=use_cuda, fused_linear_cross_entropy=use_cuda and args.config != "gpt2")
     fmodel, trainable, frozen = make_functional(model, disable_autograd_tracking=True, partition_trainable=True)
     cut = int(seq * (1.0 - frac))
 

@@ -110,14 +110,12 @@ COMPARE_SHAPES = {"rows": 16384, "hidden": 4096, "ffn": 14336, "vocab": 128256, 
                   "heads": 32, "kv_heads": 8, "head_dim": 128, "seq": 1024, "lora_r": 16}
 
 
-def _fwd_bwd(fn, *inputs):
-    """Forward, then backward of the summed output (gradients of every input that requires one)."""
+def _fwd_bwd(fn, *inputs, dy=None):
+    """Forward, then the gradients of every input that requires one for the fixed output gradient ``dy``."""
     out = fn(*inputs)
     out = out[0] if isinstance(out, tuple) else out
-    out.float().sum().backward()
-    for t in inputs:
-        if isinstance(t, torch.Tensor):
-            t.grad = None
+    wrt = [t for t in inputs if isinstance(t, torch.Tensor) and t.requires_grad]
+    torch.autograd.grad(out, wrt, dy if dy is not None else torch.ones_like(out))
 
 
 def compare_cases(impl: str):
@@ -143,7 +141,7 @@ def compare_cases(impl: str):
         add_rms = lambda x, r, w: opaque_fused_add_rms_norm(x, r, w, 1e-5)
         swiglu = opaque_swiglu
         ce = lambda z, lab: opaque_cross_entropy_loss(z, lab)
-        lora = lambda x, w, a, b: opaque_lora_w(x, w, a, b, 2.0)
+        lora = lambda x, w, a, b: opaque_lora_w(x, w, a.t(), b.t(), 2.0)       # the reference takes A [in, r] and B [r, out]
 
         def lce(h, w, lab):
             return Opaque_LinearCrossEntropyLoss.apply(h, w, lab, -100, 0, 0.0, False)
@@ -184,15 +182,16 @@ def compare_cases(impl: str):
     w = torch.ones(H, **bf)
     emit(f"rms_norm fwd {R}x{H}", timeit(lambda: rms(x, w), 20, 5, flush), bytes_=2 * x.numel() * 2)
     xg = x.clone().requires_grad_(True)
-    wg = w.clone().requires_grad_(True)
-    emit(f"rms_norm fwd+bwd (dx, dw) {R}x{H}", timeit(lambda: _fwd_bwd(rms, xg, wg), 20, 5, flush), bytes_=5 * x.numel() * 2)
+    dyx = torch.randn(R, H, **bf)
+    emit(f"rms_norm fwd+bwd (dx; frozen weight) {R}x{H}", timeit(lambda: _fwd_bwd(rms, xg, w, dy=dyx), 20, 5, flush), bytes_=5 * x.numel() * 2)
     res = torch.randn(R, H, **bf)
     emit(f"fused add + rms_norm fwd {R}x{H}", timeit(lambda: add_rms(x, res, w), 20, 5, flush), bytes_=4 * x.numel() * 2)
     g, u = torch.randn(R, I, **bf), torch.randn(R, I, **bf)
     emit(f"swiglu fwd {R}x{I}", timeit(lambda: swiglu(g, u), 20, 5, flush), bytes_=3 * g.numel() * 2)
     gg, ug = g.clone().requires_grad_(True), u.clone().requires_grad_(True)
-    emit(f"swiglu fwd+bwd {R}x{I}", timeit(lambda: _fwd_bwd(swiglu, gg, ug), 20, 5, flush), bytes_=8 * g.numel() * 2)
-    del g, u, gg, ug
+    dyh = torch.randn(R, I, **bf)
+    emit(f"swiglu fwd+bwd {R}x{I}", timeit(lambda: _fwd_bwd(swiglu, gg, ug, dy=dyh), 20, 5, flush), bytes_=8 * g.numel() * 2)
+    del g, u, gg, ug, dyh
     B, T, nh, nkv, hd = R // S["seq"], S["seq"], S["heads"], S["kv_heads"], S["head_dim"]
     if rope_layout == "bhtd":
         q, k = torch.randn(B, nh, T, hd, **bf), torch.randn(B, nkv, T, hd, **bf)
@@ -208,7 +207,12 @@ def compare_cases(impl: str):
     z = torch.randn(CR, V, **bf)
     lab = torch.randint(0, V, (CR,), device=dev)
     zg = z.clone().requires_grad_(True)
-    emit(f"cross_entropy loss + dlogits {CR}x{V}", timeit(lambda: _fwd_bwd(ce, zg, lab), 10, 3, flush), bytes_=2 * z.numel() * 2)
+    emit(f"cross_entropy loss + dlogits (autograd op, logits kept) {CR}x{V}", timeit(lambda: _fwd_bwd(ce, zg, lab), 10, 3, flush),
+         bytes_=2 * z.numel() * 2)
+    if impl == "ours":
+        from opaque_b200.ops.functional import cross_entropy_fused_
+        emit(f"cross_entropy loss + dlogits in place (one pass, as the engine calls it) {CR}x{V}",
+             timeit(lambda: cross_entropy_fused_(z, lab), 10, 3, flush), bytes_=2 * z.numel() * 2)
     del z, zg
     LR = S["lce_rows"]
     h = (torch.randn(LR, H, **bf) * 0.5).requires_grad_(True)
@@ -216,8 +220,10 @@ def compare_cases(impl: str):
     labl = torch.randint(0, V, (LR,), device=dev)
     # fused linear + cross-entropy with a frozen head: logits (forward) and dlogits @ W (backward) = 4 R V H FLOPs as
     # the algorithmic minimum (a recomputing backward does 6)
-    emit(f"linear + cross_entropy fwd+bwd (frozen head) {LR}x{H}x{V}", timeit(lambda: _fwd_bwd(lce, h, wv, labl), 5, 2, flush),
-         flops=4.0 * LR * V * H)
+    def lce_step():
+        out = lce(h, wv, labl)
+        torch.autograd.grad(out.sum() if out.ndim else out, [h])
+    emit(f"linear + cross_entropy fwd+bwd (frozen head) {LR}x{H}x{V}", timeit(lce_step, 5, 2, flush), flops=4.0 * LR * V * H)
     del h, wv
     xl = torch.randn(R, H, **bf).requires_grad_(True)
     wl = torch.randn(H, H, **bf) * 0.02
@@ -225,8 +231,31 @@ def compare_cases(impl: str):
     lb = torch.randn(H, S["lora_r"], **bf).requires_grad_(True)
     emit(f"LoRA linear fwd (frozen W + r{S['lora_r']}) {R}x{H}x{H}", timeit(lambda: lora(xl, wl, la, lb), 20, 5, flush),
          flops=2.0 * R * H * H)
-    emit(f"LoRA linear fwd+bwd (dx, dA, dB summed over rows) {R}x{H}x{H}", timeit(lambda: _fwd_bwd(lora, xl, wl, la, lb), 20, 5, flush),
+    dyl = torch.randn(R, H, **bf)
+    emit(f"LoRA linear fwd+bwd (dx, dA, dB summed over rows) {R}x{H}x{H}", timeit(lambda: _fwd_bwd(lora, xl, wl, la, lb, dy=dyl), 20, 5, flush),
          flops=4.0 * R * H * H)
+    if impl == "ours":
+        # the dense products of the model path on CTA pairs, beside the library GEMM on the same shapes
+        st = ops.StatusWord(dev)
+        for M, N, K in [(16384, 4096, 4096), (16384, 14336, 4096), (16384, 4096, 14336), (16384, 6144, 4096)]:
+            xx = torch.randn(M, K, **bf)
+            ww = torch.randn(N, K, **bf) * 0.02
+            fl = 2.0 * M * N * K
+            emit(f"gemm x W^T, CTA pairs {M}x{N}x{K}", timeit(lambda: ops.gemm_pair(xx, ww, status=st), 20, 5, flush), flops=fl)
+            emit(f"gemm x W^T, single CTA {M}x{N}x{K}", timeit(lambda: ops.gemm(xx, ww, status=st, kernel="single"), 20, 5, flush), flops=fl)
+            emit(f"library x W^T {M}x{N}x{K}", timeit(lambda: torch.matmul(xx, ww.t()), 20, 5, flush), flops=fl)
+            wk = ww.t().contiguous()
+            emit(f"gemm dY W ([K,N] operand), CTA pairs {M}x{N}x{K}", timeit(lambda: ops.gemm_pair(xx, wk, b_layout="kn", status=st), 20, 5, flush), flops=fl)
+            emit(f"library dY W {M}x{N}x{K}", timeit(lambda: torch.matmul(xx, wk), 20, 5, flush), flops=fl)
+            del xx, ww, wk
+        M, I, K = 16384, 14336, 4096
+        xx, wg_, wu_ = torch.randn(M, K, **bf), torch.randn(I, K, **bf) * 0.02, torch.randn(I, K, **bf) * 0.02
+        fl = 4.0 * M * I * K
+        emit(f"gate+up GEMM with SwiGLU epilogue (h, gate, up stored) {M}x2x{I}x{K}", timeit(lambda: ops.gemm_glu(xx, wg_, wu_, status=st), 10, 3, flush), flops=fl)
+        emit(f"gate+up GEMM with SwiGLU epilogue (h only) {M}x2x{I}x{K}", timeit(lambda: ops.gemm_glu(xx, wg_, wu_, save_preact=False, status=st), 10, 3, flush), flops=fl)
+        emit(f"library gate, up GEMMs + SwiGLU kernel {M}x2x{I}x{K}", timeit(lambda: ops.swiglu(torch.matmul(xx, wg_.t()), torch.matmul(xx, wu_.t())), 10, 3, flush), flops=fl)
+        if st.read():
+            raise SystemExit(f"a device wait timed out (status {st.read()})")
 
 
 def main():

@@ -210,17 +210,108 @@ def ghost_norm(a: torch.Tensor | None, g: torch.Tensor, norm2: torch.Tensor, tok
     lib.check(rc, "ghost_norm")
 
 
+PAIR_GEMM = True          # dense (ungrouped) products run on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2)
+
+
+def _check_b(b: torch.Tensor, layout: str, K: int, what: str) -> int:
+    if b.ndim != 2 or b.stride(1) != 1:
+        raise ValueError(f"{what} must be a row-major 2-D matrix")
+    kn = layout == "kn"
+    if (b.shape[0] if kn else b.shape[1]) != K:
+        raise ValueError(f"{what}: inner dimensions differ")
+    return b.shape[1] if kn else b.shape[0]
+
+
+def gemm_pair(a: torch.Tensor, b: torch.Tensor, *, b_layout: str = "nk", a2: torch.Tensor | None = None,
+              b2: torch.Tensor | None = None, b2_layout: str = "nk", bias: torch.Tensor | None = None,
+              out: torch.Tensor | None = None, status: StatusWord | None = None,
+              wait_budget_s: float = DEFAULT_WAIT_BUDGET_S) -> torch.Tensor:
+    """``a @ op(b) + a2 @ op(b2) + bias`` with two CTAs per 256 x 256 accumulator tile (bf16 in/out, fp32 accumulation).
+
+    Layouts as in :func:`gemm`; the second segment has its own layout, so ``dX = dG·Wg + dU·Wu`` (both weights
+    stored ``[K, N]`` from the product's point of view) and the LoRA data gradient ``dY·W + q·A`` are one launch each.
+    """
+    _need_bf16(a, b)
+    if a.ndim != 2 or a.stride(1) != 1:
+        raise ValueError("a must be a row-major 2-D matrix")
+    M, K = a.shape
+    N = _check_b(b, b_layout, K, "b")
+    K2 = 0
+    if a2 is not None:
+        _need_bf16(a2, b2)
+        if a2.ndim != 2 or a2.shape[0] != M or a2.stride(1) != 1:
+            raise ValueError("second segment: a2 must be [M, K2] row-major")
+        K2 = a2.shape[1]
+        if _check_b(b2, b2_layout, K2, "b2") != N:
+            raise ValueError("second segment: b2 must cover the same N")
+    if bias is not None:
+        _need_bf16(bias)
+        if bias.numel() != N or not bias.is_contiguous():
+            raise ValueError("bias must hold N contiguous values")
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    elif out.shape != (M, N) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        raise ValueError("out must be a row-major bf16 [M, N] matrix")
+    rc = lib.load().ob_gemm_pair(
+        a.data_ptr(), b.data_ptr(), None, lib.ptr(a2), lib.ptr(b2), None, lib.ptr(bias), out.data_ptr(), None, None,
+        M, N, K, K2, a.stride(0), b.stride(0), a2.stride(0) if a2 is not None else 0,
+        b2.stride(0) if b2 is not None else 0, out.stride(0), int(b_layout == "kn"), int(b2_layout == "kn"), 0, 0,
+        status.ptr() if status else None, wait_budget_s, lib.sm_count(), lib.stream())
+    lib.check(rc, "gemm_pair")
+    return out
+
+
+_GLU_ACT = {"silu": 0, "gelu": 1, "gelu_pytorch_tanh": 2, "gelu_tanh": 2}
+
+
+def gemm_glu(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *, act: str = "silu", save_preact: bool = True,
+             status: StatusWord | None = None, wait_budget_s: float = DEFAULT_WAIT_BUDGET_S):
+    """Gated-MLP up-projection in ONE launch: ``act(a W_gᵀ) * (a W_uᵀ)`` with both products in one accumulator tile.
+
+    ``w_gate`` and ``w_up`` are ``[I, K]`` as stored.  Returns ``(h, gate, up)``; ``gate`` / ``up`` (the bf16
+    pre-activations the backward pass needs) are ``None`` with ``save_preact=False``.
+    """
+    _need_bf16(a, w_gate, w_up)
+    if a.ndim != 2 or a.stride(1) != 1 or w_gate.ndim != 2 or w_gate.shape != w_up.shape or w_gate.stride(1) != 1 \
+            or w_up.stride(1) != 1 or w_gate.stride(0) != w_up.stride(0) or w_gate.shape[1] != a.shape[1]:
+        raise ValueError("gemm_glu: a [M, K] and w_gate, w_up [I, K] row-major with equal pitch")
+    M, K = a.shape
+    inter = w_gate.shape[0]
+    h = torch.empty(M, inter, dtype=torch.bfloat16, device=a.device)
+    g = torch.empty_like(h) if save_preact else None
+    u = torch.empty_like(h) if save_preact else None
+    rc = lib.load().ob_gemm_pair(
+        a.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), None, None, None, None, h.data_ptr(), lib.ptr(g), lib.ptr(u),
+        M, 2 * inter, K, 0, a.stride(0), w_gate.stride(0), 0, 0, h.stride(0), 0, 0, 1, _GLU_ACT[act],
+        status.ptr() if status else None, wait_budget_s, lib.sm_count(), lib.stream())
+    lib.check(rc, "gemm_glu")
+    return h, g, u
+
+
+def gemm_glu_ref(a, w_gate, w_up, *, act="silu"):
+    """fp32 oracle of :func:`gemm_glu` (returns ``h`` only)."""
+    g, u = a.float() @ w_gate.float().t(), a.float() @ w_up.float().t()
+    if act == "silu":
+        return torch.nn.functional.silu(g) * u
+    return torch.nn.functional.gelu(g, approximate="tanh" if "tanh" in act else "none") * u
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, b_layout: str = "nk", a2: torch.Tensor | None = None,
          b2: torch.Tensor | None = None, bias: torch.Tensor | None = None, group_offs: torch.Tensor | None = None,
          out: torch.Tensor | None = None, status: StatusWord | None = None,
-         wait_budget_s: float = DEFAULT_WAIT_BUDGET_S) -> torch.Tensor:
+         wait_budget_s: float = DEFAULT_WAIT_BUDGET_S, kernel: str = "auto") -> torch.Tensor:
     """``a @ op(b) + a2 @ b2ᵀ + bias`` on the tcgen05 path (bf16 in/out, fp32 accumulation).
 
     ``b_layout="nk"``: ``b`` is ``[N, K]`` (a weight matrix as stored; ``op(b) = bᵀ``);  ``"kn"``: ``b`` is ``[K, N]``
     (``op(b) = b`` — data gradients ``dY @ W`` without a transposed copy).  ``a2 [M, r]``, ``b2 [N, r]`` add a
     low-rank segment accumulated in the same tile (LoRA-fused linear).  With ``group_offs`` (int32 ``[E + 1]`` row
     offsets, rows sorted by group) ``b`` is ``[E, N, K]`` / ``[E, K, N]`` and rows of group e use slab e (MoE experts).
+    ``kernel``: ``"pair"`` (two CTAs per 256 x 256 tile), ``"single"`` (one CTA per 128 x 256 tile) or ``"auto"``
+    (pairs for ungrouped products while :data:`PAIR_GEMM` is on; grouped products always run on single CTAs).
     """
+    if group_offs is None and (kernel == "pair" or (kernel == "auto" and PAIR_GEMM)):
+        return gemm_pair(a, b, b_layout=b_layout, a2=a2, b2=b2, bias=bias, out=out, status=status,
+                         wait_budget_s=wait_budget_s)
     _need_bf16(a, b)
     if a.ndim != 2 or a.stride(1) != 1:
         raise ValueError("a must be a row-major 2-D matrix")
@@ -390,7 +481,7 @@ from .functional import (activation, cross_entropy, cross_entropy_ref, fused_add
                          layer_norm, merge_heads3, plain_torch_ops, rms_norm, rms_norm_ref, rope_qk, rope_qk_ref, rope_tables, rows_group_sum_, swiglu)
 
 __all__ = [
-    "gemm", "gemm_ref", "ghost_set_wide", "push_grad_", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_", "merge_heads3",
+    "gemm", "gemm_pair", "gemm_glu", "gemm_glu_ref", "gemm_ref", "ghost_set_wide", "push_grad_", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_", "merge_heads3",
     "DeviceWaitTimeout", "KernelLibraryError", "StatusWord", "clip_weighted_sum", "cross_entropy",
     "cross_entropy_ref", "embedding_wgrad", "fused_add_rms_norm", "geglu", "ghost_norm", "ghost_norm_ref", "glu_ref",
     "philox_normal_add_", "pick_block_n", "pick_splits", "rms_norm", "rms_norm_ref", "rope_qk", "rope_qk_ref",

@@ -31,6 +31,16 @@ int ob_gemm_tn(const void* a, const void* b, const void* a2, const void* b2, con
                long long ldo, int b_kn, const int* group_offs, int num_groups, int* status, double wait_budget_s,
                int num_sms, void* stream);
 
+// Dense GEMM on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles):  D = A op1(B) + A2 op2(B2) + bias.
+// b_kn / b2_kn = 1: that B operand is stored [K, N] row-major, 0: [N, K].  glu != 0: `b` holds the gate rows and `b_up`
+// the up rows of a gated MLP ([N/2, K] each; N counts both), out [M, N/2] = act(gate) * up (glu_act: 0 silu, 1 gelu erf,
+// 2 gelu tanh) and the optional out_gate / out_up receive the pre-activations.
+int ob_gemm_pair(const void* a, const void* b, const void* b_up, const void* a2, const void* b2, const void* b2_up,
+                 const void* bias, void* out, void* out_gate, void* out_up, long long rows_a, int N, int K1, int K2,
+                 long long lda, long long ldb, long long lda2, long long ldb2, long long ldo, int b_kn, int b2_kn, int glu,
+                 int glu_act, int* status, double wait_budget_s, int num_sms, void* stream);
+unsigned int ob_debug_idesc_bf16(int m, int n, int a_mn_major, int b_mn_major);
+
 // LayerNorm over the last dimension (bf16 in/out, fp32 statistics saved per row).
 int ob_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, long long rows,
                      int H, float eps, void* stream);

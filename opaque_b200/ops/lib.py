@@ -21,6 +21,7 @@ _SIGNATURES = {
     "ob_wgrad_clip_pe": [P, P, I, I, I, I, LL, LL, P, I, P, P, LL, LL, LL, I, P, D, I, P],
     "ob_ghost_norm": [P, P, P, I, I, I, I, LL, LL, P, P, P, LL, P, D, I, P],
     "ob_gemm_tn": [P, P, P, P, P, P, LL, I, I, I, LL, LL, LL, LL, LL, I, P, I, P, D, I, P],
+    "ob_gemm_pair": [P, P, P, P, P, P, P, P, P, P, LL, I, I, I, LL, LL, LL, LL, LL, I, I, I, I, P, D, I, P],
     "ob_layernorm_fwd": [P, P, P, P, P, P, LL, I, F, P],
     "ob_layernorm_bwd_dx": [P, P, P, P, P, P, LL, I, P],
     "ob_rows_group_sum": [P, P, P, P, I, I, I, LL, P, LL, I, P, LL, P],
@@ -67,6 +68,8 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int
+    lib.ob_debug_idesc_bf16.argtypes = [I, I, I, I]
+    lib.ob_debug_idesc_bf16.restype = c_uint
     return lib
 
 

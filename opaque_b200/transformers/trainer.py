@@ -461,8 +461,10 @@ class DPTrainer:
         kw = dict(a.sampling_kwargs)
         mode = a.sampling_mode
         rng = range(n_local)
+        cap = self._truncation_cap()
+        self._sampled_records = n_local          # the population one draw runs over (the accountant's dataset_size)
         if mode == "poisson":
-            return PoissonSampler(rng, q, n_steps=steps, truncated_batch_size=kw.get("truncated_batch_size"), key=data_key), q
+            return PoissonSampler(rng, q, n_steps=steps, truncated_batch_size=cap, key=data_key), q
         if mode == "random_allocation":
             bins = int(kw.get("num_bins", max(1, round(1 / q))))
             return RandomAllocationSampler(rng, bins, n_steps=steps, key=data_key), 1.0 / bins
@@ -471,7 +473,8 @@ class DPTrainer:
             return KOutOfTSampler(rng, int(kw.get("k", 1)), t, n_steps=steps, key=data_key), kw.get("k", 1) / t
         bands = int(a.privacy_noise_mechanism_kwargs.get("bands", a.privacy_noise_mechanism_kwargs.get("bandwidth", kw.get("bands", 1))))
         if mode == "cyclic_poisson":
-            return CyclicPoissonSampler(rng, min(1.0, q * bands), bands=bands, n_steps=steps, key=data_key), min(1.0, q * bands)
+            return CyclicPoissonSampler(rng, min(1.0, q * bands), bands=bands, n_steps=steps, key=data_key,
+                                        **({"truncated_batch_size": cap} if cap is not None else {})), min(1.0, q * bands)
         if mode == "b_min_sep":
             return BMinSepSampler(rng, bands, q, steps, key=data_key), q
         if mode == "balls_in_bins":
@@ -480,6 +483,24 @@ class DPTrainer:
         if mode == "sequential":
             return SequentialBatchSampler(rng, min(a.per_device_train_batch_size, n_local), n_steps=steps), q
         raise ValueError(mode)
+
+    def _truncation_cap(self) -> int | None:
+        """``sampling_kwargs['truncated_batch_size']`` (alias ``max_batch_size``): a hard cap on the Poisson batch.
+
+        Truncation changes the mechanism, so the cap is also handed to the accountant; sampling modes that cannot
+        truncate refuse the key instead of ignoring it (reference: trainer/_dp_trainer.py:4238-4296).
+        """
+        kw = self.args.sampling_kwargs if isinstance(self.args.sampling_kwargs, Mapping) else {}
+        raw = kw.get("truncated_batch_size", kw.get("max_batch_size"))
+        if raw is None:
+            return None
+        if self.args.sampling_mode not in ("poisson", "cyclic_poisson"):
+            raise ValueError(f"sampling_kwargs['truncated_batch_size'] applies to Poisson sampling only, not to "
+                             f"sampling_mode={self.args.sampling_mode!r}")
+        cap = int(raw)
+        if cap < 1:
+            raise ValueError("truncated_batch_size must be >= 1")
+        return cap
 
     def _participation(self, sampler, steps: int) -> tuple[int, int | None]:
         """(min_sep, max_participations) implied by the sampler for MF sensitivity."""
@@ -504,7 +525,12 @@ class DPTrainer:
                                     expected_batch_size=float(a.train_batch_size),
                                     num_groups=len(a.clipping_norm) if isinstance(a.clipping_norm, Mapping) else 1)
             if a.sampling_mode == "poisson":
-                return sgd_acc.poisson(g, q)      # disjoint shards: each record is sampled by one rank at rate q
+                # disjoint shards: each record is sampled by one rank at rate q; with a cap the truncated mechanism is
+                # accounted over the population that one draw runs over
+                cap = self._truncation_cap()
+                if cap is not None:
+                    return sgd_acc.poisson(g, q, truncated_batch_size=cap, dataset_size=int(self._sampled_records))
+                return sgd_acc.poisson(g, q)
             if a.sampling_mode == "random_allocation":
                 return acc.per_step(_EpochProcess(sgd_acc.random_allocation(g, sampler.num_bins), sampler.num_bins))
             if a.sampling_mode == "k_out_of_t":
@@ -514,13 +540,18 @@ class DPTrainer:
         ms, mp = self._participation(sampler, steps)
         inner = ftrl_acc.mf_gaussian(nm, strat, n_steps=steps, min_sep=ms, max_participations=mp)
         if a.sampling_mode in ("cyclic_poisson",):
-            return ftrl_acc.per_step(ftrl_acc.poisson(inner, q, n_steps=steps))
+            cap = self._truncation_cap()
+            extra = dict(truncated_batch_size=cap, dataset_size=int(self._sampled_records)) if cap is not None else {}
+            return ftrl_acc.per_step(ftrl_acc.poisson(inner, q, n_steps=steps, **extra))
         if a.sampling_mode == "b_min_sep" and a.sampling_kwargs.get("amplified", False):
             n_coef = len(np.trim_zeros(np.asarray(strat.coefficients(steps), float), "b"))
             if n_coef <= sampler.bands:          # Monte-Carlo accountant for the subsampled banded mechanism
                 return ftrl_acc.per_step(ftrl_acc.b_min_sep(ftrl_acc.mf_gaussian(nm, strat, n_steps=steps), bands=sampler.bands,
                                                            n_steps=steps, sampling_prob=sampler.sampling_prob))
         if a.sampling_mode == "poisson" and a.privacy_noise_mechanism == "mf_identity":
+            cap = self._truncation_cap()
+            if cap is not None:
+                return sgd_acc.poisson(sgd_acc.gaussian(nm), q, truncated_batch_size=cap, dataset_size=int(self._sampled_records))
             return sgd_acc.poisson(sgd_acc.gaussian(nm), q)
         return ftrl_acc.per_step(inner)
 

@@ -273,3 +273,23 @@ def test_sft_and_dpo_trainers_accept_a_moe_model_on_the_reference_engine(tmp_pat
     scfg = SFTConfig(output_dir=str(tmp_path / "sft"), per_device_train_batch_size=4, max_steps=2, privacy_noise_multiplier=1.0,
                      use_cpu=True, save_steps=0, gradient_checkpointing=True)
     assert SFTTrainer(model=MoEForCausalLM(MoEConfig.tiny(), dtype=torch.float32), args=scfg, train_dataset=rows).train()["global_step"] == 2
+
+
+def test_truncated_poisson_cap_reaches_the_accountant(tmp_path):
+    """A cap on the Poisson batch changes the mechanism: epsilon with the cap is the truncated accountant's, and is at
+    least the plain-Poisson epsilon; sampling modes that cannot truncate refuse the key."""
+    from opaque_b200.dpsgd import accounting as d
+    torch.manual_seed(0)
+    plain = DPTrainer(model=TinyLM(), args=_args(tmp_path / "p", save_steps=100), train_dataset=_data()).train()["epsilon"]
+    tr = DPTrainer(model=TinyLM(), args=_args(tmp_path / "t", save_steps=100, sampling_kwargs={"truncated_batch_size": 9}),
+                   train_dataset=_data())
+    capped = tr.train()["epsilon"]
+    want = (d.poisson(d.gaussian(1.0), 8 / 64, truncated_batch_size=9, dataset_size=64) * 6).epsilon_at(tr.target_delta)
+    assert math.isclose(capped, want, rel_tol=1e-9) and capped >= plain - 1e-12
+    assert tr.sampler.truncated_batch_size == 9
+    alias = DPTrainer(model=TinyLM(), args=_args(tmp_path / "a", save_steps=100, sampling_kwargs={"max_batch_size": 9}),
+                      train_dataset=_data()).train()["epsilon"]
+    assert math.isclose(alias, capped, rel_tol=1e-12)
+    with pytest.raises(ValueError, match="Poisson sampling only"):
+        DPTrainer(model=TinyLM(), args=_args(tmp_path / "r", sampling_mode="random_allocation",
+                                             sampling_kwargs={"truncated_batch_size": 9}), train_dataset=_data()).train()

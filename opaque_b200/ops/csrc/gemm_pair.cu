@@ -1,0 +1,495 @@
+// Dense forward / data-gradient GEMM on CTA pairs (sm_100a, tcgen05 cta_group::2):
+//
+//     D[M, N] = A[M, K1] * op1(B) + A2[M, K2] * op2(B2) + bias          (bf16 in / bf16 out, fp32 accumulation)
+//
+// Two CTAs of a 2x1 cluster share one 256 x 256 accumulator tile.  Each CTA loads ITS OWN 128 rows of A and ITS OWN
+// half (128 columns of N) of the B tile with ordinary TMA copies of this GPU's memory; one thread of the leader CTA
+// (cluster rank 0) issues `tcgen05.mma.cta_group::2` over both CTAs' shared memory, and each CTA's tensor memory
+// receives the accumulator rows of its own 128 rows of M.  Per k-block an SM therefore stages 32 KB for the work that
+// a single-CTA 128 x 256 tile stages 48 KB for, which is what lifts the operand-feed bound of the single-CTA kernels.
+//
+// Protocol (every wait bounded; a timeout records a code in the status word and the kernel unwinds):
+//   * full[s]  (leader only, 1 arrival + 64 KB of transactions): the leader's producer arms it for both CTAs' bytes;
+//     the peer's producer points its copies' completion at the leader's barrier (shared::cluster address from `mapa`).
+//   * empty[s] (each CTA, 1 arrival): the leader's `tcgen05.commit` arrives at both CTAs' barriers at once.
+//   * tmem_full[a] (each CTA, 1 arrival): same two-CTA commit after the last k-block of a tile.
+//   * tmem_empty[a] (leader only, 8 arrivals): the four epilogue warps of both CTAs; the peer's arrive remotely.
+// No copy in this file uses cluster multicast.
+//
+// Epilogues: plain store (+ bias), or GLU: the B halves come from TWO weight matrices (gate rows to rank 0, up rows to
+// rank 1), so every accumulator row holds 128 gate and 128 up pre-activations and the epilogue writes
+// act(gate) * up, optionally together with gate and up themselves for the backward pass.
+// Second K segment: LoRA (x A^T)(s B)^T in the forward pass, or the second operand pair of dX = dG Wg + dU Wu.
+//
+// Reference counterpart: the library GEMMs inside packages/opaque-patches/src/opaque/api/patches/kernels/lora.py:217-293
+// and the gate/up/SwiGLU sequence of kernels/swiglu.py:29-58.
+#include "common.cuh"
+#include "api.h"
+
+namespace ob {
+
+int make_bf16_map_2d(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld,
+                     int box_cols, int box_rows);
+
+constexpr int GP_BM = 128;           // rows of M per CTA (256 per pair)
+constexpr int GP_BN = 256;           // accumulator columns per pair tile
+constexpr int GP_BNH = 128;          // columns of N whose B rows one CTA stages
+constexpr int GP_BK = 64;
+constexpr int GP_STAGES = 6;
+constexpr int GP_A_BYTES = GP_BM * GP_BK * 2;
+constexpr int GP_B_BYTES = GP_BNH * GP_BK * 2;
+constexpr int GP_STAGE_BYTES = GP_A_BYTES + GP_B_BYTES;
+constexpr int GP_THREADS = 192;
+constexpr int GP_GROUP_M = 8;        // pair tiles (256 rows each) per raster band
+constexpr int GP_SMEM = GP_STAGES * GP_STAGE_BYTES + 256 + 1024;
+
+enum : int { GP_EPI_STORE = 0, GP_EPI_GLU = 1 };
+
+struct PairParams {
+  int M, N, K1, K2;
+  int kn1, kn2;                      // 1: the segment's B operand is stored [K, N] (N-major), 0: [N, K]
+  __nv_bfloat16* out;                // STORE: [M, N];  GLU: [M, N / 2] activations
+  long long ldo;
+  __nv_bfloat16* out_gate;           // GLU only, optional: pre-activations, pitch ldo
+  __nv_bfloat16* out_up;
+  const __nv_bfloat16* bias;         // STORE only
+  int act;                           // GLU: 0 silu, 1 gelu (erf), 2 gelu (tanh)
+  int* status;
+  unsigned long long wait_budget_ns;
+};
+
+// ---------------------------------------------------------------------------------------------- cluster helpers
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load issued by one CTA of a pair; the completion bytes go to `bar_cluster_addr`, which may be the peer's.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// One arrival at the barrier at this shared-memory offset in EVERY CTA of `cta_mask`, once all MMAs issued so far
+// by this thread have finished (an mbarrier signal, not a data copy).
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(cta_mask)
+               : "memory");
+}
+
+struct GpItem {
+  int row0;      // first row of this CTA's half of the pair tile
+  int nt;        // tile index along N
+};
+
+__device__ __forceinline__ GpItem gp_decode(int w, int tiles_m, int tiles_n, int rank) {
+  const int band = GP_GROUP_M * tiles_n;
+  const int b = w / band, r = w % band;
+  const int m_in_band = min(GP_GROUP_M, tiles_m - b * GP_GROUP_M);
+  const int mt = b * GP_GROUP_M + r % m_in_band;
+  GpItem it;
+  it.row0 = mt * (2 * GP_BM) + rank * GP_BM;
+  it.nt = r / m_in_band;
+  return it;
+}
+
+__device__ __forceinline__ float gp_act(float g, int act) {
+  if (act == 0) return g / (1.0f + __expf(-g));
+  if (act == 1) return 0.5f * g * (1.0f + erff(g * 0.70710678118654752f));
+  const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+  return 0.5f * g * (1.0f + t);
+}
+
+__device__ __forceinline__ void gp_store32(__nv_bfloat16* dst, const float* v, bool vec_ok, int n_left) {
+  if (vec_ok && n_left >= 32) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+      __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+      __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+      uint4 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&h0);
+      pk.y = *reinterpret_cast<uint32_t*>(&h1);
+      pk.z = *reinterpret_cast<uint32_t*>(&h2);
+      pk.w = *reinterpret_cast<uint32_t*>(&h3);
+      *reinterpret_cast<uint4*>(dst + j) = pk;
+    }
+  } else {
+    for (int j = 0; j < 32; ++j)
+      if (j < n_left) dst[j] = __float2bfloat16_rn(v[j]);
+  }
+}
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_b_up, const __grid_constant__ CUtensorMap map_a2,
+                 const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_b2_up,
+                 const PairParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // the dynamic shared-memory window starts at the same offset in both CTAs, so the rounded offsets agree too
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GP_STAGES * GP_STAGE_BYTES);
+  uint64_t* full = bars;                               // used in the leader CTA only
+  uint64_t* empty = bars + GP_STAGES;
+  uint64_t* tmem_full = bars + 2 * GP_STAGES;
+  uint64_t* tmem_empty = bars + 2 * GP_STAGES + 2;     // used in the leader CTA only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * GP_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int tiles_n = EPI == GP_EPI_GLU ? (p.N / 2 + GP_BNH - 1) / GP_BNH : (p.N + GP_BN - 1) / GP_BN;
+  const int tiles_m = (p.M + 2 * GP_BM - 1) / (2 * GP_BM);
+  const int total_work = tiles_m * tiles_n;
+  const int nk1 = (p.K1 + GP_BK - 1) / GP_BK;
+  const int nk2 = (p.K2 + GP_BK - 1) / GP_BK;
+  const int num_kb = nk1 + nk2;
+  const uint64_t budget = p.wait_budget_ns;
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GP_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 8);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(rank == 1 && EPI == GP_EPI_GLU ? &map_b_up : &map_b);
+    if (nk2) {
+      tma_prefetch_desc(&map_a2);
+      tma_prefetch_desc(rank == 1 && EPI == GP_EPI_GLU ? &map_b2_up : &map_b2);
+    }
+  }
+  if (warp == 1) {                   // one warp of EACH CTA takes part in a pair allocation
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                // both CTAs' barriers are initialised before any remote arrival or copy
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- TMA producer (one per CTA)
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const CUtensorMap* mb1 = (EPI == GP_EPI_GLU && rank == 1) ? &map_b_up : &map_b;
+      const CUtensorMap* mb2 = (EPI == GP_EPI_GLU && rank == 1) ? &map_b2_up : &map_b2;
+      for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
+        const GpItem it = gp_decode(w, tiles_m, tiles_n, rank);
+        // first column of N (= row of a [N, K] operand) of this CTA's half of the B tile
+        const int bn0 = EPI == GP_EPI_GLU ? it.nt * GP_BNH : it.nt * GP_BN + static_cast<int>(rank) * GP_BNH;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_EMPTY, budget)) {
+            ok = false;
+            break;
+          }
+          if (leader) mbar_expect_tx(&full[stage], 2 * GP_STAGE_BYTES);
+          const uint32_t bar = map_to_cta(smem_u32(&full[stage]), 0);
+          uint8_t* a_dst = smem + stage * GP_STAGE_BYTES;
+          uint8_t* b_dst = a_dst + GP_A_BYTES;
+          const bool first = kb < nk1;
+          const int k0 = (first ? kb : kb - nk1) * GP_BK;
+          tma_load_2d_pair(a_dst, first ? &map_a : &map_a2, bar, k0, it.row0);
+          const CUtensorMap* mb = first ? mb1 : mb2;
+          if (first ? p.kn1 : p.kn2) {
+#pragma unroll
+            for (int j = 0; j < GP_BNH / 64; ++j)
+              tma_load_2d_pair(b_dst + j * (GP_BK * 128), mb, bar, bn0 + 64 * j, k0);
+          } else {
+            tma_load_2d_pair(b_dst, mb, bar, k0, bn0);
+          }
+          if (++stage == GP_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (leader && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer (leader CTA only)
+      constexpr uint32_t idesc_k = make_idesc_bf16(2 * GP_BM, GP_BN, 0, 0);
+      constexpr uint32_t idesc_n = make_idesc_bf16(2 * GP_BM, GP_BN, 0, 1);
+      int stage = 0, acc_iter = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
+        const int as = acc_iter & 1;
+        if (!mbar_wait(&tmem_empty[as], ((acc_iter >> 1) & 1) ^ 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_EMPTY,
+                       budget)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * GP_BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, p.status, OB_ERR_WAIT_FULL, budget)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * GP_STAGE_BYTES);
+          const uint32_t b_addr = a_addr + GP_A_BYTES;
+          const bool kn = kb < nk1 ? p.kn1 != 0 : p.kn2 != 0;
+#pragma unroll
+          for (int kk = 0; kk < GP_BK / 16; ++kk) {
+            // K-major operand: rows 128 B apart, 8-row groups 1024 B apart, 32 B per 16-element k-step.
+            // N-major operand: 64-column blocks GP_BK*128 B apart, 8-row (k) groups 1024 B apart, 2048 B per k-step.
+            const uint64_t ad = make_smem_desc(a_addr + kk * 32, 16, 1024, 2);
+            const uint64_t bd = kn ? make_smem_desc(b_addr + kk * (16 * 128), GP_BK * 128, 1024, 2)
+                                   : make_smem_desc(b_addr + kk * 32, 16, 1024, 2);
+            umma_bf16_pair(d_tmem, ad, bd, kn ? idesc_n : idesc_k, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[stage], 3);          // frees the stage in both CTAs
+          if (++stage == GP_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_pair(&tmem_full[as], 3);           // the accumulator halves of both CTAs are complete
+        ++acc_iter;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps (4 per CTA)
+    const int q = warp & 3;
+    int acc_iter = 0;
+    bool ok = true;
+    const bool vec_ok = ((p.ldo & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                        (EPI != GP_EPI_GLU || p.out_gate == nullptr ||
+                         (((reinterpret_cast<uintptr_t>(p.out_gate) | reinterpret_cast<uintptr_t>(p.out_up)) & 15) == 0));
+    for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
+      const GpItem it = gp_decode(w, tiles_m, tiles_n, rank);
+      const int as = acc_iter & 1;
+      if (!mbar_wait(&tmem_full[as], (acc_iter >> 1) & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL, budget)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row = it.row0 + q * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * GP_BN;
+      if constexpr (EPI == GP_EPI_STORE) {
+        __nv_bfloat16* orow = p.out + static_cast<long long>(row) * p.ldo;
+        const int n0 = it.nt * GP_BN;
+#pragma unroll 1
+        for (int c = 0; c < GP_BN / 32; ++c) {
+          const int nc = n0 + c * 32;
+          if (nc >= p.N) break;
+          float v[32];
+          tmem_ld32(t_row + c * 32, v);
+          tmem_ld_wait();
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nc + j < p.N) v[j] += __bfloat162float(__ldg(p.bias + nc + j));
+          }
+          if (row < p.M) gp_store32(orow + nc, v, vec_ok, p.N - nc);
+        }
+      } else {
+        const int nh = p.N / 2;
+        const int n0 = it.nt * GP_BNH;
+        const long long ro = static_cast<long long>(row) * p.ldo;
+#pragma unroll 1
+        for (int c = 0; c < GP_BNH / 32; ++c) {
+          const int nc = n0 + c * 32;
+          if (nc >= nh) break;
+          float g[32], u[32];
+          tmem_ld32(t_row + c * 32, g);
+          tmem_ld32(t_row + GP_BNH + c * 32, u);
+          tmem_ld_wait();
+          if (row < p.M) {
+            if (p.out_gate != nullptr) {
+              gp_store32(p.out_gate + ro + nc, g, vec_ok, nh - nc);
+              gp_store32(p.out_up + ro + nc, u, vec_ok, nh - nc);
+              // the backward pass reads the ROUNDED pre-activations, so the activation is formed from them too
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                g[j] = __bfloat162float(__float2bfloat16_rn(g[j]));
+                u[j] = __bfloat162float(__float2bfloat16_rn(u[j]));
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) g[j] = gp_act(g[j], p.act) * u[j];
+            gp_store32(p.out + ro + nc, g, vec_ok, nh - nc);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (leader) mbar_arrive(&tmem_empty[as]);
+        else mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[as]), 0));
+      }
+      ++acc_iter;
+    }
+  }
+
+  // Nobody leaves (or frees tensor memory) while the other CTA may still signal this CTA's barriers, complete copies
+  // on them or accumulate into its tensor memory.
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // A wait gave up (after its whole budget), so some copies of this CTA may never be consumed.  They were issued at
+    // least one budget ago and a tile copy lasts microseconds; one more millisecond lets any straggler land before the
+    // shared memory is given back.
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 1000000ull) {}
+  }
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+static int pair_grid(const void* kernel, int sms) {
+  // clusters that can be co-resident (two CTAs of a pair must sit on paired SMs); one cluster per SM pair
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(sms), 1, 1);
+  cfg.blockDim = dim3(GP_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = GP_SMEM;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters <= 0) {
+    cudaGetLastError();
+    clusters = sms / 2;
+  }
+  if (clusters > sms / 2) clusters = sms / 2;
+  return clusters;
+}
+
+}  // namespace ob
+
+// D = A op1(B) + A2 op2(B2) + bias on CTA pairs.  b_kn / b2_kn = 1: that operand is stored [K, N].
+// glu != 0: `b` holds the gate rows and `b_up` the up rows ([N/2, K] each, or [K, N/2] with b_kn); N counts gate and up
+// columns together; out [M, N/2] = act(gate) * up, and out_gate / out_up (optional, both or none) receive the
+// pre-activations.  glu_act: 0 silu, 1 gelu erf, 2 gelu tanh.  With a second segment in GLU mode b2 / b2_up likewise.
+extern "C" int ob_gemm_pair(const void* a, const void* b, const void* b_up, const void* a2, const void* b2,
+                            const void* b2_up, const void* bias, void* out, void* out_gate, void* out_up,
+                            long long rows_a, int N, int K1, int K2, long long lda, long long ldb, long long lda2,
+                            long long ldb2, long long ldo, int b_kn, int b2_kn, int glu, int glu_act, int* status,
+                            double wait_budget_s, int num_sms, void* stream) {
+  using namespace ob;
+  if (rows_a <= 0 || N <= 0 || K1 <= 0) return 0;
+  if (rows_a > 0x7fffffffLL - 2 * GP_BM) return -50;
+  if (K2 > 0 && (a2 == nullptr || b2 == nullptr)) return -51;
+  if (glu && (b_up == nullptr || (N & 1) || (K2 > 0 && b2_up == nullptr) || bias != nullptr)) return -52;
+  if (glu && ((out_gate == nullptr) != (out_up == nullptr))) return -53;
+  const int nb = glu ? N / 2 : N;               // columns of N covered by ONE B operand
+  CUtensorMap ma, mb, mbu, ma2, mb2, mb2u;
+  int rc = make_bf16_map_2d(&ma, a, rows_a, K1, lda, GP_BK, GP_BM);
+  if (rc) return rc;
+  auto b_map = [&](CUtensorMap* m, const void* base, int K, long long ld, int kn) {
+    return kn ? make_bf16_map_2d(m, base, K, nb, ld, 64, GP_BK) : make_bf16_map_2d(m, base, nb, K, ld, GP_BK, GP_BNH);
+  };
+  rc = b_map(&mb, b, K1, ldb, b_kn);
+  if (rc) return rc;
+  if (glu) {
+    rc = b_map(&mbu, b_up, K1, ldb, b_kn);
+    if (rc) return rc;
+  } else {
+    mbu = mb;
+  }
+  if (K2 > 0) {
+    rc = make_bf16_map_2d(&ma2, a2, rows_a, K2, lda2, GP_BK, GP_BM);
+    if (rc) return rc;
+    rc = b_map(&mb2, b2, K2, ldb2, b2_kn);
+    if (rc) return rc;
+    if (glu) {
+      rc = b_map(&mb2u, b2_up, K2, ldb2, b2_kn);
+      if (rc) return rc;
+    } else {
+      mb2u = mb2;
+    }
+  } else {
+    ma2 = ma;
+    mb2 = mb;
+    mb2u = mbu;
+  }
+  static bool configured = false;
+  static int clusters_store = 0, clusters_glu = 0;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_pair_kernel<GP_EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_pair_kernel<GP_EPI_GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_SMEM) != cudaSuccess)
+      return -54;
+    clusters_store = pair_grid(reinterpret_cast<const void*>(gemm_pair_kernel<GP_EPI_STORE>), num_sms);
+    clusters_glu = pair_grid(reinterpret_cast<const void*>(gemm_pair_kernel<GP_EPI_GLU>), num_sms);
+    configured = true;
+  }
+  PairParams p;
+  p.M = static_cast<int>(rows_a);
+  p.N = N; p.K1 = K1; p.K2 = K2;
+  p.kn1 = b_kn; p.kn2 = b2_kn;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.ldo = ldo;
+  p.out_gate = static_cast<__nv_bfloat16*>(out_gate);
+  p.out_up = static_cast<__nv_bfloat16*>(out_up);
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.act = glu_act;
+  p.status = status;
+  p.wait_budget_ns = static_cast<unsigned long long>(wait_budget_s * 1e9);
+  const long long tiles_m = (rows_a + 2 * GP_BM - 1) / (2 * GP_BM);
+  const long long tiles_n = glu ? (nb + GP_BNH - 1) / GP_BNH : (N + GP_BN - 1) / GP_BN;
+  const long long total = tiles_m * tiles_n;
+  const int avail = glu ? clusters_glu : clusters_store;
+  const int clusters = static_cast<int>(total < avail ? total : avail);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (glu)
+    gemm_pair_kernel<GP_EPI_GLU><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mbu, ma2, mb2, mb2u, p);
+  else
+    gemm_pair_kernel<GP_EPI_STORE><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mbu, ma2, mb2, mb2u, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -55;
+}
+
+// Bit patterns of the descriptors the tensor-core kernels build, for host-side checks.
+extern "C" unsigned int ob_debug_idesc_bf16(int m, int n, int a_mn_major, int b_mn_major) {
+  return ob::make_idesc_bf16(m, n, a_mn_major, b_mn_major);
+}

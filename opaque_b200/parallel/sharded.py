@@ -91,6 +91,7 @@ class FlatSpace:
                 self.direct_elems = end
             off = end
         chunk = group.world * ALIGN
+        self.used = off                    # flat length without the padding that depends on the number of ranks
         self.total = max((off + chunk - 1) // chunk * chunk, chunk)
         self.shard = self.total // group.world
         self.shard_lo = group.rank * self.shard
@@ -279,25 +280,38 @@ class ShardedDPOptimizer:
 
     # ---- checkpoint -----------------------------------------------------------------------
     def state_dict(self) -> dict[str, Any]:
-        """Full (unsharded) optimizer state on every rank; rank 0 writes it."""
+        """Full (unsharded) optimizer state on every rank; rank 0 writes it.
+
+        The tensors are cut to ``used`` elements — the layout's own length, without the tail padding that makes the
+        space divisible by the number of ranks — so a run saved on N GPUs resumes on any other number."""
         sp = self.space
+        n = sp.used
         sd = {"step": self.step_count, "phi": self.phi, "key_seed": str(self.key.seed),
-              "master": sp.gather_full(sp.master).cpu(), "m": sp.gather_full(sp.m).cpu(),
-              "v": sp.gather_full(sp.v).cpu(), "total": sp.total}
+              "master": sp.gather_full(sp.master)[:n].cpu(), "m": sp.gather_full(sp.m)[:n].cpu(),
+              "v": sp.gather_full(sp.v)[:n].cpu(), "used": n}
         if self.ftrl_state is not None:
-            sd["ftrl_state"] = torch.stack([sp.gather_full(self.ftrl_state[b]) for b in range(self.nbuf)]).cpu()
+            sd["ftrl_state"] = torch.stack([sp.gather_full(self.ftrl_state[b])[:n] for b in range(self.nbuf)]).cpu()
         return sd
 
     @torch.no_grad()
     def load_state_dict(self, sd: dict[str, Any]) -> None:
         sp = self.space
-        if int(sd["total"]) != sp.total:
-            raise ValueError("checkpoint was written for a different parameter layout")
+        n = int(sd["used"]) if "used" in sd else min(int(sd["total"]), sp.used)   # older files stored the padded length
+        if n != sp.used or ("used" not in sd and int(sd["total"]) < sp.used):
+            raise ValueError(f"checkpoint was written for a different parameter layout ({n} flat elements, this model has {sp.used})")
         lo, hi = sp.shard_lo, sp.shard_lo + sp.shard
         self.step_count, self.phi = int(sd["step"]), float(sd["phi"])
-        sp.master.copy_(sd["master"][lo:hi])
-        sp.m.copy_(sd["m"][lo:hi])
-        sp.v.copy_(sd["v"][lo:hi])
-        sp.params.local.copy_(sd["master"].to(torch.bfloat16))
+
+        def shard_of(full: torch.Tensor) -> torch.Tensor:
+            """This rank's slice of a saved flat tensor, zero beyond the saved length (re-padding for this world size)."""
+            out = torch.zeros(*full.shape[:-1], sp.shard, dtype=full.dtype)
+            a, b = min(lo, n), min(hi, n)
+            if b > a:
+                out[..., :b - a] = full[..., a:b]
+            return out
+        sp.master.copy_(shard_of(sd["master"]))
+        sp.m.copy_(shard_of(sd["m"]))
+        sp.v.copy_(shard_of(sd["v"]))
+        sp.params.local[:n].copy_(sd["master"][:n].to(torch.bfloat16))
         if self.ftrl_state is not None and "ftrl_state" in sd:
-            self.ftrl_state.copy_(sd["ftrl_state"][:, lo:hi])
+            self.ftrl_state.copy_(shard_of(sd["ftrl_state"]))

@@ -13,7 +13,7 @@ optimizer, with the accountant charged once per step.  Two gradient engines shar
 Checkpoints are atomic directories ``checkpoint-N`` (written as ``checkpoint-N.tmp`` then renamed) holding
 ``model.safetensors`` (or adapter weights), ``dp_optimizer.pt``, ``dp_state.pt`` (runtime bundle, version 3:
 clip / noise / sampler state, DP hyper-parameters for drift detection), ``accountant.json``,
-``trainer_state.json`` and ``rng_state_{rank}.pth``; resuming uses the saved accountant as a prefix so
+``trainer_state.json`` and ``rng_state.pth`` (``rng_state_{rank}.pth`` with several ranks); resuming uses the saved accountant as a prefix so
 calibration and stop-at-ε account for budget already spent.
 
 A retryable OOM on any rank is turned into a cluster-wide decision (one MAX all-reduce of a flag): every rank
@@ -211,25 +211,105 @@ class PredictionOutput:
 
 @dataclasses.dataclass
 class RuntimeCheckpoint:
-    """Everything besides weights / optimizer needed to continue a DP run bit-for-bit."""
+    """Everything besides weights / optimizer needed to continue a DP run bit-for-bit (``dp_state.pt``).
+
+    The first block carries the field names of the reference's bundle
+    (packages/opaque-transformers/src/opaque/api/transformers/trainer/_checkpoint.py:198-290); ``extras`` holds what
+    this trainer checks in addition (sampling mode, clipping settings, mechanism arguments, engine).  The file is a
+    ``torch.save`` of a plain dict with these keys, never a pickled class instance, so reading it needs neither
+    this package nor the reference: ``torch.load(path)["noise_multiplier"]``.  A bundle written by the reference (a
+    pickled instance of ITS dataclass) loads through :func:`load_runtime_checkpoint`, which resolves that class name to
+    this one.
+    """
     version: int
     clip_state: dict
     noise_state: dict
-    sampler_state: dict
+    sampler_state: dict | None
     sample_rate: float
     target_delta: float
     noise_multiplier: float
+    expected_steps_per_epoch: int
     expected_batch_size: float
-    max_steps: int
-    mechanism: str
-    mechanism_kwargs: dict
-    sampling_mode: str
-    clipping_norm: Any
-    clipping_mode: str
-    engine: str
-    mf_horizon: int | None = None
-    min_sep: int | None = None
-    max_participations: int | None = None
+    total_steps: int
+    mechanism_kind: str = "gaussian"
+    mf_n_steps: int | None = None
+    mf_min_sep: int | None = None
+    mf_max_participations: int | None = None
+    lr_scheduler: str | None = None
+    learning_rate: float | None = None
+    warmup_steps: float | None = None
+    lr_scheduler_kwargs: dict | None = None
+    extras: dict = dataclasses.field(default_factory=dict)
+
+    # names used elsewhere in this trainer
+    @property
+    def max_steps(self) -> int:
+        return self.total_steps
+
+    @property
+    def mechanism(self) -> str:
+        return self.mechanism_kind
+
+    def to_dict(self) -> dict:
+        return {"format": "opaque dp_state bundle", **{f.name: getattr(self, f.name) for f in dataclasses.fields(self)}}
+
+    @classmethod
+    def from_dict(cls, d: Mapping) -> "RuntimeCheckpoint":
+        names = {f.name for f in dataclasses.fields(cls)}
+        missing = {"version", "clip_state", "noise_state", "sample_rate", "target_delta", "noise_multiplier", "total_steps"} - set(d)
+        if missing:
+            raise ValueError(f"dp_state bundle lacks {sorted(missing)}")
+        return cls(**{k: v for k, v in d.items() if k in names})
+
+
+def save_runtime_checkpoint(bundle: RuntimeCheckpoint, path: str) -> None:
+    """Write ``dp_state.pt``: ``torch.save`` of the bundle as a plain dict."""
+    torch.save(bundle.to_dict(), path)
+
+
+class _BundleUnpickler(pickle.Unpickler):
+    """Resolves the reference's ``RuntimeCheckpoint`` class (and nothing else of its packages) to this module's."""
+
+    def find_class(self, module, name):
+        if name == "RuntimeCheckpoint" and module.endswith("trainer._checkpoint"):
+            return _ForeignBundle
+        return super().find_class(module, name)
+
+
+class _ForeignBundle:
+    """Receives the attribute dict of a pickled foreign dataclass instance."""
+
+    def __setstate__(self, state):
+        self.__dict__.update(state)
+
+
+class _BundlePickle:
+    """``pickle_module`` for ``torch.load`` with the class resolution above."""
+    __name__ = "pickle"
+    Unpickler = _BundleUnpickler
+    load = staticmethod(lambda f, **kw: _BundleUnpickler(f, **kw).load())
+    loads = staticmethod(pickle.loads)
+    dumps = staticmethod(pickle.dumps)
+    dump = staticmethod(pickle.dump)
+    Pickler = pickle.Pickler
+    HIGHEST_PROTOCOL = pickle.HIGHEST_PROTOCOL
+    DEFAULT_PROTOCOL = pickle.DEFAULT_PROTOCOL
+    PickleError = pickle.PickleError
+    UnpicklingError = pickle.UnpicklingError
+    PicklingError = pickle.PicklingError
+
+
+def load_runtime_checkpoint(path: str) -> RuntimeCheckpoint:
+    """Read ``dp_state.pt`` written by this trainer (a dict) or by the reference's trainer (its dataclass instance)."""
+    obj = torch.load(path, map_location="cpu", weights_only=False, pickle_module=_BundlePickle)
+    if isinstance(obj, _ForeignBundle):
+        obj = dict(obj.__dict__)
+    if not isinstance(obj, Mapping):
+        raise TypeError(f"{path} does not hold a dp_state bundle (got {type(obj).__name__})")
+    bundle = RuntimeCheckpoint.from_dict(obj)
+    if bundle.version != DP_STATE_BUNDLE_VERSION:
+        raise ValueError(f"unsupported dp_state bundle version {bundle.version} (expected {DP_STATE_BUNDLE_VERSION})")
+    return bundle
 
 
 def build_lr_schedule(args: TrainingArguments, max_steps: int):
@@ -1066,11 +1146,24 @@ class DPTrainer:
         a = self.args
         ref = self.engine_kind == "reference"
         ms, mp = self._participation(self.sampler, self.state.max_steps)
+        if ref:
+            clip_sd, noise_sd = state_dict(self._clip_state), state_dict(_noise_public(self._noise_state))
+        else:
+            # fused engine: the noise stream is (key, optimizer step), both in dp_optimizer.pt; the adaptive clipping state
+            # (bounds, step counter of ITS noise stream, last counts) lives in the engine and is saved here
+            ad = self._fused.adaptive
+            clip_sd = {"adaptive": state_dict(ad), "clipping_norm": self._fused.clipping_norm} if ad is not None else {}
+            noise_sd = {}
+        per_epoch = max(1, round(1.0 / self.sample_rate)) if self.sample_rate else 1
         return RuntimeCheckpoint(
-            DP_STATE_BUNDLE_VERSION, state_dict(self._clip_state) if ref else {}, state_dict(_noise_public(self._noise_state)) if ref else {},
-            state_dict(self.sampler), self.sample_rate, self.target_delta, self.noise_multiplier, self.expected_batch,
-            self.state.max_steps, a.privacy_noise_mechanism, dict(a.privacy_noise_mechanism_kwargs), a.sampling_mode,
-            a.clipping_norm, a.clipping_mode, self.engine_kind, self.state.max_steps if self._strategy else None, ms, mp)
+            version=DP_STATE_BUNDLE_VERSION, clip_state=clip_sd, noise_state=noise_sd, sampler_state=state_dict(self.sampler),
+            sample_rate=self.sample_rate, target_delta=self.target_delta, noise_multiplier=self.noise_multiplier,
+            expected_steps_per_epoch=per_epoch, expected_batch_size=self.expected_batch, total_steps=self.state.max_steps,
+            mechanism_kind=a.privacy_noise_mechanism, mf_n_steps=self.state.max_steps if self._strategy else None,
+            mf_min_sep=ms, mf_max_participations=mp, lr_scheduler=a.lr_scheduler, learning_rate=float(a.learning_rate),
+            warmup_steps=float(a.warmup_steps), lr_scheduler_kwargs=dict(a.lr_scheduler_kwargs),
+            extras={"mechanism_kwargs": dict(a.privacy_noise_mechanism_kwargs), "sampling_mode": a.sampling_mode,
+                    "clipping_norm": a.clipping_norm, "clipping_mode": a.clipping_mode, "engine": self.engine_kind})
 
     def _save_checkpoint(self, step: int) -> str:
         a = self.args
@@ -1086,8 +1179,7 @@ class DPTrainer:
             torch.save(opt_sd, os.path.join(tmp, FILES["optimizer"]))
             if self.engine_kind == "reference" and self._strategy is not None:
                 torch.save(state_dict(self._noise_state._inner_state), os.path.join(tmp, "dp_noise_buffers.pt"))
-            with open(os.path.join(tmp, FILES["state"]), "wb") as f:
-                pickle.dump(self._runtime(), f)
+            save_runtime_checkpoint(self._runtime(), os.path.join(tmp, FILES["state"]))
             with open(os.path.join(tmp, FILES["accountant"]), "w") as f:
                 f.write(self.accountant.to_json())
             with open(os.path.join(tmp, FILES["trainer_state"]), "w") as f:
@@ -1097,7 +1189,8 @@ class DPTrainer:
         rng = {"python": random.getstate(), "numpy": np.random.get_state(), "torch": torch.get_rng_state(),
                "cuda": torch.cuda.get_rng_state_all() if torch.cuda.is_available() else None}
         if os.path.isdir(tmp):
-            torch.save(rng, os.path.join(tmp, f"rng_state_{a.process_index}.pth"))
+            # Hugging Face naming: one `rng_state.pth` for a single process, `rng_state_{rank}.pth` with several
+            torch.save(rng, os.path.join(tmp, "rng_state.pth" if a.world_size == 1 else f"rng_state_{a.process_index}.pth"))
         _barrier()
         if a.should_save:
             shutil.rmtree(final, ignore_errors=True)
@@ -1108,15 +1201,15 @@ class DPTrainer:
         return final
 
     def _load_checkpoint_meta(self, path: str):
-        with open(os.path.join(path, FILES["state"]), "rb") as f:
-            runtime: RuntimeCheckpoint = pickle.load(f)
-        if runtime.version != DP_STATE_BUNDLE_VERSION:
-            raise ValueError(f"checkpoint bundle version {runtime.version} != {DP_STATE_BUNDLE_VERSION}")
+        runtime = load_runtime_checkpoint(os.path.join(path, FILES["state"]))
         a = self.args
-        drift = {"privacy_noise_mechanism": (runtime.mechanism, a.privacy_noise_mechanism), "sampling_mode": (runtime.sampling_mode, a.sampling_mode),
-                 "clipping_norm": (runtime.clipping_norm, a.clipping_norm), "clipping_mode": (runtime.clipping_mode, a.clipping_mode),
+        ex = runtime.extras
+        drift = {"privacy_noise_mechanism": (runtime.mechanism, a.privacy_noise_mechanism),
                  "max_steps": (runtime.max_steps, self.state.max_steps),
-                 "expected_batch_size": (runtime.expected_batch_size, float(a.train_batch_size))}
+                 "expected_batch_size": (float(runtime.expected_batch_size), float(a.train_batch_size))}
+        for key, now in (("sampling_mode", a.sampling_mode), ("clipping_norm", a.clipping_norm), ("clipping_mode", a.clipping_mode)):
+            if key in ex:                       # a bundle written by the reference carries no such entry: nothing to compare
+                drift[key] = (ex[key], now)
         bad = {k: v for k, v in drift.items() if v[0] != v[1]}
         if bad:
             raise ValueError(f"refusing to resume: DP-relevant arguments changed since the checkpoint was written: {bad}")
@@ -1132,6 +1225,11 @@ class DPTrainer:
         opt_sd = torch.load(os.path.join(path, FILES["optimizer"]), weights_only=False)
         if self.engine_kind == "fused":
             self._fused.opt.load_state_dict(opt_sd)
+            if self._fused.adaptive is not None and runtime.clip_state.get("adaptive") is not None:
+                # bounds and the step counter of the adaptive mechanism's own noise stream: without them a resumed run
+                # would restart from the initial bound and draw the same Gaussians for new clipped-count releases
+                self._fused.adaptive = from_state_dict(self._fused.adaptive, runtime.clip_state["adaptive"])
+                self._fused.clipping_norm = runtime.clip_state["clipping_norm"]
         else:
             self._trainable = {n: p.detach().clone() for n, p in self.model.named_parameters() if p.requires_grad}
             self._opt_state = from_state_dict(self._optimizer.init(self._trainable), opt_sd)
@@ -1146,6 +1244,8 @@ class DPTrainer:
         st = json.load(open(os.path.join(path, FILES["trainer_state"])))
         self.state = DPTrainerState(**{k: v for k, v in st.items() if k in {f.name for f in dataclasses.fields(DPTrainerState)}})
         rng_file = os.path.join(path, f"rng_state_{self.args.process_index}.pth")
+        if not os.path.exists(rng_file):
+            rng_file = os.path.join(path, "rng_state.pth")
         if os.path.exists(rng_file):
             rng = torch.load(rng_file, weights_only=False)
             random.setstate(rng["python"])

@@ -1,0 +1,84 @@
+"""The CTA-pair GEMM (tcgen05 cta_group::2) against fp32 PyTorch references (run on a B200: ``pytest -m gpu``)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from opaque_b200.ops import lib
+    assert lib.available(), "the sm_100a kernel library must load on a GPU machine"
+    return torch.device("cuda", 0)
+
+
+def rel(x, y):
+    return float((x.float() - y.float()).norm() / (y.float().norm() + 1e-30))
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (128, 256, 128), (300, 520, 200), (1000, 136, 72), (1024, 768, 3072),
+                                   (4096, 4096, 1024), (2048, 1536, 8192)])
+def test_pair_gemm_layouts_bias_segments(dev, M, N, K):
+    from opaque_b200 import ops
+    torch.manual_seed(M + N + K)
+    st = ops.StatusWord(dev)
+    a = torch.randn(M, K, device=dev).bfloat16()
+    w = (torch.randn(N, K, device=dev) / math.sqrt(K)).bfloat16()
+    bias = torch.randn(N, device=dev).bfloat16()
+    y = torch.full((M + 1, N), 7.0, device=dev).bfloat16()
+    ops.gemm_pair(a, w, out=y[:M], status=st)
+    assert st.read() == 0 and rel(y[:M], ops.gemm_ref(a, w)) < 4e-3 and bool((y[M] == 7.0).all())     # no write past row M
+    assert rel(ops.gemm_pair(a, w, bias=bias, status=st), ops.gemm_ref(a, w, bias=bias)) < 4e-3
+    wt = w.t().contiguous()                                   # [K, N]
+    y = ops.gemm_pair(a, wt, b_layout="kn", status=st)
+    assert st.read() == 0 and rel(y, ops.gemm_ref(a, wt, b_layout="kn")) < 4e-3
+    for r in (8, 16, 80):
+        xa = torch.randn(M, r, device=dev).bfloat16()
+        lb = torch.randn(N, r, device=dev).bfloat16()
+        y = ops.gemm_pair(a, w, a2=xa, b2=lb, bias=bias, status=st)
+        assert st.read() == 0 and rel(y, ops.gemm_ref(a, w, a2=xa, b2=lb, bias=bias)) < 4e-3
+        # data gradient of a LoRA linear: dY W + q A with both operands stored [K, N]
+        la = torch.randn(r, N, device=dev).bfloat16()
+        y = ops.gemm_pair(a, wt, b_layout="kn", a2=xa, b2=la, b2_layout="kn", status=st)
+        ref = a.float() @ wt.float() + xa.float() @ la.float()
+        assert st.read() == 0 and rel(y, ref) < 4e-3
+    # two full-width [K, N] segments: dX = dG Wg + dU Wu
+    a2 = torch.randn(M, K, device=dev).bfloat16()
+    wt2 = (torch.randn(K, N, device=dev) / math.sqrt(K)).bfloat16()
+    y = ops.gemm_pair(a, wt, b_layout="kn", a2=a2, b2=wt2, b2_layout="kn", status=st)
+    assert st.read() == 0 and rel(y, a.float() @ wt.float() + a2.float() @ wt2.float()) < 4e-3
+    # the single-CTA kernel stays available and agrees
+    assert rel(ops.gemm(a, w, bias=bias, kernel="single", status=st), ops.gemm_ref(a, w, bias=bias)) < 4e-3
+
+
+@pytest.mark.parametrize("M,I,K,act", [(256, 128, 64, "silu"), (300, 328, 200, "silu"), (2048, 1408, 2048, "silu"),
+                                       (1024, 512, 256, "gelu_pytorch_tanh"), (512, 256, 128, "gelu")])
+def test_pair_gemm_glu_epilogue(dev, M, I, K, act):
+    from opaque_b200 import ops
+    torch.manual_seed(M + I)
+    st = ops.StatusWord(dev)
+    a = torch.randn(M, K, device=dev).bfloat16()
+    wg = (torch.randn(I, K, device=dev) / math.sqrt(K)).bfloat16()
+    wu = (torch.randn(I, K, device=dev) / math.sqrt(K)).bfloat16()
+    h, g, u = ops.gemm_glu(a, wg, wu, act=act, status=st)
+    assert st.read() == 0
+    assert rel(g, a.float() @ wg.float().t()) < 4e-3 and rel(u, a.float() @ wu.float().t()) < 4e-3
+    assert rel(h, ops.gemm_glu_ref(a, wg, wu, act=act)) < 6e-3
+    # the activation is formed from the stored (rounded) pre-activations: the backward pass sees the same values
+    gf, uf = g.float(), u.float()
+    act_g = torch.nn.functional.silu(gf) if act == "silu" else torch.nn.functional.gelu(gf, approximate="tanh" if "tanh" in act else "none")
+    assert rel(h, act_g * uf) < 3e-3
+    h2, g2, u2 = ops.gemm_glu(a, wg, wu, act=act, save_preact=False, status=st)
+    assert g2 is None and u2 is None and rel(h2, ops.gemm_glu_ref(a, wg, wu, act=act)) < 6e-3
+
+
+def test_instruction_descriptor_bitfields():
+    """kind::f16 instruction descriptor: D format [4,6), A / B format [7,10) / [10,13), majors 15 / 16, N>>3 [17,23), M>>4 [24,29)."""
+    from opaque_b200.ops import lib
+    f = lib.load().ob_debug_idesc_bf16
+    base = (1 << 4) | (1 << 7) | (1 << 10)
+    assert f(128, 256, 0, 0) == base | (32 << 17) | (8 << 24)
+    assert f(256, 256, 0, 1) == base | (1 << 16) | (32 << 17) | (16 << 24)
+    assert f(128, 128, 1, 1) == base | (1 << 15) | (1 << 16) | (16 << 17) | (8 << 24)

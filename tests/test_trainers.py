@@ -64,7 +64,7 @@ def test_dp_trainer_runs_logs_and_accounts(tmp_path):
     assert any("loss" in h for h in tr.state.log_history) and tr.evaluate()["eval_loss"] > 0
     ck = list_checkpoints(str(tmp_path))
     assert [os.path.basename(c) for c in ck] == ["checkpoint-3", "checkpoint-6"]
-    for f in ("model.safetensors", "dp_optimizer.pt", "dp_state.pt", "accountant.json", "trainer_state.json", "rng_state_0.pth"):
+    for f in ("model.safetensors", "dp_optimizer.pt", "dp_state.pt", "accountant.json", "trainer_state.json", "rng_state.pth"):
         assert os.path.exists(os.path.join(ck[-1], f)), f
     acct = json.load(open(os.path.join(ck[-1], "accountant.json")))
     assert acct["process"]["type"] == "Repeated" and acct["process"]["count"] == 6
@@ -293,3 +293,46 @@ def test_truncated_poisson_cap_reaches_the_accountant(tmp_path):
     with pytest.raises(ValueError, match="Poisson sampling only"):
         DPTrainer(model=TinyLM(), args=_args(tmp_path / "r", sampling_mode="random_allocation",
                                              sampling_kwargs={"truncated_batch_size": 9}), train_dataset=_data()).train()
+
+
+def test_dp_state_bundle_is_a_plain_dict_with_the_reference_field_names(tmp_path):
+    """`dp_state.pt` is a torch.save of a dict (no class of this package is needed to read it); a bundle pickled as the
+    reference's own dataclass instance loads too."""
+    import pickle
+    import sys
+    import types
+
+    from opaque_b200.transformers.trainer import DP_STATE_BUNDLE_VERSION, load_runtime_checkpoint
+    torch.manual_seed(0)
+    tr = DPTrainer(model=TinyLM(), args=_args(tmp_path, max_steps=3, save_steps=3), train_dataset=_data())
+    tr.train()
+    path = os.path.join(list_checkpoints(str(tmp_path))[-1], "dp_state.pt")
+    raw = torch.load(path, weights_only=False)
+    assert type(raw) is dict
+    for k in ("version", "clip_state", "noise_state", "sampler_state", "sample_rate", "target_delta", "noise_multiplier",
+              "expected_steps_per_epoch", "expected_batch_size", "total_steps", "mechanism_kind", "mf_n_steps", "mf_min_sep",
+              "mf_max_participations", "lr_scheduler", "learning_rate", "warmup_steps", "lr_scheduler_kwargs"):
+        assert k in raw, k
+    assert raw["version"] == DP_STATE_BUNDLE_VERSION and raw["total_steps"] == 3 and raw["mechanism_kind"] == "gaussian"
+    b = load_runtime_checkpoint(path)
+    assert b.max_steps == 3 and b.extras["sampling_mode"] == "poisson"
+    # a reference-shaped file: an instance of a dataclass living at the reference's module path
+    mod_name = "opaque.api.transformers.trainer._checkpoint"
+    import dataclasses as dc
+    fake = types.ModuleType(mod_name)
+    cls = dc.make_dataclass("RuntimeCheckpoint", [(k, object) for k in raw if k not in ("format", "extras")])
+    cls.__module__ = mod_name
+    fake.RuntimeCheckpoint = cls
+    parents = ["opaque", "opaque.api", "opaque.api.transformers", "opaque.api.transformers.trainer"]
+    added = [m for m in parents + [mod_name] if m not in sys.modules]
+    for m in parents:
+        sys.modules.setdefault(m, types.ModuleType(m))
+    sys.modules[mod_name] = fake
+    try:
+        foreign = os.path.join(str(tmp_path), "foreign_dp_state.pt")
+        torch.save(cls(**{k: v for k, v in raw.items() if k not in ("format", "extras")}), foreign)
+    finally:
+        for m in added:
+            sys.modules.pop(m, None)
+    got = load_runtime_checkpoint(foreign)                    # the reference's class is NOT importable here
+    assert got.noise_multiplier == raw["noise_multiplier"] and got.sampler_state == raw["sampler_state"] and got.extras == {}

@@ -313,6 +313,11 @@ def main() -> None:
         torch.cuda.synchronize()
 
     loss_fn = model.per_example_loss
+    if frac < 1.0 and isinstance(model, LlamaForCausalLM):
+        # only the last `frac` of the positions carry labels (shift_labels): the head and cross-entropy run on those rows
+        # alone, with static shapes and without a device-to-host read of the number of scored rows
+        import functools
+        loss_fn = functools.partial(model.per_example_loss, scored_suffix=seq - int(seq * (1.0 - frac)))
     # set-up (untimed, not a training step): capture the microbatch graphs of every static size, and run every tail
     # microbatch size once (the gradient shard is zeroed again afterwards) so that library plan selection
     # and the caching allocator have seen each shape before a timed step meets it

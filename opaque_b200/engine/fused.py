@@ -167,7 +167,7 @@ class Capture:
         B, T = self.batch_size, self.tokens
         if dlogits.shape[0] != B * T or e.shape[0] != B * T:
             return None
-        picked = dlogits.view(B, T, -1).gather(2, ids.view(B, 1, T).expand(B, T, T))        # [b, t', t]
+        picked = dlogits.unflatten(0, (B, T)).gather(2, ids.view(B, 1, T).expand(B, T, T))   # [b, t', t]; rows may be padded
         inner = torch.bmm(hidden.view(B, T, -1), e.view(B, T, -1).transpose(1, 2))           # [b, t', t]
         return (picked.float() * inner.float()).sum(dim=(1, 2))
 
@@ -260,6 +260,25 @@ class Capture:
 
 # ===================================================================================== layer functions
 
+OWN_GEMM = True        # forward / data-gradient products of linear layers run on this library's tcgen05 GEMMs
+
+
+def _own_gemm_ok(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> bool:
+    """True when ``x Wᵀ`` (and ``dY W``) can run on the library's GEMM: bf16 CUDA operands whose rows TMA can address."""
+    return (OWN_GEMM and x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.ndim == 2
+            and weight.stride(1) == 1 and weight.stride(0) % 8 == 0 and weight.shape[0] % 8 == 0 and weight.shape[1] % 8 == 0
+            and (weight.data_ptr() & 15) == 0 and (bias is None or (bias.dtype == torch.bfloat16 and bias.is_contiguous()))
+            and ops.functional.kernels_enabled())
+
+
+def _rows(x: torch.Tensor) -> torch.Tensor:
+    """``x`` as a ``[rows, features]`` matrix with contiguous, 16-byte aligned rows."""
+    x2d = x.reshape(-1, x.shape[-1])
+    if x2d.stride(1) != 1 or x2d.stride(0) % 8 or (x2d.data_ptr() & 15):
+        x2d = x2d.contiguous()
+    return x2d
+
+
 class _DPLinear(Function):
     """``y = x Wᵀ (+ b)`` with the weight gradient deferred to the capture."""
 
@@ -267,15 +286,20 @@ class _DPLinear(Function):
     def forward(ctx, x, weight, bias):
         ctx.save_for_backward(x, weight)
         ctx.bias = bias
+        ctx.own = _own_gemm_ok(x, weight, bias)
+        if ctx.own:
+            return ops.gemm(_rows(x), weight, bias=bias).view(*x.shape[:-1], weight.shape[0])
         return torch.nn.functional.linear(x, weight, bias)
 
     @staticmethod
     def backward(ctx, gy):
         x, weight = ctx.saved_tensors
         cap = current_capture()
-        dx = gy @ weight if ctx.needs_input_grad[0] else None
         g2d = gy.reshape(-1, gy.shape[-1])
         g2d = g2d if g2d.is_contiguous() else g2d.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = ops.gemm(g2d, weight, b_layout="kn").view(x.shape) if ctx.own else gy @ weight
         x2d = x.reshape(-1, x.shape[-1])
         x2d = x2d if x2d.is_contiguous() else x2d.contiguous()
         if cap is None:
@@ -291,11 +315,84 @@ class _DPLinear(Function):
         return dx, None, None
 
 
+class _FrozenLinear(Function):
+    """``y = x Wᵀ (+ b)`` with frozen ``W``: forward and data gradient on the library's GEMM, no weight gradient."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        ctx.save_for_backward(weight)
+        ctx.xshape = x.shape
+        return ops.gemm(_rows(x), weight, bias=bias).view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        (weight,) = ctx.saved_tensors
+        if not ctx.needs_input_grad[0]:
+            return None, None, None
+        g2d = gy.reshape(-1, gy.shape[-1])
+        g2d = g2d if g2d.is_contiguous() else g2d.contiguous()
+        return ops.gemm(g2d, weight, b_layout="kn").view(ctx.xshape), None, None
+
+
 def dp_linear(x: torch.Tensor, weight: torch.nn.Parameter, bias: torch.nn.Parameter | None = None) -> torch.Tensor:
     """``x W^T (+ b)`` whose weight gradient is deferred to the active capture."""
     if weight.requires_grad and x.is_cuda and current_capture() is not None:
         return _DPLinear.apply(x, weight, bias)
+    if not weight.requires_grad and (bias is None or not bias.requires_grad) and _own_gemm_ok(x, weight, bias):
+        return _FrozenLinear.apply(x, weight, bias)
     return torch.nn.functional.linear(x, weight, bias)
+
+
+class _GLUUp(Function):
+    """Gated-MLP up-projection ``act(x Wgᵀ) * (x Wuᵀ)`` as ONE GEMM launch with the activation in its epilogue.
+
+    Backward: one element-wise pass gives ``dG`` and ``dU`` from the stored pre-activations, and
+    ``dX = dG·Wg + dU·Wu`` is ONE two-segment GEMM launch.  Trainable ``Wg`` / ``Wu`` hand ``(x, dG)`` and ``(x, dU)``
+    to the capture like any DP linear.
+    """
+
+    @staticmethod
+    def forward(ctx, x, w_gate, w_up, act):
+        x2d = _rows(x)
+        h, g, u = ops.gemm_glu(x2d, w_gate, w_up, act=act)
+        trainable = w_gate.requires_grad or w_up.requires_grad
+        ctx.save_for_backward(g, u, w_gate, w_up, *((x2d,) if trainable else ()))
+        ctx.act, ctx.xshape, ctx.trainable = act, x.shape, trainable
+        return h.view(*x.shape[:-1], w_gate.shape[0])
+
+    @staticmethod
+    def backward(ctx, dh):
+        g, u, w_gate, w_up = ctx.saved_tensors[:4]
+        inter = g.shape[1]
+        d2 = dh.reshape(-1, inter)
+        d2 = d2 if d2.is_contiguous() else d2.contiguous()
+        dg, du = ops.functional.glu_backward(d2, g, u, ctx.act)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = ops.gemm_pair(dg, w_gate, b_layout="kn", a2=du, b2=w_up, b2_layout="kn").view(ctx.xshape)
+        if ctx.trainable:
+            x2d = ctx.saved_tensors[4]
+            cap = current_capture()
+            if cap is None:
+                return dx, dg.t() @ x2d, du.t() @ x2d, None
+            dgc, duc = dg.contiguous(), du.contiguous()
+            if w_gate.requires_grad:
+                cap.add_linear(w_gate, x2d, dgc)
+            if w_up.requires_grad:
+                cap.add_linear(w_up, x2d, duc)
+        return dx, None, None, None
+
+
+def glu_up(x: torch.Tensor, w_gate: torch.nn.Parameter, w_up: torch.nn.Parameter, act: str = "silu") -> torch.Tensor | None:
+    """Fused gate/up projection with the gated activation, or ``None`` when the fused kernel does not apply (the caller
+    then runs the two projections and the activation separately)."""
+    if not (_own_gemm_ok(x, w_gate) and _own_gemm_ok(x, w_up) and w_gate.shape == w_up.shape
+            and w_gate.stride(0) == w_up.stride(0)):
+        return None
+    trainable = w_gate.requires_grad or w_up.requires_grad
+    if trainable and (current_capture() is None or w_gate.requires_grad != w_up.requires_grad):
+        return None
+    return _GLUUp.apply(x, w_gate, w_up, act)
 
 
 class _DPEmbedding(Function):
@@ -364,7 +461,7 @@ class _LoRALinear(Function):
         dx = None
         if ctx.needs_input_grad[0]:
             if FUSE_LORA_GEMM and _lora_gemm_ok(g2d, weight, lora_a, lora_b, None):
-                dx = ops.gemm(g2d, weight, b_layout="kn", a2=q, b2=lora_a.t().contiguous())
+                dx = ops.gemm_pair(g2d, weight, b_layout="kn", a2=q, b2=lora_a, b2_layout="kn")
             else:
                 dx = g2d @ weight
                 dx.addmm_(q, lora_a)
@@ -629,6 +726,10 @@ class FusedDPEngine:
             stats = torch.stack([res.losses.mean(), res.norms.mean(),
                                  (res.norms > sens).float().mean()]).tolist()   # one D2H read
             res.loss, res.grad_norm_mean, res.clip_rate = stats
+        if read_metrics or self.group.world > 1:
+            # With several ranks the status word is read after EVERY step, also for a rank whose Poisson batch was empty
+            # and for callers that skip the metrics: a barrier that gave up made the shard step a no-op on this rank (the
+            # kernels check the same word), and the job must stop here instead of training on with diverged replicas.
             self.group.check("fused DP step")
         if self.adaptive is not None:
             self._adapt(res)

@@ -141,7 +141,7 @@ class _LinearCrossEntropy(Function):
     """
 
     @staticmethod
-    def forward(ctx, hidden, weight, labels, row_weight, chunk, ignore_index, softcap=0.0):
+    def forward(ctx, hidden, weight, labels, row_weight, chunk, ignore_index, softcap=0.0, compact=True):
         R, d = hidden.shape
         V = weight.shape[0]
         out = torch.zeros(R, dtype=torch.float32, device=hidden.device)
@@ -149,33 +149,59 @@ class _LinearCrossEntropy(Function):
         cap = fused.current_capture()
         trainable = weight.requires_grad and cap is not None
         use_kernel = hidden.is_cuda and hidden.dtype == torch.bfloat16
-        if trainable:
-            logits = hidden @ weight.t()
+        own = fused._own_gemm_ok(hidden, weight) and hidden.stride(1) == 1 and hidden.stride(0) % 8 == 0
+
+        def head(h):            # logits = h Wᵀ
+            return ops.gemm(h, weight) if own else h @ weight.t()
+
+        def head_t(dz):         # dh = dlogits W
+            return ops.gemm(dz, weight, b_layout="kn") if own else dz @ weight
+        # fused path: the head GEMM's epilogue produces the cross-entropy statistics straight from tensor memory and
+        # stores the bf16 logits once; a one-pass kernel turns them into gradients in place
+        fused_ce = own and use_kernel
+        need_dh = ctx.needs_input_grad[0]
+
+        def head_ce(h, lab, rw):
+            """(nll, w·dlogits | None) for the rows ``h``."""
+            if fused_ce:
+                nll, lse, z = ops.linear_ce_forward(h, weight, lab, ignore_index=ignore_index, softcap=softcap,
+                                                    store_logits=need_dh or trainable)
+                if z is not None:
+                    ops.linear_ce_dlogits_(z, lab, lse, rw, ignore_index=ignore_index, softcap=softcap)
+                return nll, z
+            z = head(h)
             if use_kernel:
-                nll = cross_entropy_fused_(logits, labels, row_weight, ignore_index=ignore_index, logit_softcapping=softcap)
-            else:
-                nll, logits = _ce_grad_ref(logits, labels, row_weight, ignore_index, softcap)
+                return cross_entropy_fused_(z, lab, rw, ignore_index=ignore_index, logit_softcapping=softcap), z
+            return _ce_grad_ref(z, lab, rw, ignore_index, softcap)
+        if trainable:
+            nll, logits = head_ce(hidden, labels, row_weight)
             out = nll * row_weight
-            dh = logits @ weight
+            dh = head_t(logits)
             ctx.capture_args = (weight, hidden, logits)
         else:
-            if hidden.is_cuda and torch.cuda.is_current_stream_capturing():
-                # graph capture: no host-visible row count; run every row (ignored rows give zero loss and gradient)
-                idx = torch.arange(R, device=hidden.device)
+            if not compact or (hidden.is_cuda and torch.cuda.is_current_stream_capturing()):
+                # no host-visible row count (graph capture), or the caller knows that nearly every row is scored: run
+                # every row (ignored rows give zero loss and gradient) and skip the device-to-host round trip
+                idx = None
             else:
                 valid = (row_weight != 0) & (labels != ignore_index)
                 idx = valid.nonzero(as_tuple=True)[0]
-            for lo in range(0, idx.numel(), chunk):
-                rows = idx[lo:lo + chunk]
-                h = hidden.index_select(0, rows)
-                logits = h @ weight.t()
-                lab, rw = labels.index_select(0, rows), row_weight.index_select(0, rows)
-                if use_kernel:
-                    nll = cross_entropy_fused_(logits, lab, rw, ignore_index=ignore_index, logit_softcapping=softcap)
+            for lo in range(0, R if idx is None else idx.numel(), chunk):
+                if idx is None:                       # contiguous row range: plain slices, no gather / scatter
+                    sl = slice(lo, min(lo + chunk, R))
+                    h, lab, rw = hidden[sl], labels[sl], row_weight[sl]
                 else:
-                    nll, logits = _ce_grad_ref(logits, lab, rw, ignore_index, softcap)
-                out.index_copy_(0, rows, nll * rw)
-                dh.index_copy_(0, rows, (logits @ weight).to(dh.dtype))
+                    rows = idx[lo:lo + chunk]
+                    h, lab, rw = hidden.index_select(0, rows), labels.index_select(0, rows), row_weight.index_select(0, rows)
+                nll, logits = head_ce(h, lab, rw)
+                if idx is None:
+                    out[sl] = nll * rw
+                    if logits is not None:
+                        dh[sl] = head_t(logits).to(dh.dtype)
+                else:
+                    out.index_copy_(0, rows, nll * rw)
+                    if logits is not None:
+                        dh.index_copy_(0, rows, head_t(logits).to(dh.dtype))
             ctx.capture_args = None
         ctx.save_for_backward(dh)
         return out
@@ -188,7 +214,7 @@ class _LinearCrossEntropy(Function):
             cap = fused.current_capture()
             cap.add_linear(weight, hidden if hidden.is_contiguous() else hidden.contiguous(), dlogits)
             ctx.capture_args = None
-        return dh * g.to(dh.dtype)[:, None], None, None, None, None, None, None
+        return dh * g.to(dh.dtype)[:, None], None, None, None, None, None, None, None
 
 
 def _ce_grad_ref(logits, labels, row_weight, ignore_index, softcap=0.0):
@@ -200,13 +226,16 @@ def _ce_grad_ref(logits, labels, row_weight, ignore_index, softcap=0.0):
 
 
 def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, row_weight: torch.Tensor,
-                         *, chunk: int = 8192, ignore_index: int = -100, softcap: float = 0.0) -> torch.Tensor:
+                         *, chunk: int = 8192, ignore_index: int = -100, softcap: float = 0.0, compact: bool = True) -> torch.Tensor:
     """``row_weight[r] · nll(hidden[r] Wᵀ, labels[r])`` for every row, never keeping full logits when ``W`` is frozen;
-    ``softcap`` > 0 applies ``softcap · tanh(logits / softcap)`` before the softmax (Gemma-2 final logit capping)."""
+    ``softcap`` > 0 applies ``softcap · tanh(logits / softcap)`` before the softmax (Gemma-2 final logit capping).
+
+    ``compact=True`` (frozen head) gathers the scored rows first, which costs one device-to-host read of their count;
+    ``compact=False`` runs every row in place — right when the caller already passes (almost) only scored rows."""
     if weight.requires_grad and fused.current_capture() is None and torch.is_grad_enabled():
         # plain autograd (reference engine, non-private training): the head's gradient flows normally
         return ops.cross_entropy(hidden @ weight.t(), labels, ignore_index=ignore_index, logit_softcapping=softcap) * row_weight
-    return _LinearCrossEntropy.apply(hidden, weight, labels, row_weight, chunk, ignore_index, softcap)
+    return _LinearCrossEntropy.apply(hidden, weight, labels, row_weight, chunk, ignore_index, softcap, compact)
 
 
 def per_example_token_weights(labels: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:

@@ -17,6 +17,7 @@ import torch
 from torch import nn
 
 from .. import ops
+from ..engine import fused
 from ..functional import functional_checkpoint
 from .layers import Embedding, LayerNorm, Linear, RMSNorm, linear_cross_entropy, per_example_token_weights
 
@@ -183,6 +184,12 @@ class LlamaMLP(nn.Module):
             raise ValueError(f"unsupported hidden_act {self.act!r}")
 
     def forward(self, x):
+        gp, up_ = self.gate_proj, self.up_proj
+        if gp.lora_A is None and up_.lora_A is None and gp.bias is None and up_.bias is None:
+            # one GEMM launch for both projections with the gated activation in its epilogue
+            h = fused.glu_up(x, gp.weight, up_.weight, self.act)
+            if h is not None:
+                return self.down_proj(h)
         g, u = self.gate_proj(x), self.up_proj(x)
         if self.act == "silu":
             return self.down_proj(ops.swiglu(g, u))
@@ -304,13 +311,26 @@ class LlamaForCausalLM(nn.Module):
         cap = self.config.final_logit_softcap
         return logits if not cap else cap * torch.tanh(logits / cap)
 
-    def per_example_loss(self, input_ids: torch.Tensor, labels: torch.Tensor, position_ids=None) -> torch.Tensor:
-        """Mean NLL over each example's scored tokens; ``labels`` are already aligned (−100 = not scored)."""
+    def per_example_loss(self, input_ids: torch.Tensor, labels: torch.Tensor, position_ids=None, *,
+                         scored_suffix: int | None = None) -> torch.Tensor:
+        """Mean NLL over each example's scored tokens; ``labels`` are already aligned (−100 = not scored).
+
+        ``scored_suffix = s`` is a promise that only the last ``s`` positions of every sequence carry a label (completion-
+        only fine-tuning with a known prompt length, "loss on the last half"): the head and the cross-entropy then run on
+        those ``B·s`` rows alone, with static shapes and without reading the number of scored rows back to the host.
+        """
         B, T = input_ids.shape
-        h = self.hidden_states(input_ids, position_ids).reshape(B * T, -1)
-        w = per_example_token_weights(labels).reshape(-1)
-        rows = linear_cross_entropy(h, self.lm_head.weight, labels.reshape(-1), w, chunk=self.ce_chunk,
-                                    softcap=float(self.config.final_logit_softcap or 0.0))
+        hs = self.hidden_states(input_ids, position_ids)
+        w = per_example_token_weights(labels)
+        softcap = float(self.config.final_logit_softcap or 0.0)
+        if scored_suffix is not None and 0 < scored_suffix <= T:
+            s = int(scored_suffix)
+            h = hs[:, T - s:, :].reshape(B * s, -1)
+            rows = linear_cross_entropy(h, self.lm_head.weight, labels[:, T - s:].reshape(-1), w[:, T - s:].reshape(-1),
+                                        chunk=self.ce_chunk, softcap=softcap, compact=False)
+            return rows.view(B, s).sum(1)
+        rows = linear_cross_entropy(hs.reshape(B * T, -1), self.lm_head.weight, labels.reshape(-1), w.reshape(-1),
+                                    chunk=self.ce_chunk, softcap=softcap)
         return rows.view(B, T).sum(1)
 
 

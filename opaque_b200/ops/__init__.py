@@ -296,6 +296,56 @@ def gemm_glu_ref(a, w_gate, w_up, *, act="silu"):
     return torch.nn.functional.gelu(g, approximate="tanh" if "tanh" in act else "none") * u
 
 
+def linear_ce_forward(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, *, ignore_index: int = -100,
+                      softcap: float = 0.0, label_smoothing: float = 0.0, store_logits: bool = False,
+                      status: StatusWord | None = None, wait_budget_s: float = DEFAULT_WAIT_BUDGET_S):
+    """Output head and token cross-entropy in one tcgen05 kernel: ``(nll, lse, logits | None)``.
+
+    ``hidden [R, d]``, ``weight [V, d]`` (bf16), ``labels [R]`` (int64).  Every 256-column logits tile is reduced to
+    per-row statistics in the GEMM epilogue, straight out of tensor memory; a small second kernel combines the tiles of
+    a row in a fixed order (bit-reproducible).  The logits reach memory only with ``store_logits=True`` (bf16, after
+    the soft cap), which is what :func:`linear_ce_dlogits_` turns into gradients in place.
+    Reference counterpart: packages/opaque-patches/src/opaque/api/patches/kernels/linear_cross_entropy.py:98-208.
+    """
+    _need_bf16(hidden, weight)
+    if hidden.ndim != 2 or weight.ndim != 2 or hidden.stride(1) != 1 or weight.stride(1) != 1 or hidden.shape[1] != weight.shape[1]:
+        raise ValueError("linear_ce_forward: hidden [R, d] and weight [V, d] must be row-major")
+    R, K = hidden.shape
+    V = weight.shape[0]
+    lab = labels.reshape(-1).to(torch.int64).contiguous()
+    if lab.numel() != R:
+        raise ValueError("one label per row is required")
+    tiles = (V + 255) // 256
+    partials = torch.empty(max(R, 1) * tiles * 4, dtype=torch.float32, device=hidden.device)     # scratch of the epilogue
+    nll = torch.empty(R, dtype=torch.float32, device=hidden.device)
+    lse = torch.empty(R, dtype=torch.float32, device=hidden.device)
+    logits = None
+    ldo = 0
+    if store_logits:
+        ldo = (V + 7) // 8 * 8                       # 16-byte aligned rows for the vector stores
+        logits = torch.empty(R, ldo, dtype=torch.bfloat16, device=hidden.device)[:, :V]
+    rc = lib.load().ob_linear_ce_fwd(hidden.data_ptr(), weight.data_ptr(), lab.data_ptr(), lib.ptr(logits), partials.data_ptr(),
+                                     nll.data_ptr(), lse.data_ptr(), R, V, K, hidden.stride(0), weight.stride(0), ldo,
+                                     float(softcap), float(label_smoothing), ignore_index,
+                                     status.ptr() if status else None, wait_budget_s, lib.sm_count(), lib.stream())
+    lib.check(rc, "linear_ce_forward")
+    return nll, lse, logits
+
+
+def linear_ce_dlogits_(logits: torch.Tensor, labels: torch.Tensor, lse: torch.Tensor, row_weight: torch.Tensor | None = None, *,
+                       ignore_index: int = -100, softcap: float = 0.0, label_smoothing: float = 0.0) -> torch.Tensor:
+    """In place: the logits stored by :func:`linear_ce_forward` become ``row_weight · ∂nll/∂(raw logits)`` (one read, one write)."""
+    _need_bf16(logits)
+    if logits.ndim != 2 or logits.stride(1) != 1:
+        raise ValueError("logits must be a row-major matrix")
+    lab = labels.reshape(-1).to(torch.int64).contiguous()
+    rc = lib.load().ob_linear_ce_dlogits(logits.data_ptr(), lab.data_ptr(), lse.data_ptr(), lib.ptr(row_weight), logits.shape[0],
+                                         logits.shape[1], logits.stride(0), float(softcap), float(label_smoothing), ignore_index,
+                                         lib.stream())
+    lib.check(rc, "linear_ce_dlogits")
+    return logits
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, b_layout: str = "nk", a2: torch.Tensor | None = None,
          b2: torch.Tensor | None = None, bias: torch.Tensor | None = None, group_offs: torch.Tensor | None = None,
          out: torch.Tensor | None = None, status: StatusWord | None = None,
@@ -447,21 +497,26 @@ def embedding_wgrad(g: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None
     lib.check(rc, "embedding_wgrad")
 
 
-def push_grad_(local: torch.Tensor, peer_table: torch.Tensor, shard_elems: int) -> None:
-    """Add a full-length local fp32 gradient into the owners' shards (peer reductions) and clear it."""
+def push_grad_(local: torch.Tensor, peer_table: torch.Tensor, shard_elems: int, *, status: StatusWord | None = None) -> None:
+    """Add a full-length local fp32 gradient into the owners' shards (peer reductions) and clear it.
+
+    With a ``status`` word that is already set (a bounded wait expired earlier) the kernel does nothing."""
     if local.dtype != torch.float32 or not local.is_contiguous() or local.numel() % 4 or shard_elems % 4:
         raise ValueError("push_grad_: contiguous fp32 buffer with a length and shard size that are multiples of 4")
-    rc = lib.load().ob_push_grad(local.data_ptr(), local.numel(), peer_table.data_ptr(), shard_elems, lib.sm_count(), lib.stream())
+    rc = lib.load().ob_push_grad(local.data_ptr(), local.numel(), peer_table.data_ptr(), shard_elems,
+                                 status.ptr() if status else None, lib.sm_count(), lib.stream())
     lib.check(rc, "push_grad")
 
 
 def shard_step(*, grad, master, m, v, params_local=None, peer_params=None, world=1, global_offset=0, seed=0,
                noise_std=0.0, inv_normalize=1.0, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, step=1,
                phi_hat=0.0, decoupled_wd=True, ftrl_state=None, ftrl_mode=0, ftrl_coef: Sequence[float] = (),
-               nbuf=0, ring_head=0, noisy_out=None, skip_update=False) -> None:
+               nbuf=0, ring_head=0, noisy_out=None, skip_update=False, status: StatusWord | None = None) -> None:
     """One fused pass over a shard: noise, AdamW(-BC) on fp32 masters, bf16 write-back to all ranks.
 
-    ``step`` is 1-based; ``phi_hat`` is the bias-corrected noise-variance EMA (0 disables the correction).
+    ``step`` is 1-based; ``phi_hat`` is the bias-corrected noise-variance EMA (0 disables the correction).  With a
+    ``status`` word that is already set (the gradient barrier before this call gave up) the kernel touches nothing:
+    a partially reduced shard is neither noised, applied nor cleared.
     """
     coef = torch.tensor(list(ftrl_coef) or [0.0], dtype=torch.float32)
     import ctypes
@@ -472,7 +527,7 @@ def shard_step(*, grad, master, m, v, params_local=None, peer_params=None, world
         float(noise_std), float(inv_normalize), ftrl_mode, nbuf, ring_head, ctypes.cast(arr, ctypes.c_void_p),
         len(coef), float(lr), float(betas[0]), float(betas[1]), float(eps), float(weight_decay),
         1.0 - betas[0] ** step, 1.0 - betas[1] ** step, float(phi_hat), int(decoupled_wd), int(skip_update),
-        lib.sm_count(), lib.stream())
+        status.ptr() if status else None, lib.sm_count(), lib.stream())
     lib.check(rc, "shard_step")
 
 
@@ -481,7 +536,7 @@ from .functional import (activation, cross_entropy, cross_entropy_ref, fused_add
                          layer_norm, merge_heads3, plain_torch_ops, rms_norm, rms_norm_ref, rope_qk, rope_qk_ref, rope_tables, rows_group_sum_, swiglu)
 
 __all__ = [
-    "gemm", "gemm_pair", "gemm_glu", "gemm_glu_ref", "gemm_ref", "ghost_set_wide", "push_grad_", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_", "merge_heads3",
+    "gemm", "gemm_pair", "gemm_glu", "linear_ce_forward", "linear_ce_dlogits_", "gemm_glu_ref", "gemm_ref", "ghost_set_wide", "push_grad_", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_", "merge_heads3",
     "DeviceWaitTimeout", "KernelLibraryError", "StatusWord", "clip_weighted_sum", "cross_entropy",
     "cross_entropy_ref", "embedding_wgrad", "fused_add_rms_norm", "geglu", "ghost_norm", "ghost_norm_ref", "glu_ref",
     "philox_normal_add_", "pick_block_n", "pick_splits", "rms_norm", "rms_norm_ref", "rope_qk", "rope_qk_ref",

@@ -39,6 +39,16 @@ int ob_gemm_pair(const void* a, const void* b, const void* b_up, const void* a2,
                  const void* bias, void* out, void* out_gate, void* out_up, long long rows_a, int N, int K1, int K2,
                  long long lda, long long ldb, long long lda2, long long ldb2, long long ldo, int b_kn, int b2_kn, int glu,
                  int glu_act, int* status, double wait_budget_s, int num_sms, void* stream);
+// Output head fused with cross-entropy statistics on CTA pairs: logits tiles stay in tensor memory, per-tile partials
+// (scratch: rows * ceil(N / 256) float4) are combined in a fixed order into nll[rows], lse[rows]; `logits_out` (optional)
+// receives the bf16 soft-capped logits for the backward pass.
+int ob_linear_ce_fwd(const void* hidden, const void* weight, const long long* labels, void* logits_out, float* partials,
+                     float* nll, float* lse, long long rows, int N, int K, long long ldh, long long ldw, long long ldo,
+                     float softcap, float smoothing, long long ignore_index, int* status, double wait_budget_s,
+                     int num_sms, void* stream);
+// In place on those stored logits: z <- row_weight * d nll / d (raw logits), one read and one write per element.
+int ob_linear_ce_dlogits(void* logits, const long long* labels, const float* lse, const float* row_weight, long long rows,
+                         int N, long long ld, float softcap, float smoothing, long long ignore_index, void* stream);
 unsigned int ob_debug_idesc_bf16(int m, int n, int a_mn_major, int b_mn_major);
 
 // LayerNorm over the last dimension (bf16 in/out, fp32 statistics saved per row).

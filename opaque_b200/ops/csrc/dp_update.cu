@@ -89,7 +89,10 @@ clip_weighted_sum_kernel(const float* __restrict__ g, const float* __restrict__ 
 // owners' shards (one 16-byte reduction per four coordinates, 7/8 of them over NVLink at 8 GPUs) and clears it.
 // Blocks that are all zero (frozen ranges, padding) send nothing.
 __global__ void __launch_bounds__(256)
-push_grad_kernel(float* __restrict__ local, long long total, float* const* peer_out, long long shard_elems) {
+push_grad_kernel(float* __restrict__ local, long long total, float* const* peer_out, long long shard_elems,
+                 const int* status) {
+  // a bounded wait that ran out earlier leaves the job in an unknown state: keep the accumulated gradient where it is
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
   const long long nv = total >> 2;
   for (long long i = blockIdx.x * 256LL + threadIdx.x; i < nv; i += gridDim.x * 256LL) {
     float4* src = reinterpret_cast<float4*>(local) + i;
@@ -152,6 +155,7 @@ struct ShardStepParams {
   // AdamW-BC
   float lr, b1, b2, eps, wd, bc1, bc2, phi_hat;
   int decoupled_wd, skip_update;
+  const int* status;       // non-zero: a bounded wait expired earlier in this step; the kernel does nothing
 };
 
 __device__ __forceinline__ void ld8(const float* src, float* dst) {
@@ -231,6 +235,10 @@ __device__ __forceinline__ void ftrl_apply8(const ShardStepParams& p, long long 
 
 __global__ void __launch_bounds__(256)
 shard_step_kernel(const ShardStepParams p) {
+  // The gradient barrier before this kernel may have given up (status != 0): the shard is then not fully reduced, and
+  // adding noise to it, stepping and clearing it would release and apply a partial sum.  Leave every buffer untouched;
+  // the host reads the status word after the step and raises.
+  if (p.status != nullptr && *reinterpret_cast<const volatile int*>(p.status) != 0) return;
   // each thread owns 8 consecutive coordinates (two Philox blocks, one 16-byte bf16 store per peer)
   const long long nv = (p.n + 7) >> 3;
   for (long long i = blockIdx.x * 256LL + threadIdx.x; i < nv; i += gridDim.x * 256LL) {
@@ -440,11 +448,11 @@ extern "C" int ob_clip_weighted_sum(const float* g, const float* c, int E, long 
   return OB_CHECK_LAUNCH();
 }
 
-extern "C" int ob_push_grad(float* local, long long total, float* const* peer_out, long long shard_elems, int sms,
-                            void* stream) {
+extern "C" int ob_push_grad(float* local, long long total, float* const* peer_out, long long shard_elems,
+                            const int* status, int sms, void* stream) {
   if (total <= 0) return 0;
   if ((total & 3) || (shard_elems & 3) || peer_out == nullptr) return -2;
-  push_grad_kernel<<<grid_for(total / 4, sms), 256, 0, static_cast<cudaStream_t>(stream)>>>(local, total, peer_out, shard_elems);
+  push_grad_kernel<<<grid_for(total / 4, sms), 256, 0, static_cast<cudaStream_t>(stream)>>>(local, total, peer_out, shard_elems, status);
   return OB_CHECK_LAUNCH();
 }
 
@@ -463,7 +471,8 @@ extern "C" int ob_shard_step(float* grad, float* master, float* m, float* v, flo
                              long long global_offset, int world, unsigned long long seed, float noise_std,
                              float inv_normalize, int ftrl_mode, int nbuf, int ring_head, const float* coef,
                              int ncoef, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
-                             float phi_hat, int decoupled_wd, int skip_update, int sms, void* stream) {
+                             float phi_hat, int decoupled_wd, int skip_update, const int* status, int sms,
+                             void* stream) {
   if (n <= 0) return 0;
   if (global_offset & 7) return -2;
   if (ncoef > 16 || nbuf > 8) return -3;
@@ -478,6 +487,7 @@ extern "C" int ob_shard_step(float* grad, float* master, float* m, float* v, flo
   for (int i = 0; i < 16; ++i) p.coef[i] = (coef && i < ncoef) ? coef[i] : 0.f;
   p.lr = lr; p.b1 = b1; p.b2 = b2; p.eps = eps; p.wd = wd; p.bc1 = bc1; p.bc2 = bc2; p.phi_hat = phi_hat;
   p.decoupled_wd = decoupled_wd; p.skip_update = skip_update;
+  p.status = status;
   shard_step_kernel<<<grid_for((n + 7) / 8, sms), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return OB_CHECK_LAUNCH();
 }

@@ -35,7 +35,13 @@ constexpr int GP_BM = 128;           // rows of M per CTA (256 per pair)
 constexpr int GP_BN = 256;           // accumulator columns per pair tile
 constexpr int GP_BNH = 128;          // columns of N whose B rows one CTA stages
 constexpr int GP_BK = 64;
-constexpr int GP_STAGES = 6;
+#ifndef OB_PAIR_STAGES
+#define OB_PAIR_STAGES 7
+#endif
+#ifndef OB_PAIR_RELAXED
+#define OB_PAIR_RELAXED 0
+#endif
+constexpr int GP_STAGES = OB_PAIR_STAGES;
 constexpr int GP_A_BYTES = GP_BM * GP_BK * 2;
 constexpr int GP_B_BYTES = GP_BNH * GP_BK * 2;
 constexpr int GP_STAGE_BYTES = GP_A_BYTES + GP_B_BYTES;
@@ -43,7 +49,7 @@ constexpr int GP_THREADS = 192;
 constexpr int GP_GROUP_M = 8;        // pair tiles (256 rows each) per raster band
 constexpr int GP_SMEM = GP_STAGES * GP_STAGE_BYTES + 256 + 1024;
 
-enum : int { GP_EPI_STORE = 0, GP_EPI_GLU = 1 };
+enum : int { GP_EPI_STORE = 0, GP_EPI_GLU = 1, GP_EPI_CE = 2 };
 
 struct PairParams {
   int M, N, K1, K2;
@@ -54,6 +60,10 @@ struct PairParams {
   __nv_bfloat16* out_up;
   const __nv_bfloat16* bias;         // STORE only
   int act;                           // GLU: 0 silu, 1 gelu (erf), 2 gelu (tanh)
+  // CE epilogue (output head + cross-entropy statistics; `out` optional: the bf16, soft-capped logits)
+  const long long* labels;           // [M]
+  float4* ce_partials;               // [M, tiles_n]: (max, sum exp(z - max), z[label] or 0, sum z) over the tile's columns
+  float softcap;                     // > 0: z = softcap * tanh(z / softcap)
   int* status;
   unsigned long long wait_budget_ns;
 };
@@ -110,6 +120,31 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mas
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                ::"r"(smem_u32(bar)), "h"(cta_mask)
                : "memory");
+}
+
+// Wait used by roles that are far from the critical path (epilogue warps waiting a whole main loop for their tile): the
+// polling thread sleeps between tries, which leaves issue slots and power to the tensor pipe.
+__device__ __forceinline__ bool mbar_wait_idle(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                               int code, uint64_t budget_ns) {
+#if OB_PAIR_RELAXED
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    __nanosleep(OB_PAIR_RELAXED);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 0x3f) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > budget_ns) {
+        *abort_flag = 1;
+        set_error(status, code);
+        return false;
+      }
+    }
+  }
+#else
+  return mbar_wait(bar, parity, abort_flag, status, code, budget_ns);
+#endif
 }
 
 struct GpItem {
@@ -303,7 +338,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
       const GpItem it = gp_decode(w, tiles_m, tiles_n, rank);
       const int as = acc_iter & 1;
-      if (!mbar_wait(&tmem_full[as], (acc_iter >> 1) & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL, budget)) {
+      if (!mbar_wait_idle(&tmem_full[as], (acc_iter >> 1) & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL, budget)) {
         ok = false;
         break;
       }
@@ -327,6 +362,49 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
           if (row < p.M) gp_store32(orow + nc, v, vec_ok, p.N - nc);
         }
+      } else if constexpr (EPI == GP_EPI_CE) {
+        // Output head: the logits tile never leaves the SM unless `out` asks for it.  Each thread owns one row and folds
+        // the tile's 256 columns into (max, sum exp, label logit, plain sum); the per-tile partials are combined per row
+        // in a fixed order by lce_combine_kernel, so the result does not depend on which CTA ran which tile.
+        const int n0 = it.nt * GP_BN;
+        const long long label = row < p.M ? p.labels[row] : -1;
+        float m = -INFINITY, ssum = 0.f, zlab = 0.f, ztot = 0.f;
+        __nv_bfloat16* orow = p.out != nullptr ? p.out + static_cast<long long>(row) * p.ldo : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < GP_BN / 32; ++c) {
+          const int nc = n0 + c * 32;
+          if (nc >= p.N) break;
+          float v[32];
+          tmem_ld32(t_row + c * 32, v);
+          tmem_ld_wait();
+          float lm = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float z = v[j];
+            if (p.softcap > 0.f) z = p.softcap * tanhf(z / p.softcap);
+            // statistics are taken from the value the backward pass will read: the bf16-rounded logit when it is stored
+            if (orow != nullptr) z = __bfloat162float(__float2bfloat16_rn(z));
+            const bool in = nc + j < p.N;
+            v[j] = in ? z : -INFINITY;
+            if (in) {
+              ztot += z;
+              lm = fmaxf(lm, z);
+              if (nc + j == label) zlab = z;
+            }
+          }
+          if (lm > m) {
+            ssum *= __expf(m - lm);
+            m = lm;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) ssum += __expf(v[j] - m);      // exp(-inf) = 0 for masked columns
+          if (orow != nullptr && row < p.M) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = nc + j < p.N ? v[j] : 0.f;
+            gp_store32(orow + nc, v, vec_ok, p.N - nc);
+          }
+        }
+        if (row < p.M) p.ce_partials[static_cast<long long>(row) * tiles_n + it.nt] = make_float4(m, ssum, zlab, ztot);
       } else {
         const int nh = p.N / 2;
         const int n0 = it.nt * GP_BNH;
@@ -381,6 +459,94 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+// One warp per row: combines the per-tile partials of the CE epilogue in a fixed order.
+__global__ void __launch_bounds__(256)
+lce_combine_kernel(const float4* __restrict__ partials, const long long* __restrict__ labels, float* __restrict__ nll,
+                   float* __restrict__ lse_out, long long rows, int tiles_n, int V, float smoothing,
+                   long long ignore_index) {
+  const long long row = (blockIdx.x * 256LL + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const long long label = labels[row];
+  const bool ignored = label == ignore_index || label < 0 || label >= V;
+  float m = -INFINITY, s = 0.f, zl = 0.f, zt = 0.f;
+  for (int t = lane; t < tiles_n; t += 32) {
+    const float4 q = partials[row * tiles_n + t];
+    if (q.x > m) {
+      s = s * __expf(m - q.x) + q.y;
+      m = q.x;
+    } else if (q.x > -INFINITY) {
+      s += q.y * __expf(q.x - m);
+    }
+    zl += q.z;
+    zt += q.w;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    const float mm = fmaxf(m, m2);
+    s = (m > -INFINITY ? s * __expf(m - mm) : 0.f) + (m2 > -INFINITY ? s2 * __expf(m2 - mm) : 0.f);
+    m = mm;
+    zl += __shfl_xor_sync(0xffffffffu, zl, o);
+    zt += __shfl_xor_sync(0xffffffffu, zt, o);
+  }
+  if (lane == 0) {
+    const float lse = m + __logf(s);
+    float loss = lse - zl;
+    if (smoothing > 0.f) loss = (1.f - smoothing) * loss + smoothing * (lse - zt / V);
+    nll[row] = ignored ? 0.f : loss;
+    if (lse_out) lse_out[row] = ignored ? 0.f : lse;
+  }
+}
+
+// In place: stored (soft-capped, bf16) logits -> w_row * d nll / d raw logits, one read and one write per element.
+__global__ void __launch_bounds__(256)
+lce_dlogits_kernel(__nv_bfloat16* __restrict__ z, const long long* __restrict__ labels, const float* __restrict__ lse,
+                   const float* __restrict__ row_weight, int V, long long ld, float softcap, float smoothing,
+                   long long ignore_index) {
+  const long long row = blockIdx.x;
+  __nv_bfloat16* zr = z + row * ld;
+  const long long label = labels[row];
+  const bool ignored = label == ignore_index || label < 0 || label >= V;
+  const float w = ignored ? 0.f : (row_weight ? row_weight[row] : 1.f);
+  const float l = lse[row];
+  const float sm = smoothing / V;
+  const bool vec = (ld & 7) == 0 && (reinterpret_cast<uintptr_t>(z) & 15) == 0;
+  const int v_vec = vec ? (V & ~7) : 0;
+  for (int i = threadIdx.x; i < (v_vec >> 3); i += 256) {
+    uint4 pk = reinterpret_cast<uint4*>(zr)[i];
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+    if (w == 0.f) {
+      pk = make_uint4(0u, 0u, 0u, 0u);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(h[j]);
+        float g0 = __expf(f.x - l) - sm, g1 = __expf(f.y - l) - sm;
+        if (i * 8 + 2 * j == label) g0 -= 1.f - smoothing;
+        if (i * 8 + 2 * j + 1 == label) g1 -= 1.f - smoothing;
+        if (softcap > 0.f) {
+          const float t0 = f.x / softcap, t1 = f.y / softcap;
+          g0 *= 1.f - t0 * t0;
+          g1 *= 1.f - t1 * t1;
+        }
+        h[j] = __floats2bfloat162_rn(w * g0, w * g1);
+      }
+    }
+    reinterpret_cast<uint4*>(zr)[i] = pk;
+  }
+  for (int i = v_vec + threadIdx.x; i < V; i += 256) {
+    const float f = __bfloat162float(zr[i]);
+    float g = __expf(f - l) - sm;
+    if (i == label) g -= 1.f - smoothing;
+    if (softcap > 0.f) {
+      const float t = f / softcap;
+      g *= 1.f - t * t;
+    }
+    zr[i] = __float2bfloat16_rn(w * g);
   }
 }
 
@@ -464,7 +630,7 @@ extern "C" int ob_gemm_pair(const void* a, const void* b, const void* b_up, cons
     clusters_glu = pair_grid(reinterpret_cast<const void*>(gemm_pair_kernel<GP_EPI_GLU>), num_sms);
     configured = true;
   }
-  PairParams p;
+  PairParams p = {};
   p.M = static_cast<int>(rows_a);
   p.N = N; p.K1 = K1; p.K2 = K2;
   p.kn1 = b_kn; p.kn2 = b2_kn;
@@ -492,4 +658,64 @@ extern "C" int ob_gemm_pair(const void* a, const void* b, const void* b_up, cons
 // Bit patterns of the descriptors the tensor-core kernels build, for host-side checks.
 extern "C" unsigned int ob_debug_idesc_bf16(int m, int n, int a_mn_major, int b_mn_major) {
   return ob::make_idesc_bf16(m, n, a_mn_major, b_mn_major);
+}
+
+// Output head fused with the cross-entropy statistics:  logits = hidden[M, K] * weight[N, K]^T on CTA pairs; the epilogue
+// folds every 256-column logits tile into per-row partials (scratch `partials`: M * ceil(N / 256) float4) and a second
+// small kernel combines them in a fixed order into nll[M] and lse[M].  The logits themselves are written (bf16, after the
+// soft cap) only when `logits_out` is given.  softcap > 0: z = softcap * tanh(z / softcap).  Rows whose label is
+// `ignore_index` or outside [0, N) get nll = lse = 0.
+extern "C" int ob_linear_ce_fwd(const void* hidden, const void* weight, const long long* labels, void* logits_out,
+                                float* partials, float* nll, float* lse, long long rows, int N, int K, long long ldh,
+                                long long ldw, long long ldo, float softcap, float smoothing, long long ignore_index,
+                                int* status, double wait_budget_s, int num_sms, void* stream) {
+  using namespace ob;
+  if (rows <= 0 || N <= 0 || K <= 0) return 0;
+  if (rows > 0x7fffffffLL - 2 * GP_BM) return -50;
+  if (labels == nullptr || partials == nullptr || nll == nullptr) return -56;
+  CUtensorMap ma, mb;
+  int rc = make_bf16_map_2d(&ma, hidden, rows, K, ldh, GP_BK, GP_BM);
+  if (rc) return rc;
+  rc = make_bf16_map_2d(&mb, weight, N, K, ldw, GP_BK, GP_BNH);
+  if (rc) return rc;
+  static bool configured = false;
+  static int clusters_ce = 0;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_pair_kernel<GP_EPI_CE>, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_SMEM) != cudaSuccess)
+      return -54;
+    clusters_ce = pair_grid(reinterpret_cast<const void*>(gemm_pair_kernel<GP_EPI_CE>), num_sms);
+    configured = true;
+  }
+  PairParams p = {};
+  p.M = static_cast<int>(rows);
+  p.N = N; p.K1 = K; p.K2 = 0;
+  p.out = static_cast<__nv_bfloat16*>(logits_out);
+  p.ldo = ldo;
+  p.labels = labels;
+  p.ce_partials = reinterpret_cast<float4*>(partials);
+  p.softcap = softcap;
+  p.status = status;
+  p.wait_budget_ns = static_cast<unsigned long long>(wait_budget_s * 1e9);
+  const long long tiles_m = (rows + 2 * GP_BM - 1) / (2 * GP_BM);
+  const int tiles_n = (N + GP_BN - 1) / GP_BN;
+  const long long total = tiles_m * tiles_n;
+  const int clusters = static_cast<int>(total < clusters_ce ? total : clusters_ce);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  gemm_pair_kernel<GP_EPI_CE><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mb, ma, mb, mb, p);
+  if (cudaGetLastError() != cudaSuccess) return -55;
+  const long long warps = rows;
+  lce_combine_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, st>>>(
+      reinterpret_cast<const float4*>(partials), labels, nll, lse, rows, tiles_n, N, smoothing, ignore_index);
+  return cudaGetLastError() == cudaSuccess ? 0 : -57;
+}
+
+// In place on the logits stored by ob_linear_ce_fwd: z <- row_weight * d nll / d (raw logits).
+extern "C" int ob_linear_ce_dlogits(void* logits, const long long* labels, const float* lse, const float* row_weight,
+                                    long long rows, int N, long long ld, float softcap, float smoothing,
+                                    long long ignore_index, void* stream) {
+  using namespace ob;
+  if (rows <= 0 || N <= 0) return 0;
+  lce_dlogits_kernel<<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(logits), labels, lse, row_weight, N, ld, softcap, smoothing, ignore_index);
+  return cudaGetLastError() == cudaSuccess ? 0 : -58;
 }

@@ -317,6 +317,21 @@ class _GLU(Function):
         return dg.view(shape), du.view(shape), None
 
 
+_GLU_ACT_CODE = {"silu": ACTIVATION_SWIGLU, "gelu": ACTIVATION_GEGLU_EXACT, "gelu_pytorch_tanh": ACTIVATION_GEGLU_APPROX,
+                 "gelu_tanh": ACTIVATION_GEGLU_APPROX}
+
+
+def glu_backward(dh: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, act: str = "silu"):
+    """``(dGate, dUp)`` of ``act(gate) * up`` for row-major bf16 matrices (views of one ``[rows, 2I]`` buffer)."""
+    I = gate.shape[1]
+    both = torch.empty(gate.shape[0], 2 * I, dtype=gate.dtype, device=gate.device)
+    dg, du = both[:, :I], both[:, I:]
+    rc = lib.load().ob_glu_bwd(dh.data_ptr(), gate.data_ptr(), up.data_ptr(), dg.data_ptr(), du.data_ptr(), gate.shape[0], I,
+                               gate.stride(0), 2 * I, _GLU_ACT_CODE[act], lib.sm_count(), lib.stream())
+    lib.check(rc, "glu_bwd")
+    return dg, du
+
+
 def swiglu(gate, up):
     """``silu(gate)·up``."""
     if _use_kernel(gate, up) and gate.shape[-1] % 8 == 0:

@@ -22,13 +22,15 @@ _SIGNATURES = {
     "ob_ghost_norm": [P, P, P, I, I, I, I, LL, LL, P, P, P, LL, P, D, I, P],
     "ob_gemm_tn": [P, P, P, P, P, P, LL, I, I, I, LL, LL, LL, LL, LL, I, P, I, P, D, I, P],
     "ob_gemm_pair": [P, P, P, P, P, P, P, P, P, P, LL, I, I, I, LL, LL, LL, LL, LL, I, I, I, I, P, D, I, P],
+    "ob_linear_ce_fwd": [P, P, P, P, P, P, P, LL, I, I, LL, LL, LL, F, F, LL, P, D, I, P],
+    "ob_linear_ce_dlogits": [P, P, P, P, LL, I, LL, F, F, LL, P],
     "ob_layernorm_fwd": [P, P, P, P, P, P, LL, I, F, P],
     "ob_layernorm_bwd_dx": [P, P, P, P, P, P, LL, I, P],
     "ob_rows_group_sum": [P, P, P, P, I, I, I, LL, P, LL, I, P, LL, P],
     "ob_merge_heads3": [P, P, P, P, P, LL, I, I, I, I, P],
     "ob_activation": [P, P, P, LL, I, I, P],
     "ob_ghost_set_wide": [I],
-    "ob_push_grad": [P, LL, P, LL, I, P],
+    "ob_push_grad": [P, LL, P, LL, P, I, P],
     "ob_rmsnorm_fwd": [P, P, P, P, P, P, LL, I, F, F, I, P],
     "ob_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, LL, I, F, P],
     "ob_glu_fwd": [P, P, P, LL, I, LL, I, I, P],
@@ -39,7 +41,7 @@ _SIGNATURES = {
     "ob_rows_sumsq": [P, I, LL, LL, P, I, P],
     "ob_clip_weighted_sum": [P, P, I, LL, LL, P, P, LL, LL, I, P],
     "ob_embedding_wgrad": [P, P, P, LL, I, LL, P, P, LL, LL, I, P],
-    "ob_shard_step": [P, P, P, P, P, P, P, P, LL, LL, I, ULL, F, F, I, I, I, P, I, F, F, F, F, F, F, F, F, I, I, I, P],
+    "ob_shard_step": [P, P, P, P, P, P, P, P, LL, LL, I, ULL, F, F, I, I, I, P, I, F, F, F, F, F, F, F, F, I, I, P, I, P],
     "ob_peer_barrier": [P, P, I, I, I, P, D, P],
     "ob_ipc_alloc": [P, LL],
     "ob_ipc_free": [P],
@@ -63,7 +65,9 @@ def load() -> ctypes.CDLL:
         if not _build.KERNEL_LIB.exists():
             raise KernelLibraryError(f"sm_100a kernel library is missing and could not be built: {exc}") from exc
         path = _build.KERNEL_LIB
-    lib = ctypes.CDLL(str(path))
+    import os
+    override = os.environ.get("OPAQUE_B200_KERNEL_LIB")          # a differently built library (kernel experiments)
+    lib = ctypes.CDLL(override or str(path))
     for name, argtypes in _SIGNATURES.items():
         fn = getattr(lib, name)
         fn.argtypes = argtypes

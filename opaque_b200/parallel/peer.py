@@ -109,7 +109,14 @@ class PeerGroup:
     """The ranks of one node that share peer memory, plus their flag barrier."""
 
     def __init__(self, device: torch.device | None = None, pg=None, *, use_ipc: bool | None = None,
-                 wait_budget_s: float = 5.0):
+                 wait_budget_s: float | None = None):
+        """``wait_budget_s``: how long a rank waits at the device barrier for its peers before it gives up with a
+        status code (default 30 s, or the environment variable ``OPAQUE_B200_PEER_WAIT_S``).  It has to exceed the
+        worst host-side skew between ranks inside one step — a first CUDA-graph capture, an out-of-memory retry, a
+        checkpoint write on one rank — and stays far below a collective-library timeout."""
+        if wait_budget_s is None:
+            import os
+            wait_budget_s = float(os.environ.get("OPAQUE_B200_PEER_WAIT_S", "30"))
         self.pg = pg if pg is not None else (dist.group.WORLD if dist.is_initialized() else None)
         self.world = dist.get_world_size(self.pg) if self.pg is not None else 1
         self.rank = dist.get_rank(self.pg) if self.pg is not None else 0

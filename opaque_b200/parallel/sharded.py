@@ -165,7 +165,7 @@ class FlatSpace:
     def push_local_gradient(self) -> None:
         """``accumulate="local"``: reduce this rank's accumulated gradient into the owners' shards (before the barrier)."""
         if self.grad_full is not None:
-            ops.push_grad_(self.grad_full, self.grad.table, self.shard)
+            ops.push_grad_(self.grad_full, self.grad.table, self.shard, status=self.group.status)
 
     @torch.no_grad()
     def gather_full(self, shard_tensor: torch.Tensor) -> torch.Tensor:
@@ -257,7 +257,7 @@ class ShardedDPOptimizer:
             eps=self.cfg.eps, weight_decay=self.cfg.weight_decay, step=t, phi_hat=phi_hat,
             decoupled_wd=self.cfg.decoupled_weight_decay, ftrl_state=self.ftrl_state, ftrl_mode=self.mode,
             ftrl_coef=self.coef, nbuf=self.nbuf, ring_head=(self.step_count % self.nbuf) if self.mode in (2, 3) else 0,
-            noisy_out=noisy_out, skip_update=skip_update)
+            noisy_out=noisy_out, skip_update=skip_update, status=g.status if g.world > 1 else None)
         if ev:
             ev[2].record()
         g.barrier()

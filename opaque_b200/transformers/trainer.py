@@ -826,6 +826,12 @@ class DPTrainer:
                                     gamma=float(a.clipping_kwargs.get("gamma", 0.01)), group_of=group_of, adaptive=adaptive,
                                     cuda_graph=a.dp_cuda_graph)
         self._graphs_ready = not a.dp_cuda_graph
+        # host-side leave notices: a rank that stops between steps tells the others through the rendezvous store, so they
+        # raise before their next device barrier instead of waiting for its flag until the bounded wait runs out
+        self._liveness = None
+        if is_distributed() and self._fused.group.world > 1:
+            from ..parallel.peer import Liveness
+            self._liveness = Liveness(self._fused.group.rank, self._fused.group.world)
 
     # ---- data -----------------------------------------------------------------------------------
     def get_train_dataloader(self):
@@ -917,6 +923,8 @@ class DPTrainer:
             named[n].copy_(v)
 
     def _fused_step(self, batch, sp) -> dict[str, float]:
+        if getattr(self, "_liveness", None) is not None:
+            self._liveness.check()
         self._call("on_pre_optimizer_step")
         if not self._graphs_ready and batch["input_ids"].shape[0]:
             self._fused.prepare_graphs(self.model.per_example_loss, {"input_ids": batch["input_ids"], "labels": batch["labels"]})

@@ -603,7 +603,8 @@ class FusedDPEngine:
         return StepResult(0.0, 0.0, 0.0, 0, None, None)
 
     def _microbatch(self, loss_fn, sub: dict[str, torch.Tensor], mb: int):
-        tokens = sub["input_ids"].shape[1] if "input_ids" in sub else 1
+        # rows of one privacy unit: a sequence [T], or several sequences that belong together ([2, T]: a preference pair)
+        tokens = math.prod(sub["input_ids"].shape[1:]) if "input_ids" in sub else 1
         cap = Capture(self, mb, tokens)
         if not self._coverage_checked:
             for _, p in self._named_trainable:          # stale gradients of earlier, non-private use would trip the check below

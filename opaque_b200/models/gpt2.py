@@ -107,6 +107,11 @@ class GPT2LMHeadModel(nn.Module):
     def forward(self, input_ids):
         return self.hidden_states(input_ids) @ self.wte.weight.t()
 
+    def token_nll(self, input_ids, labels):
+        """Per-token negative log-likelihood ``[N, T]`` (0 where ignored)."""
+        from .llama import _token_nll
+        return _token_nll(self, self.wte.weight, input_ids, labels)
+
     def per_example_loss(self, input_ids, labels):
         B, T = input_ids.shape
         h = self.hidden_states(input_ids).reshape(B * T, -1)

@@ -12,6 +12,7 @@ here the modules are owned by the framework and keep HF parameter names so check
 """
 from __future__ import annotations
 
+import contextlib
 import math
 
 import torch
@@ -21,6 +22,22 @@ from torch.autograd import Function
 from .. import ops
 from ..engine import fused
 from ..ops.functional import cross_entropy_fused_, cross_entropy_ref
+
+
+_ADAPTERS_OFF = 0
+
+
+@contextlib.contextmanager
+def adapters_disabled():
+    """Run the enclosed forward passes WITHOUT the LoRA factors: the frozen base model of an adapter-tuned policy, which
+    is the reference model of preference optimisation — no second copy of the weights
+    (reference: packages/opaque-alignment/src/opaque/api/alignment/dpo/reference/_adapter.py)."""
+    global _ADAPTERS_OFF
+    _ADAPTERS_OFF += 1
+    try:
+        yield
+    finally:
+        _ADAPTERS_OFF -= 1
 
 
 class Linear(nn.Module):
@@ -51,7 +68,7 @@ class Linear(nn.Module):
                 self.bias.requires_grad_(False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if self.lora_A is not None:
+        if self.lora_A is not None and not _ADAPTERS_OFF:
             return fused.lora_linear(x, self.weight, self.bias, self.lora_A, self.lora_B, self.scaling)
         return fused.dp_linear(x, self.weight, self.bias)
 
@@ -212,6 +229,10 @@ class _LinearCrossEntropy(Function):
         if ctx.capture_args is not None:
             weight, hidden, dlogits = ctx.capture_args
             cap = fused.current_capture()
+            # The stored dlogits carry row_weight only; a loss built on top of the per-row NLL (a weighted or pairwise
+            # objective) reaches the head's weight gradient through the upstream factor g of every row.  The gradient
+            # is sum_r g_r dlogits_r^T h_r, so the factor goes onto the (narrow) hidden rows, not the vocabulary-wide ones.
+            hidden = hidden * g.to(hidden.dtype)[:, None]
             cap.add_linear(weight, hidden if hidden.is_contiguous() else hidden.contiguous(), dlogits)
             ctx.capture_args = None
         return dh * g.to(dh.dtype)[:, None], None, None, None, None, None, None, None

@@ -311,6 +311,12 @@ class LlamaForCausalLM(nn.Module):
         cap = self.config.final_logit_softcap
         return logits if not cap else cap * torch.tanh(logits / cap)
 
+    def token_nll(self, input_ids: torch.Tensor, labels: torch.Tensor, position_ids=None) -> torch.Tensor:
+        """Per-token negative log-likelihood ``[N, T]`` (0 where ignored): the building block of sequence log-probabilities
+        (preference losses) on the fused engine."""
+        return _token_nll(self, self.lm_head.weight, input_ids, labels, float(self.config.final_logit_softcap or 0.0),
+                          position_ids=position_ids)
+
     def per_example_loss(self, input_ids: torch.Tensor, labels: torch.Tensor, position_ids=None, *,
                          scored_suffix: int | None = None) -> torch.Tensor:
         """Mean NLL over each example's scored tokens; ``labels`` are already aligned (−100 = not scored).
@@ -332,6 +338,15 @@ class LlamaForCausalLM(nn.Module):
         rows = linear_cross_entropy(hs.reshape(B * T, -1), self.lm_head.weight, labels.reshape(-1), w.reshape(-1),
                                     chunk=self.ce_chunk, softcap=softcap)
         return rows.view(B, T).sum(1)
+
+
+def _token_nll(model, head_weight, input_ids, labels, softcap=0.0, **kw):
+    """Per-token NLL ``[N, T]`` (0 where the label is ignored) through the fused head + cross-entropy path."""
+    N, T = input_ids.shape
+    h = model.hidden_states(input_ids, **kw).reshape(N * T, -1)
+    valid = (labels != -100).float().reshape(-1)
+    rows = linear_cross_entropy(h, head_weight, labels.reshape(-1), valid, softcap=softcap)
+    return rows.view(N, T)
 
 
 def shift_labels(input_ids: torch.Tensor, loss_fraction: float = 1.0, ignore_index: int = -100) -> torch.Tensor:

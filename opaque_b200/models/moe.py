@@ -293,6 +293,11 @@ class MoEForCausalLM(nn.Module):
     def forward(self, input_ids, position_ids=None):
         return self.lm_head(self.hidden_states(input_ids, position_ids))
 
+    def token_nll(self, input_ids, labels, position_ids=None):
+        """Per-token negative log-likelihood ``[N, T]`` (0 where ignored)."""
+        from .llama import _token_nll
+        return _token_nll(self, self.lm_head.weight, input_ids, labels, position_ids=position_ids)
+
     def per_example_loss(self, input_ids, labels, position_ids=None):
         B, T = input_ids.shape
         h = self.hidden_states(input_ids, position_ids).reshape(B * T, -1)

@@ -315,7 +315,7 @@ def linear_ce_forward(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.
     lab = labels.reshape(-1).to(torch.int64).contiguous()
     if lab.numel() != R:
         raise ValueError("one label per row is required")
-    tiles = (V + 255) // 256
+    tiles = 2 * ((V + 255) // 256)                  # two column groups per 256-wide tile
     partials = torch.empty(max(R, 1) * tiles * 4, dtype=torch.float32, device=hidden.device)     # scratch of the epilogue
     nll = torch.empty(R, dtype=torch.float32, device=hidden.device)
     lse = torch.empty(R, dtype=torch.float32, device=hidden.device)
@@ -346,6 +346,22 @@ def linear_ce_dlogits_(logits: torch.Tensor, labels: torch.Tensor, lse: torch.Te
     return logits
 
 
+def pick_gemm_kernel(M: int, N: int, K: int, sms: int = 148) -> str:
+    """``"pair"`` or ``"single"`` for an ungrouped ``[M, K] x [K, N]`` product.
+
+    The pair kernel (512 x 256 output tiles on SM pairs, half the operand bytes per FLOP) wins on large products; its
+    tiles are coarse, so a product with few tiles or a short K leaves SM pairs idle in the last wave or pays the
+    un-overlapped part of its epilogue too often.  The estimate is work / (waves x capacity), times the measured
+    steady-state rate of each kernel, times K / (K + per-tile overhead in k).
+    """
+    clusters = max(sms // 2, 1)
+    t_pair = -(-M // 512) * -(-N // 256)
+    t_single = -(-M // 128) * -(-N // 256)
+    eff_pair = t_pair / (-(-t_pair // clusters) * clusters) * (K / (K + 384.0))
+    eff_single = 0.88 * t_single / (-(-t_single // sms) * sms) * (K / (K + 64.0))
+    return "pair" if eff_pair >= eff_single else "single"
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, b_layout: str = "nk", a2: torch.Tensor | None = None,
          b2: torch.Tensor | None = None, bias: torch.Tensor | None = None, group_offs: torch.Tensor | None = None,
          out: torch.Tensor | None = None, status: StatusWord | None = None,
@@ -356,10 +372,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, b_layout: str = "nk", a2: torch.Te
     (``op(b) = b`` — data gradients ``dY @ W`` without a transposed copy).  ``a2 [M, r]``, ``b2 [N, r]`` add a
     low-rank segment accumulated in the same tile (LoRA-fused linear).  With ``group_offs`` (int32 ``[E + 1]`` row
     offsets, rows sorted by group) ``b`` is ``[E, N, K]`` / ``[E, K, N]`` and rows of group e use slab e (MoE experts).
-    ``kernel``: ``"pair"`` (two CTAs per 256 x 256 tile), ``"single"`` (one CTA per 128 x 256 tile) or ``"auto"``
-    (pairs for ungrouped products while :data:`PAIR_GEMM` is on; grouped products always run on single CTAs).
+    ``kernel``: ``"pair"`` (two CTAs per 512 x 256 tile), ``"single"`` (one CTA per 128 x 256 tile) or ``"auto"``
+    (:func:`pick_gemm_kernel` for ungrouped products while :data:`PAIR_GEMM` is on; grouped products always run on
+    single CTAs).
     """
-    if group_offs is None and (kernel == "pair" or (kernel == "auto" and PAIR_GEMM)):
+    if group_offs is None and kernel == "auto" and PAIR_GEMM:
+        kernel = pick_gemm_kernel(a.shape[0], b.shape[1] if b_layout == "kn" else b.shape[0], a.shape[1], lib.sm_count())
+    if group_offs is None and kernel == "pair":
         return gemm_pair(a, b, b_layout=b_layout, a2=a2, b2=b2, bias=bias, out=out, status=status,
                          wait_budget_s=wait_budget_s)
     _need_bf16(a, b)
@@ -536,7 +555,7 @@ from .functional import (activation, cross_entropy, cross_entropy_ref, fused_add
                          layer_norm, merge_heads3, plain_torch_ops, rms_norm, rms_norm_ref, rope_qk, rope_qk_ref, rope_tables, rows_group_sum_, swiglu)
 
 __all__ = [
-    "gemm", "gemm_pair", "gemm_glu", "linear_ce_forward", "linear_ce_dlogits_", "gemm_glu_ref", "gemm_ref", "ghost_set_wide", "push_grad_", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_", "merge_heads3",
+    "gemm", "gemm_pair", "gemm_glu", "pick_gemm_kernel", "linear_ce_forward", "linear_ce_dlogits_", "gemm_glu_ref", "gemm_ref", "ghost_set_wide", "push_grad_", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_", "merge_heads3",
     "DeviceWaitTimeout", "KernelLibraryError", "StatusWord", "clip_weighted_sum", "cross_entropy",
     "cross_entropy_ref", "embedding_wgrad", "fused_add_rms_norm", "geglu", "ghost_norm", "ghost_norm_ref", "glu_ref",
     "philox_normal_add_", "pick_block_n", "pick_splits", "rms_norm", "rms_norm_ref", "rope_qk", "rope_qk_ref",

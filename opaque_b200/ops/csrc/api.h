@@ -40,7 +40,7 @@ int ob_gemm_pair(const void* a, const void* b, const void* b_up, const void* a2,
                  long long lda, long long ldb, long long lda2, long long ldb2, long long ldo, int b_kn, int b2_kn, int glu,
                  int glu_act, int* status, double wait_budget_s, int num_sms, void* stream);
 // Output head fused with cross-entropy statistics on CTA pairs: logits tiles stay in tensor memory, per-tile partials
-// (scratch: rows * ceil(N / 256) float4) are combined in a fixed order into nll[rows], lse[rows]; `logits_out` (optional)
+// (scratch: rows * 2 * ceil(N / 256) float4) are combined in a fixed order into nll[rows], lse[rows]; `logits_out` (optional)
 // receives the bf16 soft-capped logits for the backward pass.
 int ob_linear_ce_fwd(const void* hidden, const void* weight, const long long* labels, void* logits_out, float* partials,
                      float* nll, float* lse, long long rows, int N, int K, long long ldh, long long ldw, long long ldo,

@@ -217,19 +217,24 @@ __host__ __device__ __forceinline__ Philox4 philox4x32_10(uint32_t c0, uint32_t 
 }
 // Four independent N(0,1) samples for the counter block `blk` (coordinates 4*blk .. 4*blk+3),
 // `stream` separates logically different noise draws under the same key.
+//
+// Box-Muller in fp32.  The radius uses all 32 bits of its uniform, u = (x + 0.5) / 2^32 in (0, 1], so the largest
+// magnitude is sqrt(-2 ln 2^-33) = 6.76 standard deviations (two-sided mass beyond it: 1.4e-11); the angle uses 24 bits.
+// Logarithm and sine / cosine are the accurate library functions (this header's callers that draw noise are compiled
+// without approximate math); sincospif needs no range reduction for an argument in [0, 2).
 __device__ __forceinline__ float4 philox_normal4(uint64_t seed, uint64_t blk, uint32_t stream) {
   const Philox4 r = philox4x32_10(static_cast<uint32_t>(blk), static_cast<uint32_t>(blk >> 32), stream, 0u,
                                   static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
-  // Box-Muller on (0,1] uniforms built from the top 24 bits (+0.5 ulp keeps log finite)
-  const float s = 1.0f / 16777216.0f;
-  const float u0 = (static_cast<float>(r.x >> 8) + 0.5f) * s;
-  const float u1 = (static_cast<float>(r.y >> 8) + 0.5f) * s;
-  const float u2 = (static_cast<float>(r.z >> 8) + 0.5f) * s;
-  const float u3 = (static_cast<float>(r.w >> 8) + 0.5f) * s;
-  const float ra = sqrtf(-2.0f * __logf(u0)), rb = sqrtf(-2.0f * __logf(u2));
+  const float s32 = 1.0f / 4294967296.0f, s24 = 1.0f / 16777216.0f;
+  // float(x) rounds large x to 24 bits (then u may be exactly 1 and the radius 0); small x, the tail, is exact
+  const float u0 = fminf((static_cast<float>(r.x) + 0.5f) * s32, 1.0f);
+  const float u2 = fminf((static_cast<float>(r.z) + 0.5f) * s32, 1.0f);
+  const float a1 = static_cast<float>(r.y >> 8) * s24;          // angle / 2 pi in [0, 1)
+  const float a3 = static_cast<float>(r.w >> 8) * s24;
+  const float ra = sqrtf(-2.0f * logf(u0)), rb = sqrtf(-2.0f * logf(u2));
   float sa, ca, sb, cb;
-  __sincosf(6.28318530717958647692f * u1, &sa, &ca);
-  __sincosf(6.28318530717958647692f * u3, &sb, &cb);
+  sincospif(2.0f * a1, &sa, &ca);
+  sincospif(2.0f * a3, &sb, &cb);
   return make_float4(ra * ca, ra * sa, rb * cb, rb * sb);
 }
 

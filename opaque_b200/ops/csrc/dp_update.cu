@@ -70,6 +70,7 @@ clip_weighted_sum_kernel(const float* __restrict__ g, const float* __restrict__ 
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int e = 0; e < E; ++e) {
       const float w = __ldg(c + e);
+      if (w == 0.f) continue;            // factor 0 = example dropped (non-finite norm): skip it, 0 * NaN is NaN
       const float4 v = __ldg(reinterpret_cast<const float4*>(g + static_cast<long long>(e) * ld) + i);
       acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
     }

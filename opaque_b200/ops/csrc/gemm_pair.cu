@@ -2,18 +2,21 @@
 //
 //     D[M, N] = A[M, K1] * op1(B) + A2[M, K2] * op2(B2) + bias          (bf16 in / bf16 out, fp32 accumulation)
 //
-// Two CTAs of a 2x1 cluster share one 256 x 256 accumulator tile.  Each CTA loads ITS OWN 128 rows of A and ITS OWN
-// half (128 columns of N) of the B tile with ordinary TMA copies of this GPU's memory; one thread of the leader CTA
-// (cluster rank 0) issues `tcgen05.mma.cta_group::2` over both CTAs' shared memory, and each CTA's tensor memory
-// receives the accumulator rows of its own 128 rows of M.  Per k-block an SM therefore stages 32 KB for the work that
-// a single-CTA 128 x 256 tile stages 48 KB for, which is what lifts the operand-feed bound of the single-CTA kernels.
+// Two CTAs of a 2x1 cluster share one 512 x 256 output tile.  Each CTA loads ITS OWN 256 rows of A and ITS OWN half
+// (128 columns of N) of the B tile with ordinary TMA copies of this GPU's memory; one thread of the leader CTA
+// (cluster rank 0) issues `tcgen05.mma.cta_group::2` (M = 256 across the pair) over both CTAs' shared memory, twice per
+// k-step: once for each 128-row half of a CTA's A tile, each half with its own 256-column accumulator in that CTA's tensor
+// memory.  Per k-block an SM stages 48 KB for 2 x (128 x 256 x 64) of tensor work: half the bytes per FLOP of a single-CTA
+// 128 x 256 tile.  Measured need for it: with 32 KB per (128 x 256 x 64) the tensor pipe was 81 % busy at 11.4 TB/s of
+// L2-to-SM traffic, whatever the number of stages.
 //
 // Protocol (every wait bounded; a timeout records a code in the status word and the kernel unwinds):
-//   * full[s]  (leader only, 1 arrival + 64 KB of transactions): the leader's producer arms it for both CTAs' bytes;
+//   * full[s]  (leader only, 1 arrival + 96 KB of transactions): the leader's producer arms it for both CTAs' bytes;
 //     the peer's producer points its copies' completion at the leader's barrier (shared::cluster address from `mapa`).
 //   * empty[s] (each CTA, 1 arrival): the leader's `tcgen05.commit` arrives at both CTAs' barriers at once.
-//   * tmem_full[a] (each CTA, 1 arrival): same two-CTA commit after the last k-block of a tile.
-//   * tmem_empty[a] (leader only, 8 arrivals): the four epilogue warps of both CTAs; the peer's arrive remotely.
+//   * tmem_full[h] (each CTA, 1 arrival, h = accumulator half): same two-CTA commit after the last k-block of a tile.
+//   * tmem_empty[h] (leader only, 16 arrivals): the eight epilogue warps of both CTAs; the peer's arrive remotely.
+//     All warps drain half 0 first, then half 1, and the next tile begins with half-0 work (see the MMA issuer).
 // No copy in this file uses cluster multicast.
 //
 // Epilogues: plain store (+ bias), or GLU: the B halves come from TWO weight matrices (gate rows to rank 0, up rows to
@@ -31,12 +34,16 @@ namespace ob {
 int make_bf16_map_2d(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld,
                      int box_cols, int box_rows);
 
-constexpr int GP_BM = 128;           // rows of M per CTA (256 per pair)
+constexpr int GP_BM = 256;           // rows of M per CTA (512 per pair tile): two 128-row halves, one accumulator each
+constexpr int GP_MMA_M = 128;        // rows of one accumulator per CTA (the pair instruction has M = 256)
 constexpr int GP_BN = 256;           // accumulator columns per pair tile
 constexpr int GP_BNH = 128;          // columns of N whose B rows one CTA stages
 constexpr int GP_BK = 64;
 #ifndef OB_PAIR_STAGES
-#define OB_PAIR_STAGES 7
+#define OB_PAIR_STAGES 4
+#endif
+#ifndef OB_PAIR_INTERLEAVE
+#define OB_PAIR_INTERLEAVE 1
 #endif
 #ifndef OB_PAIR_RELAXED
 #define OB_PAIR_RELAXED 0
@@ -45,9 +52,10 @@ constexpr int GP_STAGES = OB_PAIR_STAGES;
 constexpr int GP_A_BYTES = GP_BM * GP_BK * 2;
 constexpr int GP_B_BYTES = GP_BNH * GP_BK * 2;
 constexpr int GP_STAGE_BYTES = GP_A_BYTES + GP_B_BYTES;
-constexpr int GP_THREADS = 192;
-constexpr int GP_GROUP_M = 8;        // pair tiles (256 rows each) per raster band
-constexpr int GP_SMEM = GP_STAGES * GP_STAGE_BYTES + 256 + 1024;
+constexpr int GP_THREADS = 320;       // TMA warp, MMA warp, 2 x 4 epilogue warps
+constexpr int GP_GROUP_M = 4;        // pair tiles (512 rows each) per raster band
+constexpr int GP_SLAB_BYTES = 4096;   // per epilogue warp: a 32-row x 64-column (or 2 x 32-column) bf16 staging tile
+constexpr int GP_SMEM = GP_STAGES * GP_STAGE_BYTES + 8 * GP_SLAB_BYTES + 256 + 1024;
 
 enum : int { GP_EPI_STORE = 0, GP_EPI_GLU = 1, GP_EPI_CE = 2 };
 
@@ -191,6 +199,57 @@ __device__ __forceinline__ void gp_store32(__nv_bfloat16* dst, const float* v, b
   }
 }
 
+// Warp-cooperative store of a [32 rows x COLS columns] tile (lane = row on entry, COLS = 32 or 64 fp32 values per lane)
+// as bf16.  The rows go through a private shared-memory slab with a 16-byte XOR swizzle and leave as whole row segments
+// (COLS * 2 bytes contiguous per row, several rows per instruction), so memory sees full 32-byte sectors instead of one
+// 16-byte piece per lane and instruction.  `out` points at (first row of the warp, first column); rows >= rows_valid and
+// columns >= cols_valid are not written.
+template <int COLS>
+__device__ __forceinline__ void gp_store_tile(uint8_t* slab, const float* v, __nv_bfloat16* out, long long ldo,
+                                              int rows_valid, int cols_valid, bool vec_ok, int lane) {
+  if (!vec_ok) {                       // unaligned destination: every lane writes its own row
+    if (lane < rows_valid) {
+      __nv_bfloat16* dst = out + static_cast<long long>(lane) * ldo;
+      for (int j = 0; j < COLS; ++j)
+        if (j < cols_valid) dst[j] = __float2bfloat16_rn(v[j]);
+    }
+    return;
+  }
+  constexpr int CHUNKS = COLS / 8;             // 16-byte chunks per row
+  constexpr int ROW_BYTES = COLS * 2;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * c], v[8 * c + 1]);
+    __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * c + 2], v[8 * c + 3]);
+    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * c + 4], v[8 * c + 5]);
+    __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * c + 6], v[8 * c + 7]);
+    uint4 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&h0);
+    pk.y = *reinterpret_cast<uint32_t*>(&h1);
+    pk.z = *reinterpret_cast<uint32_t*>(&h2);
+    pk.w = *reinterpret_cast<uint32_t*>(&h3);
+    *reinterpret_cast<uint4*>(slab + lane * ROW_BYTES + ((c ^ (lane & (CHUNKS - 1))) << 4)) = pk;
+  }
+  __syncwarp();
+  constexpr int ROWS_PER_INSTR = 32 / CHUNKS;
+  const int c = lane % CHUNKS;
+#pragma unroll
+  for (int i = 0; i < 32 / ROWS_PER_INSTR; ++i) {
+    const int r = i * ROWS_PER_INSTR + lane / CHUNKS;
+    const uint4 pk = *reinterpret_cast<const uint4*>(slab + r * ROW_BYTES + ((c ^ (r & (CHUNKS - 1))) << 4));
+    if (r < rows_valid) {
+      __nv_bfloat16* dst = out + static_cast<long long>(r) * ldo + 8 * c;
+      if (8 * c + 8 <= cols_valid) {
+        *reinterpret_cast<uint4*>(dst) = pk;
+      } else if (8 * c < cols_valid) {
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&pk);
+        for (int j = 0; j < cols_valid - 8 * c; ++j) dst[j] = e[j];
+      }
+    }
+  }
+  __syncwarp();
+}
+
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -200,11 +259,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   // the dynamic shared-memory window starts at the same offset in both CTAs, so the rounded offsets agree too
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GP_STAGES * GP_STAGE_BYTES);
+  uint8_t* slabs = smem + GP_STAGES * GP_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(slabs + 8 * GP_SLAB_BYTES);
   uint64_t* full = bars;                               // used in the leader CTA only
   uint64_t* empty = bars + GP_STAGES;
-  uint64_t* tmem_full = bars + 2 * GP_STAGES;
-  uint64_t* tmem_empty = bars + 2 * GP_STAGES + 2;     // used in the leader CTA only
+  uint64_t* tmem_full = bars + 2 * GP_STAGES;          // [2]: one per accumulator half
+  uint64_t* tmem_empty = bars + 2 * GP_STAGES + 2;     // [2], used in the leader CTA only
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * GP_STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -227,7 +287,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 8);
+      mbar_init(&tmem_empty[a], 16);                   // eight epilogue warps in each CTA
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -271,7 +331,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           uint8_t* b_dst = a_dst + GP_A_BYTES;
           const bool first = kb < nk1;
           const int k0 = (first ? kb : kb - nk1) * GP_BK;
-          tma_load_2d_pair(a_dst, first ? &map_a : &map_a2, bar, k0, it.row0);
+          tma_load_2d_pair(a_dst, first ? &map_a : &map_a2, bar, k0, it.row0);          // 256 rows x 64 k in one box
           const CUtensorMap* mb = first ? mb1 : mb2;
           if (first ? p.kn1 : p.kn2) {
 #pragma unroll
@@ -287,49 +347,98 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   } else if (warp == 1) {
     if (leader && lane == 0) {
       // ---------------------------------------------------------------- MMA issuer (leader CTA only)
-      constexpr uint32_t idesc_k = make_idesc_bf16(2 * GP_BM, GP_BN, 0, 0);
-      constexpr uint32_t idesc_n = make_idesc_bf16(2 * GP_BM, GP_BN, 0, 1);
+      // Each CTA holds 256 rows of A per stage: two 128-row halves, one accumulator (256 TMEM columns) each, both
+      // multiplied with the SAME B tile, so a stage's 48 KB feed 2 x (128 x 256 x 64) of work per SM.
+      // The two accumulators fill all of tensor memory, so a tile's epilogue cannot hide behind the next tile's whole
+      // main loop.  It hides behind its first k-blocks instead: the epilogue warps drain half 0 first, and the next
+      // tile starts with the half-0 products of its first GP_STAGES k-blocks while half 1 is still being drained.
+      constexpr uint32_t idesc_k = make_idesc_bf16(2 * GP_MMA_M, GP_BN, 0, 0);
+      constexpr uint32_t idesc_n = make_idesc_bf16(2 * GP_MMA_M, GP_BN, 0, 1);
       int stage = 0, acc_iter = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
-        const int as = acc_iter & 1;
-        if (!mbar_wait(&tmem_empty[as], ((acc_iter >> 1) & 1) ^ 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_EMPTY,
-                       budget)) {
-          ok = false;
-          break;
+      auto issue_one = [&](int h, int kb, int st, int kk) {
+        const uint32_t a_addr = smem_u32(smem + st * GP_STAGE_BYTES);
+        const uint32_t b_addr = a_addr + GP_A_BYTES;
+        const bool kn = kb < nk1 ? p.kn1 != 0 : p.kn2 != 0;
+        // K-major operand: rows 128 B apart, 8-row groups 1024 B apart, 32 B per 16-element k-step.
+        // N-major operand: 64-column blocks GP_BK*128 B apart, 8-row (k) groups 1024 B apart, 2048 B per k-step.
+        const uint64_t ad = make_smem_desc(a_addr + h * (GP_MMA_M * 128) + kk * 32, 16, 1024, 2);
+        const uint64_t bd = kn ? make_smem_desc(b_addr + kk * (16 * 128), GP_BK * 128, 1024, 2)
+                               : make_smem_desc(b_addr + kk * 32, 16, 1024, 2);
+        umma_bf16_pair(tmem_base + h * GP_BN, ad, bd, kn ? idesc_n : idesc_k, (kb > 0 || kk > 0) ? 1u : 0u);
+      };
+      auto issue_half = [&](int h, int kb, int st) {
+#pragma unroll
+        for (int kk = 0; kk < GP_BK / 16; ++kk) issue_one(h, kb, st, kk);
+        if (kb == num_kb - 1) umma_commit_pair(&tmem_full[h], 3);   // this half's accumulators (both CTAs) are complete
+      };
+      // steady state: the two accumulators alternate k-step by k-step, so no instruction waits on the one before it
+      auto issue_both = [&](int kb, int st) {
+#if OB_PAIR_INTERLEAVE
+#pragma unroll
+        for (int kk = 0; kk < GP_BK / 16; ++kk) {
+          issue_one(0, kb, st, kk);
+          issue_one(1, kb, st, kk);
         }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + as * GP_BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        if (kb == num_kb - 1) {
+          umma_commit_pair(&tmem_full[0], 3);
+          umma_commit_pair(&tmem_full[1], 3);
+        }
+#else
+        issue_half(0, kb, st);
+        issue_half(1, kb, st);
+#endif
+      };
+      for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
+        const uint32_t acc_parity = static_cast<uint32_t>(acc_iter & 1);
+        const int lead = num_kb < GP_STAGES ? num_kb : GP_STAGES;
+        // head of the tile: half 0 of the first `lead` k-blocks, then half 1 of the same stages
+        for (int i = 0; ok && i < lead; ++i) {
+          int st = stage + i;
+          uint32_t ph = phase;
+          if (st >= GP_STAGES) { st -= GP_STAGES; ph ^= 1; }
+          if (!mbar_wait(&full[st], ph, abort_flag, p.status, OB_ERR_WAIT_FULL, budget)) { ok = false; break; }
+          if (i == 0 && !mbar_wait(&tmem_empty[0], acc_parity ^ 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_EMPTY, budget)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_half(0, i, st);
+        }
+        for (int i = 0; ok && i < lead; ++i) {
+          if (i == 0) {
+            if (!mbar_wait(&tmem_empty[1], acc_parity ^ 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_EMPTY, budget)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+          }
+          issue_half(1, i, stage);
+          umma_commit_pair(&empty[stage], 3);          // frees the stage in both CTAs
+          if (++stage == GP_STAGES) { stage = 0; phase ^= 1; }
+        }
+        for (int kb = lead; ok && kb < num_kb; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag, p.status, OB_ERR_WAIT_FULL, budget)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + stage * GP_STAGE_BYTES);
-          const uint32_t b_addr = a_addr + GP_A_BYTES;
-          const bool kn = kb < nk1 ? p.kn1 != 0 : p.kn2 != 0;
-#pragma unroll
-          for (int kk = 0; kk < GP_BK / 16; ++kk) {
-            // K-major operand: rows 128 B apart, 8-row groups 1024 B apart, 32 B per 16-element k-step.
-            // N-major operand: 64-column blocks GP_BK*128 B apart, 8-row (k) groups 1024 B apart, 2048 B per k-step.
-            const uint64_t ad = make_smem_desc(a_addr + kk * 32, 16, 1024, 2);
-            const uint64_t bd = kn ? make_smem_desc(b_addr + kk * (16 * 128), GP_BK * 128, 1024, 2)
-                                   : make_smem_desc(b_addr + kk * 32, 16, 1024, 2);
-            umma_bf16_pair(d_tmem, ad, bd, kn ? idesc_n : idesc_k, (kb > 0 || kk > 0) ? 1u : 0u);
-          }
-          umma_commit_pair(&empty[stage], 3);          // frees the stage in both CTAs
+          issue_both(kb, stage);
+          umma_commit_pair(&empty[stage], 3);
           if (++stage == GP_STAGES) { stage = 0; phase ^= 1; }
         }
-        if (!ok) break;
-        umma_commit_pair(&tmem_full[as], 3);           // the accumulator halves of both CTAs are complete
         ++acc_iter;
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue warps (4 per CTA)
+    // ------------------------------------------------------------------ epilogue warps (8 per CTA)
+    // Warp (q, g): TMEM lane quarter q = warp % 4 (the only lanes a warp may read), column group g = 0 for warps 2-5 and
+    // 1 for warps 6-9.  All eight warps drain accumulator half 0 first (each its own rows and columns), release it, then
+    // half 1: the tensor pipe gets half 0 back after half the drain time.
     const int q = warp & 3;
+    const int g = (warp - 2) >> 2;
+    uint8_t* slab = slabs + (warp - 2) * GP_SLAB_BYTES;
     int acc_iter = 0;
     bool ok = true;
     const bool vec_ok = ((p.ldo & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
@@ -337,108 +446,113 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                          (((reinterpret_cast<uintptr_t>(p.out_gate) | reinterpret_cast<uintptr_t>(p.out_up)) & 15) == 0));
     for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
       const GpItem it = gp_decode(w, tiles_m, tiles_n, rank);
-      const int as = acc_iter & 1;
-      if (!mbar_wait_idle(&tmem_full[as], (acc_iter >> 1) & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL, budget)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      const int row = it.row0 + q * 32 + lane;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * GP_BN;
-      if constexpr (EPI == GP_EPI_STORE) {
-        __nv_bfloat16* orow = p.out + static_cast<long long>(row) * p.ldo;
-        const int n0 = it.nt * GP_BN;
 #pragma unroll 1
-        for (int c = 0; c < GP_BN / 32; ++c) {
-          const int nc = n0 + c * 32;
-          if (nc >= p.N) break;
-          float v[32];
-          tmem_ld32(t_row + c * 32, v);
-          tmem_ld_wait();
-          if (p.bias != nullptr) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (nc + j < p.N) v[j] += __bfloat162float(__ldg(p.bias + nc + j));
-          }
-          if (row < p.M) gp_store32(orow + nc, v, vec_ok, p.N - nc);
+      for (int h = 0; h < 2; ++h) {
+        if (!mbar_wait_idle(&tmem_full[h], acc_iter & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL, budget)) {
+          ok = false;
+          break;
         }
-      } else if constexpr (EPI == GP_EPI_CE) {
-        // Output head: the logits tile never leaves the SM unless `out` asks for it.  Each thread owns one row and folds
-        // the tile's 256 columns into (max, sum exp, label logit, plain sum); the per-tile partials are combined per row
-        // in a fixed order by lce_combine_kernel, so the result does not depend on which CTA ran which tile.
-        const int n0 = it.nt * GP_BN;
-        const long long label = row < p.M ? p.labels[row] : -1;
-        float m = -INFINITY, ssum = 0.f, zlab = 0.f, ztot = 0.f;
-        __nv_bfloat16* orow = p.out != nullptr ? p.out + static_cast<long long>(row) * p.ldo : nullptr;
+        tc_fence_after();
+        const int row = it.row0 + h * GP_MMA_M + q * 32 + lane;
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + h * GP_BN;
+        if constexpr (EPI == GP_EPI_STORE) {
+          const int n0 = it.nt * GP_BN + g * (GP_BN / 2);
 #pragma unroll 1
-        for (int c = 0; c < GP_BN / 32; ++c) {
-          const int nc = n0 + c * 32;
-          if (nc >= p.N) break;
-          float v[32];
-          tmem_ld32(t_row + c * 32, v);
-          tmem_ld_wait();
-          float lm = -INFINITY;
+          for (int c = 0; c < GP_BN / 2 / 64; ++c) {          // 64 columns per round: two loads in flight, one wait
+            const int nc = n0 + c * 64;
+            if (nc >= p.N) break;
+            float v[64];
+            tmem_ld32(t_row + g * (GP_BN / 2) + c * 64, v);
+            tmem_ld32(t_row + g * (GP_BN / 2) + c * 64 + 32, v + 32);
+            tmem_ld_wait();
+            if (p.bias != nullptr) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float z = v[j];
-            if (p.softcap > 0.f) z = p.softcap * tanhf(z / p.softcap);
-            // statistics are taken from the value the backward pass will read: the bf16-rounded logit when it is stored
-            if (orow != nullptr) z = __bfloat162float(__float2bfloat16_rn(z));
-            const bool in = nc + j < p.N;
-            v[j] = in ? z : -INFINITY;
-            if (in) {
-              ztot += z;
-              lm = fmaxf(lm, z);
-              if (nc + j == label) zlab = z;
+              for (int j = 0; j < 64; ++j)
+                if (nc + j < p.N) v[j] += __bfloat162float(__ldg(p.bias + nc + j));
+            }
+            gp_store_tile<64>(slab, v, p.out + static_cast<long long>(row - lane) * p.ldo + nc, p.ldo, p.M - (row - lane),
+                              p.N - nc, vec_ok, lane);
+          }
+        } else if constexpr (EPI == GP_EPI_CE) {
+          // Output head: the logits tile never leaves the SM unless `out` asks for it.  Each thread owns one row and folds
+          // its 128 columns of the tile into (max, sum exp, label logit, plain sum); the partials (two per tile and row)
+          // are combined per row in a fixed order by lce_combine_kernel, so the result does not depend on which CTA ran
+          // which tile.
+          const int n0 = it.nt * GP_BN + g * (GP_BN / 2);
+          const long long label = row < p.M ? p.labels[row] : -1;
+          float m = -INFINITY, ssum = 0.f, zlab = 0.f, ztot = 0.f;
+          __nv_bfloat16* orow = p.out != nullptr ? p.out + static_cast<long long>(row) * p.ldo : nullptr;
+#pragma unroll 1
+          for (int c = 0; c < GP_BN / 2 / 32; ++c) {
+            const int nc = n0 + c * 32;
+            if (nc >= p.N) break;
+            float v[32];
+            tmem_ld32(t_row + g * (GP_BN / 2) + c * 32, v);
+            tmem_ld_wait();
+            float lm = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float z = v[j];
+              if (p.softcap > 0.f) z = p.softcap * tanhf(z / p.softcap);
+              // statistics are taken from the value the backward pass will read: the bf16-rounded logit when it is stored
+              if (orow != nullptr) z = __bfloat162float(__float2bfloat16_rn(z));
+              const bool in = nc + j < p.N;
+              v[j] = in ? z : -INFINITY;
+              if (in) {
+                ztot += z;
+                lm = fmaxf(lm, z);
+                if (nc + j == label) zlab = z;
+              }
+            }
+            if (lm > m) {
+              ssum *= __expf(m - lm);
+              m = lm;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) ssum += __expf(v[j] - m);      // exp(-inf) = 0 for masked columns
+            if (p.out != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = nc + j < p.N ? v[j] : 0.f;
+              gp_store_tile<32>(slab, v, p.out + static_cast<long long>(row - lane) * p.ldo + nc, p.ldo, p.M - (row - lane),
+                                p.N - nc, vec_ok, lane);
             }
           }
-          if (lm > m) {
-            ssum *= __expf(m - lm);
-            m = lm;
-          }
-#pragma unroll
-          for (int j = 0; j < 32; ++j) ssum += __expf(v[j] - m);      // exp(-inf) = 0 for masked columns
-          if (orow != nullptr && row < p.M) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = nc + j < p.N ? v[j] : 0.f;
-            gp_store32(orow + nc, v, vec_ok, p.N - nc);
-          }
-        }
-        if (row < p.M) p.ce_partials[static_cast<long long>(row) * tiles_n + it.nt] = make_float4(m, ssum, zlab, ztot);
-      } else {
-        const int nh = p.N / 2;
-        const int n0 = it.nt * GP_BNH;
-        const long long ro = static_cast<long long>(row) * p.ldo;
+          if (row < p.M)
+            p.ce_partials[static_cast<long long>(row) * (2 * tiles_n) + 2 * it.nt + g] = make_float4(m, ssum, zlab, ztot);
+        } else {
+          const int nh = p.N / 2;
+          const int n0 = it.nt * GP_BNH + g * (GP_BNH / 2);
 #pragma unroll 1
-        for (int c = 0; c < GP_BNH / 32; ++c) {
-          const int nc = n0 + c * 32;
-          if (nc >= nh) break;
-          float g[32], u[32];
-          tmem_ld32(t_row + c * 32, g);
-          tmem_ld32(t_row + GP_BNH + c * 32, u);
-          tmem_ld_wait();
-          if (row < p.M) {
+          for (int c = 0; c < GP_BNH / 2 / 32; ++c) {
+            const int nc = n0 + c * 32;
+            if (nc >= nh) break;
+            float gt[32], up[32];
+            tmem_ld32(t_row + g * (GP_BNH / 2) + c * 32, gt);
+            tmem_ld32(t_row + GP_BNH + g * (GP_BNH / 2) + c * 32, up);
+            tmem_ld_wait();
+            const long long r0o = static_cast<long long>(row - lane) * p.ldo + nc;
+            const int rows_valid = p.M - (row - lane);
             if (p.out_gate != nullptr) {
-              gp_store32(p.out_gate + ro + nc, g, vec_ok, nh - nc);
-              gp_store32(p.out_up + ro + nc, u, vec_ok, nh - nc);
+              gp_store_tile<32>(slab, gt, p.out_gate + r0o, p.ldo, rows_valid, nh - nc, vec_ok, lane);
+              gp_store_tile<32>(slab + GP_SLAB_BYTES / 2, up, p.out_up + r0o, p.ldo, rows_valid, nh - nc, vec_ok, lane);
               // the backward pass reads the ROUNDED pre-activations, so the activation is formed from them too
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
-                g[j] = __bfloat162float(__float2bfloat16_rn(g[j]));
-                u[j] = __bfloat162float(__float2bfloat16_rn(u[j]));
+                gt[j] = __bfloat162float(__float2bfloat16_rn(gt[j]));
+                up[j] = __bfloat162float(__float2bfloat16_rn(up[j]));
               }
             }
 #pragma unroll
-            for (int j = 0; j < 32; ++j) g[j] = gp_act(g[j], p.act) * u[j];
-            gp_store32(p.out + ro + nc, g, vec_ok, nh - nc);
+            for (int j = 0; j < 32; ++j) gt[j] = gp_act(gt[j], p.act) * up[j];
+            gp_store_tile<32>(slab, gt, p.out + r0o, p.ldo, rows_valid, nh - nc, vec_ok, lane);
           }
         }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if (leader) mbar_arrive(&tmem_empty[as]);
-        else mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[as]), 0));
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (leader) mbar_arrive(&tmem_empty[h]);
+          else mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[h]), 0));
+        }
       }
       ++acc_iter;
     }
@@ -661,7 +775,7 @@ extern "C" unsigned int ob_debug_idesc_bf16(int m, int n, int a_mn_major, int b_
 }
 
 // Output head fused with the cross-entropy statistics:  logits = hidden[M, K] * weight[N, K]^T on CTA pairs; the epilogue
-// folds every 256-column logits tile into per-row partials (scratch `partials`: M * ceil(N / 256) float4) and a second
+// folds every 128-column half of a logits tile into per-row partials (scratch `partials`: M * 2 * ceil(N / 256) float4) and a second
 // small kernel combines them in a fixed order into nll[M] and lse[M].  The logits themselves are written (bf16, after the
 // soft cap) only when `logits_out` is given.  softcap > 0: z = softcap * tanh(z / softcap).  Rows whose label is
 // `ignore_index` or outside [0, N) get nll = lse = 0.
@@ -705,7 +819,7 @@ extern "C" int ob_linear_ce_fwd(const void* hidden, const void* weight, const lo
   if (cudaGetLastError() != cudaSuccess) return -55;
   const long long warps = rows;
   lce_combine_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, st>>>(
-      reinterpret_cast<const float4*>(partials), labels, nll, lse, rows, tiles_n, N, smoothing, ignore_index);
+      reinterpret_cast<const float4*>(partials), labels, nll, lse, rows, 2 * tiles_n, N, smoothing, ignore_index);
   return cudaGetLastError() == cudaSuccess ? 0 : -57;
 }
 

@@ -564,13 +564,16 @@ wgrad_clip_pe_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           break;
         }
         tc_fence_after();
+        // an example with factor 0 (non-finite norm, padding) is skipped, not multiplied: 0 * NaN would poison the sum
+        if (c != 0.f) {
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          float v[32];
-          tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * WP_BLOCK_N + half * 128 + ch * 32, v);
-          tmem_ld_wait();
+          for (int ch = 0; ch < 4; ++ch) {
+            float v[32];
+            tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * WP_BLOCK_N + half * 128 + ch * 32, v);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[ch * 32 + j] = fmaf(c, v[j], acc[ch * 32 + j]);
+            for (int j = 0; j < 32; ++j) acc[ch * 32 + j] = fmaf(c, v[j], acc[ch * 32 + j]);
+          }
         }
         tc_fence_before();
         __syncwarp();

@@ -521,18 +521,42 @@ class DPTrainer:
         return torch.stack(out) if out else torch.zeros(0, device=self.device)
 
     # ---- set-up -----------------------------------------------------------------------------------
+    def _fused_blockers(self) -> list[str]:
+        """Reasons why this run cannot use the fused engine (empty list: it can)."""
+        why = []
+        if self.device.type != "cuda":
+            why.append("no CUDA device")
+        if not hasattr(self.model, "per_example_loss"):
+            why.append("the model has no per_example_loss (convert it with opaque_b200.patches)")
+        if self.compute_loss_func is not None:
+            why.append("compute_loss_func is set")
+        if self.args.label_smoothing_factor:        # label smoothing lives in the trainer's default loss (reference engine)
+            why.append("label_smoothing_factor is set")
+        if not why:
+            from ..device import fused_kernels_available
+            if not fused_kernels_available():
+                why.append("the sm_100a kernel library is not available")
+        return why
+
     def _resolve_engine(self) -> str:
         want = self.args.dp_engine
-        # label smoothing lives in the trainer's default loss, which only the reference engine calls
-        fused_ok = (self.device.type == "cuda" and hasattr(self.model, "per_example_loss") and self.compute_loss_func is None
-                    and not self.args.label_smoothing_factor)
-        if fused_ok:
-            from ..device import fused_kernels_available
-            fused_ok = fused_kernels_available()
-        if want == "fused" and not fused_ok:
-            raise RuntimeError("dp_engine='fused' needs a B200, the kernel library, a model with per_example_loss and no "
-                               "label_smoothing_factor / compute_loss_func")
-        return "fused" if (want in ("auto", "fused") and fused_ok) else "reference"
+        why = self._fused_blockers()
+        if want == "fused" and why:
+            raise RuntimeError("dp_engine='fused' is not possible here: " + "; ".join(why))
+        if want == "auto" and why and self.device.type == "cuda":
+            # the vmap engine is several times slower on a GPU: never take it silently
+            import warnings
+            warnings.warn("dp_engine='auto' falls back to the reference (vmap) engine: " + "; ".join(why), RuntimeWarning,
+                          stacklevel=3)
+        return "fused" if (want in ("auto", "fused") and not why) else "reference"
+
+    def _fused_loss_fn(self):
+        """Per-example loss the fused engine differentiates (keyword arguments = the entries of :meth:`_fused_payload`)."""
+        return self.model.per_example_loss
+
+    def _fused_payload(self, batch) -> dict[str, torch.Tensor]:
+        """Tensors of one local batch, leading dimension = privacy units."""
+        return {"input_ids": batch["input_ids"], "labels": batch["labels"]}
 
     def _build_sampler(self, n_local: int, steps: int, data_key: RngKey):
         a = self.args
@@ -926,14 +950,15 @@ class DPTrainer:
         if getattr(self, "_liveness", None) is not None:
             self._liveness.check()
         self._call("on_pre_optimizer_step")
-        if not self._graphs_ready and batch["input_ids"].shape[0]:
-            self._fused.prepare_graphs(self.model.per_example_loss, {"input_ids": batch["input_ids"], "labels": batch["labels"]})
+        payload = self._fused_payload(batch)
+        loss_fn = self._fused_loss_fn()
+        if not self._graphs_ready and payload["input_ids"].shape[0]:
+            self._fused.prepare_graphs(loss_fn, payload)
             self._graphs_ready = True
-        payload = {"input_ids": batch["input_ids"], "labels": batch["labels"]}
         while True:                                   # cluster-wide agreement on out-of-memory, then a smaller microbatch
             oom = False
             try:
-                res = self._fused.accumulate(self.model.per_example_loss, payload)
+                res = self._fused.accumulate(loss_fn, payload)
             except Exception as exc:      # noqa: BLE001 — only OOM is swallowed, and only with auto_find_microbatch_size
                 if not (self.args.auto_find_microbatch_size and _is_retryable_oom(exc)):
                     raise

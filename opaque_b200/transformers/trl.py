@@ -148,17 +148,76 @@ class DPOTrainer(DPTrainer):
             for m in model.modules():
                 if isinstance(m, torch.nn.Dropout):
                     m.p = 0.0
-        reference_free = all(t in dpo_losses.REFERENCE_FREE for t in ([args.loss_type] if isinstance(args.loss_type, str) else args.loss_type))
-        self.ref_model = None if reference_free else (ref_model if ref_model is not None else copy.deepcopy(model).requires_grad_(False))
-        args.dp_engine = "reference"        # the pair loss is not a plain LM loss; it runs on the functional engine
+        self._reference_free = all(t in dpo_losses.REFERENCE_FREE for t in ([args.loss_type] if isinstance(args.loss_type, str) else args.loss_type))
+        # The reference log-probabilities are computed ONCE, before the first update.  Without an explicit ref_model that
+        # needs no second copy of the weights: the policy itself at its initial point (adapters switched off under LoRA,
+        # so the reference is the frozen base model).  Only TR-DPO (sync_ref_model) owns a separate, moving reference.
+        self.ref_model = ref_model
+        if ref_model is None and args.sync_ref_model and not self._reference_free:
+            self.ref_model = copy.deepcopy(model).requires_grad_(False)
         super().__init__(model=model, args=args, train_dataset=train_dataset, eval_dataset=eval_dataset,
                          processing_class=processing_class, data_collator=data_collator, **kw)
-        if self.ref_model is not None:
-            self.ref_model.to(self.device).eval()
-            self.train_dataset = self._precompute_ref_logps(self.train_dataset)
+        if not self._reference_free:
+            if self.ref_model is not None:
+                self.ref_model.to(self.device).eval()
+            self.train_dataset = self._precompute_ref_logps(self.train_dataset, "train")
             if self.eval_dataset is not None:
-                self.eval_dataset = self._precompute_ref_logps(self.eval_dataset)
+                self.eval_dataset = self._precompute_ref_logps(self.eval_dataset, "eval")
         self._bco_delta = 0.0
+
+    # ---- engine selection ------------------------------------------------------------------------------------------
+    def _fused_blockers(self) -> list[str]:
+        why = [w for w in super()._fused_blockers() if "per_example_loss" not in w]
+        if not hasattr(self.model, "token_nll"):
+            why.append("the model has no token_nll (convert it with opaque_b200.patches)")
+        if self._dpo.ld_alpha is not None:
+            why.append("ld_alpha (length-desensitised log-probabilities) needs token-level terms")
+        if self._dpo.use_weighting:
+            why.append("use_weighting (WPO) needs token-level terms")
+        return why
+
+    def _fused_payload(self, batch) -> dict[str, torch.Tensor]:
+        """One privacy unit = one preference pair: ``input_ids`` / ``labels`` ``[B, 2, T]`` (chosen, rejected; both padded
+        to the same length) and the precomputed reference log-probabilities ``[B, 2]``."""
+        ci, ri, cl, rl = batch["chosen_input_ids"], batch["rejected_input_ids"], batch["chosen_labels"], batch["rejected_labels"]
+        T = max(ci.shape[1], ri.shape[1])
+        T = (T + 63) // 64 * 64                          # whole 64-row blocks per pair for the per-example GEMM path
+
+        def pad(t, value):
+            return torch.nn.functional.pad(t, (0, T - t.shape[1]), value=value)
+        ids = torch.stack([pad(ci, 0), pad(ri, 0)], dim=1)
+        labels = torch.stack([pad(cl, -100), pad(rl, -100)], dim=1)
+        B = ids.shape[0]
+        ref = torch.zeros(B, 2, device=ids.device)
+        if "ref_chosen_logps" in batch:
+            ref = torch.stack([batch["ref_chosen_logps"], batch["ref_rejected_logps"]], dim=1).to(ids.device, torch.float32)
+        return {"input_ids": ids, "labels": labels, "ref_logps": ref}
+
+    def _fused_loss_fn(self):
+        return self._fused_pair_loss
+
+    def _sequence_logps(self, model, ids, labels):
+        """``(sum, mean)`` log-probability of the scored tokens of every sequence (``[N]`` each), differentiable."""
+        nll = model.token_nll(ids, labels)
+        cnt = (labels != -100).sum(1).clamp_min(1)
+        s = -nll.sum(1)
+        return s, s / cnt
+
+    def _fused_pair_loss(self, input_ids, labels, ref_logps):
+        a = self._dpo
+        B, _, T = input_ids.shape
+        s, m = self._sequence_logps(self.model, input_ids.reshape(2 * B, T), labels.reshape(2 * B, T))
+        s, m = s.view(B, 2), m.view(B, 2)
+        c_sum, r_sum, c_avg, r_avg = s[:, 0], s[:, 1], m[:, 0], m[:, 1]
+        use_avg = a.loss_type == "ipo" or (not isinstance(a.loss_type, str) and "ipo" in a.loss_type)
+        c_ratio = (c_avg if use_avg else c_sum) - ref_logps[:, 0]
+        r_ratio = (r_avg if use_avg else r_sum) - ref_logps[:, 1]
+        return dpo_losses.dpo_loss(a.loss_type, chosen_logratio=c_ratio, rejected_logratio=r_ratio, beta=a.beta,
+                                   label_smoothing=a.label_smoothing, loss_weights=a.loss_weights, chosen_nll=-c_avg,
+                                   chosen_avg_logp=c_avg, rejected_avg_logp=r_avg, bco_delta=self._bco_delta,
+                                   discopop_tau=a.discopop_tau, simpo_gamma=a.simpo_gamma, orpo_lambda=a.orpo_lambda,
+                                   f_divergence_type=a.f_divergence_type, f_alpha=a.f_alpha_divergence_coef,
+                                   chosen_logp=c_sum, rejected_logp=r_sum, cpo_alpha=a.cpo_alpha)
 
     @staticmethod
     def tokenize_row(row, tokenizer):
@@ -184,21 +243,87 @@ class DPOTrainer(DPTrainer):
             return lp, mask
         return sft_losses.sequence_logp(logits, labels, average=average)
 
+    def _reference_forward(self):
+        """``(module, context)`` that evaluates the reference policy: the explicit / TR-DPO reference model, or the
+        policy itself with its adapters switched off (equal to the initial policy: LoRA starts at zero)."""
+        import contextlib
+
+        from ..models.layers import adapters_disabled
+        if self.ref_model is not None:
+            return self.ref_model, contextlib.nullcontext()
+        return self.model, adapters_disabled()
+
+    def _ref_cache_path(self, dataset, split: str) -> str | None:
+        """File under ``output_dir`` keyed by the data and the reference weights, or ``None`` when caching is off."""
+        import hashlib
+        import os
+        if not self.args.output_dir or not len(dataset):
+            return None
+        h = hashlib.blake2b(digest_size=12)
+        h.update(f"{len(dataset)}|{self._dpo.max_length}|{self._dpo.loss_type}".encode())
+        for i in (0, len(dataset) // 2, len(dataset) - 1):
+            row = dataset[i]
+            h.update(repr((list(row["prompt_input_ids"])[:64], list(row["chosen_input_ids"])[:64], list(row["rejected_input_ids"])[:64])).encode())
+        module, _ = self._reference_forward()
+        for n, p in list(module.named_parameters())[:4]:
+            if "lora_" not in n:
+                h.update(n.encode())
+                h.update(p.detach().float().flatten()[:256].cpu().numpy().tobytes())
+        return os.path.join(self.args.output_dir, f"ref_logps_{split}_{h.hexdigest()}.pt")
+
     @torch.no_grad()
-    def _precompute_ref_logps(self, dataset):
-        """Reference log-probabilities of every pair, computed once (sharded by rank, then gathered)."""
+    def _precompute_ref_logps(self, dataset, split: str = "train"):
+        """Reference log-probabilities of every pair, computed once: each rank scores every ``world``-th pair, the
+        results are gathered with one tensor all-gather, and rank 0 keeps them in a cache file under ``output_dir``
+        (parity: packages/opaque-alignment/src/opaque/api/alignment/dpo/reference/_precompute.py:270-321, 449)."""
+        import os
+
+        from ..distributed import get_rank, get_world_size, is_distributed
         if dataset is None or (len(dataset) and "ref_chosen_logps" in dataset[0]):
             return dataset
-        bs = self._dpo.precompute_ref_batch_size or self.args.eval_batch_size
-        out = []
-        for lo in range(0, len(dataset), bs):
-            rows = [dataset[i] for i in range(lo, min(len(dataset), lo + bs))]
-            batch = self._to_device(self.data_collator(rows))
-            c = sft_losses.sequence_logp(_logits(self.ref_model(batch["chosen_input_ids"])), batch["chosen_labels"])
-            r = sft_losses.sequence_logp(_logits(self.ref_model(batch["rejected_input_ids"])), batch["rejected_labels"])
-            for row, ci, ri in zip(rows, c.tolist(), r.tolist()):
-                out.append({**row, "ref_chosen_logps": ci, "ref_rejected_logps": ri})
-        return out
+        n = len(dataset)
+        cache = self._ref_cache_path(dataset, split)
+        table = None
+        if cache and os.path.exists(cache):
+            got = torch.load(cache, map_location="cpu")
+            if tuple(got.shape) == (n, 2):
+                table = got
+        if table is None:
+            rank, world = (get_rank(), get_world_size()) if is_distributed() else (0, 1)
+            mine = list(range(rank, n, world))
+            bs = self._dpo.precompute_ref_batch_size or self.args.eval_batch_size
+            module, ctx = self._reference_forward()
+            was_training = module.training
+            module.eval()
+            local = torch.zeros(len(mine), 2, dtype=torch.float32, device=self.device)
+            with ctx:
+                for lo in range(0, len(mine), bs):
+                    rows = [dataset[i] for i in mine[lo:lo + bs]]
+                    batch = self._to_device(self.data_collator(rows))
+                    for col, side in enumerate(("chosen", "rejected")):
+                        if hasattr(module, "token_nll") and self.device.type == "cuda":
+                            lp = -module.token_nll(batch[f"{side}_input_ids"], batch[f"{side}_labels"]).sum(1)
+                        else:
+                            lp = sft_losses.sequence_logp(_logits(module(batch[f"{side}_input_ids"])), batch[f"{side}_labels"])
+                        local[lo:lo + len(rows), col] = lp.float()
+            module.train(was_training)
+            table = torch.zeros(n, 2, dtype=torch.float32)
+            if world > 1:
+                per = (n + world - 1) // world                      # equal-length pieces for the tensor all-gather
+                padded = torch.zeros(per, 2, dtype=torch.float32, device=self.device)
+                padded[:len(mine)] = local
+                pieces = [torch.zeros_like(padded) for _ in range(world)]
+                torch.distributed.all_gather(pieces, padded)
+                for r, piece in enumerate(pieces):
+                    idx = list(range(r, n, world))
+                    table[idx] = piece[:len(idx)].cpu()
+            else:
+                table[mine] = local.cpu()
+            if cache and rank == 0:
+                os.makedirs(os.path.dirname(cache), exist_ok=True)
+                torch.save(table, cache)
+        vals = table.tolist()
+        return [{**dataset[i], "ref_chosen_logps": vals[i][0], "ref_rejected_logps": vals[i][1]} for i in range(n)]
 
     def _pair_terms(self, call, ex):
         cl, rl = ex["chosen_labels"].unsqueeze(0), ex["rejected_labels"].unsqueeze(0)
@@ -255,7 +380,7 @@ class DPOTrainer(DPTrainer):
         for (n, p), (_, r) in zip(self.model.named_parameters(), self.ref_model.named_parameters()):
             r.mul_(1 - al).add_(p.detach().to(r.dtype), alpha=al)
         strip = lambda rows: [{k: v for k, v in row.items() if not k.startswith("ref_")} for row in rows]
-        self.train_dataset = self._precompute_ref_logps(strip(self.train_dataset))
+        self.train_dataset = self._precompute_ref_logps(strip(self.train_dataset), f"train_step{self.state.global_step}")
         self._local_data = None      # rebuilt on the next epoch boundary by _setup; current sampler keeps its indices
 
 

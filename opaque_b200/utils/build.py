@@ -18,8 +18,13 @@ CSRC = PKG / "ops" / "csrc"
 KERNEL_LIB = PKG / "ops" / "libopaque_b200.so"
 ACC_SRC = PKG / "accounting" / "csrc"
 
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "--use_fast_math", "-Xcompiler", "-fPIC", "-shared"]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
+# Approximate division / exp / tanh are fine in the GEMM epilogues and activation kernels.  The translation unit that draws
+# the DP noise and applies the optimizer is compiled WITHOUT them: its logarithm, sine / cosine, square roots and divisions
+# are the IEEE-accurate ones.
+FAST_MATH = "--use_fast_math"
+EXACT_MATH_SOURCES = {"dp_update.cu"}
+OBJ_DIR = CSRC / "build"
 
 
 def _find(tool: str, extra: list[str]) -> str | None:
@@ -56,10 +61,16 @@ def _stale(target: Path, sources: list[Path]) -> bool:
     return any(s.stat().st_mtime > t for s in sources)
 
 
+def _flags_for(src: Path) -> list[str]:
+    return list(NVCC_FLAGS) + ([] if src.name in EXACT_MATH_SOURCES else [FAST_MATH])
+
+
 def build_kernels(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every ``.cu`` under ``ops/csrc`` into one shared library for sm_100a."""
+    """Compile every ``.cu`` under ``ops/csrc`` (one object each, rebuilt only when stale) and link one shared library
+    for sm_100a."""
     sources = sorted(CSRC.glob("*.cu"))
-    deps = sources + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
+    headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
+    deps = sources + headers
     if not force and not _stale(KERNEL_LIB, deps):
         return KERNEL_LIB
     nvcc = _find("nvcc", ["/usr/local/cuda/bin/nvcc"])
@@ -70,17 +81,33 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
     with _build_lock(KERNEL_LIB):
         if not force and not _stale(KERNEL_LIB, deps):
             return KERNEL_LIB
+        OBJ_DIR.mkdir(exist_ok=True)
+        procs, objs, log = [], [], []
+        for src in sources:
+            obj = OBJ_DIR / (src.stem + ".o")
+            objs.append(obj)
+            if force or _stale(obj, [src] + headers):
+                cmd = [nvcc, *_flags_for(src), "-c", str(src), "-o", str(obj)]
+                if verbose:
+                    cmd.insert(1, "-Xptxas=-v")
+                procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        failed = []
+        for src, obj, proc in procs:                      # the objects compile side by side
+            out, _ = proc.communicate()
+            log.append(out)
+            if proc.returncode != 0:
+                obj.unlink(missing_ok=True)
+                failed.append(f"{src.name}:\n{out}")
+        if failed:
+            raise RuntimeError("nvcc failed:\n" + "\n".join(failed))
         tmp = KERNEL_LIB.with_suffix(f".so.tmp{os.getpid()}")
-        cmd = [nvcc, *NVCC_FLAGS, "-o", str(tmp), *map(str, sources)]
-        if verbose:
-            cmd.insert(1, "-Xptxas=-v")
-        res = subprocess.run(cmd, capture_output=True, text=True)
+        res = subprocess.run([nvcc, "-shared", "-o", str(tmp), *map(str, objs)], capture_output=True, text=True)
         if res.returncode != 0:
             tmp.unlink(missing_ok=True)
-            raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+            raise RuntimeError("nvcc link failed:\n" + res.stdout + res.stderr)
         os.replace(tmp, KERNEL_LIB)
     if verbose:
-        print(res.stderr)
+        print("\n".join(log))
     return KERNEL_LIB
 
 

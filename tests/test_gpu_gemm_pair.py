@@ -105,7 +105,9 @@ def test_fused_head_cross_entropy_forward_and_dlogits(dev, R, V, K, softcap, smo
     # forward only: no logits reach memory
     nll, lse, z = ops.linear_ce_forward(h, w, lab, softcap=softcap, label_smoothing=smoothing, status=st)
     assert st.read() == 0 and z is None
-    assert float((nll - nll_ref).abs().max()) < 2e-2 and bool((nll[::7] == 0).all())
+    err = (nll - nll_ref.detach()).abs()
+    assert float(err.max()) < 2e-2, (int(err.argmax()), nll[int(err.argmax())].item(), nll_ref[int(err.argmax())].item())
+    assert bool((nll[::7] == 0).all())
     # bit-reproducible: per-tile partials are combined in a fixed order
     nll2, _, _ = ops.linear_ce_forward(h, w, lab, softcap=softcap, label_smoothing=smoothing, status=st)
     assert torch.equal(nll, nll2)
@@ -113,7 +115,10 @@ def test_fused_head_cross_entropy_forward_and_dlogits(dev, R, V, K, softcap, smo
     nll_s, lse_s, z = ops.linear_ce_forward(h, w, lab, softcap=softcap, label_smoothing=smoothing, store_logits=True, status=st)
     zc = z_ref.detach() if not softcap else softcap * torch.tanh(z_ref.detach() / softcap)
     assert st.read() == 0 and z.shape == (R, V) and rel(z, zc) < 4e-3
-    assert float((nll_s - nll_ref).abs().max()) < 3e-2
+    # the statistics are those of the STORED (bf16-rounded, already capped) logits, which is what the backward pass reads
+    nll_of_stored = ops.cross_entropy_ref(z.float(), lab, label_smoothing=smoothing)
+    assert float((nll_s - nll_of_stored).abs().max()) < 2e-3
+    assert float((nll_s - nll_ref.detach()).abs().max()) < 0.1
     (nll_ref * rw).sum().backward()
     ops.linear_ce_dlogits_(z, lab, lse_s, rw, softcap=softcap, label_smoothing=smoothing)
     assert rel(z, z_ref.grad) < 2e-2 and bool((z[::7] == 0).all())

@@ -509,3 +509,34 @@ def test_layernorm_weight_and_bias_sums_in_one_pass_and_head_merge(dev):
     out = ops.merge_heads3(gq, gk, gv)
     ref = torch.stack([t.transpose(1, 2) for t in (gq, gk, gv)], dim=2).reshape(B, T, 3 * heads * hd)
     assert torch.equal(out, ref)
+
+
+def test_philox_gaussian_tails_follow_the_normal_law(dev):
+    """Tail mass of the device Gaussian over 1e9 draws: P(|z| > 4) and P(|z| > 5) against the normal law, and the cut.
+
+    The radius of the Box-Muller pair uses 32 uniform bits, so no draw exceeds sqrt(-2 ln 2^-33) = 6.76 standard
+    deviations.  (The reference's CPU sampler clamps its uniform to [eps, 1 - eps] of its compute dtype, fp32: a cut at
+    5.2 standard deviations, packages/opaque-dpsgd/src/opaque/api/dpsgd/noise/_gaussian.py:257-264.)
+    """
+    from opaque_b200 import ops
+    n_chunk, chunks = 250_000_000, 4
+    over4 = over5 = 0
+    top = 0.0
+    s1 = s2 = 0.0
+    buf = torch.empty(n_chunk, device=dev)
+    for c in range(chunks):
+        buf.zero_()
+        ops.philox_normal_add_(buf, seed=20240611, offset=c * n_chunk, std=1.0)
+        a = buf.abs()
+        over4 += int((a > 4.0).sum())
+        over5 += int((a > 5.0).sum())
+        top = max(top, float(a.max()))
+        s1 += float(buf.double().sum())
+        s2 += float((buf.double() ** 2).sum())
+    n = n_chunk * chunks
+    p4, p5 = math.erfc(4 / math.sqrt(2)), math.erfc(5 / math.sqrt(2))          # two-sided tail mass
+    for got, p in ((over4, p4), (over5, p5)):
+        sd = math.sqrt(n * p)
+        assert abs(got - n * p) < 5 * sd, (got, n * p, sd)
+    assert 5.5 < top <= 6.77
+    assert abs(s1 / n) < 5 / math.sqrt(n) and abs(s2 / n - 1.0) < 5 * math.sqrt(2.0 / n)

@@ -77,3 +77,45 @@ def test_fused_trainer_steps_down_after_a_simulated_oom(tmp_path):
     out = tr.train()
     assert fired and out["global_step"] == 4 and tr._fused.microbatch_size == 4
     assert float(tr._fused.space.grad.local.abs().max()) == 0.0          # consumed by the last step, nothing left over
+
+
+def _pairs(n=48, vocab=256, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    rows = []
+    for _ in range(n):
+        lp, lc, lr = (int(torch.randint(8, 20, (1,), generator=g)) for _ in range(3))
+        rows.append({"prompt_input_ids": torch.randint(0, vocab, (lp,), generator=g).tolist(),
+                     "chosen_input_ids": torch.randint(0, vocab, (lc,), generator=g).tolist(),
+                     "rejected_input_ids": torch.randint(0, vocab, (lr,), generator=g).tolist()})
+    return rows
+
+
+@pytest.mark.parametrize("loss_type", ["sigmoid", "ipo", "simpo", "orpo"])
+def test_dpo_runs_on_the_fused_engine_and_matches_the_reference_engine(tmp_path, loss_type):
+    """One preference pair = one privacy unit on the fused engine ([B, 2, T] batches, rows of a pair clipped together);
+    first-step loss and mean per-pair gradient norm equal those of the vmap engine on the same batch."""
+    from opaque_b200.transformers.trl import DPOConfig, DPOTrainer
+
+    def run(engine, out):
+        torch.manual_seed(0)
+        model = _model()
+        with torch.no_grad():                       # LoRA B starts at zero: move off the saddle so both factors get gradients
+            for n, p in model.named_parameters():
+                if n.endswith("lora_B"):
+                    p.copy_(torch.randn_like(p) * 0.05)
+        args = DPOConfig(output_dir=str(out), per_device_train_batch_size=8, max_steps=2, learning_rate=1e-4, logging_steps=1,
+                         save_steps=0, privacy_noise_multiplier=1.0, clipping_norm=1.0, optim="adamw-bc", lr_scheduler="constant",
+                         seed=3, dp_engine=engine, bf16=True, loss_type=loss_type, beta=0.5, microbatch_size=4)
+        tr = DPOTrainer(model=model, args=args, train_dataset=_pairs())
+        tr.train()
+        first = next(h for h in tr.state.log_history if "loss" in h)
+        return tr, first
+    fused, f = run("fused", tmp_path / "f")
+    ref, r = run("reference", tmp_path / "r")
+    assert fused.engine_kind == "fused" and ref.engine_kind == "reference"
+    assert fused.ref_model is None                    # adapter-disabled policy, no copy of the weights
+    assert math.isfinite(f["loss"]) and abs(f["loss"] - r["loss"]) < 3e-2 * max(1.0, abs(r["loss"]))
+    assert abs(f["grad_norm"] - r["grad_norm"]) < 8e-2 * max(r["grad_norm"], 1e-3)
+    if loss_type not in ("simpo", "orpo"):           # reference-based heads: the cached table exists and is reused
+        files = [x for x in os.listdir(tmp_path / "f") if x.startswith("ref_logps_train_")]
+        assert len(files) == 1

@@ -833,3 +833,117 @@ extern "C" int ob_linear_ce_dlogits(void* logits, const long long* labels, const
       static_cast<__nv_bfloat16*>(logits), labels, lse, row_weight, N, ld, softcap, smoothing, ignore_index);
   return cudaGetLastError() == cudaSuccess ? 0 : -58;
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// The same forward (losses and log-sum-exps, logits never stored) for callers that must not allocate: the per-tile
+// statistics go to a fixed array inside the library image instead of caller-provided scratch.  See no_alloc.h for who
+// needs this, the size limit and the sharing rules.
+#include "no_alloc.h"
+#include <cstdio>
+#include <mutex>
+
+// In HOST code this name is only a handle for the symbol, not a device address; device code may use it directly.
+static __device__ __align__(256) float4 g_lce_static_partials[OB_NO_ALLOC_MAX_PARTIALS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float4* g_lce_static_ptr[kMaxDevices] = {nullptr};
+std::mutex g_lce_static_mutex;
+thread_local char g_no_alloc_error[256] = {0};
+
+// Device address of the static scratch array on the CURRENT device (looked up once per device, then cached).
+int lce_static_scratch(float4** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    snprintf(g_no_alloc_error, sizeof(g_no_alloc_error), "cudaGetDevice failed or device index %d is outside [0, %d)", dev, kMaxDevices);
+    return -61;
+  }
+  std::lock_guard<std::mutex> lock(g_lce_static_mutex);
+  if (g_lce_static_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(&ptr, g_lce_static_partials);
+    if (err != cudaSuccess || ptr == nullptr) {
+      snprintf(g_no_alloc_error, sizeof(g_no_alloc_error), "cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(err));
+      return -62;
+    }
+    g_lce_static_ptr[dev] = static_cast<float4*>(ptr);
+  }
+  *out = g_lce_static_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int ob_no_alloc_last_error(char* buf, int len) {
+  int i = 0;
+  for (; g_no_alloc_error[i] && i < len - 1; ++i) buf[i] = g_no_alloc_error[i];
+  if (len > 0) buf[i] = 0;
+  return 0;
+}
+
+extern "C" int ob_linear_ce_fwd_noalloc(const void* hidden, const void* weight, const long long* labels, float* nll,
+                                        float* lse, long long rows, int N, int K, long long ldh, long long ldw,
+                                        float softcap, float smoothing, long long ignore_index, int* status,
+                                        double wait_budget_s, int num_sms, void* stream) {
+  using namespace ob;
+  g_no_alloc_error[0] = 0;
+  if (rows <= 0 || N <= 0 || K <= 0) return 0;
+  if (hidden == nullptr || weight == nullptr || labels == nullptr || nll == nullptr) {
+    snprintf(g_no_alloc_error, sizeof(g_no_alloc_error), "hidden, weight, labels and nll must be device pointers");
+    return -56;
+  }
+  const int tiles_n = (N + GP_BN - 1) / GP_BN;
+  const long long need = rows * 2LL * tiles_n;
+  if (need > OB_NO_ALLOC_MAX_PARTIALS) {
+    snprintf(g_no_alloc_error, sizeof(g_no_alloc_error),
+             "problem too large for the static scratch: rows * 2 * ceil(N / 256) = %lld records, the array holds %d "
+             "(rows = %lld, N = %d): split the rows over several calls",
+             need, OB_NO_ALLOC_MAX_PARTIALS, rows, N);
+    return OB_NO_ALLOC_TOO_LARGE;
+  }
+  float4* partials = nullptr;
+  int rc = lce_static_scratch(&partials);
+  if (rc) return rc;
+  CUtensorMap ma, mb;
+  rc = make_bf16_map_2d(&ma, hidden, rows, K, ldh, GP_BK, GP_BM);
+  if (rc == 0) rc = make_bf16_map_2d(&mb, weight, N, K, ldw, GP_BK, GP_BNH);
+  if (rc) {
+    snprintf(g_no_alloc_error, sizeof(g_no_alloc_error), "operands must have 16-byte aligned rows (tensor map code %d)", rc);
+    return rc;
+  }
+  static bool configured = false;
+  static int clusters_ce = 0;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_pair_kernel<GP_EPI_CE>, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_SMEM) != cudaSuccess) {
+      snprintf(g_no_alloc_error, sizeof(g_no_alloc_error), "cudaFuncSetAttribute(shared memory) failed");
+      return -54;
+    }
+    clusters_ce = pair_grid(reinterpret_cast<const void*>(gemm_pair_kernel<GP_EPI_CE>), num_sms);
+    configured = true;
+  }
+  PairParams p = {};
+  p.M = static_cast<int>(rows);
+  p.N = N; p.K1 = K; p.K2 = 0;
+  p.out = nullptr;                    // forward only: the logits never reach memory
+  p.ldo = 0;
+  p.labels = labels;
+  p.ce_partials = partials;
+  p.softcap = softcap;
+  p.status = status;
+  p.wait_budget_ns = static_cast<unsigned long long>(wait_budget_s * 1e9);
+  const long long tiles_m = (rows + 2 * GP_BM - 1) / (2 * GP_BM);
+  const long long total = tiles_m * tiles_n;
+  const int clusters = static_cast<int>(total < clusters_ce ? total : clusters_ce);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  gemm_pair_kernel<GP_EPI_CE><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mb, ma, mb, mb, p);
+  cudaError_t err = cudaGetLastError();
+  if (err == cudaSuccess) {
+    lce_combine_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, st>>>(
+        partials, labels, nll, lse, rows, 2 * tiles_n, N, smoothing, ignore_index);
+    err = cudaGetLastError();
+  }
+  if (err != cudaSuccess) {
+    snprintf(g_no_alloc_error, sizeof(g_no_alloc_error), "kernel launch failed: %s", cudaGetErrorString(err));
+    return -55;
+  }
+  return 0;
+}

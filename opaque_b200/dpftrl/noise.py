@@ -47,6 +47,19 @@ class StreamingMatrix(NamedTuple):
     multiply_next: Callable[[Any, Any], tuple[Any, Any]]  # (x_t, state) -> (row_t · X, state)
     row_norms_squared: Callable[[int], np.ndarray] | None = None
 
+    def __matmul__(self, other):
+        """``self @ other`` for another streaming matrix (composition) or a ``[n, ...]`` tensor (row-by-row product)."""
+        if isinstance(other, StreamingMatrix):
+            return multiply_streaming_matrices(self, other)
+        if isinstance(other, torch.Tensor):
+            return multiply_array(self, other)
+        return NotImplemented
+
+    def __mul__(self, factor: float) -> "StreamingMatrix":
+        return scale_rows_and_columns(self, row_scale=np.array([float(factor)]))
+
+    __rmul__ = __mul__
+
     def materialize(self, n: int) -> np.ndarray:
         """Dense ``n × n`` matrix (tests / small horizons): column j is the response to ``e_j``."""
         out = np.zeros((n, n))
@@ -70,6 +83,85 @@ def prefix_sum_streaming() -> StreamingMatrix:
         new = tree_map(lambda a, b: a + b, s, x)
         return new, new
     return StreamingMatrix(init, nxt, lambda n: np.arange(1, n + 1, dtype=float))
+
+
+# ---- algebra on streaming operators (parity: packages/opaque-dpftrl/src/opaque/api/dpftrl/noise/_streaming_matrix.py:157-305)
+
+def diagonal_streaming(diag) -> StreamingMatrix:
+    """``diag(d_0, d_1, ...)``; rows past ``len(diag)`` reuse the last entry.  The state is the row index (a Python int)."""
+    d = np.asarray(diag, dtype=np.float64).reshape(-1)
+    if d.size == 0:
+        raise ValueError("diagonal_streaming needs at least one entry")
+
+    def nxt(x, i):
+        f = float(d[min(i, d.size - 1)])
+        return tree_map(lambda t: t * f if isinstance(t, torch.Tensor) else t, x), i + 1
+
+    def norms(n):
+        return np.concatenate([d[:n], np.full(max(0, n - d.size), d[-1])]) ** 2
+    return StreamingMatrix(lambda tpl: 0, nxt, norms)
+
+
+def multiply_streaming_matrices(a: StreamingMatrix, b: StreamingMatrix) -> StreamingMatrix:
+    """``A @ B``: every input goes through ``B``'s row, the result through ``A``'s (both stay streaming)."""
+    def init(tpl):
+        return a.init_multiply(tpl), b.init_multiply(tpl)
+
+    def nxt(x, state):
+        sa, sb = state
+        inner, sb = b.multiply_next(x, sb)
+        outer, sa = a.multiply_next(inner, sa)
+        return outer, (sa, sb)
+
+    def norms(n):                              # no closed form for a product: materialise (small horizons / tests)
+        m = StreamingMatrix(init, nxt, None).materialize(n)
+        return (m ** 2).sum(1)
+    return StreamingMatrix(init, nxt, norms)
+
+
+def multiply_array(a: StreamingMatrix, x: torch.Tensor) -> torch.Tensor:
+    """``A @ x`` for ``x [n, ...]``, one row at a time."""
+    state = a.init_multiply(x[0])
+    rows = []
+    for i in range(x.shape[0]):
+        y, state = a.multiply_next(x[i], state)
+        rows.append(y)
+    return torch.stack(rows)
+
+
+def scale_rows_and_columns(matrix: StreamingMatrix, row_scale=None, col_scale=None) -> StreamingMatrix:
+    """``diag(row_scale) @ matrix @ diag(col_scale)``."""
+    out = matrix
+    if row_scale is not None:
+        out = multiply_streaming_matrices(diagonal_streaming(row_scale), out)
+    if col_scale is not None:
+        out = multiply_streaming_matrices(out, diagonal_streaming(col_scale))
+    return out
+
+
+def momentum_sgd_matrix(momentum: float = 0.0, learning_rates=None) -> StreamingMatrix:
+    """Workload of SGD with momentum and per-step learning rates: row t of ``A`` maps the gradient stream to the
+    iterate displacement, ``m_t = μ m_{t-1} + g_t``, ``θ_t = θ_{t-1} + η_t m_t`` (``η`` repeats its last entry)."""
+    lr = np.ones(1) if learning_rates is None else np.asarray(learning_rates, dtype=np.float64).reshape(-1)
+    if lr.min() <= 0:
+        raise ValueError("learning rates must be positive")
+    mu = float(momentum)
+
+    def init(tpl):
+        zero = tree_map(lambda t: torch.zeros_like(t, dtype=torch.float64 if t.dtype == torch.float64 else torch.float32)
+                        if isinstance(t, torch.Tensor) else t, tpl)
+        return 0, zero, zero
+
+    def nxt(x, state):
+        i, mom, acc = state
+        eta = float(lr[min(i, lr.size - 1)])
+        mom = tree_map(lambda m, g: mu * m + g, mom, x)
+        acc = tree_map(lambda a, m: a + eta * m, acc, mom)
+        return acc, (i + 1, mom, acc)
+
+    def norms(n):
+        return (StreamingMatrix(init, nxt, None).materialize(n) ** 2).sum(1)
+    return StreamingMatrix(init, nxt, norms)
 
 
 def _zeros_state(tpl: Any, k: int) -> Any:
@@ -300,8 +392,8 @@ class MfStrategy:
         c = np.trim_zeros(np.asarray(c), "b")
         if len(c) <= 1:
             return None
-        if len(c) > 9:
-            raise ValueError("the fused kernel supports at most 8 history buffers; use fewer bands or the streaming path")
+        if len(c) > 64:
+            raise ValueError("the fused kernel supports at most 63 history buffers; use fewer bands or the streaming path")
         return {"kind": "banded", "coef": c.tolist()}
 
 
@@ -344,7 +436,7 @@ class BltStrategy(MfStrategy):
             raise ValueError("max_buffers must be in [1, 16]")
 
     def params(self, n: int) -> tuple[np.ndarray, np.ndarray]:
-        s, d = optimize_blt(n, min(self.max_buffers, 8), self.min_sep_hint, self.max_participations_hint)
+        s, d = optimize_blt(n, self.max_buffers, self.min_sep_hint, self.max_participations_hint)
         return np.array(s), np.array(d)
 
     def coefficients(self, n):
@@ -433,21 +525,76 @@ class LambdaCgdStrategy(MfStrategy):
     def coefficients(self, n):
         return self.lambda_ ** np.arange(n)       # C = (I − λ S)⁻¹ has geometric columns
 
-    def scale(self, n: int) -> float:
-        if not self.normalized:
+    def column_norm(self, n: int, t: int) -> float:
+        """``d_t``: norm of column ``t`` of ``C = (I − λS)⁻¹`` truncated to ``n`` rows,
+        ``sqrt((1 − λ^{2(n−t)}) / (1 − λ²))`` (reference: dpftrl/noise/_lambda_cgd.py:90-108)."""
+        if not 0 <= t < n:
+            raise ValueError(f"step {t} is outside the calibrated horizon [0, {n})")
+        lam2 = self.lambda_ ** 2
+        if lam2 == 0.0:
             return 1.0
-        return 1.0 / math.sqrt(toeplitz_sensitivity_squared(self.coefficients(n), n, 1, 1))
+        tail = lam2 ** (n - t)
+        return math.sqrt((1.0 if tail < 1e-30 else 1.0 - tail) / (1.0 - lam2))
+
+    def gram_matrix(self, n: int) -> np.ndarray:
+        """``C'ᵀC'`` of the (column-normalised) strategy matrix: ``G_ij = λ^{|i−j|} d_max(i,j) / d_min(i,j)``."""
+        if not self.normalized:
+            return toeplitz_gram(self.coefficients(n), n)
+        d = self.row_scales(n)
+        i, j = np.meshgrid(np.arange(n), np.arange(n), indexing="ij")
+        lo, hi = np.minimum(i, j), np.maximum(i, j)
+        return (self.lambda_ ** (hi - lo)) * d[hi] / d[lo]
+
+    def row_scales(self, n: int) -> np.ndarray:
+        """Per-row factors of ``C⁻¹``: ``d_t`` when normalised (every column of the scaled ``C`` then has unit norm), else 1."""
+        return np.array([self.column_norm(n, t) for t in range(n)]) if self.normalized else np.ones(n)
 
     def sensitivity(self, n, min_sep=1, max_participations=None):
-        return self.scale(n) * math.sqrt(toeplitz_sensitivity_squared(self.coefficients(n), n, min_sep, max_participations))
+        """Largest norm of a sum of participating columns of ``C·diag(d)⁻¹`` (all inner products are non-negative, so the
+        worst record takes part as often as ``min_sep`` / ``max_participations`` allow): ``⟨c'_i, c'_j⟩ = λ^{j−i} d_j / d_i``."""
+        d = self.row_scales(n)
+        if not self.normalized:
+            return math.sqrt(toeplitz_sensitivity_squared(self.coefficients(n), n, min_sep, max_participations))
+        b = max(int(min_sep), 1)
+        k_max = max_participations if max_participations is not None else math.ceil(n / b)
+        best = 0.0
+        for start in range(min(b, n)):
+            idx = list(range(start, n, b))[:k_max]
+            tot = 0.0
+            for a_i, i in enumerate(idx):
+                tot += 1.0
+                for j in idx[a_i + 1:]:
+                    tot += 2.0 * (self.lambda_ ** (j - i)) * d[j] / d[i]
+            best = max(best, tot)
+            # a later window of k_max participations can be heavier than the first one: slide it
+            full = list(range(start, n, b))
+            for off in range(1, max(0, len(full) - k_max) + 1):
+                w = full[off:off + k_max]
+                tot = sum(1.0 for _ in w) + sum(2.0 * (self.lambda_ ** (j - i)) * d[j] / d[i] for a_i, i in enumerate(w) for j in w[a_i + 1:])
+                best = max(best, tot)
+        return math.sqrt(best)
 
     def streaming_matrix(self, n):
-        d = 1.0 / self.scale(n)
-        return fir_streaming(np.array([d, -self.lambda_ * d]))
+        base = fir_streaming(np.array([1.0, -self.lambda_]))
+        if not self.normalized:
+            return base
+        sm = scale_rows_and_columns(base, row_scale=self.row_scales(n))
+        d = self.row_scales(n)
+        per_row = np.where(np.arange(n) == 0, 1.0, 1.0 + self.lambda_ ** 2) * d ** 2      # ‖row_t(C⁻¹)‖² (not cumulative)
+        return StreamingMatrix(sm.init_multiply, sm.multiply_next, lambda m: per_row[:m])
+
+    def row_norm(self, n: int, t: int) -> float:
+        """``‖row_t(C⁻¹)‖ = d_t·sqrt(1 + λ²)`` (``d_0`` at the first step): factor between σ and the realised std."""
+        t = min(t, n - 1)
+        d = self.column_norm(n, t) if self.normalized else 1.0
+        return d if (t == 0 or self.lambda_ == 0.0) else d * math.sqrt(1.0 + self.lambda_ ** 2)
 
     def fused_mechanism(self, n, step=0):
-        d = 1.0 / self.scale(n)
-        return {"kind": "fir", "coef": [d, -self.lambda_ * d]}
+        """FIR taps ``(d_t, −λ d_t)`` of the current step; ``coef_fn`` gives the fused optimizer each later step's pair."""
+        def taps(t):
+            d = self.column_norm(n, min(t, n - 1)) if self.normalized else 1.0
+            return [d, -self.lambda_ * d]
+        return {"kind": "fir", "coef": taps(step), "coef_fn": taps}
 
 
 def identity_strategy() -> IdentityStrategy:

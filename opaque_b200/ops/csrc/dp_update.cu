@@ -134,6 +134,10 @@ embedding_wgrad_kernel(const __nv_bfloat16* __restrict__ g, const long long* __r
 
 // ---------------------------------------------------------------------------------------------
 // Fused shard step.
+// Longest correlated-noise recurrence the fused step handles: 63 history buffers for the ring modes (a banded C or a
+// banded inverse with up to 64 coefficients), 32 (scale, decay) pairs for BLT.  Up to 8 buffers run fully unrolled.
+constexpr int OB_FTRL_MAX_COEF = 64;
+
 struct ShardStepParams {
   float* grad;             // [n] fp32 sum of clipped gradients for this shard; zeroed on exit
   float* master;           // [n] fp32 parameters
@@ -152,7 +156,7 @@ struct ShardStepParams {
   // DP-FTRL: mode 0 = iid Gaussian, 1 = BLT inverse (scale s_j, decay d_j), 2 = banded inverse (IIR),
   // 3 = FIR over past raw draws
   int ftrl_mode, nbuf, ring_head;
-  float coef[16];          // BLT: s_0..s_{nbuf-1}, d_0..d_{nbuf-1}; banded: c_0, c_1..c_{bands-1}
+  float coef[OB_FTRL_MAX_COEF];   // BLT: s_0..s_{nbuf-1}, d_0..d_{nbuf-1}; banded / FIR: c_0, c_1..c_{nbuf}
   // AdamW-BC
   float lr, b1, b2, eps, wd, bc1, bc2, phi_hat;
   int decoupled_wd, skip_update;
@@ -189,6 +193,12 @@ __device__ __forceinline__ void ftrl_apply8(const ShardStepParams& p, long long 
         }
       }
     }
+    for (int b = 8; b < p.nbuf; ++b) {          // beyond the unrolled eight: same recurrence, buffers re-read below
+      float t[8];
+      ld8(st + b * p.n, t);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) corr[j] += p.coef[b] * t[j];
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) x[j] = z[j] - corr[j];
 #pragma unroll
@@ -206,6 +216,13 @@ __device__ __forceinline__ void ftrl_apply8(const ShardStepParams& p, long long 
         st8(st + b * p.n, t);
       }
     }
+    for (int b = 8; b < p.nbuf; ++b) {
+      float t[8];
+      ld8(st + b * p.n, t);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) t[j] = p.coef[p.nbuf + b] * t[j] + x[j];
+      st8(st + b * p.n, t);
+    }
   } else {
     // ring of the previous nbuf values: mode 2 keeps outputs (banded C, IIR), mode 3 keeps raw draws (FIR)
     float acc[8];
@@ -221,6 +238,14 @@ __device__ __forceinline__ void ftrl_apply8(const ShardStepParams& p, long long 
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] += p.coef[b] * t[j];
       }
+    }
+    for (int b = 9; b <= p.nbuf; ++b) {         // longer histories: a plain loop over the ring
+      int slot = p.ring_head - b;
+      if (slot < 0) slot += p.nbuf;
+      float t[8];
+      ld8(st + slot * p.n, t);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += p.coef[b] * t[j];
     }
     if (p.ftrl_mode == 2) {
 #pragma unroll
@@ -476,7 +501,7 @@ extern "C" int ob_shard_step(float* grad, float* master, float* m, float* v, flo
                              void* stream) {
   if (n <= 0) return 0;
   if (global_offset & 7) return -2;
-  if (ncoef > 16 || nbuf > 8) return -3;
+  if (ncoef > OB_FTRL_MAX_COEF || nbuf >= OB_FTRL_MAX_COEF) return -3;
   ShardStepParams p;
   p.grad = grad; p.master = master; p.m = m; p.v = v; p.ftrl_state = ftrl_state;
   p.peer_params = reinterpret_cast<__nv_bfloat16* const*>(peer_params);
@@ -485,7 +510,7 @@ extern "C" int ob_shard_step(float* grad, float* master, float* m, float* v, flo
   p.n = n; p.global_offset = global_offset; p.world = world; p.seed = seed;
   p.noise_std = noise_std; p.inv_normalize = inv_normalize;
   p.ftrl_mode = ftrl_mode; p.nbuf = nbuf; p.ring_head = ring_head;
-  for (int i = 0; i < 16; ++i) p.coef[i] = (coef && i < ncoef) ? coef[i] : 0.f;
+  for (int i = 0; i < OB_FTRL_MAX_COEF; ++i) p.coef[i] = (coef && i < ncoef) ? coef[i] : 0.f;
   p.lr = lr; p.b1 = b1; p.b2 = b2; p.eps = eps; p.wd = wd; p.bc1 = bc1; p.bc2 = bc2; p.phi_hat = phi_hat;
   p.decoupled_wd = decoupled_wd; p.skip_update = skip_update;
   p.status = status;

@@ -193,7 +193,9 @@ class ShardedDPOptimizer:
     ``mechanism`` is ``None`` (iid Gaussian, DP-SGD) or a dict describing a DP-FTRL inverse:
     ``{"kind": "blt", "scale": [...], "decay": [...]}``, ``{"kind": "banded", "coef": [...]}``
     (``coef[0]`` the diagonal of ``C``; the state holds ``len(coef) − 1`` previous outputs) or
-    ``{"kind": "fir", "coef": [...]}`` (taps of a banded ``C⁻¹``; the state holds previous raw draws).
+    ``{"kind": "fir", "coef": [...]}`` (taps of a banded ``C⁻¹``; the state holds previous raw draws).  A ``"coef_fn"``
+    entry (``step -> coefficients`` of the same length) replaces the coefficients before every step: mechanisms whose
+    rows are scaled step by step (column-normalised λ-CGD).  Up to 63 history buffers (32 BLT pairs).
     """
 
     def __init__(self, space: FlatSpace, config: DPStepConfig, *, key: RngKey, mechanism: dict | None = None):
@@ -209,18 +211,18 @@ class ShardedDPOptimizer:
         if mechanism is not None:
             if mechanism["kind"] == "blt":
                 s, d = list(mechanism["scale"]), list(mechanism["decay"])
-                if len(s) != len(d) or not 1 <= len(s) <= 8:
-                    raise ValueError("BLT needs 1..8 (scale, decay) pairs")
+                if len(s) != len(d) or not 1 <= len(s) <= 32:
+                    raise ValueError("BLT needs 1..32 (scale, decay) pairs")
                 self.mode, self.nbuf, self.coef = 1, len(s), [float(x) for x in s + d]
             elif mechanism["kind"] == "banded":
                 c = [float(x) for x in mechanism["coef"]]
-                if not 2 <= len(c) <= 9 or c[0] == 0:
-                    raise ValueError("banded inverse needs 2..9 coefficients with a non-zero diagonal")
+                if not 2 <= len(c) <= 64 or c[0] == 0:
+                    raise ValueError("banded inverse needs 2..64 coefficients with a non-zero diagonal")
                 self.mode, self.nbuf, self.coef = 2, len(c) - 1, c
             elif mechanism["kind"] == "fir":
                 c = [float(x) for x in mechanism["coef"]]
-                if not 2 <= len(c) <= 9:
-                    raise ValueError("FIR noise needs 2..9 taps")
+                if not 2 <= len(c) <= 64:
+                    raise ValueError("FIR noise needs 2..64 taps")
                 self.mode, self.nbuf, self.coef = 3, len(c) - 1, c
             else:
                 raise ValueError(f"unknown mechanism kind {mechanism['kind']!r}")
@@ -241,6 +243,11 @@ class ShardedDPOptimizer:
         if self.cfg.noise_bias_correction:
             self.phi = b2 * self.phi + (1 - b2) * var
         phi_hat = self.phi / (1 - b2 ** t) if self.cfg.noise_bias_correction else 0.0
+        if self.mechanism is not None and callable(self.mechanism.get("coef_fn")):
+            c = [float(x) for x in self.mechanism["coef_fn"](self.step_count)]
+            if len(c) != len(self.coef):
+                raise ValueError("coef_fn must keep the number of coefficients")
+            self.coef = c
         seed = fold_in(self.key, self.step_count).seed
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if self.timing is not None else None
         if ev:

@@ -186,3 +186,57 @@ def test_paired_second_moment_mf_noise_shares_one_budget():
         single_fn(SecondMomentClippingOutput(clipped(tmpl, C), clipped(tmpl, C2)), single_st)
     with pytest.raises(ValueError):
         noise_fn(SecondMomentClippingOutput(clipped(tmpl, C * 2), clipped(tmpl, C2)), st1)      # the bound must stay constant
+
+
+def test_streaming_matrix_algebra_matches_dense_products():
+    """Products, diagonal scaling and the momentum-SGD workload against their dense definitions."""
+    import numpy as np
+    from opaque_b200.dpftrl import noise as N
+    n = 7
+    fir = N.fir_streaming(np.array([1.0, -0.4, 0.1]))
+    inv = N.toeplitz_inverse_streaming(np.array([1.0, 0.5, 0.25]))
+    A, B = fir.materialize(n), inv.materialize(n)
+    assert np.allclose((fir @ inv).materialize(n), A @ B)
+    r, c = np.linspace(1, 2, n), np.linspace(0.5, 1.5, n)
+    assert np.allclose(N.scale_rows_and_columns(fir, r, c).materialize(n), np.diag(r) @ A @ np.diag(c))
+    assert np.allclose((fir * 3.0).materialize(n), 3.0 * A)
+    assert np.allclose(N.diagonal_streaming([2.0, 5.0]).materialize(4), np.diag([2.0, 5.0, 5.0, 5.0]))
+    x = torch.randn(n, 3, dtype=torch.float64)
+    assert torch.allclose((fir @ x).double(), torch.as_tensor(A) @ x, atol=1e-5)      # streaming states are fp32
+    mu, lr = 0.9, np.array([0.1, 0.2, 0.3, 0.4, 0.5, 0.6, 0.7])
+    W = np.zeros((n, n))
+    for j in range(n):
+        mom = acc = 0.0
+        for t in range(n):
+            mom = mu * mom + (1.0 if t == j else 0.0)
+            acc = acc + lr[t] * mom
+            W[t, j] = acc
+    assert np.allclose(N.momentum_sgd_matrix(mu, lr).materialize(n), W)
+
+
+def test_lambda_cgd_is_column_normalised_per_row():
+    """Normalised λ-CGD: ``C⁻¹`` rows carry ``d_t`` (column norms of ``C``), every column of ``C·diag(d)⁻¹`` has unit norm,
+    the streaming operator equals the dense inverse, and the sensitivity equals the brute-force value from the Gram."""
+    import itertools
+    import numpy as np
+    from opaque_b200.dpftrl import noise as N
+    n, lam = 9, 0.6
+    st = N.lambda_cgd_strategy(lambda_=lam, normalized=True)
+    C = np.array([[lam ** (i - j) if i >= j else 0.0 for j in range(n)] for i in range(n)])
+    d = np.sqrt((C ** 2).sum(0))
+    assert np.allclose(st.row_scales(n), d)
+    Cn = C / d[None, :]
+    assert np.allclose((Cn ** 2).sum(0), 1.0)
+    assert np.allclose(st.streaming_matrix(n).materialize(n), np.linalg.inv(Cn))
+    assert np.allclose(st.gram_matrix(n), Cn.T @ Cn)
+    for min_sep, k in ((1, 1), (2, None), (3, 2), (1, 3)):
+        best = 0.0
+        kk = k if k is not None else n
+        for r in range(1, kk + 1):
+            for idx in itertools.combinations(range(n), r):
+                if all(b - a >= min_sep for a, b in zip(idx, idx[1:])):
+                    best = max(best, float(np.linalg.norm(Cn[:, list(idx)].sum(1))))
+        assert math.isclose(st.sensitivity(n, min_sep, k), best, rel_tol=1e-9), (min_sep, k)
+    assert math.isclose(st.row_norm(n, 0), d[0]) and math.isclose(st.row_norm(n, 4), d[4] * math.sqrt(1 + lam * lam))
+    mech = st.fused_mechanism(n)
+    assert mech["kind"] == "fir" and np.allclose(mech["coef_fn"](5), [d[5], -lam * d[5]])

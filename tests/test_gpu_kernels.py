@@ -540,3 +540,38 @@ def test_philox_gaussian_tails_follow_the_normal_law(dev):
         assert abs(got - n * p) < 5 * sd, (got, n * p, sd)
     assert 5.5 < top <= 6.77
     assert abs(s1 / n) < 5 / math.sqrt(n) and abs(s2 / n - 1.0) < 5 * math.sqrt(2.0 / n)
+
+
+@pytest.mark.parametrize("name", ["identity", "mf_band16", "mf_blt10", "mf_bsr8", "mf_bisr4", "mf_lambda_cgd"])
+def test_fused_correlated_noise_equals_the_streaming_path_for_every_strategy(dev, name):
+    """The fused shard step's correlated noise (any history length) against the strategy's streaming ``C⁻¹`` applied to the
+    SAME Philox draws, over 50 steps; the mechanism dictionary comes from the strategy's own ``fused_mechanism``."""
+    from opaque_b200 import dpftrl, ops
+    from opaque_b200.parallel.peer import PeerGroup
+    from opaque_b200.parallel.sharded import DPStepConfig, FlatSpace, ShardedDPOptimizer
+    from opaque_b200.random import fold_in, key
+    steps = 50
+    strat = {"identity": lambda: dpftrl.identity_strategy(), "mf_band16": lambda: dpftrl.band_mf_strategy(bands=16),
+             "mf_blt10": lambda: dpftrl.blt_strategy(max_buffers=10), "mf_bsr8": lambda: dpftrl.bsr_strategy(bandwidth=8),
+             "mf_bisr4": lambda: dpftrl.bisr_strategy(bandwidth=4),
+             "mf_lambda_cgd": lambda: dpftrl.lambda_cgd_strategy(lambda_=0.7, normalized=True)}[name]()
+    p = torch.nn.Parameter(torch.zeros(1024, 8, device=dev, dtype=torch.bfloat16))
+    space = FlatSpace([("w", p)], PeerGroup(dev))
+    space.bind()
+    k = key(11)
+    mech = strat.fused_mechanism(steps)
+    opt = ShardedDPOptimizer(space, DPStepConfig(lr=0.0), key=k, mechanism=mech)
+    if name in ("mf_band16", "mf_blt10"):
+        assert opt.nbuf > 8                                    # beyond the unrolled fast path
+    sm = strat.streaming_matrix(steps)
+    n = space.shard
+    state = sm.init_multiply(torch.zeros(n, device=dev))
+    out = torch.zeros(n, device=dev)
+    worst = 0.0
+    for t in range(steps):
+        z = torch.zeros(n, device=dev)
+        ops.philox_normal_add_(z, seed=fold_in(k, t).seed, offset=0, std=1.0)
+        want, state = sm.multiply_next(z, state)
+        opt.step(noise_std=1.0, normalize_by=1.0, noisy_out=out, skip_update=True)
+        worst = max(worst, float((out - want).abs().max()) / (float(want.abs().max()) + 1e-12))
+    assert worst < 2e-4, worst

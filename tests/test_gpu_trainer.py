@@ -52,7 +52,10 @@ def test_fused_trainer_steps_checkpoints_and_resumes(tmp_path):
 
 @pytest.mark.parametrize("kw", [dict(dp_cuda_graph=True), dict(privacy_noise_mechanism="mf_blt", privacy_noise_mechanism_kwargs={"max_buffers": 2},
                                                               sampling_mode="sequential"),
-                                dict(clipping_mode="adaptive", clipping_norm=0.5), dict(clipping_mode="auto")])
+                                dict(clipping_mode="adaptive", clipping_norm=0.5), dict(clipping_mode="auto"),
+                                dict(privacy_noise_mechanism="mf_band"), dict(privacy_noise_mechanism="mf_bsr"),
+                                dict(privacy_noise_mechanism="mf_bisr"), dict(privacy_noise_mechanism="mf_lambda_cgd"),
+                                dict(privacy_noise_mechanism="mf_identity")])
 def test_fused_trainer_options(tmp_path, kw):
     from opaque_b200.transformers import DPTrainer
     tr = DPTrainer(model=_model(lora=kw.get("privacy_noise_mechanism") is None), args=_args(tmp_path, save_steps=0, **kw), train_dataset=_rows())

@@ -28,6 +28,7 @@
 // and the gate/up/SwiGLU sequence of kernels/swiglu.py:29-58.
 #include "common.cuh"
 #include "api.h"
+#include <cstdlib>
 
 namespace ob {
 
@@ -53,7 +54,7 @@ constexpr int GP_A_BYTES = GP_BM * GP_BK * 2;
 constexpr int GP_B_BYTES = GP_BNH * GP_BK * 2;
 constexpr int GP_STAGE_BYTES = GP_A_BYTES + GP_B_BYTES;
 constexpr int GP_THREADS = 320;       // TMA warp, MMA warp, 2 x 4 epilogue warps
-constexpr int GP_GROUP_M = 4;        // pair tiles (512 rows each) per raster band
+constexpr int GP_GROUP_M = 8;        // pair tiles (512 rows each) per raster band (measured: 8 >= 4 > 16 on the MLP shapes)
 constexpr int GP_SLAB_BYTES = 4096;   // per epilogue warp: a 32-row x 64-column (or 2 x 32-column) bf16 staging tile
 constexpr int GP_SMEM = GP_STAGES * GP_STAGE_BYTES + 8 * GP_SLAB_BYTES + 256 + 1024;
 
@@ -68,6 +69,7 @@ struct PairParams {
   __nv_bfloat16* out_up;
   const __nv_bfloat16* bias;         // STORE only
   int act;                           // GLU: 0 silu, 1 gelu (erf), 2 gelu (tanh)
+  int group_m;                       // pair tiles (512 rows each) per raster band
   // CE epilogue (output head + cross-entropy statistics; `out` optional: the bf16, soft-capped logits)
   const long long* labels;           // [M]
   float4* ce_partials;               // [M, tiles_n]: (max, sum exp(z - max), z[label] or 0, sum z) over the tile's columns
@@ -160,11 +162,11 @@ struct GpItem {
   int nt;        // tile index along N
 };
 
-__device__ __forceinline__ GpItem gp_decode(int w, int tiles_m, int tiles_n, int rank) {
-  const int band = GP_GROUP_M * tiles_n;
+__device__ __forceinline__ GpItem gp_decode(int w, int tiles_m, int tiles_n, int rank, int group_m) {
+  const int band = group_m * tiles_n;
   const int b = w / band, r = w % band;
-  const int m_in_band = min(GP_GROUP_M, tiles_m - b * GP_GROUP_M);
-  const int mt = b * GP_GROUP_M + r % m_in_band;
+  const int m_in_band = min(group_m, tiles_m - b * group_m);
+  const int mt = b * group_m + r % m_in_band;
   GpItem it;
   it.row0 = mt * (2 * GP_BM) + rank * GP_BM;
   it.nt = r / m_in_band;
@@ -317,7 +319,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const CUtensorMap* mb1 = (EPI == GP_EPI_GLU && rank == 1) ? &map_b_up : &map_b;
       const CUtensorMap* mb2 = (EPI == GP_EPI_GLU && rank == 1) ? &map_b2_up : &map_b2;
       for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
-        const GpItem it = gp_decode(w, tiles_m, tiles_n, rank);
+        const GpItem it = gp_decode(w, tiles_m, tiles_n, rank, p.group_m);
         // first column of N (= row of a [N, K] operand) of this CTA's half of the B tile
         const int bn0 = EPI == GP_EPI_GLU ? it.nt * GP_BNH : it.nt * GP_BN + static_cast<int>(rank) * GP_BNH;
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -445,7 +447,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         (EPI != GP_EPI_GLU || p.out_gate == nullptr ||
                          (((reinterpret_cast<uintptr_t>(p.out_gate) | reinterpret_cast<uintptr_t>(p.out_up)) & 15) == 0));
     for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
-      const GpItem it = gp_decode(w, tiles_m, tiles_n, rank);
+      const GpItem it = gp_decode(w, tiles_m, tiles_n, rank, p.group_m);
 #pragma unroll 1
       for (int h = 0; h < 2; ++h) {
         if (!mbar_wait_idle(&tmem_full[h], acc_iter & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL, budget)) {
@@ -664,6 +666,17 @@ lce_dlogits_kernel(__nv_bfloat16* __restrict__ z, const long long* __restrict__ 
   }
 }
 
+// Raster band height in pair tiles (L2 reuse of the B tiles inside a band); OB_PAIR_GROUP_M overrides it for experiments.
+static int pair_group_m() {
+  static int v = 0;
+  if (v == 0) {
+    const char* e = getenv("OB_PAIR_GROUP_M");
+    v = e ? atoi(e) : GP_GROUP_M;
+    if (v < 1) v = GP_GROUP_M;
+  }
+  return v;
+}
+
 static int pair_grid(const void* kernel, int sms) {
   // clusters that can be co-resident (two CTAs of a pair must sit on paired SMs); one cluster per SM pair
   cudaLaunchConfig_t cfg = {};
@@ -745,6 +758,7 @@ extern "C" int ob_gemm_pair(const void* a, const void* b, const void* b_up, cons
     configured = true;
   }
   PairParams p = {};
+  p.group_m = pair_group_m();
   p.M = static_cast<int>(rows_a);
   p.N = N; p.K1 = K1; p.K2 = K2;
   p.kn1 = b_kn; p.kn2 = b2_kn;
@@ -801,6 +815,7 @@ extern "C" int ob_linear_ce_fwd(const void* hidden, const void* weight, const lo
     configured = true;
   }
   PairParams p = {};
+  p.group_m = pair_group_m();
   p.M = static_cast<int>(rows);
   p.N = N; p.K1 = K; p.K2 = 0;
   p.out = static_cast<__nv_bfloat16*>(logits_out);
@@ -921,6 +936,7 @@ extern "C" int ob_linear_ce_fwd_noalloc(const void* hidden, const void* weight, 
     configured = true;
   }
   PairParams p = {};
+  p.group_m = pair_group_m();
   p.M = static_cast<int>(rows);
   p.N = N; p.K1 = K; p.K2 = 0;
   p.out = nullptr;                    // forward only: the logits never reach memory

@@ -704,10 +704,16 @@ class DPTrainer:
             torch.use_deterministic_algorithms(True, warn_only=True)
             os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
         inert = self.inert_arguments()
+        # settings that would change WHAT is trained if they were honoured are refused, not ignored
+        refused = {k: v for k, v in inert.items() if k in ("torch_compile", "dataloader_drop_last", "use_mps_device", "label_names")}
+        if refused:
+            raise ValueError("these TrainingArguments cannot be honoured by this trainer (no tracing compiler on the hot path, batches "
+                             "come from the DP sampler, CUDA / CPU devices only, labels are derived from input_ids): "
+                             + ", ".join(f"{k}={v!r}" for k, v in sorted(refused.items())))
         if inert and self.is_world_process_zero():
             import warnings
-            warnings.warn("these TrainingArguments are accepted for compatibility and have no effect here: "
-                          + ", ".join(sorted(inert)), stacklevel=3)
+            warnings.warn("these TrainingArguments are accepted for compatibility and have NO effect here: "
+                          + ", ".join(f"{k}={v!r}" for k, v in sorted(inert.items())), RuntimeWarning, stacklevel=3)
 
     def _setup(self, resume: str | None) -> None:
         a = self.args

@@ -255,21 +255,15 @@ class TrainingArguments:
 
     @classmethod
     def from_hf(cls, hf_args: Any, **overrides: Any) -> "TrainingArguments":
-        """Build from a Hugging Face ``TrainingArguments``-like object; sharded-training options are rejected."""
-        get = (lambda k, d=None: hf_args.get(k, d)) if isinstance(hf_args, Mapping) else (lambda k, d=None: getattr(hf_args, k, d))
-        for bad in ("fsdp", "fsdp_config", "deepspeed"):
-            if get(bad):
-                raise ValueError(f"{bad} is not supported: data parallelism (with sharded DP state) is the only mode")
-        if (get("gradient_accumulation_steps", 1) or 1) != 1:
-            raise ValueError("gradient_accumulation_steps has no DP meaning here; use microbatch_size")
-        names = {f.name for f in dataclasses.fields(cls)}
-        kw = {n: get(n) for n in names if get(n) is not None and not n.startswith("_")}
-        if get("max_grad_norm") is not None and "clipping_norm" not in overrides:
-            kw["clipping_norm"] = float(get("max_grad_norm"))
-        if get("lr_scheduler_type") is not None:
-            kw["lr_scheduler"] = str(getattr(get("lr_scheduler_type"), "value", get("lr_scheduler_type")))
-        kw.update(overrides)
-        return cls(**kw)
+        """Build from a Hugging Face ``TrainingArguments`` (object or mapping); ``overrides`` carry the DP settings.
+
+        The conversion is manifest-driven (:mod:`opaque_b200.transformers.hf_convert`): the effective Hugging Face batch
+        (per-device × accumulation) becomes the logical Poisson batch and the per-device size the microbatch,
+        ``max_grad_norm`` becomes the per-example clipping norm, optimizer aliases collapse onto ``adamw``, sharded-model /
+        quantised-optimizer options are refused, fields without meaning here are dropped with a warning."""
+        from .hf_convert import convert_hf_training_arguments
+        own = {f.name for f in dataclasses.fields(cls) if not f.name.startswith("_")}
+        return cls(**convert_hf_training_arguments(hf_args, own, **overrides))
 
 
 __all__ = ["ALLOWED_SAMPLERS", "MECHANISMS", "MECH_DEFAULTS", "SAMPLER_BY_MECHANISM", "SAMPLING_MODES",

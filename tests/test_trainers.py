@@ -53,6 +53,33 @@ def test_training_arguments_validation_and_parsing():
     assert hf.clipping_norm == 0.5 and hf.lr_scheduler == "cosine"
 
 
+def test_hf_training_arguments_conversion_manifest():
+    """Every field of the installed transformers.TrainingArguments is classified; the batch collapse keeps the
+    privacy-relevant batch; refused and ignored fields behave as documented."""
+    import dataclasses
+
+    import transformers
+
+    from opaque_b200.transformers import hf_convert
+    own = {f.name for f in dataclasses.fields(TrainingArguments) if not f.name.startswith("_")}
+    unknown = [f.name for f in dataclasses.fields(transformers.TrainingArguments) if hf_convert.classify(f.name, own) == "unknown"]
+    assert not unknown, unknown
+    # (a mapping with the Hugging Face field names: instantiating transformers.TrainingArguments itself needs accelerate)
+    hf = dict(output_dir="x", per_device_train_batch_size=4, gradient_accumulation_steps=8, learning_rate=3e-4, max_grad_norm=0.7,
+              optim="adamw_torch_fused", lr_scheduler_type="cosine", warmup_ratio=0.1, auto_find_batch_size=True, use_cpu=True,
+              report_to="none", do_train=False, fsdp="", deepspeed=None)
+    a = TrainingArguments.from_hf(hf, privacy_noise_multiplier=1.0)
+    assert a.per_device_train_batch_size == 32 and a.microbatch_size == 4 and a.auto_find_microbatch_size
+    assert a.clipping_norm == 0.7 and a.optim == "adamw" and a.lr_scheduler == "cosine" and a.warmup_steps == 0.1
+    assert a.learning_rate == 3e-4 and a.privacy_noise_multiplier == 1.0
+    assert TrainingArguments.from_hf({"max_grad_norm": 0.7}, clipping_norm=2.0, privacy_noise_multiplier=1.0).clipping_norm == 2.0
+    for bad in ({"fsdp": "full_shard"}, {"deepspeed": "ds.json"}, {"optim": "paged_adamw_8bit"}, {"neftune_noise_alpha": 5.0}, {"fp16": True}):
+        with pytest.raises(ValueError):
+            TrainingArguments.from_hf(bad, privacy_noise_multiplier=1.0)
+    with pytest.warns(RuntimeWarning, match="ddp_bucket_cap_mb"):
+        TrainingArguments.from_hf({"ddp_bucket_cap_mb": 50}, privacy_noise_multiplier=1.0)
+
+
 def test_dp_trainer_runs_logs_and_accounts(tmp_path):
     torch.manual_seed(0)
     tr = DPTrainer(model=TinyLM(), args=_args(tmp_path), train_dataset=_data(), eval_dataset=_data(16, seed=1))
@@ -195,7 +222,7 @@ def test_compatibility_arguments_are_applied_or_named(tmp_path):
                  prediction_loss_only=True, tf32=True)
     tr = DPTrainer(model=TinyLM(), args=args, train_dataset=data, eval_dataset=held_out)
     assert set(tr.inert_arguments()) == {"dataloader_num_workers", "hub_model_id"}
-    with pytest.warns(UserWarning, match="dataloader_num_workers, hub_model_id"):
+    with pytest.warns(RuntimeWarning, match="dataloader_num_workers=4, hub_model_id='x/y'"):
         out = tr.train()
     assert out["train_tokens_per_second"] > 0 and out["num_input_tokens_seen"] > 0
     best = tr.state.best_model_checkpoint
@@ -205,6 +232,9 @@ def test_compatibility_arguments_are_applied_or_named(tmp_path):
     assert math.isclose(tr.evaluate(held_out)["eval_loss"], tr.state.best_metric, rel_tol=1e-5)   # the best weights are back
     pred = tr.predict(held_out)
     assert pred.predictions is None and "test_loss" in pred.metrics
+    # a setting that would change what is trained if it were honoured is refused instead of ignored
+    with pytest.raises(ValueError, match="torch_compile"):
+        DPTrainer(model=TinyLM(), args=_args(tmp_path / "c", torch_compile=True, save_steps=0), train_dataset=data).train()
     # label smoothing: the trainer's default loss mixes in the uniform target (reference engine)
     from opaque_b200.transformers.trainer import default_per_example_loss
     model = TinyLM()

@@ -2,7 +2,7 @@
 
 Parity: packages/opaque-alignment/src/opaque/alignment/__init__.py (namespaces ``data, dpo, metric, sft``).
 """
-from . import data, dpo, sft
+from . import chat_template, data, dpo, sft
 from . import sft as metric
 
-__all__ = ["data", "dpo", "metric", "sft"]
+__all__ = ["chat_template", "data", "dpo", "metric", "sft"]

@@ -100,5 +100,8 @@ def split_prompt_completion(messages: Sequence[Mapping[str, str]]):
     return list(messages[:last]), list(messages[last:])
 
 
-__all__ = ["IGNORE_INDEX", "apply_chat_template", "completion_mask", "language_modeling_collator",
+from .chat_template import apply_chat_template_with_mask, clone_chat_template, get_training_chat_template  # noqa: E402
+
+__all__ = ["IGNORE_INDEX", "apply_chat_template", "apply_chat_template_with_mask", "clone_chat_template", "completion_mask",
+           "get_training_chat_template", "language_modeling_collator",
            "preference_collator", "shift_labels", "split_prompt_completion"]

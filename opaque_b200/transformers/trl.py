@@ -78,6 +78,15 @@ class SFTTrainer(DPTrainer):
             c = tokenizer(row["completion"], add_special_tokens=False)["input_ids"]
             ids = (p + c)[: args.max_length] if args.max_length else p + c
             return {"input_ids": ids, "completion_mask": adata.completion_mask(len(ids), len(p))}
+        if "messages" in row and args.assistant_only_loss and getattr(tokenizer, "chat_template", None):
+            # every assistant turn of a multi-turn conversation carries loss: the mask comes from the template's
+            # {% generation %} markers (installed on a private copy of the template when they are missing)
+            template = adata.get_training_chat_template(tokenizer)
+            enc = adata.apply_chat_template_with_mask(tokenizer, list(row["messages"]), chat_template=template)
+            ids, mask = enc["input_ids"], enc["completion_mask"]
+            if args.max_length:
+                ids, mask = ids[: args.max_length], mask[: args.max_length]
+            return {"input_ids": ids, "completion_mask": mask}
         if "messages" in row:
             prompt, completion = adata.split_prompt_completion(row["messages"])
             p = tokenizer(adata.apply_chat_template(prompt, tokenizer, add_generation_prompt=True))["input_ids"]

@@ -116,6 +116,42 @@ PYBIND11_MODULE(_native, m) {
   m.def("blt_sensitivity_squared", [](std::vector<double> s, std::vector<double> d, std::int64_t n, std::int64_t ms, py::object mp) {
     return blt_sens_sq(s, d, n, ms, opt_int(mp)); }, py::arg("scale"), py::arg("decay"), py::arg("n"), py::arg("min_sep") = 1, py::arg("max_participations") = py::none());
   m.def("toeplitz_gram_matrix", &toeplitz_gram);
+  // ---- Toeplitz-column strategies (lambda-CGD, banded inverse square root), optionally column-normalised
+  auto mp = [](py::object o) -> std::int64_t { return o.is_none() ? -1 : o.cast<std::int64_t>(); };
+  m.def("lambda_cgd_sensitivity_squared", [mp](double l, std::size_t n, std::int64_t ms, py::object k, double) {
+    return lambda_cgd_sens_sq(l, n, ms, mp(k), false); },
+    py::arg("lambda_"), py::arg("n_steps"), py::arg("min_sep") = 1, py::arg("max_participations") = py::none(), py::arg("momentum") = 0.0);
+  m.def("lambda_cgd_normalized_sensitivity_squared", [mp](double l, std::size_t n, std::int64_t ms, py::object k, double) {
+    return lambda_cgd_sens_sq(l, n, ms, mp(k), true); },
+    py::arg("lambda_"), py::arg("n_steps"), py::arg("min_sep") = 1, py::arg("max_participations") = py::none(), py::arg("momentum") = 0.0);
+  m.def("lambda_cgd_max_column_norm", &lambda_cgd_max_column_norm, py::arg("lambda_"), py::arg("n_steps"));
+  m.def("lambda_cgd_gram_matrix", [mp](double l, std::size_t n, std::int64_t ms, py::object k, bool norm, double beta) {
+    const std::int64_t kk = mp(k); py::gil_scoped_release r; return lambda_cgd_bnb_gram(l, n, ms, kk, norm, beta, nullptr); },
+    py::arg("lambda_"), py::arg("n_steps"), py::arg("min_sep") = 1, py::arg("max_participations") = py::none(),
+    py::arg("normalized") = true, py::arg("momentum") = 0.0);
+  m.def("lambda_cgd_gram_matrix_lr", [mp](double l, double beta, std::size_t n, std::int64_t ms, py::object k, bool norm, std::vector<double> w) {
+    const std::int64_t kk = mp(k); py::gil_scoped_release r; return lambda_cgd_bnb_gram(l, n, ms, kk, norm, beta, &w); },
+    py::arg("lambda_"), py::arg("momentum"), py::arg("n_steps"), py::arg("min_sep"), py::arg("max_participations"),
+    py::arg("normalized"), py::arg("lr_weights"));
+  m.def("bisr_strategy_coefficients", &inverse_toeplitz_coefficients, py::arg("coefficients"), py::arg("n"));
+  m.def("bisr_sensitivity_squared", [mp](std::vector<double> taps, std::size_t n, std::int64_t ms, py::object k, double) {
+    return toeplitz_columns_sens_sq(inverse_toeplitz_coefficients(taps, n), n, ms, mp(k), false); },
+    py::arg("coefficients"), py::arg("n_steps"), py::arg("min_sep") = 1, py::arg("max_participations") = py::none(), py::arg("momentum") = 0.0);
+  m.def("bisr_normalized_sensitivity_squared", [mp](std::vector<double> taps, std::size_t n, std::int64_t ms, py::object k, double) {
+    return toeplitz_columns_sens_sq(inverse_toeplitz_coefficients(taps, n), n, ms, mp(k), true); },
+    py::arg("coefficients"), py::arg("n_steps"), py::arg("min_sep") = 1, py::arg("max_participations") = py::none(), py::arg("momentum") = 0.0);
+  m.def("bisr_gram_matrix", [mp](std::vector<double> taps, std::size_t n, std::int64_t ms, py::object k, bool norm, double beta) {
+    const std::int64_t kk = mp(k); py::gil_scoped_release r; return toeplitz_columns_bnb_gram(inverse_toeplitz_coefficients(taps, n), n, ms, kk, norm, beta, nullptr); },
+    py::arg("coefficients"), py::arg("n_steps"), py::arg("min_sep") = 1, py::arg("max_participations") = py::none(),
+    py::arg("normalized") = true, py::arg("momentum") = 0.0);
+  m.def("bisr_gram_matrix_lr", [mp](std::vector<double> taps, double beta, std::size_t n, std::int64_t ms, py::object k, bool norm, std::vector<double> w) {
+    const std::int64_t kk = mp(k); py::gil_scoped_release r; return toeplitz_columns_bnb_gram(inverse_toeplitz_coefficients(taps, n), n, ms, kk, norm, beta, &w); },
+    py::arg("coefficients"), py::arg("momentum"), py::arg("n_steps"), py::arg("min_sep"), py::arg("max_participations"),
+    py::arg("normalized"), py::arg("lr_weights"));
+  m.def("toeplitz_bnb_gram_matrix", [mp](std::vector<double> coef, std::size_t n, std::int64_t ms, py::object k, bool norm) {
+    const std::int64_t kk = mp(k); py::gil_scoped_release r; return toeplitz_columns_bnb_gram(coef, n, ms, kk, norm, 0.0, nullptr); },
+    py::arg("strategy_coef"), py::arg("n_steps"), py::arg("min_sep") = 1, py::arg("max_participations") = py::none(),
+    py::arg("normalized") = true);
   m.def("norm_ppf", &norm_ppf);
   m.def("norm_cdf", &norm_cdf);
 }

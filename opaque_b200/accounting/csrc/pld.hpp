@@ -145,4 +145,17 @@ double blt_sens_sq(const std::vector<double>& scale, const std::vector<double>& 
                    std::int64_t min_sep, std::int64_t max_part);
 std::vector<double> toeplitz_gram(const std::vector<double>& coef, std::size_t n);
 
+// ---- Toeplitz-column strategies, optionally column-normalised (mf.cpp): lambda-CGD, banded inverse square root ----
+// max_part < 0 means "as many as min_sep allows".
+std::vector<double> inverse_toeplitz_coefficients(const std::vector<double>& taps, std::size_t n);
+double toeplitz_columns_sens_sq(const std::vector<double>& coef, std::size_t n, std::int64_t min_sep, std::int64_t max_part,
+                                bool normalized);
+std::vector<double> toeplitz_columns_bnb_gram(const std::vector<double>& coef, std::size_t n, std::int64_t min_sep,
+                                              std::int64_t max_part, bool normalized, double momentum,
+                                              const std::vector<double>* lr_weights);
+double lambda_cgd_sens_sq(double lambda, std::size_t n, std::int64_t min_sep, std::int64_t max_part, bool normalized);
+double lambda_cgd_max_column_norm(double lambda, std::size_t n);
+std::vector<double> lambda_cgd_bnb_gram(double lambda, std::size_t n, std::int64_t min_sep, std::int64_t max_part,
+                                        bool normalized, double momentum, const std::vector<double>* lr_weights);
+
 }  // namespace obacc

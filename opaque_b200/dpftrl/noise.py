@@ -552,27 +552,8 @@ class LambdaCgdStrategy(MfStrategy):
     def sensitivity(self, n, min_sep=1, max_participations=None):
         """Largest norm of a sum of participating columns of ``C·diag(d)⁻¹`` (all inner products are non-negative, so the
         worst record takes part as often as ``min_sep`` / ``max_participations`` allow): ``⟨c'_i, c'_j⟩ = λ^{j−i} d_j / d_i``."""
-        d = self.row_scales(n)
-        if not self.normalized:
-            return math.sqrt(toeplitz_sensitivity_squared(self.coefficients(n), n, min_sep, max_participations))
-        b = max(int(min_sep), 1)
-        k_max = max_participations if max_participations is not None else math.ceil(n / b)
-        best = 0.0
-        for start in range(min(b, n)):
-            idx = list(range(start, n, b))[:k_max]
-            tot = 0.0
-            for a_i, i in enumerate(idx):
-                tot += 1.0
-                for j in idx[a_i + 1:]:
-                    tot += 2.0 * (self.lambda_ ** (j - i)) * d[j] / d[i]
-            best = max(best, tot)
-            # a later window of k_max participations can be heavier than the first one: slide it
-            full = list(range(start, n, b))
-            for off in range(1, max(0, len(full) - k_max) + 1):
-                w = full[off:off + k_max]
-                tot = sum(1.0 for _ in w) + sum(2.0 * (self.lambda_ ** (j - i)) * d[j] / d[i] for a_i, i in enumerate(w) for j in w[a_i + 1:])
-                best = max(best, tot)
-        return math.sqrt(best)
+        fn = native.lambda_cgd_normalized_sensitivity_squared if self.normalized else native.lambda_cgd_sensitivity_squared
+        return math.sqrt(float(fn(self.lambda_, int(n), int(min_sep), max_participations)))
 
     def streaming_matrix(self, n):
         base = fir_streaming(np.array([1.0, -self.lambda_]))

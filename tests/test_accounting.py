@@ -137,3 +137,53 @@ def test_native_sensitivities():
     # identity strategy: k participations -> sensitivity^2 = k
     assert native.toeplitz_minsep_sensitivity_squared([1.0], 12, 3, None) == 4.0
     assert abs(native.norm_ppf(0.975) - 1.959963984540054) < 1e-12
+
+
+def test_native_lambda_cgd_and_bisr_matrix_functions_match_dense_algebra():
+    """Column-normalised Toeplitz strategies in the native core against dense numpy constructions."""
+    import itertools
+
+    import numpy as np
+    from opaque_b200.accounting.core import native
+    n, lam, b, k = 12, 0.65, 3, 3
+    C = np.array([[lam ** (i - j) if i >= j else 0.0 for j in range(n)] for i in range(n)])
+    d = np.sqrt((C ** 2).sum(0))
+    Cn = C / d
+
+    def brute(M, min_sep, kmax):
+        best = 0.0
+        for r in range(1, kmax + 1):
+            for idx in itertools.combinations(range(n), r):
+                if all(y - x >= min_sep for x, y in zip(idx, idx[1:])):
+                    best = max(best, float((M[:, list(idx)].sum(1) ** 2).sum()))
+        return best
+    assert math.isclose(native.lambda_cgd_sensitivity_squared(lam, n, b, k), brute(C, b, k), rel_tol=1e-9)
+    assert math.isclose(native.lambda_cgd_normalized_sensitivity_squared(lam, n, b, k), brute(Cn, b, k), rel_tol=1e-9)
+    assert math.isclose(native.lambda_cgd_normalized_sensitivity_squared(lam, n, 1, 1), 1.0, rel_tol=1e-12)
+    assert math.isclose(native.lambda_cgd_max_column_norm(lam, n), d[0], rel_tol=1e-12)
+    # balls-in-bins Gram: m_i = sum over epochs of column (b e + i), momentum filter and per-row weights on top
+    E = n // b
+    for beta, w in ((0.0, None), (0.8, None), (0.5, np.linspace(1.0, 0.2, n))):
+        F = np.array([[beta ** (i - j) if i >= j else 0.0 for j in range(n)] for i in range(n)])
+        M = F @ Cn
+        if w is not None:
+            M = np.diag(w) @ M
+        m = np.stack([sum(M[:, b * e + i] for e in range(E)) for i in range(b)])
+        want = m @ m.T
+        got = (native.lambda_cgd_gram_matrix(lam, n, b, None, True, beta) if w is None else
+               native.lambda_cgd_gram_matrix_lr(lam, beta, n, b, None, True, w.tolist()))
+        assert np.allclose(np.array(got).reshape(b, b), want, rtol=1e-10)
+    # banded inverse square root: C is the dense inverse of the banded C^-1
+    taps = [1.0, -0.5, -0.125, -0.0625]
+    Cinv = np.array([[taps[i - j] if 0 <= i - j < len(taps) else 0.0 for j in range(n)] for i in range(n)])
+    Cb = np.linalg.inv(Cinv)
+    assert np.allclose(native.bisr_strategy_coefficients(taps, n), Cb[:, 0])
+    assert math.isclose(native.bisr_sensitivity_squared(taps, n, b, k), brute(Cb, b, k), rel_tol=1e-9)
+    Cbn = Cb / np.sqrt((Cb ** 2).sum(0))
+    assert math.isclose(native.bisr_normalized_sensitivity_squared(taps, n, b, k), brute(Cbn, b, k), rel_tol=1e-9)
+    mb = np.stack([sum(Cbn[:, b * e + i] for e in range(E)) for i in range(b)])
+    assert np.allclose(np.array(native.bisr_gram_matrix(taps, n, b, None, True, 0.0)).reshape(b, b), mb @ mb.T, rtol=1e-10)
+    # the strategy object's own (Python) sensitivity agrees with the native one
+    from opaque_b200.dpftrl import noise as N
+    st = N.lambda_cgd_strategy(lambda_=lam, normalized=True)
+    assert math.isclose(st.sensitivity(n, b, k) ** 2, native.lambda_cgd_normalized_sensitivity_squared(lam, n, b, k), rel_tol=1e-9)

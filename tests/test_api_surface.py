@@ -74,3 +74,16 @@ def test_key_signatures():
                                               "preprocess_logits_for_metrics"]
     for m in ("train", "evaluate", "predict", "save_model", "training_step"):
         assert callable(getattr(DPTrainer, m))
+
+
+def test_native_accounting_stub_declares_every_public_name():
+    """``accounting/_native.pyi`` is the typed surface of the C++ core: nothing public is missing from it."""
+    import ast
+    import pathlib
+
+    from opaque_b200.accounting import _native
+    stub = pathlib.Path(_native.__file__).with_name("_native.pyi")
+    tree = ast.parse(stub.read_text())
+    declared = {n.name for n in tree.body if isinstance(n, (ast.FunctionDef, ast.ClassDef))}
+    public = {n for n in dir(_native) if not n.startswith("_")}
+    assert public <= declared, sorted(public - declared)

@@ -1,0 +1,54 @@
+"""Named argument presets shared by the example scripts: ``--preset NAME`` fills in a documented configuration, explicit
+command-line flags still win.
+
+Parity: the ``--preset`` tables of the reference's examples (examples/train_dpsgd.py:845-900: ``smoke``,
+``mellum-kstack`` …); the presets here name this repository's benchmark configurations (synthetic data, no downloads).
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+
+PRESETS: dict[str, dict[str, dict]] = {
+    "train_dpsgd": {
+        "smoke": dict(steps=10, n=2048, batch=64, sigma=1.0, lr=0.1),
+        "mlp-60k": dict(steps=200, n=60000, batch=256, clip=1.0, sigma=1.0, lr=0.1, delta=1e-5),     # benchmark config 1
+    },
+    "train_dpftrl": {
+        "smoke": dict(steps=8, n=512, batch=16, seq=8),
+        "blt-4": dict(strategy="blt", buffers=4, sampler="sequential", steps=64, batch=32, sigma=2.0),
+        "band-16": dict(strategy="band_mf", bands=16, sampler="b_min_sep", steps=64, batch=32, sigma=2.0),
+        "lambda-cgd": dict(strategy="lambda_cgd", lambda_=0.5, sampler="balls_in_bins", steps=64, batch=32, sigma=2.0),
+    },
+    "train_sft": {
+        "smoke": dict(steps=5, n=256, batch=16),
+        "dft": dict(steps=40, n=2048, batch=64, loss="dft", sigma=0.8, lr=5e-3),
+    },
+    "train_dpo": {
+        "smoke": dict(steps=5, n=128, batch=8),
+        "ipo": dict(steps=40, n=1024, batch=32, loss_type="ipo", beta=0.1, sigma=0.8),
+        "simpo": dict(steps=40, n=1024, batch=32, loss_type="simpo", beta=2.0, sigma=0.8),
+    },
+}
+
+
+def add_preset_argument(ap: argparse.ArgumentParser, script: str) -> None:
+    names = sorted(PRESETS[script])
+    ap.add_argument("--preset", default=None, choices=names, help="named configuration; explicit flags override it")
+
+
+def apply_preset(ap: argparse.ArgumentParser, args: argparse.Namespace, script: str, argv: list[str] | None = None) -> argparse.Namespace:
+    """Fill ``args`` from the chosen preset, except for options that were given explicitly on the command line."""
+    if not getattr(args, "preset", None):
+        return args
+    argv = sys.argv[1:] if argv is None else argv
+    given = set()
+    for action in ap._actions:
+        if any(tok == opt or tok.startswith(opt + "=") for opt in action.option_strings for tok in argv):
+            given.add(action.dest)
+    for key, value in PRESETS[script][args.preset].items():
+        if not hasattr(args, key):
+            raise KeyError(f"preset {args.preset!r} sets unknown option {key!r}")
+        if key not in given:
+            setattr(args, key, value)
+    return args

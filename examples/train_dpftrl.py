@@ -19,6 +19,8 @@ import sys
 import time
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from _presets import add_preset_argument, apply_preset  # noqa: E402
 
 import torch
 import torch.distributed as dist
@@ -81,7 +83,8 @@ def main() -> None:
     ap.add_argument("--delta", type=float, default=1e-5)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--backend", default=None)
-    a = ap.parse_args()
+    add_preset_argument(ap, "train_dpftrl")
+    a = apply_preset(ap, ap.parse_args(), "train_dpftrl")
 
     if int(os.environ.get("WORLD_SIZE", "1")) > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")

@@ -18,6 +18,8 @@ import sys
 import time
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from _presets import add_preset_argument, apply_preset  # noqa: E402
 
 import torch
 import torch.distributed as dist
@@ -44,7 +46,8 @@ def main() -> None:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--backend", default=None)
     ap.add_argument("--microbatch", type=int, default=None)
-    args = ap.parse_args()
+    add_preset_argument(ap, "train_dpsgd")
+    args = apply_preset(ap, ap.parse_args(), "train_dpsgd")
 
     if int(os.environ.get("WORLD_SIZE", "1")) > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")

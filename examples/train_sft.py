@@ -14,6 +14,8 @@ import os
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from _presets import add_preset_argument, apply_preset  # noqa: E402
 
 import torch
 from torch import nn
@@ -52,7 +54,8 @@ def main() -> None:
     ap.add_argument("--lr", type=float, default=1e-2)
     ap.add_argument("--loss", default="nll", choices=["nll", "dft"])
     ap.add_argument("--delta", type=float, default=1e-5)
-    a = ap.parse_args()
+    add_preset_argument(ap, "train_sft")
+    a = apply_preset(ap, ap.parse_args(), "train_sft")
 
     g = torch.Generator().manual_seed(0)
     rows = []

@@ -57,6 +57,7 @@ def parse() -> argparse.Namespace:
                     help="peer: every microbatch's gradient tiles are reduced straight into the owners' shards; "
                          "local: accumulate in a local fp32 buffer and push once per step")
     ap.add_argument("--cuda-graph", type=int, default=-1, help="1/0: replay microbatches as CUDA graphs (default: per config)")
+    ap.add_argument("--group-lora-qkv", type=int, default=1, help="0: run q / k / v LoRA projections as three separate launches")
     return ap.parse_args()
 
 
@@ -218,6 +219,8 @@ def main() -> None:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
 
     torch.manual_seed(1234)
+    from opaque_b200.engine import fused as _fused
+    _fused.GROUP_LORA_QKV = bool(args.group_lora_qkv)
     mechanism, sampling = None, None
     if args.config == "llama8b-lora":
         seq, per_gpu, mb, frac, vocab = 1024, 64, 16, 0.5, 128256

@@ -483,6 +483,119 @@ class _LoRALinear(Function):
         return dx, None, None, None, None, None
 
 
+GROUP_LORA_QKV = True      # LoRA on q, k and v of one block runs as grouped launches (see _LoRAQKV)
+
+
+def stacked_weight_view(weights) -> torch.Tensor | None:
+    """``[sum(out_i), in]`` view over weights that sit back to back in ONE allocation (see ``fuse_storage``), else None."""
+    w0 = weights[0]
+    if any(w.ndim != 2 or not w.is_contiguous() or w.shape[1] != w0.shape[1] or w.dtype != w0.dtype for w in weights):
+        return None
+    ptr = w0.data_ptr()
+    for w in weights:
+        if w.data_ptr() != ptr or w.untyped_storage().data_ptr() != w0.untyped_storage().data_ptr():
+            return None
+        ptr += w.numel() * w.element_size()
+    return torch.as_strided(w0.detach(), (sum(w.shape[0] for w in weights), w0.shape[1]), (w0.shape[1], 1))
+
+
+@torch.no_grad()
+def fuse_storage(params) -> None:
+    """Move the data of several (frozen) 2-D parameters with equal input width into one allocation, back to back, so that
+    :func:`stacked_weight_view` can hand them to ONE GEMM launch.  Values are unchanged; nothing else refers to the old
+    storage afterwards."""
+    rows = sum(p.shape[0] for p in params)
+    buf = torch.empty(rows, params[0].shape[1], dtype=params[0].dtype, device=params[0].device)
+    lo = 0
+    for p in params:
+        buf[lo:lo + p.shape[0]].copy_(p.data)
+        p.data = buf[lo:lo + p.shape[0]]
+        lo += p.shape[0]
+
+
+class _LoRAQKV(Function):
+    """Query, key and value projections of one attention block with LoRA on all three, as grouped launches:
+
+    forward   one rank-``3r`` side product ``x·[Aq;Ak;Av]ᵀ`` and ONE tcgen05 GEMM ``x·[Wq;Wk;Wv]ᵀ`` whose low-rank second
+              K segment applies the block-diagonal ``[Bq, Bk, Bv]``;
+    backward  one side product ``[dq|dk|dv]·blockdiag(B)``, ONE data-gradient GEMM ``[dq|dk|dv]·[Wq;Wk;Wv] + q·[Aq;Ak;Av]``
+              (no three partial ``dx`` tensors to add up), and the per-example factor gradients to the capture.
+
+    Counterpart of packages/opaque-patches/src/opaque/api/patches/kernels/lora.py:582-718 (three projections sharing X).
+    """
+
+    @staticmethod
+    def forward(ctx, x, w_all, bias_all, scaling, aq, bq, ak, bk, av, bv):
+        x2d = _rows(x)
+        r = aq.shape[0]
+        outs = (bq.shape[0], bk.shape[0], bv.shape[0])
+        a_cat = torch.cat([aq, ak, av], dim=0)                                   # [3r, in]
+        xa = (x2d @ a_cat.t()) * scaling                                         # [R, 3r], kept for the backward pass
+        b_block = torch.zeros(sum(outs), 3 * r, dtype=bq.dtype, device=bq.device)
+        lo = 0
+        for j, (b, n) in enumerate(zip((bq, bk, bv), outs)):
+            b_block[lo:lo + n, j * r:(j + 1) * r] = b
+            lo += n
+        y = ops.gemm_pair(x2d, w_all, a2=xa, b2=b_block, bias=bias_all)
+        ctx.save_for_backward(x2d, xa, w_all, a_cat, b_block, aq, bq, ak, bk, av, bv)
+        ctx.scaling, ctx.xshape, ctx.outs = scaling, x.shape, outs
+        q, k, v = torch.split(y, outs, dim=1)
+        lead = x.shape[:-1]
+        return q.unflatten(0, lead) if len(lead) > 1 else q, k.unflatten(0, lead) if len(lead) > 1 else k, \
+            v.unflatten(0, lead) if len(lead) > 1 else v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        x2d, xa, w_all, a_cat, b_block, aq, bq, ak, bk, av, bv = ctx.saved_tensors
+        s, outs = ctx.scaling, ctx.outs
+        r = aq.shape[0]
+        R = x2d.shape[0]
+        g_all = torch.cat([dq.reshape(R, outs[0]), dk.reshape(R, outs[1]), dv.reshape(R, outs[2])], dim=1)     # [R, sum(out)]
+        q_all = (g_all @ b_block) * s                                            # [R, 3r]: (g_j B_j) s for each projection
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = ops.gemm_pair(g_all, w_all, b_layout="kn", a2=q_all, b2=a_cat, b2_layout="kn").view(ctx.xshape)
+        cap = current_capture()
+        if cap is not None:
+            lo = 0
+            for j, (a, b) in enumerate(((aq, bq), (ak, bk), (av, bv))):
+                g_j = g_all[:, lo:lo + outs[j]]
+                lo += outs[j]
+                cap.add_lora(a, b, x2d, xa[:, j * r:(j + 1) * r], g_j, q_all[:, j * r:(j + 1) * r])
+            return (dx,) + (None,) * 9
+        grads = []
+        lo = 0
+        for j in range(3):
+            g_j = g_all[:, lo:lo + outs[j]]
+            lo += outs[j]
+            grads += [q_all[:, j * r:(j + 1) * r].t() @ x2d, g_j.t() @ xa[:, j * r:(j + 1) * r]]
+        return (dx, None, None, None, *grads)
+
+
+def lora_qkv(x: torch.Tensor, q_proj, k_proj, v_proj):
+    """``(q, k, v)`` of three LoRA-adapted projections sharing ``x`` through the grouped path, or ``None`` when it does not
+    apply (different ranks / scalings, weights not stored back to back, biases on only some of them, CPU …)."""
+    mods = (q_proj, k_proj, v_proj)
+    if not GROUP_LORA_QKV or any(m.lora_A is None for m in mods) or not (x.is_cuda and x.dtype == torch.bfloat16 and ops.functional.kernels_enabled()):
+        return None
+    r = q_proj.lora_A.shape[0]
+    if r % 8 or any(m.lora_A.shape[0] != r or m.scaling != q_proj.scaling or m.weight.requires_grad for m in mods):
+        return None
+    if any(m.lora_A.dtype != torch.bfloat16 or m.lora_B.dtype != torch.bfloat16 for m in mods):
+        return None
+    have_bias = [m.bias is not None for m in mods]
+    if any(have_bias) and not all(have_bias):
+        return None
+    w_all = stacked_weight_view([m.weight for m in mods])
+    if w_all is None or not _own_gemm_ok(x, w_all):
+        return None
+    bias_all = torch.cat([m.bias for m in mods]) if all(have_bias) else None
+    if bias_all is not None and bias_all.requires_grad:
+        return None
+    return _LoRAQKV.apply(x, w_all, bias_all, q_proj.scaling, q_proj.lora_A, q_proj.lora_B, k_proj.lora_A, k_proj.lora_B,
+                          v_proj.lora_A, v_proj.lora_B)
+
+
 def lora_linear(x, weight, bias, lora_a, lora_b, scaling: float):
     """Frozen base linear plus LoRA factors; per-example factor gradients go to the active capture."""
     if x.is_cuda and x.dtype == torch.bfloat16 and ops.functional.kernels_enabled():

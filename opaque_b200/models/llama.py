@@ -119,11 +119,15 @@ class LlamaAttention(nn.Module):
 
     def forward(self, x, cos, sin, pos):
         B, T, _ = x.shape
-        q, k = self.q_proj(x), self.k_proj(x)
+        qkv = fused.lora_qkv(x, self.q_proj, self.k_proj, self.v_proj)      # grouped launches when all three carry LoRA
+        if qkv is not None:
+            q, k, v = qkv
+        else:
+            q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
         if self.qk_full:
             q, k = self.q_norm(q), self.k_norm(k)
         q, k = q.view(B, T, self.nh, self.hd), k.view(B, T, self.nkv, self.hd)
-        v = self.v_proj(x).view(B, T, self.nkv, self.hd)
+        v = v.view(B, T, self.nkv, self.hd)
         if self.q_norm is not None and not self.qk_full and not self.qk_after:
             q, k = self.q_norm(q), self.k_norm(k)
         if self.use_rope:
@@ -286,6 +290,13 @@ class LlamaForCausalLM(nn.Module):
         for name, mod in self.named_modules():
             if isinstance(mod, Linear) and name.split(".")[-1] in targets:
                 mod.add_lora(r, alpha)
+        if {"q_proj", "k_proj", "v_proj"} <= set(targets):
+            # frozen q / k / v weights of a block go back to back into one allocation: the three projections (and their data
+            # gradients) then run as ONE GEMM launch each
+            for layer in self.model.layers:
+                att = layer.self_attn
+                if att.q_proj.weight.device.type == "cuda":
+                    fused.fuse_storage([att.q_proj.weight, att.k_proj.weight, att.v_proj.weight])
 
     # ---- forward ------------------------------------------------------------------------------
     def hidden_states(self, input_ids: torch.Tensor, position_ids: torch.Tensor | None = None) -> torch.Tensor:

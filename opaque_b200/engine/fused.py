@@ -432,6 +432,17 @@ def _lora_gemm_ok(x2d, weight, lora_a, lora_b, bias) -> bool:
             and (bias is None or bias.dtype == torch.bfloat16))
 
 
+def _small_gemm(a: torch.Tensor, b: torch.Tensor, layout: str) -> torch.Tensor:
+    """Rank-r side product of the LoRA path (``x·Aᵀ`` with ``layout="nk"``, ``g·B`` with ``"kn"``) on the single-CTA
+    tcgen05 kernel when the operands qualify, so the adapter path launches no library GEMM either."""
+    n = b.shape[0] if layout == "nk" else b.shape[1]
+    if (OWN_GEMM and a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.stride(1) == 1
+            and a.stride(0) % 8 == 0 and b.is_contiguous() and n % 8 == 0 and a.shape[1] % 8 == 0 and (a.data_ptr() & 15) == 0
+            and (b.data_ptr() & 15) == 0 and ops.functional.kernels_enabled()):
+        return ops.gemm(a, b, b_layout=layout, kernel="single")
+    return a @ (b.t() if layout == "nk" else b)
+
+
 class _LoRALinear(Function):
     """``y = x Wᵀ + s·(x Aᵀ) Bᵀ`` with frozen ``W``; per-example ``dA``, ``dB`` go to the capture."""
 
@@ -439,7 +450,7 @@ class _LoRALinear(Function):
     def forward(ctx, x, weight, bias, lora_a, lora_b, scaling):
         x2d = x.reshape(-1, x.shape[-1])
         x2d = x2d if x2d.is_contiguous() else x2d.contiguous()
-        xa = (x2d @ lora_a.t()) * scaling                 # s · x Aᵀ, kept for the backward pass
+        xa = _small_gemm(x2d, lora_a, "nk") * scaling     # s · x Aᵀ, kept for the backward pass
         if FUSE_LORA_GEMM and _lora_gemm_ok(x2d, weight, lora_a, lora_b, bias):
             # one tcgen05 pass: the low-rank product is a second K segment of the same accumulator tile
             y = ops.gemm(x2d, weight, a2=xa, b2=lora_b, bias=bias)
@@ -457,7 +468,7 @@ class _LoRALinear(Function):
         s = ctx.scaling
         g2d = gy.reshape(-1, gy.shape[-1])
         g2d = g2d if g2d.is_contiguous() else g2d.contiguous()
-        q = (g2d @ lora_b) * s                                     # [R, r]
+        q = _small_gemm(g2d, lora_b, "kn") * s                     # [R, r]
         dx = None
         if ctx.needs_input_grad[0]:
             if FUSE_LORA_GEMM and _lora_gemm_ok(g2d, weight, lora_a, lora_b, None):
@@ -530,7 +541,7 @@ class _LoRAQKV(Function):
         r = aq.shape[0]
         outs = (bq.shape[0], bk.shape[0], bv.shape[0])
         a_cat = torch.cat([aq, ak, av], dim=0)                                   # [3r, in]
-        xa = (x2d @ a_cat.t()) * scaling                                         # [R, 3r], kept for the backward pass
+        xa = _small_gemm(x2d, a_cat, "nk") * scaling                             # [R, 3r], kept for the backward pass
         b_block = torch.zeros(sum(outs), 3 * r, dtype=bq.dtype, device=bq.device)
         lo = 0
         for j, (b, n) in enumerate(zip((bq, bk, bv), outs)):
@@ -551,7 +562,7 @@ class _LoRAQKV(Function):
         r = aq.shape[0]
         R = x2d.shape[0]
         g_all = torch.cat([dq.reshape(R, outs[0]), dk.reshape(R, outs[1]), dv.reshape(R, outs[2])], dim=1)     # [R, sum(out)]
-        q_all = (g_all @ b_block) * s                                            # [R, 3r]: (g_j B_j) s for each projection
+        q_all = _small_gemm(g_all, b_block, "kn") * s                            # [R, 3r]: (g_j B_j) s for each projection
         dx = None
         if ctx.needs_input_grad[0]:
             dx = ops.gemm_pair(g_all, w_all, b_layout="kn", a2=q_all, b2=a_cat, b2_layout="kn").view(ctx.xshape)

@@ -201,57 +201,6 @@ __device__ __forceinline__ void gp_store32(__nv_bfloat16* dst, const float* v, b
   }
 }
 
-// Warp-cooperative store of a [32 rows x COLS columns] tile (lane = row on entry, COLS = 32 or 64 fp32 values per lane)
-// as bf16.  The rows go through a private shared-memory slab with a 16-byte XOR swizzle and leave as whole row segments
-// (COLS * 2 bytes contiguous per row, several rows per instruction), so memory sees full 32-byte sectors instead of one
-// 16-byte piece per lane and instruction.  `out` points at (first row of the warp, first column); rows >= rows_valid and
-// columns >= cols_valid are not written.
-template <int COLS>
-__device__ __forceinline__ void gp_store_tile(uint8_t* slab, const float* v, __nv_bfloat16* out, long long ldo,
-                                              int rows_valid, int cols_valid, bool vec_ok, int lane) {
-  if (!vec_ok) {                       // unaligned destination: every lane writes its own row
-    if (lane < rows_valid) {
-      __nv_bfloat16* dst = out + static_cast<long long>(lane) * ldo;
-      for (int j = 0; j < COLS; ++j)
-        if (j < cols_valid) dst[j] = __float2bfloat16_rn(v[j]);
-    }
-    return;
-  }
-  constexpr int CHUNKS = COLS / 8;             // 16-byte chunks per row
-  constexpr int ROW_BYTES = COLS * 2;
-#pragma unroll
-  for (int c = 0; c < CHUNKS; ++c) {
-    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * c], v[8 * c + 1]);
-    __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * c + 2], v[8 * c + 3]);
-    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * c + 4], v[8 * c + 5]);
-    __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * c + 6], v[8 * c + 7]);
-    uint4 pk;
-    pk.x = *reinterpret_cast<uint32_t*>(&h0);
-    pk.y = *reinterpret_cast<uint32_t*>(&h1);
-    pk.z = *reinterpret_cast<uint32_t*>(&h2);
-    pk.w = *reinterpret_cast<uint32_t*>(&h3);
-    *reinterpret_cast<uint4*>(slab + lane * ROW_BYTES + ((c ^ (lane & (CHUNKS - 1))) << 4)) = pk;
-  }
-  __syncwarp();
-  constexpr int ROWS_PER_INSTR = 32 / CHUNKS;
-  const int c = lane % CHUNKS;
-#pragma unroll
-  for (int i = 0; i < 32 / ROWS_PER_INSTR; ++i) {
-    const int r = i * ROWS_PER_INSTR + lane / CHUNKS;
-    const uint4 pk = *reinterpret_cast<const uint4*>(slab + r * ROW_BYTES + ((c ^ (r & (CHUNKS - 1))) << 4));
-    if (r < rows_valid) {
-      __nv_bfloat16* dst = out + static_cast<long long>(r) * ldo + 8 * c;
-      if (8 * c + 8 <= cols_valid) {
-        *reinterpret_cast<uint4*>(dst) = pk;
-      } else if (8 * c < cols_valid) {
-        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&pk);
-        for (int j = 0; j < cols_valid - 8 * c; ++j) dst[j] = e[j];
-      }
-    }
-  }
-  __syncwarp();
-}
-
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -472,7 +421,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               for (int j = 0; j < 64; ++j)
                 if (nc + j < p.N) v[j] += __bfloat162float(__ldg(p.bias + nc + j));
             }
-            gp_store_tile<64>(slab, v, p.out + static_cast<long long>(row - lane) * p.ldo + nc, p.ldo, p.M - (row - lane),
+            store_tile_bf16<64>(slab, v, p.out + static_cast<long long>(row - lane) * p.ldo + nc, p.ldo, p.M - (row - lane),
                               p.N - nc, vec_ok, lane);
           }
         } else if constexpr (EPI == GP_EPI_CE) {
@@ -515,7 +464,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (p.out != nullptr) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = nc + j < p.N ? v[j] : 0.f;
-              gp_store_tile<32>(slab, v, p.out + static_cast<long long>(row - lane) * p.ldo + nc, p.ldo, p.M - (row - lane),
+              store_tile_bf16<32>(slab, v, p.out + static_cast<long long>(row - lane) * p.ldo + nc, p.ldo, p.M - (row - lane),
                                 p.N - nc, vec_ok, lane);
             }
           }
@@ -535,8 +484,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const long long r0o = static_cast<long long>(row - lane) * p.ldo + nc;
             const int rows_valid = p.M - (row - lane);
             if (p.out_gate != nullptr) {
-              gp_store_tile<32>(slab, gt, p.out_gate + r0o, p.ldo, rows_valid, nh - nc, vec_ok, lane);
-              gp_store_tile<32>(slab + GP_SLAB_BYTES / 2, up, p.out_up + r0o, p.ldo, rows_valid, nh - nc, vec_ok, lane);
+              store_tile_bf16<32>(slab, gt, p.out_gate + r0o, p.ldo, rows_valid, nh - nc, vec_ok, lane);
+              store_tile_bf16<32>(slab + GP_SLAB_BYTES / 2, up, p.out_up + r0o, p.ldo, rows_valid, nh - nc, vec_ok, lane);
               // the backward pass reads the ROUNDED pre-activations, so the activation is formed from them too
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
@@ -546,7 +495,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
 #pragma unroll
             for (int j = 0; j < 32; ++j) gt[j] = gp_act(gt[j], p.act) * up[j];
-            gp_store_tile<32>(slab, gt, p.out + r0o, p.ldo, rows_valid, nh - nc, vec_ok, lane);
+            store_tile_bf16<32>(slab, gt, p.out + r0o, p.ldo, rows_valid, nh - nc, vec_ok, lane);
           }
         }
         tc_fence_before();

@@ -12,7 +12,9 @@
 //
 // Tile 128 x 256, K block 64, 4-stage TMA ring (128-byte swizzle), accumulators double-buffered in TMEM (2 x 256
 // columns) so the epilogue of tile i overlaps the MMAs of tile i+1.  Warp 0 issues TMA, warp 1 issues tcgen05.mma and
-// owns TMEM, warps 2-5 convert fp32 accumulators to bf16 and store 16-byte vectors.  Every wait is bounded.
+// owns TMEM, warps 2-9 convert fp32 accumulators to bf16 and store them as whole 128-byte row segments (staged through
+// a swizzled shared-memory slab per warp): with a short K (768) the drain of one tile takes about as long as its MMAs,
+// so four warps storing one 16-byte piece per lane and row left the tensor pipe waiting.  Every wait is bounded.
 #include "common.cuh"
 #include "api.h"
 
@@ -28,10 +30,11 @@ constexpr int GT_STAGES = 4;
 constexpr int GT_A_BYTES = GT_BM * GT_BK * 2;
 constexpr int GT_B_BYTES = GT_BN * GT_BK * 2;
 constexpr int GT_STAGE_BYTES = GT_A_BYTES + GT_B_BYTES;
-constexpr int GT_THREADS = 192;
+constexpr int GT_THREADS = 320;      // TMA producer warp, MMA warp, 8 epilogue warps
+constexpr int GT_SLAB_BYTES = 4096;   // per epilogue warp: 32 rows x 64 columns of bf16 on their way to memory
 constexpr int GT_MAX_GROUPS = 256;
 constexpr int GT_GROUP_M = 16;       // m-tiles per raster band (L2 reuse of the B tiles inside a band)
-constexpr int GT_SMEM = GT_STAGES * GT_STAGE_BYTES + 256 + (GT_MAX_GROUPS + 2) * 4 + 1024;
+constexpr int GT_SMEM = GT_STAGES * GT_STAGE_BYTES + 8 * GT_SLAB_BYTES + 256 + (GT_MAX_GROUPS + 2) * 4 + 1024;
 
 struct GemmParams {
   int M, N, K1, K2;
@@ -81,14 +84,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GT_STAGES * GT_STAGE_BYTES);
+  uint8_t* slabs = smem + GT_STAGES * GT_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(slabs + 8 * GT_SLAB_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + GT_STAGES;
   uint64_t* tmem_full = bars + 2 * GT_STAGES;
   uint64_t* tmem_empty = bars + 2 * GT_STAGES + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * GT_STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* tile_start = reinterpret_cast<int*>(smem + GT_STAGES * GT_STAGE_BYTES + 256);
+  int* tile_start = reinterpret_cast<int*>(slabs + 8 * GT_SLAB_BYTES + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = (p.N + GT_BN - 1) / GT_BN;
@@ -104,7 +108,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4);
+      mbar_init(&tmem_empty[a], 8);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -219,7 +223,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   } else {
+    // Eight warps drain one 128 x 256 accumulator: warp w reads TMEM lanes 32 * (w % 4) .. (the lane quarter a warp may
+    // touch) and one 128-column half, 64 columns per round (two loads in flight, one wait), and hands the rows to memory
+    // through its shared-memory slab as whole 128-byte row segments.
     const int q = warp & 3;
+    const int g = (warp - 2) >> 2;
+    uint8_t* slab = slabs + (warp - 2) * GT_SLAB_BYTES;
     int acc_iter = 0, cursor = 0;
     bool ok = true;
     const bool vec_ok = ((p.ldo & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
@@ -231,40 +240,23 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         break;
       }
       tc_fence_after();
-      const int row = it.row0 + q * 32 + lane;
-      __nv_bfloat16* orow = p.out + static_cast<long long>(row) * p.ldo;
+      const int row0 = it.row0 + q * 32;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * GT_BN + g * (GT_BN / 2);
 #pragma unroll 1
-      for (int c = 0; c < GT_BN / 32; ++c) {
-        const int nc = it.n0 + c * 32;
+      for (int c = 0; c < GT_BN / 2 / 64; ++c) {
+        const int nc = it.n0 + g * (GT_BN / 2) + c * 64;
         if (nc >= p.N) break;
-        float v[32];
-        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * GT_BN + c * 32, v);
+        float v[64];
+        tmem_ld32(t_row + c * 64, v);
+        tmem_ld32(t_row + c * 64 + 32, v + 32);
         tmem_ld_wait();
         if (p.bias != nullptr) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
+          for (int j = 0; j < 64; ++j)
             if (nc + j < p.N) v[j] += __bfloat162float(__ldg(p.bias + nc + j));
         }
-        if (row < it.row_end) {
-          if (vec_ok && nc + 32 <= p.N) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-              __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-              __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-              __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-              uint4 pk;
-              pk.x = *reinterpret_cast<uint32_t*>(&h0);
-              pk.y = *reinterpret_cast<uint32_t*>(&h1);
-              pk.z = *reinterpret_cast<uint32_t*>(&h2);
-              pk.w = *reinterpret_cast<uint32_t*>(&h3);
-              *reinterpret_cast<uint4*>(orow + nc + j) = pk;
-            }
-          } else {
-            for (int j = 0; j < 32; ++j)
-              if (nc + j < p.N) orow[nc + j] = __float2bfloat16_rn(v[j]);
-          }
-        }
+        store_tile_bf16<64>(slab, v, p.out + static_cast<long long>(row0) * p.ldo + nc, p.ldo, it.row_end - row0,
+                            p.N - nc, vec_ok, lane);
       }
       tc_fence_before();
       __syncwarp();

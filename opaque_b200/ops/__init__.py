@@ -225,11 +225,13 @@ def _check_b(b: torch.Tensor, layout: str, K: int, what: str) -> int:
 def gemm_pair(a: torch.Tensor, b: torch.Tensor, *, b_layout: str = "nk", a2: torch.Tensor | None = None,
               b2: torch.Tensor | None = None, b2_layout: str = "nk", bias: torch.Tensor | None = None,
               out: torch.Tensor | None = None, status: StatusWord | None = None,
-              wait_budget_s: float = DEFAULT_WAIT_BUDGET_S) -> torch.Tensor:
-    """``a @ op(b) + a2 @ op(b2) + bias`` with two CTAs per 256 x 256 accumulator tile (bf16 in/out, fp32 accumulation).
+              wait_budget_s: float = DEFAULT_WAIT_BUDGET_S, tile: str = "512x256") -> torch.Tensor:
+    """``a @ op(b) + a2 @ op(b2) + bias`` on CTA pairs (``tcgen05 … cta_group::2``; bf16 in/out, fp32 accumulation).
 
     Layouts as in :func:`gemm`; the second segment has its own layout, so ``dX = dG·Wg + dU·Wu`` (both weights
     stored ``[K, N]`` from the product's point of view) and the LoRA data gradient ``dY·W + q·A`` are one launch each.
+    ``tile``: ``"512x256"`` (one tile fills tensor memory; fewest operand bytes per FLOP, for long K) or ``"256x256"``
+    (two accumulators alternate, so a tile drains during the whole main loop of the next; for short K).
     """
     _need_bf16(a, b)
     if a.ndim != 2 or a.stride(1) != 1:
@@ -252,6 +254,16 @@ def gemm_pair(a: torch.Tensor, b: torch.Tensor, *, b_layout: str = "nk", a2: tor
         out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
     elif out.shape != (M, N) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
         raise ValueError("out must be a row-major bf16 [M, N] matrix")
+    if tile == "256x256":
+        rc = lib.load().ob_gemm_pair_db(
+            a.data_ptr(), b.data_ptr(), lib.ptr(a2), lib.ptr(b2), lib.ptr(bias), out.data_ptr(),
+            M, N, K, K2, a.stride(0), b.stride(0), a2.stride(0) if a2 is not None else 0,
+            b2.stride(0) if b2 is not None else 0, out.stride(0), int(b_layout == "kn"), int(b2_layout == "kn"),
+            status.ptr() if status else None, wait_budget_s, lib.sm_count(), lib.stream())
+        lib.check(rc, "gemm_pair (256x256)")
+        return out
+    if tile != "512x256":
+        raise ValueError("tile must be '512x256' or '256x256'")
     rc = lib.load().ob_gemm_pair(
         a.data_ptr(), b.data_ptr(), None, lib.ptr(a2), lib.ptr(b2), None, lib.ptr(bias), out.data_ptr(), None, None,
         M, N, K, K2, a.stride(0), b.stride(0), a2.stride(0) if a2 is not None else 0,
@@ -259,6 +271,19 @@ def gemm_pair(a: torch.Tensor, b: torch.Tensor, *, b_layout: str = "nk", a2: tor
         status.ptr() if status else None, wait_budget_s, lib.sm_count(), lib.stream())
     lib.check(rc, "gemm_pair")
     return out
+
+
+def die_map() -> list[int] | None:
+    """Die (0 / 1) of every SM of the current device by ``%smid``, or ``None`` when no two-die split was measured.
+
+    Probed once per device and process by timing atomics from every SM (a line's home L2 slice answers faster to SMs of
+    its own die); the CTA-pair GEMMs use it to keep tiles that share operands on one die.  Synchronises the device on
+    the first call, so call it outside CUDA-graph captures (the GEMM entry points skip the probe while capturing).
+    """
+    import ctypes
+    buf = (ctypes.c_ubyte * 256)()
+    n = lib.load().ob_die_map(buf, 256)
+    return [int(buf[i]) for i in range(n)] if n > 0 else None
 
 
 _GLU_ACT = {"silu": 0, "gelu": 1, "gelu_pytorch_tanh": 2, "gelu_tanh": 2}

@@ -39,6 +39,15 @@ int ob_gemm_pair(const void* a, const void* b, const void* b_up, const void* a2,
                  const void* bias, void* out, void* out_gate, void* out_up, long long rows_a, int N, int K1, int K2,
                  long long lda, long long ldb, long long lda2, long long ldb2, long long ldo, int b_kn, int b2_kn, int glu,
                  int glu_act, int* status, double wait_budget_s, int num_sms, void* stream);
+// Same product (store epilogue only) on 256 x 256 pair tiles with double-buffered accumulators: the variant for short K.
+int ob_gemm_pair_db(const void* a, const void* b, const void* a2, const void* b2, const void* bias, void* out,
+                    long long rows_a, int N, int K1, int K2, long long lda, long long ldb, long long lda2, long long ldb2,
+                    long long ldo, int b_kn, int b2_kn, int* status, double wait_budget_s, int num_sms, void* stream);
+// Die map of the current device (which SMs share a die, probed by atomic latency; once per device and process).
+// ob_pair_init: probes if needed, returns 1000 * (SM pairs on die 0) + (SM pairs on die 1), 0 if no two-die split was
+// found; call it outside stream captures.  ob_die_map: smid -> 0 / 1 into out[0 .. n), returns the SM count or 0.
+int ob_pair_init(void);
+int ob_die_map(unsigned char* out, int n);
 // Output head fused with cross-entropy statistics on CTA pairs: logits tiles stay in tensor memory, per-tile partials
 // (scratch: rows * 2 * ceil(N / 256) float4) are combined in a fixed order into nll[rows], lse[rows]; `logits_out` (optional)
 // receives the bf16 soft-capped logits for the backward pass.

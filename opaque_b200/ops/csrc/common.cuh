@@ -25,6 +25,7 @@ enum : int {
   OB_ERR_WAIT_SCALED = 5,
   OB_ERR_WAIT_PEER = 6,      // a peer's flag did not arrive in time
   OB_ERR_DRAIN = 7,
+  OB_ERR_CLAIM = 8,          // a tile-claim word was shared by two launches in flight
 };
 
 __device__ __forceinline__ void set_error(int* status, int code) {
@@ -162,6 +163,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// 32 lanes x 16 consecutive fp32 columns (half the registers of tmem_ld32 in flight).
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }
@@ -304,6 +316,103 @@ __device__ __forceinline__ void store_tile_bf16(uint8_t* slab, const float* v, _
         *reinterpret_cast<uint4*>(dst) = pk;
       } else if (8 * c < cols_valid) {
         const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&pk);
+        for (int j = 0; j < cols_valid - 8 * c; ++j) dst[j] = e[j];
+      }
+    }
+  }
+  __syncwarp();
+}
+
+// v[0 .. 63] += bias[nc .. nc + 63] (bf16 values, the same for every row): one 16-byte load per 8 columns when the
+// slice is aligned and inside N (64 scalar loads per thread made the epilogue LSU-bound: 12 % of a 512 x 256 tile).
+__device__ __forceinline__ void add_bias64(float* v, const __nv_bfloat16* bias, int nc, int N) {
+  if (nc + 64 <= N && (reinterpret_cast<uintptr_t>(bias + nc) & 15) == 0) {
+    const uint4* bp = reinterpret_cast<const uint4*>(bias + nc);
+#pragma unroll
+    for (int j8 = 0; j8 < 8; ++j8) {
+      const uint4 pk = __ldg(bp + j8);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 f = __bfloat1622float2(h[t]);
+        v[8 * j8 + 2 * t] += f.x;
+        v[8 * j8 + 2 * t + 1] += f.y;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 64; ++j)
+      if (nc + j < N) v[j] += __bfloat162float(__ldg(bias + nc + j));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Epilogue stores through the TMA engine.  A warp writes its [32 rows x 64 columns] bf16 tile into a 4 KB shared-memory
+// slab in the 128-byte-swizzled layout the tensor map expects (16-byte chunk j of row r at chunk position j ^ (r & 7);
+// the slab is 1024-byte aligned), and one lane issues a bulk tensor store.  Rows and columns outside the tensor are
+// clipped by the hardware.  Against 16-byte st.global per lane this halves the bytes the SM pushes into the crossbar
+// (measured: 266 MB vs 134 MB for a 134 MB output) and takes the stores off the warp's critical path; a drain of a
+// 128 x 256 accumulator half by eight warps took 4.4 k clocks with st.global.
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the issuing thread's earlier bulk stores have finished READING shared memory (the slab may be rewritten)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... have finished altogether (before the kernel gives its shared memory back)
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// pk[0 .. 31]: this lane's row of 64 bf16 values, two per register.  `use_tma` is warp-uniform.  Without it (unaligned
+// output, or rows that must be masked at a bound the tensor map does not know) the tile leaves through the slab as
+// 16-byte st.global row segments, or element by element when even that is not aligned.
+__device__ __forceinline__ void store_tile64_packed(uint8_t* slab, const uint32_t* pk, const CUtensorMap* map, bool use_tma,
+                                                    int col0, int row0, __nv_bfloat16* out, long long ldo, int rows_valid,
+                                                    int cols_valid, bool vec_ok, int lane) {
+  if (lane == 0) tma_store_wait_read();
+  __syncwarp();
+  if (!use_tma && !vec_ok) {
+    if (lane < rows_valid) {
+      __nv_bfloat16* dst = out + static_cast<long long>(row0 + lane) * ldo + col0;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&pk[j]);
+        if (2 * j < cols_valid) dst[2 * j] = h.x;
+        if (2 * j + 1 < cols_valid) dst[2 * j + 1] = h.y;
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+    *reinterpret_cast<uint4*>(slab + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+        make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+  if (use_tma) {
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(map, slab, col0, row0);
+      tma_store_commit();
+    }
+    return;
+  }
+  __syncwarp();
+  const int c = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3);
+    const uint4 q = *reinterpret_cast<const uint4*>(slab + r * 128 + ((c ^ (r & 7)) << 4));
+    if (r < rows_valid) {
+      __nv_bfloat16* dst = out + static_cast<long long>(row0 + r) * ldo + col0 + 8 * c;
+      if (8 * c + 8 <= cols_valid) {
+        *reinterpret_cast<uint4*>(dst) = q;
+      } else if (8 * c < cols_valid) {
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&q);
         for (int j = 0; j < cols_valid - 8 * c; ++j) dst[j] = e[j];
       }
     }

@@ -28,6 +28,9 @@
 // and the gate/up/SwiGLU sequence of kernels/swiglu.py:29-58.
 #include "common.cuh"
 #include "api.h"
+#include "die_map.cuh"
+
+#include <atomic>
 #include <cstdlib>
 
 namespace ob {
@@ -76,6 +79,11 @@ struct PairParams {
   float softcap;                     // > 0: z = softcap * tanh(z / softcap)
   int* status;
   unsigned long long wait_budget_ns;
+  int tma_store;                     // STORE: the output leaves through bulk tensor stores (map_out is valid)
+  // Die-aware tile assignment (see gp_schedule); claim == nullptr: cluster c simply takes tiles c, c + clusters, ...
+  unsigned long long* claim;         // this launch's claim word (zero on entry, zero again after the last claim)
+  int n_front;                       // clusters expected on die 0: slots [0, n_front) walk tiles [0, split)
+  int split;                         //   and slots [n_front, clusters) walk tiles [split, total)
 };
 
 // ---------------------------------------------------------------------------------------------- cluster helpers
@@ -132,6 +140,63 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mas
                : "memory");
 }
 
+// Tile assignment of one cluster: tiles first, first + stride, ... < end (in raster order).
+//
+// A B200 is two dies, each with its own half of the L2; a tile operand that an SM finds only in the other die's half
+// costs a trip over the die-to-die link (2.4x the latency, measured).  Tiles that are adjacent in raster order share
+// their A rows or B columns, so the clusters of one die should work on one contiguous range of the raster and the
+// clusters of the other die on the rest: each die then pulls the remote-homed half of ITS operands once, instead of
+// both dies pulling everything.  Which die a cluster sits on is only known once it runs (%smid and the probed map of
+// die_map.cuh), so the assignment is claimed at start-up: clusters on die 0 take slots from the front of [0, clusters),
+// clusters on die 1 from the back, with ONE 64-bit atomic each (low word: front claims so far, high word: back claims).
+// Exactly `clusters` claims are made per launch, so every slot is taken exactly once whatever the placement; a cluster
+// that finds the slots of its own die exhausted simply gets one of the other range.  The last claimer zeroes the word.
+struct GpSchedule {
+  int first, end, stride;
+};
+
+__device__ __forceinline__ GpSchedule gp_claim_schedule(const PairParams& p, int total_work, int cluster_id,
+                                                        int num_clusters) {
+  GpSchedule s;
+  s.first = cluster_id;
+  s.end = total_work;
+  s.stride = num_clusters;
+  if (p.claim == nullptr) return s;
+  unsigned smid;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+  const int die = g_sm_die[smid & (DM_MAX_SMS - 1)];
+  const unsigned long long old = atomicAdd(p.claim, die ? (1ull << 32) : 1ull);
+  const int lo = static_cast<int>(old & 0xffffffffull), hi = static_cast<int>(old >> 32);
+  if (lo + hi == num_clusters - 1) atomicExch(p.claim, 0ull);
+  const int slot = die ? num_clusters - 1 - hi : lo;
+  if (lo + hi >= num_clusters || slot < 0 || slot >= num_clusters) {
+    // more claims than clusters: the word was shared with another launch in flight; refuse to compute anything
+    set_error(p.status, OB_ERR_CLAIM);
+    s.first = s.end = 0;
+    return s;
+  }
+  if (slot < p.n_front) {
+    s.first = slot;
+    s.stride = p.n_front;
+    s.end = p.split;
+  } else {
+    s.first = p.split + (slot - p.n_front);
+    s.stride = num_clusters - p.n_front;
+    s.end = total_work;
+  }
+  return s;
+}
+
+// Every role of both CTAs reads the schedule from the LEADER's shared memory (written before the start-up cluster barrier).
+__device__ __forceinline__ GpSchedule gp_read_schedule(const int* sched_local) {
+  const uint32_t a = map_to_cta(smem_u32(sched_local), 0);
+  GpSchedule s;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(s.first) : "r"(a) : "memory");
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(s.end) : "r"(a + 4) : "memory");
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(s.stride) : "r"(a + 8) : "memory");
+  return s;
+}
+
 // Wait used by roles that are far from the critical path (epilogue warps waiting a whole main loop for their tile): the
 // polling thread sleeps between tries, which leaves issue slots and power to the tensor pipe.
 __device__ __forceinline__ bool mbar_wait_idle(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
@@ -173,31 +238,25 @@ __device__ __forceinline__ GpItem gp_decode(int w, int tiles_m, int tiles_n, int
   return it;
 }
 
-__device__ __forceinline__ float gp_act(float g, int act) {
-  if (act == 0) return g / (1.0f + __expf(-g));
-  if (act == 1) return 0.5f * g * (1.0f + erff(g * 0.70710678118654752f));
+// The activation is a compile-time choice inside the loops that use it: with a run-time selector per element the
+// compiler evaluated all three (erf and tanh expansions included) for every value and selected afterwards, which made
+// the GLU drain six times longer than its stores.
+template <int ACT>
+__device__ __forceinline__ float gp_act(float g) {
+  if constexpr (ACT == 0) return g / (1.0f + __expf(-g));
+  if constexpr (ACT == 1) return 0.5f * g * (1.0f + erff(g * 0.70710678118654752f));
   const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
   return 0.5f * g * (1.0f + t);
 }
 
-__device__ __forceinline__ void gp_store32(__nv_bfloat16* dst, const float* v, bool vec_ok, int n_left) {
-  if (vec_ok && n_left >= 32) {
+// pkg[j] <- bf16x2(act(g) * u) from packed bf16 pairs of g and u (32 registers = 64 values per lane)
+template <int ACT>
+__device__ __forceinline__ void gp_glu_inplace(uint32_t* pkg, const uint32_t* pku) {
 #pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-      __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-      __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-      __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-      uint4 pk;
-      pk.x = *reinterpret_cast<uint32_t*>(&h0);
-      pk.y = *reinterpret_cast<uint32_t*>(&h1);
-      pk.z = *reinterpret_cast<uint32_t*>(&h2);
-      pk.w = *reinterpret_cast<uint32_t*>(&h3);
-      *reinterpret_cast<uint4*>(dst + j) = pk;
-    }
-  } else {
-    for (int j = 0; j < 32; ++j)
-      if (j < n_left) dst[j] = __float2bfloat16_rn(v[j]);
+  for (int j = 0; j < 32; ++j) {
+    const float2 fg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pkg[j]));
+    const float2 fu = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pku[j]));
+    pkg[j] = pack_bf16x2(gp_act<ACT>(fg.x) * fu.x, gp_act<ACT>(fg.y) * fu.y);
   }
 }
 
@@ -206,7 +265,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_b_up, const __grid_constant__ CUtensorMap map_a2,
                  const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_b2_up,
-                 const PairParams p) {
+                 const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_out_gate,
+                 const __grid_constant__ CUtensorMap map_out_up, const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
   // the dynamic shared-memory window starts at the same offset in both CTAs, so the rounded offsets agree too
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -218,6 +278,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   uint64_t* tmem_empty = bars + 2 * GP_STAGES + 2;     // [2], used in the leader CTA only
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * GP_STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* sched = reinterpret_cast<int*>(tmem_slot + 2);  // [3]: first, end, stride (valid in the leader CTA)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -253,11 +314,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     tmem_alloc_pair(tmem_slot, 512);
     tmem_relinquish_pair();
   }
+  if (leader && threadIdx.x == 64) {  // a thread with nothing else to do during start-up claims the cluster's tiles
+    const GpSchedule sc = gp_claim_schedule(p, total_work, cluster_id, num_clusters);
+    sched[0] = sc.first;
+    sched[1] = sc.end;
+    sched[2] = sc.stride;
+  }
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();                // both CTAs' barriers are initialised before any remote arrival or copy
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const GpSchedule sc = gp_read_schedule(sched);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -267,7 +335,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool ok = true;
       const CUtensorMap* mb1 = (EPI == GP_EPI_GLU && rank == 1) ? &map_b_up : &map_b;
       const CUtensorMap* mb2 = (EPI == GP_EPI_GLU && rank == 1) ? &map_b2_up : &map_b2;
-      for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
+      for (int w = sc.first; ok && w < sc.end; w += sc.stride) {
         const GpItem it = gp_decode(w, tiles_m, tiles_n, rank, p.group_m);
         // first column of N (= row of a [N, K] operand) of this CTA's half of the B tile
         const int bn0 = EPI == GP_EPI_GLU ? it.nt * GP_BNH : it.nt * GP_BN + static_cast<int>(rank) * GP_BNH;
@@ -341,7 +409,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         issue_half(1, kb, st);
 #endif
       };
-      for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
+      for (int w = sc.first; ok && w < sc.end; w += sc.stride) {
         const uint32_t acc_parity = static_cast<uint32_t>(acc_iter & 1);
         const int lead = num_kb < GP_STAGES ? num_kb : GP_STAGES;
         // head of the tile: half 0 of the first `lead` k-blocks, then half 1 of the same stages
@@ -369,13 +437,30 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           umma_commit_pair(&empty[stage], 3);          // frees the stage in both CTAs
           if (++stage == GP_STAGES) { stage = 0; phase ^= 1; }
         }
-        for (int kb = lead; ok && kb < num_kb; ++kb) {
+        // tail of the tile, the mirror image: half 0 finishes its last `tail` k-blocks first and is handed to the epilogue
+        // while half 1 still has `tail` k-blocks of work on the same (still resident) stages, so the tensor pipe is busy
+        // during the drain of half 0, and the drain of half 1 overlaps the head of the next tile.
+        const int tail = num_kb - lead < GP_STAGES ? num_kb - lead : GP_STAGES;
+        for (int kb = lead; ok && kb < num_kb - tail; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag, p.status, OB_ERR_WAIT_FULL, budget)) {
             ok = false;
             break;
           }
           tc_fence_after();
           issue_both(kb, stage);
+          umma_commit_pair(&empty[stage], 3);
+          if (++stage == GP_STAGES) { stage = 0; phase ^= 1; }
+        }
+        for (int i = 0; ok && i < tail; ++i) {
+          int st = stage + i;
+          uint32_t ph = phase;
+          if (st >= GP_STAGES) { st -= GP_STAGES; ph ^= 1; }
+          if (!mbar_wait(&full[st], ph, abort_flag, p.status, OB_ERR_WAIT_FULL, budget)) { ok = false; break; }
+          tc_fence_after();
+          issue_half(0, num_kb - tail + i, st);
+        }
+        for (int i = 0; ok && i < tail; ++i) {
+          issue_half(1, num_kb - tail + i, stage);
           umma_commit_pair(&empty[stage], 3);
           if (++stage == GP_STAGES) { stage = 0; phase ^= 1; }
         }
@@ -395,8 +480,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const bool vec_ok = ((p.ldo & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                         (EPI != GP_EPI_GLU || p.out_gate == nullptr ||
                          (((reinterpret_cast<uintptr_t>(p.out_gate) | reinterpret_cast<uintptr_t>(p.out_up)) & 15) == 0));
-    for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
+    for (int w = sc.first; ok && w < sc.end; w += sc.stride) {
       const GpItem it = gp_decode(w, tiles_m, tiles_n, rank, p.group_m);
+      auto release_half = [&](int hh) {          // this warp is done READING accumulator half hh
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (leader) mbar_arrive(&tmem_empty[hh]);
+          else mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[hh]), 0));
+        }
+      };
 #pragma unroll 1
       for (int h = 0; h < 2; ++h) {
         if (!mbar_wait_idle(&tmem_full[h], acc_iter & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL, budget)) {
@@ -407,22 +500,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int row = it.row0 + h * GP_MMA_M + q * 32 + lane;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + h * GP_BN;
         if constexpr (EPI == GP_EPI_STORE) {
+          // Both 64-column rounds of this warp's share go to registers (packed bf16) first, so the accumulator half is
+          // back with the tensor pipe before a single store is issued; the stores then overlap the next MMAs.
           const int n0 = it.nt * GP_BN + g * (GP_BN / 2);
-#pragma unroll 1
-          for (int c = 0; c < GP_BN / 2 / 64; ++c) {          // 64 columns per round: two loads in flight, one wait
-            const int nc = n0 + c * 64;
-            if (nc >= p.N) break;
-            float v[64];
-            tmem_ld32(t_row + g * (GP_BN / 2) + c * 64, v);
-            tmem_ld32(t_row + g * (GP_BN / 2) + c * 64 + 32, v + 32);
-            tmem_ld_wait();
-            if (p.bias != nullptr) {
+          const int row0w = row - lane;
+          uint32_t pk[2][32];
 #pragma unroll
-              for (int j = 0; j < 64; ++j)
-                if (nc + j < p.N) v[j] += __bfloat162float(__ldg(p.bias + nc + j));
+          for (int c = 0; c < 2; ++c) {
+            const int nc = n0 + c * 64;
+            if (nc < p.N) {
+              float v[64];
+              tmem_ld32(t_row + g * (GP_BN / 2) + c * 64, v);
+              tmem_ld32(t_row + g * (GP_BN / 2) + c * 64 + 32, v + 32);
+              tmem_ld_wait();
+              if (p.bias != nullptr) add_bias64(v, p.bias, nc, p.N);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) pk[c][j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
             }
-            store_tile_bf16<64>(slab, v, p.out + static_cast<long long>(row - lane) * p.ldo + nc, p.ldo, p.M - (row - lane),
-                              p.N - nc, vec_ok, lane);
+          }
+          release_half(h);
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int nc = n0 + c * 64;
+            if (nc < p.N)
+              store_tile64_packed(slab, pk[c], &map_out, p.tma_store != 0, nc, row0w, p.out, p.ldo, p.M - row0w, p.N - nc,
+                                  vec_ok, lane);
           }
         } else if constexpr (EPI == GP_EPI_CE) {
           // Output head: the logits tile never leaves the SM unless `out` asks for it.  Each thread owns one row and folds
@@ -471,42 +573,47 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (row < p.M)
             p.ce_partials[static_cast<long long>(row) * (2 * tiles_n) + 2 * it.nt + g] = make_float4(m, ssum, zlab, ztot);
         } else {
+          // GLU: this warp's 64 columns of h come from 64 gate and 64 up columns of the same rows.  Everything is read
+          // and packed first (four rounds of 16 + 16 columns), the accumulator half is released, then up to three
+          // [32 x 64] tiles (gate, up, h) leave through the slab.
           const int nh = p.N / 2;
           const int n0 = it.nt * GP_BNH + g * (GP_BNH / 2);
-#pragma unroll 1
-          for (int c = 0; c < GP_BNH / 2 / 32; ++c) {
-            const int nc = n0 + c * 32;
-            if (nc >= nh) break;
-            float gt[32], up[32];
-            tmem_ld32(t_row + g * (GP_BNH / 2) + c * 32, gt);
-            tmem_ld32(t_row + GP_BNH + g * (GP_BNH / 2) + c * 32, up);
-            tmem_ld_wait();
-            const long long r0o = static_cast<long long>(row - lane) * p.ldo + nc;
-            const int rows_valid = p.M - (row - lane);
-            if (p.out_gate != nullptr) {
-              store_tile_bf16<32>(slab, gt, p.out_gate + r0o, p.ldo, rows_valid, nh - nc, vec_ok, lane);
-              store_tile_bf16<32>(slab + GP_SLAB_BYTES / 2, up, p.out_up + r0o, p.ldo, rows_valid, nh - nc, vec_ok, lane);
-              // the backward pass reads the ROUNDED pre-activations, so the activation is formed from them too
+          const int row0w = row - lane;
+          uint32_t pkg[32], pku[32];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                gt[j] = __bfloat162float(__float2bfloat16_rn(gt[j]));
-                up[j] = __bfloat162float(__float2bfloat16_rn(up[j]));
+          for (int c = 0; c < 4; ++c) {            // 16 + 16 columns per round: few fp32 registers in flight
+            if (n0 + c * 16 < nh) {
+              float gt[16], up[16];
+              tmem_ld16(t_row + g * (GP_BNH / 2) + c * 16, gt);
+              tmem_ld16(t_row + GP_BNH + g * (GP_BNH / 2) + c * 16, up);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                pkg[8 * c + j] = pack_bf16x2(gt[2 * j], gt[2 * j + 1]);
+                pku[8 * c + j] = pack_bf16x2(up[2 * j], up[2 * j + 1]);
               }
             }
-#pragma unroll
-            for (int j = 0; j < 32; ++j) gt[j] = gp_act(gt[j], p.act) * up[j];
-            store_tile_bf16<32>(slab, gt, p.out + r0o, p.ldo, rows_valid, nh - nc, vec_ok, lane);
+          }
+          release_half(h);
+          // h is formed from the ROUNDED pre-activations (what the backward pass reads when they are stored), after the
+          // accumulator has gone back (the activation needs no tensor memory) and in place, to keep registers free
+          if (n0 < nh) {
+            const bool tma = p.tma_store != 0;
+            if (p.out_gate != nullptr) {
+              store_tile64_packed(slab, pkg, &map_out_gate, tma, n0, row0w, p.out_gate, p.ldo, p.M - row0w, nh - n0, vec_ok, lane);
+              store_tile64_packed(slab, pku, &map_out_up, tma, n0, row0w, p.out_up, p.ldo, p.M - row0w, nh - n0, vec_ok, lane);
+            }
+            if (p.act == 0) gp_glu_inplace<0>(pkg, pku);
+            else if (p.act == 1) gp_glu_inplace<1>(pkg, pku);
+            else gp_glu_inplace<2>(pkg, pku);
+            store_tile64_packed(slab, pkg, &map_out, tma, n0, row0w, p.out, p.ldo, p.M - row0w, nh - n0, vec_ok, lane);
           }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          if (leader) mbar_arrive(&tmem_empty[h]);
-          else mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[h]), 0));
-        }
+        if constexpr (EPI == GP_EPI_CE) release_half(h);
       }
       ++acc_iter;
     }
+    if (lane == 0) tma_store_wait_all();         // this lane's bulk stores are done before shared memory is given back
   }
 
   // Nobody leaves (or frees tensor memory) while the other CTA may still signal this CTA's barriers, complete copies
@@ -518,6 +625,240 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // least one budget ago and a tile copy lasts microseconds; one more millisecond lets any straggler land before the
     // shared memory is given back.
     const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 1000000ull) {}
+  }
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Short-K variant: 256 x 256 pair tiles with DOUBLE-BUFFERED accumulators.
+//
+// The 512 x 256 kernel above fills tensor memory with one tile, so its drain hides only behind the first k-blocks of the
+// next tile; with K = 768 (GPT-2's projections: 12 k-blocks) the drain is as long as the main loop and every SM pair
+// stores at the same moment.  Here each CTA owns 128 rows and one 128 x 256 accumulator per tile (256 TMEM columns),
+// two of them alternate, and the eight epilogue warps drain tile i during the whole main loop of tile i + 1.  A stage
+// is 32 KB per CTA (128 rows of A, 128 columns' worth of B) for 128 x 256 x 64 of work: 64 bytes per tensor clock,
+// against 96 for the single-CTA 128 x 256 tile and 48 for the 512 x 256 pair tile.  Plain store epilogue (+ bias,
+// + second K segment) only.  Same barrier protocol and unwind rules as gemm_pair_kernel.
+constexpr int GD_BM = 128;                              // rows of M per CTA (256 per pair)
+constexpr int GD_STAGES = 6;
+constexpr int GD_A_BYTES = GD_BM * GP_BK * 2;
+constexpr int GD_B_BYTES = GP_BNH * GP_BK * 2;
+constexpr int GD_STAGE_BYTES = GD_A_BYTES + GD_B_BYTES;
+constexpr int GD_GROUP_M = 16;                          // pair tiles (256 rows each) per raster band
+constexpr int GD_SMEM = GD_STAGES * GD_STAGE_BYTES + 8 * GP_SLAB_BYTES + 256 + 1024;
+static_assert((2 * GD_STAGES + 4) * 8 + 8 <= 256, "barrier block");
+
+__device__ __forceinline__ GpItem gd_decode(int w, int tiles_m, int tiles_n, int rank) {
+  const int band = GD_GROUP_M * tiles_n;
+  const int b = w / band, r = w % band;
+  const int m_in_band = min(GD_GROUP_M, tiles_m - b * GD_GROUP_M);
+  const int mt = b * GD_GROUP_M + r % m_in_band;
+  GpItem it;
+  it.row0 = mt * (2 * GD_BM) + rank * GD_BM;
+  it.nt = r / m_in_band;
+  return it;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS, 1)
+gemm_pair_db_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
+                    const __grid_constant__ CUtensorMap map_out, const PairParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* slabs = smem + GD_STAGES * GD_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(slabs + 8 * GP_SLAB_BYTES);
+  uint64_t* full = bars;                               // used in the leader CTA only
+  uint64_t* empty = bars + GD_STAGES;
+  uint64_t* tmem_full = bars + 2 * GD_STAGES;          // [2]: one per accumulator buffer
+  uint64_t* tmem_empty = bars + 2 * GD_STAGES + 2;     // [2], used in the leader CTA only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * GD_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* sched = reinterpret_cast<int*>(tmem_slot + 2);  // [3]: first, end, stride (valid in the leader CTA)
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int tiles_n = (p.N + GP_BN - 1) / GP_BN;
+  const int tiles_m = (p.M + 2 * GD_BM - 1) / (2 * GD_BM);
+  const int total_work = tiles_m * tiles_n;
+  const int nk1 = (p.K1 + GP_BK - 1) / GP_BK;
+  const int nk2 = (p.K2 + GP_BK - 1) / GP_BK;
+  const int num_kb = nk1 + nk2;
+  const uint64_t budget = p.wait_budget_ns;
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GD_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 16);                   // eight epilogue warps in each CTA
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+    if (nk2) {
+      tma_prefetch_desc(&map_a2);
+      tma_prefetch_desc(&map_b2);
+    }
+  }
+  if (warp == 1) {                   // one warp of EACH CTA takes part in a pair allocation
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  if (leader && threadIdx.x == 64) {  // a thread with nothing else to do during start-up claims the cluster's tiles
+    const GpSchedule sc = gp_claim_schedule(p, total_work, cluster_id, num_clusters);
+    sched[0] = sc.first;
+    sched[1] = sc.end;
+    sched[2] = sc.stride;
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                // both CTAs' barriers are initialised before any remote arrival or copy
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const GpSchedule sc = gp_read_schedule(sched);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- TMA producer (one per CTA)
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = sc.first; ok && w < sc.end; w += sc.stride) {
+        const GpItem it = gd_decode(w, tiles_m, tiles_n, rank);
+        const int bn0 = it.nt * GP_BN + static_cast<int>(rank) * GP_BNH;     // this CTA's half of the B tile
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_EMPTY, budget)) {
+            ok = false;
+            break;
+          }
+          if (leader) mbar_expect_tx(&full[stage], 2 * GD_STAGE_BYTES);
+          const uint32_t bar = map_to_cta(smem_u32(&full[stage]), 0);
+          uint8_t* a_dst = smem + stage * GD_STAGE_BYTES;
+          uint8_t* b_dst = a_dst + GD_A_BYTES;
+          const bool first = kb < nk1;
+          const int k0 = (first ? kb : kb - nk1) * GP_BK;
+          tma_load_2d_pair(a_dst, first ? &map_a : &map_a2, bar, k0, it.row0);
+          const CUtensorMap* mb = first ? &map_b : &map_b2;
+          if (first ? p.kn1 : p.kn2) {
+#pragma unroll
+            for (int j = 0; j < GP_BNH / 64; ++j)
+              tma_load_2d_pair(b_dst + j * (GP_BK * 128), mb, bar, bn0 + 64 * j, k0);
+          } else {
+            tma_load_2d_pair(b_dst, mb, bar, k0, bn0);
+          }
+          if (++stage == GD_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (leader && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer (leader CTA only)
+      constexpr uint32_t idesc_k = make_idesc_bf16(2 * GD_BM, GP_BN, 0, 0);
+      constexpr uint32_t idesc_n = make_idesc_bf16(2 * GD_BM, GP_BN, 0, 1);
+      int stage = 0, acc_iter = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = sc.first; ok && w < sc.end; w += sc.stride) {
+        const int as = acc_iter & 1;
+        if (!mbar_wait(&tmem_empty[as], ((acc_iter >> 1) & 1) ^ 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_EMPTY,
+                       budget)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * GP_BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, p.status, OB_ERR_WAIT_FULL, budget)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * GD_STAGE_BYTES);
+          const uint32_t b_addr = a_addr + GD_A_BYTES;
+          const bool kn = kb < nk1 ? p.kn1 != 0 : p.kn2 != 0;
+#pragma unroll
+          for (int kk = 0; kk < GP_BK / 16; ++kk) {
+            // K-major operand: rows 128 B apart, 8-row groups 1024 B apart, 32 B per 16-element k-step.
+            // N-major operand: 64-column blocks GP_BK*128 B apart, 8-row (k) groups 1024 B apart, 2048 B per k-step.
+            const uint64_t ad = make_smem_desc(a_addr + kk * 32, 16, 1024, 2);
+            const uint64_t bd = kn ? make_smem_desc(b_addr + kk * (16 * 128), GP_BK * 128, 1024, 2)
+                                   : make_smem_desc(b_addr + kk * 32, 16, 1024, 2);
+            umma_bf16_pair(d_tmem, ad, bd, kn ? idesc_n : idesc_k, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[stage], 3);          // frees the stage in both CTAs
+          if (++stage == GD_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_pair(&tmem_full[as], 3);           // this tile's accumulators (both CTAs) are complete
+        ++acc_iter;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps (8 per CTA)
+    const int q = warp & 3;                  // TMEM lane quarter this warp may read
+    const int g = (warp - 2) >> 2;           // 128-column half of the tile
+    uint8_t* slab = slabs + (warp - 2) * GP_SLAB_BYTES;
+    int acc_iter = 0;
+    bool ok = true;
+    const bool vec_ok = ((p.ldo & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    for (int w = sc.first; ok && w < sc.end; w += sc.stride) {
+      const GpItem it = gd_decode(w, tiles_m, tiles_n, rank);
+      const int as = acc_iter & 1;
+      if (!mbar_wait_idle(&tmem_full[as], (acc_iter >> 1) & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL, budget)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row0 = it.row0 + q * 32;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * GP_BN + g * (GP_BN / 2);
+      uint32_t pk[2][32];                    // both rounds in registers, then the accumulator goes back (see above)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int nc = it.nt * GP_BN + g * (GP_BN / 2) + c * 64;
+        if (nc < p.N) {
+          float v[64];
+          tmem_ld32(t_row + c * 64, v);
+          tmem_ld32(t_row + c * 64 + 32, v + 32);
+          tmem_ld_wait();
+          if (p.bias != nullptr) add_bias64(v, p.bias, nc, p.N);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) pk[c][j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (leader) mbar_arrive(&tmem_empty[as]);
+        else mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[as]), 0));
+      }
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int nc = it.nt * GP_BN + g * (GP_BN / 2) + c * 64;
+        if (nc < p.N)
+          store_tile64_packed(slab, pk[c], &map_out, p.tma_store != 0, nc, row0, p.out, p.ldo, p.M - row0, p.N - nc, vec_ok,
+                              lane);
+      }
+      ++acc_iter;
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  // Nobody leaves (or frees tensor memory) while the other CTA may still signal this CTA's barriers, complete copies
+  // on them or accumulate into its tensor memory.
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();              // lets copies issued before a timed-out wait land (see above)
     while (globaltimer_ns() - t0 < 1000000ull) {}
   }
   cluster_sync_all();
@@ -626,12 +967,12 @@ static int pair_group_m() {
   return v;
 }
 
-static int pair_grid(const void* kernel, int sms) {
+static int pair_grid(const void* kernel, int sms, int smem_bytes = GP_SMEM) {
   // clusters that can be co-resident (two CTAs of a pair must sit on paired SMs); one cluster per SM pair
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(sms), 1, 1);
   cfg.blockDim = dim3(GP_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = GP_SMEM;
+  cfg.dynamicSmemBytes = smem_bytes;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
   attr.val.clusterDim.x = 2;
@@ -649,6 +990,95 @@ static int pair_grid(const void* kernel, int sms) {
 }
 
 }  // namespace ob
+
+namespace ob {
+// ---- die-aware tile assignment: host side ------------------------------------------------------------------------
+// Claim words: a ring in device memory, one word per launch, each back to zero after its launch's last claim.  Two
+// launches share a word only if 4096 pair-GEMM launches lie between them and both are in flight at once; a kernel that
+// sees that reports OB_ERR_CLAIM instead of computing.
+constexpr int GP_CLAIM_RING = 4096;
+static __device__ unsigned long long g_pair_claim[GP_CLAIM_RING];
+
+static int pair_die_aware() {          // OB_PAIR_DIE_AWARE=0 switches the die-aware assignment off
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("OB_PAIR_DIE_AWARE");
+    v = (e && atoi(e) == 0) ? 0 : 1;
+  }
+  return v;
+}
+
+// Tensor map for bulk stores of a [rows, cols] bf16 output (32-row x 64-column boxes); returns false when the output
+// is not aligned for it (the kernels then store with ordinary vector / scalar stores).
+static bool pair_out_map(CUtensorMap* m, void* out, long long rows, long long cols, long long ldo) {
+  if (out == nullptr || (reinterpret_cast<uintptr_t>(out) & 15) != 0 || ((ldo * 2) & 15) != 0) return false;
+  return make_bf16_map_2d(m, out, rows, cols, ldo, 64, 32) == 0;
+}
+
+static void pair_set_schedule(PairParams* p, long long total, int clusters, cudaStream_t st) {
+  p->claim = nullptr;
+  p->n_front = clusters;
+  p->split = static_cast<int>(total);
+  if (!pair_die_aware() || p->status == nullptr || clusters < 4 || total < 4) return;
+  static std::atomic<bool> ready[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (!ready[dev].load(std::memory_order_acquire)) {
+    // the probe synchronises the device: never during a stream capture (ob_pair_init() runs it at load time instead)
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) {
+      cudaGetLastError();
+      return;
+    }
+    die_map_for_current_device();
+    ready[dev].store(true, std::memory_order_release);
+  }
+  const DieMap& dm = die_map_for_current_device();
+  if (!dm.valid) return;
+  static unsigned long long* ring[64] = {};
+  if (ring[dev] == nullptr) {
+    void* sym = nullptr;
+    if (cudaGetSymbolAddress(&sym, g_pair_claim) != cudaSuccess) {
+      cudaGetLastError();
+      return;
+    }
+    ring[dev] = static_cast<unsigned long long*>(sym);
+  }
+  static std::atomic<unsigned> next{0};
+  const int tp = dm.tpcs[0] + dm.tpcs[1];
+  int n_front = static_cast<int>((static_cast<long long>(clusters) * dm.tpcs[0] + tp / 2) / tp);
+  if (n_front < 1) n_front = 1;
+  if (n_front > clusters - 1) n_front = clusters - 1;
+  const long long waves = (total + clusters - 1) / clusters;
+  long long split = (total * n_front + clusters / 2) / clusters;
+  const long long lo = total - static_cast<long long>(clusters - n_front) * waves, hi = static_cast<long long>(n_front) * waves;
+  if (split < lo) split = lo;
+  if (split > hi) split = hi;
+  if (split < 1) split = 1;
+  if (split > total - 1) split = total - 1;
+  p->claim = ring[dev] + (next.fetch_add(1, std::memory_order_relaxed) % GP_CLAIM_RING);
+  p->n_front = n_front;
+  p->split = static_cast<int>(split);
+}
+
+}  // namespace ob
+
+// Probes the die map of the current device (no-op after the first call); call once outside any stream capture.
+extern "C" int ob_pair_init() {
+  using namespace ob;
+  const DieMap& dm = die_map_for_current_device();
+  return dm.valid ? dm.tpcs[0] * 1000 + dm.tpcs[1] : 0;
+}
+
+// smid -> die (0 / 1) of the current device as probed; returns the number of SMs, 0 when no two-die split was found.
+extern "C" int ob_die_map(unsigned char* out, int n) {
+  using namespace ob;
+  const DieMap& dm = die_map_for_current_device();
+  if (!dm.valid) return 0;
+  for (int i = 0; i < n && i < DM_MAX_SMS; ++i) out[i] = dm.die[i];
+  return dm.sms;
+}
 
 // D = A op1(B) + A2 op2(B2) + bias on CTA pairs.  b_kn / b2_kn = 1: that operand is stored [K, N].
 // glu != 0: `b` holds the gate rows and `b_up` the up rows ([N/2, K] each, or [K, N/2] with b_kn); N counts gate and up
@@ -725,10 +1155,67 @@ extern "C" int ob_gemm_pair(const void* a, const void* b, const void* b_up, cons
   const int avail = glu ? clusters_glu : clusters_store;
   const int clusters = static_cast<int>(total < avail ? total : avail);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  pair_set_schedule(&p, total, clusters, st);
+  CUtensorMap mo = ma, mog = ma, mou = ma;
+  p.tma_store = pair_out_map(&mo, out, rows_a, nb, ldo) ? 1 : 0;          // nb: the width of the output (N / 2 for GLU)
+  if (glu && out_gate != nullptr && p.tma_store)
+    p.tma_store = (pair_out_map(&mog, out_gate, rows_a, nb, ldo) && pair_out_map(&mou, out_up, rows_a, nb, ldo)) ? 1 : 0;
   if (glu)
-    gemm_pair_kernel<GP_EPI_GLU><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mbu, ma2, mb2, mb2u, p);
+    gemm_pair_kernel<GP_EPI_GLU><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mbu, ma2, mb2, mb2u, mo, mog, mou, p);
   else
-    gemm_pair_kernel<GP_EPI_STORE><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mbu, ma2, mb2, mb2u, p);
+    gemm_pair_kernel<GP_EPI_STORE><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mbu, ma2, mb2, mb2u, mo, mog, mou, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -55;
+}
+
+// The double-buffered 256 x 256 pair-tile kernel (plain store epilogue); arguments as in ob_gemm_pair.
+extern "C" int ob_gemm_pair_db(const void* a, const void* b, const void* a2, const void* b2, const void* bias, void* out,
+                               long long rows_a, int N, int K1, int K2, long long lda, long long ldb, long long lda2,
+                               long long ldb2, long long ldo, int b_kn, int b2_kn, int* status, double wait_budget_s,
+                               int num_sms, void* stream) {
+  using namespace ob;
+  if (rows_a <= 0 || N <= 0 || K1 <= 0) return 0;
+  if (rows_a > 0x7fffffffLL - 2 * GD_BM) return -50;
+  if (K2 > 0 && (a2 == nullptr || b2 == nullptr)) return -51;
+  CUtensorMap ma, mb, ma2, mb2;
+  int rc = make_bf16_map_2d(&ma, a, rows_a, K1, lda, GP_BK, GD_BM);
+  if (rc) return rc;
+  auto b_map = [&](CUtensorMap* m, const void* base, int K, long long ld, int kn) {
+    return kn ? make_bf16_map_2d(m, base, K, N, ld, 64, GP_BK) : make_bf16_map_2d(m, base, N, K, ld, GP_BK, GP_BNH);
+  };
+  rc = b_map(&mb, b, K1, ldb, b_kn);
+  if (rc) return rc;
+  if (K2 > 0) {
+    rc = make_bf16_map_2d(&ma2, a2, rows_a, K2, lda2, GP_BK, GD_BM);
+    if (rc) return rc;
+    rc = b_map(&mb2, b2, K2, ldb2, b2_kn);
+    if (rc) return rc;
+  } else {
+    ma2 = ma;
+    mb2 = mb;
+  }
+  static bool configured = false;
+  static int clusters_db = 0;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_pair_db_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GD_SMEM) != cudaSuccess)
+      return -54;
+    clusters_db = pair_grid(reinterpret_cast<const void*>(gemm_pair_db_kernel), num_sms, GD_SMEM);
+    configured = true;
+  }
+  PairParams p = {};
+  p.M = static_cast<int>(rows_a);
+  p.N = N; p.K1 = K1; p.K2 = K2;
+  p.kn1 = b_kn; p.kn2 = b2_kn;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.ldo = ldo;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.status = status;
+  p.wait_budget_ns = static_cast<unsigned long long>(wait_budget_s * 1e9);
+  const long long total = ((rows_a + 2 * GD_BM - 1) / (2 * GD_BM)) * ((N + GP_BN - 1) / GP_BN);
+  const int clusters = static_cast<int>(total < clusters_db ? total : clusters_db);
+  pair_set_schedule(&p, total, clusters, static_cast<cudaStream_t>(stream));
+  CUtensorMap mo = ma;
+  p.tma_store = pair_out_map(&mo, out, rows_a, N, ldo) ? 1 : 0;
+  gemm_pair_db_kernel<<<2 * clusters, GP_THREADS, GD_SMEM, static_cast<cudaStream_t>(stream)>>>(ma, mb, ma2, mb2, mo, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -55;
 }
 
@@ -779,7 +1266,8 @@ extern "C" int ob_linear_ce_fwd(const void* hidden, const void* weight, const lo
   const long long total = tiles_m * tiles_n;
   const int clusters = static_cast<int>(total < clusters_ce ? total : clusters_ce);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  gemm_pair_kernel<GP_EPI_CE><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mb, ma, mb, mb, p);
+  pair_set_schedule(&p, total, clusters, st);
+  gemm_pair_kernel<GP_EPI_CE><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mb, ma, mb, mb, ma, ma, ma, p);
   if (cudaGetLastError() != cudaSuccess) return -55;
   const long long warps = rows;
   lce_combine_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, st>>>(
@@ -899,7 +1387,7 @@ extern "C" int ob_linear_ce_fwd_noalloc(const void* hidden, const void* weight, 
   const long long total = tiles_m * tiles_n;
   const int clusters = static_cast<int>(total < clusters_ce ? total : clusters_ce);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  gemm_pair_kernel<GP_EPI_CE><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mb, ma, mb, mb, p);
+  gemm_pair_kernel<GP_EPI_CE><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mb, ma, mb, mb, ma, ma, ma, p);
   cudaError_t err = cudaGetLastError();
   if (err == cudaSuccess) {
     lce_combine_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, st>>>(

@@ -44,6 +44,7 @@ struct GemmParams {
   const int* group_offs;   // [num_groups + 1] or nullptr
   int num_groups;
   int b_group_rows;        // distance, in rows of B, between consecutive groups' slabs
+  int tma_store;           // the output leaves through bulk tensor stores (map_out is valid)
   int* status;
   unsigned long long wait_budget_ns;
 };
@@ -81,7 +82,7 @@ template <bool B_KN>
 __global__ void __launch_bounds__(GT_THREADS, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
-               const GemmParams p) {
+               const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* slabs = smem + GT_STAGES * GT_STAGE_BYTES;
@@ -242,27 +243,37 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc_fence_after();
       const int row0 = it.row0 + q * 32;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * GT_BN + g * (GT_BN / 2);
-#pragma unroll 1
-      for (int c = 0; c < GT_BN / 2 / 64; ++c) {
-        const int nc = it.n0 + g * (GT_BN / 2) + c * 64;
-        if (nc >= p.N) break;
-        float v[64];
-        tmem_ld32(t_row + c * 64, v);
-        tmem_ld32(t_row + c * 64 + 32, v + 32);
-        tmem_ld_wait();
-        if (p.bias != nullptr) {
+      // Both 64-column rounds go to registers (packed bf16) first, so the accumulator is back with the tensor pipe before
+      // a single store is issued.  Tiles that end inside a group's rows are masked by hand; all others leave through
+      // bulk tensor stores, which clip at the tensor's own bounds.
+      uint32_t pk[2][32];
 #pragma unroll
-          for (int j = 0; j < 64; ++j)
-            if (nc + j < p.N) v[j] += __bfloat162float(__ldg(p.bias + nc + j));
+      for (int c = 0; c < 2; ++c) {
+        const int nc = it.n0 + g * (GT_BN / 2) + c * 64;
+        if (nc < p.N) {
+          float v[64];
+          tmem_ld32(t_row + c * 64, v);
+          tmem_ld32(t_row + c * 64 + 32, v + 32);
+          tmem_ld_wait();
+          if (p.bias != nullptr) add_bias64(v, p.bias, nc, p.N);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) pk[c][j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
         }
-        store_tile_bf16<64>(slab, v, p.out + static_cast<long long>(row0) * p.ldo + nc, p.ldo, it.row_end - row0,
-                            p.N - nc, vec_ok, lane);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[as]);
+      const bool use_tma = p.tma_store != 0 && (p.group_offs == nullptr || row0 + 32 <= it.row_end);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int nc = it.n0 + g * (GT_BN / 2) + c * 64;
+        if (nc < p.N)
+          store_tile64_packed(slab, pk[c], &map_out, use_tma, nc, row0, p.out, p.ldo, it.row_end - row0, p.N - nc, vec_ok,
+                              lane);
+      }
       ++acc_iter;
     }
+    if (lane == 0) tma_store_wait_all();         // this lane's bulk stores are done before shared memory is given back
   }
 
   tc_fence_before();
@@ -324,9 +335,14 @@ extern "C" int ob_gemm_tn(const void* a, const void* b, const void* a2, const vo
   const long long tiles_m_bound = (rows_a + GT_BM - 1) / GT_BM + (group_offs ? groups : 0);
   const long long total = tiles_m_bound * tiles_n;
   const int grid = static_cast<int>(total < num_sms ? total : num_sms);
+  CUtensorMap mo = ma;
+  p.tma_store = 0;
+  if ((reinterpret_cast<uintptr_t>(out) & 15) == 0 && ((ldo * 2) & 15) == 0 &&
+      make_bf16_map_2d(&mo, out, rows_a, N, ldo, 64, 32) == 0)
+    p.tma_store = 1;
   if (b_kn)
-    gemm_tn_kernel<true><<<grid, GT_THREADS, GT_SMEM, static_cast<cudaStream_t>(stream)>>>(ma, mb, ma2, mb2, p);
+    gemm_tn_kernel<true><<<grid, GT_THREADS, GT_SMEM, static_cast<cudaStream_t>(stream)>>>(ma, mb, ma2, mb2, mo, p);
   else
-    gemm_tn_kernel<false><<<grid, GT_THREADS, GT_SMEM, static_cast<cudaStream_t>(stream)>>>(ma, mb, ma2, mb2, p);
+    gemm_tn_kernel<false><<<grid, GT_THREADS, GT_SMEM, static_cast<cudaStream_t>(stream)>>>(ma, mb, ma2, mb2, mo, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -44;
 }

@@ -22,6 +22,9 @@ _SIGNATURES = {
     "ob_ghost_norm": [P, P, P, I, I, I, I, LL, LL, P, P, P, LL, P, D, I, P],
     "ob_gemm_tn": [P, P, P, P, P, P, LL, I, I, I, LL, LL, LL, LL, LL, I, P, I, P, D, I, P],
     "ob_gemm_pair": [P, P, P, P, P, P, P, P, P, P, LL, I, I, I, LL, LL, LL, LL, LL, I, I, I, I, P, D, I, P],
+    "ob_pair_init": [],
+    "ob_die_map": [P, I],
+    "ob_gemm_pair_db": [P, P, P, P, P, P, LL, I, I, I, LL, LL, LL, LL, LL, I, I, P, D, I, P],
     "ob_linear_ce_fwd": [P, P, P, P, P, P, P, LL, I, I, LL, LL, LL, F, F, LL, P, D, I, P],
     "ob_linear_ce_dlogits": [P, P, P, P, LL, I, LL, F, F, LL, P],
     "ob_layernorm_fwd": [P, P, P, P, P, P, LL, I, F, P],

@@ -20,8 +20,14 @@ def rel(x, y):
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (128, 256, 128), (300, 520, 200), (1000, 136, 72), (1024, 768, 3072),
                                    (4096, 4096, 1024), (2048, 1536, 8192)])
-def test_pair_gemm_layouts_bias_segments(dev, M, N, K):
-    from opaque_b200 import ops
+@pytest.mark.parametrize("tile", ["512x256", "256x256"])
+def test_pair_gemm_layouts_bias_segments(dev, M, N, K, tile):
+    from opaque_b200 import ops as _ops
+    import functools
+    import types
+    # both tile variants must satisfy the same contract
+    ops = types.SimpleNamespace(**{k: getattr(_ops, k) for k in ("StatusWord", "gemm_ref", "gemm")},
+                                gemm_pair=functools.partial(_ops.gemm_pair, tile=tile))
     torch.manual_seed(M + N + K)
     st = ops.StatusWord(dev)
     a = torch.randn(M, K, device=dev).bfloat16()
@@ -122,3 +128,35 @@ def test_fused_head_cross_entropy_forward_and_dlogits(dev, R, V, K, softcap, smo
     (nll_ref * rw).sum().backward()
     ops.linear_ce_dlogits_(z, lab, lse_s, rw, softcap=softcap, label_smoothing=smoothing)
     assert rel(z, z_ref.grad) < 2e-2 and bool((z[::7] == 0).all())
+
+
+def test_die_map_splits_the_sms_and_pairs_agree(dev):
+    from opaque_b200 import ops
+    dm = ops.die_map()
+    if dm is None:
+        pytest.skip("no two-die split measured on this device")
+    assert len(dm) == torch.cuda.get_device_properties(dev).multi_processor_count
+    assert 0 < sum(dm) < len(dm)                                             # both dies present
+    assert all(dm[i] == dm[i + 1] for i in range(0, len(dm) - 1, 2))         # the two SMs of a pair share a die
+    assert ops.die_map() == dm                                               # cached, not re-measured
+
+
+@pytest.mark.parametrize("tile", ["512x256", "256x256"])
+def test_claimed_tile_schedule_covers_every_tile_across_ring_wraps(dev, tile):
+    """The die-aware assignment claims one slot per cluster from a ring of self-resetting words: every tile must be
+    computed exactly once, also after more launches than the ring has words and for grids smaller than the GPU."""
+    from opaque_b200 import ops
+    torch.manual_seed(7)
+    st = ops.StatusWord(dev)
+    for M, N, K in [(1024, 1024, 128), (4096, 2048, 64), (5000, 3000, 192)]:
+        a = torch.randn(M, K, device=dev).bfloat16()
+        w = (torch.randn(N, K, device=dev) / math.sqrt(K)).bfloat16()
+        ref = ops.gemm_ref(a, w)
+        y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        for i in range(1500):
+            if i % 500 == 0:
+                y.fill_(float("nan"))                                        # a skipped tile would stay NaN
+            ops.gemm_pair(a, w, out=y, status=st, tile=tile)
+            if i % 500 == 0:
+                assert st.read() == 0 and rel(y, ref) < 4e-3
+        assert st.read() == 0 and rel(y, ref) < 4e-3

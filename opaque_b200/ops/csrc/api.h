@@ -47,6 +47,7 @@ int ob_gemm_pair_db(const void* a, const void* b, const void* a2, const void* b2
 // ob_pair_init: probes if needed, returns 1000 * (SM pairs on die 0) + (SM pairs on die 1), 0 if no two-die split was
 // found; call it outside stream captures.  ob_die_map: smid -> 0 / 1 into out[0 .. n), returns the SM count or 0.
 int ob_pair_init(void);
+int ob_pair_set_die_aware(int on);   // die-aware tile assignment of the pair GEMMs (default off); returns the old value
 int ob_die_map(unsigned char* out, int n);
 // Output head fused with cross-entropy statistics on CTA pairs: logits tiles stay in tensor memory, per-tile partials
 // (scratch: rows * 2 * ceil(N / 256) float4) are combined in a fixed order into nll[rows], lse[rows]; `logits_out` (optional)

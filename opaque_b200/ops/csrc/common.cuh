@@ -272,57 +272,6 @@ __device__ __forceinline__ void red_add_f32(float* addr, float v) {
   asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
 }
 
-// Warp-cooperative store of a [32 rows x COLS columns] tile (lane = row on entry, COLS = 32 or 64 fp32 values per lane)
-// as bf16.  The rows go through a private shared-memory slab with a 16-byte XOR swizzle and leave as whole row segments
-// (COLS * 2 bytes contiguous per row, several rows per instruction), so memory sees full 32-byte sectors instead of one
-// 16-byte piece per lane and instruction.  `out` points at (first row of the warp, first column); rows >= rows_valid and
-// columns >= cols_valid are not written.
-template <int COLS>
-__device__ __forceinline__ void store_tile_bf16(uint8_t* slab, const float* v, __nv_bfloat16* out, long long ldo,
-                                              int rows_valid, int cols_valid, bool vec_ok, int lane) {
-  if (!vec_ok) {                       // unaligned destination: every lane writes its own row
-    if (lane < rows_valid) {
-      __nv_bfloat16* dst = out + static_cast<long long>(lane) * ldo;
-      for (int j = 0; j < COLS; ++j)
-        if (j < cols_valid) dst[j] = __float2bfloat16_rn(v[j]);
-    }
-    return;
-  }
-  constexpr int CHUNKS = COLS / 8;             // 16-byte chunks per row
-  constexpr int ROW_BYTES = COLS * 2;
-#pragma unroll
-  for (int c = 0; c < CHUNKS; ++c) {
-    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * c], v[8 * c + 1]);
-    __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * c + 2], v[8 * c + 3]);
-    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * c + 4], v[8 * c + 5]);
-    __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * c + 6], v[8 * c + 7]);
-    uint4 pk;
-    pk.x = *reinterpret_cast<uint32_t*>(&h0);
-    pk.y = *reinterpret_cast<uint32_t*>(&h1);
-    pk.z = *reinterpret_cast<uint32_t*>(&h2);
-    pk.w = *reinterpret_cast<uint32_t*>(&h3);
-    *reinterpret_cast<uint4*>(slab + lane * ROW_BYTES + ((c ^ (lane & (CHUNKS - 1))) << 4)) = pk;
-  }
-  __syncwarp();
-  constexpr int ROWS_PER_INSTR = 32 / CHUNKS;
-  const int c = lane % CHUNKS;
-#pragma unroll
-  for (int i = 0; i < 32 / ROWS_PER_INSTR; ++i) {
-    const int r = i * ROWS_PER_INSTR + lane / CHUNKS;
-    const uint4 pk = *reinterpret_cast<const uint4*>(slab + r * ROW_BYTES + ((c ^ (r & (CHUNKS - 1))) << 4));
-    if (r < rows_valid) {
-      __nv_bfloat16* dst = out + static_cast<long long>(r) * ldo + 8 * c;
-      if (8 * c + 8 <= cols_valid) {
-        *reinterpret_cast<uint4*>(dst) = pk;
-      } else if (8 * c < cols_valid) {
-        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&pk);
-        for (int j = 0; j < cols_valid - 8 * c; ++j) dst[j] = e[j];
-      }
-    }
-  }
-  __syncwarp();
-}
-
 // v[0 .. 63] += bias[nc .. nc + 63] (bf16 values, the same for every row): one 16-byte load per 8 columns when the
 // slice is aligned and inside N (64 scalar loads per thread made the epilogue LSU-bound: 12 % of a 512 x 256 tile).
 __device__ __forceinline__ void add_bias64(float* v, const __nv_bfloat16* bias, int nc, int N) {

@@ -254,10 +254,55 @@ template <int ACT>
 __device__ __forceinline__ void gp_glu_inplace(uint32_t* pkg, const uint32_t* pku) {
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
-    const float2 fg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pkg[j]));
-    const float2 fu = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pku[j]));
-    pkg[j] = pack_bf16x2(gp_act<ACT>(fg.x) * fu.x, gp_act<ACT>(fg.y) * fu.y);
+    const float gx = __uint_as_float(pkg[j] << 16), gy = __uint_as_float(pkg[j] & 0xffff0000u);
+    const float ux = __uint_as_float(pku[j] << 16), uy = __uint_as_float(pku[j] & 0xffff0000u);
+    pkg[j] = pack_bf16x2(gp_act<ACT>(gx) * ux, gp_act<ACT>(gy) * uy);
   }
+}
+
+// Cross-entropy statistics of 64 logits per lane, given as 32 packed bf16 pairs: running maximum m, sum of exp(z - m),
+// the label's logit and the plain sum.  FULL: all 64 columns lie inside the vocabulary (no per-column checks).
+// Two accumulators per quantity keep the dependent chains short; exp is one FFMA + ex2.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+template <bool FULL>
+__device__ __forceinline__ void ce_fold64(const uint32_t* pk, int nc, int N, int lab, float& m, float& ssum, float& zlab,
+                                          float& ztot) {
+  constexpr float LOG2E = 1.4426950408889634f;
+  float lm0 = -INFINITY, lm1 = -INFINITY, t0 = 0.f, t1 = 0.f;
+  const int d = lab - nc;                                  // position of the label inside this round, if 0 <= d < 64
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const float x = __uint_as_float(pk[j] << 16), y = __uint_as_float(pk[j] & 0xffff0000u);
+    if (FULL || nc + 2 * j < N) {
+      t0 += x;
+      lm0 = fmaxf(lm0, x);
+    }
+    if (FULL || nc + 2 * j + 1 < N) {
+      t1 += y;
+      lm1 = fmaxf(lm1, y);
+    }
+    if (d == 2 * j) zlab = x;
+    if (d == 2 * j + 1) zlab = y;
+  }
+  ztot += t0 + t1;
+  const float lm = fmaxf(lm0, lm1);
+  if (lm > m) {
+    ssum *= ex2_approx((m - lm) * LOG2E);                 // m = -inf on the first round: ex2(-inf) = 0
+    m = lm;
+  }
+  const float ml = m * LOG2E;
+  float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const float x = __uint_as_float(pk[j] << 16), y = __uint_as_float(pk[j] & 0xffff0000u);
+    if (FULL || nc + 2 * j < N) s0 += ex2_approx(fmaf(x, LOG2E, -ml));
+    if (FULL || nc + 2 * j + 1 < N) s1 += ex2_approx(fmaf(y, LOG2E, -ml));
+  }
+  ssum += s0 + s1;
 }
 
 template <int EPI>
@@ -533,42 +578,76 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           // which tile.
           const int n0 = it.nt * GP_BN + g * (GP_BN / 2);
           const long long label = row < p.M ? p.labels[row] : -1;
+          const int lab = (label >= 0 && label < p.N) ? static_cast<int>(label) : -(1 << 30);     // never matches a column
           float m = -INFINITY, ssum = 0.f, zlab = 0.f, ztot = 0.f;
-          __nv_bfloat16* orow = p.out != nullptr ? p.out + static_cast<long long>(row) * p.ldo : nullptr;
-#pragma unroll 1
-          for (int c = 0; c < GP_BN / 2 / 32; ++c) {
-            const int nc = n0 + c * 32;
-            if (nc >= p.N) break;
-            float v[32];
-            tmem_ld32(t_row + g * (GP_BN / 2) + c * 32, v);
-            tmem_ld_wait();
-            float lm = -INFINITY;
+          if (p.out != nullptr) {
+            // Training: the logits are stored (bf16) for the backward pass, and the statistics are taken from the stored,
+            // rounded values.  So the accumulator is read, soft-capped and packed to bf16 first and handed back; the
+            // exponentials and the stores then run beside the next tile's MMAs (with K = 768 the drain of a tile is
+            // otherwise longer than its main loop).
+            const int row0w = row - lane;
+            uint32_t pk[2][32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float z = v[j];
-              if (p.softcap > 0.f) z = p.softcap * tanhf(z / p.softcap);
-              // statistics are taken from the value the backward pass will read: the bf16-rounded logit when it is stored
-              if (orow != nullptr) z = __bfloat162float(__float2bfloat16_rn(z));
-              const bool in = nc + j < p.N;
-              v[j] = in ? z : -INFINITY;
-              if (in) {
-                ztot += z;
-                lm = fmaxf(lm, z);
-                if (nc + j == label) zlab = z;
+            for (int c = 0; c < 2; ++c) {
+              const int nc = n0 + c * 64;
+              if (nc < p.N) {
+                float v[64];
+                tmem_ld32(t_row + g * (GP_BN / 2) + c * 64, v);
+                tmem_ld32(t_row + g * (GP_BN / 2) + c * 64 + 32, v + 32);
+                tmem_ld_wait();
+                if (p.softcap > 0.f) {
+#pragma unroll
+                  for (int j = 0; j < 64; ++j) v[j] = p.softcap * tanhf(v[j] / p.softcap);
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) pk[c][j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
               }
             }
-            if (lm > m) {
-              ssum *= __expf(m - lm);
-              m = lm;
-            }
+            release_half(h);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) ssum += __expf(v[j] - m);      // exp(-inf) = 0 for masked columns
-            if (p.out != nullptr) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = nc + j < p.N ? v[j] : 0.f;
-              store_tile_bf16<32>(slab, v, p.out + static_cast<long long>(row - lane) * p.ldo + nc, p.ldo, p.M - (row - lane),
-                                p.N - nc, vec_ok, lane);
+            for (int c = 0; c < 2; ++c) {
+              const int nc = n0 + c * 64;
+              if (nc < p.N) {
+                if (nc + 64 <= p.N) ce_fold64<true>(pk[c], nc, p.N, lab, m, ssum, zlab, ztot);
+                else ce_fold64<false>(pk[c], nc, p.N, lab, m, ssum, zlab, ztot);
+                store_tile64_packed(slab, pk[c], &map_out, p.tma_store != 0, nc, row0w, p.out, p.ldo, p.M - row0w, p.N - nc,
+                                    vec_ok, lane);
+              }
             }
+          } else {
+            // Forward only (evaluation, reference log-probabilities): fp32 statistics, nothing stored.
+#pragma unroll 1
+            for (int c = 0; c < GP_BN / 2 / 32; ++c) {
+              const int nc = n0 + c * 32;
+              if (nc >= p.N) break;
+              float v[32];
+              tmem_ld32(t_row + g * (GP_BN / 2) + c * 32, v);
+              tmem_ld_wait();
+              if (p.softcap > 0.f) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = p.softcap * tanhf(v[j] / p.softcap);
+              }
+              float lm = -INFINITY;
+              const int d = lab - nc;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const bool in = nc + j < p.N;
+                const float z = v[j];
+                v[j] = in ? z : -INFINITY;
+                if (in) {
+                  ztot += z;
+                  lm = fmaxf(lm, z);
+                }
+                if (d == j) zlab = z;
+              }
+              if (lm > m) {
+                ssum *= __expf(m - lm);
+                m = lm;
+              }
+#pragma unroll
+              for (int j = 0; j < 32; ++j) ssum += __expf(v[j] - m);      // exp(-inf) = 0 for masked columns
+            }
+            release_half(h);
           }
           if (row < p.M)
             p.ce_partials[static_cast<long long>(row) * (2 * tiles_n) + 2 * it.nt + g] = make_float4(m, ssum, zlab, ztot);
@@ -609,7 +688,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             store_tile64_packed(slab, pkg, &map_out, tma, n0, row0w, p.out, p.ldo, p.M - row0w, nh - n0, vec_ok, lane);
           }
         }
-        if constexpr (EPI == GP_EPI_CE) release_half(h);
       }
       ++acc_iter;
     }
@@ -999,11 +1077,16 @@ namespace ob {
 constexpr int GP_CLAIM_RING = 4096;
 static __device__ unsigned long long g_pair_claim[GP_CLAIM_RING];
 
-static int pair_die_aware() {          // OB_PAIR_DIE_AWARE=0 switches the die-aware assignment off
-  static int v = -1;
+// Off by default: on the shapes measured it cut the sectors crossing the die-to-die link by 15 - 22 % and changed
+// neither the kernel time nor the tensor-pipe utilisation (the loads are not what the MMA thread waits for most).
+// OB_PAIR_DIE_AWARE=1 or ob_pair_set_die_aware(1) switches it on.
+static std::atomic<int> g_die_aware{-1};
+static int pair_die_aware() {
+  int v = g_die_aware.load(std::memory_order_relaxed);
   if (v < 0) {
     const char* e = getenv("OB_PAIR_DIE_AWARE");
-    v = (e && atoi(e) == 0) ? 0 : 1;
+    v = (e && atoi(e) != 0) ? 1 : 0;
+    g_die_aware.store(v, std::memory_order_relaxed);
   }
   return v;
 }
@@ -1063,6 +1146,13 @@ static void pair_set_schedule(PairParams* p, long long total, int clusters, cuda
 }
 
 }  // namespace ob
+
+// Die-aware tile assignment on (1) / off (0) for later launches of this process; returns the previous setting.
+extern "C" int ob_pair_set_die_aware(int on) {
+  const int prev = ob::pair_die_aware();
+  ob::g_die_aware.store(on ? 1 : 0, std::memory_order_relaxed);
+  return prev;
+}
 
 // Probes the die map of the current device (no-op after the first call); call once outside any stream capture.
 extern "C" int ob_pair_init() {
@@ -1267,7 +1357,9 @@ extern "C" int ob_linear_ce_fwd(const void* hidden, const void* weight, const lo
   const int clusters = static_cast<int>(total < clusters_ce ? total : clusters_ce);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   pair_set_schedule(&p, total, clusters, st);
-  gemm_pair_kernel<GP_EPI_CE><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mb, ma, mb, mb, ma, ma, ma, p);
+  CUtensorMap mo = ma;
+  p.tma_store = (logits_out != nullptr && pair_out_map(&mo, logits_out, rows, N, ldo)) ? 1 : 0;
+  gemm_pair_kernel<GP_EPI_CE><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mb, ma, mb, mb, mo, ma, ma, p);
   if (cudaGetLastError() != cudaSuccess) return -55;
   const long long warps = rows;
   lce_combine_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, st>>>(

@@ -258,6 +258,29 @@ def compare_cases(impl: str):
             raise SystemExit(f"a device wait timed out (status {st.read()})")
 
 
+def pair_small_case():
+    """Two rounds of one launch each: CTA-pair GEMM (512 x 256 tiles), its 256 x 256 variant, the single-CTA kernel, the
+    gated up-projection and the library GEMM on y[8192, 8192] = x[8192, 4096] W^T (inputs + output 192 MB > L2).  A small
+    case for counter captures (one launch per kernel and round; nothing is timed here)."""
+    from opaque_b200 import ops
+    dev = torch.device("cuda", 0)
+    M, N, K = 8192, 8192, 4096
+    x = torch.randn(M, K, device=dev).bfloat16()
+    w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+    st = ops.StatusWord(dev)
+    for _ in range(2):
+        y = ops.gemm_pair(x, w, status=st)
+        y2 = ops.gemm_pair(x, w, status=st, tile="256x256")
+        y3 = ops.gemm(x, w, status=st, kernel="single")
+        h, g, u = ops.gemm_glu(x, w[: N // 2], w[N // 2:], status=st)
+        ref = torch.matmul(x, w.t())
+    torch.cuda.synchronize()
+    if st.read():
+        raise SystemExit(f"a device wait timed out (status {st.read()})")
+    err = [float((t.float() - ref.float()).abs().max()) for t in (y, y2, y3)]
+    print(json.dumps({"case": "pair-small", "max_abs_diff_vs_library": err}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default="all")
@@ -269,6 +292,8 @@ def main():
         return compare_cases("reference")
     if args.case == "compare":
         return compare_cases("ours")
+    if args.case == "pair-small":
+        return pair_small_case()
     if args.case == "wgrad-rs":
         return fused_reduce_scatter_case()
     from opaque_b200 import ops

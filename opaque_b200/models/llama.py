@@ -233,6 +233,25 @@ class LlamaDecoderLayer(nn.Module):
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **nk)
         self.mlp = LlamaMLP(cfg, dtype, device)
 
+    @property
+    def standard(self) -> bool:
+        """Plain pre-norm block (``h += attn(norm(h)); h += mlp(norm(h))`` with RMSNorm and no residual multiplier)."""
+        return not (self.parallel or self.sandwich or self.post_norm) and self.res == 1.0
+
+    def forward_carried(self, x, residual, cos, sin, pos):
+        """The standard block on a split stream: the hidden state is ``x + residual`` and the sum is only ever formed
+        inside the next norm kernel (forward), its two gradient branches only inside that kernel's backward.  Saves the
+        four element-wise add launches per block that the plain form costs (two forward, two backward).
+        Returns ``(mlp output, residual)``; the caller folds the last pair into the final norm."""
+        if residual is None:
+            residual = x
+            n = self.input_layernorm(x)
+        else:
+            n, residual = self.input_layernorm(x, residual)
+        a = self.self_attn(n, cos, sin, pos)
+        n2, residual = self.post_attention_layernorm(a, residual)
+        return self.mlp(n2), residual
+
     def forward(self, h, cos, sin, pos):
         if self.parallel:
             n = self.input_layernorm(h)
@@ -306,6 +325,14 @@ class LlamaForCausalLM(nn.Module):
         cos, sin = self.rope_cos, self.rope_sin
         if self.config.local_rope_theta is not None:           # (global, local) table pairs; windowed layers take the second
             cos, sin = (self.rope_cos, self.rope_cos_local), (self.rope_sin, self.rope_sin_local)
+        if (h.is_cuda and ops.functional.kernels_enabled() and isinstance(self.model.norm, RMSNorm)
+                and not (self.activation_checkpointing and torch.is_grad_enabled())
+                and all(layer.standard for layer in self.model.layers)):
+            x, res = h, None
+            for layer in self.model.layers:
+                x, res = layer.forward_carried(x, res, cos, sin, position_ids)
+            h = self.model.norm(x, res)[0] if res is not None else self.model.norm(x)
+            return h if self.config.logits_scaling == 1.0 else h / self.config.logits_scaling
         for layer in self.model.layers:
             if self.activation_checkpointing and torch.is_grad_enabled():
                 if ops.functional.kernels_enabled():

@@ -367,6 +367,60 @@ rope_qk_kernel(__nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ k, con
   }
 }
 
+// Out-of-place rotary embedding with 16-byte accesses: reads Q / K through (batch, token, head) strides (views into a
+// fused q|k|v projection buffer, or the [B, H, T, D] gradients an attention kernel returns) and writes contiguous
+// [rows, H, D] outputs, so no copy is needed before or after.  One thread rotates 8 + 8 elements (columns d .. d+7 and
+// half+d .. half+d+7 of one head).  D % 16 == 0; all pointers and strides 16-byte aligned.
+struct RopeSrc {
+  const __nv_bfloat16* ptr;
+  long long sb, st, sh;      // element strides of batch, token and head; the last dimension is contiguous
+};
+
+__global__ void __launch_bounds__(256)
+rope_qk_oop_kernel(RopeSrc qs, RopeSrc ks, __nv_bfloat16* __restrict__ qo, __nv_bfloat16* __restrict__ ko,
+                   const float* __restrict__ cs, const float* __restrict__ sn, const int* __restrict__ pos,
+                   long long rows, int seq_len, int Hq, int Hk, int D, float sign) {
+  const int half = D >> 1;
+  const int chunks = half >> 3;                          // 8-element chunks per half head
+  const long long per_row = static_cast<long long>(Hq + Hk) * chunks;
+  const long long total = rows * per_row;
+  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < total; i += gridDim.x * 256LL) {
+    const long long r = i / per_row;
+    const int rem = static_cast<int>(i % per_row);
+    const int h = rem / chunks;
+    const int d = (rem % chunks) << 3;
+    const long long b = r / seq_len, t = r % seq_len;
+    const int pidx = pos ? pos[r] : static_cast<int>(t);
+    const bool is_q = h < Hq;
+    const int hh = is_q ? h : h - Hq;
+    const RopeSrc& src = is_q ? qs : ks;
+    const __nv_bfloat16* in = src.ptr + b * src.sb + t * src.st + hh * src.sh;
+    __nv_bfloat16* out = (is_q ? qo + r * Hq * D : ko + r * Hk * D) + static_cast<long long>(hh) * D;
+    const uint4 lo4 = *reinterpret_cast<const uint4*>(in + d);
+    const uint4 hi4 = *reinterpret_cast<const uint4*>(in + half + d);
+    const float* cp = cs + static_cast<long long>(pidx) * half + d;
+    const float* sp = sn + static_cast<long long>(pidx) * half + d;
+    const float4 c0 = *reinterpret_cast<const float4*>(cp), c1 = *reinterpret_cast<const float4*>(cp + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    const __nv_bfloat162* lo = reinterpret_cast<const __nv_bfloat162*>(&lo4);
+    const __nv_bfloat162* hi = reinterpret_cast<const __nv_bfloat162*>(&hi4);
+    uint4 olo, ohi;
+    __nv_bfloat162* plo = reinterpret_cast<__nv_bfloat162*>(&olo);
+    __nv_bfloat162* phi = reinterpret_cast<__nv_bfloat162*>(&ohi);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 l = __bfloat1622float2(lo[j]), hv = __bfloat1622float2(hi[j]);
+      const float sx = sv[2 * j] * sign, sy = sv[2 * j + 1] * sign;
+      plo[j] = __floats2bfloat162_rn(l.x * c[2 * j] - hv.x * sx, l.y * c[2 * j + 1] - hv.y * sy);
+      phi[j] = __floats2bfloat162_rn(hv.x * c[2 * j] + l.x * sx, hv.y * c[2 * j + 1] + l.y * sy);
+    }
+    *reinterpret_cast<uint4*>(out + d) = olo;
+    *reinterpret_cast<uint4*>(out + half + d) = ohi;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Cross-entropy over one row per CTA.  z = softcap * tanh(scale*logit / softcap) (softcap = 0: off).
 // Outputs nll[row] = lse - z[label] (label smoothing: minus (eps/V) * (sum z - V*lse) mix), lse[row];
@@ -587,6 +641,27 @@ extern "C" int ob_rope_qk(void* q, void* k, const float* cos_t, const float* sin
   rope_qk_kernel<<<flat_grid(work, 256, sms), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), cos_t, sin_t, pos, rows, seq_len, Hq, Hk, D,
       ldq, ldk, backward ? -1.f : 1.f);
+  return OB_CHECK_LAUNCH();
+}
+
+// Out-of-place, strided-input form (see rope_qk_oop_kernel): q_in / k_in are read through element strides (batch, token,
+// head), q_out / k_out are contiguous [rows, H, D].  Returns -2 when D % 16 != 0, -3 when something is not 16-byte aligned.
+extern "C" int ob_rope_qk_oop(const void* q_in, const void* k_in, void* q_out, void* k_out, const float* cos_t,
+                              const float* sin_t, const int* pos, long long rows, int seq_len, int Hq, int Hk, int D,
+                              long long q_sb, long long q_st, long long q_sh, long long k_sb, long long k_st, long long k_sh,
+                              int backward, int sms, void* stream) {
+  if (rows <= 0) return 0;
+  if (D % 16) return -2;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (!al(q_in) || !al(k_in) || !al(q_out) || !al(k_out) || !al(cos_t) || !al(sin_t) ||
+      ((q_sb | q_st | q_sh | k_sb | k_st | k_sh) & 7) != 0)
+    return -3;
+  RopeSrc qs{static_cast<const __nv_bfloat16*>(q_in), q_sb, q_st, q_sh};
+  RopeSrc ks{static_cast<const __nv_bfloat16*>(k_in), k_sb, k_st, k_sh};
+  const long long work = rows * (Hq + Hk) * (D / 16);
+  rope_qk_oop_kernel<<<flat_grid(work, 256, sms), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      qs, ks, static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_out), cos_t, sin_t, pos, rows, seq_len, Hq,
+      Hk, D, backward ? -1.f : 1.f);
   return OB_CHECK_LAUNCH();
 }
 

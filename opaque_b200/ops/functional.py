@@ -446,13 +446,20 @@ def rope_qk_ref(q, k, cos, sin, pos=None, sign=1.0):
 
 
 class _RoPE(Function):
+    """Joint rotary embedding.  Inputs may be any 4-D ``[B, T, H, D]`` views with a contiguous last dimension (slices of a
+    fused q|k|v projection, the ``[B, H, T, D]``-laid-out gradients an attention kernel returns): the kernel reads them
+    through their strides and writes contiguous outputs, so nothing is copied before or after."""
+
     @staticmethod
     def forward(ctx, q, k, cos, sin, pos):
         ctx.save_for_backward(cos, sin, pos if pos is not None else torch.empty(0))
         ctx.has_pos = pos is not None
-        q, k = q.contiguous().clone(), k.contiguous().clone()
-        _RoPE._run(q, k, cos, sin, pos, 0)
-        return q, k
+        return _RoPE._run(q, k, cos, sin, pos, 0)
+
+    @staticmethod
+    def _strided_ok(x):
+        return (x.ndim == 4 and x.stride(-1) == 1 and x.shape[-1] % 16 == 0 and x.data_ptr() % 16 == 0
+                and all(s % 8 == 0 for s in x.stride()[:3]))
 
     @staticmethod
     def _run(q, k, cos, sin, pos, backward):
@@ -462,15 +469,27 @@ class _RoPE(Function):
         p32 = None
         if pos is not None:
             p32 = pos.reshape(-1).to(torch.int32)
+        if _RoPE._strided_ok(q) and _RoPE._strided_ok(k) and cos.data_ptr() % 16 == 0 and sin.data_ptr() % 16 == 0 \
+                and cos.is_contiguous() and sin.is_contiguous():
+            qo = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+            ko = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+            rc = lib.load().ob_rope_qk_oop(q.data_ptr(), k.data_ptr(), qo.data_ptr(), ko.data_ptr(), cos.data_ptr(),
+                                           sin.data_ptr(), lib.ptr(p32), rows, T, Hq, Hk, D, q.stride(0), q.stride(1),
+                                           q.stride(2), k.stride(0), k.stride(1), k.stride(2), backward, lib.sm_count(),
+                                           lib.stream())
+            lib.check(rc, "rope_qk")
+            return qo, ko
+        # general case: one copy into contiguous storage, rotated in place
+        q, k = q.clone(memory_format=torch.contiguous_format), k.clone(memory_format=torch.contiguous_format)
         rc = lib.load().ob_rope_qk(q.data_ptr(), k.data_ptr(), cos.data_ptr(), sin.data_ptr(), lib.ptr(p32), rows, T,
                                    Hq, Hk, D, Hq * D, Hk * D, backward, lib.sm_count(), lib.stream())
         lib.check(rc, "rope_qk")
+        return q, k
 
     @staticmethod
     def backward(ctx, dq, dk):
         cos, sin, pos = ctx.saved_tensors
-        dq, dk = dq.contiguous().clone(), dk.contiguous().clone()
-        _RoPE._run(dq, dk, cos, sin, pos if ctx.has_pos else None, 1)
+        dq, dk = _RoPE._run(dq, dk, cos, sin, pos if ctx.has_pos else None, 1)
         return dq, dk, None, None, None
 
 

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "ob_glu_fwd": [P, P, P, LL, I, LL, I, I, P],
     "ob_glu_bwd": [P, P, P, P, P, LL, I, LL, LL, I, I, P],
     "ob_rope_qk": [P, P, P, P, P, LL, I, I, I, I, LL, LL, I, I, P],
+    "ob_rope_qk_oop": [P, P, P, P, P, P, P, LL, I, I, I, I, LL, LL, LL, LL, LL, LL, I, I, P],
     "ob_cross_entropy": [P, I, P, P, P, P, LL, I, LL, F, F, F, LL, I, P],
     "ob_philox_normal_add": [P, I, LL, ULL, LL, F, U, I, P],
     "ob_rows_sumsq": [P, I, LL, LL, P, I, P],

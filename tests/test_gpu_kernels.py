@@ -255,6 +255,23 @@ def test_norm_activation_rope_kernels(dev):
     q1.backward(gq)
     back, _ = ops.rope_qk_ref(gq, k.detach(), cos, sin, pos, sign=-1.0)
     assert rel(q.grad, back) < 1e-3
+    # strided views are read through their strides: slices of a fused q|k|v buffer, [B, H, T, D]-laid-out tensors
+    buf = torch.randn(2, 64, (8 + 2 + 2) * 64, device=dev).bfloat16()
+    qv, kv = buf[..., : 8 * 64].view(2, 64, 8, 64), buf[..., 8 * 64: 10 * 64].view(2, 64, 2, 64)
+    qt = torch.randn(2, 8, 64, 64, device=dev).bfloat16().transpose(1, 2)
+    kt = torch.randn(2, 2, 64, 64, device=dev).bfloat16().transpose(1, 2)
+    for qq, kk in ((qv, kv), (qt, kt)):
+        assert not qq.is_contiguous()
+        q3, k3 = ops.rope_qk(qq, kk, cos, sin, pos)
+        q4, k4 = ops.rope_qk_ref(qq.contiguous(), kk.contiguous(), cos, sin, pos)
+        assert q3.is_contiguous() and torch.equal(q3, q4) and torch.equal(k3, k4)
+    # head sizes the 16-byte kernel does not take fall back to the general one
+    q5 = torch.randn(2, 64, 4, 24, device=dev).bfloat16()
+    k5 = torch.randn(2, 64, 2, 24, device=dev).bfloat16()
+    c5, s5 = ops.rope_tables(24, 128, 10000.0, device=dev)
+    a5, b5 = ops.rope_qk(q5, k5, c5, s5, None)
+    a6, b6 = ops.rope_qk_ref(q5, k5, c5, s5, None)
+    assert rel(a5, a6) < 4e-3 and rel(b5, b6) < 4e-3          # fused multiply-adds round differently from the eager reference
 
 
 @pytest.mark.parametrize("H", [1024, 2048, 4096, 8192, 1536])

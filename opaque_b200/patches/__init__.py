@@ -17,7 +17,7 @@ from typing import Any
 
 import torch
 
-from . import kernels
+from . import inplace, kernels
 from ..models import GPT2Config, GPT2LMHeadModel, LlamaConfig, LlamaForCausalLM, MoEConfig, MoEForCausalLM
 
 _FAMILIES: dict[str, Callable[[Any, dict], torch.nn.Module]] = {}
@@ -31,9 +31,9 @@ MOE_LIKE = ("mixtral", "qwen2_moe", "qwen3_moe", "hunyuan_v1_moe", "gpt_oss")
 ROPE_INTERLEAVED = frozenset({"glm4", "cohere", "cohere2"})      # families that rotate the pairs (2i, 2i+1); q / k rows are permuted on conversion
 UNSUPPORTED = {
     "gemma3": "the multimodal wrapper; convert its text model (model_type gemma3_text)",
-    "deepseek_v4": "multi-head latent attention",
-    "qwen3_next": "gated delta-net layers", "qwen3_5_moe": "gated delta-net layers",
 }
+# deepseek_v4 (latent attention), qwen3_next and qwen3_5_moe (gated delta-net layers) are not converted either: they stay
+# Hugging Face models and get kernel forwards in place (patches/inplace.py), as the reference does for them.
 
 
 def register_family(model_type: str, builder: Callable[[Any, dict], torch.nn.Module]) -> None:
@@ -333,8 +333,9 @@ def _convert_state_dict(mtype: str, sd: dict, out: torch.nn.Module) -> dict:
 
 
 def supported_families() -> list[str]:
-    """Sorted Hugging Face ``model_type`` names that ``apply_model_patches`` converts."""
-    return sorted(_FAMILIES)
+    """Sorted Hugging Face ``model_type`` names that ``apply_model_patches`` accepts: converted into this package's models,
+    or (``inplace.inplace_families()``) kept as Hugging Face models with kernel forwards patched in."""
+    return sorted(set(_FAMILIES) | set(inplace.INPLACE_FAMILIES))
 
 
 def _is_framework_model(model: Any) -> bool:
@@ -354,6 +355,12 @@ def apply_transformers_model_patches(model: Any, *, performance: bool = True, co
     mtype = _cfg_get(cfg, "model_type")
     if mtype in UNSUPPORTED:
         raise NotImplementedError(f"model_type {mtype!r} is not converted: {UNSUPPORTED[mtype]}")
+    if mtype in inplace.INPLACE_FAMILIES:
+        if not isinstance(model, torch.nn.Module):
+            raise ValueError(f"model_type {mtype!r} is patched in place: pass the instantiated Hugging Face model, not a config")
+        if performance:
+            inplace.apply_inplace_patches(model, mtype)
+        return model
     if mtype not in _FAMILIES:
         raise ValueError(f"model_type {mtype!r} has no registered family; known: {supported_families()}")
     out = _FAMILIES[mtype](cfg, kw)
@@ -405,4 +412,4 @@ def is_runtime_patched() -> bool:
 
 
 __all__ = ["apply_model_patches", "apply_peft_model_patches", "apply_runtime_patches", "apply_transformers_model_patches",
-           "is_runtime_patched", "kernels", "register_family", "supported_families"]
+           "inplace", "is_runtime_patched", "kernels", "register_family", "supported_families"]

@@ -82,9 +82,45 @@ def test_converted_model_matches_hf_logits(name, cfg, cls):
     assert torch.allclose(ours.per_example_loss(ids, labels), ref, atol=2e-4)
 
 
-def test_unsupported_families_are_refused_with_a_reason():
-    with pytest.raises(NotImplementedError, match="latent attention"):
+def _tiny_qwen3_next(**kw):
+    cfg = transformers.Qwen3NextConfig(
+        vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=16, max_position_embeddings=64, num_experts=4, num_experts_per_tok=2,
+        moe_intermediate_size=64, shared_expert_intermediate_size=64, linear_num_value_heads=4, linear_num_key_heads=2,
+        linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4, full_attention_interval=2, **kw)
+    torch.manual_seed(0)
+    return transformers.Qwen3NextForCausalLM(cfg)
+
+
+def test_inplace_families_keep_the_hugging_face_model_and_swap_forwards():
+    """qwen3_next / qwen3_5_moe / deepseek_v4 are not converted: the Hugging Face model gets kernel forwards in place, which
+    fall back to the original code off the GPU, so outputs are unchanged here; removing the patches restores the classes'
+    forwards."""
+    from opaque_b200.patches import inplace
+    assert {"deepseek_v4", "qwen3_next", "qwen3_5_moe"} <= set(patches.supported_families())
+    hf = _tiny_qwen3_next().float().eval()
+    ids = torch.randint(0, 128, (2, 12))
+    with torch.no_grad():
+        want = hf(ids).logits
+    out = patches.apply_model_patches(hf)
+    assert out is hf
+    counts = inplace.apply_inplace_patches(hf)                       # idempotent
+    assert counts["rms_norm"] >= 9 and counts["mlp"] >= 4 and counts["experts"] == 4
+    norm = next(m for m in hf.modules() if type(m).__name__ == "Qwen3NextRMSNorm")
+    assert "forward" in norm.__dict__
+    with torch.no_grad():
+        got = hf(ids).logits
+    assert torch.equal(got, want)
+    assert inplace.remove_inplace_patches(hf) == sum(counts.values()) and "forward" not in norm.__dict__
+    with pytest.raises(ValueError, match="instantiated"):
         patches.apply_model_patches({"model_type": "deepseek_v4"})
+    with pytest.raises(ValueError, match="not an in-place family"):
+        inplace.apply_inplace_patches(torch.nn.Linear(2, 2), "llama")
+
+
+def test_unsupported_families_are_refused_with_a_reason():
+    with pytest.raises(NotImplementedError, match="multimodal"):
+        patches.apply_model_patches({"model_type": "gemma3"})
     with pytest.raises(NotImplementedError, match="per-head weights"):
         patches.apply_model_patches(transformers.CohereConfig(**COMMON, use_qk_norm=True))
     with pytest.raises(ValueError, match="no registered family"):

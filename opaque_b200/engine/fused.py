@@ -151,6 +151,32 @@ class Capture:
                        ldm=r, ldn=1, n_valid=r, accumulate=False, group_stride=stride, block_n=64,
                        status=self.status)
 
+    def add_lora_qkv(self, factors, x2d: torch.Tensor, xa: torch.Tensor, g_parts, q_all: torch.Tensor) -> None:
+        """The three LoRA pairs of one attention block: ``factors = ((A_q, B_q), (A_k, B_k), (A_v, B_v))`` sharing ``x2d``.
+
+        When the flat space holds ``A_q, A_k, A_v`` back to back (it does, see ``FlatSpace``), their per-example
+        gradients are ONE launch: ``[q_i | k_i | v_i]ᵀ x_i`` is the ``[3r, in]`` block that starts at ``A_q``'s offset,
+        and ``x`` is read once instead of three times.  The ``dB`` products have different left operands and stay separate.
+        """
+        r, d_in = factors[0][0].shape
+        slots = [self.engine.slot_of(a) for a, _ in factors]
+        contiguous = all(sl.direct for sl in slots) and all(slots[j + 1].offset == slots[j].offset + r * d_in for j in range(2)) \
+            and q_all.is_contiguous() and q_all.shape[1] == 3 * r
+        if not contiguous:
+            for j, (a, b) in enumerate(factors):
+                self.add_lora(a, b, x2d, xa[:, j * r:(j + 1) * r], g_parts[j], q_all[:, j * r:(j + 1) * r])
+            return
+        stride = self.pe.stride(0)
+        ops.wgrad_clip(x2d, q_all, self.pe, seg_offsets=self.seg, num_groups=self.batch_size, out_offset=slots[0].offset,
+                       ldm=1, ldn=d_in, n_valid=3 * r, accumulate=False, group_stride=stride, block_n=64, status=self.status)
+        for j, (_, b) in enumerate(factors):
+            sb = self.engine.slot_of(b)
+            if not sb.direct:
+                raise RuntimeError("LoRA factors must be direct parameters of the flat space")
+            ops.wgrad_clip(g_parts[j], xa[:, j * r:(j + 1) * r], self.pe, seg_offsets=self.seg, num_groups=self.batch_size,
+                           out_offset=sb.offset, ldm=r, ldn=1, n_valid=r, accumulate=False, group_stride=stride, block_n=64,
+                           status=self.status)
+
     def _tied_cross_term(self, slot_name: str) -> torch.Tensor | None:
         """``<g_embedding, g_head>`` per example for a weight used as input embedding AND output head.
 
@@ -568,11 +594,11 @@ class _LoRAQKV(Function):
             dx = ops.gemm_pair(g_all, w_all, b_layout="kn", a2=q_all, b2=a_cat, b2_layout="kn").view(ctx.xshape)
         cap = current_capture()
         if cap is not None:
-            lo = 0
-            for j, (a, b) in enumerate(((aq, bq), (ak, bk), (av, bv))):
-                g_j = g_all[:, lo:lo + outs[j]]
+            lo, parts = 0, []
+            for j in range(3):
+                parts.append(g_all[:, lo:lo + outs[j]])
                 lo += outs[j]
-                cap.add_lora(a, b, x2d, xa[:, j * r:(j + 1) * r], g_j, q_all[:, j * r:(j + 1) * r])
+            cap.add_lora_qkv(((aq, bq), (ak, bk), (av, bv)), x2d, xa, parts, q_all)
             return (dx,) + (None,) * 9
         grads = []
         lo = 0

@@ -73,8 +73,22 @@ class FlatSpace:
         self.group = group
         is_direct = direct or default_direct
         label = group_of or (lambda name: "")
-        # stable: direct parameters first, and inside them every clipping group contiguous
-        ordered = sorted(named_params, key=lambda np_: (not is_direct(*np_), label(np_[0]) if is_direct(*np_) else ""))
+        # stable: direct parameters first, and inside them every clipping group contiguous.  The LoRA `A` factors of the
+        # q, k and v projections of one attention block are placed back to back (at the position of the block's first
+        # one), so their per-example gradients `[q_i | k_i | v_i]ᵀ x_i` are ONE GEMM launch writing one contiguous range.
+        names = [n for n, _ in named_params]
+        index = {n: i for i, n in enumerate(names)}
+
+        def position(name: str) -> tuple:
+            for j, proj in enumerate(("q_proj", "k_proj", "v_proj")):
+                tail = f".{proj}.lora_A"
+                if name.endswith(tail):
+                    first = name[: -len(tail)] + ".q_proj.lora_A"
+                    if first in index and all(name[: -len(tail)] + f".{p}.lora_A" in index for p in ("k_proj", "v_proj")):
+                        return (index[first], j)
+            return (index[name], 0)
+        ordered = sorted(named_params, key=lambda np_: (not is_direct(*np_), label(np_[0]) if is_direct(*np_) else "",
+                                                        position(np_[0])))
         self.slots: dict[str, Slot] = {}
         self.group_label: dict[str, str] = {}
         self.direct_ranges: dict[str, tuple[int, int]] = {}
@@ -106,6 +120,8 @@ class FlatSpace:
         self.m = torch.zeros_like(self.master)
         self.v = torch.zeros_like(self.master)
         self._named = list(ordered)
+        import hashlib
+        self.layout_hash = hashlib.sha256(";".join(f"{sl.name}@{sl.offset}+{sl.numel}" for sl in self.slots.values()).encode()).hexdigest()[:16]
 
     # ---- binding --------------------------------------------------------------------------
     @torch.no_grad()
@@ -295,7 +311,7 @@ class ShardedDPOptimizer:
         n = sp.used
         sd = {"step": self.step_count, "phi": self.phi, "key_seed": str(self.key.seed),
               "master": sp.gather_full(sp.master)[:n].cpu(), "m": sp.gather_full(sp.m)[:n].cpu(),
-              "v": sp.gather_full(sp.v)[:n].cpu(), "used": n}
+              "v": sp.gather_full(sp.v)[:n].cpu(), "used": n, "layout": sp.layout_hash}
         if self.ftrl_state is not None:
             sd["ftrl_state"] = torch.stack([sp.gather_full(self.ftrl_state[b])[:n] for b in range(self.nbuf)]).cpu()
         return sd
@@ -306,6 +322,9 @@ class ShardedDPOptimizer:
         n = int(sd["used"]) if "used" in sd else min(int(sd["total"]), sp.used)   # older files stored the padded length
         if n != sp.used or ("used" not in sd and int(sd["total"]) < sp.used):
             raise ValueError(f"checkpoint was written for a different parameter layout ({n} flat elements, this model has {sp.used})")
+        if sd.get("layout") is not None and sd["layout"] != sp.layout_hash:
+            raise ValueError("checkpoint was written for a different order of the parameters in the flat space "
+                             f"(layout {sd['layout']}, this build lays them out as {sp.layout_hash})")
         lo, hi = sp.shard_lo, sp.shard_lo + sp.shard
         self.step_count, self.phi = int(sd["step"]), float(sd["phi"])
 

@@ -190,6 +190,13 @@ class LlamaMLP(nn.Module):
     def forward(self, x):
         gp, up_ = self.gate_proj, self.up_proj
         if gp.lora_A is None and up_.lora_A is None and gp.bias is None and up_.bias is None:
+            dp = self.down_proj
+            if dp.lora_A is None and dp.bias is None:
+                # frozen MLP: forward and backward as one function (the GLU backward rides in the down projection's
+                # data-gradient epilogue)
+                y = fused.glu_mlp(x, gp.weight, up_.weight, dp.weight, self.act)
+                if y is not None:
+                    return y
             # one GEMM launch for both projections with the gated activation in its epilogue
             h = fused.glu_up(x, gp.weight, up_.weight, self.act)
             if h is not None:

@@ -323,6 +323,32 @@ def gemm_glu(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *, act: 
     return h, g, u
 
 
+def gemm_glu_bwd(dy: torch.Tensor, w_down: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, *, act: str = "silu",
+                 status: StatusWord | None = None, wait_budget_s: float = DEFAULT_WAIT_BUDGET_S):
+    """Backward of ``y = (act(gate) * up) @ w_downᵀ`` up to the pre-activations, in ONE launch: ``(dgate, dup)``.
+
+    ``dy [M, d]``, ``w_down [d, I]`` as stored, ``gate`` / ``up [M, I]`` (the bf16 pre-activations :func:`gemm_glu` kept).
+    The product ``dH = dy @ w_down`` lives only in tensor memory: the epilogue rounds it to bf16 (what a stored ``dH``
+    would hold), multiplies with ``up * act'(gate)`` and ``act(gate)`` and stores the two gradients.  ``I % 64 == 0``.
+    """
+    _need_bf16(dy, w_down, gate, up)
+    if dy.ndim != 2 or dy.stride(1) != 1 or w_down.ndim != 2 or w_down.stride(1) != 1 or w_down.shape[0] != dy.shape[1]:
+        raise ValueError("gemm_glu_bwd: dy [M, d] and w_down [d, I] must be row-major")
+    M, K = dy.shape
+    inter = w_down.shape[1]
+    if gate.shape != (M, inter) or up.shape != (M, inter) or gate.stride(1) != 1 or up.stride(1) != 1 \
+            or gate.stride(0) != up.stride(0) or inter % 64:
+        raise ValueError("gemm_glu_bwd: gate / up must be [M, I] with equal pitch and I % 64 == 0")
+    dg = torch.empty(M, inter, dtype=torch.bfloat16, device=dy.device)
+    du = torch.empty_like(dg)
+    rc = lib.load().ob_gemm_pair_glu_bwd(dy.data_ptr(), w_down.data_ptr(), gate.data_ptr(), up.data_ptr(), dg.data_ptr(),
+                                         du.data_ptr(), M, inter, K, dy.stride(0), w_down.stride(0), gate.stride(0),
+                                         dg.stride(0), 1, _GLU_ACT[act], status.ptr() if status else None, wait_budget_s,
+                                         lib.sm_count(), lib.stream())
+    lib.check(rc, "gemm_glu_bwd")
+    return dg, du
+
+
 def gemm_glu_ref(a, w_gate, w_up, *, act="silu"):
     """fp32 oracle of :func:`gemm_glu` (returns ``h`` only)."""
     g, u = a.float() @ w_gate.float().t(), a.float() @ w_up.float().t()
@@ -592,7 +618,7 @@ from .functional import (activation, cross_entropy, cross_entropy_ref, fused_add
                          layer_norm, merge_heads3, plain_torch_ops, rms_norm, rms_norm_ref, rope_qk, rope_qk_ref, rope_tables, rows_group_sum_, swiglu)
 
 __all__ = [
-    "gemm", "gemm_pair", "gemm_glu", "pick_gemm_kernel", "die_map", "set_die_aware_tiles", "linear_ce_forward", "linear_ce_dlogits_", "gemm_glu_ref", "gemm_ref", "ghost_set_wide", "push_grad_", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_", "merge_heads3",
+    "gemm", "gemm_pair", "gemm_glu", "gemm_glu_bwd", "pick_gemm_kernel", "die_map", "set_die_aware_tiles", "linear_ce_forward", "linear_ce_dlogits_", "gemm_glu_ref", "gemm_ref", "ghost_set_wide", "push_grad_", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_", "merge_heads3",
     "DeviceWaitTimeout", "KernelLibraryError", "StatusWord", "clip_weighted_sum", "cross_entropy",
     "cross_entropy_ref", "embedding_wgrad", "fused_add_rms_norm", "geglu", "ghost_norm", "ghost_norm_ref", "glu_ref",
     "philox_normal_add_", "pick_block_n", "pick_splits", "rms_norm", "rms_norm_ref", "rope_qk", "rope_qk_ref",

@@ -39,6 +39,11 @@ int ob_gemm_pair(const void* a, const void* b, const void* b_up, const void* a2,
                  const void* bias, void* out, void* out_gate, void* out_up, long long rows_a, int N, int K1, int K2,
                  long long lda, long long ldb, long long lda2, long long ldb2, long long ldo, int b_kn, int b2_kn, int glu,
                  int glu_act, int* status, double wait_budget_s, int num_sms, void* stream);
+// Data gradient of a gated MLP's down projection with the activation's backward in the epilogue: dH = dY op(W) stays in
+// tensor memory; dGate = dH * up * act'(gate) and dUp = dH * act(gate) are stored (bf16 [M, N], pitch ld_out).  N % 64 == 0.
+int ob_gemm_pair_glu_bwd(const void* dy, const void* w, const void* gate, const void* up, void* dgate, void* dup,
+                         long long rows_a, int N, int K, long long lddy, long long ldw, long long ld_gu, long long ld_out,
+                         int b_kn, int glu_act, int* status, double wait_budget_s, int num_sms, void* stream);
 // Same product (store epilogue only) on 256 x 256 pair tiles with double-buffered accumulators: the variant for short K.
 int ob_gemm_pair_db(const void* a, const void* b, const void* a2, const void* b2, const void* bias, void* out,
                     long long rows_a, int N, int K1, int K2, long long lda, long long ldb, long long lda2, long long ldb2,

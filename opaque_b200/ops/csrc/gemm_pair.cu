@@ -61,7 +61,7 @@ constexpr int GP_GROUP_M = 8;        // pair tiles (512 rows each) per raster ba
 constexpr int GP_SLAB_BYTES = 4096;   // per epilogue warp: a 32-row x 64-column (or 2 x 32-column) bf16 staging tile
 constexpr int GP_SMEM = GP_STAGES * GP_STAGE_BYTES + 8 * GP_SLAB_BYTES + 256 + 1024;
 
-enum : int { GP_EPI_STORE = 0, GP_EPI_GLU = 1, GP_EPI_CE = 2 };
+enum : int { GP_EPI_STORE = 0, GP_EPI_GLU = 1, GP_EPI_CE = 2, GP_EPI_GLUBWD = 3 };
 
 struct PairParams {
   int M, N, K1, K2;
@@ -80,6 +80,11 @@ struct PairParams {
   int* status;
   unsigned long long wait_budget_ns;
   int tma_store;                     // STORE: the output leaves through bulk tensor stores (map_out is valid)
+  // GLU-backward epilogue (data gradient of a gated MLP's down projection): the accumulator is dH; with the stored
+  // pre-activations it becomes dGate (-> out) and dUp (-> out_up) without dH ever reaching memory
+  const __nv_bfloat16* glu_g;        // [M, N] gate pre-activations, pitch ld_gu
+  const __nv_bfloat16* glu_u;        // [M, N] up pre-activations
+  long long ld_gu;
   // Die-aware tile assignment (see gp_schedule); claim == nullptr: cluster c simply takes tiles c, c + clusters, ...
   unsigned long long* claim;         // this launch's claim word (zero on entry, zero again after the last claim)
   int n_front;                       // clusters expected on die 0: slots [0, n_front) walk tiles [0, split)
@@ -247,6 +252,52 @@ __device__ __forceinline__ float gp_act(float g) {
   if constexpr (ACT == 1) return 0.5f * g * (1.0f + erff(g * 0.70710678118654752f));
   const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
   return 0.5f * g * (1.0f + t);
+}
+
+// Value and derivative of the gate activation (compile-time choice, see gp_act).
+template <int ACT>
+__device__ __forceinline__ void gp_act_grad(float g, float& a, float& da) {
+  if constexpr (ACT == 0) {
+    const float sg = 1.0f / (1.0f + __expf(-g));
+    a = g * sg;
+    da = sg * (1.0f + g * (1.0f - sg));
+  } else if constexpr (ACT == 1) {
+    const float cdf = 0.5f * (1.0f + erff(g * 0.70710678118654752f));
+    a = g * cdf;
+    da = cdf + g * 0.3989422804014327f * __expf(-0.5f * g * g);
+  } else {
+    const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+    a = 0.5f * g * (1.0f + t);
+    da = 0.5f * (1.0f + t) + 0.5f * g * (1.0f - t * t) * 0.7978845608028654f * (1.0f + 0.134145f * g * g);
+  }
+}
+
+// 64 columns of one row: packed bf16 dH (pd) and the row's gate / up pre-activations (16-byte loads) -> packed
+// dGate = dH * up * act'(gate) and dUp = dH * act(gate).  dH enters bf16-rounded, as it would from memory.
+template <int ACT>
+__device__ __forceinline__ void gp_glu_bwd64(const uint32_t* pd, const __nv_bfloat16* grow, const __nv_bfloat16* urow,
+                                             bool in_row, uint32_t* og, uint32_t* ou) {
+#pragma unroll
+  for (int s8 = 0; s8 < 8; ++s8) {
+    uint4 g4 = make_uint4(0u, 0u, 0u, 0u), u4 = g4;
+    if (in_row) {
+      g4 = __ldg(reinterpret_cast<const uint4*>(grow) + s8);
+      u4 = __ldg(reinterpret_cast<const uint4*>(urow) + s8);
+    }
+    const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t d2 = pd[4 * s8 + j];
+      const float dx = __uint_as_float(d2 << 16), dy = __uint_as_float(d2 & 0xffff0000u);
+      const float gx = __uint_as_float(gw[j] << 16), gy = __uint_as_float(gw[j] & 0xffff0000u);
+      const float ux = __uint_as_float(uw[j] << 16), uy = __uint_as_float(uw[j] & 0xffff0000u);
+      float ax, dax, ay, day;
+      gp_act_grad<ACT>(gx, ax, dax);
+      gp_act_grad<ACT>(gy, ay, day);
+      og[4 * s8 + j] = pack_bf16x2(dx * ux * dax, dy * uy * day);
+      ou[4 * s8 + j] = pack_bf16x2(dx * ax, dy * ay);
+    }
+  }
 }
 
 // pkg[j] <- bf16x2(act(g) * u) from packed bf16 pairs of g and u (32 registers = 64 values per lane)
@@ -524,7 +575,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     bool ok = true;
     const bool vec_ok = ((p.ldo & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                         (EPI != GP_EPI_GLU || p.out_gate == nullptr ||
-                         (((reinterpret_cast<uintptr_t>(p.out_gate) | reinterpret_cast<uintptr_t>(p.out_up)) & 15) == 0));
+                         (((reinterpret_cast<uintptr_t>(p.out_gate) | reinterpret_cast<uintptr_t>(p.out_up)) & 15) == 0)) &&
+                        (EPI != GP_EPI_GLUBWD || (reinterpret_cast<uintptr_t>(p.out_up) & 15) == 0);
     for (int w = sc.first; ok && w < sc.end; w += sc.stride) {
       const GpItem it = gp_decode(w, tiles_m, tiles_n, rank, p.group_m);
       auto release_half = [&](int hh) {          // this warp is done READING accumulator half hh
@@ -651,6 +703,42 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
           if (row < p.M)
             p.ce_partials[static_cast<long long>(row) * (2 * tiles_n) + 2 * it.nt + g] = make_float4(m, ssum, zlab, ztot);
+        } else if constexpr (EPI == GP_EPI_GLUBWD) {
+          // Data gradient of the down projection with the gated activation's backward in the epilogue: the tile is dH;
+          // it is read, rounded to bf16 and packed, the accumulator half goes back, and the row's gate / up
+          // pre-activations turn it into dGate and dUp tiles, which leave through the slab.  N % 64 == 0 (host-checked).
+          const int n0 = it.nt * GP_BN + g * (GP_BN / 2);
+          const int row0w = row - lane;
+          uint32_t pd[2][32];
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int nc = n0 + c * 64;
+            if (nc < p.N) {
+              float v[64];
+              tmem_ld32(t_row + g * (GP_BN / 2) + c * 64, v);
+              tmem_ld32(t_row + g * (GP_BN / 2) + c * 64 + 32, v + 32);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) pd[c][j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+            }
+          }
+          release_half(h);
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int nc = n0 + c * 64;
+            if (nc < p.N) {
+              const bool in_row = row < p.M;
+              const __nv_bfloat16* grow = p.glu_g + static_cast<long long>(row) * p.ld_gu + nc;
+              const __nv_bfloat16* urow = p.glu_u + static_cast<long long>(row) * p.ld_gu + nc;
+              uint32_t og[32], ou[32];
+              if (p.act == 0) gp_glu_bwd64<0>(pd[c], grow, urow, in_row, og, ou);
+              else if (p.act == 1) gp_glu_bwd64<1>(pd[c], grow, urow, in_row, og, ou);
+              else gp_glu_bwd64<2>(pd[c], grow, urow, in_row, og, ou);
+              const bool tma = p.tma_store != 0;
+              store_tile64_packed(slab, og, &map_out, tma, nc, row0w, p.out, p.ldo, p.M - row0w, p.N - nc, vec_ok, lane);
+              store_tile64_packed(slab, ou, &map_out_up, tma, nc, row0w, p.out_up, p.ldo, p.M - row0w, p.N - nc, vec_ok, lane);
+            }
+          }
         } else {
           // GLU: this warp's 64 columns of h come from 64 gate and 64 up columns of the same rows.  Everything is read
           // and packed first (four rounds of 16 + 16 columns), the accumulator half is released, then up to three
@@ -1254,6 +1342,57 @@ extern "C" int ob_gemm_pair(const void* a, const void* b, const void* b_up, cons
     gemm_pair_kernel<GP_EPI_GLU><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mbu, ma2, mb2, mb2u, mo, mog, mou, p);
   else
     gemm_pair_kernel<GP_EPI_STORE><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mbu, ma2, mb2, mb2u, mo, mog, mou, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -55;
+}
+
+// Data gradient of a gated MLP's down projection fused with the activation's backward:
+//   dH = dY[M, K] * op(W)  (W stored [K, N] with b_kn = 1: the down-projection weight as stored),  N = intermediate size,
+//   dGate = dH * up * act'(gate),  dUp = dH * act(gate)   (bf16 [M, N], pitch ld_out);  dH never reaches memory.
+// gate / up: the stored pre-activations [M, N] (pitch ld_gu).  N % 64 == 0; all rows 16-byte aligned.
+extern "C" int ob_gemm_pair_glu_bwd(const void* dy, const void* w, const void* gate, const void* up, void* dgate, void* dup,
+                                    long long rows_a, int N, int K, long long lddy, long long ldw, long long ld_gu,
+                                    long long ld_out, int b_kn, int glu_act, int* status, double wait_budget_s,
+                                    int num_sms, void* stream) {
+  using namespace ob;
+  if (rows_a <= 0 || N <= 0 || K <= 0) return 0;
+  if (rows_a > 0x7fffffffLL - 2 * GP_BM) return -50;
+  if (gate == nullptr || up == nullptr || dgate == nullptr || dup == nullptr) return -57;
+  auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if ((N & 63) != 0 || (ld_gu & 7) != 0 || (ld_out & 7) != 0 || !al(gate) || !al(up) || !al(dgate) || !al(dup)) return -58;
+  CUtensorMap ma, mb;
+  int rc = make_bf16_map_2d(&ma, dy, rows_a, K, lddy, GP_BK, GP_BM);
+  if (rc) return rc;
+  rc = b_kn ? make_bf16_map_2d(&mb, w, K, N, ldw, 64, GP_BK) : make_bf16_map_2d(&mb, w, N, K, ldw, GP_BK, GP_BNH);
+  if (rc) return rc;
+  static bool configured = false;
+  static int clusters_gb = 0;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_pair_kernel<GP_EPI_GLUBWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, GP_SMEM) != cudaSuccess)
+      return -54;
+    clusters_gb = pair_grid(reinterpret_cast<const void*>(gemm_pair_kernel<GP_EPI_GLUBWD>), num_sms);
+    configured = true;
+  }
+  PairParams p = {};
+  p.group_m = pair_group_m();
+  p.M = static_cast<int>(rows_a);
+  p.N = N; p.K1 = K; p.K2 = 0;
+  p.kn1 = b_kn; p.kn2 = 0;
+  p.out = static_cast<__nv_bfloat16*>(dgate);
+  p.out_up = static_cast<__nv_bfloat16*>(dup);
+  p.ldo = ld_out;
+  p.glu_g = static_cast<const __nv_bfloat16*>(gate);
+  p.glu_u = static_cast<const __nv_bfloat16*>(up);
+  p.ld_gu = ld_gu;
+  p.act = glu_act;
+  p.status = status;
+  p.wait_budget_ns = static_cast<unsigned long long>(wait_budget_s * 1e9);
+  const long long total = ((rows_a + 2 * GP_BM - 1) / (2 * GP_BM)) * ((N + GP_BN - 1) / GP_BN);
+  const int clusters = static_cast<int>(total < clusters_gb ? total : clusters_gb);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  pair_set_schedule(&p, total, clusters, st);
+  CUtensorMap mog = ma, mou = ma;
+  p.tma_store = (pair_out_map(&mog, dgate, rows_a, N, ld_out) && pair_out_map(&mou, dup, rows_a, N, ld_out)) ? 1 : 0;
+  gemm_pair_kernel<GP_EPI_GLUBWD><<<2 * clusters, GP_THREADS, GP_SMEM, st>>>(ma, mb, mb, ma, mb, mb, mog, ma, mou, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -55;
 }
 

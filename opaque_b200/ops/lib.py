@@ -25,6 +25,7 @@ _SIGNATURES = {
     "ob_pair_init": [],
     "ob_pair_set_die_aware": [I],
     "ob_die_map": [P, I],
+    "ob_gemm_pair_glu_bwd": [P, P, P, P, P, P, LL, I, I, LL, LL, LL, LL, I, I, P, D, I, P],
     "ob_gemm_pair_db": [P, P, P, P, P, P, LL, I, I, I, LL, LL, LL, LL, LL, I, I, P, D, I, P],
     "ob_linear_ce_fwd": [P, P, P, P, P, P, P, LL, I, I, LL, LL, LL, F, F, LL, P, D, I, P],
     "ob_linear_ce_dlogits": [P, P, P, P, LL, I, LL, F, F, LL, P],

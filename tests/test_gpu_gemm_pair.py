@@ -80,6 +80,46 @@ def test_pair_gemm_glu_epilogue(dev, M, I, K, act):
     assert g2 is None and u2 is None and rel(h2, ops.gemm_glu_ref(a, wg, wu, act=act)) < 6e-3
 
 
+@pytest.mark.parametrize("M,I,K,act", [(256, 128, 64, "silu"), (300, 320, 200, "silu"), (2048, 1408, 2048, "silu"),
+                                       (512, 256, 128, "gelu_pytorch_tanh"), (512, 256, 128, "gelu")])
+def test_down_projection_data_gradient_with_glu_backward_epilogue(dev, M, I, K, act):
+    """dH = dY W_down stays in tensor memory; the epilogue's (dGate, dUp) equal the element-wise backward applied to the
+    bf16-rounded dH, and the whole frozen-MLP function matches autograd through the separate operations."""
+    from opaque_b200 import ops
+    from opaque_b200.engine import fused
+    torch.manual_seed(M + I + K)
+    st = ops.StatusWord(dev)
+    dy = torch.randn(M, K, device=dev).bfloat16()
+    wd = (torch.randn(K, I, device=dev) / math.sqrt(K)).bfloat16()           # down projection as stored: [d, I]
+    g = torch.randn(M, I, device=dev).bfloat16()
+    u = torch.randn(M, I, device=dev).bfloat16()
+    dg, du = ops.gemm_glu_bwd(dy, wd, g, u, act=act, status=st)
+    assert st.read() == 0
+    dh = (dy.float() @ wd.float()).bfloat16().float()
+    gf = g.float().requires_grad_(True)
+    a = torch.nn.functional.silu(gf) if act == "silu" else torch.nn.functional.gelu(gf, approximate="tanh" if "tanh" in act else "none")
+    (a * u.float()).backward(dh)
+    assert rel(dg, gf.grad) < 6e-3 and rel(du, dh * a.detach()) < 6e-3
+    if act != "silu" or I % 64:
+        return
+    # the frozen MLP as one function against the composed path
+    x = torch.randn(M, K, device=dev).bfloat16().requires_grad_(True)
+    wg = (torch.randn(I, K, device=dev) / math.sqrt(K)).bfloat16()
+    wu = (torch.randn(I, K, device=dev) / math.sqrt(K)).bfloat16()
+    old, fused.FUSE_GLU_MLP = fused.FUSE_GLU_MLP, True          # the fused form is an option (off by default)
+    try:
+        y = fused.glu_mlp(x, wg, wu, wd, "silu")
+    finally:
+        fused.FUSE_GLU_MLP = old
+    assert y is not None
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr = x.detach().float().requires_grad_(True)
+    yr = (torch.nn.functional.silu(xr @ wg.float().t()) * (xr @ wu.float().t())) @ wd.float().t()
+    yr.backward(gy.float())
+    assert rel(y, yr) < 1e-2 and rel(x.grad, xr.grad) < 2e-2
+
+
 def test_instruction_descriptor_bitfields():
     """kind::f16 instruction descriptor: D format [4,6), A / B format [7,10) / [10,13), majors 15 / 16, N>>3 [17,23), M>>4 [24,29)."""
     from opaque_b200.ops import lib

@@ -174,6 +174,21 @@ class _Experts(Function):
         return dx, None, dtopk.to(wrow.dtype), gw1.to(w1.dtype), gw2.to(w2.dtype), None, None
 
 
+class _GroupedFrozenLinear(Function):
+    """``rows of group e @ w[e]ᵀ`` for frozen expert weights ``w [E, N, K]``: two grouped-GEMM launches, forward and data
+    gradient (against the weight as stored); no weight gradient."""
+
+    @staticmethod
+    def forward(ctx, a, w, offs):
+        ctx.save_for_backward(w, offs)
+        return grouped_linear(a, w, offs)
+
+    @staticmethod
+    def backward(ctx, dy):
+        w, offs = ctx.saved_tensors
+        return grouped_linear(dy.contiguous(), w, offs, transposed=True), None, None
+
+
 class MoEExperts(nn.Module):
     def __init__(self, cfg: MoEConfig, dtype, device):
         super().__init__()
@@ -190,11 +205,43 @@ class MoEExperts(nn.Module):
             raise ValueError(f"unknown expert_act {self.act!r}")
 
     def forward(self, x2d, topk_idx, topk_w, batch, tokens):
-        # biased / clamped experts exist only in the dense form (every expert for every token): correct on both engines
-        # while the experts are frozen (LoRA on attention); the fused engine refuses to TRAIN them (they bypass its layers)
-        if not ops.functional.kernels_enabled() or self.gate_up_bias is not None or self.act != "swiglu":
-            return self._dense(x2d, topk_idx, topk_w)
-        return _Experts.apply(x2d, topk_idx, topk_w, self.gate_up_proj, self.down_proj, batch, tokens)
+        if ops.functional.kernels_enabled() and self.gate_up_bias is None and self.act == "swiglu":
+            return _Experts.apply(x2d, topk_idx, topk_w, self.gate_up_proj, self.down_proj, batch, tokens)
+        # biased / clamped experts (GPT-OSS): while they are FROZEN (LoRA on attention) tokens are sorted by expert and the
+        # two projections are launches of the grouped GEMM, with the bias rows and the clamped activation as element-wise
+        # steps in between; to TRAIN them only the dense form exists (every expert for every token), which the fused
+        # engine refuses (they bypass its layers) and the reference engine maps over examples
+        if ops.functional.kernels_enabled() and x2d.is_cuda and x2d.dtype == torch.bfloat16 and self._frozen() \
+                and self.gate_up_proj.shape[2] % 64 == 0 and self.down_proj.shape[2] % 64 == 0 and self.gate_up_proj.shape[0] <= 256:
+            return self._sorted_frozen(x2d, topk_idx, topk_w, batch, tokens)
+        return self._dense(x2d, topk_idx, topk_w)
+
+    def _frozen(self) -> bool:
+        ps = (self.gate_up_proj, self.down_proj, self.gate_up_bias, self.down_bias)
+        return not any(p is not None and p.requires_grad for p in ps)
+
+    def _sorted_frozen(self, x2d, topk_idx, topk_w, batch, tokens):
+        """Frozen experts with bias rows and / or the GPT-OSS activation on the grouped GEMM (``k / E`` of the dense form's
+        arithmetic).  Gradients flow to the tokens and the routing weights; the expert parameters get none."""
+        E, two_i, _ = self.gate_up_proj.shape
+        I = two_i // 2
+        token_sorted, slot_sorted, offs, _ = route_sort(topk_idx, E, batch, tokens)
+        rows = token_sorted.shape[0]
+        expert_of_row = torch.searchsorted(offs.to(torch.int64), torch.arange(rows, device=x2d.device), right=True).clamp_(max=E - 1)
+        xs = x2d.index_select(0, token_sorted)
+        h = _GroupedFrozenLinear.apply(xs, self.gate_up_proj, offs)
+        if self.gate_up_bias is not None:
+            h = h + self.gate_up_bias.index_select(0, expert_of_row)
+        if self.act == "gpt_oss":
+            gate, up = h[:, :I].float().clamp(max=7.0), h[:, I:].float().clamp(min=-7.0, max=7.0)
+            act = ((up + 1.0) * gate * torch.sigmoid(1.702 * gate)).to(h.dtype)
+        else:
+            act = ops.swiglu(h[:, :I], h[:, I:])
+        y = _GroupedFrozenLinear.apply(act.contiguous(), self.down_proj, offs)
+        if self.down_bias is not None:
+            y = y + self.down_bias.index_select(0, expert_of_row)
+        wrow = topk_w.reshape(-1).index_select(0, slot_sorted).to(y.dtype)
+        return torch.zeros_like(x2d).index_add(0, token_sorted, y * wrow[:, None])
 
     def _dense(self, x2d, topk_idx, topk_w):
         """Plain-PyTorch form for ``plain_torch_ops()`` (the reference engine maps it over examples with ``vmap``, which

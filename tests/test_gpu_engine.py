@@ -262,3 +262,42 @@ def test_trainable_parameter_outside_the_dp_layers_is_refused():
     ids = torch.randint(0, 256, (4, 64), device=dev)
     with pytest.raises(RuntimeError, match="stray_scale"):
         eng.accumulate(m.per_example_loss, {"input_ids": ids, "labels": shift_labels(ids, 1.0)})
+
+
+@pytest.mark.parametrize("act,bias", [("gpt_oss", True), ("swiglu", True)])
+def test_frozen_biased_experts_run_on_the_grouped_gemm_and_match_the_dense_form(act, bias):
+    """GPT-OSS style experts (bias rows, clamped activation) that are frozen take the sorted grouped-GEMM path; outputs
+    and the gradients reaching tokens and routing weights equal the dense every-expert-for-every-token form."""
+    from opaque_b200.models.moe import MoEConfig, MoEExperts
+    from opaque_b200.ops import lib
+    torch.manual_seed(3)
+    cfg = MoEConfig(vocab_size=64, hidden_size=128, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=4,
+                    num_experts=6, moe_intermediate_size=64, num_shared_experts=0, num_experts_per_tok=2,
+                    max_position_embeddings=64, expert_act=act, expert_bias=bias)
+    ex = MoEExperts(cfg, torch.bfloat16, "cuda")
+    with torch.no_grad():
+        if bias:
+            ex.gate_up_bias.normal_(0, 0.5)
+            ex.down_bias.normal_(0, 0.5)
+        ex.gate_up_proj.normal_(0, 0.1)
+        ex.down_proj.normal_(0, 0.1)
+    for p_ in ex.parameters():
+        p_.requires_grad_(False)
+    T = 96
+    x = torch.randn(T, 128, device="cuda").bfloat16()
+    idx = torch.stack([torch.randperm(6, device="cuda")[:2] for _ in range(T)])
+    w = torch.rand(T, 2, device="cuda").bfloat16()
+    gy = torch.randn(T, 128, device="cuda").bfloat16()
+
+    def run(fn):
+        xx, ww = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        y = fn(xx, ww)
+        y.backward(gy)
+        return y.detach().float(), xx.grad.float(), ww.grad.float()
+
+    before = lib.LAUNCHES
+    got = run(lambda xx, ww: ex(xx, idx, ww, 2, T // 2))
+    assert lib.LAUNCHES > before, "the grouped path did not run"
+    want = run(lambda xx, ww: ex._dense(xx, idx, ww))
+    rel = lambda a, b: float((a - b).norm() / (b.norm() + 1e-30))
+    assert rel(got[0], want[0]) < 2e-2 and rel(got[1], want[1]) < 3e-2 and rel(got[2], want[2]) < 3e-2

@@ -100,7 +100,13 @@ class Capture:
 
     def add_linear(self, weight: torch.nn.Parameter, x2d: torch.Tensor, g2d: torch.Tensor) -> None:
         slot = self.engine.slot_of(weight)
-        ops.ghost_norm(x2d, g2d, self._part(slot.name), self.tokens, status=self.status)
+        path = NORM_PATH if NORM_PATH != "auto" else ops.pick_norm_path(self.tokens, x2d.shape[1], g2d.shape[1])
+        if path == "direct" and self.tokens % 64 == 0 and x2d.shape[0] == self.batch_size * self.tokens \
+                and x2d.stride(1) == 1 and g2d.stride(1) == 1:
+            # long sequences on a small layer: the per-example product itself is cheaper than the two Gram matrices
+            ops.direct_norm2(x2d, g2d, self._part(slot.name), self.tokens, status=self.status)
+        else:
+            ops.ghost_norm(x2d, g2d, self._part(slot.name), self.tokens, status=self.status)
         self.records.append(("linear", slot, g2d, x2d))
 
     def add_embedding(self, weight: torch.nn.Parameter, ids: torch.Tensor, g2d: torch.Tensor) -> None:
@@ -286,6 +292,7 @@ class Capture:
 
 # ===================================================================================== layer functions
 
+NORM_PATH = "auto"     # per-example norms of weight matrices: "ghost", "direct", or "auto" (ops.pick_norm_path per layer)
 OWN_GEMM = True        # forward / data-gradient products of linear layers run on this library's tcgen05 GEMMs
 
 

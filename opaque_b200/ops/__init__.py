@@ -116,6 +116,44 @@ def wgrad_clip(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, ro
     lib.check(rc, "wgrad_clip")
 
 
+def direct_norm2(a: torch.Tensor, g: torch.Tensor, norm2: torch.Tensor, rows_per_example: int, *, splits: int | None = None,
+                 status: StatusWord | None = None, wait_budget_s: float = DEFAULT_WAIT_BUDGET_S) -> torch.Tensor:
+    """``norm2[e] += ‖a_eᵀ g_e‖²_F`` for example e = rows ``[e·R, (e+1)·R)`` of ``a [T, d_in]`` and ``g [T, d_out]``.
+
+    The direct form of a per-example gradient norm: the per-example products pass through tensor memory tile by tile
+    (the clip-weighted weight-gradient kernel with a different epilogue) and only their squares are summed.
+    ``2·R·d_in·d_out`` FLOPs per example against ``R²·(d_in + d_out)`` for :func:`ghost_norm`; see
+    :func:`pick_norm_path`.  ``R % 64 == 0``.
+    """
+    _need_bf16(a, g)
+    T, M = a.shape
+    N = g.shape[1]
+    if g.shape[0] != T or a.stride(1) != 1 or g.stride(1) != 1:
+        raise ValueError("a [T, d_in] and g [T, d_out] must be row-major with the same number of rows")
+    if rows_per_example <= 0 or rows_per_example % 64 or T % rows_per_example:
+        raise ValueError("rows_per_example must be a multiple of 64 that divides the number of rows")
+    B = T // rows_per_example
+    if norm2.dtype != torch.float32 or norm2.numel() < B or not norm2.is_contiguous():
+        raise ValueError("norm2 must hold one contiguous fp32 value per example")
+    sms = lib.sm_count()
+    if splits is None:
+        tiles = math.ceil(M / 128) * math.ceil(N / 256)
+        splits = pick_splits(tiles, T, sms, max_splits=B)
+    rc = lib.load().ob_direct_norm2(a.data_ptr(), g.data_ptr(), B, rows_per_example, M, N, a.stride(0), g.stride(0), splits,
+                                    norm2.data_ptr(), status.ptr() if status else None, wait_budget_s, sms, lib.stream())
+    lib.check(rc, "direct_norm2")
+    return norm2
+
+
+def pick_norm_path(rows_per_example: int, d_in: int, d_out: int) -> str:
+    """``"ghost"`` (Gram matrices, ``R²·(d_in + d_out)`` FLOPs on the upper triangle) or ``"direct"`` (the per-example
+    product itself, ``2·R·d_in·d_out``) for one layer.  The Gram kernel runs at about 0.7 of the product kernel's rate, so
+    the direct form wins once ``R > 1.4·d_in·d_out / (d_in + d_out)``; it needs ``R % 64 == 0``."""
+    if rows_per_example % 64:
+        return "ghost"
+    return "direct" if rows_per_example * (d_in + d_out) > 1.4 * d_in * d_out else "ghost"
+
+
 def wgrad_clip_per_example(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, ex_scale: torch.Tensor | None,
                            rows_per_example: int, out_offset: int = 0, ldm: int | None = None, accumulate: bool = True,
                            splits: int | None = None, peer_table: torch.Tensor | None = None, shard_elems: int = 0,
@@ -618,7 +656,7 @@ from .functional import (activation, cross_entropy, cross_entropy_ref, fused_add
                          layer_norm, merge_heads3, plain_torch_ops, rms_norm, rms_norm_ref, rope_qk, rope_qk_ref, rope_tables, rows_group_sum_, swiglu)
 
 __all__ = [
-    "gemm", "gemm_pair", "gemm_glu", "gemm_glu_bwd", "pick_gemm_kernel", "die_map", "set_die_aware_tiles", "linear_ce_forward", "linear_ce_dlogits_", "gemm_glu_ref", "gemm_ref", "ghost_set_wide", "push_grad_", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_", "merge_heads3",
+    "gemm", "gemm_pair", "gemm_glu", "gemm_glu_bwd", "direct_norm2", "pick_norm_path", "pick_gemm_kernel", "die_map", "set_die_aware_tiles", "linear_ce_forward", "linear_ce_dlogits_", "gemm_glu_ref", "gemm_ref", "ghost_set_wide", "push_grad_", "wgrad_clip_per_example", "plain_torch_ops", "layer_norm", "activation", "rows_group_sum_", "merge_heads3",
     "DeviceWaitTimeout", "KernelLibraryError", "StatusWord", "clip_weighted_sum", "cross_entropy",
     "cross_entropy_ref", "embedding_wgrad", "fused_add_rms_norm", "geglu", "ghost_norm", "ghost_norm_ref", "glu_ref",
     "philox_normal_add_", "pick_block_n", "pick_splits", "rms_norm", "rms_norm_ref", "rope_qk", "rope_qk_ref",

@@ -18,6 +18,9 @@ int ob_wgrad_clip_pe(const void* a, const void* b, int num_examples, int ex_rows
                      long long ldb, const float* ex_scale, int splits, float* out, float* const* peer_out,
                      long long shard_elems, long long out_offset, long long ldm, int accumulate, int* status,
                      double wait_budget_s, int num_sms, void* stream);
+// Direct per-example gradient norms on the same kernel: norm2[e] += || a_e^T b_e ||_F^2 (nothing else is written).
+int ob_direct_norm2(const void* a, const void* b, int num_examples, int ex_rows, int M, int N, long long lda, long long ldb,
+                    int splits, float* norm2, int* status, double wait_budget_s, int num_sms, void* stream);
 
 int ob_ghost_norm(const void* a, const void* g, const int* ids, int B, int T, int Da, int Dg, long long lda,
                   long long ldg, float* norm2, const int* seg, const int* seg_out, long long total_rows, int* status,

@@ -401,6 +401,7 @@ struct WgradPeParams {
   long long out_offset;
   long long ldm;
   int accumulate;
+  float* norm2_out;                  // NORM kernel: [num_examples] squared Frobenius norms are added here; nothing else is written
   int* status;
   unsigned long long wait_budget_ns;
 };
@@ -411,6 +412,11 @@ __device__ __forceinline__ float* resolve_out_pe(const WgradPeParams& p, long lo
   return p.peer_out[owner] + (idx - owner * p.shard_elems);
 }
 
+// NORM = true: the direct form of a per-example gradient norm.  The same per-example products P_e = A_e^T G_e pass through
+// tensor memory tile by tile, but the epilogue only sums their squares into norm2_out[e]; nothing is scaled, accumulated or
+// stored.  Costs 2 T d_in d_out FLOPs per example against T^2 (d_in + d_out) for the Gram-matrix form, so it is the
+// cheaper one for long sequences on small layers.
+template <bool NORM>
 __global__ void __launch_bounds__(WP_THREADS, 1)
 wgrad_clip_pe_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const WgradPeParams p) {
@@ -564,8 +570,22 @@ wgrad_clip_pe_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           break;
         }
         tc_fence_after();
+        if constexpr (NORM) {
+          // rows / columns outside the matrices were zero-filled by the tensor maps, so no masking is needed
+          float ss = 0.f;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            float v[32];
+            tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * WP_BLOCK_N + half * 128 + ch * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) ss = fmaf(v[j], v[j], ss);
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          if (lane == 0) atomicAdd(p.norm2_out + e, ss);
+        } else if (c != 0.f) {
         // an example with factor 0 (non-finite norm, padding) is skipped, not multiplied: 0 * NaN would poison the sum
-        if (c != 0.f) {
 #pragma unroll
           for (int ch = 0; ch < 4; ++ch) {
             float v[32];
@@ -581,6 +601,7 @@ wgrad_clip_pe_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         ++acc_iter;
       }
       if (!ok) break;
+      if constexpr (NORM) continue;
       if (e1 <= e0 && p.accumulate) continue;
       const int m = m0 + q * 32 + lane;
       if (m < p.M) {
@@ -725,16 +746,16 @@ extern "C" int ob_wgrad_clip(const void* a, const void* b, int T, int M, int N, 
   return -1;
 }
 
-extern "C" int ob_wgrad_clip_pe(const void* a, const void* b, int num_examples, int ex_rows, int M, int N, long long lda,
-                                long long ldb, const float* ex_scale, int splits, float* out, float* const* peer_out,
-                                long long shard_elems, long long out_offset, long long ldm, int accumulate, int* status,
-                                double wait_budget_s, int num_sms, void* stream) {
+static int launch_wgrad_pe(const void* a, const void* b, int num_examples, int ex_rows, int M, int N, long long lda,
+                           long long ldb, const float* ex_scale, int splits, float* out, float* const* peer_out,
+                           long long shard_elems, long long out_offset, long long ldm, int accumulate, float* norm2_out,
+                           int* status, double wait_budget_s, int num_sms, void* stream) {
   using namespace ob;
   if (num_examples <= 0 || ex_rows <= 0 || M <= 0 || N <= 0) return 0;
   if (ex_rows % WG_BLOCK_K) return -3;
   if (splits < 1) splits = 1;
   if (splits > num_examples) splits = num_examples;
-  if (splits > 1 && !accumulate) return -4;          // split partial sums must be reduced into the destination
+  if (splits > 1 && !accumulate && norm2_out == nullptr) return -4;   // split partial sums must be reduced into the destination
   const long long T = static_cast<long long>(num_examples) * ex_rows;
   if (T > 0x7fffffffLL) return -5;
   CUtensorMap ma, mb;
@@ -744,7 +765,8 @@ extern "C" int ob_wgrad_clip_pe(const void* a, const void* b, int num_examples, 
   if (rc) return rc;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(wgrad_clip_pe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WP_SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(wgrad_clip_pe_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, WP_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(wgrad_clip_pe_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, WP_SMEM) != cudaSuccess)
       return -20;
     configured = true;
   }
@@ -759,13 +781,35 @@ extern "C" int ob_wgrad_clip_pe(const void* a, const void* b, int num_examples, 
   p.out_offset = out_offset;
   p.ldm = ldm;
   p.accumulate = accumulate;
+  p.norm2_out = norm2_out;
   p.status = status;
   p.wait_budget_ns = static_cast<unsigned long long>(wait_budget_s * 1e9);
   const long long tiles = static_cast<long long>((M + WG_BLOCK_M - 1) / WG_BLOCK_M) * ((N + WP_BLOCK_N - 1) / WP_BLOCK_N);
   const long long total = tiles * splits;
   const int grid = static_cast<int>(total < num_sms ? total : num_sms);
-  wgrad_clip_pe_kernel<<<grid, WP_THREADS, WP_SMEM, static_cast<cudaStream_t>(stream)>>>(ma, mb, p);
+  if (norm2_out != nullptr)
+    wgrad_clip_pe_kernel<true><<<grid, WP_THREADS, WP_SMEM, static_cast<cudaStream_t>(stream)>>>(ma, mb, p);
+  else
+    wgrad_clip_pe_kernel<false><<<grid, WP_THREADS, WP_SMEM, static_cast<cudaStream_t>(stream)>>>(ma, mb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int ob_wgrad_clip_pe(const void* a, const void* b, int num_examples, int ex_rows, int M, int N, long long lda,
+                                long long ldb, const float* ex_scale, int splits, float* out, float* const* peer_out,
+                                long long shard_elems, long long out_offset, long long ldm, int accumulate, int* status,
+                                double wait_budget_s, int num_sms, void* stream) {
+  return launch_wgrad_pe(a, b, num_examples, ex_rows, M, N, lda, ldb, ex_scale, splits, out, peer_out, shard_elems, out_offset,
+                         ldm, accumulate, nullptr, status, wait_budget_s, num_sms, stream);
+}
+
+// Direct per-example gradient norms: norm2[e] += || a_e^T b_e ||_F^2 for example e = rows [e * ex_rows, (e + 1) * ex_rows)
+// of a [T, M] and b [T, N] (ex_rows % 64 == 0).  `splits` spreads the examples of one tile over several CTAs.
+extern "C" int ob_direct_norm2(const void* a, const void* b, int num_examples, int ex_rows, int M, int N, long long lda,
+                               long long ldb, int splits, float* norm2, int* status, double wait_budget_s, int num_sms,
+                               void* stream) {
+  if (norm2 == nullptr) return -6;
+  return launch_wgrad_pe(a, b, num_examples, ex_rows, M, N, lda, ldb, nullptr, splits, nullptr, nullptr, 0, 0, N, 0, norm2, status,
+                         wait_budget_s, num_sms, stream);
 }
 
 extern "C" int ob_last_detail(char* buf, int len) {

@@ -19,6 +19,7 @@ P, I, LL, F, D, U, ULL = c_void_p, c_int, c_longlong, c_float, c_double, c_uint,
 _SIGNATURES = {
     "ob_wgrad_clip": [P, P, I, I, I, LL, LL, P, P, I, I, P, P, LL, P, LL, LL, LL, LL, I, I, I, P, D, I, P],
     "ob_wgrad_clip_pe": [P, P, I, I, I, I, LL, LL, P, I, P, P, LL, LL, LL, I, P, D, I, P],
+    "ob_direct_norm2": [P, P, I, I, I, I, LL, LL, I, P, P, D, I, P],
     "ob_ghost_norm": [P, P, P, I, I, I, I, LL, LL, P, P, P, LL, P, D, I, P],
     "ob_gemm_tn": [P, P, P, P, P, P, LL, I, I, I, LL, LL, LL, LL, LL, I, P, I, P, D, I, P],
     "ob_gemm_pair": [P, P, P, P, P, P, P, P, P, P, LL, I, I, I, LL, LL, LL, LL, LL, I, I, I, I, P, D, I, P],

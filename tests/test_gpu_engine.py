@@ -301,3 +301,29 @@ def test_frozen_biased_experts_run_on_the_grouped_gemm_and_match_the_dense_form(
     want = run(lambda xx, ww: ex._dense(xx, idx, ww))
     rel = lambda a, b: float((a - b).norm() / (b.norm() + 1e-30))
     assert rel(got[0], want[0]) < 2e-2 and rel(got[1], want[1]) < 3e-2 and rel(got[2], want[2]) < 3e-2
+
+
+def test_direct_norm_path_gives_the_same_clipped_step_as_the_ghost_path():
+    """Forcing every weight matrix through the direct norm kernel changes nothing but rounding: norms and the clipped
+    gradient sum equal the Gram-matrix path's."""
+    from opaque_b200.engine import fused
+    from opaque_b200.models import GPT2Config, GPT2LMHeadModel
+    from opaque_b200.random import key
+    results = {}
+    for path in ("ghost", "direct"):
+        torch.manual_seed(11)
+        cfg = GPT2Config(vocab_size=256, n_positions=128, n_embd=128, n_layer=2, n_head=4)
+        model = GPT2LMHeadModel(cfg, dtype=torch.bfloat16, device="cuda")
+        ids = torch.randint(0, 256, (4, 128), device="cuda")
+        old, fused.NORM_PATH = fused.NORM_PATH, path
+        try:
+            eng = fused.FusedDPEngine(model, clipping_norm=0.5, noise_multiplier=0.0, normalize_by=1.0, key=key(0), microbatch_size=4)
+            res = eng.accumulate(model.per_example_loss, {"input_ids": ids, "labels": ids})
+            torch.cuda.synchronize()
+            assert eng.status.read() == 0
+        finally:
+            fused.NORM_PATH = old
+        results[path] = (res.norms.float().cpu().clone(), eng.space.grad.local.float().cpu().clone())
+    (n_g, g_g), (n_d, g_d) = results["ghost"], results["direct"]
+    assert torch.allclose(n_g, n_d, rtol=5e-3)
+    assert float((g_g - g_d).norm() / (g_g.norm() + 1e-30)) < 1e-2

@@ -592,3 +592,26 @@ def test_fused_correlated_noise_equals_the_streaming_path_for_every_strategy(dev
         opt.step(noise_std=1.0, normalize_by=1.0, noisy_out=out, skip_update=True)
         worst = max(worst, float((out - want).abs().max()) / (float(want.abs().max()) + 1e-12))
     assert worst < 2e-4, worst
+
+
+@pytest.mark.parametrize("B,T,Da,Dg", [(3, 64, 96, 200), (2, 4096, 128, 256), (5, 256, 768, 768), (4, 512, 136, 72)])
+def test_direct_per_example_norms_match_the_products(dev, B, T, Da, Dg):
+    """``‖A_eᵀ G_e‖²`` from the product kernel's norm epilogue against fp32 products, and against the Gram-matrix kernel."""
+    from opaque_b200 import ops
+    torch.manual_seed(B * T + Da)
+    a = torch.randn(B * T, Da, device=dev).bfloat16()
+    g = (torch.randn(B * T, Dg, device=dev) / math.sqrt(T)).bfloat16()
+    st = ops.StatusWord(dev)
+    n2 = torch.full((B,), 0.5, device=dev)                     # the kernel ADDS
+    ops.direct_norm2(a, g, n2, T, status=st)
+    want = torch.stack([(a[e * T:(e + 1) * T].float().t() @ g[e * T:(e + 1) * T].float()).square().sum() for e in range(B)])
+    assert st.read() == 0 and rel(n2 - 0.5, want) < 2e-3
+    ghost = torch.zeros(B, device=dev)
+    ops.ghost_norm(a, g, ghost, T, status=st)
+    assert rel(ghost, want) < 2e-3
+    for splits in (1, B):
+        n3 = torch.zeros(B, device=dev)
+        ops.direct_norm2(a, g, n3, T, splits=splits, status=st)
+        assert rel(n3, want) < 2e-3
+    assert ops.pick_norm_path(4096, 128, 256) == "direct" and ops.pick_norm_path(512, 4096, 4096) == "ghost"
+    assert ops.pick_norm_path(4100, 128, 256) == "ghost"       # not a multiple of 64 rows

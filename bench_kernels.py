@@ -6,6 +6,10 @@
   python bench_kernels.py --impl reference     # the reference's own Triton / library kernels on the same shapes
                                                # (unmodified code from baseline/_ref; nothing of this package is loaded)
   python bench_kernels.py --case compare       # this package's kernels on exactly those shapes
+  python bench_kernels.py --case sustained     # seconds-long power-capped loops: pair GEMM / GLU against the library, with clocks
+  python bench_kernels.py --case short-k       # GPT-2-sized products, graph-timed over rotating buffers
+  python bench_kernels.py --case head          # output head: fused head + cross-entropy against plain GEMMs
+  python bench_kernels.py --case pair-small    # one launch per GEMM kernel on a small case (for counter captures)
 
 Each line is JSON: achieved TFLOP/s or GB/s and the fraction "of measured" peak, where the peaks come from
 MEASURED_PEAKS.json next to this file (cuBLAS bf16 burst and a STREAM-style copy), else the documented fallback
@@ -281,6 +285,154 @@ def pair_small_case():
     print(json.dumps({"case": "pair-small", "max_abs_diff_vs_library": err}))
 
 
+def _graph_time(fns, launches=16, reps=7):
+    """ms per launch of ``launches`` back-to-back calls (cycling through ``fns``) captured in ONE CUDA graph: neither host
+    launch latency nor a warm L2 enters when the functions work on rotating buffers larger than L2 in total."""
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            for i in range(launches):
+                fns[i % len(fns)]()
+    ts = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b) / launches)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def short_k_case():
+    """GPT-2-sized products (K = 768 / N = 768) and two Llama-sized ones: single-CTA / pair 256x256 / pair 512x256 / library,
+    forward form (x W^T + bias) and data-gradient form (dY W), graph-timed over four rotating buffer sets."""
+    from opaque_b200 import ops
+    dev = torch.device("cuda", 0)
+    st = ops.StatusWord(dev)
+    nset = 4
+    for M, N, K in [(16384, 2304, 768), (16384, 768, 768), (16384, 3072, 768), (16384, 768, 3072), (16384, 4096, 4096),
+                    (8192, 4096, 4096)]:
+        xs = [torch.randn(M, K, device=dev).bfloat16() for _ in range(nset)]
+        outs = [torch.empty(M, N, device=dev, dtype=torch.bfloat16) for _ in range(nset)]
+        w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+        b = torch.randn(N, device=dev).bfloat16()
+        wk = w.t().contiguous()
+        row = {"case": "short-k", "shape": [M, N, K]}
+        mk = lambda f: [(lambda i=i: f(i)) for i in range(nset)]
+        row["single_nk_bias"] = _graph_time(mk(lambda i: ops.gemm(xs[i], w, bias=b, out=outs[i], status=st, kernel="single")))
+        row["pair256_nk_bias"] = _graph_time(mk(lambda i: ops.gemm_pair(xs[i], w, bias=b, out=outs[i], status=st, tile="256x256")))
+        row["pair512_nk_bias"] = _graph_time(mk(lambda i: ops.gemm_pair(xs[i], w, bias=b, out=outs[i], status=st)))
+        row["library_nk_bias"] = _graph_time(mk(lambda i: torch.addmm(b, xs[i], w.t(), out=outs[i])))
+        row["single_kn"] = _graph_time(mk(lambda i: ops.gemm(xs[i], wk, b_layout="kn", out=outs[i], status=st, kernel="single")))
+        row["pair256_kn"] = _graph_time(mk(lambda i: ops.gemm_pair(xs[i], wk, b_layout="kn", out=outs[i], status=st, tile="256x256")))
+        row["pair512_kn"] = _graph_time(mk(lambda i: ops.gemm_pair(xs[i], wk, b_layout="kn", out=outs[i], status=st)))
+        row["library_kn"] = _graph_time(mk(lambda i: torch.matmul(xs[i], wk, out=outs[i])))
+        row["auto_pick"] = ops.pick_gemm_kernel(M, N, K)
+        print(json.dumps({k: (round(v, 4) if isinstance(v, float) else v) for k, v in row.items()}), flush=True)
+    if st.read():
+        raise SystemExit(f"a device wait timed out (status {st.read()})")
+
+
+def head_case():
+    """Output head alone on 8192 rows: fused head + cross-entropy forward (logits stored / not stored), with the in-place
+    dlogits, against the plain pair GEMM that only stores the logits, and the library GEMM (back-to-back launches)."""
+    from opaque_b200 import ops
+    dev = torch.device("cuda", 0)
+    st = ops.StatusWord(dev)
+
+    def run(fn, n=8, w=2):
+        for _ in range(w):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+    for M, K, V in [(8192, 768, 50257), (8192, 4096, 128256)]:
+        h = torch.randn(M, K, device=dev).bfloat16()
+        w = (torch.randn(V, K, device=dev) * 0.02).bfloat16()
+        lab = torch.randint(0, V, (M,), device=dev)
+        buf = torch.empty(M, (V + 7) // 8 * 8, device=dev, dtype=torch.bfloat16)
+        rw = torch.ones(M, device=dev)
+
+        def fused():
+            nll, lse, lg = ops.linear_ce_forward(h, w, lab, store_logits=True, status=st)
+            ops.linear_ce_dlogits_(lg, lab, lse, rw)
+        row = {"case": "head", "shape": [M, K, V],
+               "fused_fwd_logits_stored": run(lambda: ops.linear_ce_forward(h, w, lab, store_logits=True, status=st)),
+               "fused_fwd_nothing_stored": run(lambda: ops.linear_ce_forward(h, w, lab, store_logits=False, status=st)),
+               "fused_fwd_plus_dlogits": run(fused),
+               "plain_pair_gemm": run(lambda: ops.gemm_pair(h, w, out=buf[:, :V], status=st))}
+        if V % 8 == 0:
+            row["library_gemm"] = run(lambda: torch.matmul(h, w.t(), out=buf[:, :V]))
+        print(json.dumps({k: (round(v, 4) if isinstance(v, float) else v) for k, v in row.items()}), flush=True)
+    if st.read():
+        raise SystemExit(f"a device wait timed out (status {st.read()})")
+
+
+def sustained_case(seconds: float = 2.5):
+    """Seconds-long back-to-back loops (the power-capped regime of a training step) with SM clock and power sampled by
+    nvidia-smi during each loop: pair GEMM, its variants, the gated up-projection, and the library on the same box."""
+    import statistics
+    import subprocess
+    import threading
+    import time
+    from opaque_b200 import ops
+    dev = torch.device("cuda", 0)
+    st = ops.StatusWord(dev)
+
+    def sample(fn):
+        for _ in range(20):
+            fn()
+        torch.cuda.synchronize()
+        rows = []
+        proc = subprocess.Popen(["nvidia-smi", "--query-gpu=clocks.sm,power.draw", "--format=csv,noheader,nounits", "-i", "0",
+                                 "-lms", "100"], stdout=subprocess.PIPE, text=True)
+        t = threading.Thread(target=lambda: [rows.append(l) for l in proc.stdout], daemon=True)
+        t.start()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n, t0 = 0, time.time()
+        a.record()
+        while time.time() - t0 < seconds:
+            for _ in range(20):
+                fn()
+            n += 20
+            torch.cuda.synchronize()
+        b.record()
+        torch.cuda.synchronize()
+        proc.terminate()
+        vals = [r.split(",") for r in rows[3:] if r.strip()]
+        clk = statistics.median(float(v[0]) for v in vals) if vals else 0.0
+        pw = statistics.median(float(v[1]) for v in vals) if vals else 0.0
+        return a.elapsed_time(b) / n, clk, pw
+    for M, N, K in [(16384, 4096, 4096), (16384, 14336, 4096)]:
+        x = torch.randn(M, K, device=dev).bfloat16()
+        w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+        wk = w.t().contiguous()
+        fl = 2.0 * M * N * K
+        for name, fn in (("pair 512x256", lambda: ops.gemm_pair(x, w, status=st)), ("library", lambda: torch.matmul(x, w.t())),
+                         ("pair 256x256", lambda: ops.gemm_pair(x, w, status=st, tile="256x256")),
+                         ("single CTA", lambda: ops.gemm(x, w, status=st, kernel="single")),
+                         ("gate+up+SwiGLU fused", lambda: ops.gemm_glu(x, w[: N // 2], w[N // 2:], status=st)),
+                         ("two library GEMMs + SwiGLU kernel", lambda: ops.swiglu(torch.matmul(x, w[: N // 2].t()), torch.matmul(x, w[N // 2:].t()))),
+                         ("pair 512x256, [K,N] operand", lambda: ops.gemm_pair(x, wk, b_layout="kn", status=st)),
+                         ("library, [K,N] operand", lambda: torch.matmul(x, wk))):
+            ms, clk, pw = sample(fn)
+            print(json.dumps({"case": "sustained", "shape": [M, N, K], "kernel": name, "tflops": round(fl / ms / 1e9), "sm_mhz": clk,
+                              "watts": round(pw, 1), "tflops_per_ghz": round(fl / ms / 1e9 / (clk / 1000)) if clk else None}), flush=True)
+    if st.read():
+        raise SystemExit(f"a device wait timed out (status {st.read()})")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default="all")
@@ -294,6 +446,12 @@ def main():
         return compare_cases("ours")
     if args.case == "pair-small":
         return pair_small_case()
+    if args.case == "short-k":
+        return short_k_case()
+    if args.case == "head":
+        return head_case()
+    if args.case == "sustained":
+        return sustained_case()
     if args.case == "wgrad-rs":
         return fused_reduce_scatter_case()
     from opaque_b200 import ops

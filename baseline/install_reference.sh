@@ -4,9 +4,9 @@
 # pip into a scratch target and the namespace trees are merged (pip --target refuses to merge into an existing
 # `opaque/` directory).  opaque-accounting is a Rust/maturin build and is skipped: the benchmark arm passes the noise
 # multiplier directly and never calls the accountant.
-#   usage: baseline/install_reference.sh [/path/to/reference]
+#   usage: baseline/install_reference.sh /path/to/reference
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:?usage: baseline/install_reference.sh /path/to/reference (the checkout of the reference repository)}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
 DEST="$HERE/_ref"
 SCRATCH="$(mktemp -d)"

@@ -8,6 +8,6 @@ the B200 layers: ``ops`` (hand-written sm_100a kernels), ``parallel``
 (peer-memory reduce-scatter / all-gather and the sharded noise+optimizer step),
 ``engine`` (reference and fused DP gradient engines) and ``models``.
 """
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 
 from .serialization import _tensors as _tensor_serializers  # noqa: E402,F401  (registers tensor / array leaves)

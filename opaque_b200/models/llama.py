@@ -91,6 +91,28 @@ class LlamaConfig:
                            num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256)
 
 
+_FLASH = {"fn": False}
+
+
+def _flash_attn():
+    """``flash_attn.flash_attn_func`` if the library is installed (it handles score capping and sliding windows inside its
+    tiles), else ``None``; outside ``torch.func`` transforms only (it is an autograd function without batching rules)."""
+    if _FLASH["fn"] is False:
+        try:
+            from flash_attn import flash_attn_func
+            _FLASH["fn"] = flash_attn_func
+        except Exception:      # noqa: BLE001 — optional dependency
+            _FLASH["fn"] = None
+    if _FLASH["fn"] is None:
+        return None
+    try:
+        if torch._C._functorch.peek_interpreter_stack() is not None:
+            return None
+    except Exception:      # noqa: BLE001
+        pass
+    return _FLASH["fn"]
+
+
 class LlamaAttention(nn.Module):
     def __init__(self, cfg: LlamaConfig, dtype, device, layer_idx: int = 0):
         super().__init__()
@@ -139,6 +161,15 @@ class LlamaAttention(nn.Module):
                 q, k = ops.rope_qk(q, k, cos, sin, pos)
         if self.q_norm is not None and self.qk_after:
             q, k = self.q_norm(q), self.k_norm(k)
+        flash = _flash_attn() if (self.sinks is None and (self.softcap or (self.window is not None and T > self.window))) else None
+        if flash is not None and q.is_cuda and q.dtype == torch.bfloat16 and ops.functional.kernels_enabled() and self.hd % 8 == 0 \
+                and self.hd <= 256:
+            # capped scores and / or a sliding window longer sequences do not fit: the flash-attention library applies
+            # tanh capping and the band mask inside its tiles ([B, T, H, D] in and out: no transposes, no [T, T] scores)
+            o = flash(q, k, v, softmax_scale=self.scale if self.scale is not None else self.hd ** -0.5, causal=True,
+                      window_size=(self.window - 1, 0) if (self.window is not None and T > self.window) else (-1, -1),
+                      softcap=float(self.softcap or 0.0))
+            return self.o_proj(o.reshape(B, T, self.nh * self.hd))
         if self.softcap or self.sinks is not None:
             # capped attention scores / attention sinks: no library attention kernel applies tanh between QK^T and the
             # softmax or appends a sink logit, so the scores are formed explicitly ([B, heads, T, T] in fp32) — correct for

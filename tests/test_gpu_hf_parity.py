@@ -15,6 +15,8 @@ def _cases():
     yield "qwen2", T.Qwen2Config(**COMMON), T.Qwen2ForCausalLM
     yield "qwen3", T.Qwen3Config(**COMMON, head_dim=32), T.Qwen3ForCausalLM
     yield "gemma", T.GemmaConfig(**COMMON, head_dim=32), T.GemmaForCausalLM
+    # capped attention scores and a sliding window shorter than the sequence: the flash-attention library path
+    yield "gemma2", T.Gemma2Config(**COMMON, head_dim=32, sliding_window=32, query_pre_attn_scalar=32), T.Gemma2ForCausalLM
     yield "gpt2", T.GPT2Config(vocab_size=320, n_positions=128, n_embd=128, n_layer=2, n_head=4), T.GPT2LMHeadModel
     yield "mixtral", T.MixtralConfig(**COMMON, num_local_experts=6, num_experts_per_tok=2), T.MixtralForCausalLM
 

@@ -631,8 +631,12 @@ def push_grad_(local: torch.Tensor, peer_table: torch.Tensor, shard_elems: int, 
 def shard_step(*, grad, master, m, v, params_local=None, peer_params=None, world=1, global_offset=0, seed=0,
                noise_std=0.0, inv_normalize=1.0, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, step=1,
                phi_hat=0.0, decoupled_wd=True, ftrl_state=None, ftrl_mode=0, ftrl_coef: Sequence[float] = (),
-               nbuf=0, ring_head=0, noisy_out=None, skip_update=False, status: StatusWord | None = None) -> None:
-    """One fused pass over a shard: noise, AdamW(-BC) on fp32 masters, bf16 write-back to all ranks.
+               nbuf=0, ring_head=0, noisy_out=None, skip_update=False, status: StatusWord | None = None,
+               optimizer: str = "adam", nesterov: bool = False) -> None:
+    """One fused pass over a shard: noise, optimizer update on fp32 masters, bf16 write-back to all ranks.
+
+    ``optimizer``: ``"adam"`` (Adam / AdamW / AdamW-BC by ``decoupled_wd`` and ``phi_hat``), ``"sgd"`` (momentum
+    ``betas[0]``, PyTorch semantics, optional Nesterov; ``v`` unused) or ``"lion"`` (``betas``; ``v`` unused).
 
     ``step`` is 1-based; ``phi_hat`` is the bias-corrected noise-variance EMA (0 disables the correction).  With a
     ``status`` word that is already set (the gradient barrier before this call gave up) the kernel touches nothing:
@@ -647,6 +651,7 @@ def shard_step(*, grad, master, m, v, params_local=None, peer_params=None, world
         float(noise_std), float(inv_normalize), ftrl_mode, nbuf, ring_head, ctypes.cast(arr, ctypes.c_void_p),
         len(coef), float(lr), float(betas[0]), float(betas[1]), float(eps), float(weight_decay),
         1.0 - betas[0] ** step, 1.0 - betas[1] ** step, float(phi_hat), int(decoupled_wd), int(skip_update),
+        {"adam": 0, "sgd": 1, "lion": 2}[optimizer], int(nesterov),
         status.ptr() if status else None, lib.sm_count(), lib.stream())
     lib.check(rc, "shard_step")
 

@@ -160,6 +160,8 @@ struct ShardStepParams {
   // AdamW-BC
   float lr, b1, b2, eps, wd, bc1, bc2, phi_hat;
   int decoupled_wd, skip_update;
+  int opt_mode;            // 0: Adam family (AdamW / AdamW-BC / Adam), 1: SGD with momentum b1 (PyTorch semantics), 2: Lion (b1, b2)
+  int nesterov;            // SGD only
   const int* status;       // non-zero: a bounded wait expired earlier in this step; the kernel does nothing
 };
 
@@ -344,14 +346,26 @@ shard_step_kernel(const ShardStepParams p) {
       float w = w8[j];
       float ge = g;
       if (!p.decoupled_wd) ge += p.wd * w;
-      const float m = p.b1 * m8[j] + (1.f - p.b1) * ge;
-      const float v = p.b2 * v8[j] + (1.f - p.b2) * ge * ge;
-      m8[j] = m;
-      v8[j] = v;
-      float vh = v / p.bc2;
-      const float corrected = vh - p.phi_hat;
-      if (corrected > 0.f) vh = corrected;
-      float u = (m / p.bc1) / (sqrtf(vh) + p.eps);
+      float u;
+      if (p.opt_mode == 0) {
+        const float m = p.b1 * m8[j] + (1.f - p.b1) * ge;
+        const float v = p.b2 * v8[j] + (1.f - p.b2) * ge * ge;
+        m8[j] = m;
+        v8[j] = v;
+        float vh = v / p.bc2;
+        const float corrected = vh - p.phi_hat;
+        if (corrected > 0.f) vh = corrected;
+        u = (m / p.bc1) / (sqrtf(vh) + p.eps);
+      } else if (p.opt_mode == 1) {
+        // buf <- mu * buf + g (a zero buffer makes the first step buf = g); Nesterov looks ahead by one more mu * buf
+        const float m = p.b1 * m8[j] + ge;
+        m8[j] = m;
+        u = p.nesterov ? ge + p.b1 * m : m;
+      } else {
+        const float c = p.b1 * m8[j] + (1.f - p.b1) * ge;
+        u = c > 0.f ? 1.f : (c < 0.f ? -1.f : 0.f);
+        m8[j] = p.b2 * m8[j] + (1.f - p.b2) * ge;
+      }
       if (p.decoupled_wd) u += p.wd * w;
       w8[j] = w - p.lr * u;
     }
@@ -497,8 +511,8 @@ extern "C" int ob_shard_step(float* grad, float* master, float* m, float* v, flo
                              long long global_offset, int world, unsigned long long seed, float noise_std,
                              float inv_normalize, int ftrl_mode, int nbuf, int ring_head, const float* coef,
                              int ncoef, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
-                             float phi_hat, int decoupled_wd, int skip_update, const int* status, int sms,
-                             void* stream) {
+                             float phi_hat, int decoupled_wd, int skip_update, int opt_mode, int nesterov,
+                             const int* status, int sms, void* stream) {
   if (n <= 0) return 0;
   if (global_offset & 7) return -2;
   if (ncoef > OB_FTRL_MAX_COEF || nbuf >= OB_FTRL_MAX_COEF) return -3;
@@ -513,6 +527,8 @@ extern "C" int ob_shard_step(float* grad, float* master, float* m, float* v, flo
   for (int i = 0; i < OB_FTRL_MAX_COEF; ++i) p.coef[i] = (coef && i < ncoef) ? coef[i] : 0.f;
   p.lr = lr; p.b1 = b1; p.b2 = b2; p.eps = eps; p.wd = wd; p.bc1 = bc1; p.bc2 = bc2; p.phi_hat = phi_hat;
   p.decoupled_wd = decoupled_wd; p.skip_update = skip_update;
+  p.opt_mode = opt_mode; p.nesterov = nesterov;
+  if (opt_mode < 0 || opt_mode > 2) return -4;
   p.status = status;
   shard_step_kernel<<<grid_for((n + 7) / 8, sms), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return OB_CHECK_LAUNCH();

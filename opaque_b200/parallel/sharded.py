@@ -201,6 +201,8 @@ class DPStepConfig:
     weight_decay: float = 0.0
     decoupled_weight_decay: bool = True
     noise_bias_correction: bool = True
+    optimizer: str = "adam"            # "adam" (Adam / AdamW / AdamW-BC), "sgd" (momentum = betas[0]) or "lion" (betas)
+    nesterov: bool = False             # SGD only
 
 
 class ShardedDPOptimizer:
@@ -256,9 +258,10 @@ class ShardedDPOptimizer:
         lr = float(self.cfg.lr(self.step_count)) if callable(self.cfg.lr) else float(self.cfg.lr)
         b1, b2 = self.cfg.betas
         var = (noise_std / normalize_by) ** 2
-        if self.cfg.noise_bias_correction:
+        bc = self.cfg.noise_bias_correction and self.cfg.optimizer == "adam"
+        if bc:
             self.phi = b2 * self.phi + (1 - b2) * var
-        phi_hat = self.phi / (1 - b2 ** t) if self.cfg.noise_bias_correction else 0.0
+        phi_hat = self.phi / (1 - b2 ** t) if bc else 0.0
         if self.mechanism is not None and callable(self.mechanism.get("coef_fn")):
             c = [float(x) for x in self.mechanism["coef_fn"](self.step_count)]
             if len(c) != len(self.coef):
@@ -280,7 +283,8 @@ class ShardedDPOptimizer:
             eps=self.cfg.eps, weight_decay=self.cfg.weight_decay, step=t, phi_hat=phi_hat,
             decoupled_wd=self.cfg.decoupled_weight_decay, ftrl_state=self.ftrl_state, ftrl_mode=self.mode,
             ftrl_coef=self.coef, nbuf=self.nbuf, ring_head=(self.step_count % self.nbuf) if self.mode in (2, 3) else 0,
-            noisy_out=noisy_out, skip_update=skip_update, status=g.status if g.world > 1 else None)
+            noisy_out=noisy_out, skip_update=skip_update, status=g.status if g.world > 1 else None,
+            optimizer=self.cfg.optimizer, nesterov=self.cfg.nesterov)
         if ev:
             ev[2].record()
         g.barrier()

@@ -821,11 +821,23 @@ class DPTrainer:
         from ..engine.fused import FusedDPEngine
         from ..parallel.sharded import DPStepConfig
         a = self.args
-        if a.optim not in ("adamw", "adamw-bc", "adam"):
-            raise ValueError("the fused engine implements AdamW / AdamW-BC; use dp_engine='reference' for other optimizers")
-        cfg = DPStepConfig(lr=self.lr_schedule, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
-                           weight_decay=a.weight_decay, decoupled_weight_decay=a.optim != "adam",
-                           noise_bias_correction=a.optim == "adamw-bc")
+        extra = dict(a.optim_args)
+        if a.optim in ("adamw", "adamw-bc", "adam"):
+            cfg = DPStepConfig(lr=self.lr_schedule, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
+                               weight_decay=a.weight_decay, decoupled_weight_decay=a.optim != "adam",
+                               noise_bias_correction=a.optim == "adamw-bc")
+        elif a.optim == "sgd" and not extra.get("dampening") and not extra.get("maximize"):
+            # PyTorch semantics as in the functional optimizer: L2 weight decay folded into the gradient, optional momentum
+            cfg = DPStepConfig(lr=self.lr_schedule, betas=(float(extra.get("momentum", 0.0)), 0.0), weight_decay=a.weight_decay,
+                               decoupled_weight_decay=False, noise_bias_correction=False, optimizer="sgd",
+                               nesterov=bool(extra.get("nesterov", False)))
+        elif a.optim == "lion":
+            cfg = DPStepConfig(lr=self.lr_schedule, betas=(a.adam_beta1, float(extra.get("beta2", 0.99))), weight_decay=a.weight_decay,
+                               decoupled_weight_decay=bool(extra.get("decoupled_weight_decay", True)),
+                               noise_bias_correction=False, optimizer="lion")
+        else:
+            raise ValueError("the fused engine implements Adam / AdamW / AdamW-BC, SGD (momentum, Nesterov) and Lion; use "
+                             "dp_engine='reference' for other optimizers")
         mech = self._strategy.fused_mechanism(steps) if self._strategy is not None else None
         bound: Any = float(a.clipping_norm) if not isinstance(a.clipping_norm, Mapping) else None
         group_of = None

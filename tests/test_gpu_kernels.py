@@ -615,3 +615,30 @@ def test_direct_per_example_norms_match_the_products(dev, B, T, Da, Dg):
         assert rel(n3, want) < 2e-3
     assert ops.pick_norm_path(4096, 128, 256) == "direct" and ops.pick_norm_path(512, 4096, 4096) == "ghost"
     assert ops.pick_norm_path(4100, 128, 256) == "ghost"       # not a multiple of 64 rows
+
+
+@pytest.mark.parametrize("name,kw", [("sgd", dict(momentum=0.0)), ("sgd", dict(momentum=0.9)), ("sgd", dict(momentum=0.9, nesterov=True)),
+                                     ("lion", dict(betas=(0.9, 0.99)))])
+def test_shard_step_sgd_and_lion_match_the_functional_optimizers(dev, name, kw):
+    """The fused update for SGD (momentum, Nesterov, L2 decay in the gradient) and Lion (decoupled decay) against the
+    functional optimizer chain over several noiseless steps."""
+    from opaque_b200 import ops, optimizers as O
+    torch.manual_seed(5)
+    n, lr, wd = 4096, 0.05, 0.01
+    w0 = torch.randn(n, device=dev)
+    grads = [torch.randn(n, device=dev) for _ in range(5)]
+    if name == "sgd":
+        opt = O.sgd(lr, momentum=kw["momentum"], weight_decay=wd, nesterov=kw.get("nesterov", False))
+        betas, dec = (kw["momentum"], 0.0), False
+    else:
+        opt = O.lion(lr, kw["betas"], wd)
+        betas, dec = kw["betas"], True
+    params = {"w": w0.clone()}
+    state = opt.init(params)
+    master, m, v = w0.clone(), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    for t, g in enumerate(grads, start=1):
+        upd, state = opt.update({"w": g}, state, params=params)
+        params = O.apply_updates(params, upd)
+        ops.shard_step(grad=g.clone(), master=master, m=m, v=v, lr=lr, betas=betas, weight_decay=wd, step=t, decoupled_wd=dec,
+                       optimizer=name, nesterov=kw.get("nesterov", False))
+        assert torch.allclose(master, params["w"], rtol=2e-5, atol=2e-6), (name, kw, t)

@@ -55,7 +55,9 @@ def test_fused_trainer_steps_checkpoints_and_resumes(tmp_path):
                                 dict(clipping_mode="adaptive", clipping_norm=0.5), dict(clipping_mode="auto"),
                                 dict(privacy_noise_mechanism="mf_band"), dict(privacy_noise_mechanism="mf_bsr"),
                                 dict(privacy_noise_mechanism="mf_bisr"), dict(privacy_noise_mechanism="mf_lambda_cgd"),
-                                dict(privacy_noise_mechanism="mf_identity")])
+                                dict(privacy_noise_mechanism="mf_identity"),
+                                dict(optim="sgd", optim_args={"momentum": 0.9}), dict(optim="sgd", optim_args={"momentum": 0.9, "nesterov": True}),
+                                dict(optim="lion", learning_rate=1e-4), dict(optim="adam"), dict(optim="adamw")])
 def test_fused_trainer_options(tmp_path, kw):
     from opaque_b200.transformers import DPTrainer
     tr = DPTrainer(model=_model(lora=kw.get("privacy_noise_mechanism") is None), args=_args(tmp_path, save_steps=0, **kw), train_dataset=_rows())

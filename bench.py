@@ -24,7 +24,7 @@ warm-up steps captures CUDA graphs (GPT-2) and visits every tail microbatch size
 ``--impl restated`` runs the same algorithm written with this package's own reference engine (context only).
 
   python bench.py [--gpus N --steps K --warmup W] [--config llama8b-lora|gpt2|llama1b-blt|moe|llama-tiny]
-                  [--impl ours|restated|reference] [--microbatch M] [--per-gpu-batch B] [--accumulate auto|peer|local]
+                  [--impl ours|restated|reference] [--microbatch M] [--per-gpu-batch B] [--accumulate auto|peer|local|pull]
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
       bench.py --gpus N --steps K --warmup W
 """
@@ -53,7 +53,7 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--microbatch", type=int, default=0)
     ap.add_argument("--per-gpu-batch", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="truncate the model (profiling only; the JSON says so)")
-    ap.add_argument("--accumulate", default="auto", choices=["auto", "peer", "local"],
+    ap.add_argument("--accumulate", default="auto", choices=["auto", "peer", "local", "pull"],
                     help="peer: every microbatch's gradient tiles are reduced straight into the owners' shards; "
                          "local: accumulate in a local fp32 buffer and push once per step")
     ap.add_argument("--cuda-graph", type=int, default=-1, help="1/0: replay microbatches as CUDA graphs (default: per config)")
@@ -330,9 +330,7 @@ def main() -> None:
         for size in range(1, mb + 1):
             ids_s = setup_ids[:size]
             engine.accumulate(loss_fn, {"input_ids": ids_s, "labels": shift_labels(ids_s, frac)})
-        engine.group.barrier()                       # every rank's set-up reductions have landed ...
-        engine.space.grad.local.zero_()              # ... and are discarded: training starts from a zero gradient shard
-        engine.group.barrier()
+        engine.reset_gradients()                     # the set-up sums are discarded on every rank: training starts from zero
     torch.cuda.synchronize()
     for _ in range(args.warmup):
         engine.step(loss_fn, to_device(host_batch()), read_metrics=True)

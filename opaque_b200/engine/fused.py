@@ -16,8 +16,9 @@ When backward finishes every example's total squared norm is known: ``c_i = min(
 (guarded), one kernel reduces ``Σ_i c_i·g_i`` of the direct buffer into the gradient and one
 clip-weighted tcgen05 GEMM per ghost layer reduces ``Aᵀ·diag(c)·G`` there too (the factor multiplies
 each example's partial product in the epilogue).  With several ranks the destination is either the
-owners' shards through peer pointers (the launches ARE the reduce-scatter) or a local fp32 buffer that
-one push kernel per step reduces into the owners' shards; see ``FlatSpace(accumulate=...)``.  After the last
+owners' shards through peer pointers (the launches ARE the reduce-scatter) or a local fp32 buffer that is reduced
+once per step — pushed into the owners' shards by one kernel, or pulled out of every rank's buffer in rank order by the
+shard step itself; see ``FlatSpace(accumulate=...)``.  After the last
 microbatch :class:`~opaque_b200.parallel.ShardedDPOptimizer` adds noise once per coordinate and
 applies AdamW-BC on each owner's shard.
 

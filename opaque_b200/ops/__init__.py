@@ -628,7 +628,7 @@ def push_grad_(local: torch.Tensor, peer_table: torch.Tensor, shard_elems: int, 
     lib.check(rc, "push_grad")
 
 
-def shard_step(*, grad, master, m, v, params_local=None, peer_params=None, world=1, global_offset=0, seed=0,
+def shard_step(*, grad=None, peer_grad=None, master, m, v, params_local=None, peer_params=None, world=1, global_offset=0, seed=0,
                noise_std=0.0, inv_normalize=1.0, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, step=1,
                phi_hat=0.0, decoupled_wd=True, ftrl_state=None, ftrl_mode=0, ftrl_coef: Sequence[float] = (),
                nbuf=0, ring_head=0, noisy_out=None, skip_update=False, status: StatusWord | None = None,
@@ -638,16 +638,25 @@ def shard_step(*, grad, master, m, v, params_local=None, peer_params=None, world
     ``optimizer``: ``"adam"`` (Adam / AdamW / AdamW-BC by ``decoupled_wd`` and ``phi_hat``), ``"sgd"`` (momentum
     ``betas[0]``, PyTorch semantics, optional Nesterov; ``v`` unused) or ``"lion"`` (``betas``; ``v`` unused).
 
+    ``peer_grad`` (int64 device table of ``world`` full-length fp32 accumulation buffers, one per rank) selects the
+    pull form: the shard's gradient is the sum over ranks, in rank order, of ``buffer_r[global_offset + i]``, read through
+    peer pointers inside this kernel — the reduce-scatter is fused in, uses no atomics and gives the same bits on every
+    run.  ``grad`` is then unused and nothing is cleared (each rank clears its own buffer after the closing barrier).
+
     ``step`` is 1-based; ``phi_hat`` is the bias-corrected noise-variance EMA (0 disables the correction).  With a
     ``status`` word that is already set (the gradient barrier before this call gave up) the kernel touches nothing:
     a partially reduced shard is neither noised, applied nor cleared.
     """
+    if (grad is None) == (peer_grad is None):
+        raise ValueError("shard_step takes either grad (this shard's reduced gradient) or peer_grad (the pull form)")
+    if grad is not None and grad.numel() != master.numel():
+        raise ValueError("grad and master must have the shard's length")
     coef = torch.tensor(list(ftrl_coef) or [0.0], dtype=torch.float32)
     import ctypes
     arr = (ctypes.c_float * len(coef))(*coef.tolist())
     rc = lib.load().ob_shard_step(
-        grad.data_ptr(), lib.ptr(master), lib.ptr(m), lib.ptr(v), lib.ptr(ftrl_state), lib.ptr(peer_params),
-        lib.ptr(params_local), lib.ptr(noisy_out), grad.numel(), global_offset, world, seed & (2**64 - 1),
+        lib.ptr(grad), lib.ptr(peer_grad), lib.ptr(master), lib.ptr(m), lib.ptr(v), lib.ptr(ftrl_state), lib.ptr(peer_params),
+        lib.ptr(params_local), lib.ptr(noisy_out), master.numel(), global_offset, world, seed & (2**64 - 1),
         float(noise_std), float(inv_normalize), ftrl_mode, nbuf, ring_head, ctypes.cast(arr, ctypes.c_void_p),
         len(coef), float(lr), float(betas[0]), float(betas[1]), float(eps), float(weight_decay),
         1.0 - betas[0] ** step, 1.0 - betas[1] ** step, float(phi_hat), int(decoupled_wd), int(skip_update),

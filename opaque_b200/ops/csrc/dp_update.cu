@@ -139,7 +139,12 @@ embedding_wgrad_kernel(const __nv_bfloat16* __restrict__ g, const long long* __r
 constexpr int OB_FTRL_MAX_COEF = 64;
 
 struct ShardStepParams {
-  float* grad;             // [n] fp32 sum of clipped gradients for this shard; zeroed on exit
+  float* grad;             // [n] fp32 sum of clipped gradients for this shard; zeroed on exit (unused when peer_grad is set)
+  const float* const* peer_grad;   // pull form: [world] full-length fp32 accumulation buffers, one per rank, or nullptr.  The
+                           // shard's gradient is then the sum over ranks r = 0..world-1, IN THAT ORDER, of
+                           // peer_grad[r][global_offset + i], read here through peer pointers: the reduce-scatter happens
+                           // inside this kernel, needs no atomics, and gives the same bits whatever the arrival order.
+                           // Nothing is cleared here: every rank clears its own buffer after the closing barrier.
   float* master;           // [n] fp32 parameters
   float* m;                // [n]
   float* v;                // [n]
@@ -261,6 +266,31 @@ __device__ __forceinline__ void ftrl_apply8(const ShardStepParams& p, long long 
   }
 }
 
+// Pull form of the gradient read: this shard's 8 coordinates from every rank's accumulation buffer, summed in rank
+// order.  Up to eight ranks' 32-byte loads are in flight per thread before the first add.
+__device__ __forceinline__ void pull_grad8(const ShardStepParams& p, long long base, float* g8) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) g8[j] = 0.f;
+  for (int r0 = 0; r0 < p.world; r0 += 8) {
+    float4 a[8], b[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      if (r0 + r < p.world) {
+        const float4* src = reinterpret_cast<const float4*>(p.peer_grad[r0 + r] + p.global_offset + base);
+        a[r] = __ldcg(src);
+        b[r] = __ldcg(src + 1);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      if (r0 + r < p.world) {
+        g8[0] += a[r].x; g8[1] += a[r].y; g8[2] += a[r].z; g8[3] += a[r].w;
+        g8[4] += b[r].x; g8[5] += b[r].y; g8[6] += b[r].z; g8[7] += b[r].w;
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256)
 shard_step_kernel(const ShardStepParams p) {
   // The gradient barrier before this kernel may have given up (status != 0): the shard is then not fully reduced, and
@@ -281,8 +311,12 @@ shard_step_kernel(const ShardStepParams p) {
     }
     float g8[8], w8[8], m8[8], v8[8];
     if (full) {
-      *reinterpret_cast<float4*>(g8) = *reinterpret_cast<const float4*>(p.grad + base);
-      *reinterpret_cast<float4*>(g8 + 4) = *reinterpret_cast<const float4*>(p.grad + base + 4);
+      if (p.peer_grad) {
+        pull_grad8(p, base, g8);
+      } else {
+        *reinterpret_cast<float4*>(g8) = *reinterpret_cast<const float4*>(p.grad + base);
+        *reinterpret_cast<float4*>(g8 + 4) = *reinterpret_cast<const float4*>(p.grad + base + 4);
+      }
       if (!p.skip_update) {
         *reinterpret_cast<float4*>(w8) = *reinterpret_cast<const float4*>(p.master + base);
         *reinterpret_cast<float4*>(w8 + 4) = *reinterpret_cast<const float4*>(p.master + base + 4);
@@ -295,7 +329,13 @@ shard_step_kernel(const ShardStepParams p) {
       for (int j = 0; j < 8; ++j) {
         const long long k = base + j;
         const bool in = k < p.n;
-        g8[j] = in ? p.grad[k] : 0.f;
+        float gk = 0.f;
+        if (in && p.peer_grad) {
+          for (int r = 0; r < p.world; ++r) gk += __ldcg(p.peer_grad[r] + p.global_offset + k);
+        } else if (in) {
+          gk = p.grad[k];
+        }
+        g8[j] = gk;
         w8[j] = (in && !p.skip_update) ? p.master[k] : 0.f;
         m8[j] = (in && !p.skip_update) ? p.m[k] : 0.f;
         v8[j] = (in && !p.skip_update) ? p.v[k] : 0.f;
@@ -371,8 +411,10 @@ shard_step_kernel(const ShardStepParams p) {
     }
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
     if (full) {
-      *reinterpret_cast<float4*>(p.grad + base) = zero4;
-      *reinterpret_cast<float4*>(p.grad + base + 4) = zero4;
+      if (!p.peer_grad) {
+        *reinterpret_cast<float4*>(p.grad + base) = zero4;
+        *reinterpret_cast<float4*>(p.grad + base + 4) = zero4;
+      }
       if (p.noisy_out) {
         *reinterpret_cast<float4*>(p.noisy_out + base) = *reinterpret_cast<const float4*>(out8);
         *reinterpret_cast<float4*>(p.noisy_out + base + 4) = *reinterpret_cast<const float4*>(out8 + 4);
@@ -399,7 +441,7 @@ shard_step_kernel(const ShardStepParams p) {
       for (int j = 0; j < 8; ++j) {
         const long long k = base + j;
         if (k >= p.n) break;
-        p.grad[k] = 0.f;
+        if (!p.peer_grad) p.grad[k] = 0.f;
         if (p.noisy_out) p.noisy_out[k] = out8[j];
         if (p.skip_update) continue;
         p.master[k] = w8[j];
@@ -506,7 +548,7 @@ extern "C" int ob_embedding_wgrad(const void* g, const long long* ids, const flo
   return OB_CHECK_LAUNCH();
 }
 
-extern "C" int ob_shard_step(float* grad, float* master, float* m, float* v, float* ftrl_state,
+extern "C" int ob_shard_step(float* grad, const float* const* peer_grad, float* master, float* m, float* v, float* ftrl_state,
                              void* const* peer_params, void* local_params, float* noisy_out, long long n,
                              long long global_offset, int world, unsigned long long seed, float noise_std,
                              float inv_normalize, int ftrl_mode, int nbuf, int ring_head, const float* coef,
@@ -515,9 +557,10 @@ extern "C" int ob_shard_step(float* grad, float* master, float* m, float* v, flo
                              const int* status, int sms, void* stream) {
   if (n <= 0) return 0;
   if (global_offset & 7) return -2;
+  if (grad == nullptr && peer_grad == nullptr) return -2;
   if (ncoef > OB_FTRL_MAX_COEF || nbuf >= OB_FTRL_MAX_COEF) return -3;
   ShardStepParams p;
-  p.grad = grad; p.master = master; p.m = m; p.v = v; p.ftrl_state = ftrl_state;
+  p.grad = grad; p.peer_grad = peer_grad; p.master = master; p.m = m; p.v = v; p.ftrl_state = ftrl_state;
   p.peer_params = reinterpret_cast<__nv_bfloat16* const*>(peer_params);
   p.local_params = static_cast<__nv_bfloat16*>(local_params);
   p.noisy_out = noisy_out;

@@ -48,7 +48,7 @@ _SIGNATURES = {
     "ob_rows_sumsq": [P, I, LL, LL, P, I, P],
     "ob_clip_weighted_sum": [P, P, I, LL, LL, P, P, LL, LL, I, P],
     "ob_embedding_wgrad": [P, P, P, LL, I, LL, P, P, LL, LL, I, P],
-    "ob_shard_step": [P, P, P, P, P, P, P, P, LL, LL, I, ULL, F, F, I, I, I, P, I, F, F, F, F, F, F, F, F, I, I, I, I, P, I, P],
+    "ob_shard_step": [P, P, P, P, P, P, P, P, P, LL, LL, I, ULL, F, F, I, I, I, P, I, F, F, F, F, F, F, F, F, I, I, I, I, P, I, P],
     "ob_peer_barrier": [P, P, I, I, I, P, D, P],
     "ob_ipc_alloc": [P, LL],
     "ob_ipc_free": [P],

@@ -66,10 +66,14 @@ class FlatSpace:
         """``accumulate="peer"`` (default): producer kernels reduce every microbatch's tiles straight into the owners'
         shards.  ``"local"``: they add into a full-length local fp32 buffer and ONE push per step reduces it into the
         owners' shards — (microbatches per step)× less reduction traffic over NVLink at the price of ``4·P`` bytes.
-        ``"auto"``: local while that buffer stays under ``LOCAL_ACCUMULATE_LIMIT_BYTES`` or leaves
+        ``"pull"``: like ``"local"``, but the buffer lives in peer-mapped memory and nothing is pushed: the fused shard
+        step READS its shard from every rank's buffer through peer pointers and adds the W values in rank order — the
+        reduce-scatter runs inside the optimizer kernel, without atomics and with the same bits whatever the arrival
+        order; one kernel and one pass over the gradient fewer per step.
+        ``"auto"``: the pull form while that buffer stays under ``LOCAL_ACCUMULATE_LIMIT_BYTES`` or leaves
         ``LOCAL_ACCUMULATE_RESERVE_BYTES`` of device memory free."""
-        if accumulate not in ("peer", "local", "auto"):
-            raise ValueError("accumulate must be 'peer', 'local' or 'auto'")
+        if accumulate not in ("peer", "local", "pull", "auto"):
+            raise ValueError("accumulate must be 'peer', 'local', 'pull' or 'auto'")
         self.group = group
         is_direct = direct or default_direct
         label = group_of or (lambda name: "")
@@ -112,10 +116,18 @@ class FlatSpace:
         self.params = group.buffer(self.total, torch.bfloat16)
         self.grad = group.buffer(self.shard, torch.float32)
         dev = group.device
+        can_pull = group.world == 1 or group.use_ipc       # the pull form needs every rank's buffer mapped here
+        if accumulate == "pull" and not can_pull:
+            raise ValueError("accumulate='pull' needs peer-mapped buffers (PeerGroup(use_ipc=True))")
         if accumulate == "auto":     # measured on 4 GPUs: per-microbatch peer reductions cost 15-35 % for 0.1-1 B parameter
-            accumulate = "local" if self._local_accumulation_fits() else "peer"                     # models
+            # models; between the two once-per-step forms the pull form saves the push kernel and its pass over the buffer
+            accumulate = ("pull" if can_pull else "local") if self._local_accumulation_fits() else "peer"
         self.accumulate = accumulate if group.world > 1 else "peer"
         self.grad_full = torch.zeros(self.total, dtype=torch.float32, device=dev) if self.accumulate == "local" else None
+        self.grad_full_table = None        # "pull": device table of every rank's accumulation buffer
+        if self.accumulate == "pull":
+            self._grad_full_buffer = group.buffer(self.total, torch.float32)
+            self.grad_full, self.grad_full_table = self._grad_full_buffer.local, self._grad_full_buffer.table
         self.master = torch.zeros(self.shard, dtype=torch.float32, device=dev)
         self.m = torch.zeros_like(self.master)
         self.v = torch.zeros_like(self.master)
@@ -180,7 +192,7 @@ class FlatSpace:
 
     def push_local_gradient(self) -> None:
         """``accumulate="local"``: reduce this rank's accumulated gradient into the owners' shards (before the barrier)."""
-        if self.grad_full is not None:
+        if self.grad_full is not None and self.grad_full_table is None:
             ops.push_grad_(self.grad_full, self.grad.table, self.shard, status=self.group.status)
 
     @torch.no_grad()
@@ -275,8 +287,9 @@ class ShardedDPOptimizer:
         g.barrier()
         if ev:
             ev[1].record()
+        pull = sp.grad_full_table is not None
         ops.shard_step(
-            grad=sp.grad.local, master=sp.master, m=sp.m, v=sp.v,
+            grad=None if pull else sp.grad.local, peer_grad=sp.grad_full_table if pull else None, master=sp.master, m=sp.m, v=sp.v,
             params_local=sp.params.local if g.world == 1 else None,
             peer_params=sp.params.table if g.world > 1 else None, world=g.world, global_offset=sp.shard_lo,
             seed=seed, noise_std=noise_std, inv_normalize=1.0 / normalize_by, lr=lr, betas=(b1, b2),
@@ -288,6 +301,8 @@ class ShardedDPOptimizer:
         if ev:
             ev[2].record()
         g.barrier()
+        if pull:            # every rank has read its shard out of this buffer: clear it for the next step's producers
+            sp.grad_full.zero_()
         if ev:
             ev[3].record()
             self.timing.append(tuple(ev))

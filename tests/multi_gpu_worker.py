@@ -3,6 +3,9 @@
 Launched by ``tests/test_gpu_multi.py`` through ``python -m torch.distributed.run``.  Every rank holds the same
 model; rank r takes examples ``r::W`` of a common batch.  Checks, on the device and through the peer-memory path only:
 
+  (mode ``pull``: nothing is pushed; the shard step reads every rank's accumulation buffer through peer pointers and
+  adds them in rank order — checked bit for bit.)
+
   1. the clip-weighted gradient sums that all ranks reduce into the owners' shards equal the oracle's sum over the
      whole batch (peer ``red.add`` reduce-scatter fused into the producer kernels);
   2. the noise that each owner adds to its shard is the same Philox stream a single rank would draw (exactly once
@@ -88,7 +91,7 @@ def main() -> int:
     dist.broadcast(ids, 0)
     labels = shift_labels(ids, 1.0)
     eng = FusedDPEngine(model, clipping_norm=C, noise_multiplier=0.0, normalize_by=float(B), key=key(11),
-                        step_config=DPStepConfig(lr=1e-2), microbatch_size=2, accumulate="local" if mode == "local" else ("peer" if mode == "full" else "auto"))
+                        step_config=DPStepConfig(lr=1e-2), microbatch_size=2, accumulate={"local": "local", "pull": "pull", "full": "peer"}.get(mode, "auto"))
     sp = eng.space
     # oracle AFTER binding (parameters are now the broadcast bf16 values), per example, on every rank
     total = {n: torch.zeros_like(p, dtype=torch.float32) for n, p in model.named_parameters() if p.requires_grad}
@@ -112,10 +115,30 @@ def main() -> int:
     eng.group.barrier()
     torch.cuda.synchronize()
     eng.group.check("accumulate")
-    got = sp.grad.local
+    if mode == "pull":
+        assert sp.accumulate == "pull"
+    if sp.accumulate == "pull":              # also what "auto" picks for a model this small
+        # nothing was pushed: the shard's gradient is the rank-ordered sum of every rank's accumulation buffer, which the
+        # shard step forms itself.  Read it here the same way (peer views), and check the kernel's sum against it bit by bit.
+        assert sp.grad_full_table is not None
+        got = torch.zeros(sp.shard, device=dev)
+        for r in range(world):
+            got += sp._grad_full_buffer.peer_view(r)[sp.shard_lo:sp.shard_lo + sp.shard]
+        pulled = [torch.empty(sp.shard, device=dev) for _ in range(2)]
+        for out in pulled:
+            ops.shard_step(peer_grad=sp.grad_full_table, master=sp.master, m=sp.m, v=sp.v, world=world,
+                           global_offset=sp.shard_lo, noisy_out=out, skip_update=True)
+        torch.cuda.synchronize()
+        bits = torch.equal(pulled[0], got) and torch.equal(pulled[0], pulled[1])
+        print(f"[rank {rank}] pull form: rank-ordered sum reproduced bit for bit: {bits}", flush=True)
+        sp.grad.local.copy_(got)             # the checks below read the reduced shard from here
+        pull_ok = bits
+    else:
+        got = sp.grad.local
+        pull_ok = True
     ref = flat_ref[sp.shard_lo:sp.shard_lo + sp.shard]
     err = float((got - ref).norm() / (ref.norm() + 1e-12))
-    ok = err < 3e-2
+    ok = err < 3e-2 and pull_ok
     print(f"[rank {rank}] reduce-scatter shard rel err {err:.3e}", flush=True)
 
     # noise: exactly once per coordinate across shard boundaries

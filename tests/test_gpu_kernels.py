@@ -642,3 +642,39 @@ def test_shard_step_sgd_and_lion_match_the_functional_optimizers(dev, name, kw):
         ops.shard_step(grad=g.clone(), master=master, m=m, v=v, lr=lr, betas=betas, weight_decay=wd, step=t, decoupled_wd=dec,
                        optimizer=name, nesterov=kw.get("nesterov", False))
         assert torch.allclose(master, params["w"], rtol=2e-5, atol=2e-6), (name, kw, t)
+
+
+@pytest.mark.parametrize("world", [1, 3, 8, 11])
+def test_shard_step_pull_form_sums_rank_buffers_in_rank_order(dev, world):
+    """The pull form of the fused shard step: the shard's gradient is read out of ``world`` full-length accumulation
+    buffers (here all on one GPU: plain loads, no kernel waits on another) and added in rank order.  The result equals
+    the ordinary step fed with that rank-ordered sum BIT FOR BIT, twice in a row, and the buffers are left as they were."""
+    from opaque_b200 import ops
+    torch.manual_seed(3)
+    total, lo, n = 8192 + 2048, 2048, 4096 + 8 * 3 + 3          # a shard in the middle of the flat space
+    bufs = [torch.randn(total, device=dev) * (10.0 ** (r % 3 - 1)) for r in range(world)]
+    table = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=dev)
+    ordered = torch.zeros(n, device=dev)
+    for b in bufs:
+        ordered += b[lo:lo + n]
+    keep = [b.clone() for b in bufs]
+    w0 = torch.randn(n, device=dev)
+    results = []
+    for form in ("pull", "pull", "push"):
+        master, m, v = w0.clone(), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        pl = torch.zeros(total, device=dev, dtype=torch.bfloat16)
+        noisy = torch.empty(n, device=dev)
+        kw = dict(master=master, m=m, v=v, params_local=pl, global_offset=lo, seed=9, noise_std=0.5, inv_normalize=0.125,
+                  lr=1e-2, weight_decay=0.1, step=1, phi_hat=1e-3, noisy_out=noisy)
+        if form == "pull":
+            ops.shard_step(peer_grad=table, world=world, **kw)
+        else:
+            ops.shard_step(grad=ordered.clone(), **kw)
+        results.append((master, m, v, pl, noisy))
+    for a, b in zip(results[0], results[1]):
+        assert torch.equal(a, b)
+    for a, b in zip(results[0], results[2]):
+        assert torch.equal(a, b)
+    assert all(torch.equal(b, k) for b, k in zip(bufs, keep))
+    with pytest.raises(ValueError):
+        ops.shard_step(master=w0, m=w0, v=w0)

@@ -26,7 +26,7 @@ def _run(world: int, mode: str, *extra: str) -> None:
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
 
 
-@pytest.mark.parametrize("mode", ["full", "lora", "local"])
+@pytest.mark.parametrize("mode", ["full", "lora", "local", "pull"])
 def test_two_ranks_match_single_process_oracle(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

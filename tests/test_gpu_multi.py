@@ -33,11 +33,12 @@ def test_two_ranks_match_single_process_oracle(mode):
     _run(2, mode)
 
 
-def test_all_visible_gpus():
+@pytest.mark.parametrize("mode", ["full", "pull"])
+def test_all_visible_gpus(mode):
     n = torch.cuda.device_count()
     if n < 4:
         pytest.skip("needs four or more GPUs")
-    _run(n, "full")
+    _run(n, mode)
 
 
 def test_short_run_parity_one_vs_two_gpus(tmp_path):

@@ -12,6 +12,7 @@ _router.py, peft/_router.py.
 """
 from __future__ import annotations
 
+import math
 from collections.abc import Callable
 from typing import Any
 
@@ -320,7 +321,8 @@ def _convert_state_dict(mtype: str, sd: dict, out: torch.nn.Module) -> dict:
         hd = cfg.hd
         perm = rope_row_permutation(hd, int(hd * factor), mtype in ROPE_INTERLEAVED)
         for k in list(res):
-            if k.endswith(("self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.q_proj.bias", "self_attn.k_proj.bias")):
+            if k.endswith(("self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.q_proj.bias", "self_attn.k_proj.bias",
+                           "self_attn.q_proj.lora_B", "self_attn.k_proj.lora_B")):       # LoRA B rows are output rows too
                 v = res[k]
                 heads = v.shape[0] // hd
                 res[k] = v.reshape(heads, hd, *v.shape[1:])[:, perm].reshape(v.shape).contiguous()
@@ -364,6 +366,7 @@ def apply_transformers_model_patches(model: Any, *, performance: bool = True, co
     if mtype not in _FAMILIES:
         raise ValueError(f"model_type {mtype!r} has no registered family; known: {supported_families()}")
     out = _FAMILIES[mtype](cfg, kw)
+    out.source_model_type = mtype               # which Hugging Face naming / rotary layout adapters are exported in
     if isinstance(model, torch.nn.Module):
         sd = _convert_state_dict(mtype, dict(model.state_dict()), out)
         missing, unexpected = out.load_state_dict(sd, strict=False)
@@ -373,9 +376,194 @@ def apply_transformers_model_patches(model: Any, *, performance: bool = True, co
     return out
 
 
+def _is_peft_wrapped(model: Any) -> bool:
+    """A model wrapped by the PEFT library: ``peft_config`` (adapter name -> config) and ``base_model.model`` (the
+    Hugging Face model with adapter layers injected).  Recognised by structure, so the library need not be importable."""
+    base = getattr(model, "base_model", None)
+    return isinstance(getattr(model, "peft_config", None), dict) and isinstance(getattr(base, "model", None), torch.nn.Module)
+
+
+_PEFT_REFUSED = {"use_dora": "DoRA (weight-decomposed adapters)", "modules_to_save": "modules_to_save (fully trained copies)",
+                 "fan_in_fan_out": "fan_in_fan_out (transposed base weights)", "layer_replication": "layer replication",
+                 "rank_pattern": "per-module ranks (rank_pattern)", "alpha_pattern": "per-module alpha (alpha_pattern)"}
+
+
+def convert_peft_model(model: Any, *, adapter_name: str | None = None, **kw: Any):
+    """Turn a PEFT-wrapped Hugging Face model (``peft.get_peft_model(hf, LoraConfig(...))``) into this package's model with
+    the same base weights AND the same LoRA factors, so that training continues from the adapter as it is.
+
+    Read from the wrapper by structure: ``peft_config[adapter]`` (``r``, ``lora_alpha``, ``target_modules``,
+    ``use_rslora``), and from the injected layers ``<module>.base_layer.weight``, ``<module>.lora_A.<adapter>.weight``
+    ``[r, in]``, ``<module>.lora_B.<adapter>.weight`` ``[out, r]``.  Options this package has no module for (DoRA,
+    ``modules_to_save``, transposed base weights, per-module ranks, adapter bias) are refused by name; LoRA dropout is
+    refused unless it is zero (a per-call random mask would have to be shared with the per-example gradient kernels).
+
+    Parity: packages/opaque-patches/src/opaque/api/patches/peft/_router.py (PEFT layers routed onto fused LoRA kernels).
+    """
+    if not _is_peft_wrapped(model):
+        raise ValueError("not a PEFT-wrapped model: expected .peft_config (dict) and .base_model.model")
+    name = adapter_name or getattr(model, "active_adapter", None) or next(iter(model.peft_config))
+    if isinstance(name, (list, tuple)):
+        if len(name) != 1:
+            raise NotImplementedError(f"several active adapters {list(name)}: pick one with adapter_name=")
+        name = name[0]
+    if name not in model.peft_config:
+        raise ValueError(f"adapter {name!r} not in {sorted(model.peft_config)}")
+    cfg = model.peft_config[name]
+    ptype = str(_cfg_get(cfg, "peft_type", "LORA")).upper().split(".")[-1]
+    if ptype != "LORA":
+        raise NotImplementedError(f"PEFT method {ptype!r}: only LoRA adapters are converted")
+    for field, what in _PEFT_REFUSED.items():
+        if _cfg_get(cfg, field, None):
+            raise NotImplementedError(f"PEFT option {what} is not supported")
+    if str(_cfg_get(cfg, "bias", "none")) != "none":
+        raise NotImplementedError("PEFT option bias != 'none' (trainable biases beside the adapter) is not supported")
+    if float(_cfg_get(cfg, "lora_dropout", 0.0) or 0.0) != 0.0:
+        raise NotImplementedError("lora_dropout > 0 is not supported: set it to 0 for differentially private training")
+    r = int(_cfg_get(cfg, "r"))
+    alpha = float(_cfg_get(cfg, "lora_alpha", r))
+    if _cfg_get(cfg, "use_rslora", False):
+        alpha = alpha * math.sqrt(r)             # rank-stabilised scaling alpha / sqrt(r), expressed as alpha' / r
+    hf = model.base_model.model
+    sd, targets = {}, set()
+    a_tag, b_tag = f".lora_A.{name}.weight", f".lora_B.{name}.weight"
+    for k, v in hf.state_dict().items():
+        if ".base_layer." in k:
+            sd[k.replace(".base_layer.", ".")] = v
+        elif k.endswith(a_tag):
+            sd[k[: -len(a_tag)] + ".lora_A"] = v
+            targets.add(k[: -len(a_tag)].split(".")[-1])
+        elif k.endswith(b_tag):
+            sd[k[: -len(b_tag)] + ".lora_B"] = v
+        elif ".lora_A." in k or ".lora_B." in k or ".lora_embedding_" in k or ".lora_magnitude_vector" in k:
+            if f".{name}." in k or k.endswith(f".{name}"):
+                raise NotImplementedError(f"adapter tensor {k!r} has no counterpart here")
+            continue                                 # another (inactive) adapter
+        else:
+            sd[k] = v
+    if not targets:
+        raise ValueError(f"adapter {name!r} has no LoRA layers in the wrapped model")
+    hcfg = hf.config
+    mtype = _cfg_get(hcfg, "model_type")
+    if mtype not in _FAMILIES:
+        raise NotImplementedError(f"model_type {mtype!r} under PEFT: only converted families ({sorted(_FAMILIES)}) take adapters")
+    out = _FAMILIES[mtype](hcfg, kw)
+    if not hasattr(out, "add_lora"):
+        raise NotImplementedError(f"model_type {mtype!r} has no LoRA support in this package")
+    out.source_model_type = mtype
+    out.add_lora(r, alpha, tuple(sorted(targets)))
+    conv = _convert_state_dict(mtype, sd, out)
+    missing, unexpected = out.load_state_dict(conv, strict=False)
+    missing = [k for k in missing if "rope_" not in k]
+    if missing or unexpected:
+        raise ValueError(f"converting PEFT-wrapped {mtype}: missing {missing[:5]}, unexpected {list(unexpected)[:5]}")
+    return out
+
+
+def _qk_row_permutation(model: Any, mtype: str) -> torch.Tensor | None:
+    """The q / k output-row permutation that conversion applied for this family (``None``: rows kept as they are)."""
+    cfg = model.config
+    factor = float(getattr(cfg, "partial_rotary_factor", 1.0))
+    if mtype in MOE_LIKE or not (mtype in ROPE_INTERLEAVED or factor < 1.0):
+        return None
+    return rope_row_permutation(cfg.hd, int(cfg.hd * factor), mtype in ROPE_INTERLEAVED)
+
+
+def peft_adapter_state_dict(model: Any, *, model_type: str | None = None) -> dict[str, torch.Tensor]:
+    """The model's LoRA factors under the names and row order the PEFT library saves them in:
+    ``base_model.model.<hugging face module path>.lora_A.weight`` / ``.lora_B.weight`` (no adapter name in the key)."""
+    mtype = model_type or getattr(model, "source_model_type", "llama")
+    perm = _qk_row_permutation(model, mtype)
+    prefix = "base_model.model." + ("model." if mtype in MOE_LIKE else "")
+    out: dict[str, torch.Tensor] = {}
+    for name, p in model.named_parameters():
+        if not name.endswith((".lora_A", ".lora_B")):
+            continue
+        v = p.detach().to("cpu").clone()
+        if perm is not None and name.endswith(("self_attn.q_proj.lora_B", "self_attn.k_proj.lora_B")):
+            inv = torch.empty_like(perm)
+            inv[perm] = torch.arange(perm.numel())
+            hd = perm.numel()
+            v = v.reshape(v.shape[0] // hd, hd, v.shape[1])[:, inv].reshape(v.shape).contiguous()
+        out[prefix + name + ".weight"] = v
+    if not out:
+        raise ValueError("the model has no LoRA factors")
+    return out
+
+
+def export_peft_adapter(model: Any, output_dir: str, *, base_model_name_or_path: str | None = None,
+                        model_type: str | None = None) -> str:
+    """Write the LoRA adapter as the two files the PEFT library loads: ``adapter_model.safetensors`` and
+    ``adapter_config.json`` (``PeftModel.from_pretrained(base, output_dir)`` on the Hugging Face side)."""
+    import json
+    import os
+    from safetensors.torch import save_file
+    sd = peft_adapter_state_dict(model, model_type=model_type)
+    mods = [m for m in model.modules() if getattr(m, "lora_A", None) is not None]
+    r = int(mods[0].lora_A.shape[0])
+    targets = sorted({k.split(".")[-3] for k in sd})
+    os.makedirs(output_dir, exist_ok=True)
+    save_file(sd, os.path.join(output_dir, "adapter_model.safetensors"), metadata={"format": "pt"})
+    cfg = {"peft_type": "LORA", "task_type": "CAUSAL_LM", "r": r, "lora_alpha": float(mods[0].scaling) * r, "lora_dropout": 0.0,
+           "bias": "none", "target_modules": targets, "fan_in_fan_out": False, "use_rslora": False, "use_dora": False,
+           "modules_to_save": None, "inference_mode": True, "base_model_name_or_path": base_model_name_or_path}
+    with open(os.path.join(output_dir, "adapter_config.json"), "w") as f:
+        json.dump(cfg, f, indent=1)
+    return output_dir
+
+
+def load_peft_adapter(model: Any, path_or_state: Any, *, model_type: str | None = None) -> Any:
+    """Load an adapter saved by the PEFT library (a directory with ``adapter_model.safetensors`` + ``adapter_config.json``,
+    or the state dict itself) into a framework model; LoRA factors are attached first if the model has none."""
+    import json
+    import os
+    mtype = model_type or getattr(model, "source_model_type", "llama")
+    if isinstance(path_or_state, (str, os.PathLike)):
+        from safetensors.torch import load_file
+        sd = load_file(os.path.join(path_or_state, "adapter_model.safetensors"))
+        with open(os.path.join(path_or_state, "adapter_config.json")) as f:
+            cfg = json.load(f)
+        if not any(getattr(m, "lora_A", None) is not None for m in model.modules()):
+            tmp = type("Cfg", (), cfg)()
+            for field, what in _PEFT_REFUSED.items():
+                if cfg.get(field):
+                    raise NotImplementedError(f"PEFT option {what} is not supported")
+            alpha = float(cfg.get("lora_alpha", cfg["r"])) * (math.sqrt(cfg["r"]) if cfg.get("use_rslora") else 1.0)
+            model.add_lora(int(tmp.r), alpha, tuple(cfg["target_modules"]))
+    else:
+        sd = dict(path_or_state)
+    perm = _qk_row_permutation(model, mtype)
+    prefix = "base_model.model." + ("model." if mtype in MOE_LIKE else "")
+    params = dict(model.named_parameters())
+    loaded = 0
+    with torch.no_grad():
+        for k, v in sd.items():
+            name = k.removeprefix(prefix)
+            for tag in (".lora_A.weight", ".lora_B.weight", ".lora_A.default.weight", ".lora_B.default.weight"):
+                if name.endswith(tag):
+                    name = name[: -len(tag)] + tag[:7]
+                    break
+            else:
+                raise ValueError(f"unexpected adapter tensor {k!r}")
+            if name not in params:
+                raise ValueError(f"adapter tensor {k!r} has no LoRA factor {name!r} in the model")
+            if perm is not None and name.endswith(("self_attn.q_proj.lora_B", "self_attn.k_proj.lora_B")):
+                hd = perm.numel()
+                v = v.reshape(v.shape[0] // hd, hd, v.shape[1])[:, perm].reshape(v.shape)
+            params[name].copy_(v)
+            loaded += 1
+    want = sum(1 for n in params if n.endswith((".lora_A", ".lora_B")))
+    if loaded != want:
+        raise ValueError(f"the adapter holds {loaded} tensors, the model has {want} LoRA factors")
+    return model
+
+
 def apply_peft_model_patches(model: Any, *, r: int | None = None, lora_alpha: float | None = None,
                              target_modules=("q_proj", "k_proj", "v_proj", "o_proj"), **kw: Any):
-    """Attach LoRA adapters (PEFT naming) to a framework model, or read ``r / alpha / targets`` from a PEFT config."""
+    """Attach LoRA adapters (PEFT naming) to a framework model, or read ``r / alpha / targets`` from a PEFT config.
+    A model already wrapped by the PEFT library is converted together with its adapter (:func:`convert_peft_model`)."""
+    if _is_peft_wrapped(model):
+        return convert_peft_model(model, **{k: v for k, v in kw.items() if k != "peft_config"})
     cfg = kw.get("peft_config")
     if cfg is not None:
         r = r or _cfg_get(cfg, "r")
@@ -390,6 +578,10 @@ def apply_peft_model_patches(model: Any, *, r: int | None = None, lora_alpha: fl
 def apply_model_patches(model: Any, *, performance: bool = True, compat: bool = True, peft: bool = True,
                         fused_linear_cross_entropy: bool = False, **kwargs: Any):
     """One call for both steps; ``fused_linear_cross_entropy`` is always on (``per_example_loss`` uses it)."""
+    if _is_peft_wrapped(model):                 # a PEFT-wrapped Hugging Face model: base weights and adapter together
+        for k in ("r", "lora_alpha", "target_modules", "peft_config"):
+            kwargs.pop(k, None)
+        return convert_peft_model(model, **kwargs)
     peft_kw = {k: kwargs.pop(k) for k in ("r", "lora_alpha", "target_modules", "peft_config") if k in kwargs}
     out = apply_transformers_model_patches(model, performance=performance, compat=compat, **kwargs)
     if peft and peft_kw:
@@ -411,5 +603,5 @@ def is_runtime_patched() -> bool:
     return _RUNTIME["patched"]
 
 
-__all__ = ["apply_model_patches", "apply_peft_model_patches", "apply_runtime_patches", "apply_transformers_model_patches",
+__all__ = ["apply_model_patches", "apply_peft_model_patches", "convert_peft_model", "export_peft_adapter", "load_peft_adapter", "peft_adapter_state_dict", "apply_runtime_patches", "apply_transformers_model_patches",
            "inplace", "is_runtime_patched", "kernels", "register_family", "supported_families"]

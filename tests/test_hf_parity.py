@@ -158,3 +158,137 @@ def test_converted_families_train_through_the_trainer_on_the_reference_engine(fa
     out = DPTrainer(model=model, args=args, train_dataset=rows).train()
     assert out["global_step"] == 2 and out["epsilon"] > 0
     assert any(not torch.equal(p, before[n]) for n, p in model.named_parameters())
+
+
+def _fake_peft_wrap(hf, r, alpha, targets, adapter="default", rslora=False):
+    """The object layout that ``peft.get_peft_model(hf, LoraConfig(...))`` produces, rebuilt by hand (the library is not
+    installed here): target linears replaced by a module with ``base_layer`` / ``lora_A[adapter]`` / ``lora_B[adapter]``,
+    and a wrapper with ``peft_config`` and ``base_model.model``."""
+    import types
+
+    class LoraLinear(torch.nn.Module):
+        def __init__(self, base):
+            super().__init__()
+            self.base_layer = base
+            self.lora_A = torch.nn.ModuleDict({adapter: torch.nn.Linear(base.in_features, r, bias=False)})
+            self.lora_B = torch.nn.ModuleDict({adapter: torch.nn.Linear(r, base.out_features, bias=False)})
+            self.scaling = {adapter: alpha / (r ** 0.5 if rslora else r)}
+            torch.nn.init.normal_(self.lora_B[adapter].weight, std=0.05)
+
+        def forward(self, x):
+            return self.base_layer(x) + self.lora_B[adapter](self.lora_A[adapter](x)) * self.scaling[adapter]
+
+    for parent in list(hf.modules()):
+        for name, child in list(parent.named_children()):
+            if name in targets and isinstance(child, torch.nn.Linear):
+                setattr(parent, name, LoraLinear(child))
+
+    class Wrapper(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.base_model = torch.nn.Module()
+            self.base_model.model = hf
+            self.peft_config = {adapter: types.SimpleNamespace(peft_type="LORA", r=r, lora_alpha=alpha, target_modules=set(targets),
+                                                               lora_dropout=0.0, bias="none", use_rslora=rslora,
+                                                               use_dora=False, modules_to_save=None, fan_in_fan_out=False)}
+            self.active_adapter = adapter
+
+        def forward(self, ids):
+            return self.base_model.model(ids)
+    return Wrapper()
+
+
+@pytest.mark.parametrize("family,rslora", [("llama", False), ("qwen2", True), ("llama-mlp", False), ("cohere", False)])
+def test_peft_wrapped_model_converts_with_its_adapter(family, rslora):
+    """A PEFT-wrapped Hugging Face model becomes a framework model with the same base weights and LoRA factors: same
+    logits, only the factors trainable.  ``cohere`` rotates interleaved pairs: the conversion permutes the q / k output
+    rows, and with them the rows of the q / k ``lora_B`` factors."""
+    import transformers as T
+    from opaque_b200 import patches
+    torch.manual_seed(0)
+    common = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, max_position_embeddings=64)
+    if family == "qwen2":
+        hf = T.Qwen2ForCausalLM(T.Qwen2Config(**common)).eval()
+        targets = ("q_proj", "k_proj", "v_proj")
+    elif family == "cohere":
+        hf = T.CohereForCausalLM(T.CohereConfig(**common, pad_token_id=0)).eval()
+        targets = ("q_proj", "k_proj")
+    elif family == "llama":
+        hf = T.LlamaForCausalLM(T.LlamaConfig(**common)).eval()
+        targets = ("q_proj", "k_proj", "v_proj", "o_proj")
+    else:
+        hf = T.LlamaForCausalLM(T.LlamaConfig(**common)).eval()
+        targets = ("o_proj", "down_proj")
+    wrapped = _fake_peft_wrap(hf, 4, 8.0, targets, rslora=rslora)
+    ids = torch.randint(0, 320, (2, 16))
+    with torch.no_grad():
+        want = wrapped(ids).logits
+    ours = patches.apply_model_patches(wrapped, dtype=torch.float32).eval()
+    with torch.no_grad():
+        got = ours(ids)[..., :320]
+    assert float((got - want).norm() / want.norm()) < 1e-4
+    trainable = sorted({n.split(".")[-1] for n, p in ours.named_parameters() if p.requires_grad})
+    assert trainable == ["lora_A", "lora_B"]
+    n_adapters = sum(1 for n, p in ours.named_parameters() if n.endswith("lora_A"))
+    assert n_adapters == 2 * len(targets)
+    # the adapter-disabled model is the base model
+    for m in wrapped.modules():
+        if hasattr(m, "scaling") and isinstance(m.scaling, dict):
+            m.scaling = {k: 0.0 for k in m.scaling}
+    from opaque_b200.models import layers
+    with torch.no_grad(), layers.adapters_disabled():
+        base = ours(ids)[..., :320]
+        assert float((base - wrapped(ids).logits).norm() / want.norm()) < 1e-4
+
+
+def test_peft_options_without_a_counterpart_are_refused():
+    import transformers as T
+    from opaque_b200 import patches
+    hf = T.LlamaForCausalLM(T.LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=1,
+                                          num_attention_heads=2, num_key_value_heads=2))
+    wrapped = _fake_peft_wrap(hf, 2, 4.0, ("q_proj",))
+    wrapped.peft_config["default"].use_dora = True
+    with pytest.raises(NotImplementedError, match="DoRA"):
+        patches.apply_model_patches(wrapped)
+    wrapped.peft_config["default"].use_dora = False
+    wrapped.peft_config["default"].lora_dropout = 0.1
+    with pytest.raises(NotImplementedError, match="dropout"):
+        patches.convert_peft_model(wrapped)
+    with pytest.raises(ValueError, match="adapter"):
+        wrapped.peft_config["default"].lora_dropout = 0.0
+        patches.convert_peft_model(wrapped, adapter_name="other")
+
+
+@pytest.mark.parametrize("family", ["llama", "cohere"])
+def test_peft_adapter_files_round_trip(family, tmp_path):
+    """Export writes the adapter under the PEFT library's names and row order (equal, tensor by tensor, to what the wrapped
+    Hugging Face model holds); loading those files into a freshly converted base model reproduces the logits."""
+    import json
+    import transformers as T
+    from opaque_b200 import patches
+    torch.manual_seed(1)
+    common = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, max_position_embeddings=64)
+    cls, cfg = ((T.CohereForCausalLM, T.CohereConfig(**common, pad_token_id=0)) if family == "cohere"
+                else (T.LlamaForCausalLM, T.LlamaConfig(**common)))
+    hf = cls(cfg).eval()
+    base_sd = {k: v.clone() for k, v in hf.state_dict().items()}
+    wrapped = _fake_peft_wrap(hf, 4, 8.0, ("q_proj", "k_proj", "v_proj"))
+    ours = patches.apply_model_patches(wrapped, dtype=torch.float32).eval()
+    out = patches.export_peft_adapter(ours, str(tmp_path / "adapter"), base_model_name_or_path="tiny")
+    saved = patches.peft_adapter_state_dict(ours)
+    theirs = {"base_model.model." + k.replace(".default.", "."): v for k, v in hf.state_dict().items() if ".lora_" in k}
+    assert sorted(saved) == sorted(theirs)
+    for k in saved:
+        assert torch.allclose(saved[k], theirs[k]), k
+    cfg_json = json.load(open(tmp_path / "adapter" / "adapter_config.json"))
+    assert cfg_json["r"] == 4 and cfg_json["lora_alpha"] == 8.0 and cfg_json["target_modules"] == ["k_proj", "q_proj", "v_proj"]
+    fresh_hf = cls(cfg).eval()
+    fresh_hf.load_state_dict(base_sd)
+    fresh = patches.apply_model_patches(fresh_hf, dtype=torch.float32).eval()
+    patches.load_peft_adapter(fresh, out)
+    ids = torch.randint(0, 320, (2, 16))
+    with torch.no_grad():
+        assert torch.allclose(fresh(ids), ours(ids), atol=1e-5)
+        assert float((fresh(ids)[..., :320] - wrapped(ids).logits).abs().max()) < 1e-3

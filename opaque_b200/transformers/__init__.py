@@ -2,8 +2,9 @@
 
 Parity: packages/opaque-transformers/src/opaque/transformers/__init__.py.
 """
-from . import trl
+from . import evaluation, trl
+from .evaluation import EvalPrediction, EvaluationResult
 from .trainer import DPTrainer, DPTrainerState, TrainerCallback
 from .training_args import TrainingArguments
 
-__all__ = ["DPTrainer", "DPTrainerState", "TrainerCallback", "TrainingArguments", "trl"]
+__all__ = ["DPTrainer", "DPTrainerState", "EvalPrediction", "EvaluationResult", "TrainerCallback", "TrainingArguments", "evaluation", "trl"]

@@ -43,7 +43,8 @@ import torch.distributed as dist
 from .. import accounting as acc
 from .. import optimizers as optim_lib
 from .. import scheduling as sched
-from ..distributed import (get_rank, get_world_size, is_distributed, local_shard, reduce_scalar, sum_gradients_, sync)
+from ..distributed import (gather_tensors, get_rank, get_world_size, is_distributed, local_shard, reduce_scalar, sum_gradients_,
+                           sync)
 from ..dpftrl import accounting as ftrl_acc
 from ..dpftrl import noise as ftrl_noise
 from ..dpftrl.sampling import BallsInBinsSampler, BMinSepSampler, CyclicPoissonSampler, SequentialBatchSampler
@@ -55,6 +56,8 @@ from ..functional import make_functional
 from ..profiling import perf_tracker
 from ..random import RngKey, fold_in, key
 from ..serialization import from_state_dict, state_dict
+from .evaluation import (EvalPrediction, EvaluationResult, PredictionAccumulator, PredictionOutput, speed_metrics, to_python,
+                         with_metric_prefix)
 from .training_args import MECHANISMS_DPFTRL, TrainingArguments
 
 DP_STATE_BUNDLE_VERSION = 3
@@ -200,13 +203,6 @@ class BestModelSaveCallback(TrainerCallback):
             control.should_save = True
             if args.output_dir:            # the training loop writes this checkpoint right after the evaluation
                 state.best_model_checkpoint = os.path.join(args.output_dir, f"checkpoint-{state.global_step}")
-
-
-@dataclasses.dataclass
-class PredictionOutput:
-    predictions: Any
-    label_ids: Any
-    metrics: dict[str, float]
 
 
 @dataclasses.dataclass
@@ -499,8 +495,14 @@ class DPTrainer:
                 f.write(text)
         return text
 
-    def push_to_hub(self, *_: Any, **__: Any) -> None:
-        raise RuntimeError("no network access: save_model() writes the same files locally for a later upload")
+    def push_to_hub(self, commit_message: str | None = "End of training", blocking: bool = True, token: str | None = None,
+                    revision: str | None = None, **kwargs: Any) -> Any:
+        """Save the model and its model card into ``output_dir`` and upload that folder to the Hub in one commit
+        (``hub_model_id`` / ``hub_token`` / ``hub_private_repo`` / ``hub_revision``).  Checkpoint folders and run-state files
+        (noise and sampler keys) are never uploaded; see :mod:`opaque_b200.transformers.hub`.  ``self.hub_client`` (or
+        ``client=``) replaces ``huggingface_hub.HfApi``."""
+        from . import hub
+        return hub.push_to_hub(self, commit_message, blocking, token, revision, **kwargs)
 
     def _call(self, hook: str, **kw: Any) -> None:
         for cb in self.callbacks:
@@ -672,9 +674,9 @@ class DPTrainer:
         return float(res.param)
 
     # fields that exist for call-compatibility with Hugging Face argument sets and have no effect here
-    _INERT_FIELDS = ("overwrite_output_dir", "eval_accumulation_steps", "log_level_replica", "log_on_each_node",
+    _INERT_FIELDS = ("overwrite_output_dir", "log_level_replica", "log_on_each_node",
                      "save_on_each_node", "restore_callback_states_from_checkpoint", "use_mps_device", "bf16_full_eval",
-                     "local_rank", "eval_do_concat_batches", "include_for_metrics", "average_tokens_across_devices",
+                     "local_rank", "average_tokens_across_devices",
                      "ignore_data_skip", "dataloader_num_workers", "dataloader_persistent_workers",
                      "dataloader_prefetch_factor", "dataloader_multiprocessing_context", "dataloader_in_order",
                      "dataloader_drop_last", "remove_unused_columns", "label_names", "disable_tqdm", "trackio_space_id",
@@ -684,11 +686,13 @@ class DPTrainer:
 
     def inert_arguments(self) -> dict[str, Any]:
         """Arguments that were set away from their default but change nothing in this trainer (data loading is
-        index-based inside the DP sampler, there is no hub client, no tracing compiler on the hot path)."""
+        index-based inside the DP sampler, the hub fields act only with ``push_to_hub``, no tracing compiler on the hot
+        path)."""
         defaults = {f.name: (f.default if f.default is not dataclasses.MISSING else f.default_factory())
                     for f in dataclasses.fields(type(self.args)) if f.name in self._INERT_FIELDS}
+        acting = {"hub_model_id", "hub_token", "hub_private_repo", "hub_revision"} if self.args.push_to_hub else set()
         return {k: getattr(self.args, k) for k, d in defaults.items()
-                if getattr(self.args, k) != d and (getattr(self.args, k) or d)}       # None and {} both mean unset
+                if k not in acting and getattr(self.args, k) != d and (getattr(self.args, k) or d)}       # None and {} both mean unset
 
     def _apply_runtime_flags(self) -> None:
         a = self.args
@@ -1078,6 +1082,8 @@ class DPTrainer:
         if a.load_best_model_at_end:
             self._load_best_model()
         self._call("on_train_end")
+        if a.push_to_hub:
+            self.push_to_hub(commit_message="End of training")
         return out
 
     def _load_best_model(self) -> None:
@@ -1111,28 +1117,90 @@ class DPTrainer:
 
     # ---- evaluation ---------------------------------------------------------------------------------
     @torch.no_grad()
+    def evaluation_loop(self, dataset: Any, description: str = "Evaluation", prediction_loss_only: bool | None = None,
+                        metric_key_prefix: str = "eval") -> EvaluationResult:
+        """One pass over ``dataset`` on THIS rank: per-example losses always, predictions / labels / inputs unless
+        ``prediction_loss_only``.  Batches stay on the device and move to host memory every ``eval_accumulation_steps``
+        batches; ``eval_do_concat_batches=False`` hands ``compute_metrics`` the per-batch list;
+        ``include_for_metrics=["inputs", "loss"]`` adds ``inputs`` / ``losses`` to the :class:`EvalPrediction`.  The
+        metrics here are this rank's (``{prefix}_loss`` = mean per-example loss); :meth:`evaluate` combines ranks."""
+        a = self.args
+        loss_only = a.prediction_loss_only if prediction_loss_only is None else prediction_loss_only
+        want = set(a.include_for_metrics or [])
+        acc_ = PredictionAccumulator(prediction_loss_only=loss_only, eval_accumulation_steps=a.eval_accumulation_steps,
+                                     eval_do_concat_batches=a.eval_do_concat_batches, include_inputs="inputs" in want,
+                                     include_losses="loss" in want)
+        if self.engine_kind == "reference" if hasattr(self, "engine_kind") else False:
+            self._write_back()
+        was_training = self.model.training
+        self.model.eval()
+        bs = a.eval_batch_size
+        tokens = 0
+        for lo in range(0, len(dataset), bs):
+            batch = self._to_device(self.data_collator([dataset[i] for i in range(lo, min(len(dataset), lo + bs))]))
+            has_labels = "labels" in batch
+            losses = self.compute_batch_per_example_loss(batch) if has_labels else None
+            logits = None
+            if not loss_only:
+                logits = self.model(batch["input_ids"])
+                logits = getattr(logits, "logits", logits)
+                if self.preprocess_logits_for_metrics is not None:
+                    logits = self.preprocess_logits_for_metrics(logits, batch.get("labels"))
+            acc_.add(losses, logits, batch.get("labels"), batch.get("input_ids"))
+            tokens += int((batch["labels"] != -100).sum()) if has_labels else 0
+        self.model.train(was_training)
+        losses, preds, labels, inputs = acc_.finalize()
+        metrics: dict[str, float] = {}
+        if losses is not None and losses.numel():
+            metrics[f"{metric_key_prefix}_loss"] = float(losses.mean())
+        res = EvaluationResult(preds, labels, metrics, acc_.num_samples)
+        res.losses, res.inputs, res.tokens = losses, inputs, tokens           # for evaluate / predict
+        res.num_batches, res.offloads = acc_.num_batches, acc_.offloads
+        return res
+
+    def _metrics_from(self, res: EvaluationResult, prefix: str, gather: bool) -> dict[str, float]:
+        """Run the user's ``compute_metrics`` on the collected predictions (gathered over ranks when the data was sharded)."""
+        if self.compute_metrics is None or res.predictions is None or res.label_ids is None:
+            return {}
+        want = set(self.args.include_for_metrics or [])
+        preds, labels, inputs, losses = res.predictions, res.label_ids, res.inputs, res.losses
+        if gather and self.args.world_size > 1:
+            if not self.args.eval_do_concat_batches:
+                raise ValueError("eval_do_concat_batches=False with several ranks: per-batch lists are not gathered; "
+                                 "call evaluation_loop on each rank instead")
+            preds, labels = self._gather_padded(preds), self._gather_padded(labels)
+            inputs = self._gather_padded(inputs) if inputs is not None else None
+            losses = gather_tensors(losses.to(self.device)).cpu() if losses is not None else None
+        out = self.compute_metrics(EvalPrediction(preds, labels, inputs if "inputs" in want else None,
+                                                  losses if "loss" in want else None))
+        return with_metric_prefix(to_python(dict(out)), prefix)
+
+    def _gather_padded(self, t: torch.Tensor) -> torch.Tensor:
+        """``gather_tensors`` for predictions whose trailing sizes differ between ranks (padded with -100 to the largest)."""
+        if not isinstance(t, torch.Tensor):
+            raise ValueError("only tensor predictions are gathered over ranks")
+        tail = [int(reduce_scalar(int(t.shape[d]), "max")) for d in range(1, t.ndim)]
+        if list(t.shape[1:]) != tail:
+            wide = t.new_full((t.shape[0], *tail), -100)
+            wide[(slice(None),) + tuple(slice(0, n) for n in t.shape[1:])] = t
+            t = wide
+        return gather_tensors(t.to(self.device)).cpu()
+
+    @torch.no_grad()
     def evaluate(self, eval_dataset: Any = None, ignore_keys=None, metric_key_prefix: str = "eval") -> dict[str, float]:
         data = eval_dataset if eval_dataset is not None else self.eval_dataset
         if data is None:
             raise ValueError("evaluation needs an eval_dataset")
         a = self.args
-        if self.engine_kind == "reference" if hasattr(self, "engine_kind") else False:
-            self._write_back()
+        start = time.time()
         shard = local_shard(data, rank=a.process_index, world_size=a.world_size)
-        was_training = self.model.training
-        self.model.eval()
-        total, count, tokens = 0.0, 0, 0
-        bs = a.eval_batch_size
-        for lo in range(0, len(shard), bs):
-            batch = self._to_device(self.data_collator([shard[i] for i in range(lo, min(len(shard), lo + bs))]))
-            losses = self.compute_batch_per_example_loss(batch)
-            total += float(losses.float().sum())
-            count += int(losses.numel())
-            tokens += int((batch["labels"] != -100).sum()) if "labels" in batch else 0
-        self.model.train(was_training)
-        total = float(reduce_scalar(total, "sum"))
-        count = int(reduce_scalar(count, "sum"))
+        res = self.evaluation_loop(shard, "Evaluation", metric_key_prefix=metric_key_prefix)
+        total = float(reduce_scalar(float(res.losses.sum()) if res.losses is not None else 0.0, "sum"))
+        count = int(reduce_scalar(int(res.losses.numel()) if res.losses is not None else 0, "sum"))
+        tokens = int(reduce_scalar(res.tokens, "sum"))
         metrics = {f"{metric_key_prefix}_loss": total / max(count, 1), f"{metric_key_prefix}_samples": float(count)}
+        metrics.update(self._metrics_from(res, metric_key_prefix, gather=True))
+        metrics.update(speed_metrics(metric_key_prefix, start, num_samples=count, num_steps=res.num_batches, num_tokens=tokens or None))
         if self.accountant is not None and self.state.global_step:
             metrics["epsilon"] = self.epsilon()
         self.log(metrics)
@@ -1141,26 +1209,15 @@ class DPTrainer:
 
     @torch.no_grad()
     def predict(self, test_dataset: Any, ignore_keys=None, metric_key_prefix: str = "test") -> PredictionOutput:
-        self.model.eval()
-        preds, labels, losses = [], [], []
-        bs = self.args.eval_batch_size
-        for lo in range(0, len(test_dataset), bs):
-            batch = self._to_device(self.data_collator([test_dataset[i] for i in range(lo, min(len(test_dataset), lo + bs))]))
-            logits = self.model(batch["input_ids"])
-            logits = getattr(logits, "logits", logits)
-            if self.preprocess_logits_for_metrics is not None:
-                logits = self.preprocess_logits_for_metrics(logits, batch.get("labels"))
-            if not self.args.prediction_loss_only:
-                preds.append(logits.float().cpu())
-            if "labels" in batch:
-                labels.append(batch["labels"].cpu())
-                losses.append(self.compute_batch_per_example_loss(batch).float().cpu())
-        p = torch.cat(preds) if preds and all(x.shape[1:] == preds[0].shape[1:] for x in preds) else preds
-        l = torch.cat(labels) if labels and all(x.shape[1:] == labels[0].shape[1:] for x in labels) else labels
-        metrics = {f"{metric_key_prefix}_loss": float(torch.cat(losses).mean())} if losses else {}
-        if self.compute_metrics is not None and labels and not self.args.prediction_loss_only:
-            metrics.update({f"{metric_key_prefix}_{k}": v for k, v in self.compute_metrics((p, l)).items()})
-        return PredictionOutput(None if self.args.prediction_loss_only else p, l, metrics)
+        start = time.time()
+        res = self.evaluation_loop(test_dataset, "Prediction", metric_key_prefix=metric_key_prefix)
+        metrics = dict(res.metrics)
+        metrics.update(self._metrics_from(res, metric_key_prefix, gather=False))
+        metrics.update(speed_metrics(metric_key_prefix, start, num_samples=res.num_samples, num_steps=res.num_batches))
+        for cb in self.callbacks:
+            if hasattr(cb, "on_predict"):
+                cb.on_predict(self.args, self.state, self.control, metrics=metrics, model=self.model)
+        return EvaluationResult(res.predictions, res.label_ids, metrics, res.num_samples)
 
     # ---- checkpoints ----------------------------------------------------------------------------------
     def save_model(self, output_dir: str | None = None) -> None:
@@ -1350,6 +1407,7 @@ def _barrier() -> None:
         dist.barrier()
 
 
-__all__ = ["BestModelSaveCallback", "DPTrainer", "DPTrainerState", "DP_STATE_BUNDLE_VERSION", "PredictionOutput",
+__all__ = ["BestModelSaveCallback", "DPTrainer", "DPTrainerState", "DP_STATE_BUNDLE_VERSION", "EvalPrediction", "EvaluationResult",
+           "PredictionAccumulator", "PredictionOutput",
            "PrinterCallback", "RuntimeCheckpoint", "TrainerCallback", "TrainerControl", "build_lr_schedule",
            "build_optimizer", "build_strategy", "default_per_example_loss", "list_checkpoints", "rotate_checkpoints"]

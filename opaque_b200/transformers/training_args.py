@@ -184,6 +184,13 @@ class TrainingArguments:
                      "noise_calibration_kwargs", "optim_args", "performance_kernels_config",
                      "gradient_checkpointing_kwargs"):
             setattr(self, name, parse_dict_field(getattr(self, name), name))
+        if isinstance(self.include_for_metrics, str):
+            self.include_for_metrics = [x for x in self.include_for_metrics.replace(",", " ").split() if x]
+        unknown = sorted(set(self.include_for_metrics or []) - {"inputs", "loss"})
+        if unknown:
+            raise ValueError(f"include_for_metrics takes 'inputs' and / or 'loss'; got {unknown}")
+        if self.eval_accumulation_steps is not None and int(self.eval_accumulation_steps) < 1:
+            raise ValueError("eval_accumulation_steps must be a positive number of batches")
         if isinstance(self.clipping_norm, str):
             try:
                 self.clipping_norm = float(self.clipping_norm)

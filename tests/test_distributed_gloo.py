@@ -224,3 +224,50 @@ def test_leave_notice_is_seen_on_the_host_before_the_next_step():
     with pytest.raises(PeerLeftError, match="preempted"):
         a.check()
     assert c.left() == [1] and b.left() == []
+
+
+class _EvalLM(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.emb = torch.nn.Embedding(32, 8)
+        self.head = torch.nn.Linear(8, 32)
+
+    def forward(self, ids):
+        return self.head(self.emb(ids))
+
+
+def _eval_once(rank, world):
+    from opaque_b200.transformers import DPTrainer, TrainingArguments
+    torch.manual_seed(0)
+    g = torch.Generator().manual_seed(4)
+    # ragged: the second half of the set is longer, so the two ranks' shards are padded to different lengths
+    data = [{"input_ids": torch.randint(0, 32, (6 if i < 7 else 10,), generator=g).tolist()} for i in range(14)]
+    seen = {}
+
+    def metrics(ep):
+        seen["shape"] = tuple(ep.predictions.shape)
+        keep = ep.label_ids != -100
+        return {"labelled_tokens": int(keep.sum()), "loss_mean": float(ep.losses.mean())}
+
+    args = TrainingArguments(output_dir=None, use_cpu=True, privacy_noise_multiplier=1.0, per_device_eval_batch_size=3,
+                             eval_accumulation_steps=1, include_for_metrics=["loss"], seed=1)
+    tr = DPTrainer(model=_EvalLM(), args=args, train_dataset=data, eval_dataset=data, compute_metrics=metrics)
+    out = tr.evaluate()
+    return {"shape": seen["shape"], "tokens": out["eval_labelled_tokens"], "loss": out["eval_loss"], "loss_mean": out["eval_loss_mean"],
+            "samples": out["eval_samples"]}
+
+
+def w_trainer_evaluate(rank, world):
+    return _eval_once(rank, world)
+
+
+def test_two_rank_evaluation_gathers_predictions_for_compute_metrics():
+    """Each rank evaluates its shard; ``compute_metrics`` gets ALL predictions (shards padded to a common length and gathered)."""
+    res = run_ranks("w_trainer_evaluate")
+    assert all(s == "ok" for s, _ in res.values()), res
+    single = _eval_once(0, 1)
+    for r in (0, 1):
+        got = res[r][1]
+        assert got["shape"] == (14, 10, 32) == single["shape"] and got["samples"] == 14.0
+        assert got["tokens"] == single["tokens"]
+        assert abs(got["loss"] - single["loss"]) < 1e-5 and abs(got["loss_mean"] - single["loss_mean"]) < 1e-5

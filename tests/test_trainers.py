@@ -366,3 +366,119 @@ def test_dp_state_bundle_is_a_plain_dict_with_the_reference_field_names(tmp_path
             sys.modules.pop(m, None)
     got = load_runtime_checkpoint(foreign)                    # the reference's class is NOT importable here
     assert got.noise_multiplier == raw["noise_multiplier"] and got.sampler_state == raw["sampler_state"] and got.extras == {}
+
+
+def test_prediction_accumulator_offload_cadence_padding_and_lists():
+    from opaque_b200.transformers.evaluation import (EvalPrediction, PredictionAccumulator, speed_metrics, with_metric_prefix)
+    g = torch.Generator().manual_seed(0)
+    batches = [(torch.rand(3, generator=g), torch.randn(3, T, 5, generator=g), torch.randint(0, 5, (3, T), generator=g))
+               for T in (4, 6, 6, 5, 4)]
+    acc = PredictionAccumulator(eval_accumulation_steps=2, include_inputs=True, include_losses=True)
+    for loss, logits, labels in batches:
+        acc.add(loss, logits, labels, inputs=labels)
+    assert acc.offloads == 2 and acc.num_samples == 15 and len(acc.logits.pending) == 1 and len(acc.logits.host) == 2
+    losses, preds, labels, inputs = acc.finalize()
+    assert preds.shape == (15, 6, 5) and labels.shape == (15, 6) and losses.shape == (15,)
+    assert torch.equal(preds[:3, :4], batches[0][1]) and bool((preds[:3, 4:] == -100).all())       # ragged tails hold -100
+    assert torch.equal(labels[9:12, :5], batches[3][2]) and bool((labels[9:12, 5:] == -100).all())
+    assert torch.equal(losses, torch.cat([b[0] for b in batches]))
+    ep = acc.eval_prediction()
+    p, l, i, ls = ep                                    # unpacks in the Hugging Face order
+    assert p is ep.predictions and l is ep.label_ids and torch.equal(i, labels) and len(ep) == 4
+    # per-batch lists instead of one tensor; a scalar (mean-reduced) loss counts once per example
+    acc = PredictionAccumulator(eval_do_concat_batches=False)
+    for loss, logits, labels in batches:
+        acc.add(loss.mean(), logits, labels)
+    losses, preds, labels, _ = acc.finalize()
+    assert isinstance(preds, list) and len(preds) == 5 and preds[1].shape == (3, 6, 5) and losses.shape == (15,)
+    assert torch.allclose(losses[:3], batches[0][0].mean().repeat(3))
+    # loss only: nothing else is kept
+    acc = PredictionAccumulator(prediction_loss_only=True)
+    acc.add(batches[0][0], batches[0][1], batches[0][2])
+    assert acc.finalize()[1:] == (None, None, None) and not acc.logits.pending
+    with pytest.raises(ValueError):
+        PredictionAccumulator(eval_accumulation_steps=0)
+    assert with_metric_prefix({"accuracy": 1.0, "eval_loss": 2.0, "epsilon": 3.0}, "eval") == {"eval_accuracy": 1.0, "eval_loss": 2.0, "epsilon": 3.0}
+    import time
+    sm = speed_metrics("eval", time.time() - 2.0, num_samples=10, num_steps=4)
+    assert 4.5 < sm["eval_samples_per_second"] < 5.5 and "eval_steps_per_second" in sm and sm["eval_runtime"] >= 2.0
+
+
+def test_evaluate_and_predict_feed_compute_metrics(tmp_path):
+    """``compute_metrics`` sees all predictions of the evaluation set (whatever ``eval_accumulation_steps``), with inputs and
+    per-example losses when ``include_for_metrics`` asks; results come back prefixed, with speed entries."""
+    torch.manual_seed(0)
+    data, held_out = _data(), _data(20, seed=9)
+    seen = {}
+
+    def metrics(ep):
+        preds, labels = ep.predictions, ep.label_ids      # (a 2-tuple unpacking works only without inputs / losses, as in Hugging Face)
+        seen.update(shape=tuple(preds.shape), inputs=ep.inputs, losses=ep.losses)
+        pred_ids = preds.argmax(-1)[:, :-1]
+        mask = labels[:, :-1] != -100 if labels.shape[1] == preds.shape[1] else torch.ones_like(pred_ids, dtype=torch.bool)
+        return {"accuracy": float((pred_ids == labels[:, :pred_ids.shape[1]])[mask].float().mean()), "eval_custom": torch.tensor(2.0)}
+
+    args = _args(tmp_path, save_steps=0, max_steps=2, per_device_eval_batch_size=6, eval_accumulation_steps=2,
+                 include_for_metrics=["inputs", "loss"])
+    tr = DPTrainer(model=TinyLM(), args=args, train_dataset=data, eval_dataset=held_out, compute_metrics=metrics)
+    assert tr.inert_arguments() == {}
+    tr.train()
+    out = tr.evaluate()
+    assert seen["shape"] == (20, 12, 32) and seen["inputs"].shape == (20, 12) and seen["losses"].shape == (20,)
+    assert 0.0 <= out["eval_accuracy"] <= 1.0 and out["eval_custom"] == 2.0 and out["eval_samples"] == 20.0
+    assert math.isclose(out["eval_loss"], float(seen["losses"].mean()), rel_tol=1e-5)
+    assert out["eval_runtime"] >= 0 and "eval_samples_per_second" in out and "eval_steps_per_second" in out
+    pred = tr.predict(held_out)
+    assert pred.predictions.shape == (20, 12, 32) and pred.num_samples == 20 and "test_accuracy" in pred.metrics and "test_loss" in pred.metrics
+    res = tr.evaluation_loop(held_out, prediction_loss_only=True)
+    assert res.predictions is None and res.num_batches == 4 and res.offloads >= 2
+    with pytest.raises(ValueError, match="include_for_metrics"):
+        _args(tmp_path, include_for_metrics=["logits"])
+
+
+def test_push_to_hub_uploads_the_model_folder_without_run_state(tmp_path):
+    """``push_to_hub`` through a stand-in client: repository created once, ONE folder upload whose ignore list keeps every
+    checkpoint folder and run-state file (noise / sampler keys) off the Hub; the model card carries the privacy line."""
+    import fnmatch
+    import types
+    from opaque_b200.transformers import hub
+
+    class FakeHub:
+        def __init__(self):
+            self.created, self.uploads = [], []
+
+        def create_repo(self, repo_id, token=None, private=None, exist_ok=False):
+            self.created.append((repo_id, token, private, exist_ok))
+            return types.SimpleNamespace(repo_id=f"someone/{repo_id}" if "/" not in repo_id else repo_id)
+
+        def upload_folder(self, **kw):
+            sent = []
+            for root, _dirs, files in os.walk(kw["folder_path"]):
+                for f in files:
+                    rel = os.path.relpath(os.path.join(root, f), kw["folder_path"])
+                    if not any(fnmatch.fnmatch(rel, pat) for pat in kw["ignore_patterns"]):
+                        sent.append(rel)
+            self.uploads.append({**kw, "sent": sorted(sent)})
+            return types.SimpleNamespace(commit_message=kw["commit_message"])
+
+    torch.manual_seed(0)
+    args = _args(tmp_path / "my-model", max_steps=4, save_steps=2, push_to_hub=True, hub_token="tok", hub_private_repo=True,
+                 hub_revision="dev")
+    tr = DPTrainer(model=TinyLM(), args=args, train_dataset=_data())
+    tr.hub_client = FakeHub()
+    assert tr.inert_arguments() == {}                       # with push_to_hub the hub_* fields act
+    tr.train()                                              # pushes at the end
+    api = tr.hub_client
+    assert api.created == [("my-model", "tok", True, True)] and tr.hub_repo_id == "someone/my-model"
+    up = api.uploads[-1]
+    assert up["repo_id"] == "someone/my-model" and up["revision"] == "dev" and up["token"] == "tok" and up["run_as_future"] is False
+    assert up["commit_message"] == "End of training"
+    assert os.path.isdir(tmp_path / "my-model" / "checkpoint-4")                 # checkpoints exist locally ...
+    assert not any(s.startswith("checkpoint-") or s.endswith((".pt", ".pth")) for s in up["sent"]), up["sent"]   # ... and stay there
+    assert "README.md" in up["sent"] and any(s.endswith((".safetensors", ".bin")) for s in up["sent"])
+    card = open(tmp_path / "my-model" / "README.md").read()
+    assert "privacy guarantee" in card and "my-model" in card
+    tr.push_to_hub("second push", blocking=False)
+    assert len(api.created) == 1 and api.uploads[-1]["run_as_future"] is True and api.uploads[-1]["commit_message"] == "second push"
+    assert set(hub.NEVER_UPLOADED) >= {"checkpoint-*", "dp_state.pt", "optimizer.pt", "rng_state*.pth"}
+    assert hub.resolve_repo_id(types.SimpleNamespace(hub_model_id="org/name", output_dir="x")) == "org/name"

@@ -83,11 +83,22 @@ class Capture:
         dev = engine.device
         sp = engine.space
         self.pe = engine.pe_buffer(batch_size)
-        self.parts = torch.zeros(self.MAX_GHOST, batch_size, dtype=torch.float32, device=dev)
+        # the norm rows and the segment table are kept per (microbatch, tokens) shape and reused by later microbatches of
+        # that shape (one memset instead of an allocation, a fill and an arange); inside a CUDA-graph capture the buffers
+        # must belong to the graph, so nothing is shared there
+        cache = getattr(engine, "_capture_buffers", None)
+        reuse = cache is not None and not (dev.type == "cuda" and torch.cuda.is_current_stream_capturing())
+        held = cache.get((batch_size, tokens_per_example)) if reuse else None
+        if held is None:
+            held = (torch.zeros(self.MAX_GHOST, batch_size, dtype=torch.float32, device=dev),
+                    torch.arange(0, (batch_size + 1) * tokens_per_example, tokens_per_example, dtype=torch.int32, device=dev))
+            if reuse:
+                cache[(batch_size, tokens_per_example)] = held
+        else:
+            held[0].zero_()
+        self.parts, self.seg = held
         self.part_slots: list[str] = []
         self.records: list[tuple] = []
-        self.seg = torch.arange(0, (batch_size + 1) * tokens_per_example, tokens_per_example, dtype=torch.int32,
-                                device=dev)
         self.status = engine.status
         self.direct_elems = sp.direct_elems
 
@@ -260,7 +271,14 @@ class Capture:
                 ops.clip_weighted_sum(self.pe[:, lo:hi], scales[g], tgt["out"], flat_offset=lo,
                                       peer_table=tgt["peer_table"], shard_elems=tgt["shard_elems"])
         if self.records:
-            row_scale = {g: c.repeat_interleave(self.tokens) for g, c in scales.items()}
+            expanded: dict[str, torch.Tensor] = {}
+
+            class _RowScale:                      # per-row factors, formed only for the record kinds that need them
+                def __getitem__(_, g: str) -> torch.Tensor:
+                    if g not in expanded:
+                        expanded[g] = scales[g].repeat_interleave(self.tokens)
+                    return expanded[g]
+            row_scale = _RowScale()
             for kind, slot, g2d, other in self.records:
                 g = label_of(slot.name)
                 if kind == "grouped":
@@ -730,6 +748,7 @@ class FusedDPEngine:
         named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
         self._named_trainable = named
         self._coverage_checked = False
+        self._capture_buffers: dict[tuple[int, int], tuple[torch.Tensor, torch.Tensor]] = {}
         if not named:
             raise ValueError("the model has no trainable parameters")
         if isinstance(clipping_norm, Mapping):

@@ -14,6 +14,16 @@ PRESETS: dict[str, dict[str, dict]] = {
         "smoke": dict(steps=10, n=2048, batch=64, sigma=1.0, lr=0.1),
         "mlp-60k": dict(steps=200, n=60000, batch=256, clip=1.0, sigma=1.0, lr=0.1, delta=1e-5),     # benchmark config 1
     },
+    "train_dpsgd_lm": {
+        "smoke": dict(model="tiny", num_train_samples=256, num_eval_samples=32, max_seq_len=16, batch_size=32, steps=4,
+                      noise_multiplier=1.0, log_steps=2, microbatch_size=16),
+        "lora-eps8": dict(model="small", lora_r=8, num_train_samples=4096, max_seq_len=128, batch_size=256, num_epochs=3.0,
+                          target_epsilon=8.0, target_delta=1e-5, learning_rate=1e-3, lr_warmup_steps=5, eval_steps=16),
+        "full-auto-clip": dict(model="small", num_train_samples=4096, max_seq_len=128, batch_size=256, num_epochs=2.0,
+                               clipping_mode="auto", noise_multiplier=0.8, optimizer="adamw-bc", learning_rate=5e-4),
+        "b200-fused": dict(model="base", engine="fused", dtype="bfloat16", lora_r=16, num_train_samples=16384, max_seq_len=512,
+                           batch_size=512, microbatch_size=8, steps=50, target_epsilon=8.0, eval_steps=25),
+    },
     "train_dpftrl": {
         "smoke": dict(steps=8, n=512, batch=16, seq=8),
         "blt-4": dict(strategy="blt", buffers=4, sampler="sequential", steps=64, batch=32, sigma=2.0),

@@ -9,6 +9,7 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CASES = {
     "train_dpsgd.py": ["--steps", "3", "--n", "2000"],
+    "train_dpsgd_lm.py": ["--preset", "smoke"],
     "train_dpftrl.py": ["--steps", "4", "--n", "256"],
     "train_sft.py": ["--steps", "2", "--n", "64"],
     "train_dpo.py": ["--steps", "2", "--n", "64"],

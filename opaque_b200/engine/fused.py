@@ -48,6 +48,7 @@ from torch.autograd import Function
 from .. import ops
 from ..parallel.peer import PeerGroup
 from ..parallel.sharded import DPStepConfig, FlatSpace, ShardedDPOptimizer
+from ..profiling import trace_range
 from ..random import RngKey
 
 _ACTIVE: "Capture | None" = None
@@ -834,7 +835,7 @@ class FusedDPEngine:
         if not self._coverage_checked:
             for _, p in self._named_trainable:          # stale gradients of earlier, non-private use would trip the check below
                 p.grad = None
-        with activate(cap):
+        with trace_range("opaque::fused/microbatch"), activate(cap):
             per_example = loss_fn(**sub)
             per_example.sum().backward()
         if not self._coverage_checked:
@@ -848,7 +849,8 @@ class FusedDPEngine:
                                    "RMSNorm, LayerNorm, LoRA, MoE experts) and cannot be clipped per example: "
                                    + ", ".join(stray[:8]) + (" ..." if len(stray) > 8 else "")
                                    + "; freeze them or use the reference engine")
-        out = cap.finalize(self.clipping_norm, mode=self.clipping_mode, gamma=self.gamma)
+        with trace_range("opaque::fused/clip"):
+            out = cap.finalize(self.clipping_norm, mode=self.clipping_mode, gamma=self.gamma)
         return per_example.detach().float(), out
 
     def _graphed_microbatch(self, loss_fn, sub: dict[str, torch.Tensor], mb: int):
@@ -947,7 +949,8 @@ class FusedDPEngine:
         """Second half of :meth:`step`: add noise to the accumulated clipped sum and update the parameters."""
         sens = self.sensitivity()
         sigma = 0.0 if self.noise_multiplier == 0 else self.noise_multiplier * sens
-        self.opt.step(noise_std=sigma, normalize_by=self.normalize_by)
+        with trace_range("opaque::fused/shard_step"):
+            self.opt.step(noise_std=sigma, normalize_by=self.normalize_by)
         if read_metrics and res.batch_size:
             stats = torch.stack([res.losses.mean(), res.norms.mean(),
                                  (res.norms > sens).float().mean()]).tolist()   # one D2H read

@@ -7,7 +7,8 @@ context exits (one synchronise per step, none per mark); on CPU it falls back
 to ``perf_counter``.  ``PerfState`` folds steps (the first ``warmup_steps`` are
 excluded from throughput), ``PerfTracker`` keeps one state per stage, and
 ``sync(PerfState)`` reduces across ranks as time = max, samples = sum,
-peak memory = max.
+peak memory = max.  ``trace_range`` names a phase for the PyTorch profiler (and NVTX when enabled), ``trace`` collects
+a Chrome trace of a few steps.
 
 Parity: packages/opaque-engine/src/opaque/api/engine/profiling/_memory.py:374-436, :689;
 _distributed.py.
@@ -32,6 +33,52 @@ class MemoryStats:
     @property
     def peak_gb(self) -> float:
         return self.peak_allocated_bytes / 2 ** 30
+
+
+_NVTX = {"on": None}      # None: decided by the environment variable OPAQUE_B200_NVTX on first use
+
+
+def enable_nvtx(on: bool = True) -> None:
+    """Also emit NVTX ranges from :func:`trace_range` (visible in Nsight Systems / Nsight Compute timelines)."""
+    _NVTX["on"] = bool(on)
+
+
+def _nvtx_on() -> bool:
+    if _NVTX["on"] is None:
+        import os
+        _NVTX["on"] = os.environ.get("OPAQUE_B200_NVTX", "0") not in ("0", "", "false", "False")
+    return bool(_NVTX["on"]) and torch.cuda.is_available()
+
+
+@contextlib.contextmanager
+def trace_range(name: str):
+    """A named range around a phase: a ``torch.profiler.record_function`` range always (free when no profiler is attached),
+    plus an NVTX range when enabled (``enable_nvtx()`` or ``OPAQUE_B200_NVTX=1``).  The functional API's own ranges
+    (``opaque::clipped_grad``, ``opaque::gaussian_noise``, ``opaque::mf_gaussian_noise``, …) and the fused engine's
+    (``opaque::fused/microbatch``, ``/clip``, ``/shard_step``) all come through here or ``record_function``."""
+    nvtx = _nvtx_on()
+    if nvtx:
+        torch.cuda.nvtx.range_push(name)
+    try:
+        with torch.profiler.record_function(name):
+            yield
+    finally:
+        if nvtx:
+            torch.cuda.nvtx.range_pop()
+
+
+@contextlib.contextmanager
+def trace(path: str | None = None, *, with_stack: bool = False, record_shapes: bool = False):
+    """Collect a ``torch.profiler`` trace of the enclosed steps (CPU activity always, CUDA when available); on exit the
+    Chrome-trace JSON goes to ``path`` when given.  Yields the profiler (``key_averages()`` for a table).  Timings under
+    a profiler are for reading the timeline, never for reporting throughput."""
+    acts = [torch.profiler.ProfilerActivity.CPU]
+    if torch.cuda.is_available():
+        acts.append(torch.profiler.ProfilerActivity.CUDA)
+    with torch.profiler.profile(activities=acts, with_stack=with_stack, record_shapes=record_shapes) as prof:
+        yield prof
+    if path:
+        prof.export_chrome_trace(path)
 
 
 def _is_cuda(device: Any) -> bool:
@@ -210,6 +257,6 @@ def sync_perf_state(state: PerfState) -> PerfState:
         peak_memory_bytes=int(reduce_scalar(state.peak_memory_bytes, "max")), phases=phases)
 
 
-__all__ = ["MemoryStats", "PerfStage", "PerfState", "PerfTracker", "StepPerf", "empty_cache",
+__all__ = ["MemoryStats", "PerfStage", "PerfState", "PerfTracker", "StepPerf", "empty_cache", "enable_nvtx",
            "get_memory_stats", "perf_tracker", "print_memory", "reset_peak_memory", "step_perf",
-           "sync_perf_state"]
+           "sync_perf_state", "trace", "trace_range"]

@@ -191,3 +191,21 @@ def test_step_perf_and_tracker():
     with tr.step("train", batch_size=3):
         pass
     assert tr.state("train").samples == 3
+
+
+def test_trace_range_and_trace_collect_named_phases(tmp_path):
+    """``trace_range`` names a phase for the PyTorch profiler (NVTX stays off without a GPU); ``trace`` writes a Chrome trace."""
+    import json
+    import torch
+    from opaque_b200 import profiling
+    profiling.enable_nvtx(True)                       # without CUDA this must stay a no-op
+    out = tmp_path / "trace.json"
+    with profiling.trace(str(out)) as prof:
+        with profiling.trace_range("opaque::test/outer"):
+            with profiling.trace_range("opaque::test/inner"):
+                torch.ones(8).sum()
+    profiling.enable_nvtx(False)
+    names = {e.key for e in prof.key_averages()}
+    assert {"opaque::test/outer", "opaque::test/inner"} <= names
+    events = json.load(open(out))["traceEvents"]
+    assert any(e.get("name") == "opaque::test/inner" for e in events)

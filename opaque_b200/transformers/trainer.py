@@ -872,6 +872,8 @@ class DPTrainer:
                                     gamma=float(a.clipping_kwargs.get("gamma", 0.01)), group_of=group_of, adaptive=adaptive,
                                     cuda_graph=a.dp_cuda_graph)
         self._graphs_ready = not a.dp_cuda_graph
+        if a.include_sync_metrics:          # CUDA events around barrier / shard step / barrier, read where the step's metrics are read
+            self._fused.opt.timing = []
         # host-side leave notices: a rank that stops between steps tells the others through the rendezvous store, so they
         # raise before their next device barrier instead of waiting for its flag until the bounded wait runs out
         self._liveness = None
@@ -998,7 +1000,12 @@ class DPTrainer:
         n = int(reduce_scalar(res.batch_size, "sum")) if is_distributed() else res.batch_size
         if "labels" in batch:
             self.state.num_input_tokens_seen += int(reduce_scalar(int((batch["labels"] != -100).sum()), "sum"))
-        return {"loss": res.loss if res.batch_size else 0.0, "grad_norm": res.grad_norm_mean if res.batch_size else 0.0,
+        sync_ms = {}
+        if self._fused.opt.timing is not None:
+            sync_ms = {f"sync/{k}": v for k, v in self._fused.opt.timing_ms().items()}
+            sync_ms["sync/exposed_wait_ms"] = sync_ms["sync/grad_barrier_ms"] + sync_ms["sync/param_barrier_ms"]
+            self._fused.opt.timing = []
+        return {**sync_ms, "loss": res.loss if res.batch_size else 0.0, "grad_norm": res.grad_norm_mean if res.batch_size else 0.0,
                 "clip_rate": res.clip_rate if res.batch_size else 0.0, "batch_size": float(n),
                 "noise_std": self.noise_multiplier * self._fused.sensitivity() / self.expected_batch,
                 "clipping_norm": self._fused.sensitivity()}

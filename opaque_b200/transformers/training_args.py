@@ -160,6 +160,7 @@ class TrainingArguments:
     gradient_checkpointing_kwargs: Any = None
     skip_memory_metrics: bool = True
     include_tokens_per_second: bool = False
+    include_sync_metrics: bool = False      # fused engine: log the gradient-barrier / shard-step / parameter-barrier times per step
     include_num_input_tokens_seen: bool = False
     debug: str = ""
     resume_from_checkpoint: str | None = None

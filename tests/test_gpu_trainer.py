@@ -65,6 +65,14 @@ def test_fused_trainer_options(tmp_path, kw):
     assert tr.engine_kind == "fused" and out["global_step"] == 4 and math.isfinite(tr.state.log_history[-2]["loss"])
 
 
+def test_fused_trainer_logs_sync_times_when_asked(tmp_path):
+    from opaque_b200.transformers import DPTrainer
+    tr = DPTrainer(model=_model(), args=_args(tmp_path, save_steps=0, include_sync_metrics=True, logging_steps=1), train_dataset=_rows())
+    tr.train()
+    rows = [r for r in tr.state.log_history if "sync/shard_step_ms" in r]
+    assert rows and all(r["sync/shard_step_ms"] > 0 and r["sync/exposed_wait_ms"] >= 0 for r in rows)
+
+
 def test_fused_trainer_steps_down_after_a_simulated_oom(tmp_path):
     """The failure is injected on the host: the loss raises OutOfMemoryError once for a microbatch of more than 4 rows."""
     from opaque_b200.transformers import DPTrainer

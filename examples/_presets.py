@@ -33,11 +33,15 @@ PRESETS: dict[str, dict[str, dict]] = {
     "train_sft": {
         "smoke": dict(steps=5, n=256, batch=16),
         "dft": dict(steps=40, n=2048, batch=64, loss="dft", sigma=0.8, lr=5e-3),
+        "llama-lora-eps8": dict(model="small", lora_r=8, steps=60, n=4096, eval_n=256, batch=128, microbatch=16, target_epsilon=8.0,
+                                lr=2e-3, lr_schedule="cosine", lr_warmup_steps=5),
     },
     "train_dpo": {
         "smoke": dict(steps=5, n=128, batch=8),
         "ipo": dict(steps=40, n=1024, batch=32, loss_type="ipo", beta=0.1, sigma=0.8),
         "simpo": dict(steps=40, n=1024, batch=32, loss_type="simpo", beta=2.0, sigma=0.8),
+        "llama-lora-eps8": dict(model="small", lora_r=8, steps=60, n=2048, eval_n=128, batch=64, microbatch=8, target_epsilon=8.0,
+                                lr=1e-3, loss_type="sigmoid", beta=0.1),
     },
 }
 

@@ -24,6 +24,7 @@ NEVER_UPLOADED = ("checkpoint-*", "checkpoint-*/**", "_*", "runs/**", "*.tmp", "
 
 
 def default_client() -> Any:
+    """``huggingface_hub.HfApi()``: the client used when neither ``client=`` nor ``trainer.hub_client`` is given."""
     try:
         from huggingface_hub import HfApi
     except ImportError as exc:       # pragma: no cover - the library ships with transformers

@@ -112,6 +112,7 @@ def check_tree(root: str, *, skip: tuple[str, ...] = ("_work", "gpurun_out", ".g
 
 
 def main(argv: list[str] | None = None) -> int:
+    """Command line: check the tree at ``argv[0]`` (default: this repository), print the findings, return 1 if there are any."""
     args = list(sys.argv[1:] if argv is None else argv)
     root = args[0] if args else os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     found = check_tree(root)

@@ -1201,7 +1201,9 @@ class DPTrainer:
         a = self.args
         start = time.time()
         shard = local_shard(data, rank=a.process_index, world_size=a.world_size)
-        res = self.evaluation_loop(shard, "Evaluation", metric_key_prefix=metric_key_prefix)
+        # nobody consumes predictions without compute_metrics: keep only the losses then (no logits pass, no host copies)
+        res = self.evaluation_loop(shard, "Evaluation", prediction_loss_only=True if self.compute_metrics is None else None,
+                                   metric_key_prefix=metric_key_prefix)
         total = float(reduce_scalar(float(res.losses.sum()) if res.losses is not None else 0.0, "sum"))
         count = int(reduce_scalar(int(res.losses.numel()) if res.losses is not None else 0, "sum"))
         tokens = int(reduce_scalar(res.tokens, "sum"))

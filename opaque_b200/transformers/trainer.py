@@ -1148,7 +1148,7 @@ class DPTrainer:
             has_labels = "labels" in batch
             losses = self.compute_batch_per_example_loss(batch) if has_labels else None
             logits = None
-            if not loss_only:
+            if not loss_only and "input_ids" in batch:       # pair batches (DPO) have no single sequence to predict for
                 logits = self.model(batch["input_ids"])
                 logits = getattr(logits, "logits", logits)
                 if self.preprocess_logits_for_metrics is not None:

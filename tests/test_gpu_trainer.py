@@ -65,6 +65,30 @@ def test_fused_trainer_options(tmp_path, kw):
     assert tr.engine_kind == "fused" and out["global_step"] == 4 and math.isfinite(tr.state.log_history[-2]["loss"])
 
 
+def test_fused_trainer_evaluates_and_predicts_on_the_gpu(tmp_path):
+    """Evaluation on the device: per-example losses from the fused head, predictions offloaded every two batches,
+    ``compute_metrics`` on the gathered tensors."""
+    from opaque_b200.transformers import DPTrainer
+    seen = {}
+
+    def metrics(ep):
+        seen["shape"] = tuple(ep.predictions.shape)
+        keep = ep.label_ids != -100
+        return {"labelled": int(keep.sum()), "mean_loss": float(ep.losses.mean())}
+
+    held_out = _rows(20, seed=5)
+    args = _args(tmp_path, save_steps=0, max_steps=2, per_device_eval_batch_size=6, eval_accumulation_steps=2, include_for_metrics=["loss"])
+    tr = DPTrainer(model=_model(), args=args, train_dataset=_rows(), eval_dataset=held_out, compute_metrics=metrics)
+    tr.train()
+    out = tr.evaluate()
+    assert seen["shape"][:2] == (20, 64) and out["eval_samples"] == 20.0 and out["eval_labelled"] == 20 * 63
+    assert math.isfinite(out["eval_loss"]) and abs(out["eval_loss"] - out["eval_mean_loss"]) < 1e-3
+    pred = tr.predict(held_out[:7])
+    assert pred.num_samples == 7 and pred.predictions.shape[0] == 7 and "test_loss" in pred.metrics
+    tr.compute_metrics = None
+    assert tr.evaluate()["eval_loss"] == pytest.approx(out["eval_loss"], rel=1e-3)        # loss-only path
+
+
 def test_fused_trainer_logs_sync_times_when_asked(tmp_path):
     from opaque_b200.transformers import DPTrainer
     tr = DPTrainer(model=_model(), args=_args(tmp_path, save_steps=0, include_sync_metrics=True, logging_steps=1), train_dataset=_rows())

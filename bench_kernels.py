@@ -572,6 +572,16 @@ def main():
         pl = torch.zeros(n, device=dev, dtype=torch.bfloat16)
         emit(f"shard_step noise+AdamW-BC {n}", timeit(lambda: ops.shard_step(grad=grad, master=master, m=m, v=v, params_local=pl, seed=1, noise_std=1.0, step=2),
                                                       iters, warm, flush), bytes_=n * (4 * 4 * 2 + 2))
+        # pull form: the shard's gradient summed in rank order out of W full-length buffers (here W buffers on this GPU, so
+        # the reads cost HBM bandwidth instead of NVLink bandwidth); nothing is cleared by the kernel
+        W = 4
+        shard = n // W // 8 * 8
+        bufs = [torch.randn(n, device=dev) for _ in range(W)]
+        table = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=dev)
+        ms, ss, vs = master[:shard], m[:shard], v[:shard]
+        emit(f"shard_step pull x{W} + noise + AdamW-BC {shard}",
+             timeit(lambda: ops.shard_step(peer_grad=table, world=W, global_offset=shard, master=ms, m=ss, v=vs, params_local=pl, seed=1,
+                                           noise_std=1.0, step=2), iters, warm, flush), bytes_=shard * (4 * W + 4 * 3 * 2 + 2))
     if st.read():
         raise SystemExit(f"a device wait timed out (status {st.read()})")
 

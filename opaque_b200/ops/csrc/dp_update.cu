@@ -267,14 +267,14 @@ __device__ __forceinline__ void ftrl_apply8(const ShardStepParams& p, long long 
 }
 
 // Pull form of the gradient read: this shard's 8 coordinates from every rank's accumulation buffer, summed in rank
-// order.  Up to eight ranks' 32-byte loads are in flight per thread before the first add.
+// order.  Four ranks' 32-byte loads are in flight per thread before the first add (more would spill registers).
 __device__ __forceinline__ void pull_grad8(const ShardStepParams& p, long long base, float* g8) {
 #pragma unroll
   for (int j = 0; j < 8; ++j) g8[j] = 0.f;
-  for (int r0 = 0; r0 < p.world; r0 += 8) {
-    float4 a[8], b[8];
+  for (int r0 = 0; r0 < p.world; r0 += 4) {
+    float4 a[4], b[4];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
+    for (int r = 0; r < 4; ++r) {
       if (r0 + r < p.world) {
         const float4* src = reinterpret_cast<const float4*>(p.peer_grad[r0 + r] + p.global_offset + base);
         a[r] = __ldcg(src);
@@ -282,7 +282,7 @@ __device__ __forceinline__ void pull_grad8(const ShardStepParams& p, long long b
       }
     }
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
+    for (int r = 0; r < 4; ++r) {
       if (r0 + r < p.world) {
         g8[0] += a[r].x; g8[1] += a[r].y; g8[2] += a[r].z; g8[3] += a[r].w;
         g8[4] += b[r].x; g8[5] += b[r].y; g8[6] += b[r].z; g8[7] += b[r].w;
@@ -291,7 +291,11 @@ __device__ __forceinline__ void pull_grad8(const ShardStepParams& p, long long b
   }
 }
 
-__global__ void __launch_bounds__(256)
+// PULL selects the gradient source at compile time, so the ordinary form keeps its register allocation.  FTRL = false is
+// the iid-noise step (DP-SGD): without the correlated-noise state it fits three blocks per SM, which this latency-bound
+// kernel (Philox rounds, accurate log / sincos / sqrt / divisions in a dependent chain) turns into bandwidth.
+template <bool PULL, bool FTRL>
+__global__ void __launch_bounds__(256, FTRL ? 2 : 3)
 shard_step_kernel(const ShardStepParams p) {
   // The gradient barrier before this kernel may have given up (status != 0): the shard is then not fully reduced, and
   // adding noise to it, stepping and clearing it would release and apply a partial sum.  Leave every buffer untouched;
@@ -311,7 +315,7 @@ shard_step_kernel(const ShardStepParams p) {
     }
     float g8[8], w8[8], m8[8], v8[8];
     if (full) {
-      if (p.peer_grad) {
+      if (PULL) {
         pull_grad8(p, base, g8);
       } else {
         *reinterpret_cast<float4*>(g8) = *reinterpret_cast<const float4*>(p.grad + base);
@@ -330,7 +334,7 @@ shard_step_kernel(const ShardStepParams p) {
         const long long k = base + j;
         const bool in = k < p.n;
         float gk = 0.f;
-        if (in && p.peer_grad) {
+        if (in && PULL) {
           for (int r = 0; r < p.world; ++r) gk += __ldcg(p.peer_grad[r] + p.global_offset + k);
         } else if (in) {
           gk = p.grad[k];
@@ -343,13 +347,13 @@ shard_step_kernel(const ShardStepParams p) {
     }
     float out8[8];
     float x8[8];
-    const bool vec_ftrl = full && p.ftrl_mode != 0 && ((p.n & 3) == 0);
+    const bool vec_ftrl = FTRL && full && p.ftrl_mode != 0 && ((p.n & 3) == 0);
     if (vec_ftrl) ftrl_apply8(p, base, z, x8);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const long long k = base + j;
       float x = vec_ftrl ? x8[j] : z[j];
-      if (k < p.n && !vec_ftrl) {
+      if (FTRL && k < p.n && !vec_ftrl) {
         if (p.ftrl_mode == 1) {
           // row t of C^{-1} Z for a buffered-linear-Toeplitz C:  x = z - sum_b s_b S_b ;  S_b <- d_b S_b + x
           float corr = 0.f;
@@ -411,7 +415,7 @@ shard_step_kernel(const ShardStepParams p) {
     }
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
     if (full) {
-      if (!p.peer_grad) {
+      if (!PULL) {
         *reinterpret_cast<float4*>(p.grad + base) = zero4;
         *reinterpret_cast<float4*>(p.grad + base + 4) = zero4;
       }
@@ -441,7 +445,7 @@ shard_step_kernel(const ShardStepParams p) {
       for (int j = 0; j < 8; ++j) {
         const long long k = base + j;
         if (k >= p.n) break;
-        if (!p.peer_grad) p.grad[k] = 0.f;
+        if (!PULL) p.grad[k] = 0.f;
         if (p.noisy_out) p.noisy_out[k] = out8[j];
         if (p.skip_update) continue;
         p.master[k] = w8[j];
@@ -573,7 +577,13 @@ extern "C" int ob_shard_step(float* grad, const float* const* peer_grad, float* 
   p.opt_mode = opt_mode; p.nesterov = nesterov;
   if (opt_mode < 0 || opt_mode > 2) return -4;
   p.status = status;
-  shard_step_kernel<<<grid_for((n + 7) / 8, sms), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  const dim3 grid = grid_for((n + 7) / 8, sms);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool pull = peer_grad != nullptr, ftrl = ftrl_mode != 0;
+  if (pull && ftrl) shard_step_kernel<true, true><<<grid, 256, 0, st>>>(p);
+  else if (pull) shard_step_kernel<true, false><<<grid, 256, 0, st>>>(p);
+  else if (ftrl) shard_step_kernel<false, true><<<grid, 256, 0, st>>>(p);
+  else shard_step_kernel<false, false><<<grid, 256, 0, st>>>(p);
   return OB_CHECK_LAUNCH();
 }
 

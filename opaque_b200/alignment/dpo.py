@@ -11,7 +11,8 @@ packages/opaque-transformers/src/opaque/api/transformers/trl/_dpo_trainer.py:878
 from __future__ import annotations
 
 import math
-from collections.abc import Sequence
+from collections.abc import Mapping, Sequence
+from typing import Any
 
 import torch
 import torch.nn.functional as F
@@ -201,3 +202,103 @@ __all__ = ["ALL_LOSS_TYPES", "PAIR_HEADS", "REFERENCE_FREE", "apo_down_loss", "a
            "discopop_loss", "dpo_loss", "exo_loss", "f_divergence_logits", "hinge_loss", "ipo_loss", "ld_dpo_logp",
            "nca_loss", "orpo_loss", "reward_margins", "robust_loss", "sigmoid_loss", "simpo_loss", "sppo_loss",
            "wpo_weight"]
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# Building blocks under the names of the reference's ``alignment.dpo.loss`` / ``.metric`` / ``.data`` namespaces.
+# Parity: packages/opaque-alignment/src/opaque/api/alignment/dpo/loss/{_orpo,_f_divergence,_mpo,_wpo,_ld_dpo}.py,
+# dpo/metric/_reward.py, dpo/data/_prompt.py.
+
+def _log1mexp(x: torch.Tensor) -> torch.Tensor:
+    """``log(1 − eˣ)`` for ``x < 0`` without cancellation (two branches around ``−ln 2``)."""
+    x = x.clamp(max=-1e-7)
+    return torch.where(x > -0.6931471805599453, torch.log(-torch.expm1(x)), torch.log1p(-torch.exp(x)))
+
+
+def odds_ratio_loss(chosen_logp: torch.Tensor, rejected_logp: torch.Tensor) -> torch.Tensor:
+    """ORPO's odds-ratio term ``−log σ(log odds(y_w) − log odds(y_l))`` with ``log odds(y) = log p − log(1 − p)``;
+    both arguments are length-normalised log-probabilities (``< 0``).  The full ORPO loss adds the chosen NLL."""
+    log_odds = (chosen_logp - _log1mexp(chosen_logp)) - (rejected_logp - _log1mexp(rejected_logp))
+    return -F.logsigmoid(log_odds)
+
+
+def f_divergence_remap(logratio: torch.Tensor, *, f_divergence_type: str = "reverse_kl", alpha: float = 1.0) -> torch.Tensor:
+    """Per-side remap ``g`` of a log-ratio for f-DPO: ``reverse_kl`` ``g(x) = x``; ``forward_kl`` ``1 − e^{−x}``;
+    ``js_divergence`` ``ln 2 + log σ(x)``; ``alpha_divergence`` ``(e^{(α−1)x} − 1)/(α − 1)`` (identity at ``α = 1``).
+    Exponentials are capped at ``e⁸⁰``.  The pair logit is ``g(chosen) − g(rejected)``."""
+    cap = 80.0
+    if f_divergence_type == "reverse_kl":
+        return logratio
+    if f_divergence_type == "forward_kl":
+        return 1.0 - torch.exp((-logratio).clamp(max=cap))
+    if f_divergence_type == "js_divergence":
+        return math.log(2.0) + F.logsigmoid(logratio)
+    if f_divergence_type == "alpha_divergence":
+        if abs(alpha - 1.0) < 1e-6:
+            return logratio
+        return (torch.exp(((alpha - 1.0) * logratio).clamp(max=cap)) - 1.0) / (alpha - 1.0)
+    raise ValueError(f"unknown f-divergence {f_divergence_type!r}")
+
+
+def mpo_combine(losses: Mapping[str, torch.Tensor], weights: Mapping[str, float]) -> torch.Tensor:
+    """``Σ_k weights[k] · losses[k]`` over the keys of ``weights`` (a mixture of heads; ``losses`` may hold more)."""
+    missing = sorted(set(weights) - set(losses))
+    if missing:
+        raise KeyError(f"weights name losses that were not computed: {missing} (available: {sorted(losses)})")
+    if not weights:
+        raise ValueError("weights is empty")
+    total = None
+    for name, w in weights.items():
+        term = float(w) * losses[name]
+        total = term if total is None else total + term
+    return total
+
+
+def wpo_weights(per_token_logps: torch.Tensor, completion_mask: torch.Tensor) -> torch.Tensor:
+    """WPO's per-sequence weight: ``exp`` of the policy's mean per-token log-probability on the completion, DETACHED
+    (a multiplicative reweighting, no gradient).  Shapes ``(..., T)`` → ``(...)``; an empty mask gives weight 1."""
+    mask = completion_mask.to(per_token_logps.dtype)
+    count = (completion_mask != 0).sum(-1).clamp(min=1)
+    avg = (per_token_logps.float() * mask.float()).sum(-1) / count
+    return avg.detach().exp()
+
+
+def ld_dpo_split(per_token_logps: torch.Tensor, completion_mask: torch.Tensor, shared_prefix_len, alpha: float) -> torch.Tensor:
+    """LD-DPO sequence log-probability: the first ``shared_prefix_len`` completion tokens weigh 1, later ones ``alpha``
+    (``alpha = 1`` is the plain masked sum).  ``shared_prefix_len`` is an int or a per-example tensor."""
+    mask = completion_mask.to(per_token_logps.dtype)
+    pos = (completion_mask != 0).cumsum(-1)
+    limit = shared_prefix_len
+    if isinstance(limit, torch.Tensor):
+        while limit.ndim < pos.ndim:
+            limit = limit.unsqueeze(-1)
+    head = (pos >= 1) & (pos <= limit)
+    weight = torch.where(head, torch.ones_like(mask), torch.full_like(mask, float(alpha)))
+    return (per_token_logps * mask * weight).sum(-1)
+
+
+def reward_metrics(chosen_logratio: torch.Tensor, rejected_logratio: torch.Tensor, *, beta: float) -> dict[str, torch.Tensor]:
+    """``rewards/chosen``, ``rewards/rejected``, ``rewards/accuracies``, ``rewards/margins`` (detached means) from the
+    per-pair log-ratios; implicit reward = ``β · logratio``.  For logging on NON-private data (or add noise first)."""
+    c, r = chosen_logratio.detach().float(), rejected_logratio.detach().float()
+    return {"rewards/chosen": (beta * c).mean(), "rewards/rejected": (beta * r).mean(),
+            "rewards/accuracies": (c > r).float().mean(), "rewards/margins": (beta * (c - r)).mean()}
+
+
+def extract_prompt(example: Mapping[str, Any]) -> dict:
+    """Split the longest common prefix of ``chosen`` and ``rejected`` (lists: tokens or chat messages) off as ``prompt``.
+    Rows that already have a ``prompt``, or no chosen / rejected pair, come back unchanged; other keys are kept."""
+    row = dict(example)
+    if "prompt" in row or "chosen" not in row or "rejected" not in row:
+        return row
+    chosen, rejected = row["chosen"], row["rejected"]
+    if not isinstance(chosen, (list, tuple)) or not isinstance(rejected, (list, tuple)):
+        raise TypeError("extract_prompt needs list-valued 'chosen' and 'rejected' (token ids or messages)")
+    k = 0
+    while k < min(len(chosen), len(rejected)) and chosen[k] == rejected[k]:
+        k += 1
+    row["prompt"], row["chosen"], row["rejected"] = list(chosen[:k]), list(chosen[k:]), list(rejected[k:])
+    return row
+
+
+__all__ += ["extract_prompt", "f_divergence_remap", "ld_dpo_split", "mpo_combine", "odds_ratio_loss", "reward_metrics", "wpo_weights"]

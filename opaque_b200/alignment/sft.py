@@ -59,6 +59,21 @@ def fused_nll_loss(hidden: torch.Tensor, head_weight: torch.Tensor, labels: torc
     return rows.view(B, T).sum(1)
 
 
+def fused_dft_loss(hidden: torch.Tensor, head_weight: torch.Tensor, labels: torch.Tensor,
+                   ignore_index: int = IGNORE_INDEX, chunk: int = 8192) -> torch.Tensor:
+    """``dft_loss`` from final hidden states ``[B, T, d]`` and the output head without keeping logits: one pass without
+    gradients gives every token's probability (the detached weight), a second pass the weighted NLL."""
+    B, T = labels.shape
+    mask = labels != ignore_index
+    h2, l1 = hidden.reshape(B * T, -1), labels.reshape(-1)
+    with torch.no_grad():
+        nll = linear_cross_entropy(h2, head_weight, l1, mask.float().reshape(-1), chunk=chunk, ignore_index=ignore_index)
+        prob = torch.exp(-nll.float()).view(B, T) * mask
+    w = prob / mask.sum(1, keepdim=True).clamp_min(1)
+    rows = linear_cross_entropy(h2, head_weight, l1, w.reshape(-1).to(torch.float32), chunk=chunk, ignore_index=ignore_index)
+    return rows.view(B, T).sum(1)
+
+
 def fused_sequence_logp(hidden, head_weight, labels, *, average: bool = False, ignore_index: int = IGNORE_INDEX,
                         chunk: int = 8192):
     """Per-sequence (sum or mean) log-probability of the labels from hidden states and the head weight, without keeping logits."""
@@ -76,5 +91,5 @@ def token_accuracy(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int
     return ((logits.argmax(-1) == labels) & mask).sum().float() / mask.sum().clamp_min(1)
 
 
-__all__ = ["IGNORE_INDEX", "dft_loss", "fused_nll_loss", "fused_sequence_logp", "nll_loss", "selective_log_softmax",
+__all__ = ["IGNORE_INDEX", "dft_loss", "fused_dft_loss", "fused_nll_loss", "fused_sequence_logp", "nll_loss", "selective_log_softmax",
            "sequence_logp", "token_accuracy", "token_logps"]

@@ -213,3 +213,14 @@ def one_run(scores: CanaryScores, *, coin_flip: CoinFlip, num_guesses: int | Non
 
 __all__ = ["CanaryScores", "CoinFlip", "OneRunEstimate", "auc", "canary_scores", "coin_flip", "epsilon_lower_bound",
            "gdp_mu_lower_bound", "gradient_scores", "loss_scores", "one_run", "p_value_eps_delta", "roc_curve"]
+
+from .. import __version__  # noqa: E402
+from ..utils.namespaces import submodule as _sub  # noqa: E402
+
+# import paths of the reference: opaque.auditing.attacks.{loss_scores, gradient_scores}, opaque.auditing.one_run.one_run.
+# ``auditing.one_run`` stays callable: the namespace forwards a call to the function it holds.
+_sub(__name__, "attacks", "Membership scores for canaries.", {"gradient_scores": gradient_scores, "loss_scores": loss_scores})
+_sub(__name__, "one_run", "Privacy auditing with one training run.",
+     {"one_run": one_run, "OneRunEstimate": OneRunEstimate, "epsilon_lower_bound": epsilon_lower_bound,
+      "gdp_mu_lower_bound": gdp_mu_lower_bound, "p_value_eps_delta": p_value_eps_delta}, call=one_run)
+_sub(__name__, "types", "Classes of the auditing façade.", {"CanaryScores": CanaryScores, "CoinFlip": CoinFlip, "OneRunEstimate": OneRunEstimate}, bind=False)

@@ -454,3 +454,10 @@ __all__ = [
     "reduce_pytree", "reduce_pytree_", "reduce_scalar", "register_sync_type", "sum_gradients",
     "sum_gradients_", "sync", "sync_object", "wait_for_everyone",
 ]
+
+from ..utils.namespaces import submodule as _sub  # noqa: E402
+
+_sub(__name__, "collectives", "Thin collectives.", {"all_reduce": all_reduce, "all_reduce_": all_reduce_, "barrier": barrier, "get_rank": get_rank,
+                                                   "get_world_size": get_world_size, "is_distributed": is_distributed})
+_sub(__name__, "gradients", "Gradient reductions over ranks.", {"reduce_pytree": reduce_pytree, "reduce_pytree_": reduce_pytree_,
+                                                               "sum_gradients": sum_gradients, "sum_gradients_": sum_gradients_})

@@ -5,8 +5,12 @@ Parity: packages/opaque-dpftrl/src/opaque/dpftrl/__init__.py.
 from ..dpsgd import clipping
 from ..dpsgd.clipping import auto_clipped_grad, clipped_grad, per_group
 from . import noise, sampling
+
+import sys as _sys
+_sys.modules[__name__ + ".clipping"] = clipping          # ``import opaque_b200.dpftrl.clipping`` is the DP-SGD clipping module
 from .noise import (band_mf_strategy, bisr_strategy, blt_strategy, bsr_strategy, identity_strategy,
                     lambda_cgd_strategy, mf_gaussian_noise)
+from .. import __version__  # noqa: F401
 from .sampling import BallsInBinsSampler, BMinSepSampler, CyclicPoissonSampler, SequentialBatchSampler
 
 

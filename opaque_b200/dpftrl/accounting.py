@@ -199,3 +199,13 @@ def b_min_sep(inner: MfGaussian, *, bands: int, n_steps: int, max_participations
 
 __all__ = ["BMinSep", "BallsInBins", "CyclicPoisson", "MfGaussian", "b_min_sep", "balls_in_bins", "mf_gaussian", "per_step",
            "poisson"]
+
+from ..utils.namespaces import submodule as _sub  # noqa: E402
+
+_sub(__name__, "mechanisms", "DP-FTRL base mechanism.", {"mf_gaussian": mf_gaussian})
+_sub(__name__, "amplification", "Amplified accounting for DP-FTRL samplers.",
+     {"b_min_sep": b_min_sep, "balls_in_bins": balls_in_bins, "poisson": poisson})
+_sub(__name__, "types", "Process classes of DP-FTRL accounting.", {"BMinSep": BMinSep, "BallsInBins": BallsInBins, "CyclicPoisson": CyclicPoisson,
+                                                                   "MfGaussian": MfGaussian}, bind=False)
+_sub(__name__ + ".mechanisms", "types", "Mechanism classes.", {"MfGaussian": MfGaussian}, bind=False)
+_sub(__name__ + ".amplification", "types", "Amplification classes.", {"BMinSep": BMinSep, "BallsInBins": BallsInBins, "CyclicPoisson": CyclicPoisson}, bind=False)

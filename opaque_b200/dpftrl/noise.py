@@ -825,3 +825,9 @@ __all__ = [
     "optimize_banded", "optimize_blt", "prefix_sum_streaming", "register_strategy", "sqrt_coefs", "strategy_from_wire",
     "strategy_to_wire", "toeplitz_gram", "toeplitz_inverse_streaming", "toeplitz_sensitivity_squared",
 ]
+
+from ..utils.namespaces import submodule as _sub  # noqa: E402
+
+_sub(__name__, "types", "Strategy and state types of the matrix-factorisation noise.",
+     {n: globals()[n] for n in ("BandMfStrategy", "BisrStrategy", "BltStrategy", "BsrStrategy", "IdentityStrategy", "LambdaCgdStrategy",
+                                "MFNoiseState", "MfStrategy", "SecondMomentMFNoiseState")}, bind=False)

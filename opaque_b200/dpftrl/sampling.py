@@ -151,3 +151,7 @@ register_serializer(SequentialBatchSampler, lambda s: {**_save_common(s), "batch
 
 __all__ = ["BMinSepSampler", "BallsInBinsSampler", "CyclicPoissonSampler", "PartitionType", "SequentialBatchSampler",
            "partition_indices"]
+
+from ..utils.namespaces import submodule as _sub  # noqa: E402
+
+_sub(__name__, "types", "Types of the DP-FTRL samplers.", {"PartitionType": PartitionType}, bind=False)

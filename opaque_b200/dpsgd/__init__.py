@@ -5,6 +5,7 @@ Parity: packages/opaque-dpsgd/src/opaque/dpsgd/__init__.py.
 from . import clipping, noise, sampling
 from .clipping import adaptive_clipped_grad, auto_clipped_grad, clipped_grad, per_group
 from .noise import gaussian_noise
+from .. import __version__  # noqa: F401
 from .sampling import BalancedRankSampler, KOutOfTSampler, PoissonSampler, RandomAllocationSampler
 
 

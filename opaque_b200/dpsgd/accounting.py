@@ -142,3 +142,15 @@ def k_out_of_t(inner: DpProcess, k: int, t: int) -> RandomAllocation:
 
 __all__ = ["AdaClip", "Gaussian", "ParallelPoisson", "Poisson", "RandomAllocation", "adaclip", "gaussian", "k_out_of_t",
            "parallel_poisson", "poisson", "random_allocation"]
+
+from ..utils.namespaces import submodule as _sub  # noqa: E402
+
+_sub(__name__, "mechanisms", "DP-SGD base mechanisms.", {"adaclip": adaclip, "gaussian": gaussian})
+_sub(__name__, "amplification", "Amplification by sampling.",
+     {"k_out_of_t": k_out_of_t, "parallel_poisson": parallel_poisson, "poisson": poisson, "random_allocation": random_allocation})
+KOutOfT = RandomAllocation          # k-out-of-t participation is accounted as a random-allocation process
+_sub(__name__, "types", "Process classes of DP-SGD accounting.", {"AdaClip": AdaClip, "Gaussian": Gaussian, "KOutOfT": KOutOfT,
+                                                                  "ParallelPoisson": ParallelPoisson, "Poisson": Poisson, "RandomAllocation": RandomAllocation}, bind=False)
+_sub(__name__ + ".mechanisms", "types", "Mechanism classes.", {"AdaClip": AdaClip, "Gaussian": Gaussian}, bind=False)
+_sub(__name__ + ".amplification", "types", "Amplification classes.", {"KOutOfT": KOutOfT, "ParallelPoisson": ParallelPoisson, "Poisson": Poisson,
+                                                                      "RandomAllocation": RandomAllocation}, bind=False)

@@ -174,3 +174,24 @@ _rst(ClippingStats, _sync_stats)
 __all__ = ["AdaptiveClipState", "AutoClipState", "FixedClipState", "adaptive_clipped_grad", "auto_clipped_fun",
            "auto_clipped_grad", "clip_pytree", "clipped_fun", "clipped_grad", "next_clipping_norm", "per_group",
            "sync_adaptive_clip_state"]
+
+from ..engine import clipping as _eng  # noqa: E402
+from ..utils.namespaces import submodule as _sub  # noqa: E402
+
+
+def _register_type_namespaces() -> None:
+    from .. import _type_names as T
+    fun = {"auto_clipped_fun": auto_clipped_fun, "auto_scale_pytree": _eng.auto_scale_pytree, "clip_pytree": clip_pytree, "clipped_fun": clipped_fun}
+    common = {"AutoClipState": AutoClipState, "FixedClipState": FixedClipState, "AutoClippedFunAux": T.AutoClippedFunAux,
+              "AutoClippedGradAux": T.AutoClippedGradAux, "ClippedGradFn": T.ClippedGradFn, "ClippedGradResult": T.ClippedGradResult}
+    _sub(__name__, "fun", "Clipping of arbitrary per-example functions and of pytrees.", fun, bind=False)
+    _sub(__name__, "types", "State and result types of the clipping transforms.",
+         {**common, "AdaptiveClipState": AdaptiveClipState, "AdaptiveClippedGradAux": T.AdaptiveClippedGradAux, "ClippingStats": _eng.ClippingStats,
+          "ClipPytreeAux": _eng.ClipPytreeAux, "ClippedFunAux": _eng.ClippedFunAux, "ClippedGradAux": _eng.ClippedGradAux}, bind=False)
+    # the DP-FTRL façade re-exports this module as ``dpftrl.clipping``: same namespaces under that path
+    for name in ("fun", "types"):
+        import sys
+        sys.modules["opaque_b200.dpftrl.clipping." + name] = sys.modules[__name__ + "." + name]
+
+
+_register_type_namespaces()

@@ -178,3 +178,15 @@ _rst(GaussianNoiseState, sync_gaussian_noise_state)
 
 __all__ = ["GaussianNoiseState", "add_noise_tree", "gaussian_noise", "sample_gaussian_cpu",
            "sync_gaussian_noise_state"]
+
+from ..utils.namespaces import submodule as _sub  # noqa: E402
+
+
+def _register_type_namespace() -> None:
+    from .. import _type_names as T
+    _sub(__name__, "types", "Types of the Gaussian noise mechanism.",
+         {"GaussianNoiseFn": T.GaussianNoiseFn, "GaussianNoiseInput": T.GaussianNoiseInput, "GaussianNoiseOutput": T.GaussianNoiseOutput,
+          "GaussianNoiseState": GaussianNoiseState}, bind=False)
+
+
+_register_type_namespace()

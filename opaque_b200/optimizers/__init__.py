@@ -515,3 +515,8 @@ for _t in (ChainState, SGDState, AdamState, LionState, AdagradState, RMSpropStat
 __all__ = ["AdamState", "GradientTransformation", "adadelta", "adafactor", "adagrad", "adam", "adamw", "ademamix",
            "apply_updates", "lion", "make_optimizer_chain", "radam", "rmsprop", "scale_by_adam", "schedule_free",
            "schedule_free_adamw", "schedule_free_sgd", "sgd", "sync_optimizer_state", "types"]
+
+from ..utils.namespaces import submodule as _sub  # noqa: E402
+
+_sub(__name__, "types", "Optimizer state classes.", {n: globals()[n] for n in (
+    "AdEMAMixState AdadeltaState AdafactorState AdagradState AdamState LionState RAdamState RMSpropState ScheduleFreeState").split()}, bind=False)

@@ -37,9 +37,14 @@ UNSUPPORTED = {
 # Hugging Face models and get kernel forwards in place (patches/inplace.py), as the reference does for them.
 
 
-def register_family(model_type: str, builder: Callable[[Any, dict], torch.nn.Module]) -> None:
-    """Register ``builder(hf_config, options) -> nn.Module`` for a Hugging Face ``model_type``."""
-    _FAMILIES[model_type] = builder
+def register_family(model_type: str, builder: Callable[..., Any]) -> None:
+    """Register a family for a Hugging Face ``model_type``: either ``builder(hf_config, options) -> nn.Module`` (the model
+    is CONVERTED into this package's modules) or a function built by ``inplace.make_apply_model_patches`` (the model stays
+    a Hugging Face model and gets kernel forwards in place)."""
+    if getattr(builder, "is_model_patch_fn", False):
+        inplace.register_inplace_family(model_type, builder)
+    else:
+        _FAMILIES[model_type] = builder
 
 
 def _cfg_get(cfg: Any, name: str, default=None):
@@ -357,6 +362,12 @@ def apply_transformers_model_patches(model: Any, *, performance: bool = True, co
     mtype = _cfg_get(cfg, "model_type")
     if mtype in UNSUPPORTED:
         raise NotImplementedError(f"model_type {mtype!r} is not converted: {UNSUPPORTED[mtype]}")
+    custom = inplace.registered_inplace_family(mtype)
+    if custom is not None:                       # a family registered through the factory API: patched in place
+        if not isinstance(model, torch.nn.Module):
+            raise ValueError(f"model_type {mtype!r} is patched in place: pass the instantiated model, not a config")
+        custom(model, performance=performance, compat=compat)
+        return model
     if mtype in inplace.INPLACE_FAMILIES:
         if not isinstance(model, torch.nn.Module):
             raise ValueError(f"model_type {mtype!r} is patched in place: pass the instantiated Hugging Face model, not a config")
@@ -603,5 +614,61 @@ def is_runtime_patched() -> bool:
     return _RUNTIME["patched"]
 
 
-__all__ = ["apply_model_patches", "apply_peft_model_patches", "convert_peft_model", "export_peft_adapter", "load_peft_adapter", "peft_adapter_state_dict", "apply_runtime_patches", "apply_transformers_model_patches",
+def apply_checkpoint_patch() -> bool:
+    """Activation checkpointing under per-example gradients needs no patch of ``torch.utils.checkpoint`` here: the fused
+    engine is explicit-batch (the stock checkpoint works), and under ``vmap(grad)`` this package's models use
+    ``functional.functional_checkpoint``.  Kept so that set-up code written for the reference runs; marks the call."""
+    _RUNTIME["checkpoint"] = True
+    return True
+
+
+def is_checkpoint_patched() -> bool:
+    """True once :func:`apply_checkpoint_patch` ran in this process."""
+    return bool(_RUNTIME.get("checkpoint"))
+
+
+def apply_masking_patches() -> str:
+    """Attention-mask construction under ``vmap``: not needed (framework models build masks from shapes only)."""
+    return apply_runtime_patches()["vmap_masking"]
+
+
+def apply_collator_patches() -> str:
+    """Empty Poisson batches in collators: handled by ``alignment.data`` collators themselves."""
+    return apply_runtime_patches()["empty_batches"]
+
+
+def apply_grouped_mm_patches() -> str:
+    """Grouped expert GEMMs under ``vmap``: not needed (they are called outside ``vmap``)."""
+    return apply_runtime_patches()["vmap_grouped_mm"]
+
+
+def supported_inplace_families() -> list[str]:
+    return sorted(set(inplace.INPLACE_FAMILIES) | set(inplace._FAMILY_APPLY))
+
+
+__all__ = ["apply_checkpoint_patch", "apply_collator_patches", "apply_grouped_mm_patches", "apply_masking_patches", "is_checkpoint_patched",
+           "apply_model_patches", "apply_peft_model_patches", "convert_peft_model", "export_peft_adapter", "load_peft_adapter", "peft_adapter_state_dict", "apply_runtime_patches", "apply_transformers_model_patches",
            "inplace", "is_runtime_patched", "kernels", "register_family", "supported_families"]
+
+
+from .. import __version__  # noqa: E402,F401
+from ..utils.namespaces import submodule as _sub  # noqa: E402
+
+# import paths of the reference.  ``torch`` and ``transformers`` are not bound as attributes of this package: the names
+# belong to the libraries (``import opaque_b200.patches.torch`` and ``from opaque_b200.patches.transformers import ...`` work).
+_sub(__name__, "peft", "LoRA / PEFT entry points.", {"apply_peft_model_patches": apply_peft_model_patches, "convert_peft_model": convert_peft_model,
+                                                    "export_peft_adapter": export_peft_adapter, "load_peft_adapter": load_peft_adapter})
+_sub(__name__, "torch", "Runtime patches of PyTorch itself (none are needed here).",
+     {"apply_checkpoint_patch": apply_checkpoint_patch, "is_checkpoint_patched": is_checkpoint_patched}, bind=False)
+_sub(__name__, "transformers", "Hugging Face model adaptation: conversion, in-place patches and the factory API for new families.",
+     {**{n: getattr(inplace, n) for n in ("FamilyPatchFn", "ForwardFactory", "ForwardFn", "ModelPatchFn", "ModulePatcher", "family_name",
+                                         "make_apply_family_patches", "make_apply_model_patches", "register_activation_kind",
+                                         "register_fused_add_rms_kind", "register_moe_kind", "register_rms_norm_kind")},
+      "apply_transformers_model_patches": apply_transformers_model_patches, "register_family": register_family,
+      "supported_families": supported_families}, bind=False)
+_sub(__name__ + ".transformers", "runtime", "Process-wide runtime patches (reported as not needed).",
+     {"apply_collator_patches": apply_collator_patches, "apply_grouped_mm_patches": apply_grouped_mm_patches,
+      "apply_masking_patches": apply_masking_patches})
+_sub(__name__ + ".transformers", "types", "Callable types of the factory API.",
+     {n: getattr(inplace, n) for n in ("FamilyPatchFn", "ForwardFactory", "ForwardFn", "ModelPatchFn", "ModulePatcher")}, bind=False)
+

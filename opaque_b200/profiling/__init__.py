@@ -260,3 +260,8 @@ def sync_perf_state(state: PerfState) -> PerfState:
 __all__ = ["MemoryStats", "PerfStage", "PerfState", "PerfTracker", "StepPerf", "empty_cache", "enable_nvtx",
            "get_memory_stats", "perf_tracker", "print_memory", "reset_peak_memory", "step_perf",
            "sync_perf_state", "trace", "trace_range"]
+
+from ..utils.namespaces import submodule as _sub  # noqa: E402
+
+_sub(__name__, "types", "Classes of the profiling façade.", {n: globals()[n] for n in ("MemoryStats", "PerfStage", "PerfState", "PerfTracker", "StepPerf")},
+     bind=False)

@@ -103,3 +103,7 @@ _reg(RngKey, lambda k: {"seed": str(k.seed), "impl": k.impl},
 
 __all__ = ["RngKey", "fold_in", "generator_from_key", "key", "philox_key", "random_key",
            "set_reproducible_pytorch_seed", "split"]
+
+from ..utils.namespaces import submodule as _sub  # noqa: E402
+
+_sub(__name__, "types", "Classes of the random façade.", {"RngKey": RngKey}, bind=False)

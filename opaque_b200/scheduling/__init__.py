@@ -331,3 +331,9 @@ __all__ = [
     "one_minus_sqrt_schedule", "polynomial_schedule", "resolve_decay", "resolve_ramp",
     "schedule_from_wire", "schedule_to_wire", "warmup_stable_decay", "with_restarts", "with_warmup",
 ]
+
+from ..utils.namespaces import submodule as _sub  # noqa: E402
+
+_sub(__name__, "types", "Schedule recipe classes.", {n: globals()[n] for n in (
+    "ConstantSchedule CosineSchedule ExponentialSchedule InverseSqrtSchedule LinearSchedule OneMinusSqrtSchedule PolynomialSchedule Schedule "
+    "WarmupStableDecay WithRestarts WithWarmup").split()}, bind=False)

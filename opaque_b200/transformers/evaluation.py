@@ -38,6 +38,23 @@ class EvaluationResult:
 PredictionOutput = EvaluationResult
 
 
+class TrainOutput(dict):
+    """What ``train()`` returns: the dict of final metrics (``out["global_step"]``, ``out["epsilon"]``, …) that ALSO has
+    the Hugging Face attributes ``global_step``, ``training_loss`` and ``metrics``."""
+
+    @property
+    def global_step(self) -> int:
+        return int(self.get("global_step", 0))
+
+    @property
+    def training_loss(self) -> float:
+        return float(self.get("train_loss", float("nan")))
+
+    @property
+    def metrics(self) -> dict:
+        return dict(self)
+
+
 class EvalPrediction:
     """Argument of ``compute_metrics``: ``predictions, label_ids = eval_pred`` works, and so do the attributes."""
 
@@ -215,5 +232,5 @@ def to_python(value: Any) -> Any:
     return value
 
 
-__all__ = ["EvalPrediction", "EvaluationResult", "PAD_VALUE", "PredictionAccumulator", "PredictionOutput", "speed_metrics",
+__all__ = ["EvalPrediction", "EvaluationResult", "PAD_VALUE", "PredictionAccumulator", "PredictionOutput", "TrainOutput", "speed_metrics",
            "to_python", "with_metric_prefix"]

@@ -56,7 +56,7 @@ from ..functional import make_functional
 from ..profiling import perf_tracker
 from ..random import RngKey, fold_in, key
 from ..serialization import from_state_dict, state_dict
-from .evaluation import (EvalPrediction, EvaluationResult, PredictionAccumulator, PredictionOutput, speed_metrics, to_python,
+from .evaluation import (EvalPrediction, EvaluationResult, PredictionAccumulator, PredictionOutput, TrainOutput, speed_metrics, to_python,
                          with_metric_prefix)
 from .training_args import MECHANISMS_DPFTRL, TrainingArguments
 
@@ -1085,6 +1085,10 @@ class DPTrainer:
             out["train_tokens_per_second"] = (self.state.num_input_tokens_seen - tokens_at_start) / max(runtime, 1e-9)
         if a.include_num_input_tokens_seen:
             out["num_input_tokens_seen"] = self.state.num_input_tokens_seen
+        step_losses = [r["loss"] for r in self.state.log_history if "loss" in r and "train_runtime" not in r]
+        if step_losses:
+            out["train_loss"] = float(np.mean(step_losses))       # mean of the logged (windowed) training losses
+        out = TrainOutput(out)
         self.log(out)
         if a.load_best_model_at_end:
             self._load_best_model()
@@ -1416,7 +1420,13 @@ def _barrier() -> None:
         dist.barrier()
 
 
-__all__ = ["BestModelSaveCallback", "DPTrainer", "DPTrainerState", "DP_STATE_BUNDLE_VERSION", "EvalPrediction", "EvaluationResult",
+__all__ = ["BestModelSaveCallback", "DPTrainer", "DPTrainerState", "DP_STATE_BUNDLE_VERSION", "EvalPrediction", "EvaluationResult", "TrainOutput",
            "PredictionAccumulator", "PredictionOutput",
            "PrinterCallback", "RuntimeCheckpoint", "TrainerCallback", "TrainerControl", "build_lr_schedule",
            "build_optimizer", "build_strategy", "default_per_example_loss", "list_checkpoints", "rotate_checkpoints"]
+
+from ..utils.namespaces import submodule as _sub  # noqa: E402
+
+_sub(__name__, "types", "Return types of the trainers.", {"EvalPrediction": EvalPrediction, "EvaluationResult": EvaluationResult,
+                                                           "PredictionOutput": PredictionOutput, "TrainOutput": TrainOutput})
+

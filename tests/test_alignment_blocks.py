@@ -1,0 +1,203 @@
+"""Building blocks added for import-path parity: preference-loss pieces, token metrics, reference helpers, fused DFT loss,
+and the factory API for in-place family patches — each against its closed form."""
+import math
+import os
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from opaque_b200.alignment import dpo, metric, reference, sft
+
+
+def test_preference_loss_pieces_match_their_closed_forms():
+    torch.manual_seed(0)
+    c, r = -torch.rand(7) * 3 - 0.05, -torch.rand(7) * 3 - 0.05          # length-normalised log-probabilities (< 0)
+    odds = lambda lp: lp - torch.log1p(-lp.exp())
+    assert torch.allclose(dpo.odds_ratio_loss(c, r), -F.logsigmoid(odds(c) - odds(r)), atol=1e-6)
+    tiny = torch.tensor([-1e-9, -30.0])                                   # both ends of log(1 - e^x) stay finite
+    assert torch.isfinite(dpo.odds_ratio_loss(tiny, tiny.flip(0))).all()
+    x = torch.randn(9)
+    assert torch.equal(dpo.f_divergence_remap(x), x)
+    assert torch.allclose(dpo.f_divergence_remap(x, f_divergence_type="forward_kl"), 1 - torch.exp(-x))
+    assert torch.allclose(dpo.f_divergence_remap(x, f_divergence_type="js_divergence"), math.log(2) + F.logsigmoid(x))
+    assert torch.allclose(dpo.f_divergence_remap(x, f_divergence_type="alpha_divergence", alpha=0.5), (torch.exp(-0.5 * x) - 1) / -0.5)
+    assert torch.equal(dpo.f_divergence_remap(x, f_divergence_type="alpha_divergence", alpha=1.0), x)
+    assert torch.isfinite(dpo.f_divergence_remap(torch.tensor([-500.0]), f_divergence_type="forward_kl")).all()
+    with pytest.raises(ValueError):
+        dpo.f_divergence_remap(x, f_divergence_type="chi2")
+    losses = {"sigmoid": torch.tensor([1.0, 2.0]), "sft": torch.tensor([3.0, 5.0]), "ipo": torch.tensor([9.0, 9.0])}
+    assert torch.equal(dpo.mpo_combine(losses, {"sigmoid": 1.0, "sft": 0.5}), torch.tensor([2.5, 4.5]))
+    with pytest.raises(KeyError):
+        dpo.mpo_combine(losses, {"hinge": 1.0})
+    lp = torch.tensor([[-0.5, -1.0, -2.0, -4.0], [-1.0, -1.0, -1.0, -1.0]], requires_grad=True)
+    mask = torch.tensor([[0, 1, 1, 1], [0, 0, 0, 0]])
+    w = dpo.wpo_weights(lp, mask)
+    assert torch.allclose(w, torch.tensor([math.exp(-7 / 3), 1.0])) and not w.requires_grad
+    # LD-DPO: the first 2 completion tokens weigh 1, later ones alpha
+    got = dpo.ld_dpo_split(lp.detach(), mask, 2, 0.25)
+    assert torch.allclose(got, torch.tensor([-1.0 - 2.0 - 0.25 * 4.0, 0.0]))
+    assert torch.allclose(dpo.ld_dpo_split(lp.detach(), mask, torch.tensor([1, 3]), 0.0), torch.tensor([-1.0, 0.0]))
+    assert torch.allclose(dpo.ld_dpo_split(lp.detach(), mask, 2, 1.0), (lp.detach() * mask).sum(-1))
+    m = dpo.reward_metrics(torch.tensor([1.0, -1.0, 2.0]), torch.tensor([0.0, 0.0, 3.0]), beta=0.5)
+    assert set(m) == {"rewards/chosen", "rewards/rejected", "rewards/accuracies", "rewards/margins"}
+    assert float(m["rewards/accuracies"]) == pytest.approx(1 / 3) and float(m["rewards/margins"]) == pytest.approx(0.5 * (1 - 1 - 1) / 3)
+    row = dpo.extract_prompt({"chosen": [1, 2, 3, 4], "rejected": [1, 2, 9], "id": 7})
+    assert row == {"prompt": [1, 2], "chosen": [3, 4], "rejected": [9], "id": 7}
+    same = {"prompt": [1], "chosen": [2], "rejected": [3]}
+    assert dpo.extract_prompt(same) == same and dpo.extract_prompt({"prompt": "p", "completion": "c"}) == {"prompt": "p", "completion": "c"}
+    msgs = dpo.extract_prompt({"chosen": [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "a"}],
+                               "rejected": [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "b"}]})
+    assert msgs["prompt"] == [{"role": "user", "content": "hi"}] and msgs["chosen"][0]["content"] == "a"
+
+
+def test_token_metrics_shift_and_mask():
+    torch.manual_seed(1)
+    logits = torch.randn(2, 5, 11)
+    labels = torch.randint(0, 11, (2, 5))
+    mask = torch.tensor([[1, 1, 1, 0, 0], [0, 0, 1, 1, 1]])
+    p = logits[:, :-1].softmax(-1)
+    ent = -(p * p.log()).sum(-1)
+    m = mask[:, 1:].float()
+    assert float(metric.entropy_from_logits(logits, mask)) == pytest.approx(float((ent * m).sum() / m.sum()), rel=1e-5)
+    hit = (logits[:, :-1].argmax(-1) == labels[:, 1:]).float()
+    assert float(metric.mean_token_accuracy(logits, labels, mask)) == pytest.approx(float((hit * m).sum() / m.sum()))
+    assert float(metric.mean_token_accuracy(logits, labels, torch.zeros_like(mask))) == 0.0
+    assert float(metric.entropy_from_logits(logits, torch.zeros_like(mask))) == 0.0
+
+
+def test_fused_dft_loss_equals_the_logits_form_with_gradients():
+    torch.manual_seed(2)
+    B, T, d, V = 3, 6, 16, 40
+    hidden = torch.randn(B, T, d, requires_grad=True)
+    head = torch.randn(V, d, requires_grad=True) * 0.3
+    head.retain_grad()
+    labels = torch.randint(0, V, (B, T))
+    labels[0, :2] = -100
+    labels[2, -1] = -100
+    want = sft.dft_loss(hidden @ head.t(), labels)
+    got = sft.fused_dft_loss(hidden, head, labels)
+    assert torch.allclose(got, want, atol=1e-5)
+    gw = torch.autograd.grad(want.sum(), hidden, retain_graph=True)[0]
+    gg = torch.autograd.grad(got.sum(), hidden)[0]
+    assert torch.allclose(gg, gw, atol=1e-5)
+
+
+def test_reference_helpers(tmp_path):
+    from opaque_b200.models import LlamaConfig, LlamaForCausalLM
+    torch.manual_seed(3)
+    model = LlamaForCausalLM(LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2,
+                                         num_key_value_heads=2, max_position_embeddings=32), dtype=torch.float32).eval()
+    ids = torch.randint(0, 64, (2, 8))
+    with torch.no_grad():
+        base = model(ids)
+    model.add_lora(4, 8.0, ("q_proj", "v_proj"))
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if n.endswith("lora_B"):
+                p.normal_(0, 0.1)
+        tuned = model(ids)
+        assert not torch.allclose(tuned, base, atol=1e-4)
+        with reference.with_disabled_adapter(model):
+            assert torch.allclose(model(ids), base, atol=1e-6)
+        with reference.null_ref_context(model):
+            assert torch.allclose(model(ids), base, atol=1e-6)
+        with reference.null_ref_context(model, ref_model=object()):          # a separate reference: the policy is left alone
+            assert torch.allclose(model(ids), tuned, atol=1e-6)
+        assert torch.allclose(model(ids), tuned, atol=1e-6)                   # restored
+
+    class FakePeft:                                  # the PEFT calls that null_ref_context makes, recorded
+        def __init__(self, adapters):
+            self.peft_config, self.active_adapter, self.calls = {a: None for a in adapters}, "default", []
+
+        def disable_adapter(self):
+            import contextlib
+
+            @contextlib.contextmanager
+            def cm():
+                self.calls.append("off")
+                yield
+                self.calls.append("on")
+            return cm()
+
+        def set_adapter(self, name):
+            self.calls.append(f"set:{name}")
+    plain, with_ref = FakePeft(["default"]), FakePeft(["default", "ref"])
+    with reference.null_ref_context(plain):
+        pass
+    with reference.null_ref_context(with_ref):
+        pass
+    assert plain.calls == ["off", "on"] and with_ref.calls == ["set:ref", "set:default"]
+
+    ref_p, pol_p = {"w": torch.zeros(3), "b": {"x": torch.ones(2)}}, {"w": torch.ones(3), "b": {"x": torch.zeros(2)}}
+    out = reference.ema_update_reference(ref_p, pol_p, 0.25)
+    assert torch.allclose(out["w"], torch.full((3,), 0.25)) and torch.allclose(out["b"]["x"], torch.full((2,), 0.75)) and float(ref_p["w"].sum()) == 0
+    with pytest.raises(ValueError):
+        reference.ema_update_reference(ref_p, pol_p, 1.5)
+
+    rows = [{"v": float(i)} for i in range(11)]
+    calls = []
+
+    def ref_fn(batch):
+        calls.append(len(batch["v"]))
+        return {"ref_chosen_logps": batch["v"] * 2, "ref_rejected_logps": -batch["v"]}
+    collate = lambda rs: {"v": torch.tensor([r["v"] for r in rs])}
+    kw = dict(cache_identity={"model": "m", "step": 0}, batch_size=4, cache_dir=str(tmp_path / "cache"))
+    out = reference.compute_ref_logprobs_for_dataset(rows, ref_fn, collate, ("ref_chosen_logps", "ref_rejected_logps"), **kw)
+    assert [r["ref_chosen_logps"] for r in out] == [2.0 * i for i in range(11)] and out[3]["ref_rejected_logps"] == -3.0 and calls == [4, 4, 3]
+    again = reference.compute_ref_logprobs_for_dataset(rows, ref_fn, collate, ("ref_chosen_logps", "ref_rejected_logps"), **kw)
+    assert again == out and calls == [4, 4, 3]                                  # served from the cache
+    files = os.listdir(tmp_path / "cache")
+    assert len(files) == 1 and oct(os.stat(tmp_path / "cache" / files[0]).st_mode & 0o777) == "0o600"
+    assert oct(os.stat(tmp_path / "cache").st_mode & 0o777) == "0o700"
+    other = reference.compute_ref_logprobs_for_dataset(rows, ref_fn, collate, ("ref_chosen_logps", "ref_rejected_logps"),
+                                                       **{**kw, "cache_identity": {"model": "m", "step": 1}})
+    assert other == out and len(calls) == 6 and len(os.listdir(tmp_path / "cache")) == 2     # another identity: recomputed
+    with pytest.raises(TypeError):
+        reference.compute_ref_logprobs_for_dataset(rows, ref_fn, collate, ("ref_chosen_logps",), cache_identity=object(), cache_dir=str(tmp_path / "c2"))
+    with pytest.raises(RuntimeError):
+        reference.compute_ref_logprobs_for_dataset(rows, ref_fn, collate, ("ref_chosen_logps",), cache_identity=1, shard=True, use_cache=False)
+
+
+def test_factory_api_patches_a_new_family_in_place():
+    """A family described as data: class names per role and registered kinds; applied through ``apply_model_patches``."""
+    from opaque_b200 import patches
+    from opaque_b200.patches import inplace
+    from opaque_b200.patches.transformers import make_apply_family_patches, make_apply_model_patches, register_family, register_rms_norm_kind
+
+    class ToyNorm(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.weight = torch.nn.Parameter(torch.ones(8))
+
+        def forward(self, x):
+            return x * self.weight
+
+    class ToyMLP(torch.nn.Module):
+        def forward(self, x):
+            return x + 1
+
+    class Toy(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.config = {"model_type": "toy_family"}
+            self.norm, self.norm2, self.mlp = ToyNorm(), ToyNorm(), ToyMLP()
+
+        def forward(self, x):
+            return self.mlp(self.norm2(self.norm(x)))
+    seen = []
+    register_rms_norm_kind("doubling", lambda original: (lambda x: 2 * original(x)))
+    family_apply = make_apply_family_patches("toy_family", lambda: seen.append("runtime"))
+    apply = make_apply_model_patches(family="toy_family", family_apply=family_apply, classes={"rms_norm": "ToyNorm", "mlp": "ToyMLP"},
+                                     rms_norm_kind="doubling", activation_kind=lambda original: (lambda x: original(x) * 10))
+    register_family("toy_family", apply)
+    assert inplace.family_name(Toy()) == "toy_family"
+    model, x = Toy(), torch.ones(8)
+    assert float(model(x)[0]) == 2.0
+    out = patches.apply_model_patches(model)
+    assert out is model and float(model(x)[0]) == (2 * 2 * 1 + 1) * 10 and seen == ["runtime"]
+    assert apply(model) == {"rms_norm": 2, "mlp": 1} and float(model(x)[0]) == 50.0 and seen == ["runtime"]      # idempotent, runtime once
+    assert inplace.remove_factory_patches(model) == 3 and float(model(x)[0]) == 2.0
+    assert apply(Toy(), mlp=False) == {"rms_norm": 2, "mlp": 0}
+    with pytest.raises(ValueError, match="not registered"):
+        make_apply_model_patches(family="t", classes={"rms_norm": "ToyNorm"}, rms_norm_kind="nope")

@@ -87,3 +87,81 @@ def test_native_accounting_stub_declares_every_public_name():
     declared = {n.name for n in tree.body if isinstance(n, (ast.FunctionDef, ast.ClassDef))}
     public = {n for n in dir(_native) if not n.startswith("_")}
     assert public <= declared, sorted(public - declared)
+
+
+SUBPATHS = {
+    "alignment.dpo.collator": "preference_collator",
+    "alignment.dpo.data": "extract_prompt",
+    "alignment.dpo.loss": "sequence_logp fused_sequence_logp sigmoid_loss hinge_loss robust_loss ipo_loss discopop_loss chosen_nll_loss "
+                          "apo_zero_loss apo_down_loss exo_loss nca_loss bco_loss sppo_loss simpo_loss odds_ratio_loss f_divergence_remap "
+                          "f_divergence_logits mpo_combine wpo_weights ld_dpo_split",
+    "alignment.dpo.metric": "reward_metrics",
+    "alignment.dpo.reference": "compute_ref_logprobs_for_dataset ema_update_reference null_ref_context with_disabled_adapter",
+    "alignment.metric": "entropy_from_logits mean_token_accuracy",
+    "alignment.sft.collator": "language_modeling_collator",
+    "alignment.sft.loss": "dft_loss fused_dft_loss fused_nll_loss nll_loss",
+    "auditing.attacks": "gradient_scores loss_scores",
+    "auditing.one_run": "one_run",
+    "dpftrl.accounting.amplification": "b_min_sep balls_in_bins poisson",
+    "dpftrl.accounting.mechanisms": "mf_gaussian",
+    "dpftrl.clipping": "auto_clipped_grad clipped_grad per_group",
+    "dpsgd.accounting.amplification": "k_out_of_t parallel_poisson poisson random_allocation",
+    "dpsgd.accounting.mechanisms": "adaclip gaussian",
+    "patches.peft": "apply_peft_model_patches",
+    "patches.torch": "apply_checkpoint_patch is_checkpoint_patched",
+    "patches.transformers": "FamilyPatchFn ForwardFactory ForwardFn ModelPatchFn ModulePatcher apply_transformers_model_patches family_name "
+                            "make_apply_family_patches make_apply_model_patches register_activation_kind register_family "
+                            "register_fused_add_rms_kind register_rms_norm_kind supported_families",
+    "patches.transformers.runtime": "apply_collator_patches apply_grouped_mm_patches apply_masking_patches",
+    "transformers.trainer.types": "EvaluationResult TrainOutput",
+    "accounting.types": "Accountant AdvantageBudget BetaBudget Budget CachedProcess CalibrateResult Composed DeltaBudget DiscretizationConfig "
+                        "DpHorizonProcess DpProcess EpsDelta EpsilonBudget Identity NonPrivate PerStep Repeated RiskBudget",
+    "alignment.dpo.collator.types": "PreferenceBatch PreferenceExample",
+    "alignment.sft.collator.types": "LMBatch LMExample",
+    "auditing.types": "CanaryScores CoinFlip OneRunEstimate",
+    "distributed.collectives": "all_reduce all_reduce_ barrier get_rank get_world_size is_distributed",
+    "distributed.gradients": "reduce_pytree reduce_pytree_ sum_gradients sum_gradients_",
+    "dpftrl.accounting.amplification.types": "BMinSep BallsInBins CyclicPoisson",
+    "dpftrl.accounting.mechanisms.types": "MfGaussian",
+    "dpftrl.accounting.types": "BMinSep BallsInBins CyclicPoisson MfGaussian",
+    "dpftrl.clipping.fun": "auto_clipped_fun auto_scale_pytree clip_pytree clipped_fun",
+    "dpftrl.clipping.types": "AutoClipState AutoClippedFunAux AutoClippedGradAux ClipPytreeAux ClippedFunAux ClippedGradAux ClippedGradFn "
+                             "ClippedGradResult FixedClipState",
+    "dpftrl.noise.types": "BandMfStrategy BisrStrategy BltStrategy BsrStrategy IdentityStrategy LambdaCgdStrategy MFNoiseState MfStrategy "
+                          "SecondMomentMFNoiseState",
+    "dpftrl.sampling.types": "PartitionType",
+    "dpsgd.accounting.amplification.types": "KOutOfT ParallelPoisson Poisson RandomAllocation",
+    "dpsgd.accounting.mechanisms.types": "AdaClip Gaussian",
+    "dpsgd.accounting.types": "AdaClip Gaussian KOutOfT ParallelPoisson Poisson RandomAllocation",
+    "dpsgd.clipping.fun": "auto_clipped_fun auto_scale_pytree clip_pytree clipped_fun",
+    "dpsgd.clipping.types": "AdaptiveClipState AdaptiveClippedGradAux AutoClipState AutoClippedFunAux AutoClippedGradAux ClippingStats "
+                            "ClippedGradFn ClippedGradResult FixedClipState",
+    "dpsgd.noise.types": "GaussianNoiseFn GaussianNoiseInput GaussianNoiseOutput GaussianNoiseState",
+    "optimizers.types": "AdEMAMixState AdadeltaState AdafactorState AdagradState AdamState LionState RAdamState RMSpropState ScheduleFreeState",
+    "patches.transformers.types": "FamilyPatchFn ForwardFactory ForwardFn ModelPatchFn ModulePatcher",
+    "profiling.types": "MemoryStats PerfStage PerfState PerfTracker StepPerf",
+    "random.types": "RngKey",
+    "scheduling.types": "ConstantSchedule CosineSchedule ExponentialSchedule InverseSqrtSchedule LinearSchedule OneMinusSqrtSchedule "
+                        "PolynomialSchedule Schedule WarmupStableDecay WithRestarts WithWarmup",
+}
+
+
+@pytest.mark.parametrize("path", sorted(SUBPATHS))
+def test_deeper_import_paths_of_the_reference_resolve(path):
+    """``from opaque.<path> import name`` of the reference works as ``from opaque_b200.<path> import name``."""
+    mod = importlib.import_module(f"opaque_b200.{path}")
+    missing = [n for n in SUBPATHS[path].split() if not hasattr(mod, n)]
+    assert not missing, f"opaque_b200.{path} lacks {missing}"
+
+
+def test_facades_carry_a_version_and_one_run_stays_callable():
+    import torch
+    import opaque_b200
+    for name in ("accounting", "alignment", "auditing", "dpftrl", "dpsgd", "transformers", "patches"):
+        assert importlib.import_module(f"opaque_b200.{name}").__version__ == opaque_b200.__version__
+    from opaque_b200 import auditing, patches
+    from opaque_b200.auditing.one_run import one_run
+    flips = auditing.coin_flip(range(40), num_canaries=20, key=__import__("opaque_b200.random", fromlist=["key"]).key(1))
+    scores = auditing.canary_scores(torch.arange(20.0))
+    assert auditing.one_run(scores, coin_flip=flips).num_canaries == one_run(scores, coin_flip=flips).num_canaries == 20
+    assert patches.torch is torch or not hasattr(patches, "torch")        # the library's name is not shadowed

@@ -79,7 +79,12 @@ def get_discretization() -> DiscretizationConfig:
 class set_discretization:
     """``set_discretization(cfg)`` sets the ambient config; usable as a context manager to restore it."""
 
-    def __init__(self, config: DiscretizationConfig | None = None, **overrides: Any):
+    def __init__(self, config: "DiscretizationConfig | float | None" = None, **overrides: Any):
+        if isinstance(config, (int, float)) and not isinstance(config, bool):      # set_discretization(1e-3): the grid step first
+            overrides = {"discretization": float(config), **overrides}
+            config = None
+        if "log_x_mass_truncation_bound" in overrides:                             # the reference's name of this field
+            overrides["log_mass_truncation_bound"] = overrides.pop("log_x_mass_truncation_bound")
         base = config or get_discretization()
         self._token = _CONFIG.set(dataclasses.replace(base, **overrides) if overrides else base)
 
@@ -528,22 +533,43 @@ class RiskBudget(Budget):
 _BUDGETS: dict[str, type] = {c.__name__: c for c in (EpsilonBudget, DeltaBudget, AdvantageBudget, BetaBudget, RiskBudget)}
 
 
-def register_budget_serializer(cls: type) -> type:
-    """Register a budget class with the wire codec."""
-    _BUDGETS[cls.__name__] = cls
-    return cls
+_BUDGET_CODECS: dict[type, tuple[str, Any, Any]] = {}        # type -> (wire name, state_dict_fn, from_state_dict_fn)
+
+
+def register_budget_serializer(typ: type, state_dict_fn=None, from_state_dict_fn=None, *, type_name: str | None = None):
+    """Register a budget class with the wire codec.
+
+    ``register_budget_serializer(Cls)`` (also usable as a decorator) is enough for a dataclass: its fields are the state.
+    With ``state_dict_fn(budget) -> JSON-like dict`` and ``from_state_dict_fn(dict) -> budget`` any class can take part;
+    ``type_name`` is the name written into checkpoints (default: the class name) and must be unique."""
+    name = type_name or typ.__name__
+    if name in _BUDGETS and _BUDGETS[name] is not typ:
+        raise ValueError(f"budget type name {name!r} is already registered for {_BUDGETS[name].__name__}")
+    if (state_dict_fn is None) != (from_state_dict_fn is None):
+        raise ValueError("give both state_dict_fn and from_state_dict_fn, or neither")
+    _BUDGETS[name] = typ
+    if state_dict_fn is not None:
+        _BUDGET_CODECS[typ] = (name, state_dict_fn, from_state_dict_fn)
+    return typ
 
 
 def budget_state_dict(b: Budget | None):
     if b is None:
         return None
-    return {"type": type(b).__name__, **dataclasses.asdict(b)}
+    codec = _BUDGET_CODECS.get(type(b))
+    if codec is not None:
+        return {"type": codec[0], "state": codec[1](b)}
+    name = next((n for n, c in _BUDGETS.items() if c is type(b)), type(b).__name__)
+    return {"type": name, **dataclasses.asdict(b)}
 
 
 def budget_from_state_dict(sd: Mapping[str, Any] | None):
     if sd is None:
         return None
     cls = _BUDGETS[sd["type"]]
+    codec = _BUDGET_CODECS.get(cls)
+    if codec is not None:
+        return codec[2](sd["state"])
     return cls(**{k: v for k, v in sd.items() if k != "type"})
 
 

@@ -50,8 +50,11 @@ def _pad(seqs: Sequence[Sequence[int]], value: int, multiple: int | None, max_le
 
 def language_modeling_collator(examples: Sequence[Mapping[str, Any]], *, pad_token_id: int = 0,
                                completion_only: bool = False, pad_to_multiple_of: int | None = None,
-                               max_length: int | None = None) -> dict[str, torch.Tensor]:
-    """Collate ``{"input_ids", ["completion_mask"]}`` rows; an empty list gives zero-length tensors (empty Poisson batch)."""
+                               max_length: int | None = None, completion_only_loss: bool | None = None) -> dict[str, torch.Tensor]:
+    """Collate ``{"input_ids", ["completion_mask"]}`` rows; an empty list gives zero-length tensors (empty Poisson batch).
+    ``completion_only_loss`` is the same switch as ``completion_only`` under its TRL name."""
+    if completion_only_loss is not None:
+        completion_only = bool(completion_only_loss)
     if len(examples) == 0:
         z = torch.zeros((0, pad_to_multiple_of or 1), dtype=torch.long)
         return {"input_ids": z, "attention_mask": z.clone(), "labels": z.clone()}

@@ -18,67 +18,78 @@ import torch
 import torch.nn.functional as F
 
 
-def sigmoid_loss(c, r, *, beta: float, label_smoothing: float = 0.0):
+def sigmoid_loss(chosen_logratio, rejected_logratio, *, beta: float, label_smoothing: float = 0.0):
     """DPO (Rafailov et al. 2023): ``−logσ(βΔ)(1−ε) − logσ(−βΔ)ε``."""
+    c, r = chosen_logratio, rejected_logratio
     d = c - r
     return -F.logsigmoid(beta * d) * (1 - label_smoothing) - F.logsigmoid(-beta * d) * label_smoothing
 
 
-def hinge_loss(c, r, *, beta: float):
+def hinge_loss(chosen_logratio, rejected_logratio, *, beta: float):
     """SLiC-style hinge: ``relu(1 − βΔ)``."""
+    c, r = chosen_logratio, rejected_logratio
     return torch.relu(1 - beta * (c - r))
 
 
-def ipo_loss(c, r, *, beta: float):
+def ipo_loss(chosen_logratio, rejected_logratio, *, beta: float):
     """IPO (Azar et al. 2023): ``(Δ − 1/(2β))²`` (log-ratios are expected length-averaged)."""
+    c, r = chosen_logratio, rejected_logratio
     return (c - r - 1 / (2 * beta)) ** 2
 
 
-def exo_loss(c, r, *, beta: float, label_smoothing: float = 1e-3):
+def exo_loss(chosen_logratio, rejected_logratio, *, beta: float, label_smoothing: float = 1e-3):
     """EXO pairwise (Ji et al. 2024): reverse KL between the preference and the label distribution."""
+    c, r = chosen_logratio, rejected_logratio
     eps = label_smoothing if label_smoothing > 0 else 1e-3
     d = beta * (c - r)
     return (torch.sigmoid(d) * (F.logsigmoid(d) - math.log(1 - eps))
             + torch.sigmoid(-d) * (F.logsigmoid(-d) - math.log(eps)))
 
 
-def nca_loss(c, r, *, beta: float):
+def nca_loss(chosen_logratio, rejected_logratio, *, beta: float):
     """NCA pairwise (Chen et al. 2024)."""
+    c, r = chosen_logratio, rejected_logratio
     return -F.logsigmoid(beta * c) - 0.5 * F.logsigmoid(-beta * c) - 0.5 * F.logsigmoid(-beta * r)
 
 
-def robust_loss(c, r, *, beta: float, label_smoothing: float = 0.1):
+def robust_loss(chosen_logratio, rejected_logratio, *, beta: float, label_smoothing: float = 0.1):
     """Robust DPO (Chowdhury et al. 2024): unbiased under label-flip probability ε."""
+    c, r = chosen_logratio, rejected_logratio
     if not 0 <= label_smoothing < 0.5:
         raise ValueError("robust DPO needs label_smoothing in [0, 0.5)")
     d = beta * (c - r)
     return (-F.logsigmoid(d) * (1 - label_smoothing) + F.logsigmoid(-d) * label_smoothing) / (1 - 2 * label_smoothing)
 
 
-def bco_loss(c, r, *, beta: float, delta: float | torch.Tensor = 0.0):
+def bco_loss(chosen_logratio, rejected_logratio, *, beta: float, delta: float | torch.Tensor = 0.0):
     """BCO pairwise (Jung et al. 2024); ``delta`` is the running mean reward (public state)."""
+    c, r = chosen_logratio, rejected_logratio
     return -F.logsigmoid(beta * c - delta) - F.logsigmoid(-(beta * r - delta))
 
 
-def sppo_loss(c, r, *, beta: float):
+def sppo_loss(chosen_logratio, rejected_logratio, *, beta: float):
     """SPPO hard-label (Wu et al. 2024)."""
+    c, r = chosen_logratio, rejected_logratio
     return (c - 0.5 / beta) ** 2 + (r + 0.5 / beta) ** 2
 
 
-def apo_zero_loss(c, r, *, beta: float):
+def apo_zero_loss(chosen_logratio, rejected_logratio, *, beta: float):
     """APO-zero (D'Oosterlinck et al. 2024): push chosen up, rejected down."""
+    c, r = chosen_logratio, rejected_logratio
     return 1 - torch.sigmoid(beta * c) + torch.sigmoid(beta * r)
 
 
-def apo_down_loss(c, r, *, beta: float):
+def apo_down_loss(chosen_logratio, rejected_logratio, *, beta: float):
     """APO-down: push both down, the rejected one further."""
+    c, r = chosen_logratio, rejected_logratio
     return torch.sigmoid(beta * c) + 1 - torch.sigmoid(beta * (c - r))
 
 
-def discopop_loss(c, r, *, beta: float, tau: float = 0.05):
+def discopop_loss(chosen_logratio, rejected_logratio, *, beta: float, discopop_tau: float = 0.05):
     """DiscoPOP (Lu et al. 2024): log-ratio-modulated blend of logistic and exponential losses."""
+    c, r = chosen_logratio, rejected_logratio
     d = beta * (c - r)
-    mod = torch.sigmoid(d / tau)
+    mod = torch.sigmoid(d / discopop_tau)
     cap = 80.0 if d.dtype in (torch.float32, torch.float64) else 10.0
     return -F.logsigmoid(d) * (1 - mod) + torch.exp((-d).clamp(max=cap)) * mod
 
@@ -88,9 +99,10 @@ def chosen_nll_loss(chosen_nll):
     return chosen_nll
 
 
-def simpo_loss(chosen_avg_logp, rejected_avg_logp, *, beta: float, gamma: float = 0.5, label_smoothing: float = 0.0):
-    """SimPO (Meng et al. 2024): reference-free, length-normalised, with target margin ``γ/β``."""
-    d = beta * (chosen_avg_logp - rejected_avg_logp - gamma / beta)
+def simpo_loss(chosen_logratio, rejected_logratio, *, beta: float, gamma: float = 0.5, label_smoothing: float = 0.0):
+    """SimPO (Meng et al. 2024): reference-free, with target margin ``γ/β``; the two arguments are the LENGTH-NORMALISED
+    policy log-probabilities (the "log-ratios" of a reference-free head)."""
+    d = beta * (chosen_logratio - rejected_logratio - gamma / beta)
     return -F.logsigmoid(d) * (1 - label_smoothing) - F.logsigmoid(-d) * label_smoothing
 
 
@@ -120,8 +132,9 @@ def wpo_weight(chosen_token_logps, chosen_mask, rejected_token_logps, rejected_m
     return w.clamp(max=1.0).detach()
 
 
-def f_divergence_logits(c, r, *, kind: str = "reverse_kl", alpha: float = 0.5):
+def f_divergence_logits(chosen_logratio, rejected_logratio, *, f_divergence_type: str = "reverse_kl", alpha: float = 0.5):
     """Remap ``Δ`` for f-DPO (Wang et al. 2023): reverse KL (identity), JS or α-divergence."""
+    c, r, kind = chosen_logratio, rejected_logratio, f_divergence_type
     if kind == "reverse_kl":
         return c - r
     if kind == "js_divergence":
@@ -158,7 +171,7 @@ def dpo_loss(loss_type: str | Sequence[str], *, chosen_logratio, rejected_lograt
         raise ValueError("loss_weights must match loss_type")
     c, r = chosen_logratio, rejected_logratio
     if f_divergence_type != "reverse_kl":
-        d = f_divergence_logits(c, r, kind=f_divergence_type, alpha=f_alpha)
+        d = f_divergence_logits(c, r, f_divergence_type=f_divergence_type, alpha=f_alpha)
         c, r = d, torch.zeros_like(d)
     total = 0.0
     for t, w in zip(types, weights):
@@ -169,7 +182,7 @@ def dpo_loss(loss_type: str | Sequence[str], *, chosen_logratio, rejected_lograt
         elif t == "bco_pair":
             term = bco_loss(c, r, beta=beta, delta=bco_delta)
         elif t == "discopop":
-            term = discopop_loss(c, r, beta=beta, tau=discopop_tau)
+            term = discopop_loss(c, r, beta=beta, discopop_tau=discopop_tau)
         elif t in PAIR_HEADS:
             term = PAIR_HEADS[t](c, r, beta=beta)
         elif t in ("sft", "chosen_nll"):

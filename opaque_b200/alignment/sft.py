@@ -31,8 +31,10 @@ def token_logps(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = 
     return selective_log_softmax(logits, safe) * mask, mask
 
 
-def sequence_logp(logits: torch.Tensor, labels: torch.Tensor, *, average: bool = False, ignore_index: int = IGNORE_INDEX):
-    """Sum (or mean) of label log-probabilities over each sequence's scored tokens."""
+def sequence_logp(logits: torch.Tensor, labels: torch.Tensor, *, average: bool = False, ignore_index: int = IGNORE_INDEX,
+                  length_normalized: bool | None = None):
+    """Sum (or mean: ``average`` / ``length_normalized``) of label log-probabilities over each sequence's scored tokens."""
+    average = bool(length_normalized) if length_normalized is not None else average
     lp, mask = token_logps(logits, labels, ignore_index)
     total = lp.sum(-1)
     return total / mask.sum(-1).clamp_min(1) if average else total
@@ -49,9 +51,10 @@ def dft_loss(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = IGN
     return -(lp.detach().exp() * lp).sum(-1) / mask.sum(-1).clamp_min(1)
 
 
-def fused_nll_loss(hidden: torch.Tensor, head_weight: torch.Tensor, labels: torch.Tensor,
+def fused_nll_loss(hidden_states: torch.Tensor, lm_head_weight: torch.Tensor, labels: torch.Tensor,
                    ignore_index: int = IGNORE_INDEX, chunk: int = 8192) -> torch.Tensor:
     """``nll_loss`` from final hidden states ``[B, T, d]`` and the output head, through the fused linear-CE node."""
+    hidden, head_weight = hidden_states, lm_head_weight
     B, T = labels.shape
     w = per_example_token_weights(labels, ignore_index).reshape(-1)
     rows = linear_cross_entropy(hidden.reshape(B * T, -1), head_weight, labels.reshape(-1), w, chunk=chunk,
@@ -59,10 +62,11 @@ def fused_nll_loss(hidden: torch.Tensor, head_weight: torch.Tensor, labels: torc
     return rows.view(B, T).sum(1)
 
 
-def fused_dft_loss(hidden: torch.Tensor, head_weight: torch.Tensor, labels: torch.Tensor,
+def fused_dft_loss(hidden_states: torch.Tensor, lm_head_weight: torch.Tensor, labels: torch.Tensor,
                    ignore_index: int = IGNORE_INDEX, chunk: int = 8192) -> torch.Tensor:
     """``dft_loss`` from final hidden states ``[B, T, d]`` and the output head without keeping logits: one pass without
     gradients gives every token's probability (the detached weight), a second pass the weighted NLL."""
+    hidden, head_weight = hidden_states, lm_head_weight
     B, T = labels.shape
     mask = labels != ignore_index
     h2, l1 = hidden.reshape(B * T, -1), labels.reshape(-1)
@@ -74,9 +78,11 @@ def fused_dft_loss(hidden: torch.Tensor, head_weight: torch.Tensor, labels: torc
     return rows.view(B, T).sum(1)
 
 
-def fused_sequence_logp(hidden, head_weight, labels, *, average: bool = False, ignore_index: int = IGNORE_INDEX,
-                        chunk: int = 8192):
+def fused_sequence_logp(hidden_states, lm_head_weight, labels, *, average: bool = False, ignore_index: int = IGNORE_INDEX,
+                        chunk: int = 8192, length_normalized: bool | None = None):
     """Per-sequence (sum or mean) log-probability of the labels from hidden states and the head weight, without keeping logits."""
+    hidden, head_weight = hidden_states, lm_head_weight
+    average = bool(length_normalized) if length_normalized is not None else average
     B, T = labels.shape
     mask = labels != ignore_index
     w = per_example_token_weights(labels, ignore_index) if average else mask.float()

@@ -45,18 +45,41 @@ class CoinFlip:
 
 @dataclasses.dataclass(frozen=True)
 class CanaryScores:
-    """One membership score per canary (higher = more likely included), aligned with ``CoinFlip.canary_indices``."""
+    """One membership score per canary (higher = more likely included).  With ``canary_indices`` (the dataset index behind
+    each score, any order) the scores are joined to a ``CoinFlip`` by identifier; without, they must already be in the
+    order of ``CoinFlip.canary_indices``."""
     scores: np.ndarray
+    canary_indices: np.ndarray | None = None
 
     def __post_init__(self):
         object.__setattr__(self, "scores", np.asarray(self.scores, dtype=np.float64).reshape(-1))
+        if self.canary_indices is not None:
+            ids = np.asarray(self.canary_indices)
+            if ids.ndim != 1 or not np.issubdtype(ids.dtype, np.integer):
+                raise ValueError("canary_indices must be a 1-D integer array")
+            if len(ids) != len(self.scores) or len(np.unique(ids)) != len(ids):
+                raise ValueError("one distinct canary index per score is required")
+            object.__setattr__(self, "canary_indices", ids.astype(np.int64))
+
+    def aligned_to(self, coin_flip: "CoinFlip") -> np.ndarray:
+        """The scores in the order of ``coin_flip.canary_indices`` (joined by identifier when identifiers are attached)."""
+        if self.canary_indices is None:
+            return self.scores
+        pos = {int(i): k for k, i in enumerate(self.canary_indices)}
+        try:
+            return self.scores[[pos[int(i)] for i in coin_flip.canary_indices]]
+        except KeyError as exc:
+            raise ValueError(f"no score for canary {exc.args[0]}") from None
 
 
-def canary_scores(scores: Any) -> CanaryScores:
-    """Wrap an array or tensor of per-canary scores as ``CanaryScores``."""
+def canary_scores(scores: Any, *, canary_indices: Any = None) -> CanaryScores:
+    """Wrap an array or tensor of per-canary scores as ``CanaryScores``; ``canary_indices`` attests which dataset index
+    each score belongs to (scores computed by another pipeline, in whatever order)."""
     if isinstance(scores, torch.Tensor):
         scores = scores.detach().float().cpu().numpy()
-    return CanaryScores(np.asarray(scores))
+    if isinstance(canary_indices, torch.Tensor):
+        canary_indices = canary_indices.cpu().numpy()
+    return CanaryScores(np.asarray(scores), None if canary_indices is None else np.asarray(canary_indices))
 
 
 def coin_flip(dataset: Any, *, num_canaries: int, key: RngKey) -> CoinFlip:
@@ -69,8 +92,66 @@ def coin_flip(dataset: Any, *, num_canaries: int, key: RngKey) -> CoinFlip:
     return CoinFlip(idx, rng.random(num_canaries) < 0.5, n)
 
 
-def loss_scores(loss_fn: Callable[[Any], torch.Tensor], canaries: Sequence[Any], *, baseline_losses: Any = None) -> CanaryScores:
-    """Score = −loss of the trained model on the canary (minus an optional pre-training baseline loss)."""
+def _dataset_scores(per_example, loss_fn, args, batch_argnums, coin_flip, dataset, reference_scores, batch_size, collate_fn) -> CanaryScores:
+    """Shared driver of the dataset forms of ``loss_scores`` / ``gradient_scores``: batches of canaries through
+    ``collate_fn``, one score per canary from ``per_example(call_args, in_dims)``, identifiers attached, reference subtracted."""
+    argnums = tuple(batch_argnums)
+    if not argnums or list(argnums) != sorted(set(argnums)) or min(argnums) < 0:
+        raise ValueError("batch_argnums must be sorted, unique and non-negative")
+    if not isinstance(batch_size, int) or isinstance(batch_size, bool):
+        raise TypeError("batch_size must be an int")
+    if batch_size < 1:
+        raise ValueError("batch_size must be positive")
+    if reference_scores is not None and reference_scores.canary_indices is None:
+        raise TypeError("reference_scores must carry canary identifiers (scores returned by the dataset form do)")
+    collate = collate_fn or torch.utils.data.default_collate
+    ids = [int(i) for i in coin_flip.canary_indices]
+    total = len(args) + len(argnums)
+    out: list[torch.Tensor] = []
+    for lo in range(0, len(ids), batch_size):
+        chunk = ids[lo:lo + batch_size]
+        batch = collate([dataset[i] for i in chunk])
+        parts = [batch] if len(argnums) == 1 else list(batch)
+        if len(parts) != len(argnums):
+            raise ValueError(f"collate_fn returned {len(parts)} batch arguments for batch_argnums={argnums}")
+        fixed = iter(args)
+        call = [parts[argnums.index(p)] if p in argnums else next(fixed) for p in range(total)]
+        in_dims = tuple(0 if p in argnums else None for p in range(total))
+        vals = per_example(call, in_dims).detach().float().reshape(-1).cpu()
+        if vals.numel() != len(chunk):
+            raise ValueError("collate_fn changed the number of rows of a batch")
+        out.append(vals)
+    scores = -torch.cat(out).numpy() if out else np.zeros(0)
+    result = CanaryScores(scores, np.asarray(ids, dtype=np.int64))
+    if reference_scores is not None:
+        result = CanaryScores(result.scores - reference_scores.aligned_to(coin_flip), result.canary_indices)
+    return result
+
+
+def loss_scores(loss_fn: Callable[..., torch.Tensor], *args: Any, batch_argnums: Sequence[int] | None = None,
+                coin_flip: "CoinFlip | None" = None, dataset: Any = None, reference_scores: CanaryScores | None = None,
+                batch_size: int = 32, collate_fn: Callable | None = None, baseline_losses: Any = None) -> CanaryScores:
+    """Score = −loss of the trained model on the canary.
+
+    Two forms.  ``loss_scores(loss_fn, canaries, baseline_losses=None)``: ``loss_fn(canary)`` for every element of a list,
+    in the order of ``CoinFlip.canary_indices``.  Dataset form (the reference's):
+    ``loss_scores(loss_fn, *fixed_args, batch_argnums=(1,), coin_flip=flips, dataset=data)`` — ``loss_fn`` is written for
+    ONE example (as for ``clipped_grad``), the canaries of ``dataset`` are collated ``batch_size`` at a time and mapped
+    with ``vmap``; the result carries each canary's dataset index, and ``reference_scores`` (the same call on the
+    untrained model) is subtracted by identifier.
+
+    Parity: packages/opaque-auditing/src/opaque/api/auditing/attacks/_loss.py:30."""
+    if coin_flip is not None or dataset is not None or batch_argnums is not None:
+        if coin_flip is None or dataset is None or batch_argnums is None:
+            raise ValueError("the dataset form needs batch_argnums=, coin_flip= and dataset=")
+
+        def per_example(call, in_dims):
+            with torch.no_grad():
+                return torch.func.vmap(loss_fn, in_dims=in_dims)(*call)
+        return _dataset_scores(per_example, loss_fn, args, batch_argnums, coin_flip, dataset, reference_scores, batch_size, collate_fn)
+    if len(args) != 1:
+        raise TypeError("loss_scores(loss_fn, canaries) takes one list of canaries (or use the dataset form)")
+    canaries = args[0]
     with torch.no_grad():
         losses = np.array([float(loss_fn(c)) for c in canaries])
     if baseline_losses is not None:
@@ -78,8 +159,38 @@ def loss_scores(loss_fn: Callable[[Any], torch.Tensor], canaries: Sequence[Any],
     return CanaryScores(-losses)
 
 
-def gradient_scores(canary_grads: Sequence[Any], released_updates: Sequence[Any]) -> CanaryScores:
-    """Score = Σ_t ⟨g_canary,t , released_t⟩ : the canary's gradient direction shows up in the noisy sums it joined."""
+def gradient_scores(*args: Any, batch_argnums: Sequence[int] | None = None, coin_flip: "CoinFlip | None" = None,
+                    dataset: Any = None, reference_scores: CanaryScores | None = None, batch_size: int = 32,
+                    collate_fn: Callable | None = None) -> CanaryScores:
+    """Two forms.  ``gradient_scores(canary_grads, released_updates)``: score = Σ_t ⟨g_canary,t , released_t⟩ — the canary's
+    gradient direction shows up in the noisy sums it joined (white-box, needs the released updates).  Dataset form (the
+    reference's): ``gradient_scores(loss_fn, params, *fixed_args, batch_argnums=(1,), coin_flip=flips, dataset=data)`` —
+    score = −‖∇_params loss(example)‖², one example at a time (a member's gradient is smaller after training);
+    ``reference_scores`` from the untrained model are subtracted by identifier.
+
+    Parity: packages/opaque-auditing/src/opaque/api/auditing/attacks/_gradient.py:35."""
+    if coin_flip is not None or dataset is not None or batch_argnums is not None:
+        if coin_flip is None or dataset is None or batch_argnums is None or len(args) < 2:
+            raise ValueError("the dataset form is gradient_scores(loss_fn, params, ..., batch_argnums=, coin_flip=, dataset=)")
+        if 0 in tuple(batch_argnums):
+            raise ValueError("position 0 is the parameters: it cannot be a batch argument")
+        loss_fn, fixed = args[0], args[1:]
+        from ..pytree import tree_leaves
+        grad_fn = torch.func.grad(loss_fn, argnums=0)
+
+        def per_example(call, in_dims):
+            rows = next(len(tree_leaves(call[p])[0]) for p, d in enumerate(in_dims) if d == 0)
+            vals = []
+            for i in range(rows):
+                one = [tree_map_index(c, i) if d == 0 else c for c, d in zip(call, in_dims)]
+                g = grad_fn(*one)
+                vals.append(sum(float((x.detach().float() ** 2).sum()) for x in tree_leaves(g) if isinstance(x, torch.Tensor)))
+            return torch.tensor(vals)
+        return _dataset_scores(per_example, loss_fn, fixed, batch_argnums, coin_flip, dataset, reference_scores, batch_size, collate_fn)
+    if len(args) != 2:
+        raise TypeError("gradient_scores(canary_grads, released_updates) takes two sequences (or use the dataset form)")
+    canary_grads, released_updates = args
+
     def flat(tree):
         from ..pytree import tree_leaves
         return torch.cat([x.detach().float().reshape(-1).cpu() for x in tree_leaves(tree) if isinstance(x, torch.Tensor)])
@@ -88,6 +199,12 @@ def gradient_scores(canary_grads: Sequence[Any], released_updates: Sequence[Any]
         steps = per_canary if isinstance(per_canary, (list, tuple)) else [per_canary] * len(released_updates)
         out.append(sum(float(flat(g) @ flat(u)) for g, u in zip(steps, released_updates)))
     return CanaryScores(np.array(out))
+
+
+def tree_map_index(tree: Any, i: int) -> Any:
+    """Row ``i`` of every tensor leaf of a batch."""
+    from ..pytree import tree_map
+    return tree_map(lambda x: x[i] if isinstance(x, torch.Tensor) else x, tree)
 
 
 # ------------------------------------------------------------------------------------------ estimators
@@ -190,7 +307,7 @@ def one_run(scores: CanaryScores, *, coin_flip: CoinFlip, num_guesses: int | Non
     With ``num_guesses=None`` and ``search=True`` a ladder of k values is tried and the confidence is split across
     them (union bound), so the reported bound stays valid.
     """
-    s, y = scores.scores, coin_flip.included.astype(bool)
+    s, y = scores.aligned_to(coin_flip), coin_flip.included.astype(bool)
     m = len(s)
     if m != coin_flip.num_canaries:
         raise ValueError("one score per canary is required")

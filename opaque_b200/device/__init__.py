@@ -66,8 +66,8 @@ def fused_kernels_available() -> bool:
     return device_capabilities().fused_kernels
 
 
-def sdpa_autocast_under_vmap_broken() -> bool:
-    """An Apple-MPS quirk of the reference; never true on CUDA or CPU."""
+def sdpa_autocast_under_vmap_broken(device_type: str | None = None) -> bool:
+    """An Apple-MPS quirk of the reference; never true on CUDA or CPU (``device_type`` is accepted for call compatibility)."""
     return False
 
 

@@ -262,12 +262,13 @@ def _packed_all_reduce_(leaves: list[torch.Tensor], op: str) -> None:
             off += g.numel()
 
 
-def reduce_pytree_(tree: Any, op: str = "sum", *, check_metadata: bool = True) -> Any:
+def reduce_pytree_(pytree: Any, op: str = "sum", *, check_metadata: bool = True) -> Any:
     """In-place cross-rank reduction of a (wrapped) gradient tree.
 
     ``sum`` keeps ``max_norm`` (each record lives on one rank) and multiplies a
     noise σ by √W (independent noises add in variance); ``mean`` divides both by W.
     """
+    tree = pytree
     if op not in ("sum", "mean"):
         raise ValueError("reduce_pytree_ supports op='sum' or 'mean'")
     if isinstance(tree, SecondMomentClippingOutput):
@@ -294,8 +295,9 @@ def reduce_pytree_(tree: Any, op: str = "sum", *, check_metadata: bool = True) -
     return tree
 
 
-def reduce_pytree(tree: Any, op: str = "sum", **kw: Any) -> Any:
+def reduce_pytree(pytree: Any, op: str = "sum", **kw: Any) -> Any:
     """Out-of-place ``reduce_pytree_``."""
+    tree = pytree
     if isinstance(tree, SecondMomentClippingOutput):
         return SecondMomentClippingOutput(reduce_pytree(tree.grads, op, **kw), reduce_pytree(tree.squared_grads, op, **kw))
     cloned = tree.clone() if isinstance(tree, ClippedPytree) else tree_map(
@@ -303,13 +305,15 @@ def reduce_pytree(tree: Any, op: str = "sum", **kw: Any) -> Any:
     return reduce_pytree_(cloned, op, **kw)
 
 
-def sum_gradients_(tree: Any) -> Any:
+def sum_gradients_(gradients: Any) -> Any:
     """Sum a ``ClippedPytree`` over ranks in place (one packed all-reduce); the sensitivity metadata must agree on every rank."""
+    tree = gradients
     return reduce_pytree_(tree, "sum")
 
 
-def sum_gradients(tree: Any) -> Any:
+def sum_gradients(gradients: Any) -> Any:
     """Out-of-place ``sum_gradients_``."""
+    tree = gradients
     return reduce_pytree(tree, "sum")
 
 

@@ -130,13 +130,28 @@ def parallel_poisson(inner: DpProcess, sample_rate: float, num_workers: int) -> 
     return ParallelPoisson(inner, float(sample_rate), int(num_workers))
 
 
-def random_allocation(inner: DpProcess, num_bins: int) -> RandomAllocation:
-    """Whole-epoch process: do NOT multiply by the steps of the epoch, multiply by the number of epochs."""
-    return RandomAllocation(inner, int(num_bins), 1)
+def random_allocation(inner: DpProcess, num_bins: int, n_steps: int | None = None) -> DpProcess:
+    """Whole-epoch process: do NOT multiply by the steps of the epoch, multiply by the number of epochs.
+
+    With ``n_steps`` (the reference's horizon form) the result already covers ``ceil(n_steps / num_bins)`` epochs — a
+    started epoch is charged in full, which bounds a run that stops inside it."""
+    epoch = RandomAllocation(inner, int(num_bins), 1)
+    if n_steps is None:
+        return epoch
+    epochs = max(-(-int(n_steps) // int(num_bins)), 1)
+    return epoch if epochs == 1 else epoch * epochs
 
 
-def k_out_of_t(inner: DpProcess, k: int, t: int) -> RandomAllocation:
-    """Each record participates in exactly ``k`` of every ``t`` steps (fixed-participation sampling)."""
+def k_out_of_t(inner: DpProcess, k: int | None = None, t: int | None = None, *, total_participations: int | None = None,
+               n_steps: int | None = None) -> RandomAllocation:
+    """Each record participates in exactly ``k`` of every ``t`` steps (fixed-participation sampling).  The reference's
+    keywords name the whole-run form: ``total_participations`` of ``n_steps`` steps (``k = total_participations, t = n_steps``)."""
+    if total_participations is not None or n_steps is not None:
+        if k is not None or t is not None or total_participations is None or n_steps is None:
+            raise ValueError("give (k, t) or (total_participations=, n_steps=)")
+        k, t = total_participations, n_steps
+    if k is None or t is None:
+        raise ValueError("give (k, t) or (total_participations=, n_steps=)")
     return RandomAllocation(inner, int(t), int(k))
 
 

@@ -107,7 +107,14 @@ class KOutOfTSampler(_Resumable):
     holding slot ``s``.  Windows use ``fold_in(key, window_index)``.
     """
 
-    def __init__(self, data_source: Sized, k: int, t: int, n_steps: int | None = None, *, key: RngKey):
+    def __init__(self, data_source: Sized, k: int | None = None, t: int | None = None, n_steps: int | None = None, *, key: RngKey,
+                 total_participations: int | None = None):
+        if total_participations is not None:        # the reference's keywords: k of the WHOLE run of n_steps steps
+            if k is not None or t is not None or n_steps is None:
+                raise ValueError("give (k, t) or (total_participations=, n_steps=)")
+            k, t = int(total_participations), int(n_steps)
+        if k is None or t is None:
+            raise ValueError("give (k, t) or (total_participations=, n_steps=)")
         if not 1 <= k <= t:
             raise ValueError(f"need 1 <= k <= t, got k={k}, t={t}")
         if n_steps is not None and n_steps < 1:

@@ -80,8 +80,34 @@ def with_batch_dim(fn: Callable, batch_argnums: int | Sequence[int] = (), batch_
     return wrapped
 
 
-def empty_collate(example: Any) -> Any:
-    """A batch of zero examples shaped like ``example`` (one element of the dataset)."""
+def empty_collate(collate_fn: Any) -> Any:
+    """Given a collate FUNCTION: the same function, except that an empty list of examples (an empty Poisson draw) gives a
+    batch with the structure of the first non-empty batch it has seen and a zero-length batch dimension (an empty first
+    call still reaches the wrapped function, which is the right place for that error).
+
+    Given an EXAMPLE (anything not callable): a batch of zero examples shaped like it (one element of the dataset).
+
+    Parity: packages/opaque-engine/src/opaque/api/engine/functional/_collate.py:50-101."""
+    if callable(collate_fn) and not isinstance(collate_fn, torch.Tensor):
+        import functools
+        seen: list[Any] = []
+
+        def empty_batch(x: Any):
+            if isinstance(x, torch.Tensor):
+                return x.new_zeros((0,) + tuple(x.shape[1:])) if x.ndim else x.new_zeros((0,))
+            return x
+
+        @functools.wraps(collate_fn)
+        def wrapped(examples, *args, **kwargs):
+            if len(examples) == 0 and seen:
+                return tree_map(empty_batch, seen[0])
+            out = collate_fn(examples, *args, **kwargs)
+            if len(examples) and not seen:
+                seen.append(tree_map(lambda x: x[:0].clone() if isinstance(x, torch.Tensor) and x.ndim else x, out))
+            return out
+        return wrapped
+    example = collate_fn
+
     def zero_len(x: Any):
         if isinstance(x, torch.Tensor):
             return x.new_zeros((0,) + tuple(x.shape))

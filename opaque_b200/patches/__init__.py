@@ -614,7 +614,7 @@ def is_runtime_patched() -> bool:
     return _RUNTIME["patched"]
 
 
-def apply_checkpoint_patch() -> bool:
+def apply_checkpoint_patch(vmap_checkpointing: bool = True) -> bool:
     """Activation checkpointing under per-example gradients needs no patch of ``torch.utils.checkpoint`` here: the fused
     engine is explicit-batch (the stock checkpoint works), and under ``vmap(grad)`` this package's models use
     ``functional.functional_checkpoint``.  Kept so that set-up code written for the reference runs; marks the call."""
@@ -627,17 +627,17 @@ def is_checkpoint_patched() -> bool:
     return bool(_RUNTIME.get("checkpoint"))
 
 
-def apply_masking_patches() -> str:
+def apply_masking_patches(vmap_masking: bool = True) -> str:
     """Attention-mask construction under ``vmap``: not needed (framework models build masks from shapes only)."""
     return apply_runtime_patches()["vmap_masking"]
 
 
-def apply_collator_patches() -> str:
+def apply_collator_patches(empty_batches: bool = True) -> str:
     """Empty Poisson batches in collators: handled by ``alignment.data`` collators themselves."""
     return apply_runtime_patches()["empty_batches"]
 
 
-def apply_grouped_mm_patches() -> str:
+def apply_grouped_mm_patches(vmap_grouped_mm: bool = True) -> str:
     """Grouped expert GEMMs under ``vmap``: not needed (they are called outside ``vmap``)."""
     return apply_runtime_patches()["vmap_grouped_mm"]
 

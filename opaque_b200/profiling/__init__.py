@@ -105,11 +105,13 @@ def empty_cache(device: Any = None) -> None:
         torch.cuda.empty_cache()
 
 
-def print_memory(device: Any = None, prefix: str = "") -> None:
-    """Print ``get_memory_stats`` in MiB with an optional prefix."""
+def print_memory(device: Any = None, label: str = "", *, prefix: str = "") -> MemoryStats:
+    """Print ``get_memory_stats`` in GiB behind an optional ``[label]`` (or a literal ``prefix``) and return the stats."""
     s = get_memory_stats(device)
+    prefix = f"[{label}] " if label else prefix
     print(f"{prefix}allocated={s.allocated_bytes / 2**30:.2f}GiB reserved={s.reserved_bytes / 2**30:.2f}GiB "
           f"peak={s.peak_allocated_bytes / 2**30:.2f}GiB")
+    return s
 
 
 @dataclasses.dataclass(frozen=True)

@@ -88,12 +88,25 @@ def random_key() -> RngKey:
     return key(int.from_bytes(os.urandom(8), "little"))
 
 
-def set_reproducible_pytorch_seed(seed: int) -> RngKey:
-    """Seed python, numpy and torch global generators and return ``key(seed)``."""
+def set_reproducible_pytorch_seed(key_val: "RngKey | int", *, deterministic: bool = True) -> RngKey:
+    """Seed the python, numpy and torch (CPU and every CUDA device) global generators from one key (or integer seed) and
+    return the key.  With ``deterministic`` also asks cuDNN for deterministic algorithms and sets the cuBLAS workspace
+    variable that deterministic GEMMs need.  Global state: call once at the start of a script.
+
+    Parity: packages/opaque-engine/src/opaque/api/engine/random/_helpers.py:39."""
+    k = key_val if isinstance(key_val, RngKey) else key(int(key_val))
+    seed = int(k.seed)
     _pyrandom.seed(seed)
     np.random.seed(seed % (1 << 32))
     torch.manual_seed(seed % _TORCH_SEED_MOD)
-    return key(seed)
+    if torch.cuda.is_available():
+        torch.cuda.manual_seed_all(seed % _TORCH_SEED_MOD)
+    if deterministic:
+        import os
+        torch.backends.cudnn.deterministic = True
+        torch.backends.cudnn.benchmark = False
+        os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
+    return k
 
 
 from ..serialization import register_serializer as _reg  # noqa: E402

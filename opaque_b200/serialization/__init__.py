@@ -24,27 +24,28 @@ _HANDLERS: dict[type, Serializer] = {}
 _SCALARS = (bool, int, float, str, type(None))
 
 
-def register_serializer(cls: type, save: StateDictFn, load: FromStateDictFn) -> None:
-    """Attach a ``(save, load)`` pair to ``cls`` (and, through the MRO, its subclasses).
+def register_serializer(typ: type, state_dict_fn: StateDictFn, from_state_dict_fn: FromStateDictFn) -> None:
+    """Attach a ``(save, load)`` pair to ``typ`` (and, through the MRO, its subclasses).
 
-    ``save(obj)`` returns keys *relative* to the object (``""`` occupies the
-    object's own slot); ``load(template, sub)`` receives the same relative keys.
+    ``state_dict_fn(obj)`` returns keys *relative* to the object (``""`` occupies the
+    object's own slot); ``from_state_dict_fn(template, sub)`` receives the same relative keys.
     """
-    _HANDLERS[cls] = (save, load)
+    _HANDLERS[typ] = (state_dict_fn, from_state_dict_fn)
 
 
-def register_template_restored(cls: type) -> None:
-    """Declare ``cls`` inert: nothing is written and the template's value is reused."""
-    _HANDLERS[cls] = (lambda obj: {}, lambda template, sub: template)
+def register_template_restored(typ: type) -> None:
+    """Declare ``typ`` inert: nothing is written and the template's value is reused."""
+    _HANDLERS[typ] = (lambda obj: {}, lambda template, sub: template)
 
 
-def lookup_serializer(cls: type) -> Serializer | None:
+def lookup_serializer(typ: type) -> Serializer | None:
     """Exact-type lookup only."""
-    return _HANDLERS.get(cls)
+    return _HANDLERS.get(typ)
 
 
-def resolve_serializer(cls: type) -> Serializer | None:
+def resolve_serializer(typ: type) -> Serializer | None:
     """Exact type, then each base class in MRO order."""
+    cls = typ
     for base in getattr(cls, "__mro__", (cls,)):
         hit = _HANDLERS.get(base)
         if hit is not None:

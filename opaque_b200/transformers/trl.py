@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import copy
 import dataclasses
+import os
 from collections.abc import Mapping, Sequence
 from typing import Any
 
@@ -36,6 +37,12 @@ class SFTConfig(TrainingArguments):
     pad_to_multiple_of: int | None = None
     logging_steps: int = 10
     use_performance_kernels: bool = True
+    model_init_kwargs: dict | None = None       # used when ``model`` is a local checkpoint path
+    trust_remote_code: bool = False
+    eos_token: str | None = None                # set on the tokenizer before tokenisation
+    chat_template_path: str | None = None       # a template file (or a directory holding chat_template.jinja) for the tokenizer
+    dataset_num_proc: int | None = None         # accepted; tokenisation here is single-process
+    log_completion_metrics: bool = False        # evaluate() adds mean token accuracy and entropy on the evaluation set
 
     def __post_init__(self):
         super().__post_init__()
@@ -44,10 +51,14 @@ class SFTConfig(TrainingArguments):
 
 
 class SFTTrainer(DPTrainer):
+    _INERT_FIELDS = DPTrainer._INERT_FIELDS + ("dataset_num_proc",)
+
     def __init__(self, model=None, args: SFTConfig | None = None, train_dataset=None, eval_dataset=None,
                  processing_class=None, data_collator=None, **kw: Any):
         args = args or SFTConfig()
         self._sft = args
+        model = _load_if_path(model, args)
+        _prepare_tokenizer(processing_class, args)
         train_dataset = self._prepare_dataset(train_dataset, processing_class, args)
         eval_dataset = self._prepare_dataset(eval_dataset, processing_class, args)
         completion_only = self._resolve_completion_only(args, train_dataset)
@@ -108,6 +119,59 @@ class SFTTrainer(DPTrainer):
         fn = sft_losses.dft_loss if self._sft.loss_type == "dft" else sft_losses.nll_loss
         return fn(logits, example["labels"].unsqueeze(0)).squeeze(0)
 
+    @torch.no_grad()
+    def evaluate(self, eval_dataset: Any = None, ignore_keys=None, metric_key_prefix: str = "eval") -> dict[str, float]:
+        metrics = super().evaluate(eval_dataset, ignore_keys, metric_key_prefix)
+        data = eval_dataset if eval_dataset is not None else self.eval_dataset
+        if self._sft.log_completion_metrics and data is not None and len(data):
+            # token statistics of the EVALUATION set (not training data): accuracy and entropy on the scored positions
+            from ..distributed import local_shard, reduce_scalar
+            a = self.args
+            shard = local_shard(data, rank=a.process_index, world_size=a.world_size)
+            was_training = self.model.training
+            self.model.eval()
+            acc_sum = ent_sum = count = 0.0
+            for lo in range(0, len(shard), a.eval_batch_size):
+                batch = self._to_device(self.data_collator([shard[i] for i in range(lo, min(len(shard), lo + a.eval_batch_size))]))
+                logits = self.model(batch["input_ids"])
+                logits = getattr(logits, "logits", logits).float()
+                keep = batch["labels"] != -100                               # labels are already aligned with the logits
+                n = float(keep.sum())
+                acc_sum += float(((logits.argmax(-1) == batch["labels"]) & keep).sum())
+                logp = logits.log_softmax(-1)
+                ent_sum += float((-(logp.exp() * logp).sum(-1) * keep).sum())
+                count += n
+            self.model.train(was_training)
+            acc_sum, ent_sum, count = (float(reduce_scalar(v, "sum")) for v in (acc_sum, ent_sum, count))
+            extra = {f"{metric_key_prefix}_mean_token_accuracy": acc_sum / max(count, 1.0), f"{metric_key_prefix}_entropy": ent_sum / max(count, 1.0)}
+            metrics.update(extra)
+            self.log(extra)
+        return metrics
+
+
+def _load_if_path(model: Any, args: Any) -> Any:
+    """A local checkpoint directory instead of a model object: load it with Hugging Face (offline) and convert it."""
+    if not isinstance(model, (str, os.PathLike)):
+        return model
+    import transformers
+    from .. import patches
+    hf = transformers.AutoModelForCausalLM.from_pretrained(model, local_files_only=True, trust_remote_code=bool(args.trust_remote_code),
+                                                           **(args.model_init_kwargs or {}))
+    return patches.apply_model_patches(hf, dtype=torch.bfloat16 if args.bf16 else torch.float32)
+
+
+def _prepare_tokenizer(tokenizer: Any, args: Any) -> None:
+    if tokenizer is None:
+        return
+    if getattr(args, "eos_token", None):
+        tokenizer.eos_token = args.eos_token
+    path = getattr(args, "chat_template_path", None)
+    if path:
+        if os.path.isdir(path):
+            path = os.path.join(path, "chat_template.jinja")
+        with open(path, encoding="utf-8") as f:
+            tokenizer.chat_template = f.read()
+
 
 @dataclasses.dataclass
 class DPOConfig(TrainingArguments):
@@ -130,6 +194,11 @@ class DPOConfig(TrainingArguments):
     ref_model_mixup_alpha: float = 0.6
     ref_model_sync_steps: int = 512
     max_length: int | None = 1024
+    pad_to_multiple_of: int | None = None
+    model_init_kwargs: dict | None = None       # used when ``model`` is a local checkpoint path
+    trust_remote_code: bool = False
+    dataset_num_proc: int | None = None         # accepted; tokenisation here is single-process
+    log_completion_metrics: bool = False        # accepted; reward accuracies and margins are always logged
 
     def __post_init__(self):
         super().__post_init__()
@@ -143,14 +212,17 @@ class DPOConfig(TrainingArguments):
 
 class DPOTrainer(DPTrainer):
     """DP-DPO; ``ref_model=None`` uses a frozen copy of the initial policy (or the base model under LoRA)."""
+    _INERT_FIELDS = DPTrainer._INERT_FIELDS + ("dataset_num_proc", "log_completion_metrics")
 
     def __init__(self, model=None, ref_model=None, args: DPOConfig | None = None, train_dataset=None, eval_dataset=None,
                  processing_class=None, data_collator=None, **kw: Any):
         args = args or DPOConfig()
         self._dpo = args
+        model = _load_if_path(model, args)
         if data_collator is None:
             pad = getattr(processing_class, "pad_token_id", None) or 0
-            data_collator = lambda rows: adata.preference_collator(rows, pad_token_id=pad, max_length=args.max_length)
+            data_collator = lambda rows: adata.preference_collator(rows, pad_token_id=pad, max_length=args.max_length,
+                                                                   pad_to_multiple_of=args.pad_to_multiple_of)
         train_dataset = self._prepare(train_dataset, processing_class)
         eval_dataset = self._prepare(eval_dataset, processing_class)
         if args.disable_dropout:

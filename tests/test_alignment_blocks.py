@@ -201,3 +201,39 @@ def test_factory_api_patches_a_new_family_in_place():
     assert apply(Toy(), mlp=False) == {"rms_norm": 2, "mlp": 0}
     with pytest.raises(ValueError, match="not registered"):
         make_apply_model_patches(family="t", classes={"rms_norm": "ToyNorm"}, rms_norm_kind="nope")
+
+
+def test_auditing_dataset_forms_join_scores_by_identifier():
+    """The dataset forms of ``loss_scores`` / ``gradient_scores`` (per-example loss as for ``clipped_grad``) against plain
+    loops; scores carry the canaries' dataset indices, so a shuffled copy audits the same."""
+    import numpy as np
+    from opaque_b200 import auditing
+    from opaque_b200.random import key
+    torch.manual_seed(0)
+    X, Y = torch.randn(60, 5), torch.randn(60)
+    data = [(X[i], Y[i]) for i in range(60)]
+    flips = auditing.coin_flip(data, num_canaries=20, key=key(1))
+    kept = flips.kept_indices()
+    w0, w = torch.zeros(5), torch.linalg.lstsq(X[kept], Y[kept].unsqueeze(1)).solution.squeeze(1)
+    loss = lambda p, x, y: (x @ p - y) ** 2
+    kw = dict(batch_argnums=(1, 2), coin_flip=flips, dataset=data, batch_size=7)
+    ref = auditing.loss_scores(loss, w0, **kw)
+    cur = auditing.loss_scores(loss, w, reference_scores=ref, **kw)
+    want = np.array([float(loss(w0, *data[i]) - loss(w, *data[i])) for i in flips.canary_indices])
+    assert np.allclose(cur.scores, want, atol=1e-5) and np.array_equal(cur.canary_indices, flips.canary_indices)
+    grad = auditing.gradient_scores(loss, w, **kw)
+    want_g = np.array([-float(((2 * (data[i][0] @ w - data[i][1]) * data[i][0]) ** 2).sum()) for i in flips.canary_indices])
+    assert np.allclose(grad.scores, want_g, rtol=1e-4)
+    shuffled = auditing.canary_scores(cur.scores[::-1].copy(), canary_indices=cur.canary_indices[::-1].copy())
+    a, b = auditing.one_run(shuffled, coin_flip=flips), auditing.one_run(cur, coin_flip=flips)
+    assert (a.num_correct, a.num_guesses, a.epsilon_lower_bound) == (b.num_correct, b.num_guesses, b.epsilon_lower_bound)
+    legacy = auditing.loss_scores(lambda c: (c[0] @ w - c[1]) ** 2, [data[i] for i in flips.canary_indices])
+    assert np.allclose(legacy.scores, -np.array([float(loss(w, *data[i])) for i in flips.canary_indices]), atol=1e-6)
+    with pytest.raises(ValueError):
+        auditing.gradient_scores(loss, w, batch_argnums=(0, 1), coin_flip=flips, dataset=data)
+    with pytest.raises(TypeError):
+        auditing.loss_scores(loss, w, reference_scores=legacy, **kw)
+    with pytest.raises(ValueError):
+        auditing.canary_scores([1.0, 2.0], canary_indices=[3, 3])
+    with pytest.raises(ValueError):
+        auditing.one_run(auditing.canary_scores(cur.scores, canary_indices=np.arange(20) + 1000), coin_flip=flips)

@@ -482,3 +482,29 @@ def test_push_to_hub_uploads_the_model_folder_without_run_state(tmp_path):
     assert len(api.created) == 1 and api.uploads[-1]["run_as_future"] is True and api.uploads[-1]["commit_message"] == "second push"
     assert set(hub.NEVER_UPLOADED) >= {"checkpoint-*", "dp_state.pt", "optimizer.pt", "rng_state*.pth"}
     assert hub.resolve_repo_id(types.SimpleNamespace(hub_model_id="org/name", output_dir="x")) == "org/name"
+
+
+def test_sft_config_fields_of_trl_act(tmp_path):
+    """``eos_token`` / ``chat_template_path`` reach the tokenizer, ``log_completion_metrics`` adds token statistics of the
+    evaluation set, ``dataset_num_proc`` is accepted and reported as inert, DPO pads pairs to a multiple."""
+    from opaque_b200.transformers.trl import DPOConfig, SFTConfig, SFTTrainer
+
+    class Tok:
+        pad_token_id, eos_token, chat_template = 0, "</s>", None
+
+        def __call__(self, text, add_special_tokens=True):
+            return {"input_ids": [1 + (ord(ch) % 30) for ch in text]}
+    (tmp_path / "tpl").mkdir()
+    (tmp_path / "tpl" / "chat_template.jinja").write_text("{% for m in messages %}{{ m['content'] }}{% endfor %}")
+    tok = Tok()
+    rows = [{"prompt": "ab", "completion": "cde"} for _ in range(32)]
+    args = SFTConfig(output_dir=str(tmp_path / "o"), per_device_train_batch_size=8, max_steps=1, privacy_noise_multiplier=1.0, use_cpu=True,
+                     save_steps=0, eos_token="<end>", chat_template_path=str(tmp_path / "tpl"), log_completion_metrics=True,
+                     dataset_num_proc=4, max_length=16)
+    tr = SFTTrainer(model=TinyLM(), args=args, train_dataset=rows, eval_dataset=rows[:8], processing_class=tok)
+    assert tok.eos_token == "<end>" and "messages" in tok.chat_template
+    assert set(tr.inert_arguments()) == {"dataset_num_proc"}
+    out = tr.evaluate()
+    assert 0.0 <= out["eval_mean_token_accuracy"] <= 1.0 and out["eval_entropy"] > 0 and out["eval_loss"] > 0
+    cfg = DPOConfig(privacy_noise_multiplier=1.0, pad_to_multiple_of=8, dataset_num_proc=2, model_init_kwargs={"torch_dtype": "float32"})
+    assert cfg.pad_to_multiple_of == 8 and cfg.trust_remote_code is False

@@ -27,6 +27,28 @@ class DeviceCapabilities:
     fused_kernels: bool
     peer_access: bool
 
+    # the reference's names for the same facts
+    @property
+    def supports_fused_kernels(self) -> bool:
+        return self.fused_kernels
+
+    @property
+    def supports_compile(self) -> bool:
+        """No tracing compiler is used on the hot path; ``torch.compile`` itself works wherever PyTorch supports it."""
+        return self.device_type in ("cuda", "cpu")
+
+    @property
+    def recommended_compile_backend(self) -> str | None:
+        return None
+
+    @property
+    def peak_memory_trackable(self) -> bool:
+        return self.device_type == "cuda"
+
+    @property
+    def supports_pin_memory(self) -> bool:
+        return self.device_type == "cuda"
+
 
 @functools.lru_cache(maxsize=None)
 def _probe(index: int) -> DeviceCapabilities:

@@ -189,9 +189,19 @@ _strategy_process_codec(BMinSep)
 
 
 def b_min_sep(inner: MfGaussian, *, bands: int, n_steps: int, max_participations: int | None = None,
-              sampling_prob: float | None = None, warm_start: bool = False):
+              sampling_prob: float | None = None, warm_start: bool = False, p0: float | None = None):
     """b-min-sep participation.  With ``sampling_prob`` the amplified Monte-Carlo accountant is used; without it the
-    scheme is only a sensitivity constraint on the un-amplified mechanism (an upper bound for any sampling rate)."""
+    scheme is only a sensitivity constraint on the un-amplified mechanism (an upper bound for any sampling rate).
+
+    ``p0`` states the rate the other way round: the STATIONARY per-example participation rate (expected batch size over
+    the number of records).  A record that is available is then included with probability ``p0 / (1 − p0·(bands − 1))``,
+    which is what ``sampling_prob`` means; give one of the two."""
+    if p0 is not None:
+        if sampling_prob is not None:
+            raise ValueError("give sampling_prob or p0, not both")
+        if not 0.0 < p0 < 1.0 or (bands > 1 and p0 * (bands - 1) >= 1.0):
+            raise ValueError(f"p0={p0} is infeasible for bands={bands}: need 0 < p0 < 1/(bands-1)")
+        sampling_prob = p0 / (1.0 - p0 * (bands - 1))
     if sampling_prob is not None:
         return BMinSep(inner, int(bands), int(n_steps), float(sampling_prob), bool(warm_start))
     return dataclasses.replace(inner, n_steps=int(n_steps), min_sep=int(bands), max_participations=max_participations)

@@ -123,6 +123,23 @@ class StepPerf:
     peak_memory_bytes: int = 0
     device_timed: bool = False
 
+    # the reference's field names, as read-only views
+    @property
+    def step_time_sec(self) -> float:
+        return self.seconds
+
+    @property
+    def samples_per_second(self) -> float:
+        return self.batch_size / self.seconds if self.seconds > 0 else 0.0
+
+    @property
+    def memory_peak_gb(self) -> float:
+        return self.peak_memory_bytes / 2 ** 30
+
+    @property
+    def marks(self) -> dict[str, float]:
+        return self.phases
+
 
 class _StepTimer:
     def __init__(self, device: Any, batch_size: int, track_memory: bool):
@@ -210,6 +227,27 @@ class PerfState:
     @property
     def seconds_per_step(self) -> float:
         return self.seconds / self.timed_steps if self.timed_steps else 0.0
+
+    # the reference's field names, as read-only views ("stable" = after the warm-up steps)
+    @property
+    def num_steps(self) -> int:
+        return self.steps
+
+    @property
+    def num_steps_stable(self) -> int:
+        return self.timed_steps
+
+    @property
+    def total_time_stable(self) -> float:
+        return self.seconds
+
+    @property
+    def total_samples_stable(self) -> int:
+        return self.samples
+
+    @property
+    def max_peak_memory_gb(self) -> float:
+        return self.peak_memory_bytes / 2 ** 30
 
 
 PerfStage = str

@@ -26,6 +26,44 @@ from .trainer import DPTrainer
 from .training_args import TrainingArguments
 
 
+# ---- conversion from TRL configuration objects ---------------------------------------------------------------------------
+# Parity: packages/opaque-transformers/src/opaque/api/transformers/trl/{_convert,_sft_convert,_dpo_convert}.py.
+
+_TRL_REFUSED = {
+    "packing": "sequence packing merges several records into one row: a row would no longer be one privacy unit",
+    "eval_packing": "sequence packing is not supported (see packing)",
+    "padding_free": "padding-free batches flatten the batch dimension that per-example clipping works on",
+    "shuffle_dataset": "batches are drawn by the DP sampler; an extra shuffle has no meaning and would suggest otherwise",
+    "use_liger_loss": "the fused head + cross-entropy kernel of this package is always used on the B200 engine",
+    "precompute_ref_log_probs": None,          # always done here; accepted
+}
+_TRL_DROPPED = {"dataset_kwargs": "preprocessing is done by the tokenizer and the collator",
+                "packing_strategy": "only meaningful with packing", "router_aux_loss_coef": "no auxiliary router loss is added",
+                "generate_during_eval": "no generation during evaluation", "padding_value": "the tokenizer's pad token is used",
+                "label_pad_token_id": "labels are padded with -100", "max_prompt_length": "prompts are kept whole; max_length truncates the pair",
+                "max_completion_length": "max_length truncates the pair", "tools": "chat templates are rendered without tool schemas"}
+
+
+def _from_trl(cls, trl_config: Any, overrides: dict) -> Any:
+    import warnings
+    from .hf_convert import _as_dict
+    raw = _as_dict(trl_config)
+    mode = raw.pop("truncation_mode", None)
+    if mode not in (None, "keep_start"):
+        raise ValueError(f"truncation_mode={mode!r} is not supported: sequences are truncated at the end (keep_start)")
+    if raw.pop("pad_token", None):
+        raise ValueError("pad_token is taken from the tokenizer (processing_class); set it there")
+    for name, why in _TRL_REFUSED.items():
+        value = raw.pop(name, None)
+        if value and why is not None:
+            raise ValueError(f"{name}={value!r} is not supported: {why}")
+    for name, why in _TRL_DROPPED.items():
+        value = raw.pop(name, None)
+        if value not in (None, False, {}, [], ""):
+            warnings.warn(f"{cls.__name__}.from_trl: {name}={value!r} is dropped ({why})", RuntimeWarning, stacklevel=3)
+    return cls.from_hf(raw, **overrides)
+
+
 @dataclasses.dataclass
 class SFTConfig(TrainingArguments):
     learning_rate: float = 2e-5
@@ -48,6 +86,13 @@ class SFTConfig(TrainingArguments):
         super().__post_init__()
         if self.loss_type not in ("nll", "dft", "chunked_nll"):
             raise ValueError("loss_type must be nll | dft | chunked_nll")
+
+    @classmethod
+    def from_trl(cls, trl_config: Any, **overrides: Any) -> "SFTConfig":
+        """Build from a ``trl.SFTConfig`` (object or mapping); ``overrides`` carry the DP settings.  Options that would break
+        the one-row-one-record contract (packing, padding-free batches, an extra shuffle) are refused by name, fields
+        without meaning here are dropped with a warning, the rest goes through :meth:`TrainingArguments.from_hf`."""
+        return _from_trl(cls, trl_config, overrides)
 
 
 class SFTTrainer(DPTrainer):
@@ -208,6 +253,11 @@ class DPOConfig(TrainingArguments):
                 raise ValueError(f"unknown DPO loss_type {t!r}")
         if self.loss_weights is not None and len(self.loss_weights) != len(types):
             raise ValueError("loss_weights must match loss_type")
+
+    @classmethod
+    def from_trl(cls, trl_config: Any, **overrides: Any) -> "DPOConfig":
+        """Build from a ``trl.DPOConfig`` (object or mapping); see :meth:`SFTConfig.from_trl`."""
+        return _from_trl(cls, trl_config, overrides)
 
 
 class DPOTrainer(DPTrainer):

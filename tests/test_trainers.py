@@ -508,3 +508,20 @@ def test_sft_config_fields_of_trl_act(tmp_path):
     assert 0.0 <= out["eval_mean_token_accuracy"] <= 1.0 and out["eval_entropy"] > 0 and out["eval_loss"] > 0
     cfg = DPOConfig(privacy_noise_multiplier=1.0, pad_to_multiple_of=8, dataset_num_proc=2, model_init_kwargs={"torch_dtype": "float32"})
     assert cfg.pad_to_multiple_of == 8 and cfg.trust_remote_code is False
+
+
+def test_trl_configs_convert_with_from_trl():
+    import warnings
+    from opaque_b200.transformers.trl import DPOConfig, SFTConfig
+    base = dict(output_dir="o", per_device_train_batch_size=4, gradient_accumulation_steps=8, learning_rate=3e-5, max_steps=10, max_grad_norm=0.7)
+    c = SFTConfig.from_trl({**base, "max_length": 256, "completion_only_loss": True, "dataset_text_field": "body", "loss_type": "dft"},
+                           privacy_noise_multiplier=1.0)
+    assert (c.per_device_train_batch_size, c.microbatch_size, c.clipping_norm, c.max_length, c.loss_type, c.dataset_text_field) == (32, 4, 0.7, 256, "dft", "body")
+    for bad in ({"packing": True}, {"padding_free": True}, {"shuffle_dataset": True}, {"truncation_mode": "keep_end"}, {"pad_token": "<pad>"}):
+        with pytest.raises(ValueError):
+            SFTConfig.from_trl({**base, **bad}, privacy_noise_multiplier=1.0)
+    with warnings.catch_warnings(record=True) as seen:
+        warnings.simplefilter("always")
+        d = DPOConfig.from_trl({**base, "beta": 0.3, "loss_type": ["sigmoid", "sft"], "loss_weights": [1.0, 0.1], "max_prompt_length": 64},
+                               privacy_noise_multiplier=1.0)
+    assert d.beta == 0.3 and d.loss_type == ["sigmoid", "sft"] and any("max_prompt_length" in str(w.message) for w in seen)

@@ -29,6 +29,10 @@ class DeviceCapabilities:
 
     # the reference's names for the same facts
     @property
+    def is_accelerator(self) -> bool:
+        return self.device_type != "cpu"
+
+    @property
     def supports_fused_kernels(self) -> bool:
         return self.fused_kernels
 

@@ -66,6 +66,11 @@ class CyclicPoissonSampler(_Resumable):
     def expected_batch_size(self) -> float:
         return self._num_samples / self.bands * self.sample_rate
 
+    @property
+    def batch_size_variance(self) -> float:
+        """Variance of one step's batch size: a Binomial over the records of the step's part (before any truncation)."""
+        return self._num_samples / self.bands * self.sample_rate * (1.0 - self.sample_rate)
+
 
 class BMinSepSampler(_Resumable):
     def __init__(self, data_source: Sized, bands: int, sampling_prob: float, n_steps: int | None, *, key: RngKey):
@@ -87,6 +92,22 @@ class BMinSepSampler(_Resumable):
         hit = free & (self.generator.random(self._num_samples) < self.sampling_prob)
         self._free_at[hit] = t + self.bands
         return np.flatnonzero(hit).tolist()
+
+    @property
+    def stationary_rate(self) -> float:
+        """Long-run fraction of steps in which a given record takes part: ``p / (1 + p·(bands − 1))``."""
+        return self.sampling_prob / (1.0 + self.sampling_prob * max(0, self.bands - 1))
+
+    @property
+    def expected_batch_size(self) -> float:
+        """Stationary expected batch size (the first ``bands`` steps, when every record is still free, are larger)."""
+        return self._num_samples * self.stationary_rate
+
+    @property
+    def batch_size_variance(self) -> float:
+        """Variance of the stationary batch size, treating records as independent: ``N·r·(1 − r)``."""
+        r = self.stationary_rate
+        return self._num_samples * r * (1.0 - r)
 
 
 class BallsInBinsSampler(_Resumable):
@@ -110,6 +131,16 @@ class BallsInBinsSampler(_Resumable):
     def expected_batch_size(self) -> float:
         return self._num_samples / self.num_bins
 
+    @property
+    def sample_rate(self) -> float:
+        """Per-step participation rate of a record: ``1 / num_bins``."""
+        return 1.0 / self.num_bins
+
+    @property
+    def num_epochs(self) -> float | None:
+        """Passes over the bins in ``n_steps`` steps (``None`` for an open-ended sampler)."""
+        return None if self.n_steps is None else self.n_steps / self.num_bins
+
 
 class SequentialBatchSampler(_Resumable):
     def __init__(self, data_source: Sized, batch_size: int, n_steps: int | None = None):
@@ -132,6 +163,10 @@ class SequentialBatchSampler(_Resumable):
     def _draw(self):
         b = self._consumed % self.batches_per_epoch
         return list(range(b * self.batch_size, (b + 1) * self.batch_size))
+
+    @property
+    def expected_batch_size(self) -> float:
+        return float(self.batch_size)
 
     @property
     def min_sep(self) -> int:

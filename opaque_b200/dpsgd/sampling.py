@@ -170,6 +170,11 @@ class RandomAllocationSampler(_Resumable):
         return np.flatnonzero(self._assign == b).tolist()
 
     @property
+    def num_epochs(self) -> float | None:
+        """Passes over the bins in ``n_steps`` steps (``None`` for an open-ended sampler)."""
+        return None if self.n_steps is None else self.n_steps / self.num_bins
+
+    @property
     def expected_batch_size(self) -> float:
         return self._num_samples / self.num_bins
 

@@ -140,6 +140,11 @@ class StepPerf:
     def marks(self) -> dict[str, float]:
         return self.phases
 
+    def to_dict(self) -> dict[str, Any]:
+        """JSON-ready: seconds, samples per second, peak memory in GB, and ``time/<phase>`` per mark."""
+        return {"step_time_sec": self.seconds, "samples_per_second": self.samples_per_second, "batch_size": self.batch_size,
+                "memory_peak_gb": self.memory_peak_gb, **{f"time/{k}": v for k, v in self.phases.items()}}
+
 
 class _StepTimer:
     def __init__(self, device: Any, batch_size: int, track_memory: bool):
@@ -248,6 +253,25 @@ class PerfState:
     @property
     def max_peak_memory_gb(self) -> float:
         return self.peak_memory_bytes / 2 ** 30
+
+    @property
+    def avg_step_time_stable(self) -> float:
+        return self.seconds_per_step
+
+    avg_step_time = avg_step_time_stable                 # warm-up steps are not timed into the totals here
+
+    @property
+    def avg_samples_per_second_stable(self) -> float:
+        return self.samples_per_second
+
+    avg_samples_per_second = avg_samples_per_second_stable
+
+    def to_dict(self) -> dict[str, Any]:
+        """JSON-ready summary of the stage (rates over the steps after warm-up)."""
+        return {"num_steps": self.steps, "num_steps_stable": self.timed_steps, "total_time_stable": self.seconds,
+                "total_samples_stable": self.samples, "avg_step_time_stable": self.seconds_per_step,
+                "avg_samples_per_second_stable": self.samples_per_second, "max_peak_memory_gb": self.max_peak_memory_gb,
+                **{f"time/{k}": v / max(self.timed_steps, 1) for k, v in self.phases.items()}}
 
 
 PerfStage = str

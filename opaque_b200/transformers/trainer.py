@@ -504,6 +504,105 @@ class DPTrainer:
         from . import hub
         return hub.push_to_hub(self, commit_message, blocking, token, revision, **kwargs)
 
+    # ---- Hugging Face Trainer conveniences -----------------------------------------------------------------------
+    @property
+    def callback_handler(self) -> "DPTrainer":
+        """The object that owns ``callbacks`` / ``add_callback`` / ``pop_callback`` / ``remove_callback`` (this trainer)."""
+        return self
+
+    def init_hf_repo(self, token: str | None = None) -> str:
+        """Create the Hub repository named by ``hub_model_id`` (or ``output_dir``) if needed; returns its id."""
+        from . import hub
+        return hub.init_hub_repo(self, token=token)
+
+    def create_scheduler(self, num_training_steps: int | None = None, optimizer: Any = None):
+        """The learning-rate schedule of this run (a ``scheduling`` recipe, ``schedule(step) -> lr``)."""
+        steps = int(num_training_steps or self.state.max_steps or self.args.max_steps or 1)
+        self.lr_schedule = build_lr_schedule(self.args, steps)
+        return self.lr_schedule
+
+    def create_optimizer(self):
+        """The functional optimizer chain for ``args.optim`` (what the reference engine steps with)."""
+        schedule = getattr(self, "lr_schedule", None) or self.create_scheduler()
+        return build_optimizer(self.args, schedule)
+
+    def get_eval_dataloader(self, eval_dataset: Any = None):
+        """Collated evaluation batches of THIS rank's shard, ``eval_batch_size`` rows each (an iterable with ``len``)."""
+        data = eval_dataset if eval_dataset is not None else self.eval_dataset
+        if data is None:
+            raise ValueError("evaluation needs an eval_dataset")
+        shard = local_shard(data, rank=self.args.process_index, world_size=self.args.world_size)
+        bs, collate = self.args.eval_batch_size, self.data_collator
+
+        class _Batches:
+            def __len__(_):
+                return (len(shard) + bs - 1) // bs
+
+            def __iter__(_):
+                for lo in range(0, len(shard), bs):
+                    yield collate([shard[i] for i in range(lo, min(len(shard), lo + bs))])
+        return _Batches()
+
+    @torch.no_grad()
+    def prediction_step(self, model: Any, inputs: Mapping[str, torch.Tensor], prediction_loss_only: bool,
+                        ignore_keys: Any = None) -> tuple[torch.Tensor | None, Any, Any]:
+        """``(mean loss, logits, labels)`` of one collated batch (logits and labels ``None`` with ``prediction_loss_only``)."""
+        batch = self._to_device(inputs)
+        loss = self.compute_batch_per_example_loss(batch).float().mean() if "labels" in batch else None
+        if prediction_loss_only or "input_ids" not in batch:
+            return loss, None, None
+        logits = model(batch["input_ids"])
+        return loss, getattr(logits, "logits", logits), batch.get("labels")
+
+    def compute_per_example_loss_and_metrics(self, model_call: Callable[..., Any], example: Mapping[str, torch.Tensor]):
+        """``(loss, metrics)`` of ONE record; the default has no extra metrics.  Override together with
+        :meth:`compute_per_example_loss` when a task wants to log per-record quantities of NON-private evaluation data."""
+        return self.compute_per_example_loss(model_call, example), {}
+
+    def log_metrics(self, split: str, metrics: Mapping[str, Any]) -> None:
+        """Print a metrics block the way the Hugging Face trainer does (rank 0 only)."""
+        if not self.is_world_process_zero():
+            return
+        rows = {k: (f"{v:.4f}" if isinstance(v, float) else str(v)) for k, v in sorted(metrics.items())}
+        width = max((len(k) for k in rows), default=0)
+        print(f"***** {split} metrics *****")
+        for k, v in rows.items():
+            print(f"  {k:<{width}} = {v:>10}")
+
+    def save_metrics(self, split: str, metrics: Mapping[str, Any], combined: bool = True) -> None:
+        """Write ``{split}_results.json`` into ``output_dir`` and (``combined``) merge into ``all_results.json``."""
+        if not self.is_world_process_zero() or not self.args.output_dir:
+            return
+        os.makedirs(self.args.output_dir, exist_ok=True)
+        plain = to_python(dict(metrics))
+        with open(os.path.join(self.args.output_dir, f"{split}_results.json"), "w") as f:
+            json.dump(plain, f, indent=4, sort_keys=True)
+        if combined:
+            path = os.path.join(self.args.output_dir, "all_results.json")
+            merged = json.load(open(path)) if os.path.exists(path) else {}
+            merged.update(plain)
+            with open(path, "w") as f:
+                json.dump(merged, f, indent=4, sort_keys=True)
+
+    def save_state(self) -> None:
+        """Write ``trainer_state.json`` (step, log history, best metric) into ``output_dir``."""
+        if not self.is_world_process_zero() or not self.args.output_dir:
+            return
+        os.makedirs(self.args.output_dir, exist_ok=True)
+        with open(os.path.join(self.args.output_dir, FILES["trainer_state"]), "w") as f:
+            f.write(self.state.to_json())
+
+    def save_accountant(self, output_dir: str | None = None) -> str | None:
+        """Write the accountant (process tree + budget) as ``accountant.json``; returns the path (rank 0), else ``None``."""
+        out = output_dir or self.args.output_dir
+        if not self.is_world_process_zero() or not out or getattr(self, "accountant", None) is None:
+            return None
+        os.makedirs(out, exist_ok=True)
+        path = os.path.join(out, FILES["accountant"])
+        with open(path, "w") as f:
+            f.write(self.accountant.to_json())
+        return path
+
     def _call(self, hook: str, **kw: Any) -> None:
         for cb in self.callbacks:
             getattr(cb, hook)(self.args, self.state, self.control, model=self.model, **kw)

@@ -261,6 +261,43 @@ class TrainingArguments:
     def to_dict(self) -> dict[str, Any]:
         return {f.name: getattr(self, f.name) for f in dataclasses.fields(self) if not f.name.startswith("_")}
 
+    # ---- read-only names that Hugging Face callbacks and integrations look up on an arguments object ----------------
+    @property
+    def parallel_mode(self) -> str:
+        """``"distributed"`` with several processes, else ``"not_distributed"`` (values of Hugging Face's ``ParallelMode``)."""
+        return "distributed" if self.world_size > 1 else "not_distributed"
+
+    @property
+    def gradient_accumulation_steps(self) -> int:
+        """Always 1: one optimizer step per sampled batch (``microbatch_size`` only splits its evaluation)."""
+        return 1
+
+    @property
+    def lr_scheduler_type(self) -> str:
+        return self.lr_scheduler
+
+    @property
+    def fp16(self) -> bool:
+        """The trainers compute in bf16 or fp32; fp16 with a loss scaler is a functional-API feature."""
+        return False
+
+    @property
+    def warmup_ratio(self) -> float:
+        """The fractional form of ``warmup_steps`` (a value below 1 IS the fraction), else 0."""
+        return float(self.warmup_steps) if 0 < self.warmup_steps < 1 else 0.0
+
+    @property
+    def device(self) -> "Any":
+        import torch
+        if self.use_cpu or not torch.cuda.is_available():
+            return torch.device("cpu")
+        return torch.device("cuda", self.local_process_index)
+
+    @property
+    def n_gpu(self) -> int:
+        """GPUs driven by THIS process: one (a process per GPU) or none."""
+        return 0 if self.device.type == "cpu" else 1
+
     @classmethod
     def from_hf(cls, hf_args: Any, **overrides: Any) -> "TrainingArguments":
         """Build from a Hugging Face ``TrainingArguments`` (object or mapping); ``overrides`` carry the DP settings.

@@ -489,6 +489,21 @@ class DPOTrainer(DPTrainer):
                                    pair_weight=weight.squeeze(0) if weight is not None else None,
                                    chosen_logp=c_sum, rejected_logp=r_sum, cpo_alpha=a.cpo_alpha)
 
+    def compute_ref_log_probs(self, dataset: Any = None, split: str = "train") -> Any:
+        """The dataset with ``ref_chosen_logps`` / ``ref_rejected_logps`` on every pair (rank-sharded, gathered, cached);
+        rows that already carry them come back unchanged.  Called by the constructor for the training and evaluation sets."""
+        return self._precompute_ref_logps(dataset if dataset is not None else self.train_dataset, split)
+
+    def dpo_loss(self, chosen_logratio: torch.Tensor, rejected_logratio: torch.Tensor, **terms: Any) -> torch.Tensor:
+        """The configured preference loss for given log-ratios, one value per pair (``loss_type``, ``beta``, label smoothing,
+        mixture weights and the head-specific tunables come from the ``DPOConfig``; ``terms`` supplies what reference-free
+        heads need: ``chosen_nll``, ``chosen_avg_logp``, ``rejected_avg_logp``, ``chosen_logp``, ``rejected_logp``)."""
+        a = self._dpo
+        return dpo_losses.dpo_loss(a.loss_type, chosen_logratio=chosen_logratio, rejected_logratio=rejected_logratio, beta=a.beta,
+                                   label_smoothing=a.label_smoothing, loss_weights=a.loss_weights, bco_delta=self._bco_delta,
+                                   discopop_tau=a.discopop_tau, simpo_gamma=a.simpo_gamma, orpo_lambda=a.orpo_lambda,
+                                   f_divergence_type=a.f_divergence_type, f_alpha=a.f_alpha_divergence_coef, cpo_alpha=a.cpo_alpha, **terms)
+
     def compute_batch_per_example_loss(self, batch):
         n = batch["chosen_input_ids"].shape[0]
         rows = [self.compute_per_example_loss(self.model, {k: v[i] for k, v in batch.items() if isinstance(v, torch.Tensor)}) for i in range(n)]

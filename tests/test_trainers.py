@@ -525,3 +525,30 @@ def test_trl_configs_convert_with_from_trl():
         d = DPOConfig.from_trl({**base, "beta": 0.3, "loss_type": ["sigmoid", "sft"], "loss_weights": [1.0, 0.1], "max_prompt_length": 64},
                                privacy_noise_multiplier=1.0)
     assert d.beta == 0.3 and d.loss_type == ["sigmoid", "sft"] and any("max_prompt_length" in str(w.message) for w in seen)
+
+
+def test_trainer_conveniences_of_the_hugging_face_surface(tmp_path, capsys):
+    torch.manual_seed(0)
+    held_out = _data(10, seed=4)
+    tr = DPTrainer(model=TinyLM(), args=_args(tmp_path, max_steps=2, save_steps=0, per_device_eval_batch_size=4), train_dataset=_data(),
+                   eval_dataset=held_out)
+    out = tr.train()
+    assert out.global_step == 2 and out.training_loss > 0 and out.metrics["global_step"] == 2 and out["epsilon"] > 0
+    loader = tr.get_eval_dataloader()
+    batches = list(loader)
+    assert len(loader) == len(batches) == 3 and batches[0]["input_ids"].shape[0] == 4 and batches[-1]["input_ids"].shape[0] == 2
+    loss, logits, labels = tr.prediction_step(tr.model, batches[0], prediction_loss_only=False)
+    assert loss > 0 and logits.shape[:2] == labels.shape and tr.prediction_step(tr.model, batches[0], True)[1] is None
+    metrics = tr.evaluate()
+    tr.log_metrics("eval", metrics)
+    assert "***** eval metrics *****" in capsys.readouterr().out
+    tr.save_metrics("eval", metrics)
+    tr.save_metrics("train", dict(out))
+    tr.save_state()
+    path = tr.save_accountant()
+    merged = json.load(open(tmp_path / "all_results.json"))
+    assert "eval_loss" in merged and "train_runtime" in merged and os.path.exists(tmp_path / "eval_results.json")
+    assert json.load(open(tmp_path / "trainer_state.json"))["global_step"] == 2 and os.path.exists(path)
+    assert tr.callback_handler.callbacks is tr.callbacks and callable(tr.create_scheduler(10)) and tr.create_optimizer() is not None
+    loss1, extra = tr.compute_per_example_loss_and_metrics(tr.model, {"input_ids": batches[0]["input_ids"][0], "labels": batches[0]["labels"][0]})
+    assert extra == {} and loss1 > 0

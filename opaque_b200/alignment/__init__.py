@@ -11,7 +11,7 @@ _LOSS = ("sigmoid_loss hinge_loss robust_loss ipo_loss discopop_loss chosen_nll_
          "bco_loss sppo_loss simpo_loss odds_ratio_loss f_divergence_remap f_divergence_logits mpo_combine wpo_weights ld_dpo_split "
          "orpo_loss dpo_loss wpo_weight ld_dpo_logp").split()
 _sub(dpo.__name__, "loss", "Preference loss heads and their building blocks.",
-     {**{n: getattr(dpo, n) for n in _LOSS}, "sequence_logp": sft.sequence_logp, "fused_sequence_logp": sft.fused_sequence_logp})
+     {**{n: getattr(dpo, n) for n in _LOSS}, "sequence_logp": dpo.completion_logp, "fused_sequence_logp": dpo.fused_completion_logp})
 _sub(dpo.__name__, "collator", "Preference-pair collation.", {"preference_collator": data.preference_collator})
 _sub(dpo.__name__, "data", "Preference dataset helpers.", {"extract_prompt": dpo.extract_prompt})
 _sub(dpo.__name__, "metric", "Reward telemetry.", {"reward_metrics": dpo.reward_metrics, "reward_margins": dpo.reward_margins})

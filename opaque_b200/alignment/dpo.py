@@ -314,4 +314,38 @@ def extract_prompt(example: Mapping[str, Any]) -> dict:
     return row
 
 
-__all__ += ["extract_prompt", "f_divergence_remap", "ld_dpo_split", "mpo_combine", "odds_ratio_loss", "reward_metrics", "wpo_weights"]
+def completion_logp(logits: torch.Tensor, input_ids: torch.Tensor, completion_mask: torch.Tensor, *, ld_alpha: float | None = None,
+                    shared_prefix_len=None, length_normalized: bool = False) -> torch.Tensor:
+    """Per-sequence log-probability of the COMPLETION tokens from UNSHIFTED tensors: ``logits (..., T, V)``, ``input_ids`` and
+    ``completion_mask`` ``(..., T)``; position ``t`` scores token ``t + 1`` (the shift happens here).  ``ld_alpha`` with
+    ``shared_prefix_len`` applies the LD-DPO weighting (:func:`ld_dpo_split`); ``length_normalized`` divides by the number
+    of completion tokens.  This is ``sequence_logp`` of the reference's ``alignment.dpo.loss`` namespace; the
+    ``(logits, labels)`` form with pre-aligned labels is ``alignment.sft.sequence_logp``.
+
+    Parity: packages/opaque-alignment/src/opaque/api/alignment/logprob/_sequence.py:31."""
+    if ld_alpha is not None and shared_prefix_len is None:
+        raise ValueError("ld_alpha needs shared_prefix_len")
+    z = logits[..., :-1, :].float()
+    target, mask = input_ids[..., 1:], completion_mask[..., 1:]
+    lp = torch.gather(z.log_softmax(-1), -1, target.unsqueeze(-1).long()).squeeze(-1)
+    if ld_alpha is not None:
+        total = ld_dpo_split(lp, mask, shared_prefix_len, ld_alpha)
+    else:
+        total = (lp * mask.to(lp.dtype)).sum(-1)
+    if length_normalized:
+        total = total / (mask != 0).sum(-1).clamp(min=1)
+    return total
+
+
+def fused_completion_logp(hidden_states: torch.Tensor, lm_head_weight: torch.Tensor, input_ids: torch.Tensor,
+                          completion_mask: torch.Tensor, *, length_normalized: bool = False) -> torch.Tensor:
+    """:func:`completion_logp` from final hidden states ``[B, T, d]`` and the output head, without keeping logits (the fused
+    head + cross-entropy node); no LD-DPO weighting here — that needs per-token values."""
+    from .sft import IGNORE_INDEX, fused_sequence_logp
+    labels = torch.full_like(input_ids, IGNORE_INDEX)
+    keep = completion_mask[..., 1:] != 0
+    labels[..., :-1] = torch.where(keep, input_ids[..., 1:], torch.full_like(input_ids[..., 1:], IGNORE_INDEX))
+    return fused_sequence_logp(hidden_states, lm_head_weight, labels, average=length_normalized)
+
+
+__all__ += ["completion_logp", "fused_completion_logp", "extract_prompt", "f_divergence_remap", "ld_dpo_split", "mpo_combine", "odds_ratio_loss", "reward_metrics", "wpo_weights"]

@@ -237,3 +237,23 @@ def test_auditing_dataset_forms_join_scores_by_identifier():
         auditing.canary_scores([1.0, 2.0], canary_indices=[3, 3])
     with pytest.raises(ValueError):
         auditing.one_run(auditing.canary_scores(cur.scores, canary_indices=np.arange(20) + 1000), coin_flip=flips)
+
+
+def test_completion_logp_shifts_and_matches_the_aligned_form():
+    from opaque_b200.alignment.dpo.loss import fused_sequence_logp, sequence_logp
+    torch.manual_seed(4)
+    B, T, d, V = 2, 7, 8, 19
+    hidden, head = torch.randn(B, T, d), torch.randn(V, d) * 0.4
+    logits = hidden @ head.t()
+    ids = torch.randint(0, V, (B, T))
+    mask = torch.tensor([[0, 0, 1, 1, 1, 0, 0], [0, 1, 1, 1, 1, 1, 1]])
+    labels = torch.full_like(ids, -100)
+    labels[:, :-1] = torch.where(mask[:, 1:] != 0, ids[:, 1:], torch.full_like(ids[:, 1:], -100))
+    want = sft.sequence_logp(logits, labels)
+    assert torch.allclose(sequence_logp(logits, ids, mask), want, atol=1e-5)
+    assert torch.allclose(sequence_logp(logits, ids, mask, length_normalized=True), sft.sequence_logp(logits, labels, average=True), atol=1e-5)
+    assert torch.allclose(fused_sequence_logp(hidden, head, ids, mask), want, atol=1e-4)
+    lp = torch.gather(logits[:, :-1].log_softmax(-1), -1, ids[:, 1:, None]).squeeze(-1)
+    assert torch.allclose(sequence_logp(logits, ids, mask, ld_alpha=0.5, shared_prefix_len=2), dpo.ld_dpo_split(lp, mask[:, 1:], 2, 0.5), atol=1e-5)
+    with pytest.raises(ValueError):
+        sequence_logp(logits, ids, mask, ld_alpha=0.5)

@@ -52,7 +52,7 @@ def nca_loss(chosen_logratio, rejected_logratio, *, beta: float):
     return -F.logsigmoid(beta * c) - 0.5 * F.logsigmoid(-beta * c) - 0.5 * F.logsigmoid(-beta * r)
 
 
-def robust_loss(chosen_logratio, rejected_logratio, *, beta: float, label_smoothing: float = 0.1):
+def robust_loss(chosen_logratio, rejected_logratio, *, beta: float, label_smoothing: float = 0.0):
     """Robust DPO (Chowdhury et al. 2024): unbiased under label-flip probability ε."""
     c, r = chosen_logratio, rejected_logratio
     if not 0 <= label_smoothing < 0.5:
@@ -94,12 +94,15 @@ def discopop_loss(chosen_logratio, rejected_logratio, *, beta: float, discopop_t
     return -F.logsigmoid(d) * (1 - mod) + torch.exp((-d).clamp(max=cap)) * mod
 
 
-def chosen_nll_loss(chosen_nll):
-    """SFT term on the chosen response (already a per-example mean NLL)."""
-    return chosen_nll
+def chosen_nll_loss(chosen_logp, /, *_args, **_kwargs):
+    """SFT regulariser on the chosen response: ``−chosen_logp`` (the argument is the policy's log-probability of the chosen
+    completion, not a log-ratio; further arguments are ignored so that it can sit in a mixture next to the pair heads).
+
+    Parity: packages/opaque-alignment/src/opaque/api/alignment/dpo/loss/_chosen_nll.py:34."""
+    return -chosen_logp
 
 
-def simpo_loss(chosen_logratio, rejected_logratio, *, beta: float, gamma: float = 0.5, label_smoothing: float = 0.0):
+def simpo_loss(chosen_logratio, rejected_logratio, *, beta: float, gamma: float = 0.0, label_smoothing: float = 0.0):
     """SimPO (Meng et al. 2024): reference-free, with target margin ``γ/β``; the two arguments are the LENGTH-NORMALISED
     policy log-probabilities (the "log-ratios" of a reference-free head)."""
     d = beta * (chosen_logratio - rejected_logratio - gamma / beta)
@@ -133,16 +136,14 @@ def wpo_weight(chosen_token_logps, chosen_mask, rejected_token_logps, rejected_m
 
 
 def f_divergence_logits(chosen_logratio, rejected_logratio, *, f_divergence_type: str = "reverse_kl", alpha: float = 0.5):
-    """Remap ``Δ`` for f-DPO (Wang et al. 2023): reverse KL (identity), JS or α-divergence."""
-    c, r, kind = chosen_logratio, rejected_logratio, f_divergence_type
-    if kind == "reverse_kl":
+    """Pair logit for f-DPO (Wang et al. 2023): ``g(chosen) − g(rejected)`` with the per-side remap ``g`` of
+    :func:`f_divergence_remap` (reverse KL: the plain difference).  ``alpha`` follows the reference's convention,
+    ``g(x) = (e^{(α−1)x} − 1)/(α − 1)`` — TRL's coefficient is ``1 − α`` of this one; both agree at 0.5."""
+    c, r = chosen_logratio, rejected_logratio
+    if f_divergence_type == "reverse_kl":
         return c - r
-    if kind == "js_divergence":
-        return (c - r) - (F.softplus(c) - F.softplus(r))
-    if kind == "alpha_divergence":
-        cap = 80.0
-        return (torch.exp((-alpha * r).clamp(max=cap)) - torch.exp((-alpha * c).clamp(max=cap))) / alpha
-    raise ValueError(f"unknown f-divergence {kind!r}")
+    return (f_divergence_remap(c, f_divergence_type=f_divergence_type, alpha=alpha)
+            - f_divergence_remap(r, f_divergence_type=f_divergence_type, alpha=alpha))
 
 
 PAIR_HEADS = {"sigmoid": sigmoid_loss, "hinge": hinge_loss, "ipo": ipo_loss, "exo_pair": exo_loss, "nca_pair": nca_loss,
@@ -186,12 +187,12 @@ def dpo_loss(loss_type: str | Sequence[str], *, chosen_logratio, rejected_lograt
         elif t in PAIR_HEADS:
             term = PAIR_HEADS[t](c, r, beta=beta)
         elif t in ("sft", "chosen_nll"):
-            term = chosen_nll_loss(chosen_nll)
+            term = chosen_nll                      # already the per-example mean NLL of the chosen response
         elif t == "cpo":
             if chosen_logp is None or rejected_logp is None:
                 raise ValueError("cpo needs the policy log-probabilities chosen_logp / rejected_logp")
             term = sigmoid_loss(chosen_logp, rejected_logp, beta=beta, label_smoothing=label_smoothing) \
-                + cpo_alpha * chosen_nll_loss(chosen_nll)
+                + cpo_alpha * chosen_nll
         elif t == "simpo":
             term = simpo_loss(chosen_avg_logp, rejected_avg_logp, beta=beta, gamma=simpo_gamma, label_smoothing=label_smoothing)
         elif t == "orpo":

@@ -1,0 +1,124 @@
+"""Worker of ``tests/test_reference_parity.py``: imports the unmodified reference (``baseline/_ref``, with the two stand-in
+modules of ``baseline/shims``) next to this package on the CPU and prints, as one JSON object, the largest differences
+between the two on pure-Python building blocks.  Run in its own process so that the reference's imports stay out of the
+test session."""
+import importlib
+import inspect
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path[:0] = [os.path.join(ROOT, "baseline", "shims"), os.path.join(ROOT, "baseline", "_ref"), ROOT]
+
+
+def both(name):
+    return importlib.import_module("opaque." + name), importlib.import_module("opaque_b200." + name)
+
+
+def flat(t):
+    tree = getattr(t, "pytree", None)
+    tree = t if tree is None else tree
+    leaves = [tree[k] for k in sorted(tree)] if isinstance(tree, dict) else list(tree)
+    return torch.cat([x.reshape(-1) for x in leaves])
+
+
+def main():
+    out = {}
+    rr, ro = both("random")
+    k1, k2 = rr.key(42), ro.key(42)
+    out["rng_equal"] = bool(k1.seed == k2.seed and rr.fold_in(k1, 3).seed == ro.fold_in(k2, 3).seed
+                            and rr.fold_in(k1, "noise").seed == ro.fold_in(k2, "noise").seed
+                            and [a.seed for a in rr.split(k1, 3)] == [a.seed for a in ro.split(k2, 3)])
+    sr, so = both("scheduling")
+    worst = 0.0
+    for name, args in (("cosine_schedule", (1.0, 0.1, 100)), ("linear_schedule", (1.0, 0.0, 50)), ("polynomial_schedule", (1.0, 0.1, 2.0, 40)),
+                       ("exponential_schedule", (1.0, 10, 0.5)), ("inverse_sqrt_schedule", (1.0, 10)), ("one_minus_sqrt_schedule", (1.0, 0.0, 30))):
+        a, b = getattr(sr, name)(*args), getattr(so, name)(*args)
+        worst = max(worst, max(abs(float(a(t)) - float(b(t))) for t in (0, 1, 7, 25, 60, 200)))
+    a, b = sr.with_warmup(sr.cosine_schedule(1.0, 0.1, 90), 10), so.with_warmup(so.cosine_schedule(1.0, 0.1, 90), 10)
+    worst = max(worst, max(abs(float(a(t)) - float(b(t))) for t in range(0, 120, 7)))
+    kw = dict(num_warmup_steps=5, num_stable_steps=20, num_decay_steps=10)
+    a, b = sr.warmup_stable_decay(1.0, 0.0, **kw), so.warmup_stable_decay(1.0, 0.0, **kw)
+    out["schedules"] = max(worst, max(abs(float(a(t)) - float(b(t))) for t in range(0, 40)))
+
+    dr, do = both("dpsgd")
+    fr, fo = both("functional")
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Tanh(), torch.nn.Linear(5, 3))
+    X, Y = torch.randn(12, 6), torch.randint(0, 3, (12,))
+
+    def run(D, Fm, R):
+        fmodel, params = Fm.make_functional(model, disable_autograd_tracking=True)
+        loss = lambda p, x, y: torch.nn.functional.cross_entropy(fmodel(p, x[None]), y[None])
+        gf, cs = D.clipped_grad(loss, clipping_norm=0.7, normalize_by=12.0, batch_argnums=(1, 2), return_aux=True, microbatch_size=5)
+        (g, aux), cs = gf(params, X, Y, state=cs)
+        nf, ns = D.gaussian_noise(noise_multiplier=1.3, key=R.key(9))
+        noisy, ns = nf(g, ns)
+        return g, noisy, aux
+    g1, n1, a1 = run(dr, fr, rr)
+    g2, n2, a2 = run(do, fo, ro)
+    out["clipped_grad"] = float((flat(g1) - flat(g2)).abs().max())
+    out["grad_norms"] = float((a1.grad_norms - a2.grad_norms).abs().max())
+    out["noise_realisation"] = float((flat(n1) - flat(n2)).abs().max())
+    out["noise_std"] = float((flat(n2) - flat(g2)).std())
+
+    fr_, fo_ = both("dpftrl")
+    same = lambda a, b: [list(x) for x in a] == [list(x) for x in b]
+    out["poisson_draws_equal"] = same(dr.PoissonSampler(range(200), 0.1, n_steps=6, key=rr.key(5)), do.PoissonSampler(range(200), 0.1, n_steps=6, key=ro.key(5)))
+    out["random_allocation_draws_equal"] = same(dr.sampling.RandomAllocationSampler(range(50), num_bins=5, n_steps=10, key=rr.key(1)),
+                                                 do.RandomAllocationSampler(range(50), 5, 10, key=ro.key(1)))
+    out["balls_in_bins_draws_equal"] = same(fr_.BallsInBinsSampler(range(60), num_bins=5, n_steps=10, key=rr.key(2)),
+                                             fo_.BallsInBinsSampler(range(60), num_bins=5, n_steps=10, key=ro.key(2)))
+
+    orr, oo = both("optimizers")
+    tr, to = both("types")
+    torch.manual_seed(1)
+    p = {"w": torch.randn(7), "b": torch.randn(3)}
+
+    def steps(O, T):
+        opt = O.adamw(1e-2, weight_decay=0.1, noise_bias_correction=True)
+        st, q = opt.init(p), {k: v.clone() for k, v in p.items()}
+        g = torch.Generator().manual_seed(3)
+        for _ in range(4):
+            grads = {k: torch.randn(v.shape, generator=g) for k, v in q.items()}
+            u, st = opt.update(T.noised(grads, max_norm=1.0, noise_stddev=0.3), st, params=q)
+            q = {k: q[k] + u[k] for k in q}            # the update is additive in both libraries
+        return q
+    q1, q2 = steps(orr, tr), steps(oo, to)
+    out["adamw_bc"] = max(float((q1[k] - q2[k]).abs().max()) for k in q1)
+
+    ref, ours = importlib.import_module("opaque.alignment.dpo.loss"), importlib.import_module("opaque_b200.alignment.dpo.loss")
+    torch.manual_seed(0)
+    c, r = torch.randn(9), torch.randn(9)
+    lc, lr_ = -torch.rand(9) * 2 - 0.1, -torch.rand(9) * 2 - 0.1
+    worst = 0.0
+    for name in ("sigmoid_loss", "hinge_loss", "robust_loss", "ipo_loss", "discopop_loss", "apo_zero_loss", "apo_down_loss", "exo_loss",
+                 "nca_loss", "bco_loss", "sppo_loss", "simpo_loss"):
+        worst = max(worst, float((getattr(ref, name)(c, r, beta=0.3) - getattr(ours, name)(c, r, beta=0.3)).abs().max()))
+    worst = max(worst, float((ref.odds_ratio_loss(lc, lr_) - ours.odds_ratio_loss(lc, lr_)).abs().max()),
+                float((ref.chosen_nll_loss(lc) - ours.chosen_nll_loss(lc)).abs().max()))
+    for kind in ("reverse_kl", "forward_kl", "js_divergence", "alpha_divergence"):
+        for alpha in (0.3, 0.5):
+            worst = max(worst, float((ref.f_divergence_logits(c, r, f_divergence_type=kind, alpha=alpha)
+                                      - ours.f_divergence_logits(c, r, f_divergence_type=kind, alpha=alpha)).abs().max()),
+                        float((ref.f_divergence_remap(c, f_divergence_type=kind, alpha=alpha)
+                               - ours.f_divergence_remap(c, f_divergence_type=kind, alpha=alpha)).abs().max()))
+    lp = -torch.rand(3, 6)
+    m = torch.tensor([[0, 1, 1, 1, 0, 0], [1, 1, 1, 1, 1, 1], [0, 0, 0, 0, 0, 0]])
+    logits, ids = torch.randn(2, 6, 11), torch.randint(0, 11, (2, 6))
+    worst = max(worst, float((ref.wpo_weights(lp, m) - ours.wpo_weights(lp, m)).abs().max()),
+                float((ref.ld_dpo_split(lp, m, 2, 0.3) - ours.ld_dpo_split(lp, m, 2, 0.3)).abs().max()),
+                float((ref.sequence_logp(logits, ids, m[:2]) - ours.sequence_logp(logits, ids, m[:2])).abs().max()),
+                float((ref.sequence_logp(logits, ids, m[:2], ld_alpha=0.4, shared_prefix_len=2)
+                       - ours.sequence_logp(logits, ids, m[:2], ld_alpha=0.4, shared_prefix_len=2)).abs().max()),
+                float((ref.mpo_combine({"a": c, "b": r}, {"a": 0.3, "b": 2.0}) - ours.mpo_combine({"a": c, "b": r}, {"a": 0.3, "b": 2.0})).abs().max()))
+    out["preference_losses"] = worst
+    out["signature_checked"] = len(inspect.signature(ref.sigmoid_loss).parameters)
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,25 @@
+"""Numerical parity with the UNMODIFIED reference on the CPU, when it is installed (``baseline/install_reference.sh`` puts it
+into ``baseline/_ref``): same key derivation, schedules, clipped gradients, even the same noise realisation and the same
+Poisson / random-allocation / balls-in-bins draws; optimizer steps and every preference-loss piece to rounding."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref", "opaque")
+
+
+@pytest.mark.skipif(not os.path.isdir(REF), reason="the reference is not installed under baseline/_ref")
+def test_building_blocks_equal_the_reference():
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    run = subprocess.run([sys.executable, "-W", "ignore", os.path.join(ROOT, "tests", "reference_parity_worker.py")], capture_output=True,
+                         text=True, timeout=600, env=env)
+    assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-3000:]
+    d = json.loads([line for line in run.stdout.splitlines() if line.startswith("{")][-1])
+    assert d["rng_equal"] and d["poisson_draws_equal"] and d["random_allocation_draws_equal"] and d["balls_in_bins_draws_equal"], d
+    assert d["schedules"] < 1e-9 and d["clipped_grad"] < 1e-6 and d["grad_norms"] < 1e-6, d
+    assert d["noise_realisation"] < 1e-6 and d["noise_std"] > 0.01, d          # the SAME noise, and it is noise
+    assert d["adamw_bc"] < 1e-6 and d["preference_losses"] < 1e-5, d

@@ -306,7 +306,10 @@ class AdafactorState:
 def adafactor(lr: LR = 1e-3, beta1: float = 0.0, decay_rate: float = -0.8, eps_grad: float = 1e-30,
               eps_root: float = 1e-3, weight_decay: float = 0.0, update_rms_clip: float = 1.0, *,
               decoupled_weight_decay: bool = True, noise_bias_correction: bool = False):
-    """Adafactor: matrices keep row / column second-moment factors; per-leaf update clipping by RMS."""
+    """Adafactor: matrices keep row / column second-moment factors (``β₂_t = 1 − t^decay_rate``), floors are relative to each
+    tensor's own scale (``eps_root``), and the whole update is clipped to a global RMS of ``update_rms_clip``.
+
+    Parity: packages/opaque-optimizers/src/opaque/api/optimizers/_adafactor.py:150-290."""
     def factored(p):
         return isinstance(p, torch.Tensor) and p.ndim >= 2
 
@@ -326,6 +329,9 @@ def adafactor(lr: LR = 1e-3, beta1: float = 0.0, decay_rate: float = -0.8, eps_g
         from ..pytree import tree_flatten_with_paths, tree_unflatten
         paths, gl, td = tree_flatten_with_paths(grads)
         rows, cols, fulls = tree_leaves(state.v_row), tree_leaves(state.v_col), tree_leaves(state.v_full)
+
+        def floor_scaled(v):         # sqrt(v) with a floor RELATIVE to the tensor's own scale: eps_root · sqrt(mean v)
+            return v.sqrt().clamp(min=eps_root * v.mean().clamp(min=1e-30).sqrt())
         for path, g, r, c, f in zip(paths, gl, rows, cols, fulls):
             g = _up(g)
             sq = g * g + eps_grad
@@ -333,16 +339,21 @@ def adafactor(lr: LR = 1e-3, beta1: float = 0.0, decay_rate: float = -0.8, eps_g
             if factored(g):
                 r = beta2 * r + (1 - beta2) * sq.mean(dim=-1)
                 c = beta2 * c + (1 - beta2) * sq.mean(dim=-2)
-                v_hat = (r.unsqueeze(-1) * c.unsqueeze(-2)) / r.mean(dim=-1, keepdim=True).unsqueeze(-1).clamp(min=eps_grad)
+                # the noise floor is removed from each factor (both estimate E[g²] along their axis), then
+                # v̂ ≈ row ⊗ col / mean(row), the mean floored relative to the factor's scale
+                r_eff, c_eff = debias_second_moment(r, ph), debias_second_moment(c, ph)
+                r_mean = r_eff.mean(dim=-1, keepdim=True).clamp(min=eps_root * r_eff.mean().clamp(min=1e-30))
+                v_hat = (r_eff / r_mean).unsqueeze(-1) * c_eff.unsqueeze(-2)
             else:
                 f = beta2 * f + (1 - beta2) * sq
-                v_hat = f
-            v_hat = debias_second_moment(v_hat, ph)
-            u = g / v_hat.sqrt().clamp(min=eps_grad ** 0.5)
-            rms = float(u.double().square().mean().sqrt()) if u.numel() else 0.0
-            u = u / max(1.0, rms / update_rms_clip)
-            new_row.append(r); new_col.append(c); new_full.append(f); outs.append(u)
-        out = tree_unflatten(td, outs)
+                v_hat = debias_second_moment(f, ph)
+            outs.append(g / floor_scaled(v_hat))
+            new_row.append(r); new_col.append(c); new_full.append(f)
+        # ONE clip factor for the whole update: its parameter-count-weighted RMS is brought down to update_rms_clip
+        total = sum(float(u.double().square().sum()) for u in outs)
+        count = sum(u.numel() for u in outs)
+        scale = max(1.0, math.sqrt(total / count) / update_rms_clip) if count else 1.0
+        out = tree_unflatten(td, [u / scale for u in outs])
         mu = state.mu
         if beta1 > 0:
             mu = tree_map(lambda m, u: beta1 * m + (1 - beta1) * u, state.mu, out)

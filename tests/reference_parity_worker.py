@@ -90,6 +90,42 @@ def main():
     q1, q2 = steps(orr, tr), steps(oo, to)
     out["adamw_bc"] = max(float((q1[k] - q2[k]).abs().max()) for k in q1)
 
+    def steps_with(O, T, make):
+        opt = make(O)
+        st, q = opt.init(p), {k: v.clone() for k, v in p.items()}
+        g = torch.Generator().manual_seed(3)
+        for _ in range(5):
+            grads = {k: torch.randn(v.shape, generator=g) for k, v in q.items()}
+            u, st = opt.update(T.noised(grads, max_norm=1.0, noise_stddev=0.3), st, params=q)
+            q = {k: q[k] + u[k] for k in q}
+        return q
+    worst = 0.0
+    for make in (lambda O: O.sgd(1e-2, momentum=0.9, weight_decay=0.01), lambda O: O.sgd(1e-2, momentum=0.9, nesterov=True), lambda O: O.adam(1e-2),
+                 lambda O: O.lion(1e-3, weight_decay=0.1), lambda O: O.adagrad(1e-2, noise_bias_correction=True),
+                 lambda O: O.rmsprop(1e-2, noise_bias_correction=True), lambda O: O.radam(1e-2), lambda O: O.adadelta(1.0),
+                 lambda O: O.ademamix(1e-2), lambda O: O.adamw(1e-2, update_rms_clip=1.0), lambda O: O.adafactor(1e-2),
+                 lambda O: O.adafactor(1e-2, beta1=0.9, noise_bias_correction=True, weight_decay=0.01)):
+        a, b = steps_with(orr, tr, make), steps_with(oo, to, make)
+        worst = max(worst, max(float((a[k] - b[k]).abs().max()) for k in a))
+    out["other_optimizers"] = worst
+
+    def clip_variant(D, Fm, R, which):
+        fmodel, params = Fm.make_functional(model, disable_autograd_tracking=True)
+        loss = lambda p_, x, y: torch.nn.functional.cross_entropy(fmodel(p_, x[None]), y[None])
+        common = dict(normalize_by=12.0, batch_argnums=(1, 2), return_aux=True)
+        if which == "auto":
+            gf, cs = D.auto_clipped_grad(loss, R=0.5, gamma=0.02, **common)
+        elif which == "adaptive":
+            gf, cs = D.adaptive_clipped_grad(loss, initial_clipping_norm=0.3, key=R.key(4), **common)
+        else:
+            gf, cs = D.clipped_grad(loss, clipping_norm=0.7, second_moment=True, **common)
+        outs = []
+        for _ in range(3):
+            (g, _aux), cs = gf(params, X, Y, state=cs)
+            outs.append(flat(g.grads) if hasattr(g, "grads") else flat(g))
+        return torch.cat(outs)
+    out["clipping_variants"] = max(float((clip_variant(dr, fr, rr, w) - clip_variant(do, fo, ro, w)).abs().max()) for w in ("auto", "adaptive", "second"))
+
     ref, ours = importlib.import_module("opaque.alignment.dpo.loss"), importlib.import_module("opaque_b200.alignment.dpo.loss")
     torch.manual_seed(0)
     c, r = torch.randn(9), torch.randn(9)
@@ -116,6 +152,37 @@ def main():
                        - ours.sequence_logp(logits, ids, m[:2], ld_alpha=0.4, shared_prefix_len=2)).abs().max()),
                 float((ref.mpo_combine({"a": c, "b": r}, {"a": 0.3, "b": 2.0}) - ours.mpo_combine({"a": c, "b": r}, {"a": 0.3, "b": 2.0})).abs().max()))
     out["preference_losses"] = worst
+
+    # collators (factory form, unshifted labels) and the shift-inside SFT losses
+    ra, oa = importlib.import_module("opaque.alignment"), importlib.import_module("opaque_b200.alignment")
+    rows = [{"input_ids": [1, 2, 3, 4, 5], "completion_mask": [0, 0, 1, 1, 1]}, {"input_ids": [6, 7, 8], "completion_mask": [0, 1, 1]}]
+    pairs = [{"chosen_input_ids": [1, 2, 3, 4, 5], "chosen_completion_mask": [0, 0, 0, 1, 1], "rejected_input_ids": [1, 2, 3, 6],
+              "rejected_completion_mask": [0, 0, 0, 1], "ref_chosen_logps": -1.0, "ref_rejected_logps": -2.0},
+             {"chosen_input_ids": [7, 8, 9, 10], "chosen_completion_mask": [0, 1, 1, 1], "rejected_input_ids": [7, 11, 12],
+              "rejected_completion_mask": [0, 1, 1], "ref_chosen_logps": -1.5, "ref_rejected_logps": -2.5}]
+    same_batch = lambda a, b: sorted(a) == sorted(b) and all(torch.equal(torch.as_tensor(a[k]), torch.as_tensor(b[k])) for k in a)
+    ok = True
+    for col in (True, False):
+        for mult in (None, 4):
+            kw = dict(completion_only_loss=col, pad_to_multiple_of=mult)
+            ok &= same_batch(ra.sft.collator.language_modeling_collator(0, 4, **kw)(rows), oa.sft.collator.language_modeling_collator(0, 4, **kw)(rows))
+    e1, e2 = ra.sft.collator.language_modeling_collator(0, 8)([]), oa.sft.collator.language_modeling_collator(0, 8)([])
+    ok &= all(e1[k].shape == e2[k].shape for k in e1)
+    for ml, mult in ((4, None), (16, 8)):
+        ok &= same_batch(ra.dpo.collator.preference_collator(0, ml, pad_to_multiple_of=mult)(pairs),
+                         oa.dpo.collator.preference_collator(0, ml, pad_to_multiple_of=mult)(pairs))
+    out["collators_equal"] = bool(ok)
+    torch.manual_seed(0)
+    logits, hid, head = torch.randn(2, 5, 13), torch.randn(5, 6), torch.randn(13, 6)
+    lab = ra.sft.collator.language_modeling_collator(0, 8, completion_only_loss=True)(rows)["labels"]
+    worst = 0.0
+    for name in ("nll_loss", "dft_loss"):
+        worst = max(worst, float((getattr(ra.sft.loss, name)(logits, lab) - getattr(oa.sft.loss, name)(logits, lab)).abs().max()))
+    for name in ("fused_nll_loss", "fused_dft_loss"):          # the reference's fused forms take ONE example
+        worst = max(worst, float((getattr(ra.sft.loss, name)(hid, head, lab[0]) - getattr(oa.sft.loss, name)(hid[None], head, lab[:1])[0]).abs().max()))
+    worst = max(worst, float((ra.metric.entropy_from_logits(logits, lab != -100) - oa.metric.entropy_from_logits(logits, lab != -100)).abs()),
+                float((ra.metric.mean_token_accuracy(logits, lab.clamp_min(0), lab != -100) - oa.metric.mean_token_accuracy(logits, lab.clamp_min(0), lab != -100)).abs()))
+    out["sft_losses_and_metrics"] = worst
     out["signature_checked"] = len(inspect.signature(ref.sigmoid_loss).parameters)
     print(json.dumps(out))
 

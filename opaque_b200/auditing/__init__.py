@@ -42,6 +42,32 @@ class CoinFlip:
         drop[self.canary_indices[~self.included]] = True
         return np.flatnonzero(~drop)
 
+    # the reference's names for the same partition
+    @property
+    def in_indices(self) -> np.ndarray:
+        """Dataset indices of the canaries whose coin came up "in" (they are trained on)."""
+        return self.canary_indices[self.included]
+
+    @property
+    def out_indices(self) -> np.ndarray:
+        """Dataset indices of the canaries that are held out."""
+        return self.canary_indices[~self.included]
+
+    def train_indices(self, dataset_size: int | None = None) -> list[int]:
+        """Dataset indices to train on (``dataset_size`` must agree with the partition's when given)."""
+        if dataset_size is not None and int(dataset_size) != self.dataset_size:
+            raise ValueError(f"the partition was drawn for {self.dataset_size} records, not {dataset_size}")
+        return self.kept_indices().tolist()
+
+    def train_subset(self, dataset: Any):
+        """``torch.utils.data.Subset`` of ``dataset`` holding the records to train on."""
+        return torch.utils.data.Subset(dataset, self.train_indices(len(dataset)))
+
+    def split_scores(self, scores: "CanaryScores") -> tuple[np.ndarray, np.ndarray]:
+        """``(scores of the included canaries, scores of the held-out canaries)``, joined by identifier when present."""
+        s = scores.aligned_to(self)
+        return s[self.included], s[~self.included]
+
 
 @dataclasses.dataclass(frozen=True)
 class CanaryScores:
@@ -288,8 +314,19 @@ def auc(scores: CanaryScores, flips: CoinFlip) -> float:
     return float(np.trapezoid(np.concatenate([[0], tpr]), np.concatenate([[0], fpr])))
 
 
+def _gdp_delta(mu: float, epsilon: float) -> float:
+    """δ(ε) of μ-GDP: ``Φ(−ε/μ + μ/2) − e^ε Φ(−ε/μ − μ/2)``."""
+    if mu <= 0:
+        return 0.0
+    return float(stats.norm.cdf(-epsilon / mu + mu / 2) - math.exp(epsilon) * stats.norm.cdf(-epsilon / mu - mu / 2))
+
+
 @dataclasses.dataclass(frozen=True)
 class OneRunEstimate:
+    """Result of :func:`one_run`.  The fields are the guess-counting audit (Steinke et al. 2023) at the confidence and δ the
+    call was given; the methods answer the questions the reference's estimate object answers — at another δ or
+    significance level — by re-running that audit on the stored scores.  (The reference derives them from order statistics
+    of the scores, Xiang et al. 2025; the names and meanings agree, the estimators differ.)"""
     epsilon_lower_bound: float
     gdp_mu_lower_bound: float
     num_canaries: int
@@ -298,6 +335,63 @@ class OneRunEstimate:
     accuracy: float
     confidence: float
     delta: float
+    in_scores: np.ndarray | None = None          # scores of the canaries that were trained on
+    out_scores: np.ndarray | None = None         # scores of the held-out canaries
+    canary_indices: np.ndarray | None = None
+
+    def _audit(self, delta: float, significance: float) -> "OneRunEstimate":
+        if self.in_scores is None or self.out_scores is None:
+            raise ValueError("this estimate carries no scores; build it with one_run()")
+        m = len(self.in_scores) + len(self.out_scores)
+        flips = CoinFlip(np.arange(m), np.r_[np.ones(len(self.in_scores), bool), np.zeros(len(self.out_scores), bool)], m)
+        return one_run(CanaryScores(np.r_[self.in_scores, self.out_scores]), coin_flip=flips, delta=delta, confidence=1.0 - significance)
+
+    def epsilon_at(self, *, delta: float, significance: float = 0.05, threshold: float | None = None) -> float:
+        """Lower bound on ε at ``delta``, valid with probability ``1 − significance``."""
+        return self._audit(delta, significance).epsilon_lower_bound
+
+    def gdp_mu(self, *, significance: float = 0.05) -> float:
+        """Lower bound on the μ of μ-GDP."""
+        return self._audit(self.delta, significance).gdp_mu_lower_bound
+
+    def delta_at(self, *, epsilon: float, significance: float = 0.05, threshold: float | None = None) -> float:
+        """δ(ε) of the refuted μ-GDP level: the mechanism's δ at this ε is at least this."""
+        return _gdp_delta(self.gdp_mu(significance=significance), epsilon)
+
+    def beta_at(self, *, alpha: float, significance: float = 0.05, threshold: float | None = None) -> float:
+        """Type-II error at false-positive rate ``alpha`` of the refuted μ-GDP level, ``Φ(Φ⁻¹(1 − α) − μ)``: some attack on
+        the mechanism does at least this well."""
+        return float(stats.norm.cdf(stats.norm.ppf(1.0 - alpha) - self.gdp_mu(significance=significance)))
+
+    def advantage(self, *, significance: float = 0.05, threshold: float | None = None) -> float:
+        """Total-variation advantage of the refuted μ-GDP level, ``2Φ(μ/2) − 1``."""
+        return float(2.0 * stats.norm.cdf(self.gdp_mu(significance=significance) / 2.0) - 1.0)
+
+    def attack_auc(self, *, confidence: float | None = None, num_samples: int = 1000, key: RngKey | None = None):
+        """Area under the ROC curve of the scores (probability that an included canary outscores a held-out one); with
+        ``confidence`` also a bootstrap interval ``(low, high)`` over ``num_samples`` resamples."""
+        a, b = np.asarray(self.in_scores), np.asarray(self.out_scores)
+
+        def area(x, y):
+            return float(((x[:, None] > y[None, :]).mean() + 0.5 * (x[:, None] == y[None, :]).mean())) if len(x) and len(y) else 0.5
+        point = area(a, b)
+        if confidence is None:
+            return point
+        rng = np.random.default_rng(fold_in(key, "attack_auc").seed if key is not None else 0)
+        draws = [area(rng.choice(a, len(a)), rng.choice(b, len(b))) for _ in range(int(num_samples))]
+        lo, hi = np.quantile(draws, [(1 - confidence) / 2, 1 - (1 - confidence) / 2])
+        return point, (float(lo), float(hi))
+
+    def attack_beta_at(self, *, alpha):
+        """Empirical attack error: ``1 − TPR`` at false-positive rate ``alpha`` (scalar or array), thresholding the scores."""
+        a, b = np.asarray(self.in_scores), np.sort(np.asarray(self.out_scores))
+        al = np.atleast_1d(np.asarray(alpha, dtype=float))
+        out = []
+        for x in al:
+            k = int(np.floor(x * len(b)))                       # how many held-out canaries may be flagged
+            thr = b[len(b) - k - 1] if k < len(b) else -np.inf  # flag scores strictly above this threshold
+            out.append(1.0 - float((a > thr).mean()) if len(a) else 1.0)
+        return out[0] if np.ndim(alpha) == 0 else np.asarray(out)
 
 
 def one_run(scores: CanaryScores, *, coin_flip: CoinFlip, num_guesses: int | None = None, delta: float = 0.0,
@@ -325,7 +419,8 @@ def one_run(scores: CanaryScores, *, coin_flip: CoinFlip, num_guesses: int | Non
         eps, r, v = max((evaluate(k, conf) for k in ladder), key=lambda t: t[0])
         confidence_used = conf
     mu = gdp_mu_lower_bound(m, r, v, confidence=confidence if num_guesses is not None else confidence_used)
-    return OneRunEstimate(eps, mu, m, r, v, v / max(r, 1), confidence, delta)
+    return OneRunEstimate(eps, mu, m, r, v, v / max(r, 1), confidence, delta, s[y].copy(), s[~y].copy(),
+                          np.asarray(coin_flip.canary_indices).copy())
 
 
 __all__ = ["CanaryScores", "CoinFlip", "OneRunEstimate", "auc", "canary_scores", "coin_flip", "epsilon_lower_bound",

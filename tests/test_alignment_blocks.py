@@ -257,3 +257,30 @@ def test_completion_logp_shifts_and_matches_the_aligned_form():
     assert torch.allclose(sequence_logp(logits, ids, mask, ld_alpha=0.5, shared_prefix_len=2), dpo.ld_dpo_split(lp, mask[:, 1:], 2, 0.5), atol=1e-5)
     with pytest.raises(ValueError):
         sequence_logp(logits, ids, mask, ld_alpha=0.5)
+
+
+def test_audit_estimate_answers_the_reference_questions():
+    import numpy as np
+    from opaque_b200 import auditing
+    from opaque_b200.random import key
+    data = list(range(400))
+    flips = auditing.coin_flip(data, num_canaries=200, key=key(3))
+    assert len(flips.in_indices) + len(flips.out_indices) == 200 and set(flips.in_indices).isdisjoint(flips.out_indices)
+    assert len(flips.train_indices(400)) == 400 - len(flips.out_indices) == len(flips.train_subset(data))
+    with pytest.raises(ValueError):
+        flips.train_indices(399)
+    scores = np.where(flips.included, 1.2, -1.2) + np.random.default_rng(0).normal(0, 1.0, 200)
+    cs = auditing.canary_scores(scores, canary_indices=flips.canary_indices)
+    ins, outs = flips.split_scores(cs)
+    assert len(ins) == int(flips.included.sum()) and ins.mean() > outs.mean()
+    est = auditing.one_run(cs, coin_flip=flips, delta=1e-5)
+    assert est.epsilon_at(delta=1e-5) == pytest.approx(est.epsilon_lower_bound) and est.epsilon_at(delta=1e-5, significance=0.2) >= est.epsilon_lower_bound
+    mu = est.gdp_mu()
+    assert mu > 0 and 0 < est.delta_at(epsilon=0.5) < 1 and est.delta_at(epsilon=0.5) > est.delta_at(epsilon=2.0)
+    assert 0 < est.beta_at(alpha=0.1) < 0.9 and 0 < est.advantage() < 1
+    point, (lo, hi) = est.attack_auc(confidence=0.9, num_samples=200, key=key(1))
+    assert 0.9 < lo <= point <= hi <= 1.0 and est.attack_auc() == point
+    betas = est.attack_beta_at(alpha=np.array([0.0, 0.1, 1.0]))
+    assert betas[0] >= betas[1] >= betas[2] == 0.0 and est.attack_beta_at(alpha=0.1) == betas[1]
+    noise_only = auditing.one_run(auditing.canary_scores(np.random.default_rng(1).normal(size=200)), coin_flip=flips, delta=1e-5)
+    assert noise_only.epsilon_at(delta=1e-5) == 0.0 and abs(noise_only.attack_auc() - 0.5) < 0.1 and noise_only.advantage() < 0.2

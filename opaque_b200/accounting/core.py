@@ -53,6 +53,11 @@ class DiscretizationConfig:
     # delta by ~1e-8 relative per mechanism); False (default) keeps every reported epsilon a strict upper bound
     proportional_normalization: bool = False
 
+    @property
+    def log_x_mass_truncation_bound(self) -> float:
+        """The reference's name of ``log_mass_truncation_bound``."""
+        return self.log_mass_truncation_bound
+
     def __post_init__(self) -> None:
         if not self.discretization > 0:
             raise ValueError("discretization must be > 0")

@@ -75,6 +75,18 @@ class CyclicPoisson(DpHorizonProcess):
     truncated_batch_size: int | None = None
     dataset_size: int | None = None
 
+    @property
+    def min_sep(self) -> int:
+        return self.bands
+
+    @property
+    def max_participations(self) -> int:
+        return -(-self.n_steps // self.bands)
+
+    @property
+    def atomic_unit(self) -> int:
+        return self.bands
+
     def __post_init__(self):
         if not 0 < self.sample_rate <= 1:
             raise ValueError("sample_rate must be in (0, 1]")
@@ -105,6 +117,24 @@ class BallsInBins(DpHorizonProcess):
     inner: MfGaussian
     num_bins: int
     n_steps: int
+
+    @property
+    def min_sep(self) -> int:
+        """Steps between two participations of a record: the number of bins."""
+        return self.num_bins
+
+    @property
+    def max_participations(self) -> int:
+        return -(-self.n_steps // self.num_bins)
+
+    @property
+    def num_epochs(self) -> float:
+        return self.n_steps / self.num_bins
+
+    @property
+    def atomic_unit(self) -> int:
+        """Steps after which the participation pattern repeats (one pass over the bins)."""
+        return self.num_bins
 
     def pld_at(self, n_steps: int, config: DiscretizationConfig | None = None):
         cfg = config or get_discretization()
@@ -161,6 +191,23 @@ class BMinSep(DpHorizonProcess):
     n_steps: int
     sampling_prob: float
     warm_start: bool = False
+
+    @property
+    def min_sep(self) -> int:
+        return self.bands
+
+    @property
+    def max_participations(self) -> int:
+        return -(-self.n_steps // self.bands)
+
+    @property
+    def atomic_unit(self) -> int:
+        return self.bands
+
+    @property
+    def p0(self) -> float:
+        """Stationary per-example participation rate ``p / (1 + p·(bands − 1))``."""
+        return self.sampling_prob / (1.0 + self.sampling_prob * max(0, self.bands - 1))
 
     def __post_init__(self):
         if self.bands < 1 or not 0 < self.sampling_prob <= 1:

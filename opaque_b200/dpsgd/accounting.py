@@ -108,6 +108,23 @@ class RandomAllocation(DpProcess):
     def _build_pld(self, config):
         return native.random_allocation_gaussian_pld(_nm(self.inner), self.num_bins, self.k, config.to_native())
 
+    # the reference's names: one epoch = ``num_bins`` steps in which a record takes part ``k`` times
+    @property
+    def steps_per_epoch(self) -> int:
+        return self.num_bins
+
+    @property
+    def total_participations(self) -> int:
+        return self.k
+
+    @property
+    def n_steps(self) -> int:
+        return self.num_bins
+
+    @property
+    def num_epochs(self) -> int:
+        return 1
+
 
 def gaussian(noise_multiplier: float) -> Gaussian:
     """One Gaussian release with the given noise multiplier (sensitivity 1)."""

@@ -62,6 +62,11 @@ class ClippedFunAux:
     batch_size: int = 0
     group_norms: dict[str, torch.Tensor] | None = None
 
+    @property
+    def value_aux(self) -> Any:
+        """The auxiliary outputs of the clipped function (``aux`` under the reference's field name)."""
+        return self.aux
+
 
 @dataclasses.dataclass(frozen=True)
 class ClippedGradAux:

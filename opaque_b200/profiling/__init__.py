@@ -34,6 +34,18 @@ class MemoryStats:
     def peak_gb(self) -> float:
         return self.peak_allocated_bytes / 2 ** 30
 
+    @property
+    def allocated_gb(self) -> float:
+        return self.allocated_bytes / 2 ** 30
+
+    @property
+    def reserved_gb(self) -> float:
+        return self.reserved_bytes / 2 ** 30
+
+    def to_dict(self) -> dict[str, float]:
+        return {"allocated_gb": self.allocated_gb, "reserved_gb": self.reserved_gb, "peak_gb": self.peak_gb,
+                "peak_reserved_gb": self.peak_reserved_bytes / 2 ** 30}
+
 
 _NVTX = {"on": None}      # None: decided by the environment variable OPAQUE_B200_NVTX on first use
 

@@ -309,23 +309,76 @@ def toeplitz_sensitivity_squared(coef: np.ndarray, n: int, min_sep: int = 1, max
     return float(native.general_sensitivity_squared_upper_bound(g.reshape(-1).tolist(), n, min_sep, max_participations))
 
 
+def _series_mul(a: torch.Tensor, b: torch.Tensor, n: int) -> torch.Tensor:
+    """First ``n`` coefficients of the product of two power series (FFT; differentiable)."""
+    a, b = a[:n], b[:n]
+    m = a.numel() + b.numel() - 1
+    size = 1 << max(1, (m - 1).bit_length())
+    out = torch.fft.irfft(torch.fft.rfft(a, size) * torch.fft.rfft(b, size), size)[: min(m, n)]
+    return out if out.numel() == n else torch.cat([out, out.new_zeros(n - out.numel())])
+
+
+def _series_inverse(c: torch.Tensor, n: int) -> torch.Tensor:
+    """First ``n`` coefficients of ``1 / C(x)`` by Newton doubling ``g ← g·(2 − C·g)`` (differentiable in ``c``)."""
+    g = (1.0 / c[0]).reshape(1)
+    m = 1
+    while m < n:
+        m = min(2 * m, n)
+        two_minus = -_series_mul(c, g, m)
+        two_minus = two_minus + torch.nn.functional.one_hot(torch.zeros((), dtype=torch.long), m).to(c.dtype) * 2.0
+        g = _series_mul(g, two_minus, m)
+    return g
+
+
+def momentum_workload_coefs(momentum: float, n: int) -> np.ndarray | None:
+    """Toeplitz coefficients ``β^k`` of the momentum-SGD workload (``None`` = prefix sums, β = 1)."""
+    if momentum < 0:
+        raise ValueError(f"momentum must be >= 0, got {momentum}")
+    return None if momentum == 1.0 else float(momentum) ** np.arange(n)
+
+
+def toeplitz_workload_error(strategy_coef, n: int, *, workload_coef=None, query_weights=None, kind: str = "mean"):
+    """Squared error of answering the workload ``W`` (lower-triangular Toeplitz, first column ``workload_coef``; prefix
+    sums when ``None``) through ``C``: query ``t`` has error ``w_t² · Σ_{k≤t} b_k²`` with ``b = workload ⊛ C⁻¹``;
+    the mean or the max over queries.  Takes and returns torch values when ``strategy_coef`` is a tensor (differentiable)."""
+    as_numpy = not isinstance(strategy_coef, torch.Tensor)
+    c = torch.as_tensor(np.asarray(strategy_coef, float) if as_numpy else strategy_coef, dtype=torch.float64)
+    inv = _series_inverse(c, n)
+    b = torch.cumsum(inv, 0) if workload_coef is None else _series_mul(torch.as_tensor(workload_coef, dtype=torch.float64), inv, n)
+    err = torch.cumsum(b * b, 0)
+    if query_weights is not None:
+        w = torch.as_tensor(query_weights, dtype=torch.float64)
+        if w.shape != (n,):
+            raise ValueError(f"query_weights must have shape ({n},), got {tuple(w.shape)}")
+        err = err * w * w
+    out = err.mean() if kind == "mean" else err.max()
+    return float(out) if as_numpy else out
+
+
 @functools.lru_cache(maxsize=64)
-def optimize_banded(n: int, bands: int, min_sep: int = 1, max_participations: int | None = None,
-                    error: str = "max") -> tuple[float, ...]:
-    """L-BFGS over the first ``bands`` Toeplitz coefficients (``c_0 = 1``) minimising sensitivity² × error."""
+def optimize_banded(n: int, bands: int, momentum: float = 1.0, lr_key: tuple[float, ...] | None = None,
+                    error: str = "mean") -> tuple[float, ...]:
+    """L-BFGS over the first ``bands`` Toeplitz coefficients, minimising (single-participation sensitivity)² × error of
+    the momentum workload with per-step learning-rate weights ``lr_key``; exact gradients by autograd.  The result has
+    unit L2 norm, so one participation has sensitivity 1 and participations at least ``bands`` steps apart add up in
+    quadrature (reference: dpftrl/noise/_toeplitz.py ``optimize``, the same objective and start point)."""
     from scipy.optimize import minimize
     bands = max(1, min(bands, n))
-    x0 = sqrt_coefs(bands)[1:]
     if bands == 1:
         return (1.0,)
+    workload = momentum_workload_coefs(momentum, n)
+    weights = None if lr_key is None else np.asarray(lr_key, float)
 
     def loss(x):
-        c = np.concatenate([[1.0], np.abs(x)])
-        inv = inverse_coef(c, n)
-        return math.log(toeplitz_sensitivity_squared(c, n, min_sep, max_participations)) + math.log(prefix_workload_error(inv, kind=error))
-    res = minimize(loss, x0, method="L-BFGS-B", options={"maxiter": 250})
-    best = res.x if res.fun <= loss(x0) else x0
-    return tuple(np.concatenate([[1.0], np.abs(best)]).tolist())
+        c = torch.tensor(x, dtype=torch.float64, requires_grad=True)
+        val = toeplitz_workload_error(c, n, workload_coef=workload, query_weights=weights, kind=error) * (c * c).sum()
+        val.backward()
+        return float(val.detach()), c.grad.numpy().copy()
+    x0 = sqrt_coefs(bands)
+    res = minimize(loss, x0, jac=True, method="L-BFGS-B", options={"maxiter": 250, "ftol": 1e-15, "gtol": 1e-10})
+    best = res.x if np.all(np.isfinite(res.x)) and res.fun <= loss(x0)[0] else x0
+    best = best * np.sign(best[0])
+    return tuple((best / np.linalg.norm(best)).tolist())
 
 
 @functools.lru_cache(maxsize=64)
@@ -367,8 +420,35 @@ def _lr_weights(lr_schedule, n: int) -> np.ndarray | None:
     return np.array([float(lr_schedule(t)) for t in range(n)])
 
 
+def _accept_n_steps(fn):
+    """The reference calls the strategy methods with keywords — ``coefficients(n_steps=…, min_sep=…, max_participations=…)``.
+    Accept ``n_steps=`` for the first positional argument, and drop participation keywords a method does not take."""
+    import functools
+    import inspect
+    takes = set(inspect.signature(fn).parameters)
+
+    @functools.wraps(fn)
+    def method(self, *args, n_steps=None, **kwargs):
+        if n_steps is not None:
+            if args:
+                raise TypeError(f"{fn.__name__}() got the horizon twice")
+            args = (n_steps,)
+        return fn(self, *args, **{k: v for k, v in kwargs.items() if k in takes})
+    method._accepts_n_steps = True
+    return method
+
+
 class MfStrategy:
     """Protocol-like base: a factorisation ``A = B C`` described by its strategy matrix ``C``."""
+
+    _HORIZON_METHODS = ("coefficients", "gram_matrix", "sensitivity", "streaming_matrix")
+
+    def __init_subclass__(cls, **kwargs):
+        super().__init_subclass__(**kwargs)
+        for name in cls._HORIZON_METHODS:
+            fn = cls.__dict__.get(name)
+            if fn is not None and not getattr(fn, "_accepts_n_steps", False):
+                setattr(cls, name, _accept_n_steps(fn))
 
     def coefficients(self, n: int) -> np.ndarray:
         raise NotImplementedError
@@ -397,6 +477,11 @@ class MfStrategy:
         return {"kind": "banded", "coef": c.tolist()}
 
 
+for _name in MfStrategy._HORIZON_METHODS:
+    setattr(MfStrategy, _name, _accept_n_steps(MfStrategy.__dict__[_name]))
+del _name
+
+
 @dataclasses.dataclass(frozen=True)
 class IdentityStrategy(MfStrategy):
     """``C = I``: independent noise every step (DP-SGD as a degenerate factorisation)."""
@@ -419,8 +504,9 @@ class BandMfStrategy(MfStrategy):
             raise ValueError("bands must be >= 1")
 
     def coefficients(self, n):
-        # optimised for one participation per band window (b-min-sep use); more participations only rescale
-        return np.array(optimize_banded(n, min(self.bands, n), 1, 1))
+        # optimised for one participation per band window (cyclic Poisson / b-min-sep use); more participations only rescale
+        lr = _lr_weights(self.lr_schedule, n)
+        return np.array(optimize_banded(n, min(self.bands, n), float(self.momentum), None if lr is None else tuple(lr.tolist())))
 
 
 @dataclasses.dataclass(frozen=True)
@@ -517,6 +603,8 @@ class LambdaCgdStrategy(MfStrategy):
     lambda_: float
     normalized: bool = True
     lr_schedule: Any = None
+    # z_t is drawn from fold_in(key, t), without the label the other strategies use (reference: dpftrl/noise/_lambda_cgd.py:279)
+    step_key_labels = ()
 
     def __post_init__(self):
         if not 0 <= self.lambda_ < 1:
@@ -701,6 +789,7 @@ def mf_gaussian_noise(grad_template: Any, strategy: MfStrategy, *, n_steps: int,
     sm = strategy.streaming_matrix(n_steps)
     row_sq = sm.row_norms_squared(n_steps) if sm.row_norms_squared is not None else np.ones(n_steps)
     inner0 = sm.init_multiply(grad_template.pytree if isinstance(grad_template, ClippedPytree) else grad_template)
+    step_labels = getattr(strategy, "step_key_labels", ("mf_gaussian_column",))
 
     def noise_fn(grads: ClippedPytree, st: MFNoiseState):
         with torch.profiler.record_function("opaque::mf_gaussian_noise"):
@@ -719,7 +808,7 @@ def mf_gaussian_noise(grad_template: Any, strategy: MfStrategy, *, n_steps: int,
             if not math.isclose(first, mn, rel_tol=1e-9, abs_tol=0.0):
                 raise ValueError(f"max_norm changed from {first} to {mn}; matrix-factorisation noise needs a constant bound")
             sigma = noise_multiplier * mn
-            step_key = fold_in(st._rng_key, "mf_gaussian_column", t)
+            step_key = fold_in(st._rng_key, *step_labels, t)
             z = _iid_normal_like(grads.pytree, sigma, step_key, compute_dtype) if sigma > 0 else tree_map(
                 lambda g: torch.zeros_like(g, dtype=compute_dtype), grads.pytree)
             x, inner = sm.multiply_next(z, st._inner_state)
@@ -822,7 +911,7 @@ __all__ = [
     "MFNoiseState", "MfStrategy", "SecondMomentMFNoiseState", "StreamingMatrix", "band_mf_strategy", "bisr_strategy", "blt_coefs",
     "blt_inverse_coef", "blt_inverse_streaming", "blt_strategy", "bsr_strategy", "fir_streaming", "identity_strategy",
     "identity_streaming", "inv_sqrt_coefs", "inverse_coef", "lambda_cgd_strategy", "mf_gaussian_noise",
-    "optimize_banded", "optimize_blt", "prefix_sum_streaming", "register_strategy", "sqrt_coefs", "strategy_from_wire",
+    "momentum_workload_coefs", "optimize_banded", "optimize_blt", "toeplitz_workload_error", "prefix_sum_streaming", "register_strategy", "sqrt_coefs", "strategy_from_wire",
     "strategy_to_wire", "toeplitz_gram", "toeplitz_inverse_streaming", "toeplitz_sensitivity_squared",
 ]
 

@@ -183,6 +183,34 @@ def main():
     worst = max(worst, float((ra.metric.entropy_from_logits(logits, lab != -100) - oa.metric.entropy_from_logits(logits, lab != -100)).abs()),
                 float((ra.metric.mean_token_accuracy(logits, lab.clamp_min(0), lab != -100) - oa.metric.mean_token_accuracy(logits, lab.clamp_min(0), lab != -100)).abs()))
     out["sft_losses_and_metrics"] = worst
+    # ------------------------------------------------------------------ DP-FTRL: strategies and correlated noise
+    import numpy as np
+    fr, fo = both("dpftrl")
+    lr = lambda t: 1.0 / (1 + t)
+    worst = 0.0
+    for n, kw in ((8, dict(bands=4)), (32, dict(bands=4, momentum=0.9)), (32, dict(bands=3, lr_schedule=lr))):
+        a, b = fr.band_mf_strategy(**kw), fo.band_mf_strategy(**kw)
+        worst = max(worst, float(np.abs(np.asarray(a.coefficients(n_steps=n)) - np.asarray(b.coefficients(n_steps=n))).max()))
+    out["band_mf_coefficients"] = worst
+    a, b = fr.bsr_strategy(bandwidth=4, alpha=1.0, beta=0.9), fo.bsr_strategy(bandwidth=4, alpha=1.0, beta=0.9)
+    out["bsr_sensitivity"] = max(abs(float(a.sensitivity(n_steps=16, min_sep=ms, max_participations=mp))
+                                     - float(b.sensitivity(n_steps=16, min_sep=ms, max_participations=mp)))
+                                 for ms, mp in ((1, None), (4, None), (4, 2)))
+    worst, spread = 0.0, 0.0
+    for make in (lambda F: F.identity_strategy(), lambda F: F.band_mf_strategy(bands=4),
+                 lambda F: F.bsr_strategy(bandwidth=4, alpha=1.0, beta=0.9),
+                 lambda F: F.lambda_cgd_strategy(lambda_=0.5), lambda F: F.lambda_cgd_strategy(lambda_=0.5, normalized=False)):
+        runs = []
+        for F, T, R in ((fr, tr, rr), (fo, to, ro)):
+            nf, ns = F.mf_gaussian_noise({"w": torch.zeros(6)}, make(F), n_steps=8, noise_multiplier=1.0, key=R.key(3))
+            rows = []
+            for _ in range(5):
+                o, ns = nf(T.clipped({"w": torch.zeros(6)}, max_norm=1.0), ns)
+                rows.append(torch.cat([o.pytree["w"], torch.tensor([float(o.noise_stddev)])]))
+            runs.append(torch.stack(rows))
+        worst = max(worst, float((runs[0] - runs[1]).abs().max()))
+        spread = max(spread, float(runs[1].std()))
+    out["mf_noise_realisation"], out["mf_noise_std"] = worst, spread
     out["signature_checked"] = len(inspect.signature(ref.sigmoid_loss).parameters)
     print(json.dumps(out))
 

@@ -55,6 +55,38 @@ def test_optimised_strategies_beat_identity():
     assert loss(blt_strategy(max_buffers=3)) < 0.5 * base
 
 
+def test_strategy_methods_accept_the_keyword_form():
+    """``n_steps=`` names the horizon; participation keywords a method does not read are accepted and ignored."""
+    for s in (identity_strategy(), band_mf_strategy(bands=3), blt_strategy(max_buffers=2), bsr_strategy(bandwidth=3)):
+        assert s.sensitivity(n_steps=12, min_sep=3, max_participations=2) == s.sensitivity(12, 3, 2)
+        assert np.array_equal(s.coefficients(n_steps=12, min_sep=3, max_participations=None), s.coefficients(12))
+        assert np.array_equal(s.gram_matrix(n_steps=6, min_sep=1, max_participations=None), s.gram_matrix(6))
+        s.streaming_matrix(n_steps=6, min_sep=1, max_participations=None)
+    with pytest.raises(TypeError):
+        identity_strategy().coefficients(4, n_steps=4)
+
+
+def test_band_mf_objective_momentum_and_learning_rate_weights():
+    """Unit-norm coefficients that minimise the MEAN squared error of the momentum workload, weighted per step."""
+    n = 48
+    base = np.asarray(band_mf_strategy(bands=4).coefficients(n))
+    assert math.isclose(float(np.linalg.norm(base)), 1.0, rel_tol=1e-12) and np.all(np.diff(base) < 0)
+    def objective(c, **kw):
+        return N.toeplitz_workload_error(c, n, **kw) * float(np.dot(c, c))
+    assert objective(base) < objective(N.sqrt_coefs(4)) and objective(base) < 0.5 * objective(np.array([1.0]))
+    for eps in (1e-3, -1e-3):                                  # a stationary point of the scale-invariant objective
+        for k in range(4):
+            bumped = base.copy(); bumped[k] += eps
+            assert objective(bumped) >= objective(base) - 1e-12
+    mom = np.asarray(band_mf_strategy(bands=4, momentum=0.5).coefficients(n))
+    w = N.momentum_workload_coefs(0.5, n)
+    assert objective(mom, workload_coef=w) < objective(base, workload_coef=w)
+    weights = np.linspace(1.0, 0.05, n)
+    lr = np.asarray(band_mf_strategy(bands=4, lr_schedule=lambda t: float(weights[t])).coefficients(n))
+    assert objective(lr, query_weights=weights) < objective(base, query_weights=weights)
+    assert math.isclose(N.toeplitz_workload_error(base, n, kind="max"), N.prefix_workload_error(N.inverse_coef(base, n)), rel_tol=1e-9)
+
+
 def test_mf_noise_statistics_horizon_and_constant_norm():
     s = blt_strategy(max_buffers=2)
     nf, st = mf_gaussian_noise({"w": torch.zeros(50_000)}, s, n_steps=3, noise_multiplier=2.0, key=key(1))

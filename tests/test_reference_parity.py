@@ -1,6 +1,7 @@
 """Numerical parity with the UNMODIFIED reference on the CPU, when it is installed (``baseline/install_reference.sh`` puts it
 into ``baseline/_ref``): same key derivation, schedules, clipped gradients, even the same noise realisation and the same
-Poisson / random-allocation / balls-in-bins draws; twelve optimizer configurations, automatic / adaptive / second-moment clipping, every
+Poisson / random-allocation / balls-in-bins draws; band-MF coefficients and the correlated-noise
+realisations of four matrix-factorisation strategies; twelve optimizer configurations, automatic / adaptive / second-moment clipping, every
 preference-loss piece, the factory collators and the shift-inside SFT losses to rounding."""
 import json
 import os
@@ -24,4 +25,7 @@ def test_building_blocks_equal_the_reference():
     assert d["schedules"] < 1e-9 and d["clipped_grad"] < 1e-6 and d["grad_norms"] < 1e-6, d
     assert d["noise_realisation"] < 1e-6 and d["noise_std"] > 0.01, d          # the SAME noise, and it is noise
     assert d["adamw_bc"] < 1e-6 and d["other_optimizers"] < 1e-5 and d["clipping_variants"] < 1e-6, d      # adaptive clipping: 3 steps of its state too
+    # band-MF coefficients from the same objective; identity / band-MF / BSR / λ-CGD noise: the same realisation and published std
+    assert d["band_mf_coefficients"] < 1e-6 and d["bsr_sensitivity"] < 1e-9, d
+    assert d["mf_noise_realisation"] < 1e-5 and d["mf_noise_std"] > 0.1, d
     assert d["preference_losses"] < 1e-5 and d["collators_equal"] and d["sft_losses_and_metrics"] < 1e-5, d

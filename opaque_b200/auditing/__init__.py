@@ -321,12 +321,190 @@ def _gdp_delta(mu: float, epsilon: float) -> float:
     return float(stats.norm.cdf(-epsilon / mu + mu / 2) - math.exp(epsilon) * stats.norm.cdf(-epsilon / mu - mu / 2))
 
 
+def _gdp_epsilon(mu: float, delta: float) -> float:
+    """The ε at which μ-GDP has exactly ``delta`` (0 when even ε = 0 needs less)."""
+    if mu <= 0 or _gdp_delta(mu, 0.0) <= delta:
+        return 0.0
+    lo, hi = 0.0, 1.0
+    while _gdp_delta(mu, hi) > delta and hi < 1e6:
+        hi *= 2.0
+    for _ in range(200):
+        mid = 0.5 * (lo + hi)
+        lo, hi = (mid, hi) if _gdp_delta(mu, mid) > delta else (lo, mid)
+    return lo
+
+
+@dataclasses.dataclass(frozen=True)
+class EpsDeltaMethod:
+    """(ε, δ) audit from ALL canaries at one threshold (order-statistics test of Xiang et al. 2025 for the (ε, δ) trade-off
+    curve): every canary is guessed "in" when its score reaches the threshold, and under (ε, δ)-DP the number of wrong
+    guesses among the ``m − round(m·δ)`` ranks outside the point mass dominates a Binomial with success probability
+    ``1 / (1 + e^ε)``.  The largest ε whose p-value stays below ``significance`` is the lower bound.  Without
+    ``threshold`` the one with the most correct guesses is taken, as the reference does
+    (reference: auditing/one_run/_eps_delta.py, _estimate.py ``_best_r_u``)."""
+    estimate: "OneRunEstimate"
+
+    def guesses_and_errors(self, threshold: float | None = None) -> tuple[int, int]:
+        a, b = np.asarray(self.estimate.in_scores, float), np.asarray(self.estimate.out_scores, float)
+        m = len(a) + len(b)
+        if threshold is not None:
+            return m, m - int((a >= threshold).sum()) - int((b < threshold).sum())
+        cuts = np.unique(np.r_[a, b, np.inf])                     # "in" iff score >= cut; +inf: everything "out"
+        a_sorted, b_sorted = np.sort(a), np.sort(b)
+        correct = (len(a) - np.searchsorted(a_sorted, cuts, "left")) + np.searchsorted(b_sorted, cuts, "left")
+        return m, m - int(correct.max())
+
+    @staticmethod
+    def p_value(guesses: int, errors: int, epsilon: float, delta: float) -> float:
+        trials = max(guesses - round(guesses * delta), 0)
+        return 1.0 if trials == 0 else float(stats.binom.cdf(errors, trials, 1.0 / (1.0 + math.exp(max(epsilon, 0.0)))))
+
+    @staticmethod
+    def _check(significance: float, delta: float = 0.0) -> None:
+        if not 0 < significance < 0.5:
+            raise ValueError(f"significance must be in (0, 0.5), got {significance}")
+        if not 0 <= delta <= 1:
+            raise ValueError(f"delta must be in [0, 1], got {delta}")
+
+    def epsilon_at(self, *, delta: float = 0.0, significance: float = 0.05, threshold: float | None = None) -> float:
+        self._check(significance, delta)
+        r, u = self.guesses_and_errors(threshold)
+        trials = max(r - round(r * delta), 1)
+        hi = max(1.1 * -math.log(significance ** (-1.0 / trials) - 1.0), 1.0)      # a perfect attack certifies no more
+        lo = 0.0
+        while hi - lo > 1e-4:
+            mid = 0.5 * (lo + hi)
+            lo, hi = (mid, hi) if self.p_value(r, u, mid, delta) < significance else (lo, mid)
+        return lo
+
+    def delta_at(self, *, epsilon: float, significance: float = 0.05, threshold: float | None = None) -> float:
+        """Largest δ at which ``epsilon`` is still refuted (0 when it is not refuted even at δ = 0)."""
+        self._check(significance)
+        if epsilon < 0:
+            raise ValueError(f"epsilon must be >= 0, got {epsilon}")
+        r, u = self.guesses_and_errors(threshold)
+        if self.p_value(r, u, epsilon, 0.0) >= significance:
+            return 0.0
+        lo, hi = 0.0, 1.0
+        while hi - lo > 1e-6:
+            mid = 0.5 * (lo + hi)
+            lo, hi = (mid, hi) if self.p_value(r, u, epsilon, mid) < significance else (lo, mid)
+        return lo
+
+
+MAX_EXACT_RANKS = 2000      # ranks beyond this many get the trivial error probability 1/2 (keeps the rank × grid table small)
+
+
+def gdp_rank_error_probabilities(num_canaries: int, ranks: int, mu: float, grid_size: int = 10_000) -> np.ndarray:
+    """Under μ-GDP, the probability that the guess for the canary with the k-th smallest |privacy loss| is wrong, for the
+    ``ranks`` LARGEST k of ``num_canaries``: ``v_k = E[sigmoid(−|L(Y_(k))|)]`` with ``Y`` drawn from the equal mixture of
+    ``N(0, 1)`` and ``N(μ, 1)`` and ``L(z) = μ²/2 − μz`` (Xiang et al. 2025, eq. 12).  The expectation over the order
+    statistic's density ``n!/((k−1)!(n−k)!) F^{k−1}(1−F)^{n−k} f`` is a sum over a grid in ``z`` sorted by ``|L|``, in logs."""
+    from scipy import special
+    n = int(num_canaries)
+    z = np.linspace(-6.0, mu + 6.0, int(grid_size))
+    mass = 0.5 * (stats.norm.pdf(z) + stats.norm.pdf(z - mu)) * (z[1] - z[0])
+    loss = np.abs(0.5 * mu * mu - mu * z)
+    order = np.argsort(loss, kind="stable")
+    mass, loss = mass[order], loss[order]
+    below = np.concatenate([[0.0], np.cumsum(mass)[:-1]])                   # mixture mass with a smaller |L|
+    tiny = 1e-300
+    log_f, log_lo, log_hi = np.log(np.maximum(mass, tiny)), np.log(np.maximum(below, tiny)), np.log(np.maximum(1.0 - below, tiny))
+    k = np.arange(n - ranks + 1, n + 1, dtype=np.float64)[:, None]
+    log_count = special.gammaln(n + 1) - special.gammaln(k) - special.gammaln(n - k + 1)
+    table = (log_count + log_f[None, :] + np.where(k > 1, (k - 1) * log_lo[None, :], 0.0)
+             + np.where(k < n, (n - k) * log_hi[None, :], 0.0) + special.log_expit(-loss)[None, :])
+    return np.clip(np.exp(special.logsumexp(table, axis=1)), 0.0, 0.5)
+
+
+def bernoulli_sum_lower_tail(probabilities: np.ndarray, num_fair: int, observed: int) -> float:
+    """Chernoff bound on ``P(Σ X_i ≤ observed)`` for independent ``X_i ~ Bernoulli(p_i)`` plus ``num_fair`` fair coins:
+    ``min_{λ ≤ 0} exp(−λ·observed + Σ log(1 − p_i + p_i e^λ))``; 1 when ``observed`` is not below the mean."""
+    v = np.asarray(probabilities, float)
+    if observed >= float(v.sum()) + 0.5 * num_fair:
+        return 1.0
+    if observed == 0:
+        return min(math.exp(float(np.log(np.maximum(1.0 - v, 1e-300)).sum()) + num_fair * math.log(0.5)), 1.0)
+
+    def slope(lam):                                                         # derivative of the exponent in λ (increasing)
+        e = math.exp(lam)
+        return -observed + float((v * e / (1.0 - v + v * e)).sum()) + num_fair * e / (1.0 + e)
+    lo, hi = -50.0, 0.0
+    if slope(lo) >= 0:
+        lam = lo
+    else:
+        while hi - lo >= 1e-10:
+            mid = 0.5 * (lo + hi)
+            lo, hi = (lo, mid) if slope(mid) > 0 else (mid, hi)
+        lam = 0.5 * (lo + hi)
+    e = math.exp(lam)
+    return min(math.exp(-lam * observed + float(np.log(1.0 - v + v * e).sum()) + num_fair * math.log(0.5 * (1.0 + e))), 1.0)
+
+
+def gdp_order_statistics_p_value(num_canaries: int, guesses: int, errors: int, mu: float, grid_size: int = 10_000) -> float:
+    """P-value of "the mechanism is μ-GDP" given ``errors`` wrong guesses among ``guesses`` (Xiang et al. 2025, theorems 2–3;
+    reference: auditing/one_run/_gdp.py ``_p_value``)."""
+    if not math.isfinite(mu) or mu <= 0.0:
+        return 1.0
+    exact = min(int(guesses), MAX_EXACT_RANKS)
+    return bernoulli_sum_lower_tail(gdp_rank_error_probabilities(num_canaries, exact, mu, grid_size), int(guesses) - exact, int(errors))
+
+
+@dataclasses.dataclass(frozen=True)
+class GdpMethod:
+    """μ-GDP audit from ALL canaries at one threshold: the largest μ whose order-statistics p-value stays below
+    ``significance`` (bisection to 1 % of μ), and what μ-GDP at that level means as ε(δ), δ(ε), β(α) and advantage.
+    Assumes the audited mechanism is Gaussian-DP-like (DP-SGD and its relatives); :class:`EpsDeltaMethod` assumes nothing."""
+    estimate: "OneRunEstimate"
+    grid_size: int = 10_000
+
+    def mu_at(self, *, significance: float = 0.05, threshold: float | None = None) -> float:
+        EpsDeltaMethod._check(significance)
+        r, u = EpsDeltaMethod(self.estimate).guesses_and_errors(threshold)
+        m = self.estimate.n_in + self.estimate.n_out
+        hi = max(1.1 * -math.log(significance ** (-1.0 / max(m, 1)) - 1.0), 1.0)
+        for _ in range(60):
+            if gdp_order_statistics_p_value(m, r, u, hi, self.grid_size) >= significance:
+                break
+            hi *= 2.0
+        else:
+            raise RuntimeError(f"no finite mu explains {u} errors in {r} guesses at significance {significance}; "
+                               f"use fewer canaries or a larger significance")
+        lo = 0.0
+        for _ in range(100):
+            if hi - lo <= 0.01 * max(1.0, hi):
+                break
+            mid = 0.5 * (lo + hi)
+            lo, hi = (mid, hi) if gdp_order_statistics_p_value(m, r, u, mid, self.grid_size) < significance else (lo, mid)
+        return lo
+
+    def epsilon_at(self, *, delta: float, significance: float = 0.05, threshold: float | None = None) -> float:
+        if not 0 < delta <= 1:
+            raise ValueError(f"mu-GDP has no pure-epsilon form: delta must be in (0, 1], got {delta}")
+        return _gdp_epsilon(self.mu_at(significance=significance, threshold=threshold), delta)
+
+    def delta_at(self, *, epsilon: float, significance: float = 0.05, threshold: float | None = None) -> float:
+        if epsilon < 0:
+            raise ValueError(f"epsilon must be >= 0, got {epsilon}")
+        return max(0.0, _gdp_delta(self.mu_at(significance=significance, threshold=threshold), epsilon))
+
+    def beta_at(self, *, alpha: float, significance: float = 0.05, threshold: float | None = None) -> float:
+        """``Φ(Φ⁻¹(1 − α) − μ)``: the type-II error some attack reaches at false-positive rate ``alpha``."""
+        if not 0 <= alpha <= 1:
+            raise ValueError(f"alpha must be in [0, 1], got {alpha}")
+        return float(stats.norm.cdf(stats.norm.ppf(1.0 - alpha) - self.mu_at(significance=significance, threshold=threshold)))
+
+    def advantage(self, *, significance: float = 0.05, threshold: float | None = None) -> float:
+        """Total-variation advantage ``2Φ(μ/2) − 1``."""
+        return float(2.0 * stats.norm.cdf(self.mu_at(significance=significance, threshold=threshold) / 2.0) - 1.0)
+
+
 @dataclasses.dataclass(frozen=True)
 class OneRunEstimate:
     """Result of :func:`one_run`.  The fields are the guess-counting audit (Steinke et al. 2023) at the confidence and δ the
-    call was given; the methods answer the questions the reference's estimate object answers — at another δ or
-    significance level — by re-running that audit on the stored scores.  (The reference derives them from order statistics
-    of the scores, Xiang et al. 2025; the names and meanings agree, the estimators differ.)"""
+    call was given; ``epsilon_at`` / ``gdp_mu`` / ``delta_at`` / ``beta_at`` / ``advantage`` re-run that audit on the stored
+    scores at another δ or significance level.  ``eps_delta()`` and ``gdp()`` give the all-canaries order-statistics audits
+    (Xiang et al. 2025) that the reference's estimate object is built on, with the reference's numbers."""
     epsilon_lower_bound: float
     gdp_mu_lower_bound: float
     num_canaries: int
@@ -345,6 +523,26 @@ class OneRunEstimate:
         m = len(self.in_scores) + len(self.out_scores)
         flips = CoinFlip(np.arange(m), np.r_[np.ones(len(self.in_scores), bool), np.zeros(len(self.out_scores), bool)], m)
         return one_run(CanaryScores(np.r_[self.in_scores, self.out_scores]), coin_flip=flips, delta=delta, confidence=1.0 - significance)
+
+    def eps_delta(self) -> EpsDeltaMethod:
+        """The all-canaries (ε, δ) order-statistics audit on the stored scores; mechanism-agnostic."""
+        if self.in_scores is None or self.out_scores is None:
+            raise ValueError("this estimate carries no scores; build it with one_run()")
+        return EpsDeltaMethod(self)
+
+    def gdp(self, *, grid_size: int = 10_000) -> GdpMethod:
+        """The μ-GDP questions as one object (``mu_at``, ``epsilon_at``, ``delta_at``, ``beta_at``, ``advantage``)."""
+        if grid_size < 16:
+            raise ValueError(f"grid_size must be >= 16, got {grid_size}")
+        return GdpMethod(self, int(grid_size))
+
+    @property
+    def n_in(self) -> int:
+        return 0 if self.in_scores is None else len(self.in_scores)
+
+    @property
+    def n_out(self) -> int:
+        return 0 if self.out_scores is None else len(self.out_scores)
 
     def epsilon_at(self, *, delta: float, significance: float = 0.05, threshold: float | None = None) -> float:
         """Lower bound on ε at ``delta``, valid with probability ``1 − significance``."""
@@ -423,7 +621,8 @@ def one_run(scores: CanaryScores, *, coin_flip: CoinFlip, num_guesses: int | Non
                           np.asarray(coin_flip.canary_indices).copy())
 
 
-__all__ = ["CanaryScores", "CoinFlip", "OneRunEstimate", "auc", "canary_scores", "coin_flip", "epsilon_lower_bound",
+__all__ = ["CanaryScores", "CoinFlip", "EpsDeltaMethod", "GdpMethod", "OneRunEstimate", "auc", "bernoulli_sum_lower_tail",
+           "gdp_order_statistics_p_value", "gdp_rank_error_probabilities", "canary_scores", "coin_flip", "epsilon_lower_bound",
            "gdp_mu_lower_bound", "gradient_scores", "loss_scores", "one_run", "p_value_eps_delta", "roc_curve"]
 
 from .. import __version__  # noqa: E402

@@ -211,6 +211,28 @@ def main():
         worst = max(worst, float((runs[0] - runs[1]).abs().max()))
         spread = max(spread, float(runs[1].std()))
     out["mf_noise_realisation"], out["mf_noise_std"] = worst, spread
+    # ------------------------------------------------------------------ auditing: order-statistics audits on the same scores
+    import dataclasses
+    ra_, oa_ = both("auditing")
+    worst = 0.0
+    for shift in (0.5, 2.0, 6.0):
+        n = 200
+        ca, cb = ra_.coin_flip(list(range(n)), num_canaries=n, key=rr.key(5)), oa_.coin_flip(list(range(n)), num_canaries=n, key=ro.key(5))
+        member = np.zeros(n, bool)
+        member[np.asarray(ca.in_indices)] = True
+        values = np.where(member, shift, 0.0) + np.random.default_rng(1).normal(size=n)
+        ea = ra_.one_run(ra_.canary_scores(values[np.asarray(ca.canary_indices)], canary_indices=ca.canary_indices), coin_flip=ca)
+        eb = oa_.one_run(oa_.canary_scores(values[np.asarray(cb.canary_indices)], canary_indices=cb.canary_indices), coin_flip=cb)
+        eb = dataclasses.replace(eb, in_scores=np.asarray(ea.in_scores), out_scores=np.asarray(ea.out_scores))   # the same split on both sides
+        for d in (0.0, 1e-5, 0.05):
+            worst = max(worst, abs(ea.eps_delta().epsilon_at(delta=d) - eb.eps_delta().epsilon_at(delta=d)),
+                        abs(ea.eps_delta().epsilon_at(delta=d, threshold=shift / 2) - eb.eps_delta().epsilon_at(delta=d, threshold=shift / 2)))
+        worst = max(worst, abs(ea.eps_delta().delta_at(epsilon=0.5) - eb.eps_delta().delta_at(epsilon=0.5)),
+                    abs(ea.gdp(grid_size=2000).epsilon_at(delta=1e-5) - eb.gdp(grid_size=2000).epsilon_at(delta=1e-5)),
+                    abs(ea.gdp(grid_size=2000).delta_at(epsilon=1.0) - eb.gdp(grid_size=2000).delta_at(epsilon=1.0)),
+                    abs(ea.gdp(grid_size=2000).beta_at(alpha=0.1) - eb.gdp(grid_size=2000).beta_at(alpha=0.1)),
+                    abs(ea.gdp(grid_size=2000).advantage() - eb.gdp(grid_size=2000).advantage()))
+    out["order_statistics_audits"] = worst
     out["signature_checked"] = len(inspect.signature(ref.sigmoid_loss).parameters)
     print(json.dumps(out))
 

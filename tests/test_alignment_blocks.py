@@ -284,3 +284,53 @@ def test_audit_estimate_answers_the_reference_questions():
     assert betas[0] >= betas[1] >= betas[2] == 0.0 and est.attack_beta_at(alpha=0.1) == betas[1]
     noise_only = auditing.one_run(auditing.canary_scores(np.random.default_rng(1).normal(size=200)), coin_flip=flips, delta=1e-5)
     assert noise_only.epsilon_at(delta=1e-5) == 0.0 and abs(noise_only.attack_auc() - 0.5) < 0.1 and noise_only.advantage() < 0.2
+
+
+def test_order_statistics_audits_on_one_estimate():
+    """``eps_delta()``: exact Binomial test on all canaries; ``gdp()``: the μ-GDP order-statistics test.  A strong attack
+    certifies more than a weak one, more δ certifies less ε, μ-GDP certifies more than the assumption-free test, and the
+    pieces (rank error probabilities, Chernoff tail) behave as their definitions say."""
+    import dataclasses
+
+    import numpy as np
+    from scipy import stats
+
+    from opaque_b200 import auditing as A
+    from opaque_b200.random import key
+    rng = np.random.default_rng(0)
+    def estimate(shift, n=300):
+        flips = A.coin_flip(list(range(n)), num_canaries=n, key=key(3))
+        member = np.zeros(n, bool)
+        member[np.asarray(flips.in_indices)] = True
+        values = np.where(member, shift, 0.0) + rng.normal(size=n)
+        ids = np.asarray(flips.canary_indices)
+        return A.one_run(A.canary_scores(values[ids], canary_indices=ids), coin_flip=flips)
+    weak, strong = estimate(0.5), estimate(3.0)
+    ed = strong.eps_delta()
+    r, u = ed.guesses_and_errors()
+    assert r == 300 and u == min(ed.guesses_and_errors(t)[1] for t in np.r_[strong.in_scores, strong.out_scores])
+    assert ed.epsilon_at() > weak.eps_delta().epsilon_at() >= 0.0
+    assert ed.epsilon_at(delta=0.0) >= ed.epsilon_at(delta=0.1) and ed.epsilon_at(threshold=1.5) <= ed.epsilon_at() + 1e-9
+    eps = ed.epsilon_at()
+    assert ed.p_value(r, u, eps - 1e-3, 0.0) < 0.05 <= ed.p_value(r, u, eps + 1e-3, 0.0)
+    assert ed.delta_at(epsilon=eps + 1.0) == 0.0 and ed.delta_at(epsilon=0.1) > 0.0
+    g = strong.gdp()
+    mu = g.mu_at()
+    assert 1.5 < mu < 3.5 and weak.gdp().mu_at() < mu                      # the canaries are 3 standard deviations apart
+    assert g.epsilon_at(delta=1e-5) > ed.epsilon_at(delta=1e-5)
+    assert g.delta_at(epsilon=g.epsilon_at(delta=1e-3)) == pytest.approx(1e-3, rel=1e-3)
+    assert 0 < g.beta_at(alpha=0.1) < 0.9 and 0 < g.advantage() < 1
+    with pytest.raises(ValueError):
+        g.epsilon_at(delta=0.0)
+    with pytest.raises(ValueError):
+        strong.gdp(grid_size=4)
+    with pytest.raises(ValueError):
+        dataclasses.replace(strong, in_scores=None).eps_delta()
+    v = A.gdp_rank_error_probabilities(50, 50, 1.0)
+    assert v.shape == (50,) and np.all(np.diff(v) <= 1e-12) and 0 < v[-1] < v[0] <= 0.5   # larger |loss| rank, fewer errors
+    assert A.gdp_rank_error_probabilities(50, 50, 1e-6)[0] == pytest.approx(0.5, abs=1e-4)
+    assert A.bernoulli_sum_lower_tail(np.full(40, 0.5), 0, 25) == 1.0
+    exact = float(stats.binom.cdf(5, 40, 0.5))
+    assert exact <= A.bernoulli_sum_lower_tail(np.full(40, 0.5), 0, 5) < 50 * exact            # a bound, and not a wild one
+    assert A.bernoulli_sum_lower_tail(np.full(10, 0.5), 10, 0) == pytest.approx(0.5 ** 20)
+    assert A.gdp_order_statistics_p_value(100, 100, 10, 0.0) == 1.0

@@ -1,7 +1,7 @@
 """Numerical parity with the UNMODIFIED reference on the CPU, when it is installed (``baseline/install_reference.sh`` puts it
 into ``baseline/_ref``): same key derivation, schedules, clipped gradients, even the same noise realisation and the same
 Poisson / random-allocation / balls-in-bins draws; band-MF coefficients and the correlated-noise
-realisations of four matrix-factorisation strategies; twelve optimizer configurations, automatic / adaptive / second-moment clipping, every
+realisations of four matrix-factorisation strategies; the (ε, δ) and μ-GDP order-statistics audits; twelve optimizer configurations, automatic / adaptive / second-moment clipping, every
 preference-loss piece, the factory collators and the shift-inside SFT losses to rounding."""
 import json
 import os
@@ -28,4 +28,5 @@ def test_building_blocks_equal_the_reference():
     # band-MF coefficients from the same objective; identity / band-MF / BSR / λ-CGD noise: the same realisation and published std
     assert d["band_mf_coefficients"] < 1e-6 and d["bsr_sensitivity"] < 1e-9, d
     assert d["mf_noise_realisation"] < 1e-5 and d["mf_noise_std"] > 0.1, d
+    assert d["order_statistics_audits"] < 1e-8, d              # eps_delta() and gdp() of the estimate on the same scores
     assert d["preference_losses"] < 1e-5 and d["collators_equal"] and d["sft_losses_and_metrics"] < 1e-5, d

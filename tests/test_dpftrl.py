@@ -87,6 +87,20 @@ def test_band_mf_objective_momentum_and_learning_rate_weights():
     assert math.isclose(N.toeplitz_workload_error(base, n, kind="max"), N.prefix_workload_error(N.inverse_coef(base, n)), rel_tol=1e-9)
 
 
+def test_lambda_cgd_draws_use_the_unlabelled_step_key():
+    """λ-CGD draws ``z_t`` from ``fold_in(key, t)``; the other strategies label the step key ``"mf_gaussian_column"``."""
+    from opaque_b200.dpftrl import lambda_cgd_strategy
+    from opaque_b200.random import fold_in
+    k = key(9)
+    def first(strategy):
+        nf, st = mf_gaussian_noise({"w": torch.zeros(5)}, strategy, n_steps=4, noise_multiplier=1.0, key=k)
+        return nf(clipped({"w": torch.zeros(5)}, 1.0), st)[0].pytree["w"]
+    z_plain = N._iid_normal_like({"w": torch.zeros(5)}, 1.0, fold_in(k, 0), torch.float32)["w"]
+    z_label = N._iid_normal_like({"w": torch.zeros(5)}, 1.0, fold_in(k, "mf_gaussian_column", 0), torch.float32)["w"]
+    assert torch.allclose(first(lambda_cgd_strategy(lambda_=0.5, normalized=False)), z_plain)
+    assert torch.allclose(first(identity_strategy()), z_label) and not torch.allclose(z_plain, z_label)
+
+
 def test_mf_noise_statistics_horizon_and_constant_norm():
     s = blt_strategy(max_buffers=2)
     nf, st = mf_gaussian_noise({"w": torch.zeros(50_000)}, s, n_steps=3, noise_multiplier=2.0, key=key(1))
